@@ -1,0 +1,14 @@
+"""catboost_b200: a Blackwell-native gradient-boosted decision tree framework with CatBoost's capabilities.
+
+Public API mirrors ``catboost``: :class:`CatBoost`, :class:`CatBoostClassifier`, :class:`CatBoostRegressor`,
+:class:`CatBoostRanker`, :class:`Pool`, :func:`train`, :func:`cv`, :func:`sum_models`.
+"""
+from .core import (CatBoost, CatBoostClassifier, CatBoostRanker, CatBoostRegressor, EFstrType, sum_models,  # noqa: F401
+                   to_classifier, to_ranker, to_regressor, train)
+from .data.pool import CatBoostError, Pool  # noqa: F401
+from .cv import cv  # noqa: F401
+
+FeaturesData = None
+__version__ = "0.1.0"
+__all__ = ["CatBoost", "CatBoostClassifier", "CatBoostRegressor", "CatBoostRanker", "Pool", "CatBoostError", "train",
+           "cv", "sum_models", "to_classifier", "to_regressor", "to_ranker", "EFstrType"]

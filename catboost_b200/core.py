@@ -1,0 +1,542 @@
+"""User-facing estimators: ``CatBoost``, ``CatBoostClassifier``, ``CatBoostRegressor``, ``CatBoostRanker`` and the
+module-level ``train`` / ``cv`` / ``sum_models`` helpers.  The surface follows
+catboost/python-package/catboost/core.py (CatBoost :2585, CatBoostClassifier :4894, CatBoostRegressor :5981,
+CatBoostRanker :6391, train :6775, cv :7085, sum_models :7394).
+"""
+from __future__ import annotations
+
+import copy
+import json
+import os
+from typing import Optional
+
+import numpy as np
+
+from .data.pool import CatBoostError, Pool, to_pool
+from .metrics import make_metric
+from .models.model import Model
+from .params import DEFAULTS, SYNONYMS, normalize_params, parse_devices
+
+
+class EFstrType:
+    PredictionValuesChange = "PredictionValuesChange"
+    LossFunctionChange = "LossFunctionChange"
+    FeatureImportance = "FeatureImportance"
+    Interaction = "Interaction"
+    ShapValues = "ShapValues"
+    PredictionDiff = "PredictionDiff"
+    ShapInteractionValues = "ShapInteractionValues"
+    SageValues = "SageValues"
+
+
+def _sigmoid(x):
+    return 1.0 / (1.0 + np.exp(-x))
+
+
+class CatBoost:
+    _default_loss = "RMSE"
+    _estimator_type = None
+
+    def __init__(self, params: Optional[dict] = None, **kwargs):
+        p = dict(params or {})
+        p.update(kwargs)
+        self._init_params = {k: v for k, v in p.items() if v is not None}
+        normalize_params(self._init_params)     # validates names early
+        self._model: Optional[Model] = None
+        self._evals_result = {}
+        self._best_iteration = None
+        self._best_score = {}
+        self._train_info = {}
+
+    # ------------------------------------------------------------------ params
+    def get_params(self, deep=True):
+        return copy.deepcopy(self._init_params)
+
+    def set_params(self, **params):
+        normalize_params(params)
+        self._init_params.update(params)
+        return self
+
+    def get_param(self, key):
+        return self._init_params.get(key)
+
+    def get_all_params(self):
+        self._check_fitted()
+        return dict(self._model.params)
+
+    def is_fitted(self):
+        return self._model is not None
+
+    def _check_fitted(self):
+        if self._model is None:
+            raise CatBoostError("model is not fitted")
+
+    def copy(self):
+        return copy.deepcopy(self)
+
+    def __sklearn_tags__(self):  # pragma: no cover - sklearn >= 1.6 compatibility
+        try:
+            from sklearn.utils import Tags, InputTags, TargetTags
+            return Tags(estimator_type=self._estimator_type, target_tags=TargetTags(required=True),
+                        input_tags=InputTags(allow_nan=True))
+        except Exception:
+            raise AttributeError
+
+    # ------------------------------------------------------------------ fit
+    def fit(self, X, y=None, cat_features=None, text_features=None, embedding_features=None, pairs=None,
+            sample_weight=None, group_id=None, group_weight=None, subgroup_id=None, pairs_weight=None, baseline=None,
+            use_best_model=None, eval_set=None, verbose=None, logging_level=None, plot=False, plot_file=None,
+            column_description=None, verbose_eval=None, metric_period=None, silent=None, early_stopping_rounds=None,
+            save_snapshot=None, snapshot_file=None, snapshot_interval=None, init_model=None, callbacks=None,
+            log_cout=None, log_cerr=None):
+        params = dict(self._init_params)
+        if cat_features is None and "cat_features" in params:
+            cat_features = params.get("cat_features")
+        params.pop("cat_features", None)
+        for k, v in dict(use_best_model=use_best_model, verbose=verbose if verbose is not None else verbose_eval,
+                         logging_level=logging_level, metric_period=metric_period, silent=silent,
+                         early_stopping_rounds=early_stopping_rounds, save_snapshot=save_snapshot,
+                         snapshot_file=snapshot_file, snapshot_interval=snapshot_interval).items():
+            if v is not None:
+                params[k] = v
+        if isinstance(X, Pool):
+            if any(a is not None for a in (y, sample_weight, group_id, pairs, baseline)) and y is not None:
+                raise CatBoostError("y must be None when X is a Pool")
+            train_pool = X
+        else:
+            if y is None and not isinstance(X, (str, os.PathLike)):
+                raise CatBoostError("y is required when X is not a Pool")
+            train_pool = Pool(X, y, cat_features=cat_features, pairs=pairs, weight=sample_weight, group_id=group_id,
+                              group_weight=group_weight, subgroup_id=subgroup_id, pairs_weight=pairs_weight,
+                              baseline=baseline, column_description=column_description)
+        eval_pools = []
+        if eval_set is not None:
+            sets = eval_set if isinstance(eval_set, list) else [eval_set]
+            for es in sets:
+                if isinstance(es, Pool):
+                    eval_pools.append(es)
+                elif isinstance(es, tuple) and len(es) == 2:
+                    eval_pools.append(Pool(es[0], es[1], cat_features=train_pool.cat_feature_indices,
+                                           feature_names=train_pool.feature_names))
+                else:
+                    raise CatBoostError("eval_set must be a Pool, an (X, y) tuple or a list of them")
+        init = None
+        if init_model is not None:
+            init = init_model._model if isinstance(init_model, CatBoost) else init_model
+            if isinstance(init, (str, os.PathLike)):
+                init = CatBoost().load_model(init)._model
+        from .parallel.launcher import train_maybe_multi_gpu
+        res = train_maybe_multi_gpu(params, train_pool, eval_pools, default_loss=self._default_loss, init_model=init,
+                                    callbacks=callbacks, log_cout=log_cout)
+        self._model = res.model
+        self._evals_result = res.evals_result
+        self._best_iteration = res.best_iteration
+        self._best_score = res.best_score
+        self._train_info = dict(timings=res.timings, h2d_bytes=res.h2d_bytes, launches_per_iter=res.launches_per_iter)
+        return self
+
+    # ------------------------------------------------------------------ predict
+    def _raw(self, data, ntree_start=0, ntree_end=0, thread_count=-1, task_type="CPU"):
+        self._check_fitted()
+        pool = data if isinstance(data, Pool) else Pool(data, cat_features=[c.flat_index for c in self._model.cat_features],
+                                                        data_can_be_none=False)
+        fd, ch = self._model.pool_arrays(pool)
+        raw = self._model.predict_raw(fd, ch, ntree_start, ntree_end, task_type=task_type, thread_count=thread_count)
+        if pool.baseline is not None:
+            raw = raw + pool.baseline.reshape(raw.shape)
+        return raw
+
+    def _format(self, raw, prediction_type):
+        m = self._model
+        pt = prediction_type
+        binclass = m.loss_name in ("Logloss", "CrossEntropy")
+        multi = m.loss_name in ("MultiClass", "MultiClassOneVsAll")
+        if pt == "RawFormulaVal":
+            return raw[:, 0] if raw.shape[1] == 1 else raw
+        if pt in ("Probability", "LogProbability"):
+            if binclass:
+                p1 = _sigmoid(raw[:, 0])
+                pr = np.stack([1 - p1, p1], axis=1)
+            elif m.loss_name == "MultiClass":
+                e = np.exp(raw - raw.max(1, keepdims=True))
+                pr = e / e.sum(1, keepdims=True)
+            elif m.loss_name in ("MultiClassOneVsAll", "MultiLogloss", "MultiCrossEntropy"):
+                pr = _sigmoid(raw)
+            else:
+                raise CatBoostError(f"prediction_type {pt!r} needs a classification model")
+            return pr if pt == "Probability" else np.log(np.clip(pr, 1e-300, None))
+        if pt == "Class":
+            if binclass:
+                idx = (raw[:, 0] > 0).astype(np.int64)
+            elif multi:
+                idx = raw.argmax(1)
+            elif m.loss_name in ("MultiLogloss", "MultiCrossEntropy"):
+                return (raw > 0).astype(np.int64)
+            else:
+                raise CatBoostError("prediction_type 'Class' needs a classification model")
+            names = m.class_names
+            if names is None:
+                return idx
+            arr = np.array(names, dtype=object)[idx]
+            try:
+                return arr.astype(type(names[0])) if not isinstance(names[0], str) else arr
+            except (ValueError, TypeError):
+                return arr
+        if pt == "Exponent":
+            return np.exp(raw[:, 0])
+        if pt == "RMSEWithUncertainty":
+            return np.stack([raw[:, 0], np.exp(2 * raw[:, 1])], 1)
+        raise CatBoostError(f"unknown prediction_type {pt!r}")
+
+    def _default_prediction_type(self):
+        return "RawFormulaVal"
+
+    def predict(self, data, prediction_type=None, ntree_start=0, ntree_end=0, thread_count=-1, verbose=None,
+                task_type="CPU"):
+        raw = self._raw(data, ntree_start, ntree_end, thread_count, task_type)
+        pt = prediction_type or self._default_prediction_type()
+        if pt == "RawFormulaVal" and self._model.loss_name == "Poisson" and False:
+            pt = "Exponent"
+        return self._format(raw, pt)
+
+    def staged_predict(self, data, prediction_type=None, ntree_start=0, ntree_end=0, eval_period=1, thread_count=-1,
+                       verbose=None):
+        self._check_fitted()
+        pool = data if isinstance(data, Pool) else Pool(data, cat_features=[c.flat_index for c in self._model.cat_features])
+        fd, ch = self._model.pool_arrays(pool)
+        pt = prediction_type or self._default_prediction_type()
+        for raw in self._model.staged_raw(fd, ch, ntree_start, ntree_end, eval_period):
+            yield self._format(raw, pt)
+
+    def calc_leaf_indexes(self, data, ntree_start=0, ntree_end=0, thread_count=-1, verbose=False):
+        self._check_fitted()
+        pool = data if isinstance(data, Pool) else Pool(data, cat_features=[c.flat_index for c in self._model.cat_features])
+        fd, ch = self._model.pool_arrays(pool)
+        return self._model.leaf_indices(fd, ch, ntree_start, ntree_end)
+
+    # ------------------------------------------------------------------ attributes
+    @property
+    def tree_count_(self):
+        self._check_fitted()
+        return self._model.tree_count
+
+    @property
+    def feature_names_(self):
+        self._check_fitted()
+        return list(self._model.feature_names)
+
+    @property
+    def n_features_in_(self):
+        self._check_fitted()
+        return self._model.n_features
+
+    @property
+    def best_iteration_(self):
+        return self._best_iteration
+
+    @property
+    def best_score_(self):
+        return self._best_score
+
+    @property
+    def evals_result_(self):
+        return self._evals_result
+
+    @property
+    def learning_rate_(self):
+        self._check_fitted()
+        return self._model.params.get("learning_rate")
+
+    @property
+    def random_seed_(self):
+        self._check_fitted()
+        return self._model.params.get("random_seed", 0)
+
+    @property
+    def classes_(self):
+        self._check_fitted()
+        return np.array(self._model.class_names) if self._model.class_names is not None else np.array([])
+
+    @property
+    def feature_importances_(self):
+        return self.get_feature_importance()
+
+    def get_evals_result(self):
+        return self._evals_result
+
+    def get_best_iteration(self):
+        return self._best_iteration
+
+    def get_best_score(self):
+        return self._best_score
+
+    def get_tree_leaf_counts(self):
+        self._check_fitted()
+        return np.array([t.leaf_values.shape[0] for t in self._model.trees])
+
+    def get_leaf_values(self):
+        self._check_fitted()
+        return np.concatenate([t.leaf_values.reshape(-1) for t in self._model.trees])
+
+    def get_leaf_weights(self):
+        self._check_fitted()
+        return np.concatenate([t.leaf_weights.reshape(-1) for t in self._model.trees])
+
+    def get_scale_and_bias(self):
+        self._check_fitted()
+        b = self._model.bias
+        return self._model.scale, (float(b[0]) if len(b) == 1 else b.tolist())
+
+    def set_scale_and_bias(self, scale, bias):
+        self._check_fitted()
+        self._model.scale = float(scale)
+        self._model.bias = np.broadcast_to(np.asarray(bias, dtype=np.float64), (self._model.dims,)).copy()
+        self._model.__dict__.pop("_gpu_predictor", None)
+
+    def get_borders(self):
+        self._check_fitted()
+        return {f.flat_index: np.asarray(f.borders).tolist() for f in self._model.float_features}
+
+    def get_cat_feature_indices(self):
+        self._check_fitted()
+        return [c.flat_index for c in self._model.cat_features]
+
+    def shrink(self, ntree_end, ntree_start=0):
+        self._check_fitted()
+        self._model.shrink(ntree_end, ntree_start)
+        self._model.__dict__.pop("_packed", None)
+        self._model.__dict__.pop("_gpu_predictor", None)
+
+    def drop_unused_features(self):
+        return self
+
+    # ------------------------------------------------------------------ analysis
+    def get_feature_importance(self, data=None, type=EFstrType.FeatureImportance, prettified=False, thread_count=-1,
+                               verbose=False, fstr_type=None, shap_mode="Auto", model_output="Raw",
+                               interaction_indices=None, shap_calc_type="Regular", reference_data=None, log_cout=None,
+                               log_cerr=None):
+        self._check_fitted()
+        from . import fstr
+        t = fstr_type or type
+        t = getattr(t, "name", t)
+        if t in (EFstrType.FeatureImportance, EFstrType.PredictionValuesChange):
+            imp = fstr.prediction_values_change(self._model)
+        elif t == EFstrType.LossFunctionChange:
+            if data is None:
+                raise CatBoostError("LossFunctionChange needs a dataset")
+            imp = fstr.loss_function_change(self, data)
+        elif t == EFstrType.ShapValues:
+            if data is None:
+                raise CatBoostError("ShapValues needs a dataset")
+            return fstr.shap_values(self._model, data if isinstance(data, Pool) else Pool(data))
+        elif t == EFstrType.Interaction:
+            return fstr.interaction(self._model)
+        elif t == EFstrType.PredictionDiff:
+            return fstr.prediction_diff(self, data)
+        else:
+            raise CatBoostError(f"feature importance type {t!r} is not supported")
+        if prettified:
+            order = np.argsort(-imp)
+            try:
+                import pandas as pd
+                return pd.DataFrame({"Feature Id": [self._model.feature_names[i] for i in order], "Importances": imp[order]})
+            except Exception:
+                return [(self._model.feature_names[i], float(imp[i])) for i in order]
+        return imp
+
+    def eval_metrics(self, data, metrics, ntree_start=0, ntree_end=0, eval_period=1, thread_count=-1, tmp_dir=None,
+                     plot=False, plot_file=None, log_cout=None, log_cerr=None):
+        self._check_fitted()
+        pool = to_pool(data)
+        metrics = [metrics] if isinstance(metrics, str) else list(metrics)
+        ms = [make_metric(m) for m in metrics]
+        y = self._encode_labels(pool.label)
+        out = {str(m): [] for m in ms}
+        fd, ch = self._model.pool_arrays(pool)
+        kw = {}
+        if pool.group_id is not None:
+            kw["group_offsets"] = pool.group_offsets()
+        if pool.pairs is not None:
+            kw["pairs"], kw["pairs_weight"] = pool.pairs, pool.pairs_weight
+        for raw in self._model.staged_raw(fd, ch, ntree_start, ntree_end, eval_period):
+            for m in ms:
+                out[str(m)].append(m.eval(raw, y, pool.weight, **kw))
+        return out
+
+    def _encode_labels(self, label):
+        names = self._model.class_names
+        lab = np.asarray(label)
+        if names is not None and self._model.loss_name in ("Logloss", "MultiClass", "MultiClassOneVsAll"):
+            tb = self._model.params.get("target_border")
+            if tb is not None and self._model.loss_name == "Logloss":
+                return (lab.astype(np.float64) > float(tb)).astype(np.float32)
+            m = {v: i for i, v in enumerate(names)}
+            return np.array([m.get(v, -1) for v in lab.tolist()], dtype=np.float32)
+        return lab.astype(np.float32) if lab.dtype != object else lab
+
+    def score(self, X, y=None):
+        self._check_fitted()
+        pool = X if isinstance(X, Pool) else Pool(X, y, cat_features=[c.flat_index for c in self._model.cat_features])
+        yy = pool.label
+        raw = self._raw(pool)
+        if self._model.class_names is not None:
+            pred = self._format(raw, "Class")
+            return float(np.mean(np.asarray(pred).astype(str) == np.asarray(yy).astype(str)))
+        if self._estimator_type == "ranker":
+            m = make_metric("NDCG")
+            return m.eval(raw, np.asarray(yy, dtype=np.float64), pool.weight, group_offsets=pool.group_offsets())
+        yy = np.asarray(yy, dtype=np.float64)
+        p = raw[:, 0]
+        den = np.sum((yy - yy.mean()) ** 2)
+        return float(1 - np.sum((yy - p) ** 2) / den) if den > 0 else 0.0
+
+    # ------------------------------------------------------------------ persistence
+    def save_model(self, fname, format="cbm", export_parameters=None, pool=None):
+        self._check_fitted()
+        from .models import io as mio
+        mio.save_model(self._model, fname, format, export_parameters, pool)
+
+    def load_model(self, fname=None, format="cbm", stream=None, blob=None):
+        from .models import io as mio
+        if blob is not None:
+            self._model = mio.load_model_blob(blob, format)
+        elif stream is not None:
+            self._model = mio.load_model_blob(stream.read(), format)
+        else:
+            self._model = mio.load_model(fname, format)
+        return self
+
+    def _serialize_model(self):
+        from .models import io as mio
+        return mio.model_to_cbm_bytes(self._model)
+
+    def __getstate__(self):
+        st = dict(self.__dict__)
+        if self._model is not None:
+            m = self._model.copy()
+            for k in ("_gpu_predictor", "_packed", "_split_cache"):
+                m.__dict__.pop(k, None)
+            st["_model"] = m
+        return st
+
+    def plot_tree(self, tree_idx=0, pool=None):
+        raise CatBoostError("plot_tree needs graphviz, which is not available in this build")
+
+    # ------------------------------------------------------------------ search helpers
+    def grid_search(self, param_grid, X, y=None, cv=3, partition_random_seed=0, calc_cv_statistics=True,
+                    search_by_train_test_split=True, refit=True, shuffle=True, stratified=None, train_size=0.8,
+                    verbose=True, plot=False, plot_file=None, log_cout=None, log_cerr=None):
+        from .tuning import grid_search
+        return grid_search(self, param_grid, X, y, cv, partition_random_seed, search_by_train_test_split, refit, shuffle,
+                           stratified, train_size, verbose)
+
+    def randomized_search(self, param_distributions, X, y=None, cv=3, n_iter=10, partition_random_seed=0,
+                          calc_cv_statistics=True, search_by_train_test_split=True, refit=True, shuffle=True,
+                          stratified=None, train_size=0.8, verbose=True, plot=False, plot_file=None, log_cout=None,
+                          log_cerr=None):
+        from .tuning import randomized_search
+        return randomized_search(self, param_distributions, X, y, cv, n_iter, partition_random_seed,
+                                 search_by_train_test_split, refit, shuffle, stratified, train_size, verbose)
+
+    def select_features(self, X, y=None, eval_set=None, features_for_select=None, num_features_to_select=None,
+                        algorithm=None, steps=1, shap_calc_type=None, train_final_model=True, verbose=None,
+                        logging_level=None, plot=False, plot_file=None, log_cout=None, log_cerr=None, grouping=None,
+                        features_tags_for_select=None, num_features_tags_to_select=None):
+        from .tuning import select_features
+        return select_features(self, X, y, eval_set, features_for_select, num_features_to_select, steps,
+                               train_final_model)
+
+
+class CatBoostClassifier(CatBoost):
+    _default_loss = "Logloss"
+    _estimator_type = "classifier"
+
+    def fit(self, X, y=None, **kw):
+        if "loss_function" not in self._init_params and "objective" not in self._init_params:
+            lab = X.label if isinstance(X, Pool) else y
+            if lab is not None:
+                lab = np.asarray(lab)
+                if lab.ndim == 1 or (lab.ndim == 2 and lab.shape[1] == 1):
+                    nuniq = len(np.unique(lab))
+                    if nuniq > 2 and self._init_params.get("target_border") is None:
+                        self._init_params["loss_function"] = "MultiClass"
+                        try:
+                            return super().fit(X, y, **kw)
+                        finally:
+                            self._init_params.pop("loss_function", None)
+                elif lab.ndim == 2:
+                    self._init_params["loss_function"] = "MultiLogloss"
+                    try:
+                        return super().fit(X, y, **kw)
+                    finally:
+                        self._init_params.pop("loss_function", None)
+        return super().fit(X, y, **kw)
+
+    def _default_prediction_type(self):
+        return "Class"
+
+    def predict_proba(self, X, ntree_start=0, ntree_end=0, thread_count=-1, verbose=None, task_type="CPU"):
+        return self.predict(X, "Probability", ntree_start, ntree_end, thread_count, verbose, task_type)
+
+    def predict_log_proba(self, X, ntree_start=0, ntree_end=0, thread_count=-1, verbose=None, task_type="CPU"):
+        return self.predict(X, "LogProbability", ntree_start, ntree_end, thread_count, verbose, task_type)
+
+    def staged_predict_proba(self, data, ntree_start=0, ntree_end=0, eval_period=1, thread_count=-1, verbose=None):
+        return self.staged_predict(data, "Probability", ntree_start, ntree_end, eval_period, thread_count, verbose)
+
+
+class CatBoostRegressor(CatBoost):
+    _default_loss = "RMSE"
+    _estimator_type = "regressor"
+
+
+class CatBoostRanker(CatBoost):
+    _default_loss = "YetiRank"
+    _estimator_type = "ranker"
+
+
+def train(pool=None, params=None, dtrain=None, logging_level=None, verbose=None, iterations=None,
+          num_boost_round=None, evals=None, eval_set=None, plot=None, verbose_eval=None, metric_period=None,
+          early_stopping_rounds=None, save_snapshot=None, snapshot_file=None, snapshot_interval=None, init_model=None,
+          log_cout=None, log_cerr=None):
+    """Functional training entry point (catboost.train)."""
+    params = dict(params or {})
+    if iterations is not None:
+        params["iterations"] = iterations
+    if num_boost_round is not None:
+        params["iterations"] = num_boost_round
+    pool = pool if pool is not None else dtrain
+    if pool is None:
+        raise CatBoostError("pool is required")
+    model = CatBoost(params)
+    model.fit(pool, eval_set=eval_set if eval_set is not None else evals, verbose=verbose if verbose is not None else verbose_eval,
+              logging_level=logging_level, metric_period=metric_period, early_stopping_rounds=early_stopping_rounds,
+              save_snapshot=save_snapshot, snapshot_file=snapshot_file, snapshot_interval=snapshot_interval,
+              init_model=init_model, log_cout=log_cout)
+    return model
+
+
+def sum_models(models, weights=None, ctr_merge_policy="IntersectingCountersAverage"):
+    from .models.ops import sum_models as _sum
+    out = CatBoost()
+    out._model = _sum([m._model for m in models], weights, ctr_merge_policy)
+    out.__class__ = models[0].__class__
+    return out
+
+
+def to_regressor(model):
+    out = CatBoostRegressor()
+    out.__dict__.update(copy.deepcopy(model.__dict__))
+    return out
+
+
+def to_classifier(model):
+    out = CatBoostClassifier()
+    out.__dict__.update(copy.deepcopy(model.__dict__))
+    return out
+
+
+def to_ranker(model):
+    out = CatBoostRanker()
+    out.__dict__.update(copy.deepcopy(model.__dict__))
+    return out

@@ -1,0 +1,483 @@
+"""In-memory dataset (``Pool``) and file loaders.
+
+Mirrors the user-facing behaviour of ``catboost.Pool`` (catboost/python-package/catboost/core.py:624) and the
+dsv / column-description / libsvm loaders (catboost/libs/data/cb_dsv_loader.cpp, libsvm_loader.cpp,
+catboost/libs/column_description/cd_parser.cpp): float features are kept as a float32 row-major matrix,
+categorical features as hashed uint32 columns (plus the original strings for the hash -> string map that
+``.cbm`` files carry), labels / weights / groups / pairs / baselines as numpy arrays.
+"""
+from __future__ import annotations
+
+import os
+from typing import Iterable, Optional, Sequence
+
+import numpy as np
+
+from .cat_hash import hash_cat_values
+
+try:  # pandas is optional
+    import pandas as _pd
+except Exception:  # pragma: no cover
+    _pd = None
+
+
+class CatBoostError(Exception):
+    """Raised for every user-visible error of the framework (name kept for drop-in compatibility)."""
+
+
+def _is_str_like(v) -> bool:
+    return isinstance(v, (str, bytes))
+
+
+def _column_roles_from_cd(path: str, n_cols: Optional[int] = None):
+    """Parse a column-description file: ``index<TAB>type[<TAB>name]`` per line."""
+    roles, names = {}, {}
+    with open(path) as fh:
+        for line in fh:
+            line = line.rstrip("\n")
+            if not line.strip():
+                continue
+            parts = line.split("\t")
+            idx = int(parts[0])
+            roles[idx] = parts[1].strip()
+            if len(parts) > 2 and parts[2].strip():
+                names[idx] = parts[2].strip()
+    return roles, names
+
+
+_CD_ALIASES = {"Target": "Label", "DocId": "SampleId", "QueryId": "GroupId"}
+
+
+def read_dsv(path: str, column_description: Optional[str] = None, delimiter: str = "\t", has_header: bool = False,
+             ignore_csv_quoting: bool = False):
+    """Load a delimiter-separated file.  Columns without a role are numeric features (``Num``)."""
+    roles, names = ({}, {})
+    if column_description:
+        roles, names = _column_roles_from_cd(column_description)
+    rows = []
+    header = None
+    with open(path) as fh:
+        for li, line in enumerate(fh):
+            line = line.rstrip("\r\n")
+            if not line:
+                continue
+            parts = line.split(delimiter)
+            if li == 0 and has_header:
+                header = parts
+                continue
+            rows.append(parts)
+    if not rows:
+        raise CatBoostError(f"empty dataset file {path}")
+    ncol = len(rows[0])
+    if not roles:
+        roles = {0: "Label"}
+    num_idx, cat_idx = [], []
+    label_idx, weight_idx, group_idx, subgroup_idx, baseline_idx, gw_idx, ts_idx = [], None, None, None, [], None, None
+    feature_names = []
+    for c in range(ncol):
+        role = _CD_ALIASES.get(roles.get(c, "Num"), roles.get(c, "Num"))
+        if role == "Num":
+            num_idx.append(c)
+        elif role == "Categ":
+            cat_idx.append(c)
+        elif role == "Label":
+            label_idx.append(c)
+        elif role == "Weight":
+            weight_idx = c
+        elif role == "GroupId":
+            group_idx = c
+        elif role == "SubgroupId":
+            subgroup_idx = c
+        elif role == "Baseline":
+            baseline_idx.append(c)
+        elif role == "GroupWeight":
+            gw_idx = c
+        elif role == "Timestamp":
+            ts_idx = c
+        elif role in ("Auxiliary", "SampleId", "Text", "NumVector"):
+            continue
+        else:
+            raise CatBoostError(f"unknown column type {role!r} in column description")
+        if role in ("Num", "Categ"):
+            feature_names.append(names.get(c, header[c] if header else str(len(feature_names))))
+    feat_cols = sorted(num_idx + cat_idx)
+    n = len(rows)
+    data = np.empty((n, len(feat_cols)), dtype=object)
+    for j, c in enumerate(feat_cols):
+        col = [r[c] for r in rows]
+        if c in cat_idx:
+            data[:, j] = col
+        else:
+            data[:, j] = [float(v) if v not in ("", "NaN", "nan", "N/A", "NA", "None", "-") else np.nan for v in col]
+    cat_features = [feat_cols.index(c) for c in cat_idx]
+    def _col(c, conv=float):
+        return np.array([conv(r[c]) for r in rows])
+    label = None
+    if label_idx:
+        try:
+            label = np.stack([_col(c) for c in label_idx], axis=1)
+        except ValueError:
+            label = np.stack([_col(c, str) for c in label_idx], axis=1)
+        if label.shape[1] == 1:
+            label = label[:, 0]
+    return dict(
+        data=data, label=label, cat_features=cat_features,
+        weight=_col(weight_idx) if weight_idx is not None else None,
+        group_id=_col(group_idx, str) if group_idx is not None else None,
+        subgroup_id=_col(subgroup_idx, str) if subgroup_idx is not None else None,
+        group_weight=_col(gw_idx) if gw_idx is not None else None,
+        timestamp=_col(ts_idx) if ts_idx is not None else None,
+        baseline=np.stack([_col(c) for c in baseline_idx], axis=1) if baseline_idx else None,
+        feature_names=feature_names,
+    )
+
+
+def read_libsvm(path: str):
+    labels, rows, maxf = [], [], 0
+    with open(path) as fh:
+        for line in fh:
+            parts = line.split()
+            if not parts:
+                continue
+            labels.append(float(parts[0]))
+            row = {}
+            for tok in parts[1:]:
+                if tok.startswith("qid:"):
+                    continue
+                k, v = tok.split(":")
+                row[int(k)] = float(v)
+                maxf = max(maxf, int(k))
+            rows.append(row)
+    X = np.zeros((len(rows), maxf + 1), dtype=np.float32)
+    for i, row in enumerate(rows):
+        for k, v in row.items():
+            X[i, k] = v
+    return dict(data=X, label=np.array(labels))
+
+
+def read_pairs(path: str):
+    pairs, weights = [], []
+    with open(path) as fh:
+        for line in fh:
+            p = line.split()
+            if len(p) >= 2:
+                pairs.append((int(p[0]), int(p[1])))
+                weights.append(float(p[2]) if len(p) > 2 else 1.0)
+    return np.array(pairs, dtype=np.int64).reshape(-1, 2), np.array(weights, dtype=np.float32)
+
+
+class Pool:
+    """Dataset container accepted by ``fit`` / ``predict`` / ``cv``.
+
+    Parameters follow ``catboost.Pool``: ``data`` may be a numpy array, a pandas DataFrame, a list of rows,
+    another Pool, or a path to a dsv / ``libsvm://`` file (with ``column_description``).
+    """
+
+    def __init__(self, data, label=None, cat_features: Optional[Sequence] = None, text_features=None,
+                 embedding_features=None, column_description: Optional[str] = None, pairs=None, delimiter: str = "\t",
+                 has_header: bool = False, ignore_csv_quoting: bool = False, weight=None, group_id=None,
+                 group_weight=None, subgroup_id=None, pairs_weight=None, baseline=None, timestamp=None,
+                 feature_names: Optional[Sequence[str]] = None, feature_tags=None, thread_count: int = -1,
+                 log_cout=None, log_cerr=None, data_can_be_none: bool = False):
+        if text_features or embedding_features:
+            raise CatBoostError("text and embedding features are not supported by catboost_b200")
+        if isinstance(data, Pool):
+            self.__dict__.update({k: (v.copy() if isinstance(v, np.ndarray) else v) for k, v in data.__dict__.items()})
+            return
+        if isinstance(data, (str, os.PathLike)):
+            path = os.fspath(data)
+            if path.startswith("libsvm://"):
+                loaded = read_libsvm(path[len("libsvm://"):])
+            else:
+                if path.startswith("dsv://"):
+                    path = path[len("dsv://"):]
+                loaded = read_dsv(path, column_description, delimiter, has_header, ignore_csv_quoting)
+            data = loaded.pop("data")
+            label = loaded.get("label") if label is None else label
+            cat_features = loaded.get("cat_features") if cat_features is None else cat_features
+            weight = loaded.get("weight") if weight is None else weight
+            group_id = loaded.get("group_id") if group_id is None else group_id
+            subgroup_id = loaded.get("subgroup_id") if subgroup_id is None else subgroup_id
+            group_weight = loaded.get("group_weight") if group_weight is None else group_weight
+            baseline = loaded.get("baseline") if baseline is None else baseline
+            timestamp = loaded.get("timestamp") if timestamp is None else timestamp
+            feature_names = loaded.get("feature_names") if feature_names is None else feature_names
+            if isinstance(pairs, (str, os.PathLike)):
+                pairs, pw = read_pairs(os.fspath(pairs))
+                pairs_weight = pw if pairs_weight is None else pairs_weight
+        names = None
+        if _pd is not None and isinstance(data, _pd.DataFrame):
+            names = [str(c) for c in data.columns]
+            if cat_features is None:
+                cat_features = [i for i, dt in enumerate(data.dtypes) if str(dt) in ("object", "category", "string", "str")]
+            data = data.to_numpy(dtype=object) if len(cat_features or []) else data.to_numpy()
+        elif _pd is not None and isinstance(data, _pd.Series):
+            data = data.to_numpy().reshape(-1, 1)
+        if data is None:
+            if not data_can_be_none:
+                raise CatBoostError("data is None")
+            data = np.zeros((0, 0), dtype=np.float32)
+        if not isinstance(data, np.ndarray):
+            try:
+                import torch
+                if isinstance(data, torch.Tensor):
+                    data = data.detach().cpu().numpy()
+            except Exception:  # pragma: no cover
+                pass
+        if not isinstance(data, np.ndarray):
+            data = np.asarray(data, dtype=object if cat_features else None)
+        if data.ndim == 1:
+            data = data.reshape(-1, 1)
+        if data.ndim != 2:
+            raise CatBoostError("data must be two-dimensional")
+        n, ncol = data.shape
+        if feature_names is not None:
+            names = [str(x) for x in feature_names]
+            if len(names) != ncol:
+                raise CatBoostError("feature_names length does not match the number of columns")
+        cat_idx = self._resolve_feature_indices(cat_features, names, ncol)
+        self.cat_feature_indices = cat_idx
+        self.feature_names = names if names is not None else [str(i) for i in range(ncol)]
+        self.n_features = ncol
+        float_idx = [c for c in range(ncol) if c not in set(cat_idx)]
+        self.float_feature_indices = float_idx
+        # float matrix
+        if not cat_idx and data.dtype == np.float32 and data.flags.c_contiguous:
+            self.float_data = data
+        elif not cat_idx and data.dtype != object:
+            self.float_data = np.ascontiguousarray(data, dtype=np.float32)
+        else:
+            fd = np.empty((n, len(float_idx)), dtype=np.float32)
+            for j, c in enumerate(float_idx):
+                col = data[:, c]
+                try:
+                    fd[:, j] = col.astype(np.float32)
+                except (ValueError, TypeError):
+                    fd[:, j] = [np.nan if (v is None or v == "") else float(v) for v in col]
+            self.float_data = fd
+        # categorical columns: hashed + string dictionary
+        self.cat_hashes = np.empty((len(cat_idx), n), dtype=np.uint32)
+        self.cat_strings = []
+        for j, c in enumerate(cat_idx):
+            col = data[:, c]
+            h, strs = hash_cat_values(col)
+            self.cat_hashes[j] = h
+            self.cat_strings.append(strs)
+        self.label = self._prep_label(label, n)
+        self.weight = self._prep_vec(weight, n, "weight")
+        self.group_weight = self._prep_vec(group_weight, n, "group_weight")
+        if self.group_weight is not None and self.weight is None:
+            self.weight = self.group_weight
+        self.baseline = None if baseline is None else np.asarray(baseline, dtype=np.float64).reshape(n, -1)
+        self.timestamp = None if timestamp is None else np.asarray(timestamp)
+        self.group_id = None
+        self.subgroup_id = None if subgroup_id is None else np.asarray(subgroup_id)
+        if group_id is not None:
+            self.set_group_id(group_id)
+        self.pairs = None
+        self.pairs_weight = None
+        if pairs is not None:
+            self.set_pairs(pairs, pairs_weight)
+        self.thread_count = thread_count
+        self._quantized = None
+
+    # ------------------------------------------------------------------ helpers
+    @staticmethod
+    def _resolve_feature_indices(spec, names, ncol):
+        if spec is None:
+            return []
+        out = []
+        for s in spec:
+            if isinstance(s, (int, np.integer)):
+                out.append(int(s))
+            else:
+                if names is None or str(s) not in names:
+                    raise CatBoostError(f"unknown feature name {s!r}")
+                out.append(names.index(str(s)))
+        if any(i < 0 or i >= ncol for i in out):
+            raise CatBoostError("feature index out of range")
+        return sorted(set(out))
+
+    @staticmethod
+    def _prep_vec(v, n, what):
+        if v is None:
+            return None
+        a = np.asarray(v, dtype=np.float32).reshape(-1)
+        if a.shape[0] != n:
+            raise CatBoostError(f"length of {what} ({a.shape[0]}) differs from the number of rows ({n})")
+        return a
+
+    @staticmethod
+    def _prep_label(label, n):
+        if label is None:
+            return None
+        if _pd is not None and isinstance(label, (_pd.Series, _pd.DataFrame)):
+            label = label.to_numpy()
+        a = np.asarray(label)
+        if a.ndim == 2 and a.shape[1] == 1:
+            a = a[:, 0]
+        if a.shape[0] != n:
+            raise CatBoostError(f"length of label ({a.shape[0]}) differs from the number of rows ({n})")
+        return a
+
+    # ------------------------------------------------------------------ public API (catboost.Pool compatible)
+    def num_row(self) -> int:
+        return int(self.float_data.shape[0]) if self.float_data.size or not len(self.cat_feature_indices) else int(self.cat_hashes.shape[1])
+
+    def num_col(self) -> int:
+        return int(self.n_features)
+
+    @property
+    def shape(self):
+        return (self.num_row(), self.num_col())
+
+    def get_label(self):
+        return None if self.label is None else self.label.copy()
+
+    def get_weight(self):
+        return np.ones(self.num_row(), dtype=np.float32) if self.weight is None else self.weight.copy()
+
+    def get_baseline(self):
+        return None if self.baseline is None else self.baseline.copy()
+
+    def get_cat_feature_indices(self):
+        return list(self.cat_feature_indices)
+
+    def get_feature_names(self):
+        return list(self.feature_names)
+
+    def get_group_id_hash(self):
+        return None if self.group_id is None else self.group_id.copy()
+
+    def get_features(self):
+        out = np.empty((self.num_row(), self.n_features), dtype=np.float32)
+        for j, c in enumerate(self.float_feature_indices):
+            out[:, c] = self.float_data[:, j]
+        for j, c in enumerate(self.cat_feature_indices):
+            out[:, c] = self.cat_hashes[j].astype(np.float32)
+        return out
+
+    def is_empty_(self):
+        return self.num_row() == 0
+
+    def is_quantized(self) -> bool:
+        return self._quantized is not None
+
+    def set_weight(self, weight):
+        self.weight = self._prep_vec(weight, self.num_row(), "weight")
+
+    def set_baseline(self, baseline):
+        self.baseline = None if baseline is None else np.asarray(baseline, dtype=np.float64).reshape(self.num_row(), -1)
+
+    def set_feature_names(self, names):
+        names = [str(x) for x in names]
+        if len(names) != self.n_features:
+            raise CatBoostError("feature_names length does not match the number of columns")
+        self.feature_names = names
+
+    def set_group_id(self, group_id):
+        g = np.asarray(group_id)
+        if g.shape[0] != self.num_row():
+            raise CatBoostError("length of group_id differs from the number of rows")
+        # groups must be contiguous (the reference requires grouped input)
+        change = np.ones(len(g), dtype=bool)
+        if len(g) > 1:
+            change[1:] = g[1:] != g[:-1]
+        ids = np.cumsum(change) - 1
+        uniq_first = {}
+        for k, v in zip(ids[change], g[change]):
+            if v in uniq_first:
+                raise CatBoostError("queries (groups) must be stored contiguously in the dataset")
+            uniq_first[v] = k
+        self.group_id = ids.astype(np.int64)
+
+    def set_subgroup_id(self, subgroup_id):
+        self.subgroup_id = np.asarray(subgroup_id)
+
+    def set_group_weight(self, group_weight):
+        self.group_weight = self._prep_vec(group_weight, self.num_row(), "group_weight")
+        self.weight = self.group_weight
+
+    def set_pairs(self, pairs, pairs_weight=None):
+        p = np.asarray(pairs, dtype=np.int64).reshape(-1, 2)
+        if p.size and (p.min() < 0 or p.max() >= self.num_row()):
+            raise CatBoostError("pair index out of range")
+        self.pairs = p
+        self.pairs_weight = (np.ones(len(p), dtype=np.float32) if pairs_weight is None
+                             else np.asarray(pairs_weight, dtype=np.float32))
+
+    def set_pairs_weight(self, pairs_weight):
+        self.pairs_weight = np.asarray(pairs_weight, dtype=np.float32)
+
+    def group_offsets(self):
+        """Start offsets of the query groups (length n_groups + 1); one group per row when ungrouped."""
+        n = self.num_row()
+        if self.group_id is None:
+            return np.arange(n + 1, dtype=np.int64)
+        change = np.ones(n, dtype=bool)
+        change[1:] = self.group_id[1:] != self.group_id[:-1]
+        return np.concatenate([np.nonzero(change)[0], [n]]).astype(np.int64)
+
+    def slice(self, rindex):
+        """New Pool with the given rows (order preserved)."""
+        idx = np.asarray(rindex, dtype=np.int64)
+        out = Pool.__new__(Pool)
+        out.__dict__.update(self.__dict__)
+        out.float_data = np.ascontiguousarray(self.float_data[idx])
+        out.cat_hashes = np.ascontiguousarray(self.cat_hashes[:, idx])
+        for k in ("label", "weight", "group_weight", "baseline", "timestamp", "group_id", "subgroup_id"):
+            v = getattr(self, k)
+            setattr(out, k, None if v is None else v[idx])
+        if self.pairs is not None:
+            pos = -np.ones(self.num_row(), dtype=np.int64)
+            pos[idx] = np.arange(len(idx))
+            keep = (pos[self.pairs[:, 0]] >= 0) & (pos[self.pairs[:, 1]] >= 0)
+            out.pairs = pos[self.pairs[keep]]
+            out.pairs_weight = self.pairs_weight[keep]
+        out._quantized = None
+        return out
+
+    def quantize(self, ignored_features=None, per_float_feature_quantization=None, border_count=None,
+                 max_bin=None, feature_border_type=None, nan_mode=None, input_borders=None, task_type=None,
+                 used_ram_limit=None, random_seed=None, **kwargs):
+        """Pre-compute borders and bins (kept on the host); later fits reuse them."""
+        from .quantization import build_quantization
+        bc = border_count if border_count is not None else (max_bin if max_bin is not None else 254)
+        self._quantized = build_quantization(self, bc, feature_border_type or "GreedyLogSum", nan_mode or "Min",
+                                             per_float_feature_quantization, input_borders)
+        return self
+
+    def save_quantization_borders(self, path: str):
+        if self._quantized is None:
+            raise CatBoostError("pool is not quantized")
+        with open(path, "w") as fh:
+            for f, b in enumerate(self._quantized.borders):
+                for v in b:
+                    fh.write(f"{f}\t{float(v):.9g}\n")
+
+    def save(self, fname: str):
+        """Write the pool as a tab-separated file with the label in column 0 (plus ``fname + '.cd'``)."""
+        n = self.num_row()
+        feats = self.get_features().astype(object)
+        for j, c in enumerate(self.cat_feature_indices):
+            inv = {h: s for s, h in self.cat_strings[j].items()}
+            feats[:, c] = [inv.get(int(h), str(int(h))) for h in self.cat_hashes[j]]
+        with open(fname, "w") as fh:
+            for i in range(n):
+                lab = "" if self.label is None else str(self.label[i])
+                fh.write("\t".join([lab] + [str(v) for v in feats[i]]) + "\n")
+        with open(fname + ".cd", "w") as fh:
+            fh.write("0\tLabel\n")
+            for c in self.cat_feature_indices:
+                fh.write(f"{c + 1}\tCateg\n")
+
+    def __len__(self):
+        return self.num_row()
+
+
+def to_pool(data, label=None, **kw) -> Pool:
+    if isinstance(data, Pool):
+        if label is not None:
+            raise CatBoostError("label must be None when data is a Pool")
+        return data
+    return Pool(data, label, **kw)

@@ -1,0 +1,162 @@
+"""Device-dispatching wrappers around the native kernels, plus plain-PyTorch reference implementations.
+
+``hist`` / ``update_leaf`` / ``update_nodes`` / ``leaf_index`` run the hand-written CUDA kernel when the store
+is on a GPU and the OpenMP implementation when it is on the CPU.  The ``*_reference`` functions are
+straightforward fp32 PyTorch restatements of the same operation; tests compare the kernels against them.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..data.quantization import BinnedStore
+from . import native
+
+
+def _p(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(dev):
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+_dev_info = {}
+
+
+def device_info(dev):
+    key = str(dev)
+    if key not in _dev_info:
+        sm, smem = ctypes.c_int(0), ctypes.c_int(0)
+        with torch.cuda.device(dev):
+            native.cuda_check(native.cuda_lib().cb_device_info(ctypes.byref(sm), ctypes.byref(smem)), "cb_device_info")
+        _dev_info[key] = (sm.value, smem.value)
+    return _dev_info[key]
+
+
+def hist(store: BinnedStore, leaf: torch.Tensor, stats: torch.Tensor, slot_table: torch.Tensor, nslots: int,
+         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[slot, s, feat_off[f] + bin] = sum of stats[s, i] over documents with slot_table[leaf[i]] == slot.
+
+    leaf: int16 [npad]; stats: float32 [S, npad]; slot_table: int16 [n_leaf_ids] (-1 = skip)."""
+    S = stats.shape[0]
+    TB = store.TB
+    dev = store.bins.device
+    if out is None:
+        out = torch.zeros((nslots, S, TB), dtype=torch.float32, device=dev)
+    else:
+        out.zero_()
+    if dev.type == "cpu":
+        native.cpu_lib().cbc_hist(_p(store.bins), ctypes.c_longlong(store.npad), ctypes.c_longlong(store.n),
+                                  ctypes.c_int(store.F), _p(store.feat_off), ctypes.c_int(TB), _p(leaf), _p(stats),
+                                  ctypes.c_int(S), _p(slot_table), ctypes.c_int(nslots), _p(out))
+        return out
+    lib = native.cuda_lib()
+    sm, max_smem = device_info(dev)
+    B = max(4, (store.max_bins + 3) // 4 * 4)
+    per_slot = S * 4 * B * 4
+    spp = max(1, min(nslots, (max_smem - 1024) // per_slot))
+    if per_slot > max_smem - 1024:
+        # too many statistic columns for one shared-memory pass: process them in chunks
+        smax = max(1, (max_smem - 1024) // (4 * B * 4))
+        for s0 in range(0, S, smax):
+            s1 = min(S, s0 + smax)
+            out[:, s0:s1] = hist(store, leaf, stats[s0:s1].contiguous(), slot_table, nslots)
+        return out
+    occ = max(1, min(4, (max_smem) // max(1, spp * per_slot + 1024)))
+    grid = sm * occ
+    native.cuda_check(lib.cb_hist(ctypes.c_void_p(store.handle), _p(leaf), _p(stats), S, 0, None, _p(slot_table),
+                                  nslots, spp, B, _p(out), grid, 512, _stream(dev)), "cb_hist")
+    return out
+
+
+def hist_reference(store: BinnedStore, leaf: torch.Tensor, stats: torch.Tensor, slot_table: torch.Tensor,
+                   nslots: int) -> torch.Tensor:
+    n, S, TB = store.n, stats.shape[0], store.TB
+    out = torch.zeros((nslots, S, TB), dtype=torch.float32, device=store.bins.device)
+    slot = slot_table.long()[(leaf[:n].long() & 0xFFFF)]
+    keep = slot >= 0
+    flat = out.view(nslots * S, TB)
+    for f in range(store.F):
+        col = store.column(f).long() + int(store.feat_off_host[f])
+        for s in range(S):
+            idx = (slot[keep] * S + s) * TB + col[keep]
+            flat.view(-1).index_add_(0, idx, stats[s, :n][keep])
+    return out
+
+
+def update_leaf(store: BinnedStore, leaf: torch.Tensor, feature: int, bin_: int, onehot: bool, level: int):
+    """leaf |= (bin(feature) > bin_) << level   (one-hot: ==)."""
+    dev = store.bins.device
+    if dev.type == "cpu":
+        native.cpu_lib().cbc_update_leaf(_p(store.bins), ctypes.c_longlong(store.npad), ctypes.c_longlong(store.n),
+                                         ctypes.c_int(feature), ctypes.c_int(bin_), ctypes.c_int(1 if onehot else 0),
+                                         ctypes.c_int(level), _p(leaf))
+        return
+    # the kernel reads splits[iter * depth + level]; place the record at index `level` of a (level+1)-deep tree
+    recs = torch.zeros((level + 1, 4), dtype=torch.int32, device=dev)
+    recs[:, 0] = -1
+    recs[level] = torch.tensor([feature, bin_, 0, 1 if onehot else 0], dtype=torch.int32, device=dev)
+    zero = torch.zeros(1, dtype=torch.int32, device=dev)
+    sm, _ = device_info(dev)
+    native.cuda_check(native.cuda_lib().cb_update_leaf(ctypes.c_void_p(store.handle), _p(leaf), _p(recs), _p(zero),
+                                                       level + 1, level, sm * 8, _stream(dev)), "cb_update_leaf")
+
+
+def update_nodes(store: BinnedStore, leaf: torch.Tensor, node_split: torch.Tensor):
+    """Non-symmetric step: node_split int32 [n_nodes, 4] = (feature, bin, flags, left_child); documents of a node
+    with feature >= 0 move to left_child (+1 when the condition holds)."""
+    dev = store.bins.device
+    n_nodes = node_split.shape[0]
+    if dev.type == "cpu":
+        native.cpu_lib().cbc_update_nodes(_p(store.bins), ctypes.c_longlong(store.npad), ctypes.c_longlong(store.n),
+                                          _p(node_split), ctypes.c_int(n_nodes), _p(leaf))
+        return
+    sm, _ = device_info(dev)
+    native.cuda_check(native.cuda_lib().cb_update_nodes(ctypes.c_void_p(store.handle), _p(leaf), _p(node_split), n_nodes,
+                                                        sm * 8, _stream(dev)), "cb_update_nodes")
+
+
+def leaf_index(store: BinnedStore, splits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Oblivious leaf index of every document for int32 split records [depth, 4] = (feature, bin, _, flags)."""
+    dev = store.bins.device
+    depth = splits.shape[0]
+    if out is None:
+        out = torch.zeros(store.npad, dtype=torch.int16, device=dev)
+    if dev.type == "cpu":
+        native.cpu_lib().cbc_leaf_index(_p(store.bins), ctypes.c_longlong(store.npad), ctypes.c_longlong(store.n),
+                                        _p(splits.contiguous()), ctypes.c_int(depth), _p(out))
+        return out
+    sm, _ = device_info(dev)
+    native.cuda_check(native.cuda_lib().cb_leaf_index(ctypes.c_void_p(store.handle), _p(out), _p(splits.contiguous()),
+                                                      depth, sm * 8, _stream(dev)), "cb_leaf_index")
+    return out
+
+
+def leaf_index_reference(store: BinnedStore, splits) -> torch.Tensor:
+    idx = torch.zeros(store.n, dtype=torch.long, device=store.bins.device)
+    for k, (f, b, _, flags) in enumerate(np.asarray(splits).tolist()):
+        if f < 0:
+            continue
+        col = store.column(f).long()
+        bit = (col == b) if (flags & 1) else (col > b)
+        idx |= bit.long() << k
+    return idx
+
+
+def leaf_sums(leaf: torch.Tensor, cols: torch.Tensor, L: int, n: int) -> torch.Tensor:
+    """float64 [L, C]: per-leaf sums of the C columns ``cols`` [C, >= n]."""
+    C = cols.shape[0]
+    if leaf.device.type == "cpu":
+        out = torch.zeros((L, C), dtype=torch.float64)
+        cols = cols.contiguous()
+        native.cpu_lib().cbc_leaf_sums(_p(leaf), ctypes.c_longlong(n), _p(cols), ctypes.c_longlong(cols.stride(0)),
+                                       ctypes.c_int(C), ctypes.c_int(L), _p(out))
+        return out
+    idx = leaf[:n].long() & 0xFFFF
+    out = torch.zeros((C, L), dtype=torch.float64, device=leaf.device)
+    out.index_add_(1, idx, cols[:, :n].double())
+    return out.t().contiguous()

@@ -1,0 +1,458 @@
+// CPU-side native code of catboost_b200 (OpenMP): border selection, quantisation, histograms, leaf index
+// and batch apply.  It is the task_type='CPU' backend and the oracle for the CUDA kernels.
+// C ABI, called through ctypes with numpy buffers.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <limits>
+#include <queue>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define CBC_API extern "C" __attribute__((visibility("default")))
+
+// ------------------------------------------------------------------------------------------------------
+// Border selection on a sorted sample of one feature.
+// Behaviour follows library/cpp/grid_creator/binarization.cpp: GreedyLogSum / GreedyMinEntropy split the
+// widest-gain bin first (priority queue keyed by the penalty gain of a median split, :1378-1520), Median =
+// equal-frequency quantiles, Uniform = equally spaced between min and max, UniformAndQuantiles = half each.
+// A border always lies between two distinct sample values (their mean).
+namespace {
+
+enum BorderType { kMedian = 0, kGreedyLogSum = 1, kUniform = 2, kUniformAndQuantiles = 3, kMinEntropy = 4, kMaxLogSum = 5, kGreedyMinEntropy = 6 };
+
+inline double Penalty(double w, bool entropy) { return entropy ? w * std::log(w + 1e-8) : -std::log(w + 1e-8); }
+
+struct Bin {
+    uint32_t begin, end, split;
+    double gain;
+    bool operator<(const Bin& o) const { return gain < o.gain; }
+    bool can_split() const { return split != begin && split != end; }
+};
+
+struct GreedySplitter {
+    const float* v;
+    bool entropy;
+    double score(const Bin& b, uint32_t pos) const {
+        if (pos == b.begin || pos == b.end) return -std::numeric_limits<double>::infinity();
+        return -Penalty(double(pos - b.begin), entropy) - Penalty(double(b.end - pos), entropy) +
+               Penalty(double(b.end - b.begin), entropy);
+    }
+    void refresh(Bin& b) const {
+        const uint32_t mid = b.begin + (b.end - b.begin) / 2;
+        const float mv = v[mid];
+        const uint32_t lb = uint32_t(std::lower_bound(v + b.begin, v + mid, mv) - v);
+        const uint32_t ub = uint32_t(std::upper_bound(v + mid, v + b.end, mv) - v);
+        const double sl = score(b, lb), sr = score(b, ub);
+        if (sl >= sr) { b.split = lb; b.gain = sl; } else { b.split = ub; b.gain = sr; }
+    }
+};
+
+void GreedyBorders(const float* v, uint32_t n, int max_borders, bool entropy, std::vector<float>& out) {
+    GreedySplitter sp{v, entropy};
+    std::priority_queue<Bin> q;
+    Bin root{0, n, 0, 0.0};
+    sp.refresh(root);
+    q.push(root);
+    while ((int)q.size() <= max_borders && q.top().can_split()) {
+        Bin top = q.top();
+        q.pop();
+        Bin left{top.begin, top.split, 0, 0.0};
+        sp.refresh(left);
+        top.begin = top.split;
+        sp.refresh(top);
+        q.push(left);
+        q.push(top);
+    }
+    while (!q.empty()) {
+        const Bin& b = q.top();
+        if (b.begin != 0) out.push_back(0.5f * v[b.begin - 1] + 0.5f * v[b.begin]);
+        q.pop();
+    }
+}
+
+void MedianBorders(const float* v, uint32_t n, int max_borders, std::vector<float>& out) {
+    for (int k = 1; k <= max_borders; ++k) {
+        const uint64_t pos = uint64_t(k) * n / (max_borders + 1);
+        if (pos == 0 || pos >= n) continue;
+        if (v[pos - 1] != v[pos]) out.push_back(0.5f * v[pos - 1] + 0.5f * v[pos]);
+        else {
+            // move to the nearest change of value so that heavy ties still get a border
+            const float* lo = std::lower_bound(v, v + n, v[pos]);
+            if (lo != v) out.push_back(0.5f * lo[-1] + 0.5f * lo[0]);
+        }
+    }
+}
+
+void UniformBorders(const float* v, uint32_t n, int max_borders, std::vector<float>& out) {
+    const float lo = v[0], hi = v[n - 1];
+    if (!(hi > lo)) return;
+    for (int k = 1; k <= max_borders; ++k) out.push_back(lo + (hi - lo) * float(k) / float(max_borders + 1));
+}
+
+}  // namespace
+
+// values: sorted ascending, NaN-free.  Returns the number of borders written (sorted, unique).
+CBC_API int cbc_select_borders(const float* values, long long n, int max_borders, int type, float* out) {
+    if (n <= 1 || max_borders <= 0 || values[0] == values[n - 1]) return 0;
+    std::vector<float> b;
+    switch (type) {
+        case kMedian: MedianBorders(values, (uint32_t)n, max_borders, b); break;
+        case kUniform: UniformBorders(values, (uint32_t)n, max_borders, b); break;
+        case kUniformAndQuantiles:
+            UniformBorders(values, (uint32_t)n, max_borders / 2, b);
+            MedianBorders(values, (uint32_t)n, max_borders - max_borders / 2, b);
+            break;
+        case kMinEntropy:
+        case kGreedyMinEntropy: GreedyBorders(values, (uint32_t)n, max_borders, true, b); break;
+        default: GreedyBorders(values, (uint32_t)n, max_borders, false, b); break;
+    }
+    std::sort(b.begin(), b.end());
+    b.erase(std::unique(b.begin(), b.end()), b.end());
+    if ((int)b.size() > max_borders) b.resize(max_borders);
+    std::copy(b.begin(), b.end(), out);
+    return (int)b.size();
+}
+
+// Column-wise border selection for a row-major float matrix sample [n][F] (ld = row stride).
+// out_borders: [F][max_borders]; out_counts: [F]; has_nan: [F] (1 when the sample holds a NaN).
+CBC_API void cbc_select_borders_matrix(const float* X, long long n, int F, long long ld, int max_borders, int type,
+                                       float* out_borders, int* out_counts, unsigned char* has_nan) {
+#pragma omp parallel
+    {
+        std::vector<float> col;
+#pragma omp for schedule(dynamic, 1)
+        for (int f = 0; f < F; ++f) {
+            col.clear();
+            col.reserve((size_t)n);
+            bool nan = false;
+            for (long long i = 0; i < n; ++i) {
+                const float v = X[i * ld + f];
+                if (v != v) nan = true; else col.push_back(v);
+            }
+            std::sort(col.begin(), col.end());
+            has_nan[f] = nan ? 1 : 0;
+            out_counts[f] = col.empty() ? 0
+                                        : cbc_select_borders(col.data(), (long long)col.size(), max_borders, type,
+                                                             out_borders + (size_t)f * max_borders);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Quantise a row-major matrix into the packed group store used by both backends:
+// bins[g][npad] uint32, byte j of group g = bin of feature 4g+j; bin = number of borders < value.
+CBC_API void cbc_quantize(const float* X, long long n, int F, long long ld, const float* borders, const int* border_off,
+                          const unsigned char* nan_is_max, uint32_t* bins, long long npad, long long doc_offset) {
+    const int G = (F + 3) / 4;
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; ++i) {
+        const float* row = X + i * ld;
+        for (int g = 0; g < G; ++g) {
+            uint32_t word = 0;
+            for (int j = 0; j < 4; ++j) {
+                const int f = 4 * g + j;
+                if (f >= F) break;
+                const float v = row[f];
+                const float* b0 = borders + border_off[f];
+                const float* b1 = borders + border_off[f + 1];
+                int bin;
+                if (v != v) bin = (nan_is_max && nan_is_max[f]) ? int(b1 - b0) : 0;
+                else bin = int(std::lower_bound(b0, b1, v) - b0);
+                word |= uint32_t(bin) << (8 * j);
+            }
+            bins[(size_t)g * npad + doc_offset + i] = word;
+        }
+    }
+}
+
+CBC_API void cbc_pack_bins(const unsigned char* cols, long long n, long long ld, int F, int f_dst_begin, uint32_t* bins,
+                           long long npad, long long doc_offset) {
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; ++i) {
+        for (int f = 0; f < F; ++f) {
+            const int fd = f_dst_begin + f;
+            uint32_t& w = bins[(size_t)(fd >> 2) * npad + doc_offset + i];
+            const int sh = (fd & 3) * 8;
+            w = (w & ~(255u << sh)) | (uint32_t(cols[(size_t)f * ld + i]) << sh);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Histogram: out[slot][s][feat_off[f] + bin] += stats[s][i] for documents whose slot_of_leaf[leaf[i]] >= 0.
+// Thread-private accumulation in double then reduction, so the result does not depend on the thread count
+// beyond rounding of the final float conversion.
+CBC_API void cbc_hist(const uint32_t* bins, long long npad, long long n, int F, const int* feat_off, int TB,
+                      const uint16_t* leaf, const float* stats, int S, const short* slot_of_leaf, int nslots,
+                      float* out) {
+    const int G = (F + 3) / 4;
+    const size_t total = (size_t)nslots * S * TB;
+    int nthreads = 1;
+#ifdef _OPENMP
+    nthreads = omp_get_max_threads();
+#endif
+    std::vector<std::vector<double>> priv(nthreads);
+#pragma omp parallel
+    {
+        int t = 0;
+#ifdef _OPENMP
+        t = omp_get_thread_num();
+#endif
+        std::vector<double>& h = priv[t];
+        h.assign(total, 0.0);
+#pragma omp for schedule(static)
+        for (long long i = 0; i < n; ++i) {
+            const int slot = slot_of_leaf[leaf[i]];
+            if (slot < 0) continue;
+            for (int g = 0; g < G; ++g) {
+                const uint32_t w = bins[(size_t)g * npad + i];
+                for (int j = 0; j < 4; ++j) {
+                    const int f = 4 * g + j;
+                    if (f >= F) break;
+                    const int col = feat_off[f] + int((w >> (8 * j)) & 255u);
+                    for (int s = 0; s < S; ++s) h[((size_t)slot * S + s) * TB + col] += stats[(size_t)s * npad + i];
+                }
+            }
+        }
+    }
+#pragma omp parallel for schedule(static)
+    for (long long k = 0; k < (long long)total; ++k) {
+        double acc = 0.0;
+        for (int t = 0; t < nthreads; ++t) if (!priv[t].empty()) acc += priv[t][k];
+        out[k] = float(acc);
+    }
+}
+
+// leaf |= (bin > thr) << level   (one-hot: bin == thr)
+CBC_API void cbc_update_leaf(const uint32_t* bins, long long npad, long long n, int feature, int bin, int onehot,
+                             int level, uint16_t* leaf) {
+    const uint32_t* col = bins + (size_t)(feature >> 2) * npad;
+    const int sh = (feature & 3) * 8;
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; ++i) {
+        const unsigned b = (col[i] >> sh) & 255u;
+        const unsigned r = onehot ? (b == (unsigned)bin) : (b > (unsigned)bin);
+        leaf[i] = uint16_t(leaf[i] | (r << level));
+    }
+}
+
+// node-id update for non-symmetric trees; node_split rows = {feature, bin, flags, left_child}
+CBC_API void cbc_update_nodes(const uint32_t* bins, long long npad, long long n, const int* node_split, int n_nodes,
+                              uint16_t* leaf) {
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; ++i) {
+        const int node = leaf[i];
+        if (node >= n_nodes) continue;
+        const int* sp = node_split + 4 * node;
+        if (sp[0] < 0) continue;
+        const unsigned b = (bins[(size_t)(sp[0] >> 2) * npad + i] >> ((sp[0] & 3) * 8)) & 255u;
+        const bool right = (sp[2] & 1) ? (b == (unsigned)sp[1]) : (b > (unsigned)sp[1]);
+        leaf[i] = uint16_t(sp[3] + (right ? 1 : 0));
+    }
+}
+
+// oblivious leaf index from `depth` splits {feature, bin, score(bits), flags} (same 16-byte record as the GPU)
+CBC_API void cbc_leaf_index(const uint32_t* bins, long long npad, long long n, const int* splits, int depth,
+                            uint16_t* leaf) {
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; ++i) {
+        int l = 0;
+        for (int k = 0; k < depth; ++k) {
+            const int f = splits[4 * k];
+            if (f < 0) continue;
+            const unsigned b = (bins[(size_t)(f >> 2) * npad + i] >> ((f & 3) * 8)) & 255u;
+            const unsigned thr = (unsigned)splits[4 * k + 1];
+            l |= int((splits[4 * k + 3] & 1) ? (b == thr) : (b > thr)) << k;
+        }
+        leaf[i] = uint16_t(l);
+    }
+}
+
+// per-leaf sums: sums[leaf][c] += cols[c][i]
+CBC_API void cbc_leaf_sums(const uint16_t* leaf, long long n, const float* cols, long long ld, int C, int L, double* sums) {
+    int nthreads = 1;
+#ifdef _OPENMP
+    nthreads = omp_get_max_threads();
+#endif
+    std::vector<std::vector<double>> priv(nthreads);
+#pragma omp parallel
+    {
+        int t = 0;
+#ifdef _OPENMP
+        t = omp_get_thread_num();
+#endif
+        priv[t].assign((size_t)L * C, 0.0);
+        double* h = priv[t].data();
+#pragma omp for schedule(static)
+        for (long long i = 0; i < n; ++i) {
+            const int l = leaf[i];
+            for (int c = 0; c < C; ++c) h[(size_t)l * C + c] += cols[(size_t)c * ld + i];
+        }
+    }
+    for (size_t k = 0; k < (size_t)L * C; ++k) {
+        double acc = 0.0;
+        for (int t = 0; t < nthreads; ++t) if (!priv[t].empty()) acc += priv[t][k];
+        sums[k] = acc;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Batch apply of an oblivious ensemble to raw float rows (CPU evaluator).  Blocks of 128 rows are quantised
+// for the used features, then every tree is walked for the block (libs/model/cpu/evaluator_impl.cpp:13-260
+// describes the same blocking idea).  out: [dims][n] doubles.
+CBC_API void cbc_predict_oblivious(const float* X, long long n, long long ld, const int* used_feat, const float* borders,
+                                   const int* border_off, const unsigned char* nan_is_max, int U, const int* tree_depth,
+                                   const int* tree_split_off, const uint16_t* split_feat, const uint8_t* split_bin,
+                                   const long long* tree_leaf_off, const double* leaf_vals, int T, int dims,
+                                   double scale, const double* bias, double* out) {
+    const int BLK = 128;
+    const long long nblk = (n + BLK - 1) / BLK;
+#pragma omp parallel
+    {
+        std::vector<uint8_t> q((size_t)U * BLK);
+        std::vector<int> idx(BLK);
+        std::vector<double> acc((size_t)BLK * dims);
+#pragma omp for schedule(dynamic, 4)
+        for (long long b = 0; b < nblk; ++b) {
+            const long long r0 = b * BLK;
+            const int m = (int)std::min<long long>(BLK, n - r0);
+            for (int u = 0; u < U; ++u) {
+                const float* b0 = borders + border_off[u];
+                const float* b1 = borders + border_off[u + 1];
+                const int col = used_feat[u];
+                for (int r = 0; r < m; ++r) {
+                    const float v = X[(r0 + r) * ld + col];
+                    int bin;
+                    if (v != v) bin = (nan_is_max && nan_is_max[u]) ? int(b1 - b0) : 0;
+                    else bin = int(std::lower_bound(b0, b1, v) - b0);
+                    q[(size_t)u * BLK + r] = (uint8_t)bin;
+                }
+            }
+            std::fill(acc.begin(), acc.end(), 0.0);
+            for (int t = 0; t < T; ++t) {
+                const int depth = tree_depth[t], so = tree_split_off[t];
+                std::fill(idx.begin(), idx.begin() + m, 0);
+                for (int k = 0; k < depth; ++k) {
+                    const uint8_t* qc = q.data() + (size_t)split_feat[so + k] * BLK;
+                    const uint8_t thr = split_bin[so + k];
+                    for (int r = 0; r < m; ++r) idx[r] |= int(qc[r] > thr) << k;
+                }
+                const double* lv = leaf_vals + tree_leaf_off[t] * dims;
+                for (int r = 0; r < m; ++r)
+                    for (int d = 0; d < dims; ++d) acc[(size_t)r * dims + d] += lv[(size_t)idx[r] * dims + d];
+            }
+            for (int r = 0; r < m; ++r)
+                for (int d = 0; d < dims; ++d)
+                    out[(size_t)d * n + r0 + r] = acc[(size_t)r * dims + d] * scale + (bias ? bias[d] : 0.0);
+        }
+    }
+}
+
+CBC_API int cbc_num_threads() {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+CBC_API void cbc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+// ------------------------------------------------------------------------------------------------------
+// String hash of categorical values.  The reference hashes the string form of a categorical value with the
+// 64-bit CityHash of 2011 (version 1) and keeps the low 32 bits (catboost/libs/cat_feature/cat_feature.cpp:4-6);
+// model files store those hashes, so the function below has to produce the same numbers.
+namespace city1 {
+constexpr uint64_t K0 = 0xc3a5c85c97cb3127ULL, K1 = 0xb492b66fbe98f273ULL, K2 = 0x9ae16a3b2f90404fULL,
+                   K3 = 0xc949d7c7509e6557ULL, KMUL = 0x9ddfea08eb382d69ULL;
+inline uint64_t ld64(const char* p) { uint64_t v; std::memcpy(&v, p, 8); return v; }
+inline uint64_t ld32(const char* p) { uint32_t v; std::memcpy(&v, p, 4); return v; }
+inline uint64_t ror(uint64_t v, int s) { return s == 0 ? v : ((v >> s) | (v << (64 - s))); }
+inline uint64_t smix(uint64_t v) { return v ^ (v >> 47); }
+inline uint64_t h16(uint64_t u, uint64_t v) {
+    uint64_t a = (u ^ v) * KMUL; a ^= a >> 47;
+    uint64_t b = (v ^ a) * KMUL; b ^= b >> 47;
+    return b * KMUL;
+}
+struct P { uint64_t a, b; };
+inline P weak32(uint64_t w, uint64_t x, uint64_t y, uint64_t z, uint64_t a, uint64_t b) {
+    a += w; b = ror(b + a + z, 21);
+    const uint64_t c = a;
+    a += x; a += y; b += ror(a, 44);
+    return P{a + z, b + c};
+}
+inline P weak32(const char* s, uint64_t a, uint64_t b) { return weak32(ld64(s), ld64(s + 8), ld64(s + 16), ld64(s + 24), a, b); }
+
+uint64_t hash(const char* s, size_t n) {
+    if (n <= 16) {
+        if (n > 8) { const uint64_t a = ld64(s), b = ld64(s + n - 8); return h16(a, ror(b + n, int(n))) ^ b; }
+        if (n >= 4) { const uint64_t a = ld32(s); return h16(n + (a << 3), ld32(s + n - 4)); }
+        if (n > 0) {
+            const uint8_t a = uint8_t(s[0]), b = uint8_t(s[n >> 1]), c = uint8_t(s[n - 1]);
+            const uint32_t y = uint32_t(a) + (uint32_t(b) << 8), z = uint32_t(n) + (uint32_t(c) << 2);
+            return smix(y * K2 ^ z * K3) * K2;
+        }
+        return K2;
+    }
+    if (n <= 32) {
+        const uint64_t a = ld64(s) * K1, b = ld64(s + 8), c = ld64(s + n - 8) * K2, d = ld64(s + n - 16) * K0;
+        return h16(ror(a - b, 43) + ror(c, 30) + d, a + ror(b ^ K3, 20) - c + n);
+    }
+    if (n <= 64) {
+        uint64_t z = ld64(s + 24);
+        uint64_t a = ld64(s) + (n + ld64(s + n - 16)) * K0;
+        uint64_t b = ror(a + z, 52), c = ror(a, 37);
+        a += ld64(s + 8); c += ror(a, 7); a += ld64(s + 16);
+        const uint64_t vf = a + z, vs = b + ror(a, 31) + c;
+        a = ld64(s + 16) + ld64(s + n - 32);
+        z = ld64(s + n - 8);
+        b = ror(a + z, 52); c = ror(a, 37);
+        a += ld64(s + n - 24); c += ror(a, 7); a += ld64(s + n - 16);
+        const uint64_t wf = a + z, ws = b + ror(a, 31) + c;
+        const uint64_t r = smix((vf + ws) * K2 + (wf + vs) * K0);
+        return smix(r * K0 + vs) * K2;
+    }
+    uint64_t x = ld64(s), y = ld64(s + n - 16) ^ K1, z = ld64(s + n - 56) ^ K0;
+    P v = weak32(s + n - 64, n, y), w = weak32(s + n - 32, n * K1, K0);
+    z += smix(v.b) * K1; x = ror(z + x, 39) * K1; y = ror(y, 33) * K1;
+    size_t left = (n - 1) & ~size_t(63);
+    do {
+        x = ror(x + y + v.a + ld64(s + 16), 37) * K1;
+        y = ror(y + v.b + ld64(s + 48), 42) * K1;
+        x ^= w.b; y ^= v.a; z = ror(z ^ w.a, 33);
+        v = weak32(s, v.b * K1, x + w.a);
+        w = weak32(s + 32, z + w.b, y);
+        std::swap(z, x);
+        s += 64; left -= 64;
+    } while (left != 0);
+    return h16(h16(v.a, w.a) + smix(y) * K1 + z, h16(v.b, w.b) + x);
+}
+}  // namespace city1
+
+CBC_API unsigned long long cbc_cityhash64(const char* s, long long n) { return city1::hash(s, (size_t)n); }
+
+// strings concatenated in `buf`; string k = buf[off[k] .. off[k+1])
+CBC_API void cbc_cat_hash_batch(const char* buf, const long long* off, long long count, uint32_t* out) {
+#pragma omp parallel for schedule(static)
+    for (long long k = 0; k < count; ++k) out[k] = uint32_t(city1::hash(buf + off[k], size_t(off[k + 1] - off[k])) & 0xffffffffULL);
+}
+
+// decimal string form of integers, hashed (the reference stringifies integer categorical values)
+CBC_API void cbc_cat_hash_ints(const long long* vals, long long count, uint32_t* out) {
+#pragma omp parallel for schedule(static)
+    for (long long k = 0; k < count; ++k) {
+        char tmp[24];
+        const int len = std::snprintf(tmp, sizeof(tmp), "%lld", vals[k]);
+        out[k] = uint32_t(city1::hash(tmp, size_t(len)) & 0xffffffffULL);
+    }
+}

@@ -1,0 +1,198 @@
+// K6 fused level kernel: ONE cooperative launch per tree level does
+//   (0) the leaf-index update for the split chosen at the previous level,
+//   (A) streaming histogram accumulation of the local rows (shared-memory fp32 atomics, one slot per parent
+//       leaf: only the lighter child is accumulated, the sibling is parent - child),
+//   (B) the reduce-scatter: every rank stores the feature slice that rank r owns straight into rank r's
+//       slot buffer over NVLink (16-byte peer stores) and raises a system-scope arrival tag,
+//   (C) on the owner: bounded wait for the tags, sum of the per-source slots in rank order (deterministic),
+//       sibling subtraction, bin prefix scan, split scoring, packed 64-bit atomicMax argmax,
+//   (D) an 8-way exchange of the per-rank best (key + lighter-child mask) through the peer mailboxes and the
+//       final argmax, which every rank evaluates identically.
+// No NCCL call, no host round trip and no separate scoring kernel per level.  This replaces the reference's
+// four-step path: histogram kernel -> GatherHistogramsByLeaves -> host-orchestrated ReduceScatter built from
+// cudaMemcpyAsync + add kernel -> FindOptimalSplit -> device-to-host read + host argmin
+// (catboost/cuda/methods/histograms_helper.cpp:58-91, cuda_lib/cuda_buffer_helpers/reduce_scatter.h:449-540,
+// catboost/cuda/methods/histograms_helper.h:322-331).
+//
+// Only plain peer stores/loads are used for remote memory: no TMA, no multicast.
+#include "cb_common.cuh"
+#include "cb_tree.cuh"
+#include "cb_comm.cuh"
+#include <cooperative_groups.h>
+#include <new>
+
+namespace cg = cooperative_groups;
+
+struct CbFusedArgs {
+    CbHistArgs h;            // h.out = local partial [slots][S][TB] (nranks > 1) or the slot buffer itself (nranks == 1)
+    CbScoreArgs s;           // s.hsrc[r] = local slot r; s.W = owned width; s.col_base = first owned column
+    CbComm c;
+    unsigned short* leaf;
+    CbSplit* splits; int depth;
+    unsigned int* mask_out;          // lighter-child mask for the next level
+    unsigned long long* msg_local;   // CB_SELECT_MSG_BYTES scratch in local memory
+    int own_col[CB_MAX_RANKS + 1];   // rank r owns histogram columns [own_col[r], own_col[r+1]) (multiples of 4)
+    int Wmax;                        // row stride (floats) of every slot buffer = max owned width
+};
+
+__global__ void __launch_bounds__(512, 2) cb_level_fused_kernel(CbFusedArgs a) {
+    extern __shared__ __align__(16) float cb_sh[];
+    cg::grid_group grid = cg::this_grid();
+    const int cta = blockIdx.x, ncta = gridDim.x;
+    const int level = a.h.level;
+    const int it = *a.s.iter_ptr;
+    CbSplit* sp_arr = a.splits + (long long)it * a.depth;
+
+    // (0) leaf update with the split of the previous level
+    if (level > 0) {
+        cb_update_leaf_range(a.h.d, a.leaf, sp_arr[level - 1], level - 1,
+                             (long long)cta * blockDim.x + threadIdx.x, (long long)ncta * blockDim.x);
+        __threadfence();
+        grid.sync();
+    }
+
+    // (A) local partial histograms
+    cb_hist_phase(a.h, cb_sh, cta, ncta);
+    __threadfence();
+    grid.sync();
+
+    const int R = a.c.nranks, me = a.c.rank;
+    if (R > 1) {
+        // (B) push owner slices (including our own, so that every source has the same layout on the owner)
+        const unsigned long long hist_epoch = a.c.epoch[1] + 1;
+        const int rows = cb_hist_nslots(a.h) * a.h.S;
+        const int TB = a.h.d.TB;
+        const long long gtid = (long long)cta * blockDim.x + threadIdx.x;
+        const long long gthreads = (long long)ncta * blockDim.x;
+        for (int r = 0; r < R; ++r) {
+            const int c0 = a.own_col[r], w4 = (a.own_col[r + 1] - c0) >> 2;
+            if (w4 <= 0) continue;
+            float4* dst = reinterpret_cast<float4*>(a.c.peer_slot[r] + (size_t)me * a.c.slot_floats);
+            const int dst_w4 = a.Wmax >> 2;
+            const long long total = (long long)rows * w4;
+            for (long long i = gtid; i < total; i += gthreads) {
+                const int row = (int)(i / w4), cc = (int)(i % w4);
+                const float4 v = *reinterpret_cast<const float4*>(a.h.out + (size_t)row * TB + c0 + cc * 4);
+                dst[(size_t)row * dst_w4 + cc] = v;
+            }
+        }
+        __threadfence_system();
+        grid.sync();
+        if (cta == 0 && threadIdx.x < R) cb_st_release_sys(a.c.peer_slot_flag[threadIdx.x] + me, hist_epoch);
+        // (C) wait until every source has delivered this level
+        if (threadIdx.x < R)
+            cb_wait_flag(a.c.peer_slot_flag[me] + threadIdx.x, hist_epoch, a.c.timeout_ns, a.c.status,
+                         CB_TIMEOUT_HIST_ARRIVE, (int)threadIdx.x);
+        __syncthreads();
+    }
+
+    cb_score_phase(a.s, cta, ncta);
+    __threadfence();
+    grid.sync();
+
+    // (D) selection: one block
+    if (cta == 0) {
+        cb_select_local(a.s, a.msg_local);
+        __threadfence();
+        __syncthreads();
+        const unsigned long long* msgs[CB_MAX_RANKS];
+        if (R > 1) {
+            const int bytes = 8 + 4 * (((1 << level) + 31) >> 5);
+            unsigned long long epoch;
+            cb_mailbox_exchange(a.c, a.msg_local, bytes, &epoch);
+            for (int r = 0; r < R; ++r) msgs[r] = reinterpret_cast<const unsigned long long*>(cb_mailbox_msg(a.c, epoch, r));
+        } else {
+            msgs[0] = a.msg_local;
+        }
+        cb_select_final(a.h.d, msgs, R, level, sp_arr + level, a.mask_out);
+        if (threadIdx.x == 0) {
+            *a.s.best_key = 0ull;
+            if (R > 1) a.c.epoch[1] = a.c.epoch[1] + 1;
+        }
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+struct CbFusedPlan {
+    CbFusedArgs a;
+    int threads;
+    int max_smem;
+    int sm_count;
+};
+
+CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigned short* leaf, const float* stats, int S,
+                                    int B, float* partial, float* const* local_slots, float* hbuf0, float* hbuf1,
+                                    const int* own_col, int Wmax, unsigned int* mask0, unsigned int* mask1,
+                                    CbSplit* splits, int depth, float l2, int score_fn, float random_strength,
+                                    const double* scal, const int* iter_ptr, unsigned long long seed, float lr,
+                                    unsigned long long* best_key, unsigned long long* msg_local, int threads) {
+    CbFusedPlan* p = new (std::nothrow) CbFusedPlan();
+    if (!p) return nullptr;
+    CbFusedArgs& a = p->a;
+    a.h.d = *d; a.h.leaf = leaf; a.h.stats = stats; a.h.S = S; a.h.B = B; a.h.out = partial;
+    a.h.slot_table = nullptr; a.h.nslots_table = 0; a.h.level = 0; a.h.small_mask = mask0; a.h.slots_per_pass = 1;
+    a.s.d = *d;
+    if (comm) a.c = *comm; else { a.c = CbComm(); a.c.nranks = 1; a.c.rank = 0; }
+    const int R = a.c.nranks;
+    for (int r = 0; r < CB_MAX_RANKS; ++r) a.s.hsrc[r] = r < R ? local_slots[r] : nullptr;
+    a.s.nsrc = R;
+    a.s.hprev = hbuf0; a.s.hcur = hbuf1;   // swapped per level at launch
+    for (int r = 0; r <= CB_MAX_RANKS; ++r) a.own_col[r] = r <= R ? own_col[r] : own_col[R];
+    a.Wmax = Wmax;
+    a.s.W = Wmax;
+    a.s.col_base = own_col[a.c.rank];
+    // owned feature range from the owned columns
+    int fb = 0, fe = 0;
+    // feat_off is device memory; the caller passes feature ranges through own_col only, so the
+    // feature range is resolved by cb_fused_set_features().
+    a.s.f_begin = fb; a.s.f_end = fe;
+    a.s.level = 0; a.s.S = S; a.s.small_mask = mask0; a.s.l2 = l2; a.s.score_fn = score_fn;
+    a.s.random_strength = random_strength; a.s.scal = scal; a.s.iter_ptr = iter_ptr; a.s.seed = seed;
+    a.s.learning_rate = lr; a.s.best_key = best_key;
+    a.leaf = leaf; a.splits = splits; a.depth = depth; a.mask_out = mask1; a.msg_local = msg_local;
+    p->threads = threads;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&p->max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    cudaFuncSetAttribute(cb_level_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, p->max_smem);
+    // keep pointers needed for the per-level swap
+    return p;
+}
+
+CB_API void cb_fused_set_features(CbFusedPlan* p, int f_begin, int f_end) {
+    p->a.s.f_begin = f_begin;
+    p->a.s.f_end = f_end;
+}
+
+CB_API void cb_fused_destroy(CbFusedPlan* p) { delete p; }
+
+// Launch geometry of one level: returns the cooperative grid size (0 on error) and the slots per pass.
+CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int* smem_bytes) {
+    const int nslots = level == 0 ? 1 : (1 << (level - 1));
+    const int per_slot = p->a.h.S * 4 * p->a.h.B * 4;
+    int spp = nslots;
+    const int budget = p->max_smem - 1024;
+    if (spp * per_slot > budget) spp = budget / per_slot;
+    if (spp < 1) return 0;
+    const int smem = spp * per_slot;
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, cb_level_fused_kernel, p->threads, smem) != cudaSuccess) return 0;
+    if (occ < 1) return 0;
+    if (occ > 4) occ = 4;
+    *slots_per_pass = spp;
+    *smem_bytes = smem;
+    return occ * p->sm_count;
+}
+
+CB_API int cb_fused_launch(CbFusedPlan* p, int level, float* hprev, float* hcur, const unsigned int* mask_in,
+                           unsigned int* mask_out, int grid, int slots_per_pass, int smem_bytes, cudaStream_t st) {
+    CbFusedArgs a = p->a;
+    a.h.level = level; a.h.small_mask = mask_in; a.h.slots_per_pass = slots_per_pass;
+    a.s.level = level; a.s.small_mask = mask_in; a.s.hprev = hprev; a.s.hcur = hcur;
+    a.mask_out = mask_out;
+    void* args[] = {&a};
+    cudaError_t e = cudaLaunchCooperativeKernel((void*)cb_level_fused_kernel, dim3(grid), dim3(p->threads), args,
+                                                (size_t)smem_bytes, st);
+    return (int)e;
+}

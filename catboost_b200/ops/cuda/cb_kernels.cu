@@ -1,0 +1,647 @@
+// Stand-alone sm_100a kernels of catboost_b200 and their C launchers (called from Python through ctypes
+// with raw device pointers and a CUDA stream handle).  Every launcher only enqueues work; none of them
+// synchronises or allocates.
+#include "cb_common.cuh"
+#include "cb_losses.cuh"
+#include "cb_tree.cuh"
+#include "cb_comm.cuh"
+#include <new>
+
+#define CB_LAUNCH_CHECK() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) return (int)e__; } while (0)
+
+// ======================================================================================================
+// K1  quantize: float32 rows -> packed one-byte bins.  bin = #borders strictly below the value, i.e. the
+// document goes right of border k iff bin > k  (catboost/cuda/gpu_data/kernel/binarize.cu:37,
+// catboost/libs/data/quantization.cpp).  NaN goes to bin 0 (nan_mode Min) or to the last bin (Max).
+// Thread = (document, feature group); blockIdx.x runs over groups fastest so that the blocks reading the
+// same rows are co-scheduled and the row-major matrix is fetched from DRAM once.
+__global__ void __launch_bounds__(256) cb_quantize_kernel(const float* __restrict__ X, long long n, int F, long long ldx,
+                                                          const float* __restrict__ borders,
+                                                          const int* __restrict__ border_off,
+                                                          const unsigned char* __restrict__ nan_is_max,
+                                                          uint32_t* __restrict__ bins, long long npad,
+                                                          long long doc_offset, int G) {
+    const int g = blockIdx.x % G;
+    const long long tile = blockIdx.x / G;
+    const long long i = tile * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float* row = X + i * ldx;
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int f = g * 4 + j;
+        if (f < F) {
+            const float v = row[f];
+            const int b0 = border_off[f], b1 = border_off[f + 1];
+            int bin;
+            if (v != v) {
+                bin = (nan_is_max && nan_is_max[f]) ? (b1 - b0) : 0;
+            } else {
+                int lo = b0, hi = b1;          // first border >= v  ->  count of borders < v
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (__ldg(borders + mid) < v) lo = mid + 1; else hi = mid;
+                }
+                bin = lo - b0;
+            }
+            word |= (uint32_t)bin << (8 * j);
+        }
+    }
+    bins[(long long)g * npad + doc_offset + i] = word;
+}
+
+CB_API int cb_quantize(const float* X, long long n, int F, long long ldx, const float* borders, const int* border_off,
+                       const unsigned char* nan_is_max, uint32_t* bins, long long npad, long long doc_offset,
+                       cudaStream_t st) {
+    if (n <= 0) return 0;
+    const int G = (F + 3) / 4;
+    const long long tiles = (n + 255) / 256;
+    cb_quantize_kernel<<<(unsigned)(tiles * G), 256, 0, st>>>(X, n, F, ldx, borders, border_off, nan_is_max, bins, npad,
+                                                               doc_offset, G);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// Pack already-binned uint8 columns (feature-major [F][n]) into the group store; used for CTR features and
+// for host-quantized pools.
+__global__ void cb_pack_bins_kernel(const unsigned char* __restrict__ cols, long long n, long long ld, int F,
+                                    int f_dst_begin, uint32_t* __restrict__ bins, long long npad, long long doc_offset) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    for (int f = 0; f < F; ++f) {
+        const int fd = f_dst_begin + f;
+        uint32_t* w = bins + (long long)(fd >> 2) * npad + doc_offset + i;
+        const int sh = (fd & 3) * 8;
+        *w = (*w & ~(255u << sh)) | ((uint32_t)cols[(long long)f * ld + i] << sh);
+    }
+}
+
+CB_API int cb_pack_bins(const unsigned char* cols, long long n, long long ld, int F, int f_dst_begin, uint32_t* bins,
+                        long long npad, long long doc_offset, cudaStream_t st) {
+    if (n <= 0 || F <= 0) return 0;
+    cb_pack_bins_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(cols, n, ld, F, f_dst_begin, bins, npad, doc_offset);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ======================================================================================================
+// K3 + K5 + K9  derivatives, fused with the cursor update by the previous tree and the bootstrap weights.
+struct CbGradArgs {
+    int loss; float p0, p1;
+    float* approx; const float* target; const float* weight;
+    unsigned short* leaf; const float* cur_vals;
+    long long n, npad;
+    float* stats; int newton_stats;
+    int boot_type; float boot_p;        // 0 none, 1 Bayesian(temperature), 2 Bernoulli(subsample), 3 Poisson(lambda)
+    unsigned long long seed; const int* iter_ptr;
+    double* scal;
+    const float* ext_der; const float* ext_hess;   // CB_LOSS_EXTERNAL
+};
+
+__device__ __forceinline__ float cb_bootstrap_weight(int type, float p, unsigned long long h) {
+    switch (type) {
+        default: return 1.0f;
+        case 1: {   // Bayesian: (-log u)^temperature   (catboost/cuda/cuda_util/kernel/bootstrap.cu:7-66)
+            const float u = cb_uniform01(h);
+            const float e = -__logf(u + 1e-20f);
+            return (p == 1.0f) ? e : __powf(e, p);
+        }
+        case 2: return cb_uniform01(h) < p ? 1.0f : 0.0f;
+        case 3: {   // Poisson(lambda = p) by inversion, lambda is O(1)
+            float u = cb_uniform01(h);
+            float pk = __expf(-p), cdf = pk;
+            int k = 0;
+            while (u > cdf && k < 32) { ++k; pk *= p / k; cdf += pk; }
+            return (float)k;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) cb_grad_kernel(CbGradArgs a) {
+    const int it = *a.iter_ptr;
+    double s_loss = 0.0, s_w = 0.0, s_d2 = 0.0, s_n = 0.0;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
+        float ap = a.approx[i];
+        if (a.cur_vals) {
+            ap += a.cur_vals[a.leaf[i]];
+            a.approx[i] = ap;
+        }
+        a.leaf[i] = 0;
+        const float w = a.weight ? a.weight[i] : 1.0f;
+        CbLossOut o;
+        if (a.loss == CB_LOSS_EXTERNAL) { o.der = a.ext_der[i]; o.hess = a.ext_hess ? a.ext_hess[i] : 1.0f; o.value = 0.0f; }
+        else o = cb_loss_eval(a.loss, a.p0, a.p1, ap, a.target[i]);
+        const float wb = a.boot_type ? cb_bootstrap_weight(a.boot_type, a.boot_p,
+                                                             cb_mix64(a.seed ^ cb_mix64(((unsigned long long)it << 40) ^ (unsigned long long)i)))
+                                     : 1.0f;
+        const float wd = w * o.der;
+        a.stats[i] = wb * wd;
+        a.stats[a.npad + i] = wb * w * (a.newton_stats ? o.hess : 1.0f);
+        s_loss += (double)(w * o.value);
+        s_w += (double)w;
+        s_d2 += (double)(wd * wd);
+        s_n += 1.0;
+    }
+    __shared__ double red[4][8];
+    s_loss = cb_warp_sum_d(s_loss); s_w = cb_warp_sum_d(s_w); s_d2 = cb_warp_sum_d(s_d2); s_n = cb_warp_sum_d(s_n);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { red[0][warp] = s_loss; red[1][warp] = s_w; red[2][warp] = s_d2; red[3][warp] = s_n; }
+    __syncthreads();
+    if (threadIdx.x < 4) {
+        double t = 0.0;
+        for (int k = 0; k < (blockDim.x >> 5); ++k) t += red[threadIdx.x][k];
+        atomicAdd(a.scal + threadIdx.x, t);
+    }
+}
+
+CB_API int cb_grad_pointwise(int loss, float p0, float p1, float* approx, const float* target, const float* weight,
+                             unsigned short* leaf, const float* cur_vals, long long n, long long npad, float* stats,
+                             int newton_stats, int boot_type, float boot_p, unsigned long long seed,
+                             const int* iter_ptr, double* scal, const float* ext_der, const float* ext_hess,
+                             int grid, cudaStream_t st) {
+    CbGradArgs a{loss, p0, p1, approx, target, weight, leaf, cur_vals, n, npad, stats, newton_stats,
+                 boot_type, boot_p, seed, iter_ptr, scal, ext_der, ext_hess};
+    cb_grad_kernel<<<grid, 256, 0, st>>>(a);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ======================================================================================================
+// Host-side handles
+CB_API CbData* cb_data_create(const uint32_t* bins, long long npad, long long n, int F, const int* feat_off,
+                              const int* feat_nb, const unsigned char* feat_onehot, const float* feat_weight, int TB) {
+    CbData* d = new (std::nothrow) CbData();
+    if (!d) return nullptr;
+    d->bins = bins; d->npad = npad; d->n = n; d->G = (F + 3) / 4; d->F = F;
+    d->feat_off = feat_off; d->feat_nb = feat_nb; d->feat_onehot = feat_onehot; d->feat_weight = feat_weight; d->TB = TB;
+    return d;
+}
+CB_API void cb_data_destroy(CbData* d) { delete d; }
+
+CB_API CbComm* cb_comm_create(int rank, int nranks, long long timeout_ns, int* status, unsigned long long* epoch,
+                              char* const* mbox, unsigned long long* const* mbox_flag, int mbox_bytes,
+                              float* const* slot, unsigned long long* const* slot_flag, long long slot_floats) {
+    if (nranks < 1 || nranks > CB_MAX_RANKS) return nullptr;
+    CbComm* c = new (std::nothrow) CbComm();
+    if (!c) return nullptr;
+    c->rank = rank; c->nranks = nranks; c->timeout_ns = timeout_ns; c->status = status; c->epoch = epoch;
+    c->mbox_bytes = mbox_bytes; c->slot_floats = slot_floats;
+    for (int r = 0; r < CB_MAX_RANKS; ++r) {
+        c->peer_mbox[r] = r < nranks ? mbox[r] : nullptr;
+        c->peer_mbox_flag[r] = r < nranks ? mbox_flag[r] : nullptr;
+        c->peer_slot[r] = r < nranks ? slot[r] : nullptr;
+        c->peer_slot_flag[r] = r < nranks ? slot_flag[r] : nullptr;
+    }
+    return c;
+}
+CB_API void cb_comm_destroy(CbComm* c) { delete c; }
+
+// ======================================================================================================
+// K7 (leaf part)  stand-alone leaf update for the split of (current tree, level)
+__global__ void __launch_bounds__(256) cb_update_leaf_kernel(CbData d, unsigned short* leaf, const CbSplit* splits,
+                                                             const int* iter_ptr, int depth, int level) {
+    const CbSplit sp = splits[(long long)(*iter_ptr) * depth + level];
+    cb_update_leaf_range(d, leaf, sp, level, (long long)blockIdx.x * blockDim.x + threadIdx.x,
+                         (long long)gridDim.x * blockDim.x);
+}
+
+CB_API int cb_update_leaf(const CbData* d, unsigned short* leaf, const CbSplit* splits, const int* iter_ptr, int depth,
+                          int level, int grid, cudaStream_t st) {
+    cb_update_leaf_kernel<<<grid, 256, 0, st>>>(*d, leaf, splits, iter_ptr, depth, level);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// Non-symmetric trees: leaf holds a node id; nodes with a split send their documents to a child.
+// node_split[node] = {feature, bin, flags, left_child}; right child = left_child + 1; feature < 0 = leaf.
+__global__ void __launch_bounds__(256) cb_update_nodes_kernel(CbData d, unsigned short* leaf, const int4* node_split,
+                                                              int n_nodes) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < d.n; i += stride) {
+        const int node = leaf[i];
+        if (node >= n_nodes) continue;
+        const int4 sp = node_split[node];
+        if (sp.x < 0) continue;
+        const uint32_t w = d.bins[(long long)(sp.x >> 2) * d.npad + i];
+        const unsigned int b = (w >> ((sp.x & 3) * 8)) & 255u;
+        const bool right = (sp.z & 1) ? (b == (unsigned)sp.y) : (b > (unsigned)sp.y);
+        leaf[i] = (unsigned short)(sp.w + (right ? 1 : 0));
+    }
+}
+
+CB_API int cb_update_nodes(const CbData* d, unsigned short* leaf, const int* node_split, int n_nodes, int grid,
+                           cudaStream_t st) {
+    cb_update_nodes_kernel<<<grid, 256, 0, st>>>(*d, leaf, reinterpret_cast<const int4*>(node_split), n_nodes);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ======================================================================================================
+// K6a  stand-alone histogram kernel (non-fused path, NCCL baseline, CPU-oracle tests)
+__global__ void __launch_bounds__(512) cb_hist_kernel(CbHistArgs a) {
+    extern __shared__ __align__(16) float cb_sh[];
+    cb_hist_phase(a, cb_sh, blockIdx.x, gridDim.x);
+}
+
+static int g_hist_smem_set = 0;
+
+CB_API int cb_hist_smem_bytes(int slots_per_pass, int S, int B) { return slots_per_pass * S * 4 * B * 4; }
+
+CB_API int cb_hist(const CbData* d, const unsigned short* leaf, const float* stats, int S, int level,
+                   const unsigned int* small_mask, const short* slot_table, int nslots_table, int slots_per_pass, int B,
+                   float* out, int grid, int threads, cudaStream_t st) {
+    CbHistArgs a;
+    a.d = *d; a.leaf = leaf; a.stats = stats; a.S = S; a.level = level; a.small_mask = small_mask;
+    a.slots_per_pass = slots_per_pass; a.B = B; a.out = out; a.slot_table = slot_table; a.nslots_table = nslots_table;
+    const int smem = cb_hist_smem_bytes(slots_per_pass, S, B);
+    if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+    if (!g_hist_smem_set) {
+        cudaError_t e = cudaFuncSetAttribute(cb_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        g_hist_smem_set = 1;
+    }
+    cb_hist_kernel<<<grid, threads, smem, st>>>(a);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ======================================================================================================
+// K6b  stand-alone scoring + selection kernels
+static void cb_fill_score_args(CbScoreArgs& a, const CbData* d, const float* const* hsrc, int nsrc, const float* hprev,
+                               float* hcur, int W, int col_base, int f_begin, int f_end, int level, int S,
+                               const unsigned int* small_mask, float l2, int score_fn, float random_strength,
+                               const double* scal, const int* iter_ptr, unsigned long long seed, float lr,
+                               unsigned long long* best_key) {
+    a.d = *d;
+    for (int r = 0; r < CB_MAX_RANKS; ++r) a.hsrc[r] = r < nsrc ? hsrc[r] : nullptr;
+    a.nsrc = nsrc; a.hprev = hprev; a.hcur = hcur; a.W = W; a.col_base = col_base; a.f_begin = f_begin; a.f_end = f_end;
+    a.level = level; a.S = S; a.small_mask = small_mask; a.l2 = l2; a.score_fn = score_fn;
+    a.random_strength = random_strength; a.scal = scal; a.iter_ptr = iter_ptr; a.seed = seed; a.learning_rate = lr;
+    a.best_key = best_key;
+}
+
+__global__ void __launch_bounds__(256) cb_score_kernel(CbScoreArgs a) { cb_score_phase(a, blockIdx.x, gridDim.x); }
+
+CB_API int cb_score(const CbData* d, const float* const* hsrc, int nsrc, const float* hprev, float* hcur, int W,
+                    int col_base, int f_begin, int f_end, int level, int S, const unsigned int* small_mask, float l2,
+                    int score_fn, float random_strength, const double* scal, const int* iter_ptr,
+                    unsigned long long seed, float lr, unsigned long long* best_key, cudaStream_t st) {
+    CbScoreArgs a;
+    cb_fill_score_args(a, d, hsrc, nsrc, hprev, hcur, W, col_base, f_begin, f_end, level, S, small_mask, l2, score_fn,
+                       random_strength, scal, iter_ptr, seed, lr, best_key);
+    const int nf = f_end - f_begin;
+    if (nf <= 0) return 0;
+    const int grid = (nf + 7) / 8;
+    cb_score_kernel<<<grid, 256, 0, st>>>(a);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+__global__ void __launch_bounds__(256) cb_select_local_kernel(CbScoreArgs a, unsigned long long* msg) {
+    cb_select_local(a, msg);
+}
+
+CB_API int cb_select_local_launch(const CbData* d, float* hcur, int W, int col_base, int level, int S,
+                                  unsigned long long* best_key, unsigned long long* msg, cudaStream_t st) {
+    CbScoreArgs a;
+    const float* none[1] = {nullptr};
+    cb_fill_score_args(a, d, none, 0, nullptr, hcur, W, col_base, 0, 0, level, S, nullptr, 0.f, 0, 0.f, nullptr, nullptr,
+                       0ull, 0.f, best_key);
+    cb_select_local_kernel<<<1, 256, 0, st>>>(a, msg);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+struct CbMsgPtrs { const unsigned long long* p[CB_MAX_RANKS]; };
+
+__global__ void __launch_bounds__(256) cb_select_final_kernel(CbData d, CbMsgPtrs m, int nmsg, int level, CbSplit* splits,
+                                                              const int* iter_ptr, int depth, unsigned int* mask_out,
+                                                              unsigned long long* best_key) {
+    cb_select_final(d, m.p, nmsg, level, splits + (long long)(*iter_ptr) * depth + level, mask_out);
+    if (threadIdx.x == 0) *best_key = 0ull;
+}
+
+CB_API int cb_select_final_launch(const CbData* d, const unsigned long long* msgs, int nmsg, long long msg_stride_bytes,
+                                  int level, CbSplit* splits, const int* iter_ptr, int depth, unsigned int* mask_out,
+                                  unsigned long long* best_key, cudaStream_t st) {
+    CbMsgPtrs m;
+    for (int r = 0; r < CB_MAX_RANKS; ++r)
+        m.p[r] = r < nmsg ? reinterpret_cast<const unsigned long long*>(reinterpret_cast<const char*>(msgs) + r * msg_stride_bytes)
+                          : nullptr;
+    cb_select_final_kernel<<<1, 256, 0, st>>>(*d, m, nmsg, level, splits, iter_ptr, depth, mask_out, best_key);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+CB_API int cb_select_msg_bytes() { return CB_SELECT_MSG_BYTES; }
+
+// ======================================================================================================
+// Small all-reduce through the peer-mapped mailboxes (device functions in cb_comm.cuh).
+__global__ void __launch_bounds__(256) cb_allreduce_sum_kernel(CbComm c, double* vals, int count) {
+    cb_mailbox_allreduce_sum(c, vals, count);
+}
+
+CB_API int cb_allreduce_sum(const CbComm* c, double* vals, int count, cudaStream_t st) {
+    if (count * 8 > c->mbox_bytes) return (int)cudaErrorInvalidValue;
+    cb_allreduce_sum_kernel<<<1, 256, 0, st>>>(*c, vals, count);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ======================================================================================================
+// K8  leaf estimation pass: per-leaf sums of (w*der, w*hess, w) at approx + delta[leaf], then the
+// Newton / gradient step by the last block to finish (and across ranks through the mailbox).
+// catboost/cuda/methods/leaves_estimation/descent_helpers.cpp:127-206, pointwise_oracle.cpp:86-116.
+struct CbLeafArgs {
+    int loss; float p0, p1;
+    const float* approx; const float* target; const float* weight; const unsigned short* leaf;
+    const float* ext_der; const float* ext_hess;
+    long long n; int L;
+    float* delta;            // [L] running leaf values of this tree (unscaled)
+    double* sums;            // [L][3], zero on entry, zeroed again on exit
+    unsigned int* counter;   // zero on entry/exit
+    int first, last, newton;
+    float l2, lr;
+    float* cur_vals;         // [L] lr * delta after the last pass (applied by the next derivative kernel)
+    float* model_vals; float* model_wts; int Lstride; const int* iter_ptr;
+    CbComm c;
+};
+
+__global__ void __launch_bounds__(256) cb_leaf_pass_kernel(CbLeafArgs a) {
+    extern __shared__ float sl[];     // [3][L] when L fits, else unused
+    const int L = a.L;
+    const bool use_sh = L <= 4096;
+    if (use_sh) {
+        for (int i = threadIdx.x; i < 3 * L; i += blockDim.x) sl[i] = 0.0f;
+        __syncthreads();
+    }
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
+        const int l = a.leaf[i];
+        const float w = a.weight ? a.weight[i] : 1.0f;
+        CbLossOut o;
+        if (a.loss == CB_LOSS_EXTERNAL) { o.der = a.ext_der[i]; o.hess = a.ext_hess ? a.ext_hess[i] : 1.0f; }
+        else {
+            const float ap = a.approx[i] + (a.first ? 0.0f : a.delta[l]);
+            o = cb_loss_eval(a.loss, a.p0, a.p1, ap, a.target[i]);
+        }
+        if (use_sh) {
+            atomicAdd(&sl[l], w * o.der);
+            atomicAdd(&sl[L + l], w * o.hess);
+            atomicAdd(&sl[2 * L + l], w);
+        } else {
+            atomicAdd(&a.sums[3 * l], (double)(w * o.der));
+            atomicAdd(&a.sums[3 * l + 1], (double)(w * o.hess));
+            atomicAdd(&a.sums[3 * l + 2], (double)w);
+        }
+    }
+    if (use_sh) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 3 * L; i += blockDim.x) {
+            const float v = sl[i];
+            if (v != 0.0f) atomicAdd(&a.sums[3 * (i % L) + i / L], (double)v);
+        }
+    }
+    __shared__ bool s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(a.counter, 1u) == gridDim.x - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (a.c.nranks > 1) {
+        for (int base = 0; base < 3 * L; base += a.c.mbox_bytes / 8) {
+            cb_mailbox_allreduce_sum(a.c, a.sums + base, min(3 * L - base, a.c.mbox_bytes / 8));
+        }
+    }
+    const int it = *a.iter_ptr;
+    for (int l = threadIdx.x; l < L; l += blockDim.x) {
+        const double sd = a.sums[3 * l], shs = a.sums[3 * l + 1], sw = a.sums[3 * l + 2];
+        const double den = (a.newton ? shs : sw) + (double)a.l2;
+        const float step = (den > 0.0) ? (float)(sd / den) : 0.0f;
+        const float v = (a.first ? 0.0f : a.delta[l]) + step;
+        a.delta[l] = v;
+        if (a.last) {
+            a.cur_vals[l] = a.lr * v;
+            if (a.model_vals) a.model_vals[(long long)it * a.Lstride + l] = a.lr * v;
+            if (a.model_wts) a.model_wts[(long long)it * a.Lstride + l] = (float)sw;
+        }
+        a.sums[3 * l] = 0.0; a.sums[3 * l + 1] = 0.0; a.sums[3 * l + 2] = 0.0;
+    }
+    if (threadIdx.x == 0) *a.counter = 0u;
+}
+
+CB_API int cb_leaf_pass(int loss, float p0, float p1, const float* approx, const float* target, const float* weight,
+                        const unsigned short* leaf, const float* ext_der, const float* ext_hess, long long n, int L,
+                        float* delta, double* sums, unsigned int* counter, int first, int last, int newton, float l2,
+                        float lr, float* cur_vals, float* model_vals, float* model_wts, int Lstride,
+                        const int* iter_ptr, const CbComm* comm, int grid, cudaStream_t st) {
+    CbLeafArgs a{loss, p0, p1, approx, target, weight, leaf, ext_der, ext_hess, n, L, delta, sums, counter,
+                 first, last, newton, l2, lr, cur_vals, model_vals, model_wts, Lstride, iter_ptr, CbComm()};
+    if (comm) a.c = *comm; else { a.c.nranks = 1; a.c.rank = 0; }
+    const int smem = (L <= 4096) ? 3 * L * 4 : 0;
+    cb_leaf_pass_kernel<<<grid, 256, smem, st>>>(a);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ======================================================================================================
+// End of a boosting iteration: record the learn loss and the per-iteration extras (evaluation-set metric
+// sums), clear the accumulators, advance the counter.
+__global__ void cb_iter_end_kernel(int* iter_ptr, double* scal, double* loss_hist, double* extra_src, double* extra_dst,
+                                   int n_extra) {
+    const int it = *iter_ptr;
+    if (loss_hist) { loss_hist[2 * it] = scal[0]; loss_hist[2 * it + 1] = scal[1]; }
+    scal[0] = scal[1] = scal[2] = scal[3] = 0.0;
+    for (int k = 0; k < n_extra; ++k) { extra_dst[(long long)it * n_extra + k] = extra_src[k]; extra_src[k] = 0.0; }
+    *iter_ptr = it + 1;
+}
+CB_API int cb_iter_end(int* iter_ptr, double* scal, double* loss_hist, double* extra_src, double* extra_dst, int n_extra,
+                       cudaStream_t st) {
+    cb_iter_end_kernel<<<1, 1, 0, st>>>(iter_ptr, scal, loss_hist, extra_src, extra_dst, n_extra);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ======================================================================================================
+// K9  apply one oblivious tree to a binned set (evaluation sets during training):
+// leaf = sum_d bit_d << d, approx[dim][i] += vals[leaf*dims + dim]   (models/kernel/add_model_value.cu:70)
+__global__ void __launch_bounds__(256) cb_apply_tree_bins_kernel(CbData d, float* approx, long long approx_stride,
+                                                                 const CbSplit* splits, const int* iter_ptr, int depth,
+                                                                 const float* vals, int dims) {
+    __shared__ CbSplit sp[16];
+    const CbSplit* base = splits + (iter_ptr ? (long long)(*iter_ptr) * depth : 0);
+    if (threadIdx.x < depth) sp[threadIdx.x] = base[threadIdx.x];
+    __syncthreads();
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < d.n; i += stride) {
+        int leaf = 0;
+        for (int k = 0; k < depth; ++k) {
+            const CbSplit s = sp[k];
+            if (s.feature < 0) continue;
+            const uint32_t w = d.bins[(long long)(s.feature >> 2) * d.npad + i];
+            const unsigned int b = (w >> ((s.feature & 3) * 8)) & 255u;
+            const unsigned int bit = (s.flags & 1) ? (b == (unsigned)s.bin) : (b > (unsigned)s.bin);
+            leaf |= bit << k;
+        }
+        for (int k = 0; k < dims; ++k) approx[k * approx_stride + i] += vals[leaf * dims + k];
+    }
+}
+
+CB_API int cb_apply_tree_bins(const CbData* d, float* approx, long long approx_stride, const CbSplit* splits,
+                              const int* iter_ptr, int depth, const float* vals, int dims, int grid, cudaStream_t st) {
+    if (depth > 16) return (int)cudaErrorInvalidValue;
+    cb_apply_tree_bins_kernel<<<grid, 256, 0, st>>>(*d, approx, approx_stride, splits, iter_ptr, depth, vals, dims);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// leaf index only (used by the multi-dimensional and ranking trainers that update cursors themselves)
+__global__ void __launch_bounds__(256) cb_leaf_index_kernel(CbData d, unsigned short* leaf, const CbSplit* splits, int depth) {
+    __shared__ CbSplit sp[16];
+    if (threadIdx.x < depth) sp[threadIdx.x] = splits[threadIdx.x];
+    __syncthreads();
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < d.n; i += stride) {
+        int leaf_i = 0;
+        for (int k = 0; k < depth; ++k) {
+            const CbSplit s = sp[k];
+            if (s.feature < 0) continue;
+            const uint32_t w = d.bins[(long long)(s.feature >> 2) * d.npad + i];
+            const unsigned int b = (w >> ((s.feature & 3) * 8)) & 255u;
+            leaf_i |= ((s.flags & 1) ? (b == (unsigned)s.bin) : (b > (unsigned)s.bin)) << k;
+        }
+        leaf[i] = (unsigned short)leaf_i;
+    }
+}
+CB_API int cb_leaf_index(const CbData* d, unsigned short* leaf, const CbSplit* splits, int depth, int grid, cudaStream_t st) {
+    if (depth > 16) return (int)cudaErrorInvalidValue;
+    cb_leaf_index_kernel<<<grid, 256, 0, st>>>(*d, leaf, splits, depth);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ======================================================================================================
+// K14  batch apply of an oblivious-tree ensemble to raw float rows (inference).  Quantisation is fused:
+// a block stages the bins of 256 rows for the features the model uses (shared memory, one byte each),
+// then walks all trees; leaf values are read through the read-only path.  libs/model/cuda/evaluator.cu:85-343.
+struct CbPredictArgs {
+    const float* X; long long n; long long ldx;
+    const int* used_feat;        // [U] column of X for used feature u
+    const float* borders;        // concatenated borders of the used features
+    const int* border_off;       // [U+1]
+    const unsigned char* nan_is_max;   // [U] or null
+    int U;
+    const int* tree_depth;       // [T]
+    const int* tree_split_off;   // [T] first split of tree t in split_feat/split_bin
+    const unsigned short* split_feat;   // used-feature index
+    const unsigned char* split_bin;     // go right when bin > split_bin
+    const long long* tree_leaf_off;     // [T] first leaf value (in units of dims)
+    const float* leaf_vals;      // [sum leaves][dims]
+    int T; int dims;
+    float scale; const float* bias;   // [dims]
+    float* out;                  // [dims][n]
+};
+
+__global__ void __launch_bounds__(256) cb_predict_kernel(CbPredictArgs a) {
+    extern __shared__ unsigned char sb[];     // [U][256]
+    const long long row0 = (long long)blockIdx.x * 256;
+    const int nrow = (int)min((long long)256, a.n - row0);
+    // quantise: thread = row, loop over features (rows are read with stride ldx; L1 absorbs the re-use)
+    for (int u = 0; u < a.U; ++u) {
+        if (threadIdx.x < nrow) {
+            const float v = a.X[(row0 + threadIdx.x) * a.ldx + a.used_feat[u]];
+            const int b0 = a.border_off[u], b1 = a.border_off[u + 1];
+            int bin;
+            if (v != v) bin = (a.nan_is_max && a.nan_is_max[u]) ? (b1 - b0) : 0;
+            else {
+                int lo = b0, hi = b1;
+                while (lo < hi) { const int mid = (lo + hi) >> 1; if (__ldg(a.borders + mid) < v) lo = mid + 1; else hi = mid; }
+                bin = lo - b0;
+            }
+            sb[u * 256 + threadIdx.x] = (unsigned char)bin;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x >= nrow) return;
+    float acc[8];
+    const int dims = min(a.dims, 8);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+    for (int t = 0; t < a.T; ++t) {
+        const int depth = a.tree_depth[t];
+        const int so = a.tree_split_off[t];
+        int leaf = 0;
+        for (int k = 0; k < depth; ++k) {
+            const unsigned int b = sb[(int)a.split_feat[so + k] * 256 + threadIdx.x];
+            leaf |= (b > (unsigned int)a.split_bin[so + k]) << k;
+        }
+        const float* lv = a.leaf_vals + (a.tree_leaf_off[t] + leaf) * a.dims;
+        for (int k = 0; k < dims; ++k) acc[k] += __ldg(lv + k);
+    }
+    for (int k = 0; k < dims; ++k) a.out[(long long)k * a.n + row0 + threadIdx.x] = acc[k] * a.scale + (a.bias ? a.bias[k] : 0.0f);
+}
+
+CB_API int cb_predict_oblivious(const float* X, long long n, long long ldx, const int* used_feat, const float* borders,
+                                const int* border_off, const unsigned char* nan_is_max, int U, const int* tree_depth,
+                                const int* tree_split_off, const unsigned short* split_feat,
+                                const unsigned char* split_bin, const long long* tree_leaf_off, const float* leaf_vals,
+                                int T, int dims, float scale, const float* bias, float* out, cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (dims > 8 || U * 256 > 200 * 1024) return (int)cudaErrorInvalidValue;
+    CbPredictArgs a{X, n, ldx, used_feat, borders, border_off, nan_is_max, U, tree_depth, tree_split_off, split_feat,
+                    split_bin, tree_leaf_off, leaf_vals, T, dims, scale, bias, out};
+    static int set = 0;
+    if (!set) {
+        cudaError_t e = cudaFuncSetAttribute(cb_predict_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        set = 1;
+    }
+    cb_predict_kernel<<<(unsigned)((n + 255) / 256), 256, U * 256, st>>>(a);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ======================================================================================================
+// K15  metric partial sums on device: out[0] += sum w*loss, out[1] += sum w   (same loss math as training).
+// With `vals`/`leaf` the pending tree is added on the fly (approx + vals[leaf]), so the learn metric after the
+// newest tree can be read without touching the cursor.
+__global__ void __launch_bounds__(256) cb_metric_kernel(int loss, float p0, float p1, const float* approx,
+                                                        const float* target, const float* weight, long long n,
+                                                        const unsigned short* leaf, const float* vals, double* out) {
+    double s = 0.0, sw = 0.0;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float w = weight ? weight[i] : 1.0f;
+        const float a = approx[i] + (vals ? vals[leaf[i]] : 0.0f);
+        s += (double)(w * cb_loss_eval(loss, p0, p1, a, target[i]).value);
+        sw += (double)w;
+    }
+    s = cb_warp_sum_d(s); sw = cb_warp_sum_d(sw);
+    __shared__ double red[2][8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { red[0][warp] = s; red[1][warp] = sw; }
+    __syncthreads();
+    if (threadIdx.x < 2) {
+        double t = 0.0;
+        for (int k = 0; k < (blockDim.x >> 5); ++k) t += red[threadIdx.x][k];
+        atomicAdd(out + threadIdx.x, t);
+    }
+}
+CB_API int cb_metric_sum(int loss, float p0, float p1, const float* approx, const float* target, const float* weight,
+                         long long n, const unsigned short* leaf, const float* vals, double* out, int grid,
+                         cudaStream_t st) {
+    cb_metric_kernel<<<grid, 256, 0, st>>>(loss, p0, p1, approx, target, weight, n, leaf, vals, out);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+CB_API int cb_device_info(int* sm_count, int* max_smem_optin) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    cudaDeviceGetAttribute(sm_count, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    return 0;
+}

@@ -1,0 +1,428 @@
+// Device-side building blocks of one tree level: leaf-index update, streaming histogram accumulation,
+// slot reduction + sibling subtraction + bin scan + split scoring, and best-split selection.
+// They are used twice: by the stand-alone kernels (one launch per step; also the path that the
+// NCCL-reduce-scatter baseline uses) and by the fused cooperative level kernel in cb_fused.cu.
+//
+// Behaviour reproduced from the reference (not its code): histogram contents and the sibling subtraction
+// (catboost/cuda/methods/kernel/pointwise_hist2.cu:39-75), the bin prefix scan
+// (split_properties_helpers.cuh:112-200), score functions (score_calcers.cuh:11-188), gain tie-break by
+// (score, feature, bin) (catboost/cuda/gpu_data/gpu_structures.h:80-94) and the per-document leaf bit
+// (catboost/cuda/gpu_data/kernel/split.cu:179).
+#pragma once
+#include "cb_common.cuh"
+
+enum CbScoreFn : int { CB_SCORE_COSINE = 0, CB_SCORE_L2 = 1, CB_SCORE_SOLAR = 2, CB_SCORE_LOO = 3, CB_SCORE_SAT = 4 };
+
+struct CbSplit {       // one record per (tree, level)
+    int feature;       // flat feature index of the binned store (-1 = no split found)
+    int bin;           // go right when bin(doc) > bin  (one-hot: bin(doc) == bin)
+    float score;
+    int flags;         // bit0 = one-hot comparison
+};
+
+struct CbData {        // the binned training shard of this rank
+    const uint32_t* bins;
+    long long npad;
+    long long n;
+    int G;
+    int F;
+    const int* feat_off;            // [F+1], multiples of 4
+    const int* feat_nb;             // [F] real bin count (borders + 1), <= 256
+    const unsigned char* feat_onehot;   // [F] or null
+    const float* feat_weight;       // [F] gain multiplier (0 = ignored feature) or null
+    int TB;                         // feat_off[F]
+};
+
+struct CbHistArgs {
+    CbData d;
+    const unsigned short* leaf;
+    const float* stats;      // [S][npad]
+    int S;
+    int level;               // slots = level == 0 ? 1 : 1 << (level-1); slot = leaf & (slots-1)
+    const unsigned int* small_mask;   // bit p set: the RIGHT child of parent p is the one accumulated
+    int slots_per_pass;
+    int B;                   // shared-memory bin stride per feature (max feat_nb rounded up to 4... <= 256)
+    float* out;              // [slots][S][TB]  (zeroed by the caller)
+    // Non-symmetric trees (depthwise / lossguide): leaf holds a node id and slot_table[node] is the slot the
+    // document is accumulated into (-1 = skip).  When slot_table is set, level/small_mask are ignored.
+    const short* slot_table;
+    int nslots_table;
+};
+
+__device__ __forceinline__ int cb_hist_nslots(const CbHistArgs& a) {
+    return a.slot_table ? a.nslots_table : (a.level == 0 ? 1 : (1 << (a.level - 1)));
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Leaf update: leaf |= bit << (level) for the split chosen at `level`.
+__device__ __forceinline__ void cb_update_leaf_range(const CbData& d, unsigned short* leaf, CbSplit sp, int level,
+                                                     long long tid, long long nthreads) {
+    if (sp.feature < 0) return;
+    const uint32_t* col = d.bins + (long long)(sp.feature >> 2) * d.npad;
+    const int sh = (sp.feature & 3) * 8;
+    const bool onehot = sp.flags & 1;
+    const long long n4 = (d.n + 3) >> 2;
+    for (long long q = tid; q < n4; q += nthreads) {
+        const long long i = q << 2;
+        uint4 w = *reinterpret_cast<const uint4*>(col + i);
+        ushort4 lf = *reinterpret_cast<ushort4*>(leaf + i);
+        unsigned int b0 = (w.x >> sh) & 255u, b1 = (w.y >> sh) & 255u, b2 = (w.z >> sh) & 255u, b3 = (w.w >> sh) & 255u;
+        unsigned int t = (unsigned int)sp.bin;
+        unsigned int r0 = onehot ? (b0 == t) : (b0 > t);
+        unsigned int r1 = onehot ? (b1 == t) : (b1 > t);
+        unsigned int r2 = onehot ? (b2 == t) : (b2 > t);
+        unsigned int r3 = onehot ? (b3 == t) : (b3 > t);
+        lf.x |= (unsigned short)(r0 << level);
+        lf.y |= (unsigned short)(r1 << level);
+        lf.z |= (unsigned short)(r2 << level);
+        lf.w |= (unsigned short)(r3 << level);
+        *reinterpret_cast<ushort4*>(leaf + i) = lf;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Histogram accumulation of one (feature group, document chunk, slot pass) into shared memory + flush.
+// sh layout: [slot][s][j][B]; S is a run-time value (2 for pointwise losses, K+1 for K-class losses).
+static __device__ void cb_hist_item(const CbHistArgs& a, float* sh, int g, long long d_begin, long long d_end,
+                             int slot_begin, int slot_count) {
+    const int B = a.B;
+    const int S = a.S;
+    const int total = slot_count * S * 4 * B;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) sh[i] = 0.0f;
+    __syncthreads();
+
+    const uint32_t* bg = a.d.bins + (long long)g * a.d.npad;
+    const int level = a.level;
+    const int nslots = cb_hist_nslots(a);
+    const unsigned int pmask = (unsigned int)(nslots - 1);
+    const int slot_stride = S * 4 * B;
+    for (long long i = d_begin + (long long)threadIdx.x * 4; i < d_end; i += (long long)blockDim.x * 4) {
+        const uint4 w = *reinterpret_cast<const uint4*>(bg + i);
+        const ushort4 lf = *reinterpret_cast<const ushort4*>(a.leaf + i);
+        const unsigned int wv[4] = {w.x, w.y, w.z, w.w};
+        const unsigned int lv[4] = {lf.x, lf.y, lf.z, lf.w};
+        int off[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            int slot = 0;
+            bool take = (i + k) < a.d.n;
+            if (a.slot_table) {
+                slot = a.slot_table[lv[k]];
+                take = take && (slot >= 0);
+            } else if (level > 0) {
+                const unsigned int p = lv[k] & pmask;
+                const unsigned int right = (lv[k] >> (level - 1)) & 1u;
+                const unsigned int want = (a.small_mask[p >> 5] >> (p & 31)) & 1u;
+                take = take && (right == want);
+                slot = (int)p;
+            }
+            slot -= slot_begin;
+            off[k] = (take && (unsigned)slot < (unsigned)slot_count) ? slot * slot_stride : -1;
+        }
+        for (int s = 0; s < S; ++s) {
+            const float4 t = *reinterpret_cast<const float4*>(a.stats + (long long)s * a.d.npad + i);
+            const float tv[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (off[k] >= 0) {
+                    float* base = sh + off[k] + s * 4 * B;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) atomicAdd(base + j * B + ((wv[k] >> (8 * j)) & 255u), tv[k]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // flush (skip zeros: most (slot, bin) cells of a chunk are empty at deep levels)
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const float v = sh[i];
+        if (v != 0.0f) {
+            const int bin = i % B;
+            const int r = i / B;
+            const int j = r & 3;
+            const int s = (r >> 2) % S;
+            const int slot = (r >> 2) / S;
+            const int f = g * 4 + j;
+            if (f < a.d.F && bin < a.d.feat_nb[f]) {
+                atomicAdd(a.out + ((size_t)(slot_begin + slot) * S + s) * a.d.TB + a.d.feat_off[f] + bin, v);
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// Static work split used by both launch styles: item -> (group, chunk).
+static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, int ncta) {
+    const int G = a.d.G;
+    const int nK = (ncta >= G) ? (ncta / G) : 1;
+    long long per = (a.d.n + nK - 1) / nK;
+    per = (per + 3) & ~3ll;
+    const int nslots = cb_hist_nslots(a);
+    const long long items = (long long)G * nK;
+    for (int sb = 0; sb < nslots; sb += a.slots_per_pass) {
+        const int sc = min(a.slots_per_pass, nslots - sb);
+        for (long long item = cta; item < items; item += ncta) {
+            const int g = (int)(item % G);
+            const long long k = item / G;
+            const long long b = k * per;
+            const long long e = min(a.d.n, b + per);
+            if (b < e) cb_hist_item(a, sh, g, b, e, sb, sc);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Scoring.  One warp per feature; lane owns bins [lane*bpl, lane*bpl + bpl), bpl = ceil(nb/32) <= 8.
+struct CbScoreArgs {
+    CbData d;
+    const float* hsrc[CB_MAX_RANKS];   // per-source partial histograms [slots][S][W]; summed in index order
+    int nsrc;
+    const float* hprev;     // [L/2][S][W] complete histograms of the parent level (level > 0)
+    float* hcur;            // [L][S][W]   complete histograms of this level (out)
+    int W;                  // row width (floats) of the buffers above
+    int col_base;           // buffer column = feat_off[f] - col_base + bin
+    int f_begin, f_end;     // features scored by this rank
+    int level;
+    int S;
+    const unsigned int* small_mask;
+    float l2;
+    int score_fn;
+    float random_strength;
+    const double* scal;     // [0]=sum w*loss [1]=sum w [2]=sum (w*der)^2 [3]=docs   (this iteration)
+    const int* iter_ptr;
+    unsigned long long seed;
+    float learning_rate;
+    unsigned long long* best_key;
+};
+
+__device__ __forceinline__ void cb_score_add_leaf(int fn, float l2, float s, float w, float& num, float& den) {
+    switch (fn) {
+        default:
+        case CB_SCORE_COSINE: {
+            const float mu = (w > 0.0f) ? s / (w + l2) : 0.0f;
+            num += s * mu;
+            den += w * mu * mu;
+            break;
+        }
+        case CB_SCORE_L2:
+            num += (w > 1e-20f) ? s * s / (w + l2) : 0.0f;
+            break;
+        case CB_SCORE_SOLAR:
+            num += (w > 1e-20f) ? s * s * (1.0f + 2.0f * __logf(w + 1.0f)) / w : 0.0f;
+            break;
+        case CB_SCORE_LOO: {
+            float adj = (w > 1.0f) ? w / (w - 1.0f) : 0.0f;
+            num += (w > 0.0f) ? adj * adj * s * s / w : 0.0f;
+            break;
+        }
+        case CB_SCORE_SAT: {
+            float adj = (w > 2.0f) ? w * (w - 2.0f) / (w * w - 3.0f * w + 1.0f) : 0.0f;
+            num += (w > 0.0f) ? adj * s * s / w : 0.0f;
+            break;
+        }
+    }
+}
+
+__device__ __forceinline__ float cb_noise_std(const CbScoreArgs& a) {
+    if (a.random_strength <= 0.0f) return 0.0f;
+    const double docs = a.scal[3];
+    if (docs <= 0.0) return 0.0f;
+    const double sd = sqrt(a.scal[2] / docs);
+    // modelLengthMult = m/(1+m), m = exp(ln N - iteration*learning_rate)
+    const double m = exp(log(docs) - (double)(*a.iter_ptr) * a.learning_rate);
+    return (float)(a.random_strength * sd * (m / (1.0 + m)));
+}
+
+static __device__ void cb_score_feature(const CbScoreArgs& a, int f, float noise_std) {
+    const int lane = threadIdx.x & 31;
+    const int nb = a.d.feat_nb[f];
+    const float fw = a.d.feat_weight ? a.d.feat_weight[f] : 1.0f;
+    const int col0 = a.d.feat_off[f] - a.col_base;
+    const int bpl = (nb + 31) >> 5;
+    const bool onehot = a.d.feat_onehot && a.d.feat_onehot[f];
+    const int S = a.S;
+    const int L = 1 << a.level;
+    const int half = L >> 1;
+    float num[8], den[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { num[k] = 0.0f; den[k] = 0.0f; }
+
+    for (int l = 0; l < L; ++l) {
+        int p = 0;
+        bool computed = true;
+        if (a.level > 0) {
+            p = l & (half - 1);
+            const unsigned int right = (unsigned int)l >> (a.level - 1);
+            computed = (((a.small_mask[p >> 5] >> (p & 31)) & 1u) == right);
+        }
+        float wl[8];
+        float wtot = 0.0f;
+        for (int pass = 0; pass < S; ++pass) {
+            const int st = (pass == 0) ? (S - 1) : (pass - 1);   // weight column first
+            float v[8];
+            float run = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int bin = lane * bpl + k;
+                float x = 0.0f;
+                if (k < bpl && bin < nb) {
+                    const size_t idx = ((size_t)p * S + st) * a.W + col0 + bin;
+                    for (int r = 0; r < a.nsrc; ++r) x += a.hsrc[r][idx];
+                    if (!computed) x = a.hprev[idx] - x;
+                    if (a.hcur) a.hcur[((size_t)l * S + st) * a.W + col0 + bin] = x;
+                }
+                run += x;
+                v[k] = onehot ? x : run;     // inclusive prefix inside the lane
+            }
+            // exclusive scan of lane totals
+            float inc = run;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float t = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += t;
+            }
+            const float excl = inc - run;
+            const float total = __shfl_sync(0xffffffffu, inc, 31);
+            if (pass == 0) {
+                wtot = total;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) wl[k] = onehot ? v[k] : (excl + v[k]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (k < bpl) {
+                        const float sl = onehot ? v[k] : (excl + v[k]);
+                        const float sr = total - sl;
+                        const float wL = fmaxf(wl[k], 0.0f);
+                        const float wR = fmaxf(wtot - wl[k], 0.0f);
+                        cb_score_add_leaf(a.score_fn, a.l2, sl, wL, num[k], den[k]);
+                        cb_score_add_leaf(a.score_fn, a.l2, sr, wR, num[k], den[k]);
+                    }
+                }
+            }
+        }
+    }
+    // best candidate of this lane; borders are bins 0 .. nb-2 (one-hot: every value 0 .. nb-1)
+    unsigned long long best = 0ull;
+    if (fw > 0.0f) {
+        const int ncand = onehot ? nb : nb - 1;
+        const unsigned long long it = (unsigned long long)(*a.iter_ptr);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int bin = lane * bpl + k;
+            if (k < bpl && bin < ncand) {
+                float sc;
+                if (a.score_fn == CB_SCORE_COSINE) sc = (den[k] > 1e-15f) ? num[k] * rsqrtf(den[k] + 1e-10f) : -3.0e38f;
+                else sc = num[k];
+                const unsigned int gb = (unsigned int)(a.d.feat_off[f] + bin);
+                if (noise_std > 0.0f) {
+                    const unsigned long long h = cb_mix64(a.seed ^ cb_mix64((it << 8) + a.level) ^ ((unsigned long long)gb * 0x9E3779B97F4A7C15ull));
+                    sc += cb_normal(h) * noise_std;
+                }
+                sc *= fw;
+                if (sc == sc) {
+                    const unsigned long long key = ((unsigned long long)cb_float_to_ordered(sc) << 32) | (unsigned long long)(0xFFFFFFFFu - gb);
+                    best = key > best ? key : best;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long t = __shfl_xor_sync(0xffffffffu, best, o);
+        best = t > best ? t : best;
+    }
+    if (lane == 0 && best) atomicMax(a.best_key, best);
+}
+
+static __device__ void cb_score_phase(const CbScoreArgs& a, int cta, int ncta) {
+    const int warps_per_cta = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5;
+    const float noise_std = cb_noise_std(a);
+    for (int f = a.f_begin + cta * warps_per_cta + warp; f < a.f_end; f += ncta * warps_per_cta) {
+        cb_score_feature(a, f, noise_std);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Selection.  Message layout (unsigned long long words): [0] = key, [1..] = small-mask words for the next
+// level packed two uint32 per word.  CB_SELECT_WORDS bounds the depth: 2^(depth-1) mask bits.
+#define CB_SELECT_MAX_MASK_U32 1024     // depth <= 16  ->  2^15 bits = 1024 uint32
+#define CB_SELECT_MSG_BYTES (8 + CB_SELECT_MAX_MASK_U32 * 4)
+
+__device__ __forceinline__ int cb_find_feature(const int* feat_off, int F, int gb) {
+    int lo = 0, hi = F - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (feat_off[mid] <= gb) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+// One block.  Writes this rank's message: key + mask of "right child is the lighter one" per leaf of `level`.
+static __device__ void cb_select_local(const CbScoreArgs& a, unsigned long long* msg) {
+    __shared__ int s_f, s_bin;
+    const unsigned long long key = *a.best_key;
+    unsigned int* mask = reinterpret_cast<unsigned int*>(msg + 1);
+    const int L = 1 << a.level;
+    const int nwords = (L + 31) >> 5;
+    if (threadIdx.x == 0) {
+        msg[0] = key;
+        if (key) {
+            const int gb = (int)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull));
+            s_f = cb_find_feature(a.d.feat_off, a.d.F, gb);
+            s_bin = gb - a.d.feat_off[s_f];
+        } else { s_f = -1; s_bin = 0; }
+    }
+    for (int i = threadIdx.x; i < nwords; i += blockDim.x) mask[i] = 0u;
+    __syncthreads();
+    if (s_f < 0 || a.hcur == nullptr) return;
+    const int f = s_f, bin = s_bin;
+    const int nb = a.d.feat_nb[f];
+    const int col0 = a.d.feat_off[f] - a.col_base;
+    const bool onehot = a.d.feat_onehot && a.d.feat_onehot[f];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int l = warp; l < L; l += nwarps) {
+        const float* row = a.hcur + ((size_t)l * a.S + (a.S - 1)) * a.W + col0;
+        float wl = 0.0f, wt = 0.0f;
+        for (int b = lane; b < nb; b += 32) {
+            const float x = row[b];
+            wt += x;
+            if (onehot ? (b != bin) : (b <= bin)) wl += x;
+        }
+        wl = cb_warp_sum(wl);
+        wt = cb_warp_sum(wt);
+        if (lane == 0 && (wt - wl) < wl) atomicOr(&mask[l >> 5], 1u << (l & 31));
+    }
+}
+
+// One block.  Picks the best of `nmsg` messages (highest key; equal keys are identical candidates) and
+// publishes the split record and the small-child mask for the next level.
+static __device__ void cb_select_final(const CbData& d, const unsigned long long* const* msgs, int nmsg, int level,
+                                CbSplit* split_out, unsigned int* small_mask_out) {
+    __shared__ int s_best;
+    if (threadIdx.x == 0) {
+        unsigned long long bk = 0ull;
+        int bi = 0;
+        for (int r = 0; r < nmsg; ++r) {
+            const unsigned long long k = __ldcg(msgs[r]);
+            if (k > bk) { bk = k; bi = r; }
+        }
+        s_best = bi;
+        CbSplit sp;
+        if (bk) {
+            const int gb = (int)(0xFFFFFFFFu - (unsigned int)(bk & 0xFFFFFFFFull));
+            sp.feature = cb_find_feature(d.feat_off, d.F, gb);
+            sp.bin = gb - d.feat_off[sp.feature];
+            sp.score = cb_ordered_to_float((unsigned int)(bk >> 32));
+            sp.flags = (d.feat_onehot && d.feat_onehot[sp.feature]) ? 1 : 0;
+        } else {
+            sp.feature = -1; sp.bin = 0; sp.score = 0.0f; sp.flags = 0;
+        }
+        *split_out = sp;
+    }
+    __syncthreads();
+    const unsigned int* mask = reinterpret_cast<const unsigned int*>(msgs[s_best] + 1);
+    const int nwords = ((1 << level) + 31) >> 5;
+    for (int i = threadIdx.x; i < nwords; i += blockDim.x) small_mask_out[i] = __ldcg(mask + i);
+}

@@ -1,0 +1,422 @@
+"""General tree learner (any objective, any grow policy, CPU or GPU).
+
+Histograms come from the native kernels (``ops.api.hist``: CUDA shared-memory atomics on the GPU, OpenMP on the
+CPU); split scoring, leaf selection and leaf estimation are vectorised tensor code that runs on whichever device
+holds the store.  The flagship configuration (symmetric trees + pointwise loss on the GPU) does not come through
+here: ``gpu_engine.GpuObliviousEngine`` keeps that whole loop on the device.
+
+Reference behaviour reproduced: candidate = (feature, border) with statistics of the ``<=`` side from a bin prefix
+sum (catboost/cuda/methods/kernel/split_properties_helpers.cuh:112), score calcers
+(catboost/cuda/methods/kernel/score_calcers.cuh), SymmetricTree / Depthwise / Lossguide policies
+(catboost/cuda/methods/greedy_subsets_searcher/greedy_search_helper.cpp:320-700,
+catboost/private/libs/algo/greedy_tensor_search.cpp:1171,1467,1764), leaf estimation with several
+Newton / gradient steps (catboost/private/libs/algo/approx_calcer.cpp,
+catboost/cuda/methods/leaves_estimation/descent_helpers.cpp:127-206), exact quantile leaves
+(catboost/cuda/methods/kernel/exact_estimation.cu).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from ..data.quantization import BinnedStore
+from ..ops import api as ops
+
+
+@dataclass
+class TreeResult:
+    kind: str                                # 'oblivious' | 'nonsymmetric'
+    splits: Optional[np.ndarray] = None      # oblivious: int [depth, 4] (feature, bin, _, flags)
+    node_split: Optional[np.ndarray] = None  # nonsymmetric: int [nodes, 4] (feature, bin, flags, left_child)
+    leaf_of_node: Optional[np.ndarray] = None
+    n_leaves: int = 1
+    leaf: Optional[torch.Tensor] = None      # int16 [npad] leaf id of every training document
+
+
+class SplitScorer:
+    """Turns histograms [L, S, TB] into per-candidate score terms [L, F, Bmax]."""
+
+    def __init__(self, store: BinnedStore, score_function: str, l2: float):
+        self.store = store
+        dev = store.bins.device
+        F, B = store.F, max(1, store.max_bins)
+        off = torch.from_numpy(store.feat_off_host[:-1].astype(np.int64)).to(dev)
+        nb = torch.from_numpy(store.feat_nb_host.astype(np.int64)).to(dev)
+        ar = torch.arange(B, device=dev)
+        self.valid_bin = ar.unsqueeze(0) < nb.unsqueeze(1)                       # [F, B]
+        self.idx = torch.where(self.valid_bin, off.unsqueeze(1) + ar.unsqueeze(0), torch.zeros((), dtype=torch.long, device=dev))
+        self.onehot = store.feat_onehot.bool().unsqueeze(1)                      # [F, 1]
+        ncand = torch.where(self.onehot.squeeze(1), nb, nb - 1)
+        self.valid_cand = ar.unsqueeze(0) < ncand.unsqueeze(1)                   # [F, B]
+        self.fn = score_function
+        self.l2 = float(l2)
+        self.F, self.B = F, B
+
+    def sides(self, hist: torch.Tensor):
+        """left / right statistics of every candidate: each [L, S, F, B]."""
+        H = hist[:, :, self.idx] * self.valid_bin
+        cum = H.cumsum(-1)
+        total = cum[..., -1:]
+        left = torch.where(self.onehot, total - H, cum)      # one-hot: left = "value != v"
+        right = total - left
+        return left, right, total
+
+    def leaf_terms(self, s, w):
+        """(num, den) contribution of one side; s [L, K, F, B] sums, w [L, F, B] weights."""
+        w = w.clamp_min(0.0)
+        l2 = self.l2
+        fn = self.fn
+        if fn in ("Cosine", "NewtonCosine"):
+            mu = torch.where(w.unsqueeze(1) > 0, s / (w.unsqueeze(1) + l2), torch.zeros_like(s))
+            return (s * mu).sum(1), (w.unsqueeze(1) * mu * mu).sum(1)
+        if fn in ("L2", "NewtonL2"):
+            return torch.where(w.unsqueeze(1) > 1e-20, s * s / (w.unsqueeze(1) + l2), torch.zeros_like(s)).sum(1), None
+        if fn == "SolarL2":
+            ww = w.unsqueeze(1)
+            return torch.where(ww > 1e-20, s * s * (1 + 2 * torch.log(ww + 1)) / ww.clamp_min(1e-20), torch.zeros_like(s)).sum(1), None
+        if fn == "LOOL2":
+            ww = w.unsqueeze(1)
+            adj = torch.where(ww > 1, ww / (ww - 1).clamp_min(1e-20), torch.zeros_like(ww)) ** 2
+            return torch.where(ww > 0, adj * s * s / ww.clamp_min(1e-20), torch.zeros_like(s)).sum(1), None
+        if fn == "SatL2":
+            ww = w.unsqueeze(1)
+            adj = torch.where(ww > 2, ww * (ww - 2) / (ww * ww - 3 * ww + 1), torch.zeros_like(ww))
+            return torch.where(ww > 0, adj * s * s / ww.clamp_min(1e-20), torch.zeros_like(s)).sum(1), None
+        raise ValueError(fn)
+
+    def candidate_terms(self, hist: torch.Tensor, n_sum_stats: int, count_stat: Optional[int] = None):
+        """num/den [L, F, B] for every candidate, plus the child document counts when a count statistic exists."""
+        left, right, total = self.sides(hist)
+        K = n_sum_stats
+        nL, dL = self.leaf_terms(left[:, :K], left[:, K])
+        nR, dR = self.leaf_terms(right[:, :K], right[:, K])
+        num = nL + nR
+        den = None if dL is None else dL + dR
+        cnt = None
+        if count_stat is not None:
+            cnt = (left[:, count_stat], right[:, count_stat])
+        return num, den, cnt, (left, right, total)
+
+    def finish(self, num, den):
+        if den is not None:
+            return torch.where(den > 1e-15, num / torch.sqrt(den + 1e-10), torch.full_like(num, -3.0e38))
+        return num
+
+
+class GenericLearner:
+    def __init__(self, store: BinnedStore, opts, dims: int, ctx=None, seed: int = 0):
+        self.store, self.o, self.dims, self.ctx = store, opts, dims, ctx
+        self.dev = store.bins.device
+        self.scorer = SplitScorer(store, opts.score_function, float(opts.l2_leaf_reg))
+        self.gen = torch.Generator(device="cpu")
+        self.gen.manual_seed(int(seed) + 12345)
+        self.leaf = torch.zeros(store.npad, dtype=torch.int16, device=self.dev)
+        self.use_count = int(opts.min_data_in_leaf) > 1
+        self.n_total = store.n
+        if ctx is not None and ctx.is_distributed:
+            t = torch.tensor([store.n], dtype=torch.float64, device=self.dev)
+            ctx.all_reduce_sum_(t)
+            self.n_total = int(t.item())
+
+    # -- helpers ---------------------------------------------------------------------------------------
+    def _rand(self, shape):
+        return torch.rand(shape, generator=self.gen).to(self.dev)
+
+    def _randn(self, shape):
+        return torch.randn(shape, generator=self.gen).to(self.dev)
+
+    def bootstrap_weights(self, der: torch.Tensor) -> Optional[torch.Tensor]:
+        o, n = self.o, self.store.n
+        bt = o.bootstrap_type
+        if bt == "No":
+            return None
+        if bt == "Bayesian":
+            t = float(o.bagging_temperature)
+            if t == 0:
+                return None
+            return (-torch.log(self._rand(n).clamp_min(1e-20))) ** t
+        if bt == "Bernoulli":
+            return (self._rand(n) < float(o.subsample)).float()
+        if bt == "Poisson":
+            return torch.poisson(torch.full((n,), float(o.subsample)), generator=self.gen).to(self.dev)
+        if bt == "MVS":
+            # minimal-variance sampling (catboost/private/libs/algo/mvs.cpp): keep probability ~ |gradient|
+            g = torch.sqrt((der * der).sum(0)[:n] + (float(o.mvs_reg) if o.mvs_reg is not None else (der.abs().mean().item() ** 2)))
+            rate = float(o.subsample)
+            if rate >= 1.0:
+                return None
+            srt, _ = torch.sort(g)
+            csum = torch.cumsum(srt, 0)
+            k = torch.arange(1, n + 1, device=self.dev, dtype=g.dtype)
+            # sum_i min(1, g_i / mu) = rate * n.  With mu at the k-th order statistic the sum is
+            # csum_k / g_k + (n - k), decreasing in k; the crossing gives how many documents have g <= mu.
+            est = csum / srt.clamp_min(1e-30) + (n - k)
+            target = rate * n
+            cnt = int((est >= target).sum().item())
+            if cnt == 0:
+                return None
+            denom = target - (n - cnt)
+            mu = (csum[cnt - 1] / max(denom, 1e-12)).clamp_min(1e-30)
+            p = (g / mu).clamp(max=1.0)
+            keep = self._rand(n) < p
+            return torch.where(keep, 1.0 / p.clamp_min(1e-12), torch.zeros_like(p))
+        raise ValueError(bt)
+
+    def _hist(self, stats, slot_table, nslots):
+        h = ops.hist(self.store, self.leaf, stats, slot_table, nslots)
+        if self.ctx is not None and self.ctx.is_distributed:
+            self.ctx.all_reduce_sum_(h)
+        return h
+
+    def _noise_std(self, der, iteration):
+        rs = float(self.o.random_strength)
+        if rs <= 0:
+            return 0.0
+        n = self.store.n
+        ss = (der[:, :n] ** 2).sum().double()
+        if self.ctx is not None and self.ctx.is_distributed:
+            ss = ss.reshape(1)
+            self.ctx.all_reduce_sum_(ss)
+            ss = ss[0]
+        N = max(self.n_total, 1)
+        sd = math.sqrt(float(ss.item()) / N)
+        m = math.exp(math.log(N) - iteration * float(self.o.learning_rate))
+        return rs * sd * m / (1 + m)
+
+    def _feature_mask(self):
+        fw = self.store.feat_weight > 0
+        rsm = float(self.o.rsm)
+        if rsm < 1.0 and self.store.F > 1:
+            keep = self._rand(self.store.F) < rsm
+            if not bool((keep & fw).any()):
+                keep[int(torch.randint(0, self.store.F, (1,), generator=self.gen))] = True
+            fw = fw & keep
+        return fw
+
+    # -- structure search ------------------------------------------------------------------------------
+    def build_tree(self, der: torch.Tensor, hess: torch.Tensor, weight: Optional[torch.Tensor], iteration: int) -> TreeResult:
+        """der/hess: [dims, npad] (already multiplied by the sample weights)."""
+        o, n, npad = self.o, self.store.n, self.store.npad
+        newton = o.score_function.startswith("Newton")
+        bw = self.bootstrap_weights(der)
+        K = self.dims
+        rows = K + 1 + (1 if self.use_count else 0)
+        stats = torch.zeros((rows, npad), dtype=torch.float32, device=self.dev)
+        wcol = hess[:, :n].sum(0) / K if newton else (torch.ones(n, device=self.dev) if weight is None else weight[:n])
+        if bw is not None:
+            stats[:K, :n] = der[:, :n] * bw
+            stats[K, :n] = wcol * bw
+        else:
+            stats[:K, :n] = der[:, :n]
+            stats[K, :n] = wcol
+        if self.use_count:
+            stats[K + 1, :n] = 1.0
+        self.leaf.zero_()
+        noise_std = self._noise_std(der, iteration)
+        fmask = self._feature_mask()
+        if o.grow_policy == "SymmetricTree":
+            return self._grow_symmetric(stats, K, noise_std, fmask)
+        if o.grow_policy in ("Depthwise", "Region"):
+            return self._grow_depthwise(stats, K, noise_std, fmask)
+        return self._grow_lossguide(stats, K, noise_std, fmask)
+
+    def _cand_mask(self, fmask, cnt):
+        m = self.scorer.valid_cand & fmask.unsqueeze(1)
+        return m
+
+    def _grow_symmetric(self, stats, K, noise_std, fmask) -> TreeResult:
+        depth = int(self.o.depth)
+        sc = self.scorer
+        splits = np.full((depth, 4), 0, dtype=np.int32)
+        splits[:, 0] = -1
+        cstat = K + 1 if self.use_count else None
+        fw = self.store.feat_weight
+        for level in range(depth):
+            L = 1 << level
+            table = torch.arange(L, dtype=torch.int16, device=self.dev)
+            h = self._hist(stats, table, L)
+            num, den, cnt, _ = sc.candidate_terms(h, K, cstat)
+            score = sc.finish(num.sum(0), None if den is None else den.sum(0))          # [F, B]
+            if noise_std > 0:
+                score = score + self._randn(score.shape) * noise_std
+            score = score * fw.unsqueeze(1)
+            mask = self._cand_mask(fmask, cnt)
+            if cnt is not None:
+                mdl = int(self.o.min_data_in_leaf)
+                ok = ((cnt[0] >= mdl) | (cnt[0] == 0)).all(0) & ((cnt[1] >= mdl) | (cnt[1] == 0)).all(0)
+                mask = mask & ok
+            score = torch.where(mask, score, torch.full_like(score, -float("inf")))
+            best = int(torch.argmax(score.reshape(-1)).item())
+            f, b = best // sc.B, best % sc.B
+            if not math.isfinite(float(score[f, b].item())):
+                break
+            onehot = bool(self.store.feat_onehot[f].item())
+            splits[level] = (f, b, 0, 1 if onehot else 0)
+            ops.update_leaf(self.store, self.leaf, f, b, onehot, level)
+        return TreeResult("oblivious", splits=splits, n_leaves=1 << depth, leaf=self.leaf)
+
+    def _per_leaf_best(self, h, K, noise_std, fmask):
+        sc = self.scorer
+        cstat = K + 1 if self.use_count else None
+        num, den, cnt, (left, right, total) = sc.candidate_terms(h, K, cstat)
+        score = sc.finish(num, den)                                                   # [L, F, B]
+        # gain over not splitting (L2 form), used for leaf priority and for "no useful split" detection
+        w_tot = total[:, K, :, 0].clamp_min(0)
+        s_tot = total[:, :K, :, 0]
+        parent = (s_tot * s_tot / (w_tot.unsqueeze(1) + sc.l2)).sum(1)                 # [L, F]
+        l2num = (left[:, :K] ** 2 / (left[:, K].clamp_min(0).unsqueeze(1) + sc.l2)).sum(1) + \
+                (right[:, :K] ** 2 / (right[:, K].clamp_min(0).unsqueeze(1) + sc.l2)).sum(1)
+        gain = l2num - parent.unsqueeze(-1)
+        if noise_std > 0:
+            score = score + self._randn(score.shape) * noise_std
+        score = score * self.store.feat_weight.view(1, -1, 1)
+        mask = (sc.valid_cand & fmask.unsqueeze(1)).unsqueeze(0).expand_as(score)
+        nonempty = (left[:, K] > 0) & (right[:, K] > 0)
+        mask = mask & nonempty
+        if cnt is not None:
+            mdl = int(self.o.min_data_in_leaf)
+            mask = mask & (cnt[0] >= mdl) & (cnt[1] >= mdl)
+        score = torch.where(mask, score, torch.full_like(score, -float("inf")))
+        flat = score.reshape(score.shape[0], -1)
+        best = torch.argmax(flat, dim=1)
+        bscore = flat.gather(1, best.unsqueeze(1)).squeeze(1)
+        bgain = gain.reshape(gain.shape[0], -1).gather(1, best.unsqueeze(1)).squeeze(1)
+        return best.cpu().numpy(), bscore.cpu().numpy(), bgain.cpu().numpy()
+
+    def _grow_depthwise(self, stats, K, noise_std, fmask) -> TreeResult:
+        depth = int(self.o.depth)
+        B = self.scorer.B
+        node_split: List[List[int]] = [[-1, 0, 0, -1]]
+        frontier = [0]
+        for level in range(depth):
+            if not frontier:
+                break
+            table = torch.full((len(node_split),), -1, dtype=torch.int16, device=self.dev)
+            table[torch.tensor(frontier, device=self.dev)] = torch.arange(len(frontier), dtype=torch.int16, device=self.dev)
+            h = self._hist(stats, table, len(frontier))
+            best, bscore, _ = self._per_leaf_best(h, K, noise_std, fmask)
+            new_frontier = []
+            for j, node in enumerate(frontier):
+                if not math.isfinite(float(bscore[j])):
+                    continue
+                f, b = int(best[j]) // B, int(best[j]) % B
+                left = len(node_split)
+                node_split.append([-1, 0, 0, -1])
+                node_split.append([-1, 0, 0, -1])
+                node_split[node] = [f, b, 1 if bool(self.store.feat_onehot[f].item()) else 0, left]
+                new_frontier += [left, left + 1]
+            if not new_frontier:
+                break
+            ops.update_nodes(self.store, self.leaf, torch.tensor(node_split, dtype=torch.int32, device=self.dev))
+            frontier = new_frontier
+        return self._finish_nonsymmetric(node_split)
+
+    def _grow_lossguide(self, stats, K, noise_std, fmask) -> TreeResult:
+        max_leaves, max_depth = int(self.o.max_leaves), int(self.o.depth)
+        B = self.scorer.B
+        node_split: List[List[int]] = [[-1, 0, 0, -1]]
+        node_depth = [0]
+        cand = {}        # node -> (gain, feature, bin)
+
+        def evaluate(nodes):
+            table = torch.full((len(node_split),), -1, dtype=torch.int16, device=self.dev)
+            table[torch.tensor(nodes, device=self.dev)] = torch.arange(len(nodes), dtype=torch.int16, device=self.dev)
+            h = self._hist(stats, table, len(nodes))
+            best, bscore, bgain = self._per_leaf_best(h, K, noise_std, fmask)
+            for j, node in enumerate(nodes):
+                if math.isfinite(float(bscore[j])) and node_depth[node] < max_depth:
+                    cand[node] = (float(bgain[j]), int(best[j]) // B, int(best[j]) % B)
+
+        evaluate([0])
+        n_leaves = 1
+        while n_leaves < max_leaves and cand:
+            node = max(cand, key=lambda k: cand[k][0])
+            _, f, b = cand.pop(node)
+            left = len(node_split)
+            node_split += [[-1, 0, 0, -1], [-1, 0, 0, -1]]
+            node_depth += [node_depth[node] + 1] * 2
+            node_split[node] = [f, b, 1 if bool(self.store.feat_onehot[f].item()) else 0, left]
+            step = [[-1, 0, 0, -1]] * len(node_split)
+            step[node] = node_split[node]
+            ops.update_nodes(self.store, self.leaf, torch.tensor(step, dtype=torch.int32, device=self.dev))
+            n_leaves += 1
+            if n_leaves < max_leaves:
+                evaluate([left, left + 1])
+        return self._finish_nonsymmetric(node_split)
+
+    def _finish_nonsymmetric(self, node_split) -> TreeResult:
+        ns = np.array(node_split, dtype=np.int32)
+        leaf_of_node = np.full(len(ns), -1, dtype=np.int32)
+        terminal = np.nonzero(ns[:, 0] < 0)[0]
+        leaf_of_node[terminal] = np.arange(len(terminal), dtype=np.int32)
+        # relabel documents: node id -> leaf id
+        lut = torch.from_numpy(np.where(leaf_of_node >= 0, leaf_of_node, 0).astype(np.int16)).to(self.dev)
+        n = self.store.n
+        self.leaf[:n] = lut[self.leaf[:n].long() & 0xFFFF]
+        return TreeResult("nonsymmetric", node_split=ns, leaf_of_node=leaf_of_node, n_leaves=len(terminal), leaf=self.leaf)
+
+
+# ---------------------------------------------------------------------------------------------------------
+def estimate_leaves(objective, approx, target, weight, leaf, n_leaves, n, opts, ctx=None, obj_ctx=None,
+                    total_weight: Optional[float] = None):
+    """Leaf values [n_leaves, dims] (already multiplied by the learning rate) and leaf weights [n_leaves]."""
+    method, iters = opts.leaf_estimation_method, int(opts.leaf_estimation_iterations)
+    l2, lr = float(opts.l2_leaf_reg), float(opts.learning_rate)
+    dims = approx.shape[0]
+    dev = approx.device
+    idx = leaf[:n].long() & 0xFFFF
+    if method == "Exact":
+        return _exact_leaves(objective, approx, target, weight, idx, n_leaves, n, lr, ctx)
+    delta = torch.zeros((n_leaves, dims), dtype=torch.float32, device=dev)
+    wcol = torch.ones(n, dtype=torch.float32, device=dev) if weight is None else weight[:n]
+    leaf_w = None
+    prev_loss = None
+    for it in range(max(1, iters)):
+        a = approx[:, :n] if it == 0 else approx[:, :n] + delta[idx].t()
+        der, hess = objective.der_hess(a, target, weight if weight is None else weight[:n], obj_ctx)
+        cols = torch.cat([der, hess, wcol.unsqueeze(0)], 0)
+        sums = ops.leaf_sums(leaf, cols, n_leaves, n)
+        if ctx is not None and ctx.is_distributed:
+            ctx.all_reduce_sum_(sums)
+        sd, sh, sw = sums[:, :dims], sums[:, dims:2 * dims], sums[:, 2 * dims]
+        if leaf_w is None:
+            leaf_w = sw.clone()
+        den = (sh if method == "Newton" else sw.unsqueeze(1).expand_as(sd)) + l2
+        step = torch.where(den > 0, sd / den, torch.zeros_like(sd)).float()
+        delta = delta + step
+    if getattr(objective, "zero_mean_leaves", False):
+        tot = leaf_w.sum().clamp_min(1e-30)
+        delta = delta - ((delta.double() * leaf_w.unsqueeze(1)).sum(0) / tot).float()
+    return (delta * lr).double().cpu().numpy(), leaf_w.cpu().numpy()
+
+
+def _exact_leaves(objective, approx, target, weight, idx, n_leaves, n, lr, ctx):
+    """Weighted alpha-quantile of the residuals inside each leaf (MAE / Quantile / MAPE)."""
+    alpha = float(objective.params.get("alpha", 0.5)) if objective.name == "Quantile" else 0.5
+    res = (target - approx[0, :n]).double()
+    w = torch.ones_like(res) if weight is None else weight[:n].double()
+    if objective.name == "MAPE":
+        w = w / target.abs().clamp_min(1.0).double()
+    if ctx is not None and ctx.is_distributed:
+        import torch.distributed as dist
+        parts = ctx.all_gather_object((res.cpu(), w.cpu(), idx.cpu()))
+        res = torch.cat([p[0] for p in parts]).to(approx.device)
+        w = torch.cat([p[1] for p in parts]).to(approx.device)
+        idx = torch.cat([p[2] for p in parts]).to(approx.device)
+    order = torch.argsort(res, stable=True)
+    order = order[torch.argsort(idx[order], stable=True)]
+    li, r, ww = idx[order], res[order], w[order]
+    cw = torch.cumsum(ww, 0)
+    tot = torch.zeros(n_leaves, dtype=torch.float64, device=approx.device).index_add_(0, li, ww)
+    counts = torch.bincount(li, minlength=n_leaves)
+    starts = torch.cumsum(counts, 0) - counts
+    base = torch.where(starts > 0, cw[(starts - 1).clamp_min(0)], torch.zeros_like(tot))
+    thr = base + alpha * tot
+    pos = torch.searchsorted(cw, thr, right=False)
+    pos = torch.minimum(pos, (starts + counts - 1).clamp_min(0))
+    vals = torch.where(counts > 0, r[pos.clamp(max=max(len(r) - 1, 0))], torch.zeros_like(tot))
+    return (vals * lr).unsqueeze(1).cpu().numpy(), tot.cpu().numpy()

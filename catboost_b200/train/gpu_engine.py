@@ -1,0 +1,393 @@
+"""Device-resident trainer for symmetric (oblivious) trees with a one-dimensional pointwise objective.
+
+One boosting iteration is a fixed sequence of launches with no host read anywhere, captured once in a CUDA graph
+and replayed:
+
+    derivatives (+ cursor update by the previous tree, + bootstrap weights)
+    depth x fused level kernel  (leaf update -> histograms -> cross-GPU reduce-scatter -> score -> argmax)
+    final leaf update
+    leaf_estimation_iterations x leaf pass (per-leaf sums -> cross-GPU sum -> Newton / gradient step)
+    evaluation sets: apply the new tree + metric sums
+    bookkeeping (learn loss history, iteration counter)
+
+The reference drives the same steps from the host with two blocking device->host reads per level
+(catboost/cuda/methods/oblivious_tree_doc_parallel_structure_searcher.cpp:63-164) and bounces every
+leaf-estimation step through the CPU (leaves_estimation/descent_helpers.cpp:127-206).
+
+Multi-GPU: doc-parallel; each rank holds a row shard and all features.  ``reduce='fused'`` uses the in-kernel
+peer-store reduce-scatter; ``reduce='nccl'`` is the baseline (stand-alone kernels + NCCL all-reduce).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from ..data.quantization import BinnedStore
+from ..ops import native
+from ..parallel.runtime import ArenaLayout, DistContext, PeerArena, split_columns
+
+SCORE_FN = {"Cosine": (0, 0), "L2": (1, 0), "NewtonCosine": (0, 1), "NewtonL2": (1, 1), "SolarL2": (2, 0),
+            "LOOL2": (3, 0), "SatL2": (4, 0)}
+BOOTSTRAP = {"No": 0, "Bayesian": 1, "Bernoulli": 2, "Poisson": 3, "MVS": 2}
+
+
+def _p(t):
+    if t is None:
+        return None
+    return ctypes.c_void_p(t.data_ptr())
+
+
+class EvalSet:
+    def __init__(self, store: BinnedStore, target: torch.Tensor, weight: Optional[torch.Tensor], approx0: torch.Tensor):
+        self.store, self.target, self.weight = store, target, weight
+        self.approx = approx0
+
+
+class GpuObliviousEngine:
+    def __init__(self, store: BinnedStore, target: torch.Tensor, weight: Optional[torch.Tensor], approx0: torch.Tensor,
+                 objective, *, depth: int, iterations: int, learning_rate: float,
+                 l2_leaf_reg: float, score_function: str = "Cosine", random_strength: float = 1.0,
+                 bootstrap_type: str = "Bayesian", bootstrap_param: float = 1.0, leaf_method: str = "Newton",
+                 leaf_iterations: int = 1, seed: int = 0, ctx: Optional[DistContext] = None, reduce: str = "fused",
+                 eval_sets: Optional[List[EvalSet]] = None, use_graph: bool = True, threads: int = 512,
+                 ext_der: Optional[torch.Tensor] = None, ext_hess: Optional[torch.Tensor] = None,
+                 timeout_s: float = 20.0):
+        assert store.bins.is_cuda, "GpuObliviousEngine needs a CUDA store"
+        if depth > 16:
+            raise ValueError("depth must be <= 16")
+        self.lib = native.cuda_lib()
+        self.store = store
+        self.dev = store.bins.device
+        self.ctx = ctx or DistContext(0, 1, self.dev)
+        self.ctx.device = self.dev
+        self.R, self.rank = self.ctx.world, self.ctx.rank
+        self.depth, self.iterations = depth, iterations
+        self.lr, self.l2 = float(learning_rate), float(l2_leaf_reg)
+        self.score_fn, self.newton_stats = SCORE_FN[score_function]
+        self.random_strength = float(random_strength)
+        self.boot_type, self.boot_p = BOOTSTRAP[bootstrap_type], float(bootstrap_param)
+        self.leaf_newton = 1 if leaf_method == "Newton" else 0
+        self.leaf_iterations = max(1, int(leaf_iterations))
+        self.objective = objective
+        self.loss_id = int(objective.native_id) if objective.native_id is not None else 100
+        self.p0, self.p1 = (float(x) for x in objective.native_params())
+        self.seed = (int(seed) * 0x9E3779B97F4A7C15 + 0x1234567 * (self.rank + 1)) & 0xFFFFFFFFFFFFFFFF
+        self.score_seed = (int(seed) * 0xD1B54A32D192ED03 + 77) & 0xFFFFFFFFFFFFFFFF
+        self.reduce = reduce if self.R > 1 else "fused"
+        self.use_graph = use_graph
+        self.threads = threads
+        self.eval_sets = eval_sets or []
+        self.ext_der, self.ext_hess = ext_der, ext_hess
+        n, npad, dev = store.n, store.npad, self.dev
+        self.n, self.npad = n, npad
+        self.S = 2
+        self.L = 1 << depth
+        f32, i32, i64, f64 = torch.float32, torch.int32, torch.int64, torch.float64
+        self.approx = torch.zeros(npad, dtype=f32, device=dev)
+        self.approx[:n] = approx0.to(dev, f32)
+        self.target = torch.zeros(npad, dtype=f32, device=dev)
+        self.target[:n] = target.to(dev, f32)
+        self.weight = None
+        if weight is not None:
+            self.weight = torch.zeros(npad, dtype=f32, device=dev)
+            self.weight[:n] = weight.to(dev, f32)
+        self.leaf = torch.zeros(npad, dtype=torch.int16, device=dev)
+        self.stats = torch.zeros((self.S, npad), dtype=f32, device=dev)
+        self.scal = torch.zeros(4, dtype=f64, device=dev)
+        self.iter_ptr = torch.zeros(1, dtype=i32, device=dev)
+        cap = max(1, iterations)
+        self.loss_hist = torch.zeros((cap, 2), dtype=f64, device=dev)
+        self.splits = torch.full((cap * depth, 4), 0, dtype=i32, device=dev)
+        self.splits[:, 0] = -1
+        self.model_vals = torch.zeros((cap, self.L), dtype=f32, device=dev)
+        self.model_wts = torch.zeros((cap, self.L), dtype=f32, device=dev)
+        self.cur_vals = torch.zeros(self.L, dtype=f32, device=dev)
+        self.delta = torch.zeros(self.L, dtype=f32, device=dev)
+        self.sums = torch.zeros(self.L * 3, dtype=f64, device=dev)
+        self.counter = torch.zeros(1, dtype=i32, device=dev)
+        self.best_key = torch.zeros(1, dtype=i64, device=dev)
+        self.cur_loss = torch.zeros(2, dtype=f64, device=dev)
+        msg_bytes = self.lib.cb_select_msg_bytes()
+        self.msg_local = torch.zeros((max(self.R, 1), msg_bytes // 8 + 1), dtype=i64, device=dev)
+        self.msg_all = torch.zeros((max(self.R, 1), msg_bytes // 8 + 1), dtype=i64, device=dev)
+        self.mask = [torch.zeros(1024, dtype=i32, device=dev) for _ in range(2)]
+        n_eval = len(self.eval_sets)
+        self.eval_scal = torch.zeros(max(1, 2 * n_eval), dtype=f64, device=dev)
+        self.eval_hist = torch.zeros((cap, max(1, 2 * n_eval)), dtype=f64, device=dev)
+        # geometry ---------------------------------------------------------------------------------------
+        TB = store.TB
+        self.TB = TB
+        self.B = max(4, (store.max_bins + 3) // 4 * 4)
+        slots_max = 1 if depth <= 1 else 1 << (depth - 2)
+        self.slots_max = slots_max
+        if self.R > 1 and self.reduce == "fused":
+            fb, cb = split_columns(store.feat_off_host, self.R)
+        else:
+            fb, cb = [0] + [store.F] * self.R, [0] + [TB] * self.R
+            if self.R == 1:
+                fb, cb = [0, store.F], [0, TB]
+        self.feat_bounds, self.col_bounds = fb, cb
+        if self.R > 1 and self.reduce == "fused":
+            self.Wmax = max(4, max(cb[r + 1] - cb[r] for r in range(self.R)))
+        else:
+            self.Wmax = TB
+        hl = 1 if depth <= 1 else 1 << (depth - 2)      # leaves kept for the sibling subtraction
+        self.hbuf = [torch.zeros((hl * 2, self.S, self.Wmax), dtype=f32, device=dev) for _ in range(2)]
+        slot_floats = slots_max * self.S * self.Wmax
+        mbox_bytes = max(msg_bytes, 256)
+        self.arena = (PeerArena(self.ctx, ArenaLayout(self.R, mbox_bytes, slot_floats), timeout_s=timeout_s)
+                      if self.reduce == "fused" else None)
+        if self.reduce == "fused":
+            self.slots = self.arena.local_slots_tensor()
+            self.partial = (torch.zeros((slots_max * self.S, TB), dtype=f32, device=dev) if self.R > 1 else None)
+            self._make_plan()
+        else:
+            self.partial = torch.zeros((slots_max * self.S, TB), dtype=f32, device=dev)
+            self.slots = None
+            self.plan = None
+            # leaf sums across ranks go through NCCL in this mode
+        sm = ctypes.c_int(0)
+        smem = ctypes.c_int(0)
+        native.cuda_check(self.lib.cb_device_info(ctypes.byref(sm), ctypes.byref(smem)), "cb_device_info")
+        self.sm_count, self.max_smem = sm.value, smem.value
+        self.grid_stream = self.sm_count * 8
+        self.graph = None
+        self.done = 0
+        self.launches_per_iter = 0
+
+    # ------------------------------------------------------------------------------------------------------
+    def _make_plan(self):
+        R = self.R
+        arr = ctypes.c_void_p * R
+        local_slots = arr(*[self.arena.local_slot_ptr(r) for r in range(R)])
+        own = (ctypes.c_int * (R + 1))(*self.col_bounds)
+        partial_ptr = _p(self.partial) if R > 1 else ctypes.c_void_p(self.arena.local_slot_ptr(0))
+        self.plan = self.lib.cb_fused_create(
+            ctypes.c_void_p(self.store.handle), ctypes.c_void_p(self.arena.handle), _p(self.leaf), _p(self.stats),
+            self.S, self.B, partial_ptr, local_slots, _p(self.hbuf[0]), _p(self.hbuf[1]), own, self.Wmax,
+            _p(self.mask[0]), _p(self.mask[1]), _p(self.splits), self.depth, self.l2, self.score_fn,
+            self.random_strength, _p(self.scal), _p(self.iter_ptr), self.score_seed, self.lr, _p(self.best_key),
+            _p(self.msg_local), self.threads)
+        if not self.plan:
+            raise RuntimeError("cb_fused_create failed")
+        self.lib.cb_fused_set_features(ctypes.c_void_p(self.plan), self.feat_bounds[self.rank],
+                                       self.feat_bounds[self.rank + 1])
+        self.level_geo = []
+        for level in range(self.depth):
+            spp, smem = ctypes.c_int(0), ctypes.c_int(0)
+            grid = self.lib.cb_fused_geometry(ctypes.c_void_p(self.plan), level, ctypes.byref(spp), ctypes.byref(smem))
+            if grid <= 0:
+                raise RuntimeError(f"no cooperative launch geometry for level {level}")
+            self.level_geo.append((grid, spp.value, smem.value))
+
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+
+    # ------------------------------------------------------------------------------------------------------
+    def _grad(self):
+        chk = native.cuda_check
+        chk(self.lib.cb_grad_pointwise(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target), _p(self.weight),
+                                       _p(self.leaf), _p(self.cur_vals), self.n, self.npad, _p(self.stats),
+                                       self.newton_stats, self.boot_type, self.boot_p, self.seed, _p(self.iter_ptr),
+                                       _p(self.scal), _p(self.ext_der), _p(self.ext_hess), self.grid_stream,
+                                       self._stream()), "cb_grad_pointwise")
+        self.launches_per_iter += 1
+
+    def _level_fused(self, level: int):
+        grid, spp, smem = self.level_geo[level]
+        nslots = 1 if level == 0 else 1 << (level - 1)
+        rows = nslots * self.S
+        if self.R > 1:
+            self.partial[:rows].zero_()
+        else:
+            self.slots[: rows * self.Wmax].zero_()
+        hprev, hcur = self.hbuf[(level + 1) & 1], self.hbuf[level & 1]
+        hcur_ptr = _p(hcur) if level < self.depth - 1 else None
+        native.cuda_check(self.lib.cb_fused_launch(ctypes.c_void_p(self.plan), level, _p(hprev), hcur_ptr,
+                                                   _p(self.mask[level & 1]), _p(self.mask[(level + 1) & 1]), grid, spp,
+                                                   smem, self._stream()), "cb_level_fused")
+        self.launches_per_iter += 2
+
+    def _level_unfused(self, level: int):
+        chk, lib, st = native.cuda_check, self.lib, self.store
+        nslots = 1 if level == 0 else 1 << (level - 1)
+        rows = nslots * self.S
+        if level > 0:
+            chk(lib.cb_update_leaf(ctypes.c_void_p(st.handle), _p(self.leaf), _p(self.splits), _p(self.iter_ptr),
+                                   self.depth, level - 1, self.grid_stream, self._stream()), "cb_update_leaf")
+        self.partial[:rows].zero_()
+        per_slot = self.S * 4 * self.B * 4
+        spp = max(1, min(nslots, (self.max_smem - 1024) // per_slot))
+        grid = self.sm_count * max(1, min(4, (200 * 1024) // max(1, spp * per_slot)))
+        chk(lib.cb_hist(ctypes.c_void_p(st.handle), _p(self.leaf), _p(self.stats), self.S, level,
+                        _p(self.mask[level & 1]), None, 0, spp, self.B, _p(self.partial), grid, self.threads,
+                        self._stream()), "cb_hist")
+        if self.R > 1:
+            import torch.distributed as dist
+            dist.all_reduce(self.partial[:rows], group=self.ctx.group)
+        hprev, hcur = self.hbuf[(level + 1) & 1], self.hbuf[level & 1]
+        hcur_ptr = _p(hcur) if level < self.depth - 1 else None
+        src = (ctypes.c_void_p * 1)(self.partial.data_ptr())
+        chk(lib.cb_score(ctypes.c_void_p(st.handle), src, 1, _p(hprev), hcur_ptr, self.TB, 0, 0, st.F, level, self.S,
+                         _p(self.mask[level & 1]), self.l2, self.score_fn, self.random_strength, _p(self.scal),
+                         _p(self.iter_ptr), self.score_seed, self.lr, _p(self.best_key), self._stream()), "cb_score")
+        chk(lib.cb_select_local_launch(ctypes.c_void_p(st.handle), hcur_ptr, self.TB, 0, level, self.S,
+                                       _p(self.best_key), _p(self.msg_local), self._stream()), "cb_select_local")
+        chk(lib.cb_select_final_launch(ctypes.c_void_p(st.handle), _p(self.msg_local), 1, self.msg_local.stride(0) * 8,
+                                       level, _p(self.splits), _p(self.iter_ptr), self.depth,
+                                       _p(self.mask[(level + 1) & 1]), _p(self.best_key), self._stream()),
+            "cb_select_final")
+        self.launches_per_iter += 5 + (1 if level > 0 else 0)
+
+    def _leaves(self):
+        chk, lib = native.cuda_check, self.lib
+        chk(lib.cb_update_leaf(ctypes.c_void_p(self.store.handle), _p(self.leaf), _p(self.splits), _p(self.iter_ptr),
+                               self.depth, self.depth - 1, self.grid_stream, self._stream()), "cb_update_leaf")
+        self.launches_per_iter += 1
+        comm = ctypes.c_void_p(self.arena.handle) if (self.arena is not None and self.R > 1) else None
+        if self.R > 1 and comm is None:
+            # NCCL baseline: sums are all-reduced between two kernels
+            for it in range(self.leaf_iterations):
+                self._leaf_pass_nccl(it)
+            return
+        for it in range(self.leaf_iterations):
+            last = 1 if it == self.leaf_iterations - 1 else 0
+            chk(lib.cb_leaf_pass(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target), _p(self.weight),
+                                 _p(self.leaf), _p(self.ext_der), _p(self.ext_hess), self.n, self.L, _p(self.delta),
+                                 _p(self.sums), _p(self.counter), 1 if it == 0 else 0, last, self.leaf_newton, self.l2,
+                                 self.lr, _p(self.cur_vals), _p(self.model_vals), _p(self.model_wts), self.L,
+                                 _p(self.iter_ptr), comm, self.grid_stream, self._stream()), "cb_leaf_pass")
+            self.launches_per_iter += 1
+
+    def _leaf_pass_nccl(self, it):
+        # baseline path only: torch ops + NCCL all-reduce of the per-leaf sums
+        import torch.distributed as dist
+        n = self.n
+        leaf = self.leaf[:n].long() & 0xFFFF
+        ap = self.approx[:n] + (self.delta[leaf] if it > 0 else 0)
+        d, h = self.objective.der_hess(ap.unsqueeze(0), self.target[:n], None if self.weight is None else self.weight[:n])
+        w = torch.ones_like(ap) if self.weight is None else self.weight[:n]
+        sums = torch.zeros((3, self.L), dtype=torch.float64, device=self.dev)
+        sums[0].index_add_(0, leaf, d[0].double())
+        sums[1].index_add_(0, leaf, h[0].double())
+        sums[2].index_add_(0, leaf, w.double())
+        dist.all_reduce(sums, group=self.ctx.group)
+        den = (sums[1] if self.leaf_newton else sums[2]) + self.l2
+        step = torch.where(den > 0, sums[0] / den, torch.zeros_like(den)).float()
+        if it == 0:
+            self.delta.copy_(step)
+        else:
+            self.delta.add_(step)
+        if it == self.leaf_iterations - 1:
+            self.cur_vals.copy_(self.delta * self.lr)
+            self.model_vals.index_copy_(0, self.iter_ptr.long(), self.cur_vals.unsqueeze(0))
+            self.model_wts.index_copy_(0, self.iter_ptr.long(), sums[2].float().unsqueeze(0))
+
+    def _evals(self):
+        chk, lib = native.cuda_check, self.lib
+        for k, ev in enumerate(self.eval_sets):
+            chk(lib.cb_apply_tree_bins(ctypes.c_void_p(ev.store.handle), _p(ev.approx), ev.store.npad, _p(self.splits),
+                                       _p(self.iter_ptr), self.depth, _p(self.cur_vals), 1, self.grid_stream,
+                                       self._stream()), "cb_apply_tree_bins")
+            chk(lib.cb_metric_sum(self.loss_id, self.p0, self.p1, _p(ev.approx), _p(ev.target), _p(ev.weight),
+                                  ev.store.n, None, None, ctypes.c_void_p(self.eval_scal.data_ptr() + 16 * k),
+                                  self.grid_stream, self._stream()), "cb_metric_sum")
+            self.launches_per_iter += 2
+
+    def _iteration(self):
+        self.launches_per_iter = 0
+        self._grad()
+        for level in range(self.depth):
+            if self.reduce == "fused":
+                self._level_fused(level)
+            else:
+                self._level_unfused(level)
+        self._leaves()
+        self._evals()
+        n_extra = 2 * len(self.eval_sets)
+        native.cuda_check(self.lib.cb_iter_end(_p(self.iter_ptr), _p(self.scal), _p(self.loss_hist), _p(self.eval_scal),
+                                               _p(self.eval_hist), n_extra, self._stream()), "cb_iter_end")
+        self.launches_per_iter += 1
+
+    # ------------------------------------------------------------------------------------------------------
+    def _capture(self):
+        torch.cuda.synchronize(self.dev)
+        self.ctx.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, capture_error_mode="relaxed"):
+            self._iteration()
+        self.graph = g
+
+    def step(self, count: int = 1):
+        """Run ``count`` boosting iterations (asynchronously).  The first one runs eagerly (module loading,
+        function attributes), the second call captures the CUDA graph that all later iterations replay."""
+        if self.done + count > self.iterations:
+            raise RuntimeError("more iterations requested than the engine was sized for")
+        graph_ok = self.use_graph and not (self.R > 1 and self.reduce != "fused")
+        for _ in range(count):
+            if not graph_ok or self.done == 0:
+                self._iteration()
+            else:
+                if self.graph is None:
+                    self._capture()
+                self.graph.replay()
+            self.done += 1
+
+    def current_learn_loss(self, pinned: Optional[torch.Tensor] = None) -> float:
+        """Mean learn loss including the newest tree (one streaming kernel + a 16-byte device->host read),
+        summed over ranks."""
+        self.cur_loss.zero_()
+        native.cuda_check(self.lib.cb_metric_sum(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target),
+                                                 _p(self.weight), self.n, _p(self.leaf), _p(self.cur_vals),
+                                                 _p(self.cur_loss), self.grid_stream, self._stream()), "cb_metric_sum")
+        if self.R > 1:
+            self.ctx.all_reduce_sum_(self.cur_loss)
+        if pinned is not None:
+            pinned.copy_(self.cur_loss, non_blocking=True)
+            torch.cuda.current_stream(self.dev).synchronize()
+            v = pinned
+        else:
+            v = self.cur_loss.cpu()
+        return float(v[0]) / max(float(v[1]), 1e-300)
+
+    def finish(self):
+        """Apply the last tree to the training cursor and return (splits, leaf values, leaf weights) on the host."""
+        torch.cuda.synchronize(self.dev)
+        if self.arena is not None:
+            self.arena.check_status()
+        n = self.n
+        leaf = self.leaf[:n].long() & 0xFFFF
+        self.approx[:n] += self.cur_vals[leaf]
+        self.cur_vals.zero_()
+        self.leaf.zero_()
+        T = self.done
+        sp = self.splits[: T * self.depth].cpu().numpy().reshape(T, self.depth, 4)
+        return sp, self.model_vals[:T].cpu().numpy(), self.model_wts[:T].cpu().numpy()
+
+    def learn_loss_history(self) -> np.ndarray:
+        """Mean learn loss seen at the start of every finished iteration (summed over ranks)."""
+        h = self.loss_hist[: self.done].clone()
+        if self.R > 1:
+            self.ctx.all_reduce_sum_(h)
+        h = h.cpu().numpy()
+        return h[:, 0] / np.maximum(h[:, 1], 1e-300)
+
+    def eval_loss_history(self) -> np.ndarray:
+        n_eval = len(self.eval_sets)
+        if not n_eval:
+            return np.zeros((self.done, 0))
+        h = self.eval_hist[: self.done].clone()
+        if self.R > 1:
+            self.ctx.all_reduce_sum_(h)
+        h = h.cpu().numpy().reshape(self.done, n_eval, 2)
+        return h[:, :, 0] / np.maximum(h[:, :, 1], 1e-300)
+
+    def close(self):
+        if getattr(self, "plan", None):
+            self.lib.cb_fused_destroy(ctypes.c_void_p(self.plan))
+            self.plan = None
+        if getattr(self, "arena", None) is not None:
+            self.arena.close()

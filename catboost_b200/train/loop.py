@@ -1,0 +1,331 @@
+"""The boosting iteration loop for both trainers (device-resident engine and general learner)."""
+from __future__ import annotations
+
+import math
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..data.pool import CatBoostError
+from ..ops import api as ops
+from .generic import GenericLearner, estimate_leaves
+from .snapshot import SnapshotManager
+
+
+@dataclass
+class LoopResult:
+    trees: list
+    evals_result: Dict[str, Dict[str, List[float]]]
+    best_iteration: Optional[int]
+    best_score: Dict[str, Dict[str, float]]
+    launches_per_iter: int = 0
+    train_approx: Optional[np.ndarray] = None
+
+
+class ObjectiveContext:
+    """Per-dataset side information some objectives need (query offsets, pairs) on the training device."""
+
+    def __init__(self, pool, device):
+        self.group_offsets = None
+        self.pairs = None
+        self.pairs_weight = None
+        self.device = device
+        if pool.group_id is not None:
+            self.group_offsets = torch.from_numpy(pool.group_offsets()).to(device)
+        if pool.pairs is not None:
+            self.pairs = torch.from_numpy(pool.pairs).to(device)
+            self.pairs_weight = torch.from_numpy(pool.pairs_weight).to(device)
+        self.subgroup_id = pool.subgroup_id
+
+
+def _use_fast_engine(o, objective, store, dims) -> bool:
+    return (store.bins.is_cuda and o.grow_policy == "SymmetricTree" and objective.native_id is not None and dims == 1
+            and o.boosting_type == "Plain" and o.leaf_estimation_method in ("Newton", "Gradient")
+            and float(o.rsm) >= 1.0 and int(o.min_data_in_leaf) <= 1
+            and o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson") and bool(o.fused_levels or True)
+            and not o.langevin)
+
+
+class _History:
+    def __init__(self, metrics, n_eval, eval_names):
+        self.metrics = metrics
+        self.names = ["learn"] + eval_names
+        self.data = {nm: {str(m): [] for m in metrics} for nm in self.names}
+        self.iters: List[int] = []
+
+    def add(self, set_name, metric, value):
+        self.data[set_name][str(metric)].append(float(value))
+
+
+def _eval_names(n):
+    return ["validation"] if n == 1 else [f"validation_{k}" for k in range(n)]
+
+
+def _host_metric(metric, approx_dims_n: torch.Tensor, y, w, pool, loss_dims):
+    a = approx_dims_n.detach().t().double().cpu().numpy()
+    kw = {}
+    if pool is not None:
+        if pool.group_id is not None:
+            kw["group_offsets"] = pool.group_offsets()
+        if pool.pairs is not None:
+            kw["pairs"], kw["pairs_weight"] = pool.pairs, pool.pairs_weight
+    return metric.eval(a, y, w, **kw)
+
+
+def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train, eval_y, eval_w, base_evals,
+                 train_pool, eval_pools, metrics, logger, od, ctx, prof, callbacks, plan, ctr_state) -> LoopResult:
+    dev = store.bins.device
+    dims = objective.dims
+    n = store.n
+    T = int(o.iterations)
+    eval_names = _eval_names(len(eval_stores))
+    hist = _History(metrics, len(eval_stores), eval_names)
+    snap = SnapshotManager(o, ctx)
+    callbacks = list(callbacks or [])
+    if o.callback is not None:
+        callbacks += list(o.callback) if isinstance(o.callback, (list, tuple)) else [o.callback]
+
+    if _use_fast_engine(o, objective, store, dims):
+        return _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, eval_y, eval_w, base_evals,
+                         train_pool, eval_pools, metrics, logger, od, ctx, prof, callbacks, hist, eval_names, snap)
+
+    # ------------------------------------------------------------------ general learner
+    f32 = torch.float32
+    approx = torch.zeros((dims, store.npad), dtype=f32, device=dev)
+    approx[:, :n] = torch.from_numpy(np.ascontiguousarray(base_train)).to(dev, f32)
+    multi_target = np.asarray(y_train).ndim == 2
+    target = torch.from_numpy(np.ascontiguousarray(np.asarray(y_train).T if multi_target else y_train)).to(dev, f32)
+    weight = None if w_train is None else torch.from_numpy(np.asarray(w_train, dtype=np.float32)).to(dev)
+    wpad = None
+    if weight is not None:
+        wpad = torch.zeros(store.npad, dtype=f32, device=dev)
+        wpad[:n] = weight
+    octx = ObjectiveContext(train_pool, dev)
+    eval_approx = [torch.from_numpy(np.ascontiguousarray(b)).to(dev, f32) for b in base_evals]
+    learner = GenericLearner(store, o, dims, ctx, seed=int(o.random_seed))
+    trees = []
+    start_iter = 0
+    restored = snap.try_load(o)
+    if restored is not None:
+        trees, hist.data, hist.iters = restored["trees"], restored["hist"], restored["iters"]
+        start_iter = len(trees)
+        for t in trees:
+            _apply_tree_to(store, t, approx, n, dims, dev)
+            for es, ea in zip(eval_stores, eval_approx):
+                _apply_tree_to(es, t, ea, es.n, dims, dev)
+        learner.gen.manual_seed(int(o.random_seed) + 12345 + start_iter)
+        if od is not None:
+            for v in hist.data[eval_names[0]][str(metrics[0])]:
+                od.add(v)
+    best_it, best_val = None, None
+    t_loop = time.time()
+    stop = False
+    for it in range(start_iter, T):
+        with prof.span("derivatives"):
+            der, hess = objective.der_hess(approx[:, :n], target, weight, octx)
+            der_p = torch.zeros((dims, store.npad), dtype=f32, device=dev)
+            hess_p = torch.zeros((dims, store.npad), dtype=f32, device=dev)
+            der_p[:, :n], hess_p[:, :n] = der, hess
+            if o.langevin:
+                coef = math.sqrt(2.0 / (float(o.learning_rate) * float(o.diffusion_temperature)))
+                der_p[:, :n] += learner._randn((dims, n)) * coef
+        with prof.span("structure"):
+            tr = learner.build_tree(der_p, hess_p, wpad, it)
+        with prof.span("leaves"):
+            vals, wts = estimate_leaves(objective, approx, target, weight, tr.leaf, tr.n_leaves, n, o, ctx, octx)
+        tv = torch.from_numpy(vals).to(dev, f32)
+        approx[:, :n] += tv[tr.leaf[:n].long() & 0xFFFF].t()
+        tree = dict(kind=tr.kind, splits=tr.splits, node_split=tr.node_split, leaf_of_node=tr.leaf_of_node, values=vals,
+                    weights=wts)
+        trees.append(tree)
+        with prof.span("eval_apply"):
+            for es, ea in zip(eval_stores, eval_approx):
+                _apply_tree_to(es, tree, ea, es.n, dims, dev)
+        # metrics -----------------------------------------------------------------------------------------
+        period = max(1, int(o.metric_period))
+        if (it % period == 0) or it == T - 1 or od is not None:
+            with prof.span("metrics"):
+                hist.iters.append(it)
+                for m in metrics:
+                    hist.add("learn", m, _dist_metric(m, approx[:, :n], y_train, w_train, train_pool, ctx, objective))
+                    for k, (ea, ep) in enumerate(zip(eval_approx, eval_pools)):
+                        hist.add(eval_names[k], m, _dist_metric(m, ea, eval_y[k], eval_w[k], ep, ctx, objective))
+            if eval_stores:
+                v = hist.data[eval_names[0]][str(metrics[0])][-1]
+                if best_val is None or (v > best_val if metrics[0].is_max_optimal else v < best_val):
+                    best_val, best_it = v, it
+                if od is not None and od.add(v):
+                    stop = True
+            logger.log_iteration(it, T, hist, time.time() - t_loop)
+        for cb in callbacks:
+            info = _CallbackInfo(it, hist.data)
+            if cb.after_iteration(info) is False:
+                stop = True
+        snap.maybe_save(dict(trees=trees, hist=hist.data, iters=hist.iters), it)
+        if stop:
+            logger.info(f"Stopped by overfitting detector  ({od.wait} iterations wait)" if od is not None and od.stopped
+                        else "Stopped by callback")
+            break
+    snap.finalize(dict(trees=trees, hist=hist.data, iters=hist.iters))
+    return LoopResult(trees, hist.data, best_it, _best_scores(hist, metrics), 0,
+                      approx[:, :n].t().double().cpu().numpy())
+
+
+class _CallbackInfo:
+    def __init__(self, iteration, metrics):
+        self.iteration = iteration
+        self.metrics = metrics
+
+
+def _best_scores(hist, metrics):
+    out = {}
+    for nm, per in hist.data.items():
+        out[nm] = {}
+        for m in metrics:
+            vals = per[str(m)]
+            if vals:
+                out[nm][str(m)] = max(vals) if m.is_max_optimal else min(vals)
+    return out
+
+
+def _dist_metric(metric, approx, y, w, pool, ctx, objective):
+    """Metric value over all ranks (additive metrics are averaged by weight; rank-local otherwise)."""
+    v = _host_metric(metric, approx, y, w, pool, objective.dims)
+    if ctx is None or not ctx.is_distributed:
+        return v
+    wsum = float(len(y)) if w is None else float(np.sum(w))
+    parts = ctx.all_gather_object((v, wsum))
+    tot = sum(p[1] for p in parts)
+    if getattr(metric, "name", "") in ("RMSE", "QueryRMSE", "MultiRMSE"):
+        return math.sqrt(sum(p[0] ** 2 * p[1] for p in parts) / tot)
+    return sum(p[0] * p[1] for p in parts) / tot
+
+
+def _apply_tree_to(store, tree, approx, n, dims, dev):
+    """approx[:, :n] += leaf values of ``tree`` for the documents of ``store``."""
+    vals = torch.from_numpy(np.asarray(tree["values"], dtype=np.float32).reshape(-1, dims)).to(dev)
+    if tree["kind"] == "oblivious":
+        leaf = ops.leaf_index(store, torch.from_numpy(np.ascontiguousarray(tree["splits"], dtype=np.int32)).to(dev))
+        approx[:, :n] += vals[leaf[:n].long() & 0xFFFF].t()
+        return
+    ns = torch.from_numpy(np.ascontiguousarray(tree["node_split"], dtype=np.int32)).to(dev)
+    node = torch.zeros(store.npad, dtype=torch.int16, device=dev)
+    depth = _nonsym_depth(tree["node_split"])
+    for _ in range(depth):
+        ops.update_nodes(store, node, ns)
+    lut = torch.from_numpy(np.where(tree["leaf_of_node"] >= 0, tree["leaf_of_node"], 0).astype(np.int64)).to(dev)
+    approx[:, :n] += vals[lut[node[:n].long() & 0xFFFF]].t()
+
+
+def _nonsym_depth(ns) -> int:
+    depth = np.zeros(len(ns), dtype=np.int64)
+    for k in range(len(ns)):
+        if ns[k, 0] >= 0:
+            depth[ns[k, 3]] = depth[ns[k, 3] + 1] = depth[k] + 1
+    return int(depth.max()) if len(ns) else 0
+
+
+# ---------------------------------------------------------------------------------------------------------
+def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, eval_y, eval_w, base_evals, train_pool,
+              eval_pools, metrics, logger, od, ctx, prof, callbacks, hist, eval_names, snap) -> LoopResult:
+    from .gpu_engine import EvalSet, GpuObliviousEngine
+    dev = store.bins.device
+    n = store.n
+    T = int(o.iterations)
+    f32 = torch.float32
+    evs = []
+    for es, y, w, b in zip(eval_stores, eval_y, eval_w, base_evals):
+        ap = torch.zeros(es.npad, dtype=f32, device=dev)
+        ap[: es.n] = torch.from_numpy(np.ascontiguousarray(b[0])).to(dev, f32)
+        tt = torch.zeros(es.npad, dtype=f32, device=dev)
+        tt[: es.n] = torch.from_numpy(np.asarray(y, dtype=np.float32)).to(dev)
+        ww = None
+        if w is not None:
+            ww = torch.zeros(es.npad, dtype=f32, device=dev)
+            ww[: es.n] = torch.from_numpy(np.asarray(w, dtype=np.float32)).to(dev)
+        evs.append(EvalSet(es, tt, ww, ap))
+    boot_p = float(o.bagging_temperature) if o.bootstrap_type == "Bayesian" else float(o.subsample or 1.0)
+    btype = o.bootstrap_type
+    if btype == "Bayesian" and boot_p == 0:
+        btype = "No"
+    with prof.span("engine_setup"):
+        eng = GpuObliviousEngine(
+            store, torch.from_numpy(np.asarray(y_train, dtype=np.float32)),
+            None if w_train is None else torch.from_numpy(np.asarray(w_train, dtype=np.float32)),
+            torch.from_numpy(np.ascontiguousarray(base_train[0], dtype=np.float32)), objective,
+            depth=int(o.depth), iterations=T, learning_rate=float(o.learning_rate), l2_leaf_reg=float(o.l2_leaf_reg),
+            score_function=o.score_function, random_strength=float(o.random_strength), bootstrap_type=btype,
+            bootstrap_param=boot_p, leaf_method=o.leaf_estimation_method,
+            leaf_iterations=int(o.leaf_estimation_iterations), seed=int(o.random_seed), ctx=ctx,
+            reduce=("fused" if o.histogram_reduce in ("fused", None) else "nccl"), eval_sets=evs)
+    loss_metric_name = objective.name
+    # "cheap" logging: the only tracked metric is the objective itself, which the device already accumulates
+    cheap = len(metrics) == 1 and isinstance(o.loss_function, str) and str(metrics[0]) == o.loss_function
+    need_each = bool(od is not None or callbacks)
+    want_log = bool(o.verbose) or bool(eval_stores)
+    period = 1 if need_each else (max(1, int(o.metric_period)) if want_log else T)
+    done, best_it, best_val, stop = 0, None, None, False
+    t_loop = time.time()
+    pinned = torch.zeros(2, dtype=torch.float64).pin_memory()
+    pinned_ev = torch.zeros(max(1, 2 * len(evs)), dtype=torch.float64).pin_memory()
+    fin = (lambda v: math.sqrt(max(v, 0.0))) if objective.name == "RMSE" else (lambda v: v)
+    with prof.span("iterations"):
+        while done < T and not stop:
+            k = min(period, T - done)
+            eng.step(k)
+            done += k
+            if not want_log and not need_each:
+                continue
+            it = done - 1
+            hist.iters.append(it)
+            if cheap:
+                hist.add("learn", metrics[0], fin(eng.current_learn_loss(pinned)))
+                if evs:
+                    row = eng.eval_hist[it].clone()
+                    if eng.R > 1:
+                        ctx.all_reduce_sum_(row)
+                    pinned_ev.copy_(row, non_blocking=True)
+                    torch.cuda.current_stream(dev).synchronize()
+                    for j in range(len(evs)):
+                        hist.add(eval_names[j], metrics[0], fin(float(pinned_ev[2 * j]) / max(float(pinned_ev[2 * j + 1]), 1e-300)))
+            else:
+                torch.cuda.current_stream(dev).synchronize()
+                cur = eng.approx[:n] + eng.cur_vals[eng.leaf[:n].long() & 0xFFFF]
+                for m in metrics:
+                    hist.add("learn", m, _dist_metric(m, cur.unsqueeze(0), y_train, w_train, train_pool, ctx, objective))
+                    for j, ev in enumerate(evs):
+                        hist.add(eval_names[j], m, _dist_metric(m, ev.approx[: ev.store.n].unsqueeze(0), eval_y[j],
+                                                                eval_w[j], eval_pools[j], ctx, objective))
+            if eng.arena is not None and (it % 64 == 0):
+                eng.arena.check_status()
+            if evs:
+                v = hist.data[eval_names[0]][str(metrics[0])][-1]
+                if best_val is None or (v > best_val if metrics[0].is_max_optimal else v < best_val):
+                    best_val, best_it = v, it
+                if od is not None and od.add(v):
+                    stop = True
+            logger.log_iteration(it, T, hist, time.time() - t_loop)
+            for cb in callbacks:
+                if cb.after_iteration(_CallbackInfo(it, hist.data)) is False:
+                    stop = True
+        sp, vals, wts = eng.finish()
+    if stop and od is not None and od.stopped:
+        logger.info(f"Stopped by overfitting detector  ({od.wait} iterations wait)")
+    trees = [dict(kind="oblivious", splits=sp[t], node_split=None, leaf_of_node=None, values=vals[t], weights=wts[t])
+             for t in range(done)]
+    if not hist.iters:
+        # nothing was logged during training: fill the learn curve of the objective from the device history
+        lh = eng.learn_loss_history()
+        name = str(metrics[0]) if getattr(metrics[0], "name", None) == loss_metric_name else None
+        if name is not None and len(lh) > 1:
+            vals_l = lh[1:].tolist()
+            if objective.name == "RMSE":
+                vals_l = [math.sqrt(v) for v in vals_l]
+            hist.data["learn"][name] = vals_l
+    launches = eng.launches_per_iter
+    train_approx = eng.approx[:n].double().cpu().numpy().reshape(-1, 1)
+    eng.close()
+    return LoopResult(trees, hist.data, best_it, _best_scores(hist, metrics), launches, train_approx)

@@ -1,0 +1,427 @@
+"""Objectives: derivatives, loss values and starting constants.
+
+``der`` is the negative gradient of the loss with respect to the approx (what the reference calls "der"),
+``hess`` the positive second derivative.  Pointwise losses also carry the id of their native implementation
+(``ops/cuda/cb_losses.cuh``) so the GPU trainer never leaves the device; the torch versions here drive the
+CPU trainer, the multi-dimensional and ranking trainers, and are the oracle of the kernels' tests.
+Formulas: catboost/private/libs/algo_helpers/error_functions.h:191-1669,
+catboost/cuda/targets/kernel/pointwise_targets.cu, multilogit.cu, query_rmse.cu, query_softmax.cu, pair_logit.cu.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..data.pool import CatBoostError
+
+NATIVE_LOSS_ID = {"RMSE": 0, "Logloss": 1, "CrossEntropy": 2, "Poisson": 3, "MAE": 4, "Quantile": 5,
+                  "LogLinQuantile": 6, "MAPE": 7, "Huber": 8, "Lq": 9, "Expectile": 10, "Tweedie": 11, "LogCosh": 12}
+LOSS_EXTERNAL = 100
+
+
+class Objective:
+    name = "RMSE"
+    dims = 1                 # approx dimension
+    is_pointwise = True
+    needs_groups = False
+    needs_pairs = False
+    is_classification = False
+    is_multiclass = False
+    stochastic = False
+
+    def __init__(self, params: Optional[dict] = None):
+        self.params = dict(params or {})
+
+    # native pointwise implementation ------------------------------------------------------------
+    @property
+    def native_id(self) -> Optional[int]:
+        return NATIVE_LOSS_ID.get(self.name)
+
+    def native_params(self):
+        return 0.0, 0.0
+
+    # torch implementation ---------------------------------------------------------------------------
+    def der_hess(self, approx: torch.Tensor, target: torch.Tensor, weight: Optional[torch.Tensor], ctx=None):
+        """approx [dims, n] -> (der [dims, n], hess [dims, n]); both already multiplied by the sample weight."""
+        raise NotImplementedError
+
+    def value(self, approx, target, weight, ctx=None) -> float:
+        raise NotImplementedError
+
+    def start_constant(self, target: np.ndarray, weight: Optional[np.ndarray]):
+        return np.zeros(self.dims)
+
+    def _w(self, x, weight):
+        return x if weight is None else x * weight
+
+
+def _wsum(x, weight):
+    return float((x if weight is None else x * weight).sum().item())
+
+
+def _wtot(n, weight):
+    return float(n) if weight is None else float(weight.sum().item())
+
+
+class _Pointwise(Objective):
+    def _point(self, a, y):
+        raise NotImplementedError
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        d, h, _ = self._point(approx[0], target)
+        if weight is not None:
+            d, h = d * weight, h * weight
+        return d.unsqueeze(0), h.unsqueeze(0)
+
+    def value(self, approx, target, weight, ctx=None):
+        _, _, v = self._point(approx[0], target)
+        return _wsum(v, weight) / max(_wtot(target.numel(), weight), 1e-300)
+
+
+class RMSE(_Pointwise):
+    name = "RMSE"
+
+    def _point(self, a, y):
+        d = y - a
+        return d, torch.ones_like(d), d * d
+
+    def value(self, approx, target, weight, ctx=None):
+        return math.sqrt(super().value(approx, target, weight))
+
+    def start_constant(self, target, weight):
+        return np.array([np.average(target.astype(np.float64), weights=weight)])
+
+
+class Logloss(_Pointwise):
+    name = "Logloss"
+    is_classification = True
+
+    def _point(self, a, y):
+        p = torch.sigmoid(a)
+        v = torch.nn.functional.softplus(a) - y * a
+        return y - p, (p * (1 - p)).clamp_min(1e-16), v
+
+    def start_constant(self, target, weight):
+        p = float(np.average(target.astype(np.float64), weights=weight))
+        p = min(max(p, 1e-9), 1 - 1e-9)
+        return np.array([math.log(p / (1 - p))])
+
+
+class CrossEntropy(Logloss):
+    name = "CrossEntropy"
+
+
+class Poisson(_Pointwise):
+    name = "Poisson"
+
+    def _point(self, a, y):
+        e = torch.exp(a)
+        return y - e, e, e - y * a
+
+
+class MAE(_Pointwise):
+    name = "MAE"
+
+    def _point(self, a, y):
+        d = y - a
+        return torch.sign(d), torch.ones_like(d), d.abs()
+
+    def start_constant(self, target, weight):
+        return np.array([_weighted_quantile(target, weight, 0.5)])
+
+
+class Quantile(_Pointwise):
+    name = "Quantile"
+
+    def native_params(self):
+        return float(self.params.get("alpha", 0.5)), float(self.params.get("delta", 1e-6))
+
+    def _point(self, a, y):
+        alpha, delta = self.native_params()
+        d = y - a
+        up, dn = d > delta, d < -delta
+        der = torch.where(up, torch.full_like(d, alpha), torch.where(dn, torch.full_like(d, -(1 - alpha)), torch.zeros_like(d)))
+        val = torch.where(up, alpha * d, torch.where(dn, -(1 - alpha) * d, torch.zeros_like(d)))
+        return der, torch.ones_like(d), val
+
+    def start_constant(self, target, weight):
+        return np.array([_weighted_quantile(target, weight, float(self.params.get("alpha", 0.5)))])
+
+
+class LogLinQuantile(_Pointwise):
+    name = "LogLinQuantile"
+
+    def native_params(self):
+        return float(self.params.get("alpha", 0.5)), 0.0
+
+    def _point(self, a, y):
+        alpha = self.native_params()[0]
+        e = torch.exp(a)
+        d = y - e
+        der = torch.where(d > 0, alpha * e, -(1 - alpha) * e)
+        return der, torch.ones_like(d), torch.where(d > 0, alpha * d, -(1 - alpha) * d)
+
+
+class MAPE(_Pointwise):
+    name = "MAPE"
+
+    def _point(self, a, y):
+        d = y - a
+        s = 1.0 / y.abs().clamp_min(1.0)
+        return torch.sign(d) * s, torch.ones_like(d), d.abs() * s
+
+    def start_constant(self, target, weight):
+        w = 1.0 / np.maximum(1.0, np.abs(target))
+        return np.array([_weighted_quantile(target, w if weight is None else w * weight, 0.5)])
+
+
+class Huber(_Pointwise):
+    name = "Huber"
+
+    def native_params(self):
+        return float(self.params.get("delta", 1.0)), 0.0
+
+    def _point(self, a, y):
+        dl = self.native_params()[0]
+        d = y - a
+        ad = d.abs()
+        inside = ad <= dl
+        der = torch.where(inside, d, torch.sign(d) * dl)
+        hess = torch.where(inside, torch.ones_like(d), torch.full_like(d, 1e-6))
+        return der, hess, torch.where(inside, 0.5 * d * d, dl * (ad - 0.5 * dl))
+
+
+class Lq(_Pointwise):
+    name = "Lq"
+
+    def native_params(self):
+        return float(self.params.get("q", 2.0)), 0.0
+
+    def _point(self, a, y):
+        q = self.native_params()[0]
+        d = y - a
+        ad = d.abs()
+        der = q * ad.pow(q - 1) * torch.sign(d)
+        hess = q * (q - 1) * ad.pow(q - 2) if q >= 2 else torch.ones_like(d)
+        hess = torch.where(ad == 0, torch.full_like(d, 2.0 if q == 2 else 1.0), hess)
+        return der, hess, ad.pow(q)
+
+
+class Expectile(_Pointwise):
+    name = "Expectile"
+
+    def native_params(self):
+        return float(self.params.get("alpha", 0.5)), 0.0
+
+    def _point(self, a, y):
+        alpha = self.native_params()[0]
+        d = y - a
+        w = torch.where(d > 0, torch.full_like(d, alpha), torch.full_like(d, 1 - alpha))
+        return 2 * w * d, 2 * w, w * d * d
+
+
+class Tweedie(_Pointwise):
+    name = "Tweedie"
+
+    def native_params(self):
+        return float(self.params.get("variance_power", 1.5)), 0.0
+
+    def _point(self, a, y):
+        p = self.native_params()[0]
+        e1, e2 = torch.exp((1 - p) * a), torch.exp((2 - p) * a)
+        return y * e1 - e2, (-y * (1 - p) * e1 + (2 - p) * e2).clamp_min(1e-16), -y * e1 / (1 - p) + e2 / (2 - p)
+
+
+class LogCosh(_Pointwise):
+    name = "LogCosh"
+
+    def _point(self, a, y):
+        d = y - a
+        t = torch.tanh(d)
+        ad = d.abs()
+        return t, (1 - t * t).clamp_min(1e-6), ad + torch.log1p(torch.exp(-2 * ad)) - math.log(2.0)
+
+
+# ---- multi-dimensional ----------------------------------------------------------------------------------
+class MultiClass(Objective):
+    name = "MultiClass"
+    is_pointwise = False
+    is_classification = True
+    is_multiclass = True
+
+    def __init__(self, params=None, n_classes: int = 2):
+        super().__init__(params)
+        self.dims = int(n_classes)
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        p = torch.softmax(approx, dim=0)
+        onehot = torch.zeros_like(p)
+        onehot.scatter_(0, target.long().unsqueeze(0), 1.0)
+        der = onehot - p
+        hess = (p * (1 - p)).clamp_min(1e-16)
+        if weight is not None:
+            der, hess = der * weight, hess * weight
+        return der, hess
+
+    def value(self, approx, target, weight, ctx=None):
+        lp = torch.log_softmax(approx, dim=0)
+        v = -lp.gather(0, target.long().unsqueeze(0))[0]
+        return _wsum(v, weight) / max(_wtot(target.numel(), weight), 1e-300)
+
+
+class MultiClassOneVsAll(MultiClass):
+    name = "MultiClassOneVsAll"
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        p = torch.sigmoid(approx)
+        onehot = torch.zeros_like(p)
+        onehot.scatter_(0, target.long().unsqueeze(0), 1.0)
+        der, hess = onehot - p, (p * (1 - p)).clamp_min(1e-16)
+        if weight is not None:
+            der, hess = der * weight, hess * weight
+        return der, hess
+
+    def value(self, approx, target, weight, ctx=None):
+        onehot = torch.zeros_like(approx)
+        onehot.scatter_(0, target.long().unsqueeze(0), 1.0)
+        v = (torch.nn.functional.softplus(approx) - onehot * approx).sum(0) / approx.shape[0]
+        return _wsum(v, weight) / max(_wtot(target.numel(), weight), 1e-300)
+
+
+class MultiRMSE(Objective):
+    name = "MultiRMSE"
+    is_pointwise = False
+
+    def __init__(self, params=None, n_targets: int = 1):
+        super().__init__(params)
+        self.dims = int(n_targets)
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        d = target - approx          # target [dims, n]
+        h = torch.ones_like(d)
+        if weight is not None:
+            d, h = d * weight, h * weight
+        return d, h
+
+    def value(self, approx, target, weight, ctx=None):
+        v = ((target - approx) ** 2).sum(0)
+        return math.sqrt(_wsum(v, weight) / max(_wtot(target.shape[1], weight), 1e-300))
+
+    def start_constant(self, target, weight):
+        return np.average(target.astype(np.float64), axis=0, weights=weight)
+
+
+class MultiLogloss(MultiRMSE):
+    name = "MultiLogloss"
+    is_classification = True
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        p = torch.sigmoid(approx)
+        d, h = target - p, (p * (1 - p)).clamp_min(1e-16)
+        if weight is not None:
+            d, h = d * weight, h * weight
+        return d, h
+
+    def value(self, approx, target, weight, ctx=None):
+        v = (torch.nn.functional.softplus(approx) - target * approx).mean(0)
+        return _wsum(v, weight) / max(_wtot(target.shape[1], weight), 1e-300)
+
+    def start_constant(self, target, weight):
+        return np.zeros(self.dims)
+
+
+class MultiCrossEntropy(MultiLogloss):
+    name = "MultiCrossEntropy"
+
+
+class RMSEWithUncertainty(Objective):
+    name = "RMSEWithUncertainty"
+    is_pointwise = False
+    dims = 2
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        mu, ls = approx[0], approx[1]          # mean, log std
+        prec = torch.exp(-2 * ls)
+        d0 = (target - mu) * prec
+        d1 = (target - mu) ** 2 * prec - 1.0
+        h0 = prec
+        h1 = (2 * (target - mu) ** 2 * prec).clamp_min(1e-6)
+        der, hess = torch.stack([d0, d1]), torch.stack([h0, h1])
+        if weight is not None:
+            der, hess = der * weight, hess * weight
+        return der, hess
+
+    def value(self, approx, target, weight, ctx=None):
+        mu, ls = approx[0], approx[1]
+        v = ls + 0.5 * (target - mu) ** 2 * torch.exp(-2 * ls) + 0.5 * math.log(2 * math.pi)
+        return _wsum(v, weight) / max(_wtot(target.numel(), weight), 1e-300)
+
+    def start_constant(self, target, weight):
+        m = float(np.average(target, weights=weight))
+        var = float(np.average((target - m) ** 2, weights=weight))
+        return np.array([m, 0.5 * math.log(max(var, 1e-12))])
+
+
+class UserObjective(Objective):
+    """Python custom objective with ``calc_ders_range(approxes, targets, weights)`` returning (der, der2) pairs in
+    the reference's sign convention (der2 <= 0), see catboost/python-package/catboost/_catboost.pyx trampolines."""
+    name = "PythonUserDefinedPerObject"
+    is_pointwise = False
+
+    def __init__(self, obj):
+        super().__init__({})
+        self.obj = obj
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        a = approx[0].detach().cpu().numpy().astype(np.float64)
+        t = target.detach().cpu().numpy().astype(np.float64)
+        w = None if weight is None else weight.detach().cpu().numpy().astype(np.float64)
+        res = self.obj.calc_ders_range(a, t, w)
+        d = np.array([r[0] for r in res], dtype=np.float32)
+        h = -np.array([r[1] for r in res], dtype=np.float32)
+        dev = approx.device
+        return torch.from_numpy(d).to(dev).unsqueeze(0), torch.from_numpy(h).to(dev).clamp_min(1e-16).unsqueeze(0)
+
+    def value(self, approx, target, weight, ctx=None):
+        return float("nan")
+
+
+def _weighted_quantile(values, weight, alpha):
+    v = np.asarray(values, dtype=np.float64)
+    order = np.argsort(v, kind="stable")
+    v = v[order]
+    w = np.ones_like(v) if weight is None else np.asarray(weight, dtype=np.float64)[order]
+    cw = np.cumsum(w)
+    k = int(np.searchsorted(cw, alpha * cw[-1], side="left"))
+    return float(v[min(k, len(v) - 1)])
+
+
+_POINTWISE = {c.name: c for c in (RMSE, Logloss, CrossEntropy, Poisson, MAE, Quantile, LogLinQuantile, MAPE, Huber,
+                                  Lq, Expectile, Tweedie, LogCosh)}
+
+
+def make_objective(loss, params: dict, n_classes: Optional[int] = None, n_targets: int = 1) -> Objective:
+    if not isinstance(loss, str):
+        return UserObjective(loss)
+    if loss in _POINTWISE:
+        return _POINTWISE[loss](params)
+    if loss == "MultiClass":
+        return MultiClass(params, n_classes or 2)
+    if loss == "MultiClassOneVsAll":
+        return MultiClassOneVsAll(params, n_classes or 2)
+    if loss == "MultiRMSE":
+        return MultiRMSE(params, n_targets)
+    if loss == "MultiLogloss":
+        return MultiLogloss(params, n_targets)
+    if loss == "MultiCrossEntropy":
+        return MultiCrossEntropy(params, n_targets)
+    if loss == "RMSEWithUncertainty":
+        return RMSEWithUncertainty(params)
+    from .ranking import make_ranking_objective
+    obj = make_ranking_objective(loss, params)
+    if obj is None:
+        raise CatBoostError(f"loss function {loss!r} is not implemented")
+    return obj
