@@ -1,0 +1,262 @@
+#!/usr/bin/env python
+"""Headline benchmark: seconds per 1000 boosting iterations (device-timed, max over ranks).
+
+    python bench.py --gpus N --steps K --warmup W [--config higgs|epsilon|small] [--impl reference]
+
+Default config ``higgs`` is the dense numeric binary-classification workload: 10.5M rows x 28 float32 features
+(21 ~N(0,1) + 7 non-linear derived), Logloss, symmetric trees depth 6, border_count 128, learning_rate 0.1,
+doc-parallel over N GPUs (strong scaling: the row count is fixed, each rank holds rows/N).
+A "step" is one boosting iteration.  Two numbers are reported:
+
+* ``value``     -- K iterations of the device-resident trainer, each bracketed by CUDA events (L2 flushed between
+                   iterations with a 512 MiB write that is not timed), max over ranks.
+* ``e2e.value`` -- the same metric through the public API (``CatBoostClassifier.fit`` on host data), including the
+                   host->device upload of the feature matrix from pinned memory, quantisation, and a device->host
+                   read of the learn loss every iteration.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+BASELINE_S_PER_1000 = {"higgs": 55.601, "epsilon": 44.971, "small": None}
+CONFIGS = {
+    # rows, float features, depth, border_count
+    "higgs": dict(rows=10_500_000, features=28, depth=6, border_count=128, model="Logloss symmetric depth6 10.5Mx28"),
+    "epsilon": dict(rows=400_000, features=2000, depth=6, border_count=128, model="Logloss symmetric depth6 400Kx2000"),
+    "small": dict(rows=200_000, features=28, depth=6, border_count=128, model="Logloss symmetric depth6 200Kx28"),
+}
+
+
+def make_data(config: str, rows: int, features: int, rank: int, world: int, seed: int = 0):
+    """Seeded synthetic shard of the named shape (rows/world rows for this rank)."""
+    lo, hi = rows * rank // world, rows * (rank + 1) // world
+    n = hi - lo
+    rng = np.random.default_rng(seed * 1000 + rank)
+    if config == "epsilon":
+        X = rng.standard_normal((n, features), dtype=np.float32)
+        X /= np.linalg.norm(X, axis=1, keepdims=True)
+        w = np.random.default_rng(seed + 7).standard_normal(features).astype(np.float32)
+        y = ((X @ w + 0.1 * rng.standard_normal(n, dtype=np.float32)) > 0).astype(np.float32)
+        return X, y
+    base = features * 3 // 4
+    X = np.empty((n, features), dtype=np.float32)
+    X[:, :base] = rng.standard_normal((n, base), dtype=np.float32)
+    r2 = np.random.default_rng(seed + 11)
+    for j in range(base, features):
+        a, b = r2.integers(0, base, 2)
+        kind = (j - base) % 3
+        X[:, j] = X[:, a] * X[:, b] if kind == 0 else (np.abs(X[:, a] - X[:, b]) if kind == 1 else X[:, a] ** 2)
+    f = np.zeros(n, dtype=np.float32)
+    for _ in range(8):
+        a, b, c = r2.integers(0, features, 3)
+        f += r2.standard_normal() * X[:, a] + 0.5 * r2.standard_normal() * X[:, b] * X[:, c]
+    f = f / max(float(f.std()), 1e-6) + 0.12
+    y = (rng.random(n, dtype=np.float32) < 1.0 / (1.0 + np.exp(-f))).astype(np.float32)
+    return X, y
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock / throttle reasons during the timed region (reading only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            p = [x.strip() for x in ln.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1])); mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        top = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(top) if top else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args):
+    """The unmodified reference cannot be built offline: its python package needs the native build
+    (build_native.py / conan-fetched dependencies / clang), and no catboost wheel is in the offline wheelhouse."""
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "catboost python package cannot be built offline (pip install of /root/reference "
+                                     "fails: no setup.py at the root; python-package build needs conan + network)"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="higgs", choices=sorted(CONFIGS))
+    ap.add_argument("--rows", type=int, default=0)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--reduce", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-flush", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.gpus > 1 and "RANK" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29541", os.path.abspath(__file__)] + sys.argv[1:]
+        return subprocess.call(cmd)
+
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    import catboost_b200 as cb
+    from catboost_b200.data.pool import Pool
+    from catboost_b200.params import resolve_options
+    from catboost_b200.parallel.runtime import DistContext
+    from catboost_b200.train.boosting import build_store, plan_features
+    from catboost_b200.train.gpu_engine import GpuObliviousEngine
+    from catboost_b200.train.objectives import make_objective
+
+    cfg = dict(CONFIGS[args.config])
+    if args.rows:
+        cfg["rows"] = args.rows
+    K, W = args.steps, args.warmup
+    X, y = make_data(args.config, cfg["rows"], cfg["features"], rank, world)
+    params = dict(loss_function="Logloss", iterations=K + W, depth=cfg["depth"], border_count=cfg["border_count"],
+                  learning_rate=0.1, l2_leaf_reg=3.0, task_type="GPU", random_seed=0, allow_writing_files=False,
+                  histogram_reduce=args.reduce)
+
+    # ---------------- device-timed trainer steps -------------------------------------------------------------
+    ctx = DistContext.current(dev)
+    pool = Pool(X, y)
+    o = resolve_options(params, "Logloss", n_rows=cfg["rows"])
+    plan = plan_features(o, pool, ctx, None)
+    store, h2d = build_store(plan, pool, dev)
+    obj = make_objective("Logloss", {})
+    p1 = float(y.mean())
+    bias = float(np.log(p1 / (1 - p1)))
+    eng = GpuObliviousEngine(store, torch.from_numpy(y), None, torch.full((len(y),), bias), obj, depth=cfg["depth"],
+                             iterations=K + W, learning_rate=0.1, l2_leaf_reg=3.0, score_function=o.score_function,
+                             random_strength=float(o.random_strength), bootstrap_type=o.bootstrap_type,
+                             bootstrap_param=float(o.bagging_temperature or 1.0), leaf_method=o.leaf_estimation_method,
+                             leaf_iterations=int(o.leaf_estimation_iterations), seed=0, ctx=ctx, reduce=args.reduce)
+    flush = None if args.no_flush else torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    eng.step(W)
+    torch.cuda.synchronize(dev)
+    ctx.barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    for k in range(K):
+        if flush is not None:
+            flush.fill_(k & 0xFF)
+        if world > 1:
+            dist.barrier(device_ids=[local])
+        evs[k][0].record()
+        eng.step(1)
+        evs[k][1].record()
+    torch.cuda.synchronize(dev)
+    ctx.barrier()
+    clocks = sampler.stop()
+    total_ms = sum(a.elapsed_time(b) for a, b in evs)
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    launches = eng.launches_per_iter * K
+    loss_curve = eng.learn_loss_history()
+    eng.finish()
+    if eng.arena is not None:
+        eng.arena.check_status()
+    eng.close()
+    del eng, store
+    torch.cuda.empty_cache()
+
+    # ---------------- end to end through the public API -----------------------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        Xp = torch.from_numpy(X).pin_memory().numpy() if hasattr(torch.Tensor, "pin_memory") else X
+        model = cb.CatBoostClassifier(**params, verbose=True, metric_period=1)
+        devnull = open(os.devnull, "w")
+        torch.cuda.synchronize(dev)
+        ctx.barrier()
+        t0 = time.perf_counter()
+        model.fit(Xp, y, log_cout=devnull)
+        torch.cuda.synchronize(dev)
+        t1 = time.perf_counter()
+        e2e_s = torch.tensor([t1 - t0], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+        iters = K + W
+        e2e = {"value": float(e2e_s.item()) / iters * 1000.0, "unit": "s/1000iter",
+               "h2d_bytes_per_step": int(X.nbytes * world // iters), "d2h_bytes_per_step": 16,
+               "fit_seconds": float(e2e_s.item()), "iterations": iters,
+               "note": "whole fit(): pinned upload + quantisation + iterations with a per-iteration learn-loss read"}
+    if rank == 0:
+        ms_per_step = total_ms / K
+        value = ms_per_step          # ms per iteration == seconds per 1000 iterations
+        base = BASELINE_S_PER_1000.get(args.config)
+        out = {"metric": "sec/1000 iters (device-timed, max over ranks)", "value": value, "unit": "s/1000iter",
+               "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": False,
+               "scaling": "strong", "vs_baseline": (value / base) if base else None, "dtype": "fp32",
+               "data": "synthetic", "impl": "ours",
+               "config": {"model": cfg["model"], "global_batch": cfg["rows"], "seq_len": cfg["features"],
+                          "parallelism": f"doc-parallel dp{world}", "loss": "Logloss", "depth": cfg["depth"],
+                          "border_count": cfg["border_count"], "learning_rate": 0.1, "histogram_reduce": args.reduce,
+                          "l2_policy": ("flush: 512 MiB write between timed iterations" if flush is not None
+                                        else "inputs larger than L2")},
+               "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+               "learn_loss_first_last": [float(loss_curve[1]) if len(loss_curve) > 1 else None, float(loss_curve[-1])]}
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier(device_ids=[local])
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

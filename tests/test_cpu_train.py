@@ -1,0 +1,120 @@
+"""CPU trainer, API surface and model behaviour (runs without a GPU)."""
+import numpy as np
+import pytest
+
+import catboost_b200 as cb
+
+
+def _binary(n=4000, F=8, seed=0):
+    rng = np.random.default_rng(seed)
+    X = rng.standard_normal((n, F), dtype=np.float32)
+    w = rng.standard_normal(F).astype(np.float32)
+    y = (X @ w + 0.3 * rng.standard_normal(n, dtype=np.float32) > 0).astype(int)
+    return X, y
+
+
+def test_classifier_learns_and_predicts():
+    X, y = _binary()
+    m = cb.CatBoostClassifier(iterations=40, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False)
+    m.fit(X[:3000], y[:3000], eval_set=(X[3000:], y[3000:]))
+    assert m.tree_count_ == 40 or m.tree_count_ == m.best_iteration_ + 1
+    acc = (m.predict(X[3000:]) == y[3000:]).mean()
+    assert acc > 0.85
+    proba = m.predict_proba(X[:10])
+    assert proba.shape == (10, 2) and np.allclose(proba.sum(1), 1)
+    ev = m.get_evals_result()
+    assert ev["learn"]["Logloss"][-1] < ev["learn"]["Logloss"][0]
+    raw = m.predict(X[:50], prediction_type="RawFormulaVal")
+    staged = list(m.staged_predict(X[:50], prediction_type="RawFormulaVal"))
+    assert np.allclose(staged[-1], raw, atol=1e-9)
+
+
+@pytest.mark.parametrize("policy", ["SymmetricTree", "Depthwise", "Lossguide"])
+def test_grow_policies(policy):
+    X, y = _binary(3000, 6, 1)
+    m = cb.CatBoostClassifier(iterations=25, depth=4, grow_policy=policy, max_leaves=12, learning_rate=0.3,
+                              verbose=False, allow_writing_files=False)
+    m.fit(X, y)
+    assert (m.predict(X) == y).mean() > 0.85
+
+
+def test_regressor_losses():
+    rng = np.random.default_rng(2)
+    X = rng.standard_normal((3000, 5), dtype=np.float32)
+    y = X[:, 0] * 2 + X[:, 1] ** 2 + 0.1 * rng.standard_normal(3000)
+    for loss in ["RMSE", "MAE", "Quantile:alpha=0.7", "Huber:delta=1.0", "LogCosh", "Poisson"]:
+        yy = np.abs(y) if loss == "Poisson" else y
+        m = cb.CatBoostRegressor(iterations=40, depth=4, learning_rate=0.3, loss_function=loss, verbose=False,
+                                 allow_writing_files=False)
+        m.fit(X, yy)
+        ev = m.get_evals_result()["learn"]
+        k = list(ev.keys())[0]
+        assert ev[k][-1] < ev[k][0], loss
+
+
+def test_multiclass():
+    rng = np.random.default_rng(3)
+    X = rng.standard_normal((3000, 6), dtype=np.float32)
+    y = np.argmax(X[:, :3] + 0.3 * rng.standard_normal((3000, 3)), axis=1)
+    labels = np.array(["a", "b", "c"])[y]
+    m = cb.CatBoostClassifier(iterations=30, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False)
+    m.fit(X, labels)
+    assert m._model.loss_name == "MultiClass"
+    assert (m.predict(X) == labels).mean() > 0.85
+    assert m.predict_proba(X).shape == (3000, 3)
+
+
+def test_one_hot_categorical():
+    rng = np.random.default_rng(4)
+    n = 3000
+    c = rng.integers(0, 3, n)
+    x = rng.standard_normal(n).astype(np.float32)
+    y = ((c == 1) * 2.0 + x > 0.5).astype(int)
+    data = np.empty((n, 2), dtype=object)
+    data[:, 0] = x
+    data[:, 1] = np.array(["u", "v", "w"])[c]
+    m = cb.CatBoostClassifier(iterations=30, depth=3, learning_rate=0.3, one_hot_max_size=10, verbose=False,
+                              allow_writing_files=False)
+    m.fit(data, y, cat_features=[1])
+    assert (m.predict(data) == y).mean() > 0.95
+
+
+def test_params_validation_and_synonyms():
+    with pytest.raises(cb.CatBoostError):
+        cb.CatBoostClassifier(no_such_param=1)
+    m = cb.CatBoostRegressor(n_estimators=5, eta=0.5, max_depth=3, verbose=False, allow_writing_files=False)
+    X, y = _binary(500, 4)
+    m.fit(X, y.astype(float))
+    assert m.tree_count_ == 5
+    assert m.get_all_params()["learning_rate"] == 0.5
+    from catboost_b200.params import parse_devices
+    assert parse_devices("0-3") == [0, 1, 2, 3] and parse_devices("0:2:5") == [0, 2, 5]
+    assert parse_devices("-1", 4) == [0, 1, 2, 3]
+
+
+def test_overfitting_detector_and_best_model():
+    X, y = _binary(2000, 5, 5)
+    yn = y.copy()
+    flip = np.random.default_rng(0).random(2000) < 0.35
+    yn[flip] = 1 - yn[flip]
+    m = cb.CatBoostClassifier(iterations=300, depth=6, learning_rate=0.5, early_stopping_rounds=10, verbose=False,
+                              allow_writing_files=False)
+    m.fit(X[:1000], yn[:1000], eval_set=(X[1000:], yn[1000:]))
+    assert m.tree_count_ < 300
+    assert m.best_iteration_ is not None and m.tree_count_ == m.best_iteration_ + 1
+
+
+def test_border_selection_native():
+    from catboost_b200.data.quantization import select_borders
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((5000, 3)).astype(np.float32)
+    X[:, 2] = np.round(X[:, 2])      # few distinct values
+    for bt in ["GreedyLogSum", "Median", "Uniform", "UniformAndQuantiles", "MinEntropy"]:
+        borders, _ = select_borders(X, 16, bt)
+        for f, b in enumerate(borders):
+            assert len(b) <= 16 and np.all(np.diff(b) > 0)
+        assert len(borders[0]) == 16
+    # greedy borders of a near-uniform sample are close to quantiles
+    b, _ = select_borders(X[:, :1], 15, "GreedyLogSum")
+    q = np.searchsorted(np.sort(X[:, 0]), b[0]) / 5000
+    assert np.all(np.abs(np.diff(q) - 1 / 16) < 0.02)

@@ -1,0 +1,207 @@
+"""Numerics of the CUDA kernels against plain PyTorch fp32 restatements of the same operation."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _store(n=5000, F=7, border_count=32, seed=0, device="cuda"):
+    from catboost_b200.data.pool import Pool
+    from catboost_b200.params import resolve_options
+    from catboost_b200.parallel.runtime import DistContext
+    from catboost_b200.train.boosting import build_store, plan_features
+    rng = np.random.default_rng(seed)
+    X = rng.standard_normal((n, F), dtype=np.float32)
+    X[rng.random((n, F)) < 0.02] = np.nan
+    y = (X[:, 0] + 0.5 * np.nan_to_num(X[:, 1]) > 0).astype(np.float32)
+    pool = Pool(X, y)
+    o = resolve_options(dict(border_count=border_count, task_type="GPU" if device == "cuda" else "CPU"), "Logloss", n)
+    plan = plan_features(o, pool, DistContext(0, 1, torch.device(device)), None)
+    store, _ = build_store(plan, pool, torch.device(device))
+    return X, y, plan, store
+
+
+def test_quantize_matches_searchsorted():
+    X, y, plan, store = _store()
+    torch.cuda.synchronize()
+    for f in range(store.F):
+        b = torch.from_numpy(plan.quant.borders[f])
+        col = torch.from_numpy(X[:, f])
+        ref = torch.searchsorted(b, col.contiguous(), right=False)      # number of borders < x
+        ref = torch.where(torch.isnan(col), torch.zeros_like(ref), ref)
+        got = store.column(f).cpu().long()
+        assert torch.equal(got, ref), f"feature {f}"
+
+
+@pytest.mark.parametrize("nslots,S", [(1, 2), (8, 2), (5, 3), (64, 2)])
+def test_hist_matches_reference(nslots, S):
+    from catboost_b200.ops import api as ops
+    X, y, plan, store = _store(n=20011, F=9, border_count=64, seed=1)
+    g = torch.Generator().manual_seed(3)
+    n, npad = store.n, store.npad
+    leaf = torch.zeros(npad, dtype=torch.int16)
+    leaf[:n] = torch.randint(0, nslots + 2, (n,), generator=g).short()
+    table = torch.full((nslots + 2,), -1, dtype=torch.int16)
+    table[:nslots] = torch.arange(nslots, dtype=torch.int16)
+    stats = torch.zeros((S, npad))
+    stats[:, :n] = torch.randn((S, n), generator=g)
+    got = ops.hist(store, leaf.cuda(), stats.cuda(), table.cuda(), nslots)
+    ref = ops.hist_reference(store, leaf.cuda(), stats.cuda(), table.cuda(), nslots)
+    torch.cuda.synchronize()
+    assert torch.allclose(got, ref, rtol=1e-4, atol=2e-3), float((got - ref).abs().max())
+
+
+def test_leaf_index_and_update_match_reference():
+    from catboost_b200.ops import api as ops
+    X, y, plan, store = _store(n=7001, F=6, border_count=16, seed=2)
+    splits = torch.tensor([[0, 3, 0, 0], [2, 7, 0, 0], [-1, 0, 0, 0], [5, 1, 0, 0]], dtype=torch.int32)
+    got = ops.leaf_index(store, splits.cuda())[: store.n].long().cpu()
+    ref = ops.leaf_index_reference(store, splits.numpy()).cpu()
+    assert torch.equal(got, ref)
+    leaf = torch.zeros(store.npad, dtype=torch.int16, device="cuda")
+    for k, (f, b, _, fl) in enumerate(splits.tolist()):
+        if f >= 0:
+            ops.update_leaf(store, leaf, f, b, bool(fl & 1), k)
+    assert torch.equal(leaf[: store.n].long().cpu(), ref)
+
+
+def _engine_vs_generic(depth, n, F, loss="Logloss", score="Cosine", leaf_iters=3):
+    """One tree of the fused device trainer against the generic (tensor-op) learner on identical statistics."""
+    from catboost_b200.params import resolve_options
+    from catboost_b200.train.generic import GenericLearner, estimate_leaves
+    from catboost_b200.train.gpu_engine import GpuObliviousEngine
+    from catboost_b200.train.objectives import make_objective
+    X, y, plan, store = _store(n=n, F=F, border_count=32, seed=5)
+    if loss == "RMSE":
+        y = (np.nan_to_num(X[:, 0]) * 2 + np.nan_to_num(X[:, 1]) ** 2).astype(np.float32)
+    obj = make_objective(loss, {})
+    o = resolve_options(dict(loss_function=loss, depth=depth, task_type="GPU", bootstrap_type="No", random_strength=0,
+                             score_function=score, leaf_estimation_iterations=leaf_iters, learning_rate=0.5,
+                             l2_leaf_reg=3.0, border_count=32), loss, n)
+    eng = GpuObliviousEngine(store, torch.from_numpy(y), None, torch.zeros(n), obj, depth=depth, iterations=3,
+                             learning_rate=0.5, l2_leaf_reg=3.0, score_function=score, random_strength=0.0,
+                             bootstrap_type="No", leaf_method="Newton", leaf_iterations=leaf_iters, seed=0)
+    eng.step(1)
+    sp, vals, wts = eng.finish()
+    # generic learner
+    approx = torch.zeros((1, store.npad), device="cuda")
+    target = torch.from_numpy(y).cuda()
+    der, hess = obj.der_hess(approx[:, :n], target, None)
+    dp = torch.zeros((1, store.npad), device="cuda"); hp = torch.zeros((1, store.npad), device="cuda")
+    dp[:, :n], hp[:, :n] = der, hess
+    gl = GenericLearner(store, o, 1)
+    tr = gl.build_tree(dp, hp, None, 0)
+    gv, gw = estimate_leaves(obj, approx, target, None, tr.leaf, tr.n_leaves, n, o)
+    assert np.array_equal(sp[0][:, :2], tr.splits[:, :2]), (sp[0], tr.splits)
+    assert np.allclose(wts[0], gw, rtol=1e-5, atol=1e-3)
+    assert np.allclose(vals[0], gv[:, 0], rtol=2e-3, atol=2e-4), float(np.abs(vals[0] - gv[:, 0]).max())
+    eng.close()
+
+
+@pytest.mark.parametrize("depth", [1, 2, 4, 6])
+def test_fused_level_kernel_matches_generic_learner(depth):
+    _engine_vs_generic(depth, 30011, 10)
+
+
+def test_fused_level_kernel_rmse_l2():
+    _engine_vs_generic(5, 20000, 6, loss="RMSE", score="L2", leaf_iters=1)
+
+
+def test_graph_replay_equals_eager():
+    from catboost_b200.train.gpu_engine import GpuObliviousEngine
+    from catboost_b200.train.objectives import make_objective
+    X, y, plan, store = _store(n=40000, F=8, border_count=64, seed=7)
+    obj = make_objective("Logloss", {})
+    outs = []
+    for use_graph in (False, True):
+        eng = GpuObliviousEngine(store, torch.from_numpy(y), None, torch.zeros(len(y)), obj, depth=5, iterations=6,
+                                 learning_rate=0.3, l2_leaf_reg=3.0, random_strength=1.0, bootstrap_type="Bayesian",
+                                 leaf_iterations=2, seed=3, use_graph=use_graph)
+        eng.step(6)
+        sp, vals, wts = eng.finish()
+        outs.append((sp, vals, eng.learn_loss_history()))
+        eng.close()
+    assert np.array_equal(outs[0][0][:, :, :2], outs[1][0][:, :, :2])
+    assert np.allclose(outs[0][1], outs[1][1], rtol=1e-3, atol=1e-4)
+    assert outs[1][2][-1] < outs[1][2][0]
+
+
+def test_unfused_path_matches_fused():
+    from catboost_b200.train.gpu_engine import GpuObliviousEngine
+    from catboost_b200.train.objectives import make_objective
+    X, y, plan, store = _store(n=25000, F=8, border_count=32, seed=9)
+    obj = make_objective("Logloss", {})
+    res = []
+    for fused in (True, False):
+        eng = GpuObliviousEngine(store, torch.from_numpy(y), None, torch.zeros(len(y)), obj, depth=4, iterations=3,
+                                 learning_rate=0.3, l2_leaf_reg=3.0, random_strength=0.0, bootstrap_type="No",
+                                 leaf_iterations=1, seed=3, use_graph=False)
+        if not fused:
+            eng.reduce = "nccl"          # stand-alone kernels (hist, score, select) without the cooperative launch
+            eng.partial = torch.zeros((eng.slots_max * eng.S, eng.TB), device="cuda")
+        eng.step(3)
+        res.append(eng.finish())
+        eng.close()
+    assert np.array_equal(res[0][0][:, :, :2], res[1][0][:, :, :2])
+    assert np.allclose(res[0][1], res[1][1], rtol=1e-3, atol=1e-4)
+
+
+def test_gpu_fit_predict_and_gpu_apply():
+    import catboost_b200 as cb
+    rng = np.random.default_rng(0)
+    n, F = 60000, 16
+    X = rng.standard_normal((n, F), dtype=np.float32)
+    w = rng.standard_normal(F).astype(np.float32)
+    y = (X @ w + 0.5 * rng.standard_normal(n, dtype=np.float32) > 0).astype(int)
+    m = cb.CatBoostClassifier(iterations=40, depth=6, learning_rate=0.2, task_type="GPU", devices="0", verbose=False,
+                              allow_writing_files=False)
+    m.fit(X[:50000], y[:50000], eval_set=(X[50000:], y[50000:]))
+    ev = m.get_evals_result()
+    assert ev["validation"]["Logloss"][-1] < 0.45
+    p_cpu = m.predict(X[50000:], prediction_type="RawFormulaVal")
+    p_gpu = m.predict(X[50000:], prediction_type="RawFormulaVal", task_type="GPU")
+    assert np.allclose(p_cpu, p_gpu, rtol=1e-4, atol=1e-4)
+    acc = float((m.predict(X[50000:]) == y[50000:]).mean())
+    assert acc > 0.88, acc
+
+
+def test_gpu_regression_rmse():
+    import catboost_b200 as cb
+    rng = np.random.default_rng(1)
+    X = rng.standard_normal((30000, 8), dtype=np.float32)
+    y = X[:, 0] * 2 + np.sin(X[:, 1] * 2) + 0.1 * rng.standard_normal(30000, dtype=np.float32)
+    m = cb.CatBoostRegressor(iterations=60, depth=5, learning_rate=0.2, task_type="GPU", verbose=False,
+                             allow_writing_files=False)
+    m.fit(X, y)
+    rmse = float(np.sqrt(np.mean((m.predict(X) - y) ** 2)))
+    assert rmse < 0.45, rmse
+
+
+def test_device_wait_times_out_without_hanging():
+    """A wait on a tag nobody writes returns with the status word set (bounded spin, no trap)."""
+    from catboost_b200.ops import native
+    from catboost_b200.parallel.runtime import ArenaLayout, DistContext, PeerArena
+    dev = torch.device("cuda", 0)
+    ctx = DistContext(0, 1, dev)
+    arena = PeerArena(ctx, ArenaLayout(1, 256, 64), timeout_s=0.05)
+    lib = native.cuda_lib()
+    # pretend to be rank 0 of 2 whose peer never writes: build a 2-rank comm over the same local buffer
+    L = ArenaLayout(2, 256, 64)
+    buf = torch.zeros(L.total_bytes, dtype=torch.uint8, device=dev)
+    arr = ctypes.c_void_p * 2
+    base = buf.data_ptr()
+    h = lib.cb_comm_create(0, 2, int(0.05e9), ctypes.c_void_p(arena.status.data_ptr()),
+                           ctypes.c_void_p(arena.epoch.data_ptr()), arr(base + L.off_mbox, base + L.off_mbox),
+                           arr(base + L.off_mbox_flag, base + L.off_mbox_flag),
+                           256, arr(base + L.off_slots, base + L.off_slots),
+                           arr(base + L.off_slot_flag, base + L.off_slot_flag), 64)
+    vals = torch.ones(4, dtype=torch.float64, device=dev)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.cb_allreduce_sum(ctypes.c_void_p(h), ctypes.c_void_p(vals.data_ptr()), 4, st) == 0
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="timed out"):
+        arena.check_status()
+    lib.cb_comm_destroy(ctypes.c_void_p(h))
