@@ -58,10 +58,11 @@ def hist(store: BinnedStore, leaf: torch.Tensor, stats: torch.Tensor, slot_table
     sm, max_smem = device_info(dev)
     B = max(4, (store.max_bins + 3) // 4 * 4)
     per_slot = S * 4 * B * 4
-    spp = max(1, min(nslots, (max_smem - 1024) // per_slot))
-    if per_slot > max_smem - 1024:
+    max_smem -= 2048
+    spp = max(1, min(nslots, max_smem // per_slot))
+    if per_slot > max_smem:
         # too many statistic columns for one shared-memory pass: process them in chunks
-        smax = max(1, (max_smem - 1024) // (4 * B * 4))
+        smax = max(1, max_smem // (4 * B * 4))
         for s0 in range(0, S, smax):
             s1 = min(S, s0 + smax)
             out[:, s0:s1] = hist(store, leaf, stats[s0:s1].contiguous(), slot_table, nslots)

@@ -155,8 +155,15 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&p->sm_count, cudaDevAttrMultiProcessorCount, dev);
     cudaDeviceGetAttribute(&p->max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-    cudaFuncSetAttribute(cb_level_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, p->max_smem);
-    // keep pointers needed for the per-level swap
+    // dynamic shared memory available to this kernel = opt-in maximum minus its static shared memory
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, cb_level_fused_kernel) != cudaSuccess) { cudaGetLastError(); delete p; return nullptr; }
+    p->max_smem -= (int)fa.sharedSizeBytes;
+    if (cudaFuncSetAttribute(cb_level_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, p->max_smem) != cudaSuccess) {
+        cudaGetLastError();
+        delete p;
+        return nullptr;
+    }
     return p;
 }
 
@@ -172,7 +179,7 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
     const int nslots = level == 0 ? 1 : (1 << (level - 1));
     const int per_slot = p->a.h.S * 4 * p->a.h.B * 4;
     int spp = nslots;
-    const int budget = p->max_smem - 1024;
+    const int budget = p->max_smem;
     if (spp * per_slot > budget) spp = budget / per_slot;
     if (spp < 1) return 0;
     const int smem = spp * per_slot;

@@ -255,12 +255,19 @@ CB_API int cb_hist(const CbData* d, const unsigned short* leaf, const float* sta
     a.d = *d; a.leaf = leaf; a.stats = stats; a.S = S; a.level = level; a.small_mask = small_mask;
     a.slots_per_pass = slots_per_pass; a.B = B; a.out = out; a.slot_table = slot_table; a.nslots_table = nslots_table;
     const int smem = cb_hist_smem_bytes(slots_per_pass, S, B);
-    if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
     if (!g_hist_smem_set) {
-        cudaError_t e = cudaFuncSetAttribute(cb_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e != cudaSuccess) return (int)e;
-        g_hist_smem_set = 1;
+        int dev = 0, optin = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        cudaFuncAttributes fa;
+        cudaError_t e = cudaFuncGetAttributes(&fa, cb_hist_kernel);
+        if (e == cudaSuccess) {
+            g_hist_smem_set = optin - (int)fa.sharedSizeBytes;
+            e = cudaFuncSetAttribute(cb_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g_hist_smem_set);
+        }
+        if (e != cudaSuccess) { g_hist_smem_set = 0; cudaGetLastError(); return (int)e; }
     }
+    if (smem > g_hist_smem_set) return (int)cudaErrorInvalidValue;
     cb_hist_kernel<<<grid, threads, smem, st>>>(a);
     CB_LAUNCH_CHECK();
     return 0;
@@ -595,7 +602,7 @@ CB_API int cb_predict_oblivious(const float* X, long long n, long long ldx, cons
     static int set = 0;
     if (!set) {
         cudaError_t e = cudaFuncSetAttribute(cb_predict_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return (int)e;
+        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
         set = 1;
     }
     cb_predict_kernel<<<(unsigned)((n + 255) / 256), 256, U * 256, st>>>(a);

@@ -220,7 +220,7 @@ class GpuObliviousEngine:
                                    self.depth, level - 1, self.grid_stream, self._stream()), "cb_update_leaf")
         self.partial[:rows].zero_()
         per_slot = self.S * 4 * self.B * 4
-        spp = max(1, min(nslots, (self.max_smem - 1024) // per_slot))
+        spp = max(1, min(nslots, (self.max_smem - 2048) // per_slot))
         grid = self.sm_count * max(1, min(4, (200 * 1024) // max(1, spp * per_slot)))
         chk(lib.cb_hist(ctypes.c_void_p(st.handle), _p(self.leaf), _p(self.stats), self.S, level,
                         _p(self.mask[level & 1]), None, 0, spp, self.B, _p(self.partial), grid, self.threads,
