@@ -1,0 +1,258 @@
+"""Feature importances and SHAP values.
+
+* PredictionValuesChange: for every split, the weighted squared deviation of the two children's values from their
+  weighted mean, summed over the trees and normalised to 100 (catboost/libs/fstr/calc_fstr.cpp).
+* ShapValues: exact TreeSHAP (path-dependent, covers = leaf weights), the algorithm the reference implements in
+  catboost/libs/fstr/shap_values.cpp; output ``[n, n_features + 1]`` (last column = expected value), or
+  ``[n, dims, n_features + 1]`` for multi-dimensional models.
+* LossFunctionChange: change of the loss when a feature's SHAP contribution is replaced by its mean.
+* Interaction: pairwise strength of features that meet in the same tree.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from .data.pool import CatBoostError, Pool
+from .metrics import make_metric
+from .models.model import Model, NonSymmetricTree, ObliviousTree
+
+
+def _split_flat_features(m: Model, sp):
+    """Flat (user column) indices a split depends on."""
+    if sp.kind == "float":
+        return [m.float_features[sp.feature].flat_index]
+    if sp.kind == "onehot":
+        return [m.cat_features[sp.feature].flat_index]
+    ctr = m.ctrs[sp.feature]
+    return [m.cat_features[c].flat_index for c in ctr.cat_features]
+
+
+def _as_nonsymmetric(t):
+    if isinstance(t, NonSymmetricTree):
+        return t
+    from .models.io import oblivious_to_nonsymmetric
+    return oblivious_to_nonsymmetric(t)
+
+
+def _node_stats(t: NonSymmetricTree, dims):
+    """cover and weighted mean value of every node (children before parents by reverse order)."""
+    n = len(t.split_of_node)
+    cover = np.zeros(n)
+    mean = np.zeros((n, dims))
+    order = _topo(t)
+    for node in reversed(order):
+        if t.split_of_node[node] < 0:
+            lf = t.leaf_of_node[node]
+            cover[node] = max(float(t.leaf_weights[lf]), 0.0) if lf < len(t.leaf_weights) else 0.0
+            mean[node] = t.leaf_values[lf]
+        else:
+            l, r = t.left[node], t.right[node]
+            cover[node] = cover[l] + cover[r]
+            if cover[node] > 0:
+                mean[node] = (mean[l] * cover[l] + mean[r] * cover[r]) / cover[node]
+            else:
+                mean[node] = 0.5 * (mean[l] + mean[r])
+    return cover, mean
+
+
+def _topo(t: NonSymmetricTree):
+    order, stack = [], [0]
+    while stack:
+        node = stack.pop()
+        order.append(node)
+        if t.split_of_node[node] >= 0:
+            stack += [int(t.right[node]), int(t.left[node])]
+    return order
+
+
+def prediction_values_change(m: Model) -> np.ndarray:
+    imp = np.zeros(m.n_features)
+    for t in m.trees:
+        ns = _as_nonsymmetric(t)
+        cover, mean = _node_stats(ns, m.dims)
+        for node in range(len(ns.split_of_node)):
+            si = ns.split_of_node[node]
+            if si < 0:
+                continue
+            l, r = ns.left[node], ns.right[node]
+            w0, w1 = cover[l], cover[r]
+            if w0 + w1 <= 0:
+                continue
+            avg = (mean[l] * w0 + mean[r] * w1) / (w0 + w1)
+            val = float((((mean[l] - avg) ** 2) * w0 + ((mean[r] - avg) ** 2) * w1).sum())
+            feats = _split_flat_features(m, m.splits[si])
+            for f in feats:
+                imp[f] += val / len(feats)
+    tot = imp.sum()
+    return imp / tot * 100.0 if tot > 0 else imp
+
+
+def interaction(m: Model):
+    pair = {}
+    for t in m.trees:
+        ns = _as_nonsymmetric(t)
+        cover, mean = _node_stats(ns, m.dims)
+        feats_in_tree = {}
+        for node in range(len(ns.split_of_node)):
+            si = ns.split_of_node[node]
+            if si < 0:
+                continue
+            l, r = ns.left[node], ns.right[node]
+            w0, w1 = cover[l], cover[r]
+            if w0 + w1 <= 0:
+                continue
+            avg = (mean[l] * w0 + mean[r] * w1) / (w0 + w1)
+            val = float((((mean[l] - avg) ** 2) * w0 + ((mean[r] - avg) ** 2) * w1).sum())
+            for f in _split_flat_features(m, m.splits[si]):
+                feats_in_tree[f] = feats_in_tree.get(f, 0.0) + val
+        fl = sorted(feats_in_tree)
+        for i in range(len(fl)):
+            for j in range(i + 1, len(fl)):
+                pair[(fl[i], fl[j])] = pair.get((fl[i], fl[j]), 0.0) + min(feats_in_tree[fl[i]], feats_in_tree[fl[j]])
+    tot = sum(pair.values())
+    out = [[a, b, v / tot * 100.0 if tot > 0 else 0.0] for (a, b), v in pair.items()]
+    return sorted(out, key=lambda x: -x[2])
+
+
+# ---- TreeSHAP ---------------------------------------------------------------------------------------------
+class _Path:
+    __slots__ = ("d", "z", "o", "w")
+
+    def __init__(self, d, z, o, w):
+        self.d, self.z, self.o, self.w = d, z, o, w
+
+
+def _extend(path, pz, po, pi):
+    l = len(path)
+    path = [_Path(p.d, p.z, p.o, p.w) for p in path]
+    path.append(_Path(pi, pz, po, 1.0 if l == 0 else 0.0))
+    for i in range(l - 1, -1, -1):
+        path[i + 1].w += po * path[i].w * (i + 1) / (l + 1)
+        path[i].w = pz * path[i].w * (l - i) / (l + 1)
+    return path
+
+
+def _unwind(path, i):
+    l = len(path) - 1
+    path = [_Path(p.d, p.z, p.o, p.w) for p in path]
+    n = path[l].w
+    o, z = path[i].o, path[i].z
+    for j in range(l - 1, -1, -1):
+        if o != 0:
+            t = path[j].w
+            path[j].w = n * (l + 1) / ((j + 1) * o)
+            n = t - path[j].w * z * (l - j) / (l + 1)
+        else:
+            path[j].w = path[j].w * (l + 1) / (z * (l - j))
+    for j in range(i, l):
+        path[j].d, path[j].z, path[j].o = path[j + 1].d, path[j + 1].z, path[j + 1].o
+    return path[:l]
+
+
+def _unwound_sum(path, i):
+    l = len(path) - 1
+    o, z = path[i].o, path[i].z
+    n = path[l].w
+    tot = 0.0
+    for j in range(l - 1, -1, -1):
+        if o != 0:
+            t = n * (l + 1) / ((j + 1) * o)
+            tot += t
+            n = path[j].w - t * z * (l - j) / (l + 1)
+        else:
+            tot += path[j].w / (z * (l - j) / (l + 1))
+    return tot
+
+
+def _tree_shap_row(m, ns, cover, outcomes_col, phi, split_feat):
+    """Accumulate SHAP values of one tree for one row.  outcomes_col: bool per model split."""
+    dims = m.dims
+
+    def recurse(node, path, pz, po, pi):
+        path = _extend(path, pz, po, pi)
+        si = ns.split_of_node[node]
+        if si < 0:
+            v = ns.leaf_values[ns.leaf_of_node[node]]
+            for i in range(1, len(path)):
+                w = _unwound_sum(path, i)
+                phi[path[i].d] += w * (path[i].o - path[i].z) * v
+            return
+        hot, cold = (ns.right[node], ns.left[node]) if outcomes_col[si] else (ns.left[node], ns.right[node])
+        f = split_feat[si]
+        iz, io = 1.0, 1.0
+        k = next((i for i in range(1, len(path)) if path[i].d == f), None)
+        if k is not None:
+            iz, io = path[k].z, path[k].o
+            path = _unwind(path, k)
+        c = cover[node]
+        if c <= 0:
+            return
+        recurse(hot, path, iz * cover[hot] / c, io, f)
+        recurse(cold, path, iz * cover[cold] / c, 0.0, f)
+
+    recurse(0, [], 1.0, 1.0, -1)
+
+
+def shap_values(m: Model, pool: Pool) -> np.ndarray:
+    fd, ch = m.pool_arrays(pool)
+    n = pool.num_row()
+    F = m.n_features
+    out = np.zeros((n, F + 1, m.dims))
+    oc = m._split_outcomes_block(fd, ch, m._ctr_values(ch))
+    split_feat = [(_split_flat_features(m, sp)[0]) for sp in m.splits]
+    bias = np.broadcast_to(m.bias, (m.dims,)).astype(np.float64)
+    expected = bias.copy()
+    prepared = []
+    for t in m.trees:
+        ns = _as_nonsymmetric(t)
+        cover, mean = _node_stats(ns, m.dims)
+        prepared.append((ns, cover))
+        expected = expected + mean[0] * m.scale
+    import sys
+    sys.setrecursionlimit(max(sys.getrecursionlimit(), 10000))
+    for r in range(n):
+        phi = np.zeros((F + 1, m.dims))
+        col = oc[:, r]
+        for ns, cover in prepared:
+            if cover[0] <= 0:
+                continue
+            _tree_shap_row(m, ns, cover, col, phi, split_feat)
+        out[r, :F] = phi[:F] * m.scale
+        out[r, F] = expected
+    if m.dims == 1:
+        return out[:, :, 0]
+    return np.transpose(out, (0, 2, 1))
+
+
+def loss_function_change(estimator, data) -> np.ndarray:
+    m = estimator._model
+    pool = data if isinstance(data, Pool) else Pool(data)
+    if pool.label is None:
+        raise CatBoostError("LossFunctionChange needs labels")
+    sv = shap_values(m, pool)
+    raw = estimator._raw(pool)
+    y = estimator._encode_labels(pool.label)
+    loss = m.params.get("loss_function", m.loss_name) if isinstance(m.params.get("loss_function", None), str) else m.loss_name
+    metric = make_metric(loss)
+    kw = {}
+    if pool.group_id is not None:
+        kw["group_offsets"] = pool.group_offsets()
+    base = metric.eval(raw, y, pool.weight, **kw)
+    imp = np.zeros(m.n_features)
+    for f in range(m.n_features):
+        contrib = sv[:, f] if m.dims == 1 else sv[:, :, f]
+        if not np.any(contrib):
+            continue
+        alt = raw - contrib.reshape(raw.shape) + contrib.reshape(raw.shape).mean(axis=0, keepdims=True)
+        v = metric.eval(alt, y, pool.weight, **kw)
+        imp[f] = (base - v) if metric.is_max_optimal else (v - base)
+    return imp
+
+
+def prediction_diff(estimator, data) -> np.ndarray:
+    pool = data if isinstance(data, Pool) else Pool(data)
+    if pool.num_row() != 2:
+        raise CatBoostError("PredictionDiff needs exactly two rows")
+    sv = shap_values(estimator._model, pool)
+    d = sv[0, :-1] - sv[1, :-1] if sv.ndim == 2 else (sv[0, :, :-1] - sv[1, :, :-1]).sum(0)
+    return np.abs(d)

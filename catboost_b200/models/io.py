@@ -268,7 +268,8 @@ def model_from_cbm_bytes(blob: bytes) -> Model:
     m.splits = order
     leaf_values = mt.vector(8, np.float64)
     leaf_weights = mt.vector(9, np.float64)
-    steps = mt.vector(10, np.uint16).reshape(-1, 2)
+    steps = mt.vector(10, np.dtype([('l', '<u2'), ('r', '<u2')]))
+    steps = np.stack([steps['l'], steps['r']], axis=1) if len(steps) else np.zeros((0, 2), dtype=np.uint16)
     node_to_leaf = mt.vector(11, np.uint32)
     m.scale = mt.scalar(14, "d", 1.0)
     multi_bias = mt.vector(16, np.float64)

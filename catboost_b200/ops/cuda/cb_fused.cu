@@ -24,7 +24,7 @@
 namespace cg = cooperative_groups;
 
 struct CbFusedArgs {
-    CbHistArgs h;            // h.out = local partial [slots][S][TB] (nranks > 1) or the slot buffer itself (nranks == 1)
+    CbHistArgs h;            // h.priv = per-block private tiles; h.out is unused by the fused kernel
     CbScoreArgs s;           // s.hsrc[r] = local slot r; s.W = owned width; s.col_base = first owned column
     CbComm c;
     unsigned short* leaf;
@@ -35,7 +35,42 @@ struct CbFusedArgs {
     int Wmax;                        // row stride (floats) of every slot buffer = max owned width
 };
 
-__global__ void __launch_bounds__(512, 2) cb_level_fused_kernel(CbFusedArgs a) {
+// Sum of the per-chunk private tiles of this rank, written to the owner's slot.  One thread = one 16-byte column
+// group of one (slot, statistic) row.
+static __device__ void cb_reduce_chunks(const CbFusedArgs& a, int cta, int ncta) {
+    const CbHistArgs& h = a.h;
+    const int G = h.d.G, S = h.S, B = h.B, TB = h.d.TB;
+    const int nK = cb_hist_chunks(G, ncta, h.d.n);
+    const int nslots = cb_hist_nslots(h);
+    const size_t slot_stride = (size_t)S * 4 * B;
+    const size_t item_stride = (size_t)nslots * slot_stride;
+    const int rows = nslots * S;
+    const int C4 = TB >> 2;
+    const int R = a.c.nranks, me = a.c.rank;
+    const long long total = (long long)rows * C4;
+    const long long gthreads = (long long)ncta * blockDim.x;
+    for (long long u = (long long)cta * blockDim.x + threadIdx.x; u < total; u += gthreads) {
+        const int row = (int)(u / C4);
+        const int col = (int)(u % C4) << 2;
+        const int f = cb_find_feature(h.d.feat_off, h.d.F, col);
+        const int bin = col - h.d.feat_off[f];
+        const int slot = row / S, st = row - slot * S;
+        const float* src = h.priv + ((size_t)slot * S + st) * 4 * B + (size_t)(f & 3) * B + bin;
+        const int g = f >> 2;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < nK; ++k) {
+            const float4 v = *reinterpret_cast<const float4*>(src + ((size_t)k * G + g) * item_stride);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        int r = 0;
+        if (R > 1) { while (r + 1 < R && col >= a.own_col[r + 1]) ++r; }
+        float* dst = (R > 1 ? a.c.peer_slot[r] + (size_t)me * a.c.slot_floats : const_cast<float*>(a.s.hsrc[0]))
+                     + (size_t)row * a.Wmax + (col - a.own_col[r]);
+        *reinterpret_cast<float4*>(dst) = acc;
+    }
+}
+
+__global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) {
     extern __shared__ __align__(16) float cb_sh[];
     cg::grid_group grid = cg::this_grid();
     const int cta = blockIdx.x, ncta = gridDim.x;
@@ -51,31 +86,18 @@ __global__ void __launch_bounds__(512, 2) cb_level_fused_kernel(CbFusedArgs a) {
         grid.sync();
     }
 
-    // (A) local partial histograms
+    // (A) local histograms: every block dumps its shared-memory tile into its private region (no atomics)
     cb_hist_phase(a.h, cb_sh, cta, ncta);
     __threadfence();
     grid.sync();
 
+    // (B) chunk reduction fused with the reduce-scatter: each 16-byte column group is summed over the chunks of
+    // this rank and stored straight into the slot of the rank that owns the column (peer store over NVLink when
+    // that is another GPU; every source keeps its own slot, so the owner later adds them in rank order).
     const int R = a.c.nranks, me = a.c.rank;
+    const unsigned long long hist_epoch = (R > 1) ? a.c.epoch[1] + 1 : 0ull;
+    cb_reduce_chunks(a, cta, ncta);
     if (R > 1) {
-        // (B) push owner slices (including our own, so that every source has the same layout on the owner)
-        const unsigned long long hist_epoch = a.c.epoch[1] + 1;
-        const int rows = cb_hist_nslots(a.h) * a.h.S;
-        const int TB = a.h.d.TB;
-        const long long gtid = (long long)cta * blockDim.x + threadIdx.x;
-        const long long gthreads = (long long)ncta * blockDim.x;
-        for (int r = 0; r < R; ++r) {
-            const int c0 = a.own_col[r], w4 = (a.own_col[r + 1] - c0) >> 2;
-            if (w4 <= 0) continue;
-            float4* dst = reinterpret_cast<float4*>(a.c.peer_slot[r] + (size_t)me * a.c.slot_floats);
-            const int dst_w4 = a.Wmax >> 2;
-            const long long total = (long long)rows * w4;
-            for (long long i = gtid; i < total; i += gthreads) {
-                const int row = (int)(i / w4), cc = (int)(i % w4);
-                const float4 v = *reinterpret_cast<const float4*>(a.h.out + (size_t)row * TB + c0 + cc * 4);
-                dst[(size_t)row * dst_w4 + cc] = v;
-            }
-        }
         __threadfence_system();
         grid.sync();
         if (cta == 0 && threadIdx.x < R) cb_st_release_sys(a.c.peer_slot_flag[threadIdx.x] + me, hist_epoch);
@@ -84,6 +106,9 @@ __global__ void __launch_bounds__(512, 2) cb_level_fused_kernel(CbFusedArgs a) {
             cb_wait_flag(a.c.peer_slot_flag[me] + threadIdx.x, hist_epoch, a.c.timeout_ns, a.c.status,
                          CB_TIMEOUT_HIST_ARRIVE, (int)threadIdx.x);
         __syncthreads();
+    } else {
+        __threadfence();
+        grid.sync();
     }
 
     cb_score_phase(a.s, cta, ncta);
@@ -129,7 +154,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     CbFusedPlan* p = new (std::nothrow) CbFusedPlan();
     if (!p) return nullptr;
     CbFusedArgs& a = p->a;
-    a.h.d = *d; a.h.leaf = leaf; a.h.stats = stats; a.h.S = S; a.h.B = B; a.h.out = partial;
+    a.h.d = *d; a.h.leaf = leaf; a.h.stats = stats; a.h.S = S; a.h.B = B; a.h.out = nullptr; a.h.priv = partial; a.h.statmax = nullptr;
     a.h.slot_table = nullptr; a.h.nslots_table = 0; a.h.level = 0; a.h.small_mask = mask0; a.h.slots_per_pass = 1;
     a.s.d = *d;
     if (comm) a.c = *comm; else { a.c = CbComm(); a.c.nranks = 1; a.c.rank = 0; }
@@ -175,31 +200,37 @@ CB_API void cb_fused_set_features(CbFusedPlan* p, int f_begin, int f_end) {
 CB_API void cb_fused_destroy(CbFusedPlan* p) { delete p; }
 
 // Launch geometry of one level: returns the cooperative grid size (0 on error) and the slots per pass.
-CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int* smem_bytes) {
+CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int* smem_bytes, int* threads) {
     const int nslots = level == 0 ? 1 : (1 << (level - 1));
-    const int per_slot = p->a.h.S * 4 * p->a.h.B * 4;
+    const int per_slot = p->a.h.S * 4 * p->a.h.B * 4 * (p->a.h.statmax ? 2 : 1);
     int spp = nslots;
     const int budget = p->max_smem;
     if (spp * per_slot > budget) spp = budget / per_slot;
     if (spp < 1) return 0;
     const int smem = spp * per_slot;
+    // one big block per SM when the tile needs more than half of the shared memory, else several 512-thread blocks
+    int thr = (smem > budget / 2) ? 1024 : p->threads;
     int occ = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, cb_level_fused_kernel, p->threads, smem) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, cb_level_fused_kernel, thr, smem) != cudaSuccess) { cudaGetLastError(); return 0; }
     if (occ < 1) return 0;
     if (occ > 4) occ = 4;
     *slots_per_pass = spp;
     *smem_bytes = smem;
+    *threads = thr;
     return occ * p->sm_count;
 }
 
+CB_API void cb_fused_set_priv(CbFusedPlan* p, float* priv, const float* statmax) { p->a.h.priv = priv; p->a.h.statmax = statmax; }
+
 CB_API int cb_fused_launch(CbFusedPlan* p, int level, float* hprev, float* hcur, const unsigned int* mask_in,
-                           unsigned int* mask_out, int grid, int slots_per_pass, int smem_bytes, cudaStream_t st) {
+                           unsigned int* mask_out, int grid, int slots_per_pass, int smem_bytes, int threads,
+                           cudaStream_t st) {
     CbFusedArgs a = p->a;
     a.h.level = level; a.h.small_mask = mask_in; a.h.slots_per_pass = slots_per_pass;
     a.s.level = level; a.s.small_mask = mask_in; a.s.hprev = hprev; a.s.hcur = hcur;
     a.mask_out = mask_out;
     void* args[] = {&a};
-    cudaError_t e = cudaLaunchCooperativeKernel((void*)cb_level_fused_kernel, dim3(grid), dim3(p->threads), args,
+    cudaError_t e = cudaLaunchCooperativeKernel((void*)cb_level_fused_kernel, dim3(grid), dim3(threads), args,
                                                 (size_t)smem_bytes, st);
     return (int)e;
 }

@@ -96,6 +96,7 @@ struct CbGradArgs {
     unsigned long long seed; const int* iter_ptr;
     double* scal;
     const float* ext_der; const float* ext_hess;   // CB_LOSS_EXTERNAL
+    float* statmax;          // [2] running max |stat| of this iteration (float bits are ordered for x >= 0)
 };
 
 __device__ __forceinline__ float cb_bootstrap_weight(int type, float p, unsigned long long h) {
@@ -120,6 +121,7 @@ __device__ __forceinline__ float cb_bootstrap_weight(int type, float p, unsigned
 __global__ void __launch_bounds__(256) cb_grad_kernel(CbGradArgs a) {
     const int it = *a.iter_ptr;
     double s_loss = 0.0, s_w = 0.0, s_d2 = 0.0, s_n = 0.0;
+    float m0 = 0.0f, m1 = 0.0f;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
         float ap = a.approx[i];
@@ -136,8 +138,11 @@ __global__ void __launch_bounds__(256) cb_grad_kernel(CbGradArgs a) {
                                                              cb_mix64(a.seed ^ cb_mix64(((unsigned long long)it << 40) ^ (unsigned long long)i)))
                                      : 1.0f;
         const float wd = w * o.der;
-        a.stats[i] = wb * wd;
-        a.stats[a.npad + i] = wb * w * (a.newton_stats ? o.hess : 1.0f);
+        const float st0 = wb * wd, st1 = wb * w * (a.newton_stats ? o.hess : 1.0f);
+        a.stats[i] = st0;
+        a.stats[a.npad + i] = st1;
+        m0 = fmaxf(m0, fabsf(st0));
+        m1 = fmaxf(m1, fabsf(st1));
         s_loss += (double)(w * o.value);
         s_w += (double)w;
         s_d2 += (double)(wd * wd);
@@ -153,15 +158,26 @@ __global__ void __launch_bounds__(256) cb_grad_kernel(CbGradArgs a) {
         for (int k = 0; k < (blockDim.x >> 5); ++k) t += red[threadIdx.x][k];
         atomicAdd(a.scal + threadIdx.x, t);
     }
+    if (a.statmax) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
+            m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
+        }
+        if (lane == 0) {
+            atomicMax(reinterpret_cast<int*>(a.statmax), __float_as_int(m0));
+            atomicMax(reinterpret_cast<int*>(a.statmax) + 1, __float_as_int(m1));
+        }
+    }
 }
 
 CB_API int cb_grad_pointwise(int loss, float p0, float p1, float* approx, const float* target, const float* weight,
                              unsigned short* leaf, const float* cur_vals, long long n, long long npad, float* stats,
                              int newton_stats, int boot_type, float boot_p, unsigned long long seed,
                              const int* iter_ptr, double* scal, const float* ext_der, const float* ext_hess,
-                             int grid, cudaStream_t st) {
+                             float* statmax, int grid, cudaStream_t st) {
     CbGradArgs a{loss, p0, p1, approx, target, weight, leaf, cur_vals, n, npad, stats, newton_stats,
-                 boot_type, boot_p, seed, iter_ptr, scal, ext_der, ext_hess};
+                 boot_type, boot_p, seed, iter_ptr, scal, ext_der, ext_hess, statmax};
     cb_grad_kernel<<<grid, 256, 0, st>>>(a);
     CB_LAUNCH_CHECK();
     return 0;
@@ -254,6 +270,7 @@ CB_API int cb_hist(const CbData* d, const unsigned short* leaf, const float* sta
     CbHistArgs a;
     a.d = *d; a.leaf = leaf; a.stats = stats; a.S = S; a.level = level; a.small_mask = small_mask;
     a.slots_per_pass = slots_per_pass; a.B = B; a.out = out; a.slot_table = slot_table; a.nslots_table = nslots_table;
+    a.priv = nullptr; a.statmax = nullptr;
     const int smem = cb_hist_smem_bytes(slots_per_pass, S, B);
     if (!g_hist_smem_set) {
         int dev = 0, optin = 0;
@@ -372,42 +389,75 @@ struct CbLeafArgs {
     float l2, lr;
     float* cur_vals;         // [L] lr * delta after the last pass (applied by the next derivative kernel)
     float* model_vals; float* model_wts; int Lstride; const int* iter_ptr;
+    float* leaf_w;           // [L] per-leaf weight sums, written by the first pass of a tree
     CbComm c;
 };
 
-__global__ void __launch_bounds__(256) cb_leaf_pass_kernel(CbLeafArgs a) {
-    extern __shared__ float sl[];     // [3][L] when L fits, else unused
+// Shared-memory accumulators are replicated per lane group: cell (leaf, stat) has `C` copies and lane `l` uses copy
+// l & (C-1), so the lanes of a warp never collide on an address (shared fp32 atomics are compare-and-swap loops;
+// without collisions every one succeeds on its first try).  C = 32 for up to 128 leaves.
+__global__ void __launch_bounds__(512) cb_leaf_pass_kernel(CbLeafArgs a, int C) {
+    extern __shared__ float sl[];     // [L][3][C] when it fits, else unused
     const int L = a.L;
-    const bool use_sh = L <= 4096;
+    const bool use_sh = C > 0;
+    const int cm = C - 1;
+    const int lane_copy = threadIdx.x & cm;
     if (use_sh) {
-        for (int i = threadIdx.x; i < 3 * L; i += blockDim.x) sl[i] = 0.0f;
+        for (int i = threadIdx.x; i < 3 * L * C; i += blockDim.x) sl[i] = 0.0f;
         __syncthreads();
     }
+    const long long n4 = (a.n + 3) >> 2;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
-        const int l = a.leaf[i];
-        const float w = a.weight ? a.weight[i] : 1.0f;
-        CbLossOut o;
-        if (a.loss == CB_LOSS_EXTERNAL) { o.der = a.ext_der[i]; o.hess = a.ext_hess ? a.ext_hess[i] : 1.0f; }
-        else {
-            const float ap = a.approx[i] + (a.first ? 0.0f : a.delta[l]);
-            o = cb_loss_eval(a.loss, a.p0, a.p1, ap, a.target[i]);
-        }
-        if (use_sh) {
-            atomicAdd(&sl[l], w * o.der);
-            atomicAdd(&sl[L + l], w * o.hess);
-            atomicAdd(&sl[2 * L + l], w);
+    for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n4; q += stride) {
+        const long long i0 = q << 2;
+        const ushort4 lf4 = *reinterpret_cast<const ushort4*>(a.leaf + i0);
+        const unsigned int lf[4] = {lf4.x, lf4.y, lf4.z, lf4.w};
+        float ap[4] = {0.f, 0.f, 0.f, 0.f}, tg[4] = {0.f, 0.f, 0.f, 0.f}, wt[4] = {1.f, 1.f, 1.f, 1.f};
+        float ed[4], eh[4];
+        if (a.loss == CB_LOSS_EXTERNAL) {
+            const float4 d4 = *reinterpret_cast<const float4*>(a.ext_der + i0);
+            ed[0] = d4.x; ed[1] = d4.y; ed[2] = d4.z; ed[3] = d4.w;
+            eh[0] = eh[1] = eh[2] = eh[3] = 1.0f;
+            if (a.ext_hess) {
+                const float4 h4 = *reinterpret_cast<const float4*>(a.ext_hess + i0);
+                eh[0] = h4.x; eh[1] = h4.y; eh[2] = h4.z; eh[3] = h4.w;
+            }
         } else {
-            atomicAdd(&a.sums[3 * l], (double)(w * o.der));
-            atomicAdd(&a.sums[3 * l + 1], (double)(w * o.hess));
-            atomicAdd(&a.sums[3 * l + 2], (double)w);
+            const float4 a4 = *reinterpret_cast<const float4*>(a.approx + i0);
+            const float4 t4 = *reinterpret_cast<const float4*>(a.target + i0);
+            ap[0] = a4.x; ap[1] = a4.y; ap[2] = a4.z; ap[3] = a4.w;
+            tg[0] = t4.x; tg[1] = t4.y; tg[2] = t4.z; tg[3] = t4.w;
+        }
+        if (a.weight) {
+            const float4 w4 = *reinterpret_cast<const float4*>(a.weight + i0);
+            wt[0] = w4.x; wt[1] = w4.y; wt[2] = w4.z; wt[3] = w4.w;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (i0 + k >= a.n) break;
+            const int l = (int)lf[k];
+            CbLossOut o;
+            if (a.loss == CB_LOSS_EXTERNAL) { o.der = ed[k]; o.hess = eh[k]; }
+            else o = cb_loss_eval(a.loss, a.p0, a.p1, ap[k] + (a.first ? 0.0f : a.delta[l]), tg[k]);
+            const float w = wt[k];
+            if (use_sh) {
+                float* cell = sl + (size_t)(l * 3) * C + lane_copy;
+                atomicAdd(cell, w * o.der);
+                atomicAdd(cell + C, w * o.hess);
+                if (a.first) atomicAdd(cell + 2 * C, w);
+            } else {
+                atomicAdd(&a.sums[3 * l], (double)(w * o.der));
+                atomicAdd(&a.sums[3 * l + 1], (double)(w * o.hess));
+                if (a.first) atomicAdd(&a.sums[3 * l + 2], (double)w);
+            }
         }
     }
     if (use_sh) {
         __syncthreads();
         for (int i = threadIdx.x; i < 3 * L; i += blockDim.x) {
-            const float v = sl[i];
-            if (v != 0.0f) atomicAdd(&a.sums[3 * (i % L) + i / L], (double)v);
+            float v = 0.0f;
+            for (int c = 0; c < C; ++c) v += sl[(size_t)i * C + c];
+            if (v != 0.0f) atomicAdd(&a.sums[i], (double)v);
         }
     }
     __shared__ bool s_last;
@@ -424,7 +474,9 @@ __global__ void __launch_bounds__(256) cb_leaf_pass_kernel(CbLeafArgs a) {
     }
     const int it = *a.iter_ptr;
     for (int l = threadIdx.x; l < L; l += blockDim.x) {
-        const double sd = a.sums[3 * l], shs = a.sums[3 * l + 1], sw = a.sums[3 * l + 2];
+        const double sd = __ldcg(&a.sums[3 * l]), shs = __ldcg(&a.sums[3 * l + 1]);
+        if (a.first) a.leaf_w[l] = (float)__ldcg(&a.sums[3 * l + 2]);
+        const double sw = (double)a.leaf_w[l];
         const double den = (a.newton ? shs : sw) + (double)a.l2;
         const float step = (den > 0.0) ? (float)(sd / den) : 0.0f;
         const float v = (a.first ? 0.0f : a.delta[l]) + step;
@@ -443,12 +495,20 @@ CB_API int cb_leaf_pass(int loss, float p0, float p1, const float* approx, const
                         const unsigned short* leaf, const float* ext_der, const float* ext_hess, long long n, int L,
                         float* delta, double* sums, unsigned int* counter, int first, int last, int newton, float l2,
                         float lr, float* cur_vals, float* model_vals, float* model_wts, int Lstride,
-                        const int* iter_ptr, const CbComm* comm, int grid, cudaStream_t st) {
+                        const int* iter_ptr, float* leaf_w, const CbComm* comm, int grid, cudaStream_t st) {
     CbLeafArgs a{loss, p0, p1, approx, target, weight, leaf, ext_der, ext_hess, n, L, delta, sums, counter,
-                 first, last, newton, l2, lr, cur_vals, model_vals, model_wts, Lstride, iter_ptr, CbComm()};
+                 first, last, newton, l2, lr, cur_vals, model_vals, model_wts, Lstride, iter_ptr, leaf_w, CbComm()};
     if (comm) a.c = *comm; else { a.c.nranks = 1; a.c.rank = 0; }
-    const int smem = (L <= 4096) ? 3 * L * 4 : 0;
-    cb_leaf_pass_kernel<<<grid, 256, smem, st>>>(a);
+    int C = 32;
+    while (C > 0 && (size_t)3 * L * C * 4 > 96 * 1024) C >>= 1;
+    const int smem = 3 * L * C * 4;
+    static int set = 0;
+    if (!set) {
+        cudaError_t e = cudaFuncSetAttribute(cb_leaf_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+        set = 1;
+    }
+    cb_leaf_pass_kernel<<<grid, 512, smem, st>>>(a, C);
     CB_LAUNCH_CHECK();
     return 0;
 }
@@ -457,16 +517,17 @@ CB_API int cb_leaf_pass(int loss, float p0, float p1, const float* approx, const
 // End of a boosting iteration: record the learn loss and the per-iteration extras (evaluation-set metric
 // sums), clear the accumulators, advance the counter.
 __global__ void cb_iter_end_kernel(int* iter_ptr, double* scal, double* loss_hist, double* extra_src, double* extra_dst,
-                                   int n_extra) {
+                                   int n_extra, float* statmax) {
     const int it = *iter_ptr;
+    if (statmax) { statmax[0] = 0.0f; statmax[1] = 0.0f; }
     if (loss_hist) { loss_hist[2 * it] = scal[0]; loss_hist[2 * it + 1] = scal[1]; }
     scal[0] = scal[1] = scal[2] = scal[3] = 0.0;
     for (int k = 0; k < n_extra; ++k) { extra_dst[(long long)it * n_extra + k] = extra_src[k]; extra_src[k] = 0.0; }
     *iter_ptr = it + 1;
 }
 CB_API int cb_iter_end(int* iter_ptr, double* scal, double* loss_hist, double* extra_src, double* extra_dst, int n_extra,
-                       cudaStream_t st) {
-    cb_iter_end_kernel<<<1, 1, 0, st>>>(iter_ptr, scal, loss_hist, extra_src, extra_dst, n_extra);
+                       float* statmax, cudaStream_t st) {
+    cb_iter_end_kernel<<<1, 1, 0, st>>>(iter_ptr, scal, loss_hist, extra_src, extra_dst, n_extra, statmax);
     CB_LAUNCH_CHECK();
     return 0;
 }

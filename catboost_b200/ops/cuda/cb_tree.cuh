@@ -47,6 +47,16 @@ struct CbHistArgs {
     // document is accumulated into (-1 = skip).  When slot_table is set, level/small_mask are ignored.
     const short* slot_table;
     int nslots_table;
+    // When `priv` is set the block does not add into `out`: it dumps its shared-memory tile, as is, into its own
+    // region priv[item][slot][s][j][B] (item = chunk * G + group) with plain coalesced stores; a later phase sums
+    // the chunks (cb_reduce_chunks).  No global atomics, no zero-fill of `out`, and a deterministic result.
+    float* priv;
+    // Fixed-point accumulation (needs `priv`): statmax[s] = max |stats[s][i]| of this iteration.  A value is scaled
+    // to 24 signed bits and split into a signed high part (q >> 12) and an unsigned low part (q & 4095), each added
+    // with a native 32-bit integer shared-memory atomic; fp32 shared atomics are compare-and-swap loops and were
+    // measured 2x slower for twice fewer operations.  The sum is exact in integers (better than fp32 accumulation)
+    // as long as a block sees at most 2^19 documents per tile, which cb_hist_chunks guarantees.
+    const float* statmax;
 };
 
 __device__ __forceinline__ int cb_hist_nslots(const CbHistArgs& a) {
@@ -83,8 +93,8 @@ __device__ __forceinline__ void cb_update_leaf_range(const CbData& d, unsigned s
 // ------------------------------------------------------------------------------------------------------
 // Histogram accumulation of one (feature group, document chunk, slot pass) into shared memory + flush.
 // sh layout: [slot][s][j][B]; S is a run-time value (2 for pointwise losses, K+1 for K-class losses).
-static __device__ void cb_hist_item(const CbHistArgs& a, float* sh, int g, long long d_begin, long long d_end,
-                             int slot_begin, int slot_count) {
+static __device__ void cb_hist_item(const CbHistArgs& a, float* sh, int g, long long item, long long d_begin,
+                             long long d_end, int slot_begin, int slot_count) {
     const int B = a.B;
     const int S = a.S;
     const int total = slot_count * S * 4 * B;
@@ -133,6 +143,13 @@ static __device__ void cb_hist_item(const CbHistArgs& a, float* sh, int g, long 
         }
     }
     __syncthreads();
+    if (a.priv) {
+        float4* dst = reinterpret_cast<float4*>(a.priv + ((size_t)item * nslots + slot_begin) * slot_stride);
+        const float4* src = reinterpret_cast<const float4*>(sh);
+        for (int i = threadIdx.x; i < (total >> 2); i += blockDim.x) dst[i] = src[i];
+        __syncthreads();
+        return;
+    }
     // flush (skip zeros: most (slot, bin) cells of a chunk are empty at deep levels)
     for (int i = threadIdx.x; i < total; i += blockDim.x) {
         const float v = sh[i];
@@ -151,10 +168,98 @@ static __device__ void cb_hist_item(const CbHistArgs& a, float* sh, int g, long 
     __syncthreads();
 }
 
+// Fixed-point variant of cb_hist_item (see CbHistArgs::statmax).  sh layout: int [slot][s][part][j][B], part 0 = high.
+static __device__ void cb_hist_item_q(const CbHistArgs& a, int* sh, int g, long long item, long long d_begin,
+                                      long long d_end, int slot_begin, int slot_count) {
+    const int B = a.B;
+    const int S = a.S;
+    const int total = slot_count * S * 8 * B;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) sh[i] = 0;
+    __syncthreads();
+
+    const uint32_t* bg = a.d.bins + (long long)g * a.d.npad;
+    const int level = a.level;
+    const int nslots = cb_hist_nslots(a);
+    const unsigned int pmask = (unsigned int)(nslots - 1);
+    const int slot_stride = S * 8 * B;
+    for (long long i = d_begin + (long long)threadIdx.x * 4; i < d_end; i += (long long)blockDim.x * 4) {
+        const uint4 w = *reinterpret_cast<const uint4*>(bg + i);
+        const ushort4 lf = *reinterpret_cast<const ushort4*>(a.leaf + i);
+        const unsigned int wv[4] = {w.x, w.y, w.z, w.w};
+        const unsigned int lv[4] = {lf.x, lf.y, lf.z, lf.w};
+        int off[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            int slot = 0;
+            bool take = (i + k) < a.d.n;
+            if (a.slot_table) {
+                slot = a.slot_table[lv[k]];
+                take = take && (slot >= 0);
+            } else if (level > 0) {
+                const unsigned int p = lv[k] & pmask;
+                const unsigned int right = (lv[k] >> (level - 1)) & 1u;
+                const unsigned int want = (a.small_mask[p >> 5] >> (p & 31)) & 1u;
+                take = take && (right == want);
+                slot = (int)p;
+            }
+            slot -= slot_begin;
+            off[k] = (take && (unsigned)slot < (unsigned)slot_count) ? slot * slot_stride : -1;
+        }
+        for (int s = 0; s < S; ++s) {
+            const float sc = 8388607.0f / fmaxf(a.statmax[s], 1e-30f);
+            const float4 t = *reinterpret_cast<const float4*>(a.stats + (long long)s * a.d.npad + i);
+            const float tv[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (off[k] >= 0) {
+                    const int q = __float2int_rn(tv[k] * sc);
+                    const int hi = q >> 12;
+                    const unsigned int lo = (unsigned int)q & 4095u;
+                    int* base = sh + off[k] + s * 8 * B;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const unsigned int bin = (wv[k] >> (8 * j)) & 255u;
+                        atomicAdd(base + j * B + bin, hi);
+                        atomicAdd(reinterpret_cast<unsigned int*>(base) + (4 + j) * B + bin, lo);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // dump as floats into the private region [item][slot][s][j][B]
+    const int cells4 = (slot_count * S * 4 * B) >> 2;
+    float4* dst = reinterpret_cast<float4*>(a.priv + ((size_t)item * nslots + slot_begin) * (size_t)(S * 4 * B));
+    const int B4 = B >> 2;
+    for (int c = threadIdx.x; c < cells4; c += blockDim.x) {
+        const int b4 = c % B4;
+        const int r = c / B4;            // (slot * S + s) * 4 + j
+        const int j = r & 3;
+        const int ss = r >> 2;           // slot * S + s
+        const float inv = fmaxf(a.statmax[ss % S], 1e-30f) * (1.0f / 8388607.0f);
+        const int4 hi = *reinterpret_cast<const int4*>(sh + (size_t)ss * 8 * B + j * B + b4 * 4);
+        const uint4 lo = *reinterpret_cast<const uint4*>(sh + (size_t)ss * 8 * B + (4 + j) * B + b4 * 4);
+        float4 v;
+        v.x = fmaf((float)hi.x, 4096.0f * inv, (float)lo.x * inv);
+        v.y = fmaf((float)hi.y, 4096.0f * inv, (float)lo.y * inv);
+        v.z = fmaf((float)hi.z, 4096.0f * inv, (float)lo.z * inv);
+        v.w = fmaf((float)hi.w, 4096.0f * inv, (float)lo.w * inv);
+        dst[c] = v;
+    }
+    __syncthreads();
+}
+
+#define CB_HIST_MAX_DOCS_PER_TILE (1 << 19)
+__device__ __forceinline__ int cb_hist_chunks(int G, int ncta, long long n) {
+    const int by_grid = (ncta >= G) ? (ncta / G) : 1;
+    const int by_docs = (int)((n + CB_HIST_MAX_DOCS_PER_TILE - 1) / CB_HIST_MAX_DOCS_PER_TILE);
+    return by_grid > by_docs ? by_grid : by_docs;
+}
+
 // Static work split used by both launch styles: item -> (group, chunk).
 static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, int ncta) {
     const int G = a.d.G;
-    const int nK = (ncta >= G) ? (ncta / G) : 1;
+    const int nK = cb_hist_chunks(G, ncta, a.d.n);
     long long per = (a.d.n + nK - 1) / nK;
     per = (per + 3) & ~3ll;
     const int nslots = cb_hist_nslots(a);
@@ -166,7 +271,8 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
             const long long k = item / G;
             const long long b = k * per;
             const long long e = min(a.d.n, b + per);
-            if (b < e) cb_hist_item(a, sh, g, b, e, sb, sc);
+            if (a.statmax) cb_hist_item_q(a, reinterpret_cast<int*>(sh), g, item, min(b, e), e, sb, sc);
+            else if (b < e || a.priv) cb_hist_item(a, sh, g, item, min(b, e), e, sb, sc);
         }
     }
 }

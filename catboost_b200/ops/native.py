@@ -115,7 +115,7 @@ _SIGS = {
     "cb_pack_bins": (c_int, [c_void_p, c_ll, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_void_p]),
     "cb_grad_pointwise": (c_int, [c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll,
                                   c_void_p, c_int, c_int, c_float, c_ull, c_void_p, c_void_p, c_void_p, c_void_p,
-                                  c_int, c_void_p]),
+                                  c_void_p, c_int, c_void_p]),
     "cb_data_create": (c_void_p, [c_void_p, c_ll, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int]),
     "cb_data_destroy": (None, [c_void_p]),
     "cb_comm_create": (c_void_p, [c_int, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -135,8 +135,8 @@ _SIGS = {
     "cb_allreduce_sum": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
     "cb_leaf_pass": (c_int, [c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll,
                              c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p,
-                             c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
-    "cb_iter_end": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+                             c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "cb_iter_end": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "cb_apply_tree_bins": (c_int, [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                                    c_void_p]),
     "cb_leaf_index": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
@@ -150,9 +150,10 @@ _SIGS = {
                                    c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int,
                                    c_float, c_void_p, c_void_p, c_ull, c_float, c_void_p, c_void_p, c_int]),
     "cb_fused_set_features": (None, [c_void_p, c_int, c_int]),
+    "cb_fused_set_priv": (None, [c_void_p, c_void_p, c_void_p]),
     "cb_fused_destroy": (None, [c_void_p]),
-    "cb_fused_geometry": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
-    "cb_fused_launch": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+    "cb_fused_geometry": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "cb_fused_launch": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_void_p]),
 }
 

@@ -54,7 +54,7 @@ class GpuObliviousEngine:
                  leaf_iterations: int = 1, seed: int = 0, ctx: Optional[DistContext] = None, reduce: str = "fused",
                  eval_sets: Optional[List[EvalSet]] = None, use_graph: bool = True, threads: int = 512,
                  ext_der: Optional[torch.Tensor] = None, ext_hess: Optional[torch.Tensor] = None,
-                 timeout_s: float = 20.0):
+                 timeout_s: float = 20.0, quantized_hist: bool = True):
         assert store.bins.is_cuda, "GpuObliviousEngine needs a CUDA store"
         if depth > 16:
             raise ValueError("depth must be <= 16")
@@ -78,6 +78,7 @@ class GpuObliviousEngine:
         self.score_seed = (int(seed) * 0xD1B54A32D192ED03 + 77) & 0xFFFFFFFFFFFFFFFF
         self.reduce = reduce if self.R > 1 else "fused"
         self.use_graph = use_graph
+        self.quantized_hist = bool(quantized_hist)
         self.threads = threads
         self.eval_sets = eval_sets or []
         self.ext_der, self.ext_hess = ext_der, ext_hess
@@ -106,10 +107,12 @@ class GpuObliviousEngine:
         self.model_wts = torch.zeros((cap, self.L), dtype=f32, device=dev)
         self.cur_vals = torch.zeros(self.L, dtype=f32, device=dev)
         self.delta = torch.zeros(self.L, dtype=f32, device=dev)
+        self.leaf_w = torch.zeros(self.L, dtype=f32, device=dev)
         self.sums = torch.zeros(self.L * 3, dtype=f64, device=dev)
         self.counter = torch.zeros(1, dtype=i32, device=dev)
         self.best_key = torch.zeros(1, dtype=i64, device=dev)
         self.cur_loss = torch.zeros(2, dtype=f64, device=dev)
+        self.statmax = torch.zeros(2, dtype=f32, device=dev)
         msg_bytes = self.lib.cb_select_msg_bytes()
         self.msg_local = torch.zeros((max(self.R, 1), msg_bytes // 8 + 1), dtype=i64, device=dev)
         self.msg_all = torch.zeros((max(self.R, 1), msg_bytes // 8 + 1), dtype=i64, device=dev)
@@ -142,7 +145,8 @@ class GpuObliviousEngine:
                       if self.reduce == "fused" else None)
         if self.reduce == "fused":
             self.slots = self.arena.local_slots_tensor()
-            self.partial = (torch.zeros((slots_max * self.S, TB), dtype=f32, device=dev) if self.R > 1 else None)
+            self.partial = None
+            self.priv = None
             self._make_plan()
         else:
             self.partial = torch.zeros((slots_max * self.S, TB), dtype=f32, device=dev)
@@ -164,7 +168,7 @@ class GpuObliviousEngine:
         arr = ctypes.c_void_p * R
         local_slots = arr(*[self.arena.local_slot_ptr(r) for r in range(R)])
         own = (ctypes.c_int * (R + 1))(*self.col_bounds)
-        partial_ptr = _p(self.partial) if R > 1 else ctypes.c_void_p(self.arena.local_slot_ptr(0))
+        partial_ptr = None
         self.plan = self.lib.cb_fused_create(
             ctypes.c_void_p(self.store.handle), ctypes.c_void_p(self.arena.handle), _p(self.leaf), _p(self.stats),
             self.S, self.B, partial_ptr, local_slots, _p(self.hbuf[0]), _p(self.hbuf[1]), own, self.Wmax,
@@ -175,13 +179,27 @@ class GpuObliviousEngine:
             raise RuntimeError("cb_fused_create failed")
         self.lib.cb_fused_set_features(ctypes.c_void_p(self.plan), self.feat_bounds[self.rank],
                                        self.feat_bounds[self.rank + 1])
+        # fixed-point accumulation is on: statmax must be known to the geometry (it doubles the tile size)
+        self.lib.cb_fused_set_priv(ctypes.c_void_p(self.plan), None, _p(self.statmax) if self.quantized_hist else None)
         self.level_geo = []
         for level in range(self.depth):
-            spp, smem = ctypes.c_int(0), ctypes.c_int(0)
-            grid = self.lib.cb_fused_geometry(ctypes.c_void_p(self.plan), level, ctypes.byref(spp), ctypes.byref(smem))
+            spp, smem, thr = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+            grid = self.lib.cb_fused_geometry(ctypes.c_void_p(self.plan), level, ctypes.byref(spp), ctypes.byref(smem),
+                                              ctypes.byref(thr))
             if grid <= 0:
                 raise RuntimeError(f"no cooperative launch geometry for level {level}")
-            self.level_geo.append((grid, spp.value, smem.value))
+            self.level_geo.append((grid, spp.value, smem.value, thr.value))
+        # private tiles: one region per (chunk, group) work item, sized for the largest level
+        G = self.store.G
+        need = 0
+        by_docs = (self.n + (1 << 19) - 1) >> 19
+        for level, (grid, _, _, _) in enumerate(self.level_geo):
+            nslots = 1 if level == 0 else 1 << (level - 1)
+            items = G * max(grid // G if grid >= G else 1, by_docs)
+            need = max(need, items * nslots * self.S * 4 * self.B)
+        self.priv = torch.empty(need, dtype=torch.float32, device=self.dev)
+        self.lib.cb_fused_set_priv(ctypes.c_void_p(self.plan), _p(self.priv),
+                                   _p(self.statmax) if self.quantized_hist else None)
 
     def _stream(self):
         return ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
@@ -192,24 +210,18 @@ class GpuObliviousEngine:
         chk(self.lib.cb_grad_pointwise(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target), _p(self.weight),
                                        _p(self.leaf), _p(self.cur_vals), self.n, self.npad, _p(self.stats),
                                        self.newton_stats, self.boot_type, self.boot_p, self.seed, _p(self.iter_ptr),
-                                       _p(self.scal), _p(self.ext_der), _p(self.ext_hess), self.grid_stream,
-                                       self._stream()), "cb_grad_pointwise")
+                                       _p(self.scal), _p(self.ext_der), _p(self.ext_hess), _p(self.statmax),
+                                       self.grid_stream, self._stream()), "cb_grad_pointwise")
         self.launches_per_iter += 1
 
     def _level_fused(self, level: int):
-        grid, spp, smem = self.level_geo[level]
-        nslots = 1 if level == 0 else 1 << (level - 1)
-        rows = nslots * self.S
-        if self.R > 1:
-            self.partial[:rows].zero_()
-        else:
-            self.slots[: rows * self.Wmax].zero_()
+        grid, spp, smem, thr = self.level_geo[level]
         hprev, hcur = self.hbuf[(level + 1) & 1], self.hbuf[level & 1]
         hcur_ptr = _p(hcur) if level < self.depth - 1 else None
         native.cuda_check(self.lib.cb_fused_launch(ctypes.c_void_p(self.plan), level, _p(hprev), hcur_ptr,
                                                    _p(self.mask[level & 1]), _p(self.mask[(level + 1) & 1]), grid, spp,
-                                                   smem, self._stream()), "cb_level_fused")
-        self.launches_per_iter += 2
+                                                   smem, thr, self._stream()), "cb_level_fused")
+        self.launches_per_iter += 1
 
     def _level_unfused(self, level: int):
         chk, lib, st = native.cuda_check, self.lib, self.store
@@ -259,7 +271,8 @@ class GpuObliviousEngine:
                                  _p(self.leaf), _p(self.ext_der), _p(self.ext_hess), self.n, self.L, _p(self.delta),
                                  _p(self.sums), _p(self.counter), 1 if it == 0 else 0, last, self.leaf_newton, self.l2,
                                  self.lr, _p(self.cur_vals), _p(self.model_vals), _p(self.model_wts), self.L,
-                                 _p(self.iter_ptr), comm, self.grid_stream, self._stream()), "cb_leaf_pass")
+                                 _p(self.iter_ptr), _p(self.leaf_w), comm, self.sm_count * 2, self._stream()),
+                "cb_leaf_pass")
             self.launches_per_iter += 1
 
     def _leaf_pass_nccl(self, it):
@@ -309,7 +322,8 @@ class GpuObliviousEngine:
         self._evals()
         n_extra = 2 * len(self.eval_sets)
         native.cuda_check(self.lib.cb_iter_end(_p(self.iter_ptr), _p(self.scal), _p(self.loss_hist), _p(self.eval_scal),
-                                               _p(self.eval_hist), n_extra, self._stream()), "cb_iter_end")
+                                               _p(self.eval_hist), n_extra, _p(self.statmax), self._stream()),
+                          "cb_iter_end")
         self.launches_per_iter += 1
 
     # ------------------------------------------------------------------------------------------------------
