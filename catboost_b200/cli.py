@@ -1,0 +1,374 @@
+"""Command-line interface: ``python -m catboost_b200 <mode> ...`` with the reference's mode names
+(catboost/app/main.cpp:21-35): fit, calc, fstr, eval-metrics, metadata, model-sum, normalize-model, select-features,
+dataset-statistics, dump-options, roc.  Option names follow catboost/private/libs/app_helpers/bind_options.cpp."""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import numpy as np
+
+
+def _add_pool_args(ap, prefix=""):
+    ap.add_argument("-f", "--learn-set", dest="learn_set")
+    ap.add_argument("-t", "--test-set", dest="test_set", action="append", default=[])
+    ap.add_argument("--column-description", "--cd", dest="cd")
+    ap.add_argument("--delimiter", default="\t")
+    ap.add_argument("--has-header", action="store_true")
+    ap.add_argument("--learn-pairs")
+    ap.add_argument("--test-pairs")
+
+
+def _pool(path, args, pairs=None):
+    from .data.pool import Pool
+    return Pool(path, column_description=args.cd, delimiter=args.delimiter, has_header=args.has_header, pairs=pairs)
+
+
+_FIT_PARAMS = [("--loss-function", str, "loss_function"), ("-i", int, "iterations"), ("--iterations", int, "iterations"),
+               ("-w", float, "learning_rate"), ("--learning-rate", float, "learning_rate"), ("-n", int, "depth"),
+               ("--depth", int, "depth"), ("--l2-leaf-reg", float, "l2_leaf_reg"), ("-x", int, "border_count"),
+               ("--border-count", int, "border_count"), ("--feature-border-type", str, "feature_border_type"),
+               ("-r", int, "random_seed"), ("--random-seed", int, "random_seed"), ("--task-type", str, "task_type"),
+               ("--devices", str, "devices"), ("--grow-policy", str, "grow_policy"), ("--max-leaves", int, "max_leaves"),
+               ("--min-data-in-leaf", int, "min_data_in_leaf"), ("--bootstrap-type", str, "bootstrap_type"),
+               ("--bagging-temperature", float, "bagging_temperature"), ("--subsample", float, "subsample"),
+               ("--random-strength", float, "random_strength"), ("--rsm", float, "rsm"),
+               ("--leaf-estimation-method", str, "leaf_estimation_method"),
+               ("--leaf-estimation-iterations", int, "leaf_estimation_iterations"), ("--score-function", str, "score_function"),
+               ("--eval-metric", str, "eval_metric"), ("--custom-metric", str, "custom_metric"),
+               ("--one-hot-max-size", int, "one_hot_max_size"), ("--max-ctr-complexity", int, "max_ctr_complexity"),
+               ("--od-type", str, "od_type"), ("--od-wait", int, "od_wait"), ("--od-pval", float, "od_pval"),
+               ("--metric-period", int, "metric_period"), ("--train-dir", str, "train_dir"),
+               ("--snapshot-file", str, "snapshot_file"), ("--snapshot-interval", float, "snapshot_interval"),
+               ("-T", int, "thread_count"), ("--thread-count", int, "thread_count"), ("--nan-mode", str, "nan_mode"),
+               ("--boosting-type", str, "boosting_type"), ("--boost-from-average", str, "boost_from_average"),
+               ("--class-weights", str, "class_weights"), ("--auto-class-weights", str, "auto_class_weights"),
+               ("--target-border", float, "target_border"), ("--simple-ctr", str, "simple_ctr"),
+               ("--combinations-ctr", str, "combinations_ctr"), ("--ignore-features", str, "ignored_features"),
+               ("--permutations", int, "permutation_count"), ("--logging-level", str, "logging_level")]
+
+
+def _fit_params(args):
+    params = {}
+    if args.params_file:
+        with open(args.params_file) as fh:
+            params.update(json.load(fh))
+    for _, _, dest in _FIT_PARAMS:
+        v = getattr(args, dest, None)
+        if v is not None:
+            params[dest] = v
+    if "class_weights" in params and isinstance(params["class_weights"], str):
+        params["class_weights"] = [float(x) for x in params["class_weights"].split(",")]
+    if "ignored_features" in params and isinstance(params["ignored_features"], str):
+        out = []
+        for tok in params["ignored_features"].replace(":", ",").split(","):
+            if "-" in tok:
+                a, b = tok.split("-")
+                out += list(range(int(a), int(b) + 1))
+            elif tok:
+                out.append(int(tok))
+        params["ignored_features"] = out
+    if "boost_from_average" in params:
+        params["boost_from_average"] = str(params["boost_from_average"]).lower() in ("1", "true", "yes")
+    if args.use_best_model is not None:
+        params["use_best_model"] = args.use_best_model.lower() in ("1", "true", "yes")
+    if args.save_snapshot:
+        params["save_snapshot"] = True
+    return params
+
+
+def mode_fit(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 fit")
+    _add_pool_args(ap)
+    ap.add_argument("-m", "--model-file", default="model.bin")
+    ap.add_argument("--model-format", default="CatboostBinary")
+    ap.add_argument("--params-file")
+    ap.add_argument("--eval-file")
+    ap.add_argument("--use-best-model")
+    ap.add_argument("--save-snapshot", action="store_true")
+    ap.add_argument("--fstr-file")
+    ap.add_argument("--verbose", type=int, default=1)
+    for flag, typ, dest in _FIT_PARAMS:
+        ap.add_argument(flag, type=typ, dest=dest, default=None)
+    args = ap.parse_args(argv)
+    if not args.learn_set:
+        ap.error("--learn-set is required")
+    from .core import CatBoost
+    params = _fit_params(args)
+    params.setdefault("verbose", bool(args.verbose))
+    learn = _pool(args.learn_set, args, args.learn_pairs)
+    tests = [_pool(t, args, args.test_pairs) for t in args.test_set]
+    model = CatBoost(params)
+    model.fit(learn, eval_set=tests or None)
+    for fmt in args.model_format.split(","):
+        fmt = {"CatboostBinary": "cbm", "Json": "json", "Cpp": "cpp", "Python": "python"}.get(fmt, fmt.lower())
+        name = args.model_file if fmt == "cbm" else f"{args.model_file}.{fmt}"
+        model.save_model(name, format=fmt)
+    if args.eval_file and tests:
+        raw = model.predict(tests[0], prediction_type="RawFormulaVal")
+        _write_eval(args.eval_file, raw, tests[0], ["RawFormulaVal"])
+    if args.fstr_file:
+        imp = model.get_feature_importance()
+        with open(args.fstr_file, "w") as fh:
+            for i in np.argsort(-imp):
+                fh.write(f"{imp[i]:.9g}\t{model.feature_names_[i]}\n")
+    return 0
+
+
+def _write_eval(path, preds, pool, types):
+    preds = np.asarray(preds)
+    if preds.ndim == 1:
+        preds = preds.reshape(-1, 1)
+    with open(path, "w") as fh:
+        cols = ["SampleId"] + [f"{types[0]}" if preds.shape[1] == 1 else f"{types[0]}:Dim={k}" for k in range(preds.shape[1])]
+        if pool.label is not None:
+            cols.append("Label")
+        fh.write("\t".join(cols) + "\n")
+        for i in range(preds.shape[0]):
+            row = [str(i)] + [f"{v:.9g}" for v in preds[i]]
+            if pool.label is not None:
+                row.append(str(pool.label[i]))
+            fh.write("\t".join(row) + "\n")
+
+
+def mode_calc(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 calc")
+    ap.add_argument("-m", "--model-file", default="model.bin")
+    ap.add_argument("--model-format", default="CatboostBinary")
+    ap.add_argument("--input-path", required=True)
+    ap.add_argument("--column-description", "--cd", dest="cd")
+    ap.add_argument("--delimiter", default="\t")
+    ap.add_argument("--has-header", action="store_true")
+    ap.add_argument("-o", "--output-path", default="output.tsv")
+    ap.add_argument("--prediction-type", default="RawFormulaVal")
+    ap.add_argument("--tree-count-limit", type=int, default=0)
+    ap.add_argument("--task-type", default="CPU")
+    args = ap.parse_args(argv)
+    from .core import CatBoost
+    fmt = {"CatboostBinary": "cbm", "Json": "json"}.get(args.model_format, args.model_format.lower())
+    model = CatBoost().load_model(args.model_file, format=fmt)
+    pool = _pool(args.input_path, args)
+    types = args.prediction_type.split(",")
+    preds = model.predict(pool, prediction_type=types[0], ntree_end=args.tree_count_limit, task_type=args.task_type)
+    _write_eval(args.output_path, preds, pool, types)
+    return 0
+
+
+def mode_fstr(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 fstr")
+    ap.add_argument("-m", "--model-file", default="model.bin")
+    ap.add_argument("--input-path")
+    ap.add_argument("--column-description", "--cd", dest="cd")
+    ap.add_argument("--delimiter", default="\t")
+    ap.add_argument("--has-header", action="store_true")
+    ap.add_argument("-o", "--output-path", default="feature_strength.tsv")
+    ap.add_argument("--fstr-type", default="FeatureImportance")
+    args = ap.parse_args(argv)
+    from .core import CatBoost
+    model = CatBoost().load_model(args.model_file)
+    data = _pool(args.input_path, args) if args.input_path else None
+    imp = model.get_feature_importance(data, type=args.fstr_type)
+    with open(args.output_path, "w") as fh:
+        if args.fstr_type in ("ShapValues",):
+            for row in np.asarray(imp):
+                fh.write("\t".join(f"{v:.9g}" for v in np.ravel(row)) + "\n")
+        elif args.fstr_type == "Interaction":
+            for a, b, v in imp:
+                fh.write(f"{v:.9g}\t{a}\t{b}\n")
+        else:
+            for i in np.argsort(-np.asarray(imp)):
+                fh.write(f"{imp[i]:.9g}\t{model.feature_names_[i]}\n")
+    return 0
+
+
+def mode_eval_metrics(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 eval-metrics")
+    ap.add_argument("-m", "--model-file", default="model.bin")
+    ap.add_argument("--input-path", required=True)
+    ap.add_argument("--column-description", "--cd", dest="cd")
+    ap.add_argument("--delimiter", default="\t")
+    ap.add_argument("--has-header", action="store_true")
+    ap.add_argument("-o", "--output-path", default="eval_metrics.tsv")
+    ap.add_argument("--metrics", required=True)
+    ap.add_argument("--eval-period", type=int, default=1)
+    args = ap.parse_args(argv)
+    from .core import CatBoost
+    model = CatBoost().load_model(args.model_file)
+    res = model.eval_metrics(_pool(args.input_path, args), args.metrics.split(","), eval_period=args.eval_period)
+    names = list(res)
+    with open(args.output_path, "w") as fh:
+        fh.write("iter\t" + "\t".join(names) + "\n")
+        for i in range(len(res[names[0]])):
+            fh.write(f"{i}\t" + "\t".join(f"{res[n][i]:.9g}" for n in names) + "\n")
+    return 0
+
+
+def mode_metadata(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 metadata")
+    ap.add_argument("action", choices=["get", "set", "dump"])
+    ap.add_argument("-m", "--model-file", default="model.bin")
+    ap.add_argument("--key")
+    ap.add_argument("--value")
+    args = ap.parse_args(argv)
+    from .core import CatBoost
+    model = CatBoost().load_model(args.model_file)
+    if args.action == "dump":
+        for k, v in model._model.info.items():
+            print(f"{k}\t{v}")
+    elif args.action == "get":
+        print(model._model.info.get(args.key, ""))
+    else:
+        model._model.info[args.key] = args.value
+        model.save_model(args.model_file)
+    return 0
+
+
+def mode_model_sum(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 model-sum")
+    ap.add_argument("-m", "--model", action="append", default=[], help="path or path=weight")
+    ap.add_argument("-o", "--output-path", default="model.bin")
+    args = ap.parse_args(argv)
+    from .core import CatBoost, sum_models
+    models, weights = [], []
+    for spec in args.model:
+        path, _, w = spec.partition("=")
+        models.append(CatBoost().load_model(path))
+        weights.append(float(w) if w else 1.0)
+    sum_models(models, weights).save_model(args.output_path)
+    return 0
+
+
+def mode_normalize_model(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 normalize-model")
+    ap.add_argument("-m", "--model-file", default="model.bin")
+    ap.add_argument("--set-scale", type=float)
+    ap.add_argument("--set-bias", type=float)
+    ap.add_argument("-o", "--output-model")
+    ap.add_argument("--print-scale-and-bias", action="store_true")
+    args = ap.parse_args(argv)
+    from .core import CatBoost
+    model = CatBoost().load_model(args.model_file)
+    scale, bias = model.get_scale_and_bias()
+    if args.set_scale is not None or args.set_bias is not None:
+        model.set_scale_and_bias(args.set_scale if args.set_scale is not None else scale,
+                                 args.set_bias if args.set_bias is not None else bias)
+        model.save_model(args.output_model or args.model_file)
+    if args.print_scale_and_bias:
+        print(model.get_scale_and_bias())
+    return 0
+
+
+def mode_select_features(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 select-features")
+    _add_pool_args(ap)
+    ap.add_argument("--params-file")
+    ap.add_argument("--features-for-select", required=True)
+    ap.add_argument("--num-features-to-select", type=int, required=True)
+    ap.add_argument("--features-selection-steps", type=int, default=1)
+    ap.add_argument("--features-selection-result-path", default="selection_result.json")
+    ap.add_argument("--use-best-model")
+    ap.add_argument("--save-snapshot", action="store_true")
+    for flag, typ, dest in _FIT_PARAMS:
+        ap.add_argument(flag, type=typ, dest=dest, default=None)
+    args = ap.parse_args(argv)
+    from .core import CatBoost
+    feats = []
+    for tok in args.features_for_select.split(","):
+        if "-" in tok:
+            a, b = tok.split("-")
+            feats += list(range(int(a), int(b) + 1))
+        else:
+            feats.append(int(tok))
+    est = CatBoost({**_fit_params(args), "verbose": False})
+    res = est.select_features(_pool(args.learn_set, args), features_for_select=feats,
+                              num_features_to_select=args.num_features_to_select, steps=args.features_selection_steps)
+    with open(args.features_selection_result_path, "w") as fh:
+        json.dump(res, fh)
+    return 0
+
+
+def mode_dataset_statistics(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 dataset-statistics")
+    ap.add_argument("--input-path", required=True)
+    ap.add_argument("--column-description", "--cd", dest="cd")
+    ap.add_argument("--delimiter", default="\t")
+    ap.add_argument("--has-header", action="store_true")
+    ap.add_argument("-o", "--output-path", default="statistics.json")
+    args = ap.parse_args(argv)
+    pool = _pool(args.input_path, args)
+    fd = pool.float_data
+    stats = {"object_count": pool.num_row(), "feature_count": pool.num_col(),
+             "float_features": [{"min": float(np.nanmin(fd[:, j])), "max": float(np.nanmax(fd[:, j])),
+                                 "mean": float(np.nanmean(fd[:, j])), "nan_count": int(np.isnan(fd[:, j]).sum())}
+                                for j in range(fd.shape[1])],
+             "cat_features": [{"unique_values": int(len(np.unique(pool.cat_hashes[j])))} for j in range(len(pool.cat_feature_indices))]}
+    if pool.label is not None and np.asarray(pool.label).dtype.kind in "fiu":
+        lab = np.asarray(pool.label, dtype=np.float64)
+        stats["target"] = {"min": float(lab.min()), "max": float(lab.max()), "mean": float(lab.mean())}
+    with open(args.output_path, "w") as fh:
+        json.dump(stats, fh, indent=1)
+    return 0
+
+
+def mode_dump_options(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 dump-options")
+    ap.add_argument("--params-file")
+    ap.add_argument("-o", "--output-path")
+    ap.add_argument("--use-best-model")
+    ap.add_argument("--save-snapshot", action="store_true")
+    for flag, typ, dest in _FIT_PARAMS:
+        ap.add_argument(flag, type=typ, dest=dest, default=None)
+    args = ap.parse_args(argv)
+    from .params import resolve_options
+    o = resolve_options(_fit_params(args))
+    text = o.to_json()
+    if args.output_path:
+        with open(args.output_path, "w") as fh:
+            fh.write(text)
+    else:
+        print(text)
+    return 0
+
+
+def mode_roc(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 roc")
+    ap.add_argument("-m", "--model-file", default="model.bin")
+    ap.add_argument("--input-path", required=True)
+    ap.add_argument("--column-description", "--cd", dest="cd")
+    ap.add_argument("--delimiter", default="\t")
+    ap.add_argument("--has-header", action="store_true")
+    ap.add_argument("-o", "--output-path", default="roc.tsv")
+    args = ap.parse_args(argv)
+    from .core import CatBoost
+    from .utils.roc import roc_curve
+    model = CatBoost().load_model(args.model_file)
+    pool = _pool(args.input_path, args)
+    fpr, tpr, thr = roc_curve(model, pool)
+    with open(args.output_path, "w") as fh:
+        fh.write("FPR\tTPR\tThreshold\n")
+        for a, b, c in zip(fpr, tpr, thr):
+            fh.write(f"{a:.9g}\t{b:.9g}\t{c:.9g}\n")
+    return 0
+
+
+MODES = {"fit": mode_fit, "calc": mode_calc, "fstr": mode_fstr, "eval-metrics": mode_eval_metrics,
+         "metadata": mode_metadata, "model-sum": mode_model_sum, "normalize-model": mode_normalize_model,
+         "select-features": mode_select_features, "dataset-statistics": mode_dataset_statistics,
+         "dump-options": mode_dump_options, "roc": mode_roc}
+
+
+def main(argv=None):
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if not argv or argv[0] in ("-h", "--help"):
+        print("usage: python -m catboost_b200 <mode> [options]\nmodes: " + ", ".join(MODES))
+        return 0
+    mode = argv[0]
+    if mode in ("run-worker", "ostr", "eval-feature", "model-based-eval"):
+        print(f"mode {mode!r} is not supported: multi-host CPU workers / object importance / feature evaluation are "
+              "outside this framework (single box, GPUs over NVLink)", file=sys.stderr)
+        return 2
+    if mode not in MODES:
+        print(f"unknown mode {mode!r}; modes: " + ", ".join(MODES), file=sys.stderr)
+        return 2
+    return MODES[mode](argv[1:])
