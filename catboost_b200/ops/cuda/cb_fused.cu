@@ -203,13 +203,20 @@ CB_API void cb_fused_destroy(CbFusedPlan* p) { delete p; }
 CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int* smem_bytes, int* threads) {
     const int nslots = level == 0 ? 1 : (1 << (level - 1));
     const int per_slot = p->a.h.S * 4 * p->a.h.B * 4 * (p->a.h.statmax ? 2 : 1);
+    const bool ring = p->a.h.statmax && p->a.h.S == 2;      // per-warp compaction rings (16 bytes x 64 entries)
+    int thr = p->threads;
+    int ring_bytes = ring ? (thr / 32) * 64 * 16 + 16 : 0;
+    int budget = p->max_smem - ring_bytes;
     int spp = nslots;
-    const int budget = p->max_smem;
+    if (spp * per_slot > budget / 2) {
+        // one 1024-thread block per SM when the tile needs more than half of the shared memory
+        thr = 1024;
+        ring_bytes = ring ? (thr / 32) * 64 * 16 + 16 : 0;
+        budget = p->max_smem - ring_bytes;
+    }
     if (spp * per_slot > budget) spp = budget / per_slot;
     if (spp < 1) return 0;
-    const int smem = spp * per_slot;
-    // one big block per SM when the tile needs more than half of the shared memory, else several 512-thread blocks
-    int thr = (smem > budget / 2) ? 1024 : p->threads;
+    const int smem = spp * per_slot + ring_bytes;
     int occ = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, cb_level_fused_kernel, thr, smem) != cudaSuccess) { cudaGetLastError(); return 0; }
     if (occ < 1) return 0;

@@ -249,6 +249,120 @@ static __device__ void cb_hist_item_q(const CbHistArgs& a, int* sh, int g, long 
     __syncthreads();
 }
 
+// Two-statistic fixed-point variant with warp-level compaction.  From level 1 on only the lighter child of every
+// parent is accumulated, so about half of the documents are skipped; issuing the atomics straight from the streaming
+// loop would leave half of the lanes idle in every atomic instruction.  Instead each warp appends its live documents
+// (bins word, tile offset, two quantised statistics = 16 bytes) to a small ring in shared memory and drains it 32
+// entries at a time, so every atomic instruction runs with all lanes busy.
+// sh layout: int hist[slot][2][part][j][B], then uint4 ring[warps][64].
+#define CB_RING 64
+__device__ __forceinline__ void cb_hist_q_apply(int* sh, int B, uint4 e) {
+    int* base = sh + (int)e.y;
+    const int q0 = (int)e.z, q1 = (int)e.w;
+    const int h0 = q0 >> 12, h1 = q1 >> 12;
+    const unsigned int l0 = (unsigned int)q0 & 4095u, l1 = (unsigned int)q1 & 4095u;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const unsigned int bin = (e.x >> (8 * j)) & 255u;
+        atomicAdd(base + j * B + bin, h0);
+        atomicAdd(reinterpret_cast<unsigned int*>(base) + (4 + j) * B + bin, l0);
+        atomicAdd(base + (8 + j) * B + bin, h1);
+        atomicAdd(reinterpret_cast<unsigned int*>(base) + (12 + j) * B + bin, l1);
+    }
+}
+
+static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long long item, long long d_begin,
+                                       long long d_end, int slot_begin, int slot_count) {
+    const int B = a.B;
+    const int total = slot_count * 16 * B;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) sh[i] = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint4* ring = reinterpret_cast<uint4*>(sh + ((total + 3) & ~3)) + warp * CB_RING;
+    const uint32_t* bg = a.d.bins + (long long)g * a.d.npad;
+    const float* st0 = a.stats;
+    const float* st1 = a.stats + a.d.npad;
+    const int level = a.level;
+    const int nslots = cb_hist_nslots(a);
+    const unsigned int pmask = (unsigned int)(nslots - 1);
+    const int slot_stride = 16 * B;
+    const float sc0 = 8388607.0f / fmaxf(a.statmax[0], 1e-30f);
+    const float sc1 = 8388607.0f / fmaxf(a.statmax[1], 1e-30f);
+    const unsigned int lt = (1u << lane) - 1u;
+    unsigned int head = 0, tail = 0;
+    for (long long ib = d_begin + (long long)(threadIdx.x & ~31) * 4; ib < d_end; ib += (long long)blockDim.x * 4) {
+        const long long i = ib + lane * 4;
+        uint4 w = make_uint4(0, 0, 0, 0);
+        ushort4 lf = make_ushort4(0, 0, 0, 0);
+        float4 s0 = make_float4(0, 0, 0, 0), s1 = make_float4(0, 0, 0, 0);
+        const bool valid = i < d_end;
+        if (valid) {
+            w = *reinterpret_cast<const uint4*>(bg + i);
+            lf = *reinterpret_cast<const ushort4*>(a.leaf + i);
+            s0 = *reinterpret_cast<const float4*>(st0 + i);
+            s1 = *reinterpret_cast<const float4*>(st1 + i);
+        }
+        const unsigned int wv[4] = {w.x, w.y, w.z, w.w};
+        const unsigned int lv[4] = {lf.x, lf.y, lf.z, lf.w};
+        const float v0[4] = {s0.x, s0.y, s0.z, s0.w};
+        const float v1[4] = {s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            int slot = 0;
+            bool take = valid && (i + k) < a.d.n;
+            if (a.slot_table) {
+                slot = a.slot_table[lv[k]];
+                take = take && (slot >= 0);
+            } else if (level > 0) {
+                const unsigned int p = lv[k] & pmask;
+                const unsigned int right = (lv[k] >> (level - 1)) & 1u;
+                const unsigned int want = (a.small_mask[p >> 5] >> (p & 31)) & 1u;
+                take = take && (right == want);
+                slot = (int)p;
+            }
+            slot -= slot_begin;
+            take = take && ((unsigned)slot < (unsigned)slot_count);
+            const unsigned int m = __ballot_sync(0xffffffffu, take);
+            if (take) {
+                ring[(tail + __popc(m & lt)) & (CB_RING - 1)] =
+                    make_uint4(wv[k], (unsigned int)(slot * slot_stride), (unsigned int)__float2int_rn(v0[k] * sc0),
+                               (unsigned int)__float2int_rn(v1[k] * sc1));
+            }
+            tail += __popc(m);
+            __syncwarp();
+            if (tail - head >= 32u) {
+                cb_hist_q_apply(sh, B, ring[(head + lane) & (CB_RING - 1)]);
+                head += 32u;
+                __syncwarp();
+            }
+        }
+    }
+    if ((unsigned int)lane < tail - head) cb_hist_q_apply(sh, B, ring[(head + lane) & (CB_RING - 1)]);
+    __syncthreads();
+    // dump as floats into the private region [item][slot][s][j][B]
+    const int cells4 = (slot_count * 8 * B) >> 2;
+    float4* dst = reinterpret_cast<float4*>(a.priv + ((size_t)item * nslots + slot_begin) * (size_t)(8 * B));
+    const int B4 = B >> 2;
+    const float inv0 = fmaxf(a.statmax[0], 1e-30f) * (1.0f / 8388607.0f);
+    const float inv1 = fmaxf(a.statmax[1], 1e-30f) * (1.0f / 8388607.0f);
+    for (int c = threadIdx.x; c < cells4; c += blockDim.x) {
+        const int b4 = c % B4;
+        const int r = c / B4;            // (slot * 2 + s) * 4 + j
+        const int j = r & 3;
+        const int ss = r >> 2;           // slot * 2 + s
+        const float inv = (ss & 1) ? inv1 : inv0;
+        const int4 hi = *reinterpret_cast<const int4*>(sh + (size_t)ss * 8 * B + j * B + b4 * 4);
+        const uint4 lo = *reinterpret_cast<const uint4*>(sh + (size_t)ss * 8 * B + (4 + j) * B + b4 * 4);
+        float4 v;
+        v.x = fmaf((float)hi.x, 4096.0f * inv, (float)lo.x * inv);
+        v.y = fmaf((float)hi.y, 4096.0f * inv, (float)lo.y * inv);
+        v.z = fmaf((float)hi.z, 4096.0f * inv, (float)lo.z * inv);
+        v.w = fmaf((float)hi.w, 4096.0f * inv, (float)lo.w * inv);
+        dst[c] = v;
+    }
+    __syncthreads();
+}
+
 #define CB_HIST_MAX_DOCS_PER_TILE (1 << 19)
 __device__ __forceinline__ int cb_hist_chunks(int G, int ncta, long long n) {
     const int by_grid = (ncta >= G) ? (ncta / G) : 1;
@@ -271,7 +385,8 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
             const long long k = item / G;
             const long long b = k * per;
             const long long e = min(a.d.n, b + per);
-            if (a.statmax) cb_hist_item_q(a, reinterpret_cast<int*>(sh), g, item, min(b, e), e, sb, sc);
+            if (a.statmax && a.S == 2) cb_hist_item_q2(a, reinterpret_cast<int*>(sh), g, item, min(b, e), e, sb, sc);
+            else if (a.statmax) cb_hist_item_q(a, reinterpret_cast<int*>(sh), g, item, min(b, e), e, sb, sc);
             else if (b < e || a.priv) cb_hist_item(a, sh, g, item, min(b, e), e, sb, sc);
         }
     }

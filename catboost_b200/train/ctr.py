@@ -1,0 +1,266 @@
+"""CTR engine: permutation-ordered target statistics for categorical features and their combinations.
+
+For every *projection* (one categorical feature, or a combination of up to ``max_ctr_complexity`` of them) and every
+CTR description (type + prior) a float feature is produced and binarised with its own borders:
+
+* training rows: statistics of the rows that precede the row in a random permutation and share its category
+  (exclusive prefix inside the category, in permutation order) -- ``(good + prior) / (total + 1)`` for the target-class
+  types (``Borders``, ``Buckets``, ``BinarizedTargetMeanValue``), the category count so far is NOT used for the counter types:
+  ``Counter`` / ``FeatureFreq`` use the count of the category in the whole learn set (they do not look at the target);
+* evaluation rows and the final model: statistics of the whole learn set.
+
+Behaviour follows catboost/cuda/ctrs/ctr_calcers.h:122-160, ctr_bins_builder.h:137-245 (equal keys contiguous in
+permutation order, segmented exclusive scan, divide with priors), catboost/private/libs/algo/online_ctr.cpp and the
+prior defaults of catboost/private/libs/options/cat_feature_options.cpp:118-140.  The device path is a stable sort by
+category of the rows taken in permutation order, a segmented exclusive scan, and a scatter back.
+Combination hashes use the model's hash rule (catboost/libs/model/hash.h:11-14) so that the stored tables can be
+looked up at apply time from raw categorical hashes.
+"""
+from __future__ import annotations
+
+import itertools
+import re
+from dataclasses import dataclass, field
+from typing import List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from ..data.pool import CatBoostError, Pool
+from ..data.quantization import FlatFeature, select_borders
+from ..models.ctr import CtrFeature, projection_hash
+
+TARGET_CTRS = ("Borders", "Buckets", "BinarizedTargetMeanValue", "FloatTargetMeanValue")
+COUNT_CTRS = ("Counter", "FeatureFreq")
+
+
+@dataclass
+class CtrSpec:
+    cat_features: Tuple[int, ...]
+    ctr_type: str
+    prior_num: float
+    prior_denom: float = 1.0
+    target_border_idx: int = 0
+    border_count: int = 15
+
+
+@dataclass
+class CtrPlan:
+    specs: List[CtrSpec]
+    target_borders: np.ndarray          # thresholds that binarise the target into classes
+    n_target_classes: int
+
+
+@dataclass
+class CtrState:
+    flat_features: List[FlatFeature]
+    train_bins: torch.Tensor            # uint8 [n_ctr, n_train] on the training device
+    eval_bins: List[torch.Tensor]
+    model_ctrs: List[CtrFeature]
+    permutation: np.ndarray = field(default=None)
+
+
+def _parse_ctr_description(desc: str, default_priors):
+    """'Borders:TargetBorderCount=1:Prior=0/1:Prior=0.5/1' -> (type, target_border_count, [(num, denom)], border_count)."""
+    parts = desc.split(":")
+    ctype = parts[0]
+    priors, tbc, bc = [], 1, None
+    for p in parts[1:]:
+        k, _, v = p.partition("=")
+        if k == "Prior":
+            a, _, b = v.partition("/")
+            priors.append((float(a), float(b) if b else 1.0))
+        elif k == "TargetBorderCount":
+            tbc = int(v)
+        elif k == "CtrBorderCount":
+            bc = int(v)
+    return ctype, tbc, priors or list(default_priors), bc
+
+
+def plan_ctrs(o, pool: Pool, ctr_cats: List[int], ctx) -> CtrPlan:
+    gpu = o.task_type == "GPU"
+    simple = o.simple_ctr
+    if simple is None:
+        simple = ["Borders", "Counter"]          # FeatureFreq is the reference's GPU name for the count-based CTR
+    if isinstance(simple, str):
+        simple = [simple]
+    combos = o.combinations_ctr if o.combinations_ctr is not None else simple
+    if isinstance(combos, str):
+        combos = [combos]
+    tbc_max = 1
+    specs: List[CtrSpec] = []
+
+    def add(projection, descs):
+        nonlocal tbc_max
+        for d in descs:
+            ctype, tbc, priors, bc = _parse_ctr_description(
+                d, [(0.0, 1.0), (0.5, 1.0), (1.0, 1.0)] if d.split(":")[0] in TARGET_CTRS else [(0.0, 1.0)])
+            if ctype not in TARGET_CTRS + COUNT_CTRS:
+                raise CatBoostError(f"unknown CTR type {ctype!r}")
+            if o.ctr_target_border_count:
+                tbc = int(o.ctr_target_border_count)
+            tbc_max = max(tbc_max, tbc)
+            for num, den in priors:
+                if ctype in TARGET_CTRS:
+                    for tb in range(tbc):
+                        specs.append(CtrSpec(tuple(projection), ctype, num, den, tb, bc or int(o.ctr_border_count)))
+                else:
+                    specs.append(CtrSpec(tuple(projection), ctype, num, den, 0, bc or int(o.ctr_border_count)))
+
+    for c in ctr_cats:
+        add((c,), simple)
+    complexity = int(o.max_ctr_complexity)
+    if complexity >= 2 and len(ctr_cats) >= 2:
+        # Static combinations: pairs (and triples when asked) among the categorical features of lowest cardinality.
+        # The reference discovers combinations greedily while a tree grows (tree CTRs, feature-parallel only);
+        # here they are enumerated up front under a fixed budget so that training stays doc-parallel.
+        card = {c: len(np.unique(pool.cat_hashes[c][: min(pool.num_row(), 200000)])) for c in ctr_cats}
+        ranked = sorted(ctr_cats, key=lambda c: card[c])
+        budget = 24
+        top = ranked[: 8]
+        for k in range(2, min(complexity, 3) + 1):
+            for proj in itertools.combinations(top, k):
+                if budget <= 0:
+                    break
+                add(tuple(sorted(proj)), combos)
+                budget -= 1
+    return CtrPlan(specs, np.zeros(0), 2)
+
+
+def _target_classes(plan: CtrPlan, y: np.ndarray, codec, n_borders: int):
+    """Binarise the target into ``n_borders + 1`` classes (MinEntropy-like equal-frequency borders for regression,
+    the class index for classification)."""
+    y = np.asarray(y, dtype=np.float64).reshape(len(y), -1)[:, 0]
+    if codec is not None and (codec.is_binclass or codec.is_multiclass):
+        cls = y.astype(np.int64)
+        k = int(cls.max()) + 1 if len(cls) else 2
+        return cls, max(k, 2), np.arange(k - 1) + 0.5
+    srt = np.sort(y)
+    borders, _ = select_borders(srt.reshape(-1, 1).astype(np.float32), n_borders, "MinEntropy")
+    b = borders[0].astype(np.float64)
+    if len(b) == 0:
+        b = np.array([float(np.mean(y))])
+    cls = np.searchsorted(b, y, side="left")
+    return cls.astype(np.int64), len(b) + 1, b
+
+
+def _projection_keys(pool: Pool, projection, device):
+    """Dense category ids of the projection for the rows of ``pool`` + the 64-bit projection hash per row."""
+    h = projection_hash([pool.cat_hashes[c] for c in projection])
+    return h
+
+
+def _ordered_stats(keys_t: torch.Tensor, order_t: torch.Tensor, cols: torch.Tensor):
+    """Exclusive prefix sums of ``cols`` [C, n] inside each key, in the order given by ``order_t`` (row ids in
+    permutation order).  Returns [C, n] aligned with the original rows."""
+    n = keys_t.shape[0]
+    k_in_order = keys_t[order_t]
+    srt = torch.argsort(k_in_order, stable=True)          # groups contiguous, permutation order inside a group
+    rows = order_t[srt]
+    ks = k_in_order[srt]
+    vals = cols[:, rows]
+    cs = torch.cumsum(vals, dim=1)
+    start = torch.ones(n, dtype=torch.bool, device=keys_t.device)
+    if n > 1:
+        start[1:] = ks[1:] != ks[:-1]
+    seg_id = torch.cumsum(start.long(), 0) - 1
+    first_idx = torch.nonzero(start).squeeze(1)
+    base = cs[:, first_idx] - vals[:, first_idx]           # cumsum before each segment
+    excl = cs - vals - base[:, seg_id]
+    out = torch.empty_like(excl)
+    out[:, rows] = excl
+    return out
+
+
+def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, eval_pools, device, ctx, codec) -> CtrState:
+    dev = torch.device(device)
+    n = train_pool.num_row()
+    rng = np.random.RandomState(int(o.random_seed) + 101)
+    if o.has_time:
+        order = np.arange(n)
+    else:
+        # block-wise shuffle like the reference (fold_permutation_block), groups stay together
+        blk = int(o.fold_permutation_block or 1)
+        if train_pool.group_id is not None:
+            off = train_pool.group_offsets()
+            g = rng.permutation(len(off) - 1)
+            order = np.concatenate([np.arange(off[k], off[k + 1]) for k in g]) if len(g) else np.zeros(0, np.int64)
+        elif blk > 1:
+            nb = (n + blk - 1) // blk
+            order = np.concatenate([np.arange(b * blk, min(n, (b + 1) * blk)) for b in rng.permutation(nb)])
+        else:
+            order = rng.permutation(n)
+    order_t = torch.from_numpy(order.astype(np.int64)).to(dev)
+    tbc = max([s.target_border_idx for s in plan.specs if s.ctr_type in TARGET_CTRS] + [0]) + 1
+    cls, n_cls, tborders = _target_classes(plan, y_train, codec, tbc)
+    plan.target_borders, plan.n_target_classes = tborders, n_cls
+    cls_t = torch.from_numpy(cls).to(dev)
+    ones = torch.ones(n, dtype=torch.float32, device=dev)
+
+    flat, train_cols, eval_cols, model_ctrs = [], [], [[] for _ in eval_pools], []
+    by_proj = {}
+    for s in plan.specs:
+        by_proj.setdefault(s.cat_features, []).append(s)
+    for proj, specs in by_proj.items():
+        h_train = projection_hash([train_pool.cat_hashes[c] for c in proj])
+        uniq, inv = np.unique(h_train, return_inverse=True)
+        keys_t = torch.from_numpy(inv.astype(np.int64)).to(dev)
+        U = len(uniq)
+        # indicators: class > border k  (Borders), one column per needed target border + the count column
+        need_tb = sorted({s.target_border_idx for s in specs if s.ctr_type in TARGET_CTRS})
+        cols = [ones] + [(cls_t > tb).float() for tb in need_tb]
+        colmat = torch.stack(cols)
+        prefix = _ordered_stats(keys_t, order_t, colmat) if any(s.ctr_type in TARGET_CTRS for s in specs) else None
+        totals = torch.zeros((len(cols), U), dtype=torch.float32, device=dev)
+        totals.index_add_(1, keys_t, colmat)
+        totals_np = totals.cpu().numpy()
+        max_count = float(totals_np[0].max()) if U else 1.0
+        eval_keys = []
+        for ep in eval_pools:
+            he = projection_hash([ep.cat_hashes[c] for c in proj])
+            pos = np.searchsorted(uniq, he)
+            pos = np.clip(pos, 0, max(U - 1, 0))
+            ok = (uniq[pos] == he) if U else np.zeros(len(he), bool)
+            eval_keys.append((torch.from_numpy(pos.astype(np.int64)).to(dev), torch.from_numpy(ok).to(dev)))
+        for s in specs:
+            if s.ctr_type in TARGET_CTRS:
+                ci = 1 + need_tb.index(s.target_border_idx)
+                tr_val = (prefix[ci] + s.prior_num) / (prefix[0] + s.prior_denom)
+                full = (totals[ci] + s.prior_num) / (totals[0] + s.prior_denom)
+                unseen = s.prior_num / s.prior_denom
+            elif s.ctr_type == "Counter":
+                denom = max_count + s.prior_denom
+                full = (totals[0] + s.prior_num) / denom
+                tr_val = full[keys_t]
+                unseen = s.prior_num / denom
+            else:   # FeatureFreq
+                denom = float(n) + s.prior_denom
+                full = (totals[0] + s.prior_num) / denom
+                tr_val = full[keys_t]
+                unseen = s.prior_num / denom
+            sample = tr_val if n <= 200000 else tr_val[torch.from_numpy(rng.choice(n, 200000, replace=False)).to(dev)]
+            borders, _ = select_borders(sample.cpu().numpy().reshape(-1, 1), s.border_count, "Uniform"
+                                        if s.ctr_type in TARGET_CTRS else "GreedyLogSum")
+            b = borders[0]
+            if len(b) == 0:
+                continue
+            bt = torch.from_numpy(b).to(dev)
+            train_cols.append(torch.searchsorted(bt, tr_val.contiguous(), right=False).to(torch.uint8))
+            for k, (pos, ok) in enumerate(eval_keys):
+                ev = torch.where(ok, full[pos] if U else torch.zeros_like(ok, dtype=torch.float32),
+                                 torch.full((len(ok),), float(unseen), device=dev))
+                eval_cols[k].append(torch.searchsorted(bt, ev.contiguous(), right=False).to(torch.uint8))
+            ctr_index = len(model_ctrs)
+            if s.ctr_type in TARGET_CTRS:
+                good = totals_np[1 + need_tb.index(s.target_border_idx)]
+                model_ctrs.append(CtrFeature(list(proj), s.ctr_type, s.prior_num, s.prior_denom, s.target_border_idx,
+                                             uniq.copy(), good.astype(np.float64), totals_np[0].astype(np.float64), 0.0))
+            else:
+                model_ctrs.append(CtrFeature(list(proj), s.ctr_type, s.prior_num, s.prior_denom, 0, uniq.copy(),
+                                             totals_np[0].astype(np.float64), totals_np[0].astype(np.float64),
+                                             max_count if s.ctr_type == "Counter" else float(n)))
+            flat.append(FlatFeature("ctr", ctr_index, borders=b, n_bins=len(b) + 1, ctr=s))
+    train_bins = torch.stack(train_cols) if train_cols else torch.zeros((0, n), dtype=torch.uint8, device=dev)
+    eval_bins = [torch.stack(c) if c else torch.zeros((0, ep.num_row()), dtype=torch.uint8, device=dev)
+                 for c, ep in zip(eval_cols, eval_pools)]
+    return CtrState(flat, train_bins, eval_bins, model_ctrs, order)
