@@ -81,22 +81,33 @@ class LabelCodec:
             if self.n_classes < 2 and not o.allow_const_label:
                 raise CatBoostError("target contains only one unique value")
 
+    def _map(self, lab: np.ndarray) -> np.ndarray:
+        names = self.class_names
+        try:
+            arr = np.asarray(names, dtype=lab.dtype if lab.dtype.kind in "fiub" else None)
+            order = np.argsort(arr, kind="stable")
+            srt = arr[order]
+            pos = np.clip(np.searchsorted(srt, lab), 0, len(srt) - 1)
+            ok = srt[pos] == lab
+            if not bool(np.all(ok)):
+                bad = lab[~ok][0]
+                raise CatBoostError(f"label {bad!r} was not seen in the training data")
+            return order[pos].astype(np.float32)
+        except TypeError:
+            m = {v: i for i, v in enumerate(names)}
+            try:
+                return np.array([m[v] for v in lab.tolist()], dtype=np.float32)
+            except KeyError as e:
+                raise CatBoostError(f"label {e.args[0]!r} was not seen in the training data")
+
     def encode(self, label) -> np.ndarray:
         lab = np.asarray(label)
         if self.loss == "Logloss":
             if self.border is not None:
                 return (lab.astype(np.float64) > self.border).astype(np.float32)
-            m = {v: i for i, v in enumerate(self.class_names)}
-            try:
-                return np.array([m[v] for v in lab.tolist()], dtype=np.float32)
-            except KeyError as e:
-                raise CatBoostError(f"label {e.args[0]!r} was not seen in the training data")
+            return self._map(lab)
         if self.is_multiclass:
-            m = {v: i for i, v in enumerate(self.class_names)}
-            try:
-                return np.array([m[v] for v in lab.tolist()], dtype=np.float32)
-            except KeyError as e:
-                raise CatBoostError(f"label {e.args[0]!r} was not seen in the training data")
+            return self._map(lab)
         if lab.dtype == object or lab.dtype.kind in "US":
             raise CatBoostError("string labels need a classification loss")
         return lab.astype(np.float32)
