@@ -713,3 +713,87 @@ CB_API int cb_device_info(int* sm_count, int* max_smem_optin) {
     cudaDeviceGetAttribute(max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     return 0;
 }
+
+// ======================================================================================================
+// Allocation-free variant of cb_leaf_pass (declared and documented in cb_noalloc.h).  The scratch of the pass
+// (per-leaf sums, block counter) is a fixed array in this library's device image instead of caller memory.
+#include "cb_noalloc.h"
+#include <cstdio>
+
+struct CbNoallocScratch {
+    double sums[CB_NOALLOC_MAX_LEAVES * 3];
+    unsigned int counter;
+};
+static __device__ __align__(256) CbNoallocScratch cb_noalloc_scratch;
+
+#define CB_NOALLOC_MAX_DEVICES 64
+static CbNoallocScratch* g_noalloc_ptr[CB_NOALLOC_MAX_DEVICES];     // device address of the array, per device
+static char g_noalloc_error[256] = "";
+
+CB_API const char* cb_noalloc_last_error(void) { return g_noalloc_error; }
+
+CB_API int cb_leaf_pass_noalloc(int loss, float p0, float p1, const float* approx, const float* target,
+                                const float* weight, const unsigned short* leaf, const float* ext_der,
+                                const float* ext_hess, long long n, int L, float* delta, int first, int last, int newton,
+                                float l2, float lr, float* cur_vals, float* model_vals, float* model_wts, int Lstride,
+                                const int* iter_ptr, float* leaf_w, int grid, cudaStream_t st) {
+    if (L < 1 || L > CB_NOALLOC_MAX_LEAVES) {
+        snprintf(g_noalloc_error, sizeof(g_noalloc_error),
+                 "cb_leaf_pass_noalloc: %d leaves requested, the built-in scratch holds at most %d", L,
+                 CB_NOALLOC_MAX_LEAVES);
+        return CB_NOALLOC_TOO_LARGE;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= CB_NOALLOC_MAX_DEVICES) {
+        snprintf(g_noalloc_error, sizeof(g_noalloc_error), "cb_leaf_pass_noalloc: cannot identify the current device (%s)",
+                 cudaGetErrorString(e));
+        cudaGetLastError();
+        return CB_NOALLOC_SETUP_FAILED;
+    }
+    if (g_noalloc_ptr[dev] == nullptr) {
+        // Set-up, once per device, with that device current: the name of a __device__ array is only a host-side
+        // stand-in; the address a kernel can use comes from the runtime.
+        CbNoallocScratch* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, cb_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            snprintf(g_noalloc_error, sizeof(g_noalloc_error), "cb_leaf_pass_noalloc: cudaGetSymbolAddress failed (%s)",
+                     cudaGetErrorString(e));
+            cudaGetLastError();
+            return e != cudaSuccess ? (int)e : CB_NOALLOC_SETUP_FAILED;
+        }
+        g_noalloc_ptr[dev] = ptr;
+    }
+    CbNoallocScratch* scratch = g_noalloc_ptr[dev];
+    // the array keeps the previous call's contents: clear what this call needs to start from zero
+    e = cudaMemsetAsync(scratch->sums, 0, sizeof(double) * 3 * (size_t)L, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(&scratch->counter, 0, sizeof(unsigned int), st);
+    if (e != cudaSuccess) {
+        snprintf(g_noalloc_error, sizeof(g_noalloc_error), "cb_leaf_pass_noalloc: clearing the scratch failed (%s)",
+                 cudaGetErrorString(e));
+        cudaGetLastError();
+        return (int)e;
+    }
+    CbLeafArgs a{loss, p0, p1, approx, target, weight, leaf, ext_der, ext_hess, n, L, delta, scratch->sums,
+                 &scratch->counter, first, last, newton, l2, lr, cur_vals, model_vals, model_wts, Lstride, iter_ptr,
+                 leaf_w, CbComm()};
+    a.c.nranks = 1; a.c.rank = 0;
+    int C = 32;
+    while (C > 0 && (size_t)3 * L * C * 4 > 96 * 1024) C >>= 1;
+    const int smem = 3 * L * C * 4;
+    e = cudaFuncSetAttribute(cb_leaf_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e != cudaSuccess) {
+        snprintf(g_noalloc_error, sizeof(g_noalloc_error), "cb_leaf_pass_noalloc: cudaFuncSetAttribute failed (%s)",
+                 cudaGetErrorString(e));
+        cudaGetLastError();
+        return (int)e;
+    }
+    cb_leaf_pass_kernel<<<grid, 512, smem, st>>>(a, C);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        snprintf(g_noalloc_error, sizeof(g_noalloc_error), "cb_leaf_pass_noalloc: launch failed (%s)", cudaGetErrorString(e));
+        return (int)e;
+    }
+    g_noalloc_error[0] = 0;
+    return 0;
+}
