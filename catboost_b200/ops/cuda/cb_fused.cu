@@ -33,6 +33,7 @@ struct CbFusedArgs {
     unsigned long long* msg_local;   // CB_SELECT_MSG_BYTES scratch in local memory
     int own_col[CB_MAX_RANKS + 1];   // rank r owns histogram columns [own_col[r], own_col[r+1]) (multiples of 4)
     int Wmax;                        // row stride (floats) of every slot buffer = max owned width
+    int smem_floats;                 // dynamic shared memory of this launch, in floats
 };
 
 // Sum of the per-chunk private tiles of this rank, written to the owner's slot.  One thread = one 16-byte column
@@ -111,7 +112,7 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
         grid.sync();
     }
 
-    cb_score_phase(a.s, cta, ncta);
+    cb_score_phase(a.s, cta, ncta, cb_sh, a.smem_floats);
     __threadfence();
     grid.sync();
 
@@ -236,6 +237,7 @@ CB_API int cb_fused_launch(CbFusedPlan* p, int level, float* hprev, float* hcur,
     a.h.level = level; a.h.small_mask = mask_in; a.h.slots_per_pass = slots_per_pass;
     a.s.level = level; a.s.small_mask = mask_in; a.s.hprev = hprev; a.s.hcur = hcur;
     a.mask_out = mask_out;
+    a.smem_floats = smem_bytes / 4;
     void* args[] = {&a};
     cudaError_t e = cudaLaunchCooperativeKernel((void*)cb_level_fused_kernel, dim3(grid), dim3(threads), args,
                                                 (size_t)smem_bytes, st);

@@ -305,7 +305,7 @@ static void cb_fill_score_args(CbScoreArgs& a, const CbData* d, const float* con
     a.best_key = best_key;
 }
 
-__global__ void __launch_bounds__(256) cb_score_kernel(CbScoreArgs a) { cb_score_phase(a, blockIdx.x, gridDim.x); }
+__global__ void __launch_bounds__(256) cb_score_kernel(CbScoreArgs a) { cb_score_phase(a, blockIdx.x, gridDim.x, nullptr, 0); }
 
 CB_API int cb_score(const CbData* d, const float* const* hsrc, int nsrc, const float* hprev, float* hcur, int W,
                     int col_base, int f_begin, int f_end, int level, int S, const unsigned int* small_mask, float l2,

@@ -454,21 +454,20 @@ __device__ __forceinline__ float cb_noise_std(const CbScoreArgs& a) {
     return (float)(a.random_strength * sd * (m / (1.0 + m)));
 }
 
-static __device__ void cb_score_feature(const CbScoreArgs& a, int f, float noise_std) {
+// Score terms of feature f accumulated over the leaves l0, l0 + lstep, ... into num/den (one warp).
+static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, int lstep, float* num, float* den) {
     const int lane = threadIdx.x & 31;
     const int nb = a.d.feat_nb[f];
-    const float fw = a.d.feat_weight ? a.d.feat_weight[f] : 1.0f;
     const int col0 = a.d.feat_off[f] - a.col_base;
     const int bpl = (nb + 31) >> 5;
     const bool onehot = a.d.feat_onehot && a.d.feat_onehot[f];
     const int S = a.S;
     const int L = 1 << a.level;
     const int half = L >> 1;
-    float num[8], den[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) { num[k] = 0.0f; den[k] = 0.0f; }
 
-    for (int l = 0; l < L; ++l) {
+    for (int l = l0; l < L; l += lstep) {
         int p = 0;
         bool computed = true;
         if (a.level > 0) {
@@ -523,7 +522,15 @@ static __device__ void cb_score_feature(const CbScoreArgs& a, int f, float noise
             }
         }
     }
-    // best candidate of this lane; borders are bins 0 .. nb-2 (one-hot: every value 0 .. nb-1)
+}
+
+// Best candidate of feature f from complete num/den (one warp); borders are bins 0 .. nb-2 (one-hot: every value).
+static __device__ void cb_score_finalize(const CbScoreArgs& a, int f, const float* num, const float* den, float noise_std) {
+    const int lane = threadIdx.x & 31;
+    const int nb = a.d.feat_nb[f];
+    const float fw = a.d.feat_weight ? a.d.feat_weight[f] : 1.0f;
+    const int bpl = (nb + 31) >> 5;
+    const bool onehot = a.d.feat_onehot && a.d.feat_onehot[f];
     unsigned long long best = 0ull;
     if (fw > 0.0f) {
         const int ncand = onehot ? nb : nb - 1;
@@ -556,12 +563,51 @@ static __device__ void cb_score_feature(const CbScoreArgs& a, int f, float noise
     if (lane == 0 && best) atomicMax(a.best_key, best);
 }
 
-static __device__ void cb_score_phase(const CbScoreArgs& a, int cta, int ncta) {
+// `red` is scratch shared memory of `red_floats` floats (the histogram tile is no longer needed at this point).
+// With fewer features than blocks a whole block scores one feature: its warps split the leaves and their partial
+// terms are summed through `red`, so the per-feature chain of dependent loads is L / warps long instead of L.
+static __device__ void cb_score_phase(const CbScoreArgs& a, int cta, int ncta, float* red, int red_floats) {
     const int warps_per_cta = blockDim.x >> 5;
-    const int warp = threadIdx.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float noise_std = cb_noise_std(a);
+    const int nf = a.f_end - a.f_begin;
+    const int L = 1 << a.level;
+    int wpf = min(min(warps_per_cta, L), red_floats / 512);
+    float num[8], den[8];
+    if (nf > 0 && ncta >= nf && wpf > 1) {
+        const int f = a.f_begin + cta;
+        const bool have = cta < nf;
+        if (have && warp < wpf) {
+            cb_score_accumulate(a, f, warp, wpf, num, den);
+            const int bpl = (a.d.feat_nb[f] + 31) >> 5;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (k < bpl) {
+                    red[(warp * 2) * 256 + lane * bpl + k] = num[k];
+                    red[(warp * 2 + 1) * 256 + lane * bpl + k] = den[k];
+                }
+            }
+        }
+        __syncthreads();
+        if (have && warp == 0) {
+            const int bpl = (a.d.feat_nb[f] + 31) >> 5;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                num[k] = 0.0f; den[k] = 0.0f;
+                if (k < bpl) {
+                    for (int w = 0; w < wpf; ++w) {
+                        num[k] += red[(w * 2) * 256 + lane * bpl + k];
+                        den[k] += red[(w * 2 + 1) * 256 + lane * bpl + k];
+                    }
+                }
+            }
+            cb_score_finalize(a, f, num, den, noise_std);
+        }
+        return;
+    }
     for (int f = a.f_begin + cta * warps_per_cta + warp; f < a.f_end; f += ncta * warps_per_cta) {
-        cb_score_feature(a, f, noise_std);
+        cb_score_accumulate(a, f, 0, 1, num, den);
+        cb_score_finalize(a, f, num, den, noise_std);
     }
 }
 
