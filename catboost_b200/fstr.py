@@ -187,8 +187,11 @@ def _tree_shap_row(m, ns, cover, outcomes_col, phi, split_feat):
         c = cover[node]
         if c <= 0:
             return
-        recurse(hot, path, iz * cover[hot] / c, io, f)
-        recurse(cold, path, iz * cover[cold] / c, 0.0, f)
+        # a branch no training row reached carries no weight: skip it when it is the cold one, and give the hot one a
+        # vanishing (but non-zero) fraction so that the path algebra stays finite
+        recurse(hot, path, iz * max(cover[hot] / c, 1e-9), io, f)
+        if cover[cold] > 0:
+            recurse(cold, path, iz * cover[cold] / c, 0.0, f)
 
     recurse(0, [], 1.0, 1.0, -1)
 

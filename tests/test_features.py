@@ -1,0 +1,212 @@
+"""Categorical / CTR features, ranking, model IO, importances, CV, CLI, snapshots (CPU)."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import catboost_b200 as cb
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = "/root/reference"
+
+
+def _cat_data(n=6000, seed=0):
+    rng = np.random.default_rng(seed)
+    c1, c2 = rng.integers(0, 40, n), rng.integers(0, 150, n)
+    x = rng.standard_normal(n).astype(np.float32)
+    e1, e2 = rng.standard_normal(40), rng.standard_normal(150)
+    y = (e1[c1] + 0.7 * e2[c2] + 0.5 * x + 0.5 * rng.standard_normal(n) > 0).astype(int)
+    data = np.empty((n, 3), dtype=object)
+    data[:, 0], data[:, 1], data[:, 2] = x, c1, np.array([f"v{k}" for k in c2])
+    return data, y
+
+
+def test_ctr_training_and_model_roundtrip(tmp_path):
+    data, y = _cat_data()
+    m = cb.CatBoostClassifier(iterations=40, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False,
+                              max_ctr_complexity=2)
+    m.fit(data[:4500], y[:4500], cat_features=[1, 2], eval_set=(data[4500:], y[4500:]))
+    assert (m.predict(data[4500:]) == y[4500:]).mean() > 0.8
+    assert len(m._model.ctrs) > 0
+    raw = m.predict(data[4500:], prediction_type="RawFormulaVal")
+    for fmt in ("cbm", "json"):
+        f = str(tmp_path / f"m.{fmt}")
+        m.save_model(f, format=fmt)
+        m2 = cb.CatBoostClassifier().load_model(f, format=fmt)
+        assert np.allclose(m2.predict(data[4500:], prediction_type="RawFormulaVal"), raw, atol=1e-9)
+        assert list(m2.classes_) == [0, 1]
+
+
+def test_ordered_ctr_matches_plain_python_oracle():
+    """Ordered target statistic of one categorical column against a sequential re-implementation."""
+    import torch
+    from catboost_b200.train.ctr import _ordered_stats
+    rng = np.random.default_rng(1)
+    n = 500
+    keys = rng.integers(0, 13, n)
+    order = rng.permutation(n)
+    good = (rng.random(n) < 0.3).astype(np.float32)
+    got = _ordered_stats(torch.from_numpy(keys), torch.from_numpy(order),
+                         torch.stack([torch.ones(n), torch.from_numpy(good)])).numpy()
+    cnt, pos = {}, {}
+    exp = np.zeros((2, n))
+    for i in order:
+        k = keys[i]
+        exp[0, i], exp[1, i] = cnt.get(k, 0), pos.get(k, 0)
+        cnt[k] = cnt.get(k, 0) + 1
+        pos[k] = pos.get(k, 0) + good[i]
+    assert np.allclose(got, exp)
+
+
+def test_cat_hash_known_values():
+    """Hashes stored in the CTR tables of a model produced by the reference must be reproduced from the raw strings."""
+    path = os.path.join(REF, "catboost/pytest/data/models/features_num_cat__dataset_adult.cbm")
+    adult = os.path.join(REF, "catboost/pytest/data/adult")
+    if not os.path.exists(path):
+        pytest.skip("reference model files are not available")
+    from catboost_b200.models.ctr import projection_hash
+    m = cb.CatBoost().load_model(path)
+    pool = cb.Pool(os.path.join(adult, "train_small"), column_description=os.path.join(adult, "train.cd"))
+    fd, ch = m._model.pool_arrays(pool)
+    checked = 0
+    for ctr in m._model.ctrs:
+        if len(ctr.cat_features) != 1 or len(ctr.hashes) == 0:
+            continue
+        ours = set(np.unique(projection_hash([ch[ctr.cat_features[0]]])).tolist())
+        stored = set(int(h) for h in ctr.hashes)
+        assert len(ours & stored) >= 0.9 * len(ours), (ctr.cat_features, len(ours & stored), len(ours))
+        checked += 1
+    assert checked >= 5
+
+
+def test_reference_models_load_and_predict():
+    iris = os.path.join(REF, "catboost/dotnet/CatBoostNetTests/testbed/iris")
+    if not os.path.exists(iris):
+        pytest.skip("reference model files are not available")
+    rows = [l.strip().split(",") for l in open(os.path.join(iris, "iris.data")) if l.strip()]
+    X = np.array([[float(v) for v in r[:4]] for r in rows], dtype=np.float32)
+    names = sorted({r[4] for r in rows})
+    yi = np.array([names.index(r[4]) for r in rows])
+    m = cb.CatBoostClassifier().load_model(os.path.join(iris, "iris_model.cbm"))
+    assert (np.asarray(m.predict(X)).astype(int) == yi).mean() > 0.97
+    adult = os.path.join(REF, "catboost/pytest/data/adult")
+    m = cb.CatBoostRegressor().load_model(os.path.join(REF, "catboost/pytest/data/models/features_num_cat__dataset_adult.cbm"))
+    pool = cb.Pool(os.path.join(adult, "train_small"), column_description=os.path.join(adult, "train.cd"))
+    pred = m.predict(pool)
+    lab = np.asarray(pool.label, dtype=float)
+    assert np.sqrt(np.mean((pred - lab) ** 2)) < 0.2          # the model was fitted on these rows (CTR tables included)
+
+
+def test_ranking_losses():
+    rng = np.random.default_rng(0)
+    sizes = rng.integers(5, 30, 150)
+    gid = np.repeat(np.arange(150), sizes)
+    n = len(gid)
+    X = rng.standard_normal((n, 8)).astype(np.float32)
+    score = X @ rng.standard_normal(8) + 0.5 * rng.standard_normal(n)
+    rel = np.digitize(score, np.quantile(score, [0.5, 0.8, 0.95])).astype(np.float32)
+    for loss in ("YetiRank", "QueryRMSE", "PairLogit", "LambdaMart"):
+        m = cb.CatBoostRanker(loss_function=loss, iterations=25, depth=4, learning_rate=0.3, verbose=False,
+                              allow_writing_files=False, eval_metric="NDCG")
+        m.fit(X, rel, group_id=gid)
+        ev = m.get_evals_result()["learn"]["NDCG"]
+        assert ev[-1] > ev[0] and ev[-1] > 0.9, (loss, ev[0], ev[-1])
+    with pytest.raises(cb.CatBoostError):
+        cb.CatBoostRanker(loss_function="YetiRank", iterations=2, verbose=False, allow_writing_files=False).fit(X, rel)
+
+
+def test_importances_and_shap_sum_to_prediction():
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((1500, 5)).astype(np.float32)
+    y = 3 * X[:, 0] + X[:, 1] * X[:, 2] + 0.1 * rng.standard_normal(1500)
+    m = cb.CatBoostRegressor(iterations=30, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False)
+    m.fit(X, y)
+    imp = m.get_feature_importance()
+    assert abs(imp.sum() - 100) < 1e-6 and imp.argmax() == 0 and imp[4] < 5
+    pool = cb.Pool(X[:40], y[:40])
+    sv = m.get_feature_importance(pool, type="ShapValues")
+    assert sv.shape == (40, 6)
+    assert np.allclose(sv.sum(1), m.predict(X[:40]), atol=1e-6)
+    lfc = m.get_feature_importance(cb.Pool(X[:300], y[:300]), type="LossFunctionChange")
+    assert lfc.argmax() == 0
+    inter = m.get_feature_importance(type="Interaction")
+    assert len(inter) > 0
+
+
+def test_cv_and_grid_search():
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((1200, 5)).astype(np.float32)
+    y = (X[:, 0] + X[:, 1] > 0).astype(int)
+    res = cb.cv(cb.Pool(X, y), dict(loss_function="Logloss", iterations=15, depth=3, learning_rate=0.3), fold_count=3,
+                as_pandas=False)
+    assert len(res["test-Logloss-mean"]) == 15 and res["test-Logloss-mean"][-1] < res["test-Logloss-mean"][0]
+    m = cb.CatBoostClassifier(iterations=10, verbose=False, allow_writing_files=False)
+    out = m.grid_search({"depth": [2, 4], "learning_rate": [0.1, 0.5]}, X, y, verbose=False)
+    assert set(out["params"]) == {"depth", "learning_rate"} and m.is_fitted()
+
+
+def test_snapshot_resume_equals_uninterrupted(tmp_path):
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((1500, 6)).astype(np.float32)
+    y = (X[:, 0] * X[:, 1] > 0).astype(int)
+    common = dict(depth=4, learning_rate=0.3, verbose=False, random_seed=3, bootstrap_type="No", random_strength=0,
+                  train_dir=str(tmp_path), allow_writing_files=True)
+    full = cb.CatBoostClassifier(iterations=20, **common).fit(X, y)
+    part = cb.CatBoostClassifier(iterations=8, save_snapshot=True, snapshot_file="s.snap", **common).fit(X, y)
+    assert part.tree_count_ == 8
+    resumed = cb.CatBoostClassifier(iterations=20, save_snapshot=True, snapshot_file="s.snap", **common).fit(X, y)
+    assert resumed.tree_count_ == 20
+    assert np.allclose(resumed.predict(X, prediction_type="RawFormulaVal"),
+                       full.predict(X, prediction_type="RawFormulaVal"), atol=1e-9)
+    # a corrupted snapshot is detected
+    p = tmp_path / "s.snap"
+    blob = bytearray(p.read_bytes())
+    blob[-5] ^= 0xFF
+    p.write_bytes(bytes(blob))
+    with pytest.raises(cb.CatBoostError):
+        cb.CatBoostClassifier(iterations=22, save_snapshot=True, snapshot_file="s.snap", **common).fit(X, y)
+
+
+def test_cli_fit_calc(tmp_path):
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((400, 4))
+    y = (X[:, 0] > 0).astype(int)
+    train = tmp_path / "train.tsv"
+    with open(train, "w") as fh:
+        for i in range(400):
+            fh.write("\t".join([str(y[i])] + [f"{v:.6f}" for v in X[i]]) + "\n")
+    cd = tmp_path / "train.cd"
+    cd.write_text("0\tLabel\n")
+    model = tmp_path / "model.bin"
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "catboost_b200", "fit", "-f", str(train), "--cd", str(cd), "-m", str(model),
+                        "--loss-function", "Logloss", "-i", "10", "--verbose", "0", "--train-dir", str(tmp_path / "info")],
+                       capture_output=True, text=True, env=env, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stderr
+    out = tmp_path / "pred.tsv"
+    r = subprocess.run([sys.executable, "-m", "catboost_b200", "calc", "-m", str(model), "--input-path", str(train),
+                        "--cd", str(cd), "-o", str(out), "--prediction-type", "Probability"],
+                       capture_output=True, text=True, env=env, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stderr
+    lines = out.read_text().strip().split("\n")
+    assert len(lines) == 401
+
+
+def test_sum_models_and_metrics():
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((800, 4)).astype(np.float32)
+    y = X[:, 0] + 0.1 * rng.standard_normal(800)
+    a = cb.CatBoostRegressor(iterations=5, depth=3, verbose=False, allow_writing_files=False, random_seed=1).fit(X, y)
+    b = cb.CatBoostRegressor(iterations=7, depth=3, verbose=False, allow_writing_files=False, random_seed=2).fit(X, y)
+    s = cb.sum_models([a, b], weights=[0.5, 0.5])
+    assert np.allclose(s.predict(X), 0.5 * a.predict(X) + 0.5 * b.predict(X), atol=1e-9)
+    ev = a.eval_metrics(cb.Pool(X, y), ["RMSE", "R2", "MAE"])
+    assert len(ev["RMSE"]) == 5 and ev["RMSE"][-1] <= ev["RMSE"][0]
+    from catboost_b200.metrics import make_metric
+    yb = (y > 0).astype(float)
+    assert abs(make_metric("AUC").eval(y.reshape(-1, 1), yb) - 1.0) < 1e-12
+    assert make_metric("NDCG:top=3").eval(np.array([[3.0], [2.0], [1.0]]), np.array([2.0, 1.0, 0.0]),
+                                          group_offsets=np.array([0, 3])) == pytest.approx(1.0)
