@@ -132,6 +132,7 @@ def main():
     ap.add_argument("--reduce", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--phases", action="store_true", help="print per-phase times of the fused level kernel")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -185,6 +186,8 @@ def main():
                              bootstrap_param=float(o.bagging_temperature or 1.0), leaf_method=o.leaf_estimation_method,
                              leaf_iterations=int(o.leaf_estimation_iterations), seed=0, ctx=ctx, reduce=args.reduce)
     flush = None if args.no_flush else torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    if args.phases and eng.plan:
+        eng.enable_phase_timing()
     eng.step(W)
     torch.cuda.synchronize(dev)
     ctx.barrier()
@@ -209,6 +212,9 @@ def main():
     total_ms = float(t.item())
     launches = eng.launches_per_iter * K
     loss_curve = eng.learn_loss_history()
+    if args.phases and eng.plan and rank == 0:
+        np.set_printoptions(precision=1, suppress=True, linewidth=160)
+        print('phase us per level [leaf_update, hist, grid_wait, reduce_push, score, select]:\n', eng.phase_times_us(), file=sys.stderr)
     eng.finish()
     if eng.arena is not None:
         eng.arena.check_status()

@@ -34,6 +34,7 @@ struct CbFusedArgs {
     int own_col[CB_MAX_RANKS + 1];   // rank r owns histogram columns [own_col[r], own_col[r+1]) (multiples of 4)
     int Wmax;                        // row stride (floats) of every slot buffer = max owned width
     int smem_floats;                 // dynamic shared memory of this launch, in floats
+    unsigned long long* phase_ts;    // optional [depth][8] globaltimer stamps written by block 0 (phase profiling)
 };
 
 // Sum of the per-chunk private tiles of this rank, written to the owner's slot.  One thread = one 16-byte column
@@ -78,6 +79,8 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
     const int level = a.h.level;
     const int it = *a.s.iter_ptr;
     CbSplit* sp_arr = a.splits + (long long)it * a.depth;
+    unsigned long long* ts = (a.phase_ts && cta == 0 && threadIdx.x == 0) ? a.phase_ts + level * 8 : nullptr;
+    if (ts) ts[0] = cb_globaltimer();
 
     // (0) leaf update with the split of the previous level
     if (level > 0) {
@@ -87,10 +90,13 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
         grid.sync();
     }
 
+    if (ts) ts[1] = cb_globaltimer();
     // (A) local histograms: every block dumps its shared-memory tile into its private region (no atomics)
     cb_hist_phase(a.h, cb_sh, cta, ncta);
+    if (ts) ts[2] = cb_globaltimer();
     __threadfence();
     grid.sync();
+    if (ts) ts[3] = cb_globaltimer();
 
     // (B) chunk reduction fused with the reduce-scatter: each 16-byte column group is summed over the chunks of
     // this rank and stored straight into the slot of the rank that owns the column (peer store over NVLink when
@@ -112,9 +118,11 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
         grid.sync();
     }
 
+    if (ts) ts[4] = cb_globaltimer();
     cb_score_phase(a.s, cta, ncta, cb_sh, a.smem_floats);
     __threadfence();
     grid.sync();
+    if (ts) ts[5] = cb_globaltimer();
 
     // (D) selection: one block
     if (cta == 0) {
@@ -134,6 +142,7 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
         if (threadIdx.x == 0) {
             *a.s.best_key = 0ull;
             if (R > 1) a.c.epoch[1] = a.c.epoch[1] + 1;
+            if (ts) ts[6] = cb_globaltimer();
         }
     }
 }
@@ -155,7 +164,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     CbFusedPlan* p = new (std::nothrow) CbFusedPlan();
     if (!p) return nullptr;
     CbFusedArgs& a = p->a;
-    a.h.d = *d; a.h.leaf = leaf; a.h.stats = stats; a.h.S = S; a.h.B = B; a.h.out = nullptr; a.h.priv = partial; a.h.statmax = nullptr;
+    a.h.d = *d; a.h.leaf = leaf; a.h.stats = stats; a.h.S = S; a.h.B = B; a.h.out = nullptr; a.h.priv = partial; a.h.statmax = nullptr; a.phase_ts = nullptr;
     a.h.slot_table = nullptr; a.h.nslots_table = 0; a.h.level = 0; a.h.small_mask = mask0; a.h.slots_per_pass = 1;
     a.s.d = *d;
     if (comm) a.c = *comm; else { a.c = CbComm(); a.c.nranks = 1; a.c.rank = 0; }
@@ -192,6 +201,8 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     }
     return p;
 }
+
+CB_API void cb_fused_set_phase_ts(CbFusedPlan* p, unsigned long long* ts) { p->a.phase_ts = ts; }
 
 CB_API void cb_fused_set_features(CbFusedPlan* p, int f_begin, int f_end) {
     p->a.s.f_begin = f_begin;

@@ -290,17 +290,34 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
     const float sc1 = 8388607.0f / fmaxf(a.statmax[1], 1e-30f);
     const unsigned int lt = (1u << lane) - 1u;
     unsigned int head = 0, tail = 0;
-    for (long long ib = d_begin + (long long)(threadIdx.x & ~31) * 4; ib < d_end; ib += (long long)blockDim.x * 4) {
+    // Software pipeline: the four loads of the next step are issued before the atomics of the current one, so the
+    // DRAM latency of a step overlaps the shared-memory work of the previous step.
+    const long long step = (long long)blockDim.x * 4;
+    const long long ib0 = d_begin + (long long)(threadIdx.x & ~31) * 4;
+    uint4 nw = make_uint4(0, 0, 0, 0);
+    ushort4 nlf = make_ushort4(0, 0, 0, 0);
+    float4 ns0 = make_float4(0, 0, 0, 0), ns1 = make_float4(0, 0, 0, 0);
+    if (ib0 + lane * 4 < d_end) {
+        const long long i = ib0 + lane * 4;
+        nw = *reinterpret_cast<const uint4*>(bg + i);
+        nlf = *reinterpret_cast<const ushort4*>(a.leaf + i);
+        ns0 = *reinterpret_cast<const float4*>(st0 + i);
+        ns1 = *reinterpret_cast<const float4*>(st1 + i);
+    }
+    for (long long ib = ib0; ib < d_end; ib += step) {
         const long long i = ib + lane * 4;
-        uint4 w = make_uint4(0, 0, 0, 0);
-        ushort4 lf = make_ushort4(0, 0, 0, 0);
-        float4 s0 = make_float4(0, 0, 0, 0), s1 = make_float4(0, 0, 0, 0);
+        const uint4 w = nw;
+        const ushort4 lf = nlf;
+        const float4 s0 = ns0, s1 = ns1;
         const bool valid = i < d_end;
-        if (valid) {
-            w = *reinterpret_cast<const uint4*>(bg + i);
-            lf = *reinterpret_cast<const ushort4*>(a.leaf + i);
-            s0 = *reinterpret_cast<const float4*>(st0 + i);
-            s1 = *reinterpret_cast<const float4*>(st1 + i);
+        {
+            const long long in = i + step;
+            if (in < d_end) {
+                nw = *reinterpret_cast<const uint4*>(bg + in);
+                nlf = *reinterpret_cast<const ushort4*>(a.leaf + in);
+                ns0 = *reinterpret_cast<const float4*>(st0 + in);
+                ns1 = *reinterpret_cast<const float4*>(st1 + in);
+            }
         }
         const unsigned int wv[4] = {w.x, w.y, w.z, w.w};
         const unsigned int lv[4] = {lf.x, lf.y, lf.z, lf.w};

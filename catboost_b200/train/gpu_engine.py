@@ -201,6 +201,16 @@ class GpuObliviousEngine:
         self.lib.cb_fused_set_priv(ctypes.c_void_p(self.plan), _p(self.priv),
                                    _p(self.statmax) if self.quantized_hist else None)
 
+    def enable_phase_timing(self):
+        """Record globaltimer stamps of the fused kernel's phases (block 0) for every level of the latest tree."""
+        self.phase_ts = torch.zeros((self.depth, 8), dtype=torch.int64, device=self.dev)
+        self.lib.cb_fused_set_phase_ts(ctypes.c_void_p(self.plan), _p(self.phase_ts))
+
+    def phase_times_us(self):
+        """[depth][6] microseconds: leaf update, histogram, wait for grid, reduce+push(+peer wait), score, select."""
+        t = self.phase_ts.cpu().numpy().astype(np.float64)
+        return (t[:, 1:7] - t[:, 0:6]) / 1000.0
+
     def _stream(self):
         return ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
 
