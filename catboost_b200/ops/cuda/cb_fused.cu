@@ -42,7 +42,7 @@ struct CbFusedArgs {
 static __device__ void cb_reduce_chunks(const CbFusedArgs& a, int cta, int ncta) {
     const CbHistArgs& h = a.h;
     const int G = h.d.G, S = h.S, B = h.B, TB = h.d.TB;
-    const int nK = cb_hist_chunks(G, ncta, h.d.n);
+    const int nK = cb_hist_chunks(G, ncta, h.d.n, h.nK);
     const int nslots = cb_hist_nslots(h);
     const size_t slot_stride = (size_t)S * 4 * B;
     const size_t item_stride = (size_t)nslots * slot_stride;
@@ -164,7 +164,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     CbFusedPlan* p = new (std::nothrow) CbFusedPlan();
     if (!p) return nullptr;
     CbFusedArgs& a = p->a;
-    a.h.d = *d; a.h.leaf = leaf; a.h.stats = stats; a.h.S = S; a.h.B = B; a.h.out = nullptr; a.h.priv = partial; a.h.statmax = nullptr; a.phase_ts = nullptr;
+    a.h.d = *d; a.h.leaf = leaf; a.h.stats = stats; a.h.S = S; a.h.B = B; a.h.out = nullptr; a.h.priv = partial; a.h.statmax = nullptr; a.phase_ts = nullptr; a.h.nK = 0; a.h.copies = 1;
     a.h.slot_table = nullptr; a.h.nslots_table = 0; a.h.level = 0; a.h.small_mask = mask0; a.h.slots_per_pass = 1;
     a.s.d = *d;
     if (comm) a.c = *comm; else { a.c = CbComm(); a.c.nranks = 1; a.c.rank = 0; }
@@ -212,7 +212,10 @@ CB_API void cb_fused_set_features(CbFusedPlan* p, int f_begin, int f_end) {
 CB_API void cb_fused_destroy(CbFusedPlan* p) { delete p; }
 
 // Launch geometry of one level: returns the cooperative grid size (0 on error) and the slots per pass.
-CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int* smem_bytes, int* threads) {
+// Launch geometry of one level.  Returns the cooperative grid size (0 on error) and, through the pointers, the
+// slots per pass, dynamic shared memory, block size, document chunks per group and cell replicas.
+CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int* smem_bytes, int* threads, int* chunks,
+                             int* copies) {
     const int nslots = level == 0 ? 1 : (1 << (level - 1));
     const int per_slot = p->a.h.S * 4 * p->a.h.B * 4 * (p->a.h.statmax ? 2 : 1);
     const bool ring = p->a.h.statmax && p->a.h.S == 2;      // per-warp compaction rings (16 bytes x 64 entries)
@@ -228,23 +231,47 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
     }
     if (spp * per_slot > budget) spp = budget / per_slot;
     if (spp < 1) return 0;
-    const int smem = spp * per_slot + ring_bytes;
+    // replicate the cells while two blocks per SM still fit (fewer bank / address collisions per atomic)
+    int C = 1;
+    if (ring && thr == p->threads) {
+        while (C < 8 && 2 * (spp * per_slot * (C * 2) + ring_bytes) <= p->max_smem) C *= 2;
+    }
+    const int smem = spp * per_slot * C + ring_bytes;
     int occ = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, cb_level_fused_kernel, thr, smem) != cudaSuccess) { cudaGetLastError(); return 0; }
     if (occ < 1) return 0;
     if (occ > 4) occ = 4;
+    const int grid = occ * p->sm_count;
+    // document chunks per group: at least what the grid offers and what the 2^19-documents-per-tile cap needs;
+    // among a few candidates take the one that fills the last round of blocks best
+    const int G = p->a.h.d.G;
+    const long long n = p->a.h.d.n;
+    const int by_grid = grid >= G ? grid / G : 1;
+    const int by_docs = (int)((n + (1 << 19) - 1) >> 19);
+    const int lo = by_grid > by_docs ? by_grid : by_docs;
+    int best = lo;
+    double best_eff = 0.0;
+    for (int k = lo; k < lo + 8; ++k) {
+        const long long items = (long long)G * k;
+        const long long rounds = (items + grid - 1) / grid;
+        const double eff = (double)items / (double)(rounds * grid);
+        if (eff > best_eff + 0.02) { best_eff = eff; best = k; }
+    }
     *slots_per_pass = spp;
     *smem_bytes = smem;
     *threads = thr;
-    return occ * p->sm_count;
+    *chunks = best;
+    *copies = C;
+    return grid;
 }
 
 CB_API void cb_fused_set_priv(CbFusedPlan* p, float* priv, const float* statmax) { p->a.h.priv = priv; p->a.h.statmax = statmax; }
 
 CB_API int cb_fused_launch(CbFusedPlan* p, int level, float* hprev, float* hcur, const unsigned int* mask_in,
                            unsigned int* mask_out, int grid, int slots_per_pass, int smem_bytes, int threads,
-                           cudaStream_t st) {
+                           int chunks, int copies, cudaStream_t st) {
     CbFusedArgs a = p->a;
+    a.h.nK = chunks; a.h.copies = copies;
     a.h.level = level; a.h.small_mask = mask_in; a.h.slots_per_pass = slots_per_pass;
     a.s.level = level; a.s.small_mask = mask_in; a.s.hprev = hprev; a.s.hcur = hcur;
     a.mask_out = mask_out;

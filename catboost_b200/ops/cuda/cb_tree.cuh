@@ -57,6 +57,8 @@ struct CbHistArgs {
     // measured 2x slower for twice fewer operations.  The sum is exact in integers (better than fp32 accumulation)
     // as long as a block sees at most 2^19 documents per tile, which cb_hist_chunks guarantees.
     const float* statmax;
+    int nK;        // document chunks per feature group chosen by the host (0 = derive from the grid)
+    int copies;    // power of two <= 8: replicas of every fixed-point cell, lane l uses replica l & (copies-1)
 };
 
 __device__ __forceinline__ int cb_hist_nslots(const CbHistArgs& a) {
@@ -256,25 +258,29 @@ static __device__ void cb_hist_item_q(const CbHistArgs& a, int* sh, int g, long 
 // entries at a time, so every atomic instruction runs with all lanes busy.
 // sh layout: int hist[slot][2][part][j][B], then uint4 ring[warps][64].
 #define CB_RING 64
-__device__ __forceinline__ void cb_hist_q_apply(int* sh, int B, uint4 e) {
-    int* base = sh + (int)e.y;
+__device__ __forceinline__ void cb_hist_q_apply(int* sh, int B, int C, int copy, uint4 e) {
+    int* base = sh + (int)e.y + copy;
     const int q0 = (int)e.z, q1 = (int)e.w;
     const int h0 = q0 >> 12, h1 = q1 >> 12;
     const unsigned int l0 = (unsigned int)q0 & 4095u, l1 = (unsigned int)q1 & 4095u;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const unsigned int bin = (e.x >> (8 * j)) & 255u;
-        atomicAdd(base + j * B + bin, h0);
-        atomicAdd(reinterpret_cast<unsigned int*>(base) + (4 + j) * B + bin, l0);
-        atomicAdd(base + (8 + j) * B + bin, h1);
-        atomicAdd(reinterpret_cast<unsigned int*>(base) + (12 + j) * B + bin, l1);
+        atomicAdd(base + (j * B + bin) * C, h0);
+        atomicAdd(reinterpret_cast<unsigned int*>(base) + ((4 + j) * B + bin) * C, l0);
+        atomicAdd(base + ((8 + j) * B + bin) * C, h1);
+        atomicAdd(reinterpret_cast<unsigned int*>(base) + ((12 + j) * B + bin) * C, l1);
     }
 }
 
-static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long long item, long long d_begin,
-                                       long long d_end, int slot_begin, int slot_count) {
+// Documents are dealt to the chunks of a group block-cyclically (block = blockDim.x * 4 documents): chunk k takes
+// blocks k, k + nK, k + 2 nK, ... so that every chunk sees the same mix of the data and the blocks finish together.
+static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long long item, int chunk, int nK,
+                                       int slot_begin, int slot_count) {
     const int B = a.B;
-    const int total = slot_count * 16 * B;
+    const int C = a.copies > 0 ? a.copies : 1;
+    const int total = slot_count * 16 * B * C;
+    const long long d_end = a.d.n;
     for (int i = threadIdx.x; i < total; i += blockDim.x) sh[i] = 0;
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -285,15 +291,17 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
     const int level = a.level;
     const int nslots = cb_hist_nslots(a);
     const unsigned int pmask = (unsigned int)(nslots - 1);
-    const int slot_stride = 16 * B;
+    const int slot_stride = 16 * B * C;
+    const int copy = lane & (C - 1);
     const float sc0 = 8388607.0f / fmaxf(a.statmax[0], 1e-30f);
     const float sc1 = 8388607.0f / fmaxf(a.statmax[1], 1e-30f);
     const unsigned int lt = (1u << lane) - 1u;
     unsigned int head = 0, tail = 0;
     // Software pipeline: the four loads of the next step are issued before the atomics of the current one, so the
     // DRAM latency of a step overlaps the shared-memory work of the previous step.
-    const long long step = (long long)blockDim.x * 4;
-    const long long ib0 = d_begin + (long long)(threadIdx.x & ~31) * 4;
+    const long long blk = (long long)blockDim.x * 4;
+    const long long step = blk * nK;
+    const long long ib0 = blk * chunk + (long long)(threadIdx.x & ~31) * 4;
     uint4 nw = make_uint4(0, 0, 0, 0);
     ushort4 nlf = make_ushort4(0, 0, 0, 0);
     float4 ns0 = make_float4(0, 0, 0, 0), ns1 = make_float4(0, 0, 0, 0);
@@ -348,13 +356,13 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
             tail += __popc(m);
             __syncwarp();
             if (tail - head >= 32u) {
-                cb_hist_q_apply(sh, B, ring[(head + lane) & (CB_RING - 1)]);
+                cb_hist_q_apply(sh, B, C, copy, ring[(head + lane) & (CB_RING - 1)]);
                 head += 32u;
                 __syncwarp();
             }
         }
     }
-    if ((unsigned int)lane < tail - head) cb_hist_q_apply(sh, B, ring[(head + lane) & (CB_RING - 1)]);
+    if ((unsigned int)lane < tail - head) cb_hist_q_apply(sh, B, C, copy, ring[(head + lane) & (CB_RING - 1)]);
     __syncthreads();
     // dump as floats into the private region [item][slot][s][j][B]
     const int cells4 = (slot_count * 8 * B) >> 2;
@@ -368,20 +376,26 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
         const int j = r & 3;
         const int ss = r >> 2;           // slot * 2 + s
         const float inv = (ss & 1) ? inv1 : inv0;
-        const int4 hi = *reinterpret_cast<const int4*>(sh + (size_t)ss * 8 * B + j * B + b4 * 4);
-        const uint4 lo = *reinterpret_cast<const uint4*>(sh + (size_t)ss * 8 * B + (4 + j) * B + b4 * 4);
+        int hi[4] = {0, 0, 0, 0};
+        unsigned int lo[4] = {0u, 0u, 0u, 0u};
+        const int* ph = sh + ((size_t)ss * 8 * B + j * B + b4 * 4) * C;
+        const int* pl = sh + ((size_t)ss * 8 * B + (4 + j) * B + b4 * 4) * C;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            for (int cc = 0; cc < C; ++cc) { hi[q] += ph[q * C + cc]; lo[q] += (unsigned int)pl[q * C + cc]; }
         float4 v;
-        v.x = fmaf((float)hi.x, 4096.0f * inv, (float)lo.x * inv);
-        v.y = fmaf((float)hi.y, 4096.0f * inv, (float)lo.y * inv);
-        v.z = fmaf((float)hi.z, 4096.0f * inv, (float)lo.z * inv);
-        v.w = fmaf((float)hi.w, 4096.0f * inv, (float)lo.w * inv);
+        v.x = fmaf((float)hi[0], 4096.0f * inv, (float)lo[0] * inv);
+        v.y = fmaf((float)hi[1], 4096.0f * inv, (float)lo[1] * inv);
+        v.z = fmaf((float)hi[2], 4096.0f * inv, (float)lo[2] * inv);
+        v.w = fmaf((float)hi[3], 4096.0f * inv, (float)lo[3] * inv);
         dst[c] = v;
     }
     __syncthreads();
 }
 
 #define CB_HIST_MAX_DOCS_PER_TILE (1 << 19)
-__device__ __forceinline__ int cb_hist_chunks(int G, int ncta, long long n) {
+__device__ __forceinline__ int cb_hist_chunks(int G, int ncta, long long n, int host_choice = 0) {
+    if (host_choice > 0) return host_choice;
     const int by_grid = (ncta >= G) ? (ncta / G) : 1;
     const int by_docs = (int)((n + CB_HIST_MAX_DOCS_PER_TILE - 1) / CB_HIST_MAX_DOCS_PER_TILE);
     return by_grid > by_docs ? by_grid : by_docs;
@@ -390,7 +404,7 @@ __device__ __forceinline__ int cb_hist_chunks(int G, int ncta, long long n) {
 // Static work split used by both launch styles: item -> (group, chunk).
 static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, int ncta) {
     const int G = a.d.G;
-    const int nK = cb_hist_chunks(G, ncta, a.d.n);
+    const int nK = cb_hist_chunks(G, ncta, a.d.n, a.nK);
     long long per = (a.d.n + nK - 1) / nK;
     per = (per + 3) & ~3ll;
     const int nslots = cb_hist_nslots(a);
@@ -402,7 +416,7 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
             const long long k = item / G;
             const long long b = k * per;
             const long long e = min(a.d.n, b + per);
-            if (a.statmax && a.S == 2) cb_hist_item_q2(a, reinterpret_cast<int*>(sh), g, item, min(b, e), e, sb, sc);
+            if (a.statmax && a.S == 2) cb_hist_item_q2(a, reinterpret_cast<int*>(sh), g, item, (int)k, nK, sb, sc);
             else if (a.statmax) cb_hist_item_q(a, reinterpret_cast<int*>(sh), g, item, min(b, e), e, sb, sc);
             else if (b < e || a.priv) cb_hist_item(a, sh, g, item, min(b, e), e, sb, sc);
         }
@@ -491,6 +505,51 @@ static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, 
             p = l & (half - 1);
             const unsigned int right = (unsigned int)l >> (a.level - 1);
             computed = (((a.small_mask[p >> 5] >> (p & 31)) & 1u) == right);
+        }
+        if (S == 2) {
+            // both statistic rows of the leaf are fetched before any dependent work (twice the loads in flight)
+            float xw[8], xs[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int bin = lane * bpl + k;
+                xw[k] = 0.0f; xs[k] = 0.0f;
+                if (k < bpl && bin < nb) {
+                    const size_t is = ((size_t)p * 2) * a.W + col0 + bin;
+                    const size_t iw = is + a.W;
+                    float s_ = 0.0f, w_ = 0.0f;
+                    for (int r = 0; r < a.nsrc; ++r) { s_ += a.hsrc[r][is]; w_ += a.hsrc[r][iw]; }
+                    if (!computed) { s_ = a.hprev[is] - s_; w_ = a.hprev[iw] - w_; }
+                    if (a.hcur) {
+                        a.hcur[((size_t)l * 2) * a.W + col0 + bin] = s_;
+                        a.hcur[((size_t)l * 2 + 1) * a.W + col0 + bin] = w_;
+                    }
+                    xs[k] = s_; xw[k] = w_;
+                }
+            }
+            float runw = 0.0f, runs = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                runw += xw[k]; runs += xs[k];
+                if (!onehot) { xw[k] = runw; xs[k] = runs; }
+            }
+            float incw = runw, incs = runs;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float tw = __shfl_up_sync(0xffffffffu, incw, o);
+                const float ts = __shfl_up_sync(0xffffffffu, incs, o);
+                if (lane >= o) { incw += tw; incs += ts; }
+            }
+            const float exw = onehot ? 0.0f : incw - runw, exs = onehot ? 0.0f : incs - runs;
+            const float totw = __shfl_sync(0xffffffffu, incw, 31), tots = __shfl_sync(0xffffffffu, incs, 31);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (k < bpl) {
+                    const float wlk = exw + xw[k], slk = exs + xs[k];
+                    cb_score_add_leaf(a.score_fn, a.l2, slk, fmaxf(wlk, 0.0f), num[k], den[k]);
+                    cb_score_add_leaf(a.score_fn, a.l2, tots - slk, fmaxf(totw - wlk, 0.0f), num[k], den[k]);
+                }
+            }
+            continue;
         }
         float wl[8];
         float wtot = 0.0f;
@@ -589,36 +648,45 @@ static __device__ void cb_score_phase(const CbScoreArgs& a, int cta, int ncta, f
     const float noise_std = cb_noise_std(a);
     const int nf = a.f_end - a.f_begin;
     const int L = 1 << a.level;
-    int wpf = min(min(warps_per_cta, L), red_floats / 512);
+    // warps per feature: as many as there are idle warps in the grid (power of two, at most one per leaf)
+    int wpf = 1;
+    while (wpf * 2 <= min(warps_per_cta, L) && (long long)nf * wpf * 2 <= (long long)ncta * warps_per_cta &&
+           warps_per_cta * 512 <= red_floats)
+        wpf *= 2;
     float num[8], den[8];
-    if (nf > 0 && ncta >= nf && wpf > 1) {
-        const int f = a.f_begin + cta;
-        const bool have = cta < nf;
-        if (have && warp < wpf) {
-            cb_score_accumulate(a, f, warp, wpf, num, den);
-            const int bpl = (a.d.feat_nb[f] + 31) >> 5;
+    if (nf > 0 && wpf > 1) {
+        const int fpc = warps_per_cta / wpf;            // features per block and round
+        const int slot = warp / wpf, sub = warp - slot * wpf;
+        for (int fbase = a.f_begin + cta * fpc; fbase < a.f_end; fbase += ncta * fpc) {
+            const int f = fbase + slot;
+            const bool have = f < a.f_end;
+            int bpl = 0;
+            if (have) {
+                cb_score_accumulate(a, f, sub, wpf, num, den);
+                bpl = (a.d.feat_nb[f] + 31) >> 5;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                if (k < bpl) {
-                    red[(warp * 2) * 256 + lane * bpl + k] = num[k];
-                    red[(warp * 2 + 1) * 256 + lane * bpl + k] = den[k];
-                }
-            }
-        }
-        __syncthreads();
-        if (have && warp == 0) {
-            const int bpl = (a.d.feat_nb[f] + 31) >> 5;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                num[k] = 0.0f; den[k] = 0.0f;
-                if (k < bpl) {
-                    for (int w = 0; w < wpf; ++w) {
-                        num[k] += red[(w * 2) * 256 + lane * bpl + k];
-                        den[k] += red[(w * 2 + 1) * 256 + lane * bpl + k];
+                for (int k = 0; k < 8; ++k) {
+                    if (k < bpl) {
+                        red[(warp * 2) * 256 + lane * bpl + k] = num[k];
+                        red[(warp * 2 + 1) * 256 + lane * bpl + k] = den[k];
                     }
                 }
             }
-            cb_score_finalize(a, f, num, den, noise_std);
+            __syncthreads();
+            if (have && sub == 0) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    num[k] = 0.0f; den[k] = 0.0f;
+                    if (k < bpl) {
+                        for (int w = warp; w < warp + wpf; ++w) {
+                            num[k] += red[(w * 2) * 256 + lane * bpl + k];
+                            den[k] += red[(w * 2 + 1) * 256 + lane * bpl + k];
+                        }
+                    }
+                }
+                cb_score_finalize(a, f, num, den, noise_std);
+            }
+            __syncthreads();
         }
         return;
     }

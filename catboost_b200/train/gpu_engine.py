@@ -183,20 +183,18 @@ class GpuObliviousEngine:
         self.lib.cb_fused_set_priv(ctypes.c_void_p(self.plan), None, _p(self.statmax) if self.quantized_hist else None)
         self.level_geo = []
         for level in range(self.depth):
-            spp, smem, thr = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+            spp, smem, thr, nk, cp = (ctypes.c_int(0) for _ in range(5))
             grid = self.lib.cb_fused_geometry(ctypes.c_void_p(self.plan), level, ctypes.byref(spp), ctypes.byref(smem),
-                                              ctypes.byref(thr))
+                                              ctypes.byref(thr), ctypes.byref(nk), ctypes.byref(cp))
             if grid <= 0:
                 raise RuntimeError(f"no cooperative launch geometry for level {level}")
-            self.level_geo.append((grid, spp.value, smem.value, thr.value))
+            self.level_geo.append((grid, spp.value, smem.value, thr.value, nk.value, cp.value))
         # private tiles: one region per (chunk, group) work item, sized for the largest level
         G = self.store.G
         need = 0
-        by_docs = (self.n + (1 << 19) - 1) >> 19
-        for level, (grid, _, _, _) in enumerate(self.level_geo):
+        for level, geo in enumerate(self.level_geo):
             nslots = 1 if level == 0 else 1 << (level - 1)
-            items = G * max(grid // G if grid >= G else 1, by_docs)
-            need = max(need, items * nslots * self.S * 4 * self.B)
+            need = max(need, G * geo[4] * nslots * self.S * 4 * self.B)
         self.priv = torch.empty(need, dtype=torch.float32, device=self.dev)
         self.lib.cb_fused_set_priv(ctypes.c_void_p(self.plan), _p(self.priv),
                                    _p(self.statmax) if self.quantized_hist else None)
@@ -225,12 +223,12 @@ class GpuObliviousEngine:
         self.launches_per_iter += 1
 
     def _level_fused(self, level: int):
-        grid, spp, smem, thr = self.level_geo[level]
+        grid, spp, smem, thr, nk, cp = self.level_geo[level]
         hprev, hcur = self.hbuf[(level + 1) & 1], self.hbuf[level & 1]
         hcur_ptr = _p(hcur) if level < self.depth - 1 else None
         native.cuda_check(self.lib.cb_fused_launch(ctypes.c_void_p(self.plan), level, _p(hprev), hcur_ptr,
                                                    _p(self.mask[level & 1]), _p(self.mask[(level + 1) & 1]), grid, spp,
-                                                   smem, thr, self._stream()), "cb_level_fused")
+                                                   smem, thr, nk, cp, self._stream()), "cb_level_fused")
         self.launches_per_iter += 1
 
     def _level_unfused(self, level: int):
