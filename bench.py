@@ -226,7 +226,9 @@ def main():
     e2e = None
     if not args.no_e2e:
         Xp = torch.from_numpy(X).pin_memory().numpy() if hasattr(torch.Tensor, "pin_memory") else X
-        model = cb.CatBoostClassifier(**params, verbose=True, metric_period=1)
+        e2e_iters = max(K + W, 100)
+        params_e2e = dict(params, iterations=e2e_iters)
+        model = cb.CatBoostClassifier(**params_e2e, verbose=True, metric_period=1)
         devnull = open(os.devnull, "w")
         torch.cuda.synchronize(dev)
         ctx.barrier()
@@ -237,11 +239,33 @@ def main():
         e2e_s = torch.tensor([t1 - t0], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
-        iters = K + W
+        iters = e2e_iters
         e2e = {"value": float(e2e_s.item()) / iters * 1000.0, "unit": "s/1000iter",
                "h2d_bytes_per_step": int(X.nbytes * world // iters), "d2h_bytes_per_step": 16,
                "fit_seconds": float(e2e_s.item()), "iterations": iters,
+               "fit_breakdown_s": {k: round(float(v), 4) for k, v in model._train_info.get("timings", {}).items()},
                "note": "whole fit(): pinned upload + quantisation + iterations with a per-iteration learn-loss read"}
+    apply_info = None
+    if not args.no_e2e and rank == 0:
+        # batch apply of the model just trained: device-resident rows, quantisation fused into the tree walk
+        from catboost_b200.models.gpu_apply import GpuPredictor
+        pred = GpuPredictor(model._model, dev)
+        rows = min(len(X), 4_000_000)
+        xd = torch.from_numpy(X[:rows]).to(dev)
+        out = torch.empty((model._model.dims, rows), dtype=torch.float32, device=dev)
+        for _ in range(2):
+            pred.predict_device(xd, out)
+        torch.cuda.synchronize(dev)
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        a0.record()
+        for _ in range(reps):
+            pred.predict_device(xd, out)
+        a1.record()
+        torch.cuda.synchronize(dev)
+        ms = a0.elapsed_time(a1) / reps
+        apply_info = {"rows_per_s": rows / (ms * 1e-3), "rows": rows, "trees": model.tree_count_, "ms": ms,
+                      "tree_rows_per_s": rows * model.tree_count_ / (ms * 1e-3), "n_gpus": 1}
     if rank == 0:
         ms_per_step = total_ms / K
         value = ms_per_step          # ms per iteration == seconds per 1000 iterations
@@ -255,7 +279,7 @@ def main():
                           "border_count": cfg["border_count"], "learning_rate": 0.1, "histogram_reduce": args.reduce,
                           "l2_policy": ("flush: 512 MiB write between timed iterations" if flush is not None
                                         else "inputs larger than L2")},
-               "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+               "clocks": clocks, "e2e": e2e, "apply": apply_info, "gpu_launches": launches,
                "learn_loss_first_last": [float(loss_curve[1]) if len(loss_curve) > 1 else None, float(loss_curve[-1])]}
         print(json.dumps(out))
     if world > 1:
