@@ -215,6 +215,11 @@ def main():
     if args.phases and eng.plan and rank == 0:
         np.set_printoptions(precision=1, suppress=True, linewidth=160)
         print('phase us per level [leaf_update, hist, grid_wait, reduce_push, score, select]:\n', eng.phase_times_us(), file=sys.stderr)
+        bt, sm = eng.block_finish_times()
+        order = np.argsort(bt)
+        print('hist end per block (us) pct 0/10/50/90/100:', np.percentile(bt, [0, 10, 50, 90, 100]), file=sys.stderr)
+        print('slowest blocks (block, sm, us):', [(int(b), int(sm[b]), float(bt[b])) for b in order[-8:]], file=sys.stderr)
+        print('fastest blocks (block, sm, us):', [(int(b), int(sm[b]), float(bt[b])) for b in order[:8]], file=sys.stderr)
     eng.finish()
     if eng.arena is not None:
         eng.arena.check_status()

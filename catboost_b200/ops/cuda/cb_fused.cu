@@ -94,6 +94,12 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
     // (A) local histograms: every block dumps its shared-memory tile into its private region (no atomics)
     cb_hist_phase(a.h, cb_sh, cta, ncta);
     if (ts) ts[2] = cb_globaltimer();
+    if (a.phase_ts && threadIdx.x == 0 && level == a.depth - 2) {
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        a.phase_ts[a.depth * 8 + cta * 2] = cb_globaltimer();
+        a.phase_ts[a.depth * 8 + cta * 2 + 1] = smid;
+    }
     __threadfence();
     grid.sync();
     if (ts) ts[3] = cb_globaltimer();
@@ -144,6 +150,9 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
             if (R > 1) a.c.epoch[1] = a.c.epoch[1] + 1;
             if (ts) ts[6] = cb_globaltimer();
         }
+        if (a.h.work) {
+            for (int i = threadIdx.x; i <= a.h.d.G; i += blockDim.x) a.h.work[i] = 0u;
+        }
     }
 }
 
@@ -164,7 +173,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     CbFusedPlan* p = new (std::nothrow) CbFusedPlan();
     if (!p) return nullptr;
     CbFusedArgs& a = p->a;
-    a.h.d = *d; a.h.leaf = leaf; a.h.stats = stats; a.h.S = S; a.h.B = B; a.h.out = nullptr; a.h.priv = partial; a.h.statmax = nullptr; a.phase_ts = nullptr; a.h.nK = 0; a.h.copies = 1;
+    a.h.d = *d; a.h.leaf = leaf; a.h.stats = stats; a.h.S = S; a.h.B = B; a.h.out = nullptr; a.h.priv = partial; a.h.statmax = nullptr; a.phase_ts = nullptr; a.h.nK = 0; a.h.copies = 1; a.h.work = nullptr;
     a.h.slot_table = nullptr; a.h.nslots_table = 0; a.h.level = 0; a.h.small_mask = mask0; a.h.slots_per_pass = 1;
     a.s.d = *d;
     if (comm) a.c = *comm; else { a.c = CbComm(); a.c.nranks = 1; a.c.rank = 0; }
@@ -203,6 +212,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
 }
 
 CB_API void cb_fused_set_phase_ts(CbFusedPlan* p, unsigned long long* ts) { p->a.phase_ts = ts; }
+CB_API void cb_fused_set_work(CbFusedPlan* p, unsigned int* work) { p->a.h.work = work; }
 
 CB_API void cb_fused_set_features(CbFusedPlan* p, int f_begin, int f_end) {
     p->a.s.f_begin = f_begin;

@@ -11,6 +11,9 @@
 #pragma once
 #include "cb_common.cuh"
 
+#define CB_HIST_MAX_DOCS_PER_TILE (1 << 19)
+#define CB_SUPER_STEPS 8        // a super-block = CB_SUPER_STEPS * blockDim.x * 4 documents
+
 enum CbScoreFn : int { CB_SCORE_COSINE = 0, CB_SCORE_L2 = 1, CB_SCORE_SOLAR = 2, CB_SCORE_LOO = 3, CB_SCORE_SAT = 4 };
 
 struct CbSplit {       // one record per (tree, level)
@@ -59,6 +62,10 @@ struct CbHistArgs {
     const float* statmax;
     int nK;        // document chunks per feature group chosen by the host (0 = derive from the grid)
     int copies;    // power of two <= 8: replicas of every fixed-point cell, lane l uses replica l & (copies-1)
+    // Dynamic work distribution (optional): work[g] hands out super-blocks of group g to the blocks that share the
+    // group, work[G] hands out whole (group, chunk) items when there are more items than blocks.  All zero on entry;
+    // the fused kernel clears them again after the level.  Evens out SMs that run at different speeds.
+    unsigned int* work;
 };
 
 __device__ __forceinline__ int cb_hist_nslots(const CbHistArgs& a) {
@@ -276,11 +283,10 @@ __device__ __forceinline__ void cb_hist_q_apply(int* sh, int B, int C, int copy,
 // Documents are dealt to the chunks of a group block-cyclically (block = blockDim.x * 4 documents): chunk k takes
 // blocks k, k + nK, k + 2 nK, ... so that every chunk sees the same mix of the data and the blocks finish together.
 static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long long item, int chunk, int nK,
-                                       int slot_begin, int slot_count) {
+                                       int slot_begin, int slot_count, bool dyn_blocks) {
     const int B = a.B;
     const int C = a.copies > 0 ? a.copies : 1;
     const int total = slot_count * 16 * B * C;
-    const long long d_end = a.d.n;
     for (int i = threadIdx.x; i < total; i += blockDim.x) sh[i] = 0;
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -300,8 +306,26 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
     // Software pipeline: the four loads of the next step are issued before the atomics of the current one, so the
     // DRAM latency of a step overlaps the shared-memory work of the previous step.
     const long long blk = (long long)blockDim.x * 4;
-    const long long step = blk * nK;
-    const long long ib0 = blk * chunk + (long long)(threadIdx.x & ~31) * 4;
+    const long long super = blk * CB_SUPER_STEPS;
+    const long long step = blk;
+    __shared__ unsigned int s_grab;
+    long long taken = 0;
+    for (long long sbi = chunk;;) {
+        long long r0;
+        if (dyn_blocks) {
+            if (taken + super > CB_HIST_MAX_DOCS_PER_TILE) break;
+            __syncthreads();
+            if (threadIdx.x == 0) s_grab = atomicAdd(a.work + g, 1u);
+            __syncthreads();
+            r0 = (long long)s_grab * super;
+        } else {
+            r0 = sbi * super;
+            sbi += nK;
+        }
+        if (r0 >= a.d.n) break;
+        taken += super;
+        const long long d_end = min(a.d.n, r0 + super);
+    const long long ib0 = r0 + (long long)(threadIdx.x & ~31) * 4;
     uint4 nw = make_uint4(0, 0, 0, 0);
     ushort4 nlf = make_ushort4(0, 0, 0, 0);
     float4 ns0 = make_float4(0, 0, 0, 0), ns1 = make_float4(0, 0, 0, 0);
@@ -362,6 +386,7 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
             }
         }
     }
+    }   // super-blocks
     if ((unsigned int)lane < tail - head) cb_hist_q_apply(sh, B, C, copy, ring[(head + lane) & (CB_RING - 1)]);
     __syncthreads();
     // dump as floats into the private region [item][slot][s][j][B]
@@ -393,7 +418,6 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
     __syncthreads();
 }
 
-#define CB_HIST_MAX_DOCS_PER_TILE (1 << 19)
 __device__ __forceinline__ int cb_hist_chunks(int G, int ncta, long long n, int host_choice = 0) {
     if (host_choice > 0) return host_choice;
     const int by_grid = (ncta >= G) ? (ncta / G) : 1;
@@ -409,14 +433,26 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
     per = (per + 3) & ~3ll;
     const int nslots = cb_hist_nslots(a);
     const long long items = (long long)G * nK;
+    const bool one_pass = a.slots_per_pass >= nslots;
+    const bool quant2 = a.statmax && a.S == 2;
+    const bool dyn_items = a.work && quant2 && one_pass && items > ncta;     // whole items from one counter
+    const bool dyn_blocks = a.work && quant2 && one_pass && items <= ncta;   // super-blocks inside a group
+    __shared__ unsigned int s_item;
     for (int sb = 0; sb < nslots; sb += a.slots_per_pass) {
         const int sc = min(a.slots_per_pass, nslots - sb);
-        for (long long item = cta; item < items; item += ncta) {
+        for (long long item = cta;; item += ncta) {
+            if (dyn_items) {
+                __syncthreads();
+                if (threadIdx.x == 0) s_item = atomicAdd(a.work + G, 1u);
+                __syncthreads();
+                item = s_item;
+            }
+            if (item >= items) break;
             const int g = (int)(item % G);
             const long long k = item / G;
             const long long b = k * per;
             const long long e = min(a.d.n, b + per);
-            if (a.statmax && a.S == 2) cb_hist_item_q2(a, reinterpret_cast<int*>(sh), g, item, (int)k, nK, sb, sc);
+            if (quant2) cb_hist_item_q2(a, reinterpret_cast<int*>(sh), g, item, (int)k, nK, sb, sc, dyn_blocks);
             else if (a.statmax) cb_hist_item_q(a, reinterpret_cast<int*>(sh), g, item, min(b, e), e, sb, sc);
             else if (b < e || a.priv) cb_hist_item(a, sh, g, item, min(b, e), e, sb, sc);
         }

@@ -151,6 +151,7 @@ _SIGS = {
                                    c_float, c_void_p, c_void_p, c_ull, c_float, c_void_p, c_void_p, c_int]),
     "cb_fused_set_features": (None, [c_void_p, c_int, c_int]),
     "cb_fused_set_phase_ts": (None, [c_void_p, c_void_p]),
+    "cb_fused_set_work": (None, [c_void_p, c_void_p]),
     "cb_fused_set_priv": (None, [c_void_p, c_void_p, c_void_p]),
     "cb_fused_destroy": (None, [c_void_p]),
     "cb_fused_geometry": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

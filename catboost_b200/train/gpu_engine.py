@@ -54,7 +54,7 @@ class GpuObliviousEngine:
                  leaf_iterations: int = 1, seed: int = 0, ctx: Optional[DistContext] = None, reduce: str = "fused",
                  eval_sets: Optional[List[EvalSet]] = None, use_graph: bool = True, threads: int = 512,
                  ext_der: Optional[torch.Tensor] = None, ext_hess: Optional[torch.Tensor] = None,
-                 timeout_s: float = 20.0, quantized_hist: bool = True):
+                 timeout_s: float = 20.0, quantized_hist: bool = True, dynamic_work: bool = True):
         assert store.bins.is_cuda, "GpuObliviousEngine needs a CUDA store"
         if depth > 16:
             raise ValueError("depth must be <= 16")
@@ -79,6 +79,7 @@ class GpuObliviousEngine:
         self.reduce = reduce if self.R > 1 else "fused"
         self.use_graph = use_graph
         self.quantized_hist = bool(quantized_hist)
+        self.dynamic_work = bool(dynamic_work)
         self.threads = threads
         self.eval_sets = eval_sets or []
         self.ext_der, self.ext_hess = ext_der, ext_hess
@@ -196,18 +197,29 @@ class GpuObliviousEngine:
             nslots = 1 if level == 0 else 1 << (level - 1)
             need = max(need, G * geo[4] * nslots * self.S * 4 * self.B)
         self.priv = torch.empty(need, dtype=torch.float32, device=self.dev)
+        self.work = torch.zeros(G + 1, dtype=torch.int32, device=self.dev)
+        if self.dynamic_work:
+            self.lib.cb_fused_set_work(ctypes.c_void_p(self.plan), _p(self.work))
         self.lib.cb_fused_set_priv(ctypes.c_void_p(self.plan), _p(self.priv),
                                    _p(self.statmax) if self.quantized_hist else None)
 
     def enable_phase_timing(self):
         """Record globaltimer stamps of the fused kernel's phases (block 0) for every level of the latest tree."""
-        self.phase_ts = torch.zeros((self.depth, 8), dtype=torch.int64, device=self.dev)
+        self.phase_ts = torch.zeros(self.depth * 8 + 2 * 4096, dtype=torch.int64, device=self.dev)
         self.lib.cb_fused_set_phase_ts(ctypes.c_void_p(self.plan), _p(self.phase_ts))
 
     def phase_times_us(self):
         """[depth][6] microseconds: leaf update, histogram, wait for grid, reduce+push(+peer wait), score, select."""
-        t = self.phase_ts.cpu().numpy().astype(np.float64)
+        t = self.phase_ts[: self.depth * 8].view(self.depth, 8).cpu().numpy().astype(np.float64)
         return (t[:, 1:7] - t[:, 0:6]) / 1000.0
+
+    def block_finish_times(self):
+        """(histogram end time relative to the level start in us, SM id) per block at level depth-2."""
+        raw = self.phase_ts.cpu().numpy()
+        grid = self.level_geo[self.depth - 2][0]
+        t0 = raw[(self.depth - 2) * 8 + 1]
+        blk = raw[self.depth * 8: self.depth * 8 + 2 * grid].reshape(grid, 2)
+        return (blk[:, 0] - t0) / 1000.0, blk[:, 1]
 
     def _stream(self):
         return ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)

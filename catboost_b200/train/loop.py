@@ -106,6 +106,9 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
     octx = ObjectiveContext(train_pool, dev)
     eval_approx = [torch.from_numpy(np.ascontiguousarray(b)).to(dev, f32) for b in base_evals]
     learner = GenericLearner(store, o, dims, ctx, seed=int(o.random_seed))
+    ordered = None
+    if o.boosting_type == "Ordered" and not (ctx is not None and ctx.is_distributed):
+        ordered = OrderedState(o, n, train_pool, dev, approx[:, :n])
     trees = []
     start_iter = 0
     restored = snap.try_load(o)
@@ -116,6 +119,8 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
             _apply_tree_to(store, t, approx, n, dims, dev)
             for es, ea in zip(eval_stores, eval_approx):
                 _apply_tree_to(es, t, ea, es.n, dims, dev)
+        if ordered is not None:
+            ordered.approx.copy_(approx[:, :n])      # ordered cursors are not stored; resume from the plain cursor
         learner.gen.manual_seed(int(o.random_seed) + 12345 + start_iter)
         if od is not None:
             for v in hist.data[eval_names[0]][str(metrics[0])]:
@@ -125,7 +130,9 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
     stop = False
     for it in range(start_iter, T):
         with prof.span("derivatives"):
-            der, hess = objective.der_hess(approx[:, :n], target, weight, octx)
+            # ordered boosting: the tree structure is learned from derivatives at the ordered cursor, where the
+            # value of a document only comes from documents that precede it in the permutation
+            der, hess = objective.der_hess(ordered.approx if ordered is not None else approx[:, :n], target, weight, octx)
             der_p = torch.zeros((dims, store.npad), dtype=f32, device=dev)
             hess_p = torch.zeros((dims, store.npad), dtype=f32, device=dev)
             der_p[:, :n], hess_p[:, :n] = der, hess
@@ -137,6 +144,8 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
         with prof.span("leaves"):
             vals, wts = estimate_leaves(objective, approx, target, weight, tr.leaf, tr.n_leaves, n, o, ctx, octx)
         tv = torch.from_numpy(vals).to(dev, f32)
+        if ordered is not None:
+            ordered.update(der, hess, weight, tr.leaf, tr.n_leaves, o)
         approx[:, :n] += tv[tr.leaf[:n].long() & 0xFFFF].t()
         tree = dict(kind=tr.kind, splits=tr.splits, node_split=tr.node_split, leaf_of_node=tr.leaf_of_node, values=vals,
                     weights=wts)
@@ -172,6 +181,59 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
     snap.finalize(dict(trees=trees, hist=hist.data, iters=hist.iters))
     return LoopResult(trees, hist.data, best_it, _best_scores(hist, metrics), 0,
                       approx[:, :n].t().double().cpu().numpy())
+
+
+class OrderedState:
+    """Ordered boosting (catboost/cuda/methods/dynamic_boosting.h:75-98,182-232, catboost/private/libs/algo/fold.cpp):
+    documents are put in a random permutation and cut into blocks whose sizes grow geometrically
+    (``fold_len_multiplier``, first block ``min_fold_size``).  The ordered cursor of a document in block b is only ever
+    moved by leaf statistics of blocks < b, so the derivatives that drive the structure search are not fitted to the
+    document's own target.  The exported model still gets its leaf values from all documents (plain cursor)."""
+
+    def __init__(self, o, n, pool, dev, approx0):
+        rng = np.random.RandomState(int(o.random_seed) + 777)
+        if pool.group_id is not None:
+            off = pool.group_offsets()
+            perm_g = rng.permutation(len(off) - 1)
+            order = np.concatenate([np.arange(off[k], off[k + 1]) for k in perm_g]) if len(perm_g) else np.zeros(0, np.int64)
+        else:
+            order = np.arange(n) if o.has_time else rng.permutation(n)
+        bounds = [0]
+        size = max(1, min(int(o.min_fold_size), n))
+        mult = max(1.0001, float(o.fold_len_multiplier))
+        while bounds[-1] < n:
+            bounds.append(min(n, bounds[-1] + int(math.ceil(size))))
+            size *= mult
+        block_of_pos = np.zeros(n, dtype=np.int64)
+        for b in range(len(bounds) - 1):
+            block_of_pos[bounds[b]:bounds[b + 1]] = b
+        block = np.zeros(n, dtype=np.int64)
+        block[order] = block_of_pos
+        self.n_blocks = len(bounds) - 1
+        self.block = torch.from_numpy(block).to(dev)
+        self.approx = approx0.clone()
+
+    def update(self, der, hess, weight, leaf, n_leaves, o):
+        dims, n = der.shape
+        idx = leaf[:n].long() & 0xFFFF
+        key = self.block * n_leaves + idx
+        B, L = self.n_blocks, n_leaves
+        sd = torch.zeros((dims, B * L), dtype=torch.float64, device=der.device)
+        sh = torch.zeros((dims, B * L), dtype=torch.float64, device=der.device)
+        sd.index_add_(1, key, der.double())
+        newton = o.leaf_estimation_method == "Newton"
+        if newton:
+            sh.index_add_(1, key, hess.double())
+        else:
+            w = torch.ones(n, dtype=torch.float64, device=der.device) if weight is None else weight[:n].double()
+            sh.index_add_(1, key, w.unsqueeze(0).expand(dims, n).contiguous())
+        sd = sd.view(dims, B, L).cumsum(1)
+        sh = sh.view(dims, B, L).cumsum(1)
+        val = sd / (sh + float(o.l2_leaf_reg))
+        # statistics of blocks < b: shift by one block; the first block learns from itself (it has no history)
+        prev = torch.cat([val[:, :1], val[:, :-1]], dim=1)
+        inc = prev[:, self.block, idx] * float(o.learning_rate)
+        self.approx += inc.float()
 
 
 class _CallbackInfo:
