@@ -12,7 +12,7 @@
 #include "cb_common.cuh"
 
 #define CB_HIST_MAX_DOCS_PER_TILE (1 << 19)
-#define CB_SUPER_STEPS 8        // a super-block = CB_SUPER_STEPS * blockDim.x * 4 documents
+#define CB_WARP_STEPS 16        // a warp-block = 128 * CB_WARP_STEPS consecutive documents
 
 enum CbScoreFn : int { CB_SCORE_COSINE = 0, CB_SCORE_L2 = 1, CB_SCORE_SOLAR = 2, CB_SCORE_LOO = 3, CB_SCORE_SAT = 4 };
 
@@ -303,48 +303,62 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
     const float sc1 = 8388607.0f / fmaxf(a.statmax[1], 1e-30f);
     const unsigned int lt = (1u << lane) - 1u;
     unsigned int head = 0, tail = 0;
-    // Software pipeline: the four loads of the next step are issued before the atomics of the current one, so the
-    // DRAM latency of a step overlaps the shared-memory work of the previous step.
-    const long long blk = (long long)blockDim.x * 4;
-    const long long super = blk * CB_SUPER_STEPS;
-    const long long step = blk;
-    __shared__ unsigned int s_grab;
-    long long taken = 0;
-    for (long long sbi = chunk;;) {
-        long long r0;
+    // Every warp streams on its own: it takes warp-blocks of 128 * CB_WARP_STEPS consecutive documents, either from a
+    // fixed cyclic schedule or (dyn_blocks) from the group's work counter, one block ahead of the one it is working on.
+    // Software pipeline: the four loads of the next step -- which may already belong to the next warp-block -- are
+    // issued before the atomics of the current step, so DRAM latency overlaps the shared-memory work.
+    const int nwarps = blockDim.x >> 5;
+    const long long WB = 128ll * CB_WARP_STEPS;
+    const long long nwb = (a.d.n + WB - 1) / WB;
+    const int max_blocks = max(1, (int)((CB_HIST_MAX_DOCS_PER_TILE / nwarps) / WB));
+    long long sched = (long long)chunk * nwarps + warp;
+    const long long sched_step = (long long)nK * nwarps;
+    int taken = 0;
+    auto next_block = [&]() -> long long {
         if (dyn_blocks) {
-            if (taken + super > CB_HIST_MAX_DOCS_PER_TILE) break;
-            __syncthreads();
-            if (threadIdx.x == 0) s_grab = atomicAdd(a.work + g, 1u);
-            __syncthreads();
-            r0 = (long long)s_grab * super;
-        } else {
-            r0 = sbi * super;
-            sbi += nK;
+            if (taken >= max_blocks) return nwb;
+            unsigned int v = 0;
+            if (lane == 0) v = atomicAdd(a.work + g, 1u);
+            v = __shfl_sync(0xffffffffu, v, 0);
+            ++taken;
+            return (long long)v;
         }
-        if (r0 >= a.d.n) break;
-        taken += super;
-        const long long d_end = min(a.d.n, r0 + super);
-    const long long ib0 = r0 + (long long)(threadIdx.x & ~31) * 4;
+        const long long v = sched;
+        sched += sched_step;
+        return v;
+    };
+    long long cur = next_block();
+    long long nxt = (cur < nwb) ? next_block() : nwb;
+    long long base = cur * WB;
+    long long bend = min(a.d.n, base + WB);
     uint4 nw = make_uint4(0, 0, 0, 0);
     ushort4 nlf = make_ushort4(0, 0, 0, 0);
     float4 ns0 = make_float4(0, 0, 0, 0), ns1 = make_float4(0, 0, 0, 0);
-    if (ib0 + lane * 4 < d_end) {
-        const long long i = ib0 + lane * 4;
+    if (cur < nwb && base + lane * 4 < a.d.n) {
+        const long long i = base + lane * 4;
         nw = *reinterpret_cast<const uint4*>(bg + i);
         nlf = *reinterpret_cast<const ushort4*>(a.leaf + i);
         ns0 = *reinterpret_cast<const float4*>(st0 + i);
         ns1 = *reinterpret_cast<const float4*>(st1 + i);
     }
-    for (long long ib = ib0; ib < d_end; ib += step) {
-        const long long i = ib + lane * 4;
+    while (cur < nwb) {
+        const long long i = base + lane * 4;
         const uint4 w = nw;
         const ushort4 lf = nlf;
         const float4 s0 = ns0, s1 = ns1;
-        const bool valid = i < d_end;
-        {
-            const long long in = i + step;
-            if (in < d_end) {
+        const bool valid = i < a.d.n;
+        // where the next step reads
+        long long nbase = base + 128;
+        long long ncur = cur, nbend = bend;
+        if (nbase >= bend) {
+            ncur = nxt;
+            nxt = (ncur < nwb) ? next_block() : nwb;
+            nbase = ncur * WB;
+            nbend = min(a.d.n, nbase + WB);
+        }
+        if (ncur < nwb) {
+            const long long in = nbase + lane * 4;
+            if (in < a.d.n) {
                 nw = *reinterpret_cast<const uint4*>(bg + in);
                 nlf = *reinterpret_cast<const ushort4*>(a.leaf + in);
                 ns0 = *reinterpret_cast<const float4*>(st0 + in);
@@ -385,8 +399,8 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
                 __syncwarp();
             }
         }
+        base = nbase; cur = ncur; bend = nbend;
     }
-    }   // super-blocks
     if ((unsigned int)lane < tail - head) cb_hist_q_apply(sh, B, C, copy, ring[(head + lane) & (CB_RING - 1)]);
     __syncthreads();
     // dump as floats into the private region [item][slot][s][j][B]

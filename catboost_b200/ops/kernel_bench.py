@@ -1,0 +1,160 @@
+"""Per-kernel timing and roofline report.
+
+    python -m catboost_b200.ops.kernel_bench [--rows N] [--features F] [--kernel name] [--reps R]
+
+Every kernel is timed in isolation with CUDA events (3 warm-up launches, an L2 flush between timed launches) and
+reported as algorithmic bytes / time against the measured copy bandwidth of the pool (``MEASURED_PEAKS.json`` at the
+repository root when present, else 6650 GB/s).  The same entry point is what the committed ncu summaries were taken on.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def _time(fn, reps, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for k in range(reps):
+        flush.fill_(k & 0xFF)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / reps
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, default=4_000_000)
+    ap.add_argument("--features", type=int, default=28)
+    ap.add_argument("--depth", type=int, default=6)
+    ap.add_argument("--trees", type=int, default=100)
+    ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--kernel", default="all")
+    args = ap.parse_args(argv)
+    from ..data.pool import Pool
+    from ..data.quantization import build_quantization, make_store, quantize_floats_into, FlatFeature
+    from ..models.gpu_apply import GpuPredictor
+    from ..params import resolve_options
+    from ..parallel.runtime import DistContext
+    from ..train.boosting import build_store, plan_features
+    from ..train.gpu_engine import GpuObliviousEngine
+    from ..train.objectives import make_objective
+    from . import api as ops
+    from . import native
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    lib = native.cuda_lib()
+    hbm, src = _peaks()
+    n, F = args.rows, args.features
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((n, F), dtype=np.float32)
+    y = (X[:, 0] + 0.5 * X[:, 1] * X[:, 2] > 0).astype(np.float32)
+    pool = Pool(X, y)
+    o = resolve_options(dict(task_type="GPU", border_count=128), "Logloss", n)
+    plan = plan_features(o, pool, DistContext(0, 1, dev), None)
+    store, _ = build_store(plan, pool, dev)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+    st = lambda: ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    out = []
+
+    def report(name, ms, nbytes, note=""):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        rec = {"kernel": name, "rows": n, "features": F, "ms": round(ms, 4), "algorithmic_MB": round(nbytes / 1e6, 1),
+               "GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / hbm, 3), "peak_source": f"{src} {hbm} GB/s",
+               "note": note}
+        out.append(rec)
+        print(json.dumps(rec))
+
+    want = lambda k: args.kernel in ("all", k)
+    obj = make_objective("Logloss", {})
+    eng = GpuObliviousEngine(store, torch.from_numpy(y), None, torch.zeros(n), obj, depth=args.depth, iterations=8,
+                             learning_rate=0.1, l2_leaf_reg=3.0, leaf_iterations=1, use_graph=False)
+    eng.step(2)
+    torch.cuda.synchronize()
+
+    if want("quantize"):
+        xd = torch.from_numpy(X).to(dev)
+        q = plan.quant
+        borders = torch.from_numpy(np.concatenate(q.borders).astype(np.float32)).to(dev)
+        boff = torch.from_numpy(np.concatenate([[0], np.cumsum([len(b) for b in q.borders])]).astype(np.int32)).to(dev)
+        nanm = torch.from_numpy(q.nan_is_max).to(dev)
+        tmp = torch.zeros_like(store.bins)
+        ms = _time(lambda: lib.cb_quantize(P(xd), n, F, xd.stride(0), P(borders), P(boff), P(nanm), P(tmp), store.npad, 0,
+                                           st()), args.reps, flush)
+        report("cb_quantize_kernel", ms, n * F * 4 + n * ((F + 3) // 4) * 4, "float32 rows -> packed bins")
+        del xd, tmp
+    if want("grad"):
+        ms = _time(lambda: eng._grad(), args.reps, flush)
+        report("cb_grad_kernel", ms, n * (4 + 4 + 2 + 4 + 2 + 8), "approx rw, target, leaf rw, stats w")
+    if want("leaf_pass"):
+        def leaf_pass():
+            lib.cb_leaf_pass(eng.loss_id, eng.p0, eng.p1, P(eng.approx), P(eng.target), None, P(eng.leaf), None, None, n,
+                             eng.L, P(eng.delta), P(eng.sums), P(eng.counter), 1, 0, 1, 3.0, 0.1, P(eng.cur_vals), None,
+                             None, eng.L, P(eng.iter_ptr), P(eng.leaf_w), None, sm * 2, st())
+        ms = _time(leaf_pass, args.reps, flush)
+        report("cb_leaf_pass_kernel", ms, n * (4 + 4 + 2), "approx, target, leaf")
+    if want("update_leaf"):
+        ms = _time(lambda: lib.cb_update_leaf(ctypes.c_void_p(store.handle), P(eng.leaf), P(eng.splits), P(eng.iter_ptr),
+                                              eng.depth, 0, sm * 8, st()), args.reps, flush)
+        report("cb_update_leaf_kernel", ms, n * (4 + 2 + 2), "one group word, leaf rw")
+    if want("apply_tree"):
+        ap_ = torch.zeros(store.npad, device=dev)
+        zero = torch.zeros(1, dtype=torch.int32, device=dev)
+        ms = _time(lambda: lib.cb_apply_tree_bins(ctypes.c_void_p(store.handle), P(ap_), store.npad, P(eng.splits), P(zero),
+                                                  eng.depth, P(eng.cur_vals), 1, sm * 8, st()), args.reps, flush)
+        report("cb_apply_tree_bins_kernel", ms, n * (4 * args.depth + 8), "depth group words (upper bound), approx rw")
+    if want("hist"):
+        leaf = torch.zeros(store.npad, dtype=torch.int16, device=dev)
+        table = torch.zeros(1, dtype=torch.int16, device=dev)
+        ms = _time(lambda: ops.hist(store, leaf, eng.stats, table, 1), args.reps, flush)
+        report("cb_hist_kernel", ms, n * ((F + 3) // 4) * (4 + 2 + 8), "stand-alone fp32-atomic histogram, one slot")
+    if want("fused"):
+        for level in range(args.depth):
+            ms = _time(lambda: eng._level_fused(level), args.reps, flush)
+            report(f"cb_level_fused_kernel[level={level}]", ms, n * ((F + 3) // 4) * (4 + 2 + 8),
+                   "bytes requested by the histogram phase (leaf/stat rows are re-read per feature group)")
+    if want("predict"):
+        model_eng = eng
+        sp, vals, wts = model_eng.finish()
+        from ..train.boosting import assemble_model
+
+        class _Codec:
+            class_names = [0, 1]
+        trees = [dict(kind="oblivious", splits=sp[t % len(sp)], values=vals[t % len(sp)], weights=wts[t % len(sp)])
+                 for t in range(args.trees)]
+        m = assemble_model(o, plan, pool, store, trees, 1, np.zeros(1), _Codec())
+        pred = GpuPredictor(m, dev)
+        xd = torch.from_numpy(X).to(dev)
+        res = torch.empty((1, n), dtype=torch.float32, device=dev)
+        ms = _time(lambda: pred.predict_device(xd, res), args.reps, flush)
+        report("cb_predict_kernel", ms, n * F * 4 + n * 4, f"{args.trees} trees depth {args.depth}; "
+               f"{n / (ms * 1e-3):.3g} rows/s, {n * args.trees / (ms * 1e-3):.3g} tree-rows/s")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -210,3 +210,18 @@ def test_sum_models_and_metrics():
     assert abs(make_metric("AUC").eval(y.reshape(-1, 1), yb) - 1.0) < 1e-12
     assert make_metric("NDCG:top=3").eval(np.array([[3.0], [2.0], [1.0]]), np.array([2.0, 1.0, 0.0]),
                                           group_offsets=np.array([0, 3])) == pytest.approx(1.0)
+
+
+def test_ordered_boosting_regularises():
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((2400, 6)).astype(np.float32)
+    y = (X[:, 0] + X[:, 1] * X[:, 2] + 0.8 * rng.standard_normal(2400) > 0).astype(int)
+    res = {}
+    for bt in ("Plain", "Ordered"):
+        m = cb.CatBoostClassifier(iterations=60, depth=5, learning_rate=0.2, boosting_type=bt, verbose=False,
+                                  allow_writing_files=False)
+        m.fit(X[:1200], y[:1200], eval_set=(X[1200:], y[1200:]), use_best_model=False)
+        ev = m.get_evals_result()
+        res[bt] = (ev["learn"]["Logloss"][-1], min(ev["validation"]["Logloss"]))
+    assert res["Ordered"][0] > res["Plain"][0]            # fits the training rows less tightly
+    assert res["Ordered"][1] < res["Plain"][1] + 0.02     # and generalises at least as well
