@@ -130,6 +130,8 @@ def main():
     ap.add_argument("--rows", type=int, default=0)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--reduce", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--cells", default="narrow", choices=["narrow", "wide", "float"],
+                    help="shared-memory histogram cells: one int32, hi/lo int32 pair, or fp32")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--phases", action="store_true", help="print per-phase times of the fused level kernel")
@@ -169,7 +171,7 @@ def main():
     X, y = make_data(args.config, cfg["rows"], cfg["features"], rank, world)
     params = dict(loss_function="Logloss", iterations=K + W, depth=cfg["depth"], border_count=cfg["border_count"],
                   learning_rate=0.1, l2_leaf_reg=3.0, task_type="GPU", random_seed=0, allow_writing_files=False,
-                  histogram_reduce=args.reduce)
+                  histogram_reduce=args.reduce, histogram_cells=args.cells)
 
     # ---------------- device-timed trainer steps -------------------------------------------------------------
     ctx = DistContext.current(dev)
@@ -184,7 +186,8 @@ def main():
                              iterations=K + W, learning_rate=0.1, l2_leaf_reg=3.0, score_function=o.score_function,
                              random_strength=float(o.random_strength), bootstrap_type=o.bootstrap_type,
                              bootstrap_param=float(o.bagging_temperature or 1.0), leaf_method=o.leaf_estimation_method,
-                             leaf_iterations=int(o.leaf_estimation_iterations), seed=0, ctx=ctx, reduce=args.reduce)
+                             leaf_iterations=int(o.leaf_estimation_iterations), seed=0, ctx=ctx, reduce=args.reduce,
+                             quantized_hist={"narrow": True, "wide": "wide", "float": False}[args.cells])
     flush = None if args.no_flush else torch.empty(512 << 20, dtype=torch.uint8, device=dev)
     if args.phases and eng.plan:
         eng.enable_phase_timing()
@@ -281,7 +284,7 @@ def main():
                "data": "synthetic", "impl": "ours",
                "config": {"model": cfg["model"], "global_batch": cfg["rows"], "seq_len": cfg["features"],
                           "parallelism": f"doc-parallel dp{world}", "loss": "Logloss", "depth": cfg["depth"],
-                          "border_count": cfg["border_count"], "learning_rate": 0.1, "histogram_reduce": args.reduce,
+                          "border_count": cfg["border_count"], "learning_rate": 0.1, "histogram_reduce": args.reduce, "histogram_cells": args.cells,
                           "l2_policy": ("flush: 512 MiB write between timed iterations" if flush is not None
                                         else "inputs larger than L2")},
                "clocks": clocks, "e2e": e2e, "apply": apply_info, "gpu_launches": launches,

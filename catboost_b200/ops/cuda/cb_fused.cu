@@ -37,8 +37,10 @@ struct CbFusedArgs {
     unsigned long long* phase_ts;    // optional [depth][8] globaltimer stamps written by block 0 (phase profiling)
 };
 
-// Sum of the per-chunk private tiles of this rank, written to the owner's slot.  One thread = one 16-byte column
-// group of one (slot, statistic) row.
+// Sum of the per-chunk private tiles of this rank, written to the owner's slot.  A unit of work is one 16-byte column
+// group of one (slot, statistic) row.  At the shallow levels there are few units and many chunks (a bundle of all
+// groups is cut into as many chunks as there are blocks), so the chunks of a unit are dealt to KS lanes of a warp
+// (KS a power of two <= 32, as many as the grid has spare threads for) and combined with shuffles.
 static __device__ void cb_reduce_chunks(const CbFusedArgs& a, int cta, int ncta) {
     const CbHistArgs& h = a.h;
     const int G = h.d.G, S = h.S, B = h.B, TB = h.d.TB;
@@ -51,24 +53,46 @@ static __device__ void cb_reduce_chunks(const CbFusedArgs& a, int cta, int ncta)
     const int R = a.c.nranks, me = a.c.rank;
     const long long total = (long long)rows * C4;
     const long long gthreads = (long long)ncta * blockDim.x;
-    for (long long u = (long long)cta * blockDim.x + threadIdx.x; u < total; u += gthreads) {
-        const int row = (int)(u / C4);
-        const int col = (int)(u % C4) << 2;
-        const int f = cb_find_feature(h.d.feat_off, h.d.F, col);
-        const int bin = col - h.d.feat_off[f];
-        const int slot = row / S, st = row - slot * S;
-        const float* src = h.priv + ((size_t)slot * S + st) * 4 * B + (size_t)(f & 3) * B + bin;
-        const int g = f >> 2;
+    int KS = 1;
+    while (KS < 32 && total * (KS * 2) <= gthreads && KS * 2 <= nK) KS <<= 1;
+    const int CW = 32 / KS;                      // units per warp
+    const int lane = threadIdx.x & 31;
+    const int cl = lane & (CW - 1), ks = lane / CW;
+    const long long gwarp = ((long long)cta * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = gthreads >> 5;
+    for (long long base = gwarp * CW; base < total; base += nwarps * CW) {
+        const long long u = base + cl;
+        const bool valid = u < total;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int k = 0; k < nK; ++k) {
-            const float4 v = *reinterpret_cast<const float4*>(src + ((size_t)k * G + g) * item_stride);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        int row = 0, col = 0;
+        if (valid) {
+            row = (int)(u / C4);
+            col = (int)(u % C4) << 2;
+            const int f = cb_find_feature(h.d.feat_off, h.d.F, col);
+            const int bin = col - h.d.feat_off[f];
+            const int slot = row / S, st = row - slot * S;
+            const float* src = h.priv + ((size_t)slot * S + st) * 4 * B + (size_t)(f & 3) * B + bin
+                               + (size_t)(f >> 2) * item_stride;
+            const size_t kstride = (size_t)G * item_stride;
+#pragma unroll 4
+            for (int k = ks; k < nK; k += KS) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)k * kstride));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
         }
-        int r = 0;
-        if (R > 1) { while (r + 1 < R && col >= a.own_col[r + 1]) ++r; }
-        float* dst = (R > 1 ? a.c.peer_slot[r] + (size_t)me * a.c.slot_floats : const_cast<float*>(a.s.hsrc[0]))
-                     + (size_t)row * a.Wmax + (col - a.own_col[r]);
-        *reinterpret_cast<float4*>(dst) = acc;
+        for (int off = CW; off < 32; off <<= 1) {
+            acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
+            acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+            acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
+            acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
+        }
+        if (valid && ks == 0) {
+            int r = 0;
+            if (R > 1) { while (r + 1 < R && col >= a.own_col[r + 1]) ++r; }
+            float* dst = (R > 1 ? a.c.peer_slot[r] + (size_t)me * a.c.slot_floats : const_cast<float*>(a.s.hsrc[0]))
+                         + (size_t)row * a.Wmax + (col - a.own_col[r]);
+            *reinterpret_cast<float4*>(dst) = acc;
+        }
     }
 }
 
@@ -160,8 +184,10 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
 struct CbFusedPlan {
     CbFusedArgs a;
     int threads;
-    int max_smem;
+    int max_smem;      // dynamic shared memory one block may use
+    int sm_smem;       // shared memory of one SM available to two resident blocks (after their static + reserved parts)
     int sm_count;
+    int max_bundle;    // widest feature-group bundle of the single-cell histogram path (0 = off)
 };
 
 CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigned short* leaf, const float* stats, int S,
@@ -173,7 +199,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     CbFusedPlan* p = new (std::nothrow) CbFusedPlan();
     if (!p) return nullptr;
     CbFusedArgs& a = p->a;
-    a.h.d = *d; a.h.leaf = leaf; a.h.stats = stats; a.h.S = S; a.h.B = B; a.h.out = nullptr; a.h.priv = partial; a.h.statmax = nullptr; a.phase_ts = nullptr; a.h.nK = 0; a.h.copies = 1; a.h.work = nullptr;
+    a.h.d = *d; a.h.leaf = leaf; a.h.stats = stats; a.h.S = S; a.h.B = B; a.h.out = nullptr; a.h.priv = partial; a.h.statmax = nullptr; a.phase_ts = nullptr; a.h.nK = 0; a.h.copies = 1; a.h.work = nullptr; a.h.narrow = 0; a.h.bundle = 0;
     a.h.slot_table = nullptr; a.h.nslots_table = 0; a.h.level = 0; a.h.small_mask = mask0; a.h.slots_per_pass = 1;
     a.s.d = *d;
     if (comm) a.c = *comm; else { a.c = CbComm(); a.c.nranks = 1; a.c.rank = 0; }
@@ -203,6 +229,9 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     cudaFuncAttributes fa;
     if (cudaFuncGetAttributes(&fa, cb_level_fused_kernel) != cudaSuccess) { cudaGetLastError(); delete p; return nullptr; }
     p->max_smem -= (int)fa.sharedSizeBytes;
+    cudaDeviceGetAttribute(&p->sm_smem, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+    p->sm_smem -= 2 * (int)fa.sharedSizeBytes;
+    p->max_bundle = 0;
     if (cudaFuncSetAttribute(cb_level_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, p->max_smem) != cudaSuccess) {
         cudaGetLastError();
         delete p;
@@ -213,6 +242,10 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
 
 CB_API void cb_fused_set_phase_ts(CbFusedPlan* p, unsigned long long* ts) { p->a.phase_ts = ts; }
 CB_API void cb_fused_set_work(CbFusedPlan* p, unsigned int* work) { p->a.h.work = work; }
+CB_API void cb_fused_set_narrow(CbFusedPlan* p, int narrow, int max_bundle) {
+    p->a.h.narrow = narrow;
+    p->max_bundle = max_bundle > 8 ? 8 : max_bundle;
+}
 
 CB_API void cb_fused_set_features(CbFusedPlan* p, int f_begin, int f_end) {
     p->a.s.f_begin = f_begin;
@@ -225,44 +258,75 @@ CB_API void cb_fused_destroy(CbFusedPlan* p) { delete p; }
 // Launch geometry of one level.  Returns the cooperative grid size (0 on error) and, through the pointers, the
 // slots per pass, dynamic shared memory, block size, document chunks per group and cell replicas.
 CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int* smem_bytes, int* threads, int* chunks,
-                             int* copies) {
+                             int* copies, int* bundle) {
     const int nslots = level == 0 ? 1 : (1 << (level - 1));
-    const int per_slot = p->a.h.S * 4 * p->a.h.B * 4 * (p->a.h.statmax ? 2 : 1);
-    const bool ring = p->a.h.statmax && p->a.h.S == 2;      // per-warp compaction rings (16 bytes x 64 entries)
-    int thr = p->threads;
-    int ring_bytes = ring ? (thr / 32) * 64 * 16 + 16 : 0;
-    int budget = p->max_smem - ring_bytes;
-    int spp = nslots;
-    if (spp * per_slot > budget / 2) {
-        // one 1024-thread block per SM when the tile needs more than half of the shared memory
-        thr = 1024;
-        ring_bytes = ring ? (thr / 32) * 64 * 16 + 16 : 0;
-        budget = p->max_smem - ring_bytes;
+    const bool narrow = p->a.h.statmax && p->a.h.S == 2 && p->a.h.narrow;
+    const int G = p->a.h.d.G;
+    const long long n = p->a.h.d.n;
+    int thr = p->threads, spp = nslots, C = 1, gpc = 0, smem = 0;
+    if (narrow && p->max_bundle > 0) {
+        // Bundled single-cell path: a block accumulates gpc groups at once.  Tile = slots * gpc * 8 * B * C ints, ring =
+        // warps * 64 * (3 + gpc) words.  Take the widest bundle that fits, with two blocks per SM when that does not
+        // cost bundle width; then replicate the cells once if there is room.
+        const int cell = 8 * p->a.h.B * 4;                   // bytes per (slot, group)
+        const int gmax = G < p->max_bundle ? G : p->max_bundle;
+        auto ring_bytes = [](int t, int g) { return (t / 32) * 64 * (3 + g) * 4 + 16; };
+        auto fit = [&](int t, int budget, int slots) {
+            int g = 0;
+            while (g < gmax && slots * (g + 1) * cell + ring_bytes(t, g + 1) <= budget) ++g;
+            return g;
+        };
+        const int half = (p->sm_smem - 2048) / 2;
+        const int g2 = fit(p->threads, half < p->max_smem ? half : p->max_smem, nslots);
+        const int g1 = fit(1024, p->max_smem, nslots);
+        int budget;
+        if (g2 >= 1 && g2 >= g1) { gpc = g2; thr = p->threads; budget = half < p->max_smem ? half : p->max_smem; }
+        else if (g1 >= 1) { gpc = g1; thr = 1024; budget = p->max_smem; }
+        else {
+            // even one group of all slots does not fit: several passes over the slots
+            gpc = 1; thr = 1024; budget = p->max_smem;
+            spp = (budget - ring_bytes(thr, 1)) / cell;
+            if (spp < 1) return 0;
+        }
+        // even out the bundles (7 groups as 4 + 3 rather than 5 + 2 changes nothing in passes but shrinks the tile)
+        const int nb = (G + gpc - 1) / gpc;
+        gpc = (G + nb - 1) / nb;
+        if (2 * spp * gpc * cell + ring_bytes(thr, gpc) <= budget) C = 2;
+        smem = spp * gpc * cell * C + ring_bytes(thr, gpc);
+    } else {
+        const int per_slot = p->a.h.S * 4 * p->a.h.B * 4 * ((p->a.h.statmax && !narrow) ? 2 : 1);
+        const bool ring = p->a.h.statmax && p->a.h.S == 2;      // per-warp compaction rings (16 bytes x 64 entries)
+        int ring_bytes = ring ? (thr / 32) * 64 * 16 + 16 : 0;
+        int budget = p->max_smem - ring_bytes;
+        if (spp * per_slot > budget / 2) {
+            // one 1024-thread block per SM when the tile needs more than half of the shared memory
+            thr = 1024;
+            ring_bytes = ring ? (thr / 32) * 64 * 16 + 16 : 0;
+            budget = p->max_smem - ring_bytes;
+        }
+        if (spp * per_slot > budget) spp = budget / per_slot;
+        if (spp < 1) return 0;
+        // replicate the cells while two blocks per SM still fit (fewer bank / address collisions per atomic)
+        if (ring && thr == p->threads) {
+            while (C < 8 && 2 * (spp * per_slot * (C * 2) + ring_bytes) <= p->max_smem) C *= 2;
+        }
+        smem = spp * per_slot * C + ring_bytes;
     }
-    if (spp * per_slot > budget) spp = budget / per_slot;
-    if (spp < 1) return 0;
-    // replicate the cells while two blocks per SM still fit (fewer bank / address collisions per atomic)
-    int C = 1;
-    if (ring && thr == p->threads) {
-        while (C < 8 && 2 * (spp * per_slot * (C * 2) + ring_bytes) <= p->max_smem) C *= 2;
-    }
-    const int smem = spp * per_slot * C + ring_bytes;
     int occ = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, cb_level_fused_kernel, thr, smem) != cudaSuccess) { cudaGetLastError(); return 0; }
     if (occ < 1) return 0;
     if (occ > 4) occ = 4;
     const int grid = occ * p->sm_count;
-    // document chunks per group: at least what the grid offers and what the 2^19-documents-per-tile cap needs;
-    // among a few candidates take the one that fills the last round of blocks best
-    const int G = p->a.h.d.G;
-    const long long n = p->a.h.d.n;
-    const int by_grid = grid >= G ? grid / G : 1;
+    // document chunks per work unit (group or bundle): at least what the grid offers and what the 2^19-documents-per-
+    // tile cap needs; among a few candidates take the one that fills the last round of blocks best
+    const int units = gpc ? (G + gpc - 1) / gpc : G;
+    const int by_grid = grid >= units ? grid / units : 1;
     const int by_docs = (int)((n + (1 << 19) - 1) >> 19);
     const int lo = by_grid > by_docs ? by_grid : by_docs;
     int best = lo;
     double best_eff = 0.0;
     for (int k = lo; k < lo + 8; ++k) {
-        const long long items = (long long)G * k;
+        const long long items = (long long)units * k;
         const long long rounds = (items + grid - 1) / grid;
         const double eff = (double)items / (double)(rounds * grid);
         if (eff > best_eff + 0.02) { best_eff = eff; best = k; }
@@ -272,6 +336,7 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
     *threads = thr;
     *chunks = best;
     *copies = C;
+    *bundle = gpc;
     return grid;
 }
 
@@ -279,9 +344,9 @@ CB_API void cb_fused_set_priv(CbFusedPlan* p, float* priv, const float* statmax)
 
 CB_API int cb_fused_launch(CbFusedPlan* p, int level, float* hprev, float* hcur, const unsigned int* mask_in,
                            unsigned int* mask_out, int grid, int slots_per_pass, int smem_bytes, int threads,
-                           int chunks, int copies, cudaStream_t st) {
+                           int chunks, int copies, int bundle, cudaStream_t st) {
     CbFusedArgs a = p->a;
-    a.h.nK = chunks; a.h.copies = copies;
+    a.h.nK = chunks; a.h.copies = copies; a.h.bundle = bundle;
     a.h.level = level; a.h.small_mask = mask_in; a.h.slots_per_pass = slots_per_pass;
     a.s.level = level; a.s.small_mask = mask_in; a.s.hprev = hprev; a.s.hcur = hcur;
     a.mask_out = mask_out;

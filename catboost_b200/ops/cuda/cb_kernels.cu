@@ -270,7 +270,7 @@ CB_API int cb_hist(const CbData* d, const unsigned short* leaf, const float* sta
     CbHistArgs a;
     a.d = *d; a.leaf = leaf; a.stats = stats; a.S = S; a.level = level; a.small_mask = small_mask;
     a.slots_per_pass = slots_per_pass; a.B = B; a.out = out; a.slot_table = slot_table; a.nslots_table = nslots_table;
-    a.priv = nullptr; a.statmax = nullptr; a.nK = 0; a.copies = 1; a.work = nullptr;
+    a.priv = nullptr; a.statmax = nullptr; a.nK = 0; a.copies = 1; a.work = nullptr; a.narrow = 0; a.bundle = 0;
     const int smem = cb_hist_smem_bytes(slots_per_pass, S, B);
     if (!g_hist_smem_set) {
         int dev = 0, optin = 0;

@@ -48,11 +48,11 @@ DEFAULTS: Dict[str, Any] = dict(
     text_processing=None, embedding_features=None, eval_fraction=None, fixed_binary_splits=None,
     data_partition=None, permutation_count=None, min_fold_size=100, cat_features=None, scale_pos_weight=None,
     gpu_cat_features_storage="GpuRam", observations_to_bootstrap="TestOnly", fused_levels=True,
-    histogram_reduce="fused", node_type="SingleHost", callback=None,
+    histogram_reduce="fused", histogram_cells="narrow", node_type="SingleHost", callback=None,
 )
 
 GPU_ONLY = {"gpu_ram_part", "pinned_memory_size", "gpu_cat_features_storage", "data_partition", "fold_len_multiplier",
-            "min_fold_size", "observations_to_bootstrap", "devices", "fused_levels", "histogram_reduce"}
+            "min_fold_size", "observations_to_bootstrap", "devices", "fused_levels", "histogram_reduce", "histogram_cells"}
 CPU_ONLY = {"rsm", "sampling_frequency", "approx_on_full_history", "model_shrink_rate", "model_shrink_mode",
             "langevin", "diffusion_temperature", "posterior_sampling", "monotone_constraints", "dev_efb_max_buckets",
             "sparse_features_conflict_fraction", "random_score_type"}

@@ -54,7 +54,8 @@ class GpuObliviousEngine:
                  leaf_iterations: int = 1, seed: int = 0, ctx: Optional[DistContext] = None, reduce: str = "fused",
                  eval_sets: Optional[List[EvalSet]] = None, use_graph: bool = True, threads: int = 512,
                  ext_der: Optional[torch.Tensor] = None, ext_hess: Optional[torch.Tensor] = None,
-                 timeout_s: float = 20.0, quantized_hist: bool = True, dynamic_work: bool = True):
+                 timeout_s: float = 20.0, quantized_hist: bool = True, dynamic_work: bool = True,
+                 der_fn=None, zero_mean_leaves: bool = False, max_bundle: int = 8):
         assert store.bins.is_cuda, "GpuObliviousEngine needs a CUDA store"
         if depth > 16:
             raise ValueError("depth must be <= 16")
@@ -78,11 +79,24 @@ class GpuObliviousEngine:
         self.score_seed = (int(seed) * 0xD1B54A32D192ED03 + 77) & 0xFFFFFFFFFFFFFFFF
         self.reduce = reduce if self.R > 1 else "fused"
         self.use_graph = use_graph
+        # False: fp32 shared atomics; "wide": 23-bit fixed point in two int32 cells; True / "narrow": one int32 cell
         self.quantized_hist = bool(quantized_hist)
+        self.narrow_hist = self.quantized_hist and quantized_hist != "wide"
+        self.max_bundle = int(max_bundle)
         self.dynamic_work = bool(dynamic_work)
         self.threads = threads
         self.eval_sets = eval_sets or []
         self.ext_der, self.ext_hess = ext_der, ext_hess
+        # Objectives without a device formula (query-wise ranking losses, Python objectives): der_fn(cursor[n]) returns
+        # (der[n], hess[n]) device tensors; they are written into the external-derivative rows before every tree.  The
+        # iteration then contains framework ops, so it is not captured into a graph.
+        self.der_fn = der_fn
+        self.zero_mean_leaves = bool(zero_mean_leaves)
+        if der_fn is not None:
+            self.loss_id = 100
+            self.use_graph = False
+            self.ext_der = torch.zeros(store.npad, dtype=torch.float32, device=self.dev)
+            self.ext_hess = torch.zeros(store.npad, dtype=torch.float32, device=self.dev)
         n, npad, dev = store.n, store.npad, self.dev
         self.n, self.npad = n, npad
         self.S = 2
@@ -182,14 +196,15 @@ class GpuObliviousEngine:
                                        self.feat_bounds[self.rank + 1])
         # fixed-point accumulation is on: statmax must be known to the geometry (it doubles the tile size)
         self.lib.cb_fused_set_priv(ctypes.c_void_p(self.plan), None, _p(self.statmax) if self.quantized_hist else None)
+        self.lib.cb_fused_set_narrow(ctypes.c_void_p(self.plan), 1 if self.narrow_hist else 0, self.max_bundle)
         self.level_geo = []
         for level in range(self.depth):
-            spp, smem, thr, nk, cp = (ctypes.c_int(0) for _ in range(5))
+            spp, smem, thr, nk, cp, bd = (ctypes.c_int(0) for _ in range(6))
             grid = self.lib.cb_fused_geometry(ctypes.c_void_p(self.plan), level, ctypes.byref(spp), ctypes.byref(smem),
-                                              ctypes.byref(thr), ctypes.byref(nk), ctypes.byref(cp))
+                                              ctypes.byref(thr), ctypes.byref(nk), ctypes.byref(cp), ctypes.byref(bd))
             if grid <= 0:
                 raise RuntimeError(f"no cooperative launch geometry for level {level}")
-            self.level_geo.append((grid, spp.value, smem.value, thr.value, nk.value, cp.value))
+            self.level_geo.append((grid, spp.value, smem.value, thr.value, nk.value, cp.value, bd.value))
         # private tiles: one region per (chunk, group) work item, sized for the largest level
         G = self.store.G
         need = 0
@@ -235,12 +250,12 @@ class GpuObliviousEngine:
         self.launches_per_iter += 1
 
     def _level_fused(self, level: int):
-        grid, spp, smem, thr, nk, cp = self.level_geo[level]
+        grid, spp, smem, thr, nk, cp, bd = self.level_geo[level]
         hprev, hcur = self.hbuf[(level + 1) & 1], self.hbuf[level & 1]
         hcur_ptr = _p(hcur) if level < self.depth - 1 else None
         native.cuda_check(self.lib.cb_fused_launch(ctypes.c_void_p(self.plan), level, _p(hprev), hcur_ptr,
                                                    _p(self.mask[level & 1]), _p(self.mask[(level + 1) & 1]), grid, spp,
-                                                   smem, thr, nk, cp, self._stream()), "cb_level_fused")
+                                                   smem, thr, nk, cp, bd, self._stream()), "cb_level_fused")
         self.launches_per_iter += 1
 
     def _level_unfused(self, level: int):
@@ -301,7 +316,11 @@ class GpuObliviousEngine:
         n = self.n
         leaf = self.leaf[:n].long() & 0xFFFF
         ap = self.approx[:n] + (self.delta[leaf] if it > 0 else 0)
-        d, h = self.objective.der_hess(ap.unsqueeze(0), self.target[:n], None if self.weight is None else self.weight[:n])
+        if self.der_fn is not None:
+            d, h = self.ext_der[:n].unsqueeze(0), self.ext_hess[:n].unsqueeze(0)
+        else:
+            d, h = self.objective.der_hess(ap.unsqueeze(0), self.target[:n],
+                                           None if self.weight is None else self.weight[:n])
         w = torch.ones_like(ap) if self.weight is None else self.weight[:n]
         sums = torch.zeros((3, self.L), dtype=torch.float64, device=self.dev)
         sums[0].index_add_(0, leaf, d[0].double())
@@ -330,8 +349,25 @@ class GpuObliviousEngine:
                                   self.grid_stream, self._stream()), "cb_metric_sum")
             self.launches_per_iter += 2
 
+    def _external_derivatives(self):
+        n = self.n
+        cur = self.approx[:n] + self.cur_vals[self.leaf[:n].long() & 0xFFFF]
+        d, h = self.der_fn(cur)
+        self.ext_der[:n] = d.reshape(-1)
+        self.ext_hess[:n] = h.reshape(-1)
+
+    def _center_leaves(self):
+        # ranking losses are invariant to a shift of the scores: keep the weighted mean of the tree's leaves at zero
+        it = self.iter_ptr.long()
+        w = self.model_wts.index_select(0, it)[0].double()
+        mean = ((self.cur_vals.double() * w).sum() / w.sum().clamp_min(1e-30)).float()
+        self.cur_vals.sub_(mean)
+        self.model_vals.index_copy_(0, it, self.cur_vals.unsqueeze(0))
+
     def _iteration(self):
         self.launches_per_iter = 0
+        if self.der_fn is not None:
+            self._external_derivatives()
         self._grad()
         for level in range(self.depth):
             if self.reduce == "fused":
@@ -339,6 +375,8 @@ class GpuObliviousEngine:
             else:
                 self._level_unfused(level)
         self._leaves()
+        if self.zero_mean_leaves:
+            self._center_leaves()
         self._evals()
         n_extra = 2 * len(self.eval_sets)
         native.cuda_check(self.lib.cb_iter_end(_p(self.iter_ptr), _p(self.scal), _p(self.loss_hist), _p(self.eval_scal),

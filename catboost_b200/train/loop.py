@@ -42,7 +42,11 @@ class ObjectiveContext:
 
 
 def _use_fast_engine(o, objective, store, dims) -> bool:
-    return (store.bins.is_cuda and o.grow_policy == "SymmetricTree" and objective.native_id is not None and dims == 1
+    # objectives without a device formula still use the fused level kernels: their derivatives are computed by the
+    # objective's tensor code once per tree, which only allows a single leaf-estimation step
+    native = objective.native_id is not None
+    external = (not native) and dims == 1 and int(o.leaf_estimation_iterations) == 1
+    return (store.bins.is_cuda and o.grow_policy == "SymmetricTree" and (native or external) and dims == 1
             and o.boosting_type == "Plain" and o.leaf_estimation_method in ("Newton", "Gradient")
             and float(o.rsm) >= 1.0 and int(o.min_data_in_leaf) <= 1
             and o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson") and bool(o.fused_levels or True)
@@ -313,6 +317,12 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
     btype = o.bootstrap_type
     if btype == "Bayesian" and boot_p == 0:
         btype = "No"
+    der_fn = None
+    if objective.native_id is None:
+        octx = ObjectiveContext(train_pool, dev)
+        t_dev = torch.from_numpy(np.asarray(y_train, dtype=np.float32)).to(dev)
+        w_dev = None if w_train is None else torch.from_numpy(np.asarray(w_train, dtype=np.float32)).to(dev)
+        der_fn = lambda cur: objective.der_hess(cur.unsqueeze(0), t_dev, w_dev, octx)
     with prof.span("engine_setup"):
         eng = GpuObliviousEngine(
             store, torch.from_numpy(np.asarray(y_train, dtype=np.float32)),
@@ -322,10 +332,13 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
             score_function=o.score_function, random_strength=float(o.random_strength), bootstrap_type=btype,
             bootstrap_param=boot_p, leaf_method=o.leaf_estimation_method,
             leaf_iterations=int(o.leaf_estimation_iterations), seed=int(o.random_seed), ctx=ctx,
-            reduce=("fused" if o.histogram_reduce in ("fused", None) else "nccl"), eval_sets=evs)
+            reduce=("fused" if o.histogram_reduce in ("fused", None) else "nccl"), eval_sets=evs,
+            quantized_hist={"narrow": True, "wide": "wide", "float": False}[o.histogram_cells or "narrow"],
+            der_fn=der_fn, zero_mean_leaves=bool(der_fn is not None and getattr(objective, "zero_mean_leaves", False)))
     loss_metric_name = objective.name
     # "cheap" logging: the only tracked metric is the objective itself, which the device already accumulates
-    cheap = len(metrics) == 1 and isinstance(o.loss_function, str) and str(metrics[0]) == o.loss_function
+    cheap = (len(metrics) == 1 and isinstance(o.loss_function, str) and str(metrics[0]) == o.loss_function
+             and der_fn is None)
     need_each = bool(od is not None or callbacks)
     want_log = bool(o.verbose) or bool(eval_stores)
     period = 1 if need_each else (max(1, int(o.metric_period)) if want_log else T)
@@ -381,7 +394,7 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
     if not hist.iters:
         # nothing was logged during training: fill the learn curve of the objective from the device history
         lh = eng.learn_loss_history()
-        name = str(metrics[0]) if getattr(metrics[0], "name", None) == loss_metric_name else None
+        name = str(metrics[0]) if (getattr(metrics[0], "name", None) == loss_metric_name and der_fn is None) else None
         if name is not None and len(lh) > 1:
             vals_l = lh[1:].tolist()
             if objective.name == "RMSE":

@@ -180,6 +180,27 @@ def test_gpu_regression_rmse():
     assert rmse < 0.45, rmse
 
 
+def test_gpu_ranking_objectives_use_fused_engine():
+    """Query-wise losses have no device formula: their derivatives come from the objective's tensor code, the tree
+    structure and the leaves from the fused level kernels and the leaf pass."""
+    import catboost_b200 as cb
+    rng = np.random.default_rng(0)
+    sizes = rng.integers(5, 40, 400)
+    gid = np.repeat(np.arange(400), sizes)
+    n = len(gid)
+    X = rng.standard_normal((n, 10)).astype(np.float32)
+    score = X @ rng.standard_normal(10) + 0.5 * rng.standard_normal(n)
+    rel = np.digitize(score, np.quantile(score, [0.5, 0.8, 0.95])).astype(np.float32)
+    for loss in ("YetiRank", "QueryRMSE", "PairLogit"):
+        m = cb.CatBoostRanker(loss_function=loss, iterations=30, depth=4, learning_rate=0.3, verbose=False,
+                              allow_writing_files=False, eval_metric="NDCG", task_type="GPU", devices="0",
+                              leaf_estimation_iterations=1)
+        m.fit(X, rel, group_id=gid)
+        assert m._train_info.get("launches_per_iter", 0) > 0, loss
+        ev = m.eval_metrics(cb.Pool(X, rel, group_id=gid), ["NDCG"], eval_period=29)["NDCG"]
+        assert ev[-1] > 0.9, (loss, ev)
+
+
 def test_device_wait_times_out_without_hanging():
     """A wait on a tag nobody writes returns with the status word set (bounded spin, no trap)."""
     from catboost_b200.ops import native
