@@ -218,6 +218,7 @@ def main():
     if args.phases and eng.plan and rank == 0:
         np.set_printoptions(precision=1, suppress=True, linewidth=160)
         print('phase us per level [leaf_update, hist, grid_wait, reduce_push, score, select]:\n', eng.phase_times_us(), file=sys.stderr)
+        print('inside score (block 0) [noise scale, first accumulate, rest]:\n', eng.score_phase_times_us(), file=sys.stderr)
         bt, sm = eng.block_finish_times()
         order = np.argsort(bt)
         print('hist end per block (us) pct 0/10/50/90/100:', np.percentile(bt, [0, 10, 50, 90, 100]), file=sys.stderr)

@@ -34,7 +34,8 @@ struct CbFusedArgs {
     int own_col[CB_MAX_RANKS + 1];   // rank r owns histogram columns [own_col[r], own_col[r+1]) (multiples of 4)
     int Wmax;                        // row stride (floats) of every slot buffer = max owned width
     int smem_floats;                 // dynamic shared memory of this launch, in floats
-    unsigned long long* phase_ts;    // optional [depth][8] globaltimer stamps written by block 0 (phase profiling)
+    unsigned long long* phase_ts;    // optional globaltimer stamps (phase profiling): [depth][8] by block 0,
+                                     // then [4096][2] per-block histogram end + SM id, then [depth][4] inside the score phase
 };
 
 // Sum of the per-chunk private tiles of this rank, written to the owner's slot.  A unit of work is one 16-byte column
@@ -149,7 +150,7 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
     }
 
     if (ts) ts[4] = cb_globaltimer();
-    cb_score_phase(a.s, cta, ncta, cb_sh, a.smem_floats);
+    cb_score_phase(a.s, cta, ncta, cb_sh, a.smem_floats, ts ? a.phase_ts + a.depth * 8 + 8192 + level * 4 : nullptr);
     __threadfence();
     grid.sync();
     if (ts) ts[5] = cb_globaltimer();
@@ -254,7 +255,6 @@ CB_API void cb_fused_set_features(CbFusedPlan* p, int f_begin, int f_end) {
 
 CB_API void cb_fused_destroy(CbFusedPlan* p) { delete p; }
 
-// Launch geometry of one level: returns the cooperative grid size (0 on error) and the slots per pass.
 // Launch geometry of one level.  Returns the cooperative grid size (0 on error) and, through the pointers, the
 // slots per pass, dynamic shared memory, block size, document chunks per group and cell replicas.
 CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int* smem_bytes, int* threads, int* chunks,
@@ -266,8 +266,7 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
     int thr = p->threads, spp = nslots, C = 1, gpc = 0, smem = 0;
     if (narrow && p->max_bundle > 0) {
         // Bundled single-cell path: a block accumulates gpc groups at once.  Tile = slots * gpc * 8 * B * C ints, ring =
-        // warps * 64 * (3 + gpc) words.  Take the widest bundle that fits, with two blocks per SM when that does not
-        // cost bundle width; then replicate the cells once if there is room.
+        // warps * 64 * (3 + gpc) words.  Take the widest bundle that fits; then replicate the cells once if there is room.
         const int cell = 8 * p->a.h.B * 4;                   // bytes per (slot, group)
         const int gmax = G < p->max_bundle ? G : p->max_bundle;
         auto ring_bytes = [](int t, int g) { return (t / 32) * 64 * (3 + g) * 4 + 16; };
@@ -276,15 +275,14 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
             while (g < gmax && slots * (g + 1) * cell + ring_bytes(t, g + 1) <= budget) ++g;
             return g;
         };
-        const int half = (p->sm_smem - 2048) / 2;
-        const int g2 = fit(p->threads, half < p->max_smem ? half : p->max_smem, nslots);
-        const int g1 = fit(1024, p->max_smem, nslots);
-        int budget;
-        if (g2 >= 1 && g2 >= g1) { gpc = g2; thr = p->threads; budget = half < p->max_smem ? half : p->max_smem; }
-        else if (g1 >= 1) { gpc = g1; thr = 1024; budget = p->max_smem; }
-        else {
+        // one 1024-thread block per SM: measured a few percent faster than two 512-thread blocks at every level (one
+        // tile instead of two leaves room for wider bundles and replicas) and it balances better
+        int budget = p->max_smem;
+        thr = 1024;
+        gpc = fit(thr, budget, nslots);
+        if (gpc < 1) {
             // even one group of all slots does not fit: several passes over the slots
-            gpc = 1; thr = 1024; budget = p->max_smem;
+            gpc = 1;
             spp = (budget - ring_bytes(thr, 1)) / cell;
             if (spp < 1) return 0;
         }

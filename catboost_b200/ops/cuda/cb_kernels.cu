@@ -118,35 +118,77 @@ __device__ __forceinline__ float cb_bootstrap_weight(int type, float p, unsigned
     }
 }
 
-__global__ void __launch_bounds__(256) cb_grad_kernel(CbGradArgs a) {
+// Four documents per thread and step with 16-byte loads / stores; the loads of the next step are issued before the
+// current one is processed (all arrays are padded to npad, a multiple of 256, so vectors never run past the end).
+struct CbGradIn { float4 ap, tg, w, ed, eh; ushort4 lf; };
+template <int LOSS>
+__device__ __forceinline__ void cb_grad_load(const CbGradArgs& a, long long i0, CbGradIn& v) {
+    const int loss = LOSS >= 0 ? LOSS : a.loss;
+    v.ap = *reinterpret_cast<const float4*>(a.approx + i0);
+    if (a.cur_vals) v.lf = *reinterpret_cast<const ushort4*>(a.leaf + i0);
+    if (a.weight) v.w = *reinterpret_cast<const float4*>(a.weight + i0);
+    if (loss == CB_LOSS_EXTERNAL) {
+        v.ed = *reinterpret_cast<const float4*>(a.ext_der + i0);
+        if (a.ext_hess) v.eh = *reinterpret_cast<const float4*>(a.ext_hess + i0);
+    } else {
+        v.tg = *reinterpret_cast<const float4*>(a.target + i0);
+    }
+}
+
+// LOSS >= 0 fixes the objective at compile time (the common ones get their own instantiation, which removes the
+// dispatch and the unused inputs from the loop); LOSS = -1 reads it from the arguments.
+template <int LOSS>
+__global__ void __launch_bounds__(256, 3) cb_grad_kernel(CbGradArgs a) {
+    const int loss = LOSS >= 0 ? LOSS : a.loss;
     const int it = *a.iter_ptr;
     double s_loss = 0.0, s_w = 0.0, s_d2 = 0.0, s_n = 0.0;
     float m0 = 0.0f, m1 = 0.0f;
+    const long long n4 = a.npad >> 2;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
-        float ap = a.approx[i];
-        if (a.cur_vals) {
-            ap += a.cur_vals[a.leaf[i]];
-            a.approx[i] = ap;
+    long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    CbGradIn nx;
+    nx.w = make_float4(1.f, 1.f, 1.f, 1.f);
+    nx.eh = make_float4(1.f, 1.f, 1.f, 1.f);
+    nx.ed = nx.tg = nx.ap = make_float4(0.f, 0.f, 0.f, 0.f);
+    nx.lf = make_ushort4(0, 0, 0, 0);
+    if (q < n4) cb_grad_load<LOSS>(a, q << 2, nx);
+    for (; q < n4; q += stride) {
+        const long long i0 = q << 2;
+        const CbGradIn v = nx;
+        if (q + stride < n4) cb_grad_load<LOSS>(a, (q + stride) << 2, nx);
+        float ap[4] = {v.ap.x, v.ap.y, v.ap.z, v.ap.w};
+        const float tg[4] = {v.tg.x, v.tg.y, v.tg.z, v.tg.w};
+        const float wt[4] = {v.w.x, v.w.y, v.w.z, v.w.w};
+        const float ed[4] = {v.ed.x, v.ed.y, v.ed.z, v.ed.w};
+        const float eh[4] = {v.eh.x, v.eh.y, v.eh.z, v.eh.w};
+        const unsigned int lf[4] = {v.lf.x, v.lf.y, v.lf.z, v.lf.w};
+        float o0[4], o1[4];
+        float f_loss = 0.f, f_w = 0.f, f_d2 = 0.f, f_n = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const long long i = i0 + k;
+            const bool live = i < a.n;
+            if (a.cur_vals) ap[k] += a.cur_vals[lf[k]];
+            const float w = wt[k];
+            CbLossOut o;
+            if (loss == CB_LOSS_EXTERNAL) { o.der = ed[k]; o.hess = eh[k]; o.value = 0.0f; }
+            else o = cb_loss_eval(loss, a.p0, a.p1, ap[k], tg[k]);
+            const float wb = a.boot_type ? cb_bootstrap_weight(a.boot_type, a.boot_p,
+                                                                 cb_mix64(a.seed ^ cb_mix64(((unsigned long long)it << 40) ^ (unsigned long long)i)))
+                                         : 1.0f;
+            const float wd = w * o.der;
+            const float st0 = live ? wb * wd : 0.0f;
+            const float st1 = live ? wb * w * (a.newton_stats ? o.hess : 1.0f) : 0.0f;
+            o0[k] = st0; o1[k] = st1;
+            m0 = fmaxf(m0, fabsf(st0));
+            m1 = fmaxf(m1, fabsf(st1));
+            if (live) { f_loss += w * o.value; f_w += w; f_d2 += wd * wd; f_n += 1.0f; }
         }
-        a.leaf[i] = 0;
-        const float w = a.weight ? a.weight[i] : 1.0f;
-        CbLossOut o;
-        if (a.loss == CB_LOSS_EXTERNAL) { o.der = a.ext_der[i]; o.hess = a.ext_hess ? a.ext_hess[i] : 1.0f; o.value = 0.0f; }
-        else o = cb_loss_eval(a.loss, a.p0, a.p1, ap, a.target[i]);
-        const float wb = a.boot_type ? cb_bootstrap_weight(a.boot_type, a.boot_p,
-                                                             cb_mix64(a.seed ^ cb_mix64(((unsigned long long)it << 40) ^ (unsigned long long)i)))
-                                     : 1.0f;
-        const float wd = w * o.der;
-        const float st0 = wb * wd, st1 = wb * w * (a.newton_stats ? o.hess : 1.0f);
-        a.stats[i] = st0;
-        a.stats[a.npad + i] = st1;
-        m0 = fmaxf(m0, fabsf(st0));
-        m1 = fmaxf(m1, fabsf(st1));
-        s_loss += (double)(w * o.value);
-        s_w += (double)w;
-        s_d2 += (double)(wd * wd);
-        s_n += 1.0;
+        if (a.cur_vals) *reinterpret_cast<float4*>(a.approx + i0) = make_float4(ap[0], ap[1], ap[2], ap[3]);
+        *reinterpret_cast<ushort4*>(a.leaf + i0) = make_ushort4(0, 0, 0, 0);
+        *reinterpret_cast<float4*>(a.stats + i0) = make_float4(o0[0], o0[1], o0[2], o0[3]);
+        *reinterpret_cast<float4*>(a.stats + a.npad + i0) = make_float4(o1[0], o1[1], o1[2], o1[3]);
+        s_loss += (double)f_loss; s_w += (double)f_w; s_d2 += (double)f_d2; s_n += (double)f_n;
     }
     __shared__ double red[4][8];
     s_loss = cb_warp_sum_d(s_loss); s_w = cb_warp_sum_d(s_w); s_d2 = cb_warp_sum_d(s_d2); s_n = cb_warp_sum_d(s_n);
@@ -178,7 +220,9 @@ CB_API int cb_grad_pointwise(int loss, float p0, float p1, float* approx, const 
                              float* statmax, int grid, cudaStream_t st) {
     CbGradArgs a{loss, p0, p1, approx, target, weight, leaf, cur_vals, n, npad, stats, newton_stats,
                  boot_type, boot_p, seed, iter_ptr, scal, ext_der, ext_hess, statmax};
-    cb_grad_kernel<<<grid, 256, 0, st>>>(a);
+    if (loss == CB_LOSS_LOGLOSS) cb_grad_kernel<CB_LOSS_LOGLOSS><<<grid, 256, 0, st>>>(a);
+    else if (loss == CB_LOSS_RMSE) cb_grad_kernel<CB_LOSS_RMSE><<<grid, 256, 0, st>>>(a);
+    else cb_grad_kernel<-1><<<grid, 256, 0, st>>>(a);
     CB_LAUNCH_CHECK();
     return 0;
 }
@@ -305,7 +349,10 @@ static void cb_fill_score_args(CbScoreArgs& a, const CbData* d, const float* con
     a.best_key = best_key;
 }
 
-__global__ void __launch_bounds__(256) cb_score_kernel(CbScoreArgs a) { cb_score_phase(a, blockIdx.x, gridDim.x, nullptr, 0); }
+__global__ void __launch_bounds__(256) cb_score_kernel(CbScoreArgs a) {
+    extern __shared__ float score_sh[];            // CB_SCORE_WARP_FLOATS per warp
+    cb_score_phase(a, blockIdx.x, gridDim.x, score_sh, (int)(blockDim.x >> 5) * CB_SCORE_WARP_FLOATS);
+}
 
 CB_API int cb_score(const CbData* d, const float* const* hsrc, int nsrc, const float* hprev, float* hcur, int W,
                     int col_base, int f_begin, int f_end, int level, int S, const unsigned int* small_mask, float l2,
@@ -317,7 +364,7 @@ CB_API int cb_score(const CbData* d, const float* const* hsrc, int nsrc, const f
     const int nf = f_end - f_begin;
     if (nf <= 0) return 0;
     const int grid = (nf + 7) / 8;
-    cb_score_kernel<<<grid, 256, 0, st>>>(a);
+    cb_score_kernel<<<grid, 256, 8 * CB_SCORE_WARP_FLOATS * sizeof(float), st>>>(a);
     CB_LAUNCH_CHECK();
     return 0;
 }
@@ -391,55 +438,95 @@ struct CbLeafArgs {
     float* model_vals; float* model_wts; int Lstride; const int* iter_ptr;
     float* leaf_w;           // [L] per-leaf weight sums, written by the first pass of a tree
     CbComm c;
+    // Fixed-point passes (optional): the first pass of a tree records vmax = {max |w der|, max |w hess|}; the later
+    // passes scale to 24 bits against twice that bound and add a signed high and an unsigned low part with native
+    // integer shared-memory atomics (fp32 shared atomics are compare-and-swap loops).  A value beyond the bound -- the
+    // derivative moved further than expected between Newton steps -- goes to the double accumulator directly.
+    float* vmax;
 };
+
+struct CbLeafIn { float4 a4, t4, w4, d4, h4; ushort4 lf4; };
+template <int LOSS>
+__device__ __forceinline__ void cb_leaf_load(const CbLeafArgs& a, long long i0, CbLeafIn& v) {
+    const int loss = LOSS >= 0 ? LOSS : a.loss;
+    v.lf4 = *reinterpret_cast<const ushort4*>(a.leaf + i0);
+    if (loss == CB_LOSS_EXTERNAL) {
+        v.d4 = *reinterpret_cast<const float4*>(a.ext_der + i0);
+        if (a.ext_hess) v.h4 = *reinterpret_cast<const float4*>(a.ext_hess + i0);
+    } else {
+        v.a4 = *reinterpret_cast<const float4*>(a.approx + i0);
+        v.t4 = *reinterpret_cast<const float4*>(a.target + i0);
+    }
+    if (a.weight) v.w4 = *reinterpret_cast<const float4*>(a.weight + i0);
+}
 
 // Shared-memory accumulators are replicated per lane group: cell (leaf, stat) has `C` copies and lane `l` uses copy
 // l & (C-1), so the lanes of a warp never collide on an address (shared fp32 atomics are compare-and-swap loops;
 // without collisions every one succeeds on its first try).  C = 32 for up to 128 leaves.
-__global__ void __launch_bounds__(512) cb_leaf_pass_kernel(CbLeafArgs a, int C) {
-    extern __shared__ float sl[];     // [L][3][C] when it fits, else unused
+// LOSS as in cb_grad_kernel.
+template <int LOSS>
+__device__ __forceinline__ void cb_leaf_pass_body(const CbLeafArgs& a, int C) {
+    extern __shared__ float sl[];     // [L][3][C] floats (or [L][4][C] ints in a fixed-point pass), else unused
+    const int loss = LOSS >= 0 ? LOSS : a.loss;
     const int L = a.L;
     const bool use_sh = C > 0;
     const int cm = C - 1;
     const int lane_copy = threadIdx.x & cm;
+    const bool quant = use_sh && a.vmax && !a.first && (a.n / gridDim.x) < (1ll << 19);
+    int* si = reinterpret_cast<int*>(sl);
+    float M0 = 0.f, M1 = 0.f, sc0 = 0.f, sc1 = 0.f;
+    if (quant) {
+        M0 = 2.0f * fmaxf(__ldcg(a.vmax), 1e-30f);
+        M1 = 2.0f * fmaxf(__ldcg(a.vmax + 1), 1e-30f);
+        sc0 = 8388607.0f / M0;
+        sc1 = 8388607.0f / M1;
+    }
+    float mx0 = 0.f, mx1 = 0.f;
     if (use_sh) {
-        for (int i = threadIdx.x; i < 3 * L * C; i += blockDim.x) sl[i] = 0.0f;
+        for (int i = threadIdx.x; i < (quant ? 4 : 3) * L * C; i += blockDim.x) sl[i] = 0.0f;
         __syncthreads();
     }
     const long long n4 = (a.n + 3) >> 2;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n4; q += stride) {
+    // the loads of the next step are issued before the current step is processed
+    long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    CbLeafIn nx;
+    nx.a4 = nx.t4 = nx.d4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    nx.w4 = nx.h4 = make_float4(1.f, 1.f, 1.f, 1.f);
+    nx.lf4 = make_ushort4(0, 0, 0, 0);
+    if (q < n4) cb_leaf_load<LOSS>(a, q << 2, nx);
+    for (; q < n4; q += stride) {
         const long long i0 = q << 2;
-        const ushort4 lf4 = *reinterpret_cast<const ushort4*>(a.leaf + i0);
-        const unsigned int lf[4] = {lf4.x, lf4.y, lf4.z, lf4.w};
-        float ap[4] = {0.f, 0.f, 0.f, 0.f}, tg[4] = {0.f, 0.f, 0.f, 0.f}, wt[4] = {1.f, 1.f, 1.f, 1.f};
-        float ed[4], eh[4];
-        if (a.loss == CB_LOSS_EXTERNAL) {
-            const float4 d4 = *reinterpret_cast<const float4*>(a.ext_der + i0);
-            ed[0] = d4.x; ed[1] = d4.y; ed[2] = d4.z; ed[3] = d4.w;
-            eh[0] = eh[1] = eh[2] = eh[3] = 1.0f;
-            if (a.ext_hess) {
-                const float4 h4 = *reinterpret_cast<const float4*>(a.ext_hess + i0);
-                eh[0] = h4.x; eh[1] = h4.y; eh[2] = h4.z; eh[3] = h4.w;
-            }
-        } else {
-            const float4 a4 = *reinterpret_cast<const float4*>(a.approx + i0);
-            const float4 t4 = *reinterpret_cast<const float4*>(a.target + i0);
-            ap[0] = a4.x; ap[1] = a4.y; ap[2] = a4.z; ap[3] = a4.w;
-            tg[0] = t4.x; tg[1] = t4.y; tg[2] = t4.z; tg[3] = t4.w;
-        }
-        if (a.weight) {
-            const float4 w4 = *reinterpret_cast<const float4*>(a.weight + i0);
-            wt[0] = w4.x; wt[1] = w4.y; wt[2] = w4.z; wt[3] = w4.w;
-        }
+        const CbLeafIn v = nx;
+        if (q + stride < n4) cb_leaf_load<LOSS>(a, (q + stride) << 2, nx);
+        const unsigned int lf[4] = {v.lf4.x, v.lf4.y, v.lf4.z, v.lf4.w};
+        const float ap[4] = {v.a4.x, v.a4.y, v.a4.z, v.a4.w}, tg[4] = {v.t4.x, v.t4.y, v.t4.z, v.t4.w};
+        const float wt[4] = {v.w4.x, v.w4.y, v.w4.z, v.w4.w};
+        const float ed[4] = {v.d4.x, v.d4.y, v.d4.z, v.d4.w}, eh[4] = {v.h4.x, v.h4.y, v.h4.z, v.h4.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             if (i0 + k >= a.n) break;
             const int l = (int)lf[k];
             CbLossOut o;
-            if (a.loss == CB_LOSS_EXTERNAL) { o.der = ed[k]; o.hess = eh[k]; }
-            else o = cb_loss_eval(a.loss, a.p0, a.p1, ap[k] + (a.first ? 0.0f : a.delta[l]), tg[k]);
+            if (loss == CB_LOSS_EXTERNAL) { o.der = ed[k]; o.hess = eh[k]; }
+            else o = cb_loss_eval(loss, a.p0, a.p1, ap[k] + (a.first ? 0.0f : a.delta[l]), tg[k]);
             const float w = wt[k];
+            if (quant) {
+                const float vd = w * o.der, vh = w * o.hess;
+                if (fabsf(vd) <= M0 && fabsf(vh) <= M1) {
+                    const int qd = __float2int_rn(vd * sc0), qh = __float2int_rn(vh * sc1);
+                    int* cell = si + (size_t)(l * 4) * C + lane_copy;
+                    atomicAdd(cell, qd >> 12);
+                    atomicAdd(reinterpret_cast<unsigned int*>(cell + C), (unsigned int)qd & 4095u);
+                    atomicAdd(cell + 2 * C, qh >> 12);
+                    atomicAdd(reinterpret_cast<unsigned int*>(cell + 3 * C), (unsigned int)qh & 4095u);
+                } else {
+                    atomicAdd(&a.sums[3 * l], (double)vd);
+                    atomicAdd(&a.sums[3 * l + 1], (double)vh);
+                }
+                continue;
+            }
+            if (a.vmax && a.first) { mx0 = fmaxf(mx0, fabsf(w * o.der)); mx1 = fmaxf(mx1, fabsf(w * o.hess)); }
             if (use_sh) {
                 float* cell = sl + (size_t)(l * 3) * C + lane_copy;
                 atomicAdd(cell, w * o.der);
@@ -452,7 +539,28 @@ __global__ void __launch_bounds__(512) cb_leaf_pass_kernel(CbLeafArgs a, int C) 
             }
         }
     }
-    if (use_sh) {
+    if (a.vmax && a.first) {
+        for (int off = 16; off > 0; off >>= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        if ((threadIdx.x & 31) == 0) {           // non-negative floats order like their bit patterns
+            atomicMax(reinterpret_cast<int*>(a.vmax), __float_as_int(mx0));
+            atomicMax(reinterpret_cast<int*>(a.vmax) + 1, __float_as_int(mx1));
+        }
+    }
+    if (quant) {
+        __syncthreads();
+        const double inv0 = (double)M0 / 8388607.0, inv1 = (double)M1 / 8388607.0;
+        for (int i = threadIdx.x; i < 2 * L; i += blockDim.x) {
+            const int l = i >> 1, s2 = i & 1;
+            const int* ph = si + (size_t)(l * 4 + 2 * s2) * C;
+            long long hi = 0, lo = 0;
+            for (int c = 0; c < C; ++c) { hi += ph[c]; lo += (unsigned int)ph[C + c]; }
+            const long long q = hi * 4096 + lo;
+            if (q != 0) atomicAdd(&a.sums[3 * l + s2], (double)q * (s2 ? inv1 : inv0));
+        }
+    } else if (use_sh) {
         __syncthreads();
         for (int i = threadIdx.x; i < 3 * L; i += blockDim.x) {
             float v = 0.0f;
@@ -488,7 +596,48 @@ __global__ void __launch_bounds__(512) cb_leaf_pass_kernel(CbLeafArgs a, int C) 
         }
         a.sums[3 * l] = 0.0; a.sums[3 * l + 1] = 0.0; a.sums[3 * l + 2] = 0.0;
     }
-    if (threadIdx.x == 0) *a.counter = 0u;
+    if (threadIdx.x == 0) {
+        *a.counter = 0u;
+        if (a.vmax && a.last) { a.vmax[0] = 0.0f; a.vmax[1] = 0.0f; }
+    }
+}
+
+__global__ void __launch_bounds__(512) cb_leaf_pass_kernel(CbLeafArgs a, int C) { cb_leaf_pass_body<-1>(a, C); }
+template <int LOSS>
+__global__ void __launch_bounds__(512) cb_leaf_pass_kernel_t(CbLeafArgs a, int C) { cb_leaf_pass_body<LOSS>(a, C); }
+
+static int cb_leaf_pass_launch(CbLeafArgs& a, const CbComm* comm, int grid, cudaStream_t st) {
+    if (comm) a.c = *comm; else { a.c.nranks = 1; a.c.rank = 0; }
+    const int planes = a.vmax ? 4 : 3;
+    int C = 32;
+    while (C > 0 && (size_t)planes * a.L * C * 4 > 96 * 1024) C >>= 1;
+    const int smem = planes * a.L * C * 4;
+    static int set = 0;
+    if (!set) {
+        cudaError_t e = cudaFuncSetAttribute(cb_leaf_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_leaf_pass_kernel_t<CB_LOSS_LOGLOSS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_leaf_pass_kernel_t<CB_LOSS_RMSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+        set = 1;
+    }
+    if (a.loss == CB_LOSS_LOGLOSS) cb_leaf_pass_kernel_t<CB_LOSS_LOGLOSS><<<grid, 512, smem, st>>>(a, C);
+    else if (a.loss == CB_LOSS_RMSE) cb_leaf_pass_kernel_t<CB_LOSS_RMSE><<<grid, 512, smem, st>>>(a, C);
+    else cb_leaf_pass_kernel<<<grid, 512, smem, st>>>(a, C);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// Same as cb_leaf_pass with the fixed-point passes switched on: vmax is a device buffer of two floats, zero before the
+// first pass of the first tree; the kernel clears it again at the end of the last pass of every tree.
+CB_API int cb_leaf_pass_q(int loss, float p0, float p1, const float* approx, const float* target, const float* weight,
+                          const unsigned short* leaf, const float* ext_der, const float* ext_hess, long long n, int L,
+                          float* delta, double* sums, unsigned int* counter, int first, int last, int newton, float l2,
+                          float lr, float* cur_vals, float* model_vals, float* model_wts, int Lstride,
+                          const int* iter_ptr, float* leaf_w, const CbComm* comm, float* vmax, int grid,
+                          cudaStream_t st) {
+    CbLeafArgs a{loss, p0, p1, approx, target, weight, leaf, ext_der, ext_hess, n, L, delta, sums, counter,
+                 first, last, newton, l2, lr, cur_vals, model_vals, model_wts, Lstride, iter_ptr, leaf_w, CbComm(), vmax};
+    return cb_leaf_pass_launch(a, comm, grid, st);
 }
 
 CB_API int cb_leaf_pass(int loss, float p0, float p1, const float* approx, const float* target, const float* weight,
@@ -497,7 +646,8 @@ CB_API int cb_leaf_pass(int loss, float p0, float p1, const float* approx, const
                         float lr, float* cur_vals, float* model_vals, float* model_wts, int Lstride,
                         const int* iter_ptr, float* leaf_w, const CbComm* comm, int grid, cudaStream_t st) {
     CbLeafArgs a{loss, p0, p1, approx, target, weight, leaf, ext_der, ext_hess, n, L, delta, sums, counter,
-                 first, last, newton, l2, lr, cur_vals, model_vals, model_wts, Lstride, iter_ptr, leaf_w, CbComm()};
+                 first, last, newton, l2, lr, cur_vals, model_vals, model_wts, Lstride, iter_ptr, leaf_w, CbComm(),
+                 nullptr};
     if (comm) a.c = *comm; else { a.c.nranks = 1; a.c.rank = 0; }
     int C = 32;
     while (C > 0 && (size_t)3 * L * C * 4 > 96 * 1024) C >>= 1;

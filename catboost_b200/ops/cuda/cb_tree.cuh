@@ -690,7 +690,7 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
 }
 
 // ------------------------------------------------------------------------------------------------------
-// Scoring.  One warp per feature; lane owns bins [lane*bpl, lane*bpl + bpl), bpl = ceil(nb/32) <= 8.
+// Scoring.  One warp (or several, splitting the leaves) per feature; bins in chunks of 32, one per lane.
 struct CbScoreArgs {
     CbData d;
     const float* hsrc[CB_MAX_RANKS];   // per-source partial histograms [slots][S][W]; summed in index order
@@ -751,19 +751,44 @@ __device__ __forceinline__ float cb_noise_std(const CbScoreArgs& a) {
     return (float)(a.random_strength * sd * (m / (1.0 + m)));
 }
 
-// Score terms of feature f accumulated over the leaves l0, l0 + lstep, ... into num/den (one warp).
-static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, int lstep, float* num, float* den) {
+// Scoring is written as short rolled loops over 32-bin chunks with its accumulators in shared memory: a level runs
+// this code once, on a handful of warps, straight after a phase that evicted it from the instruction caches, so its
+// run time is the number of instruction lines it has to fetch, not the arithmetic.
+// Per-warp scratch (floats): num[256], den[256], pw[256] (prefix of the weight column), ps[256] (prefix of a
+// derivative column).
+#define CB_SCORE_WARP_FLOATS 1024
+
+// Column `st` of leaf l for the 32 bins of chunk c: summed over the sources, completed from the parent when the leaf
+// is the sibling that was not accumulated, stored into the complete histogram of this level.
+__device__ __forceinline__ float cb_score_load(const CbScoreArgs& a, int l, int p, bool computed, int st, int col0,
+                                               int bin, int nb) {
+    float x = 0.0f;
+    if (bin < nb) {
+        const size_t idx = ((size_t)p * a.S + st) * a.W + col0 + bin;
+        for (int r = 0; r < a.nsrc; ++r) x += __ldcg(a.hsrc[r] + idx);
+        if (!computed) x = a.hprev[idx] - x;
+        if (a.hcur) a.hcur[((size_t)l * a.S + st) * a.W + col0 + bin] = x;
+    }
+    return x;
+}
+
+// Score terms of feature f accumulated over the leaves l0, l0 + lstep, ... into sc[0..255] (num) and sc[256..511]
+// (den); sc[512..] is scratch.  One warp.
+static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, int lstep, float* sc) {
     const int lane = threadIdx.x & 31;
     const int nb = a.d.feat_nb[f];
     const int col0 = a.d.feat_off[f] - a.col_base;
-    const int bpl = (nb + 31) >> 5;
     const bool onehot = a.d.feat_onehot && a.d.feat_onehot[f];
     const int S = a.S;
     const int L = 1 << a.level;
     const int half = L >> 1;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) { num[k] = 0.0f; den[k] = 0.0f; }
-
+    const int bpl = (nb + 31) >> 5;
+    float* num = sc;
+    float* den = sc + 256;
+    float* pw = sc + 512;
+    float* ps = sc + 768;
+    for (int b = lane; b < 512; b += 32) sc[b] = 0.0f;
+    __syncwarp();
     for (int l = l0; l < L; l += lstep) {
         int p = 0;
         bool computed = true;
@@ -772,95 +797,34 @@ static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, 
             const unsigned int right = (unsigned int)l >> (a.level - 1);
             computed = (((a.small_mask[p >> 5] >> (p & 31)) & 1u) == right);
         }
-        if (S == 2) {
-            // both statistic rows of the leaf are fetched before any dependent work (twice the loads in flight)
-            float xw[8], xs[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int bin = lane * bpl + k;
-                xw[k] = 0.0f; xs[k] = 0.0f;
-                if (k < bpl && bin < nb) {
-                    const size_t is = ((size_t)p * 2) * a.W + col0 + bin;
-                    const size_t iw = is + a.W;
-                    float s_ = 0.0f, w_ = 0.0f;
-                    for (int r = 0; r < a.nsrc; ++r) { s_ += a.hsrc[r][is]; w_ += a.hsrc[r][iw]; }
-                    if (!computed) { s_ = a.hprev[is] - s_; w_ = a.hprev[iw] - w_; }
-                    if (a.hcur) {
-                        a.hcur[((size_t)l * 2) * a.W + col0 + bin] = s_;
-                        a.hcur[((size_t)l * 2 + 1) * a.W + col0 + bin] = w_;
-                    }
-                    xs[k] = s_; xw[k] = w_;
-                }
-            }
-            float runw = 0.0f, runs = 0.0f;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                runw += xw[k]; runs += xs[k];
-                if (!onehot) { xw[k] = runw; xs[k] = runs; }
-            }
-            float incw = runw, incs = runs;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const float tw = __shfl_up_sync(0xffffffffu, incw, o);
-                const float ts = __shfl_up_sync(0xffffffffu, incs, o);
-                if (lane >= o) { incw += tw; incs += ts; }
-            }
-            const float exw = onehot ? 0.0f : incw - runw, exs = onehot ? 0.0f : incs - runs;
-            const float totw = __shfl_sync(0xffffffffu, incw, 31), tots = __shfl_sync(0xffffffffu, incs, 31);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                if (k < bpl) {
-                    const float wlk = exw + xw[k], slk = exs + xs[k];
-                    cb_score_add_leaf(a.score_fn, a.l2, slk, fmaxf(wlk, 0.0f), num[k], den[k]);
-                    cb_score_add_leaf(a.score_fn, a.l2, tots - slk, fmaxf(totw - wlk, 0.0f), num[k], den[k]);
-                }
-            }
-            continue;
-        }
-        float wl[8];
-        float wtot = 0.0f;
-        for (int pass = 0; pass < S; ++pass) {
-            const int st = (pass == 0) ? (S - 1) : (pass - 1);   // weight column first
-            float v[8];
+        float totw = 0.0f, exw = 0.0f;
+        for (int pass = 0; pass < S; ++pass) {           // weight column first, then the derivative columns
+            const bool is_w = pass == 0;
+            const int c_st = is_w ? S - 1 : pass - 1;
+            float* pre = is_w ? pw : ps;
+            // lane owns bins [lane * bpl, lane * bpl + bpl): inclusive prefix inside the lane, then one warp scan
             float run = 0.0f;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
+            for (int k = 0; k < bpl; ++k) {
                 const int bin = lane * bpl + k;
-                float x = 0.0f;
-                if (k < bpl && bin < nb) {
-                    const size_t idx = ((size_t)p * S + st) * a.W + col0 + bin;
-                    for (int r = 0; r < a.nsrc; ++r) x += a.hsrc[r][idx];
-                    if (!computed) x = a.hprev[idx] - x;
-                    if (a.hcur) a.hcur[((size_t)l * S + st) * a.W + col0 + bin] = x;
-                }
+                const float x = cb_score_load(a, l, p, computed, c_st, col0, bin, nb);
                 run += x;
-                v[k] = onehot ? x : run;     // inclusive prefix inside the lane
+                pre[bin] = onehot ? x : run;
             }
-            // exclusive scan of lane totals
             float inc = run;
-#pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const float t = __shfl_up_sync(0xffffffffu, inc, o);
                 if (lane >= o) inc += t;
             }
-            const float excl = inc - run;
+            const float excl = onehot ? 0.0f : inc - run;
             const float total = __shfl_sync(0xffffffffu, inc, 31);
-            if (pass == 0) {
-                wtot = total;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) wl[k] = onehot ? v[k] : (excl + v[k]);
-            } else {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    if (k < bpl) {
-                        const float sl = onehot ? v[k] : (excl + v[k]);
-                        const float sr = total - sl;
-                        const float wL = fmaxf(wl[k], 0.0f);
-                        const float wR = fmaxf(wtot - wl[k], 0.0f);
-                        cb_score_add_leaf(a.score_fn, a.l2, sl, wL, num[k], den[k]);
-                        cb_score_add_leaf(a.score_fn, a.l2, sr, wR, num[k], den[k]);
-                    }
-                }
+            if (is_w) { totw = total; exw = excl; continue; }
+            for (int k = 0; k < bpl; ++k) {
+                const int bin = lane * bpl + k;
+                const float slk = excl + ps[bin], wlk = exw + pw[bin];
+                float n_ = num[bin], d_ = den[bin];
+                cb_score_add_leaf(a.score_fn, a.l2, slk, fmaxf(wlk, 0.0f), n_, d_);
+                cb_score_add_leaf(a.score_fn, a.l2, total - slk, fmaxf(totw - wlk, 0.0f), n_, d_);
+                num[bin] = n_; den[bin] = d_;
             }
         }
     }
@@ -871,33 +835,27 @@ static __device__ void cb_score_finalize(const CbScoreArgs& a, int f, const floa
     const int lane = threadIdx.x & 31;
     const int nb = a.d.feat_nb[f];
     const float fw = a.d.feat_weight ? a.d.feat_weight[f] : 1.0f;
-    const int bpl = (nb + 31) >> 5;
     const bool onehot = a.d.feat_onehot && a.d.feat_onehot[f];
     unsigned long long best = 0ull;
     if (fw > 0.0f) {
         const int ncand = onehot ? nb : nb - 1;
         const unsigned long long it = (unsigned long long)(*a.iter_ptr);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const int bin = lane * bpl + k;
-            if (k < bpl && bin < ncand) {
-                float sc;
-                if (a.score_fn == CB_SCORE_COSINE) sc = (den[k] > 1e-15f) ? num[k] * rsqrtf(den[k] + 1e-10f) : -3.0e38f;
-                else sc = num[k];
-                const unsigned int gb = (unsigned int)(a.d.feat_off[f] + bin);
-                if (noise_std > 0.0f) {
-                    const unsigned long long h = cb_mix64(a.seed ^ cb_mix64((it << 8) + a.level) ^ ((unsigned long long)gb * 0x9E3779B97F4A7C15ull));
-                    sc += cb_normal(h) * noise_std;
-                }
-                sc *= fw;
-                if (sc == sc) {
-                    const unsigned long long key = ((unsigned long long)cb_float_to_ordered(sc) << 32) | (unsigned long long)(0xFFFFFFFFu - gb);
-                    best = key > best ? key : best;
-                }
+        for (int bin = lane; bin < ncand; bin += 32) {
+            float sc;
+            if (a.score_fn == CB_SCORE_COSINE) sc = (den[bin] > 1e-15f) ? num[bin] * rsqrtf(den[bin] + 1e-10f) : -3.0e38f;
+            else sc = num[bin];
+            const unsigned int gb = (unsigned int)(a.d.feat_off[f] + bin);
+            if (noise_std > 0.0f) {
+                const unsigned long long h = cb_mix64(a.seed ^ cb_mix64((it << 8) + a.level) ^ ((unsigned long long)gb * 0x9E3779B97F4A7C15ull));
+                sc += cb_normal(h) * noise_std;
+            }
+            sc *= fw;
+            if (sc == sc) {
+                const unsigned long long key = ((unsigned long long)cb_float_to_ordered(sc) << 32) | (unsigned long long)(0xFFFFFFFFu - gb);
+                best = key > best ? key : best;
             }
         }
     }
-#pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const unsigned long long t = __shfl_xor_sync(0xffffffffu, best, o);
         best = t > best ? t : best;
@@ -905,61 +863,47 @@ static __device__ void cb_score_finalize(const CbScoreArgs& a, int f, const floa
     if (lane == 0 && best) atomicMax(a.best_key, best);
 }
 
-// `red` is scratch shared memory of `red_floats` floats (the histogram tile is no longer needed at this point).
-// With fewer features than blocks a whole block scores one feature: its warps split the leaves and their partial
-// terms are summed through `red`, so the per-feature chain of dependent loads is L / warps long instead of L.
-static __device__ void cb_score_phase(const CbScoreArgs& a, int cta, int ncta, float* red, int red_floats) {
-    const int warps_per_cta = blockDim.x >> 5;
+// `red` is scratch shared memory of `red_floats` floats (the histogram tile is no longer needed at this point), at
+// least CB_SCORE_WARP_FLOATS per scoring warp.  With fewer features than warps several warps score one feature: they
+// split the leaves and the first of them adds the partial terms up, so the per-feature chain of dependent loads is
+// L / warps long instead of L.
+static __device__ void cb_score_phase(const CbScoreArgs& a, int cta, int ncta, float* red, int red_floats,
+                                      unsigned long long* ts = nullptr) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const float noise_std = cb_noise_std(a);
+    int wpc = min((int)(blockDim.x >> 5), red_floats / CB_SCORE_WARP_FLOATS);    // scoring warps per block
+    float noise_std = 0.0f;
+    if (a.random_strength > 0.0f) {
+        if (lane == 0) noise_std = cb_noise_std(a);
+        noise_std = __shfl_sync(0xffffffffu, noise_std, 0);
+    }
+    if (ts) ts[0] = cb_globaltimer();
     const int nf = a.f_end - a.f_begin;
     const int L = 1 << a.level;
+    if (wpc < 1 || nf <= 0) return;
     // warps per feature: as many as there are idle warps in the grid (power of two, at most one per leaf)
     int wpf = 1;
-    while (wpf * 2 <= min(warps_per_cta, L) && (long long)nf * wpf * 2 <= (long long)ncta * warps_per_cta &&
-           warps_per_cta * 512 <= red_floats)
-        wpf *= 2;
-    float num[8], den[8];
-    if (nf > 0 && wpf > 1) {
-        const int fpc = warps_per_cta / wpf;            // features per block and round
-        const int slot = warp / wpf, sub = warp - slot * wpf;
-        for (int fbase = a.f_begin + cta * fpc; fbase < a.f_end; fbase += ncta * fpc) {
-            const int f = fbase + slot;
-            const bool have = f < a.f_end;
-            int bpl = 0;
-            if (have) {
-                cb_score_accumulate(a, f, sub, wpf, num, den);
-                bpl = (a.d.feat_nb[f] + 31) >> 5;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    if (k < bpl) {
-                        red[(warp * 2) * 256 + lane * bpl + k] = num[k];
-                        red[(warp * 2 + 1) * 256 + lane * bpl + k] = den[k];
-                    }
-                }
+    while (wpf * 2 <= min(wpc, L) && (long long)nf * wpf * 2 <= (long long)ncta * wpc) wpf *= 2;
+    const int fpc = wpc / wpf;                           // features per block and round
+    const int slot = warp / wpf, sub = warp - slot * wpf;
+    float* sc = red + (size_t)warp * CB_SCORE_WARP_FLOATS;
+    for (int fbase = a.f_begin + cta * fpc; fbase < a.f_end; fbase += ncta * fpc) {
+        const int f = fbase + slot;
+        const bool have = slot < fpc && f < a.f_end;
+        if (have) cb_score_accumulate(a, f, sub, wpf, sc);
+        if (ts) ts[1] = cb_globaltimer();
+        if (wpf > 1) __syncthreads();
+        if (have && sub == 0) {
+            const int nb = a.d.feat_nb[f];
+            for (int w = 1; w < wpf; ++w) {
+                const float* o = sc + (size_t)w * CB_SCORE_WARP_FLOATS;
+                for (int bin = lane; bin < nb; bin += 32) { sc[bin] += o[bin]; sc[256 + bin] += o[256 + bin]; }
             }
-            __syncthreads();
-            if (have && sub == 0) {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    num[k] = 0.0f; den[k] = 0.0f;
-                    if (k < bpl) {
-                        for (int w = warp; w < warp + wpf; ++w) {
-                            num[k] += red[(w * 2) * 256 + lane * bpl + k];
-                            den[k] += red[(w * 2 + 1) * 256 + lane * bpl + k];
-                        }
-                    }
-                }
-                cb_score_finalize(a, f, num, den, noise_std);
-            }
-            __syncthreads();
+            __syncwarp();
+            cb_score_finalize(a, f, sc, sc + 256, noise_std);
         }
-        return;
+        if (wpf > 1) __syncthreads();
     }
-    for (int f = a.f_begin + cta * warps_per_cta + warp; f < a.f_end; f += ncta * warps_per_cta) {
-        cb_score_accumulate(a, f, 0, 1, num, den);
-        cb_score_finalize(a, f, num, den, noise_std);
-    }
+    if (ts) ts[2] = cb_globaltimer();
 }
 
 // ------------------------------------------------------------------------------------------------------

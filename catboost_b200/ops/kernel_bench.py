@@ -116,7 +116,15 @@ def main(argv=None):
                              eng.L, P(eng.delta), P(eng.sums), P(eng.counter), 1, 0, 1, 3.0, 0.1, P(eng.cur_vals), None,
                              None, eng.L, P(eng.iter_ptr), P(eng.leaf_w), None, sm * 2, st())
         ms = _time(leaf_pass, args.reps, flush)
-        report("cb_leaf_pass_kernel", ms, n * (4 + 4 + 2), "approx, target, leaf")
+        report("cb_leaf_pass_kernel", ms, n * (4 + 4 + 2), "first pass of a tree (fp32 cells): approx, target, leaf")
+        vmax = torch.tensor([1.0, 0.25], dtype=torch.float32, device=dev)
+
+        def leaf_pass_q():
+            lib.cb_leaf_pass_q(eng.loss_id, eng.p0, eng.p1, P(eng.approx), P(eng.target), None, P(eng.leaf), None, None, n,
+                               eng.L, P(eng.delta), P(eng.sums), P(eng.counter), 0, 0, 1, 3.0, 0.1, P(eng.cur_vals), None,
+                               None, eng.L, P(eng.iter_ptr), P(eng.leaf_w), None, P(vmax), sm * 2, st())
+        ms = _time(leaf_pass_q, args.reps, flush)
+        report("cb_leaf_pass_kernel[newton step]", ms, n * (4 + 4 + 2), "later pass (fixed-point cells): approx, target, leaf")
     if want("update_leaf"):
         ms = _time(lambda: lib.cb_update_leaf(ctypes.c_void_p(store.handle), P(eng.leaf), P(eng.splits), P(eng.iter_ptr),
                                               eng.depth, 0, sm * 8, st()), args.reps, flush)

@@ -111,6 +111,7 @@ class GpuObliviousEngine:
             self.weight = torch.zeros(npad, dtype=f32, device=dev)
             self.weight[:n] = weight.to(dev, f32)
         self.leaf = torch.zeros(npad, dtype=torch.int16, device=dev)
+        self.leaf_vmax = torch.zeros(2, dtype=f32, device=dev)
         self.stats = torch.zeros((self.S, npad), dtype=f32, device=dev)
         self.scal = torch.zeros(4, dtype=f64, device=dev)
         self.iter_ptr = torch.zeros(1, dtype=i32, device=dev)
@@ -220,13 +221,19 @@ class GpuObliviousEngine:
 
     def enable_phase_timing(self):
         """Record globaltimer stamps of the fused kernel's phases (block 0) for every level of the latest tree."""
-        self.phase_ts = torch.zeros(self.depth * 8 + 2 * 4096, dtype=torch.int64, device=self.dev)
+        self.phase_ts = torch.zeros(self.depth * 8 + 2 * 4096 + self.depth * 4, dtype=torch.int64, device=self.dev)
         self.lib.cb_fused_set_phase_ts(ctypes.c_void_p(self.plan), _p(self.phase_ts))
 
     def phase_times_us(self):
         """[depth][6] microseconds: leaf update, histogram, wait for grid, reduce+push(+peer wait), score, select."""
         t = self.phase_ts[: self.depth * 8].view(self.depth, 8).cpu().numpy().astype(np.float64)
         return (t[:, 1:7] - t[:, 0:6]) / 1000.0
+
+    def score_phase_times_us(self):
+        """[depth][3] microseconds inside the score phase of block 0: noise scale, first accumulate, until its end."""
+        t = self.phase_ts[: self.depth * 8].view(self.depth, 8).cpu().numpy().astype(np.float64)
+        s = self.phase_ts[self.depth * 8 + 8192:].view(self.depth, 4).cpu().numpy().astype(np.float64)
+        return np.stack([s[:, 0] - t[:, 4], s[:, 1] - s[:, 0], s[:, 2] - s[:, 1]], 1) / 1000.0
 
     def block_finish_times(self):
         """(histogram end time relative to the level start in us, SM id) per block at level depth-2."""
@@ -302,12 +309,13 @@ class GpuObliviousEngine:
             return
         for it in range(self.leaf_iterations):
             last = 1 if it == self.leaf_iterations - 1 else 0
-            chk(lib.cb_leaf_pass(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target), _p(self.weight),
-                                 _p(self.leaf), _p(self.ext_der), _p(self.ext_hess), self.n, self.L, _p(self.delta),
-                                 _p(self.sums), _p(self.counter), 1 if it == 0 else 0, last, self.leaf_newton, self.l2,
-                                 self.lr, _p(self.cur_vals), _p(self.model_vals), _p(self.model_wts), self.L,
-                                 _p(self.iter_ptr), _p(self.leaf_w), comm, self.sm_count * 2, self._stream()),
-                "cb_leaf_pass")
+            chk(lib.cb_leaf_pass_q(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target), _p(self.weight),
+                                   _p(self.leaf), _p(self.ext_der), _p(self.ext_hess), self.n, self.L, _p(self.delta),
+                                   _p(self.sums), _p(self.counter), 1 if it == 0 else 0, last, self.leaf_newton,
+                                   self.l2, self.lr, _p(self.cur_vals), _p(self.model_vals), _p(self.model_wts), self.L,
+                                   _p(self.iter_ptr), _p(self.leaf_w), comm,
+                                   _p(self.leaf_vmax) if self.quantized_hist and self.leaf_iterations > 1 else None,
+                                   self.sm_count * 2, self._stream()), "cb_leaf_pass")
             self.launches_per_iter += 1
 
     def _leaf_pass_nccl(self, it):
