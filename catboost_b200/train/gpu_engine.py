@@ -55,7 +55,8 @@ class GpuObliviousEngine:
                  eval_sets: Optional[List[EvalSet]] = None, use_graph: bool = True, threads: int = 512,
                  ext_der: Optional[torch.Tensor] = None, ext_hess: Optional[torch.Tensor] = None,
                  timeout_s: float = 20.0, quantized_hist: bool = True, dynamic_work: bool = True,
-                 der_fn=None, zero_mean_leaves: bool = False, max_bundle: int = 8):
+                 der_fn=None, zero_mean_leaves: bool = False, max_bundle: int = 8,
+                 fused_leaf_steps: bool = True):
         assert store.bins.is_cuda, "GpuObliviousEngine needs a CUDA store"
         if depth > 16:
             raise ValueError("depth must be <= 16")
@@ -112,6 +113,8 @@ class GpuObliviousEngine:
             self.weight[:n] = weight.to(dev, f32)
         self.leaf = torch.zeros(npad, dtype=torch.int16, device=dev)
         self.leaf_vmax = torch.zeros(2, dtype=f32, device=dev)
+        self.leaf_grid = None
+        self.fused_leaf_steps = bool(fused_leaf_steps)
         self.stats = torch.zeros((self.S, npad), dtype=f32, device=dev)
         self.scal = torch.zeros(4, dtype=f64, device=dev)
         self.iter_ptr = torch.zeros(1, dtype=i32, device=dev)
@@ -306,6 +309,17 @@ class GpuObliviousEngine:
             # NCCL baseline: sums are all-reduced between two kernels
             for it in range(self.leaf_iterations):
                 self._leaf_pass_nccl(it)
+            return
+        if self.leaf_grid is None:
+            self.leaf_grid = int(lib.cb_leaf_newton_max_grid(self.L)) if self.der_fn is None and self.loss_id != 100 else 0
+        if self.leaf_grid > 0 and self.fused_leaf_steps:
+            # all steps of the leaf estimation in one cooperative launch
+            chk(lib.cb_leaf_newton(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target), _p(self.weight),
+                                   _p(self.leaf), self.n, self.L, _p(self.delta), _p(self.sums), _p(self.leaf_vmax),
+                                   self.leaf_iterations, self.leaf_newton, self.l2, self.lr, _p(self.cur_vals),
+                                   _p(self.model_vals), _p(self.model_wts), self.L, _p(self.iter_ptr), _p(self.leaf_w),
+                                   comm, self.leaf_grid, self._stream()), "cb_leaf_newton")
+            self.launches_per_iter += 1
             return
         for it in range(self.leaf_iterations):
             last = 1 if it == self.leaf_iterations - 1 else 0
