@@ -10,9 +10,9 @@ A "step" is one boosting iteration.  Two numbers are reported:
 
 * ``value``     -- K iterations of the device-resident trainer, each bracketed by CUDA events (L2 flushed between
                    iterations with a 512 MiB write that is not timed), max over ranks.
-* ``e2e.value`` -- the same metric through the public API (``CatBoostClassifier.fit`` on host data), including the
-                   host->device upload of the feature matrix from pinned memory, quantisation, and a device->host
-                   read of the learn loss every iteration.
+* ``e2e.value`` -- the same metric through the public API: wall seconds of one ``CatBoostClassifier.fit`` of 1000
+                   iterations on host data, including the host->device upload of the feature matrix from pinned
+                   memory, border selection, quantisation, and a device->host read of the learn loss every iteration.
 """
 from __future__ import annotations
 
@@ -124,7 +124,7 @@ def reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default="higgs", choices=sorted(CONFIGS))
     ap.add_argument("--rows", type=int, default=0)
@@ -133,6 +133,8 @@ def main():
     ap.add_argument("--cells", default="narrow", choices=["narrow", "wide", "float"],
                     help="shared-memory histogram cells: one int32, hi/lo int32 pair, or fp32")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-iters", type=int, default=0,
+                    help="boosting iterations of the end-to-end fit() (default 1000: the metric's own iteration count)")
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--phases", action="store_true", help="print per-phase times of the fused level kernel")
     args = ap.parse_args()
@@ -235,7 +237,7 @@ def main():
     e2e = None
     if not args.no_e2e:
         Xp = torch.from_numpy(X).pin_memory().numpy() if hasattr(torch.Tensor, "pin_memory") else X
-        e2e_iters = max(K + W, 100)
+        e2e_iters = args.e2e_iters if args.e2e_iters > 0 else (1000 if args.config != "small" else 200)
         params_e2e = dict(params, iterations=e2e_iters)
         model = cb.CatBoostClassifier(**params_e2e, verbose=True, metric_period=1)
         devnull = open(os.devnull, "w")

@@ -12,6 +12,7 @@ Binned store layout (replaces the reference's compressed index, catboost/cuda/gp
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass, field
 from typing import List, Optional
 
@@ -73,8 +74,9 @@ def build_quantization(pool, border_count: int = 254, border_type: str = "Greedy
     if nan_mode not in ("Min", "Max", "Forbidden"):
         raise CatBoostError(f"unknown nan_mode {nan_mode!r}")
     if n > MAX_SAMPLE_FOR_BORDERS:
-        rng = np.random.RandomState(seed)
-        idx = np.sort(rng.choice(n, MAX_SAMPLE_FOR_BORDERS, replace=False))
+        # Floyd's sampler of the Generator API: O(sample), where RandomState.choice permutes all n rows
+        rng = np.random.default_rng(seed)
+        idx = np.sort(rng.choice(n, MAX_SAMPLE_FOR_BORDERS, replace=False, shuffle=False))
         sample = X[idx]
     else:
         sample = X
@@ -205,6 +207,9 @@ def make_store(features: List[FlatFeature], n: int, device, feature_weights=None
     return store
 
 
+LAST_QUANTIZE = {"kernel": None}       # which device kernel the latest quantize_floats_into call used
+
+
 def quantize_floats_into(store: BinnedStore, X: np.ndarray, quant: FeatureQuantization, flat_begin: int = 0,
                          float_subset: Optional[List[int]] = None, chunk_rows: int = 0, pinned: bool = True):
     """Bin the float columns of ``X`` (host, float32 row-major) into flat features
@@ -242,6 +247,9 @@ def quantize_floats_into(store: BinnedStore, X: np.ndarray, quant: FeatureQuanti
         chunk_rows = max(1, (256 << 20) // max(1, 4 * ld))     # ~256 MiB staging chunks
     stream = torch.cuda.current_stream(dev)
     copied = 0
+    use_tma = os.environ.get("CB200_QUANTIZE_TMA", "1") != "0"
+    used_tma = False
+    d_status = torch.zeros(1, dtype=torch.int32, device=dev)
     xt = torch.from_numpy(X)
     for r0 in range(0, n, chunk_rows):
         r1 = min(n, r0 + chunk_rows)
@@ -253,10 +261,24 @@ def quantize_floats_into(store: BinnedStore, X: np.ndarray, quant: FeatureQuanti
                 pass
         d_chunk = src.to(dev, non_blocking=True)
         copied += (r1 - r0) * ld * 4
-        native.cuda_check(lib.cb_quantize(_ptr(d_chunk), r1 - r0, F, d_chunk.stride(0), _ptr(d_borders), _ptr(d_boff),
-                                          _ptr(d_nan), _ptr(store.bins[g0:]), store.npad, r0,
-                                          ctypes.c_void_p(stream.cuda_stream)), "cb_quantize")
+        rc = -2
+        if use_tma:
+            # tiled bulk copies into shared memory (needs a 16-byte aligned base and row pitch)
+            rc = lib.cb_quantize_tma(_ptr(d_chunk), r1 - r0, F, d_chunk.stride(0), _ptr(d_borders), _ptr(d_boff),
+                                     _ptr(d_nan), _ptr(store.bins[g0:]), store.npad, r0, _ptr(d_status),
+                                     ctypes.c_void_p(stream.cuda_stream))
+            if rc not in (0, -2):
+                native.cuda_check(rc, "cb_quantize_tma")
+        if rc == -2:
+            native.cuda_check(lib.cb_quantize(_ptr(d_chunk), r1 - r0, F, d_chunk.stride(0), _ptr(d_borders),
+                                              _ptr(d_boff), _ptr(d_nan), _ptr(store.bins[g0:]), store.npad, r0,
+                                              ctypes.c_void_p(stream.cuda_stream)), "cb_quantize")
+        else:
+            used_tma = True
         d_chunk.record_stream(stream)
+    LAST_QUANTIZE["kernel"] = "tma" if used_tma else "plain"
+    if used_tma and int(d_status.item()) != 0:
+        raise RuntimeError(f"cb_quantize_tma: a bulk copy did not arrive in time (status {int(d_status.item()):#x})")
     return copied
 
 

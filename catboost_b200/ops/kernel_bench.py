@@ -106,6 +106,17 @@ def main(argv=None):
         ms = _time(lambda: lib.cb_quantize(P(xd), n, F, xd.stride(0), P(borders), P(boff), P(nanm), P(tmp), store.npad, 0,
                                            st()), args.reps, flush)
         report("cb_quantize_kernel", ms, n * F * 4 + n * ((F + 3) // 4) * 4, "float32 rows -> packed bins")
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        plain = tmp.clone()
+        tmp.zero_()
+        rc = lib.cb_quantize_tma(P(xd), n, F, xd.stride(0), P(borders), P(boff), P(nanm), P(tmp), store.npad, 0, P(status),
+                                 st())
+        if rc == 0:
+            ms = _time(lambda: lib.cb_quantize_tma(P(xd), n, F, xd.stride(0), P(borders), P(boff), P(nanm), P(tmp),
+                                                   store.npad, 0, P(status), st()), args.reps, flush)
+            report("cb_quantize_tma_kernel", ms, n * F * 4 + n * ((F + 3) // 4) * 4,
+                   f"tiled bulk copies into shared memory; status {int(status.item())}; equal to plain kernel: "
+                   f"{bool(torch.equal(tmp, plain))}")
         del xd, tmp
     if want("grad"):
         ms = _time(lambda: eng._grad(), args.reps, flush)

@@ -44,6 +44,10 @@ class TrainResult:
 
 
 # ---------------------------------------------------------------------------------------------------------
+def _unique_labels(lab: np.ndarray) -> np.ndarray:
+    return np.unique(np.asarray(lab))
+
+
 class LabelCodec:
     """Target preparation: class-name mapping, target border, class weights
     (catboost/private/libs/labels/label_converter.cpp, target/data_providers.cpp)."""
@@ -61,7 +65,7 @@ class LabelCodec:
                 self.class_names = [0, 1]
             else:
                 self.border = None
-                uniq = sorted(set().union(*ctx.all_gather_object(set(np.unique(lab).tolist()))))
+                uniq = sorted(set().union(*ctx.all_gather_object(set(_unique_labels(lab).tolist()))))
                 if o.class_names is not None:
                     uniq = list(o.class_names)
                 if len(uniq) > 2:
@@ -71,7 +75,7 @@ class LabelCodec:
                     raise CatBoostError("target contains only one unique value")
                 self.class_names = uniq if len(uniq) == 2 else (uniq + [uniq[0] if not uniq else uniq[0]])[:2]
         elif self.is_multiclass:
-            uniq = sorted(set().union(*ctx.all_gather_object(set(np.unique(lab).tolist()))))
+            uniq = sorted(set().union(*ctx.all_gather_object(set(_unique_labels(lab).tolist()))))
             if o.class_names is not None:
                 uniq = list(o.class_names)
             if o.classes_count:
@@ -83,6 +87,22 @@ class LabelCodec:
 
     def _map(self, lab: np.ndarray) -> np.ndarray:
         names = self.class_names
+        # few numeric classes: one vectorised comparison per class (a search per label costs a second per 10M rows)
+        if lab.dtype.kind in "fiub" and lab.size and len(names) <= 32 and \
+                all(isinstance(v, (int, float, np.integer, np.floating)) for v in names):
+            out = np.zeros(lab.shape, dtype=np.float32)
+            hits = 0
+            for i, v in enumerate(names):
+                m = lab == v
+                hits += int(np.count_nonzero(m))
+                if i == 1:
+                    out += m
+                elif i:
+                    out += m.astype(np.float32) * np.float32(i)
+            if hits != lab.size:
+                bad = lab[~np.isin(lab, np.asarray(names, dtype=lab.dtype))]
+                raise CatBoostError(f"label {bad[0]!r} was not seen in the training data")
+            return out
         try:
             arr = np.asarray(names, dtype=lab.dtype if lab.dtype.kind in "fiub" else None)
             order = np.argsort(arr, kind="stable")

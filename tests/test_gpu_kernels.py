@@ -36,6 +36,22 @@ def test_quantize_matches_searchsorted():
         assert torch.equal(got, ref), f"feature {f}"
 
 
+@pytest.mark.parametrize("n,F", [(5000, 8), (70001, 28), (3001, 72)])
+def test_quantize_tma_matches_searchsorted(n, F):
+    """Row pitch a multiple of 16 bytes: the tiled-bulk-copy kernel is used; several feature boxes, ragged last tile."""
+    from catboost_b200.data import quantization as Q
+    X, y, plan, store = _store(n=n, F=F, border_count=64)
+    assert Q.LAST_QUANTIZE["kernel"] == "tma"
+    bins = store.bins.cpu().numpy()
+    q = plan.quant
+    for f in range(F):
+        col = X[:, f]
+        ref = np.searchsorted(q.borders[f], col, side="left")
+        ref[np.isnan(col)] = len(q.borders[f]) if q.nan_is_max[f] else 0
+        got = (bins[f // 4, :n].view(np.uint32) >> (8 * (f % 4))) & 255
+        assert np.array_equal(got, ref.astype(np.uint32)), f
+
+
 @pytest.mark.parametrize("nslots,S", [(1, 2), (8, 2), (5, 3), (64, 2)])
 def test_hist_matches_reference(nslots, S):
     from catboost_b200.ops import api as ops
