@@ -93,7 +93,9 @@ class Model:
 
     # ------------------------------------------------------------------ construction helpers
     def split_index(self, sp: Split) -> int:
-        cache = self.__dict__.setdefault("_split_cache", {s.key(): i for i, s in enumerate(self.splits)})
+        cache = self.__dict__.get("_split_cache")
+        if cache is None or len(cache) != len(self.splits):
+            cache = self.__dict__["_split_cache"] = {s.key(): i for i, s in enumerate(self.splits)}
         k = sp.key()
         if k not in cache:
             cache[k] = len(self.splits)

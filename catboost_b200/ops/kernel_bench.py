@@ -154,8 +154,8 @@ def main(argv=None):
     if want("fused"):
         for level in range(args.depth):
             ms = _time(lambda: eng._level_fused(level), args.reps, flush)
-            report(f"cb_level_fused_kernel[level={level}]", ms, n * ((F + 3) // 4) * (4 + 2 + 8),
-                   "bytes requested by the histogram phase (leaf/stat rows are re-read per feature group)")
+            report(f"cb_level_fused_kernel[level={level}]", ms, n * (((F + 3) // 4) * 4 + 2 + 8),
+                   "whole level (leaf update, histogram, reduce, score, select); bytes = one pass over bins, leaf, stats")
     if want("predict"):
         model_eng = eng
         sp, vals, wts = model_eng.finish()
