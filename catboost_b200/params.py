@@ -48,7 +48,7 @@ DEFAULTS: Dict[str, Any] = dict(
     text_processing=None, embedding_features=None, eval_fraction=None, fixed_binary_splits=None,
     data_partition=None, permutation_count=None, min_fold_size=100, cat_features=None, scale_pos_weight=None,
     gpu_cat_features_storage="GpuRam", observations_to_bootstrap="TestOnly", fused_levels=True,
-    histogram_reduce="fused", histogram_cells="narrow", node_type="SingleHost", callback=None,
+    histogram_reduce="fused", histogram_cells="narrow", bayesian_matrix_reg=0.1, node_type="SingleHost", callback=None,
 )
 
 GPU_ONLY = {"gpu_ram_part", "pinned_memory_size", "gpu_cat_features_storage", "data_partition", "fold_len_multiplier",

@@ -110,6 +110,11 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
     octx = ObjectiveContext(train_pool, dev)
     eval_approx = [torch.from_numpy(np.ascontiguousarray(b)).to(dev, f32) for b in base_evals]
     learner = GenericLearner(store, o, dims, ctx, seed=int(o.random_seed))
+    plearner = None
+    if getattr(objective, "pairwise_scoring", False) and o.grow_policy == "SymmetricTree" and \
+            not (ctx is not None and ctx.is_distributed):
+        from .pairwise import PairwiseLearner
+        plearner = PairwiseLearner(store, o, seed=int(o.random_seed))
     ordered = None
     if o.boosting_type == "Ordered" and not (ctx is not None and ctx.is_distributed):
         ordered = OrderedState(o, n, train_pool, dev, approx[:, :n])
@@ -143,10 +148,19 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
             if o.langevin:
                 coef = math.sqrt(2.0 / (float(o.learning_rate) * float(o.diffusion_temperature)))
                 der_p[:, :n] += learner._randn((dims, n)) * coef
-        with prof.span("structure"):
-            tr = learner.build_tree(der_p, hess_p, wpad, it)
-        with prof.span("leaves"):
-            vals, wts = estimate_leaves(objective, approx, target, weight, tr.leaf, tr.n_leaves, n, o, ctx, octx)
+        if plearner is not None:
+            # pairwise losses: the split score and the leaf values come from linear systems over all leaves
+            with prof.span("structure"):
+                wi_, li_, g_, h_ = objective.pair_terms(approx[:, :n], target, weight, octx)
+                der1 = torch.zeros(n, dtype=f32, device=dev).index_add_(0, wi_, g_).index_add_(0, li_, -g_)
+                tr = plearner.build_tree(wi_, li_, h_, der1, it)
+            with prof.span("leaves"):
+                vals, wts = plearner.leaf_values(tr.n_leaves, wi_, li_, h_, der1, float(o.learning_rate))
+        else:
+            with prof.span("structure"):
+                tr = learner.build_tree(der_p, hess_p, wpad, it)
+            with prof.span("leaves"):
+                vals, wts = estimate_leaves(objective, approx, target, weight, tr.leaf, tr.n_leaves, n, o, ctx, octx)
         tv = torch.from_numpy(vals).to(dev, f32)
         if ordered is not None:
             ordered.update(der, hess, weight, tr.leaf, tr.n_leaves, o)

@@ -143,6 +143,21 @@ class PairLogit(_GroupObjective):
             der, hess = lay.scatter(d, n), lay.scatter(hh, n)
         return der.unsqueeze(0), hess.clamp_min(1e-16).unsqueeze(0)
 
+    def pair_terms(self, approx, target, weight, ctx=None):
+        """(winner doc, loser doc, gradient magnitude g, second derivative h) of every pair: the winner's derivative
+        gets +g, the loser's -g.  Used by the pairwise structure search."""
+        a = approx[0]
+        if ctx is not None and ctx.pairs is not None:
+            wi, li, pw = ctx.pairs[:, 0], ctx.pairs[:, 1], ctx.pairs_weight.float()
+        else:
+            lay = _layout(ctx)
+            pm = _make_pairs_from_labels(lay, target)                 # [q, i, j]: i beats j
+            q, i, j = pm.nonzero(as_tuple=True)
+            wi, li = lay.index[q, i], lay.index[q, j]
+            pw = torch.ones(wi.shape[0], device=a.device)
+        p = torch.sigmoid(a[li] - a[wi])
+        return wi, li, pw * p, pw * p * (1 - p)
+
     def value(self, approx, target, weight, ctx=None):
         return float("nan")
 
@@ -197,6 +212,42 @@ class YetiRank(_GroupObjective):
             W = lay.gather(weight)
             der, hess = der * W, hess * W
         return lay.scatter(der, n).unsqueeze(0), lay.scatter(hess, n).clamp_min(1e-16).unsqueeze(0)
+
+    def pair_terms(self, approx, target, weight, ctx=None):
+        """Pairs of neighbours in ``permutations`` noisy orderings, as (winner, loser, g, h); see PairLogit.pair_terms."""
+        lay = _layout(ctx)
+        a = approx[0]
+        dev = a.device
+        if self._gen is None:
+            self._gen = torch.Generator(device="cpu")
+            self._gen.manual_seed(20240229)
+        A = lay.gather(a, -1e30)
+        T = lay.gather(target)
+        Q, L = lay.Q, lay.Lmax
+        empty = torch.zeros(0, dtype=torch.long, device=dev)
+        if L < 2:
+            return empty, empty, torch.zeros(0, device=dev), torch.zeros(0, device=dev)
+        decay_pow = self.decay ** torch.arange(L - 1, device=dev, dtype=torch.float32)
+        out = []
+        for _ in range(self.permutations):
+            u = torch.rand((Q, L), generator=self._gen).to(dev).clamp(1e-6, 1 - 1e-6)
+            noisy = A + torch.log(u / (1.000001 - u))
+            noisy = torch.where(lay.mask, noisy, torch.full_like(noisy, -1e30))
+            order = torch.argsort(noisy, dim=1, descending=True, stable=True)
+            first, second = order[:, :-1], order[:, 1:]
+            valid = lay.mask.gather(1, first) & lay.mask.gather(1, second)
+            t1, t2 = T.gather(1, first), T.gather(1, second)
+            wgt = 0.15 * decay_pow.unsqueeze(0) * (t1 - t2).abs() * valid
+            win = torch.where(t1 > t2, first, second)
+            los = torch.where(t1 > t2, second, first)
+            keep = wgt > 0
+            wdoc, ldoc = lay.index.gather(1, win)[keep], lay.index.gather(1, los)[keep]
+            w = wgt[keep] / self.permutations
+            if weight is not None:
+                w = w * weight[wdoc]
+            p = torch.sigmoid(a[ldoc] - a[wdoc])
+            out.append((wdoc, ldoc, w * p, w * p * (1 - p)))
+        return tuple(torch.cat([o[k] for o in out]) for k in range(4))
 
     def value(self, approx, target, weight, ctx=None):
         return float("nan")
@@ -277,4 +328,5 @@ def make_ranking_objective(loss, params):
         return None
     obj = cls(params)
     obj.name = loss
+    obj.pairwise_scoring = loss in ("PairLogitPairwise", "YetiRankPairwise")
     return obj

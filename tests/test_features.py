@@ -225,3 +225,60 @@ def test_ordered_boosting_regularises():
         res[bt] = (ev["learn"]["Logloss"][-1], min(ev["validation"]["Logloss"]))
     assert res["Ordered"][0] > res["Plain"][0]            # fits the training rows less tightly
     assert res["Ordered"][1] < res["Plain"][1] + 0.02     # and generalises at least as well
+
+
+def test_pairwise_histograms_match_bruteforce_and_train():
+    """The range-update construction of the per-candidate pair systems against a direct loop over pairs and borders,
+    then end-to-end training with the pairwise losses."""
+    import torch
+    from catboost_b200.data.pool import Pool
+    from catboost_b200.params import resolve_options
+    from catboost_b200.parallel.runtime import DistContext
+    from catboost_b200.train.boosting import build_store, plan_features
+    from catboost_b200.train.pairwise import PairwiseLearner, _solve_pairwise
+    rng = np.random.default_rng(3)
+    n, F = 80, 4
+    X = rng.standard_normal((n, F)).astype(np.float32)
+    pool = Pool(X, rng.random(n).astype(np.float32))
+    o = resolve_options(dict(border_count=8, depth=3, l2_leaf_reg=1.0), "PairLogitPairwise", n)
+    plan = plan_features(o, pool, DistContext(0, 1, torch.device("cpu")), None)
+    store, _ = build_store(plan, pool, torch.device("cpu"))
+    pl = PairwiseLearner(store, o)
+    P = 300
+    wi = torch.from_numpy(rng.integers(0, n, P))
+    li = torch.from_numpy(rng.integers(0, n, P))
+    keep = wi != li
+    wi, li = wi[keep], li[keep]
+    h = torch.from_numpy(rng.random(len(wi)).astype(np.float32))
+    der = torch.from_numpy(rng.standard_normal(n).astype(np.float32))
+    L = 2
+    leaf = torch.from_numpy(rng.integers(0, L, n))
+    for f in range(F):
+        got = pl._feature_scores(f, leaf, L, wi, li, h, der).numpy()
+        nb = int(store.feat_nb_host[f])
+        b = pl.bins[f]
+        ref = []
+        for t in range(nb - 1):
+            child = leaf + (b > t).long() * L
+            S = 2 * L
+            M = torch.zeros((S, S), dtype=torch.float64)
+            for p in range(len(wi)):
+                a_, b_ = int(child[wi[p]]), int(child[li[p]])
+                w = float(h[p])
+                M[a_, a_] += w; M[b_, b_] += w; M[a_, b_] -= w; M[b_, a_] -= w
+            d = torch.zeros(S, dtype=torch.float64).index_add_(0, child, der.double())
+            ref.append(float(_solve_pairwise(M, d, pl.l2, pl.prior)[1]))
+        assert np.allclose(got, np.array(ref), rtol=1e-8, atol=1e-10), f
+    # training
+    sizes = rng.integers(5, 25, 80)
+    gid = np.repeat(np.arange(80), sizes)
+    m_ = len(gid)
+    Xr = rng.standard_normal((m_, 6)).astype(np.float32)
+    sc = Xr @ rng.standard_normal(6) + 0.3 * rng.standard_normal(m_)
+    rel = np.digitize(sc, np.quantile(sc, [0.5, 0.8])).astype(np.float32)
+    for loss in ("PairLogitPairwise", "YetiRankPairwise"):
+        m = cb.CatBoostRanker(loss_function=loss, iterations=12, depth=3, learning_rate=0.3, verbose=False,
+                              allow_writing_files=False, eval_metric="NDCG", border_count=16)
+        m.fit(Xr, rel, group_id=gid)
+        ev = m.get_evals_result()["learn"]["NDCG"]
+        assert ev[-1] > ev[0] and ev[-1] > 0.95, (loss, ev[0], ev[-1])
