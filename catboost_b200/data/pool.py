@@ -166,6 +166,20 @@ def read_pairs(path: str):
     return np.array(pairs, dtype=np.int64).reshape(-1, 2), np.array(weights, dtype=np.float32)
 
 
+class _ColumnView:
+    """A list of equally long 1-D arrays that indexes like the object matrix ``data[:, c]`` the Pool constructor uses."""
+    ndim = 2
+    dtype = np.dtype(object)
+
+    def __init__(self, cols):
+        self.cols = cols
+        self.shape = (len(cols[0]) if cols else 0, len(cols))
+
+    def __getitem__(self, key):
+        rows, c = key
+        return self.cols[c][rows]
+
+
 class Pool:
     """Dataset container accepted by ``fit`` / ``predict`` / ``cv``.
 
@@ -210,21 +224,27 @@ class Pool:
             names = [str(c) for c in data.columns]
             if cat_features is None:
                 cat_features = [i for i, dt in enumerate(data.dtypes) if str(dt) in ("object", "category", "string", "str")]
-            data = data.to_numpy(dtype=object) if len(cat_features or []) else data.to_numpy()
+            if len(cat_features or []):
+                # keep the columns in their own dtypes: integer categorical columns are hashed by the native routine
+                # from their distinct values, float columns are copied without a detour through Python objects
+                frame_cols = [data.iloc[:, c].to_numpy() for c in range(data.shape[1])]
+                data = _ColumnView(frame_cols)
+            else:
+                data = data.to_numpy()
         elif _pd is not None and isinstance(data, _pd.Series):
             data = data.to_numpy().reshape(-1, 1)
         if data is None:
             if not data_can_be_none:
                 raise CatBoostError("data is None")
             data = np.zeros((0, 0), dtype=np.float32)
-        if not isinstance(data, np.ndarray):
+        if not isinstance(data, (np.ndarray, _ColumnView)):
             try:
                 import torch
                 if isinstance(data, torch.Tensor):
                     data = data.detach().cpu().numpy()
             except Exception:  # pragma: no cover
                 pass
-        if not isinstance(data, np.ndarray):
+        if not isinstance(data, (np.ndarray, _ColumnView)):
             data = np.asarray(data, dtype=object if cat_features else None)
         if data.ndim == 1:
             data = data.reshape(-1, 1)

@@ -150,6 +150,27 @@ def _projection_keys(pool: Pool, projection, device):
     return h
 
 
+_MAGIC_I64 = 0x4906BA494954CB65        # models.ctr.MAGIC_MULT; below 2^63, so the same bits as a signed constant
+
+
+def _cat_column_t(pool: Pool, c: int, device) -> torch.Tensor:
+    """Sign-extended 32-bit category hashes of one categorical feature as an int64 device tensor (cached on the pool)."""
+    cache = pool.__dict__.setdefault("_cat_hash_tensors", {})
+    key = (c, str(device))
+    if key not in cache:
+        col = np.asarray(pool.cat_hashes[c], dtype=np.uint32).view(np.int32).astype(np.int64)
+        cache[key] = torch.from_numpy(col).to(device)
+    return cache[key]
+
+
+def projection_hash_t(cols) -> torch.Tensor:
+    """models.ctr.projection_hash on the device: 64-bit wrap-around arithmetic, returned as int64 (same bits)."""
+    res = torch.zeros_like(cols[0])
+    for b in cols:
+        res = (res + b * _MAGIC_I64) * _MAGIC_I64
+    return res
+
+
 def _ordered_stats(keys_t: torch.Tensor, order_t: torch.Tensor, cols: torch.Tensor):
     """Exclusive prefix sums of ``cols`` [C, n] inside each key, in the order given by ``order_t`` (row ids in
     permutation order).  Returns [C, n] aligned with the original rows."""
@@ -202,10 +223,15 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
     for s in plan.specs:
         by_proj.setdefault(s.cat_features, []).append(s)
     for proj, specs in by_proj.items():
-        h_train = projection_hash([train_pool.cat_hashes[c] for c in proj])
-        uniq, inv = np.unique(h_train, return_inverse=True)
-        keys_t = torch.from_numpy(inv.astype(np.int64)).to(dev)
-        U = len(uniq)
+        # hashing, grouping and look-ups stay on the training device (a host sort of 45M 64-bit keys per projection
+        # would dominate the whole fit)
+        h_train_t = projection_hash_t([_cat_column_t(train_pool, c, dev) for c in proj])
+        uniq_t, keys_t = torch.unique(h_train_t, return_inverse=True)
+        U = int(uniq_t.numel())
+        # model tables want the hashes in unsigned order: the signed-sorted list is that order rotated
+        rot = int((uniq_t < 0).sum().item())
+        uniq_s = uniq_t.cpu().numpy().view(np.uint64)
+        uniq = np.concatenate([uniq_s[rot:], uniq_s[:rot]])
         # indicators: class > border k  (Borders), one column per needed target border + the count column
         need_tb = sorted({s.target_border_idx for s in specs if s.ctr_type in TARGET_CTRS})
         cols = [ones] + [(cls_t > tb).float() for tb in need_tb]
@@ -213,15 +239,19 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
         prefix = _ordered_stats(keys_t, order_t, colmat) if any(s.ctr_type in TARGET_CTRS for s in specs) else None
         totals = torch.zeros((len(cols), U), dtype=torch.float32, device=dev)
         totals.index_add_(1, keys_t, colmat)
-        totals_np = totals.cpu().numpy()
+        totals_s = totals.cpu().numpy()
+        totals_np = np.concatenate([totals_s[:, rot:], totals_s[:, :rot]], axis=1)
         max_count = float(totals_np[0].max()) if U else 1.0
         eval_keys = []
         for ep in eval_pools:
-            he = projection_hash([ep.cat_hashes[c] for c in proj])
-            pos = np.searchsorted(uniq, he)
-            pos = np.clip(pos, 0, max(U - 1, 0))
-            ok = (uniq[pos] == he) if U else np.zeros(len(he), bool)
-            eval_keys.append((torch.from_numpy(pos.astype(np.int64)).to(dev), torch.from_numpy(ok).to(dev)))
+            he_t = projection_hash_t([_cat_column_t(ep, c, dev) for c in proj])
+            if U:
+                pos = torch.searchsorted(uniq_t, he_t).clamp(max=U - 1)
+                ok = uniq_t[pos] == he_t
+            else:
+                pos = torch.zeros_like(he_t)
+                ok = torch.zeros(he_t.shape, dtype=torch.bool, device=dev)
+            eval_keys.append((pos, ok))
         for s in specs:
             if s.ctr_type in TARGET_CTRS:
                 ci = 1 + need_tb.index(s.target_border_idx)
@@ -238,7 +268,8 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
                 full = (totals[0] + s.prior_num) / denom
                 tr_val = full[keys_t]
                 unseen = s.prior_num / denom
-            sample = tr_val if n <= 200000 else tr_val[torch.from_numpy(rng.choice(n, 200000, replace=False)).to(dev)]
+            sample = tr_val if n <= 200000 else tr_val[torch.from_numpy(
+                np.random.default_rng(int(o.random_seed) + 7).choice(n, 200000, replace=False, shuffle=False)).to(dev)]
             borders, _ = select_borders(sample.cpu().numpy().reshape(-1, 1), s.border_count, "Uniform"
                                         if s.ctr_type in TARGET_CTRS else "GreedyLogSum")
             b = borders[0]
