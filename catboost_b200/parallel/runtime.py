@@ -73,6 +73,19 @@ class DistContext:
     def is_distributed(self):
         return self.world > 1
 
+    @property
+    def single_host(self) -> bool:
+        """True when every rank runs on the same machine (peer-mapped memory is only possible then).  Ranks on several
+        machines (torchrun --nnodes > 1) train with the NCCL reduction path instead of the peer arena."""
+        if not self.is_distributed:
+            return True
+        cached = getattr(self, "_single_host", None)
+        if cached is None:
+            import socket
+            names = self.all_gather_object(socket.gethostname() + ":" + os.environ.get("GROUP_RANK", "0"))
+            cached = self._single_host = len(set(names)) == 1
+        return cached
+
     def barrier(self):
         if self.is_distributed:
             import torch.distributed as dist

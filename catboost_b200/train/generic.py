@@ -116,6 +116,7 @@ class GenericLearner:
         self.gen.manual_seed(int(seed) + 12345)
         self.leaf = torch.zeros(store.npad, dtype=torch.int16, device=self.dev)
         self.use_count = int(opts.min_data_in_leaf) > 1
+        self.monotone = None          # float tensor [F] in {-1, 0, +1} per flat feature, set by set_monotone()
         self.n_total = store.n
         if ctx is not None and ctx.is_distributed:
             t = torch.tensor([store.n], dtype=torch.float64, device=self.dev)
@@ -224,6 +225,25 @@ class GenericLearner:
             return self._grow_depthwise(stats, K, noise_std, fmask)
         return self._grow_lossguide(stats, K, noise_std, fmask)
 
+    def set_monotone(self, per_float_feature: dict):
+        """``per_float_feature``: {float-feature index: +1 / -1}.  A candidate on a constrained feature is only allowed
+        when in every leaf the value of the right child is not below (+1) / above (-1) the value of the left child;
+        finished trees are repaired by ``enforce_monotone_leaves`` (catboost/private/libs/algo/monotonic_constraint_utils.cpp)."""
+        c = np.zeros(self.store.F, dtype=np.float32)
+        for f, ff in enumerate(self.store.features):
+            if ff.kind == "float" and int(ff.source) in per_float_feature:
+                c[f] = float(per_float_feature[int(ff.source)])
+        self.monotone = torch.from_numpy(c).to(self.dev) if np.any(c != 0) else None
+
+    def _monotone_ok(self, left, right, K):
+        """[F, B] mask of the candidates that respect the constraints (single-dimension models)."""
+        l2 = self.scorer.l2
+        vl = left[:, 0] / (left[:, K].clamp_min(0) + l2 + 1e-20)             # [L, F, B]
+        vr = right[:, 0] / (right[:, K].clamp_min(0) + l2 + 1e-20)
+        diff = (vr - vl) * self.monotone.view(1, -1, 1)
+        empty = (left[:, K] <= 0) | (right[:, K] <= 0)
+        return ((diff >= 0) | empty).all(0)
+
     def _cand_mask(self, fmask, cnt):
         m = self.scorer.valid_cand & fmask.unsqueeze(1)
         return m
@@ -239,12 +259,14 @@ class GenericLearner:
             L = 1 << level
             table = torch.arange(L, dtype=torch.int16, device=self.dev)
             h = self._hist(stats, table, L)
-            num, den, cnt, _ = sc.candidate_terms(h, K, cstat)
+            num, den, cnt, sides_ = sc.candidate_terms(h, K, cstat)
             score = sc.finish(num.sum(0), None if den is None else den.sum(0))          # [F, B]
             if noise_std > 0:
                 score = score + self._randn(score.shape) * noise_std
             score = score * fw.unsqueeze(1)
             mask = self._cand_mask(fmask, cnt)
+            if self.monotone is not None and K == 1:
+                mask = mask & self._monotone_ok(sides_[0], sides_[1], K)
             if cnt is not None:
                 mdl = int(self.o.min_data_in_leaf)
                 ok = ((cnt[0] >= mdl) | (cnt[0] == 0)).all(0) & ((cnt[1] >= mdl) | (cnt[1] == 0)).all(0)
@@ -361,6 +383,34 @@ class GenericLearner:
 
 
 # ---------------------------------------------------------------------------------------------------------
+def enforce_monotone_leaves(vals: np.ndarray, wts: np.ndarray, splits: np.ndarray, monotone_flat: np.ndarray) -> np.ndarray:
+    """Repair the leaf values of an oblivious tree so that, for every level that splits a constrained feature, the leaf
+    on the right of that split is not below (+1) / above (-1) its mirror leaf on the left: violating pairs are replaced
+    by their weighted mean (pool-adjacent-violators on two elements), repeated until nothing moves."""
+    vals = np.array(vals, dtype=np.float64, copy=True)
+    w = np.maximum(np.asarray(wts, dtype=np.float64), 1e-12)
+    levels = [(k, float(monotone_flat[int(splits[k, 0])])) for k in range(splits.shape[0])
+              if splits[k, 0] >= 0 and monotone_flat[int(splits[k, 0])] != 0]
+    if not levels:
+        return vals
+    idx = np.arange(vals.shape[0])
+    for _ in range(4 * len(levels) + 4):
+        moved = False
+        for k, c in levels:
+            lo = idx[(idx >> k) & 1 == 0]
+            hi = lo | (1 << k)
+            bad = c * (vals[hi, 0] - vals[lo, 0]) < -1e-15
+            if bad.any():
+                a, b = lo[bad], hi[bad]
+                mean = (vals[a, 0] * w[a] + vals[b, 0] * w[b]) / (w[a] + w[b])
+                vals[a, 0] = mean
+                vals[b, 0] = mean
+                moved = True
+        if not moved:
+            break
+    return vals
+
+
 def estimate_leaves(objective, approx, target, weight, leaf, n_leaves, n, opts, ctx=None, obj_ctx=None,
                     total_weight: Optional[float] = None):
     """Leaf values [n_leaves, dims] (already multiplied by the learning rate) and leaf weights [n_leaves]."""

@@ -79,6 +79,8 @@ class GpuObliviousEngine:
         self.seed = (int(seed) * 0x9E3779B97F4A7C15 + 0x1234567 * (self.rank + 1)) & 0xFFFFFFFFFFFFFFFF
         self.score_seed = (int(seed) * 0xD1B54A32D192ED03 + 77) & 0xFFFFFFFFFFFFFFFF
         self.reduce = reduce if self.R > 1 else "fused"
+        if self.R > 1 and self.reduce == "fused" and not self.ctx.single_host:
+            self.reduce = "nccl"          # ranks on several machines: no peer-mapped arena, histograms go through NCCL
         self.use_graph = use_graph
         # False: fp32 shared atomics; "wide": 23-bit fixed point in two int32 cells; True / "narrow": one int32 cell
         self.quantized_hist = bool(quantized_hist)

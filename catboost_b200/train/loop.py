@@ -41,6 +41,37 @@ class ObjectiveContext:
         self.subgroup_id = pool.subgroup_id
 
 
+def _parse_monotone(spec, pool) -> dict:
+    """monotone_constraints as {float-feature index: +1/-1}.  Accepts a list per feature, a dict by index or name, or
+    the strings "(1,0,-1)" / "0:1,3:-1" / "name:1" (catboost/private/libs/options/monotone_constraints.cpp)."""
+    per_col = {}
+    if isinstance(spec, str):
+        body = spec.strip().strip("()[]")
+        items = [x.strip() for x in body.split(",") if x.strip()]
+        if items and all(":" not in x for x in items):
+            per_col = {i: int(float(x)) for i, x in enumerate(items)}
+        else:
+            for x in items:
+                k, v = x.split(":")
+                k = k.strip()
+                per_col[int(k) if k.lstrip("-").isdigit() else pool.feature_names.index(k)] = int(float(v))
+    elif isinstance(spec, dict):
+        for k, v in spec.items():
+            per_col[pool.feature_names.index(k) if isinstance(k, str) and not k.isdigit() else int(k)] = int(v)
+    else:
+        per_col = {i: int(v) for i, v in enumerate(spec)}
+    out = {}
+    for col, c in per_col.items():
+        if c == 0:
+            continue
+        if c not in (-1, 1):
+            raise CatBoostError("monotone constraints must be -1, 0 or 1")
+        if col not in pool.float_feature_indices:
+            raise CatBoostError("monotone constraints apply to numerical features only")
+        out[pool.float_feature_indices.index(col)] = c
+    return out
+
+
 def _use_fast_engine(o, objective, store, dims) -> bool:
     # objectives without a device formula still use the fused level kernels: their derivatives are computed by the
     # objective's tensor code once per tree, which only allows a single leaf-estimation step
@@ -50,7 +81,7 @@ def _use_fast_engine(o, objective, store, dims) -> bool:
             and o.boosting_type == "Plain" and o.leaf_estimation_method in ("Newton", "Gradient")
             and float(o.rsm) >= 1.0 and int(o.min_data_in_leaf) <= 1
             and o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson") and bool(o.fused_levels or True)
-            and not o.langevin)
+            and not o.langevin and not o.monotone_constraints)
 
 
 class _History:
@@ -110,6 +141,14 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
     octx = ObjectiveContext(train_pool, dev)
     eval_approx = [torch.from_numpy(np.ascontiguousarray(b)).to(dev, f32) for b in base_evals]
     learner = GenericLearner(store, o, dims, ctx, seed=int(o.random_seed))
+    monotone_flat = None
+    if o.monotone_constraints:
+        mono = _parse_monotone(o.monotone_constraints, train_pool)
+        learner.set_monotone(mono)
+        if learner.monotone is not None:
+            if o.grow_policy != "SymmetricTree" or dims != 1:
+                raise CatBoostError("monotone_constraints need symmetric trees and a one-dimensional model")
+            monotone_flat = learner.monotone.cpu().numpy()
     plearner = None
     if getattr(objective, "pairwise_scoring", False) and o.grow_policy == "SymmetricTree" and \
             not (ctx is not None and ctx.is_distributed):
@@ -161,6 +200,9 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
                 tr = learner.build_tree(der_p, hess_p, wpad, it)
             with prof.span("leaves"):
                 vals, wts = estimate_leaves(objective, approx, target, weight, tr.leaf, tr.n_leaves, n, o, ctx, octx)
+        if monotone_flat is not None and tr.kind == "oblivious":
+            from .generic import enforce_monotone_leaves
+            vals = enforce_monotone_leaves(vals, wts, tr.splits, monotone_flat)
         tv = torch.from_numpy(vals).to(dev, f32)
         if ordered is not None:
             ordered.update(der, hess, weight, tr.leaf, tr.n_leaves, o)

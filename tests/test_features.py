@@ -282,3 +282,25 @@ def test_pairwise_histograms_match_bruteforce_and_train():
         m.fit(Xr, rel, group_id=gid)
         ev = m.get_evals_result()["learn"]["NDCG"]
         assert ev[-1] > ev[0] and ev[-1] > 0.95, (loss, ev[0], ev[-1])
+
+
+def test_monotone_constraints():
+    rng = np.random.default_rng(0)
+    n = 3000
+    X = rng.uniform(-2, 2, (n, 3)).astype(np.float32)
+    y = (np.sin(3 * X[:, 0]) + 0.5 * X[:, 0] + X[:, 1] ** 2 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    grid = np.linspace(-2, 2, 150).astype(np.float32)
+
+    def worst_decrease(m, sign):
+        w = 0.0
+        for x1 in (-1.0, 0.0, 1.5):
+            Z = np.stack([grid, np.full(150, x1, np.float32), np.zeros(150, np.float32)], 1)
+            w = max(w, float(np.max(-sign * np.diff(m.predict(Z)))))
+        return w
+
+    free = cb.CatBoostRegressor(iterations=60, depth=4, learning_rate=0.2, verbose=False, allow_writing_files=False).fit(X, y)
+    assert worst_decrease(free, 1) > 0.05
+    for spec, sign in (([1, 0, 0], 1), ("0:-1", -1), ({"0": 1}, 1)):
+        m = cb.CatBoostRegressor(iterations=60, depth=4, learning_rate=0.2, verbose=False, allow_writing_files=False,
+                                 monotone_constraints=spec).fit(X, y)
+        assert worst_decrease(m, sign) <= 1e-9, spec
