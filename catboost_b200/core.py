@@ -329,6 +329,10 @@ class CatBoost:
             if data is None:
                 raise CatBoostError("ShapValues needs a dataset")
             return fstr.shap_values(self._model, data if isinstance(data, Pool) else Pool(data))
+        elif t == EFstrType.ShapInteractionValues:
+            if data is None:
+                raise CatBoostError("ShapInteractionValues needs a dataset")
+            return fstr.shap_interaction_values(self._model, data if isinstance(data, Pool) else Pool(data))
         elif t == EFstrType.Interaction:
             return fstr.interaction(self._model)
         elif t == EFstrType.PredictionDiff:

@@ -164,18 +164,21 @@ def _unwound_sum(path, i):
     return tot
 
 
-def _tree_shap_row(m, ns, cover, outcomes_col, phi, split_feat):
-    """Accumulate SHAP values of one tree for one row.  outcomes_col: bool per model split."""
-    dims = m.dims
+def _tree_shap_row(m, ns, cover, outcomes_col, phi, split_feat, condition=0, condition_feature=-1):
+    """Accumulate SHAP values of one tree for one row.  outcomes_col: bool per model split.
+    condition = +1 / -1 fixes ``condition_feature`` as present / absent (used for the interaction values)."""
 
-    def recurse(node, path, pz, po, pi):
-        path = _extend(path, pz, po, pi)
+    def recurse(node, path, pz, po, pi, cfrac):
+        if cfrac == 0.0:
+            return
+        if condition == 0 or condition_feature != pi:
+            path = _extend(path, pz, po, pi)
         si = ns.split_of_node[node]
         if si < 0:
             v = ns.leaf_values[ns.leaf_of_node[node]]
             for i in range(1, len(path)):
                 w = _unwound_sum(path, i)
-                phi[path[i].d] += w * (path[i].o - path[i].z) * v
+                phi[path[i].d] += w * (path[i].o - path[i].z) * v * cfrac
             return
         hot, cold = (ns.right[node], ns.left[node]) if outcomes_col[si] else (ns.left[node], ns.right[node])
         f = split_feat[si]
@@ -189,11 +192,19 @@ def _tree_shap_row(m, ns, cover, outcomes_col, phi, split_feat):
             return
         # a branch no training row reached carries no weight: skip it when it is the cold one, and give the hot one a
         # vanishing (but non-zero) fraction so that the path algebra stays finite
-        recurse(hot, path, iz * max(cover[hot] / c, 1e-9), io, f)
+        hot_z = max(cover[hot] / c, 1e-9)
+        cold_z = cover[cold] / c
+        hot_c, cold_c = cfrac, cfrac
+        if condition > 0 and f == condition_feature:
+            cold_c = 0.0
+        elif condition < 0 and f == condition_feature:
+            hot_c *= hot_z
+            cold_c *= cold_z
+        recurse(hot, path, iz * hot_z, io, f, hot_c)
         if cover[cold] > 0:
-            recurse(cold, path, iz * cover[cold] / c, 0.0, f)
+            recurse(cold, path, iz * cold_z, 0.0, f, cold_c)
 
-    recurse(0, [], 1.0, 1.0, -1)
+    recurse(0, [], 1.0, 1.0, -1, 1.0)
 
 
 def shap_values(m: Model, pool: Pool) -> np.ndarray:
@@ -225,6 +236,46 @@ def shap_values(m: Model, pool: Pool) -> np.ndarray:
     if m.dims == 1:
         return out[:, :, 0]
     return np.transpose(out, (0, 2, 1))
+
+
+def shap_interaction_values(m: Model, pool: Pool) -> np.ndarray:
+    """Exact TreeSHAP interaction values ``[n, F + 1, F + 1]`` (one-dimensional models): entry (i, j), i != j, is half
+    the difference of feature i's SHAP value with feature j fixed present and fixed absent; the diagonal holds the
+    rest of feature i's SHAP value; the last row / column carry the expected value in their corner
+    (catboost/libs/fstr/shap_interaction_values.cpp)."""
+    if m.dims != 1:
+        raise CatBoostError("ShapInteractionValues are implemented for one-dimensional models")
+    fd, ch = m.pool_arrays(pool)
+    n, F = pool.num_row(), m.n_features
+    oc = m._split_outcomes_block(fd, ch, m._ctr_values(ch))
+    split_feat = [(_split_flat_features(m, sp)[0]) for sp in m.splits]
+    prepared = []
+    for t in m.trees:
+        ns = _as_nonsymmetric(t)
+        cover, _ = _node_stats(ns, 1)
+        if cover[0] > 0:
+            prepared.append((ns, cover, {split_feat[si] for si in ns.split_of_node if si >= 0}))
+    base = shap_values(m, pool)                                   # [n, F + 1]
+    out = np.zeros((n, F + 1, F + 1))
+    import sys
+    sys.setrecursionlimit(max(sys.getrecursionlimit(), 10000))
+    for r in range(n):
+        col = oc[:, r]
+        for j in range(F):
+            on = np.zeros((F + 1, 1))
+            off = np.zeros((F + 1, 1))
+            for ns, cover, used in prepared:
+                if j not in used:
+                    continue                                      # fixing an unused feature changes nothing
+                _tree_shap_row(m, ns, cover, col, on, split_feat, 1, j)
+                _tree_shap_row(m, ns, cover, col, off, split_feat, -1, j)
+            half = (on[:F, 0] - off[:F, 0]) * 0.5 * m.scale
+            half[j] = 0.0
+            out[r, :F, j] = half
+        for i in range(F):
+            out[r, i, i] = base[r, i] - out[r, i, :F].sum()
+        out[r, F, F] = base[r, F]
+    return out
 
 
 def loss_function_change(estimator, data) -> np.ndarray:

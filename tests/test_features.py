@@ -304,3 +304,19 @@ def test_monotone_constraints():
         m = cb.CatBoostRegressor(iterations=60, depth=4, learning_rate=0.2, verbose=False, allow_writing_files=False,
                                  monotone_constraints=spec).fit(X, y)
         assert worst_decrease(m, sign) <= 1e-9, spec
+
+
+def test_shap_interaction_values():
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((600, 4)).astype(np.float32)
+    y = (2 * X[:, 0] + X[:, 1] * X[:, 2] + 0.05 * rng.standard_normal(600)).astype(np.float32)
+    m = cb.CatBoostRegressor(iterations=15, depth=3, learning_rate=0.3, verbose=False, allow_writing_files=False).fit(X, y)
+    P = cb.Pool(X[:5], y[:5])
+    sv = m.get_feature_importance(P, type="ShapValues")
+    iv = m.get_feature_importance(P, type="ShapInteractionValues")
+    assert iv.shape == (5, 5, 5)
+    assert np.allclose(iv[:, :4, :4].sum(2), sv[:, :4], atol=1e-10)            # rows add up to the SHAP values
+    assert np.allclose(iv[:, :4, :4], iv[:, :4, :4].transpose(0, 2, 1), atol=1e-10)
+    assert np.allclose(iv.sum((1, 2)), m.predict(X[:5]), atol=1e-8)
+    mean_abs = np.abs(iv[:, :4, :4]).mean(0)
+    assert mean_abs[1, 2] > 5 * mean_abs[0, 3]                                  # the x1 * x2 term is the interaction
