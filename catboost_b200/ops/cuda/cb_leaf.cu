@@ -24,7 +24,8 @@ struct CbLeafNewtonArgs {
     const float* approx; const float* target; const float* weight; const unsigned short* leaf;
     long long n; int L;
     float* delta;            // [L] running leaf values of this tree (unscaled); written by block 0
-    double* sums;            // [L][3] zero on entry, zero on exit
+    double* sums;            // [3][L][3] zero on entry, zero on exit (one rank rotates through the three copies)
+    unsigned int* counter;   // zero on entry / exit
     float* vmax;             // [2] zero on entry, zero on exit
     int steps, newton;
     float l2, lr;
@@ -53,6 +54,11 @@ __global__ void __launch_bounds__(512) cb_leaf_newton_kernel(CbLeafNewtonArgs a,
     const int lane_copy = threadIdx.x & (C - 1);
     int* si = reinterpret_cast<int*>(sl);
     float* sdelta = sl + (size_t)4 * L * C;
+    float* sleafw = sdelta + L;
+    // One rank: every block takes the Newton step itself from the complete sums, so a step needs a single grid barrier.
+    // The sums rotate through three copies; block 0 clears the copy of step s + 2 after the barrier of step s, when
+    // nobody can still be reading it and nobody can already be adding to it.
+    const bool solo = a.c.nranks <= 1;
     const long long n4 = (a.n + 3) >> 2;
     const long long stride = (long long)gridDim.x * blockDim.x;
     const bool can_quant = (a.n / gridDim.x) < (1ll << 19);
@@ -66,8 +72,10 @@ __global__ void __launch_bounds__(512) cb_leaf_newton_kernel(CbLeafNewtonArgs a,
             sc0 = 8388607.0f / M0;
             sc1 = 8388607.0f / M1;
         }
+        double* S = a.sums + (solo ? (size_t)(step % 3) * 3 * L : 0);
         for (int i = threadIdx.x; i < 4 * L * C; i += blockDim.x) sl[i] = 0.0f;
-        for (int i = threadIdx.x; i < L; i += blockDim.x) sdelta[i] = first ? 0.0f : __ldcg(a.delta + i);
+        if (!solo || first)
+            for (int i = threadIdx.x; i < L; i += blockDim.x) sdelta[i] = first ? 0.0f : __ldcg(a.delta + i);
         __syncthreads();
         float mx0 = 0.f, mx1 = 0.f;
         long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -99,8 +107,8 @@ __global__ void __launch_bounds__(512) cb_leaf_newton_kernel(CbLeafNewtonArgs a,
                         atomicAdd(cell + 2 * C, qh >> 12);
                         atomicAdd(reinterpret_cast<unsigned int*>(cell + 3 * C), (unsigned int)qh & 4095u);
                     } else {
-                        atomicAdd(&a.sums[3 * l], (double)vd);
-                        atomicAdd(&a.sums[3 * l + 1], (double)vh);
+                        atomicAdd(&S[3 * l], (double)vd);
+                        atomicAdd(&S[3 * l + 1], (double)vh);
                     }
                 } else {
                     float* cell = sl + (size_t)(l * 4) * C + lane_copy;
@@ -133,7 +141,7 @@ __global__ void __launch_bounds__(512) cb_leaf_newton_kernel(CbLeafNewtonArgs a,
                 long long hi = 0, lo = 0;
                 for (int c = 0; c < C; ++c) { hi += ph[c]; lo += (unsigned int)ph[C + c]; }
                 const long long qq = hi * 4096 + lo;
-                if (qq != 0) atomicAdd(&a.sums[3 * l + s2], (double)qq * (s2 ? inv1 : inv0));
+                if (qq != 0) atomicAdd(&S[3 * l + s2], (double)qq * (s2 ? inv1 : inv0));
             }
         } else {
             for (int i = threadIdx.x; i < 3 * L; i += blockDim.x) {
@@ -141,11 +149,50 @@ __global__ void __launch_bounds__(512) cb_leaf_newton_kernel(CbLeafNewtonArgs a,
                 if (s3 == 2 && !first) continue;
                 float vsum = 0.0f;
                 for (int c = 0; c < C; ++c) vsum += sl[(size_t)(l * 4 + s3) * C + c];
-                if (vsum != 0.0f) atomicAdd(&a.sums[i], (double)vsum);
+                if (vsum != 0.0f) atomicAdd(&S[i], (double)vsum);
             }
         }
         __threadfence();
         grid.sync();
+        if (solo) {
+            const int it = *a.iter_ptr;
+            for (int l = threadIdx.x; l < L; l += blockDim.x) {
+                const double sd = __ldcg(&S[3 * l]), shs = __ldcg(&S[3 * l + 1]);
+                if (first) sleafw[l] = (float)__ldcg(&S[3 * l + 2]);
+                const double sw = (double)sleafw[l];
+                const double den = (a.newton ? shs : sw) + (double)a.l2;
+                const float stp = (den > 0.0) ? (float)(sd / den) : 0.0f;
+                const float v = sdelta[l] + stp;
+                sdelta[l] = v;
+                if (blockIdx.x == 0) {
+                    a.delta[l] = v;
+                    if (first) a.leaf_w[l] = sleafw[l];
+                    if (last) {
+                        a.cur_vals[l] = a.lr * v;
+                        if (a.model_vals) a.model_vals[(long long)it * a.Lstride + l] = a.lr * v;
+                        if (a.model_wts) a.model_wts[(long long)it * a.Lstride + l] = (float)sw;
+                    }
+                }
+            }
+            if (blockIdx.x == 0) {
+                double* Z = a.sums + (size_t)((step + 2) % 3) * 3 * L;
+                for (int i = threadIdx.x; i < 3 * L; i += blockDim.x) Z[i] = 0.0;
+                __threadfence();
+            }
+            __syncthreads();
+            if (last) {
+                // the block that finishes last clears what the final steps left behind
+                __shared__ bool s_last_block;
+                __threadfence();
+                if (threadIdx.x == 0) s_last_block = (atomicAdd(a.counter, 1u) == gridDim.x - 1);
+                __syncthreads();
+                if (s_last_block) {
+                    for (int i = threadIdx.x; i < 9 * L; i += blockDim.x) a.sums[i] = 0.0;
+                    if (threadIdx.x == 0) { *a.counter = 0u; a.vmax[0] = 0.0f; a.vmax[1] = 0.0f; }
+                }
+            }
+            continue;
+        }
         if (blockIdx.x == 0) {
             if (a.c.nranks > 1) {
                 for (int base = 0; base < 3 * L; base += a.c.mbox_bytes / 8)
@@ -192,8 +239,8 @@ static int cb_leaf_newton_launch_t(CbLeafNewtonArgs& a, int C, int smem, int gri
 
 static int cb_leaf_newton_cells(int L, int* smem) {
     int C = 32;
-    while (C > 1 && (size_t)(4 * L * C + L) * 4 > 96 * 1024) C >>= 1;
-    *smem = (4 * L * C + L) * 4;
+    while (C > 1 && (size_t)(4 * L * C + 2 * L) * 4 > 96 * 1024) C >>= 1;
+    *smem = (4 * L * C + 2 * L) * 4;
     return (size_t)*smem <= 96 * 1024 ? C : 0;
 }
 
@@ -214,11 +261,12 @@ CB_API int cb_leaf_newton_max_grid(int L) {
 }
 
 CB_API int cb_leaf_newton(int loss, float p0, float p1, const float* approx, const float* target, const float* weight,
-                          const unsigned short* leaf, long long n, int L, float* delta, double* sums, float* vmax,
+                          const unsigned short* leaf, long long n, int L, float* delta, double* sums,
+                          unsigned int* counter, float* vmax,
                           int steps, int newton, float l2, float lr, float* cur_vals, float* model_vals,
                           float* model_wts, int Lstride, const int* iter_ptr, float* leaf_w, const CbComm* comm,
                           int grid, cudaStream_t st) {
-    CbLeafNewtonArgs a{loss, p0, p1, approx, target, weight, leaf, n, L, delta, sums, vmax, steps, newton, l2, lr,
+    CbLeafNewtonArgs a{loss, p0, p1, approx, target, weight, leaf, n, L, delta, sums, counter, vmax, steps, newton, l2, lr,
                        cur_vals, model_vals, model_wts, Lstride, iter_ptr, leaf_w, CbComm()};
     if (comm) a.c = *comm; else { a.c.nranks = 1; a.c.rank = 0; }
     int smem = 0;

@@ -129,7 +129,7 @@ class GpuObliviousEngine:
         self.cur_vals = torch.zeros(self.L, dtype=f32, device=dev)
         self.delta = torch.zeros(self.L, dtype=f32, device=dev)
         self.leaf_w = torch.zeros(self.L, dtype=f32, device=dev)
-        self.sums = torch.zeros(self.L * 3, dtype=f64, device=dev)
+        self.sums = torch.zeros(self.L * 9, dtype=f64, device=dev)     # three rotating copies of [L][3]
         self.counter = torch.zeros(1, dtype=i32, device=dev)
         self.best_key = torch.zeros(1, dtype=i64, device=dev)
         self.cur_loss = torch.zeros(2, dtype=f64, device=dev)
@@ -317,7 +317,8 @@ class GpuObliviousEngine:
         if self.leaf_grid > 0 and self.fused_leaf_steps:
             # all steps of the leaf estimation in one cooperative launch
             chk(lib.cb_leaf_newton(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target), _p(self.weight),
-                                   _p(self.leaf), self.n, self.L, _p(self.delta), _p(self.sums), _p(self.leaf_vmax),
+                                   _p(self.leaf), self.n, self.L, _p(self.delta), _p(self.sums), _p(self.counter),
+                                   _p(self.leaf_vmax),
                                    self.leaf_iterations, self.leaf_newton, self.l2, self.lr, _p(self.cur_vals),
                                    _p(self.model_vals), _p(self.model_wts), self.L, _p(self.iter_ptr), _p(self.leaf_w),
                                    comm, self.leaf_grid, self._stream()), "cb_leaf_newton")
