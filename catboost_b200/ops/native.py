@@ -22,7 +22,7 @@ from pathlib import Path
 
 _HERE = Path(__file__).resolve().parent
 CUDA_SRC = [_HERE / "cuda" / "cb_kernels.cu", _HERE / "cuda" / "cb_fused.cu", _HERE / "cuda" / "cb_leaf.cu",
-            _HERE / "cuda" / "cb_quantize_tma.cu"]
+            _HERE / "cuda" / "cb_quantize_tma.cu", _HERE / "cuda" / "cb_ranking.cu"]
 CUDA_HDR = sorted((_HERE / "cuda").glob("*.cuh")) + sorted((_HERE / "cuda").glob("*.h"))
 CPU_SRC = [_HERE / "cpu" / "cb_cpu.cpp"]
 CUDA_LIB = _HERE / "libcb200_cuda.so"
@@ -142,6 +142,9 @@ _SIGS = {
                                c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "cb_quantize_tma": (c_int, [c_void_p, c_ll, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_void_p,
                                 c_void_p]),
+    "cb_yetirank_max_group": (c_int, []),
+    "cb_yetirank": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_ll, c_int, c_float, c_ull, c_void_p, c_void_p,
+                            c_void_p, c_void_p]),
     "cb_leaf_newton_max_grid": (c_int, [c_int]),
     "cb_leaf_newton": (c_int, [c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_int,

@@ -34,6 +34,7 @@ class _GroupLayout:
         self.index = torch.where(self.mask, offsets[:-1].unsqueeze(1) + ar.unsqueeze(0), torch.zeros((), dtype=torch.long, device=offsets.device))
         self.Q, self.Lmax = Q, Lmax
         n = int(offsets[-1].item())
+        self.n = n
         self.group_of_row = torch.repeat_interleave(torch.arange(Q, device=offsets.device), sizes, output_size=n)
 
     def gather(self, x, fill=0.0):
@@ -173,10 +174,31 @@ class YetiRank(_GroupObjective):
         self.decay = float(self.params.get("decay", 0.85))
         self._gen = None
 
+    def _der_hess_device(self, a, target, weight, lay, noise=None):
+        """The hand-written kernel (ops/cuda/cb_ranking.cu): one block per group, sort + pair accumulation in shared
+        memory.  ``noise``: optional [permutations, n] uniforms (tests); else a counter-based generator seeded per call."""
+        import ctypes
+        from ..ops import native
+        lib = native.cuda_lib()
+        n = a.shape[0]
+        self._calls = getattr(self, "_calls", 0) + 1
+        der = torch.zeros(n, dtype=torch.float32, device=a.device)
+        hess = torch.full((n,), 1e-16, dtype=torch.float32, device=a.device)
+        P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+        a32, t32 = a.contiguous().float(), target.contiguous().float()
+        w32 = None if weight is None else weight.contiguous().float()
+        off = lay.offsets.contiguous()
+        native.cuda_check(lib.cb_yetirank(P(a32), P(t32), P(w32), P(off), lay.Q, n, self.permutations, self.decay,
+                                          (20240229 + 7919 * self._calls) & 0xFFFFFFFFFFFFFFFF, P(noise), P(der), P(hess),
+                                          ctypes.c_void_p(torch.cuda.current_stream(a.device).cuda_stream)), "cb_yetirank")
+        return der.unsqueeze(0), hess.unsqueeze(0)
+
     def der_hess(self, approx, target, weight, ctx=None):
         lay = _layout(ctx)
         a, n = approx[0], approx.shape[1]
         dev = a.device
+        if a.is_cuda and lay.Lmax <= 2048 and lay.Q > 0 and lay.n == n:
+            return self._der_hess_device(a, target, weight, lay)
         if self._gen is None:
             self._gen = torch.Generator(device="cpu")
             self._gen.manual_seed(20240229)

@@ -217,6 +217,48 @@ def test_gpu_ranking_objectives_use_fused_engine():
         assert ev[-1] > 0.9, (loss, ev)
 
 
+def test_yetirank_kernel_matches_tensor_reference():
+    """cb_yetirank_kernel with given uniforms against the same computation written with tensor ops."""
+    from catboost_b200.train.ranking import YetiRank, _GroupLayout
+    rng = np.random.default_rng(5)
+    sizes = rng.integers(1, 70, 300)
+    off = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    n = int(off[-1])
+    dev = torch.device("cuda")
+    a = torch.from_numpy(rng.standard_normal(n).astype(np.float32)).to(dev)
+    t = torch.from_numpy(rng.integers(0, 4, n).astype(np.float32)).to(dev)
+    w = torch.from_numpy(rng.uniform(0.5, 2.0, n).astype(np.float32)).to(dev)
+    obj = YetiRank({"permutations": 6, "decay": 0.85})
+    lay = _GroupLayout(torch.from_numpy(off).to(dev))
+    P = obj.permutations
+    noise = torch.from_numpy(rng.uniform(0.01, 0.99, (P, n)).astype(np.float32)).to(dev)
+    der, hess = obj._der_hess_device(a, t, w, lay, noise=noise)
+    # reference
+    A, T = lay.gather(a, -1e30), lay.gather(t)
+    Q, L = lay.Q, lay.Lmax
+    rd = torch.zeros((Q, L), device=dev, dtype=torch.float64)
+    rh = torch.zeros((Q, L), device=dev, dtype=torch.float64)
+    decay_pow = 0.85 ** torch.arange(L - 1, device=dev, dtype=torch.float64)
+    for p_ in range(P):
+        u = lay.gather(noise[p_], 0.5).clamp(1e-6, 1 - 1e-6)
+        noisy = torch.where(lay.mask, A + torch.log(u / (1.000001 - u)), torch.full_like(A, -1e30))
+        order = torch.argsort(noisy, dim=1, descending=True, stable=True)
+        first, second = order[:, :-1], order[:, 1:]
+        valid = lay.mask.gather(1, first) & lay.mask.gather(1, second)
+        t1, t2 = T.gather(1, first), T.gather(1, second)
+        wgt = 0.15 * decay_pow.unsqueeze(0) * (t1 - t2).abs().double() * valid
+        win = torch.where(t1 > t2, first, second)
+        los = torch.where(t1 > t2, second, first)
+        pr = torch.sigmoid((A.gather(1, los) - A.gather(1, win)).double())
+        rd.scatter_add_(1, win, wgt * pr); rd.scatter_add_(1, los, -wgt * pr)
+        rh.scatter_add_(1, win, wgt * pr * (1 - pr)); rh.scatter_add_(1, los, wgt * pr * (1 - pr))
+    W = lay.gather(w).double()
+    ref_d = lay.scatter(rd / P * W, n).float()
+    ref_h = lay.scatter(rh / P * W, n).float().clamp_min(1e-16)
+    assert torch.allclose(der[0], ref_d, rtol=2e-4, atol=2e-6), float((der[0] - ref_d).abs().max())
+    assert torch.allclose(hess[0], ref_h, rtol=2e-4, atol=2e-6)
+
+
 def test_device_wait_times_out_without_hanging():
     """A wait on a tag nobody writes returns with the status word set (bounded spin, no trap)."""
     from catboost_b200.ops import native
