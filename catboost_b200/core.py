@@ -106,7 +106,12 @@ class CatBoost:
         else:
             if y is None and not isinstance(X, (str, os.PathLike)):
                 raise CatBoostError("y is required when X is not a Pool")
-            train_pool = Pool(X, y, cat_features=cat_features, pairs=pairs, weight=sample_weight, group_id=group_id,
+            if text_features is None:
+                text_features = params.get("text_features")
+            if embedding_features is None:
+                embedding_features = params.get("embedding_features")
+            train_pool = Pool(X, y, cat_features=cat_features, text_features=text_features,
+                              embedding_features=embedding_features, pairs=pairs, weight=sample_weight, group_id=group_id,
                               group_weight=group_weight, subgroup_id=subgroup_id, pairs_weight=pairs_weight,
                               baseline=baseline, column_description=column_description)
         eval_pools = []
@@ -117,6 +122,8 @@ class CatBoost:
                     eval_pools.append(es)
                 elif isinstance(es, tuple) and len(es) == 2:
                     eval_pools.append(Pool(es[0], es[1], cat_features=train_pool.cat_feature_indices,
+                                           text_features=getattr(train_pool, "text_feature_indices", None) or None,
+                                           embedding_features=getattr(train_pool, "embedding_feature_indices", None) or None,
                                            feature_names=train_pool.feature_names))
                 else:
                     raise CatBoostError("eval_set must be a Pool, an (X, y) tuple or a list of them")
@@ -136,10 +143,18 @@ class CatBoost:
         return self
 
     # ------------------------------------------------------------------ predict
+    def _pool_kwargs(self):
+        """How raw prediction data has to be read: the column roles the model was trained with."""
+        kw = dict(cat_features=[c.flat_index for c in self._model.cat_features])
+        est = getattr(self._model, "estimators", None)
+        if est is not None:
+            kw["text_features"] = list(est.text_flat) or None
+            kw["embedding_features"] = list(est.emb_flat) or None
+        return kw
+
     def _raw(self, data, ntree_start=0, ntree_end=0, thread_count=-1, task_type="CPU"):
         self._check_fitted()
-        pool = data if isinstance(data, Pool) else Pool(data, cat_features=[c.flat_index for c in self._model.cat_features],
-                                                        data_can_be_none=False)
+        pool = data if isinstance(data, Pool) else Pool(data, data_can_be_none=False, **self._pool_kwargs())
         fd, ch = self._model.pool_arrays(pool)
         raw = self._model.predict_raw(fd, ch, ntree_start, ntree_end, task_type=task_type, thread_count=thread_count)
         if pool.baseline is not None:
@@ -202,7 +217,7 @@ class CatBoost:
     def staged_predict(self, data, prediction_type=None, ntree_start=0, ntree_end=0, eval_period=1, thread_count=-1,
                        verbose=None):
         self._check_fitted()
-        pool = data if isinstance(data, Pool) else Pool(data, cat_features=[c.flat_index for c in self._model.cat_features])
+        pool = data if isinstance(data, Pool) else Pool(data, **self._pool_kwargs())
         fd, ch = self._model.pool_arrays(pool)
         pt = prediction_type or self._default_prediction_type()
         for raw in self._model.staged_raw(fd, ch, ntree_start, ntree_end, eval_period):
@@ -210,7 +225,7 @@ class CatBoost:
 
     def calc_leaf_indexes(self, data, ntree_start=0, ntree_end=0, thread_count=-1, verbose=False):
         self._check_fitted()
-        pool = data if isinstance(data, Pool) else Pool(data, cat_features=[c.flat_index for c in self._model.cat_features])
+        pool = data if isinstance(data, Pool) else Pool(data, **self._pool_kwargs())
         fd, ch = self._model.pool_arrays(pool)
         return self._model.leaf_indices(fd, ch, ntree_start, ntree_end)
 
@@ -380,7 +395,7 @@ class CatBoost:
 
     def score(self, X, y=None):
         self._check_fitted()
-        pool = X if isinstance(X, Pool) else Pool(X, y, cat_features=[c.flat_index for c in self._model.cat_features])
+        pool = X if isinstance(X, Pool) else Pool(X, y, **self._pool_kwargs())
         yy = pool.label
         raw = self._raw(pool)
         if self._model.class_names is not None:

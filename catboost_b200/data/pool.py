@@ -193,8 +193,6 @@ class Pool:
                  group_weight=None, subgroup_id=None, pairs_weight=None, baseline=None, timestamp=None,
                  feature_names: Optional[Sequence[str]] = None, feature_tags=None, thread_count: int = -1,
                  log_cout=None, log_cerr=None, data_can_be_none: bool = False):
-        if text_features or embedding_features:
-            raise CatBoostError("text and embedding features are not supported by catboost_b200")
         if isinstance(data, Pool):
             self.__dict__.update({k: (v.copy() if isinstance(v, np.ndarray) else v) for k, v in data.__dict__.items()})
             return
@@ -224,7 +222,7 @@ class Pool:
             names = [str(c) for c in data.columns]
             if cat_features is None:
                 cat_features = [i for i, dt in enumerate(data.dtypes) if str(dt) in ("object", "category", "string", "str")]
-            if len(cat_features or []):
+            if len(cat_features or []) or text_features or embedding_features:
                 # keep the columns in their own dtypes: integer categorical columns are hashed by the native routine
                 # from their distinct values, float columns are copied without a detour through Python objects
                 frame_cols = [data.iloc[:, c].to_numpy() for c in range(data.shape[1])]
@@ -245,7 +243,7 @@ class Pool:
             except Exception:  # pragma: no cover
                 pass
         if not isinstance(data, (np.ndarray, _ColumnView)):
-            data = np.asarray(data, dtype=object if cat_features else None)
+            data = np.asarray(data, dtype=object if (cat_features or text_features or embedding_features) else None)
         if data.ndim == 1:
             data = data.reshape(-1, 1)
         if data.ndim != 2:
@@ -259,7 +257,18 @@ class Pool:
         self.cat_feature_indices = cat_idx
         self.feature_names = names if names is not None else [str(i) for i in range(ncol)]
         self.n_features = ncol
-        float_idx = [c for c in range(ncol) if c not in set(cat_idx)]
+        text_idx = self._resolve_feature_indices(text_features, names, ncol)
+        emb_idx = self._resolve_feature_indices(embedding_features, names, ncol)
+        self.text_feature_indices, self.embedding_feature_indices = text_idx, emb_idx
+        self.text_data = [np.array(["" if v is None else str(v) for v in data[:, c]], dtype=object) for c in text_idx]
+        self.embedding_data = []
+        for c in emb_idx:
+            try:
+                self.embedding_data.append(np.stack([np.asarray(v, dtype=np.float32).reshape(-1) for v in data[:, c]]))
+            except ValueError:
+                raise CatBoostError(f"embedding feature {c}: all rows must hold vectors of the same length")
+        special = set(cat_idx) | set(text_idx) | set(emb_idx)
+        float_idx = [c for c in range(ncol) if c not in special]
         self.float_feature_indices = float_idx
         # float matrix
         if not cat_idx and data.dtype == np.float32 and data.flags.c_contiguous:
@@ -438,6 +447,21 @@ class Pool:
         change[1:] = self.group_id[1:] != self.group_id[:-1]
         return np.concatenate([np.nonzero(change)[0], [n]]).astype(np.int64)
 
+    def with_estimated(self, extra: np.ndarray, names):
+        """A pool whose text / embedding columns are replaced by numeric columns computed from them (appended after the
+        original feature positions, so the other features keep their indices)."""
+        out = Pool.__new__(Pool)
+        out.__dict__.update(self.__dict__)
+        extra = np.ascontiguousarray(extra, dtype=np.float32)
+        out.float_data = np.ascontiguousarray(np.concatenate([self.float_data, extra], 1), dtype=np.float32)
+        out.float_feature_indices = list(self.float_feature_indices) + [self.n_features + k for k in range(extra.shape[1])]
+        out.feature_names = list(self.feature_names) + [str(x) for x in names]
+        out.n_features = self.n_features + extra.shape[1]
+        out.text_data, out.embedding_data = [], []
+        out.text_feature_indices, out.embedding_feature_indices = [], []
+        out.__dict__.pop("_cat_hash_tensors", None)
+        return out
+
     def slice(self, rindex):
         """New Pool with the given rows (order preserved)."""
         idx = np.asarray(rindex, dtype=np.int64)
@@ -445,6 +469,8 @@ class Pool:
         out.__dict__.update(self.__dict__)
         out.float_data = np.ascontiguousarray(self.float_data[idx])
         out.cat_hashes = np.ascontiguousarray(self.cat_hashes[:, idx])
+        out.text_data = [t[idx] for t in getattr(self, "text_data", [])]
+        out.embedding_data = [e[idx] for e in getattr(self, "embedding_data", [])]
         for k in ("label", "weight", "group_weight", "baseline", "timestamp", "group_id", "subgroup_id"):
             v = getattr(self, k)
             setattr(out, k, None if v is None else v[idx])

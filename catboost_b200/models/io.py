@@ -170,6 +170,12 @@ def model_to_cbm_bytes(m: Model) -> bytes:
     info.setdefault("params", json.dumps({"loss_function": {"type": m.loss_name}}))
     info["catboost_b200_meta"] = json.dumps({"loss_name": m.loss_name, "n_features": m.n_features,
                                              "feature_names": m.feature_names})
+    if getattr(m, "estimators", None) is not None:
+        # text / embedding processing (dictionaries, class statistics, reference embeddings): this framework's own
+        # extension of the container, ignored by other readers
+        import base64
+        import pickle
+        info["catboost_b200_estimators"] = base64.b64encode(pickle.dumps(m.estimators)).decode("ascii")
     kv = []
     for k in sorted(info):
         kv.append(b.table(2, [(0, "o", b.string(k)), (1, "o", b.string(info[k]))]))
@@ -289,6 +295,10 @@ def model_from_cbm_bytes(blob: bytes) -> Model:
             m.trees.append(_read_nonsymmetric(tree_splits[s0:s0 + sz], steps[s0:s0 + sz], node_to_leaf[s0:s0 + sz],
                                               leaf_values, leaf_weights, m.dims))
     meta = json.loads(m.info.get("catboost_b200_meta", "{}")) if "catboost_b200_meta" in m.info else {}
+    if "catboost_b200_estimators" in m.info:
+        import base64
+        import pickle
+        m.estimators = pickle.loads(base64.b64decode(m.info.pop("catboost_b200_estimators")))
     params = {}
     try:
         params = json.loads(m.info.get("params", "{}"))

@@ -276,6 +276,9 @@ class Model:
     # ------------------------------------------------------------------ pool plumbing
     def pool_arrays(self, pool: Pool) -> Tuple[np.ndarray, Optional[np.ndarray]]:
         """Map a pool's columns onto the model's float / cat feature indexing."""
+        est = getattr(self, "estimators", None)
+        if est is not None and (getattr(pool, "text_data", None) or getattr(pool, "embedding_data", None)):
+            pool = pool.with_estimated(est.transform(pool), est.names)
         if pool.n_features < self.n_features:
             raise CatBoostError(f"the model needs {self.n_features} features, the data has {pool.n_features}")
         want_f = [f.flat_index for f in self.float_features]

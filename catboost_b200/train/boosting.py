@@ -344,9 +344,25 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
     if objective.needs_groups and train_pool.group_id is None:
         raise CatBoostError(f"{o.loss_name} needs group_id")
 
+    # ---- text / embedding columns -> estimated numeric features ----------------------------------------
+    estimators = None
+    if getattr(train_pool, "text_data", None) or getattr(train_pool, "embedding_data", None):
+        if ctx.is_distributed:
+            raise CatBoostError("text and embedding features are supported on one rank only")
+        if multi_target:
+            raise CatBoostError("text and embedding features need a single target")
+        from ..data.estimated import EstimatedFeatures
+        with prof.span("estimated_features"):
+            estimators = EstimatedFeatures(o.text_processing if isinstance(o.text_processing, dict) else None,
+                                           seed=int(o.random_seed))
+            n_cls = (codec.n_classes or 2) if objective.is_classification else 0
+            learn = estimators.fit(train_pool, np.asarray(y_train), int(n_cls))
+            train_pool = train_pool.with_estimated(learn, estimators.names)
+            eval_pools = [ep.with_estimated(estimators.transform(ep), estimators.names) for ep in eval_pools]
+
     # ---- features --------------------------------------------------------------------------------------
     with prof.span("quantization"):
-        plan = plan_features(o, train_pool, ctx, train_pool._quantized)
+        plan = plan_features(o, train_pool, ctx, getattr(train_pool, "_quantized", None))
         fweights = None
         if o.feature_weights is not None:
             fw = o.feature_weights
@@ -422,6 +438,7 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
             keep = max(best_it + 1, int(o.best_model_min_trees))
             base_trees = init_model.tree_count if init_model is not None else 0
             model.shrink(base_trees + keep)
+        model.estimators = estimators
         model.params = {k: v for k, v in o.items() if not k.startswith("_") and k != "callback"}
         model.info["params"] = o.to_json()
         model.info["catboost_b200_version"] = "0.1"

@@ -320,3 +320,36 @@ def test_shap_interaction_values():
     assert np.allclose(iv.sum((1, 2)), m.predict(X[:5]), atol=1e-8)
     mean_abs = np.abs(iv[:, :4, :4]).mean(0)
     assert mean_abs[1, 2] > 5 * mean_abs[0, 3]                                  # the x1 * x2 term is the interaction
+
+
+def test_text_and_embedding_features(tmp_path):
+    rng = np.random.default_rng(0)
+    n = 900
+    pos, neg = ["great", "excellent", "love", "good"], ["bad", "awful", "hate", "poor"]
+    neutral = ["the", "a", "movie", "was", "it", "very", "film"]
+    y = rng.integers(0, 2, n)
+    data = np.empty((n, 4), dtype=object)
+    data[:, :2] = rng.standard_normal((n, 2)).astype(np.float32)
+    centers = rng.standard_normal((2, 6))
+    for i in range(n):
+        w = list(rng.choice(neutral, 4)) + list(rng.choice(pos if y[i] else neg, 2))
+        rng.shuffle(w)
+        data[i, 2] = " ".join(w)
+        data[i, 3] = (centers[y[i]] * 0.6 + rng.standard_normal(6)).astype(np.float32)
+    tr, te = slice(0, 700), slice(700, n)
+    m = cb.CatBoostClassifier(iterations=30, depth=4, learning_rate=0.2, verbose=False, allow_writing_files=False)
+    m.fit(data[tr], y[tr], text_features=[2], embedding_features=[3], eval_set=(data[te], y[te]))
+    acc = float((m.predict(data[te]) == y[te]).mean())
+    assert acc > 0.9, acc
+    assert any(nm.startswith("text2_bow_") for nm in m._model.feature_names)
+    assert any(nm.startswith("emb3_knn_") for nm in m._model.feature_names)
+    path = str(tmp_path / "text.cbm")
+    m.save_model(path)
+    m2 = cb.CatBoostClassifier().load_model(path)
+    assert np.allclose(m2.predict(data[te], prediction_type="RawFormulaVal"),
+                       m.predict(data[te], prediction_type="RawFormulaVal"))
+    # text only, regression: bag of words without target statistics
+    yr = np.array([t.count("great") + t.count("love") - t.count("bad") for t in data[:, 2]], dtype=np.float32)
+    r = cb.CatBoostRegressor(iterations=40, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False)
+    r.fit(data[tr][:, [2]], yr[tr], text_features=[0])
+    assert float(np.sqrt(np.mean((r.predict(data[te][:, [2]]) - yr[te]) ** 2))) < 0.5
