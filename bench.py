@@ -27,7 +27,7 @@ import time
 
 import numpy as np
 
-BASELINE_S_PER_1000 = {"higgs": 55.601, "epsilon": 44.971, "small": None, "criteo": None}
+BASELINE_S_PER_1000 = {"higgs": 55.601, "epsilon": 44.971, "small": None, "criteo": None, "ranking": None}
 CONFIGS = {
     # rows, float features, depth, border_count
     "higgs": dict(rows=10_500_000, features=28, depth=6, border_count=128, model="Logloss symmetric depth6 10.5Mx28"),
@@ -35,6 +35,8 @@ CONFIGS = {
     "small": dict(rows=200_000, features=28, depth=6, border_count=128, model="Logloss symmetric depth6 200Kx28"),
     # categorical workload (13 numeric + 26 categorical columns, CTR features); end-to-end fit() only.  The named
     # reference config has 45M rows: pass --rows 45000000 for the full size.
+    # learning to rank: 2M documents x 700 features in groups of about 100, YetiRank, 64 borders; end-to-end fit() only
+    "ranking": dict(rows=2_000_000, features=700, depth=6, border_count=64, model="YetiRank symmetric depth6 2Mx700"),
     "criteo": dict(rows=4_500_000, features=39, depth=8, border_count=128, model="Logloss symmetric depth8 13num+26cat CTR"),
 }
 
@@ -85,6 +87,43 @@ def make_criteo_like(rows: int, rank: int, world: int, seed: int = 0):
         cols[f"c{j}"] = c.astype(np.int64)
     y = (rng.random(n, dtype=np.float32) < 1.0 / (1.0 + np.exp(-f))).astype(np.float32)
     return pd.DataFrame(cols), y, [f"c{j}" for j in range(26)]
+
+
+def bench_ranking(args, cfg, rank, world, dev):
+    """End-to-end fit() of the ranking workload: YetiRank derivatives by the per-group kernel, trees by the fused level
+    kernels; the per-iteration time is the wall time of the iterations phase."""
+    import torch
+    import catboost_b200 as cb
+    n, F = cfg["rows"] // world, cfg["features"]
+    rng = np.random.default_rng(17 + rank)
+    X = rng.standard_normal((n, F), dtype=np.float32)
+    wv = np.random.default_rng(3).standard_normal(F).astype(np.float32) / np.sqrt(F)
+    score = X @ wv + 0.5 * rng.standard_normal(n, dtype=np.float32)
+    rel = np.digitize(score, np.quantile(score[: min(n, 200000)], [0.5, 0.8, 0.93, 0.98])).astype(np.float32)
+    gid = np.arange(n) // 100
+    iters = args.e2e_iters if args.e2e_iters > 0 else max(args.steps + args.warmup, 50)
+    model = cb.CatBoostRanker(loss_function="YetiRank", iterations=iters, depth=cfg["depth"], border_count=cfg["border_count"],
+                              learning_rate=0.1, task_type="GPU", random_seed=0, allow_writing_files=False, verbose=False)
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    model.fit(X, rel, group_id=gid)
+    torch.cuda.synchronize(dev)
+    fit_s = time.perf_counter() - t0
+    tm = model._train_info.get("timings", {})
+    it_s = float(tm.get("iterations", float("nan")))
+    ndcg = model.eval_metrics(cb.Pool(X[:200000], rel[:200000], group_id=gid[:200000]), ["NDCG"], eval_period=iters)["NDCG"]
+    if rank == 0:
+        print(json.dumps({"metric": "sec/1000 iters (wall time of the iterations phase of fit())", "value": it_s / iters * 1000.0,
+                          "unit": "s/1000iter", "n_gpus": world, "steps": iters, "warmup": 0, "ms_per_step": it_s / iters * 1000.0,
+                          "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "fp32",
+                          "data": "synthetic", "impl": "ours",
+                          "config": {"model": cfg["model"], "global_batch": cfg["rows"], "seq_len": F,
+                                     "parallelism": f"doc-parallel dp{world}", "depth": cfg["depth"], "group_size": 100},
+                          "e2e": {"value": fit_s / iters * 1000.0, "unit": "s/1000iter", "fit_seconds": fit_s,
+                                  "fit_breakdown_s": {k: round(float(v), 4) for k, v in tm.items()}},
+                          "ndcg_first_last": [float(ndcg[0]), float(ndcg[-1])],
+                          "gpu_launches": int(model._train_info.get("launches_per_iter", 0)) * iters}))
+    return 0
 
 
 def bench_criteo(args, cfg, rank, world, dev):
@@ -226,6 +265,8 @@ def main():
     K, W = args.steps, args.warmup
     if args.config == "criteo":
         return bench_criteo(args, cfg, rank, world, dev)
+    if args.config == "ranking":
+        return bench_ranking(args, cfg, rank, world, dev)
     X, y = make_data(args.config, cfg["rows"], cfg["features"], rank, world)
     params = dict(loss_function="Logloss", iterations=K + W, depth=cfg["depth"], border_count=cfg["border_count"],
                   learning_rate=0.1, l2_leaf_reg=3.0, task_type="GPU", random_seed=0, allow_writing_files=False,

@@ -1,12 +1,88 @@
 """Training loggers: console lines, ``learn_error.tsv`` / ``test_error.tsv`` / ``time_left.tsv`` and
-``catboost_training.json`` under ``train_dir`` (catboost/libs/loggers/logger.h, catboost_logger_helpers.cpp).
-TensorBoard event files are not written."""
+``catboost_training.json`` under ``train_dir`` (catboost/libs/loggers/logger.h, catboost_logger_helpers.cpp), and
+TensorBoard scalar event files ``learn/events.out.tfevents`` / ``test/events.out.tfevents``
+(catboost/libs/loggers/tensorboard_logger.cpp)."""
 from __future__ import annotations
 
 import json
 import os
 import sys
 import time
+
+
+def _crc32c_table():
+    tab = []
+    for i in range(256):
+        c = i
+        for _ in range(8):
+            c = (c >> 1) ^ 0x82F63B78 if c & 1 else c >> 1
+        tab.append(c)
+    return tab
+
+
+_CRC_TAB = _crc32c_table()
+
+
+def _masked_crc32c(data: bytes) -> int:
+    c = 0xFFFFFFFF
+    for b in data:
+        c = _CRC_TAB[(c ^ b) & 0xFF] ^ (c >> 8)
+    c ^= 0xFFFFFFFF
+    return ((((c >> 15) | (c << 17)) & 0xFFFFFFFF) + 0xA282EAD8) & 0xFFFFFFFF
+
+
+def _varint(v: int) -> bytes:
+    out = bytearray()
+    v &= (1 << 64) - 1
+    while True:
+        b = v & 0x7F
+        v >>= 7
+        if v:
+            out.append(b | 0x80)
+        else:
+            out.append(b)
+            return bytes(out)
+
+
+class TensorBoardWriter:
+    """Scalar summaries in the TFRecord / Event protobuf layout, written without any TensorFlow dependency:
+    record = length (8 bytes LE), masked CRC-32C of the length, payload, masked CRC-32C of the payload;
+    payload = Event{wall_time = 1 (double), step = 2 (int64), file_version = 3 / summary = 5};
+    Summary{value = 1: {tag = 1 (string), simple_value = 2 (float)}}."""
+
+    def __init__(self, directory: str):
+        import struct
+        self._struct = struct
+        os.makedirs(directory, exist_ok=True)
+        self.fh = open(os.path.join(directory, "events.out.tfevents"), "wb")
+        self._record(self._event(time.time(), 0, version="brain.Event:2"))
+
+    def _event(self, wall, step, version=None, tag=None, value=None) -> bytes:
+        st = self._struct
+        ev = b"\x09" + st.pack("<d", wall) + b"\x10" + _varint(step)
+        if version is not None:
+            v = version.encode()
+            ev += b"\x1a" + _varint(len(v)) + v
+        if tag is not None:
+            t = tag.encode()
+            val = b"\x0a" + _varint(len(t)) + t + b"\x15" + st.pack("<f", float(value))
+            summ = b"\x0a" + _varint(len(val)) + val
+            ev += b"\x2a" + _varint(len(summ)) + summ
+        return ev
+
+    def _record(self, payload: bytes):
+        st = self._struct
+        head = st.pack("<Q", len(payload))
+        self.fh.write(head + st.pack("<I", _masked_crc32c(head)) + payload + st.pack("<I", _masked_crc32c(payload)))
+
+    def add_scalar(self, tag: str, value: float, step: int):
+        self._record(self._event(time.time(), int(step), tag=tag, value=value))
+
+    def close(self):
+        try:
+            self.fh.close()
+        except Exception:
+            pass
 
 
 class TrainLogger:
@@ -20,6 +96,7 @@ class TrainLogger:
         self.metric_names = metric_names
         self.n_eval = n_eval
         self.files = {}
+        self.tb = {}
         self.json_iters = []
         self.dir = None
         if enabled and o.allow_writing_files and o.train_dir:
@@ -33,6 +110,9 @@ class TrainLogger:
                     self.files["test"].write("iter\t" + "\t".join(metric_names) + "\n")
                 self.files["time"] = open(os.path.join(self.dir, "time_left.tsv"), "w")
                 self.files["time"].write("iter\tPassed\tRemaining\n")
+                self.tb = {"learn": TensorBoardWriter(os.path.join(self.dir, "learn"))}
+                if n_eval:
+                    self.tb["test"] = TensorBoardWriter(os.path.join(self.dir, "test"))
             except OSError:
                 self.dir = None
                 self.files = {}
@@ -64,6 +144,11 @@ class TrainLogger:
             if "test" in self.files and len(names) > 1:
                 self.files["test"].write(f"{it}\t" + "\t".join(f"{hist.data[names[1]][m][-1]:.9g}" for m in self.metric_names) + "\n")
             self.files["time"].write(f"{it}\t{int(elapsed * 1000)}\t{int(remaining * 1000)}\n")
+            for m in self.metric_names:
+                if "learn" in self.tb:
+                    self.tb["learn"].add_scalar(m, hist.data["learn"][m][-1], it)
+                if "test" in self.tb and len(names) > 1 and hist.data[names[1]][m]:
+                    self.tb["test"].add_scalar(m, hist.data[names[1]][m][-1], it)
             rec = {"iteration": it, "passed_time": elapsed, "remaining_time": remaining,
                    "learn": [hist.data["learn"][m][-1] for m in self.metric_names]}
             if len(names) > 1:
@@ -71,6 +156,9 @@ class TrainLogger:
             self.json_iters.append(rec)
 
     def close(self):
+        for w in self.tb.values():
+            w.close()
+        self.tb = {}
         for f in self.files.values():
             try:
                 f.close()

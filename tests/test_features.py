@@ -353,3 +353,27 @@ def test_text_and_embedding_features(tmp_path):
     r = cb.CatBoostRegressor(iterations=40, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False)
     r.fit(data[tr][:, [2]], yr[tr], text_features=[0])
     assert float(np.sqrt(np.mean((r.predict(data[te][:, [2]]) - yr[te]) ** 2))) < 0.5
+
+
+def test_training_logs_and_tensorboard_events(tmp_path):
+    import struct
+    from catboost_b200.utils.logging import _masked_crc32c
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((400, 4)).astype(np.float32)
+    y = (X[:, 0] > 0).astype(int)
+    d = str(tmp_path / "info")
+    cb.CatBoostClassifier(iterations=5, depth=3, verbose=False, train_dir=d).fit(X[:300], y[:300], eval_set=(X[300:], y[300:]))
+    assert os.path.exists(os.path.join(d, "learn_error.tsv")) and os.path.exists(os.path.join(d, "catboost_training.json"))
+    for part in ("learn", "test"):
+        raw = open(os.path.join(d, part, "events.out.tfevents"), "rb").read()
+        pos, records = 0, 0
+        while pos < len(raw):
+            (ln,) = struct.unpack("<Q", raw[pos:pos + 8])
+            assert struct.unpack("<I", raw[pos + 8:pos + 12])[0] == _masked_crc32c(raw[pos:pos + 8])
+            payload = raw[pos + 12:pos + 12 + ln]
+            assert struct.unpack("<I", raw[pos + 12 + ln:pos + 16 + ln])[0] == _masked_crc32c(payload)
+            pos += 16 + ln
+            records += 1
+        assert records == 1 + 5            # the version record + one scalar per iteration
+        assert b"Logloss" in raw
+    assert _masked_crc32c(b"123456789") == ((((0xE3069283 >> 15) | (0xE3069283 << 17)) & 0xFFFFFFFF) + 0xA282EAD8) & 0xFFFFFFFF
