@@ -21,14 +21,29 @@ class Profiler:
             return
         if self.sync:
             self._sync()
+        nvtx = self._nvtx()
+        if nvtx is not None:
+            nvtx.range_push(label)                # shows up as a named range in Nsight traces
         t0 = time.perf_counter()
         try:
             yield
         finally:
+            if nvtx is not None:
+                nvtx.range_pop()
             if self.sync:
                 self._sync()
             self.acc[label] = self.acc.get(label, 0.0) + time.perf_counter() - t0
             self.count[label] = self.count.get(label, 0) + 1
+
+    @staticmethod
+    def _nvtx():
+        try:
+            import torch
+            if torch.cuda.is_available():
+                return torch.cuda.nvtx
+        except Exception:
+            pass
+        return None
 
     @staticmethod
     def _sync():

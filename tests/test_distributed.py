@@ -92,3 +92,64 @@ def test_two_gpus_fused_matches_nccl_baseline():
     assert fused["acc"] > 0.9 and base["acc"] > 0.9
     assert fused["splits"] == base["splits"]
     assert np.allclose(fused["pred"], base["pred"], rtol=1e-3, atol=1e-3)
+
+
+FAIL_WORKER = r'''
+import os, sys, time, datetime
+import numpy as np
+import torch
+import torch.distributed as dist
+sys.path.insert(0, {root!r})
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+import catboost_b200 as cb
+rng = np.random.default_rng(rank)
+X = rng.standard_normal((3000, 6), dtype=np.float32)
+y = (X[:, 0] > 0).astype(np.float32)
+if rank == 1:
+    # the failure is made on the host: this rank never joins the training collectives
+    time.sleep(1.0)
+    os._exit(17)
+t0 = time.time()
+try:
+    cb.CatBoostClassifier(iterations=5, depth=3, verbose=False, allow_writing_files=False, task_type="CPU").fit(X, y)
+    print("RESULT finished-without-error", flush=True)
+except BaseException as e:
+    print("RESULT error-after %.1f s: %s" % (time.time() - t0, type(e).__name__), flush=True)
+os._exit(0)
+'''
+
+
+def test_lost_rank_is_detected_by_the_survivor():
+    """A rank that exits before the first collective: the other rank's next collective ends with an error inside the
+    process-group timeout instead of waiting forever (host-side failure, CPU ranks)."""
+    d = tempfile.mkdtemp()
+    script = os.path.join(d, "fail_worker.py")
+    with open(script, "w") as fh:
+        fh.write(FAIL_WORKER.format(root=ROOT))
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT="29617")
+        procs.append(subprocess.Popen([sys.executable, script], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                                      env=env))
+    out0, _ = procs[0].communicate(timeout=180)
+    procs[1].wait(timeout=60)
+    assert procs[1].returncode == 17
+    line = [l for l in out0.splitlines() if l.startswith("RESULT")]
+    assert line and line[0].startswith("RESULT error-after"), out0[-2000:]
+
+
+def test_corrupted_snapshot_is_rejected(tmp_path):
+    import catboost_b200 as cb
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((500, 4)).astype(np.float32)
+    y = (X[:, 0] > 0).astype(int)
+    snap = str(tmp_path / "snap.bin")
+    kw = dict(iterations=6, depth=3, verbose=False, allow_writing_files=True, train_dir=str(tmp_path / "info"),
+              save_snapshot=True, snapshot_file=snap, task_type="CPU")
+    cb.CatBoostClassifier(**kw).fit(X, y)
+    blob = bytearray(open(snap, "rb").read())
+    blob[-20] ^= 0xFF                                   # flip a byte of the payload: the stored md5 no longer matches
+    open(snap, "wb").write(bytes(blob))
+    with pytest.raises(cb.CatBoostError, match="corrupted"):
+        cb.CatBoostClassifier(**kw).fit(X, y)
