@@ -259,6 +259,27 @@ def test_yetirank_kernel_matches_tensor_reference():
     assert torch.allclose(hess[0], ref_h, rtol=2e-4, atol=2e-6)
 
 
+def test_training_is_repeatable():
+    """Two runs with the same seed choose the same splits (the tile reduction has a fixed order; only the last bits of
+    the double-precision leaf sums may differ between runs)."""
+    import catboost_b200 as cb
+    rng = np.random.default_rng(2)
+    X = rng.standard_normal((150000, 12), dtype=np.float32)
+    y = (X[:, 0] * X[:, 1] + X[:, 2] + 0.3 * rng.standard_normal(150000) > 0).astype(int)
+    runs = []
+    for _ in range(2):
+        m = cb.CatBoostClassifier(iterations=25, depth=6, learning_rate=0.2, task_type="GPU", devices="0", verbose=False,
+                                  allow_writing_files=False, random_seed=7)
+        m.fit(X, y)
+        runs.append(m)
+    s0 = [(s.feature, s.border) for s in runs[0]._model.splits]
+    s1 = [(s.feature, s.border) for s in runs[1]._model.splits]
+    assert s0 == s1
+    p0 = runs[0].predict(X[:5000], prediction_type="RawFormulaVal")
+    p1 = runs[1].predict(X[:5000], prediction_type="RawFormulaVal")
+    assert np.allclose(p0, p1, rtol=1e-5, atol=1e-6)
+
+
 def test_device_wait_times_out_without_hanging():
     """A wait on a tag nobody writes returns with the status word set (bounded spin, no trap)."""
     from catboost_b200.ops import native
