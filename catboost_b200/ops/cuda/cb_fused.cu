@@ -34,7 +34,6 @@ struct CbFusedArgs {
     int own_col[CB_MAX_RANKS + 1];   // rank r owns histogram columns [own_col[r], own_col[r+1]) (multiples of 4)
     int Wmax;                        // row stride (floats) of every slot buffer = max owned width
     int smem_floats;                 // dynamic shared memory of this launch, in floats
-    int fuse_leaf_update;            // bundled histogram path: leaf update of the previous split inside the histogram pass
     unsigned long long* phase_ts;    // optional globaltimer stamps (phase profiling): [depth][8] by block 0,
                                      // then [4096][2] per-block histogram end + SM id, then [depth][4] inside the score phase
 };
@@ -108,9 +107,8 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
     unsigned long long* ts = (a.phase_ts && cta == 0 && threadIdx.x == 0) ? a.phase_ts + level * 8 : nullptr;
     if (ts) ts[0] = cb_globaltimer();
 
-    // (0) leaf update with the split of the previous level -- done inside the histogram pass on the bundled path
-    const bool fused_update = a.fuse_leaf_update && a.h.bundle > 0 && a.h.narrow && a.h.statmax && a.h.S == 2;
-    if (level > 0 && !fused_update) {
+    // (0) leaf update with the split of the previous level
+    if (level > 0) {
         cb_update_leaf_range(a.h.d, a.leaf, sp_arr[level - 1], level - 1,
                              (long long)cta * blockDim.x + threadIdx.x, (long long)ncta * blockDim.x);
         __threadfence();
@@ -119,7 +117,7 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
 
     if (ts) ts[1] = cb_globaltimer();
     // (A) local histograms: every block dumps its shared-memory tile into its private region (no atomics)
-    cb_hist_phase(a.h, cb_sh, cta, ncta, (fused_update && level > 0) ? sp_arr + level - 1 : nullptr);
+    cb_hist_phase(a.h, cb_sh, cta, ncta);
     if (ts) ts[2] = cb_globaltimer();
     if (a.phase_ts && threadIdx.x == 0 && level == a.depth - 2) {
         unsigned int smid;
@@ -347,7 +345,6 @@ CB_API int cb_fused_launch(CbFusedPlan* p, int level, float* hprev, float* hcur,
                            int chunks, int copies, int bundle, cudaStream_t st) {
     CbFusedArgs a = p->a;
     a.h.nK = chunks; a.h.copies = copies; a.h.bundle = bundle;
-    a.fuse_leaf_update = 1;
     a.h.level = level; a.h.small_mask = mask_in; a.h.slots_per_pass = slots_per_pass;
     a.s.level = level; a.s.small_mask = mask_in; a.s.hprev = hprev; a.s.hcur = hcur;
     a.mask_out = mask_out;

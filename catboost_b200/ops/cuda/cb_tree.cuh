@@ -484,7 +484,7 @@ template <int GMAX, int V>
 __device__ __forceinline__ void cb_bundle_load(const uint32_t* bg, long long npad, const unsigned short* leaf,
                                                const float* st0, const float* st1, long long i, int gcnt,
                                                unsigned int (&w)[GMAX][V], unsigned int (&lf)[V], float (&s0)[V],
-                                               float (&s1)[V], const uint32_t* bx, unsigned int (&wx)[V]) {
+                                               float (&s1)[V]) {
     typedef typename CbVec<V>::U UV;
     typedef typename CbVec<V>::H HV;
     typedef typename CbVec<V>::F FV;
@@ -497,12 +497,6 @@ __device__ __forceinline__ void cb_bundle_load(const uint32_t* bg, long long npa
             for (int k = 0; k < V; ++k) w[gl][k] = xp[k];
         }
     }
-    if (bx) {                                    // the group row of the previous split when it is outside the bundle
-        const UV x = *reinterpret_cast<const UV*>(bx + i);
-        const unsigned int* xp = reinterpret_cast<const unsigned int*>(&x);
-#pragma unroll
-        for (int k = 0; k < V; ++k) wx[k] = xp[k];
-    }
     const HV l = *reinterpret_cast<const HV*>(leaf + i);
     const FV f0 = *reinterpret_cast<const FV*>(st0 + i);
     const FV f1 = *reinterpret_cast<const FV*>(st1 + i);
@@ -513,12 +507,9 @@ __device__ __forceinline__ void cb_bundle_load(const uint32_t* bg, long long npa
     for (int k = 0; k < V; ++k) { lf[k] = lp[k]; s0[k] = p0[k]; s1[k] = p1[k]; }
 }
 
-// prev_split (optional): the leaf update for the split of the previous level is done on the fly -- the pass reads every
-// document anyway: leaf |= bit << (level - 1), written back by the first bundle.  The update is idempotent, so bundles
-// that read a row before or after the write-back see the same value.
 template <int GMAX>
 static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int gcnt, int chunk, int nK,
-                                      int slot_begin, int slot_count, const CbSplit* prev_split) {
+                                      int slot_begin, int slot_count) {
     constexpr int V = CB_BUNDLE_V(GMAX);
     const int B = a.B;
     const int C = a.copies > 0 ? a.copies : 1;
@@ -551,25 +542,6 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
     const unsigned int lt = (1u << lane) - 1u;
     unsigned int head = 0, tail = 0;
     const long long step = blk * nK;
-    // fused leaf update with the split of the previous level
-    int up_gl = -1, up_sh = 0, up_bin = 0;
-    bool up = false, up_onehot = false, up_store = false;
-    const uint32_t* bx = nullptr;
-    if (prev_split && level > 0) {
-        const CbSplit ps = *prev_split;
-        if (ps.feature >= 0) {
-            up = true;
-            const int pg = ps.feature >> 2;
-            up_sh = (ps.feature & 3) * 8;
-            up_bin = ps.bin;
-            up_onehot = ps.flags & 1;
-            if (pg >= g0 && pg < g0 + gcnt) up_gl = pg - g0; else bx = a.d.bins + (long long)pg * npad;
-            up_store = (g0 == 0);
-        }
-    }
-    unsigned int wx[V];
-#pragma unroll
-    for (int k = 0; k < V; ++k) wx[k] = 0u;
 #if CB_BUNDLE_PF
     unsigned int nw[GMAX][V];
     unsigned int nlf[V];
@@ -580,12 +552,8 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
         for (int gl = 0; gl < GMAX; ++gl) nw[gl][k] = 0u;
         nlf[k] = 0u; ns0[k] = 0.f; ns1[k] = 0.f;
     }
-    unsigned int nwx[V];
-#pragma unroll
-    for (int k = 0; k < V; ++k) nwx[k] = 0u;
     if (blk * chunk + (long long)threadIdx.x * V < d_end)
-        cb_bundle_load<GMAX, V>(bg, npad, a.leaf, st0, st1, blk * chunk + (long long)threadIdx.x * V, gcnt, nw, nlf, ns0,
-                                ns1, bx, nwx);
+        cb_bundle_load<GMAX, V>(bg, npad, a.leaf, st0, st1, blk * chunk + (long long)threadIdx.x * V, gcnt, nw, nlf, ns0, ns1);
 #endif
     // i - lane * V is the same in all lanes of a warp, so the loop bound is warp-uniform (ballots inside)
     for (long long i = blk * chunk + (long long)threadIdx.x * V; i - lane * V < d_end; i += step) {
@@ -597,33 +565,12 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
         for (int k = 0; k < V; ++k) {
 #pragma unroll
             for (int gl = 0; gl < GMAX; ++gl) w[gl][k] = nw[gl][k];
-            lf[k] = nlf[k]; s0[k] = ns0[k]; s1[k] = ns1[k]; wx[k] = nwx[k];
+            lf[k] = nlf[k]; s0[k] = ns0[k]; s1[k] = ns1[k];
         }
-        if (i + step < d_end)
-            cb_bundle_load<GMAX, V>(bg, npad, a.leaf, st0, st1, i + step, gcnt, nw, nlf, ns0, ns1, bx, nwx);
+        if (i + step < d_end) cb_bundle_load<GMAX, V>(bg, npad, a.leaf, st0, st1, i + step, gcnt, nw, nlf, ns0, ns1);
 #else
-        if (i < d_end) cb_bundle_load<GMAX, V>(bg, npad, a.leaf, st0, st1, i, gcnt, w, lf, s0, s1, bx, wx);
+        if (i < d_end) cb_bundle_load<GMAX, V>(bg, npad, a.leaf, st0, st1, i, gcnt, w, lf, s0, s1);
 #endif
-        if (up && i < d_end) {
-#pragma unroll
-            for (int k = 0; k < V; ++k) {
-                unsigned int word = wx[k];
-#pragma unroll
-                for (int gl = 0; gl < GMAX; ++gl)
-                    if (gl == up_gl) word = w[gl][k];
-                const unsigned int bv = (word >> up_sh) & 255u;
-                const unsigned int r = up_onehot ? (bv == (unsigned int)up_bin) : (bv > (unsigned int)up_bin);
-                lf[k] |= r << (level - 1);
-            }
-            if (up_store) {
-                typedef typename CbVec<V>::H HV;
-                HV o;
-                unsigned short* op = reinterpret_cast<unsigned short*>(&o);
-#pragma unroll
-                for (int k = 0; k < V; ++k) op[k] = (unsigned short)lf[k];
-                *reinterpret_cast<HV*>(const_cast<unsigned short*>(a.leaf) + i) = o;
-            }
-        }
 #pragma unroll
         for (int k = 0; k < V; ++k) {
             bool take = (i + k) < d_end;
@@ -696,8 +643,7 @@ __device__ __forceinline__ int cb_hist_chunks(int G, int ncta, long long n, int 
 }
 
 // Static work split used by both launch styles: item -> (group or bundle of groups, chunk).
-static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, int ncta,
-                                     const CbSplit* prev_split = nullptr) {
+static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, int ncta) {
     const int G = a.d.G;
     const int nK = cb_hist_chunks(G, ncta, a.d.n, a.nK);
     long long per = (a.d.n + nK - 1) / nK;
@@ -726,9 +672,9 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
                 const int g0 = g * gpc;
                 const int gcnt = min(gpc, G - g0);
                 int* shi = reinterpret_cast<int*>(sh);
-                if (gpc <= 2) cb_hist_bundle<2>(a, shi, g0, gcnt, (int)k, nK, sb, sc, prev_split);
-                else if (gpc <= 4) cb_hist_bundle<4>(a, shi, g0, gcnt, (int)k, nK, sb, sc, prev_split);
-                else cb_hist_bundle<8>(a, shi, g0, gcnt, (int)k, nK, sb, sc, prev_split);
+                if (gpc <= 2) cb_hist_bundle<2>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
+                else if (gpc <= 4) cb_hist_bundle<4>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
+                else cb_hist_bundle<8>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
                 continue;
             }
             const long long b = k * per;
