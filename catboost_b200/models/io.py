@@ -537,8 +537,16 @@ def save_model(m: Model, fname: str, format: str = "cbm", export_parameters=None
     elif fmt == "cpp":
         with open(fname, "w") as fh:
             fh.write(model_to_cpp(m))
-    elif fmt in ("onnx", "coreml", "pmml"):
-        raise CatBoostError(f"export format {format!r} is not available in this build (no {fmt} writer dependency)")
+    elif fmt == "onnx":
+        from .export import model_to_onnx_bytes
+        with open(fname, "wb") as fh:
+            fh.write(model_to_onnx_bytes(m))
+    elif fmt == "pmml":
+        from .export import model_to_pmml
+        with open(fname, "w") as fh:
+            fh.write(model_to_pmml(m))
+    elif fmt == "coreml":
+        raise CatBoostError("export format 'coreml' is not available in this build")
     else:
         raise CatBoostError(f"unknown model format {format!r}")
 

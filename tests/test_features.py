@@ -377,3 +377,114 @@ def test_training_logs_and_tensorboard_events(tmp_path):
         assert records == 1 + 5            # the version record + one scalar per iteration
         assert b"Logloss" in raw
     assert _masked_crc32c(b"123456789") == ((((0xE3069283 >> 15) | (0xE3069283 << 17)) & 0xFFFFFFFF) + 0xA282EAD8) & 0xFFFFFFFF
+
+
+def _pb_fields(buf):
+    """Generic protobuf reader: list of (field, wire type, value) of one message."""
+    out, pos = [], 0
+    while pos < len(buf):
+        key, shift = 0, 0
+        while True:
+            b = buf[pos]; pos += 1
+            key |= (b & 0x7F) << shift; shift += 7
+            if not b & 0x80:
+                break
+        field, wire = key >> 3, key & 7
+        if wire == 0:
+            v, shift = 0, 0
+            while True:
+                b = buf[pos]; pos += 1
+                v |= (b & 0x7F) << shift; shift += 7
+                if not b & 0x80:
+                    break
+        elif wire == 2:
+            ln, shift = 0, 0
+            while True:
+                b = buf[pos]; pos += 1
+                ln |= (b & 0x7F) << shift; shift += 7
+                if not b & 0x80:
+                    break
+            v = buf[pos:pos + ln]; pos += ln
+        elif wire == 5:
+            v = buf[pos:pos + 4]; pos += 4
+        else:
+            v = buf[pos:pos + 8]; pos += 8
+        out.append((field, wire, v))
+    return out
+
+
+def test_onnx_and_pmml_export(tmp_path):
+    """The ONNX file is decoded with a generic protobuf reader and its tree ensemble is evaluated by hand; the PMML file is
+    parsed as XML and evaluated by hand.  Both must reproduce the model's predictions."""
+    import struct
+    import xml.etree.ElementTree as ET
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((400, 5)).astype(np.float32)
+    y = (2 * X[:, 0] - X[:, 3] + 0.1 * rng.standard_normal(400)).astype(np.float32)
+    m = cb.CatBoostRegressor(iterations=12, depth=3, learning_rate=0.3, verbose=False, allow_writing_files=False).fit(X, y)
+    ref = m.predict(X[:30])
+    # ---- ONNX
+    p = str(tmp_path / "m.onnx")
+    m.save_model(p, format="onnx")
+    model = _pb_fields(open(p, "rb").read())
+    graph = _pb_fields([v for f, w, v in model if f == 7][0])
+    node = _pb_fields([v for f, w, v in graph if f == 1][0])
+    assert [v for f, w, v in node if f == 4][0] == b"TreeEnsembleRegressor"
+    attrs = {}
+    for f, w, v in node:
+        if f == 5:
+            a = _pb_fields(v)
+            name = [x for ff, ww, x in a if ff == 1][0].decode()
+            if any(ff == 8 for ff, _, _ in a):
+                packed = [x for ff, ww, x in a if ff == 8][0]
+                vals, pos = [], 0
+                while pos < len(packed):
+                    val, shift = 0, 0
+                    while True:
+                        b = packed[pos]; pos += 1
+                        val |= (b & 0x7F) << shift; shift += 7
+                        if not b & 0x80:
+                            break
+                    vals.append(val)
+                attrs[name] = vals
+            elif any(ff == 7 for ff, _, _ in a):
+                packed = [x for ff, ww, x in a if ff == 7][0]
+                attrs[name] = list(struct.unpack(f"<{len(packed) // 4}f", packed))
+            elif any(ff == 9 for ff, _, _ in a):
+                attrs[name] = [x.decode() for ff, ww, x in a if ff == 9]
+    nodes = {(t, n): k for k, (t, n) in enumerate(zip(attrs["nodes_treeids"], attrs["nodes_nodeids"]))}
+    leaf_w = {(t, n): w for t, n, w in zip(attrs["target_treeids"], attrs["target_nodeids"], attrs["target_weights"])}
+    pred = np.full(30, attrs["base_values"][0], dtype=np.float64)
+    for r in range(30):
+        for t in sorted(set(attrs["nodes_treeids"])):
+            n = 0
+            while True:
+                k = nodes[(t, n)]
+                if attrs["nodes_modes"][k] == "LEAF":
+                    pred[r] += leaf_w[(t, n)]
+                    break
+                go = X[r, attrs["nodes_featureids"][k]] > attrs["nodes_values"][k]
+                n = attrs["nodes_truenodeids"][k] if go else attrs["nodes_falsenodeids"][k]
+    assert np.allclose(pred, ref, atol=1e-4)
+    # ---- PMML
+    p2 = str(tmp_path / "m.pmml")
+    m.save_model(p2, format="pmml")
+    ns = {"p": "http://www.dmg.org/PMML-4_3"}
+    root = ET.parse(p2).getroot()
+    names = [f"{i}" for i in range(5)]
+    const = float(root.find(".//p:Target", ns).get("rescaleConstant"))
+
+    def walk(node, row):
+        for child in node.findall("p:Node", ns):
+            sp = child.find("p:SimplePredicate", ns)
+            ok = True if sp is None else row[names.index(sp.get("field"))] > float(sp.get("value"))
+            if ok:
+                return float(child.get("score")) if child.get("score") is not None else walk(child, row)
+        raise AssertionError("no branch taken")
+
+    pred2 = np.full(30, const)
+    for r in range(30):
+        for tm in root.iterfind(".//p:TreeModel", ns):
+            top = tm.find("p:Node", ns)
+            pred2[r] += float(top.get("score")) if top.get("score") is not None else walk(top, X[r])
+    assert np.allclose(pred2, ref, atol=1e-4)
