@@ -9,9 +9,10 @@
 // delta; a second grid barrier releases the other blocks into the next step.
 //
 // Cells: the first step uses fp32 cells (shared fp32 atomics are compare-and-swap loops, but the scale of the values
-// is not known yet) and records max |w der|, max |w hess|; later steps scale to 24 bits against twice those bounds
-// and add a signed high and an unsigned low part with native integer atomics.  A value beyond the bound goes to the
-// double accumulator directly.
+// is not known yet) and records max |w der|, max |w hess|; later steps use fixed point with native integer atomics:
+// one int32 cell per (leaf, statistic, replica), scaled so that twice the recorded bound times the number of documents
+// a replica can receive stays below 2^31 (about 21 bits per value with 32 replicas at 10M documents -- finer than what
+// an fp32 running sum keeps).  A value beyond the bound goes to the double accumulator directly.
 #include "cb_common.cuh"
 #include "cb_losses.cuh"
 #include "cb_comm.cuh"
@@ -46,7 +47,7 @@ __device__ __forceinline__ void cb_leaf_docs_load(const CbLeafNewtonArgs& a, lon
 
 // C = replicas of every cell (lane l uses replica l & (C-1)), a power of two <= 32.
 template <int LOSS>
-__global__ void __launch_bounds__(512) cb_leaf_newton_kernel(CbLeafNewtonArgs a, int C) {
+__global__ void __launch_bounds__(512, 2) cb_leaf_newton_kernel(CbLeafNewtonArgs a, int C) {
     extern __shared__ float sl[];                 // cells: [L][4][C]; then delta copy: [L]
     cg::grid_group grid = cg::this_grid();
     const int loss = LOSS >= 0 ? LOSS : a.loss;
@@ -61,7 +62,10 @@ __global__ void __launch_bounds__(512) cb_leaf_newton_kernel(CbLeafNewtonArgs a,
     const bool solo = a.c.nranks <= 1;
     const long long n4 = (a.n + 3) >> 2;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    const bool can_quant = (a.n / gridDim.x) < (1ll << 19);
+    const bool can_quant = (a.n / gridDim.x) < (1ll << 22);
+    // documents one replica of a cell can receive: those of the threads that share the replica index
+    const long long per_thread = ((n4 + stride - 1) / stride) * 4;
+    const float qcap = fminf(8388607.0f, floorf(2147483647.0f / (float)(per_thread * (blockDim.x / C) + 1)) - 1.0f);
     for (int step = 0; step < a.steps; ++step) {
         const bool first = step == 0, last = step == a.steps - 1;
         const bool quant = !first && can_quant;
@@ -69,8 +73,8 @@ __global__ void __launch_bounds__(512) cb_leaf_newton_kernel(CbLeafNewtonArgs a,
         if (quant) {
             M0 = 2.0f * fmaxf(__ldcg(a.vmax), 1e-30f);
             M1 = 2.0f * fmaxf(__ldcg(a.vmax + 1), 1e-30f);
-            sc0 = 8388607.0f / M0;
-            sc1 = 8388607.0f / M1;
+            sc0 = qcap / M0;
+            sc1 = qcap / M1;
         }
         double* S = a.sums + (solo ? (size_t)(step % 3) * 3 * L : 0);
         for (int i = threadIdx.x; i < 4 * L * C; i += blockDim.x) sl[i] = 0.0f;
@@ -99,13 +103,10 @@ __global__ void __launch_bounds__(512) cb_leaf_newton_kernel(CbLeafNewtonArgs a,
                 const float w = wt[k];
                 const float vd = w * o.der, vh = w * o.hess;
                 if (quant) {
-                    if (fabsf(vd) <= M0 && fabsf(vh) <= M1) {
-                        const int qd = __float2int_rn(vd * sc0), qh = __float2int_rn(vh * sc1);
+                    if (fmaxf(fabsf(vd) * sc0, fabsf(vh) * sc1) <= qcap) {
                         int* cell = si + (size_t)(l * 4) * C + lane_copy;
-                        atomicAdd(cell, qd >> 12);
-                        atomicAdd(reinterpret_cast<unsigned int*>(cell + C), (unsigned int)qd & 4095u);
-                        atomicAdd(cell + 2 * C, qh >> 12);
-                        atomicAdd(reinterpret_cast<unsigned int*>(cell + 3 * C), (unsigned int)qh & 4095u);
+                        atomicAdd(cell, __float2int_rn(vd * sc0));
+                        atomicAdd(cell + C, __float2int_rn(vh * sc1));
                     } else {
                         atomicAdd(&S[3 * l], (double)vd);
                         atomicAdd(&S[3 * l + 1], (double)vh);
@@ -134,13 +135,12 @@ __global__ void __launch_bounds__(512) cb_leaf_newton_kernel(CbLeafNewtonArgs a,
         }
         __syncthreads();
         if (quant) {
-            const double inv0 = (double)M0 / 8388607.0, inv1 = (double)M1 / 8388607.0;
+            const double inv0 = (double)M0 / (double)qcap, inv1 = (double)M1 / (double)qcap;
             for (int i = threadIdx.x; i < 2 * L; i += blockDim.x) {
                 const int l = i >> 1, s2 = i & 1;
-                const int* ph = si + (size_t)(l * 4 + 2 * s2) * C;
-                long long hi = 0, lo = 0;
-                for (int c = 0; c < C; ++c) { hi += ph[c]; lo += (unsigned int)ph[C + c]; }
-                const long long qq = hi * 4096 + lo;
+                const int* ph = si + (size_t)(l * 4 + s2) * C;
+                long long qq = 0;
+                for (int c = 0; c < C; ++c) qq += ph[c];
                 if (qq != 0) atomicAdd(&S[3 * l + s2], (double)qq * (s2 ? inv1 : inv0));
             }
         } else {
