@@ -115,6 +115,9 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
         grid.sync();
     }
 
+    // the score noise scale only depends on the iteration: one thread per block works it out now, off the critical path
+    __shared__ float s_noise_std;
+    if (threadIdx.x == 0) s_noise_std = cb_noise_std(a.s);
     if (ts) ts[1] = cb_globaltimer();
     // (A) local histograms: every block dumps its shared-memory tile into its private region (no atomics)
     cb_hist_phase(a.h, cb_sh, cta, ncta);
@@ -150,7 +153,8 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
     }
 
     if (ts) ts[4] = cb_globaltimer();
-    cb_score_phase(a.s, cta, ncta, cb_sh, a.smem_floats, ts ? a.phase_ts + a.depth * 8 + 8192 + level * 4 : nullptr);
+    cb_score_phase(a.s, cta, ncta, cb_sh, a.smem_floats, ts ? a.phase_ts + a.depth * 8 + 8192 + level * 4 : nullptr,
+                   s_noise_std);
     __threadfence();
     grid.sync();
     if (ts) ts[5] = cb_globaltimer();

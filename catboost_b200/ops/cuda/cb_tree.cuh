@@ -802,7 +802,9 @@ static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, 
             const bool is_w = pass == 0;
             const int c_st = is_w ? S - 1 : pass - 1;
             float* pre = is_w ? pw : ps;
-            // lane owns bins [lane * bpl, lane * bpl + bpl): inclusive prefix inside the lane, then one warp scan
+            // lane owns bins [lane * bpl, lane * bpl + bpl): inclusive prefix inside the lane, then one warp scan.
+            // (Issuing all loads of the leaf first in an unrolled loop was measured slower: more instruction lines to
+            // fetch cost more than the overlapped load latency saved.)
             float run = 0.0f;
             for (int k = 0; k < bpl; ++k) {
                 const int bin = lane * bpl + k;
@@ -867,12 +869,14 @@ static __device__ void cb_score_finalize(const CbScoreArgs& a, int f, const floa
 // least CB_SCORE_WARP_FLOATS per scoring warp.  With fewer features than warps several warps score one feature: they
 // split the leaves and the first of them adds the partial terms up, so the per-feature chain of dependent loads is
 // L / warps long instead of L.
+// noise_in >= 0: the standard deviation of the score noise, already computed by the caller (it only depends on the
+// iteration, so the fused kernel computes it while the histogram phase runs); < 0: compute it here.
 static __device__ void cb_score_phase(const CbScoreArgs& a, int cta, int ncta, float* red, int red_floats,
-                                      unsigned long long* ts = nullptr) {
+                                      unsigned long long* ts = nullptr, float noise_in = -1.0f) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int wpc = min((int)(blockDim.x >> 5), red_floats / CB_SCORE_WARP_FLOATS);    // scoring warps per block
-    float noise_std = 0.0f;
-    if (a.random_strength > 0.0f) {
+    float noise_std = fmaxf(noise_in, 0.0f);
+    if (noise_in < 0.0f && a.random_strength > 0.0f) {
         if (lane == 0) noise_std = cb_noise_std(a);
         noise_std = __shfl_sync(0xffffffffu, noise_std, 0);
     }
