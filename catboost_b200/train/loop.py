@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import math
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
@@ -403,6 +404,53 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
     pinned = torch.zeros(2, dtype=torch.float64).pin_memory()
     pinned_ev = torch.zeros(max(1, 2 * len(evs)), dtype=torch.float64).pin_memory()
     fin = (lambda v: math.sqrt(max(v, 0.0))) if objective.name == "RMSE" else (lambda v: v)
+    # Plain per-iteration logging of the objective (no evaluation sets, detector or callbacks): the learn loss after j trees
+    # is what iteration j accumulates at its start, so it is read from the device history one iteration behind the
+    # launches, on a side stream that only waits for the iteration before the one in flight -- the GPU never idles for
+    # the host, and no extra pass over the data is needed.  The last value comes from an explicit pass.
+    lagged = bool(cheap and want_log and period == 1 and not evs and od is None and not callbacks and dev.type == "cuda"
+                  and os.environ.get("CB200_LAGGED_LOG", "1") != "0")
+    if lagged:
+        with prof.span("iterations"):
+            side = torch.cuda.Stream(dev)
+            main = torch.cuda.current_stream(dev)
+            ev_prev, next_log = None, 0
+
+            def read_row(j):
+                row = eng.loss_hist[j]
+                if eng.R > 1:
+                    row = row.clone()
+                    ctx.all_reduce_sum_(row)
+                pinned.copy_(row, non_blocking=True)
+
+            def emit(idx, value):
+                hist.iters.append(idx)
+                hist.add("learn", metrics[0], fin(value))
+                logger.log_iteration(idx, T, hist, time.time() - t_loop)
+
+            while done < T:
+                eng.step(1)
+                done += 1
+                ev_cur = torch.cuda.Event()
+                ev_cur.record(main)
+                if ev_prev is not None:
+                    with torch.cuda.stream(side):
+                        side.wait_event(ev_prev)
+                        read_row(done - 2)                    # complete once iteration done-2 has finished
+                    side.synchronize()
+                    if done - 3 >= next_log:
+                        emit(done - 3, float(pinned[0]) / max(float(pinned[1]), 1e-300))
+                        next_log = done - 2
+                ev_prev = ev_cur
+                if eng.arena is not None and (done % 64 == 0):
+                    eng.arena.check_status()
+            torch.cuda.synchronize(dev)
+            for idx in range(next_log, T - 1):
+                read_row(idx + 1)
+                torch.cuda.current_stream(dev).synchronize()
+                emit(idx, float(pinned[0]) / max(float(pinned[1]), 1e-300))
+            emit(T - 1, eng.current_learn_loss(pinned))
+            sp, vals, wts = eng.finish()
     with prof.span("iterations"):
         while done < T and not stop:
             k = min(period, T - done)
@@ -442,7 +490,8 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
             for cb in callbacks:
                 if cb.after_iteration(_CallbackInfo(it, hist.data)) is False:
                     stop = True
-        sp, vals, wts = eng.finish()
+        if not lagged:
+            sp, vals, wts = eng.finish()
     if stop and od is not None and od.stopped:
         logger.info(f"Stopped by overfitting detector  ({od.wait} iterations wait)")
     trees = [dict(kind="oblivious", splits=sp[t], node_split=None, leaf_of_node=None, values=vals[t], weights=wts[t])

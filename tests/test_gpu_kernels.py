@@ -280,6 +280,24 @@ def test_training_is_repeatable():
     assert np.allclose(p0, p1, rtol=1e-5, atol=1e-6)
 
 
+def test_logged_learn_curve_matches_model():
+    """Per-iteration logging reads the learn loss from the device history behind the launches: the logged curve must be
+    the loss of the model after each tree."""
+    import io
+    import catboost_b200 as cb
+    rng = np.random.default_rng(3)
+    X = rng.standard_normal((40000, 8), dtype=np.float32)
+    y = (X[:, 0] + X[:, 1] * X[:, 2] > 0).astype(int)
+    for T in (1, 2, 9):
+        m = cb.CatBoostClassifier(iterations=T, depth=4, learning_rate=0.3, task_type="GPU", devices="0", verbose=True,
+                                  allow_writing_files=False)
+        m.fit(X, y, log_cout=io.StringIO())
+        logged = m.get_evals_result()["learn"]["Logloss"]
+        assert len(logged) == T
+        ref = m.eval_metrics(cb.Pool(X, y), ["Logloss"])["Logloss"]
+        assert np.allclose(logged, ref, rtol=1e-4, atol=1e-5), (T, logged, ref)
+
+
 def test_device_wait_times_out_without_hanging():
     """A wait on a tag nobody writes returns with the status word set (bounded spin, no trap)."""
     from catboost_b200.ops import native
