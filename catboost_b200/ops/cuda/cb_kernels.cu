@@ -762,43 +762,101 @@ struct CbPredictArgs {
     float* out;                  // [dims][n]
 };
 
+// Four rows per thread (1024 rows per block): the split descriptors of a chunk of trees are staged in shared memory
+// as one word (feature << 8 | bin) per split, so a tree level costs one broadcast read + per row one byte read, a
+// compare and an or.
+#define CB_PRED_CHUNK_SPLITS 3072
+template <int CB_PRED_ROWS>
 __global__ void __launch_bounds__(256) cb_predict_kernel(CbPredictArgs a) {
-    extern __shared__ unsigned char sb[];     // [U][256]
-    const long long row0 = (long long)blockIdx.x * 256;
-    const int nrow = (int)min((long long)256, a.n - row0);
-    // quantise: thread = row, loop over features (rows are read with stride ldx; L1 absorbs the re-use)
+    extern __shared__ unsigned char sb[];     // [U][1024] bins, then uint32 desc[CB_PRED_CHUNK_SPLITS]
+    const int RB = 256 * CB_PRED_ROWS;
+    unsigned int* desc = reinterpret_cast<unsigned int*>(sb + (((size_t)a.U * RB + 15) & ~(size_t)15));
+    const long long row0 = (long long)blockIdx.x * RB;
+    const int nrow = (int)min((long long)RB, a.n - row0);
+    // quantise: thread = row (4 of them), loop over features; rows are read with stride ldx, L1 absorbs the re-use
     for (int u = 0; u < a.U; ++u) {
-        if (threadIdx.x < nrow) {
-            const float v = a.X[(row0 + threadIdx.x) * a.ldx + a.used_feat[u]];
-            const int b0 = a.border_off[u], b1 = a.border_off[u + 1];
-            int bin;
-            if (v != v) bin = (a.nan_is_max && a.nan_is_max[u]) ? (b1 - b0) : 0;
-            else {
-                int lo = b0, hi = b1;
-                while (lo < hi) { const int mid = (lo + hi) >> 1; if (__ldg(a.borders + mid) < v) lo = mid + 1; else hi = mid; }
-                bin = lo - b0;
+        const int b0 = a.border_off[u], nbd = a.border_off[u + 1] - b0;
+        const float* bd = a.borders + b0;
+        const int col = a.used_feat[u];
+        const bool nmax = a.nan_is_max && a.nan_is_max[u];
+#pragma unroll
+        for (int r = 0; r < CB_PRED_ROWS; ++r) {
+            const int lr = r * 256 + threadIdx.x;
+            if (lr < nrow) {
+                const float v = a.X[(row0 + lr) * a.ldx + col];
+                int pos = 0;                       // borders < v, fixed power-of-two steps (no data-dependent trip count)
+#pragma unroll
+                for (int step = 128; step > 0; step >>= 1) {
+                    const int idx = pos + step;
+                    if (idx <= nbd && __ldg(bd + idx - 1) < v) pos = idx;
+                }
+                sb[(u * 256 + threadIdx.x) * CB_PRED_ROWS + r] = (unsigned char)((v != v) ? (nmax ? nbd : 0) : pos);
             }
-            sb[u * 256 + threadIdx.x] = (unsigned char)bin;
         }
     }
-    __syncthreads();
-    if (threadIdx.x >= nrow) return;
-    float acc[8];
+    float acc[CB_PRED_ROWS][8];
     const int dims = min(a.dims, 8);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
-    for (int t = 0; t < a.T; ++t) {
-        const int depth = a.tree_depth[t];
-        const int so = a.tree_split_off[t];
-        int leaf = 0;
-        for (int k = 0; k < depth; ++k) {
-            const unsigned int b = sb[(int)a.split_feat[so + k] * 256 + threadIdx.x];
-            leaf |= (b > (unsigned int)a.split_bin[so + k]) << k;
+    for (int r = 0; r < CB_PRED_ROWS; ++r)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[r][k] = 0.0f;
+    int t = 0;
+    while (t < a.T) {
+        // trees [t, t_end): as many as fit into the descriptor buffer
+        const int s_begin = a.tree_split_off[t];
+        int t_end = t, s_end = s_begin;
+        while (t_end < a.T && a.tree_split_off[t_end] + a.tree_depth[t_end] - s_begin <= CB_PRED_CHUNK_SPLITS) {
+            s_end = a.tree_split_off[t_end] + a.tree_depth[t_end];
+            ++t_end;
         }
-        const float* lv = a.leaf_vals + (a.tree_leaf_off[t] + leaf) * a.dims;
-        for (int k = 0; k < dims; ++k) acc[k] += __ldg(lv + k);
+        if (t_end == t) return;                     // a single tree deeper than the buffer cannot happen (depth <= 16)
+        __syncthreads();
+        for (int i = threadIdx.x; i < s_end - s_begin; i += blockDim.x)
+            desc[i] = ((unsigned int)a.split_feat[s_begin + i] << 8) | (unsigned int)a.split_bin[s_begin + i];
+        __syncthreads();
+        for (int tt = t; tt < t_end; ++tt) {
+            const int depth = a.tree_depth[tt];
+            const unsigned int* dsc = desc + (a.tree_split_off[tt] - s_begin);
+            int leaf[CB_PRED_ROWS];
+            if (CB_PRED_ROWS == 4 && depth <= 8) {
+                // the bins of the thread's four rows sit in one word: one per-byte compare decides all four rows
+                unsigned int leaf4 = 0u;
+                const unsigned int* words = reinterpret_cast<const unsigned int*>(sb) + threadIdx.x;
+                for (int k = 0; k < depth; ++k) {
+                    const unsigned int d = dsc[k];
+                    const unsigned int w = words[(d >> 8) * 256];
+                    const unsigned int m = __vcmpgtu4(w, __byte_perm(d, 0, 0x0000));
+                    leaf4 |= (m & 0x01010101u) << k;
+                }
+#pragma unroll
+                for (int r = 0; r < CB_PRED_ROWS; ++r) leaf[r] = (int)((leaf4 >> (8 * r)) & 255u);
+            } else {
+#pragma unroll
+                for (int r = 0; r < CB_PRED_ROWS; ++r) leaf[r] = 0;
+                for (int k = 0; k < depth; ++k) {
+                    const unsigned int d = dsc[k];
+                    const unsigned char* col = sb + ((d >> 8) * 256 + threadIdx.x) * CB_PRED_ROWS;
+                    const unsigned int thr = d & 255u;
+#pragma unroll
+                    for (int r = 0; r < CB_PRED_ROWS; ++r) leaf[r] |= ((unsigned int)col[r] > thr) << k;
+                }
+            }
+            const float* lv0 = a.leaf_vals + a.tree_leaf_off[tt] * a.dims;
+#pragma unroll
+            for (int r = 0; r < CB_PRED_ROWS; ++r) {
+                const float* lv = lv0 + (long long)leaf[r] * a.dims;
+                for (int k = 0; k < dims; ++k) acc[r][k] += __ldg(lv + k);
+            }
+        }
+        t = t_end;
     }
-    for (int k = 0; k < dims; ++k) a.out[(long long)k * a.n + row0 + threadIdx.x] = acc[k] * a.scale + (a.bias ? a.bias[k] : 0.0f);
+#pragma unroll
+    for (int r = 0; r < CB_PRED_ROWS; ++r) {
+        const int lr = r * 256 + threadIdx.x;
+        if (lr < nrow)
+            for (int k = 0; k < dims; ++k)
+                a.out[(long long)k * a.n + row0 + lr] = acc[r][k] * a.scale + (a.bias ? a.bias[k] : 0.0f);
+    }
 }
 
 CB_API int cb_predict_oblivious(const float* X, long long n, long long ldx, const int* used_feat, const float* borders,
@@ -807,16 +865,26 @@ CB_API int cb_predict_oblivious(const float* X, long long n, long long ldx, cons
                                 const unsigned char* split_bin, const long long* tree_leaf_off, const float* leaf_vals,
                                 int T, int dims, float scale, const float* bias, float* out, cudaStream_t st) {
     if (n <= 0) return 0;
-    if (dims > 8 || U * 256 > 200 * 1024) return (int)cudaErrorInvalidValue;
+    // four rows per thread when the bins of 1024 rows fit in shared memory, else one row per thread
+    int rows = 4;
+    size_t pred_smem = (((size_t)U * 256 * rows + 15) & ~(size_t)15) + CB_PRED_CHUNK_SPLITS * 4;
+    if (pred_smem > 200 * 1024) {
+        rows = 1;
+        pred_smem = (((size_t)U * 256 + 15) & ~(size_t)15) + CB_PRED_CHUNK_SPLITS * 4;
+    }
+    if (dims > 8 || pred_smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     CbPredictArgs a{X, n, ldx, used_feat, borders, border_off, nan_is_max, U, tree_depth, tree_split_off, split_feat,
                     split_bin, tree_leaf_off, leaf_vals, T, dims, scale, bias, out};
     static int set = 0;
     if (!set) {
-        cudaError_t e = cudaFuncSetAttribute(cb_predict_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(cb_predict_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_predict_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
         set = 1;
     }
-    cb_predict_kernel<<<(unsigned)((n + 255) / 256), 256, U * 256, st>>>(a);
+    const unsigned pred_grid = (unsigned)((n + 256 * rows - 1) / (256 * rows));
+    if (rows == 4) cb_predict_kernel<4><<<pred_grid, 256, pred_smem, st>>>(a);
+    else cb_predict_kernel<1><<<pred_grid, 256, pred_smem, st>>>(a);
     CB_LAUNCH_CHECK();
     return 0;
 }

@@ -182,6 +182,11 @@ def test_gpu_fit_predict_and_gpu_apply():
     assert np.allclose(p_cpu, p_gpu, rtol=1e-4, atol=1e-4)
     acc = float((m.predict(X[50000:]) == y[50000:]).mean())
     assert acc > 0.88, acc
+    # deeper than 8 levels: the apply kernel takes its per-row path instead of the four-rows-per-word compare
+    deep = cb.CatBoostClassifier(iterations=6, depth=10, learning_rate=0.2, task_type="GPU", devices="0", verbose=False,
+                                 allow_writing_files=False).fit(X[:50000], y[:50000])
+    assert np.allclose(deep.predict(X[50000:], prediction_type="RawFormulaVal"),
+                       deep.predict(X[50000:], prediction_type="RawFormulaVal", task_type="GPU"), rtol=1e-4, atol=1e-4)
 
 
 def test_gpu_regression_rmse():
