@@ -115,6 +115,9 @@ def plan_ctrs(o, pool: Pool, ctr_cats: List[int], ctx) -> CtrPlan:
         # The reference discovers combinations greedily while a tree grows (tree CTRs, feature-parallel only);
         # here they are enumerated up front under a fixed budget so that training stays doc-parallel.
         card = {c: len(np.unique(pool.cat_hashes[c][: min(pool.num_row(), 200000)])) for c in ctr_cats}
+        if ctx is not None and ctx.is_distributed:          # every rank must enumerate the same combinations
+            all_cards = ctx.all_gather_object(card)
+            card = {c: max(d[c] for d in all_cards) for c in ctr_cats}
         ranked = sorted(ctr_cats, key=lambda c: card[c])
         budget = 24
         top = ranked[: 8]
@@ -193,9 +196,34 @@ def _ordered_stats(keys_t: torch.Tensor, order_t: torch.Tensor, cols: torch.Tens
     return out
 
 
+def _all_gather_rows(ctx, t: torch.Tensor, counts) -> torch.Tensor:
+    """Concatenation over the ranks (in rank order) of per-rank vectors of different lengths."""
+    import torch.distributed as dist
+    m = max(counts)
+    buf = torch.zeros(m, dtype=t.dtype, device=t.device)
+    buf[: t.shape[0]] = t
+    outs = [torch.empty_like(buf) for _ in counts]
+    dist.all_gather(outs, buf, group=ctx.group)
+    return torch.cat([o_[:c] for o_, c in zip(outs, counts)])
+
+
 def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, eval_pools, device, ctx, codec) -> CtrState:
+    """Several ranks: the statistics of a category must come from all rows, not from the rows of one rank, so the
+    categorical hashes and the targets are all-gathered (the reference mirrors them on every device for the same
+    reason, catboost/cuda/gpu_data/feature_parallel_dataset_builder.cpp), every rank computes the same tables, borders
+    and learn values from the same global permutation, and keeps the rows of its own shard."""
     dev = torch.device(device)
-    n = train_pool.num_row()
+    n_local = train_pool.num_row()
+    dist_mode = ctx is not None and ctx.is_distributed
+    if dist_mode:
+        counts = [int(c) for c in ctx.all_gather_object(n_local)]
+        lo_row = sum(counts[: ctx.rank])
+        n = sum(counts)
+        gather = lambda t: _all_gather_rows(ctx, t, counts)
+        y_train = gather(torch.from_numpy(np.ascontiguousarray(y_train, dtype=np.float32)).to(dev)).cpu().numpy()
+    else:
+        lo_row, n = 0, n_local
+        gather = lambda t: t
     rng = np.random.RandomState(int(o.random_seed) + 101)
     if o.has_time:
         order = np.arange(n)
@@ -204,6 +232,9 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
         blk = int(o.fold_permutation_block or 1)
         if train_pool.group_id is not None:
             off = train_pool.group_offsets()
+            if dist_mode:
+                sizes = np.concatenate(ctx.all_gather_object(np.diff(off)))
+                off = np.concatenate([[0], np.cumsum(sizes)])
             g = rng.permutation(len(off) - 1)
             order = np.concatenate([np.arange(off[k], off[k + 1]) for k in g]) if len(g) else np.zeros(0, np.int64)
         elif blk > 1:
@@ -219,13 +250,20 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
     ones = torch.ones(n, dtype=torch.float32, device=dev)
 
     flat, train_cols, eval_cols, model_ctrs = [], [], [[] for _ in eval_pools], []
+    cat_cache = {}
+
+    def gathered_cat(c):
+        if c not in cat_cache:
+            cat_cache[c] = gather(_cat_column_t(train_pool, c, dev))
+        return cat_cache[c]
+
     by_proj = {}
     for s in plan.specs:
         by_proj.setdefault(s.cat_features, []).append(s)
     for proj, specs in by_proj.items():
         # hashing, grouping and look-ups stay on the training device (a host sort of 45M 64-bit keys per projection
         # would dominate the whole fit)
-        h_train_t = projection_hash_t([_cat_column_t(train_pool, c, dev) for c in proj])
+        h_train_t = projection_hash_t([gathered_cat(c) for c in proj])
         uniq_t, keys_t = torch.unique(h_train_t, return_inverse=True)
         U = int(uniq_t.numel())
         # model tables want the hashes in unsigned order: the signed-sorted list is that order rotated
@@ -276,7 +314,7 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
             if len(b) == 0:
                 continue
             bt = torch.from_numpy(b).to(dev)
-            train_cols.append(torch.searchsorted(bt, tr_val.contiguous(), right=False).to(torch.uint8))
+            train_cols.append(torch.searchsorted(bt, tr_val.contiguous(), right=False).to(torch.uint8)[lo_row:lo_row + n_local])
             for k, (pos, ok) in enumerate(eval_keys):
                 ev = torch.where(ok, full[pos] if U else torch.zeros_like(ok, dtype=torch.float32),
                                  torch.full((len(ok),), float(unseen), device=dev))
@@ -291,7 +329,7 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
                                              totals_np[0].astype(np.float64), totals_np[0].astype(np.float64),
                                              max_count if s.ctr_type == "Counter" else float(n)))
             flat.append(FlatFeature("ctr", ctr_index, borders=b, n_bins=len(b) + 1, ctr=s))
-    train_bins = torch.stack(train_cols) if train_cols else torch.zeros((0, n), dtype=torch.uint8, device=dev)
+    train_bins = torch.stack(train_cols) if train_cols else torch.zeros((0, n_local), dtype=torch.uint8, device=dev)
     eval_bins = [torch.stack(c) if c else torch.zeros((0, ep.num_row()), dtype=torch.uint8, device=dev)
                  for c, ep in zip(eval_cols, eval_pools)]
     return CtrState(flat, train_bins, eval_bins, model_ctrs, order)

@@ -32,10 +32,24 @@ y = (X @ w + 0.3 * rng.standard_normal(n, dtype=np.float32) > 0).astype(np.float
 lo, hi = n * rank // world, n * (rank + 1) // world
 params = dict(iterations=12, depth=5, learning_rate=0.3, verbose=False, allow_writing_files=False, random_strength=0,
               bootstrap_type="No", task_type="GPU" if backend == "nccl" else "CPU", border_count=32)
-if mode != "default":
+fit_kw = {{}}
+if mode == "cat":
+    # two categorical columns with many values: their target statistics must come from the rows of all ranks
+    c1 = rng.integers(0, 300, n)
+    c2 = rng.integers(0, 40, n)
+    eff = rng.standard_normal(300)[c1] + 0.5 * rng.standard_normal(40)[c2]
+    y = (0.3 * (X @ w) + eff + 0.3 * rng.standard_normal(n) > 0).astype(np.float32)
+    Xo = np.empty((n, F + 2), dtype=object)
+    Xo[:, :F] = X
+    Xo[:, F] = c1
+    Xo[:, F + 1] = c2
+    X = Xo
+    fit_kw["cat_features"] = [F, F + 1]
+    params.update(one_hot_max_size=2, max_ctr_complexity=1)
+elif mode != "default":
     params["histogram_reduce"] = mode
 m = cb.CatBoostClassifier(**params)
-m.fit(X[lo:hi], y[lo:hi])
+m.fit(X[lo:hi], y[lo:hi], **fit_kw)
 pred = m.predict(X[:2000], prediction_type="RawFormulaVal")
 if rank == 0:
     with open(out_path, "wb") as fh:
@@ -118,6 +132,13 @@ except BaseException as e:
     print("RESULT error-after %.1f s: %s" % (time.time() - t0, type(e).__name__), flush=True)
 os._exit(0)
 '''
+
+
+def test_gloo_two_ranks_with_categorical_features():
+    """CTR statistics are computed from the rows of all ranks: the two-rank model must be as good as a model trained on
+    one rank with all rows (shard-local statistics would lose most of the signal of a 300-value feature)."""
+    res = _run(2, "gloo", mode="cat", port=29619)
+    assert res["acc"] > 0.85, res["acc"]
 
 
 def test_lost_rank_is_detected_by_the_survivor():
