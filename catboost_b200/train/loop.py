@@ -408,8 +408,9 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
     # is what iteration j accumulates at its start, so it is read from the device history one iteration behind the
     # launches, on a side stream that only waits for the iteration before the one in flight -- the GPU never idles for
     # the host, and no extra pass over the data is needed.  The last value comes from an explicit pass.
+    # (one rank only: with several ranks the value needs a collective, which stays on the main stream)
     lagged = bool(cheap and want_log and period == 1 and not evs and od is None and not callbacks and dev.type == "cuda"
-                  and os.environ.get("CB200_LAGGED_LOG", "1") != "0")
+                  and eng.R == 1 and os.environ.get("CB200_LAGGED_LOG", "1") != "0")
     if lagged:
         with prof.span("iterations"):
             side = torch.cuda.Stream(dev)
