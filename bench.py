@@ -170,7 +170,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                          "-lms", "50", "-i", str(self.idx)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -184,6 +184,15 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        if not self.lines:
+            # a timed region shorter than the sampling period: take one reading right away (clocks take longer than
+            # that to fall back after the last kernel)
+            try:
+                one = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i",
+                                      str(self.idx)], capture_output=True, text=True, timeout=10)
+                self.lines += [ln.strip() for ln in one.stdout.splitlines() if ln.strip()]
+            except (OSError, subprocess.SubprocessError):
+                pass
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
