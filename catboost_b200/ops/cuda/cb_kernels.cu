@@ -138,7 +138,7 @@ __device__ __forceinline__ void cb_grad_load(const CbGradArgs& a, long long i0, 
 // LOSS >= 0 fixes the objective at compile time (the common ones get their own instantiation, which removes the
 // dispatch and the unused inputs from the loop); LOSS = -1 reads it from the arguments.
 template <int LOSS>
-__global__ void __launch_bounds__(256, 3) cb_grad_kernel(CbGradArgs a) {
+__global__ void __launch_bounds__(256, 4) cb_grad_kernel(CbGradArgs a) {
     const int loss = LOSS >= 0 ? LOSS : a.loss;
     const int it = *a.iter_ptr;
     double s_loss = 0.0, s_w = 0.0, s_d2 = 0.0, s_n = 0.0;
