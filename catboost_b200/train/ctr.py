@@ -250,6 +250,10 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
     ones = torch.ones(n, dtype=torch.float32, device=dev)
 
     flat, train_cols, eval_cols, model_ctrs = [], [], [[] for _ in eval_pools], []
+    sample_idx = None          # rows the CTR borders are chosen from (one draw for all CTR features)
+    if n > 200000:
+        sample_idx = torch.from_numpy(np.random.default_rng(int(o.random_seed) + 7).choice(
+            n, 200000, replace=False, shuffle=False)).to(dev)
     cat_cache = {}
 
     def gathered_cat(c):
@@ -306,11 +310,19 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
                 full = (totals[0] + s.prior_num) / denom
                 tr_val = full[keys_t]
                 unseen = s.prior_num / denom
-            sample = tr_val if n <= 200000 else tr_val[torch.from_numpy(
-                np.random.default_rng(int(o.random_seed) + 7).choice(n, 200000, replace=False, shuffle=False)).to(dev)]
-            borders, _ = select_borders(sample.cpu().numpy().reshape(-1, 1), s.border_count, "Uniform"
-                                        if s.ctr_type in TARGET_CTRS else "GreedyLogSum")
-            b = borders[0]
+            sample = tr_val if sample_idx is None else tr_val[sample_idx]
+            if s.ctr_type in TARGET_CTRS:
+                # Uniform grid between the smallest and largest sampled value, computed where the values are (same
+                # arithmetic as the host routine: float32, lo + (hi - lo) * k / (count + 1))
+                lo_v, hi_v = np.float32(sample.min().item()), np.float32(sample.max().item())
+                if hi_v > lo_v:
+                    kk = np.arange(1, s.border_count + 1, dtype=np.float32)
+                    b = np.unique((lo_v + (hi_v - lo_v) * kk / np.float32(s.border_count + 1)).astype(np.float32))
+                else:
+                    b = np.zeros(0, dtype=np.float32)
+            else:
+                borders, _ = select_borders(sample.cpu().numpy().reshape(-1, 1), s.border_count, "GreedyLogSum")
+                b = borders[0]
             if len(b) == 0:
                 continue
             bt = torch.from_numpy(b).to(dev)
