@@ -32,7 +32,18 @@ def hash_cat_values(col):
     col = np.asarray(col)
     lib = native.cpu_lib()
     if col.dtype.kind in "iu":
-        uniq, inv = np.unique(col.astype(np.int64), return_inverse=True)
+        c64 = col.astype(np.int64).reshape(-1)
+        mn, mx = (int(c64.min()), int(c64.max())) if c64.size else (0, 0)
+        if c64.size and mx - mn <= max(50_000_000, 4 * c64.size):
+            # dense integer codes: distinct values and their positions by counting instead of sorting
+            off = c64 - mn
+            present = np.zeros(mx - mn + 1, dtype=bool)
+            present[off] = True
+            uniq = np.flatnonzero(present).astype(np.int64) + mn
+            rank_of = np.cumsum(present, dtype=np.int64) - 1
+            inv = rank_of[off]
+        else:
+            uniq, inv = np.unique(c64, return_inverse=True)
         out = np.empty(len(uniq), dtype=np.uint32)
         lib.cbc_cat_hash_ints(uniq.ctypes.data_as(ctypes.c_void_p), ctypes.c_longlong(len(uniq)),
                               out.ctypes.data_as(ctypes.c_void_p))
