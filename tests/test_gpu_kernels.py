@@ -303,6 +303,23 @@ def test_logged_learn_curve_matches_model():
         assert np.allclose(logged, ref, rtol=1e-4, atol=1e-5), (T, logged, ref)
 
 
+def test_generic_gpu_path_metrics_match_host():
+    """MultiClass trains through the general learner on the GPU; its per-iteration metrics are evaluated on the device
+    and must agree with the host metric code."""
+    import catboost_b200 as cb
+    rng = np.random.default_rng(4)
+    X = rng.standard_normal((20000, 8), dtype=np.float32)
+    y = np.argmax(X[:, :3] + 0.3 * rng.standard_normal((20000, 3)), 1)
+    m = cb.CatBoostClassifier(loss_function="MultiClass", iterations=8, depth=4, learning_rate=0.3, task_type="GPU",
+                              devices="0", verbose=False, allow_writing_files=False, custom_metric=["Accuracy"])
+    m.fit(X, y)
+    ev = m.get_evals_result()["learn"]
+    ref = m.eval_metrics(cb.Pool(X, y), ["MultiClass", "Accuracy"])
+    assert np.allclose(ev["MultiClass"], ref["MultiClass"], rtol=1e-4, atol=1e-5)
+    assert np.allclose(ev["Accuracy"], ref["Accuracy"], atol=1e-6)
+    assert ev["Accuracy"][-1] > 0.8
+
+
 def test_device_wait_times_out_without_hanging():
     """A wait on a tag nobody writes returns with the status word set (bounded spin, no trap)."""
     from catboost_b200.ops import native
