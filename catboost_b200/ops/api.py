@@ -69,8 +69,10 @@ def hist(store: BinnedStore, leaf: torch.Tensor, stats: torch.Tensor, slot_table
         return out
     occ = max(1, min(4, (max_smem) // max(1, spp * per_slot + 1024)))
     grid = sm * occ
-    native.cuda_check(lib.cb_hist(ctypes.c_void_p(store.handle), _p(leaf), _p(stats), S, 0, None, _p(slot_table),
-                                  nslots, spp, B, _p(out), grid, 512, _stream(dev)), "cb_hist")
+    # integer cells: every statistic is scaled by its largest magnitude (shared fp32 atomics are compare-and-swap loops)
+    statmax = stats[:, : store.n].abs().amax(dim=1).clamp_min(1e-30).contiguous()
+    native.cuda_check(lib.cb_hist_n(ctypes.c_void_p(store.handle), _p(leaf), _p(stats), S, 0, None, _p(slot_table),
+                                    nslots, spp, B, _p(out), _p(statmax), grid, 512, _stream(dev)), "cb_hist_n")
     return out
 
 

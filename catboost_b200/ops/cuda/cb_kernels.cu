@@ -308,13 +308,32 @@ static int g_hist_smem_set = 0;
 
 CB_API int cb_hist_smem_bytes(int slots_per_pass, int S, int B) { return slots_per_pass * S * 4 * B * 4; }
 
+static int cb_hist_launch(const CbData* d, const unsigned short* leaf, const float* stats, int S, int level,
+                          const unsigned int* small_mask, const short* slot_table, int nslots_table, int slots_per_pass,
+                          int B, float* out, const float* statmax, int grid, int threads, cudaStream_t st);
+
 CB_API int cb_hist(const CbData* d, const unsigned short* leaf, const float* stats, int S, int level,
                    const unsigned int* small_mask, const short* slot_table, int nslots_table, int slots_per_pass, int B,
                    float* out, int grid, int threads, cudaStream_t st) {
+    return cb_hist_launch(d, leaf, stats, S, level, small_mask, slot_table, nslots_table, slots_per_pass, B, out, nullptr,
+                          grid, threads, st);
+}
+
+// Same histogram with integer cells: statmax[s] = max |stats[s][i]| (device array of S floats).
+CB_API int cb_hist_n(const CbData* d, const unsigned short* leaf, const float* stats, int S, int level,
+                     const unsigned int* small_mask, const short* slot_table, int nslots_table, int slots_per_pass, int B,
+                     float* out, const float* statmax, int grid, int threads, cudaStream_t st) {
+    return cb_hist_launch(d, leaf, stats, S, level, small_mask, slot_table, nslots_table, slots_per_pass, B, out, statmax,
+                          grid, threads, st);
+}
+
+static int cb_hist_launch(const CbData* d, const unsigned short* leaf, const float* stats, int S, int level,
+                          const unsigned int* small_mask, const short* slot_table, int nslots_table, int slots_per_pass,
+                          int B, float* out, const float* statmax, int grid, int threads, cudaStream_t st) {
     CbHistArgs a;
     a.d = *d; a.leaf = leaf; a.stats = stats; a.S = S; a.level = level; a.small_mask = small_mask;
     a.slots_per_pass = slots_per_pass; a.B = B; a.out = out; a.slot_table = slot_table; a.nslots_table = nslots_table;
-    a.priv = nullptr; a.statmax = nullptr; a.nK = 0; a.copies = 1; a.work = nullptr; a.narrow = 0; a.bundle = 0;
+    a.priv = nullptr; a.statmax = statmax; a.nK = 0; a.copies = 1; a.work = nullptr; a.narrow = 0; a.bundle = 0;
     const int smem = cb_hist_smem_bytes(slots_per_pass, S, B);
     if (!g_hist_smem_set) {
         int dev = 0, optin = 0;

@@ -177,6 +177,81 @@ static __device__ void cb_hist_item(const CbHistArgs& a, float* sh, int g, long 
     __syncthreads();
 }
 
+// Single-int32-cell variant of cb_hist_item for any number of statistics, used by the stand-alone histogram launcher
+// (general learner: multi-class, depthwise, lossguide, ranking).  Statistic s is scaled by qmax / statmax[s] with
+// qmax = (2^31 - 1) / documents of this chunk (capped at 2^23 - 1), rounded to nearest and added with a native integer
+// atomic (fp32 shared atomics are compare-and-swap loops); the flush converts back and adds into `out` with global
+// float atomics.  sh layout: int [slot][s][j][B].
+static __device__ void cb_hist_item_n(const CbHistArgs& a, int* sh, int g, long long d_begin, long long d_end,
+                                      int slot_begin, int slot_count) {
+    const int B = a.B;
+    const int S = a.S;
+    const int total = slot_count * S * 4 * B;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) sh[i] = 0;
+    __syncthreads();
+    const uint32_t* bg = a.d.bins + (long long)g * a.d.npad;
+    const int level = a.level;
+    const int nslots = cb_hist_nslots(a);
+    const unsigned int pmask = (unsigned int)(nslots - 1);
+    const int slot_stride = S * 4 * B;
+    const float qmax = fminf(8388607.0f, floorf(2147483647.0f / (float)max(1ll, d_end - d_begin)) - 1.0f);
+    for (long long i = d_begin + (long long)threadIdx.x * 4; i < d_end; i += (long long)blockDim.x * 4) {
+        const uint4 w = *reinterpret_cast<const uint4*>(bg + i);
+        const ushort4 lf = *reinterpret_cast<const ushort4*>(a.leaf + i);
+        const unsigned int wv[4] = {w.x, w.y, w.z, w.w};
+        const unsigned int lv[4] = {lf.x, lf.y, lf.z, lf.w};
+        int off[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            int slot = 0;
+            bool take = (i + k) < a.d.n;
+            if (a.slot_table) {
+                slot = a.slot_table[lv[k]];
+                take = take && (slot >= 0);
+            } else if (level > 0) {
+                const unsigned int p = lv[k] & pmask;
+                const unsigned int right = (lv[k] >> (level - 1)) & 1u;
+                const unsigned int want = (a.small_mask[p >> 5] >> (p & 31)) & 1u;
+                take = take && (right == want);
+                slot = (int)p;
+            }
+            slot -= slot_begin;
+            off[k] = (take && (unsigned)slot < (unsigned)slot_count) ? slot * slot_stride : -1;
+        }
+        for (int s = 0; s < S; ++s) {
+            const float sc = qmax / fmaxf(a.statmax[s], 1e-30f);
+            const float4 t = *reinterpret_cast<const float4*>(a.stats + (long long)s * a.d.npad + i);
+            const float tv[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (off[k] >= 0) {
+                    int* base = sh + off[k] + s * 4 * B;
+                    const int q = __float2int_rn(tv[k] * sc);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) atomicAdd(base + j * B + ((wv[k] >> (8 * j)) & 255u), q);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int v = sh[i];
+        if (v != 0) {
+            const int bin = i % B;
+            const int r = i / B;
+            const int j = r & 3;
+            const int s = (r >> 2) % S;
+            const int slot = (r >> 2) / S;
+            const int f = g * 4 + j;
+            if (f < a.d.F && bin < a.d.feat_nb[f]) {
+                atomicAdd(a.out + ((size_t)(slot_begin + slot) * S + s) * a.d.TB + a.d.feat_off[f] + bin,
+                          (float)v * (fmaxf(a.statmax[s], 1e-30f) / qmax));
+            }
+        }
+    }
+    __syncthreads();
+}
+
 // Fixed-point variant of cb_hist_item (see CbHistArgs::statmax).  sh layout: int [slot][s][part][j][B], part 0 = high.
 static __device__ void cb_hist_item_q(const CbHistArgs& a, int* sh, int g, long long item, long long d_begin,
                                       long long d_end, int slot_begin, int slot_count) {
@@ -650,7 +725,7 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
     per = (per + 3) & ~3ll;
     const int nslots = cb_hist_nslots(a);
     const bool one_pass = a.slots_per_pass >= nslots;
-    const bool quant2 = a.statmax && a.S == 2;
+    const bool quant2 = a.statmax && a.priv && a.S == 2;      // without private tiles: the stand-alone integer path
     const int gpc = (quant2 && a.narrow && a.bundle > 0) ? a.bundle : 0;      // groups per block, 0 = per-group paths
     const int nb = gpc ? (G + gpc - 1) / gpc : G;
     const long long items = (long long)nb * nK;
@@ -682,6 +757,7 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
             const long long it2 = k * G + g;
             if (quant2 && a.narrow) cb_hist_item_q2<true>(a, reinterpret_cast<int*>(sh), g, it2, (int)k, nK, sb, sc);
             else if (quant2) cb_hist_item_q2<false>(a, reinterpret_cast<int*>(sh), g, it2, (int)k, nK, sb, sc);
+            else if (a.statmax && !a.priv) { if (b < e) cb_hist_item_n(a, reinterpret_cast<int*>(sh), g, min(b, e), e, sb, sc); }
             else if (a.statmax) cb_hist_item_q(a, reinterpret_cast<int*>(sh), g, it2, min(b, e), e, sb, sc);
             else if (b < e || a.priv) cb_hist_item(a, sh, g, it2, min(b, e), e, sb, sc);
         }

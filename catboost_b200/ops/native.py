@@ -127,6 +127,8 @@ _SIGS = {
     "cb_hist_smem_bytes": (c_int, [c_int, c_int, c_int]),
     "cb_hist": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                         c_int, c_int, c_void_p]),
+    "cb_hist_n": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                          c_void_p, c_int, c_int, c_void_p]),
     "cb_score": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_void_p, c_float, c_int, c_float, c_void_p, c_void_p, c_ull, c_float, c_void_p, c_void_p]),
     "cb_select_local_launch": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
