@@ -255,10 +255,23 @@ class GenericLearner:
         splits[:, 0] = -1
         cstat = K + 1 if self.use_count else None
         fw = self.store.feat_weight
+        h_prev, small_right = None, None
         for level in range(depth):
             L = 1 << level
-            table = torch.arange(L, dtype=torch.int16, device=self.dev)
-            h = self._hist(stats, table, L)
+            if h_prev is None:
+                table = torch.arange(L, dtype=torch.int16, device=self.dev)
+                h = self._hist(stats, table, L)
+            else:
+                # sibling subtraction: only the lighter child of every parent is accumulated, the other one is the
+                # parent's histogram minus it (catboost/cuda/methods/pointwise_kernels.cpp:70-92)
+                half = L >> 1
+                ar = torch.arange(L, device=self.dev)
+                parent, bit = ar & (half - 1), ar >> (level - 1)
+                is_small = bit == small_right[parent].long()
+                table = torch.where(is_small, parent, torch.full_like(parent, -1)).to(torch.int16)
+                h_small = self._hist(stats, table, half)
+                h_big = h_prev - h_small
+                h = torch.where(is_small.view(L, 1, 1), h_small[parent], h_big[parent])
             num, den, cnt, sides_ = sc.candidate_terms(h, K, cstat)
             score = sc.finish(num.sum(0), None if den is None else den.sum(0))          # [F, B]
             if noise_std > 0:
@@ -279,6 +292,9 @@ class GenericLearner:
             onehot = bool(self.store.feat_onehot[f].item())
             splits[level] = (f, b, 0, 1 if onehot else 0)
             ops.update_leaf(self.store, self.leaf, f, b, onehot, level)
+            # which child of every leaf is the lighter one (by the weight column) decides what the next level accumulates
+            small_right = sides_[1][:, K, f, b] < sides_[0][:, K, f, b]
+            h_prev = h
         return TreeResult("oblivious", splits=splits, n_leaves=1 << depth, leaf=self.leaf)
 
     def _per_leaf_best(self, h, K, noise_std, fmask):
