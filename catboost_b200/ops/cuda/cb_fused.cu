@@ -14,7 +14,7 @@
 // (catboost/cuda/methods/histograms_helper.cpp:58-91, cuda_lib/cuda_buffer_helpers/reduce_scatter.h:449-540,
 // catboost/cuda/methods/histograms_helper.h:322-331).
 //
-// Only plain peer stores/loads are used for remote memory: no TMA, no multicast.
+// Only plain peer stores / loads touch remote memory: no bulk-copy engine, no switch-side reduction.
 #include "cb_common.cuh"
 #include "cb_tree.cuh"
 #include "cb_comm.cuh"
