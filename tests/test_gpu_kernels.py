@@ -320,6 +320,30 @@ def test_generic_gpu_path_metrics_match_host():
     assert ev["Accuracy"][-1] > 0.8
 
 
+def test_gpu_categorical_features_with_ctrs():
+    """Categorical columns: hashing, grouping and ordered target statistics on the device, trees by the fused engine; the
+    CPU evaluator applies the stored CTR tables to the same rows."""
+    import catboost_b200 as cb
+    import pandas as pd
+    rng = np.random.default_rng(6)
+    n = 60000
+    c1, c2 = rng.integers(0, 500, n), rng.integers(0, 30, n)
+    num = rng.standard_normal((n, 3)).astype(np.float32)
+    eff = rng.standard_normal(500)[c1] + 0.5 * rng.standard_normal(30)[c2]
+    y = (0.5 * num[:, 0] + eff + 0.3 * rng.standard_normal(n) > 0).astype(int)
+    df = pd.DataFrame({"a": num[:, 0], "b": num[:, 1], "c": num[:, 2], "k1": c1, "k2": c2})
+    tr, te = slice(0, 50000), slice(50000, n)
+    m = cb.CatBoostClassifier(iterations=60, depth=6, learning_rate=0.2, task_type="GPU", devices="0", verbose=False,
+                              allow_writing_files=False, one_hot_max_size=2, max_ctr_complexity=1)
+    m.fit(df.iloc[tr], y[tr], cat_features=["k1", "k2"])
+    assert m._train_info.get("launches_per_iter", 0) > 0            # the fused engine trained it
+    acc = float((m.predict(df.iloc[te]) == y[te]).mean())
+    assert acc > 0.85, acc
+    base = cb.CatBoostClassifier(iterations=60, depth=6, learning_rate=0.2, task_type="GPU", devices="0", verbose=False,
+                                 allow_writing_files=False).fit(num[tr], y[tr])
+    assert acc > float((base.predict(num[te]) == y[te]).mean()) + 0.1      # the categorical signal is used
+
+
 def test_device_wait_times_out_without_hanging():
     """A wait on a tag nobody writes returns with the status word set (bounded spin, no trap)."""
     from catboost_b200.ops import native
