@@ -326,6 +326,41 @@ class CatBoost:
         return self
 
     # ------------------------------------------------------------------ analysis
+    def plot_partial_dependence(self, data, features, plot=False, plot_file=None, thread_count=-1):
+        """Partial dependence of the raw prediction on one or two numerical features
+        (catboost/python-package/catboost/core.py ``plot_partial_dependence``): every document's value of the feature is
+        replaced by each border-bucket representative in turn and the predictions are averaged.  Returns
+        ``(values, None)``: ``values`` has one axis per feature (bucket order); no figure is drawn."""
+        self._check_fitted()
+        pool = data if isinstance(data, Pool) else Pool(data, **self._pool_kwargs())
+        feats = [features] if isinstance(features, (int, str, np.integer)) else list(features)
+        if not 1 <= len(feats) <= 2:
+            raise CatBoostError("partial dependence is computed for one or two features")
+        m = self._model
+        cols, grids = [], []
+        for f in feats:
+            c = pool.feature_names.index(f) if isinstance(f, str) else int(f)
+            ff = next((x for x in m.float_features if x.flat_index == c), None)
+            if ff is None:
+                raise CatBoostError("partial dependence needs numerical features that the model knows")
+            b = np.asarray(ff.borders, dtype=np.float64)
+            if len(b) == 0:
+                grid = np.array([0.0])
+            else:
+                # one representative per bucket: below the first border, between neighbours, above the last one
+                grid = np.concatenate([[b[0] - 1.0], (b[:-1] + b[1:]) / 2.0, [b[-1] + 1.0]])
+            cols.append(pool.float_feature_indices.index(c))
+            grids.append(grid)
+        fd, ch = m.pool_arrays(pool)
+        base = np.array(fd, dtype=np.float32, copy=True)
+        out = np.zeros([len(g) for g in grids])
+        for idx in np.ndindex(*out.shape):
+            work = base.copy()
+            for k, j in enumerate(idx):
+                work[:, cols[k]] = grids[k][j]
+            out[idx] = float(np.mean(m.predict_raw(work, ch)[:, 0]))
+        return out, None
+
     def get_feature_importance(self, data=None, type=EFstrType.FeatureImportance, prettified=False, thread_count=-1,
                                verbose=False, fstr_type=None, shap_mode="Auto", model_output="Raw",
                                interaction_indices=None, shap_calc_type="Regular", reference_data=None, log_cout=None,

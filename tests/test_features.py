@@ -488,3 +488,17 @@ def test_onnx_and_pmml_export(tmp_path):
             top = tm.find("p:Node", ns)
             pred2[r] += float(top.get("score")) if top.get("score") is not None else walk(top, X[r])
     assert np.allclose(pred2, ref, atol=1e-4)
+
+
+def test_partial_dependence():
+    rng = np.random.default_rng(0)
+    X = rng.uniform(-2, 2, (2000, 3)).astype(np.float32)
+    y = (3 * X[:, 0] + np.sin(X[:, 1]) + 0.05 * rng.standard_normal(2000)).astype(np.float32)
+    m = cb.CatBoostRegressor(iterations=40, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False,
+                             border_count=16).fit(X, y)
+    pd0, fig = m.plot_partial_dependence(X[:300], 0)
+    assert fig is None and pd0.ndim == 1 and len(pd0) == len(m._model.float_features[0].borders) + 1
+    assert np.all(np.diff(pd0) > -0.05) and pd0[-1] - pd0[0] > 6          # increasing like 3 * x0 over [-2, 2]
+    pd2, _ = m.plot_partial_dependence(X[:100], [0, 2])
+    assert pd2.shape == (len(m._model.float_features[0].borders) + 1, len(m._model.float_features[2].borders) + 1)
+    assert np.abs(pd2[:, 0] - pd2[:, -1]).max() < 0.5                      # x2 carries no signal
