@@ -24,9 +24,11 @@ _HERE = Path(__file__).resolve().parent
 CUDA_SRC = [_HERE / "cuda" / "cb_kernels.cu", _HERE / "cuda" / "cb_fused.cu", _HERE / "cuda" / "cb_leaf.cu",
             _HERE / "cuda" / "cb_quantize_tma.cu", _HERE / "cuda" / "cb_ranking.cu"]
 CUDA_HDR = sorted((_HERE / "cuda").glob("*.cuh")) + sorted((_HERE / "cuda").glob("*.h"))
-CPU_SRC = [_HERE / "cpu" / "cb_cpu.cpp"]
+CPU_SRC = [_HERE / "cpu" / "cb_cpu.cpp", _HERE / "cpu" / "cb_cityhash.h"]
+MODEL_SRC = [_HERE / "cpu" / "cb_model_capi.cpp", _HERE / "cpu" / "cb_model_capi.h", _HERE / "cpu" / "cb_cityhash.h"]
 CUDA_LIB = _HERE / "libcb200_cuda.so"
 CPU_LIB = _HERE / "libcb200_cpu.so"
+MODEL_LIB = _HERE / "libcb200model.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -77,7 +79,7 @@ def build_cpu(force: bool = False) -> Path:
     cxx = shutil.which("g++") or shutil.which("c++")
     if cxx is None:
         raise RuntimeError("g++ not found: cannot build the CPU backend")
-    cmd = [cxx, "-O3", "-march=x86-64-v3", "-std=c++17", "-fopenmp", "-fPIC", "-shared", *map(str, CPU_SRC),
+    cmd = [cxx, "-O3", "-march=x86-64-v3", "-std=c++17", "-fopenmp", "-fPIC", "-shared", str(CPU_SRC[0]),
            "-o", str(CPU_LIB)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
@@ -85,8 +87,24 @@ def build_cpu(force: bool = False) -> Path:
     return CPU_LIB
 
 
+def build_model_lib(force: bool = False) -> Path:
+    """The stand-alone evaluator with the C interface of ``cpu/cb_model_capi.h`` (no Python, torch or CUDA inside)."""
+    if not force and not _newer(MODEL_SRC, MODEL_LIB):
+        return MODEL_LIB
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        raise RuntimeError("g++ not found: cannot build the model evaluator")
+    cmd = [cxx, "-O3", "-march=x86-64-v3", "-std=c++17", "-fopenmp", "-fPIC", "-shared", "-fvisibility=hidden",
+           str(MODEL_SRC[0]), "-o", str(MODEL_LIB)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    return MODEL_LIB
+
+
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_cpu(force)
+    build_model_lib(force)
     build_cuda(force, verbose)
 
 
