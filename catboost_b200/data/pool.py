@@ -276,22 +276,31 @@ class Pool:
         elif not cat_idx and data.dtype != object:
             self.float_data = np.ascontiguousarray(data, dtype=np.float32)
         else:
-            fd = np.empty((n, len(float_idx)), dtype=np.float32)
-            for j, c in enumerate(float_idx):
+            fcols = []
+            for c in float_idx:
                 col = data[:, c]
                 try:
-                    fd[:, j] = col.astype(np.float32)
+                    fcols.append(np.ascontiguousarray(col, dtype=np.float32))
                 except (ValueError, TypeError):
-                    fd[:, j] = [np.nan if (v is None or v == "") else float(v) for v in col]
+                    fcols.append(np.array([np.nan if (v is None or v == "") else float(v) for v in col], dtype=np.float32))
+            fd = np.empty((n, len(float_idx)), dtype=np.float32)
+            if fcols and n:
+                import ctypes
+                from ..ops import native
+                ptrs = (ctypes.c_void_p * len(fcols))(*[f.ctypes.data for f in fcols])
+                native.cpu_lib().cbc_interleave_f32(ptrs, ctypes.c_int(len(fcols)), ctypes.c_longlong(n),
+                                                    fd.ctypes.data_as(ctypes.c_void_p))
             self.float_data = fd
         # categorical columns: hashed + string dictionary
         self.cat_hashes = np.empty((len(cat_idx), n), dtype=np.uint32)
         self.cat_strings = []
+        self._cat_distinct = {}
         for j, c in enumerate(cat_idx):
             col = data[:, c]
-            h, strs = hash_cat_values(col)
+            h, strs, distinct = hash_cat_values(col)
             self.cat_hashes[j] = h
             self.cat_strings.append(strs)
+            self._cat_distinct[j] = distinct
         self.label = self._prep_label(label, n)
         self.weight = self._prep_vec(weight, n, "weight")
         self.group_weight = self._prep_vec(group_weight, n, "group_weight")
@@ -438,6 +447,14 @@ class Pool:
     def set_pairs_weight(self, pairs_weight):
         self.pairs_weight = np.asarray(pairs_weight, dtype=np.float32)
 
+    def cat_distinct_values(self, j: int) -> np.ndarray:
+        """Sorted distinct hashes of categorical feature ``j`` (position in ``cat_feature_indices``); known from the
+        hashing pass for a pool built from raw columns, computed on demand otherwise."""
+        cache = self.__dict__.setdefault("_cat_distinct", {})
+        if j not in cache:
+            cache[j] = np.unique(self.cat_hashes[j])
+        return cache[j]
+
     def group_offsets(self):
         """Start offsets of the query groups (length n_groups + 1); one group per row when ungrouped."""
         n = self.num_row()
@@ -469,6 +486,8 @@ class Pool:
         out.__dict__.update(self.__dict__)
         out.float_data = np.ascontiguousarray(self.float_data[idx])
         out.cat_hashes = np.ascontiguousarray(self.cat_hashes[:, idx])
+        out._cat_distinct = {}
+        out.__dict__.pop("_cat_hash_tensors", None)
         out.text_data = [t[idx] for t in getattr(self, "text_data", [])]
         out.embedding_data = [e[idx] for e in getattr(self, "embedding_data", [])]
         for k in ("label", "weight", "group_weight", "baseline", "timestamp", "group_id", "subgroup_id"):

@@ -393,3 +393,37 @@ CBC_API void cbc_cat_hash_ints(const long long* vals, long long count, uint32_t*
         out[k] = uint32_t(city1::hash(tmp, size_t(len)) & 0xffffffffULL);
     }
 }
+
+// One categorical column of integers with a small value range [mn, mn + range): the hash of every row through a direct
+// table, filled on first use.  `table` [range] and `seen` [range] (zero-initialised by the caller) come back holding the
+// hash of every value that occurs.  Two threads may fill the same entry: they write the same number.
+CBC_API void cbc_cat_hash_dense_ints(const long long* vals, long long n, long long mn, long long range, uint32_t* out,
+                                     uint32_t* table, unsigned char* seen) {
+    (void)range;
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; ++i) {
+        const long long off = vals[i] - mn;
+        if (!__atomic_load_n(&seen[off], __ATOMIC_ACQUIRE)) {
+            char tmp[24];
+            const int len = std::snprintf(tmp, sizeof(tmp), "%lld", vals[i]);
+            table[off] = uint32_t(city1::hash(tmp, size_t(len)) & 0xffffffffULL);
+            __atomic_store_n(&seen[off], (unsigned char)1, __ATOMIC_RELEASE);
+        }
+        out[i] = table[off];
+    }
+}
+
+// Row-major matrix [n][F] from F separate float32 columns (blocks of rows per thread, so that reads stream and the
+// writes of a block stay in cache).
+CBC_API void cbc_interleave_f32(const float* const* cols, int F, long long n, float* out) {
+    const long long BLK = 2048;
+#pragma omp parallel for schedule(static)
+    for (long long b0 = 0; b0 < n; b0 += BLK) {
+        const long long b1 = std::min(n, b0 + BLK);
+        for (int j = 0; j < F; ++j) {
+            const float* c = cols[j];
+            float* o = out + b0 * F + j;
+            for (long long r = b0; r < b1; ++r, o += F) *o = c[r];
+        }
+    }
+}

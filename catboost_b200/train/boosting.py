@@ -193,7 +193,7 @@ def plan_features(o: Options, pool: Pool, ctx: DistContext, quant: Optional[Feat
     for j, c in enumerate(pool.cat_feature_indices):
         if c in ignored:
             continue
-        uniq = np.unique(pool.cat_hashes[j])
+        uniq = pool.cat_distinct_values(j)
         if ctx.is_distributed:
             uniq = np.unique(np.concatenate(ctx.all_gather_object(uniq)))
         if len(uniq) <= 1:

@@ -114,7 +114,7 @@ def plan_ctrs(o, pool: Pool, ctr_cats: List[int], ctx) -> CtrPlan:
         # Static combinations: pairs (and triples when asked) among the categorical features of lowest cardinality.
         # The reference discovers combinations greedily while a tree grows (tree CTRs, feature-parallel only);
         # here they are enumerated up front under a fixed budget so that training stays doc-parallel.
-        card = {c: len(np.unique(pool.cat_hashes[c][: min(pool.num_row(), 200000)])) for c in ctr_cats}
+        card = {c: len(pool.cat_distinct_values(c)) for c in ctr_cats}
         if ctx is not None and ctx.is_distributed:          # every rank must enumerate the same combinations
             all_cards = ctx.all_gather_object(card)
             card = {c: max(d[c] for d in all_cards) for c in ctr_cats}
@@ -161,8 +161,8 @@ def _cat_column_t(pool: Pool, c: int, device) -> torch.Tensor:
     cache = pool.__dict__.setdefault("_cat_hash_tensors", {})
     key = (c, str(device))
     if key not in cache:
-        col = np.asarray(pool.cat_hashes[c], dtype=np.uint32).view(np.int32).astype(np.int64)
-        cache[key] = torch.from_numpy(col).to(device)
+        col = np.ascontiguousarray(pool.cat_hashes[c], dtype=np.uint32).view(np.int32)
+        cache[key] = torch.from_numpy(col).to(device).long()            # widened (sign-extended) on the device
     return cache[key]
 
 
@@ -174,26 +174,39 @@ def projection_hash_t(cols) -> torch.Tensor:
     return res
 
 
-def _ordered_stats(keys_t: torch.Tensor, order_t: torch.Tensor, cols: torch.Tensor):
-    """Exclusive prefix sums of ``cols`` [C, n] inside each key, in the order given by ``order_t`` (row ids in
-    permutation order).  Returns [C, n] aligned with the original rows."""
-    n = keys_t.shape[0]
-    k_in_order = keys_t[order_t]
-    srt = torch.argsort(k_in_order, stable=True)          # groups contiguous, permutation order inside a group
+def _group_rows(h: torch.Tensor, order_t: torch.Tensor):
+    """One stable sort of the projection hashes taken in permutation order: rows of equal hash become contiguous and
+    keep the permutation order inside their group.  Returns (rows, seg_id, first_idx, uniq): the row id at every sorted
+    position, the dense group number of every sorted position, the first sorted position of every group, and the
+    distinct hashes in (signed) increasing order."""
+    n = h.shape[0]
+    sorted_h, srt = torch.sort(h[order_t], stable=True)
     rows = order_t[srt]
-    ks = k_in_order[srt]
-    vals = cols[:, rows]
-    cs = torch.cumsum(vals, dim=1)
-    start = torch.ones(n, dtype=torch.bool, device=keys_t.device)
+    start = torch.ones(n, dtype=torch.bool, device=h.device)
     if n > 1:
-        start[1:] = ks[1:] != ks[:-1]
-    seg_id = torch.cumsum(start.long(), 0) - 1
+        start[1:] = sorted_h[1:] != sorted_h[:-1]
+    seg_id = torch.cumsum(start, 0, dtype=torch.int64) - 1
     first_idx = torch.nonzero(start).squeeze(1)
-    base = cs[:, first_idx] - vals[:, first_idx]           # cumsum before each segment
-    excl = cs - vals - base[:, seg_id]
-    out = torch.empty_like(excl)
-    out[:, rows] = excl
-    return out
+    return rows, seg_id, first_idx, sorted_h[first_idx]
+
+
+def _segment_stats(cols, rows, seg_id, first_idx, want_prefix: bool):
+    """``cols``: list of 0/1 indicator vectors [n] (int32).  Per column: the total inside every group [U] and, if asked,
+    the exclusive running count inside the group in permutation order, aligned with the original rows [n].  Integer
+    running sums: exact for any row count."""
+    n = rows.shape[0]
+    last_idx = torch.cat([first_idx[1:], first_idx.new_tensor([n])]) - 1
+    totals, prefix = [], []
+    for col in cols:
+        vals = col[rows]
+        cs = torch.cumsum(vals, 0, dtype=torch.int32)
+        base = cs[first_idx] - vals[first_idx]
+        totals.append((cs[last_idx] - base).float())
+        if want_prefix:
+            out = torch.empty(n, dtype=torch.float32, device=rows.device)
+            out[rows] = (cs - vals - base[seg_id]).float()
+            prefix.append(out)
+    return torch.stack(totals), (torch.stack(prefix) if want_prefix else None)
 
 
 def _all_gather_rows(ctx, t: torch.Tensor, counts) -> torch.Tensor:
@@ -247,7 +260,7 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
     cls, n_cls, tborders = _target_classes(plan, y_train, codec, tbc)
     plan.target_borders, plan.n_target_classes = tborders, n_cls
     cls_t = torch.from_numpy(cls).to(dev)
-    ones = torch.ones(n, dtype=torch.float32, device=dev)
+    ones = torch.ones(n, dtype=torch.int32, device=dev)
 
     flat, train_cols, eval_cols, model_ctrs = [], [], [[] for _ in eval_pools], []
     sample_idx = None          # rows the CTR borders are chosen from (one draw for all CTR features)
@@ -268,19 +281,18 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
         # hashing, grouping and look-ups stay on the training device (a host sort of 45M 64-bit keys per projection
         # would dominate the whole fit)
         h_train_t = projection_hash_t([gathered_cat(c) for c in proj])
-        uniq_t, keys_t = torch.unique(h_train_t, return_inverse=True)
+        rows_t, seg_id, first_idx, uniq_t = _group_rows(h_train_t, order_t)
         U = int(uniq_t.numel())
+        keys_t = torch.empty(n, dtype=torch.int64, device=dev)          # dense group number of every row
+        keys_t[rows_t] = seg_id
         # model tables want the hashes in unsigned order: the signed-sorted list is that order rotated
         rot = int((uniq_t < 0).sum().item())
         uniq_s = uniq_t.cpu().numpy().view(np.uint64)
         uniq = np.concatenate([uniq_s[rot:], uniq_s[:rot]])
         # indicators: class > border k  (Borders), one column per needed target border + the count column
         need_tb = sorted({s.target_border_idx for s in specs if s.ctr_type in TARGET_CTRS})
-        cols = [ones] + [(cls_t > tb).float() for tb in need_tb]
-        colmat = torch.stack(cols)
-        prefix = _ordered_stats(keys_t, order_t, colmat) if any(s.ctr_type in TARGET_CTRS for s in specs) else None
-        totals = torch.zeros((len(cols), U), dtype=torch.float32, device=dev)
-        totals.index_add_(1, keys_t, colmat)
+        cols = [ones] + [(cls_t > tb).int() for tb in need_tb]
+        totals, prefix = _segment_stats(cols, rows_t, seg_id, first_idx, any(s.ctr_type in TARGET_CTRS for s in specs))
         totals_s = totals.cpu().numpy()
         totals_np = np.concatenate([totals_s[:, rot:], totals_s[:, :rot]], axis=1)
         max_count = float(totals_np[0].max()) if U else 1.0

@@ -43,14 +43,15 @@ def test_ctr_training_and_model_roundtrip(tmp_path):
 def test_ordered_ctr_matches_plain_python_oracle():
     """Ordered target statistic of one categorical column against a sequential re-implementation."""
     import torch
-    from catboost_b200.train.ctr import _ordered_stats
+    from catboost_b200.train.ctr import _group_rows, _segment_stats
     rng = np.random.default_rng(1)
     n = 500
-    keys = rng.integers(0, 13, n)
+    keys = rng.integers(-6, 7, n)
     order = rng.permutation(n)
-    good = (rng.random(n) < 0.3).astype(np.float32)
-    got = _ordered_stats(torch.from_numpy(keys), torch.from_numpy(order),
-                         torch.stack([torch.ones(n), torch.from_numpy(good)])).numpy()
+    good = (rng.random(n) < 0.3).astype(np.int32)
+    rows, seg_id, first_idx, uniq = _group_rows(torch.from_numpy(keys), torch.from_numpy(order))
+    assert uniq.tolist() == sorted(set(keys.tolist()))
+    totals, got = _segment_stats([torch.ones(n, dtype=torch.int32), torch.from_numpy(good)], rows, seg_id, first_idx, True)
     cnt, pos = {}, {}
     exp = np.zeros((2, n))
     for i in order:
@@ -58,7 +59,8 @@ def test_ordered_ctr_matches_plain_python_oracle():
         exp[0, i], exp[1, i] = cnt.get(k, 0), pos.get(k, 0)
         cnt[k] = cnt.get(k, 0) + 1
         pos[k] = pos.get(k, 0) + good[i]
-    assert np.allclose(got, exp)
+    assert np.allclose(got.numpy(), exp)
+    assert totals[0].tolist() == [cnt[k] for k in uniq.tolist()] and totals[1].tolist() == [pos[k] for k in uniq.tolist()]
 
 
 def test_cat_hash_known_values():
