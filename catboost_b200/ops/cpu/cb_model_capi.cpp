@@ -247,6 +247,11 @@ void parse_model(Model& m, const uint8_t* data, size_t size) {
     const Table mt = core.table(1);
     if (!mt.ok) fail("the model file holds no trees");
     for (const Table& kv : core.tables(2)) m.info[kv.string(0)] = kv.string(1);
+    {
+        size_t d;
+        if (mt.vec(12, 4, &d) || mt.vec(13, 4, &d) || mt.vec(18, 4, &d))
+            fail("the model uses text or embedding features, which this evaluator does not compute");
+    }
     m.dims = std::max(1, (int)mt.scalar<int32_t>(0, 1));
     m.tree_splits = mt.vector<int>(1);
     m.tree_sizes = mt.vector<int>(2);

@@ -162,3 +162,21 @@ def test_header_is_plain_c_and_links(tmp_path):
     trees, value = res.stdout.split()
     assert int(trees) == 12
     assert abs(float(value) - float(m.predict(X[7:8])[0])) < 1e-6
+
+
+def test_model_files_written_by_the_reference():
+    """Models saved by the reference itself (numerical + categorical with 26 CTR features; text models are refused)."""
+    import os
+    ref = os.environ.get("CATBOOST_REFERENCE", "/root/reference") + "/catboost/pytest/data"
+    path = ref + "/models/features_num_cat__dataset_adult.cbm"
+    if not os.path.exists(path):
+        pytest.skip("reference model files are not available")
+    m = cb.CatBoost().load_model(path)
+    pool = cb.Pool(ref + "/adult/test_small", column_description=ref + "/adult/train.cd")
+    nm = NativeModelCalcer(path)
+    assert nm.tree_count == m.tree_count_ and nm.cat_features_count == 11
+    fd, ch = m._model.pool_arrays(pool)
+    np.testing.assert_allclose(nm.predict_hashed(fd, ch.T)[:, 0], m.predict(pool, prediction_type="RawFormulaVal"),
+                               rtol=1e-6, atol=1e-6)
+    with pytest.raises(NativeModelError, match="text or embedding"):
+        NativeModelCalcer(ref + "/models/features_num_cat_text__dataset_rotten_tomatoes__binclass.cbm")
