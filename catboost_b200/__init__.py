@@ -7,6 +7,7 @@ from .core import (CatBoost, CatBoostClassifier, CatBoostRanker, CatBoostRegress
                    to_classifier, to_ranker, to_regressor, train)
 from .data.pool import CatBoostError, Pool  # noqa: F401
 from .cv import cv  # noqa: F401
+from .eval_features import eval_features  # noqa: F401
 
 FeaturesData = None
 __version__ = "0.1.0"

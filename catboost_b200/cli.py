@@ -352,7 +352,70 @@ def mode_roc(argv):
     return 0
 
 
-MODES = {"fit": mode_fit, "calc": mode_calc, "fstr": mode_fstr, "eval-metrics": mode_eval_metrics,
+def mode_ostr(argv):
+    """Object importance (catboost/app/mode_ostr.cpp): one line per scored training object."""
+    ap = argparse.ArgumentParser(prog="catboost_b200 ostr")
+    ap.add_argument("-m", "--model-file", default="model.bin")
+    ap.add_argument("-f", "--learn-set", required=True)
+    ap.add_argument("-t", "--test-set", required=True)
+    ap.add_argument("--column-description", "--cd", dest="cd")
+    ap.add_argument("--delimiter", default="\t")
+    ap.add_argument("--has-header", action="store_true")
+    ap.add_argument("-o", "--output-path", default="object_importances.tsv")
+    ap.add_argument("--ostr-type", default="Average", choices=["Average", "PerObject"])
+    ap.add_argument("--top-size", type=int, default=-1)
+    ap.add_argument("--update-method", default="SinglePoint")
+    ap.add_argument("--importance-values-sign", default="All", choices=["All", "Positive", "Negative"])
+    args = ap.parse_args(argv)
+    from .core import CatBoost
+    model = CatBoost().load_model(args.model_file)
+    idx, val = model.get_object_importance(_pool(args.test_set, args), _pool(args.learn_set, args), top_size=args.top_size,
+                                           type=args.ostr_type, update_method=args.update_method,
+                                           importance_values_sign=args.importance_values_sign)
+    with open(args.output_path, "w") as fh:
+        if args.ostr_type == "Average":
+            for i, v in zip(idx, val):
+                fh.write(f"{int(i)}\t{v:.9g}\n")
+        else:
+            for ii, vv in zip(idx, val):
+                fh.write("\t".join(f"{int(i)}:{v:.9g}" for i, v in zip(ii, vv)) + "\n")
+    return 0
+
+
+def mode_eval_feature(argv):
+    """Feature evaluation on folds of one dataset (catboost/app/mode_eval_feature.cpp)."""
+    ap = argparse.ArgumentParser(prog="catboost_b200 eval-feature")
+    ap.add_argument("-f", "--learn-set", required=True)
+    ap.add_argument("--column-description", "--cd", dest="cd")
+    ap.add_argument("--delimiter", default="\t")
+    ap.add_argument("--has-header", action="store_true")
+    ap.add_argument("--features-to-evaluate", required=True, help="comma separated feature indices or names")
+    ap.add_argument("--feature-eval-mode", default="SeqAdd", choices=["All", "SeqAdd", "SeqRem", "SeqAddAndAll"])
+    ap.add_argument("--fold-count", type=int, default=5)
+    ap.add_argument("--loss-function", default="RMSE")
+    ap.add_argument("-i", "--iterations", type=int, default=100)
+    ap.add_argument("--params-file")
+    ap.add_argument("--task-type", default="CPU")
+    ap.add_argument("-o", "--output-path", default="feature_eval.json")
+    args = ap.parse_args(argv)
+    import json
+    from .eval_features import eval_features
+    params = {}
+    if args.params_file:
+        with open(args.params_file) as fh:
+            params = json.load(fh)
+    params.setdefault("loss_function", args.loss_function)
+    params.setdefault("iterations", args.iterations)
+    params.setdefault("task_type", args.task_type)
+    feats = [int(x) if x.strip().lstrip("-").isdigit() else x.strip() for x in args.features_to_evaluate.split(",")]
+    res = eval_features(_pool(args.learn_set, args), params, feats, eval_type=args.feature_eval_mode,
+                        fold_count=args.fold_count)
+    with open(args.output_path, "w") as fh:
+        json.dump(res, fh, indent=1)
+    return 0
+
+
+MODES = {"ostr": mode_ostr, "eval-feature": mode_eval_feature, "fit": mode_fit, "calc": mode_calc, "fstr": mode_fstr, "eval-metrics": mode_eval_metrics,
          "metadata": mode_metadata, "model-sum": mode_model_sum, "normalize-model": mode_normalize_model,
          "select-features": mode_select_features, "dataset-statistics": mode_dataset_statistics,
          "dump-options": mode_dump_options, "roc": mode_roc}
@@ -364,9 +427,9 @@ def main(argv=None):
         print("usage: python -m catboost_b200 <mode> [options]\nmodes: " + ", ".join(MODES))
         return 0
     mode = argv[0]
-    if mode in ("run-worker", "ostr", "eval-feature", "model-based-eval"):
-        print(f"mode {mode!r} is not supported: multi-host CPU workers / object importance / feature evaluation are "
-              "outside this framework (single box, GPUs over NVLink)", file=sys.stderr)
+    if mode in ("run-worker", "model-based-eval"):
+        print(f"mode {mode!r} is not supported: training over several hosts starts one process per GPU with torchrun "
+              "(every rank calls fit on its row shard); model-based evaluation is covered by eval-feature", file=sys.stderr)
         return 2
     if mode not in MODES:
         print(f"unknown mode {mode!r}; modes: " + ", ".join(MODES), file=sys.stderr)

@@ -361,6 +361,29 @@ class CatBoost:
             out[idx] = float(np.mean(m.predict_raw(work, ch)[:, 0]))
         return out, None
 
+    def get_object_importance(self, pool, train_pool, top_size=-1, type="Average", update_method="SinglePoint",
+                              importance_values_sign="All", thread_count=-1, verbose=False, ostr_type=None,
+                              log_cout=None, log_cerr=None):
+        """Influence of the training objects on the loss over ``pool`` (LeafInfluence;
+        catboost/python-package/catboost/core.py ``get_object_importance``).  Returns ``(indices, scores)`` ordered by
+        decreasing |score|: one pair of arrays for ``type='Average'``, one pair of lists for ``'PerObject'``."""
+        self._check_fitted()
+        from .ostr import object_importance, select
+        from .params import parse_loss
+        from .train.objectives import make_objective
+        if ostr_type is not None:
+            type = ostr_type
+        if not isinstance(pool, Pool) or not isinstance(train_pool, Pool):
+            raise CatBoostError("pool and train_pool must be Pool objects with labels")
+        if pool.label is None or train_pool.label is None:
+            raise CatBoostError("object importance needs the labels of both datasets")
+        params = dict(self._model.params)
+        lname, lparams = parse_loss(params.get("loss_function") or self._model.loss_name)
+        objective = make_objective(lname, lparams)
+        scores = object_importance(self._model, objective, params, train_pool, pool, self._encode_labels(train_pool.label),
+                                   self._encode_labels(pool.label), update_method=update_method)
+        return select(scores, type, -1 if top_size is None else int(top_size), importance_values_sign)
+
     def get_feature_importance(self, data=None, type=EFstrType.FeatureImportance, prettified=False, thread_count=-1,
                                verbose=False, fstr_type=None, shap_mode="Auto", model_output="Raw",
                                interaction_indices=None, shap_calc_type="Regular", reference_data=None, log_cout=None,

@@ -504,3 +504,96 @@ def test_partial_dependence():
     pd2, _ = m.plot_partial_dependence(X[:100], [0, 2])
     assert pd2.shape == (len(m._model.float_features[0].borders) + 1, len(m._model.float_features[2].borders) + 1)
     assert np.abs(pd2[:, 0] - pd2[:, -1]).max() < 0.5                      # x2 carries no signal
+
+
+def _refit_leaves(model, leaf_tr, leaf_te, y, w, lr, l2, loss):
+    """Leaf values of fixed tree structures re-estimated with document weights ``w`` (one Newton step per tree)."""
+    T = leaf_tr.shape[1]
+    bias = float(np.ravel(model.bias)[0])
+    a = np.full(len(y), bias)
+    at = np.full(leaf_te.shape[0], bias)
+    for t in range(T):
+        if loss == "RMSE":
+            der, hess = y - a, np.ones_like(a)
+        else:
+            p = 1.0 / (1.0 + np.exp(-a))
+            der, hess = y - p, p * (1 - p)
+        L = model.trees[t].leaf_values.shape[0]
+        D = np.bincount(leaf_tr[:, t], weights=w * der, minlength=L)
+        H = np.bincount(leaf_tr[:, t], weights=w * hess, minlength=L) + l2
+        val = lr * D / H
+        a = a + val[leaf_tr[:, t]]
+        at = at + val[leaf_te[:, t]]
+    return at
+
+
+@pytest.mark.parametrize("loss", ["RMSE", "Logloss"])
+def test_object_importance_against_reweighted_refit(loss):
+    rng = np.random.default_rng(5)
+    n, m = 120, 15
+    X = rng.standard_normal((n + m, 4)).astype(np.float32)
+    f = X[:, 0] + 0.5 * X[:, 1] * X[:, 2]
+    y = (f + 0.3 * rng.standard_normal(n + m)).astype(np.float32) if loss == "RMSE" else (f > 0).astype(np.float32)
+    cls = cb.CatBoostRegressor if loss == "RMSE" else cb.CatBoostClassifier
+    lr, l2 = 0.3, 2.0
+    mdl = cls(iterations=8, depth=3, learning_rate=lr, l2_leaf_reg=l2, bootstrap_type="No", leaf_estimation_iterations=1,
+              leaf_estimation_method="Newton", boost_from_average=False, random_strength=0, verbose=False,
+              allow_writing_files=False, loss_function=loss).fit(X[:n], y[:n])
+    train, test = cb.Pool(X[:n], y[:n]), cb.Pool(X[n:], y[n:])
+    M = mdl._model
+    leaf_tr, leaf_te = M.leaf_indices(X[:n]), M.leaf_indices(X[n:])
+    base = _refit_leaves(M, leaf_tr, leaf_te, y[:n].astype(np.float64), np.ones(n), lr, l2, loss)
+    np.testing.assert_allclose(base, mdl.predict(X[n:], prediction_type="RawFormulaVal"), rtol=1e-4, atol=1e-4)
+    from catboost_b200.ostr import object_importance
+    from catboost_b200.train.objectives import make_objective
+    scores = object_importance(M, make_objective(loss, {}), M.params, train, test, y[:n], y[n:], update_method="AllPoints",
+                               device="cpu")
+    if loss == "RMSE":
+        der_te = y[n:] - base
+    else:
+        der_te = y[n:] - 1.0 / (1.0 + np.exp(-base))
+    eps = 1e-4
+    for i in (0, 7, 33, 90):
+        w = np.ones(n)
+        w[i] = 1 + eps
+        up = _refit_leaves(M, leaf_tr, leaf_te, y[:n].astype(np.float64), w, lr, l2, loss)
+        w[i] = 1 - eps
+        dn = _refit_leaves(M, leaf_tr, leaf_te, y[:n].astype(np.float64), w, lr, l2, loss)
+        np.testing.assert_allclose(scores[i], der_te * (up - dn) / (2 * eps), rtol=2e-3, atol=1e-7)
+    # the public call: ordering, signs, sizes
+    idx, val = mdl.get_object_importance(test, train, top_size=10, update_method="AllPoints")
+    assert len(idx) == 10 and np.all(np.diff(np.abs(val)) <= 1e-15)
+    np.testing.assert_allclose(val, scores.mean(axis=1)[idx], rtol=1e-9, atol=1e-12)
+    idx_p, val_p = mdl.get_object_importance(test, train, importance_values_sign="Positive", update_method="SinglePoint")
+    assert np.all(val_p > 0) and len(idx_p) <= n
+    per_idx, per_val = mdl.get_object_importance(test, train, type="PerObject", top_size=3, update_method="AllPoints")
+    assert len(per_idx) == m and all(len(v) == 3 for v in per_val)
+
+
+def test_eval_features_finds_the_useful_feature(tmp_path):
+    rng = np.random.default_rng(3)
+    n = 900
+    X = rng.standard_normal((n, 4)).astype(np.float32)
+    y = (2.0 * X[:, 1] + 0.1 * rng.standard_normal(n)).astype(np.float32)      # only feature 1 matters
+    res = cb.eval_features(cb.Pool(X, y), {"loss_function": "RMSE", "iterations": 30, "depth": 3, "learning_rate": 0.3},
+                           [1, 3], eval_type="SeqAddAndAll", fold_count=6)
+    cases = res["RMSE"]["cases"]
+    assert set(cases) == {"all features", "with 1", "with 3"} and len(res["RMSE"]["baseline"]) == 6
+    assert cases["with 1"]["delta_mean"] > 0.5 and cases["with 1"]["decision"] == "GOOD"
+    assert abs(cases["with 3"]["delta_mean"]) < 0.1 and cases["with 3"]["decision"] != "GOOD"
+    assert cases["all features"]["decision"] == "GOOD"
+    # command line: the same evaluation from a file, and object importance of a saved model
+    from catboost_b200 import cli
+    data = tmp_path / "d.tsv"
+    np.savetxt(data, np.column_stack([y, X]), delimiter="\t", fmt="%.6g")
+    out = tmp_path / "fe.json"
+    assert cli.main(["eval-feature", "-f", str(data), "--features-to-evaluate", "1", "--fold-count", "3", "-i", "15",
+                     "-o", str(out)]) == 0
+    import json
+    assert json.loads(out.read_text())["RMSE"]["cases"]["all features"]["delta_mean"] > 0.3
+    m = cb.CatBoostRegressor(iterations=10, depth=3, verbose=False, allow_writing_files=False).fit(X, y)
+    m.save_model(str(tmp_path / "m.cbm"))
+    ostr = tmp_path / "ostr.tsv"
+    assert cli.main(["ostr", "-m", str(tmp_path / "m.cbm"), "-f", str(data), "-t", str(data), "--top-size", "5",
+                     "-o", str(ostr)]) == 0
+    assert len(ostr.read_text().strip().splitlines()) == 5
