@@ -597,3 +597,47 @@ def test_eval_features_finds_the_useful_feature(tmp_path):
     assert cli.main(["ostr", "-m", str(tmp_path / "m.cbm"), "-f", str(data), "-t", str(data), "--top-size", "5",
                      "-o", str(ostr)]) == 0
     assert len(ostr.read_text().strip().splitlines()) == 5
+
+
+def test_utils_module(tmp_path):
+    from catboost_b200 import utils
+    cd = tmp_path / "train.cd"
+    utils.create_cd(label=0, cat_features=[2, 4], weight=5, auxiliary_columns=[6], feature_names={1: "age", 2: "city"},
+                    output_path=str(cd))
+    assert cd.read_text().splitlines() == ["0\tLabel\t", "1\tNum\tage", "2\tCateg\tcity", "4\tCateg\t", "5\tWeight\t",
+                                           "6\tAuxiliary\t"]
+    with pytest.raises(cb.CatBoostError):
+        utils.create_cd(label=0, cat_features=[0], output_path=str(cd))
+    info = utils.read_cd(str(cd), column_count=8)
+    assert info["cat_feature_indices"] == [1, 3] and info["non_feature_column_indices"] == [0, 5, 6]
+    assert info["column_type_to_indices"]["Categ"] == [2, 4] and info["column_names"][1] == "age"
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((800, 4)).astype(np.float32)
+    y = (X[:, 0] + 0.3 * rng.standard_normal(800) > 0).astype(int)
+    m = cb.CatBoostClassifier(iterations=20, depth=3, verbose=False, allow_writing_files=False).fit(X, y)
+    pool = cb.Pool(X, y)
+    raw = m.predict(X, prediction_type="RawFormulaVal")
+    from catboost_b200.metrics import make_metric
+    assert utils.eval_metric(y, raw, "Logloss") == [make_metric("Logloss").eval(raw, y.astype(float))]
+    assert utils.eval_metric(y, raw, "AUC")[0] > 0.9
+    fpr, tpr, thr = utils.get_roc_curve(m, pool)
+    assert fpr[0] == 0 and tpr[-1] == 1 and np.all(np.diff(fpr) >= 0) and np.all(np.diff(thr) <= 0)
+    t_fpr, f = utils.get_fpr_curve(curve=(fpr, tpr, thr))
+    t_fnr, g = utils.get_fnr_curve(m, pool)
+    assert np.allclose(f, fpr) and np.allclose(g, 1 - tpr)
+    b = utils.select_threshold(m, pool, FPR=0.05)
+    p = m.predict_proba(X)[:, 1]
+    assert np.mean(p[y == 0] >= b) <= 0.05 + 1e-9
+    assert 0 < utils.select_threshold(curve=(fpr, tpr, thr)) < 1
+    cm = utils.get_confusion_matrix(m, pool)
+    pred = np.asarray(m.predict(X)).astype(int).reshape(-1)
+    assert cm.sum() == 800 and cm[1, 1] == np.sum((y == 1) & (pred == 1)) and cm[0, 1] == np.sum((y == 0) & (pred == 1))
+    grid = utils.calculate_quantization_grid(X[:, 0], 7, "Median")
+    assert len(grid) == 7 and np.all(np.diff(grid) > 0)
+    data = tmp_path / "d.tsv"
+    np.savetxt(data, np.column_stack([y, X]), delimiter="\t", fmt="%.6g")
+    qp = utils.quantize(str(data), border_count=16)
+    assert qp.is_quantized() and qp.num_row() == 800
+    assert isinstance(utils.get_gpu_device_count(), int)
+    onx = utils.convert_to_onnx_object(m)
+    assert onx is not None
