@@ -163,3 +163,88 @@ def leaf_sums(leaf: torch.Tensor, cols: torch.Tensor, L: int, n: int) -> torch.T
     out = torch.zeros((C, L), dtype=torch.float64, device=leaf.device)
     out.index_add_(1, idx, cols[:, :n].double())
     return out.t().contiguous()
+
+
+# ---- CTR engine (ops/cuda/cb_ctr.cu) ---------------------------------------------------------------------------
+CTR_MAX_SPECS = 16
+CTR_MAX_TB = 4
+
+
+def ctr_scan(sorted_h: torch.Tensor, rows: torch.Tensor, cls_u8: torch.Tensor, need_tb):
+    """Segmented exclusive scans over documents sorted by (projection hash, permutation position).
+
+    Returns (excl int32 [1 + len(need_tb), n] per sorted position, seg_id int32 [n], distinct hashes int64 [U],
+    per-segment totals int32 [1 + len(need_tb), U])."""
+    lib = native.cuda_lib()
+    dev = sorted_h.device
+    n = int(sorted_h.shape[0])
+    nb = len(need_tb)
+    if nb > CTR_MAX_TB:
+        raise ValueError(f"at most {CTR_MAX_TB} target borders per projection")
+    C = 1 + nb
+    tile, agg = lib.cb_ctr_tile(), lib.cb_ctr_agg_bytes()
+    excl = torch.empty((C, n), dtype=torch.int32, device=dev)
+    seg_id = torch.empty(n, dtype=torch.int32, device=dev)
+    open_ = torch.empty(n, dtype=torch.uint8, device=dev)
+    tile_agg = torch.empty(((n + tile - 1) // tile) * agg, dtype=torch.uint8, device=dev)
+    uniq = torch.empty(n, dtype=torch.int64, device=dev)
+    totals = torch.empty((C, n), dtype=torch.int32, device=dev)
+    nseg = torch.zeros(1, dtype=torch.int32, device=dev)
+    tb = (ctypes.c_int * max(1, nb))(*[int(t) for t in need_tb])
+    with torch.cuda.device(dev):
+        native.cuda_check(lib.cb_ctr_scan(_p(sorted_h.contiguous()), _p(rows.contiguous()), _p(cls_u8.contiguous()),
+                                          ctypes.c_longlong(n), ctypes.c_int(nb), tb, _p(excl), _p(seg_id), _p(open_),
+                                          _p(tile_agg), _p(uniq), _p(totals), _p(nseg), _stream(dev)), "cb_ctr_scan")
+    U = int(nseg.item())
+    return excl, seg_id, uniq[:U].clone(), totals[:, :U].contiguous()
+
+
+def _ctr_spec_arrays(descs):
+    S = len(descs)
+    ci = (ctypes.c_int * S)
+    cf = (ctypes.c_float * S)
+    return (ci(*[int(d[0]) for d in descs]), ci(*[int(d[1]) for d in descs]), cf(*[float(d[2]) for d in descs]),
+            cf(*[float(d[3]) for d in descs]), cf(*[float(d[4]) for d in descs]))
+
+
+def ctr_minmax(descs, excl, totals, seg_id):
+    """[(min, max)] of the CTR values of ``descs`` over all documents (float32)."""
+    lib = native.cuda_lib()
+    dev = excl.device
+    S = len(descs)
+    if S == 0:
+        return []
+    mm = torch.tensor([-1, 0] * S, dtype=torch.int32, device=dev)       # bit patterns: min starts at all ones, max at 0
+    kind, col, pn, pd, den = _ctr_spec_arrays(descs)
+    n = int(excl.shape[1])
+    # the kernel reads only row 0 of ``totals`` (the counts), so the row stride does not matter
+    with torch.cuda.device(dev):
+        native.cuda_check(lib.cb_ctr_minmax(ctypes.c_int(S), kind, col, pn, pd, den, _p(excl), _p(totals), _p(seg_id),
+                                            ctypes.c_longlong(n), _p(mm), _stream(dev)), "cb_ctr_minmax")
+    vals = mm.cpu().numpy().view(np.float32)
+    return [(np.float32(vals[2 * s]), np.float32(vals[2 * s + 1])) for s in range(S)]
+
+
+def ctr_binarize(descs, borders, excl, totals, seg_id, rows, row_lo: int, n_out: int) -> torch.Tensor:
+    """uint8 [len(descs), n_out]: border bucket of every CTR for documents row_lo .. row_lo + n_out."""
+    lib = native.cuda_lib()
+    dev = excl.device
+    S = len(descs)
+    out = torch.empty((S, n_out), dtype=torch.uint8, device=dev)
+    if S == 0 or n_out == 0:
+        return out
+    kind, col, pn, pd, den = _ctr_spec_arrays(descs)
+    offs, cnts, flat = [], [], []
+    for b in borders:
+        offs.append(len(flat))
+        cnts.append(len(b))
+        flat.extend(float(x) for x in b)
+    bt = torch.tensor(flat, dtype=torch.float32, device=dev)
+    n = int(excl.shape[1])
+    with torch.cuda.device(dev):
+        native.cuda_check(lib.cb_ctr_binarize(ctypes.c_int(S), kind, col, pn, pd, den, (ctypes.c_int * S)(*offs),
+                                              (ctypes.c_int * S)(*cnts), _p(bt), ctypes.c_int(len(flat)), _p(excl),
+                                              _p(totals), _p(seg_id), _p(rows.contiguous()), ctypes.c_longlong(n),
+                                              ctypes.c_longlong(row_lo), ctypes.c_longlong(n_out), _p(out), _stream(dev)),
+                          "cb_ctr_binarize")
+    return out

@@ -22,7 +22,7 @@ from pathlib import Path
 
 _HERE = Path(__file__).resolve().parent
 CUDA_SRC = [_HERE / "cuda" / "cb_kernels.cu", _HERE / "cuda" / "cb_fused.cu", _HERE / "cuda" / "cb_leaf.cu",
-            _HERE / "cuda" / "cb_quantize_tma.cu", _HERE / "cuda" / "cb_ranking.cu"]
+            _HERE / "cuda" / "cb_quantize_tma.cu", _HERE / "cuda" / "cb_ranking.cu", _HERE / "cuda" / "cb_ctr.cu"]
 CUDA_HDR = sorted((_HERE / "cuda").glob("*.cuh")) + sorted((_HERE / "cuda").glob("*.h"))
 CPU_SRC = [_HERE / "cpu" / "cb_cpu.cpp", _HERE / "cpu" / "cb_cityhash.h"]
 MODEL_SRC = [_HERE / "cpu" / "cb_model_capi.cpp", _HERE / "cpu" / "cb_model_capi.h", _HERE / "cpu" / "cb_cityhash.h"]
@@ -145,6 +145,16 @@ _SIGS = {
     "cb_hist_smem_bytes": (c_int, [c_int, c_int, c_int]),
     "cb_hist": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                         c_int, c_int, c_void_p]),
+    "cb_ctr_tile": (c_int, []),
+    "cb_ctr_agg_bytes": (c_int, []),
+    "cb_ctr_max_tb": (c_int, []),
+    "cb_ctr_max_specs": (c_int, []),
+    "cb_ctr_scan": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_void_p, c_void_p]),
+    "cb_ctr_minmax": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll,
+                              c_void_p, c_void_p]),
+    "cb_ctr_binarize": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_void_p, c_void_p]),
     "cb_hist_n": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                           c_void_p, c_int, c_int, c_void_p]),
     "cb_score": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,

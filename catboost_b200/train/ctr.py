@@ -209,6 +209,79 @@ def _segment_stats(cols, rows, seg_id, first_idx, want_prefix: bool):
     return torch.stack(totals), (torch.stack(prefix) if want_prefix else None)
 
 
+class _TensorGroup:
+    """Grouping, ordered statistics and bucketing of one projection as tensor operations (host training, and the
+    oracle of the device kernels)."""
+
+    def __init__(self, h, order_t, cls_t, need_tb, want_prefix):
+        n = h.shape[0]
+        rows_t, seg_id, first_idx, self.uniq_t = _group_rows(h, order_t)
+        self.keys_t = torch.empty(n, dtype=torch.int64, device=h.device)       # dense group number of every row
+        self.keys_t[rows_t] = seg_id
+        cols = [torch.ones(n, dtype=torch.int32, device=h.device)] + [(cls_t > tb).int() for tb in need_tb]
+        self.totals, self.prefix = _segment_stats(cols, rows_t, seg_id, first_idx, want_prefix)
+
+    def _values(self, d):
+        kind, ci, pn, pd, denom = d
+        if kind == 0:
+            return (self.prefix[ci] + pn) / (self.prefix[0] + pd)
+        return ((self.totals[0] + pn) / denom)[self.keys_t]
+
+    def value_ranges(self, descs):
+        out = []
+        for d in descs:
+            v = self._values(d)
+            out.append((np.float32(v.min().item()), np.float32(v.max().item())))
+        return out
+
+    def sample_values(self, d, sample_idx):
+        v = self._values(d)
+        return v if sample_idx is None else v[sample_idx]
+
+    def binarize(self, descs, borders, lo_row, n_local):
+        dev = self.keys_t.device
+        return [torch.searchsorted(torch.from_numpy(b).to(dev), self._values(d).contiguous(), right=False)
+                .to(torch.uint8)[lo_row:lo_row + n_local] for d, b in zip(descs, borders)]
+
+
+class _KernelGroup:
+    """The same through the hand-written kernels of ops/cuda/cb_ctr.cu: one library sort, then segmented scans, value
+    range and bucketing without materialising a CTR value in memory."""
+
+    def __init__(self, h, order_t, cls_u8, need_tb, want_prefix):
+        from ..ops import api as ops
+        self.ops = ops
+        sorted_h, srt = torch.sort(h[order_t], stable=True)
+        self.rows_t = order_t[srt]
+        self.n = int(h.shape[0])
+        self.excl, self.seg_id, self.uniq_t, self.totals_i = ops.ctr_scan(sorted_h, self.rows_t, cls_u8, need_tb)
+        self.totals = self.totals_i.float()
+        self._keys = None
+
+    def value_ranges(self, descs):
+        out = []
+        for k in range(0, len(descs), self.ops.CTR_MAX_SPECS):
+            out += self.ops.ctr_minmax(descs[k:k + self.ops.CTR_MAX_SPECS], self.excl, self.totals_i, self.seg_id)
+        return out
+
+    def sample_values(self, d, sample_idx):
+        kind, ci, pn, pd, denom = d
+        assert kind == 1
+        if self._keys is None:
+            self._keys = torch.empty(self.n, dtype=torch.int32, device=self.rows_t.device)
+            self._keys[self.rows_t] = self.seg_id
+        keys = self._keys if sample_idx is None else self._keys[sample_idx]
+        return ((self.totals[0] + pn) / denom)[keys.long()]
+
+    def binarize(self, descs, borders, lo_row, n_local):
+        out = []
+        for k in range(0, len(descs), self.ops.CTR_MAX_SPECS):
+            m = self.ops.ctr_binarize(descs[k:k + self.ops.CTR_MAX_SPECS], borders[k:k + self.ops.CTR_MAX_SPECS], self.excl,
+                                      self.totals_i, self.seg_id, self.rows_t, lo_row, n_local)
+            out += [m[j] for j in range(m.shape[0])]
+        return out
+
+
 def _all_gather_rows(ctx, t: torch.Tensor, counts) -> torch.Tensor:
     """Concatenation over the ranks (in rank order) of per-rank vectors of different lengths."""
     import torch.distributed as dist
@@ -260,7 +333,7 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
     cls, n_cls, tborders = _target_classes(plan, y_train, codec, tbc)
     plan.target_borders, plan.n_target_classes = tborders, n_cls
     cls_t = torch.from_numpy(cls).to(dev)
-    ones = torch.ones(n, dtype=torch.int32, device=dev)
+    cls_u8 = cls_t.to(torch.uint8)
 
     flat, train_cols, eval_cols, model_ctrs = [], [], [[] for _ in eval_pools], []
     sample_idx = None          # rows the CTR borders are chosen from (one draw for all CTR features)
@@ -281,18 +354,19 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
         # hashing, grouping and look-ups stay on the training device (a host sort of 45M 64-bit keys per projection
         # would dominate the whole fit)
         h_train_t = projection_hash_t([gathered_cat(c) for c in proj])
-        rows_t, seg_id, first_idx, uniq_t = _group_rows(h_train_t, order_t)
+        # indicators: class > border k  (Borders), one column per needed target border + the count column
+        need_tb = sorted({s.target_border_idx for s in specs if s.ctr_type in TARGET_CTRS})
+        want_prefix = any(s.ctr_type in TARGET_CTRS for s in specs)
+        if dev.type == "cuda":
+            grp = _KernelGroup(h_train_t, order_t, cls_u8, need_tb, want_prefix)
+        else:
+            grp = _TensorGroup(h_train_t, order_t, cls_t, need_tb, want_prefix)
+        uniq_t, totals = grp.uniq_t, grp.totals
         U = int(uniq_t.numel())
-        keys_t = torch.empty(n, dtype=torch.int64, device=dev)          # dense group number of every row
-        keys_t[rows_t] = seg_id
         # model tables want the hashes in unsigned order: the signed-sorted list is that order rotated
         rot = int((uniq_t < 0).sum().item())
         uniq_s = uniq_t.cpu().numpy().view(np.uint64)
         uniq = np.concatenate([uniq_s[rot:], uniq_s[:rot]])
-        # indicators: class > border k  (Borders), one column per needed target border + the count column
-        need_tb = sorted({s.target_border_idx for s in specs if s.ctr_type in TARGET_CTRS})
-        cols = [ones] + [(cls_t > tb).int() for tb in need_tb]
-        totals, prefix = _segment_stats(cols, rows_t, seg_id, first_idx, any(s.ctr_type in TARGET_CTRS for s in specs))
         totals_s = totals.cpu().numpy()
         totals_np = np.concatenate([totals_s[:, rot:], totals_s[:, :rot]], axis=1)
         max_count = float(totals_np[0].max()) if U else 1.0
@@ -306,46 +380,52 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
                 pos = torch.zeros_like(he_t)
                 ok = torch.zeros(he_t.shape, dtype=torch.bool, device=dev)
             eval_keys.append((pos, ok))
+        # every CTR of the projection as (kind, numerator column, prior numerator, prior denominator, denominator)
+        descs = []
         for s in specs:
             if s.ctr_type in TARGET_CTRS:
-                ci = 1 + need_tb.index(s.target_border_idx)
-                tr_val = (prefix[ci] + s.prior_num) / (prefix[0] + s.prior_denom)
-                full = (totals[ci] + s.prior_num) / (totals[0] + s.prior_denom)
-                unseen = s.prior_num / s.prior_denom
+                descs.append((0, 1 + need_tb.index(s.target_border_idx), float(s.prior_num), float(s.prior_denom), 1.0))
             elif s.ctr_type == "Counter":
-                denom = max_count + s.prior_denom
-                full = (totals[0] + s.prior_num) / denom
-                tr_val = full[keys_t]
-                unseen = s.prior_num / denom
+                descs.append((1, 0, float(s.prior_num), float(s.prior_denom), max_count + s.prior_denom))
             else:   # FeatureFreq
-                denom = float(n) + s.prior_denom
-                full = (totals[0] + s.prior_num) / denom
-                tr_val = full[keys_t]
-                unseen = s.prior_num / denom
-            sample = tr_val if sample_idx is None else tr_val[sample_idx]
-            if s.ctr_type in TARGET_CTRS:
-                # Uniform grid between the smallest and largest sampled value, computed where the values are (same
-                # arithmetic as the host routine: float32, lo + (hi - lo) * k / (count + 1))
-                lo_v, hi_v = np.float32(sample.min().item()), np.float32(sample.max().item())
+                descs.append((1, 0, float(s.prior_num), float(s.prior_denom), float(n) + s.prior_denom))
+        target_pos = [k for k, d in enumerate(descs) if d[0] == 0]
+        ranges = dict(zip(target_pos, grp.value_ranges([descs[k] for k in target_pos]))) if target_pos else {}
+        all_borders = []
+        for k, (s, d) in enumerate(zip(specs, descs)):
+            if d[0] == 0:
+                # Uniform grid between the smallest and largest learn value (same arithmetic as the host routine:
+                # float32, lo + (hi - lo) * k / (count + 1))
+                lo_v, hi_v = ranges[k]
                 if hi_v > lo_v:
                     kk = np.arange(1, s.border_count + 1, dtype=np.float32)
                     b = np.unique((lo_v + (hi_v - lo_v) * kk / np.float32(s.border_count + 1)).astype(np.float32))
                 else:
                     b = np.zeros(0, dtype=np.float32)
             else:
+                sample = grp.sample_values(d, sample_idx)
                 borders, _ = select_borders(sample.cpu().numpy().reshape(-1, 1), s.border_count, "GreedyLogSum")
-                b = borders[0]
-            if len(b) == 0:
-                continue
+                b = np.asarray(borders[0], dtype=np.float32)
+            all_borders.append(b)
+        keep = [k for k, b in enumerate(all_borders) if len(b)]
+        cols_out = grp.binarize([descs[k] for k in keep], [all_borders[k] for k in keep], lo_row, n_local) if keep else []
+        for k, col in zip(keep, cols_out):
+            s, d, b = specs[k], descs[k], all_borders[k]
+            train_cols.append(col)
+            if d[0] == 0:
+                full = (totals[d[1]] + s.prior_num) / (totals[0] + s.prior_denom)
+                unseen = s.prior_num / s.prior_denom
+            else:
+                full = (totals[0] + s.prior_num) / d[4]
+                unseen = s.prior_num / d[4]
             bt = torch.from_numpy(b).to(dev)
-            train_cols.append(torch.searchsorted(bt, tr_val.contiguous(), right=False).to(torch.uint8)[lo_row:lo_row + n_local])
-            for k, (pos, ok) in enumerate(eval_keys):
+            for e, (pos, ok) in enumerate(eval_keys):
                 ev = torch.where(ok, full[pos] if U else torch.zeros_like(ok, dtype=torch.float32),
                                  torch.full((len(ok),), float(unseen), device=dev))
-                eval_cols[k].append(torch.searchsorted(bt, ev.contiguous(), right=False).to(torch.uint8))
+                eval_cols[e].append(torch.searchsorted(bt, ev.contiguous(), right=False).to(torch.uint8))
             ctr_index = len(model_ctrs)
-            if s.ctr_type in TARGET_CTRS:
-                good = totals_np[1 + need_tb.index(s.target_border_idx)]
+            if d[0] == 0:
+                good = totals_np[d[1]]
                 model_ctrs.append(CtrFeature(list(proj), s.ctr_type, s.prior_num, s.prior_denom, s.target_border_idx,
                                              uniq.copy(), good.astype(np.float64), totals_np[0].astype(np.float64), 0.0))
             else:

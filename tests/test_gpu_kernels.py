@@ -369,3 +369,41 @@ def test_device_wait_times_out_without_hanging():
     with pytest.raises(RuntimeError, match="timed out"):
         arena.check_status()
     lib.cb_comm_destroy(ctypes.c_void_p(h))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,card,nb", [(50_000, 37, 1), (300_001, 5, 2), (20_000, 15_000, 0), (4097, 1, 1), (9000, 3, 4)])
+def test_ctr_kernels_match_tensor_implementation(n, card, nb):
+    """Segmented scans, totals, value ranges and buckets of the CTR kernels against the tensor code."""
+    from catboost_b200.train.ctr import _KernelGroup, _TensorGroup
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(n + card)
+    # long and short groups, negative hashes included; several tiles
+    h = (torch.randint(0, card, (n,), generator=g) * 7919 - 3 * card * 1000).to(dev)
+    order = torch.randperm(n, generator=g).to(dev)
+    cls = torch.randint(0, nb + 2, (n,), generator=g).to(dev)
+    need_tb = list(range(nb))
+    kg = _KernelGroup(h, order, cls.to(torch.uint8), need_tb, True)
+    tg = _TensorGroup(h, order, cls, need_tb, True)
+    assert torch.equal(kg.uniq_t, tg.uniq_t)
+    assert torch.equal(kg.totals, tg.totals)
+    # exclusive prefixes: kernel output is in sorted order, the tensor code's in document order
+    back = torch.empty_like(tg.prefix)
+    back[:, kg.rows_t] = kg.excl.float()
+    assert torch.equal(back, tg.prefix)
+    keys = torch.empty(n, dtype=torch.int64, device=dev)
+    keys[kg.rows_t] = kg.seg_id.long()
+    assert torch.equal(keys, tg.keys_t)
+    descs = [(0, 1 + k, 0.5 * (k + 1), 1.0, 1.0) for k in range(nb)] + [(1, 0, 0.0, 1.0, float(tg.totals[0].max()) + 1.0),
+                                                                       (1, 0, 1.0, 1.0, float(n) + 1.0)]
+    target = [d for d in descs if d[0] == 0]
+    assert kg.value_ranges(target) == tg.value_ranges(target)
+    rng = np.random.default_rng(0)
+    borders = [np.sort(rng.uniform(0.0, 1.0, 15)).astype(np.float32) for _ in descs]
+    lo, cnt = n // 5, n // 2
+    a = kg.binarize(descs, borders, lo, cnt)
+    b = tg.binarize(descs, borders, lo, cnt)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    sample = torch.arange(0, n, 7, device=dev)
+    assert torch.equal(kg.sample_values(descs[-1], sample), tg.sample_values(descs[-1], sample))
