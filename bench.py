@@ -111,6 +111,35 @@ def bench_ranking(args, cfg, rank, world, dev):
     fit_s = time.perf_counter() - t0
     tm = model._train_info.get("timings", {})
     it_s = float(tm.get("iterations", float("nan")))
+    # batch apply of the trained model: rows already on the device (kernel throughput) and rows from host memory
+    # through the public predict call (staging, copies and the read-back included)
+    apply = None
+    if rank == 0:
+        from catboost_b200.models.gpu_apply import GpuPredictor
+        pred = GpuPredictor(model._model, dev)
+        n_dev = min(n, 1_000_000)
+        Xd = torch.from_numpy(X[:n_dev]).to(dev)
+        out = torch.empty((pred.dims, n_dev), dtype=torch.float32, device=dev)
+        for _ in range(3):
+            pred.predict_device(Xd, out)
+        reps = max(1, 100_000_000 // n_dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(dev)
+        e0.record()
+        for _ in range(reps):
+            pred.predict_device(Xd, out)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        dev_s = e0.elapsed_time(e1) / 1000.0
+        n_host = min(n, 2_000_000)
+        model.predict(X[:100_000], prediction_type="RawFormulaVal", task_type="GPU")
+        t1 = time.perf_counter()
+        model.predict(X[:n_host], prediction_type="RawFormulaVal", task_type="GPU")
+        host_s = time.perf_counter() - t1
+        apply = {"trees": iters, "features": F, "device_rows": n_dev * reps, "device_rows_per_s": n_dev * reps / dev_s,
+                 "tree_rows_per_s": n_dev * reps * iters / dev_s, "host_rows": n_host, "host_rows_per_s": n_host / host_s,
+                 "note": "device: 100M rows as repeated passes over 1M resident rows; host: predict() from pageable memory"}
+        del Xd, out
     ev_pool = cb.Pool(X[:200000], rel[:200000], group_id=gid[:200000])
     ndcg = [model.eval_metrics(ev_pool, ["NDCG"], ntree_end=1)["NDCG"][-1], model.eval_metrics(ev_pool, ["NDCG"], eval_period=iters)["NDCG"][-1]]
     if rank == 0:
@@ -122,7 +151,7 @@ def bench_ranking(args, cfg, rank, world, dev):
                                      "parallelism": f"doc-parallel dp{world}", "depth": cfg["depth"], "group_size": 100},
                           "e2e": {"value": fit_s / iters * 1000.0, "unit": "s/1000iter", "fit_seconds": fit_s,
                                   "fit_breakdown_s": {k: round(float(v), 4) for k, v in tm.items()}},
-                          "ndcg_first_last": [float(ndcg[0]), float(ndcg[-1])],
+                          "ndcg_first_last": [float(ndcg[0]), float(ndcg[-1])], "apply": apply,
                           "gpu_launches": int(model._train_info.get("launches_per_iter", 0)) * iters}))
     return 0
 

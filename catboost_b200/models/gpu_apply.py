@@ -51,22 +51,55 @@ class GpuPredictor:
                           "cb_predict_oblivious")
         return out
 
-    def predict(self, X: np.ndarray, chunk_rows: int = 1 << 22) -> np.ndarray:
+    def predict(self, X: np.ndarray, chunk_rows: int = 0) -> np.ndarray:
+        """Rows from host memory, in chunks through two pinned staging buffers and two streams: while one chunk is
+        copied to the device and evaluated, the host fills the other buffer, and results come back asynchronously."""
         X = np.ascontiguousarray(X, dtype=np.float32)
-        n = X.shape[0]
+        n, F = X.shape
         res = np.empty((n, self.dims), dtype=np.float64)
+        if n == 0:
+            return res
+        if chunk_rows <= 0:
+            chunk_rows = max(4096, min(n, (64 << 20) // max(F, 1)))          # about 256 MB of floats per buffer
         xt = torch.from_numpy(X)
         with torch.cuda.device(self.dev):
-            for r0 in range(0, n, chunk_rows):
+            nbuf = 2 if n > chunk_rows else 1
+            stage = [torch.empty((chunk_rows, F), dtype=torch.float32).pin_memory() for _ in range(nbuf)]
+            back = [torch.empty((self.dims, chunk_rows), dtype=torch.float32).pin_memory() for _ in range(nbuf)]
+            dbuf = [torch.empty((chunk_rows, F), dtype=torch.float32, device=self.dev) for _ in range(nbuf)]
+            dout = [torch.empty((self.dims, chunk_rows), dtype=torch.float32, device=self.dev) for _ in range(nbuf)]
+            streams = [torch.cuda.Stream(self.dev) for _ in range(nbuf)]
+            pending = [None] * nbuf                          # (event, r0, r1) of the chunk in flight on every buffer
+            cur = torch.cuda.current_stream(self.dev)
+            for st in streams:
+                st.wait_stream(cur)
+
+            def drain(k):
+                if pending[k] is not None:
+                    ev, r0, r1, h_out = pending[k]
+                    ev.synchronize()
+                    res[r0:r1] = h_out.t().numpy()
+                    pending[k] = None
+
+            for c, r0 in enumerate(range(0, n, chunk_rows)):
+                k = c % nbuf
                 r1 = min(n, r0 + chunk_rows)
-                src = xt[r0:r1]
-                try:
-                    src = src.pin_memory()
-                except RuntimeError:
-                    pass
-                d = src.to(self.dev, non_blocking=True)
-                o = self.predict_device(d)
-                res[r0:r1] = o.t().double().cpu().numpy()
+                m = r1 - r0
+                drain(k)
+                stage[k][:m].copy_(xt[r0:r1])
+                # a short last chunk uses the front of the buffers as a dense [dims, m] block
+                d_out = dout[k].view(-1)[: self.dims * m].view(self.dims, m)
+                h_out = back[k].view(-1)[: self.dims * m].view(self.dims, m)
+                with torch.cuda.stream(streams[k]):
+                    dbuf[k][:m].copy_(stage[k][:m], non_blocking=True)
+                    self.predict_device(dbuf[k][:m], d_out)
+                    h_out.copy_(d_out, non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(streams[k])
+                pending[k] = (ev, r0, r1, h_out)
+            for k in range(nbuf):
+                drain(k)
+            cur.wait_stream(streams[0])
         return res
 
 

@@ -407,3 +407,20 @@ def test_ctr_kernels_match_tensor_implementation(n, card, nb):
         assert torch.equal(x, y)
     sample = torch.arange(0, n, 7, device=dev)
     assert torch.equal(kg.sample_values(descs[-1], sample), tg.sample_values(descs[-1], sample))
+
+
+@pytest.mark.gpu
+def test_gpu_apply_streams_chunks_through_two_buffers():
+    """Host rows in several chunks (the last one short), three output dimensions."""
+    import catboost_b200 as cb
+    from catboost_b200.models.gpu_apply import GpuPredictor
+    rng = np.random.default_rng(4)
+    X = rng.standard_normal((4500, 9)).astype(np.float32)
+    y = np.digitize(X[:, 0] + 0.4 * X[:, 3], [-0.4, 0.5])
+    m = cb.CatBoostClassifier(iterations=25, depth=5, loss_function="MultiClass", verbose=False, allow_writing_files=False,
+                              task_type="CPU").fit(X, y)
+    want = m.predict(X, prediction_type="RawFormulaVal")
+    pred = GpuPredictor(m._model, "cuda:0")
+    for chunk in (1000, 4500, 7000):
+        got = pred.predict(X, chunk_rows=chunk)
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
