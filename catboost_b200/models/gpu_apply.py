@@ -2,7 +2,8 @@
 
 The reference's GPU evaluator quantises into an intermediate uchar4 buffer and evaluates in a second kernel
 (catboost/libs/model/cuda/evaluator.cu:85-343, float-only / oblivious / one-dimensional only).  Here one kernel
-(``cb_predict_kernel``) stages the bins of a 256-row tile in shared memory and walks all trees; models with up
+(``cb_predict_kernel``) stages the bins of a tile of rows in shared memory (32 features at a time, their borders in
+shared memory, a warp reading one row's values as one contiguous piece) and walks all trees; models with up
 to 8 output dimensions are supported.  Rows are streamed from pinned host memory in chunks so that any dataset
 size fits.
 """
@@ -31,6 +32,8 @@ class GpuPredictor:
         self.sfeat, self.sbin, self.loff = t(p["sfeat"]), t(p["sbin"]), t(p["loff"])
         self.vals = t(p["vals"], np.float32)
         self.T, self.dims, self.U = p["T"], model.dims, len(p["used"])
+        boff = np.asarray(p["boff"], dtype=np.int64)
+        self.max_borders = int(np.diff(boff).max()) if len(boff) > 1 else 1
         self.scale = float(model.scale)
         self.bias = t(np.broadcast_to(model.bias, (model.dims,)), np.float32)
         if self.dims > 8:
@@ -47,7 +50,7 @@ class GpuPredictor:
         native.cuda_check(self.lib.cb_predict_oblivious(P(X), n, X.stride(0), P(self.used), P(self.borders), P(self.boff),
                                                         P(self.nanmax), self.U, P(self.depth), P(self.soff),
                                                         P(self.sfeat), P(self.sbin), P(self.loff), P(self.vals), self.T,
-                                                        self.dims, self.scale, P(self.bias), P(out), st),
+                                                        self.dims, self.scale, P(self.bias), P(out), self.max_borders, st),
                           "cb_predict_oblivious")
         return out
 

@@ -779,6 +779,7 @@ struct CbPredictArgs {
     int T; int dims;
     float scale; const float* bias;   // [dims]
     float* out;                  // [dims][n]
+    int max_borders;             // largest border count of a used feature
 };
 
 // Four rows per thread (1024 rows per block): the split descriptors of a chunk of trees are staged in shared memory
@@ -787,29 +788,60 @@ struct CbPredictArgs {
 #define CB_PRED_CHUNK_SPLITS 3072
 template <int CB_PRED_ROWS>
 __global__ void __launch_bounds__(256) cb_predict_kernel(CbPredictArgs a) {
-    extern __shared__ unsigned char sb[];     // [U][1024] bins, then uint32 desc[CB_PRED_CHUNK_SPLITS]
+    // shared memory: bins [U][USTR] (USTR = 256 * rows per thread + 4: the pad keeps the byte writes of 32 features of
+    // one row in 32 different banks), split descriptors [CB_PRED_CHUNK_SPLITS], borders of 32 features [max_borders][32]
+    extern __shared__ unsigned char sb[];
     const int RB = 256 * CB_PRED_ROWS;
-    unsigned int* desc = reinterpret_cast<unsigned int*>(sb + (((size_t)a.U * RB + 15) & ~(size_t)15));
+    const int USTR = RB + 4;
+    unsigned int* desc = reinterpret_cast<unsigned int*>(sb + (((size_t)a.U * USTR + 15) & ~(size_t)15));
+    float* s_bd = reinterpret_cast<float*>(desc + CB_PRED_CHUNK_SPLITS);
     const long long row0 = (long long)blockIdx.x * RB;
     const int nrow = (int)min((long long)RB, a.n - row0);
-    // quantise: thread = row (4 of them), loop over features; rows are read with stride ldx, L1 absorbs the re-use
-    for (int u = 0; u < a.U; ++u) {
-        const int b0 = a.border_off[u], nbd = a.border_off[u + 1] - b0;
-        const float* bd = a.borders + b0;
-        const int col = a.used_feat[u];
-        const bool nmax = a.nan_is_max && a.nan_is_max[u];
-#pragma unroll
-        for (int r = 0; r < CB_PRED_ROWS; ++r) {
-            const int lr = r * 256 + threadIdx.x;
-            if (lr < nrow) {
-                const float v = a.X[(row0 + lr) * a.ldx + col];
-                int pos = 0;                       // borders < v, fixed power-of-two steps (no data-dependent trip count)
-#pragma unroll
-                for (int step = 128; step > 0; step >>= 1) {
-                    const int idx = pos + step;
-                    if (idx <= nbd && __ldg(bd + idx - 1) < v) pos = idx;
+    // quantise, 32 used features at a time: their borders go to shared memory transposed ([border][feature], so a
+    // lane's binary search never meets another lane's bank); then a warp takes one row at a time, lane = feature, so
+    // that the row's values are read as one contiguous piece when the model uses neighbouring columns
+    {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        const int mb = a.max_borders;
+        for (int c0 = 0; c0 < a.U; c0 += 32) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < mb * 32; i += blockDim.x) {
+                const int j = i >> 5, u = c0 + (i & 31);
+                float bv = __int_as_float(0x7f800000);                 // +inf: never below a value
+                if (u < a.U) {
+                    const int b0 = a.border_off[u];
+                    if (j < a.border_off[u + 1] - b0) bv = a.borders[b0 + j];
                 }
-                sb[(u * 256 + threadIdx.x) * CB_PRED_ROWS + r] = (unsigned char)((v != v) ? (nmax ? nbd : 0) : pos);
+                s_bd[i] = bv;
+            }
+            __syncthreads();
+            const int u = c0 + lane;
+            if (u < a.U) {
+                const int col = a.used_feat[u];
+                const int nbd = a.border_off[u + 1] - a.border_off[u];
+                const bool nmax = a.nan_is_max && a.nan_is_max[u];
+                unsigned char* dst = sb + (size_t)u * USTR;
+                // four rows per step: their loads are issued together, the searches run while later loads land
+                for (int lr0 = warp; lr0 < nrow; lr0 += 32) {
+                    float v[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int lr = lr0 + 8 * q;
+                        v[q] = lr < nrow ? a.X[(row0 + lr) * a.ldx + col] : 0.0f;
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int lr = lr0 + 8 * q;
+                        if (lr >= nrow) break;
+                        int pos = 0;               // borders < v, fixed power-of-two steps
+#pragma unroll
+                        for (int step = 128; step > 0; step >>= 1) {
+                            const int idx = pos + step;
+                            if (idx <= mb && s_bd[((idx - 1) << 5) + lane] < v[q]) pos = idx;
+                        }
+                        dst[(lr & 255) * CB_PRED_ROWS + (lr >> 8)] = (unsigned char)((v[q] != v[q]) ? (nmax ? nbd : 0) : pos);
+                    }
+                }
             }
         }
     }
@@ -840,10 +872,9 @@ __global__ void __launch_bounds__(256) cb_predict_kernel(CbPredictArgs a) {
             if (CB_PRED_ROWS == 4 && depth <= 8) {
                 // the bins of the thread's four rows sit in one word: one per-byte compare decides all four rows
                 unsigned int leaf4 = 0u;
-                const unsigned int* words = reinterpret_cast<const unsigned int*>(sb) + threadIdx.x;
                 for (int k = 0; k < depth; ++k) {
                     const unsigned int d = dsc[k];
-                    const unsigned int w = words[(d >> 8) * 256];
+                    const unsigned int w = reinterpret_cast<const unsigned int*>(sb + (size_t)(d >> 8) * USTR)[threadIdx.x];
                     const unsigned int m = __vcmpgtu4(w, __byte_perm(d, 0, 0x0000));
                     leaf4 |= (m & 0x01010101u) << k;
                 }
@@ -854,7 +885,7 @@ __global__ void __launch_bounds__(256) cb_predict_kernel(CbPredictArgs a) {
                 for (int r = 0; r < CB_PRED_ROWS; ++r) leaf[r] = 0;
                 for (int k = 0; k < depth; ++k) {
                     const unsigned int d = dsc[k];
-                    const unsigned char* col = sb + ((d >> 8) * 256 + threadIdx.x) * CB_PRED_ROWS;
+                    const unsigned char* col = sb + (size_t)(d >> 8) * USTR + threadIdx.x * CB_PRED_ROWS;
                     const unsigned int thr = d & 255u;
 #pragma unroll
                     for (int r = 0; r < CB_PRED_ROWS; ++r) leaf[r] |= ((unsigned int)col[r] > thr) << k;
@@ -882,22 +913,27 @@ CB_API int cb_predict_oblivious(const float* X, long long n, long long ldx, cons
                                 const int* border_off, const unsigned char* nan_is_max, int U, const int* tree_depth,
                                 const int* tree_split_off, const unsigned short* split_feat,
                                 const unsigned char* split_bin, const long long* tree_leaf_off, const float* leaf_vals,
-                                int T, int dims, float scale, const float* bias, float* out, cudaStream_t st) {
+                                int T, int dims, float scale, const float* bias, float* out, int max_borders,
+                                cudaStream_t st) {
     if (n <= 0) return 0;
+    if (max_borders < 1) max_borders = 1;
+    if (max_borders > 255) return (int)cudaErrorInvalidValue;
     // four rows per thread when the bins of 1024 rows fit in shared memory, else one row per thread
+    const size_t CB_PRED_SMEM_MAX = 224 * 1024;
+    const size_t fixed = CB_PRED_CHUNK_SPLITS * 4 + (size_t)max_borders * 32 * sizeof(float);
     int rows = 4;
-    size_t pred_smem = (((size_t)U * 256 * rows + 15) & ~(size_t)15) + CB_PRED_CHUNK_SPLITS * 4;
-    if (pred_smem > 200 * 1024) {
+    size_t pred_smem = (((size_t)U * (256 * rows + 4) + 15) & ~(size_t)15) + fixed;
+    if (pred_smem > CB_PRED_SMEM_MAX) {
         rows = 1;
-        pred_smem = (((size_t)U * 256 + 15) & ~(size_t)15) + CB_PRED_CHUNK_SPLITS * 4;
+        pred_smem = (((size_t)U * (256 + 4) + 15) & ~(size_t)15) + fixed;
     }
-    if (dims > 8 || pred_smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    if (dims > 8 || pred_smem > CB_PRED_SMEM_MAX) return (int)cudaErrorInvalidValue;
     CbPredictArgs a{X, n, ldx, used_feat, borders, border_off, nan_is_max, U, tree_depth, tree_split_off, split_feat,
-                    split_bin, tree_leaf_off, leaf_vals, T, dims, scale, bias, out};
+                    split_bin, tree_leaf_off, leaf_vals, T, dims, scale, bias, out, max_borders};
     static int set = 0;
     if (!set) {
-        cudaError_t e = cudaFuncSetAttribute(cb_predict_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_predict_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(cb_predict_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CB_PRED_SMEM_MAX);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_predict_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CB_PRED_SMEM_MAX);
         if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
         set = 1;
     }

@@ -185,7 +185,7 @@ _SIGS = {
     "cb_leaf_index": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "cb_predict_oblivious": (c_int, [c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
-                                     c_void_p, c_void_p]),
+                                     c_void_p, c_int, c_void_p]),
     "cb_metric_sum": (c_int, [c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
                              c_int, c_void_p]),
     "cb_device_info": (c_int, [c_void_p, c_void_p]),
