@@ -172,6 +172,27 @@ def main(argv=None):
         ms = _time(lambda: pred.predict_device(xd, res), args.reps, flush)
         report("cb_predict_kernel", ms, n * F * 4 + n * 4, f"{args.trees} trees depth {args.depth}; "
                f"{n / (ms * 1e-3):.3g} rows/s, {n * args.trees / (ms * 1e-3):.3g} tree-rows/s")
+    if want("ctr"):
+        # one categorical projection of Zipf-distributed values: the three CTR kernels after the (library) sort
+        g = torch.Generator().manual_seed(1)
+        card = 100_000
+        h = (torch.rand(n, generator=g) ** 3 * card).long().to(dev) * 2654435761 - (1 << 40)
+        order = torch.randperm(n, generator=g).to(dev)
+        cls = torch.from_numpy((y > 0.5).astype(np.uint8)).to(dev)
+        sorted_h, srt = torch.sort(h[order], stable=True)
+        rows = order[srt]
+        ms = _time(lambda: ops.ctr_scan(sorted_h, rows, cls, [0]), args.reps, flush)
+        # reads: hash 8 + row id 8 + class 1 (gathered); writes: two prefix columns 8 + group number 4 + flag 1, read again
+        # and rewritten by the fix-up pass
+        report("cb_ctr_scan (3 launches)", ms, n * (8 + 8 + 1 + 13 + 8 + 13 + 12), "segmented scans of count + one indicator")
+        excl, seg_id, uniq, totals = ops.ctr_scan(sorted_h, rows, cls, [0])
+        descs = [(0, 1, 0.0, 1.0, 1.0), (0, 1, 0.5, 1.0, 1.0), (0, 1, 1.0, 1.0, 1.0),
+                 (1, 0, 0.0, 1.0, float(totals[0].max().item()) + 1.0)]
+        ms = _time(lambda: ops.ctr_minmax(descs[:3], excl, totals, seg_id), args.reps, flush)
+        report("cb_ctr_minmax_kernel", ms, n * 8, "range of three target-statistic CTRs")
+        borders = [np.linspace(0.02, 0.98, 15).astype(np.float32) for _ in descs]
+        ms = _time(lambda: ops.ctr_binarize(descs, borders, excl, totals, seg_id, rows, 0, n), args.reps, flush)
+        report("cb_ctr_binarize_kernel", ms, n * (8 + 4 + 8 + 4 * 1), "four CTRs -> bytes in document order (scattered)")
     return 0
 
 
