@@ -848,6 +848,35 @@ __device__ __forceinline__ float cb_score_load(const CbScoreArgs& a, int l, int 
     return x;
 }
 
+// The same for the up to 8 bins a lane owns (bins lane * bpl + k), with every load issued before the first use.  Used
+// when a warp walks many leaves of one feature: there the chain of dependent L2 round trips is what the warp waits for,
+// and the longer code is fetched once and reused for every leaf.
+__device__ __forceinline__ void cb_score_load8(const CbScoreArgs& a, int l, int p, bool computed, int st, int col0,
+                                               int lane, int bpl, int nb, float* x) {
+    const size_t base = ((size_t)p * a.S + st) * a.W + col0 + lane * bpl;
+    const int left = nb - lane * bpl;                  // bins of this lane that exist
+    float prev[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const bool ok = k < bpl && k < left;
+        x[k] = ok ? __ldcg(a.hsrc[0] + base + k) : 0.0f;
+        prev[k] = (ok && !computed) ? a.hprev[base + k] : 0.0f;
+    }
+    for (int r = 1; r < a.nsrc; ++r) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (k < bpl && k < left) x[k] += __ldcg(a.hsrc[r] + base + k);
+    }
+    const size_t obase = ((size_t)l * a.S + st) * a.W + col0 + lane * bpl;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        if (k < bpl && k < left) {
+            if (!computed) x[k] = prev[k] - x[k];
+            if (a.hcur) a.hcur[obase + k] = x[k];
+        }
+    }
+}
+
 // Score terms of feature f accumulated over the leaves l0, l0 + lstep, ... into sc[0..255] (num) and sc[256..511]
 // (den); sc[512..] is scratch.  One warp.
 static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, int lstep, float* sc) {
@@ -865,6 +894,7 @@ static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, 
     float* ps = sc + 768;
     for (int b = lane; b < 512; b += 32) sc[b] = 0.0f;
     __syncwarp();
+    const bool batched = (L / lstep) >= 4 && bpl <= 8;       // several leaves per warp: overlap the loads of a leaf
     for (int l = l0; l < L; l += lstep) {
         int p = 0;
         bool computed = true;
@@ -882,11 +912,23 @@ static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, 
             // (Issuing all loads of the leaf first in an unrolled loop was measured slower: more instruction lines to
             // fetch cost more than the overlapped load latency saved.)
             float run = 0.0f;
-            for (int k = 0; k < bpl; ++k) {
-                const int bin = lane * bpl + k;
-                const float x = cb_score_load(a, l, p, computed, c_st, col0, bin, nb);
-                run += x;
-                pre[bin] = onehot ? x : run;
+            if (batched) {
+                float x8[8];
+                cb_score_load8(a, l, p, computed, c_st, col0, lane, bpl, nb, x8);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (k < bpl) {
+                        run += x8[k];
+                        pre[lane * bpl + k] = onehot ? x8[k] : run;
+                    }
+                }
+            } else {
+                for (int k = 0; k < bpl; ++k) {
+                    const int bin = lane * bpl + k;
+                    const float x = cb_score_load(a, l, p, computed, c_st, col0, bin, nb);
+                    run += x;
+                    pre[bin] = onehot ? x : run;
+                }
             }
             float inc = run;
             for (int o = 1; o < 32; o <<= 1) {
