@@ -164,7 +164,7 @@ def bench_criteo(args, cfg, rank, world, dev):
     iters = args.e2e_iters if args.e2e_iters > 0 else max(args.steps + args.warmup, 50)
     model = cb.CatBoostClassifier(loss_function="Logloss", iterations=iters, depth=cfg["depth"], border_count=cfg["border_count"],
                                   learning_rate=0.1, task_type="GPU", random_seed=0, allow_writing_files=False,
-                                  max_ctr_complexity=1, verbose=False)
+                                  max_ctr_complexity=int(args.ctr_complexity), verbose=False)
     torch.cuda.synchronize(dev)
     t0 = time.perf_counter()
     model.fit(df, y, cat_features=cats)
@@ -179,7 +179,7 @@ def bench_criteo(args, cfg, rank, world, dev):
                           "data": "synthetic", "impl": "ours",
                           "config": {"model": cfg["model"], "global_batch": cfg["rows"], "seq_len": 39,
                                      "parallelism": f"doc-parallel dp{world}", "depth": cfg["depth"],
-                                     "ctr": "simple_ctr defaults, max_ctr_complexity=1",
+                                     "ctr": f"simple_ctr defaults, max_ctr_complexity={int(args.ctr_complexity)}",
                                      "note": "auxiliary config; the named size is 45M rows (--rows 45000000)"},
                           "e2e": {"value": fit_s / iters * 1000.0, "unit": "s/1000iter", "fit_seconds": fit_s,
                                   "fit_breakdown_s": {k: round(float(v), 4) for k, v in tm.items()}},
@@ -267,6 +267,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-iters", type=int, default=0,
                     help="boosting iterations of the end-to-end fit() (default 1000: the metric's own iteration count)")
+    ap.add_argument("--ctr-complexity", type=int, default=1, help="max_ctr_complexity of the categorical config")
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--phases", action="store_true", help="print per-phase times of the fused level kernel")
     args = ap.parse_args()
