@@ -96,11 +96,17 @@ def bench_ranking(args, cfg, rank, world, dev):
     import catboost_b200 as cb
     n, F = cfg["rows"] // world, cfg["features"]
     rng = np.random.default_rng(17 + rank)
-    X = rng.standard_normal((n, F), dtype=np.float32)
+    # 60 % exact zeros, the rest U(0, 1); queries of 5 .. 200 documents; relevance 0 .. 4 from quantiles of a latent
+    # linear score plus noise
+    X = rng.random((n, F), dtype=np.float32)
+    for r0 in range(0, n, 250_000):
+        blk = X[r0:r0 + 250_000]
+        blk[rng.random(blk.shape, dtype=np.float32) < 0.6] = 0.0
     wv = np.random.default_rng(3).standard_normal(F).astype(np.float32) / np.sqrt(F)
-    score = X @ wv + 0.5 * rng.standard_normal(n, dtype=np.float32)
+    score = X @ wv + 0.15 * rng.standard_normal(n, dtype=np.float32)
     rel = np.digitize(score, np.quantile(score[: min(n, 200000)], [0.5, 0.8, 0.93, 0.98])).astype(np.float32)
-    gid = np.arange(n) // 100
+    sizes = rng.integers(5, 201, size=n // 5 + 1)
+    gid = np.repeat(np.arange(len(sizes)), sizes)[:n]
     iters = args.e2e_iters if args.e2e_iters > 0 else max(args.steps + args.warmup, 50)
     model = cb.CatBoostRanker(loss_function="YetiRank", iterations=iters, depth=cfg["depth"], border_count=cfg["border_count"],
                               learning_rate=0.1, task_type="GPU", random_seed=0, allow_writing_files=False, verbose=False)
@@ -140,7 +146,8 @@ def bench_ranking(args, cfg, rank, world, dev):
                  "tree_rows_per_s": n_dev * reps * iters / dev_s, "host_rows": n_host, "host_rows_per_s": n_host / host_s,
                  "note": "device: 100M rows as repeated passes over 1M resident rows; host: predict() from pageable memory"}
         del Xd, out
-    ev_pool = cb.Pool(X[:200000], rel[:200000], group_id=gid[:200000])
+    n_ev = int(np.searchsorted(gid, gid[min(n, 200000) - 1]))           # whole queries only
+    ev_pool = cb.Pool(X[:n_ev], rel[:n_ev], group_id=gid[:n_ev])
     ndcg = [model.eval_metrics(ev_pool, ["NDCG"], ntree_end=1)["NDCG"][-1], model.eval_metrics(ev_pool, ["NDCG"], eval_period=iters)["NDCG"][-1]]
     if rank == 0:
         print(json.dumps({"metric": "sec/1000 iters (wall time of the iterations phase of fit())", "value": it_s / iters * 1000.0,
@@ -148,7 +155,7 @@ def bench_ranking(args, cfg, rank, world, dev):
                           "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "fp32",
                           "data": "synthetic", "impl": "ours",
                           "config": {"model": cfg["model"], "global_batch": cfg["rows"], "seq_len": F,
-                                     "parallelism": f"doc-parallel dp{world}", "depth": cfg["depth"], "group_size": 100},
+                                     "parallelism": f"doc-parallel dp{world}", "depth": cfg["depth"], "group_size": "uniform 5..200"},
                           "e2e": {"value": fit_s / iters * 1000.0, "unit": "s/1000iter", "fit_seconds": fit_s,
                                   "fit_breakdown_s": {k: round(float(v), 4) for k, v in tm.items()}},
                           "ndcg_first_last": [float(ndcg[0]), float(ndcg[-1])], "apply": apply,
