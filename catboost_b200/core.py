@@ -140,6 +140,7 @@ class CatBoost:
         self._best_iteration = res.best_iteration
         self._best_score = res.best_score
         self._train_info = dict(timings=res.timings, h2d_bytes=res.h2d_bytes, launches_per_iter=res.launches_per_iter)
+        self._eval_pools = list(eval_pools)
         return self
 
     # ------------------------------------------------------------------ predict
@@ -361,6 +362,123 @@ class CatBoost:
             out[idx] = float(np.mean(m.predict_raw(work, ch)[:, 0]))
         return out, None
 
+    # ------------------------------------------------------------------ uncertainty
+    def virtual_ensembles_predict(self, data, prediction_type="VirtEnsembles", ntree_end=0, virtual_ensembles_count=10,
+                                  thread_count=-1, verbose=None):
+        """Predictions of ``virtual_ensembles_count`` truncated sub-models (catboost/private/libs/algo/apply.cpp:526-606):
+        with T trees and period = T // (2 K), ensemble k is the model cut after ``T - (K - 1 - k) * period`` trees.
+        ``VirtEnsembles`` returns [documents, K, dimensions]; ``TotalUncertainty`` returns per document
+        [mean, knowledge uncertainty] for regression, [mean, knowledge, data uncertainty] for RMSEWithUncertainty and
+        [data uncertainty, total uncertainty] for classification."""
+        self._check_fitted()
+        if prediction_type not in ("VirtEnsembles", "TotalUncertainty"):
+            raise CatBoostError("prediction_type must be 'VirtEnsembles' or 'TotalUncertainty'")
+        m = self._model
+        T = len(m.trees)
+        end = T if not ntree_end or ntree_end > T else int(ntree_end)
+        K = int(virtual_ensembles_count)
+        period = end // (2 * K) if K > 0 else 0
+        if period <= 0 or period * K >= end:
+            raise CatBoostError(f"Not enough trees in model for {K} virtual Ensembles")
+        pool = data if isinstance(data, Pool) else Pool(data, **self._pool_kwargs())
+        fd, ch = m.pool_arrays(pool)
+        begin = end - period * K
+        acc = m.predict_raw(fd, ch, 0, begin)
+        ens = []
+        for k in range(K):
+            lo = begin + k * period
+            part = m.predict_raw(fd, ch, lo, lo + period) - np.broadcast_to(m.bias, (m.dims,))
+            acc = acc + part
+            ens.append(acc.copy())
+        ens = np.stack(ens, axis=1)                                        # [n, K, dims]
+        loss = m.loss_name
+        if loss == "RMSEWithUncertainty":
+            ens = ens.copy()
+            ens[:, :, 1] = np.exp(2.0 * ens[:, :, 1])
+        if prediction_type == "VirtEnsembles":
+            return ens
+        if loss == "RMSEWithUncertainty":
+            return np.stack([ens[:, :, 0].mean(1), ens[:, :, 0].var(1), ens[:, :, 1].mean(1)], axis=1)
+        if m.class_names is None:
+            return np.stack([ens[:, :, 0].mean(1), ens[:, :, 0].var(1)], axis=1)
+
+        def entropy(p):
+            return -(p * np.log(np.clip(p, 1e-300, None))).sum(-1)
+        if m.dims == 1:
+            p1 = _sigmoid(ens[:, :, 0])
+            probs = np.stack([1 - p1, p1], axis=-1)
+        else:
+            e = np.exp(ens - ens.max(-1, keepdims=True))
+            probs = e / e.sum(-1, keepdims=True)
+        return np.stack([entropy(probs).mean(1), entropy(probs.mean(1))], axis=1)
+
+    def iterate_leaf_indexes(self, data, ntree_start=0, ntree_end=0):
+        """Generator over documents: the leaf index of every tree."""
+        for row in self.calc_leaf_indexes(data, ntree_start, ntree_end):
+            yield row
+
+    def set_leaf_values(self, new_leaf_values):
+        """Replace all leaf values (flat: trees in order, leaves in order, dimensions innermost)."""
+        self._check_fitted()
+        vals = np.asarray(new_leaf_values, dtype=np.float64).reshape(-1)
+        total = sum(t.leaf_values.size for t in self._model.trees)
+        if len(vals) != total:
+            raise CatBoostError(f"expected {total} leaf values, got {len(vals)}")
+        pos = 0
+        for t in self._model.trees:
+            k = t.leaf_values.size
+            t.leaf_values = vals[pos:pos + k].reshape(t.leaf_values.shape).copy()
+            pos += k
+        self._model.__dict__.pop("_gpu_predictor", None)
+        self._model.__dict__.pop("_packed", None)
+
+    def set_feature_names(self, feature_names):
+        self._check_fitted()
+        names = [str(x) for x in feature_names]
+        if len(names) != self._model.n_features:
+            raise CatBoostError("feature_names length does not match the number of features of the model")
+        self._model.feature_names = names
+        for f in self._model.float_features:
+            f.name = names[f.flat_index]
+        for c in self._model.cat_features:
+            c.name = names[c.flat_index]
+
+    def get_metadata(self):
+        """Key-value strings stored in the model file (a live dict: assignments are saved with the model)."""
+        self._check_fitted()
+        return self._model.info
+
+    def get_n_features_in(self):
+        self._check_fitted()
+        return int(self._model.n_features)
+
+    def get_text_feature_indices(self):
+        est = getattr(self._model, "estimators", None) if self._model is not None else None
+        return list(getattr(est, "text_indices", []) or []) if est is not None else []
+
+    def get_embedding_feature_indices(self):
+        est = getattr(self._model, "estimators", None) if self._model is not None else None
+        return list(getattr(est, "embedding_indices", []) or []) if est is not None else []
+
+    def save_borders(self, fname):
+        """Borders of the numerical features as ``feature index<TAB>border`` lines (the input_borders format)."""
+        self._check_fitted()
+        with open(fname, "w") as fh:
+            for f in self._model.float_features:
+                for b in f.borders:
+                    fh.write(f"{f.flat_index}\t{float(b)!r}\n")
+
+    def get_test_eval(self):
+        """Raw predictions on the single evaluation set of the last fit."""
+        evs = self.get_test_evals()
+        if len(evs) != 1:
+            raise CatBoostError("the model was fitted with %d evaluation sets: use get_test_evals" % len(evs))
+        return evs[0]
+
+    def get_test_evals(self):
+        self._check_fitted()
+        return [self._raw(p) for p in getattr(self, "_eval_pools", [])]
+
     def get_object_importance(self, pool, train_pool, top_size=-1, type="Average", update_method="SinglePoint",
                               importance_values_sign="All", thread_count=-1, verbose=False, ostr_type=None,
                               log_cout=None, log_cerr=None):
@@ -489,12 +607,102 @@ class CatBoost:
 
     def __getstate__(self):
         st = dict(self.__dict__)
+        st.pop("_eval_pools", None)
         if self._model is not None:
             m = self._model.copy()
             for k in ("_gpu_predictor", "_packed", "_split_cache"):
                 m.__dict__.pop(k, None)
             st["_model"] = m
         return st
+
+    def calc_feature_statistics(self, data, target=None, feature=None, prediction_type=None, cat_feature_values=None,
+                                plot=False, max_cat_features_on_plot=10, thread_count=-1, plot_file=None):
+        """Per-bucket statistics of numerical features (catboost/python-package/catboost/core.py
+        ``calc_feature_statistics``): borders, the bucket of every object, mean target, mean prediction, objects per
+        bucket, and the mean prediction when the feature of every object is moved into each bucket.  Returns the dict of
+        one feature, or {feature: dict} for a list of features; nothing is drawn."""
+        self._check_fitted()
+        pool = data if isinstance(data, Pool) else Pool(data, target, **self._pool_kwargs())
+        y = pool.label if target is None else np.asarray(target)
+        if y is None:
+            raise CatBoostError("calc_feature_statistics needs the target")
+        y = np.asarray(self._encode_labels(y), dtype=np.float64).reshape(len(y), -1)[:, 0]
+        m = self._model
+        if prediction_type is None:
+            prediction_type = "Probability" if m.class_names is not None and m.dims == 1 else "RawFormulaVal"
+
+        def pred_of(raw):
+            out = self._format(raw, prediction_type)
+            out = np.asarray(out, dtype=np.float64)
+            return out[:, -1] if out.ndim == 2 else out
+        feats = [feature] if isinstance(feature, (int, str, np.integer)) else list(feature if feature is not None else
+                                                                                  [f.flat_index for f in m.float_features])
+        fd, ch = m.pool_arrays(pool)
+        base_pred = pred_of(m.predict_raw(fd, ch))
+        res = {}
+        for f in feats:
+            c = pool.feature_names.index(f) if isinstance(f, str) else int(f)
+            ff = next((x for x in m.float_features if x.flat_index == c), None)
+            if ff is None:
+                raise CatBoostError("feature statistics are computed for numerical features of the model")
+            col = m.float_features.index(ff)
+            borders = np.asarray(ff.borders, dtype=np.float32)
+            bins = np.searchsorted(borders, fd[:, col], side="left").astype(np.int64)
+            nb = len(borders) + 1
+            cnt = np.bincount(bins, minlength=nb).astype(np.float64)
+            safe = np.maximum(cnt, 1.0)
+            w = pool.weight if pool.weight is not None else np.ones(len(y))
+            wsum = np.bincount(bins, weights=w, minlength=nb)
+            grid = np.concatenate([[borders[0] - 1.0], (borders[:-1] + borders[1:]) / 2.0, [borders[-1] + 1.0]]) \
+                if len(borders) else np.array([0.0])
+            varying = np.zeros(nb)
+            work = np.array(fd, dtype=np.float32, copy=True)
+            for j in range(nb):
+                work[:, col] = grid[j]
+                varying[j] = float(np.mean(pred_of(m.predict_raw(work, ch))))
+            res[f] = {"borders": borders, "binarized_feature": bins,
+                      "mean_target": np.bincount(bins, weights=y, minlength=nb) / safe,
+                      "mean_weighted_target": np.bincount(bins, weights=y * w, minlength=nb) / np.maximum(wsum, 1e-300),
+                      "mean_prediction": np.bincount(bins, weights=base_pred, minlength=nb) / safe,
+                      "objects_per_bin": cnt.astype(np.int64), "predictions_on_varying_feature": varying}
+        return res[feats[0]] if isinstance(feature, (int, str, np.integer)) else res
+
+    def compare(self, model, data, metrics, ntree_start=0, ntree_end=0, eval_period=1, thread_count=-1, tmp_dir=None,
+                log_cout=None, log_cerr=None):
+        """Metric curves of this model and of ``model`` on the same data: {metric: (own values, other values)}.
+        (The reference draws them in a notebook widget.)"""
+        a = self.eval_metrics(data, metrics, ntree_start, ntree_end, eval_period)
+        b = model.eval_metrics(data, metrics, ntree_start, ntree_end, eval_period)
+        return {k: (a[k], b[k]) for k in a}
+
+    def create_metric_calcer(self, metrics, ntree_start=0, ntree_end=0, eval_period=1, thread_count=-1, tmp_dir=None):
+        """Metric values over several batches of data: ``add(pool)`` any number of times, then ``eval_metrics()``."""
+        self._check_fitted()
+        return _BatchMetricCalcer(self, metrics, ntree_start, ntree_end, eval_period)
+
+    def plot_predictions(self, data, features_to_change, plot=False, plot_file=None):
+        """Predictions of every object of ``data`` while one numerical feature takes each bucket of its grid.
+        Returns ({feature: array [objects, buckets]}, None); nothing is drawn."""
+        self._check_fitted()
+        pool = data if isinstance(data, Pool) else Pool(data, **self._pool_kwargs())
+        m = self._model
+        fd, ch = m.pool_arrays(pool)
+        out = {}
+        for f in features_to_change:
+            c = pool.feature_names.index(f) if isinstance(f, str) else int(f)
+            ff = next((x for x in m.float_features if x.flat_index == c), None)
+            if ff is None:
+                raise CatBoostError("plot_predictions varies numerical features of the model")
+            col = m.float_features.index(ff)
+            b = np.asarray(ff.borders, dtype=np.float64)
+            grid = np.concatenate([[b[0] - 1.0], (b[:-1] + b[1:]) / 2.0, [b[-1] + 1.0]]) if len(b) else np.array([0.0])
+            vals = np.zeros((fd.shape[0], len(grid)))
+            work = np.array(fd, dtype=np.float32, copy=True)
+            for j, g in enumerate(grid):
+                work[:, col] = g
+                vals[:, j] = m.predict_raw(work, ch)[:, 0]
+            out[f] = vals
+        return out, None
 
     def plot_tree(self, tree_idx=0, pool=None):
         raise CatBoostError("plot_tree needs graphviz, which is not available in this build")
@@ -617,3 +825,37 @@ def to_ranker(model):
     out = CatBoostRanker()
     out.__dict__.update(copy.deepcopy(model.__dict__))
     return out
+
+
+class _BatchMetricCalcer:
+    """Collects raw staged predictions and targets of several batches; evaluates the metrics over all of them."""
+
+    def __init__(self, model, metrics, ntree_start, ntree_end, eval_period):
+        self.model, self.metrics = model, [metrics] if isinstance(metrics, str) else list(metrics)
+        self.range = (ntree_start, ntree_end, max(1, int(eval_period)))
+        self.stages, self.labels, self.weights = None, [], []
+
+    def add(self, pool):
+        if not isinstance(pool, Pool) or pool.label is None:
+            raise CatBoostError("add() needs a Pool with labels")
+        m = self.model._model
+        fd, ch = m.pool_arrays(pool)
+        staged = list(m.staged_raw(fd, ch, self.range[0], self.range[1], self.range[2]))
+        if self.stages is None:
+            self.stages = [[s.copy()] for s in staged]
+        else:
+            for acc, s in zip(self.stages, staged):
+                acc.append(s.copy())
+        self.labels.append(np.asarray(self.model._encode_labels(pool.label)))
+        self.weights.append(np.ones(pool.num_row()) if pool.weight is None else np.asarray(pool.weight, dtype=np.float64))
+
+    def eval_metrics(self):
+        from .metrics import make_metric
+        if self.stages is None:
+            raise CatBoostError("no data was added")
+        y, w = np.concatenate(self.labels), np.concatenate(self.weights)
+        out = {}
+        for name in self.metrics:
+            mt = make_metric(name)
+            out[str(mt)] = [mt.eval(np.concatenate(parts), y, w) for parts in self.stages]
+        return out

@@ -436,6 +436,50 @@ class Pool:
         self.group_weight = self._prep_vec(group_weight, self.num_row(), "group_weight")
         self.weight = self.group_weight
 
+    def set_timestamp(self, timestamp):
+        ts = np.asarray(timestamp)
+        if len(ts) != self.num_row():
+            raise CatBoostError("timestamp length does not match the number of rows")
+        self.timestamp = ts
+
+    def train_eval_split(self, has_time=False, is_classification=False, eval_fraction=0.2, save_eval_pool=True,
+                         random_seed=0):
+        """(train pool, eval pool): the last ``eval_fraction`` of the rows when ``has_time`` (or of the time order given
+        by ``timestamp``), a random subset otherwise; whole query groups stay together; stratified by label for
+        classification."""
+        n = self.num_row()
+        if not 0.0 < eval_fraction < 1.0:
+            raise CatBoostError("eval_fraction must be inside (0, 1)")
+        rng = np.random.default_rng(random_seed)
+        if self.group_id is not None:
+            off = self.group_offsets()
+            g = np.arange(len(off) - 1)
+            if not has_time:
+                rng.shuffle(g)
+            k = max(1, int(round(len(g) * eval_fraction)))
+            ev_groups = np.sort(g[-k:])
+            is_eval = np.zeros(n, dtype=bool)
+            for q in ev_groups:
+                is_eval[off[q]:off[q + 1]] = True
+        else:
+            if has_time:
+                order = np.argsort(self.timestamp, kind="stable") if self.timestamp is not None else np.arange(n)
+                k = max(1, int(round(n * eval_fraction)))
+                is_eval = np.zeros(n, dtype=bool)
+                is_eval[order[-k:]] = True
+            elif is_classification and self.label is not None:
+                is_eval = np.zeros(n, dtype=bool)
+                lab = np.asarray(self.label).reshape(n, -1)[:, 0]
+                for c in np.unique(lab):
+                    idx = np.nonzero(lab == c)[0]
+                    rng.shuffle(idx)
+                    is_eval[idx[: max(1, int(round(len(idx) * eval_fraction)))]] = True
+            else:
+                is_eval = np.zeros(n, dtype=bool)
+                is_eval[rng.permutation(n)[: max(1, int(round(n * eval_fraction)))]] = True
+        train = self.slice(np.nonzero(~is_eval)[0])
+        return train, (self.slice(np.nonzero(is_eval)[0]) if save_eval_pool else None)
+
     def set_pairs(self, pairs, pairs_weight=None):
         p = np.asarray(pairs, dtype=np.int64).reshape(-1, 2)
         if p.size and (p.min() < 0 or p.max() >= self.num_row()):

@@ -641,3 +641,62 @@ def test_utils_module(tmp_path):
     assert isinstance(utils.get_gpu_device_count(), int)
     onx = utils.convert_to_onnx_object(m)
     assert onx is not None
+
+
+def test_remaining_public_methods(tmp_path):
+    rng = np.random.default_rng(8)
+    X = rng.standard_normal((900, 4)).astype(np.float32)
+    y = (X[:, 0] - 0.5 * X[:, 2] + 0.2 * rng.standard_normal(900)).astype(np.float32)
+    m = cb.CatBoostRegressor(iterations=40, depth=3, learning_rate=0.2, verbose=False, allow_writing_files=False,
+                             border_count=12).fit(X[:700], y[:700], eval_set=(X[700:], y[700:]))
+    # virtual ensembles: the last one is the whole model; uncertainty columns
+    ve = m.virtual_ensembles_predict(X[:50], virtual_ensembles_count=5)
+    assert ve.shape == (50, 5, 1)
+    np.testing.assert_allclose(ve[:, -1, 0], m.predict(X[:50]), rtol=1e-6, atol=1e-8)
+    T = m.tree_count_
+    np.testing.assert_allclose(ve[:, 0, 0], m.predict(X[:50], ntree_end=T - 4 * (T // 10)), rtol=1e-6, atol=1e-8)
+    tu = m.virtual_ensembles_predict(X[:50], prediction_type="TotalUncertainty", virtual_ensembles_count=5)
+    assert tu.shape == (50, 2) and np.all(tu[:, 1] >= 0)
+    with pytest.raises(cb.CatBoostError):
+        m.virtual_ensembles_predict(X[:5], virtual_ensembles_count=40)
+    clf = cb.CatBoostClassifier(iterations=20, depth=3, verbose=False, allow_writing_files=False).fit(X, (y > 0).astype(int))
+    cu = clf.virtual_ensembles_predict(X[:30], prediction_type="TotalUncertainty", virtual_ensembles_count=4)
+    assert cu.shape == (30, 2) and np.all(cu[:, 1] + 1e-12 >= cu[:, 0])          # total >= data uncertainty
+    # evaluation-set predictions, leaf iteration, metadata, names, borders
+    np.testing.assert_allclose(m.get_test_eval()[:, 0], m.predict(X[700:]), rtol=1e-6)
+    rows = list(m.iterate_leaf_indexes(X[:3]))
+    assert len(rows) == 3 and len(rows[0]) == T
+    assert m.get_n_features_in() == 4 and m.get_text_feature_indices() == [] and isinstance(m.get_metadata(), dict)
+    m.set_feature_names(["a", "b", "c", "d"])
+    assert m.feature_names_ == ["a", "b", "c", "d"]
+    m.save_borders(str(tmp_path / "borders.tsv"))
+    assert len((tmp_path / "borders.tsv").read_text().splitlines()) == sum(len(f.borders) for f in m._model.float_features)
+    # leaf values can be replaced as a flat vector
+    before = m.predict(X[:20])
+    flat = np.concatenate([t.leaf_values.reshape(-1) for t in m._model.trees])
+    m.set_leaf_values(flat * 2.0)
+    bias = float(np.ravel(m._model.bias)[0])
+    np.testing.assert_allclose(m.predict(X[:20]) - bias, 2.0 * (before - bias), rtol=1e-6, atol=1e-8)
+    m.set_leaf_values(flat)
+    # feature statistics, prediction curves, model comparison, batched metrics
+    st = m.calc_feature_statistics(X, y, feature=0)
+    nb = len(st["borders"]) + 1
+    assert len(st["mean_target"]) == nb and st["objects_per_bin"].sum() == 900
+    assert st["predictions_on_varying_feature"][-1] > st["predictions_on_varying_feature"][0]
+    pp, fig = m.plot_predictions(X[:10], [0])
+    assert fig is None and pp[0].shape == (10, nb)
+    m2 = cb.CatBoostRegressor(iterations=T, depth=2, verbose=False, allow_writing_files=False).fit(X[:700], y[:700])
+    cmp_ = m.compare(m2, cb.Pool(X[700:], y[700:]), ["RMSE"], eval_period=10)
+    assert len(cmp_["RMSE"][0]) == len(cmp_["RMSE"][1]) == (T + 9) // 10
+    calc = m.create_metric_calcer(["RMSE"], eval_period=20)
+    calc.add(cb.Pool(X[:400], y[:400]))
+    calc.add(cb.Pool(X[400:], y[400:]))
+    whole = m.eval_metrics(cb.Pool(X, y), ["RMSE"], eval_period=20)["RMSE"]
+    np.testing.assert_allclose(calc.eval_metrics()["RMSE"], whole, rtol=1e-9)
+    # pool helpers
+    pool = cb.Pool(X, (y > 0).astype(int))
+    tr, ev = pool.train_eval_split(is_classification=True, eval_fraction=0.25)
+    assert tr.num_row() + ev.num_row() == 900 and abs(ev.num_row() - 225) <= 2
+    pool.set_timestamp(np.arange(900)[::-1])
+    tr, ev = pool.train_eval_split(has_time=True, eval_fraction=0.1)
+    assert ev.num_row() == 90 and np.array_equal(np.asarray(ev.timestamp), np.arange(810, 900)[::-1])
