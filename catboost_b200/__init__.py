@@ -9,7 +9,15 @@ from .data.pool import CatBoostError, Pool  # noqa: F401
 from .cv import cv  # noqa: F401
 from .eval_features import eval_features  # noqa: F401
 
-FeaturesData = None
+from .gp import sample_gaussian_process  # noqa: F401
+from .compat import (EFeaturesSelectionAlgorithm, EFeaturesSelectionGrouping, EShapCalcType, FeaturesData,  # noqa: F401
+                     MultiRegressionCustomMetric, MultiRegressionCustomObjective, MultiTargetCustomMetric,
+                     MultiTargetCustomObjective)
+
+CatboostError = CatBoostError          # spelling kept by the reference for old code
 __version__ = "0.1.0"
 __all__ = ["CatBoost", "CatBoostClassifier", "CatBoostRegressor", "CatBoostRanker", "Pool", "CatBoostError", "train",
-           "cv", "sum_models", "to_classifier", "to_regressor", "to_ranker", "EFstrType"]
+           "cv", "sum_models", "to_classifier", "to_regressor", "to_ranker", "EFstrType", "EShapCalcType",
+           "EFeaturesSelectionAlgorithm", "EFeaturesSelectionGrouping", "FeaturesData", "CatboostError",
+           "sample_gaussian_process", "eval_features", "MultiRegressionCustomMetric", "MultiRegressionCustomObjective",
+           "MultiTargetCustomMetric", "MultiTargetCustomObjective"]

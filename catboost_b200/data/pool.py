@@ -218,6 +218,13 @@ class Pool:
                 pairs, pw = read_pairs(os.fspath(pairs))
                 pairs_weight = pw if pairs_weight is None else pairs_weight
         names = None
+        if type(data).__name__ == "FeaturesData" and hasattr(data, "columns") and hasattr(data, "get_feature_names"):
+            if cat_features is not None:
+                raise CatBoostError("cat_features must not be given with FeaturesData: it knows its categorical columns")
+            fcols, cat_features = data.columns()
+            if feature_names is None:
+                feature_names = data.get_feature_names()
+            data = _ColumnView(fcols)
         if _pd is not None and isinstance(data, _pd.DataFrame):
             names = [str(c) for c in data.columns]
             if cat_features is None:

@@ -130,6 +130,13 @@ class GenericLearner:
     def _randn(self, shape):
         return torch.randn(shape, generator=self.gen).to(self.dev)
 
+    def _score_noise(self, shape):
+        """Unit noise added to split scores: standard normal, or standard Gumbel for random_score_type='Gumbel'."""
+        if str(self.o.random_score_type) == "Gumbel":
+            u = torch.rand(shape, generator=self.gen).clamp_(1e-12, 1.0 - 1e-7)
+            return (-torch.log(-torch.log(u))).to(self.dev)
+        return self._randn(shape)
+
     def bootstrap_weights(self, der: torch.Tensor) -> Optional[torch.Tensor]:
         o, n = self.o, self.store.n
         bt = o.bootstrap_type
@@ -275,7 +282,7 @@ class GenericLearner:
             num, den, cnt, sides_ = sc.candidate_terms(h, K, cstat)
             score = sc.finish(num.sum(0), None if den is None else den.sum(0))          # [F, B]
             if noise_std > 0:
-                score = score + self._randn(score.shape) * noise_std
+                score = score + self._score_noise(score.shape) * noise_std
             score = score * fw.unsqueeze(1)
             mask = self._cand_mask(fmask, cnt)
             if self.monotone is not None and K == 1:
@@ -310,7 +317,7 @@ class GenericLearner:
                 (right[:, :K] ** 2 / (right[:, K].clamp_min(0).unsqueeze(1) + sc.l2)).sum(1)
         gain = l2num - parent.unsqueeze(-1)
         if noise_std > 0:
-            score = score + self._randn(score.shape) * noise_std
+            score = score + self._score_noise(score.shape) * noise_std
         score = score * self.store.feat_weight.view(1, -1, 1)
         mask = (sc.valid_cand & fmask.unsqueeze(1)).unsqueeze(0).expand_as(score)
         nonempty = (left[:, K] > 0) & (right[:, K] > 0)

@@ -82,7 +82,8 @@ def _use_fast_engine(o, objective, store, dims) -> bool:
             and o.boosting_type == "Plain" and o.leaf_estimation_method in ("Newton", "Gradient")
             and float(o.rsm) >= 1.0 and int(o.min_data_in_leaf) <= 1
             and o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson") and bool(o.fused_levels or True)
-            and not o.langevin and not o.monotone_constraints)
+            and not o.langevin and not o.monotone_constraints and not o.model_shrink_rate
+            and str(o.random_score_type) != "Gumbel")
 
 
 class _History:
@@ -177,7 +178,25 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
     best_it, best_val = None, None
     t_loop = time.time()
     stop = False
+    shrink_rate = float(o.model_shrink_rate or 0.0)
+    if shrink_rate > 0.0:
+        approx0 = approx[:, :n].clone()
+        eval_approx0 = [ea.clone() for ea in eval_approx]
     for it in range(start_iter, T):
+        if shrink_rate > 0.0 and trees:
+            # model shrinkage (catboost/private/libs/algo/train.cpp, model_shrink_rate): before every iteration the sum of
+            # the trees built so far is multiplied by 1 - rate * learning_rate (Constant) or 1 - rate / iteration
+            # (Decreasing); the starting value is left alone
+            c = shrink_rate / float(it + 1) if str(o.model_shrink_mode or "Constant") == "Decreasing" \
+                else shrink_rate * float(o.learning_rate)
+            if not 0.0 <= c < 1.0:
+                raise CatBoostError("model_shrink_rate * learning_rate must be in [0, 1)")
+            f = 1.0 - c
+            approx[:, :n] = approx0 + (approx[:, :n] - approx0) * f
+            for ea, ea0 in zip(eval_approx, eval_approx0):
+                ea.copy_(ea0 + (ea - ea0) * f)
+            for tr_ in trees:
+                tr_["values"] = tr_["values"] * f
         with prof.span("derivatives"):
             # ordered boosting: the tree structure is learned from derivatives at the ordered cursor, where the
             # value of a document only comes from documents that precede it in the permutation

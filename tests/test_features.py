@@ -700,3 +700,35 @@ def test_remaining_public_methods(tmp_path):
     pool.set_timestamp(np.arange(900)[::-1])
     tr, ev = pool.train_eval_split(has_time=True, eval_fraction=0.1)
     assert ev.num_row() == 90 and np.array_equal(np.asarray(ev.timestamp), np.arange(810, 900)[::-1])
+
+
+def test_features_data_shrinkage_and_gp_sampling():
+    rng = np.random.default_rng(2)
+    n = 400
+    num = rng.standard_normal((n, 3)).astype(np.float32)
+    cat = np.array([[f"c{v}".encode()] for v in rng.integers(0, 4, n)], dtype=object)
+    y = (num[:, 0] + (cat[:, 0] == b"c1") * 2.0).astype(np.float32)
+    fdata = cb.FeaturesData(num, cat, num_feature_names=["a", "b", "c"], cat_feature_names=["k"])
+    assert fdata.get_feature_count() == 4 and fdata.get_feature_names() == ["a", "b", "c", "k"]
+    pool = cb.Pool(fdata, y)
+    assert pool.get_cat_feature_indices() == [3] and pool.get_feature_names() == ["a", "b", "c", "k"]
+    m = cb.CatBoostRegressor(iterations=30, depth=3, learning_rate=0.3, verbose=False, allow_writing_files=False).fit(pool)
+    assert np.sqrt(np.mean((m.predict(pool) - y) ** 2)) < 0.5
+    assert cb.CatboostError is cb.CatBoostError and cb.EShapCalcType.Exact == "Exact"
+    # shrinkage pulls the model towards zero: smaller predictions, and the stored trees reproduce the training cursor
+    X = num
+    t = (2.0 * X[:, 0]).astype(np.float32)
+    kw = dict(iterations=40, depth=3, learning_rate=0.2, verbose=False, allow_writing_files=False, boost_from_average=False,
+              bootstrap_type="No", random_strength=0)
+    plain = cb.CatBoostRegressor(**kw).fit(X, t)
+    shr = cb.CatBoostRegressor(model_shrink_rate=1.0, **kw).fit(X, t)
+    assert np.abs(shr.predict(X)).mean() < 0.9 * np.abs(plain.predict(X)).mean()
+    res = np.sqrt(np.mean((shr.predict(X) - t) ** 2))
+    assert abs(shr.evals_result_["learn"]["RMSE"][-1] - res) < 1e-4
+    # posterior samples: close to the data where there is data, different from each other
+    models = cb.sample_gaussian_process(X, t, samples=3, posterior_iterations=60, prior_iterations=10, depth=3, sigma=0.5,
+                                        random_seed=1)
+    assert len(models) == 3
+    preds = np.stack([mm.predict(X) for mm in models])
+    assert np.sqrt(np.mean((preds.mean(0) - t) ** 2)) < 0.8
+    assert np.abs(preds[0] - preds[1]).max() > 1e-3
