@@ -6,6 +6,7 @@ CatBoostRanker :6391, train :6775, cv :7085, sum_models :7394).
 from __future__ import annotations
 
 import copy
+import math
 import json
 import os
 from typing import Optional
@@ -183,7 +184,9 @@ class CatBoost:
             return pr if pt == "Probability" else np.log(np.clip(pr, 1e-300, None))
         if pt == "Class":
             if binclass:
-                idx = (raw[:, 0] > 0).astype(np.int64)
+                thr = float(m.info.get("binclass_probability_threshold", 0.5))
+                border = math.log(thr / (1.0 - thr)) if 0.0 < thr < 1.0 else (math.inf if thr >= 1.0 else -math.inf)
+                idx = (raw[:, 0] > border).astype(np.int64)
             elif multi:
                 idx = raw.argmax(1)
             elif m.loss_name in ("MultiLogloss", "MultiCrossEntropy"):
@@ -768,6 +771,24 @@ class CatBoostClassifier(CatBoost):
 
     def staged_predict_proba(self, data, ntree_start=0, ntree_end=0, eval_period=1, thread_count=-1, verbose=None):
         return self.staged_predict(data, "Probability", ntree_start, ntree_end, eval_period, thread_count, verbose)
+
+    def staged_predict_log_proba(self, data, ntree_start=0, ntree_end=0, eval_period=1, thread_count=-1, verbose=None):
+        return self.staged_predict(data, "LogProbability", ntree_start, ntree_end, eval_period, thread_count, verbose)
+
+    def set_probability_threshold(self, binclass_probability_threshold=None):
+        """Probability above which a binary model predicts the positive class (stored with the model); None restores 0.5."""
+        self._check_fitted()
+        if binclass_probability_threshold is None:
+            self._model.info.pop("binclass_probability_threshold", None)
+            return
+        t = float(binclass_probability_threshold)
+        if not 0.0 <= t <= 1.0:
+            raise CatBoostError("the probability threshold must be in [0, 1]")
+        self._model.info["binclass_probability_threshold"] = repr(t)
+
+    def get_probability_threshold(self):
+        self._check_fitted()
+        return float(self._model.info.get("binclass_probability_threshold", 0.5))
 
 
 class CatBoostRegressor(CatBoost):

@@ -732,3 +732,18 @@ def test_features_data_shrinkage_and_gp_sampling():
     preds = np.stack([mm.predict(X) for mm in models])
     assert np.sqrt(np.mean((preds.mean(0) - t) ** 2)) < 0.8
     assert np.abs(preds[0] - preds[1]).max() > 1e-3
+
+
+def test_probability_threshold_is_stored_with_the_model(tmp_path):
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((500, 3)).astype(np.float32)
+    y = (X[:, 0] > 0).astype(int)
+    m = cb.CatBoostClassifier(iterations=20, depth=3, verbose=False, allow_writing_files=False).fit(X, y)
+    p = m.predict_proba(X)[:, 1]
+    m.set_probability_threshold(0.8)
+    assert np.array_equal(np.asarray(m.predict(X)).astype(int).reshape(-1), (p > 0.8).astype(int))
+    m.save_model(str(tmp_path / "m.cbm"))
+    assert cb.CatBoostClassifier().load_model(str(tmp_path / "m.cbm")).get_probability_threshold() == 0.8
+    m.set_probability_threshold(None)
+    assert np.array_equal(np.asarray(m.predict(X)).astype(int).reshape(-1), (p > 0.5).astype(int))
+    assert len(list(m.staged_predict_log_proba(X[:5], eval_period=10))) == 2
