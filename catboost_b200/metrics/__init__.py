@@ -510,3 +510,49 @@ def make_metric(desc) -> Metric:
 
 def is_max_optimal(desc: str) -> bool:
     return make_metric(desc).is_max_optimal
+
+
+# ---- metric objects (catboost/python-package/catboost/metrics.py) ----------------------------------------------
+# ``metrics.AUC(type='Ranking')``, ``metrics.Quantile(alpha=0.3)``: an object whose string form is the metric description
+# accepted everywhere a metric name is (eval_metric, custom_metric, eval_metrics) and that can evaluate itself.
+class BuiltinMetric:
+    _name = ""
+
+    def __init__(self, **params):
+        self._params = {k: v for k, v in params.items() if v is not None}
+
+    def __str__(self):
+        if not self._params:
+            return self._name
+        def fmt(v):
+            return str(v).lower() if isinstance(v, bool) else str(v)
+        return self._name + ":" + ";".join(f"{k}={fmt(v)}" for k, v in self._params.items())
+
+    __repr__ = __str__
+
+    def set_hints(self, **hints):
+        self._params["hints"] = "|".join(f"{k}~{v}" for k, v in hints.items())
+        return self
+
+    def is_max_optimal(self):
+        return bool(_METRICS[self._name][1])
+
+    def eval(self, label, approx, weight=None, group_id=None, group_weight=None, subgroup_id=None, pairs=None,
+             thread_count=-1):
+        from ..utils import eval_metric
+        return eval_metric(label, approx, str(self), weight, group_id, group_weight, subgroup_id, pairs, thread_count)[0]
+
+    @classmethod
+    def params_with_defaults(cls):
+        return {}
+
+
+def _make_metric_classes():
+    made = {}
+    for _nm in _METRICS:
+        made[_nm] = type(_nm, (BuiltinMetric,), {"_name": _nm, "__doc__": f"The {_nm} metric; keyword arguments are its parameters."})
+    return made
+
+
+_METRIC_CLASSES = _make_metric_classes()
+globals().update(_METRIC_CLASSES)

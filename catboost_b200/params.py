@@ -163,8 +163,19 @@ def normalize_params(params: Optional[dict]) -> dict:
             raise CatBoostError(f"unknown parameter {k!r}")
         if name in out and out[name] != v:
             raise CatBoostError(f"parameter {name!r} is given twice through synonyms")
+        if name in ("loss_function", "eval_metric", "custom_metric", "custom_loss"):
+            v = _metric_objects_to_text(v)
         out[name] = v
     return out
+
+
+def _metric_objects_to_text(v):
+    """Metric objects of ``catboost_b200.metrics`` (``metrics.AUC(type='Ranking')``) stand for their description."""
+    def one(x):
+        return str(x) if type(x).__mro__[1:2] and any(c.__name__ == "BuiltinMetric" for c in type(x).__mro__) else x
+    if isinstance(v, (list, tuple)):
+        return [one(x) for x in v]
+    return one(v)
 
 
 def resolve_options(params: Optional[dict], default_loss: str = "RMSE", n_rows: Optional[int] = None,

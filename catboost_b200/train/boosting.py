@@ -269,6 +269,8 @@ def _metric_list(o: Options):
     if isinstance(o.loss_function, str) and o.loss_function not in descs:
         descs.append(o.loss_function)
     out, seen = [], set()
+    from ..metrics import BuiltinMetric
+    descs = [str(d) if isinstance(d, BuiltinMetric) else d for d in descs]        # metric objects: their description
     for d in descs:
         if not isinstance(d, str):
             out.append(d)

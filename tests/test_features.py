@@ -747,3 +747,18 @@ def test_probability_threshold_is_stored_with_the_model(tmp_path):
     m.set_probability_threshold(None)
     assert np.array_equal(np.asarray(m.predict(X)).astype(int).reshape(-1), (p > 0.5).astype(int))
     assert len(list(m.staged_predict_log_proba(X[:5], eval_period=10))) == 2
+
+
+def test_metric_objects():
+    from catboost_b200 import metrics
+    assert str(metrics.Quantile(alpha=0.3)) == "Quantile:alpha=0.3" and str(metrics.RMSE()) == "RMSE"
+    assert metrics.AUC().is_max_optimal() and not metrics.Logloss().is_max_optimal()
+    y, a = np.array([0, 1, 1, 0, 1.0]), np.array([-1, 2, 0.5, -0.2, 0.1])
+    assert metrics.AUC().eval(y, a) == 1.0
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((300, 3)).astype(np.float32)
+    t = (X[:, 0] + 0.5 * rng.standard_normal(300) > 0).astype(int)
+    m = cb.CatBoostClassifier(iterations=10, depth=2, verbose=False, allow_writing_files=False, eval_metric=metrics.AUC(),
+                              custom_metric=[metrics.Accuracy()], use_best_model=False).fit(X, t, eval_set=(X, t))
+    assert list(m.evals_result_["validation"]) == ["AUC", "Accuracy", "Logloss"]
+    assert len(m.eval_metrics(cb.Pool(X, t), [metrics.F1()], eval_period=5)["F1"]) == 2
