@@ -762,3 +762,29 @@ def test_metric_objects():
                               custom_metric=[metrics.Accuracy()], use_best_model=False).fit(X, t, eval_set=(X, t))
     assert list(m.evals_result_["validation"]) == ["AUC", "Accuracy", "Logloss"]
     assert len(m.eval_metrics(cb.Pool(X, t), [metrics.F1()], eval_period=5)["F1"]) == 2
+
+
+def test_public_tokenizer_and_dictionary(tmp_path):
+    from catboost_b200.text_processing import Dictionary, Tokenizer
+    tk = Tokenizer(lowercasing=True, separator_type="BySense", token_types=["Word", "Number"])
+    assert tk.tokenize("The cat, the CAT and 42 dogs!") == ["the", "cat", "the", "cat", "and", "42", "dogs"]
+    toks, kinds = tk.tokenize("a 7", types=True)
+    assert kinds == ["Word", "Number"]
+    assert Tokenizer(number_process_policy="Replace", number_token="#").tokenize("buy 3 apples") == ["buy", "#", "apples"]
+    assert Tokenizer(delimiter=",;", split_by_set=True).tokenize("a,b;;c") == ["a", "b", "c"]
+    assert Tokenizer(delimiter=",", skip_empty=False).tokenize("a,,b") == ["a", "", "b"]
+    docs = ["the cat sat", "the cat ran", "a dog ran", "the end"]
+    d = Dictionary(occurence_lower_bound=2).fit(docs, tk)
+    assert d.size == 3 and d.get_top_tokens() == ["the", "cat", "ran"] and d.get_token(0) == "the"
+    assert d.apply(docs, tk) == [[0, 1], [0, 1, 2], [2], [0]]
+    assert d.apply("the unknown cat", tk, unknown_token_policy="Insert") == [0, d.unknown_token_id, 1]
+    assert d.min_unused_token_id == d.unknown_token_id + 2
+    bi = Dictionary(gram_order=2, occurence_lower_bound=2).fit(docs, tk)
+    assert bi.get_top_tokens() == ["the cat"]
+    letters = Dictionary(token_level_type="Letter", occurence_lower_bound=4, end_of_word_policy="Skip").fit(docs, tk)
+    assert set(letters.get_top_tokens()) == {"a", "t", "e"}
+    d.save(str(tmp_path / "dict.tsv"))
+    d2 = Dictionary().load(str(tmp_path / "dict.tsv"))
+    assert d2.get_top_tokens() == d.get_top_tokens() and d2.apply(docs, tk) == d.apply(docs, tk)
+    with pytest.raises(cb.CatBoostError):
+        Dictionary().size
