@@ -788,3 +788,33 @@ def test_public_tokenizer_and_dictionary(tmp_path):
     assert d2.get_top_tokens() == d.get_top_tokens() and d2.apply(docs, tk) == d.apply(docs, tk)
     with pytest.raises(cb.CatBoostError):
         Dictionary().size
+
+
+def test_polynomial_view_reproduces_the_model():
+    from catboost_b200 import monoforest
+    rng = np.random.default_rng(6)
+    X = rng.standard_normal((600, 4)).astype(np.float32)
+    y = (X[:, 0] * X[:, 1] + X[:, 2]).astype(np.float32)
+    m = cb.CatBoostRegressor(iterations=25, depth=3, learning_rate=0.3, verbose=False, allow_writing_files=False,
+                             border_count=8).fit(X, y)
+    poly = monoforest.to_polynom(m)
+    assert poly[0].splits == [] and all(len(mn.splits) <= 3 for mn in poly)
+    np.testing.assert_allclose(monoforest.eval_polynom(poly, X)[:, 0], m.predict(X), rtol=1e-6, atol=1e-6)
+    # merged monomials: at most one condition per feature, no duplicates
+    keys = [tuple((s.feature_idx, s.border) for s in mn.splits) for mn in poly]
+    assert len(set(keys)) == len(keys) and all(len({f for f, _ in k}) == len(k) for k in keys)
+    assert monoforest.to_polynom_string(m).count(" + ") == len(poly) - 1
+    expl = monoforest.explain_features(m)
+    assert {e.feature for e in expl} <= {0, 1, 2, 3}
+    strength = monoforest.calc_features_strength(m)
+    assert strength[3] < min(strength[0], strength[2])             # the noise feature matters least
+    xs, ys = expl[0].calc_pdp()
+    assert len(ys) == len(xs) + 1
+    mc = cb.CatBoostClassifier(iterations=8, depth=2, loss_function="MultiClass", verbose=False,
+                               allow_writing_files=False).fit(X, np.digitize(X[:, 0], [-0.5, 0.5]))
+    pm = monoforest.to_polynom(mc)
+    np.testing.assert_allclose(monoforest.eval_polynom(pm, X), mc.predict(X, prediction_type="RawFormulaVal"), rtol=1e-6,
+                               atol=1e-6)
+    dw = cb.CatBoostRegressor(iterations=3, depth=2, grow_policy="Depthwise", verbose=False, allow_writing_files=False).fit(X, y)
+    with pytest.raises(cb.CatBoostError):
+        monoforest.to_polynom(dw)
