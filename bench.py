@@ -255,7 +255,7 @@ def reference_arm(args):
     """The unmodified reference cannot be built offline: its python package needs the native build
     (build_native.py / conan-fetched dependencies / clang), and no catboost wheel is in the offline wheelhouse."""
     print(json.dumps({"impl": "reference",
-                      "unavailable": "catboost python package cannot be built offline (pip install of /root/reference "
+                      "unavailable": "catboost python package cannot be built offline (pip install of the reference tree "
                                      "fails: no setup.py at the root; python-package build needs conan + network)"}))
     return 0
 

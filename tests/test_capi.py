@@ -167,7 +167,8 @@ def test_header_is_plain_c_and_links(tmp_path):
 def test_model_files_written_by_the_reference():
     """Models saved by the reference itself (numerical + categorical with 26 CTR features; text models are refused)."""
     import os
-    ref = os.environ.get("CATBOOST_REFERENCE", "/root/reference") + "/catboost/pytest/data"
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.environ.get("CATBOOST_REFERENCE", os.path.join(os.path.dirname(here), "reference")) + "/catboost/pytest/data"
     path = ref + "/models/features_num_cat__dataset_adult.cbm"
     if not os.path.exists(path):
         pytest.skip("reference model files are not available")

@@ -10,7 +10,7 @@ import pytest
 import catboost_b200 as cb
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = "/root/reference"
+REF = os.environ.get("CATBOOST_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 def _cat_data(n=6000, seed=0):
