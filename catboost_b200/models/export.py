@@ -1,7 +1,8 @@
-"""Model export to ONNX (ai.onnx.ml TreeEnsemble operators) and PMML (MiningModel of TreeModels).
+"""Model export to ONNX (ai.onnx.ml TreeEnsemble operators), CoreML (TreeEnsembleRegressor) and PMML (MiningModel of
+TreeModels).
 
-Both writers are self-contained: the ONNX file is a protobuf ``ModelProto`` encoded by hand (field numbers of
-onnx/onnx.proto), the PMML file is plain XML.  As in the reference (catboost/libs/model/model_export/onnx_helpers.cpp,
+The writers are self-contained: the ONNX and CoreML files are protobuf messages encoded by hand (field numbers of
+onnx/onnx.proto and of the CoreML specification), the PMML file is plain XML.  As in the reference (catboost/libs/model/model_export/onnx_helpers.cpp,
 pmml_helpers.cpp) only models over numerical features are exportable; a split "value > border" becomes the ONNX node
 mode BRANCH_GT with the true branch on the right child.
 """
@@ -212,3 +213,57 @@ def model_to_pmml(m: Model) -> str:
         out.append('      </Segment>')
     out += ['    </Segmentation>', '  </MiningModel>', '</PMML>']
     return "\n".join(out)
+
+
+# ---- CoreML -------------------------------------------------------------------------------------------------
+def _f_double(field, v):
+    return _key(field, 1) + struct.pack("<d", float(v))
+
+
+def model_to_coreml_bytes(m: Model, export_parameters=None) -> bytes:
+    """CoreML ``Model`` with a TreeEnsembleRegressor (field numbers of Model.proto, TreeEnsemble.proto and
+    FeatureTypes.proto of the CoreML specification; the reference writes the same structure in
+    catboost/libs/model/model_export/coreml_helpers.cpp).  Every feature of the dataset is a double input named after
+    the feature; the output ``prediction`` is the raw formula value, or the probability of the positive class with
+    ``export_parameters={'prediction_type': 'probability'}`` on a binary classifier (logistic post-transform).  A split
+    ``value > border`` is the node behaviour BranchOnValueGreaterThan."""
+    trees = _flatten_trees(m)
+    params = dict(export_parameters or {})
+    want_proba = str(params.get("prediction_type", "raw")).lower() == "probability"
+    if want_proba and not (m.dims == 1 and m.class_names is not None):
+        raise CatBoostError("prediction_type 'probability' is exported for binary classifiers")
+    dims = m.dims
+    nodes = b""
+    for ti, ns in enumerate(trees):
+        for node in range(len(ns.split_of_node)):
+            si = int(ns.split_of_node[node])
+            body = _f_varint(1, ti) + _f_varint(2, node)
+            if si >= 0:
+                sp = m.splits[si]
+                ff = m.float_features[sp.feature]
+                body += _f_varint(3, 3) + _f_varint(10, ff.flat_index) + _f_double(11, sp.border) + \
+                    _f_varint(12, int(ns.right[node])) + _f_varint(13, int(ns.left[node]))
+                if ff.nan_mode == "Max":
+                    body += _f_varint(14, 1)
+            else:
+                body += _f_varint(3, 6)
+                lv = ns.leaf_values[int(ns.leaf_of_node[node])] * m.scale
+                for d in range(dims):
+                    body += _f_bytes(20, (_f_varint(1, d) if d else b"") + _f_double(2, lv[d]))
+            nodes += _f_bytes(1, body)
+    bias = [float(b) for b in np.broadcast_to(m.bias, (dims,))]
+    ensemble = nodes + _f_varint(2, dims) + _f_bytes(3, b"".join(struct.pack("<d", b) for b in bias))
+    regressor = _f_bytes(1, ensemble) + (_f_varint(2, 2) if want_proba else b"")
+    double_type = _f_bytes(2, b"")                                   # FeatureType { doubleType {} }
+    inputs = b"".join(_f_bytes(1, _f_str(1, str(nm)) + _f_bytes(3, double_type)) for nm in m.feature_names)
+    if dims == 1:
+        out_type = double_type
+    else:
+        out_type = _f_bytes(5, _packed_ints(1, [dims]) + _f_varint(2, 65600))     # multiArrayType { shape, DOUBLE }
+    output = _f_bytes(10, _f_str(1, "prediction") + _f_bytes(3, out_type))
+    meta = _f_str(1, "catboost_b200 model") + _f_str(2, "0.1")
+    for k_, v_ in sorted(m.info.items()):
+        if k_ in ("params", "model_guid", "catboost_version_info"):
+            meta += _f_bytes(100, _f_str(1, k_) + _f_str(2, str(v_)))
+    description = inputs + output + _f_str(11, "prediction") + _f_bytes(100, meta)
+    return _f_varint(1, 1) + _f_bytes(2, description) + _f_bytes(302, regressor)

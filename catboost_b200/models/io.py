@@ -546,7 +546,9 @@ def save_model(m: Model, fname: str, format: str = "cbm", export_parameters=None
         with open(fname, "w") as fh:
             fh.write(model_to_pmml(m))
     elif fmt == "coreml":
-        raise CatBoostError("export format 'coreml' is not available in this build")
+        from .export import model_to_coreml_bytes
+        with open(fname, "wb") as fh:
+            fh.write(model_to_coreml_bytes(m, export_parameters))
     else:
         raise CatBoostError(f"unknown model format {format!r}")
 

@@ -818,3 +818,85 @@ def test_polynomial_view_reproduces_the_model():
     dw = cb.CatBoostRegressor(iterations=3, depth=2, grow_policy="Depthwise", verbose=False, allow_writing_files=False).fit(X, y)
     with pytest.raises(cb.CatBoostError):
         monoforest.to_polynom(dw)
+
+
+def _pb_fields(buf):
+    """Generic protobuf wire decoding: list of (field number, wire type, value)."""
+    import struct
+    out, pos = [], 0
+    while pos < len(buf):
+        key, shift = 0, 0
+        while True:
+            b = buf[pos]; pos += 1
+            key |= (b & 0x7F) << shift; shift += 7
+            if not b & 0x80:
+                break
+        field, wire = key >> 3, key & 7
+        if wire == 0:
+            v, shift = 0, 0
+            while True:
+                b = buf[pos]; pos += 1
+                v |= (b & 0x7F) << shift; shift += 7
+                if not b & 0x80:
+                    break
+        elif wire == 1:
+            v = struct.unpack_from("<d", buf, pos)[0]; pos += 8
+        elif wire == 2:
+            ln, shift = 0, 0
+            while True:
+                b = buf[pos]; pos += 1
+                ln |= (b & 0x7F) << shift; shift += 7
+                if not b & 0x80:
+                    break
+            v = buf[pos:pos + ln]; pos += ln
+        elif wire == 5:
+            v = struct.unpack_from("<f", buf, pos)[0]; pos += 4
+        else:
+            raise AssertionError("unexpected wire type")
+        out.append((field, wire, v))
+    return out
+
+
+def test_coreml_export_decodes_to_the_same_trees(tmp_path):
+    rng = np.random.default_rng(9)
+    X = rng.standard_normal((500, 4)).astype(np.float32)
+    y = (X[:, 0] - X[:, 3] > 0).astype(int)
+    m = cb.CatBoostClassifier(iterations=12, depth=3, verbose=False, allow_writing_files=False).fit(X, y)
+    path = tmp_path / "m.mlmodel"
+    m.save_model(str(path), format="coreml", export_parameters={"prediction_type": "probability"})
+    top = _pb_fields(path.read_bytes())
+    assert [f for f, _, _ in top] == [1, 2, 302] and top[0][2] == 1
+    desc = _pb_fields(top[1][2])
+    names = [_pb_fields(v)[0][2].decode() for f, _, v in desc if f == 1]
+    assert names == ["0", "1", "2", "3"]
+    assert [v for f, _, v in desc if f == 11][0] == b"prediction"
+    reg = _pb_fields(top[2][2])
+    assert [v for f, _, v in reg if f == 2] == [2]                       # logistic transform
+    ens = _pb_fields([v for f, _, v in reg if f == 1][0])
+    import struct
+    base = struct.unpack("<d", [v for f, _, v in ens if f == 3][0])[0]
+    nodes = {}
+    for f, _, v in ens:
+        if f == 1:
+            d = {}
+            for ff, _, vv in _pb_fields(v):
+                d.setdefault(ff, []).append(vv)
+            nodes[(d.get(1, [0])[0], d.get(2, [0])[0])] = d
+    # evaluate the decoded ensemble on a few rows
+    for row in X[:25]:
+        total = base
+        for t in range(12):
+            node = 0
+            while True:
+                d = nodes[(t, node)]
+                if d[3][0] == 6:
+                    total += _pb_fields(d[20][0])[-1][2]
+                    break
+                assert d[3][0] == 3
+                go = row[d.get(10, [0])[0]] > d[11][0]
+                node = d.get(12, [0])[0] if go else d.get(13, [0])[0]
+        want = m.predict(row.reshape(1, -1), prediction_type="RawFormulaVal")[0]
+        assert abs(total - want) < 1e-6
+    with pytest.raises(cb.CatBoostError):
+        cb.CatBoostRegressor(iterations=2, depth=2, verbose=False, allow_writing_files=False).fit(X, y.astype(float)) \
+            .save_model(str(path), format="coreml", export_parameters={"prediction_type": "probability"})
