@@ -16,6 +16,7 @@
 //
 // Only plain peer stores / loads touch remote memory: no bulk-copy engine, no switch-side reduction.
 #include "cb_common.cuh"
+#include <cstdlib>
 #include "cb_tree.cuh"
 #include "cb_comm.cuh"
 #include <cooperative_groups.h>
@@ -193,6 +194,8 @@ struct CbFusedPlan {
     int sm_smem;       // shared memory of one SM available to two resident blocks (after their static + reserved parts)
     int sm_count;
     int max_bundle;    // widest feature-group bundle of the single-cell histogram path (0 = off)
+    int max_copies;    // most replicas of a histogram cell (2 for dense columns; more when one bin dominates a column,
+                       // where most lanes of a warp would otherwise add to the same cell)
 };
 
 CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigned short* leaf, const float* stats, int S,
@@ -237,6 +240,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     cudaDeviceGetAttribute(&p->sm_smem, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
     p->sm_smem -= 2 * (int)fa.sharedSizeBytes;
     p->max_bundle = 0;
+    p->max_copies = 2;
     if (cudaFuncSetAttribute(cb_level_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, p->max_smem) != cudaSuccess) {
         cudaGetLastError();
         delete p;
@@ -261,6 +265,10 @@ CB_API void cb_fused_destroy(CbFusedPlan* p) { delete p; }
 
 // Launch geometry of one level.  Returns the cooperative grid size (0 on error) and, through the pointers, the
 // slots per pass, dynamic shared memory, block size, document chunks per group and cell replicas.
+CB_API void cb_fused_set_max_copies(CbFusedPlan* p, int max_copies) {
+    p->max_copies = max_copies >= 8 ? 8 : (max_copies >= 4 ? 4 : (max_copies >= 2 ? 2 : 1));
+}
+
 CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int* smem_bytes, int* threads, int* chunks,
                              int* copies, int* bundle) {
     const int nslots = level == 0 ? 1 : (1 << (level - 1));
@@ -293,7 +301,9 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
         // even out the bundles (7 groups as 4 + 3 rather than 5 + 2 changes nothing in passes but shrinks the tile)
         const int nb = (G + gpc - 1) / gpc;
         gpc = (G + nb - 1) / nb;
-        if (2 * spp * gpc * cell + ring_bytes(thr, gpc) <= budget) C = 2;
+        int max_copies = p->max_copies;
+        if (const char* e = getenv("CB200_MAX_COPIES")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4 || v == 8) max_copies = v; }
+        while (C < max_copies && 2 * C * spp * gpc * cell + ring_bytes(thr, gpc) <= budget) C *= 2;
         smem = spp * gpc * cell * C + ring_bytes(thr, gpc);
     } else {
         const int per_slot = p->a.h.S * 4 * p->a.h.B * 4 * ((p->a.h.statmax && !narrow) ? 2 : 1);

@@ -203,6 +203,12 @@ class GpuObliviousEngine:
         # fixed-point accumulation is on: statmax must be known to the geometry (it doubles the tile size)
         self.lib.cb_fused_set_priv(ctypes.c_void_p(self.plan), None, _p(self.statmax) if self.quantized_hist else None)
         self.lib.cb_fused_set_narrow(ctypes.c_void_p(self.plan), 1 if self.narrow_hist else 0, self.max_bundle)
+        # columns where one bin holds a large share of the documents (sparse data): most lanes of a warp would add to
+        # the same histogram cell, so such data gets up to 8 replicas of every cell instead of 2 (measured on 60 % zeros:
+        # 6.8 -> 4.9 ms per iteration; on dense data more replicas cost about 1 %)
+        self.dominant_bin_share = self._dominant_bin_share()
+        if self.dominant_bin_share > 0.25:
+            self.lib.cb_fused_set_max_copies(ctypes.c_void_p(self.plan), 8)
         self.level_geo = []
         for level in range(self.depth):
             spp, smem, thr, nk, cp, bd = (ctypes.c_int(0) for _ in range(6))
@@ -260,6 +266,23 @@ class GpuObliviousEngine:
                                        _p(self.scal), _p(self.ext_der), _p(self.ext_hess), _p(self.statmax),
                                        self.grid_stream, self._stream()), "cb_grad_pointwise")
         self.launches_per_iter += 1
+
+    def _dominant_bin_share(self, sample: int = 16384) -> float:
+        """Mean over the features of the share of their most frequent bin, from the first rows of the store (all ranks
+        agree on the value)."""
+        st = self.store
+        m = int(min(st.n, sample))
+        if m <= 0 or st.F <= 0:
+            return 0.0
+        G = st.bins.shape[0]
+        b = st.bins[:, :m].contiguous().view(torch.uint8).view(G, m, 4).permute(0, 2, 1).reshape(G * 4, m)
+        idx = b.long() + (torch.arange(G * 4, device=b.device) * 256).unsqueeze(1)
+        cnt = torch.bincount(idx.reshape(-1), minlength=G * 4 * 256).view(G * 4, 256)
+        t = torch.stack([cnt.max(1).values[: st.F].double().sum(), torch.tensor(float(m) * st.F, dtype=torch.float64,
+                                                                                 device=b.device)])
+        if self.ctx is not None and self.ctx.is_distributed:
+            self.ctx.all_reduce_sum_(t)
+        return float((t[0] / t[1].clamp_min(1.0)).item())
 
     def _level_fused(self, level: int):
         grid, spp, smem, thr, nk, cp, bd = self.level_geo[level]
