@@ -252,11 +252,57 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    """The unmodified reference cannot be built offline: its python package needs the native build
-    (build_native.py / conan-fetched dependencies / clang), and no catboost wheel is in the offline wheelhouse."""
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "catboost python package cannot be built offline (pip install of the reference tree "
-                                     "fails: no setup.py at the root; python-package build needs conan + network)"}))
+    """The unmodified reference through its own public API (``CatBoostClassifier(task_type='GPU').fit``), when an
+    installed copy exists under ``baseline/_ref``; nothing of this package is imported on this path.  Without an
+    installed copy the arm prints why: the reference's CMake tree cannot be configured with the tool chain of this image
+    (its global flags are clang-only and the base library needs the ragel and yasm generators, none of which is
+    installed and none of which can be fetched offline)."""
+    ref_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref")
+    sys.path.insert(0, ref_dir)
+    try:
+        import catboost as ref                      # noqa: F401  (the reference's python package, if it was built)
+    except Exception as e:                          # ImportError, or a broken native module
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "no installed reference under baseline/_ref (" + type(e).__name__ + "): its CMake "
+                                         "configure stops at the clang-only flags of cmake/global_flags.compiler.gnu.cmake "
+                                         "under gcc, and util/ needs ragel + yasm; clang, ragel, yasm, swig and conan are "
+                                         "not in the image and cannot be fetched offline"}))
+        return 0
+    import torch
+    cfg = dict(CONFIGS[args.config])
+    if args.rows:
+        cfg["rows"] = args.rows
+    if args.config in ("criteo", "ranking"):
+        print(json.dumps({"impl": "reference", "unavailable": f"reference arm is wired for the dense configs, not {args.config}"}))
+        return 0
+    K, W = args.steps, max(3, args.warmup)
+    X, y = make_data(args.config, cfg["rows"], cfg["features"], 0, 1)
+    devices = "0" if args.gpus <= 1 else f"0-{args.gpus - 1}"
+    common = dict(loss_function="Logloss", depth=cfg["depth"], border_count=cfg["border_count"], learning_rate=0.1,
+                  l2_leaf_reg=3.0, task_type="GPU", devices=devices, random_seed=0, allow_writing_files=False, verbose=False)
+    # the reference has no per-iteration device timer in its public API: time fit() at W and at W + K iterations and
+    # take the difference (data loading and quantisation cancel out)
+    def fit_seconds(iters):
+        m = ref.CatBoostClassifier(iterations=iters, **common)
+        t0 = time.perf_counter()
+        m.fit(X, y)
+        return time.perf_counter() - t0
+    fit_seconds(W)
+    sampler = ClockSampler(0)
+    sampler.start()
+    t_small, t_big = fit_seconds(W), fit_seconds(W + K)
+    clocks = sampler.stop()
+    ms = max(t_big - t_small, 0.0) / K * 1000.0
+    t0 = time.perf_counter()
+    ref.CatBoostClassifier(iterations=1000, **common).fit(X, y)
+    e2e_s = time.perf_counter() - t0
+    print(json.dumps({"metric": "sec/1000 iters (difference of two fit() wall times)", "value": ms, "unit": "s/1000iter",
+                      "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": False,
+                      "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "impl": "reference",
+                      "config": {"model": cfg["model"], "global_batch": cfg["rows"], "seq_len": cfg["features"],
+                                 "parallelism": f"reference doc-parallel devices={devices}"},
+                      "clocks": clocks, "e2e": {"value": e2e_s, "unit": "s/1000iter", "h2d_bytes_per_step": int(X.nbytes // 1000),
+                                                "d2h_bytes_per_step": 0}, "gpu_launches": None}))
     return 0
 
 

@@ -67,19 +67,63 @@ def select_borders(sample: np.ndarray, border_count: int, border_type: str = "Gr
     return [out[f, :counts[f]].copy() for f in range(F)], has_nan
 
 
+def _border_sample(X: np.ndarray, seed: int, ctx=None):
+    """Rows the float borders are chosen from, and per-feature NaN flags over ALL rows.
+
+    One process: every row, or a seeded subsample of MAX_SAMPLE_FOR_BORDERS rows.  Several ranks: the same rule applied
+    to the concatenation of the ranks' shards in rank order -- every rank draws the same global row numbers, picks the
+    ones it holds, and the pieces are gathered on rank 0 (which returns the sample; the others return None).  The
+    borders therefore do not depend on how the rows are split over the ranks, and a NaN that only occurs on one rank
+    is seen (the reference builds its grid from the whole learn set, catboost/libs/data/quantization.cpp)."""
+    n = X.shape[0]
+    if ctx is None or not ctx.is_distributed:
+        if n > MAX_SAMPLE_FOR_BORDERS:
+            # Floyd's sampler of the Generator API: O(sample), where RandomState.choice permutes all n rows
+            rng = np.random.default_rng(seed)
+            idx = np.sort(rng.choice(n, MAX_SAMPLE_FOR_BORDERS, replace=False, shuffle=False))
+            return X[idx], None
+        return X, None
+    counts = ctx.all_gather_object(int(n))
+    total, off = int(sum(counts)), int(sum(counts[: ctx.rank]))
+    if total > MAX_SAMPLE_FOR_BORDERS:
+        rng = np.random.default_rng(seed)
+        idx = np.sort(rng.choice(total, MAX_SAMPLE_FOR_BORDERS, replace=False, shuffle=False))
+        mine = idx[(idx >= off) & (idx < off + n)] - off
+        part = X[mine]
+    else:
+        part = X
+    # a NaN anywhere in a column sets its flag (one pass over the shard, blocked to keep the temporary small)
+    nan_local = np.zeros(X.shape[1], dtype=bool)
+    for r0 in range(0, n, 1 << 18):
+        nan_local |= np.isnan(X[r0:r0 + (1 << 18)]).any(0)
+    flags = ctx.all_gather_object(nan_local)
+    has_nan_all = np.logical_or.reduce(flags) if flags else nan_local
+    sample = ctx.gather_rows(np.ascontiguousarray(part, dtype=np.float32), 0)
+    return sample, has_nan_all
+
+
 def build_quantization(pool, border_count: int = 254, border_type: str = "GreedyLogSum", nan_mode: str = "Min",
-                       per_float_feature_quantization=None, input_borders=None, seed: int = 0) -> FeatureQuantization:
+                       per_float_feature_quantization=None, input_borders=None, seed: int = 0,
+                       ctx=None) -> FeatureQuantization:
+    """Float border grids.  With a distributed ``ctx`` this is a collective call: the grid is built on rank 0 from a
+    sample of all ranks' rows and broadcast."""
     X = pool.float_data
     n, F = X.shape
     if nan_mode not in ("Min", "Max", "Forbidden"):
         raise CatBoostError(f"unknown nan_mode {nan_mode!r}")
-    if n > MAX_SAMPLE_FOR_BORDERS:
-        # Floyd's sampler of the Generator API: O(sample), where RandomState.choice permutes all n rows
-        rng = np.random.default_rng(seed)
-        idx = np.sort(rng.choice(n, MAX_SAMPLE_FOR_BORDERS, replace=False, shuffle=False))
-        sample = X[idx]
-    else:
-        sample = X
+    sample, has_nan_all = _border_sample(X, seed, ctx)
+    if ctx is not None and ctx.is_distributed:
+        q = None
+        if ctx.rank == 0:
+            class _Rows:
+                float_data = sample
+            q = build_quantization(_Rows, border_count, border_type, nan_mode, per_float_feature_quantization,
+                                   input_borders, seed)
+            q.has_nan = np.asarray(has_nan_all).astype(np.uint8)
+        q = ctx.broadcast_object(q, 0)
+        if nan_mode == "Forbidden" and np.asarray(has_nan_all).any():
+            raise CatBoostError("NaN values are present but nan_mode is Forbidden")
+        return q
     borders, has_nan = select_borders(sample, min(border_count, 255), border_type)
     if nan_mode == "Forbidden" and has_nan.any():
         raise CatBoostError("NaN values are present but nan_mode is Forbidden")

@@ -21,6 +21,12 @@ from ..data.pool import CatBoostError
 from ..utils.flatbuf import Builder, Table
 from .model import (CatFeatureInfo, FloatFeatureInfo, Model, NonSymmetricTree, ObliviousTree, OneHotFeatureInfo, Split)
 
+
+def _estimator_registry() -> Dict[str, type]:
+    """The only classes a model file's text/embedding block may instantiate."""
+    from ..data import estimated as est
+    return {c.__name__: c for c in (est.EstimatedFeatures, est._Dictionary, est._TextCalcers, est._EmbeddingCalcers)}
+
 MAGIC = b"CBM1"
 CORE_FORMAT = "FlabuffersModel_v1"
 STATIC_CTR_PART = "static_provider_v1"
@@ -174,8 +180,9 @@ def model_to_cbm_bytes(m: Model) -> bytes:
         # text / embedding processing (dictionaries, class statistics, reference embeddings): this framework's own
         # extension of the container, ignored by other readers
         import base64
-        import pickle
-        info["catboost_b200_estimators"] = base64.b64encode(pickle.dumps(m.estimators)).decode("ascii")
+        from ..utils import plainser
+        info["catboost_b200_estimators"] = base64.b64encode(
+            plainser.dumps(m.estimators, _estimator_registry())).decode("ascii")
     kv = []
     for k in sorted(info):
         kv.append(b.table(2, [(0, "o", b.string(k)), (1, "o", b.string(info[k]))]))
@@ -296,9 +303,16 @@ def model_from_cbm_bytes(blob: bytes) -> Model:
                                               leaf_values, leaf_weights, m.dims))
     meta = json.loads(m.info.get("catboost_b200_meta", "{}")) if "catboost_b200_meta" in m.info else {}
     if "catboost_b200_estimators" in m.info:
+        # plain data only: the stream can name the four estimator classes below and nothing else, and loading it
+        # runs no code from the file (model files are routinely passed around)
         import base64
-        import pickle
-        m.estimators = pickle.loads(base64.b64decode(m.info.pop("catboost_b200_estimators")))
+        import binascii
+        from ..utils import plainser
+        try:
+            m.estimators = plainser.loads(base64.b64decode(m.info.pop("catboost_b200_estimators"), validate=True),
+                                          _estimator_registry())
+        except (plainser.PlainDataError, binascii.Error, UnicodeDecodeError, struct.error) as e:
+            raise CatBoostError(f"the model file carries an unreadable text/embedding processing block: {e}") from e
     params = {}
     try:
         params = json.loads(m.info.get("params", "{}"))

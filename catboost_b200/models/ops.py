@@ -36,7 +36,7 @@ def sum_models(models, weights=None, ctr_merge_policy="IntersectingCountersAvera
         out.ctrs += list(m.ctrs)
         for k, v in m.one_hot.items():
             out.one_hot.setdefault(k, v)
-        out.bias = out.bias + w * m.scale * np.broadcast_to(m.bias, (base.dims,)) if False else out.bias + w * np.broadcast_to(m.bias, (base.dims,))
+        out.bias = out.bias + w * np.broadcast_to(m.bias, (base.dims,))
         remap = {}
         for i, sp in enumerate(m.splits):
             sp2 = type(sp)(sp.kind, sp.feature + (ctr_shift if sp.kind == "ctr" else 0), sp.border, sp.value)

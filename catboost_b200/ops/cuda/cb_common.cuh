@@ -77,6 +77,15 @@ __device__ __forceinline__ bool cb_wait_flag(const unsigned long long* flag, uns
     return true;
 }
 
+// Function attributes (the opt-in to more than 48 KB of dynamic shared memory) belong to a device, not to the process:
+// `seen` is one static word per call site with a bit per device ordinal; true the first time the current device asks.
+static inline bool cb_first_on_device(unsigned long long* seen) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const unsigned long long bit = 1ull << (dev & 63);
+    return (__atomic_fetch_or(seen, bit, __ATOMIC_ACQ_REL) & bit) == 0ull;
+}
+
 // float -> uint32 whose unsigned order equals the float order (NaN excluded by the callers)
 __device__ __forceinline__ unsigned int cb_float_to_ordered(float x) {
     unsigned int u = __float_as_uint(x);

@@ -335,7 +335,8 @@ static int cb_hist_launch(const CbData* d, const unsigned short* leaf, const flo
     a.slots_per_pass = slots_per_pass; a.B = B; a.out = out; a.slot_table = slot_table; a.nslots_table = nslots_table;
     a.priv = nullptr; a.statmax = statmax; a.nK = 0; a.copies = 1; a.work = nullptr; a.narrow = 0; a.bundle = 0;
     const int smem = cb_hist_smem_bytes(slots_per_pass, S, B);
-    if (!g_hist_smem_set) {
+    static unsigned long long set = 0ull;
+    if (cb_first_on_device(&set) || !g_hist_smem_set) {
         int dev = 0, optin = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
@@ -345,7 +346,7 @@ static int cb_hist_launch(const CbData* d, const unsigned short* leaf, const flo
             g_hist_smem_set = optin - (int)fa.sharedSizeBytes;
             e = cudaFuncSetAttribute(cb_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g_hist_smem_set);
         }
-        if (e != cudaSuccess) { g_hist_smem_set = 0; cudaGetLastError(); return (int)e; }
+        if (e != cudaSuccess) { g_hist_smem_set = 0; set = 0ull; cudaGetLastError(); return (int)e; }
     }
     if (smem > g_hist_smem_set) return (int)cudaErrorInvalidValue;
     cb_hist_kernel<<<grid, threads, smem, st>>>(a);
@@ -631,13 +632,12 @@ static int cb_leaf_pass_launch(CbLeafArgs& a, const CbComm* comm, int grid, cuda
     int C = 32;
     while (C > 0 && (size_t)planes * a.L * C * 4 > 96 * 1024) C >>= 1;
     const int smem = planes * a.L * C * 4;
-    static int set = 0;
-    if (!set) {
+    static unsigned long long set = 0ull;
+    if (cb_first_on_device(&set)) {
         cudaError_t e = cudaFuncSetAttribute(cb_leaf_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_leaf_pass_kernel_t<CB_LOSS_LOGLOSS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_leaf_pass_kernel_t<CB_LOSS_RMSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
-        set = 1;
+        if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
     }
     if (a.loss == CB_LOSS_LOGLOSS) cb_leaf_pass_kernel_t<CB_LOSS_LOGLOSS><<<grid, 512, smem, st>>>(a, C);
     else if (a.loss == CB_LOSS_RMSE) cb_leaf_pass_kernel_t<CB_LOSS_RMSE><<<grid, 512, smem, st>>>(a, C);
@@ -671,11 +671,10 @@ CB_API int cb_leaf_pass(int loss, float p0, float p1, const float* approx, const
     int C = 32;
     while (C > 0 && (size_t)3 * L * C * 4 > 96 * 1024) C >>= 1;
     const int smem = 3 * L * C * 4;
-    static int set = 0;
-    if (!set) {
+    static unsigned long long set = 0ull;
+    if (cb_first_on_device(&set)) {
         cudaError_t e = cudaFuncSetAttribute(cb_leaf_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
-        set = 1;
+        if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
     }
     cb_leaf_pass_kernel<<<grid, 512, smem, st>>>(a, C);
     CB_LAUNCH_CHECK();
@@ -930,12 +929,11 @@ CB_API int cb_predict_oblivious(const float* X, long long n, long long ldx, cons
     if (dims > 8 || pred_smem > CB_PRED_SMEM_MAX) return (int)cudaErrorInvalidValue;
     CbPredictArgs a{X, n, ldx, used_feat, borders, border_off, nan_is_max, U, tree_depth, tree_split_off, split_feat,
                     split_bin, tree_leaf_off, leaf_vals, T, dims, scale, bias, out, max_borders};
-    static int set = 0;
-    if (!set) {
+    static unsigned long long set = 0ull;
+    if (cb_first_on_device(&set)) {
         cudaError_t e = cudaFuncSetAttribute(cb_predict_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CB_PRED_SMEM_MAX);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_predict_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CB_PRED_SMEM_MAX);
-        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
-        set = 1;
+        if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
     }
     const unsigned pred_grid = (unsigned)((n + 256 * rows - 1) / (256 * rows));
     if (rows == 4) cb_predict_kernel<4><<<pred_grid, 256, pred_smem, st>>>(a);
@@ -1018,10 +1016,16 @@ CB_API int cb_leaf_pass_noalloc(int loss, float p0, float p1, const float* appro
     }
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= CB_NOALLOC_MAX_DEVICES) {
+    if (e != cudaSuccess || dev < 0) {
         snprintf(g_noalloc_error, sizeof(g_noalloc_error), "cb_leaf_pass_noalloc: cannot identify the current device (%s)",
                  cudaGetErrorString(e));
         cudaGetLastError();
+        return CB_NOALLOC_SETUP_FAILED;
+    }
+    if (dev >= CB_NOALLOC_MAX_DEVICES) {
+        snprintf(g_noalloc_error, sizeof(g_noalloc_error),
+                 "cb_leaf_pass_noalloc: device ordinal %d is beyond the %d devices this entry point keeps an address for",
+                 dev, CB_NOALLOC_MAX_DEVICES);
         return CB_NOALLOC_SETUP_FAILED;
     }
     if (g_noalloc_ptr[dev] == nullptr) {

@@ -225,12 +225,11 @@ __global__ void __launch_bounds__(512, 2) cb_leaf_newton_kernel(CbLeafNewtonArgs
 // code (0 = ok), or -2 when the tree has too many leaves for the shared-memory cells (use the per-step kernel).
 template <int LOSS>
 static int cb_leaf_newton_launch_t(CbLeafNewtonArgs& a, int C, int smem, int grid, cudaStream_t st) {
-    static bool set = false;
-    if (!set) {
+    static unsigned long long set = 0ull;
+    if (cb_first_on_device(&set)) {
         cudaError_t e = cudaFuncSetAttribute(cb_leaf_newton_kernel<LOSS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              100 * 1024);
-        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
-        set = true;
+        if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
     }
     void* args[] = {&a, &C};
     return (int)cudaLaunchCooperativeKernel((void*)cb_leaf_newton_kernel<LOSS>, dim3(grid), dim3(512), args,

@@ -19,6 +19,10 @@
 //   * The array is shared by all calls on a device and keeps what the last call left in it.  Each call clears the part
 //     it uses on the caller's stream before launching, so calls on one stream are safe back to back; two calls that
 //     can overlap on the GPU (different streams, no dependency) race on the array and must be ordered by the caller.
+//   * Not thread-safe: the per-device address cache and the error text are plain process-wide variables.  A host with
+//     several threads serialises its calls (one lock around cb_leaf_pass_noalloc and cb_noalloc_last_error); in
+//     particular two threads must not make the first call on a device at the same time.
+//   * Devices with an ordinal of 64 or more are rejected with CB_NOALLOC_SETUP_FAILED.
 //   * No cudaMalloc, cudaFree or other allocating routine is called.  Single-GPU only (no peer exchange).
 #pragma once
 #include <cuda_runtime.h>

@@ -181,14 +181,13 @@ CB_API int cb_quantize_tma(const float* X, long long n, int F, long long ldx, co
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return -2;
     const int smem = 1024 + 2 * CBQ_STAGE_BYTES + CBQ_FBOX * CBQ_BORDER_STRIDE * 4 + 2 * CBQ_FBOX * 4 + 16;
-    static bool set = false;
+    static unsigned long long set = 0ull;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (!set) {
+    if (cb_first_on_device(&set)) {
         cudaError_t e = cudaFuncSetAttribute(cb_quantize_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
-        set = true;
+        if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
     }
     const long long tiles = (n + CBQ_ROWS - 1) / CBQ_ROWS;
     long long grid = (long long)sms * 2;

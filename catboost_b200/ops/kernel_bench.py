@@ -3,8 +3,8 @@
     python -m catboost_b200.ops.kernel_bench [--rows N] [--features F] [--kernel name] [--reps R]
 
 Every kernel is timed in isolation with CUDA events (3 warm-up launches, an L2 flush between timed launches) and
-reported as algorithmic bytes / time against the measured copy bandwidth of the pool (``MEASURED_PEAKS.json`` at the
-repository root when present, else 6650 GB/s).  The same entry point is what the committed ncu summaries were taken on.
+reported as algorithmic bytes / time against a copy bandwidth given with ``--peak-gbs`` (the number a STREAM-style
+copy reaches on the machine; default 6650 GB/s).  The same entry point is what the committed ncu summaries were taken on.
 """
 from __future__ import annotations
 
@@ -16,15 +16,6 @@ import sys
 
 import numpy as np
 import torch
-
-
-def _peaks():
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-    path = os.path.join(root, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        with open(path) as fh:
-            return float(json.load(fh)["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
 
 
 def _time(fn, reps, flush):
@@ -51,6 +42,7 @@ def main(argv=None):
     ap.add_argument("--trees", type=int, default=100)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--kernel", default="all")
+    ap.add_argument("--peak-gbs", type=float, default=0.0, help="measured copy bandwidth of the GPU in GB/s")
     args = ap.parse_args(argv)
     from ..data.pool import Pool
     from ..data.quantization import build_quantization, make_store, quantize_floats_into, FlatFeature
@@ -66,7 +58,7 @@ def main(argv=None):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     lib = native.cuda_lib()
-    hbm, src = _peaks()
+    hbm, src = (args.peak_gbs, "given") if args.peak_gbs > 0 else (6650.0, "default")
     n, F = args.rows, args.features
     rng = np.random.default_rng(0)
     X = rng.standard_normal((n, F), dtype=np.float32)

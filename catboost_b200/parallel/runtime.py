@@ -108,6 +108,27 @@ class DistContext:
         dist.all_gather_object(out, obj, group=self.group)
         return out
 
+    def gather_rows(self, arr, dst: int = 0):
+        """The rows of every rank's 2-D numpy array, concatenated in rank order, on rank ``dst`` (None elsewhere).
+        Goes through tensor collectives (padded to the longest piece), not through pickled objects."""
+        import numpy as np
+        if not self.is_distributed:
+            return arr
+        import torch.distributed as dist
+        counts = self.all_gather_object(int(arr.shape[0]))
+        m = max(max(counts), 1)
+        on_gpu = dist.get_backend(self.group) == "nccl"
+        dev = self.device if (on_gpu and self.device is not None) else torch.device("cpu")
+        t = torch.zeros((m,) + tuple(arr.shape[1:]), dtype=torch.from_numpy(arr[:0]).dtype)
+        t[: arr.shape[0]] = torch.from_numpy(np.ascontiguousarray(arr))
+        t = t.to(dev)
+        if self.rank == dst:
+            outs = [torch.empty_like(t) for _ in range(self.world)]
+            dist.gather(t, outs, dst=dst, group=self.group)
+            return np.concatenate([outs[r][: counts[r]].cpu().numpy() for r in range(self.world)], 0)
+        dist.gather(t, None, dst=dst, group=self.group)
+        return None
+
     def broadcast_object(self, obj, src=0):
         if not self.is_distributed:
             return obj

@@ -172,14 +172,9 @@ def plan_features(o: Options, pool: Pool, ctx: DistContext, quant: Optional[Feat
     for x in (o.ignored_features or []):
         ignored.add(pool.feature_names.index(x) if isinstance(x, str) and x in pool.feature_names else int(x))
     if quant is None:
-        if ctx.is_distributed:
-            quant = build_quantization(pool, int(o.border_count), o.feature_border_type, o.nan_mode,
-                                       o.per_float_feature_quantization, o.input_borders, seed=int(o.random_seed)) \
-                if ctx.rank == 0 else None
-            quant = ctx.broadcast_object(quant, 0)
-        else:
-            quant = build_quantization(pool, int(o.border_count), o.feature_border_type, o.nan_mode,
-                                       o.per_float_feature_quantization, o.input_borders, seed=int(o.random_seed))
+        quant = build_quantization(pool, int(o.border_count), o.feature_border_type, o.nan_mode,
+                                   o.per_float_feature_quantization, o.input_borders, seed=int(o.random_seed),
+                                   ctx=ctx if ctx.is_distributed else None)
     plan.quant = quant
     for j, c in enumerate(pool.float_feature_indices):
         if c in ignored or len(quant.borders[j]) == 0:

@@ -31,7 +31,7 @@ from ..parallel.runtime import ArenaLayout, DistContext, PeerArena, split_column
 
 SCORE_FN = {"Cosine": (0, 0), "L2": (1, 0), "NewtonCosine": (0, 1), "NewtonL2": (1, 1), "SolarL2": (2, 0),
             "LOOL2": (3, 0), "SatL2": (4, 0)}
-BOOTSTRAP = {"No": 0, "Bayesian": 1, "Bernoulli": 2, "Poisson": 3, "MVS": 2}
+BOOTSTRAP = {"No": 0, "Bayesian": 1, "Bernoulli": 2, "Poisson": 3}
 
 
 def _p(t):

@@ -81,7 +81,7 @@ def _use_fast_engine(o, objective, store, dims) -> bool:
     return (store.bins.is_cuda and o.grow_policy == "SymmetricTree" and (native or external) and dims == 1
             and o.boosting_type == "Plain" and o.leaf_estimation_method in ("Newton", "Gradient")
             and float(o.rsm) >= 1.0 and int(o.min_data_in_leaf) <= 1
-            and o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson") and bool(o.fused_levels or True)
+            and o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson")
             and not o.langevin and not o.monotone_constraints and not o.model_shrink_rate
             and str(o.random_score_type) != "Gumbel")
 

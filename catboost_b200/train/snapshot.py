@@ -3,16 +3,19 @@
 The reference stores models + metric history (not cursors) and re-applies the ensemble on restore
 (catboost/cuda/methods/boosting_progress_tracker.cpp:189-260, doc_parallel_boosting.h:500-512); the file is
 written to a temporary name and renamed atomically (catboost/libs/helpers/progress_helper.h:40-89).  The same
-contract is kept here; the payload is a pickle with a label, the options fingerprint and an md5 of the body.
+contract is kept here.  File layout: label line, 32 hex digits md5 of the body, body = a plain-data stream
+(``utils/plainser.py``: little-endian PODs with ui32 size prefixes in the manner of the reference's ysaveload
+streams) holding the options fingerprint and the state (trees as arrays, metric history, iteration list).  Reading
+a snapshot never executes anything stored in it.
 """
 from __future__ import annotations
 
 import hashlib
 import os
-import pickle
 import time
 
 from ..data.pool import CatBoostError
+from ..utils import plainser
 
 LABEL = b"catboost_b200_snapshot_v1\n"
 _FINGERPRINT_KEYS = ("loss_function", "depth", "learning_rate", "l2_leaf_reg", "border_count", "grow_policy",
@@ -44,13 +47,16 @@ class SnapshotManager:
         digest, body = blob[len(LABEL):len(LABEL) + 32], blob[len(LABEL) + 32:]
         if hashlib.md5(body).hexdigest().encode() != digest:
             raise CatBoostError(f"snapshot {self.path} is corrupted (checksum mismatch)")
-        payload = pickle.loads(body)
-        if payload["fingerprint"] != self.fp:
+        try:
+            payload = plainser.loads(body)
+        except (plainser.PlainDataError, UnicodeDecodeError) as e:
+            raise CatBoostError(f"snapshot {self.path} is unreadable: {e}") from e
+        if not isinstance(payload, dict) or payload.get("fingerprint") != self.fp:
             raise CatBoostError("snapshot was written with different training parameters")
         return payload["state"]
 
     def _write(self, state):
-        body = pickle.dumps({"fingerprint": self.fp, "state": state}, protocol=4)
+        body = plainser.dumps({"fingerprint": self.fp, "state": state})
         os.makedirs(os.path.dirname(os.path.abspath(self.path)), exist_ok=True)
         tmp = self.path + ".tmp"
         with open(tmp, "wb") as fh:

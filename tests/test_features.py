@@ -900,3 +900,38 @@ def test_coreml_export_decodes_to_the_same_trees(tmp_path):
     with pytest.raises(cb.CatBoostError):
         cb.CatBoostRegressor(iterations=2, depth=2, verbose=False, allow_writing_files=False).fit(X, y.astype(float)) \
             .save_model(str(path), format="coreml", export_parameters={"prediction_type": "probability"})
+
+
+def test_model_file_cannot_run_code_on_load(tmp_path):
+    """A .cbm whose text/embedding block was replaced by a pickle (or names a foreign class) is rejected and nothing
+    from it is executed; the plain-data container round-trips the values it is meant for."""
+    import base64
+    import pickle
+    from catboost_b200.data.pool import CatBoostError
+    from catboost_b200.models import io as mio
+    from catboost_b200.utils import plainser
+
+    state = {"a": [1, 2.5, "x", None, True], "t": (np.arange(6, dtype=np.int32).reshape(2, 3), b"raw"),
+             ("k", 1): np.float32(3.5)}
+    back = plainser.loads(plainser.dumps(state))
+    assert back["a"] == state["a"] and back["t"][1] == b"raw" and back[("k", 1)] == 3.5
+    assert back["t"][0].dtype == np.int32 and np.array_equal(back["t"][0], state["t"][0])
+    with pytest.raises(plainser.PlainDataError):
+        plainser.loads(plainser.dumps(state)[:-3])
+
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((300, 3)).astype(np.float32)
+    y = (X[:, 0] > 0).astype(int)
+    m = cb.CatBoostClassifier(iterations=3, depth=2, verbose=False, allow_writing_files=False).fit(X, y)
+    marker = tmp_path / "executed"
+
+    class Evil:
+        def __reduce__(self):
+            return (open, (str(marker), "w"))
+
+    for payload in (pickle.dumps(Evil()), plainser.dumps([1]).replace(b"\x07", b"\x0b", 1) + b"\x04\x00\x00\x00Evil"):
+        m._model.info["catboost_b200_estimators"] = base64.b64encode(payload).decode("ascii")
+        blob = mio.model_to_cbm_bytes(m._model)
+        with pytest.raises(CatBoostError):
+            mio.model_from_cbm_bytes(blob)
+        assert not marker.exists()
