@@ -317,6 +317,7 @@ def main():
     ap.add_argument("--reduce", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--cells", default="narrow", choices=["narrow", "wide", "float"],
                     help="shared-memory histogram cells: one int32, hi/lo int32 pair, or fp32")
+    ap.add_argument("--single-cells", action="store_true", help="time only the cell type given by --cells")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-iters", type=int, default=0,
                     help="boosting iterations of the end-to-end fit() (default 1000: the metric's own iteration count)")
@@ -374,53 +375,91 @@ def main():
     obj = make_objective("Logloss", {})
     p1 = float(y.mean())
     bias = float(np.log(p1 / (1 - p1)))
-    eng = GpuObliviousEngine(store, torch.from_numpy(y), None, torch.full((len(y),), bias), obj, depth=cfg["depth"],
-                             iterations=K + W, learning_rate=0.1, l2_leaf_reg=3.0, score_function=o.score_function,
-                             random_strength=float(o.random_strength), bootstrap_type=o.bootstrap_type,
-                             bootstrap_param=float(o.bagging_temperature or 1.0), leaf_method=o.leaf_estimation_method,
-                             leaf_iterations=int(o.leaf_estimation_iterations), seed=0, ctx=ctx, reduce=args.reduce,
-                             quantized_hist={"narrow": True, "wide": "wide", "float": False}[args.cells])
     flush = None if args.no_flush else torch.empty(512 << 20, dtype=torch.uint8, device=dev)
-    if args.phases and eng.plan:
-        eng.enable_phase_timing()
-    eng.step(W)
-    torch.cuda.synchronize(dev)
-    ctx.barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    for k in range(K):
-        if flush is not None:
-            flush.fill_(k & 0xFF)
+
+    def make_engine(cells, reduce, iterations):
+        return GpuObliviousEngine(store, torch.from_numpy(y), None, torch.full((len(y),), bias), obj, depth=cfg["depth"],
+                                  iterations=iterations, learning_rate=0.1, l2_leaf_reg=3.0, score_function=o.score_function,
+                                  random_strength=float(o.random_strength), bootstrap_type=o.bootstrap_type,
+                                  bootstrap_param=float(o.bagging_temperature or 1.0), leaf_method=o.leaf_estimation_method,
+                                  leaf_iterations=int(o.leaf_estimation_iterations), seed=0, ctx=ctx, reduce=reduce,
+                                  leaf_backtracking=str(o.leaf_estimation_backtracking or "AnyImprovement"),
+                                  quantized_hist={"narrow": True, "wide": "wide", "float": False}[cells])
+
+    def timed_run(cells, with_clocks):
+        """K timed iterations (CUDA events around each, L2 flushed before each, max over ranks of the sum)."""
+        eng = make_engine(cells, args.reduce, K + W)
+        if args.phases and eng.plan:
+            eng.enable_phase_timing()
+        eng.step(W)
+        torch.cuda.synchronize(dev)
+        ctx.barrier()
+        sampler = ClockSampler(local) if with_clocks else None
+        if sampler:
+            sampler.start()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+        for k in range(K):
+            if flush is not None:
+                flush.fill_(k & 0xFF)
+            if world > 1:
+                dist.barrier(device_ids=[local])
+            evs[k][0].record()
+            eng.step(1)
+            evs[k][1].record()
+        torch.cuda.synchronize(dev)
+        ctx.barrier()
+        clocks = sampler.stop() if sampler else None
+        t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], dtype=torch.float64, device=dev)
         if world > 1:
-            dist.barrier(device_ids=[local])
-        evs[k][0].record()
-        eng.step(1)
-        evs[k][1].record()
-    torch.cuda.synchronize(dev)
-    ctx.barrier()
-    clocks = sampler.stop()
-    total_ms = sum(a.elapsed_time(b) for a, b in evs)
-    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res = dict(total_ms=float(t.item()), clocks=clocks, launches=eng.launches_per_iter * K,
+                   loss_curve=eng.learn_loss_history(), splits=eng.splits[: 5 * cfg["depth"]].clone(),
+                   vals=eng.model_vals[:5].clone())
+        if args.phases and eng.plan and rank == 0:
+            np.set_printoptions(precision=1, suppress=True, linewidth=160)
+            print('phase us per level [leaf_update, hist, grid_wait, reduce_push, score, select]:\n', eng.phase_times_us(), file=sys.stderr)
+            print('inside score (block 0) [noise scale, first accumulate, rest]:\n', eng.score_phase_times_us(), file=sys.stderr)
+            bt, sm = eng.block_finish_times()
+            order = np.argsort(bt)
+            print('hist end per block (us) pct 0/10/50/90/100:', np.percentile(bt, [0, 10, 50, 90, 100]), file=sys.stderr)
+            print('slowest blocks (block, sm, us):', [(int(b), int(sm[b]), float(bt[b])) for b in order[-8:]], file=sys.stderr)
+        eng.finish()
+        if eng.arena is not None:
+            eng.arena.check_status()
+        eng.close()
+        del eng
+        return res
+
+    main_run = timed_run(args.cells, True)
+    total_ms, clocks, launches, loss_curve = (main_run[k] for k in ("total_ms", "clocks", "launches", "loss_curve"))
+    # the same steps with the other cell type (exact 24-bit hi/lo pairs when the headline run uses single int32 cells)
+    other_cells = "wide" if args.cells == "narrow" else "narrow"
+    other_run = None if args.single_cells else timed_run(other_cells, False)
+    # multi-GPU self-check after the timed region: the first trees are the same on every rank, and the same as those of
+    # the path that reduces the histograms with NCCL instead of the in-kernel peer stores
+    consistency = None
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
-    launches = eng.launches_per_iter * K
-    loss_curve = eng.learn_loss_history()
-    if args.phases and eng.plan and rank == 0:
-        np.set_printoptions(precision=1, suppress=True, linewidth=160)
-        print('phase us per level [leaf_update, hist, grid_wait, reduce_push, score, select]:\n', eng.phase_times_us(), file=sys.stderr)
-        print('inside score (block 0) [noise scale, first accumulate, rest]:\n', eng.score_phase_times_us(), file=sys.stderr)
-        bt, sm = eng.block_finish_times()
-        order = np.argsort(bt)
-        print('hist end per block (us) pct 0/10/50/90/100:', np.percentile(bt, [0, 10, 50, 90, 100]), file=sys.stderr)
-        print('slowest blocks (block, sm, us):', [(int(b), int(sm[b]), float(bt[b])) for b in order[-8:]], file=sys.stderr)
-        print('fastest blocks (block, sm, us):', [(int(b), int(sm[b]), float(bt[b])) for b in order[:8]], file=sys.stderr)
-    eng.finish()
-    if eng.arena is not None:
-        eng.arena.check_status()
-    eng.close()
-    del eng, store
+        sp = main_run["splits"].contiguous()
+        gathered = [torch.empty_like(sp) for _ in range(world)]
+        dist.all_gather(gathered, sp)
+        same_ranks = all(bool(torch.equal(g, gathered[0])) for g in gathered)
+        vl = main_run["vals"].contiguous()
+        gv = [torch.empty_like(vl) for _ in range(world)]
+        dist.all_gather(gv, vl)
+        same_vals = all(bool(torch.equal(g, gv[0])) for g in gv)
+        base = make_engine(args.cells, "nccl", 3)
+        base.step(3)
+        torch.cuda.synchronize(dev)
+        nb = 3 * cfg["depth"]
+        match = (base.splits[:nb, :2] == sp[:nb, :2]).all(1).float().mean()
+        leaf_diff = (base.model_vals[:3] - vl[:3]).abs().max()
+        base.finish()
+        base.close()
+        del base
+        consistency = {"first_5_trees_identical_on_all_ranks": bool(same_ranks and same_vals),
+                       "first_3_trees_splits_equal_to_nccl_path": float(match.item()),
+                       "first_3_trees_max_leaf_value_diff_vs_nccl_path": float(leaf_diff.item())}
+    del store
     torch.cuda.empty_cache()
 
     # ---------------- end to end through the public API -----------------------------------------------------------
@@ -473,7 +512,10 @@ def main():
         base = BASELINE_S_PER_1000.get(args.config)
         out = {"metric": "sec/1000 iters (device-timed, max over ranks)", "value": value, "unit": "s/1000iter",
                "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": False,
-               "scaling": "strong", "vs_baseline": (value / base) if base else None, "dtype": "fp32",
+               "scaling": "strong", "vs_baseline": (value / base) if base else None,
+               "dtype": {"narrow": "fp32 statistics, histogram cells int32 fixed point (13-16 bit addends, exact integer sums)",
+                         "wide": "fp32 statistics, histogram cells 24-bit fixed point in int32 hi/lo pairs (exact integer sums)",
+                         "float": "fp32"}[args.cells],
                "data": "synthetic", "impl": "ours",
                "config": {"model": cfg["model"], "global_batch": cfg["rows"], "seq_len": cfg["features"],
                           "parallelism": f"doc-parallel dp{world}", "loss": "Logloss", "depth": cfg["depth"],
@@ -481,6 +523,10 @@ def main():
                           "l2_policy": ("flush: 512 MiB write between timed iterations" if flush is not None
                                         else "inputs larger than L2")},
                "clocks": clocks, "e2e": e2e, "apply": apply_info, "gpu_launches": launches,
+               "other_cells": (None if other_run is None else
+                               {"histogram_cells": other_cells, "value": other_run["total_ms"] / K, "unit": "s/1000iter",
+                                "learn_loss_last": float(other_run["loss_curve"][-1])}),
+               "multi_gpu_consistency": consistency,
                "learn_loss_first_last": [float(loss_curve[1]) if len(loss_curve) > 1 else None, float(loss_curve[-1])]}
         print(json.dumps(out))
     if world > 1:

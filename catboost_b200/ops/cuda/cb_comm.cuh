@@ -49,3 +49,45 @@ static __device__ void cb_mailbox_allreduce_sum(const CbComm& c, double* vals, i
     __syncthreads();
 }
 
+
+// ---- tagged words ("low latency" messages) ---------------------------------------------------------------
+// A 32-bit payload travels together with a 32-bit tag in one 8-byte store, which is single-copy atomic also through
+// a peer mapping: the reader polls the word itself until the tag is the one it expects, so a message needs neither
+// a system-scope fence nor a separate flag (one NVLink hop instead of store + fence + flag + poll).  The tag is the
+// low half of a monotonically increasing epoch, never 0; buffers start out zeroed.  A buffer may only be rewritten
+// when every reader of its previous content is known to be done (the callers alternate two parities and rely on the
+// fact that a rank cannot run more than one exchange ahead of a peer it needs an answer from).
+__device__ __forceinline__ void cb_ll_store(unsigned long long* dst, unsigned int payload, unsigned int tag) {
+    const unsigned long long v = ((unsigned long long)tag << 32) | (unsigned long long)payload;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long cb_ll_peek(const unsigned long long* src) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(src) : "memory");
+    return v;
+}
+// Payload of the word once its tag is `tag`.  Bounded: after timeout_ns the status word is set and 0 is returned.
+__device__ __forceinline__ unsigned int cb_ll_load(const unsigned long long* src, unsigned int tag, long long timeout_ns,
+                                                   int* status, int code, int detail) {
+    unsigned long long v = cb_ll_peek(src);
+    if ((unsigned int)(v >> 32) == tag) return (unsigned int)v;
+    const unsigned long long t0 = cb_globaltimer();
+    unsigned int spins = 0;
+    for (;;) {
+        v = cb_ll_peek(src);
+        if ((unsigned int)(v >> 32) == tag) return (unsigned int)v;
+        if ((++spins & 63u) == 0u && (long long)(cb_globaltimer() - t0) > timeout_ns) {
+            if (atomicCAS(status, CB_OK, code) == CB_OK) status[1] = detail;
+            return 0u;
+        }
+    }
+}
+// Tag of an epoch: never 0, so a zero-filled buffer never looks delivered.
+__device__ __forceinline__ unsigned int cb_ll_tag(unsigned long long epoch) {
+    const unsigned int t = (unsigned int)epoch;
+    return t ? t : 0x80000000u;
+}
+// Mailbox area of (parity, source rank) in rank `owner`'s arena, as tagged words.
+__device__ __forceinline__ unsigned long long* cb_ll_box(const CbComm& c, int owner, int parity, int src) {
+    return reinterpret_cast<unsigned long long*>(c.peer_mbox[owner] + (size_t)(parity * c.nranks + src) * c.mbox_bytes);
+}

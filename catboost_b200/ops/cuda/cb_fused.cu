@@ -1,13 +1,15 @@
 // K6 fused level kernel: ONE cooperative launch per tree level does
-//   (0) the leaf-index update for the split chosen at the previous level,
-//   (A) streaming histogram accumulation of the local rows (shared-memory fp32 atomics, one slot per parent
+//   (0) the leaf-index update for the split chosen at the previous level (inside the histogram pass when the
+//       bundled path runs: the pass has the bin words of its documents in registers anyway),
+//   (A) streaming histogram accumulation of the local rows (shared-memory integer atomics, one slot per parent
 //       leaf: only the lighter child is accumulated, the sibling is parent - child),
-//   (B) the reduce-scatter: every rank stores the feature slice that rank r owns straight into rank r's
-//       slot buffer over NVLink (16-byte peer stores) and raises a system-scope arrival tag,
-//   (C) on the owner: bounded wait for the tags, sum of the per-source slots in rank order (deterministic),
-//       sibling subtraction, bin prefix scan, split scoring, packed 64-bit atomicMax argmax,
-//   (D) an 8-way exchange of the per-rank best (key + lighter-child mask) through the peer mailboxes and the
-//       final argmax, which every rank evaluates identically.
+//   (B) the reduce-scatter: every rank sums its chunk tiles and stores the feature slice that rank r owns straight
+//       into rank r's slot buffer over NVLink as tagged 8-byte words (value + level tag),
+//   (C) on the owner: the score phase polls the words it needs until they carry this level's tag (bounded), sums the
+//       per-source slots in rank order (deterministic), sibling subtraction, bin prefix scan, split scoring, packed
+//       64-bit atomicMax argmax -- no fence, flag or grid barrier stands between (B) and (C),
+//   (D) an exchange of the per-rank best (key + lighter-child mask) as tagged words through the peer mailboxes and
+//       the final argmax, which every rank evaluates identically.
 // No NCCL call, no host round trip and no separate scoring kernel per level.  This replaces the reference's
 // four-step path: histogram kernel -> GatherHistogramsByLeaves -> host-orchestrated ReduceScatter built from
 // cudaMemcpyAsync + add kernel -> FindOptimalSplit -> device-to-host read + host argmin
@@ -32,6 +34,9 @@ struct CbFusedArgs {
     CbSplit* splits; int depth;
     unsigned int* mask_out;          // lighter-child mask for the next level
     unsigned long long* msg_local;   // CB_SELECT_MSG_BYTES scratch in local memory
+    unsigned long long* msg_stage;   // [nranks][msg_stage_stride] words: the peers' messages, unpacked from the mailbox
+    int msg_stage_stride;
+    int fuse_leaf;                   // 1: the histogram pass of this launch also applies the previous level's split
     int own_col[CB_MAX_RANKS + 1];   // rank r owns histogram columns [own_col[r], own_col[r+1]) (multiples of 4)
     int Wmax;                        // row stride (floats) of every slot buffer = max owned width
     int smem_floats;                 // dynamic shared memory of this launch, in floats
@@ -43,7 +48,7 @@ struct CbFusedArgs {
 // group of one (slot, statistic) row.  At the shallow levels there are few units and many chunks (a bundle of all
 // groups is cut into as many chunks as there are blocks), so the chunks of a unit are dealt to KS lanes of a warp
 // (KS a power of two <= 32, as many as the grid has spare threads for) and combined with shuffles.
-static __device__ void cb_reduce_chunks(const CbFusedArgs& a, int cta, int ncta) {
+static __device__ void cb_reduce_chunks(const CbFusedArgs& a, int cta, int ncta, unsigned int ll_tag) {
     const CbHistArgs& h = a.h;
     const int G = h.d.G, S = h.S, B = h.B, TB = h.d.TB;
     const int nK = cb_hist_chunks(G, ncta, h.d.n, h.nK);
@@ -89,11 +94,21 @@ static __device__ void cb_reduce_chunks(const CbFusedArgs& a, int cta, int ncta)
             acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
         }
         if (valid && ks == 0) {
-            int r = 0;
-            if (R > 1) { while (r + 1 < R && col >= a.own_col[r + 1]) ++r; }
-            float* dst = (R > 1 ? a.c.peer_slot[r] + (size_t)me * a.c.slot_floats : const_cast<float*>(a.s.hsrc[0]))
-                         + (size_t)row * a.Wmax + (col - a.own_col[r]);
-            *reinterpret_cast<float4*>(dst) = acc;
+            if (R > 1) {
+                // tagged words: {value, level tag} pairs, two per 16-byte store (each 8-byte half is atomic on its own)
+                int r = 0;
+                while (r + 1 < R && col >= a.own_col[r + 1]) ++r;
+                unsigned long long* dst = reinterpret_cast<unsigned long long*>(a.c.peer_slot[r] + (size_t)me * a.c.slot_floats)
+                                          + (size_t)row * a.Wmax + (col - a.own_col[r]);
+                const unsigned long long t = (unsigned long long)ll_tag << 32;
+                const unsigned long long w0 = t | __float_as_uint(acc.x), w1 = t | __float_as_uint(acc.y);
+                const unsigned long long w2 = t | __float_as_uint(acc.z), w3 = t | __float_as_uint(acc.w);
+                asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(dst), "l"(w0), "l"(w1) : "memory");
+                asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(dst + 2), "l"(w2), "l"(w3) : "memory");
+            } else {
+                float* dst = const_cast<float*>(a.s.hsrc[0]) + (size_t)row * a.Wmax + col;
+                *reinterpret_cast<float4*>(dst) = acc;
+            }
         }
     }
 }
@@ -107,9 +122,13 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
     CbSplit* sp_arr = a.splits + (long long)it * a.depth;
     unsigned long long* ts = (a.phase_ts && cta == 0 && threadIdx.x == 0) ? a.phase_ts + level * 8 : nullptr;
     if (ts) ts[0] = cb_globaltimer();
+    const int R = a.c.nranks, me = a.c.rank;
+    // every block reads the level counter before the first grid barrier; block 0 advances it at the very end
+    const unsigned long long hist_epoch = (R > 1) ? a.c.epoch[1] + 1 : 0ull;
+    const unsigned int ll_tag = (R > 1) ? cb_ll_tag(hist_epoch) : 0u;
 
-    // (0) leaf update with the split of the previous level
-    if (level > 0) {
+    // (0) leaf update with the split of the previous level: its own pass, unless the histogram pass does it
+    if (level > 0 && !a.fuse_leaf) {
         cb_update_leaf_range(a.h.d, a.leaf, sp_arr[level - 1], level - 1,
                              (long long)cta * blockDim.x + threadIdx.x, (long long)ncta * blockDim.x);
         __threadfence();
@@ -136,22 +155,13 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
     // (B) chunk reduction fused with the reduce-scatter: each 16-byte column group is summed over the chunks of
     // this rank and stored straight into the slot of the rank that owns the column (peer store over NVLink when
     // that is another GPU; every source keeps its own slot, so the owner later adds them in rank order).
-    const int R = a.c.nranks, me = a.c.rank;
-    const unsigned long long hist_epoch = (R > 1) ? a.c.epoch[1] + 1 : 0ull;
-    cb_reduce_chunks(a, cta, ncta);
-    if (R > 1) {
-        __threadfence_system();
-        grid.sync();
-        if (cta == 0 && threadIdx.x < R) cb_st_release_sys(a.c.peer_slot_flag[threadIdx.x] + me, hist_epoch);
-        // (C) wait until every source has delivered this level
-        if (threadIdx.x < R)
-            cb_wait_flag(a.c.peer_slot_flag[me] + threadIdx.x, hist_epoch, a.c.timeout_ns, a.c.status,
-                         CB_TIMEOUT_HIST_ARRIVE, (int)threadIdx.x);
-        __syncthreads();
-    } else {
+    cb_reduce_chunks(a, cta, ncta, ll_tag);
+    if (R <= 1) {
         __threadfence();
         grid.sync();
     }
+    // several ranks: (C) needs no barrier here, the words announce themselves and the score phase polls exactly those
+    // it reads (a.s.ll_epoch is set by the host)
 
     if (ts) ts[4] = cb_globaltimer();
     cb_score_phase(a.s, cta, ncta, cb_sh, a.smem_floats, ts ? a.phase_ts + a.depth * 8 + 8192 + level * 4 : nullptr,
@@ -167,17 +177,35 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
         __syncthreads();
         const unsigned long long* msgs[CB_MAX_RANKS];
         if (R > 1) {
-            const int bytes = 8 + 4 * (((1 << level) + 31) >> 5);
-            unsigned long long epoch;
-            cb_mailbox_exchange(a.c, a.msg_local, bytes, &epoch);
-            for (int r = 0; r < R; ++r) msgs[r] = reinterpret_cast<const unsigned long long*>(cb_mailbox_msg(a.c, epoch, r));
+            // key (two words) + mask words, each as a tagged word into every rank's mailbox; then unpack the R messages
+            // that arrived here into the staging rows
+            __shared__ unsigned long long s_epoch;
+            if (threadIdx.x == 0) { s_epoch = a.c.epoch[0] + 1; a.c.epoch[0] = s_epoch; }
+            __syncthreads();
+            const unsigned long long epoch = s_epoch;
+            const unsigned int tag = cb_ll_tag(epoch);
+            const int parity = (int)(epoch & 1ull);
+            const int nw = 2 + (((1 << level) + 31) >> 5);
+            const unsigned int* src = reinterpret_cast<const unsigned int*>(a.msg_local);
+            for (int idx = threadIdx.x; idx < nw * R; idx += blockDim.x) {
+                const int r = idx / nw, i = idx - r * nw;
+                cb_ll_store(cb_ll_box(a.c, r, parity, me) + i, src[i], tag);
+            }
+            for (int idx = threadIdx.x; idx < nw * R; idx += blockDim.x) {
+                const int r = idx / nw, i = idx - r * nw;
+                reinterpret_cast<unsigned int*>(a.msg_stage + (size_t)r * a.msg_stage_stride)[i] =
+                    cb_ll_load(cb_ll_box(a.c, me, parity, r) + i, tag, a.c.timeout_ns, a.c.status, CB_TIMEOUT_MAILBOX, r);
+            }
+            __threadfence();
+            __syncthreads();
+            for (int r = 0; r < R; ++r) msgs[r] = a.msg_stage + (size_t)r * a.msg_stage_stride;
         } else {
             msgs[0] = a.msg_local;
         }
         cb_select_final(a.h.d, msgs, R, level, sp_arr + level, a.mask_out);
         if (threadIdx.x == 0) {
             *a.s.best_key = 0ull;
-            if (R > 1) a.c.epoch[1] = a.c.epoch[1] + 1;
+            if (R > 1) a.c.epoch[1] = hist_epoch;
             if (ts) ts[6] = cb_globaltimer();
         }
         if (a.h.work) {
@@ -194,6 +222,7 @@ struct CbFusedPlan {
     int sm_smem;       // shared memory of one SM available to two resident blocks (after their static + reserved parts)
     int sm_count;
     int max_bundle;    // widest feature-group bundle of the single-cell histogram path (0 = off)
+    int fuse_leaf_update;   // 1: let the bundled histogram pass apply the previous level's split (default)
     int max_copies;    // most replicas of a histogram cell (2 for dense columns; more when one bin dominates a column,
                        // where most lanes of a warp would otherwise add to the same cell)
 };
@@ -203,7 +232,8 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
                                     const int* own_col, int Wmax, unsigned int* mask0, unsigned int* mask1,
                                     CbSplit* splits, int depth, float l2, int score_fn, float random_strength,
                                     const double* scal, const int* iter_ptr, unsigned long long seed, float lr,
-                                    unsigned long long* best_key, unsigned long long* msg_local, int threads) {
+                                    unsigned long long* best_key, unsigned long long* msg_local,
+                                    unsigned long long* msg_stage, int msg_stage_stride, int threads) {
     CbFusedPlan* p = new (std::nothrow) CbFusedPlan();
     if (!p) return nullptr;
     CbFusedArgs& a = p->a;
@@ -228,6 +258,9 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     a.s.random_strength = random_strength; a.s.scal = scal; a.s.iter_ptr = iter_ptr; a.s.seed = seed;
     a.s.learning_rate = lr; a.s.best_key = best_key;
     a.leaf = leaf; a.splits = splits; a.depth = depth; a.mask_out = mask1; a.msg_local = msg_local;
+    a.msg_stage = msg_stage; a.msg_stage_stride = msg_stage_stride; a.fuse_leaf = 0;
+    a.h.prev_splits = nullptr; a.h.prev_iter = iter_ptr; a.h.prev_depth = depth; a.h.leaf_rw = leaf;
+    a.s.ll_epoch = R > 1 ? a.c.epoch + 1 : nullptr; a.s.ll_timeout_ns = a.c.timeout_ns; a.s.ll_status = a.c.status;
     p->threads = threads;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -241,6 +274,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     p->sm_smem -= 2 * (int)fa.sharedSizeBytes;
     p->max_bundle = 0;
     p->max_copies = 2;
+    p->fuse_leaf_update = 1;
     if (cudaFuncSetAttribute(cb_level_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, p->max_smem) != cudaSuccess) {
         cudaGetLastError();
         delete p;
@@ -249,6 +283,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     return p;
 }
 
+CB_API void cb_fused_set_fuse_leaf(CbFusedPlan* p, int on) { p->fuse_leaf_update = on ? 1 : 0; }
 CB_API void cb_fused_set_phase_ts(CbFusedPlan* p, unsigned long long* ts) { p->a.phase_ts = ts; }
 CB_API void cb_fused_set_work(CbFusedPlan* p, unsigned int* work) { p->a.h.work = work; }
 CB_API void cb_fused_set_narrow(CbFusedPlan* p, int narrow, int max_bundle) {
@@ -324,6 +359,12 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
         }
         smem = spp * per_slot * C + ring_bytes;
     }
+    // the score phase reuses the tile as scratch: CB_SCORE_WARP_FLOATS floats per scoring warp, at least 8 warps' worth
+    // (a small tile -- few bins, one slot -- would otherwise leave it without a single warp)
+    {
+        const int want = (thr / 32 < 8 ? thr / 32 : 8) * CB_SCORE_WARP_FLOATS * 4;
+        if (smem < want) smem = want;
+    }
     int occ = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, cb_level_fused_kernel, thr, smem) != cudaSuccess) { cudaGetLastError(); return 0; }
     if (occ < 1) return 0;
@@ -363,6 +404,12 @@ CB_API int cb_fused_launch(CbFusedPlan* p, int level, float* hprev, float* hcur,
     a.s.level = level; a.s.small_mask = mask_in; a.s.hprev = hprev; a.s.hcur = hcur;
     a.mask_out = mask_out;
     a.smem_floats = smem_bytes / 4;
+    // the bundled histogram pass can apply the previous level's split itself (see CbHistArgs::prev_split)
+    // ... when one bundle holds every feature group: then the split feature's bin word is already in registers and each
+    // document is streamed by exactly one block.  With several bundles each of them would have to fetch that word as
+    // well, which costs more than the separate pass (measured at 10.5M x 28, level 5, 4 bundles: +86 us against 18 us).
+    a.fuse_leaf = (level > 0 && bundle >= a.h.d.G && a.h.statmax && a.h.S == 2 && a.h.narrow && p->fuse_leaf_update) ? 1 : 0;
+    a.h.prev_splits = a.fuse_leaf ? a.splits : nullptr;
     void* args[] = {&a};
     cudaError_t e = cudaLaunchCooperativeKernel((void*)cb_level_fused_kernel, dim3(grid), dim3(threads), args,
                                                 (size_t)smem_bytes, st);

@@ -330,7 +330,7 @@ CB_API int cb_hist_n(const CbData* d, const unsigned short* leaf, const float* s
 static int cb_hist_launch(const CbData* d, const unsigned short* leaf, const float* stats, int S, int level,
                           const unsigned int* small_mask, const short* slot_table, int nslots_table, int slots_per_pass,
                           int B, float* out, const float* statmax, int grid, int threads, cudaStream_t st) {
-    CbHistArgs a;
+    CbHistArgs a = CbHistArgs();
     a.d = *d; a.leaf = leaf; a.stats = stats; a.S = S; a.level = level; a.small_mask = small_mask;
     a.slots_per_pass = slots_per_pass; a.B = B; a.out = out; a.slot_table = slot_table; a.nslots_table = nslots_table;
     a.priv = nullptr; a.statmax = statmax; a.nK = 0; a.copies = 1; a.work = nullptr; a.narrow = 0; a.bundle = 0;
@@ -378,7 +378,7 @@ CB_API int cb_score(const CbData* d, const float* const* hsrc, int nsrc, const f
                     int col_base, int f_begin, int f_end, int level, int S, const unsigned int* small_mask, float l2,
                     int score_fn, float random_strength, const double* scal, const int* iter_ptr,
                     unsigned long long seed, float lr, unsigned long long* best_key, cudaStream_t st) {
-    CbScoreArgs a;
+    CbScoreArgs a = CbScoreArgs();
     cb_fill_score_args(a, d, hsrc, nsrc, hprev, hcur, W, col_base, f_begin, f_end, level, S, small_mask, l2, score_fn,
                        random_strength, scal, iter_ptr, seed, lr, best_key);
     const int nf = f_end - f_begin;
@@ -395,7 +395,7 @@ __global__ void __launch_bounds__(256) cb_select_local_kernel(CbScoreArgs a, uns
 
 CB_API int cb_select_local_launch(const CbData* d, float* hcur, int W, int col_base, int level, int S,
                                   unsigned long long* best_key, unsigned long long* msg, cudaStream_t st) {
-    CbScoreArgs a;
+    CbScoreArgs a = CbScoreArgs();
     const float* none[1] = {nullptr};
     cb_fill_score_args(a, d, none, 0, nullptr, hcur, W, col_base, 0, 0, level, S, nullptr, 0.f, 0, 0.f, nullptr, nullptr,
                        0ull, 0.f, best_key);

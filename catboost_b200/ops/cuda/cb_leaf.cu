@@ -1,12 +1,22 @@
 // Leaf values of one oblivious tree in ONE cooperative launch: all Newton / gradient steps of the leaf estimation
 // (catboost/cuda/methods/leaves_estimation/*, catboost/private/libs/algo/approx_calcer.cpp) run back to back inside
-// the kernel, separated by grid barriers, instead of one launch per step.
+// the kernel, separated by ONE grid barrier per step, instead of one launch (and one host round trip) per step.
 //
 // A step: every block streams its documents (approx, target, leaf -- the same ones in every step, so from the second
-// step on they mostly come out of L2), evaluates the objective's derivatives at approx + delta[leaf], accumulates
-// per-leaf sums in lane-replicated shared-memory cells, adds them into the global double accumulators; after a grid
-// barrier block 0 all-reduces the sums over the ranks through the peer mailboxes, takes the step and publishes the new
-// delta; a second grid barrier releases the other blocks into the next step.
+// step on they mostly come out of L2), evaluates the objective at approx + delta[leaf], accumulates per-leaf sums in
+// lane-replicated shared-memory cells and adds them into the global double accumulators of the step (three rotating
+// copies).  After the grid barrier the sums of this rank are complete.  With several ranks block 0 then sends them to
+// every rank as tagged words (cb_comm.cuh) and EVERY block polls the R messages in its own arena and adds them in rank
+// order; with one rank every block reads the accumulators directly.  Either way each block takes the Newton step
+// itself, in shared memory, with bit-identical arithmetic, so no second barrier and no single-block serial section
+// is needed.
+//
+// Step-length control (leaf_estimation_backtracking, catboost/cuda/methods/leaves_estimation/descent_helpers.cpp:127-206,
+// step_estimator.cpp): every pass also sums the loss at the point it evaluates.  A pass whose point does not satisfy
+// the condition (AnyImprovement: the loss did not get worse; Armijo: sufficient decrease, C = 1e-5) is not accepted:
+// the next pass evaluates base + (step / 2) * direction instead.  As in the reference a rejected try uses up one of
+// the leaf_estimation_iterations; unlike the reference the move taken after the last pass is not verified (the
+// reference spends an extra pass on that).
 //
 // Cells: the first step uses fp32 cells (shared fp32 atomics are compare-and-swap loops, but the scale of the values
 // is not known yet) and records max |w der|, max |w hess|; later steps use fixed point with native integer atomics:
@@ -20,12 +30,14 @@
 
 namespace cg = cooperative_groups;
 
+enum CbBacktrack : int { CB_BT_NONE = 0, CB_BT_ANY_IMPROVEMENT = 1, CB_BT_ARMIJO = 2 };
+
 struct CbLeafNewtonArgs {
     int loss; float p0, p1;
     const float* approx; const float* target; const float* weight; const unsigned short* leaf;
     long long n; int L;
     float* delta;            // [L] running leaf values of this tree (unscaled); written by block 0
-    double* sums;            // [3][L][3] zero on entry, zero on exit (one rank rotates through the three copies)
+    double* sums;            // [3][3L + 4] zero on entry, zero on exit: per leaf (der, hess, weight), then the loss sum
     unsigned int* counter;   // zero on entry / exit
     float* vmax;             // [2] zero on entry, zero on exit
     int steps, newton;
@@ -33,6 +45,7 @@ struct CbLeafNewtonArgs {
     float* cur_vals;         // [L] lr * delta after the last step
     float* model_vals; float* model_wts; int Lstride; const int* iter_ptr;
     float* leaf_w;           // [L] per-leaf weight sums
+    int backtrack;           // CbBacktrack
     CbComm c;
 };
 
@@ -45,10 +58,17 @@ __device__ __forceinline__ void cb_leaf_docs_load(const CbLeafNewtonArgs& a, lon
     if (a.weight) v.w4 = __ldcg(reinterpret_cast<const float4*>(a.weight + i0));
 }
 
-// C = replicas of every cell (lane l uses replica l & (C-1)), a power of two <= 32.
-template <int LOSS>
+__device__ __forceinline__ double cb_ll_load_double(const unsigned long long* box, int i, unsigned int tag,
+                                                    const CbComm& c, int src) {
+    const unsigned int lo = cb_ll_load(box + 2 * i, tag, c.timeout_ns, c.status, CB_TIMEOUT_MAILBOX, src);
+    const unsigned int hi = cb_ll_load(box + 2 * i + 1, tag, c.timeout_ns, c.status, CB_TIMEOUT_MAILBOX, src);
+    return __longlong_as_double((long long)(((unsigned long long)hi << 32) | lo));
+}
+
+// C = replicas of every cell (lane l uses replica l & (C-1)), a power of two <= 32.  BT = step-length control compiled in.
+template <int LOSS, bool BT>
 __global__ void __launch_bounds__(512, 2) cb_leaf_newton_kernel(CbLeafNewtonArgs a, int C) {
-    extern __shared__ float sl[];                 // cells: [L][4][C]; then delta copy: [L]
+    extern __shared__ float sl[];                 // cells: [L][4][C]; then delta, leaf weights, base point, direction: [L] each
     cg::grid_group grid = cg::this_grid();
     const int loss = LOSS >= 0 ? LOSS : a.loss;
     const int L = a.L;
@@ -56,16 +76,22 @@ __global__ void __launch_bounds__(512, 2) cb_leaf_newton_kernel(CbLeafNewtonArgs
     int* si = reinterpret_cast<int*>(sl);
     float* sdelta = sl + (size_t)4 * L * C;
     float* sleafw = sdelta + L;
-    // One rank: every block takes the Newton step itself from the complete sums, so a step needs a single grid barrier.
-    // The sums rotate through three copies; block 0 clears the copy of step s + 2 after the barrier of step s, when
-    // nobody can still be reading it and nobody can already be adding to it.
-    const bool solo = a.c.nranks <= 1;
+    float* sbase = sleafw + L;
+    float* sdir = sbase + L;
+    __shared__ double s_red[16];
+    __shared__ double s_value;
+    const int R = a.c.nranks, me = a.c.rank;
+    const bool solo = R <= 1;
+    const unsigned long long epoch0 = solo ? 0ull : *a.c.epoch;      // every block reads it before the first barrier
+    const int SS = 3 * L + 4;                                        // doubles per copy of the accumulators
     const long long n4 = (a.n + 3) >> 2;
     const long long stride = (long long)gridDim.x * blockDim.x;
     const bool can_quant = (a.n / gridDim.x) < (1ll << 22);
     // documents one replica of a cell can receive: those of the threads that share the replica index
     const long long per_thread = ((n4 + stride - 1) / stride) * 4;
     const float qcap = fminf(8388607.0f, floorf(2147483647.0f / (float)(per_thread * (blockDim.x / C) + 1)) - 1.0f);
+    double f_base = 0.0, dirgrad = 0.0;           // loss and gradient . direction at the last accepted point
+    float cur_step = 1.0f;
     for (int step = 0; step < a.steps; ++step) {
         const bool first = step == 0, last = step == a.steps - 1;
         const bool quant = !first && can_quant;
@@ -76,12 +102,12 @@ __global__ void __launch_bounds__(512, 2) cb_leaf_newton_kernel(CbLeafNewtonArgs
             sc0 = qcap / M0;
             sc1 = qcap / M1;
         }
-        double* S = a.sums + (solo ? (size_t)(step % 3) * 3 * L : 0);
+        double* S = a.sums + (size_t)(step % 3) * SS;
         for (int i = threadIdx.x; i < 4 * L * C; i += blockDim.x) sl[i] = 0.0f;
-        if (!solo || first)
-            for (int i = threadIdx.x; i < L; i += blockDim.x) sdelta[i] = first ? 0.0f : __ldcg(a.delta + i);
+        if (first)
+            for (int i = threadIdx.x; i < L; i += blockDim.x) { sdelta[i] = 0.0f; sbase[i] = 0.0f; sdir[i] = 0.0f; }
         __syncthreads();
-        float mx0 = 0.f, mx1 = 0.f;
+        float mx0 = 0.f, mx1 = 0.f, vsum = 0.f;
         long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x;
         CbLeafDocs nx;
         nx.a4 = nx.t4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -102,6 +128,7 @@ __global__ void __launch_bounds__(512, 2) cb_leaf_newton_kernel(CbLeafNewtonArgs
                 const CbLossOut o = cb_loss_eval(loss, a.p0, a.p1, ap[k] + sdelta[l], tg[k]);
                 const float w = wt[k];
                 const float vd = w * o.der, vh = w * o.hess;
+                if (BT) vsum += w * o.value;
                 if (quant) {
                     if (fmaxf(fabsf(vd) * sc0, fabsf(vh) * sc1) <= qcap) {
                         int* cell = si + (size_t)(l * 4) * C + lane_copy;
@@ -133,7 +160,16 @@ __global__ void __launch_bounds__(512, 2) cb_leaf_newton_kernel(CbLeafNewtonArgs
                 atomicMax(reinterpret_cast<int*>(a.vmax) + 1, __float_as_int(mx1));
             }
         }
+        if (BT) {
+            double dv = cb_warp_sum_d((double)vsum);
+            if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = dv;
+        }
         __syncthreads();
+        if (BT && threadIdx.x == 0) {
+            double t = 0.0;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += s_red[w];
+            if (t != 0.0) atomicAdd(&S[3 * L], t);
+        }
         if (quant) {
             const double inv0 = (double)M0 / (double)qcap, inv1 = (double)M1 / (double)qcap;
             for (int i = threadIdx.x; i < 2 * L; i += blockDim.x) {
@@ -147,101 +183,146 @@ __global__ void __launch_bounds__(512, 2) cb_leaf_newton_kernel(CbLeafNewtonArgs
             for (int i = threadIdx.x; i < 3 * L; i += blockDim.x) {
                 const int l = i / 3, s3 = i - 3 * l;
                 if (s3 == 2 && !first) continue;
-                float vsum = 0.0f;
-                for (int c = 0; c < C; ++c) vsum += sl[(size_t)(l * 4 + s3) * C + c];
-                if (vsum != 0.0f) atomicAdd(&S[i], (double)vsum);
+                float vs = 0.0f;
+                for (int c = 0; c < C; ++c) vs += sl[(size_t)(l * 4 + s3) * C + c];
+                if (vs != 0.0f) atomicAdd(&S[i], (double)vs);
             }
         }
         __threadfence();
         grid.sync();
-        if (solo) {
-            const int it = *a.iter_ptr;
-            for (int l = threadIdx.x; l < L; l += blockDim.x) {
-                const double sd = __ldcg(&S[3 * l]), shs = __ldcg(&S[3 * l + 1]);
-                if (first) sleafw[l] = (float)__ldcg(&S[3 * l + 2]);
-                const double sw = (double)sleafw[l];
-                const double den = (a.newton ? shs : sw) + (double)a.l2;
-                const float stp = (den > 0.0) ? (float)(sd / den) : 0.0f;
-                const float v = sdelta[l] + stp;
-                sdelta[l] = v;
-                if (blockIdx.x == 0) {
-                    a.delta[l] = v;
-                    if (first) a.leaf_w[l] = sleafw[l];
-                    if (last) {
-                        a.cur_vals[l] = a.lr * v;
-                        if (a.model_vals) a.model_vals[(long long)it * a.Lstride + l] = a.lr * v;
-                        if (a.model_wts) a.model_wts[(long long)it * a.Lstride + l] = (float)sw;
+        // ---- the sums of this rank are complete -------------------------------------------------------------
+        const unsigned long long epoch = epoch0 + (unsigned long long)step + 1ull;
+        const unsigned int tag = cb_ll_tag(epoch);
+        const int parity = (int)(epoch & 1ull);
+        if (!solo && blockIdx.x == 0) {
+            // one tagged copy of (der, hess[, weight]) per leaf and of the loss sum to every rank, this one included
+            const int cnt = 3 * L + 1;
+            for (int idx = threadIdx.x; idx < cnt * R; idx += blockDim.x) {
+                const int r = idx / cnt, i = idx - r * cnt;
+                if (i < 3 * L && (i % 3) == 2 && !first) continue;
+                const unsigned long long bits = (unsigned long long)__double_as_longlong(__ldcg(&S[i]));
+                unsigned long long* box = cb_ll_box(a.c, r, parity, me);
+                cb_ll_store(box + 2 * i, (unsigned int)bits, tag);
+                cb_ll_store(box + 2 * i + 1, (unsigned int)(bits >> 32), tag);
+            }
+        }
+        if (threadIdx.x == 0) {
+            double v = 0.0;
+            if (BT) {
+                if (solo) v = __ldcg(&S[3 * L]);
+                else for (int r = 0; r < R; ++r) v += cb_ll_load_double(cb_ll_box(a.c, me, parity, r), 3 * L, tag, a.c, r);
+            }
+            s_value = v;
+        }
+        __syncthreads();
+        bool accept = true;
+        if (BT && !first) {
+            const double v = s_value;
+            accept = (a.backtrack == CB_BT_ARMIJO) ? (v <= f_base - 1e-5 * (double)cur_step * dirgrad) : (v <= f_base);
+            if (!(v == v)) accept = false;
+        }
+        const int it = *a.iter_ptr;
+        double dg = 0.0;
+        for (int l = threadIdx.x; l < L; l += blockDim.x) {
+            float nd;
+            if (accept) {
+                double sd = 0.0, shs = 0.0, sw = 0.0;
+                if (solo) {
+                    sd = __ldcg(&S[3 * l]); shs = __ldcg(&S[3 * l + 1]);
+                    if (first) sw = __ldcg(&S[3 * l + 2]);
+                } else {
+                    for (int r = 0; r < R; ++r) {
+                        const unsigned long long* box = cb_ll_box(a.c, me, parity, r);
+                        sd += cb_ll_load_double(box, 3 * l, tag, a.c, r);
+                        shs += cb_ll_load_double(box, 3 * l + 1, tag, a.c, r);
+                        if (first) sw += cb_ll_load_double(box, 3 * l + 2, tag, a.c, r);
                     }
                 }
+                if (first) sleafw[l] = (float)sw;
+                const double den = (a.newton ? shs : (double)sleafw[l]) + (double)a.l2;
+                const float dir = (den > 0.0) ? (float)(sd / den) : 0.0f;
+                if (BT) { sbase[l] = sdelta[l]; sdir[l] = dir; dg += sd * (double)dir; }
+                nd = sdelta[l] + dir;
+            } else {
+                nd = sbase[l] + 0.5f * cur_step * sdir[l];
             }
+            sdelta[l] = nd;
             if (blockIdx.x == 0) {
-                double* Z = a.sums + (size_t)((step + 2) % 3) * 3 * L;
-                for (int i = threadIdx.x; i < 3 * L; i += blockDim.x) Z[i] = 0.0;
-                __threadfence();
-            }
-            __syncthreads();
-            if (last) {
-                // the block that finishes last clears what the final steps left behind
-                __shared__ bool s_last_block;
-                __threadfence();
-                if (threadIdx.x == 0) s_last_block = (atomicAdd(a.counter, 1u) == gridDim.x - 1);
-                __syncthreads();
-                if (s_last_block) {
-                    for (int i = threadIdx.x; i < 9 * L; i += blockDim.x) a.sums[i] = 0.0;
-                    if (threadIdx.x == 0) { *a.counter = 0u; a.vmax[0] = 0.0f; a.vmax[1] = 0.0f; }
+                a.delta[l] = nd;
+                if (first) a.leaf_w[l] = sleafw[l];
+                if (last) {
+                    a.cur_vals[l] = a.lr * nd;
+                    if (a.model_vals) a.model_vals[(long long)it * a.Lstride + l] = a.lr * nd;
+                    if (a.model_wts) a.model_wts[(long long)it * a.Lstride + l] = sleafw[l];
                 }
             }
-            continue;
+        }
+        if (BT) {
+            if (accept) {
+                // gradient . direction at the new base point, added up in a fixed order (every block gets the same bits)
+                dg = cb_warp_sum_d(dg);
+                __syncthreads();
+                if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = dg;
+                __syncthreads();
+                double t = 0.0;
+                for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += s_red[w];
+                dirgrad = t;
+                f_base = s_value;
+                cur_step = 1.0f;
+            } else {
+                cur_step *= 0.5f;
+            }
         }
         if (blockIdx.x == 0) {
-            if (a.c.nranks > 1) {
-                for (int base = 0; base < 3 * L; base += a.c.mbox_bytes / 8)
-                    cb_mailbox_allreduce_sum(a.c, a.sums + base, min(3 * L - base, a.c.mbox_bytes / 8));
-            }
-            const int it = *a.iter_ptr;
-            for (int l = threadIdx.x; l < L; l += blockDim.x) {
-                const double sd = __ldcg(&a.sums[3 * l]), shs = __ldcg(&a.sums[3 * l + 1]);
-                if (first) a.leaf_w[l] = (float)__ldcg(&a.sums[3 * l + 2]);
-                const double sw = (double)a.leaf_w[l];
-                const double den = (a.newton ? shs : sw) + (double)a.l2;
-                const float stp = (den > 0.0) ? (float)(sd / den) : 0.0f;
-                const float v = (first ? 0.0f : sdelta[l]) + stp;
-                a.delta[l] = v;
-                if (last) {
-                    a.cur_vals[l] = a.lr * v;
-                    if (a.model_vals) a.model_vals[(long long)it * a.Lstride + l] = a.lr * v;
-                    if (a.model_wts) a.model_wts[(long long)it * a.Lstride + l] = (float)sw;
-                }
-                a.sums[3 * l] = 0.0; a.sums[3 * l + 1] = 0.0; a.sums[3 * l + 2] = 0.0;
-            }
-            if (last && threadIdx.x == 0) { a.vmax[0] = 0.0f; a.vmax[1] = 0.0f; }
+            double* Z = a.sums + (size_t)((step + 2) % 3) * SS;
+            for (int i = threadIdx.x; i < SS; i += blockDim.x) Z[i] = 0.0;
             __threadfence();
         }
-        if (!last) grid.sync();
+        __syncthreads();
+        if (last) {
+            // the block that finishes last clears what the final steps left behind
+            __shared__ bool s_last_block;
+            __threadfence();
+            if (threadIdx.x == 0) s_last_block = (atomicAdd(a.counter, 1u) == gridDim.x - 1);
+            __syncthreads();
+            if (s_last_block) {
+                for (int i = threadIdx.x; i < 3 * SS; i += blockDim.x) a.sums[i] = 0.0;
+                if (threadIdx.x == 0) {
+                    *a.counter = 0u; a.vmax[0] = 0.0f; a.vmax[1] = 0.0f;
+                    if (!solo) *a.c.epoch = epoch0 + (unsigned long long)a.steps;
+                }
+            }
+        }
     }
 }
 
 // Launcher.  `grid` must not exceed the number of co-resident blocks (cb_leaf_newton_max_grid).  Returns a CUDA error
-// code (0 = ok), or -2 when the tree has too many leaves for the shared-memory cells (use the per-step kernel).
-template <int LOSS>
+// code (0 = ok), or -2 when the tree has too many leaves for the shared-memory cells or for one mailbox message (use
+// the per-step kernel).
+template <int LOSS, bool BT>
 static int cb_leaf_newton_launch_t(CbLeafNewtonArgs& a, int C, int smem, int grid, cudaStream_t st) {
     static unsigned long long set = 0ull;
     if (cb_first_on_device(&set)) {
-        cudaError_t e = cudaFuncSetAttribute(cb_leaf_newton_kernel<LOSS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(cb_leaf_newton_kernel<LOSS, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              100 * 1024);
         if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
     }
     void* args[] = {&a, &C};
-    return (int)cudaLaunchCooperativeKernel((void*)cb_leaf_newton_kernel<LOSS>, dim3(grid), dim3(512), args,
+    return (int)cudaLaunchCooperativeKernel((void*)cb_leaf_newton_kernel<LOSS, BT>, dim3(grid), dim3(512), args,
                                             (size_t)smem, st);
 }
 
 static int cb_leaf_newton_cells(int L, int* smem) {
     int C = 32;
-    while (C > 1 && (size_t)(4 * L * C + 2 * L) * 4 > 96 * 1024) C >>= 1;
-    *smem = (4 * L * C + 2 * L) * 4;
+    while (C > 1 && (size_t)(4 * L * C + 4 * L) * 4 > 96 * 1024) C >>= 1;
+    *smem = (4 * L * C + 4 * L) * 4;
     return (size_t)*smem <= 96 * 1024 ? C : 0;
 }
+
+// Doubles the caller must provide (zeroed) as `sums`: three rotating copies of (3 per leaf + the loss sum, padded).
+CB_API int cb_leaf_newton_sums_doubles(int L) { return 3 * (3 * L + 4); }
+// Bytes one mailbox message of this kernel takes (tagged words): the arena's mailbox slots must be at least this big.
+CB_API int cb_leaf_newton_msg_bytes(int L) { return (3 * L + 1) * 16; }
 
 CB_API int cb_leaf_newton_max_grid(int L) {
     int smem = 0;
@@ -250,8 +331,8 @@ CB_API int cb_leaf_newton_max_grid(int L) {
     int dev = 0, sms = 0, occ = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(cb_leaf_newton_kernel<-1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, cb_leaf_newton_kernel<-1>, 512, smem) != cudaSuccess) {
+    cudaFuncSetAttribute(cb_leaf_newton_kernel<-1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, cb_leaf_newton_kernel<-1, true>, 512, smem) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
@@ -264,14 +345,20 @@ CB_API int cb_leaf_newton(int loss, float p0, float p1, const float* approx, con
                           unsigned int* counter, float* vmax,
                           int steps, int newton, float l2, float lr, float* cur_vals, float* model_vals,
                           float* model_wts, int Lstride, const int* iter_ptr, float* leaf_w, const CbComm* comm,
-                          int grid, cudaStream_t st) {
+                          int backtrack, int grid, cudaStream_t st) {
     CbLeafNewtonArgs a{loss, p0, p1, approx, target, weight, leaf, n, L, delta, sums, counter, vmax, steps, newton, l2, lr,
-                       cur_vals, model_vals, model_wts, Lstride, iter_ptr, leaf_w, CbComm()};
+                       cur_vals, model_vals, model_wts, Lstride, iter_ptr, leaf_w, backtrack, CbComm()};
     if (comm) a.c = *comm; else { a.c.nranks = 1; a.c.rank = 0; }
     int smem = 0;
     const int C = cb_leaf_newton_cells(L, &smem);
     if (C == 0 || loss == CB_LOSS_EXTERNAL) return -2;
-    if (loss == CB_LOSS_LOGLOSS) return cb_leaf_newton_launch_t<CB_LOSS_LOGLOSS>(a, C, smem, grid, st);
-    if (loss == CB_LOSS_RMSE) return cb_leaf_newton_launch_t<CB_LOSS_RMSE>(a, C, smem, grid, st);
-    return cb_leaf_newton_launch_t<-1>(a, C, smem, grid, st);
+    if (a.c.nranks > 1 && cb_leaf_newton_msg_bytes(L) > a.c.mbox_bytes) return -2;
+    const bool bt = backtrack != CB_BT_NONE && steps > 1;
+    if (loss == CB_LOSS_LOGLOSS)
+        return bt ? cb_leaf_newton_launch_t<CB_LOSS_LOGLOSS, true>(a, C, smem, grid, st)
+                  : cb_leaf_newton_launch_t<CB_LOSS_LOGLOSS, false>(a, C, smem, grid, st);
+    if (loss == CB_LOSS_RMSE)
+        return bt ? cb_leaf_newton_launch_t<CB_LOSS_RMSE, true>(a, C, smem, grid, st)
+                  : cb_leaf_newton_launch_t<CB_LOSS_RMSE, false>(a, C, smem, grid, st);
+    return bt ? cb_leaf_newton_launch_t<-1, true>(a, C, smem, grid, st) : cb_leaf_newton_launch_t<-1, false>(a, C, smem, grid, st);
 }

@@ -10,6 +10,7 @@
 // (catboost/cuda/gpu_data/kernel/split.cu:179).
 #pragma once
 #include "cb_common.cuh"
+#include "cb_comm.cuh"
 
 #define CB_HIST_MAX_DOCS_PER_TILE (1 << 19)
 
@@ -66,6 +67,17 @@ struct CbHistArgs {
     unsigned int* work;
     int narrow;    // two-statistic fixed-point path: 1 = single int32 cells (scale limited by the tile's documents)
     int bundle;    // with narrow cells: feature groups accumulated together by one block (<= 8), 0 = one group per block
+    // Leaf update fused into the bundled histogram pass: when set, `leaf` still holds the indices of two levels ago and
+    // *prev_split is the split chosen at level - 1.  Every block works the new bit out for the documents it streams
+    // (it has their bin words in registers anyway); the block of bundle 0 in the first slot pass writes the leaf back.
+    // Blocks that read a leaf word before or after that store get the same result, because setting the bit twice
+    // changes nothing.
+    // The kernel arguments are never modified on the device, so the split is named by where it will be:
+    // prev_splits[*prev_iter * prev_depth + level - 1]; prev_splits == nullptr switches the fusion off.
+    const CbSplit* prev_splits;
+    const int* prev_iter;
+    int prev_depth;
+    unsigned short* leaf_rw;
 };
 
 __device__ __forceinline__ int cb_hist_nslots(const CbHistArgs& a) {
@@ -339,6 +351,9 @@ static __device__ void cb_hist_item_q(const CbHistArgs& a, int* sh, int g, long 
 // (bins word, tile offset, two quantised statistics = 16 bytes) to a small ring in shared memory and drains it 32
 // entries at a time, so every atomic instruction runs with all lanes busy.
 // sh layout: int hist[slot][2][part][j][B], then uint4 ring[warps][64].
+#ifndef CB_UPD_ON
+#define CB_UPD_ON true
+#endif
 #define CB_RING 64
 template <bool NARROW>
 __device__ __forceinline__ void cb_hist_q_apply(int* sh, int B, int C, int copy, uint4 e) {
@@ -582,7 +597,7 @@ __device__ __forceinline__ void cb_bundle_load(const uint32_t* bg, long long npa
     for (int k = 0; k < V; ++k) { lf[k] = lp[k]; s0[k] = p0[k]; s1[k] = p1[k]; }
 }
 
-template <int GMAX>
+template <int GMAX, bool UPD>
 static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int gcnt, int chunk, int nK,
                                       int slot_begin, int slot_count) {
     constexpr int V = CB_BUNDLE_V(GMAX);
@@ -617,6 +632,15 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
     const unsigned int lt = (1u << lane) - 1u;
     unsigned int head = 0, tail = 0;
     const long long step = blk * nK;
+    // fused leaf update (see CbHistArgs::prev_splits; UPD is only used when this bundle holds every feature group).
+    // upk packs what the inner loop needs: group inside the bundle | byte shift << 8 | bin << 16 | one-hot << 24,
+    // or -1 when the previous level found no split.
+    int upk = -1;
+    if (UPD) {
+        const CbSplit psp = a.prev_splits[(long long)(*a.prev_iter) * a.prev_depth + level - 1];
+        if (psp.feature >= 0)
+            upk = ((psp.feature >> 2) - g0) | (((psp.feature & 3) * 8) << 8) | ((psp.bin & 255) << 16) | ((psp.flags & 1) << 24);
+    }
 #if CB_BUNDLE_PF
     unsigned int nw[GMAX][V];
     unsigned int nlf[V];
@@ -646,6 +670,25 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
 #else
         if (i < d_end) cb_bundle_load<GMAX, V>(bg, npad, a.leaf, st0, st1, i, gcnt, w, lf, s0, s1);
 #endif
+        if (UPD && upk >= 0 && i < d_end) {
+            typedef typename CbVec<V>::H HV;
+            const int ugl = upk & 255, ush = (upk >> 8) & 255;
+            const unsigned int ubin = (unsigned int)(upk >> 16) & 255u;
+            HV out;
+            unsigned short* op = reinterpret_cast<unsigned short*>(&out);
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                unsigned int uw = 0u;
+#pragma unroll
+                for (int gl = 0; gl < GMAX; ++gl)
+                    if (gl == ugl) uw = w[gl][k];
+                const unsigned int b = (uw >> ush) & 255u;
+                const unsigned int r = (upk >> 24) ? (b == ubin) : (b > ubin);
+                lf[k] |= r << (level - 1);
+                op[k] = (unsigned short)lf[k];
+            }
+            if (slot_begin == 0) *reinterpret_cast<HV*>(a.leaf_rw + i) = out;
+        }
 #pragma unroll
         for (int k = 0; k < V; ++k) {
             bool take = (i + k) < d_end;
@@ -747,9 +790,15 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
                 const int g0 = g * gpc;
                 const int gcnt = min(gpc, G - g0);
                 int* shi = reinterpret_cast<int*>(sh);
-                if (gpc <= 2) cb_hist_bundle<2>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
-                else if (gpc <= 4) cb_hist_bundle<4>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
-                else cb_hist_bundle<8>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
+                if (CB_UPD_ON && a.prev_splits && a.level > 0 && gpc >= G) {
+                    if (gpc <= 2) cb_hist_bundle<2, true>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
+                    else if (gpc <= 4) cb_hist_bundle<4, true>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
+                    else cb_hist_bundle<8, true>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
+                } else {
+                    if (gpc <= 2) cb_hist_bundle<2, false>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
+                    else if (gpc <= 4) cb_hist_bundle<4, false>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
+                    else cb_hist_bundle<8, false>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
+                }
                 continue;
             }
             const long long b = k * per;
@@ -787,7 +836,24 @@ struct CbScoreArgs {
     unsigned long long seed;
     float learning_rate;
     unsigned long long* best_key;
+    // Several ranks: hsrc[r] holds tagged words (float payload + 32-bit tag per 8 bytes, cb_comm.cuh) that source r
+    // stores straight into this rank's arena; a load polls the word until its tag is that of level counter
+    // *ll_epoch + 1 (bounded by ll_timeout_ns, then ll_status is set and 0 is used).  ll_epoch == nullptr: hsrc[r] are
+    // plain floats.  The counter is advanced by the launch itself only after every score read of the level is done.
+    const unsigned long long* ll_epoch;
+    long long ll_timeout_ns;
+    int* ll_status;
 };
+
+__device__ __forceinline__ unsigned int cb_score_tag(const CbScoreArgs& a) {
+    return a.ll_epoch ? cb_ll_tag(*a.ll_epoch + 1ull) : 0u;
+}
+
+__device__ __forceinline__ float cb_score_src(const CbScoreArgs& a, int r, size_t idx, unsigned int tag) {
+    if (tag == 0u) return __ldcg(a.hsrc[r] + idx);
+    const unsigned long long* w = reinterpret_cast<const unsigned long long*>(a.hsrc[r]) + idx;
+    return __uint_as_float(cb_ll_load(w, tag, a.ll_timeout_ns, a.ll_status, CB_TIMEOUT_HIST_ARRIVE, r));
+}
 
 __device__ __forceinline__ void cb_score_add_leaf(int fn, float l2, float s, float w, float& num, float& den) {
     switch (fn) {
@@ -837,11 +903,11 @@ __device__ __forceinline__ float cb_noise_std(const CbScoreArgs& a) {
 // Column `st` of leaf l for the 32 bins of chunk c: summed over the sources, completed from the parent when the leaf
 // is the sibling that was not accumulated, stored into the complete histogram of this level.
 __device__ __forceinline__ float cb_score_load(const CbScoreArgs& a, int l, int p, bool computed, int st, int col0,
-                                               int bin, int nb) {
+                                               int bin, int nb, unsigned int tag) {
     float x = 0.0f;
     if (bin < nb) {
         const size_t idx = ((size_t)p * a.S + st) * a.W + col0 + bin;
-        for (int r = 0; r < a.nsrc; ++r) x += __ldcg(a.hsrc[r] + idx);
+        for (int r = 0; r < a.nsrc; ++r) x += cb_score_src(a, r, idx, tag);
         if (!computed) x = a.hprev[idx] - x;
         if (a.hcur) a.hcur[((size_t)l * a.S + st) * a.W + col0 + bin] = x;
     }
@@ -852,20 +918,44 @@ __device__ __forceinline__ float cb_score_load(const CbScoreArgs& a, int l, int 
 // when a warp walks many leaves of one feature: there the chain of dependent L2 round trips is what the warp waits for,
 // and the longer code is fetched once and reused for every leaf.
 __device__ __forceinline__ void cb_score_load8(const CbScoreArgs& a, int l, int p, bool computed, int st, int col0,
-                                               int lane, int bpl, int nb, float* x) {
+                                               int lane, int bpl, int nb, float* x, unsigned int tag) {
     const size_t base = ((size_t)p * a.S + st) * a.W + col0 + lane * bpl;
     const int left = nb - lane * bpl;                  // bins of this lane that exist
     float prev[8];
+    if (tag != 0u) {
+        // tagged words: peek at all of a source's words first (the loads overlap), then poll the ones not there yet
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const bool ok = k < bpl && k < left;
-        x[k] = ok ? __ldcg(a.hsrc[0] + base + k) : 0.0f;
-        prev[k] = (ok && !computed) ? a.hprev[base + k] : 0.0f;
-    }
-    for (int r = 1; r < a.nsrc; ++r) {
+        for (int k = 0; k < 8; ++k) {
+            x[k] = 0.0f;
+            prev[k] = (k < bpl && k < left && !computed) ? a.hprev[base + k] : 0.0f;
+        }
+        for (int r = 0; r < a.nsrc; ++r) {
+            const unsigned long long* w = reinterpret_cast<const unsigned long long*>(a.hsrc[r]) + base;
+            unsigned long long v[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-            if (k < bpl && k < left) x[k] += __ldcg(a.hsrc[r] + base + k);
+            for (int k = 0; k < 8; ++k) v[k] = (k < bpl && k < left) ? cb_ll_peek(w + k) : 0ull;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (k < bpl && k < left) {
+                    unsigned int pay = (unsigned int)v[k];
+                    if ((unsigned int)(v[k] >> 32) != tag)
+                        pay = cb_ll_load(w + k, tag, a.ll_timeout_ns, a.ll_status, CB_TIMEOUT_HIST_ARRIVE, r);
+                    x[k] += __uint_as_float(pay);
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const bool ok = k < bpl && k < left;
+            x[k] = ok ? __ldcg(a.hsrc[0] + base + k) : 0.0f;
+            prev[k] = (ok && !computed) ? a.hprev[base + k] : 0.0f;
+        }
+        for (int r = 1; r < a.nsrc; ++r) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (k < bpl && k < left) x[k] += __ldcg(a.hsrc[r] + base + k);
+        }
     }
     const size_t obase = ((size_t)l * a.S + st) * a.W + col0 + lane * bpl;
 #pragma unroll
@@ -888,6 +978,7 @@ static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, 
     const int L = 1 << a.level;
     const int half = L >> 1;
     const int bpl = (nb + 31) >> 5;
+    const unsigned int tag = cb_score_tag(a);
     float* num = sc;
     float* den = sc + 256;
     float* pw = sc + 512;
@@ -914,7 +1005,7 @@ static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, 
             float run = 0.0f;
             if (batched) {
                 float x8[8];
-                cb_score_load8(a, l, p, computed, c_st, col0, lane, bpl, nb, x8);
+                cb_score_load8(a, l, p, computed, c_st, col0, lane, bpl, nb, x8, tag);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     if (k < bpl) {
@@ -925,7 +1016,7 @@ static __device__ void cb_score_accumulate(const CbScoreArgs& a, int f, int l0, 
             } else {
                 for (int k = 0; k < bpl; ++k) {
                     const int bin = lane * bpl + k;
-                    const float x = cb_score_load(a, l, p, computed, c_st, col0, bin, nb);
+                    const float x = cb_score_load(a, l, p, computed, c_st, col0, bin, nb, tag);
                     run += x;
                     pre[bin] = onehot ? x : run;
                 }

@@ -178,7 +178,9 @@ _SIGS = {
     "cb_leaf_newton_max_grid": (c_int, [c_int]),
     "cb_leaf_newton": (c_int, [c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_int,
-                               c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "cb_leaf_newton_sums_doubles": (c_int, [c_int]),
+    "cb_leaf_newton_msg_bytes": (c_int, [c_int]),
     "cb_iter_end": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "cb_apply_tree_bins": (c_int, [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                                    c_void_p]),
@@ -191,7 +193,8 @@ _SIGS = {
     "cb_device_info": (c_int, [c_void_p, c_void_p]),
     "cb_fused_create": (c_void_p, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int,
-                                   c_float, c_void_p, c_void_p, c_ull, c_float, c_void_p, c_void_p, c_int]),
+                                   c_float, c_void_p, c_void_p, c_ull, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int]),
+    "cb_fused_set_fuse_leaf": (None, [c_void_p, c_int]),
     "cb_fused_set_features": (None, [c_void_p, c_int, c_int]),
     "cb_fused_set_phase_ts": (None, [c_void_p, c_void_p]),
     "cb_fused_set_work": (None, [c_void_p, c_void_p]),
@@ -212,7 +215,7 @@ def cuda_lib() -> ctypes.CDLL:
         if not CUDA_LIB.exists() or (_nvcc() is not None and _newer([s for s in CUDA_SRC if s.exists()] + CUDA_HDR,
                                                                      CUDA_LIB)):
             build_cuda()
-        lib = ctypes.CDLL(str(CUDA_LIB))
+        lib = ctypes.CDLL(os.environ.get("CB200_CUDA_LIB") or str(CUDA_LIB))     # the variable names another build to load
         for name, (res, args) in _SIGS.items():
             fn = getattr(lib, name)
             fn.restype = res

@@ -447,10 +447,24 @@ def estimate_leaves(objective, approx, target, weight, leaf, n_leaves, n, opts, 
     delta = torch.zeros((n_leaves, dims), dtype=torch.float32, device=dev)
     wcol = torch.ones(n, dtype=torch.float32, device=dev) if weight is None else weight[:n]
     leaf_w = None
-    prev_loss = None
+    # Step-length control (catboost/cuda/methods/leaves_estimation/descent_helpers.cpp:127-206, step_estimator.cpp): every
+    # pass evaluates the loss at the point it takes its derivatives at; a point that fails the condition is dropped and
+    # the next pass tries half the step from the last accepted point.  A rejected try uses up one iteration.
+    mode = str(getattr(opts, "leaf_estimation_backtracking", None) or "No")
+    wvec = weight if weight is None else weight[:n]
+    backtrack = mode in ("AnyImprovement", "Armijo") and max(1, iters) > 1
+    base, direction, f_base, dirgrad, cur_step = delta, torch.zeros_like(delta), None, 0.0, 1.0
     for it in range(max(1, iters)):
         a = approx[:, :n] if it == 0 else approx[:, :n] + delta[idx].t()
-        der, hess = objective.der_hess(a, target, weight if weight is None else weight[:n], obj_ctx)
+        if backtrack:
+            v = _loss_sum(objective, a, target, wvec, obj_ctx, ctx)
+            if v is None:
+                backtrack = False
+            elif it > 0 and not (v <= f_base - (1e-5 * cur_step * dirgrad if mode == "Armijo" else 0.0)):
+                cur_step *= 0.5
+                delta = base + cur_step * direction
+                continue
+        der, hess = objective.der_hess(a, target, wvec, obj_ctx)
         cols = torch.cat([der, hess, wcol.unsqueeze(0)], 0)
         sums = ops.leaf_sums(leaf, cols, n_leaves, n)
         if ctx is not None and ctx.is_distributed:
@@ -460,11 +474,35 @@ def estimate_leaves(objective, approx, target, weight, leaf, n_leaves, n, opts, 
             leaf_w = sw.clone()
         den = (sh if method == "Newton" else sw.unsqueeze(1).expand_as(sd)) + l2
         step = torch.where(den > 0, sd / den, torch.zeros_like(sd)).float()
+        if backtrack:
+            base, direction, f_base, cur_step = delta, step, v, 1.0
+            dirgrad = float((sd.double() * step.double()).sum().item())
         delta = delta + step
     if getattr(objective, "zero_mean_leaves", False):
         tot = leaf_w.sum().clamp_min(1e-30)
         delta = delta - ((delta.double() * leaf_w.unsqueeze(1)).sum(0) / tot).float()
     return (delta * lr).double().cpu().numpy(), leaf_w.cpu().numpy()
+
+
+def _loss_sum(objective, a, target, weight, obj_ctx, ctx):
+    """Weighted sum of the loss over all ranks at approx ``a`` (None when the objective has no finite value)."""
+    import math
+    try:
+        if hasattr(objective, "_point") and a.shape[0] == 1:
+            v = objective._point(a[0], target)[2]
+            s = float((v if weight is None else v * weight).double().sum().item())
+        else:
+            wt = float(target.shape[-1] if weight is None else weight.sum().item())
+            s = float(objective.value(a, target, weight, obj_ctx)) * wt
+    except (NotImplementedError, RuntimeError, TypeError, IndexError):
+        return None
+    if not math.isfinite(s):
+        return None
+    if ctx is not None and ctx.is_distributed:
+        t = torch.tensor([s], dtype=torch.float64, device=a.device)
+        ctx.all_reduce_sum_(t)
+        s = float(t.item())
+    return s
 
 
 def _exact_leaves(objective, approx, target, weight, idx, n_leaves, n, lr, ctx):

@@ -56,7 +56,8 @@ class GpuObliviousEngine:
                  ext_der: Optional[torch.Tensor] = None, ext_hess: Optional[torch.Tensor] = None,
                  timeout_s: float = 20.0, quantized_hist: bool = True, dynamic_work: bool = True,
                  der_fn=None, zero_mean_leaves: bool = False, max_bundle: int = 8,
-                 fused_leaf_steps: bool = True):
+                 fused_leaf_steps: bool = True, leaf_backtracking: str = "AnyImprovement",
+                 fuse_leaf_update: bool = True):
         assert store.bins.is_cuda, "GpuObliviousEngine needs a CUDA store"
         if depth > 16:
             raise ValueError("depth must be <= 16")
@@ -117,6 +118,8 @@ class GpuObliviousEngine:
         self.leaf_vmax = torch.zeros(2, dtype=f32, device=dev)
         self.leaf_grid = None
         self.fused_leaf_steps = bool(fused_leaf_steps)
+        self.leaf_backtracking = {"No": 0, "AnyImprovement": 1, "Armijo": 2}[str(leaf_backtracking or "AnyImprovement")]
+        self.fuse_leaf_update = bool(fuse_leaf_update)
         self.stats = torch.zeros((self.S, npad), dtype=f32, device=dev)
         self.scal = torch.zeros(4, dtype=f64, device=dev)
         self.iter_ptr = torch.zeros(1, dtype=i32, device=dev)
@@ -129,7 +132,8 @@ class GpuObliviousEngine:
         self.cur_vals = torch.zeros(self.L, dtype=f32, device=dev)
         self.delta = torch.zeros(self.L, dtype=f32, device=dev)
         self.leaf_w = torch.zeros(self.L, dtype=f32, device=dev)
-        self.sums = torch.zeros(self.L * 9, dtype=f64, device=dev)     # three rotating copies of [L][3]
+        # three rotating copies of the per-leaf (der, hess, weight) sums + the loss sum
+        self.sums = torch.zeros(max(self.L * 9, int(self.lib.cb_leaf_newton_sums_doubles(self.L))), dtype=f64, device=dev)
         self.counter = torch.zeros(1, dtype=i32, device=dev)
         self.best_key = torch.zeros(1, dtype=i64, device=dev)
         self.cur_loss = torch.zeros(2, dtype=f64, device=dev)
@@ -160,8 +164,12 @@ class GpuObliviousEngine:
             self.Wmax = TB
         hl = 1 if depth <= 1 else 1 << (depth - 2)      # leaves kept for the sibling subtraction
         self.hbuf = [torch.zeros((hl * 2, self.S, self.Wmax), dtype=f32, device=dev) for _ in range(2)]
-        slot_floats = slots_max * self.S * self.Wmax
-        mbox_bytes = max(msg_bytes, 256)
+        # several ranks: the slots hold tagged 8-byte words (value + level tag), so twice the floats; a mailbox slot must
+        # hold the largest tagged message (split key + lighter-child mask, or the per-leaf sums of a Newton step)
+        slot_floats = slots_max * self.S * self.Wmax * (2 if self.R > 1 else 1)
+        select_words = 2 + max(1, (1 << max(depth - 1, 0)) // 32)
+        mbox_bytes = max(msg_bytes, 256, 8 * select_words,
+                         int(self.lib.cb_leaf_newton_msg_bytes(self.L)) if self.L <= 4096 else 0)
         self.arena = (PeerArena(self.ctx, ArenaLayout(self.R, mbox_bytes, slot_floats), timeout_s=timeout_s)
                       if self.reduce == "fused" else None)
         if self.reduce == "fused":
@@ -195,7 +203,7 @@ class GpuObliviousEngine:
             self.S, self.B, partial_ptr, local_slots, _p(self.hbuf[0]), _p(self.hbuf[1]), own, self.Wmax,
             _p(self.mask[0]), _p(self.mask[1]), _p(self.splits), self.depth, self.l2, self.score_fn,
             self.random_strength, _p(self.scal), _p(self.iter_ptr), self.score_seed, self.lr, _p(self.best_key),
-            _p(self.msg_local), self.threads)
+            _p(self.msg_local), _p(self.msg_all), self.msg_all.stride(0), self.threads)
         if not self.plan:
             raise RuntimeError("cb_fused_create failed")
         self.lib.cb_fused_set_features(ctypes.c_void_p(self.plan), self.feat_bounds[self.rank],
@@ -203,6 +211,7 @@ class GpuObliviousEngine:
         # fixed-point accumulation is on: statmax must be known to the geometry (it doubles the tile size)
         self.lib.cb_fused_set_priv(ctypes.c_void_p(self.plan), None, _p(self.statmax) if self.quantized_hist else None)
         self.lib.cb_fused_set_narrow(ctypes.c_void_p(self.plan), 1 if self.narrow_hist else 0, self.max_bundle)
+        self.lib.cb_fused_set_fuse_leaf(ctypes.c_void_p(self.plan), 1 if self.fuse_leaf_update else 0)
         # columns where one bin holds a large share of the documents (sparse data): most lanes of a warp would add to
         # the same histogram cell, so such data gets up to 8 replicas of every cell instead of 2 (measured on 60 % zeros:
         # 6.8 -> 4.9 ms per iteration; on dense data more replicas cost about 1 %)
@@ -339,14 +348,17 @@ class GpuObliviousEngine:
             self.leaf_grid = int(lib.cb_leaf_newton_max_grid(self.L)) if self.der_fn is None and self.loss_id != 100 else 0
         if self.leaf_grid > 0 and self.fused_leaf_steps:
             # all steps of the leaf estimation in one cooperative launch
-            chk(lib.cb_leaf_newton(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target), _p(self.weight),
+            rc = lib.cb_leaf_newton(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target), _p(self.weight),
                                    _p(self.leaf), self.n, self.L, _p(self.delta), _p(self.sums), _p(self.counter),
                                    _p(self.leaf_vmax),
                                    self.leaf_iterations, self.leaf_newton, self.l2, self.lr, _p(self.cur_vals),
                                    _p(self.model_vals), _p(self.model_wts), self.L, _p(self.iter_ptr), _p(self.leaf_w),
-                                   comm, self.leaf_grid, self._stream()), "cb_leaf_newton")
-            self.launches_per_iter += 1
-            return
+                                   comm, self.leaf_backtracking, self.leaf_grid, self._stream())
+            if rc != -2:
+                chk(rc, "cb_leaf_newton")
+                self.launches_per_iter += 1
+                return
+            self.leaf_grid = 0          # too many leaves for one mailbox message: one launch per step instead
         for it in range(self.leaf_iterations):
             last = 1 if it == self.leaf_iterations - 1 else 0
             chk(lib.cb_leaf_pass_q(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target), _p(self.weight),

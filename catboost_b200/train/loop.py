@@ -451,6 +451,7 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
             leaf_iterations=int(o.leaf_estimation_iterations), seed=int(o.random_seed), ctx=ctx,
             reduce=("fused" if o.histogram_reduce in ("fused", None) else "nccl"), eval_sets=evs,
             quantized_hist={"narrow": True, "wide": "wide", "float": False}[o.histogram_cells or "narrow"],
+            leaf_backtracking=str(o.leaf_estimation_backtracking or "AnyImprovement"),
             der_fn=der_fn, zero_mean_leaves=bool(der_fn is not None and getattr(objective, "zero_mean_leaves", False)))
     loss_metric_name = objective.name
     # "cheap" logging: the only tracked metric is the objective itself, which the device already accumulates
