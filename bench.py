@@ -37,7 +37,7 @@ CONFIGS = {
     # reference config has 45M rows: pass --rows 45000000 for the full size.
     # learning to rank: 2M documents x 700 features in groups of about 100, YetiRank, 64 borders; end-to-end fit() only
     "ranking": dict(rows=2_000_000, features=700, depth=6, border_count=64, model="YetiRank symmetric depth6 2Mx700"),
-    "criteo": dict(rows=4_500_000, features=39, depth=8, border_count=128, model="Logloss symmetric depth8 13num+26cat CTR"),
+    "criteo": dict(rows=45_000_000, features=39, depth=8, border_count=128, model="Logloss symmetric depth8 13num+26cat CTR"),
 }
 
 
@@ -70,21 +70,46 @@ def make_data(config: str, rows: int, features: int, rank: int, world: int, seed
 
 
 def make_criteo_like(rows: int, rank: int, world: int, seed: int = 0):
-    """13 numeric + 26 integer-coded categorical columns with Zipf-distributed cardinalities from 10 to 1M."""
+    """The categorical workload: 13 numeric columns (integer counts from a log-normal distribution, 20 % missing) and 26
+    categorical columns whose cardinalities are drawn log-uniformly from [10, 1e6] and whose values follow Zipf(s = 1.1);
+    about 25 % positives from a logistic model over per-category random effects.  Every rank draws the same
+    cardinalities and effect tables (seeded by ``seed``) and its own rows (seeded by the rank)."""
     import pandas as pd
     lo, hi = rows * rank // world, rows * (rank + 1) // world
     n = hi - lo
     rng = np.random.default_rng(seed * 1000 + rank)
-    num = rng.standard_normal((n, 13), dtype=np.float32)
-    cards = [10, 30, 100, 300, 1000, 3000, 10_000, 30_000, 100_000, 300_000, 1_000_000] + [50 * (k + 1) for k in range(15)]
     tab_rng = np.random.default_rng(seed + 5)
-    f = num[:, 0] * 0.7 + 0.5 * num[:, 1] * num[:, 2]
-    cols = {f"n{j}": num[:, j] for j in range(13)}
+    cards = np.unique(np.round(np.exp(tab_rng.uniform(np.log(10.0), np.log(1e6), 26))).astype(np.int64))
+    while len(cards) < 26:
+        cards = np.unique(np.concatenate([cards, np.round(np.exp(tab_rng.uniform(np.log(10.0), np.log(1e6), 26 - len(cards)))).astype(np.int64)]))
+    cards = tab_rng.permutation(cards)[:26]
+    cols = {}
+    f = np.zeros(n, dtype=np.float32)
+    for j in range(13):
+        v = np.floor(np.exp(rng.normal(1.0, 1.5, n))).astype(np.float32)
+        if j < 4:
+            f += (0.25 - 0.1 * j) * np.log1p(v) - 0.3
+        v[rng.random(n) < 0.2] = np.nan
+        cols[f"n{j}"] = v
     for j, card in enumerate(cards):
-        c = np.minimum(rng.zipf(1.25, n), card) - 1
-        effect = (tab_rng.standard_normal(card) * 0.25).astype(np.float32)
-        f = f + effect[c]
-        cols[f"c{j}"] = c.astype(np.int64)
+        # Zipf(1.1) truncated to the cardinality: inversion of the continuous power law x^-1.1 on [1, card + 1), floored
+        # (P(k) proportional to k^-0.1 - (k + 1)^-0.1, which is k^-1.1 up to a slowly varying factor)
+        top = float(card + 1) ** -0.1
+        c = (np.floor((1.0 - rng.random(n, dtype=np.float32) * np.float32(1.0 - top)) ** np.float32(-10.0)).astype(np.int64) - 1)
+        c = np.clip(c, 0, int(card) - 1).astype(np.int32)
+        effect = (tab_rng.standard_normal(int(card)) * 0.35).astype(np.float32)
+        f += effect[c]
+        cols[f"c{j}"] = c
+    # intercept for about 25 % positives (bisection on a sample of this rank; the ranks agree to within sampling noise)
+    fs = f[: min(n, 200_000)].astype(np.float64)
+    a, b = -20.0, 20.0
+    for _ in range(40):
+        mid = 0.5 * (a + b)
+        if np.mean(1.0 / (1.0 + np.exp(-(fs + mid)))) > 0.25:
+            b = mid
+        else:
+            a = mid
+    f += np.float32(0.5 * (a + b))
     y = (rng.random(n, dtype=np.float32) < 1.0 / (1.0 + np.exp(-f))).astype(np.float32)
     return pd.DataFrame(cols), y, [f"c{j}" for j in range(26)]
 
@@ -187,7 +212,8 @@ def bench_criteo(args, cfg, rank, world, dev):
                           "config": {"model": cfg["model"], "global_batch": cfg["rows"], "seq_len": 39,
                                      "parallelism": f"doc-parallel dp{world}", "depth": cfg["depth"],
                                      "ctr": f"simple_ctr defaults, max_ctr_complexity={int(args.ctr_complexity)}",
-                                     "note": "auxiliary config; the named size is 45M rows (--rows 45000000)"},
+                                     "generator": "13 log-normal counts with 20% NaN + 26 Zipf(1.1) categoricals, "
+                                                  "cardinalities log-uniform in [10, 1e6], ~25% positives"},
                           "e2e": {"value": fit_s / iters * 1000.0, "unit": "s/1000iter", "fit_seconds": fit_s,
                                   "fit_breakdown_s": {k: round(float(v), 4) for k, v in tm.items()}},
                           "features_in_store": model._train_info.get("h2d_bytes")}))
@@ -321,7 +347,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-iters", type=int, default=0,
                     help="boosting iterations of the end-to-end fit() (default 1000: the metric's own iteration count)")
-    ap.add_argument("--ctr-complexity", type=int, default=1, help="max_ctr_complexity of the categorical config")
+    ap.add_argument("--ctr-complexity", type=int, default=2, help="max_ctr_complexity of the categorical config")
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--phases", action="store_true", help="print per-phase times of the fused level kernel")
     args = ap.parse_args()

@@ -76,6 +76,33 @@ def hist(store: BinnedStore, leaf: torch.Tensor, stats: torch.Tensor, slot_table
     return out
 
 
+_SCORE_FN_ID = {"Cosine": 0, "NewtonCosine": 0, "L2": 1, "NewtonL2": 1, "SolarL2": 2, "LOOL2": 3, "SatL2": 4}
+
+
+def leaf_search(store: BinnedStore, hist_: torch.Tensor, K: int, l2: float, score_function: str, noise_std: float = 0.0,
+                seed: int = 0, leaf_id: Optional[torch.Tensor] = None, fmask: Optional[torch.Tensor] = None,
+                min_data: float = 0.0):
+    """Best split of every leaf from its complete histogram ``hist_[leaf, S, TB]`` (K derivative columns, the weight
+    column, optionally a document-count column) on the GPU: ``(score, feature, bin, gain)`` arrays on the host, feature
+    -1 where a leaf has no admissible candidate.  One warp per (leaf, feature), then one warp per leaf."""
+    dev = store.bins.device
+    nleaf, S = int(hist_.shape[0]), int(hist_.shape[1])
+    F = store.F
+    sc = torch.empty((nleaf, F), dtype=torch.float32, device=dev)
+    bn = torch.empty((nleaf, F), dtype=torch.int32, device=dev)
+    gn = torch.empty((nleaf, F), dtype=torch.float32, device=dev)
+    best = torch.empty((nleaf, 4), dtype=torch.float32, device=dev)
+    fm = None if fmask is None else fmask.to(torch.float32).contiguous()
+    lid = None if leaf_id is None else leaf_id.to(torch.int32).contiguous()
+    native.cuda_check(native.cuda_lib().cb_leaf_search(
+        ctypes.c_void_p(store.handle), _p(hist_.contiguous()), nleaf, S, int(K), float(l2), _SCORE_FN_ID[score_function],
+        float(noise_std), int(seed) & 0xFFFFFFFFFFFFFFFF, _p(lid), _p(fm), float(min_data), _p(sc), _p(bn), _p(gn), _p(best),
+        _stream(dev)), "cb_leaf_search")
+    b = best.cpu()
+    ints = b.view(torch.int32)
+    return b[:, 0].numpy(), ints[:, 1].numpy(), ints[:, 2].numpy(), b[:, 3].numpy()
+
+
 def hist_reference(store: BinnedStore, leaf: torch.Tensor, stats: torch.Tensor, slot_table: torch.Tensor,
                    nslots: int) -> torch.Tensor:
     n, S, TB = store.n, stats.shape[0], store.TB

@@ -685,17 +685,17 @@ CB_API int cb_leaf_pass(int loss, float p0, float p1, const float* approx, const
 // End of a boosting iteration: record the learn loss and the per-iteration extras (evaluation-set metric
 // sums), clear the accumulators, advance the counter.
 __global__ void cb_iter_end_kernel(int* iter_ptr, double* scal, double* loss_hist, double* extra_src, double* extra_dst,
-                                   int n_extra, float* statmax) {
+                                   int n_extra, float* statmax, int n_statmax) {
     const int it = *iter_ptr;
-    if (statmax) { statmax[0] = 0.0f; statmax[1] = 0.0f; }
+    if (statmax) for (int k = 0; k < n_statmax; ++k) statmax[k] = 0.0f;
     if (loss_hist) { loss_hist[2 * it] = scal[0]; loss_hist[2 * it + 1] = scal[1]; }
     scal[0] = scal[1] = scal[2] = scal[3] = 0.0;
     for (int k = 0; k < n_extra; ++k) { extra_dst[(long long)it * n_extra + k] = extra_src[k]; extra_src[k] = 0.0; }
     *iter_ptr = it + 1;
 }
 CB_API int cb_iter_end(int* iter_ptr, double* scal, double* loss_hist, double* extra_src, double* extra_dst, int n_extra,
-                       float* statmax, cudaStream_t st) {
-    cb_iter_end_kernel<<<1, 1, 0, st>>>(iter_ptr, scal, loss_hist, extra_src, extra_dst, n_extra, statmax);
+                       float* statmax, int n_statmax, cudaStream_t st) {
+    cb_iter_end_kernel<<<1, 1, 0, st>>>(iter_ptr, scal, loss_hist, extra_src, extra_dst, n_extra, statmax, n_statmax);
     CB_LAUNCH_CHECK();
     return 0;
 }

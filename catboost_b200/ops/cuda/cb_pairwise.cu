@@ -1,0 +1,293 @@
+// Pairwise split search (PairLogitPairwise / YetiRankPairwise) as kernels: pairwise histograms, bin prefix sums,
+// assembly of one 2L x 2L linear system per candidate border, Cholesky solve and gain, all on the device.
+//
+// Behaviour reproduced from the reference (not its code): a pair (winner i, loser j, weight w) contributes w to the
+// off-diagonal cell (child of i, child of j) of the candidate's leaf-pair matrix; the four configurations of a pair
+// under a border come from four histograms per (leaf pair, bin) and bin prefix sums
+// (catboost/cuda/methods/kernel/pairwise_hist_one_byte_6bit.cuh:260, pairwise_hist.cu, split_pairwise.cu:21-419); the
+// candidate's leaf values solve (Laplacian + regularisation) x = derivative sums with the last unknown pinned
+// (catboost/cuda/methods/kernel/linear_solver.cu:71-398, catboost/private/libs/algo/pairwise_scoring.cpp:123-260) and
+// its score is x.d - x'Mx / 2.
+//
+// Histogram layout (floats): H[f][bin][a][b][4] for the ordered leaf pair (a = leaf of the winner, b = leaf of the
+// loser).  Float features, lo / hi = smaller / larger bin of the pair:
+//   [0] += w at bin lo when the winner has the smaller bin     [1] += w at bin hi when the winner has the smaller bin
+//   [2] += w at bin lo otherwise (loser smaller, or equal)     [3] += w at bin hi otherwise
+// After an inclusive prefix sum over the bins, for border t (a document goes right iff bin > t):
+//   both left  = ([1] + [3])(t)               winner left, loser right = ([0] - [1])(t)
+//   both right = total - ([0] + [2])(t)       winner right, loser left = ([2] - [3])(t)
+// One-hot features (right iff bin == v), no prefix sum:
+//   [0] += w at v = bin_i = bin_j (both right)   [1] += w at v = bin_i != bin_j (winner right)
+//   [2] += w at v = bin_j != bin_i (loser right)  both left = total - [0] - [1] - [2]
+#include "cb_common.cuh"
+#include "cb_tree.cuh"
+
+struct CbPairHistArgs {
+    CbData d;
+    const unsigned short* leaf;     // current leaf of every document (< L)
+    const int* wi; const int* li;   // winner / loser document of every pair
+    const float* w;                 // pair weights
+    long long npairs;
+    int L, B;                       // leaves, bins per feature in the layout (>= max feat_nb)
+    int g0, ng;                     // feature groups [g0, g0 + ng) of the store are accumulated
+    float* H;                       // [ng * 4][B][L][L][4]
+};
+
+// One thread per (pair, feature group): the two bin words give four features at once; 8 atomics.
+__global__ void __launch_bounds__(256) cb_pair_hist_kernel(CbPairHistArgs a) {
+    const long long total = a.npairs * a.ng;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const size_t fstride = (size_t)a.B * a.L * a.L * 4;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const long long p = idx / a.ng;
+        const int gl = (int)(idx - p * a.ng);
+        const int g = a.g0 + gl;
+        const int i = a.wi[p], j = a.li[p];
+        const float w = a.w[p];
+        if (w == 0.0f) continue;
+        const uint32_t wi_ = a.d.bins[(long long)g * a.d.npad + i], wj_ = a.d.bins[(long long)g * a.d.npad + j];
+        const int la = a.leaf[i], lb = a.leaf[j];
+        const size_t cell = ((size_t)la * a.L + lb) * 4;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int f = g * 4 + q;
+            if (f >= a.d.F) break;
+            const int bi = (int)((wi_ >> (8 * q)) & 255u), bj = (int)((wj_ >> (8 * q)) & 255u);
+            float* Hf = a.H + (size_t)(gl * 4 + q) * fstride;
+            const size_t bs = (size_t)a.L * a.L * 4;
+            if (a.d.feat_onehot && a.d.feat_onehot[f]) {
+                if (bi == bj) atomicAdd(Hf + bi * bs + cell, w);
+                else { atomicAdd(Hf + bi * bs + cell + 1, w); atomicAdd(Hf + bj * bs + cell + 2, w); }
+            } else {
+                const bool wsmall = bi < bj;
+                const int lo = wsmall ? bi : bj, hi = wsmall ? bj : bi;
+                atomicAdd(Hf + lo * bs + cell + (wsmall ? 0 : 2), w);
+                atomicAdd(Hf + hi * bs + cell + (wsmall ? 1 : 3), w);
+            }
+        }
+    }
+}
+
+// Per-document derivative sums D[f][bin][leaf] for the same features (one thread per (document, group)).
+__global__ void __launch_bounds__(256) cb_pair_der_hist_kernel(CbData d, const unsigned short* leaf, const float* der, int L,
+                                                               int B, int g0, int ng, float* D) {
+    const long long total = d.n * ng;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const long long i = idx / ng;
+        const int gl = (int)(idx - i * ng);
+        const int g = g0 + gl;
+        const float v = der[i];
+        const uint32_t wd = d.bins[(long long)g * d.npad + i];
+        const int l = leaf[i];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (g * 4 + q >= d.F) break;
+            const int b = (int)((wd >> (8 * q)) & 255u);
+            atomicAdd(D + ((size_t)(gl * 4 + q) * B + b) * L + l, v);
+        }
+    }
+}
+
+// Inclusive prefix sum over the bins of every column (cols = floats per bin) of the float features; one-hot features
+// are left as they are.
+__global__ void __launch_bounds__(256) cb_pair_scan_kernel(CbData d, int f0, int nf, int B, long long cols, float* H) {
+    const long long total = (long long)nf * cols;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int fl = (int)(idx / cols);
+        const long long c = idx - (long long)fl * cols;
+        const int f = f0 + fl;
+        if (f >= d.F || (d.feat_onehot && d.feat_onehot[f])) continue;
+        float* col = H + (size_t)fl * B * cols + c;
+        float run = 0.0f;
+        for (int b = 0; b < B; ++b) { run += col[(size_t)b * cols]; col[(size_t)b * cols] = run; }
+    }
+}
+
+struct CbPairSolveArgs {
+    CbData d;
+    const float* H;          // scanned pair histograms of features [f0, f0 + nf)
+    const float* D;          // scanned derivative histograms [nf][B][L]
+    int f0, nf, L, B;
+    float l2, prior;
+    float* gain;             // [nf][B]: gain of candidate (feature, bin); -inf where there is no candidate
+};
+
+// One block per candidate (feature, bin).  S = 2L unknowns, children ordered [left of leaf 0 .. L-1, right of 0 .. L-1].
+// Shared memory: A [S][S] doubles (symmetrised weights, then the system, then its Cholesky factor), dvec [S], x [S],
+// mx [S].  blockDim.x >= S.
+__global__ void __launch_bounds__(128) cb_pair_solve_kernel(CbPairSolveArgs a) {
+    extern __shared__ double sm[];
+    const int L = a.L, S = 2 * L;
+    double* A = sm;
+    double* W = A + (size_t)S * S;          // symmetric weights (kept for the gain)
+    double* dv = W + (size_t)S * S;
+    double* x = dv + S;
+    double* red = x + S;
+    const int fl = blockIdx.x / a.B, t = blockIdx.x % a.B;
+    const int f = a.f0 + fl;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const bool onehot = a.d.feat_onehot && a.d.feat_onehot[f];
+    const int nb = a.d.feat_nb[f];
+    const int ncand = onehot ? nb : nb - 1;
+    const float fw = a.d.feat_weight ? a.d.feat_weight[f] : 1.0f;
+    if (t >= ncand || fw <= 0.0f) {
+        if (tid == 0) a.gain[(size_t)fl * a.B + t] = -INFINITY;
+        return;
+    }
+    const size_t bs = (size_t)L * L * 4;
+    const float* Hf = a.H + (size_t)fl * a.B * bs;
+    const float* Ht = Hf + (size_t)t * bs;
+    const float* Hlast = Hf + (size_t)(nb - 1) * bs;      // float features: totals = prefix at the last bin
+    for (int c = tid; c < S * S; c += nt) W[c] = 0.0;
+    __syncthreads();
+    // off-diagonal weights of the directed pair cells, then symmetrise: W[u][v] = w(u -> v) + w(v -> u)
+    for (int c = tid; c < L * L; c += nt) {
+        const int la = c / L, lb = c % L;
+        const float* h = Ht + (size_t)c * 4;
+        double ll, lr, rl, rr;
+        if (onehot) {
+            // totals of a one-hot feature: sum over its values of the three stored configurations
+            double tot = 0.0;
+            for (int v = 0; v < nb; ++v) {
+                const float* hv = Hf + (size_t)v * bs + (size_t)c * 4;
+                tot += (double)hv[0] + 0.5 * ((double)hv[1] + (double)hv[2]);
+            }
+            rr = h[0]; rl = h[1]; lr = h[2];
+            ll = tot - rr - rl - lr;
+        } else {
+            const float* hl = Hlast + (size_t)c * 4;
+            const double tot = (double)hl[0] + (double)hl[2];
+            ll = (double)h[1] + (double)h[3];
+            lr = (double)h[0] - (double)h[1];
+            rl = (double)h[2] - (double)h[3];
+            rr = tot - ((double)h[0] + (double)h[2]);
+        }
+        // directed cell (child of winner, child of loser): add to both orientations of the symmetric matrix
+        atomicAdd(&W[(size_t)la * S + lb], ll);             atomicAdd(&W[(size_t)lb * S + la], ll);
+        atomicAdd(&W[(size_t)la * S + (lb + L)], lr);       atomicAdd(&W[(size_t)(lb + L) * S + la], lr);
+        atomicAdd(&W[(size_t)(la + L) * S + lb], rl);       atomicAdd(&W[(size_t)lb * S + (la + L)], rl);
+        atomicAdd(&W[(size_t)(la + L) * S + (lb + L)], rr); atomicAdd(&W[(size_t)(lb + L) * S + (la + L)], rr);
+    }
+    // derivative sums of the children
+    for (int l = tid; l < L; l += nt) {
+        const float* Df = a.D + (size_t)fl * a.B * L;
+        double left, tot;
+        if (onehot) {
+            tot = 0.0;
+            for (int v = 0; v < nb; ++v) tot += (double)Df[(size_t)v * L + l];
+            left = tot - (double)Df[(size_t)t * L + l];
+        } else {
+            tot = (double)Df[(size_t)(nb - 1) * L + l];
+            left = (double)Df[(size_t)t * L + l];
+        }
+        dv[l] = left;
+        dv[l + L] = tot - left;
+    }
+    __syncthreads();
+    // Laplacian M = diag(rowsum W) - W; system = M[:-1, :-1] + non_diag + I * (diag - non_diag + 1e-9)
+    const double cellp = 1.0 / (double)S;
+    const double non_diag = -(double)a.prior * cellp;
+    const double diag = (double)a.prior * (1.0 - cellp) + (double)a.l2;
+    const int n = S - 1;
+    for (int r = tid; r < S; r += nt) {
+        double rs = 0.0;
+        for (int c = 0; c < S; ++c) rs += W[(size_t)r * S + c];
+        x[r] = rs;                                  // row sums (x is free until the solve)
+    }
+    __syncthreads();
+    for (int c = tid; c < S * S; c += nt) {
+        const int r = c / S, k = c % S;
+        const double m = (r == k ? x[r] : 0.0) - W[c];
+        A[c] = m + non_diag + (r == k ? (diag - non_diag + 1e-9) : 0.0);
+    }
+    __syncthreads();
+    // Cholesky of the leading n x n block (lower triangle, in place), right-looking
+    for (int k = 0; k < n; ++k) {
+        if (tid == 0) A[(size_t)k * S + k] = sqrt(fmax(A[(size_t)k * S + k], 1e-300));
+        __syncthreads();
+        const double dk = A[(size_t)k * S + k];
+        for (int r = k + 1 + tid; r < n; r += nt) A[(size_t)r * S + k] /= dk;
+        __syncthreads();
+        const int m = n - k - 1;
+        for (int c = tid; c < m * m; c += nt) {
+            const int r = k + 1 + c / m, q = k + 1 + c % m;
+            if (q <= r) A[(size_t)r * S + q] -= A[(size_t)r * S + k] * A[(size_t)q * S + k];
+        }
+        __syncthreads();
+    }
+    // forward and backward substitution by one warp-sized loop (n <= 127)
+    if (tid == 0) {
+        for (int r = 0; r < n; ++r) {
+            double v = dv[r];
+            for (int q = 0; q < r; ++q) v -= A[(size_t)r * S + q] * x[q];
+            x[r] = v / A[(size_t)r * S + r];
+        }
+        for (int r = n - 1; r >= 0; --r) {
+            double v = x[r];
+            for (int q = r + 1; q < n; ++q) v -= A[(size_t)q * S + r] * x[q];
+            x[r] = v / A[(size_t)r * S + r];
+        }
+        x[n] = 0.0;
+        double mean = 0.0;
+        for (int r = 0; r < S; ++r) mean += x[r];
+        mean /= (double)S;
+        for (int r = 0; r < S; ++r) x[r] -= mean;
+    }
+    __syncthreads();
+    // gain = x.d - x'Mx / 2 with M x = rowsum * x - W x
+    double part = 0.0;
+    for (int r = tid; r < S; r += nt) {
+        double rs = 0.0, wx = 0.0;
+        for (int c = 0; c < S; ++c) { rs += W[(size_t)r * S + c]; wx += W[(size_t)r * S + c] * x[c]; }
+        part += x[r] * dv[r] - 0.5 * x[r] * (rs * x[r] - wx);
+    }
+    part = cb_warp_sum_d(part);
+    if ((tid & 31) == 0) red[tid >> 5] = part;
+    __syncthreads();
+    if (tid == 0) {
+        double g = 0.0;
+        for (int w = 0; w < (nt >> 5); ++w) g += red[w];
+        a.gain[(size_t)fl * a.B + t] = (float)(g * (double)fw);
+    }
+}
+
+CB_API long long cb_pair_hist_floats(int nfeat, int L, int B) { return (long long)nfeat * B * L * L * 4; }
+
+// Pair histograms + derivative histograms of feature groups [g0, g0 + ng) (H and D zeroed by the caller), scanned.
+CB_API int cb_pair_hist(const CbData* d, const unsigned short* leaf, const int* wi, const int* li, const float* w,
+                        long long npairs, const float* der, int L, int B, int g0, int ng, float* H, float* D, int grid,
+                        cudaStream_t st) {
+    CbPairHistArgs a{*d, leaf, wi, li, w, npairs, L, B, g0, ng, H};
+    if (npairs > 0) cb_pair_hist_kernel<<<grid, 256, 0, st>>>(a);
+    cb_pair_der_hist_kernel<<<grid, 256, 0, st>>>(*d, leaf, der, L, B, g0, ng, D);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    return 0;
+}
+
+CB_API int cb_pair_scan(const CbData* d, int f0, int nf, int L, int B, float* H, float* D, int grid, cudaStream_t st) {
+    cb_pair_scan_kernel<<<grid, 256, 0, st>>>(*d, f0, nf, B, (long long)L * L * 4, H);
+    cb_pair_scan_kernel<<<grid, 256, 0, st>>>(*d, f0, nf, B, (long long)L, D);
+    return (int)cudaGetLastError();
+}
+
+CB_API int cb_pair_solve_smem_bytes(int L) { const int S = 2 * L; return (2 * S * S + 2 * S + 8) * 8; }
+
+CB_API int cb_pair_solve(const CbData* d, const float* H, const float* D, int f0, int nf, int L, int B, float l2, float prior,
+                         float* gain, cudaStream_t st) {
+    const int smem = cb_pair_solve_smem_bytes(L);
+    int dev = 0, optin = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (smem > optin) return -2;
+    static unsigned long long set = 0ull;
+    if (cb_first_on_device(&set)) {
+        cudaError_t e = cudaFuncSetAttribute(cb_pair_solve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+        if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
+    }
+    CbPairSolveArgs a{*d, H, D, f0, nf, L, B, l2, prior, gain};
+    cb_pair_solve_kernel<<<(unsigned)(nf * B), 128, smem, st>>>(a);
+    return (int)cudaGetLastError();
+}

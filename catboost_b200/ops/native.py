@@ -22,7 +22,8 @@ from pathlib import Path
 
 _HERE = Path(__file__).resolve().parent
 CUDA_SRC = [_HERE / "cuda" / "cb_kernels.cu", _HERE / "cuda" / "cb_fused.cu", _HERE / "cuda" / "cb_leaf.cu",
-            _HERE / "cuda" / "cb_quantize_tma.cu", _HERE / "cuda" / "cb_ranking.cu", _HERE / "cuda" / "cb_ctr.cu"]
+            _HERE / "cuda" / "cb_quantize_tma.cu", _HERE / "cuda" / "cb_ranking.cu", _HERE / "cuda" / "cb_ctr.cu",
+            _HERE / "cuda" / "cb_multiclass.cu", _HERE / "cuda" / "cb_search.cu", _HERE / "cuda" / "cb_pairwise.cu"]
 CUDA_HDR = sorted((_HERE / "cuda").glob("*.cuh")) + sorted((_HERE / "cuda").glob("*.h"))
 CPU_SRC = [_HERE / "cpu" / "cb_cpu.cpp", _HERE / "cpu" / "cb_cityhash.h"]
 MODEL_SRC = [_HERE / "cpu" / "cb_model_capi.cpp", _HERE / "cpu" / "cb_model_capi.h", _HERE / "cpu" / "cb_cityhash.h"]
@@ -181,7 +182,25 @@ _SIGS = {
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "cb_leaf_newton_sums_doubles": (c_int, [c_int]),
     "cb_leaf_newton_msg_bytes": (c_int, [c_int]),
-    "cb_iter_end": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "cb_iter_end": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "cb_leaf_search": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_ull, c_void_p, c_void_p,
+                               c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "cb_pair_hist_floats": (c_ll, [c_int, c_int, c_int]),
+    "cb_pair_hist": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int,
+                             c_void_p, c_void_p, c_int, c_void_p]),
+    "cb_pair_scan": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "cb_pair_solve_smem_bytes": (c_int, [c_int]),
+    "cb_pair_solve": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p]),
+    "cb_mc_max_classes": (c_int, []),
+    "cb_mc_grad": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_void_p, c_int, c_int, c_float,
+                           c_ull, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "cb_mc_leaf_sums_doubles": (c_int, [c_int, c_int]),
+    "cb_mc_leaf_msg_bytes": (c_int, [c_int, c_int]),
+    "cb_mc_leaf_smem_bytes": (c_int, [c_int, c_int]),
+    "cb_mc_leaf_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                c_void_p, c_int, c_void_p]),
+    "cb_mc_metric": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "cb_apply_tree_bins": (c_int, [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                                    c_void_p]),
     "cb_leaf_index": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),

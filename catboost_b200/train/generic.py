@@ -304,7 +304,21 @@ class GenericLearner:
             h_prev = h
         return TreeResult("oblivious", splits=splits, n_leaves=1 << depth, leaf=self.leaf)
 
-    def _per_leaf_best(self, h, K, noise_std, fmask):
+    def _per_leaf_best(self, h, K, noise_std, fmask, node_ids=None):
+        if self.dev.type == "cuda" and self.monotone is None:
+            # device search: one warp per (leaf, feature) + one warp per leaf, 16 bytes per leaf read back
+            self._search_calls = getattr(self, "_search_calls", 0) + 1
+            lid = None if node_ids is None else torch.tensor(list(node_ids), dtype=torch.int32, device=self.dev)
+            score, feat, bins, gain = ops.leaf_search(
+                self.store, h, K, self.scorer.l2, self.o.score_function, noise_std,
+                (int(self.o.random_seed) * 1000003 + self._search_calls * 7919) & 0x7FFFFFFFFFFFFFFF, lid, fmask.float(),
+                float(self.o.min_data_in_leaf) if self.use_count else 0.0)
+            best = np.where(feat >= 0, feat.astype(np.int64) * self.scorer.B + bins, 0)
+            return best, np.where(feat >= 0, score, -np.inf), gain
+        return self._per_leaf_best_tensor(h, K, noise_std, fmask)
+
+    def _per_leaf_best_tensor(self, h, K, noise_std, fmask):
+        """The same search as tensor code (CPU path, monotone constraints, and the oracle of the device kernel)."""
         sc = self.scorer
         cstat = K + 1 if self.use_count else None
         num, den, cnt, (left, right, total) = sc.candidate_terms(h, K, cstat)
@@ -343,7 +357,7 @@ class GenericLearner:
             table = torch.full((len(node_split),), -1, dtype=torch.int16, device=self.dev)
             table[torch.tensor(frontier, device=self.dev)] = torch.arange(len(frontier), dtype=torch.int16, device=self.dev)
             h = self._hist(stats, table, len(frontier))
-            best, bscore, _ = self._per_leaf_best(h, K, noise_std, fmask)
+            best, bscore, _ = self._per_leaf_best(h, K, noise_std, fmask, frontier)
             new_frontier = []
             for j, node in enumerate(frontier):
                 if not math.isfinite(float(bscore[j])):
@@ -371,7 +385,7 @@ class GenericLearner:
             table = torch.full((len(node_split),), -1, dtype=torch.int16, device=self.dev)
             table[torch.tensor(nodes, device=self.dev)] = torch.arange(len(nodes), dtype=torch.int16, device=self.dev)
             h = self._hist(stats, table, len(nodes))
-            best, bscore, bgain = self._per_leaf_best(h, K, noise_std, fmask)
+            best, bscore, bgain = self._per_leaf_best(h, K, noise_std, fmask, nodes)
             for j, node in enumerate(nodes):
                 if math.isfinite(float(bscore[j])) and node_depth[node] < max_depth:
                     cand[node] = (float(bgain[j]), int(best[j]) // B, int(best[j]) % B)
@@ -472,8 +486,18 @@ def estimate_leaves(objective, approx, target, weight, leaf, n_leaves, n, opts, 
         sd, sh, sw = sums[:, :dims], sums[:, dims:2 * dims], sums[:, 2 * dims]
         if leaf_w is None:
             leaf_w = sw.clone()
-        den = (sh if method == "Newton" else sw.unsqueeze(1).expand_as(sd)) + l2
-        step = torch.where(den > 0, sd / den, torch.zeros_like(sd)).float()
+        blocks = getattr(objective, "hess_blocks", None) if (method == "Newton" and dims > 1) else None
+        if blocks is not None:
+            # the K x K Hessian block of every leaf (catboost/cuda/methods/leaves_estimation/descent_helpers.cpp:91-117):
+            # (H + l2 I) step = gradient
+            H = blocks(a, target, wvec, idx, n_leaves)
+            if ctx is not None and ctx.is_distributed:
+                ctx.all_reduce_sum_(H)
+            H = H + l2 * torch.eye(dims, dtype=H.dtype, device=H.device)
+            step = torch.linalg.solve(H, sd.double().unsqueeze(-1)).squeeze(-1).float()
+        else:
+            den = (sh if method == "Newton" else sw.unsqueeze(1).expand_as(sd)) + l2
+            step = torch.where(den > 0, sd / den, torch.zeros_like(sd)).float()
         if backtrack:
             base, direction, f_base, cur_step = delta, step, v, 1.0
             dirgrad = float((sd.double() * step.double()).sum().item())

@@ -57,7 +57,7 @@ class GpuObliviousEngine:
                  timeout_s: float = 20.0, quantized_hist: bool = True, dynamic_work: bool = True,
                  der_fn=None, zero_mean_leaves: bool = False, max_bundle: int = 8,
                  fused_leaf_steps: bool = True, leaf_backtracking: str = "AnyImprovement",
-                 fuse_leaf_update: bool = True):
+                 fuse_leaf_update: bool = True, dims: int = 1):
         assert store.bins.is_cuda, "GpuObliviousEngine needs a CUDA store"
         if depth > 16:
             raise ValueError("depth must be <= 16")
@@ -103,11 +103,27 @@ class GpuObliviousEngine:
             self.ext_hess = torch.zeros(store.npad, dtype=torch.float32, device=self.dev)
         n, npad, dev = store.n, store.npad, self.dev
         self.n, self.npad = n, npad
-        self.S = 2
+        # K > 1: MultiClass.  K derivative columns + one weight column drive the same level kernels; the cursor, the leaf
+        # values and the model rows get K entries per document / leaf
+        self.K = K = int(dims)
+        if K > 1:
+            if K > int(self.lib.cb_mc_max_classes()):
+                raise ValueError("too many classes for the device trainer")
+            if der_fn is not None or ext_der is not None:
+                raise ValueError("external derivatives are one-dimensional")
+            if self.quantized_hist:
+                self.narrow_hist = False          # single-cell bundles exist for two statistics only: exact hi/lo cells
+            else:
+                self.quantized_hist = True
+        self.S = K + 1
         self.L = 1 << depth
         f32, i32, i64, f64 = torch.float32, torch.int32, torch.int64, torch.float64
-        self.approx = torch.zeros(npad, dtype=f32, device=dev)
-        self.approx[:n] = approx0.to(dev, f32)
+        if K > 1:
+            self.approx = torch.zeros((K, npad), dtype=f32, device=dev)
+            self.approx[:, :n] = approx0.to(dev, f32).reshape(K, n)
+        else:
+            self.approx = torch.zeros(npad, dtype=f32, device=dev)
+            self.approx[:n] = approx0.to(dev, f32).reshape(-1)
         self.target = torch.zeros(npad, dtype=f32, device=dev)
         self.target[:n] = target.to(dev, f32)
         self.weight = None
@@ -127,17 +143,19 @@ class GpuObliviousEngine:
         self.loss_hist = torch.zeros((cap, 2), dtype=f64, device=dev)
         self.splits = torch.full((cap * depth, 4), 0, dtype=i32, device=dev)
         self.splits[:, 0] = -1
-        self.model_vals = torch.zeros((cap, self.L), dtype=f32, device=dev)
+        self.model_vals = torch.zeros((cap, self.L * K), dtype=f32, device=dev)
         self.model_wts = torch.zeros((cap, self.L), dtype=f32, device=dev)
-        self.cur_vals = torch.zeros(self.L, dtype=f32, device=dev)
-        self.delta = torch.zeros(self.L, dtype=f32, device=dev)
+        self.cur_vals = torch.zeros(self.L * K, dtype=f32, device=dev)
+        self.delta = torch.zeros(self.L * K, dtype=f32, device=dev)
         self.leaf_w = torch.zeros(self.L, dtype=f32, device=dev)
         # three rotating copies of the per-leaf (der, hess, weight) sums + the loss sum
-        self.sums = torch.zeros(max(self.L * 9, int(self.lib.cb_leaf_newton_sums_doubles(self.L))), dtype=f64, device=dev)
+        self.sums = torch.zeros(max(self.L * 9, int(self.lib.cb_leaf_newton_sums_doubles(self.L)),
+                                    int(self.lib.cb_mc_leaf_sums_doubles(K, self.L)) if K > 1 else 0), dtype=f64, device=dev)
+        self.sums_combined = torch.zeros_like(self.sums) if K > 1 else None
         self.counter = torch.zeros(1, dtype=i32, device=dev)
         self.best_key = torch.zeros(1, dtype=i64, device=dev)
         self.cur_loss = torch.zeros(2, dtype=f64, device=dev)
-        self.statmax = torch.zeros(2, dtype=f32, device=dev)
+        self.statmax = torch.zeros(self.S, dtype=f32, device=dev)
         msg_bytes = self.lib.cb_select_msg_bytes()
         self.msg_local = torch.zeros((max(self.R, 1), msg_bytes // 8 + 1), dtype=i64, device=dev)
         self.msg_all = torch.zeros((max(self.R, 1), msg_bytes // 8 + 1), dtype=i64, device=dev)
@@ -169,7 +187,8 @@ class GpuObliviousEngine:
         slot_floats = slots_max * self.S * self.Wmax * (2 if self.R > 1 else 1)
         select_words = 2 + max(1, (1 << max(depth - 1, 0)) // 32)
         mbox_bytes = max(msg_bytes, 256, 8 * select_words,
-                         int(self.lib.cb_leaf_newton_msg_bytes(self.L)) if self.L <= 4096 else 0)
+                         int(self.lib.cb_leaf_newton_msg_bytes(self.L)) if self.L <= 4096 else 0,
+                         int(self.lib.cb_mc_leaf_msg_bytes(K, self.L)) if (K > 1 and self.L <= 1024) else 0)
         self.arena = (PeerArena(self.ctx, ArenaLayout(self.R, mbox_bytes, slot_floats), timeout_s=timeout_s)
                       if self.reduce == "fused" else None)
         if self.reduce == "fused":
@@ -189,6 +208,7 @@ class GpuObliviousEngine:
         self.grid_stream = self.sm_count * 8
         self.graph = None
         self.done = 0
+        self._warmed = False
         self.launches_per_iter = 0
 
     # ------------------------------------------------------------------------------------------------------
@@ -269,6 +289,13 @@ class GpuObliviousEngine:
     # ------------------------------------------------------------------------------------------------------
     def _grad(self):
         chk = native.cuda_check
+        if self.K > 1:
+            chk(self.lib.cb_mc_grad(_p(self.approx), _p(self.target), _p(self.weight), _p(self.leaf), _p(self.cur_vals),
+                                    self.n, self.npad, self.K, _p(self.stats), self.newton_stats, self.boot_type, self.boot_p,
+                                    self.seed, _p(self.iter_ptr), _p(self.scal), _p(self.statmax), self.grid_stream,
+                                    self._stream()), "cb_mc_grad")
+            self.launches_per_iter += 1
+            return
         chk(self.lib.cb_grad_pointwise(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target), _p(self.weight),
                                        _p(self.leaf), _p(self.cur_vals), self.n, self.npad, _p(self.stats),
                                        self.newton_stats, self.boot_type, self.boot_p, self.seed, _p(self.iter_ptr),
@@ -339,6 +366,18 @@ class GpuObliviousEngine:
                                self.depth, self.depth - 1, self.grid_stream, self._stream()), "cb_update_leaf")
         self.launches_per_iter += 1
         comm = ctypes.c_void_p(self.arena.handle) if (self.arena is not None and self.R > 1) else None
+        if self.K > 1:
+            if self.R > 1 and comm is None:
+                raise RuntimeError("MultiClass on several ranks needs the peer arena (histogram_reduce='fused')")
+            for it in range(self.leaf_iterations):
+                first, last = (1 if it == 0 else 0), (1 if it == self.leaf_iterations - 1 else 0)
+                chk(lib.cb_mc_leaf_step(_p(self.approx), _p(self.target), _p(self.weight), _p(self.leaf), self.n, self.npad,
+                                        self.K, self.L, _p(self.delta), _p(self.sums), _p(self.sums_combined), _p(self.leaf_w),
+                                        first, last, self.leaf_newton, self.l2, self.lr, _p(self.cur_vals), _p(self.model_vals),
+                                        _p(self.model_wts), self.L, _p(self.iter_ptr), comm, self.sm_count * 4, self._stream()),
+                    "cb_mc_leaf_step")
+                self.launches_per_iter += 2
+            return
         if self.R > 1 and comm is None:
             # NCCL baseline: sums are all-reduced between two kernels
             for it in range(self.leaf_iterations):
@@ -402,8 +441,14 @@ class GpuObliviousEngine:
         chk, lib = native.cuda_check, self.lib
         for k, ev in enumerate(self.eval_sets):
             chk(lib.cb_apply_tree_bins(ctypes.c_void_p(ev.store.handle), _p(ev.approx), ev.store.npad, _p(self.splits),
-                                       _p(self.iter_ptr), self.depth, _p(self.cur_vals), 1, self.grid_stream,
+                                       _p(self.iter_ptr), self.depth, _p(self.cur_vals), self.K, self.grid_stream,
                                        self._stream()), "cb_apply_tree_bins")
+            if self.K > 1:
+                chk(lib.cb_mc_metric(_p(ev.approx), _p(ev.target), _p(ev.weight), ev.store.n, ev.store.npad, self.K, None,
+                                     None, ctypes.c_void_p(self.eval_scal.data_ptr() + 16 * k), self.grid_stream,
+                                     self._stream()), "cb_mc_metric")
+                self.launches_per_iter += 2
+                continue
             chk(lib.cb_metric_sum(self.loss_id, self.p0, self.p1, _p(ev.approx), _p(ev.target), _p(ev.weight),
                                   ev.store.n, None, None, ctypes.c_void_p(self.eval_scal.data_ptr() + 16 * k),
                                   self.grid_stream, self._stream()), "cb_metric_sum")
@@ -440,7 +485,7 @@ class GpuObliviousEngine:
         self._evals()
         n_extra = 2 * len(self.eval_sets)
         native.cuda_check(self.lib.cb_iter_end(_p(self.iter_ptr), _p(self.scal), _p(self.loss_hist), _p(self.eval_scal),
-                                               _p(self.eval_hist), n_extra, _p(self.statmax), self._stream()),
+                                               _p(self.eval_hist), n_extra, _p(self.statmax), self.S, self._stream()),
                           "cb_iter_end")
         self.launches_per_iter += 1
 
@@ -460,8 +505,9 @@ class GpuObliviousEngine:
             raise RuntimeError("more iterations requested than the engine was sized for")
         graph_ok = self.use_graph and not (self.R > 1 and self.reduce != "fused")
         for _ in range(count):
-            if not graph_ok or self.done == 0:
+            if not graph_ok or not self._warmed:
                 self._iteration()
+                self._warmed = True
             else:
                 if self.graph is None:
                     self._capture()
@@ -472,9 +518,14 @@ class GpuObliviousEngine:
         """Mean learn loss including the newest tree (one streaming kernel + a 16-byte device->host read),
         summed over ranks."""
         self.cur_loss.zero_()
-        native.cuda_check(self.lib.cb_metric_sum(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target),
-                                                 _p(self.weight), self.n, _p(self.leaf), _p(self.cur_vals),
-                                                 _p(self.cur_loss), self.grid_stream, self._stream()), "cb_metric_sum")
+        if self.K > 1:
+            native.cuda_check(self.lib.cb_mc_metric(_p(self.approx), _p(self.target), _p(self.weight), self.n, self.npad,
+                                                    self.K, _p(self.leaf), _p(self.cur_vals), _p(self.cur_loss),
+                                                    self.grid_stream, self._stream()), "cb_mc_metric")
+        else:
+            native.cuda_check(self.lib.cb_metric_sum(self.loss_id, self.p0, self.p1, _p(self.approx), _p(self.target),
+                                                     _p(self.weight), self.n, _p(self.leaf), _p(self.cur_vals),
+                                                     _p(self.cur_loss), self.grid_stream, self._stream()), "cb_metric_sum")
         if self.R > 1:
             self.ctx.all_reduce_sum_(self.cur_loss)
         if pinned is not None:
@@ -492,12 +543,57 @@ class GpuObliviousEngine:
             self.arena.check_status()
         n = self.n
         leaf = self.leaf[:n].long() & 0xFFFF
-        self.approx[:n] += self.cur_vals[leaf]
+        if self.K > 1:
+            self.approx[:, :n] += self.cur_vals.view(self.L, self.K)[leaf].t()
+        else:
+            self.approx[:n] += self.cur_vals[leaf]
         self.cur_vals.zero_()
         self.leaf.zero_()
         T = self.done
         sp = self.splits[: T * self.depth].cpu().numpy().reshape(T, self.depth, 4)
         return sp, self.model_vals[:T].cpu().numpy(), self.model_wts[:T].cpu().numpy()
+
+    # ------------------------------------------------------------------------------------------------------
+    def export_trees(self):
+        """(splits [T, depth, 4], leaf values [T, L], leaf weights [T, L]) of the finished iterations, on the host.
+        Unlike ``finish`` this leaves the engine ready to continue (used for snapshots)."""
+        torch.cuda.synchronize(self.dev)
+        T = self.done
+        return (self.splits[: T * self.depth].cpu().numpy().reshape(T, self.depth, 4),
+                self.model_vals[:T].cpu().numpy(), self.model_wts[:T].cpu().numpy())
+
+    def restore_trees(self, splits: np.ndarray, vals: np.ndarray, wts: np.ndarray):
+        """Continue a run from ``T0 = len(splits)`` finished trees: the trees go back into the device-side model, the
+        training and evaluation cursors are rebuilt by applying the trees in their original order (the same fp32
+        additions the uninterrupted run made, so the continuation is bit-identical), and the iteration counter --
+        which also drives the counter-based random numbers of the bootstrap and of the score noise -- is set to T0.
+        The reference restores the same way: models are stored, cursors are recomputed
+        (catboost/cuda/methods/doc_parallel_boosting.h:500-512)."""
+        if self.done != 0:
+            raise RuntimeError("restore_trees must be called before the first step")
+        T0 = int(len(splits))
+        if T0 == 0:
+            return
+        if T0 > self.iterations:
+            raise RuntimeError("the snapshot holds more trees than this run asks for")
+        sp = torch.from_numpy(np.ascontiguousarray(splits, dtype=np.int32).reshape(T0 * self.depth, 4)).to(self.dev)
+        self.splits[: T0 * self.depth] = sp
+        self.model_vals[:T0] = torch.from_numpy(np.ascontiguousarray(vals, dtype=np.float32)).to(self.dev)
+        self.model_wts[:T0] = torch.from_numpy(np.ascontiguousarray(wts, dtype=np.float32)).to(self.dev)
+        chk, lib = native.cuda_check, self.lib
+        sets = [(self.store, self.approx)] + [(ev.store, ev.approx) for ev in self.eval_sets]
+        for t in range(T0):
+            sp_ptr = ctypes.c_void_p(self.splits.data_ptr() + t * self.depth * 16)
+            v_ptr = ctypes.c_void_p(self.model_vals.data_ptr() + t * self.L * self.K * 4)
+            for st, ap in sets:
+                chk(lib.cb_apply_tree_bins(ctypes.c_void_p(st.handle), _p(ap), st.npad, sp_ptr, None, self.depth, v_ptr, self.K,
+                                           self.grid_stream, self._stream()), "cb_apply_tree_bins")
+        self.iter_ptr.fill_(T0)
+        self.cur_vals.zero_()
+        self.leaf.zero_()
+        self.done = T0
+        self._resumed = True
+        torch.cuda.synchronize(self.dev)
 
     def learn_loss_history(self) -> np.ndarray:
         """Mean learn loss seen at the start of every finished iteration (summed over ranks)."""

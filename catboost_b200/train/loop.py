@@ -78,7 +78,15 @@ def _use_fast_engine(o, objective, store, dims) -> bool:
     # objective's tensor code once per tree, which only allows a single leaf-estimation step
     native = objective.native_id is not None
     external = (not native) and dims == 1 and int(o.leaf_estimation_iterations) == 1
-    return (store.bins.is_cuda and o.grow_policy == "SymmetricTree" and (native or external) and dims == 1
+    if dims > 1:
+        # MultiClass: K derivative columns through the same level kernels, K x K Newton leaves on the device.  The leaf
+        # kernel keeps K + K (K + 1) / 2 + 1 cells per leaf in shared memory and has no step-length control.
+        K, L = int(dims), 1 << int(o.depth)
+        ok = (native and objective.name == "MultiClass" and 2 <= K <= 16 and L * (K + K * (K + 1) // 2 + 1) * 4 <= 96 * 1024
+              and (int(o.leaf_estimation_iterations) == 1 or str(o.leaf_estimation_backtracking) == "No"))
+        if not ok:
+            return False
+    return (store.bins.is_cuda and o.grow_policy == "SymmetricTree" and (native or external)
             and o.boosting_type == "Plain" and o.leaf_estimation_method in ("Newton", "Gradient")
             and float(o.rsm) >= 1.0 and int(o.min_data_in_leaf) <= 1
             and o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson")
@@ -152,10 +160,13 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
                 raise CatBoostError("monotone_constraints need symmetric trees and a one-dimensional model")
             monotone_flat = learner.monotone.cpu().numpy()
     plearner = None
-    if getattr(objective, "pairwise_scoring", False) and o.grow_policy == "SymmetricTree" and \
-            not (ctx is not None and ctx.is_distributed):
-        from .pairwise import PairwiseLearner
-        plearner = PairwiseLearner(store, o, seed=int(o.random_seed))
+    if getattr(objective, "pairwise_scoring", False) and o.grow_policy == "SymmetricTree":
+        from .pairwise import PairwiseKernelLearner, PairwiseLearner
+        if store.bins.is_cuda and int(o.depth) <= 6:
+            # kernels: pair histograms, per-candidate systems, Cholesky and gain on the device; histograms summed over ranks
+            plearner = PairwiseKernelLearner(store, o, seed=int(o.random_seed), ctx=ctx)
+        elif not (ctx is not None and ctx.is_distributed):
+            plearner = PairwiseLearner(store, o, seed=int(o.random_seed))
     ordered = None
     if o.boosting_type == "Ordered" and not (ctx is not None and ctx.is_distributed):
         ordered = OrderedState(o, n, train_pool, dev, approx[:, :n])
@@ -420,9 +431,14 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
     T = int(o.iterations)
     f32 = torch.float32
     evs = []
+    K = int(objective.dims)
     for es, y, w, b in zip(eval_stores, eval_y, eval_w, base_evals):
-        ap = torch.zeros(es.npad, dtype=f32, device=dev)
-        ap[: es.n] = torch.from_numpy(np.ascontiguousarray(b[0])).to(dev, f32)
+        if K > 1:
+            ap = torch.zeros((K, es.npad), dtype=f32, device=dev)
+            ap[:, : es.n] = torch.from_numpy(np.ascontiguousarray(b)).to(dev, f32)
+        else:
+            ap = torch.zeros(es.npad, dtype=f32, device=dev)
+            ap[: es.n] = torch.from_numpy(np.ascontiguousarray(b[0])).to(dev, f32)
         tt = torch.zeros(es.npad, dtype=f32, device=dev)
         tt[: es.n] = torch.from_numpy(np.asarray(y, dtype=np.float32)).to(dev)
         ww = None
@@ -444,23 +460,49 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
         eng = GpuObliviousEngine(
             store, torch.from_numpy(np.asarray(y_train, dtype=np.float32)),
             None if w_train is None else torch.from_numpy(np.asarray(w_train, dtype=np.float32)),
-            torch.from_numpy(np.ascontiguousarray(base_train[0], dtype=np.float32)), objective,
+            torch.from_numpy(np.ascontiguousarray(base_train if K > 1 else base_train[0], dtype=np.float32)), objective,
             depth=int(o.depth), iterations=T, learning_rate=float(o.learning_rate), l2_leaf_reg=float(o.l2_leaf_reg),
             score_function=o.score_function, random_strength=float(o.random_strength), bootstrap_type=btype,
             bootstrap_param=boot_p, leaf_method=o.leaf_estimation_method,
             leaf_iterations=int(o.leaf_estimation_iterations), seed=int(o.random_seed), ctx=ctx,
             reduce=("fused" if o.histogram_reduce in ("fused", None) else "nccl"), eval_sets=evs,
             quantized_hist={"narrow": True, "wide": "wide", "float": False}[o.histogram_cells or "narrow"],
-            leaf_backtracking=str(o.leaf_estimation_backtracking or "AnyImprovement"),
+            leaf_backtracking=str(o.leaf_estimation_backtracking or "AnyImprovement"), dims=K,
             der_fn=der_fn, zero_mean_leaves=bool(der_fn is not None and getattr(objective, "zero_mean_leaves", False)))
+    # resume from a snapshot: same container and state as the general learner writes (trees + metric history), so either
+    # trainer can pick up the other's file
+    start = 0
+    restored = snap.try_load(o)
+    if restored is not None and restored.get("trees"):
+        t0 = restored["trees"]
+        if any(t.get("kind") != "oblivious" or len(t["splits"]) != int(o.depth) for t in t0):
+            raise CatBoostError("the snapshot was written by a run with a different tree shape")
+        hist.data, hist.iters = restored["hist"], list(restored["iters"])
+        eng.restore_trees(np.stack([np.asarray(t["splits"], dtype=np.int32) for t in t0]),
+                          np.stack([np.asarray(t["values"], dtype=np.float32).reshape(-1) for t in t0]),
+                          np.stack([np.asarray(t["weights"], dtype=np.float32).reshape(-1) for t in t0]))
+        start = len(t0)
+        if od is not None and eval_names:
+            for v in hist.data.get(eval_names[0], {}).get(str(metrics[0]), []):
+                od.add(v)
+
+    def snapshot_state():
+        sp_, vals_, wts_ = eng.export_trees()
+        return dict(trees=[dict(kind="oblivious", splits=sp_[t], node_split=None, leaf_of_node=None,
+                                values=(vals_[t].reshape(-1, K) if K > 1 else vals_[t]), weights=wts_[t])
+                           for t in range(len(sp_))], hist=hist.data, iters=hist.iters)
+
     loss_metric_name = objective.name
     # "cheap" logging: the only tracked metric is the objective itself, which the device already accumulates
     cheap = (len(metrics) == 1 and isinstance(o.loss_function, str) and str(metrics[0]) == o.loss_function
              and der_fn is None)
     need_each = bool(od is not None or callbacks)
-    want_log = bool(o.verbose) or bool(eval_stores)
+    # metrics other than the objective only exist if they are evaluated along the way (the objective's own curve can be
+    # filled from the device history afterwards)
+    want_log = bool(o.verbose) or bool(eval_stores) or not cheap
     period = 1 if need_each else (max(1, int(o.metric_period)) if want_log else T)
-    done, best_it, best_val, stop = 0, None, None, False
+    done, best_it, best_val, stop = start, None, None, False
+    final_loss = None
     t_loop = time.time()
     pinned = torch.zeros(2, dtype=torch.float64).pin_memory()
     pinned_ev = torch.zeros(max(1, 2 * len(evs)), dtype=torch.float64).pin_memory()
@@ -471,7 +513,7 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
     # the host, and no extra pass over the data is needed.  The last value comes from an explicit pass.
     # (one rank only: with several ranks the value needs a collective, which stays on the main stream)
     lagged = bool(cheap and want_log and period == 1 and not evs and od is None and not callbacks and dev.type == "cuda"
-                  and eng.R == 1 and os.environ.get("CB200_LAGGED_LOG", "1") != "0")
+                  and eng.R == 1 and start == 0 and os.environ.get("CB200_LAGGED_LOG", "1") != "0")
     if lagged:
         with prof.span("iterations"):
             side = torch.cuda.Stream(dev)
@@ -506,6 +548,8 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
                 ev_prev = ev_cur
                 if eng.arena is not None and (done % 64 == 0):
                     eng.arena.check_status()
+                if snap.due() and done < T:
+                    snap.maybe_save(snapshot_state, done - 1)
             torch.cuda.synchronize(dev)
             for idx in range(next_log, T - 1):
                 read_row(idx + 1)
@@ -516,8 +560,12 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
     with prof.span("iterations"):
         while done < T and not stop:
             k = min(period, T - done)
+            if snap.enabled and not want_log and not need_each:
+                k = min(k, 64)                       # come up for air so that a due snapshot can be written
             eng.step(k)
             done += k
+            if snap.due() and done < T:
+                snap.maybe_save(snapshot_state, done - 1)
             if not want_log and not need_each:
                 continue
             it = done - 1
@@ -534,12 +582,16 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
                         hist.add(eval_names[j], metrics[0], fin(float(pinned_ev[2 * j]) / max(float(pinned_ev[2 * j + 1]), 1e-300)))
             else:
                 torch.cuda.current_stream(dev).synchronize()
-                cur = eng.approx[:n] + eng.cur_vals[eng.leaf[:n].long() & 0xFFFF]
+                lf_ = eng.leaf[:n].long() & 0xFFFF
+                if K > 1:
+                    cur = eng.approx[:, :n] + eng.cur_vals.view(eng.L, K)[lf_].t()
+                else:
+                    cur = (eng.approx[:n] + eng.cur_vals[lf_]).unsqueeze(0)
                 for m in metrics:
-                    hist.add("learn", m, _dist_metric(m, cur.unsqueeze(0), y_train, w_train, train_pool, ctx, objective))
+                    hist.add("learn", m, _dist_metric(m, cur, y_train, w_train, train_pool, ctx, objective))
                     for j, ev in enumerate(evs):
-                        hist.add(eval_names[j], m, _dist_metric(m, ev.approx[: ev.store.n].unsqueeze(0), eval_y[j],
-                                                                eval_w[j], eval_pools[j], ctx, objective))
+                        ea_ = ev.approx[:, : ev.store.n] if K > 1 else ev.approx[: ev.store.n].unsqueeze(0)
+                        hist.add(eval_names[j], m, _dist_metric(m, ea_, eval_y[j], eval_w[j], eval_pools[j], ctx, objective))
             if eng.arena is not None and (it % 64 == 0):
                 eng.arena.check_status()
             if evs:
@@ -553,21 +605,24 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
                 if cb.after_iteration(_CallbackInfo(it, hist.data)) is False:
                     stop = True
         if not lagged:
+            final_loss = eng.current_learn_loss(pinned) if (not hist.iters and done > 0) else None
             sp, vals, wts = eng.finish()
     if stop and od is not None and od.stopped:
         logger.info(f"Stopped by overfitting detector  ({od.wait} iterations wait)")
-    trees = [dict(kind="oblivious", splits=sp[t], node_split=None, leaf_of_node=None, values=vals[t], weights=wts[t])
-             for t in range(done)]
+    trees = [dict(kind="oblivious", splits=sp[t], node_split=None, leaf_of_node=None,
+                  values=(vals[t].reshape(-1, K) if K > 1 else vals[t]), weights=wts[t]) for t in range(done)]
+    snap.finalize(dict(trees=trees, hist=hist.data, iters=hist.iters))
     if not hist.iters:
         # nothing was logged during training: fill the learn curve of the objective from the device history
         lh = eng.learn_loss_history()
         name = str(metrics[0]) if (getattr(metrics[0], "name", None) == loss_metric_name and der_fn is None) else None
-        if name is not None and len(lh) > 1:
-            vals_l = lh[1:].tolist()
+        if name is not None and len(lh) >= 1 and final_loss is not None:
+            vals_l = lh[1:].tolist() + [final_loss]          # row j = loss after j trees; the last one from its own pass
             if objective.name == "RMSE":
                 vals_l = [math.sqrt(v) for v in vals_l]
             hist.data["learn"][name] = vals_l
     launches = eng.launches_per_iter
-    train_approx = eng.approx[:n].double().cpu().numpy().reshape(-1, 1)
+    train_approx = (eng.approx[:, :n].t().double().cpu().numpy() if K > 1
+                    else eng.approx[:n].double().cpu().numpy().reshape(-1, 1))
     eng.close()
     return LoopResult(trees, hist.data, best_it, _best_scores(hist, metrics), launches, train_approx)

@@ -18,7 +18,8 @@ import torch
 from ..data.pool import CatBoostError
 
 NATIVE_LOSS_ID = {"RMSE": 0, "Logloss": 1, "CrossEntropy": 2, "Poisson": 3, "MAE": 4, "Quantile": 5,
-                  "LogLinQuantile": 6, "MAPE": 7, "Huber": 8, "Lq": 9, "Expectile": 10, "Tweedie": 11, "LogCosh": 12}
+                  "LogLinQuantile": 6, "MAPE": 7, "Huber": 8, "Lq": 9, "Expectile": 10, "Tweedie": 11, "LogCosh": 12,
+                  "MultiClass": 50}
 LOSS_EXTERNAL = 100
 
 
@@ -38,6 +39,8 @@ class Objective:
     # native pointwise implementation ------------------------------------------------------------
     @property
     def native_id(self) -> Optional[int]:
+        """Identifier of the objective's device formula (pointwise losses: cb_losses.cuh; 50 = softmax MultiClass,
+        cb_multiclass.cu), None when the derivatives only exist as tensor code."""
         return NATIVE_LOSS_ID.get(self.name)
 
     def native_params(self):
@@ -271,8 +274,23 @@ class MultiClass(Objective):
         v = -lp.gather(0, target.long().unsqueeze(0))[0]
         return _wsum(v, weight) / max(_wtot(target.numel(), weight), 1e-300)
 
+    def hess_blocks(self, approx, target, weight, idx, n_leaves):
+        """Per-leaf K x K Hessian blocks of the negative log-likelihood, [n_leaves, K, K] float64:
+        sum over the leaf's documents of w (diag(p) - p p^T)."""
+        p = torch.softmax(approx, dim=0).double()                      # [K, n]
+        w = torch.ones(p.shape[1], dtype=torch.float64, device=p.device) if weight is None else weight.double()
+        K = p.shape[0]
+        H = torch.zeros((n_leaves, K, K), dtype=torch.float64, device=p.device)
+        pw = p * w
+        for k in range(K):
+            row = -(pw[k].unsqueeze(0) * p)                            # [K, n]: -w p_k p_j
+            row[k] += pw[k]
+            H[:, k, :].index_add_(0, idx, row.t())
+        return H
+
 
 class MultiClassOneVsAll(MultiClass):
+    hess_blocks = None
     name = "MultiClassOneVsAll"
 
     def der_hess(self, approx, target, weight, ctx=None):

@@ -17,7 +17,10 @@ range of borders, so the off-diagonal weights of all candidates of the feature a
 difference array ``[borders + 1, 2L, 2L]`` followed by a prefix sum over the borders -- the same role as the reference's
 pairwise histograms (4 values per bin, feature and leaf pair).  The systems of a feature are solved as one batch.
 
-This is tensor code (device-resident, batched Cholesky-class solves through the framework); single rank.
+``PairwiseLearner`` is tensor code (batched solves through the framework, single rank): the CPU path and the oracle.
+``PairwiseKernelLearner`` runs the same search as hand-written kernels (``ops/cuda/cb_pairwise.cu``: four pair histograms
+per (feature, bin, leaf pair), bin prefix sums, one block per candidate that assembles the system, factorises it and
+scores it) and sums the histograms over the ranks, so pairwise losses train on several GPUs.
 """
 from __future__ import annotations
 
@@ -67,6 +70,8 @@ class PairwiseLearner:
         """Gain of every border of feature f: [nb - 1] float64."""
         dev = self.dev
         nbf = int(self.nb[f].item())
+        if bool(self.onehot[f].item()):
+            return self._onehot_scores(f, leaf, L, wi, li, h, der, nbf)
         T = nbf - 1                                  # candidate borders t = 0 .. T-1, right child iff bin > t
         if T <= 0:
             return torch.zeros(0, dtype=torch.float64, device=dev)
@@ -111,6 +116,23 @@ class PairwiseLearner:
         _, gain = _solve_pairwise(M, D, self.l2, self.prior)
         return gain
 
+    def _onehot_scores(self, f, leaf, L, wi, li, h, der, nbf) -> torch.Tensor:
+        """Gain of every value of a one-hot feature (right child iff bin == value), one system per value."""
+        S = 2 * L
+        b = self.bins[f]
+        n = der.shape[0]
+        gains = []
+        for v in range(nbf):
+            child = leaf[:n] + (b[:n] == v).long() * L
+            W = torch.zeros(S * S, dtype=torch.float64, device=self.dev)
+            W.index_add_(0, child[wi] * S + child[li], h.double())
+            W = W.view(S, S)
+            W = W + W.t()
+            M = torch.diag(W.sum(-1)) - W
+            D = torch.zeros(S, dtype=torch.float64, device=self.dev).index_add_(0, child, der.double())
+            gains.append(_solve_pairwise(M, D, self.l2, self.prior)[1])
+        return torch.stack(gains) if gains else torch.zeros(0, dtype=torch.float64, device=self.dev)
+
     def build_tree(self, wi, li, h, der, iteration: int, random_strength: float = 0.0) -> TreeResult:
         """wi / li: winner / loser document of every pair; h: pair weights; der: per-document derivative [n]."""
         o = self.o
@@ -125,8 +147,8 @@ class PairwiseLearner:
             L = 1 << level
             best = (-float("inf"), -1, -1)
             for f in range(F):
-                if bool(self.onehot[f].item()) or float(fw[f].item()) <= 0:
-                    continue                                     # one-hot candidates are scored by the pointwise path
+                if float(fw[f].item()) <= 0:
+                    continue
                 gain = self._feature_scores(f, leaf, L, wi, li, h, der)
                 if gain.numel() == 0:
                     continue
@@ -139,8 +161,9 @@ class PairwiseLearner:
             if best[1] < 0 or not np.isfinite(best[0]):
                 break
             _, f, t = best
-            splits[level] = (f, t, 0, 0)
-            leaf = leaf + (self.bins[f] > t).long() * L
+            oh = bool(self.onehot[f].item())
+            splits[level] = (f, t, 0, 1 if oh else 0)
+            leaf = leaf + ((self.bins[f] == t) if oh else (self.bins[f] > t)).long() * L
         self.leaf.zero_()
         self.leaf[:n] = leaf.to(torch.int16)
         return TreeResult("oblivious", splits=splits, n_leaves=1 << depth, leaf=self.leaf)
@@ -157,6 +180,107 @@ class PairwiseLearner:
         M = torch.diag(W.sum(-1)) - W
         d = torch.zeros(S, dtype=torch.float64, device=self.dev).index_add_(0, lf, der.double())
         cnt = torch.bincount(lf, minlength=S).double()
+        if S < 2:
+            return np.zeros((S, 1)), cnt.cpu().numpy()
+        x, _ = _solve_pairwise(M, d, self.l2, self.prior)
+        return (x * lr).unsqueeze(1).cpu().numpy(), cnt.cpu().numpy()
+
+
+class PairwiseKernelLearner(PairwiseLearner):
+    """The same search on the GPU with the kernels of ``cb_pairwise.cu``; histograms are summed over the ranks (queries
+    are never split between ranks, so every pair is local to one of them).  Leaf values of the finished tree come from
+    one more system over the final leaves, assembled from a pair histogram without a feature dimension."""
+
+    H_BUDGET_BYTES = 1 << 30
+
+    def __init__(self, store, opts, seed: int = 0, ctx=None):
+        self.store, self.o = store, opts
+        self.dev = store.bins.device
+        self.ctx = ctx
+        self.leaf = torch.zeros(store.npad, dtype=torch.int16, device=self.dev)
+        self.l2 = float(opts.l2_leaf_reg)
+        self.prior = float(opts.bayesian_matrix_reg if opts.bayesian_matrix_reg is not None else 0.1)
+        self.gen = torch.Generator(device="cpu")
+        self.gen.manual_seed(int(seed) + 4242)
+        self.onehot = store.feat_onehot.bool()
+        self.bins = None                                 # the kernels read the packed store directly
+        self.B = max(4, (store.max_bins + 3) // 4 * 4)
+
+    def _reduce(self, t):
+        if self.ctx is not None and self.ctx.is_distributed:
+            self.ctx.all_reduce_sum_(t)
+
+    def level_gains(self, L: int, wi, li, h, der_pad) -> torch.Tensor:
+        """Gain of every candidate of the level: float32 [F_padded_to_groups, B] (-inf where there is none)."""
+        import ctypes
+        from ..ops import native
+        lib, st = native.cuda_lib(), self.store
+        G, B = st.G, self.B
+        per_group = 4 * B * L * L * 4 * 4
+        ng_max = max(1, min(G, self.H_BUDGET_BYTES // per_group))
+        gains = torch.full((G * 4, B), -float("inf"), dtype=torch.float32, device=self.dev)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        p = lambda t: ctypes.c_void_p(t.data_ptr())
+        grid = 148 * 8
+        wi32, li32 = wi.to(torch.int32).contiguous(), li.to(torch.int32).contiguous()
+        h32 = h.to(torch.float32).contiguous()
+        if lib.cb_pair_solve_smem_bytes(L) > 227 * 1024:
+            raise RuntimeError("too many leaves for the pairwise solve kernel")
+        for g0 in range(0, G, ng_max):
+            ng = min(ng_max, G - g0)
+            H = torch.zeros(ng * 4 * B * L * L * 4, dtype=torch.float32, device=self.dev)
+            D = torch.zeros(ng * 4 * B * L, dtype=torch.float32, device=self.dev)
+            native.cuda_check(lib.cb_pair_hist(ctypes.c_void_p(st.handle), p(self.leaf), p(wi32), p(li32), p(h32),
+                                               int(wi32.numel()), p(der_pad), L, B, g0, ng, p(H), p(D), grid, stream),
+                              "cb_pair_hist")
+            self._reduce(H)
+            self._reduce(D)
+            native.cuda_check(lib.cb_pair_scan(ctypes.c_void_p(st.handle), g0 * 4, ng * 4, L, B, p(H), p(D), grid, stream),
+                              "cb_pair_scan")
+            nf = min(ng * 4, st.F - g0 * 4)
+            out = gains[g0 * 4: g0 * 4 + nf]
+            native.cuda_check(lib.cb_pair_solve(ctypes.c_void_p(st.handle), p(H), p(D), g0 * 4, nf, L, B, self.l2, self.prior,
+                                                p(out), stream), "cb_pair_solve")
+            del H, D
+        return gains[: st.F]
+
+    def build_tree(self, wi, li, h, der, iteration: int, random_strength: float = 0.0) -> TreeResult:
+        from ..ops import api as ops
+        depth = int(self.o.depth)
+        st = self.store
+        splits = np.full((depth, 4), 0, dtype=np.int32)
+        splits[:, 0] = -1
+        self.leaf.zero_()
+        der_pad = torch.zeros(st.npad, dtype=torch.float32, device=self.dev)
+        der_pad[: st.n] = der.float()
+        for level in range(depth):
+            gains = self.level_gains(1 << level, wi, li, h, der_pad)
+            if random_strength > 0:
+                noise = torch.randn(gains.shape, generator=self.gen, dtype=torch.float32).to(self.dev) * random_strength
+                gains = torch.where(torch.isfinite(gains), gains + noise * st.feat_weight.unsqueeze(1), gains)
+            flat = int(torch.argmax(gains.reshape(-1)).item())
+            f, t = flat // gains.shape[1], flat % gains.shape[1]
+            if not np.isfinite(float(gains[f, t].item())):
+                break
+            oh = bool(self.onehot[f].item())
+            splits[level] = (f, t, 0, 1 if oh else 0)
+            ops.update_leaf(st, self.leaf, f, t, oh, level)
+        return TreeResult("oblivious", splits=splits, n_leaves=1 << depth, leaf=self.leaf)
+
+    def leaf_values(self, leaf_count: int, wi, li, h, der, lr: float):
+        n = self.store.n
+        lf = self.leaf[:n].long() & 0xFFFF
+        S = leaf_count
+        W = torch.zeros(S * S, dtype=torch.float64, device=self.dev)
+        W.index_add_(0, lf[wi] * S + lf[li], h.double())
+        d = torch.zeros(S, dtype=torch.float64, device=self.dev).index_add_(0, lf, der.double())
+        cnt = torch.bincount(lf, minlength=S).double()
+        self._reduce(W)
+        self._reduce(d)
+        self._reduce(cnt)
+        W = W.view(S, S)
+        W = W + W.t()
+        M = torch.diag(W.sum(-1)) - W
         if S < 2:
             return np.zeros((S, 1)), cnt.cpu().numpy()
         x, _ = _solve_pairwise(M, d, self.l2, self.prior)

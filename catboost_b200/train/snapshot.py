@@ -63,11 +63,16 @@ class SnapshotManager:
             fh.write(LABEL + hashlib.md5(body).hexdigest().encode() + body)
         os.replace(tmp, self.path)
 
+    def due(self) -> bool:
+        """True when this rank writes snapshots and the interval since the last one has passed (callers whose state is
+        expensive to collect -- a device -> host copy -- ask before collecting it)."""
+        return self.enabled and (time.time() - self.last >= self.interval)
+
     def maybe_save(self, state, iteration):
-        if self.enabled and (time.time() - self.last >= self.interval):
-            self._write(state)
+        if self.due():
+            self._write(state() if callable(state) else state)
             self.last = time.time()
 
     def finalize(self, state):
         if self.enabled:
-            self._write(state)
+            self._write(state() if callable(state) else state)

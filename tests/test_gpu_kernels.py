@@ -424,3 +424,38 @@ def test_gpu_apply_streams_chunks_through_two_buffers():
     for chunk in (1000, 4500, 7000):
         got = pred.predict(X, chunk_rows=chunk)
         np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+
+
+def test_gpu_snapshot_resume_equals_uninterrupted(tmp_path):
+    """The device trainer stops after 7 of 20 iterations, a second fit picks the snapshot up and ends with exactly the
+    model of an uninterrupted run (random bootstrap weights and score noise included: they are functions of the
+    iteration counter, which the snapshot restores)."""
+    import catboost_b200 as cb
+    rng = np.random.default_rng(4)
+    X = rng.standard_normal((30_000, 9)).astype(np.float32)
+    y = (X[:, 0] * X[:, 1] + 0.5 * X[:, 2] > 0).astype(int)
+    Xe, ye = X[:5000], y[:5000]
+    common = dict(depth=5, learning_rate=0.3, verbose=False, random_seed=3, task_type="GPU", train_dir=str(tmp_path),
+                  allow_writing_files=True, leaf_estimation_iterations=3)
+    full = cb.CatBoostClassifier(iterations=20, **common).fit(X, y, eval_set=(Xe, ye))
+    part = cb.CatBoostClassifier(iterations=7, save_snapshot=True, snapshot_file="g.snap", **common).fit(X, y, eval_set=(Xe, ye))
+    assert part.tree_count_ == 7 and (tmp_path / "g.snap").exists()
+    import shutil
+    shutil.copy(tmp_path / "g.snap", tmp_path / "g2.snap")
+    resumed = cb.CatBoostClassifier(iterations=20, save_snapshot=True, snapshot_file="g.snap", **common).fit(X, y, eval_set=(Xe, ye))
+    assert resumed.tree_count_ == 20
+    a = resumed.predict(X, prediction_type="RawFormulaVal")
+    b = full.predict(X, prediction_type="RawFormulaVal")
+    # same structure; the values agree to float rounding (the per-leaf sums are added with floating-point atomics, whose
+    # order is not fixed, so not even two identical runs agree to the last bit)
+    assert [(s.feature, s.border) for s in resumed._model.splits] == [(s.feature, s.border) for s in full._model.splits]
+    assert np.allclose(a, b, rtol=1e-5, atol=1e-5), float(np.abs(a - b).max())
+    ev_full = full.get_evals_result()["validation"]["Logloss"]
+    ev_res = resumed.get_evals_result()["validation"]["Logloss"]
+    assert len(ev_res) == len(ev_full) and np.allclose(ev_res, ev_full, rtol=1e-6)
+    # the general learner (taken here because of rsm < 1) continues a snapshot written by the device trainer: same
+    # container, same state
+    cont = cb.CatBoostClassifier(iterations=9, save_snapshot=True, snapshot_file="g2.snap", rsm=0.9, **common).fit(X, y)
+    assert cont.tree_count_ == 9
+    first = lambda m, k: [(s.feature, s.border) for t in m._model.trees[:k] for s in (m._model.splits[i] for i in t.splits)]
+    assert first(cont, 7) == first(part, 7)
