@@ -27,12 +27,14 @@ import time
 
 import numpy as np
 
-BASELINE_S_PER_1000 = {"higgs": 55.601, "epsilon": 44.971, "small": None, "criteo": None, "ranking": None}
+BASELINE_S_PER_1000 = {"higgs": 55.601, "epsilon": 44.971, "small": None, "criteo": None, "ranking": None, "sparse": None}
 CONFIGS = {
     # rows, float features, depth, border_count
     "higgs": dict(rows=10_500_000, features=28, depth=6, border_count=128, model="Logloss symmetric depth6 10.5Mx28"),
     "epsilon": dict(rows=400_000, features=2000, depth=6, border_count=128, model="Logloss symmetric depth6 400Kx2000"),
     "small": dict(rows=200_000, features=28, depth=6, border_count=128, model="Logloss symmetric depth6 200Kx28"),
+    # the feature matrix of the ranking workload (60 % exact zeros, 64 borders) under Logloss: isolates the level kernels
+    "sparse": dict(rows=2_000_000, features=700, depth=6, border_count=64, model="Logloss symmetric depth6 2Mx700 60% zeros"),
     # categorical workload (13 numeric + 26 categorical columns, CTR features); end-to-end fit() only.  The named
     # reference config has 45M rows: pass --rows 45000000 for the full size.
     # learning to rank: 2M documents x 700 features in groups of about 100, YetiRank, 64 borders; end-to-end fit() only
@@ -46,6 +48,14 @@ def make_data(config: str, rows: int, features: int, rank: int, world: int, seed
     lo, hi = rows * rank // world, rows * (rank + 1) // world
     n = hi - lo
     rng = np.random.default_rng(seed * 1000 + rank)
+    if config == "sparse":
+        X = rng.random((n, features), dtype=np.float32)
+        for r0 in range(0, n, 250_000):
+            blk = X[r0:r0 + 250_000]
+            blk[rng.random(blk.shape, dtype=np.float32) < 0.6] = 0.0
+        w = np.random.default_rng(seed + 3).standard_normal(features).astype(np.float32) / np.sqrt(features)
+        s_ = X @ w + 0.15 * rng.standard_normal(n, dtype=np.float32)
+        return X, (s_ > np.median(s_[: min(n, 200_000)])).astype(np.float32)
     if config == "epsilon":
         X = rng.standard_normal((n, features), dtype=np.float32)
         X /= np.linalg.norm(X, axis=1, keepdims=True)

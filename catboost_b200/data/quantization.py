@@ -60,10 +60,23 @@ def select_borders(sample: np.ndarray, border_count: int, border_type: str = "Gr
     counts = np.zeros(F, dtype=np.int32)
     has_nan = np.zeros(F, dtype=np.uint8)
     if n and F:
-        native.cpu_lib().cbc_select_borders_matrix(_ptr(sample), ctypes.c_longlong(n), ctypes.c_int(F),
+        lib = native.cpu_lib()
+        # Launchers that start one process per GPU pin OMP_NUM_THREADS to 1; border selection runs on one rank while
+        # the others wait for it, so it takes the cores this process may run on, whatever the variable says
+        old = int(lib.cbc_num_threads())
+        try:
+            cores = len(os.sched_getaffinity(0))
+        except (AttributeError, OSError):
+            cores = os.cpu_count() or 1
+        want = max(old, min(cores, 64))
+        if want != old:
+            lib.cbc_set_num_threads(want)
+        lib.cbc_select_borders_matrix(_ptr(sample), ctypes.c_longlong(n), ctypes.c_int(F),
                                                    ctypes.c_longlong(sample.strides[0] // 4),
                                                    ctypes.c_int(border_count), ctypes.c_int(BORDER_TYPES[border_type]),
                                                    _ptr(out), _ptr(counts), _ptr(has_nan))
+        if want != old:
+            lib.cbc_set_num_threads(old)
     return [out[f, :counts[f]].copy() for f in range(F)], has_nan
 
 

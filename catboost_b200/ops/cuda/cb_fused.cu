@@ -259,6 +259,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     a.s.learning_rate = lr; a.s.best_key = best_key;
     a.leaf = leaf; a.splits = splits; a.depth = depth; a.mask_out = mask1; a.msg_local = msg_local;
     a.msg_stage = msg_stage; a.msg_stage_stride = msg_stage_stride; a.fuse_leaf = 0;
+    a.h.domw = nullptr;
     a.h.prev_splits = nullptr; a.h.prev_iter = iter_ptr; a.h.prev_depth = depth; a.h.leaf_rw = leaf;
     a.s.ll_epoch = R > 1 ? a.c.epoch + 1 : nullptr; a.s.ll_timeout_ns = a.c.timeout_ns; a.s.ll_status = a.c.status;
     p->threads = threads;
@@ -283,6 +284,8 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     return p;
 }
 
+// domw: one packed word per feature group (the dominant bin of each of its four features, 255 = none), or null
+CB_API void cb_fused_set_dominant(CbFusedPlan* p, const unsigned int* domw) { p->a.h.domw = domw; }
 CB_API void cb_fused_set_fuse_leaf(CbFusedPlan* p, int on) { p->fuse_leaf_update = on ? 1 : 0; }
 CB_API void cb_fused_set_phase_ts(CbFusedPlan* p, unsigned long long* ts) { p->a.phase_ts = ts; }
 CB_API void cb_fused_set_work(CbFusedPlan* p, unsigned int* work) { p->a.h.work = work; }
@@ -316,10 +319,11 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
         // warps * 64 * (3 + gpc) words.  Take the widest bundle that fits; then replicate the cells once if there is room.
         const int cell = 8 * p->a.h.B * 4;                   // bytes per (slot, group)
         const int gmax = G < p->max_bundle ? G : p->max_bundle;
+        const bool skip = p->a.h.domw != nullptr;       // dominant-bin skipping: 256 bytes of slot totals per slot
         auto ring_bytes = [](int t, int g) { return (t / 32) * 64 * (3 + g) * 4 + 16; };
         auto fit = [&](int t, int budget, int slots) {
             int g = 0;
-            while (g < gmax && slots * (g + 1) * cell + ring_bytes(t, g + 1) <= budget) ++g;
+            while (g < gmax && slots * (g + 1) * cell + ring_bytes(t, g + 1) + (skip ? slots * 256 : 0) <= budget) ++g;
             return g;
         };
         // one 1024-thread block per SM: measured a few percent faster than two 512-thread blocks at every level (one
@@ -330,7 +334,7 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
         if (gpc < 1) {
             // even one group of all slots does not fit: several passes over the slots
             gpc = 1;
-            spp = (budget - ring_bytes(thr, 1)) / cell;
+            spp = (budget - ring_bytes(thr, 1)) / (cell + (skip ? 256 : 0));
             if (spp < 1) return 0;
         }
         // even out the bundles (7 groups as 4 + 3 rather than 5 + 2 changes nothing in passes but shrinks the tile)
@@ -338,8 +342,8 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
         gpc = (G + nb - 1) / nb;
         int max_copies = p->max_copies;
         if (const char* e = getenv("CB200_MAX_COPIES")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4 || v == 8) max_copies = v; }
-        while (C < max_copies && 2 * C * spp * gpc * cell + ring_bytes(thr, gpc) <= budget) C *= 2;
-        smem = spp * gpc * cell * C + ring_bytes(thr, gpc);
+        while (C < max_copies && 2 * C * spp * gpc * cell + ring_bytes(thr, gpc) + (skip ? spp * 256 : 0) <= budget) C *= 2;
+        smem = spp * gpc * cell * C + ring_bytes(thr, gpc) + (skip ? spp * 256 : 0);
     } else {
         const int per_slot = p->a.h.S * 4 * p->a.h.B * 4 * ((p->a.h.statmax && !narrow) ? 2 : 1);
         const bool ring = p->a.h.statmax && p->a.h.S == 2;      // per-warp compaction rings (16 bytes x 64 entries)

@@ -22,17 +22,21 @@ struct CbYetiArgs {
     float* der; float* hess;   // [n]
 };
 
-__global__ void __launch_bounds__(CB_YETI_THREADS) cb_yetirank_kernel(CbYetiArgs a) {
-    __shared__ float s_key[CB_YETI_MAX_GROUP];
-    __shared__ unsigned short s_idx[CB_YETI_MAX_GROUP];
-    __shared__ float s_ap[CB_YETI_MAX_GROUP];
-    __shared__ float s_tg[CB_YETI_MAX_GROUP];
-    __shared__ float s_der[CB_YETI_MAX_GROUP];
-    __shared__ float s_hes[CB_YETI_MAX_GROUP];
+// MAXG = largest group the instantiation holds in shared memory.  Typical data has groups of tens to hundreds of
+// documents: the small instantiation (256 documents, 128 threads, 5.5 KB) keeps sixteen blocks resident per SM, so
+// the barriers of one group's sort overlap the work of the others; the large one covers groups up to 2048.
+template <int MAXG, int THREADS>
+__global__ void __launch_bounds__(THREADS) cb_yetirank_kernel(CbYetiArgs a) {
+    __shared__ float s_key[MAXG];
+    __shared__ unsigned short s_idx[MAXG];
+    __shared__ float s_ap[MAXG];
+    __shared__ float s_tg[MAXG];
+    __shared__ float s_der[MAXG];
+    __shared__ float s_hes[MAXG];
     for (int q = blockIdx.x; q < a.Q; q += gridDim.x) {
         const long long b = a.offsets[q], e = a.offsets[q + 1];
         const int L = (int)(e - b);
-        if (L > CB_YETI_MAX_GROUP) continue;       // handled by the caller
+        if (L > MAXG) continue;                    // handled by the larger instantiation or by the caller
         int P2 = 1;
         while (P2 < L) P2 <<= 1;
         for (int i = threadIdx.x; i < L; i += blockDim.x) {
@@ -103,20 +107,27 @@ __global__ void __launch_bounds__(CB_YETI_THREADS) cb_yetirank_kernel(CbYetiArgs
 }
 
 // Returns 0, or a CUDA error code.  Groups longer than cb_yetirank_max_group() are skipped (their der / hess entries are
-// left untouched): the caller computes those with the tensor implementation.
+// left untouched): the caller computes those with the tensor implementation.  max_group = size of the largest group
+// (known to the caller from the offsets; it picks the instantiation).
 CB_API int cb_yetirank_max_group() { return CB_YETI_MAX_GROUP; }
 
 CB_API int cb_yetirank(const float* approx, const float* target, const float* weight, const long long* offsets, int Q,
                        long long n, int permutations, float decay, unsigned long long seed, const float* noise,
-                       float* der, float* hess, cudaStream_t st) {
+                       float* der, float* hess, int max_group, cudaStream_t st) {
     if (Q <= 0) return 0;
     CbYetiArgs a{approx, target, weight, offsets, Q, permutations, decay, seed, noise, n, der, hess};
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int grid = sms * 4;
-    if (grid > Q) grid = Q;
-    cb_yetirank_kernel<<<grid, CB_YETI_THREADS, 0, st>>>(a);
+    if (max_group <= 256) {
+        int grid = sms * 16;
+        if (grid > Q) grid = Q;
+        cb_yetirank_kernel<256, 128><<<grid, 128, 0, st>>>(a);
+    } else {
+        int grid = sms * 4;
+        if (grid > Q) grid = Q;
+        cb_yetirank_kernel<CB_YETI_MAX_GROUP, CB_YETI_THREADS><<<grid, CB_YETI_THREADS, 0, st>>>(a);
+    }
     const cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : (int)e;
 }

@@ -74,6 +74,12 @@ struct CbHistArgs {
     // changes nothing.
     // The kernel arguments are never modified on the device, so the split is named by where it will be:
     // prev_splits[*prev_iter * prev_depth + level - 1]; prev_splits == nullptr switches the fusion off.
+    // Dominant-bin skipping (bundled path): domw[g] packs, for the four features of group g, the bin that most of their
+    // documents fall into (255 = none).  Documents are not accumulated into that bin; every slot keeps lane-replicated
+    // totals of its two statistics instead and the bin is restored as total - sum of the other bins before the tile
+    // is dumped.  On sparse data most (document, feature) pairs hit the dominant bin, so this removes most shared-memory
+    // atomics and the hot spot they create.  nullptr = off.
+    const unsigned int* domw;
     const CbSplit* prev_splits;
     const int* prev_iter;
     int prev_depth;
@@ -541,19 +547,27 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
 #ifndef CB_BUNDLE_PF
 #define CB_BUNDLE_PF 1       // 1 = keep the next step's loads in registers while the current step is processed
 #endif
-template <int GMAX>
+template <int GMAX, bool SKIP>
 __device__ __forceinline__ void cb_hist_bundle_drain(int* sh, const unsigned int* ring, int e, int gcnt, int gstride,
-                                                     int B, int cs, int copy) {
-    int* base = sh + (int)ring[e] + copy;
+                                                     int B, int cs, int copy, const unsigned int* sdom, int* tot, int lane) {
+    const unsigned int head_word = ring[e];          // SKIP: slot << 20 | tile offset of the slot; else the offset
+    int* base = sh + (int)(SKIP ? (head_word & 0xFFFFFu) : head_word) + copy;
     const int q0 = (int)ring[CB_RING + e], q1 = (int)ring[2 * CB_RING + e];
     const int soff = gstride >> 1;               // distance between the two statistics of a cell
+    if (SKIP) {
+        int* t = tot + (int)(head_word >> 20) * 64 + lane;
+        atomicAdd(t, q0);
+        atomicAdd(t + 32, q1);
+    }
 #pragma unroll
     for (int gl = 0; gl < GMAX; ++gl) {
         if (gl < gcnt) {
             const unsigned int w = ring[(3 + gl) * CB_RING + e];
+            const unsigned int eq = SKIP ? __vcmpeq4(w, sdom[gl]) : 0u;
             int* pg = base + gl * gstride;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
+                if (SKIP && ((eq >> (8 * j)) & 1u)) continue;
                 const int bin = (int)((w >> (8 * j)) & 255u);
                 int* p = pg + ((j * B + bin) << cs);
                 atomicAdd(p, q0);
@@ -597,7 +611,7 @@ __device__ __forceinline__ void cb_bundle_load(const uint32_t* bg, long long npa
     for (int k = 0; k < V; ++k) { lf[k] = lp[k]; s0[k] = p0[k]; s1[k] = p1[k]; }
 }
 
-template <int GMAX, bool UPD>
+template <int GMAX, bool UPD, bool SKIP>
 static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int gcnt, int chunk, int nK,
                                       int slot_begin, int slot_count) {
     constexpr int V = CB_BUNDLE_V(GMAX);
@@ -607,7 +621,14 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
     const int gstride = 2 * 4 * B * C;
     const int slot_stride = gcnt * gstride;
     const int total = slot_count * slot_stride;
+    // SKIP: per-slot totals [slot][2][32 lane copies] behind the rings of all warps
+    int* tot = sh + ((total + 3) & ~3) + (int)(blockDim.x >> 5) * (3 + gcnt) * CB_RING;
+    __shared__ unsigned int s_dom[8];
     for (int i = threadIdx.x; i < total; i += blockDim.x) sh[i] = 0;
+    if (SKIP) {
+        for (int i = threadIdx.x; i < slot_count * 64; i += blockDim.x) tot[i] = 0;
+        if (threadIdx.x < 8) s_dom[threadIdx.x] = threadIdx.x < gcnt ? a.domw[g0 + threadIdx.x] : 0xFFFFFFFFu;
+    }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned int* ring = reinterpret_cast<unsigned int*>(sh + ((total + 3) & ~3)) + warp * (3 + gcnt) * CB_RING;
@@ -708,7 +729,7 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
             const unsigned int m = __ballot_sync(0xffffffffu, take);
             if (take) {
                 const int e = (int)((tail + __popc(m & lt)) & (CB_RING - 1));
-                ring[e] = (unsigned int)(slot * slot_stride);
+                ring[e] = (unsigned int)(slot * slot_stride) | (SKIP ? ((unsigned int)slot << 20) : 0u);
                 ring[CB_RING + e] = (unsigned int)__float2int_rn(s0[k] * sc0);
                 ring[2 * CB_RING + e] = (unsigned int)__float2int_rn(s1[k] * sc1);
 #pragma unroll
@@ -718,15 +739,42 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
             tail += __popc(m);
             __syncwarp();
             if (tail - head >= 32u) {
-                cb_hist_bundle_drain<GMAX>(sh, ring, (int)((head + lane) & (CB_RING - 1)), gcnt, gstride, B, cs, copy);
+                cb_hist_bundle_drain<GMAX, SKIP>(sh, ring, (int)((head + lane) & (CB_RING - 1)), gcnt, gstride, B, cs, copy,
+                                                 s_dom, tot, lane);
                 head += 32u;
                 __syncwarp();
             }
         }
     }
     if ((unsigned int)lane < tail - head)
-        cb_hist_bundle_drain<GMAX>(sh, ring, (int)((head + lane) & (CB_RING - 1)), gcnt, gstride, B, cs, copy);
+        cb_hist_bundle_drain<GMAX, SKIP>(sh, ring, (int)((head + lane) & (CB_RING - 1)), gcnt, gstride, B, cs, copy, s_dom,
+                                         tot, lane);
     __syncthreads();
+    if (SKIP) {
+        // restore the skipped bin of every (slot, group, statistic, feature) row: slot total minus the other bins.  The
+        // value is spread over the C replicas of the cell so that each stays inside 32 bits.
+        const int rows = slot_count * gcnt * 8;
+        for (int row = warp; row < rows; row += (int)(blockDim.x >> 5)) {
+            const int sj = row & 7, gl = (row >> 3) % gcnt, slot = (row >> 3) / gcnt;
+            const unsigned int dbin = (s_dom[gl] >> (8 * (sj & 3))) & 255u;
+            if (dbin == 255u) continue;
+            const int* src = sh + (size_t)slot * slot_stride + gl * gstride + (((sj >> 2) * 4 + (sj & 3)) * B << cs);
+            long long part = 0;
+            for (int i = lane; i < B * C; i += 32) part += src[i];
+            long long t = tot[slot * 64 + (sj >> 2) * 32 + lane];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                part += __shfl_xor_sync(0xffffffffu, part, o);
+                t += __shfl_xor_sync(0xffffffffu, t, o);
+            }
+            const long long rest = t - part;
+            if (lane < C) {
+                int* cell = const_cast<int*>(src) + ((int)dbin << cs) + lane;
+                *cell = (int)(rest / C) + (lane == 0 ? (int)(rest % C) : 0);
+            }
+        }
+        __syncthreads();
+    }
     // dump as floats into the private regions [chunk * G + group][slot][s][j][B]
     const int B4 = B >> 2;
     const int cells4 = slot_count * gcnt * 8 * B4;
@@ -790,15 +838,16 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
                 const int g0 = g * gpc;
                 const int gcnt = min(gpc, G - g0);
                 int* shi = reinterpret_cast<int*>(sh);
-                if (CB_UPD_ON && a.prev_splits && a.level > 0 && gpc >= G) {
-                    if (gpc <= 2) cb_hist_bundle<2, true>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
-                    else if (gpc <= 4) cb_hist_bundle<4, true>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
-                    else cb_hist_bundle<8, true>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
-                } else {
-                    if (gpc <= 2) cb_hist_bundle<2, false>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
-                    else if (gpc <= 4) cb_hist_bundle<4, false>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
-                    else cb_hist_bundle<8, false>(a, shi, g0, gcnt, (int)k, nK, sb, sc);
-                }
+                const bool upd = CB_UPD_ON && a.prev_splits && a.level > 0 && gpc >= G;
+#define CB_BUNDLE_CALL(GM) do { \
+                    if (a.domw) { if (upd) cb_hist_bundle<GM, true, true>(a, shi, g0, gcnt, (int)k, nK, sb, sc); \
+                                  else cb_hist_bundle<GM, false, true>(a, shi, g0, gcnt, (int)k, nK, sb, sc); } \
+                    else { if (upd) cb_hist_bundle<GM, true, false>(a, shi, g0, gcnt, (int)k, nK, sb, sc); \
+                           else cb_hist_bundle<GM, false, false>(a, shi, g0, gcnt, (int)k, nK, sb, sc); } } while (0)
+                if (gpc <= 2) CB_BUNDLE_CALL(2);
+                else if (gpc <= 4) CB_BUNDLE_CALL(4);
+                else CB_BUNDLE_CALL(8);
+#undef CB_BUNDLE_CALL
                 continue;
             }
             const long long b = k * per;

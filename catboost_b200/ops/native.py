@@ -175,7 +175,7 @@ _SIGS = {
                                 c_void_p]),
     "cb_yetirank_max_group": (c_int, []),
     "cb_yetirank": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_ll, c_int, c_float, c_ull, c_void_p, c_void_p,
-                            c_void_p, c_void_p]),
+                            c_void_p, c_int, c_void_p]),
     "cb_leaf_newton_max_grid": (c_int, [c_int]),
     "cb_leaf_newton": (c_int, [c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_int,
@@ -214,6 +214,7 @@ _SIGS = {
                                    c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int,
                                    c_float, c_void_p, c_void_p, c_ull, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int]),
     "cb_fused_set_fuse_leaf": (None, [c_void_p, c_int]),
+    "cb_fused_set_dominant": (None, [c_void_p, c_void_p]),
     "cb_fused_set_features": (None, [c_void_p, c_int, c_int]),
     "cb_fused_set_phase_ts": (None, [c_void_p, c_void_p]),
     "cb_fused_set_work": (None, [c_void_p, c_void_p]),

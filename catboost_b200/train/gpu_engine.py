@@ -20,6 +20,7 @@ peer-store reduce-scatter; ``reduce='nccl'`` is the baseline (stand-alone kernel
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import numpy as np
@@ -57,7 +58,7 @@ class GpuObliviousEngine:
                  timeout_s: float = 20.0, quantized_hist: bool = True, dynamic_work: bool = True,
                  der_fn=None, zero_mean_leaves: bool = False, max_bundle: int = 8,
                  fused_leaf_steps: bool = True, leaf_backtracking: str = "AnyImprovement",
-                 fuse_leaf_update: bool = True, dims: int = 1):
+                 fuse_leaf_update: bool = True, dims: int = 1, skip_dominant_bin: bool = True):
         assert store.bins.is_cuda, "GpuObliviousEngine needs a CUDA store"
         if depth > 16:
             raise ValueError("depth must be <= 16")
@@ -136,6 +137,7 @@ class GpuObliviousEngine:
         self.fused_leaf_steps = bool(fused_leaf_steps)
         self.leaf_backtracking = {"No": 0, "AnyImprovement": 1, "Armijo": 2}[str(leaf_backtracking or "AnyImprovement")]
         self.fuse_leaf_update = bool(fuse_leaf_update)
+        self.skip_dominant_bin = bool(skip_dominant_bin) and os.environ.get("CB200_SKIP_DOMINANT", "1") != "0"
         self.stats = torch.zeros((self.S, npad), dtype=f32, device=dev)
         self.scal = torch.zeros(4, dtype=f64, device=dev)
         self.iter_ptr = torch.zeros(1, dtype=i32, device=dev)
@@ -235,9 +237,17 @@ class GpuObliviousEngine:
         # columns where one bin holds a large share of the documents (sparse data): most lanes of a warp would add to
         # the same histogram cell, so such data gets up to 8 replicas of every cell instead of 2 (measured on 60 % zeros:
         # 6.8 -> 4.9 ms per iteration; on dense data more replicas cost about 1 %)
-        self.dominant_bin_share = self._dominant_bin_share()
-        if self.dominant_bin_share > 0.25:
-            self.lib.cb_fused_set_max_copies(ctypes.c_void_p(self.plan), 8)
+        self.dominant_bin_share, self.domw = self._dominant_bins()
+        if not (self.narrow_hist and self.S == 2 and self.skip_dominant_bin):
+            self.domw = None
+        if self.domw is not None and self.dominant_bin_share > 0.25:
+            # sparse data: most (document, feature) pairs would hit one hot cell per feature; those are skipped and the
+            # cell is restored from per-slot totals
+            self.lib.cb_fused_set_dominant(ctypes.c_void_p(self.plan), _p(self.domw))
+        else:
+            self.domw = None
+            if self.dominant_bin_share > 0.25:
+                self.lib.cb_fused_set_max_copies(ctypes.c_void_p(self.plan), 8)
         self.level_geo = []
         for level in range(self.depth):
             spp, smem, thr, nk, cp, bd = (ctypes.c_int(0) for _ in range(6))
@@ -303,22 +313,37 @@ class GpuObliviousEngine:
                                        self.grid_stream, self._stream()), "cb_grad_pointwise")
         self.launches_per_iter += 1
 
-    def _dominant_bin_share(self, sample: int = 16384) -> float:
-        """Mean over the features of the share of their most frequent bin, from the first rows of the store (all ranks
-        agree on the value)."""
+    def _dominant_bins(self, sample: int = 65536):
+        """(mean share of the most frequent bin over the features, packed dominant bins per feature group or None).
+
+        Counted on a strided sample of this rank's rows and summed over the ranks, so every rank takes the same
+        decision.  A feature gets a dominant bin when at least 30 % of the sampled documents share one bin; the packed
+        word of a group holds 255 for its other features."""
         st = self.store
-        m = int(min(st.n, sample))
-        if m <= 0 or st.F <= 0:
-            return 0.0
+        if st.n <= 0 or st.F <= 0:
+            return 0.0, None
         G = st.bins.shape[0]
-        b = st.bins[:, :m].contiguous().view(torch.uint8).view(G, m, 4).permute(0, 2, 1).reshape(G * 4, m)
+        step = max(1, st.n // sample)
+        rows = st.bins[:, : st.n: step].contiguous()
+        m = rows.shape[1]
+        b = rows.view(torch.uint8).view(G, m, 4).permute(0, 2, 1).reshape(G * 4, m)
         idx = b.long() + (torch.arange(G * 4, device=b.device) * 256).unsqueeze(1)
-        cnt = torch.bincount(idx.reshape(-1), minlength=G * 4 * 256).view(G * 4, 256)
-        t = torch.stack([cnt.max(1).values[: st.F].double().sum(), torch.tensor(float(m) * st.F, dtype=torch.float64,
-                                                                                 device=b.device)])
+        cnt = torch.bincount(idx.reshape(-1), minlength=G * 4 * 256).view(G * 4, 256).double()
+        tot = torch.tensor([float(m)], dtype=torch.float64, device=b.device)
         if self.ctx is not None and self.ctx.is_distributed:
-            self.ctx.all_reduce_sum_(t)
-        return float((t[0] / t[1].clamp_min(1.0)).item())
+            self.ctx.all_reduce_sum_(cnt)
+            self.ctx.all_reduce_sum_(tot)
+        top, arg = cnt.max(1)
+        share = top / tot.clamp_min(1.0)
+        mean_share = float(share[: st.F].mean().item())
+        dom = torch.where(share >= 0.30, arg, torch.full_like(arg, 255))
+        dom[st.F:] = 255
+        if st.max_bins >= 256 or not bool((dom != 255).any()):
+            return mean_share, None
+        d = dom.view(G, 4).to(torch.int64)
+        packed = (d[:, 0] | (d[:, 1] << 8) | (d[:, 2] << 16) | (d[:, 3] << 24))
+        packed = torch.where(packed >= 2 ** 31, packed - 2 ** 32, packed).to(torch.int32).contiguous()
+        return mean_share, packed
 
     def _level_fused(self, level: int):
         grid, spp, smem, thr, nk, cp, bd = self.level_geo[level]

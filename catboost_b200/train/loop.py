@@ -497,9 +497,10 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
     cheap = (len(metrics) == 1 and isinstance(o.loss_function, str) and str(metrics[0]) == o.loss_function
              and der_fn is None)
     need_each = bool(od is not None or callbacks)
-    # metrics other than the objective only exist if they are evaluated along the way (the objective's own curve can be
-    # filled from the device history afterwards)
-    want_log = bool(o.verbose) or bool(eval_stores) or not cheap
+    # metrics the caller asked for beyond the objective only exist if they are evaluated along the way (the objective's
+    # own curve can be filled from the device history afterwards)
+    asked = bool(o.custom_metric) or bool(o.custom_loss)
+    want_log = bool(o.verbose) or bool(eval_stores) or (asked and not cheap)
     period = 1 if need_each else (max(1, int(o.metric_period)) if want_log else T)
     done, best_it, best_val, stop = start, None, None, False
     final_loss = None

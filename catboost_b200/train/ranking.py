@@ -189,7 +189,7 @@ class YetiRank(_GroupObjective):
         w32 = None if weight is None else weight.contiguous().float()
         off = lay.offsets.contiguous()
         native.cuda_check(lib.cb_yetirank(P(a32), P(t32), P(w32), P(off), lay.Q, n, self.permutations, self.decay,
-                                          (20240229 + 7919 * self._calls) & 0xFFFFFFFFFFFFFFFF, P(noise), P(der), P(hess),
+                                          (20240229 + 7919 * self._calls) & 0xFFFFFFFFFFFFFFFF, P(noise), P(der), P(hess), int(lay.Lmax),
                                           ctypes.c_void_p(torch.cuda.current_stream(a.device).cuda_stream)), "cb_yetirank")
         return der.unsqueeze(0), hess.unsqueeze(0)
 

@@ -381,3 +381,26 @@ def test_pairwise_kernels_match_the_tensor_oracle():
     m.fit(Xr, rel, group_id=gid)
     s = m.predict(Xr)
     assert np.corrcoef(s, Xr[:, 0] + 0.5 * Xr[:, 1])[0, 1] > 0.6
+
+
+def test_dominant_bin_skipping_gives_the_same_trees():
+    """Sparse columns (60 % zeros): with the dominant bin skipped and restored from the slot totals the histograms are
+    the same integers, so the trees are the same as without skipping."""
+    rng = np.random.default_rng(13)
+    n, F = 80_003, 22
+    X = rng.random((n, F), dtype=np.float32)
+    X[rng.random((n, F)) < 0.6] = 0.0
+    X[:, 3] = rng.standard_normal(n)                     # one dense column: no dominant bin there
+    y = (X[:, 0] + X[:, 1] * 2 + X[:, 3] * 0.3 + 0.2 * rng.standard_normal(n) > 0.9).astype(np.float32)
+    store = _store_of(X, y, 64)
+    outs = []
+    for skip in (True, False):
+        eng = _engine(store, y, "narrow", 6, 5, skip_dominant_bin=skip, leaf_iterations=2, random_strength=0.0)
+        assert (eng.domw is not None) == skip
+        eng.step(5)
+        sp, vals, wts = eng.finish()
+        outs.append((sp.copy(), vals.copy(), wts.copy()))
+        eng.close()
+    assert np.array_equal(outs[0][0][:, :, :2], outs[1][0][:, :, :2]), np.argwhere(outs[0][0] != outs[1][0])[:8]
+    assert np.allclose(outs[0][2], outs[1][2], rtol=1e-6)
+    assert np.allclose(outs[0][1], outs[1][1], rtol=1e-4, atol=1e-5)
