@@ -359,6 +359,7 @@ def main():
                     help="boosting iterations of the end-to-end fit() (default 1000: the metric's own iteration count)")
     ap.add_argument("--ctr-complexity", type=int, default=2, help="max_ctr_complexity of the categorical config")
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--apply-100m", action="store_true", help="stream 100M rows through predict() (repeated passes over the host matrix)")
     ap.add_argument("--phases", action="store_true", help="print per-phase times of the fused level kernel")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -541,7 +542,23 @@ def main():
         torch.cuda.synchronize(dev)
         ms = a0.elapsed_time(a1) / reps
         apply_info = {"rows_per_s": rows / (ms * 1e-3), "rows": rows, "trees": model.tree_count_, "ms": ms,
-                      "tree_rows_per_s": rows * model.tree_count_ / (ms * 1e-3), "n_gpus": 1}
+                      "tree_rows_per_s": rows * model.tree_count_ / (ms * 1e-3), "n_gpus": 1,
+                      "note": "kernel only: rows resident on one device"}
+        del xd, out, pred
+        torch.cuda.empty_cache()
+        # the public call on all GPUs of the run: rows streamed from pinned host memory (H2D of every row and D2H of every
+        # prediction inside the timed region), one contiguous row range per device
+        devs = list(range(world))
+        model.predict(Xp[:200_000], prediction_type="RawFormulaVal", task_type="GPU", devices=devs)      # warm-up
+        reps_h = max(1, 100_000_000 // len(Xp)) if args.apply_100m else 1
+        t0 = time.perf_counter()
+        for _ in range(reps_h):
+            model.predict(Xp, prediction_type="RawFormulaVal", task_type="GPU", devices=devs)
+        dt = time.perf_counter() - t0
+        apply_info["host"] = {"rows_per_s": len(Xp) * reps_h / dt, "rows": len(Xp) * reps_h, "n_gpus": world,
+                              "seconds": dt, "h2d_bytes": int(Xp.nbytes) * reps_h,
+                              "note": "predict(task_type='GPU', devices=all) from pinned host memory; every pass copies "
+                                      "all rows to the devices again"}
     if rank == 0:
         ms_per_step = total_ms / K
         value = ms_per_step          # ms per iteration == seconds per 1000 iterations

@@ -99,8 +99,19 @@ def mode_fit(argv):
     params.setdefault("verbose", bool(args.verbose))
     learn = _pool(args.learn_set, args, args.learn_pairs)
     tests = [_pool(t, args, args.test_pairs) for t in args.test_set]
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        # a rank of a multi-process run (run-worker / torchrun): every rank read the whole file, keeps its row shard
+        # (queries whole) and fit() is a collective call
+        from .parallel.launcher import shard_bounds
+        r, w = dist.get_rank(), dist.get_world_size()
+        b = shard_bounds(learn, w)
+        learn = learn.slice_range(b[r], b[r + 1])
+        tests = [t.slice_range(*[shard_bounds(t, w)[k] for k in (r, r + 1)]) for t in tests]
     model = CatBoost(params)
     model.fit(learn, eval_set=tests or None)
+    if dist.is_available() and dist.is_initialized() and dist.get_rank() != 0:
+        return 0
     for fmt in args.model_format.split(","):
         fmt = {"CatboostBinary": "cbm", "Json": "json", "Cpp": "cpp", "Python": "python"}.get(fmt, fmt.lower())
         name = args.model_file if fmt == "cbm" else f"{args.model_file}.{fmt}"
@@ -415,7 +426,88 @@ def mode_eval_feature(argv):
     return 0
 
 
-MODES = {"ostr": mode_ostr, "eval-feature": mode_eval_feature, "fit": mode_fit, "calc": mode_calc, "fstr": mode_fstr, "eval-metrics": mode_eval_metrics,
+def mode_run_worker(argv):
+    """One rank of a training run over several processes / hosts (the counterpart of the reference's
+    ``catboost run-worker`` + master, catboost/app/main.cpp:21-35, catboost/private/libs/distributed): every participant
+    runs ``run-worker --rank R --world-size W --master-addr A --master-port P -- <fit options>``; the ranks join one
+    process group (gloo for CPU training, NCCL for task_type GPU), each trains on its row shard of the learn set and rank
+    0 writes the model."""
+    import os
+    if "--" in argv:
+        k = argv.index("--")
+        own, fit_args = argv[:k], argv[k + 1:]
+    else:
+        own, fit_args = argv, []
+    ap = argparse.ArgumentParser(prog="catboost_b200 run-worker")
+    ap.add_argument("--rank", type=int, default=int(os.environ.get("RANK", 0)))
+    ap.add_argument("--world-size", type=int, default=int(os.environ.get("WORLD_SIZE", 1)))
+    ap.add_argument("--master-addr", default=os.environ.get("MASTER_ADDR", "127.0.0.1"))
+    ap.add_argument("--master-port", type=int, default=int(os.environ.get("MASTER_PORT", 29500)))
+    ap.add_argument("--backend", default=None, help="gloo (CPU) or nccl (GPU); default: by --task-type of the fit options")
+    args = ap.parse_args(own)
+    import torch
+    import torch.distributed as dist
+    gpu = any(a.upper() == "GPU" for a in fit_args)
+    backend = args.backend or ("nccl" if gpu and torch.cuda.is_available() else "gloo")
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = args.master_addr, str(args.master_port)
+    kw = {}
+    if backend == "nccl":
+        local = int(os.environ.get("LOCAL_RANK", args.rank % max(1, torch.cuda.device_count())))
+        torch.cuda.set_device(local)
+        kw["device_id"] = torch.device("cuda", local)
+    dist.init_process_group(backend, rank=args.rank, world_size=args.world_size, **kw)
+    try:
+        return mode_fit(fit_args)
+    finally:
+        try:
+            dist.barrier()
+        except Exception:
+            pass
+        dist.destroy_process_group()
+
+
+def mode_model_based_eval(argv):
+    """Feature evaluation that starts from a trained baseline (catboost/app/mode_model_based_eval.cpp, catboost/libs/
+    train_lib/model_based_eval.cpp): for every feature set the baseline's first trees are kept and training continues
+    once without the set (ignored) and once with it; the report gives the final metric of both continuations."""
+    ap = argparse.ArgumentParser(prog="catboost_b200 model-based-eval")
+    _add_pool_args(ap)
+    ap.add_argument("--features-to-evaluate", required=True, help="feature sets separated by ';', indices by ','")
+    ap.add_argument("--baseline-model-snapshot", "--baseline-model", dest="baseline", required=True)
+    ap.add_argument("--offset", type=int, default=0, help="trees of the baseline that are kept")
+    ap.add_argument("--experiment-size", type=int, default=100, help="iterations of every continuation")
+    ap.add_argument("--loss-function", default=None)
+    ap.add_argument("--task-type", default="CPU")
+    ap.add_argument("-o", "--output-path", default="model_based_eval.json")
+    args = ap.parse_args(argv)
+    import json
+    from .core import CatBoost
+    learn = _pool(args.learn_set, args, args.learn_pairs)
+    tests = [_pool(t, args, args.test_pairs) for t in args.test_set]
+    base = CatBoost().load_model(args.baseline)
+    loss = args.loss_function or base._model.loss_name
+    if args.offset > 0:
+        base.shrink(args.offset)
+    sets = [[int(x) for x in part.split(",") if x.strip()] for part in args.features_to_evaluate.split(";") if part.strip()]
+    report = []
+    for fs in sets:
+        row = {"features": fs}
+        for name, ignored in (("without", fs), ("with", [])):
+            m = CatBoost(dict(loss_function=loss, iterations=args.experiment_size, task_type=args.task_type,
+                              ignored_features=ignored, verbose=False, allow_writing_files=False))
+            m.fit(learn, eval_set=tests or None, init_model=base)
+            ev = m.get_evals_result()
+            key = "validation" if tests else "learn"
+            metric = next(iter(ev[key]))
+            row[name] = {"metric": metric, "value": float(ev[key][metric][-1])}
+        row["delta"] = row["with"]["value"] - row["without"]["value"]
+        report.append(row)
+    with open(args.output_path, "w") as fh:
+        json.dump(report, fh, indent=1)
+    return 0
+
+
+MODES = {"run-worker": mode_run_worker, "model-based-eval": mode_model_based_eval, "ostr": mode_ostr, "eval-feature": mode_eval_feature, "fit": mode_fit, "calc": mode_calc, "fstr": mode_fstr, "eval-metrics": mode_eval_metrics,
          "metadata": mode_metadata, "model-sum": mode_model_sum, "normalize-model": mode_normalize_model,
          "select-features": mode_select_features, "dataset-statistics": mode_dataset_statistics,
          "dump-options": mode_dump_options, "roc": mode_roc}
@@ -427,10 +519,6 @@ def main(argv=None):
         print("usage: python -m catboost_b200 <mode> [options]\nmodes: " + ", ".join(MODES))
         return 0
     mode = argv[0]
-    if mode in ("run-worker", "model-based-eval"):
-        print(f"mode {mode!r} is not supported: training over several hosts starts one process per GPU with torchrun "
-              "(every rank calls fit on its row shard); model-based evaluation is covered by eval-feature", file=sys.stderr)
-        return 2
     if mode not in MODES:
         print(f"unknown mode {mode!r}; modes: " + ", ".join(MODES), file=sys.stderr)
         return 2

@@ -154,11 +154,12 @@ class CatBoost:
             kw["embedding_features"] = list(est.emb_flat) or None
         return kw
 
-    def _raw(self, data, ntree_start=0, ntree_end=0, thread_count=-1, task_type="CPU"):
+    def _raw(self, data, ntree_start=0, ntree_end=0, thread_count=-1, task_type="CPU", devices=None):
         self._check_fitted()
         pool = data if isinstance(data, Pool) else Pool(data, data_can_be_none=False, **self._pool_kwargs())
         fd, ch = self._model.pool_arrays(pool)
-        raw = self._model.predict_raw(fd, ch, ntree_start, ntree_end, task_type=task_type, thread_count=thread_count)
+        raw = self._model.predict_raw(fd, ch, ntree_start, ntree_end, task_type=task_type, thread_count=thread_count,
+                                      device=devices)
         if pool.baseline is not None:
             raw = raw + pool.baseline.reshape(raw.shape)
         return raw
@@ -211,11 +212,11 @@ class CatBoost:
         return "RawFormulaVal"
 
     def predict(self, data, prediction_type=None, ntree_start=0, ntree_end=0, thread_count=-1, verbose=None,
-                task_type="CPU"):
-        raw = self._raw(data, ntree_start, ntree_end, thread_count, task_type)
+                task_type="CPU", devices=None):
+        """``task_type='GPU'`` evaluates float-only symmetric models on the device; ``devices`` ('0-7', '0:2', a list)
+        shards the rows over several GPUs of this machine."""
+        raw = self._raw(data, ntree_start, ntree_end, thread_count, task_type, devices)
         pt = prediction_type or self._default_prediction_type()
-        if pt == "RawFormulaVal" and self._model.loss_name == "Poisson" and False:
-            pt = "Exponent"
         return self._format(raw, pt)
 
     def staged_predict(self, data, prediction_type=None, ntree_start=0, ntree_end=0, eval_period=1, thread_count=-1,

@@ -553,6 +553,28 @@ class Pool:
         out._quantized = None
         return out
 
+    def slice_range(self, begin: int, end: int):
+        """New Pool with rows [begin, end) as VIEWS of this pool's arrays (no copy; used by the multi-GPU launcher, whose
+        workers map the parent's arrays from shared memory and keep only their own rows in sight)."""
+        begin, end = int(begin), int(end)
+        out = Pool.__new__(Pool)
+        out.__dict__.update(self.__dict__)
+        out.float_data = self.float_data[begin:end]
+        out.cat_hashes = self.cat_hashes[:, begin:end]
+        out._cat_distinct = {}
+        out.__dict__.pop("_cat_hash_tensors", None)
+        out.text_data = [t[begin:end] for t in getattr(self, "text_data", [])]
+        out.embedding_data = [e[begin:end] for e in getattr(self, "embedding_data", [])]
+        for k in ("label", "weight", "group_weight", "baseline", "timestamp", "group_id", "subgroup_id"):
+            v = getattr(self, k)
+            setattr(out, k, None if v is None else v[begin:end])
+        if self.pairs is not None:
+            keep = ((self.pairs[:, 0] >= begin) & (self.pairs[:, 0] < end) & (self.pairs[:, 1] >= begin) & (self.pairs[:, 1] < end))
+            out.pairs = self.pairs[keep] - begin
+            out.pairs_weight = self.pairs_weight[keep]
+        out._quantized = None
+        return out
+
     def quantize(self, ignored_features=None, per_float_feature_quantization=None, border_count=None,
                  max_bin=None, feature_border_type=None, nan_mode=None, input_borders=None, task_type=None,
                  used_ram_limit=None, random_seed=None, **kwargs):

@@ -5,7 +5,9 @@ The reference's GPU evaluator quantises into an intermediate uchar4 buffer and e
 (``cb_predict_kernel``) stages the bins of a tile of rows in shared memory (32 features at a time, their borders in
 shared memory, a warp reading one row's values as one contiguous piece) and walks all trees; models with up
 to 8 output dimensions are supported.  Rows are streamed from pinned host memory in chunks so that any dataset
-size fits.
+size fits; when the caller's matrix already lives in pinned memory the chunks are copied straight from it.  With
+several devices the rows are cut into one contiguous range per device and every range is streamed by its own host
+thread (the reference's GPU evaluator is single-device: catboost/libs/model/cuda/evaluator.cu).
 """
 from __future__ import annotations
 
@@ -54,20 +56,22 @@ class GpuPredictor:
                           "cb_predict_oblivious")
         return out
 
-    def predict(self, X: np.ndarray, chunk_rows: int = 0) -> np.ndarray:
+    def predict(self, X: np.ndarray, chunk_rows: int = 0, out: np.ndarray = None) -> np.ndarray:
         """Rows from host memory, in chunks through two pinned staging buffers and two streams: while one chunk is
         copied to the device and evaluated, the host fills the other buffer, and results come back asynchronously."""
         X = np.ascontiguousarray(X, dtype=np.float32)
         n, F = X.shape
-        res = np.empty((n, self.dims), dtype=np.float64)
+        res = np.empty((n, self.dims), dtype=np.float64) if out is None else out
         if n == 0:
             return res
         if chunk_rows <= 0:
             chunk_rows = max(4096, min(n, (64 << 20) // max(F, 1)))          # about 256 MB of floats per buffer
         xt = torch.from_numpy(X)
+        src_pinned = bool(xt.is_pinned())            # the caller's rows are page-locked: no staging copy needed
         with torch.cuda.device(self.dev):
             nbuf = 2 if n > chunk_rows else 1
-            stage = [torch.empty((chunk_rows, F), dtype=torch.float32).pin_memory() for _ in range(nbuf)]
+            stage = [None if src_pinned else torch.empty((chunk_rows, F), dtype=torch.float32).pin_memory()
+                     for _ in range(nbuf)]
             back = [torch.empty((self.dims, chunk_rows), dtype=torch.float32).pin_memory() for _ in range(nbuf)]
             dbuf = [torch.empty((chunk_rows, F), dtype=torch.float32, device=self.dev) for _ in range(nbuf)]
             dout = [torch.empty((self.dims, chunk_rows), dtype=torch.float32, device=self.dev) for _ in range(nbuf)]
@@ -89,12 +93,14 @@ class GpuPredictor:
                 r1 = min(n, r0 + chunk_rows)
                 m = r1 - r0
                 drain(k)
-                stage[k][:m].copy_(xt[r0:r1])
+                if not src_pinned:
+                    stage[k][:m].copy_(xt[r0:r1])
+                h_src = xt[r0:r1] if src_pinned else stage[k][:m]
                 # a short last chunk uses the front of the buffers as a dense [dims, m] block
                 d_out = dout[k].view(-1)[: self.dims * m].view(self.dims, m)
                 h_out = back[k].view(-1)[: self.dims * m].view(self.dims, m)
                 with torch.cuda.stream(streams[k]):
-                    dbuf[k][:m].copy_(stage[k][:m], non_blocking=True)
+                    dbuf[k][:m].copy_(h_src, non_blocking=True)
                     self.predict_device(dbuf[k][:m], d_out)
                     h_out.copy_(d_out, non_blocking=True)
                     ev = torch.cuda.Event()
@@ -106,10 +112,65 @@ class GpuPredictor:
         return res
 
 
+class MultiGpuPredictor:
+    """The same model resident on several GPUs of this machine; a batch is cut into one contiguous row range per device
+    and the ranges are evaluated concurrently, each by its own host thread (copies and launches release the interpreter
+    lock, so the threads overlap)."""
+
+    def __init__(self, model, devices):
+        self.devices = [torch.device("cuda", int(d)) for d in devices]
+        self.parts = [GpuPredictor(model, d) for d in self.devices]
+        self.T, self.dims = self.parts[0].T, self.parts[0].dims
+
+    def predict(self, X: np.ndarray, chunk_rows: int = 0) -> np.ndarray:
+        import threading
+        X = np.ascontiguousarray(X, dtype=np.float32)
+        n = X.shape[0]
+        res = np.empty((n, self.dims), dtype=np.float64)
+        R = len(self.parts)
+        if n < 4096 * R or R == 1:
+            return self.parts[0].predict(X, chunk_rows, res)
+        bounds = [n * r // R for r in range(R + 1)]
+        errors = []
+
+        def work(r):
+            try:
+                self.parts[r].predict(X[bounds[r]:bounds[r + 1]], chunk_rows, res[bounds[r]:bounds[r + 1]])
+            except Exception as e:          # surfaced on the calling thread
+                errors.append(e)
+
+        threads = [threading.Thread(target=work, args=(r,)) for r in range(R)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        if errors:
+            raise errors[0]
+        return res
+
+
 def predict_oblivious_gpu(model, X: np.ndarray, device=None) -> np.ndarray:
+    """``device``: None (current device), a device / ordinal, or a CatBoost devices string ('0-3', '0:2') or list:
+    several devices shard the rows."""
+    devs = None
+    if isinstance(device, (list, tuple)):
+        devs = [int(d) for d in device]
+    elif isinstance(device, str) and not device.startswith("cuda"):
+        from ..params import parse_devices
+        devs = parse_devices(device, torch.cuda.device_count())
+    if devs is not None and len(devs) > 1:
+        key = "_gpu_predictor_multi"
+        pred = model.__dict__.get(key)
+        if pred is None or pred.T != len(model.trees) or [d.index for d in pred.devices] != devs:
+            pred = MultiGpuPredictor(model, devs)
+            model.__dict__[key] = pred
+        return pred.predict(X)
+    if devs is not None:
+        device = torch.device("cuda", devs[0])
     key = "_gpu_predictor"
     pred = model.__dict__.get(key)
-    if pred is None or pred.T != len(model.trees):
+    if pred is None or pred.T != len(model.trees) or (device is not None and torch.device(device) != pred.dev
+                                                      and torch.device(device).index is not None):
         pred = GpuPredictor(model, device)
         model.__dict__[key] = pred
     return pred.predict(X)

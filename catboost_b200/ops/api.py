@@ -76,6 +76,25 @@ def hist(store: BinnedStore, leaf: torch.Tensor, stats: torch.Tensor, slot_table
     return out
 
 
+def sort_pairs(keys: torch.Tensor):
+    """Stable ascending sort of int64 keys: ``(sorted_keys, order)`` with ``order`` int64 such that
+    ``sorted_keys == keys[order]`` and equal keys keep their input order.  On the GPU this is the hand-written radix sort
+    of ``cb_sort.cu`` (8 passes of 8 bits); on the CPU the framework's stable sort."""
+    if not keys.is_cuda:
+        return torch.sort(keys, stable=True)
+    dev = keys.device
+    n = int(keys.numel())
+    ka = keys.contiguous().clone()
+    kb = torch.empty_like(ka)
+    va = torch.empty(n, dtype=torch.int32, device=dev)
+    vb = torch.empty(n, dtype=torch.int32, device=dev)
+    lib = native.cuda_lib()
+    scratch = torch.empty(max(1, int(lib.cb_sort_scratch_bytes(n))), dtype=torch.uint8, device=dev)
+    native.cuda_check(lib.cb_sort_pairs_i64(_p(ka), _p(va), _p(kb), _p(vb), n, _p(scratch), 1, _stream(dev)),
+                      "cb_sort_pairs_i64")
+    return ka, va.long()
+
+
 _SCORE_FN_ID = {"Cosine": 0, "NewtonCosine": 0, "L2": 1, "NewtonL2": 1, "SolarL2": 2, "LOOL2": 3, "SatL2": 4}
 
 

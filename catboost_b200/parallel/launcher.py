@@ -3,6 +3,10 @@
 ``fit(task_type='GPU', devices='0-7')`` from a plain Python process spawns one worker per device; each worker joins a
 ``torch.distributed`` NCCL group on 127.0.0.1, takes a contiguous row shard (query groups are kept whole, like
 catboost/cuda/gpu_data/doc_parallel_dataset_builder.cpp:20-55), trains doc-parallel and rank 0 hands the result back.
+The data set reaches the workers through POSIX shared memory: the parent copies every large array of the pool once
+into a shared segment, a worker maps the segments and looks at its own rows only (views, no copy), so host memory
+holds two copies of the data in total whatever the number of GPUs (the reference keeps one copy because its workers are
+threads of one process).
 When the caller already runs under ``torchrun`` (torch.distributed initialised, world size > 1) ``fit`` is a
 collective call: every rank passes its own row shard and all ranks return the same model.
 """
@@ -44,6 +48,64 @@ def shard_bounds(pool: Pool, world: int) -> List[int]:
     return bounds
 
 
+_SHARED_ATTRS = ("float_data", "cat_hashes", "label", "weight", "group_weight", "baseline", "timestamp", "group_id",
+                 "subgroup_id", "pairs", "pairs_weight")
+
+
+def share_pool(pool: Pool):
+    """(descriptor, segments): the large numeric arrays of ``pool`` copied into shared-memory segments, everything else
+    (names, indices, text columns) pickled inside the descriptor.  The caller unlinks the segments when done."""
+    from multiprocessing import shared_memory
+    segments, arrays = [], {}
+    small = dict(pool.__dict__)
+    small.pop("_cat_hash_tensors", None)
+    small["_quantized"] = None
+    small["_cat_distinct"] = {}
+
+    def put(key, arr):
+        a = np.ascontiguousarray(arr)
+        seg = shared_memory.SharedMemory(create=True, size=max(1, a.nbytes))
+        np.ndarray(a.shape, dtype=a.dtype, buffer=seg.buf)[...] = a
+        segments.append(seg)
+        arrays[key] = (seg.name, a.shape, a.dtype.str)
+
+    for k in _SHARED_ATTRS:
+        v = small.get(k)
+        if isinstance(v, np.ndarray) and v.dtype.kind in "fiub" and v.nbytes >= (1 << 16):
+            put(k, v)
+            small[k] = None
+    emb = list(small.get("embedding_data") or [])
+    for j, e in enumerate(emb):
+        if isinstance(e, np.ndarray) and e.dtype.kind in "fiub":
+            put(f"embedding_data:{j}", e)
+            emb[j] = None
+    small["embedding_data"] = emb
+    return {"small": pickle.dumps(small, protocol=4), "arrays": arrays}, segments
+
+
+def attach_pool(desc):
+    """Pool whose large arrays are views of the shared segments named in ``desc`` (+ the handles to keep alive)."""
+    from multiprocessing import shared_memory
+    pool = Pool.__new__(Pool)
+    pool.__dict__.update(pickle.loads(desc["small"]))
+    handles = []
+    for key, (name, shape, dt) in desc["arrays"].items():
+        seg = shared_memory.SharedMemory(name=name)
+        try:
+            # the segment belongs to the parent: keep this process's exit from unlinking it
+            from multiprocessing import resource_tracker
+            resource_tracker.unregister(seg._name, "shared_memory")
+        except Exception:
+            pass
+        handles.append(seg)
+        arr = np.ndarray(shape, dtype=np.dtype(dt), buffer=seg.buf)
+        if key.startswith("embedding_data:"):
+            pool.embedding_data[int(key.split(":")[1])] = arr
+        else:
+            setattr(pool, key, arr)
+    return pool, handles
+
+
 def _worker(rank: int, world: int, port: int, devices, params, pool_blob_path, eval_blob_paths, default_loss, out_path,
             backend: str):
     import torch.distributed as dist
@@ -59,16 +121,19 @@ def _worker(rank: int, world: int, port: int, devices, params, pool_blob_path, e
         dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         from ..train.boosting import train_model
+        keep = []
         with open(pool_blob_path, "rb") as fh:
-            pool: Pool = pickle.load(fh)
+            pool, hs = attach_pool(pickle.load(fh))
+        keep += hs
         b = shard_bounds(pool, world)
-        shard = pool.slice(np.arange(b[rank], b[rank + 1]))
+        shard = pool.slice_range(b[rank], b[rank + 1])
         evals = []
         for p in eval_blob_paths:
             with open(p, "rb") as fh:
-                ep: Pool = pickle.load(fh)
+                ep, hs = attach_pool(pickle.load(fh))
+            keep += hs
             eb = shard_bounds(ep, world)
-            evals.append(ep.slice(np.arange(eb[rank], eb[rank + 1])))
+            evals.append(ep.slice_range(eb[rank], eb[rank + 1]))
         params = dict(params)
         params["devices"] = ":".join(str(d) for d in devices)
         res = train_model(params, shard, evals, default_loss=default_loss, ctx=DistContext.current())
@@ -83,6 +148,15 @@ def _worker(rank: int, world: int, port: int, devices, params, pool_blob_path, e
         except Exception:
             pass
         dist.destroy_process_group()
+        try:
+            del shard, evals, pool
+        except NameError:
+            pass
+        for seg in locals().get("keep", []):
+            try:
+                seg.close()
+            except BufferError:
+                pass
 
 
 def train_maybe_multi_gpu(params, train_pool: Pool, eval_pools, default_loss="RMSE", init_model=None, callbacks=None,
@@ -112,13 +186,18 @@ def spawn_training(params, train_pool, eval_pools, devices, default_loss="RMSE",
     world = len(devices)
     tmp = tempfile.mkdtemp(prefix="cb200_")
     pool_path = os.path.join(tmp, "train.pkl")
+    segments = []
+    desc, segs = share_pool(train_pool)
+    segments += segs
     with open(pool_path, "wb") as fh:
-        pickle.dump(train_pool, fh, protocol=4)
+        pickle.dump(desc, fh, protocol=4)
     eval_paths = []
     for k, ep in enumerate(eval_pools):
         pth = os.path.join(tmp, f"eval{k}.pkl")
+        desc, segs = share_pool(ep)
+        segments += segs
         with open(pth, "wb") as fh:
-            pickle.dump(ep, fh, protocol=4)
+            pickle.dump(desc, fh, protocol=4)
         eval_paths.append(pth)
     out_path = os.path.join(tmp, "result.pkl")
     port = _free_port()
@@ -132,6 +211,12 @@ def spawn_training(params, train_pool, eval_pools, devices, default_loss="RMSE",
         res.options = Options(res.options)
         return res
     finally:
+        for seg in segments:
+            try:
+                seg.close()
+                seg.unlink()
+            except (OSError, BufferError):
+                pass
         for f in [pool_path, out_path] + eval_paths:
             try:
                 os.remove(f)

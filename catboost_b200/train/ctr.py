@@ -11,7 +11,7 @@ CTR description (type + prior) a float feature is produced and binarised with it
 
 Behaviour follows catboost/cuda/ctrs/ctr_calcers.h:122-160, ctr_bins_builder.h:137-245 (equal keys contiguous in
 permutation order, segmented exclusive scan, divide with priors), catboost/private/libs/algo/online_ctr.cpp and the
-prior defaults of catboost/private/libs/options/cat_feature_options.cpp:118-140.  The device path is a stable sort by
+prior defaults of catboost/private/libs/options/cat_feature_options.cpp:118-140.  The device path is a stable (hand-written radix) sort by
 category of the rows taken in permutation order, a segmented exclusive scan, and a scatter back.
 Combination hashes use the model's hash rule (catboost/libs/model/hash.h:11-14) so that the stored tables can be
 looked up at apply time from raw categorical hashes.
@@ -174,13 +174,22 @@ def projection_hash_t(cols) -> torch.Tensor:
     return res
 
 
+def _stable_sort(keys: torch.Tensor):
+    """(sorted keys, order): the hand-written radix sort on the GPU (ops/cuda/cb_sort.cu), the framework's stable sort on
+    the CPU."""
+    from ..ops import api as ops
+    if keys.dtype != torch.int64:
+        return torch.sort(keys, stable=True)
+    return ops.sort_pairs(keys)
+
+
 def _group_rows(h: torch.Tensor, order_t: torch.Tensor):
     """One stable sort of the projection hashes taken in permutation order: rows of equal hash become contiguous and
     keep the permutation order inside their group.  Returns (rows, seg_id, first_idx, uniq): the row id at every sorted
     position, the dense group number of every sorted position, the first sorted position of every group, and the
     distinct hashes in (signed) increasing order."""
     n = h.shape[0]
-    sorted_h, srt = torch.sort(h[order_t], stable=True)
+    sorted_h, srt = _stable_sort(h[order_t])
     rows = order_t[srt]
     start = torch.ones(n, dtype=torch.bool, device=h.device)
     if n > 1:
@@ -251,7 +260,7 @@ class _KernelGroup:
     def __init__(self, h, order_t, cls_u8, need_tb, want_prefix):
         from ..ops import api as ops
         self.ops = ops
-        sorted_h, srt = torch.sort(h[order_t], stable=True)
+        sorted_h, srt = _stable_sort(h[order_t])
         self.rows_t = order_t[srt]
         self.n = int(h.shape[0])
         self.excl, self.seg_id, self.uniq_t, self.totals_i = ops.ctr_scan(sorted_h, self.rows_t, cls_u8, need_tb)

@@ -168,8 +168,8 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
         elif not (ctx is not None and ctx.is_distributed):
             plearner = PairwiseLearner(store, o, seed=int(o.random_seed))
     ordered = None
-    if o.boosting_type == "Ordered" and not (ctx is not None and ctx.is_distributed):
-        ordered = OrderedState(o, n, train_pool, dev, approx[:, :n])
+    if o.boosting_type == "Ordered":
+        ordered = OrderedState(o, n, train_pool, dev, approx[:, :n], ctx)
     trees = []
     start_iter = 0
     restored = snap.try_load(o)
@@ -281,25 +281,43 @@ class OrderedState:
     moved by leaf statistics of blocks < b, so the derivatives that drive the structure search are not fitted to the
     document's own target.  The exported model still gets its leaf values from all documents (plain cursor)."""
 
-    def __init__(self, o, n, pool, dev, approx0):
-        rng = np.random.RandomState(int(o.random_seed) + 777)
-        if pool.group_id is not None:
-            off = pool.group_offsets()
-            perm_g = rng.permutation(len(off) - 1)
-            order = np.concatenate([np.arange(off[k], off[k + 1]) for k in perm_g]) if len(perm_g) else np.zeros(0, np.int64)
-        else:
-            order = np.arange(n) if o.has_time else rng.permutation(n)
+    def __init__(self, o, n, pool, dev, approx0, ctx=None):
+        self.ctx = ctx if (ctx is not None and ctx.is_distributed) else None
+        rank = self.ctx.rank if self.ctx is not None else 0
+        rng = np.random.RandomState(int(o.random_seed) + 777 + 7919 * rank)
+        n_total = n
+        if self.ctx is not None:
+            n_total = int(sum(self.ctx.all_gather_object(int(n))))
         bounds = [0]
-        size = max(1, min(int(o.min_fold_size), n))
+        size = max(1, min(int(o.min_fold_size), n_total))
         mult = max(1.0001, float(o.fold_len_multiplier))
-        while bounds[-1] < n:
-            bounds.append(min(n, bounds[-1] + int(math.ceil(size))))
+        while bounds[-1] < n_total:
+            bounds.append(min(n_total, bounds[-1] + int(math.ceil(size))))
             size *= mult
-        block_of_pos = np.zeros(n, dtype=np.int64)
-        for b in range(len(bounds) - 1):
-            block_of_pos[bounds[b]:bounds[b + 1]] = b
-        block = np.zeros(n, dtype=np.int64)
-        block[order] = block_of_pos
+        if self.ctx is None:
+            if pool.group_id is not None:
+                off = pool.group_offsets()
+                perm_g = rng.permutation(len(off) - 1)
+                order = np.concatenate([np.arange(off[k], off[k + 1]) for k in perm_g]) if len(perm_g) else np.zeros(0, np.int64)
+            else:
+                order = np.arange(n) if o.has_time else rng.permutation(n)
+            block_of_pos = np.zeros(n, dtype=np.int64)
+            for b in range(len(bounds) - 1):
+                block_of_pos[bounds[b]:bounds[b + 1]] = b
+            block = np.zeros(n, dtype=np.int64)
+            block[order] = block_of_pos
+        else:
+            # several ranks: every document (every query) draws a position in the global permutation on its own; the
+            # blocks are ranges of global positions, so a rank holds a random part of every block and the per-block leaf
+            # statistics are summed over the ranks
+            if pool.group_id is not None:
+                off = pool.group_offsets()
+                ug = rng.random_sample(len(off) - 1)
+                u = np.repeat(ug, np.diff(off))
+            else:
+                u = rng.random_sample(n)
+            pos = np.minimum((u * n_total).astype(np.int64), n_total - 1)
+            block = np.searchsorted(np.asarray(bounds[1:], dtype=np.int64), pos, side="right")
         self.n_blocks = len(bounds) - 1
         self.block = torch.from_numpy(block).to(dev)
         self.approx = approx0.clone()
@@ -318,6 +336,9 @@ class OrderedState:
         else:
             w = torch.ones(n, dtype=torch.float64, device=der.device) if weight is None else weight[:n].double()
             sh.index_add_(1, key, w.unsqueeze(0).expand(dims, n).contiguous())
+        if self.ctx is not None:
+            self.ctx.all_reduce_sum_(sd)
+            self.ctx.all_reduce_sum_(sh)
         sd = sd.view(dims, B, L).cumsum(1)
         sh = sh.view(dims, B, L).cumsum(1)
         val = sd / (sh + float(o.l2_leaf_reg))
@@ -351,7 +372,8 @@ def _device_metric(metric, approx, y, w):
     """The common additive metrics evaluated where the approximations live (a host round trip of a 1M x 5 cursor per
     iteration costs more than growing the tree).  Returns None for metrics without a device formula."""
     name = getattr(metric, "name", None)
-    if name not in ("Logloss", "RMSE", "MAE", "MultiClass", "Accuracy") or getattr(metric, "params", None):
+    if name not in ("Logloss", "RMSE", "MAE", "MultiClass", "Accuracy", "AUC", "Precision", "Recall", "F1", "R2") \
+            or getattr(metric, "params", None):
         return None
     if not approx.is_cuda or isinstance(y, torch.Tensor) or np.ndim(y) != 1:
         return None
@@ -364,6 +386,39 @@ def _device_metric(metric, approx, y, w):
     yt = _Y_CACHE[key][1]
     wt = None if w is None else torch.from_numpy(np.ascontiguousarray(w, dtype=np.float32)).to(dev)
     a = approx.float()
+    if name in ("AUC", "Precision", "Recall", "F1", "R2"):
+        if a.shape[0] != 1:
+            return None
+        wd = torch.ones_like(yt, dtype=torch.float64) if wt is None else wt.double()
+        if name == "R2":
+            mean = (yt.double() * wd).sum() / wd.sum()
+            ss_res = (((yt - a[0]).double() ** 2) * wd).sum()
+            ss_tot = (((yt.double() - mean) ** 2) * wd).sum()
+            return float((1.0 - ss_res / ss_tot.clamp_min(1e-300)).item())
+        pos = yt > 0.5
+        if name == "AUC":
+            # weighted Mann-Whitney statistic with ties counted half (sort on the device, catboost/cuda/targets/auc.cpp)
+            order = torch.argsort(a[0], stable=True)
+            s_, p_, w_ = a[0][order], pos[order], wd[order]
+            wpos, wneg = torch.where(p_, w_, torch.zeros_like(w_)), torch.where(p_, torch.zeros_like(w_), w_)
+            _, inv, cnt = torch.unique_consecutive(s_, return_inverse=True, return_counts=True)
+            gneg = torch.zeros(cnt.shape[0], dtype=torch.float64, device=dev).index_add_(0, inv, wneg)
+            gpos = torch.zeros(cnt.shape[0], dtype=torch.float64, device=dev).index_add_(0, inv, wpos)
+            below = torch.cumsum(gneg, 0) - gneg                      # negative weight strictly below each tie group
+            num = (gpos * (below + 0.5 * gneg)).sum()
+            den = wpos.sum() * wneg.sum()
+            return float((num / den.clamp_min(1e-300)).item()) if float(den.item()) > 0 else 0.5
+        pred = a[0] > 0
+        tp = (wd * (pred & pos)).sum()
+        fp = (wd * (pred & ~pos)).sum()
+        fn = (wd * (~pred & pos)).sum()
+        prec = tp / (tp + fp).clamp_min(1e-300)
+        rec = tp / (tp + fn).clamp_min(1e-300)
+        if name == "Precision":
+            return float(prec.item()) if float((tp + fp).item()) > 0 else 1.0
+        if name == "Recall":
+            return float(rec.item()) if float((tp + fn).item()) > 0 else 1.0
+        return float((2 * prec * rec / (prec + rec).clamp_min(1e-300)).item())
     if name == "Logloss":
         per = torch.nn.functional.softplus(a[0]) - yt * a[0]
     elif name == "RMSE":

@@ -46,6 +46,8 @@ if mode == "cat":
     X = Xo
     fit_kw["cat_features"] = [F, F + 1]
     params.update(one_hot_max_size=2, max_ctr_complexity=1)
+elif mode == "ordered":
+    params["boosting_type"] = "Ordered"
 elif mode != "default":
     params["histogram_reduce"] = mode
 m = cb.CatBoostClassifier(**params)
@@ -96,6 +98,13 @@ def test_gloo_two_ranks_match_single_process():
     # splits and differ only by the summation order of the histograms
     assert res["splits"] == ref_splits
     assert np.allclose(res["pred"], ref, rtol=1e-3, atol=1e-3)
+
+
+def test_gloo_two_ranks_ordered_boosting():
+    """boosting_type='Ordered' on two ranks: the blocks of the global permutation are spread over the ranks and their
+    per-leaf statistics are summed, so the run learns as well as a single process does."""
+    res = _run(2, "gloo", "ordered", port=29619)
+    assert res["acc"] > 0.9
 
 
 def test_split_columns_with_fewer_features_than_ranks():
@@ -187,3 +196,36 @@ def test_corrupted_snapshot_is_rejected(tmp_path):
     open(snap, "wb").write(bytes(blob))
     with pytest.raises(cb.CatBoostError, match="corrupted"):
         cb.CatBoostClassifier(**kw).fit(X, y)
+
+
+def test_launcher_hands_the_pool_over_in_shared_memory():
+    """fit() from one process on several devices: the workers map the parent's arrays from shared memory and train on
+    views of their own rows (gloo ranks on the CPU here); the model equals the single-process one."""
+    import catboost_b200 as cb
+    from catboost_b200.parallel.launcher import attach_pool, share_pool, spawn_training
+    rng = np.random.default_rng(0)
+    n, F = 24000, 10
+    X = rng.standard_normal((n, F), dtype=np.float32)
+    w = rng.standard_normal(F).astype(np.float32)
+    y = (X @ w + 0.3 * rng.standard_normal(n, dtype=np.float32) > 0).astype(np.float32)
+    pool = cb.Pool(X, y)
+    desc, segs = share_pool(pool)
+    try:
+        assert "float_data" in desc["arrays"] and len(desc["small"]) < 100_000
+        back, handles = attach_pool(desc)
+        assert np.array_equal(back.float_data, pool.float_data) and np.array_equal(back.label, pool.label)
+        view = back.slice_range(100, 200)
+        assert view.float_data.base is not None and np.array_equal(view.float_data, pool.float_data[100:200])
+        del back, view
+        for h in handles:
+            h.close()
+    finally:
+        for s in segs:
+            s.close()
+            s.unlink()
+    params = dict(iterations=12, depth=5, learning_rate=0.3, verbose=False, allow_writing_files=False, random_strength=0,
+                  bootstrap_type="No", task_type="CPU", border_count=32, loss_function="Logloss")
+    res = spawn_training(params, pool, [], [0, 1], default_loss="Logloss", backend="gloo")
+    ref, ref_splits = _single("CPU")
+    got_splits = [(s.feature, s.border) for s in res.model.splits]
+    assert got_splits == ref_splits

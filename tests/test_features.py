@@ -935,3 +935,47 @@ def test_model_file_cannot_run_code_on_load(tmp_path):
         with pytest.raises(CatBoostError):
             mio.model_from_cbm_bytes(blob)
         assert not marker.exists()
+
+
+def test_cli_run_worker_and_model_based_eval(tmp_path):
+    """Two `run-worker` processes train one model over a gloo group (the multi-host CPU path on one machine), and
+    `model-based-eval` compares continuations of a baseline with and without a feature set."""
+    import json
+    import socket
+    rng = np.random.default_rng(0)
+    n = 3000
+    X = rng.standard_normal((n, 5))
+    y = (X[:, 0] + 0.5 * X[:, 1] > 0).astype(int)
+    train = tmp_path / "train.tsv"
+    with open(train, "w") as fh:
+        for i in range(n):
+            fh.write("\t".join([str(y[i])] + [f"{v:.6f}" for v in X[i]]) + "\n")
+    cd = tmp_path / "train.cd"
+    cd.write_text("0\tLabel\n")
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    model = tmp_path / "dist.bin"
+    procs = []
+    for r in range(2):
+        cmd = [sys.executable, "-m", "catboost_b200", "run-worker", "--rank", str(r), "--world-size", "2", "--master-addr",
+               "127.0.0.1", "--master-port", str(port), "--", "-f", str(train), "--cd", str(cd), "-m", str(model),
+               "--loss-function", "Logloss", "-i", "15", "--verbose", "0", "--train-dir", str(tmp_path / f"info{r}")]
+        procs.append(subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env, cwd=str(tmp_path)))
+    for p in procs:
+        out, err = p.communicate(timeout=300)
+        assert p.returncode == 0, err[-2000:]
+    m = cb.CatBoostClassifier().load_model(str(model))
+    assert m.tree_count_ == 15
+    assert float((m.predict(X.astype(np.float32)) == y).mean()) > 0.9
+    out_json = tmp_path / "mbe.json"
+    r = subprocess.run([sys.executable, "-m", "catboost_b200", "model-based-eval", "-f", str(train), "--cd", str(cd),
+                        "--baseline-model", str(model), "--offset", "5", "--experiment-size", "10",
+                        "--features-to-evaluate", "0;3,4", "-o", str(out_json)],
+                       capture_output=True, text=True, env=env, cwd=str(tmp_path))
+    assert r.returncode == 0, r.stderr[-2000:]
+    rep = json.loads(out_json.read_text())
+    assert len(rep) == 2 and rep[0]["features"] == [0]
+    # the informative feature matters (lower Logloss with it), the noise features hardly do
+    assert rep[0]["delta"] < -0.01 and abs(rep[1]["delta"]) < abs(rep[0]["delta"])

@@ -459,3 +459,61 @@ def test_gpu_snapshot_resume_equals_uninterrupted(tmp_path):
     assert cont.tree_count_ == 9
     first = lambda m, k: [(s.feature, s.border) for t in m._model.trees[:k] for s in (m._model.splits[i] for i in t.splits)]
     assert first(cont, 7) == first(part, 7)
+
+
+def test_gpu_apply_from_pinned_memory_and_several_devices():
+    """predict(task_type='GPU'): rows taken straight from pinned memory (no staging copy) and, with more than one GPU,
+    sharded over the devices, against the CPU evaluator."""
+    import catboost_b200 as cb
+    rng = np.random.default_rng(6)
+    X = rng.standard_normal((60_000, 12)).astype(np.float32)
+    y = (X[:, 0] + X[:, 1] * X[:, 2] > 0).astype(int)
+    m = cb.CatBoostClassifier(iterations=25, depth=5, learning_rate=0.3, task_type="GPU", verbose=False,
+                              allow_writing_files=False).fit(X, y)
+    ref = m.predict(X, prediction_type="RawFormulaVal")
+    Xp = torch.from_numpy(X).pin_memory().numpy()
+    assert torch.from_numpy(Xp).is_pinned()
+    got = m.predict(Xp, prediction_type="RawFormulaVal", task_type="GPU", devices="0")
+    assert np.allclose(got, ref, rtol=1e-5, atol=1e-5)
+    from catboost_b200.models.gpu_apply import GpuPredictor
+    small = GpuPredictor(m._model, "cuda:0").predict(Xp, chunk_rows=7000)          # several chunks, short last one
+    assert np.allclose(small[:, 0], ref, rtol=1e-5, atol=1e-5)
+    if torch.cuda.device_count() >= 2:
+        both = m.predict(Xp, prediction_type="RawFormulaVal", task_type="GPU", devices="0-1")
+        assert np.allclose(both, ref, rtol=1e-5, atol=1e-5)
+        # the same model on the second device after the first (function attributes are per device)
+        second = m.predict(X, prediction_type="RawFormulaVal", task_type="GPU", devices="1")
+        assert np.allclose(second, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_device_side_metrics_match_host_metrics():
+    """AUC / F1 / Precision / Recall logged during a GPU fit are evaluated where the cursor lives; they agree with the
+    host implementations applied to the finished model."""
+    import catboost_b200 as cb
+    rng = np.random.default_rng(12)
+    X = rng.standard_normal((15_000, 6)).astype(np.float32)
+    y = (X[:, 0] + 0.5 * X[:, 1] + 0.7 * rng.standard_normal(15_000) > 0.2).astype(int)
+    w = (rng.random(15_000) + 0.5).astype(np.float32)
+    names = ["AUC", "F1", "Precision", "Recall"]
+    m = cb.CatBoostClassifier(iterations=10, depth=4, learning_rate=0.3, task_type="GPU", verbose=False,
+                              allow_writing_files=False, custom_metric=names)
+    m.fit(X, y, sample_weight=w)
+    ev = m.get_evals_result()["learn"]
+    ref = m.eval_metrics(cb.Pool(X, y, weight=w), names)
+    for nm in names:
+        assert len(ev[nm]) == 10
+        assert np.allclose(ev[nm], ref[nm], rtol=1e-4, atol=1e-5), (nm, ev[nm][-1], ref[nm][-1])
+
+
+@pytest.mark.parametrize("n", [1, 31, 2048, 2049, 1_000_003])
+def test_radix_sort_is_stable_and_matches_framework_sort(n):
+    from catboost_b200.ops import api as ops
+    g = torch.Generator().manual_seed(n)
+    # few distinct keys (long runs of equal keys test stability), negative keys, and full-range 64-bit keys
+    for keys in (torch.randint(-5, 5, (n,), generator=g, dtype=torch.int64),
+                 torch.randint(-2 ** 62, 2 ** 62, (n,), generator=g, dtype=torch.int64) * 2 + 1):
+        k = keys.cuda()
+        sk, order = ops.sort_pairs(k)
+        ref_k, ref_o = torch.sort(k, stable=True)
+        assert torch.equal(sk, ref_k)
+        assert torch.equal(order, ref_o)
