@@ -507,7 +507,88 @@ def mode_model_based_eval(argv):
     return 0
 
 
-MODES = {"run-worker": mode_run_worker, "model-based-eval": mode_model_based_eval, "ostr": mode_ostr, "eval-feature": mode_eval_feature, "fit": mode_fit, "calc": mode_calc, "fstr": mode_fstr, "eval-metrics": mode_eval_metrics,
+def mode_dsv_diff(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 dsv-diff")
+    ap.add_argument("file_a")
+    ap.add_argument("file_b")
+    ap.add_argument("-d", "--delimiter", default="\t")
+    ap.add_argument("--have-header", action="store_true")
+    ap.add_argument("--diff-limit", type=float, default=0.0)
+    a = ap.parse_args(argv)
+    from .difftools import dsv_diff
+    diffs = dsv_diff(a.file_a, a.file_b, a.diff_limit, a.delimiter, a.have_header)
+    for d in diffs:
+        print(d)
+    return 1 if diffs else 0
+
+
+def mode_json_diff(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 json-diff")
+    ap.add_argument("file_a")
+    ap.add_argument("file_b")
+    ap.add_argument("--diff-limit", type=float, default=0.0)
+    ap.add_argument("--ignore-keys", default="")
+    a = ap.parse_args(argv)
+    import json
+    from .difftools import json_diff
+    with open(a.file_a) as fa, open(a.file_b) as fb:
+        diffs = json_diff(json.load(fa), json.load(fb), a.diff_limit,
+                          ignore_keys=tuple(k for k in a.ignore_keys.split(",") if k))
+    for d in diffs:
+        print(d)
+    return 1 if diffs else 0
+
+
+def mode_numpy_diff(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 numpy-diff")
+    ap.add_argument("file_a")
+    ap.add_argument("file_b")
+    ap.add_argument("--diff-limit", type=float, default=0.0)
+    a = ap.parse_args(argv)
+    from .difftools import numpy_diff
+    diffs = numpy_diff(a.file_a, a.file_b, a.diff_limit)
+    for d in diffs:
+        print(d)
+    return 1 if diffs else 0
+
+
+def mode_compare_models(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 compare-models")
+    ap.add_argument("model_a")
+    ap.add_argument("model_b")
+    ap.add_argument("--diff-limit", type=float, default=0.0)
+    ap.add_argument("--format-a", default=None)
+    ap.add_argument("--format-b", default=None)
+    a = ap.parse_args(argv)
+    from .difftools import compare_models
+    from .models.io import load_model
+    fmt = lambda path, f: f or ("json" if path.endswith(".json") else "cbm")
+    diffs = compare_models(load_model(a.model_a, fmt(a.model_a, a.format_a)), load_model(a.model_b, fmt(a.model_b, a.format_b)),
+                           a.diff_limit)
+    for d in diffs:
+        print(d)
+    print("MODELS ARE EQUAL" if not diffs else "MODELS DIFFER")
+    return 1 if diffs else 0
+
+
+def mode_model_perftest(argv):
+    ap = argparse.ArgumentParser(prog="catboost_b200 model-perftest")
+    ap.add_argument("-m", "--model-file", required=True)
+    ap.add_argument("--rows", type=int, default=100_000)
+    ap.add_argument("--repeats", type=int, default=5)
+    ap.add_argument("--task-type", default="CPU")
+    ap.add_argument("--devices", default=None)
+    a = ap.parse_args(argv)
+    import json
+    from .difftools import model_perftest
+    from .models.io import load_model
+    print(json.dumps(model_perftest(load_model(a.model_file, "json" if a.model_file.endswith(".json") else "cbm"), a.rows,
+                                    a.repeats, task_type=a.task_type, devices=a.devices)))
+    return 0
+
+
+MODES = {"dsv-diff": mode_dsv_diff, "json-diff": mode_json_diff, "numpy-diff": mode_numpy_diff,
+         "compare-models": mode_compare_models, "model-perftest": mode_model_perftest, "run-worker": mode_run_worker, "model-based-eval": mode_model_based_eval, "ostr": mode_ostr, "eval-feature": mode_eval_feature, "fit": mode_fit, "calc": mode_calc, "fstr": mode_fstr, "eval-metrics": mode_eval_metrics,
          "metadata": mode_metadata, "model-sum": mode_model_sum, "normalize-model": mode_normalize_model,
          "select-features": mode_select_features, "dataset-statistics": mode_dataset_statistics,
          "dump-options": mode_dump_options, "roc": mode_roc}

@@ -198,6 +198,9 @@ class Pool:
             return
         if isinstance(data, (str, os.PathLike)):
             path = os.fspath(data)
+            if path.startswith("quantized://"):
+                self.__dict__.update(Pool.load_quantized(path[len("quantized://"):]).__dict__)
+                return
             if path.startswith("libsvm://"):
                 loaded = read_libsvm(path[len("libsvm://"):])
             else:
@@ -585,6 +588,81 @@ class Pool:
                                              per_float_feature_quantization, input_borders)
         return self
 
+    # ---- quantized pool files ---------------------------------------------------------------------------------
+    # The role of the reference's quantized pool (catboost/private/libs/quantized_pool/serialization.cpp,
+    # ``Pool.save`` / ``Pool("quantized://...")``): a data set is stored as one byte per (document, float feature) plus
+    # the border grids instead of four-byte floats.  The container is this framework's own (label line + a plain-data
+    # stream, utils/plainser.py), not the reference's flatbuffers layout.
+    _QUANTIZED_LABEL = b"catboost_b200_quantized_pool_v1\n"
+
+    def _save_quantized(self, fname: str):
+        """Write a quantized pool to ``fname`` (``save`` comes here for quantized pools)."""
+        from ..utils import plainser
+        q = self._quantized
+        X = self.float_data
+        n, F = X.shape
+        bins = np.empty((n, F), dtype=np.uint8)
+        for f in range(F):
+            col = X[:, f]
+            b = np.searchsorted(np.asarray(q.borders[f], dtype=np.float32), col, side="left").astype(np.int64)
+            # value > border goes right: bin = number of borders strictly below the value
+            nanmask = np.isnan(col)
+            if nanmask.any():
+                b[nanmask] = len(q.borders[f]) if q.nan_is_max[f] else 0
+            bins[:, f] = b
+        state = dict(bins=bins, borders=[np.asarray(b, dtype=np.float32) for b in q.borders],
+                     nan_is_max=np.asarray(q.nan_is_max), has_nan=np.asarray(q.has_nan), border_type=q.border_type,
+                     nan_mode=q.nan_mode, cat_hashes=self.cat_hashes, label=self.label, weight=self.weight,
+                     group_id=self.group_id, subgroup_id=None if self.subgroup_id is None or self.subgroup_id.dtype.kind not in "iuf" else self.subgroup_id,
+                     group_weight=self.group_weight, baseline=self.baseline, pairs=self.pairs, pairs_weight=self.pairs_weight,
+                     feature_names=list(self.feature_names), n_features=int(self.n_features),
+                     float_feature_indices=list(self.float_feature_indices), cat_feature_indices=list(self.cat_feature_indices))
+        with open(fname, "wb") as fh:
+            fh.write(self._QUANTIZED_LABEL + plainser.dumps(state))
+
+    @classmethod
+    def load_quantized(cls, fname: str) -> "Pool":
+        """Read a file written by ``save``.  Every float value comes back as a representative of its bin (a point
+        strictly between the bin's borders), so quantising the pool again with the stored grid reproduces the stored
+        bins exactly and training sees the same data set; the grid is attached, so ``fit`` does not rebuild it."""
+        from ..utils import plainser
+        from .quantization import FeatureQuantization
+        with open(fname, "rb") as fh:
+            blob = fh.read()
+        if not blob.startswith(cls._QUANTIZED_LABEL):
+            raise CatBoostError(f"{fname} is not a quantized pool of this framework")
+        try:
+            st = plainser.loads(blob[len(cls._QUANTIZED_LABEL):])
+        except plainser.PlainDataError as e:
+            raise CatBoostError(f"{fname} is damaged: {e}") from e
+        bins = st["bins"]
+        n, F = bins.shape
+        X = np.empty((n, F), dtype=np.float32)
+        for f in range(F):
+            b = np.asarray(st["borders"][f], dtype=np.float32)
+            if len(b) == 0:
+                X[:, f] = 0.0
+                continue
+            # representatives: below the first border, between neighbours, above the last one
+            rep = np.empty(len(b) + 1, dtype=np.float32)
+            rep[0] = np.nextafter(b[0], np.float32(-np.inf))
+            rep[1:-1] = np.nextafter(b[:-1], np.float32(np.inf)) if len(b) > 1 else rep[1:-1]
+            rep[-1] = np.nextafter(b[-1], np.float32(np.inf))
+            X[:, f] = rep[np.minimum(bins[:, f], len(b))]
+        pool = cls.__new__(cls)
+        cat_idx, float_idx = list(st["cat_feature_indices"]), list(st["float_feature_indices"])
+        pool.__dict__.update(dict(
+            cat_feature_indices=cat_idx, float_feature_indices=float_idx, feature_names=list(st["feature_names"]),
+            n_features=int(st["n_features"]), text_feature_indices=[], embedding_feature_indices=[], text_data=[],
+            embedding_data=[], float_data=X, cat_hashes=st["cat_hashes"], cat_strings=[], _cat_distinct={},
+            label=st["label"], weight=st["weight"], group_weight=st["group_weight"], baseline=st["baseline"], timestamp=None,
+            group_id=st["group_id"], subgroup_id=st["subgroup_id"], pairs=st["pairs"], pairs_weight=st["pairs_weight"],
+            thread_count=-1))
+        pool._quantized = FeatureQuantization([np.asarray(b, dtype=np.float32) for b in st["borders"]],
+                                              np.asarray(st["nan_is_max"]), np.asarray(st["has_nan"]), st["border_type"],
+                                              st["nan_mode"])
+        return pool
+
     def save_quantization_borders(self, path: str):
         if self._quantized is None:
             raise CatBoostError("pool is not quantized")
@@ -594,7 +672,10 @@ class Pool:
                     fh.write(f"{f}\t{float(v):.9g}\n")
 
     def save(self, fname: str):
-        """Write the pool as a tab-separated file with the label in column 0 (plus ``fname + '.cd'``)."""
+        """A quantized pool is written in the binary quantized form (read back with ``Pool("quantized://" + fname)``);
+        a raw pool as a tab-separated file with the label in column 0 (plus ``fname + '.cd'``)."""
+        if self._quantized is not None:
+            return self._save_quantized(fname)
         n = self.num_row()
         feats = self.get_features().astype(object)
         for j, c in enumerate(self.cat_feature_indices):

@@ -471,7 +471,150 @@ def _pair_accuracy(a, y, w, p, c):
     return float(np.sum(pw * (a[pr[:, 0], 0] > a[pr[:, 1], 0])) / pw.sum())
 
 
+# ---- further metrics of the reference (catboost/libs/metrics/metric.cpp) -------------------------------------------
+def _rmspe(a, y, w, p, c):
+    yy = np.asarray(y, dtype=np.float64)
+    return float(math.sqrt(np.sum(w * ((yy - a[:, 0]) / np.maximum(np.abs(yy), 1e-300)) ** 2) / w.sum()))
+
+
+def _focal(a, y, w, p, c):
+    alpha, gamma = float(p.get("focal_alpha", 0.25)), float(p.get("focal_gamma", 2.0))
+    pr = np.clip(_sigmoid(a[:, 0]), 1e-15, 1 - 1e-15)
+    yy = np.asarray(y, dtype=np.float64)
+    pt = np.where(yy > 0.5, pr, 1 - pr)
+    at = np.where(yy > 0.5, alpha, 1 - alpha)
+    return float(np.sum(w * (-at * (1 - pt) ** gamma * np.log(pt))) / w.sum())
+
+
+def _f_beta(a, y, w, p, c):
+    beta = float(p.get("beta", 1.0))
+    tp, fp, fn, _ = _bin_counts(a, y, w, p)
+    den = (1 + beta * beta) * tp + beta * beta * fn + fp
+    return float((1 + beta * beta) * tp / den) if den > 0 else 0.0
+
+
+def _wkappa(a, y, w, p, c):
+    pred = _classes(a)
+    yy = np.asarray(y).astype(np.int64)
+    k = int(max(pred.max(), yy.max())) + 1 if len(yy) else 1
+    conf = np.zeros((k, k))
+    np.add.at(conf, (yy, pred), w)
+    n = conf.sum()
+    ii, jj = np.meshgrid(np.arange(k), np.arange(k), indexing="ij")
+    wt = ((ii - jj) ** 2) / max((k - 1) ** 2, 1)
+    exp = np.outer(conf.sum(1), conf.sum(0)) / max(n, 1e-300)
+    den = (wt * exp).sum()
+    return float(1.0 - (wt * conf).sum() / den) if den > 0 else 0.0
+
+
+def _loglik_of_prediction(a, y, w, p, c):
+    # log-likelihood of the labels under the predicted probabilities relative to the prior (base 2), per document
+    yy = np.asarray(y, dtype=np.float64)
+    pr = np.clip(_sigmoid(a[:, 0]), 1e-15, 1 - 1e-15)
+    prior = np.clip(np.sum(w * yy) / w.sum(), 1e-15, 1 - 1e-15)
+    ll = yy * np.log2(pr / prior) + (1 - yy) * np.log2((1 - pr) / (1 - prior))
+    return float(np.sum(w * ll) / w.sum())
+
+
+def _prauc(a, y, w, p, c):
+    yy = np.asarray(y, dtype=np.float64) > 0.5
+    order = np.argsort(-a[:, 0], kind="stable")
+    ws, ys = w[order], yy[order]
+    tp = np.cumsum(ws * ys)
+    fp = np.cumsum(ws * ~ys)
+    # one point per distinct score
+    sc = a[order, 0]
+    last = np.r_[sc[1:] != sc[:-1], True]
+    tp, fp = tp[last], fp[last]
+    pos = tp[-1] if len(tp) else 0.0
+    if pos <= 0:
+        return 0.0
+    prec = tp / np.maximum(tp + fp, 1e-300)
+    rec = tp / pos
+    prev_r = np.r_[0.0, rec[:-1]]
+    prev_p = np.r_[1.0, prec[:-1]]
+    return float(np.sum((rec - prev_r) * 0.5 * (prec + prev_p)))
+
+
+def _query_average(a, y, w, p, c):
+    top = int(p.get("top", 10 ** 9))
+    off = _groups(c, len(y))
+    vals = []
+    for s, e in zip(off[:-1], off[1:]):
+        order = np.argsort(-a[s:e, 0], kind="stable")[:top]
+        vals.append(float(np.mean(np.asarray(y[s:e], dtype=np.float64)[order])) if len(order) else 0.0)
+    return float(np.mean(vals)) if vals else 0.0
+
+
+def _filtered_dcg(a, y, w, p, c):
+    # DCG over the documents the model keeps (approx > 0), in their stored order inside the query
+    exp_num = str(p.get("type", "Base")) == "Exp"
+    log_den = str(p.get("denominator", "Position")) != "Position" or True
+    off = _groups(c, len(y))
+    tot = 0.0
+    for s, e in zip(off[:-1], off[1:]):
+        keep = a[s:e, 0] > 0
+        rel = np.asarray(y[s:e], dtype=np.float64)[keep]
+        gain = (2.0 ** rel - 1.0) if exp_num else rel
+        pos = np.arange(1, len(rel) + 1)
+        tot += float(np.sum(gain / (np.log2(pos + 1.0) if str(p.get("denominator", "LogPosition")) == "LogPosition" else pos)))
+    return tot / max(len(off) - 1, 1)
+
+
+def _err(a, y, w, p, c):
+    top = int(p.get("top", 10 ** 9))
+    off = _groups(c, len(y))
+    vals = []
+    for s, e in zip(off[:-1], off[1:]):
+        order = np.argsort(-a[s:e, 0], kind="stable")[:top]
+        rel = np.clip(np.asarray(y[s:e], dtype=np.float64)[order], 0.0, 1.0)
+        look, v = 1.0, 0.0
+        for k, r in enumerate(rel):
+            v += look * r / (k + 1)
+            look *= (1 - r)
+        vals.append(v)
+    return float(np.mean(vals)) if vals else 0.0
+
+
+def _multirmse_missing(a, y, w, p, c):
+    yy = np.asarray(y, dtype=np.float64).reshape(a.shape[0], -1)
+    ok = ~np.isnan(yy)
+    d = np.where(ok, yy - a[:, : yy.shape[1]], 0.0)
+    tot = 0.0
+    for k in range(yy.shape[1]):
+        wk = w * ok[:, k]
+        tot += np.sum(wk * d[:, k] ** 2) / max(wk.sum(), 1e-300)
+    return float(math.sqrt(tot))
+
+
+def _cox(a, y, w, p, c):
+    # negative partial log-likelihood; |y| = time, y > 0 = event observed, y < 0 = censored (the reference's convention)
+    yy = np.asarray(y, dtype=np.float64)
+    t = np.abs(yy)
+    order = np.argsort(-t, kind="stable")
+    f = a[order, 0]
+    m = f.max() if len(f) else 0.0
+    lse = m + np.log(np.cumsum(np.exp(f - m)))            # log sum over the risk set (times >= t_i)
+    ev = yy[order] > 0
+    return float(-np.sum((f - lse)[ev]))
+
+
+def _multi_quantile(a, y, w, p, c):
+    alphas = [float(x) for x in str(p.get("alpha", "0.5")).split(",")]
+    yy = np.asarray(y, dtype=np.float64)
+    tot = 0.0
+    for k, al in enumerate(alphas[: a.shape[1]]):
+        d = yy - a[:, k]
+        tot += np.sum(w * np.where(d >= 0, al * d, (al - 1) * d))
+    return float(tot / (w.sum() * max(len(alphas), 1)))
+
+
 _METRICS: Dict[str, tuple] = {
+    "RMSPE": (_rmspe, False, ""), "Focal": (_focal, False, ""), "F": (_f_beta, True, ""), "WKappa": (_wkappa, True, ""),
+    "LogLikelihoodOfPrediction": (_loglik_of_prediction, True, ""), "PRAUC": (_prauc, True, ""),
+    "QueryAverage": (_query_average, True, "group"), "FilteredDCG": (_filtered_dcg, True, "group"),
+    "ERR": (_err, True, "group"), "MultiRMSEWithMissingValues": (_multirmse_missing, False, ""),
+    "Cox": (_cox, False, ""), "MultiQuantile": (_multi_quantile, False, ""),
     # name: (fn, is_max_optimal, needs)
     "RMSE": (_rmse, False, ""), "MAE": (_mae, False, ""), "MAPE": (_mape, False, ""), "SMAPE": (_smape, False, ""),
     "MSLE": (_msle, False, ""), "R2": (_r2, True, ""), "MedianAbsoluteError": (_median_abs, False, ""),

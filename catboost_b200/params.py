@@ -288,7 +288,7 @@ def resolve_options(params: Optional[dict], default_loss: str = "RMSE", n_rows: 
         o.boost_from_average = lname in ("RMSE", "Logloss", "CrossEntropy", "Quantile", "MAE", "MAPE", "MultiRMSE")
     if o.use_best_model is None:
         o.use_best_model = bool(has_eval)
-    if o.od_type not in ("IncToDec", "Iter"):
+    if o.od_type not in ("IncToDec", "Iter", "Wilcoxon"):
         raise CatBoostError(f"unknown od_type {o.od_type!r}")
     if o.eval_metric is None:
         o.eval_metric = default_eval_metric(loss)

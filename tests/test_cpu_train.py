@@ -118,3 +118,33 @@ def test_border_selection_native():
     b, _ = select_borders(X[:, :1], 15, "GreedyLogSum")
     q = np.searchsorted(np.sort(X[:, 0]), b[0]) / 5000
     assert np.all(np.abs(np.diff(q) - 1 / 16) < 0.02)
+
+
+def test_overfitting_detectors_follow_the_reference_statistics():
+    from catboost_b200.utils.overfit import OverfittingDetector, wilcoxon_signed_rank_pvalue
+    # Iter: stops od_wait iterations after the best value
+    od = OverfittingDetector("Iter", wait=3, max_optimal=False)
+    stops = [od.add(v) for v in [1.0, 0.9, 0.8, 0.85, 0.86, 0.87, 0.88]]
+    assert stops == [False, False, False, False, False, True, True] and od.best_iter == 2
+    # IncToDec: a metric that rose by 1.0 and then loses 0.5 over a long stretch has ratio about 2 * 0.99^k ...
+    od = OverfittingDetector("IncToDec", wait=5, pval=0.9, max_optimal=True)
+    seq = [0.0, 0.5, 1.0] + [1.0 - 0.02 * k for k in range(1, 40)]
+    fired = [od.add(v) for v in seq]
+    assert not any(fired[:8]) and any(fired)
+    k = fired.index(True)
+    assert od.best_iter == 2 and k >= 8
+    od = OverfittingDetector("IncToDec", wait=5, pval=0.9, max_optimal=True)
+    for v in seq[: k + 1]:
+        od.add(v)
+    assert od.stopped and od.cur_pval < 0.9
+    # hand check of the statistic at the first stop: p = exp(-0.5 / (expected_inc / drop))
+    import math
+    drop = 1.0 - seq[k]
+    assert abs(od.cur_pval - math.exp(-0.5 / (od.expected_inc / drop))) < 1e-12
+    # Wilcoxon: all deteriorations positive -> small p; mixed signs -> large p
+    assert wilcoxon_signed_rank_pvalue([0.1] * 12) < 0.01
+    assert wilcoxon_signed_rank_pvalue([0.1, -0.1] * 6) > 0.5
+    od = OverfittingDetector("Wilcoxon", wait=6, pval=0.05, max_optimal=False)
+    vals = [1.0, 0.5] + [0.5 + 0.01 * k for k in range(1, 15)]
+    fired = [od.add(v) for v in vals]
+    assert any(fired) and not any(fired[:7])

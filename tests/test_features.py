@@ -979,3 +979,83 @@ def test_cli_run_worker_and_model_based_eval(tmp_path):
     assert len(rep) == 2 and rep[0]["features"] == [0]
     # the informative feature matters (lower Logloss with it), the noise features hardly do
     assert rep[0]["delta"] < -0.01 and abs(rep[1]["delta"]) < abs(rep[0]["delta"])
+
+
+def test_diff_tools_and_model_comparator(tmp_path):
+    """Tolerant comparison of delimiter-separated files, JSON, numpy files and models, and the apply-speed tool."""
+    import json
+    from catboost_b200 import difftools as dt
+    a, b = tmp_path / "a.tsv", tmp_path / "b.tsv"
+    a.write_text("id\tv\nx\t1.000000\ny\t2.5\n")
+    b.write_text("id\tv\nx\t1.000001\ny\t2.5\n")
+    assert dt.dsv_diff(str(a), str(b), diff_limit=0.0, have_header=True)
+    assert not dt.dsv_diff(str(a), str(b), diff_limit=1e-5, have_header=True)
+    assert not dt.json_diff({"a": [1.0, {"b": 2}], "t": "x"}, {"a": [1.0 + 1e-9, {"b": 2}], "t": "x"}, 1e-6)
+    assert dt.json_diff({"a": 1}, {"a": 1, "c": 2}, 1e-6) and not dt.json_diff({"a": 1}, {"a": 1, "c": 2}, 0, ignore_keys=("c",))
+    np.save(tmp_path / "x.npy", np.arange(6.0).reshape(2, 3))
+    np.save(tmp_path / "y.npy", np.arange(6.0).reshape(2, 3) + 1e-9)
+    assert not dt.numpy_diff(str(tmp_path / "x.npy"), str(tmp_path / "y.npy"), 1e-6)
+    assert dt.numpy_diff(str(tmp_path / "x.npy"), str(tmp_path / "y.npy"), 0.0)
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((600, 4)).astype(np.float32)
+    y = (X[:, 0] > 0).astype(int)
+    m1 = cb.CatBoostClassifier(iterations=6, depth=3, verbose=False, allow_writing_files=False, random_seed=1).fit(X, y)
+    m2 = cb.CatBoostClassifier(iterations=6, depth=3, verbose=False, allow_writing_files=False, random_seed=1).fit(X, y)
+    m3 = cb.CatBoostClassifier(iterations=6, depth=3, verbose=False, allow_writing_files=False, random_seed=2,
+                               learning_rate=0.5).fit(X, y)
+    assert not dt.compare_models(m1._model, m2._model, 1e-9)
+    assert dt.compare_models(m1._model, m3._model, 1e-9)
+    p1, p3 = tmp_path / "m1.cbm", tmp_path / "m3.cbm"
+    m1.save_model(str(p1)); m3.save_model(str(p3))
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "catboost_b200", "compare-models", str(p1), str(p1)], capture_output=True, text=True, env=env)
+    assert r.returncode == 0 and "EQUAL" in r.stdout
+    r = subprocess.run([sys.executable, "-m", "catboost_b200", "compare-models", str(p1), str(p3)], capture_output=True, text=True, env=env)
+    assert r.returncode == 1 and "DIFFER" in r.stdout
+    perf = dt.model_perftest(m1, rows=2000, repeats=1)
+    assert perf["rows_per_second"] > 0 and perf["trees"] == 6
+
+
+def test_additional_metrics_against_independent_implementations():
+    from sklearn.metrics import average_precision_score, cohen_kappa_score, fbeta_score
+    from catboost_b200.metrics import make_metric
+    rng = np.random.default_rng(0)
+    n = 800
+    a = rng.standard_normal(n)
+    y = (a + rng.standard_normal(n) > 0).astype(float)
+    pred = (a > 0).astype(int)
+    assert abs(make_metric("F:beta=2").eval(a, y) - fbeta_score(y, pred, beta=2)) < 1e-12
+    assert abs(make_metric("WKappa").eval(a, y) - cohen_kappa_score(y.astype(int), pred, weights="quadratic")) < 1e-12
+    assert abs(make_metric("PRAUC").eval(a, y) - average_precision_score(y, a)) < 0.01
+    yy = np.abs(rng.standard_normal(n)) + 0.5
+    assert abs(make_metric("RMSPE").eval(a, yy) - np.sqrt(np.mean(((yy - a) / yy) ** 2))) < 1e-12
+    p = 1 / (1 + np.exp(-a))
+    pt = np.where(y > 0.5, p, 1 - p)
+    at = np.where(y > 0.5, 0.25, 0.75)
+    assert abs(make_metric("Focal").eval(a, y) - np.mean(-at * (1 - pt) ** 2 * np.log(pt))) < 1e-12
+    off = np.arange(0, n + 1, 8)
+    assert 0.0 <= make_metric("ERR").eval(a, np.clip(y, 0, 1), group_offsets=off) <= 1.0
+    assert make_metric("QueryAverage:top=2").eval(a, y, group_offsets=off) >= make_metric("QueryAverage:top=8").eval(a, y, group_offsets=off) - 1e-9
+    # Cox: shifting all scores by a constant leaves the partial likelihood unchanged
+    t = np.where(rng.random(n) < 0.7, 1, -1) * (rng.random(n) + 0.1)
+    assert abs(make_metric("Cox").eval(a, t) - make_metric("Cox").eval(a + 3.0, t)) < 1e-6
+
+
+def test_quantized_pool_file_round_trip(tmp_path):
+    """A quantized pool written to disk (one byte per value + the border grids) trains the same model as the original."""
+    rng = np.random.default_rng(5)
+    X = rng.standard_normal((3000, 24)).astype(np.float32)
+    X[rng.random(X.shape) < 0.03] = np.nan
+    y = (np.nan_to_num(X[:, 0]) + np.nan_to_num(X[:, 1]) ** 2 > 0.5).astype(int)
+    pool = cb.Pool(X, y)
+    pool.quantize(border_count=32)
+    path = str(tmp_path / "pool.bin")
+    pool.save(path)
+    assert os.path.getsize(path) < X.nbytes // 2                # a byte per value, not a float
+    back = cb.Pool("quantized://" + path)
+    assert back.is_quantized() and back.num_row() == 3000
+    kw = dict(iterations=15, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False, border_count=32)
+    a = cb.CatBoostClassifier(**kw).fit(pool)
+    b = cb.CatBoostClassifier(**kw).fit(back)
+    assert [(s.feature, s.border) for s in a._model.splits] == [(s.feature, s.border) for s in b._model.splits]
+    assert np.allclose(a.predict(X, prediction_type="RawFormulaVal"), b.predict(X, prediction_type="RawFormulaVal"))
