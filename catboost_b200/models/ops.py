@@ -49,3 +49,42 @@ def sum_models(models, weights=None, ctr_merge_policy="IntersectingCountersAvera
                 out.trees.append(NonSymmetricTree(so, t.left, t.right, t.leaf_of_node, t.leaf_values * (w * m.scale),
                                                   t.leaf_weights))
     return out
+
+
+def carry_model(model: Model, float_values: dict) -> Model:
+    """A copy of ``model`` with some float features fixed to given values (the reference's ``CarryModel``,
+    catboost/libs/carry_model/carry.h): every split on a carried feature has a known outcome, so symmetric trees lose
+    those levels (their leaves are the matching half of the old ones) and the model no longer reads the feature --
+    whatever value the data holds for it.  ``float_values``: {float feature index: value}.  Oblivious trees only."""
+    out = model.copy()
+    for key in ("_split_cache", "_packed", "_gpu_predictor", "_gpu_predictor_multi"):
+        out.__dict__.pop(key, None)
+    carried = {int(k): float(v) for k, v in float_values.items()}
+    new_trees = []
+    for t in model.trees:
+        if not isinstance(t, ObliviousTree):
+            raise CatBoostError("carry_model supports symmetric (oblivious) trees")
+        keep_levels, fixed_bits = [], 0
+        for level, s in enumerate(t.splits):
+            sp = model.splits[s]
+            if sp.kind == "float" and sp.feature in carried:
+                v = carried[sp.feature]
+                goes_right = (not np.isnan(v)) and v > sp.border
+                if np.isnan(v):
+                    ff = model.float_features[sp.feature]
+                    goes_right = str(getattr(ff, "nan_mode", "Min")) == "Max"
+                fixed_bits |= (1 if goes_right else 0) << level
+            else:
+                keep_levels.append(level)
+        n_new = 1 << len(keep_levels)
+        idx = np.zeros(n_new, dtype=np.int64)
+        for j in range(n_new):
+            old = fixed_bits
+            for k, level in enumerate(keep_levels):
+                old |= ((j >> k) & 1) << level
+            idx[j] = old
+        vals = np.asarray(t.leaf_values)[idx]
+        wts = np.asarray(t.leaf_weights)[idx] if len(t.leaf_weights) else np.zeros(n_new)
+        new_trees.append(ObliviousTree([t.splits[level] for level in keep_levels], vals, wts))
+    out.trees = new_trees
+    return out

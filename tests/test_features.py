@@ -1059,3 +1059,19 @@ def test_quantized_pool_file_round_trip(tmp_path):
     b = cb.CatBoostClassifier(**kw).fit(back)
     assert [(s.feature, s.border) for s in a._model.splits] == [(s.feature, s.border) for s in b._model.splits]
     assert np.allclose(a.predict(X, prediction_type="RawFormulaVal"), b.predict(X, prediction_type="RawFormulaVal"))
+
+
+def test_carry_model_fixes_features():
+    from catboost_b200.models.ops import carry_model
+    rng = np.random.default_rng(2)
+    X = rng.standard_normal((1500, 5)).astype(np.float32)
+    y = X[:, 0] + X[:, 1] * X[:, 2] + 0.1 * rng.standard_normal(1500)
+    m = cb.CatBoostRegressor(iterations=20, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False).fit(X, y)
+    carried = carry_model(m._model, {1: 0.7, 4: -0.2})
+    Xf = X.copy()
+    Xf[:, 1], Xf[:, 4] = 0.7, -0.2
+    ref = m._model.predict_raw(Xf)
+    Xg = X.copy()
+    Xg[:, 1], Xg[:, 4] = rng.standard_normal(1500), 99.0          # the carried model ignores these columns
+    assert np.allclose(carried.predict_raw(Xg), ref)
+    assert sum(len(t.splits) for t in carried.trees) < sum(len(t.splits) for t in m._model.trees)
