@@ -146,10 +146,13 @@ def bench_ranking(args, cfg, rank, world, dev):
     model = cb.CatBoostRanker(loss_function="YetiRank", iterations=iters, depth=cfg["depth"], border_count=cfg["border_count"],
                               learning_rate=0.1, task_type="GPU", random_seed=0, allow_writing_files=False, verbose=False)
     torch.cuda.synchronize(dev)
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
     t0 = time.perf_counter()
     model.fit(X, rel, group_id=gid)
     torch.cuda.synchronize(dev)
     fit_s = time.perf_counter() - t0
+    clocks = sampler.stop()
     tm = model._train_info.get("timings", {})
     it_s = float(tm.get("iterations", float("nan")))
     # batch apply of the trained model: rows already on the device (kernel throughput) and rows from host memory
@@ -193,7 +196,7 @@ def bench_ranking(args, cfg, rank, world, dev):
                                      "parallelism": f"doc-parallel dp{world}", "depth": cfg["depth"], "group_size": "uniform 5..200"},
                           "e2e": {"value": fit_s / iters * 1000.0, "unit": "s/1000iter", "fit_seconds": fit_s,
                                   "fit_breakdown_s": {k: round(float(v), 4) for k, v in tm.items()}},
-                          "ndcg_first_last": [float(ndcg[0]), float(ndcg[-1])], "apply": apply,
+                          "clocks": clocks, "ndcg_first_last": [float(ndcg[0]), float(ndcg[-1])], "apply": apply,
                           "gpu_launches": int(model._train_info.get("launches_per_iter", 0)) * iters}))
     return 0
 
@@ -208,10 +211,13 @@ def bench_criteo(args, cfg, rank, world, dev):
                                   learning_rate=0.1, task_type="GPU", random_seed=0, allow_writing_files=False,
                                   max_ctr_complexity=int(args.ctr_complexity), verbose=False)
     torch.cuda.synchronize(dev)
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
     t0 = time.perf_counter()
     model.fit(df, y, cat_features=cats)
     torch.cuda.synchronize(dev)
     fit_s = time.perf_counter() - t0
+    clocks = sampler.stop()
     tm = model._train_info.get("timings", {})
     it_s = float(tm.get("iterations", float("nan")))
     if rank == 0:
@@ -226,7 +232,8 @@ def bench_criteo(args, cfg, rank, world, dev):
                                                   "cardinalities log-uniform in [10, 1e6], ~25% positives"},
                           "e2e": {"value": fit_s / iters * 1000.0, "unit": "s/1000iter", "fit_seconds": fit_s,
                                   "fit_breakdown_s": {k: round(float(v), 4) for k, v in tm.items()}},
-                          "features_in_store": model._train_info.get("h2d_bytes")}))
+                          "clocks": clocks, "features_in_store": model._train_info.get("h2d_bytes"),
+                          "gpu_launches": int(model._train_info.get("launches_per_iter", 0)) * iters}))
     return 0
 
 

@@ -539,7 +539,7 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
 // Every lane takes V consecutive documents per step (V = 1 for wide bundles, 2 otherwise, vector loads); the loads of
 // the next step are issued before the current step is processed.  Measured alone on 10.5M x 28, level 3, all 7 groups
 // in one bundle: loads 95 us, compaction 11 us, atomics 70 us (4.2e12 shared atomics/s, close to one per bank and clock).
-// sh layout: int tile[slot][group][j][B][C][statistic], then uint32 ring[warp][3 + gcnt][CB_RING] (word-major, so
+// sh layout: int tile[slot][group][statistic][j][B][C], then uint32 ring[warp][3 + gcnt][CB_RING] (word-major, so
 // that lanes touch consecutive banks).
 #ifndef CB_BUNDLE_V
 #define CB_BUNDLE_V(GMAX) ((GMAX) > 4 ? 1 : 2)     // documents per lane and step: bounded by the 64-register budget
@@ -547,22 +547,23 @@ static __device__ void cb_hist_item_q2(const CbHistArgs& a, int* sh, int g, long
 #ifndef CB_BUNDLE_PF
 #define CB_BUNDLE_PF 1       // 1 = keep the next step's loads in registers while the current step is processed
 #endif
-// One reduction into shared memory through a 32-bit shared-window address with an immediate byte offset: no 64-bit
-// pointer arithmetic and no second address for the neighbouring statistic.
-template <int OFF>
+// One reduction into shared memory through a 32-bit shared-window address: no 64-bit pointer arithmetic.
 __device__ __forceinline__ void cb_red_shared(unsigned int addr, int v) {
-    asm volatile("red.shared.add.s32 [%0+%1], %2;" ::"r"(addr), "n"(OFF), "r"(v) : "memory");
+    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
-// Tile layout of the bundled path: int tile[slot][group][j][B][C][2] -- the two statistics of a cell are neighbours, so
-// one address serves both reductions.  sbase = shared-window address of the tile; cst4 = bytes per bin (8 C),
-// fst4 = bytes per feature (B * 8 C), gst4 = bytes per group (4 B * 8 C).
+// Tile layout of the bundled path: int tile[slot][group][statistic][j][B][C].  sbase = shared-window address of the
+// tile; cst4 = bytes per bin (4 C), fst4 = bytes per feature (B * 4 C), sst4 = bytes between the two statistics of a
+// cell (4 features), gst4 = bytes per group.  (Keeping the two statistics of a cell next to each other would save the
+// second address but halves the banks one reduction can spread over: measured 357 us against 281 us at level 0 of
+// 10.5M x 28.)
 template <int GMAX, bool SKIP>
 __device__ __forceinline__ void cb_hist_bundle_drain(unsigned int sbase, const unsigned int* ring, int e, int gcnt,
                                                      unsigned int gst4, unsigned int fst4, unsigned int cst4, int copy,
                                                      const unsigned int* sdom, int* tot, int lane) {
     const unsigned int head_word = ring[e];          // SKIP: slot << 20 | tile offset (ints) of the slot; else the offset
-    unsigned int ag = sbase + (((SKIP ? (head_word & 0xFFFFFu) : head_word) + 2u * (unsigned int)copy) << 2);
+    unsigned int ag = sbase + (((SKIP ? (head_word & 0xFFFFFu) : head_word) + (unsigned int)copy) << 2);
+    const unsigned int sst4 = gst4 >> 1;
     const int q0 = (int)ring[CB_RING + e], q1 = (int)ring[2 * CB_RING + e];
     if (SKIP) {
         int* t = tot + (int)(head_word >> 20) * 64 + lane;
@@ -579,8 +580,8 @@ __device__ __forceinline__ void cb_hist_bundle_drain(unsigned int sbase, const u
             for (int j = 0; j < 4; ++j) {
                 if (!(SKIP && ((eq >> (8 * j)) & 1u))) {
                     const unsigned int addr = af + ((w >> (8 * j)) & 255u) * cst4;
-                    cb_red_shared<0>(addr, q0);
-                    cb_red_shared<4>(addr, q1);
+                    cb_red_shared(addr, q0);
+                    cb_red_shared(addr + sst4, q1);
                 }
                 af += fst4;
             }
@@ -653,7 +654,7 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
     const unsigned int pmask = (unsigned int)(nslots - 1);
     const int copy = lane & (C - 1);
     const unsigned int sbase = (unsigned int)__cvta_generic_to_shared(sh);
-    const unsigned int cst4 = 8u << cs, fst4 = (unsigned int)B * cst4, gst4 = 4u * fst4;
+    const unsigned int cst4 = 4u << cs, fst4 = (unsigned int)B * cst4, gst4 = 8u * fst4;
     const long long d_end = a.d.n;
     const long long blk = (long long)blockDim.x * V;
     float qmax = 8388607.0f;
@@ -772,10 +773,9 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
             const int sj = row & 7, gl = (row >> 3) % gcnt, slot = (row >> 3) / gcnt;
             const unsigned int dbin = (s_dom[gl] >> (8 * (sj & 3))) & 255u;
             if (dbin == 255u) continue;
-            const int st = sj >> 2;
-            const int* src = sh + (size_t)slot * slot_stride + gl * gstride + (((sj & 3) * B) << (cs + 1)) + st;
+            const int* src = sh + (size_t)slot * slot_stride + gl * gstride + (((sj >> 2) * 4 + (sj & 3)) * B << cs);
             long long part = 0;
-            for (int i = lane; i < B * C; i += 32) part += src[2 * i];
+            for (int i = lane; i < B * C; i += 32) part += src[i];
             long long t = tot[slot * 64 + (sj >> 2) * 32 + lane];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
@@ -784,7 +784,7 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
             }
             const long long rest = t - part;
             if (lane < C) {
-                int* cell = const_cast<int*>(src) + 2 * (((int)dbin << cs) + lane);
+                int* cell = const_cast<int*>(src) + ((int)dbin << cs) + lane;
                 *cell = (int)(rest / C) + (lane == 0 ? (int)(rest % C) : 0);
             }
         }
@@ -802,11 +802,11 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
         r >>= 3;
         const int gl = r % gcnt;
         const int slot = r / gcnt;
-        const int* src = sh + ((((size_t)(slot * gcnt + gl) * 4 + (sj & 3)) * B + b4 * 4) * C) * 2 + (sj >> 2);
+        const int* src = sh + (((size_t)(slot * gcnt + gl) * 8 + sj) * B + b4 * 4) * C;
         long long q4[4] = {0, 0, 0, 0};          // the replicas together may exceed 32 bits
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-            for (int cc = 0; cc < C; ++cc) q4[q] += src[2 * (q * C + cc)];
+            for (int cc = 0; cc < C; ++cc) q4[q] += src[q * C + cc];
         const float inv = (sj & 4) ? inv1 : inv0;
         float* dst = a.priv + (((size_t)chunk * a.d.G + g0 + gl) * nslots + slot_begin + slot) * (size_t)(8 * B)
                      + sj * B + b4 * 4;
