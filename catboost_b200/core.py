@@ -128,6 +128,22 @@ class CatBoost:
                                            feature_names=train_pool.feature_names))
                 else:
                     raise CatBoostError("eval_set must be a Pool, an (X, y) tuple or a list of them")
+        frac = params.get("eval_fraction")
+        if frac is not None and float(frac) > 0 and not eval_pools:
+            # the last part of the learn set becomes the evaluation set (whole queries when there are groups), as in
+            # catboost/libs/train_lib (eval_fraction)
+            from .parallel.launcher import shard_bounds
+            n_all = train_pool.num_row()
+            if not 0.0 < float(frac) < 1.0:
+                raise CatBoostError("eval_fraction must be in (0, 1)")
+            cut = int(round(n_all * (1.0 - float(frac))))
+            if train_pool.group_id is not None:
+                off = train_pool.group_offsets()
+                cut = int(off[np.searchsorted(off, cut)]) if cut < n_all else n_all
+            if cut <= 0 or cut >= n_all:
+                raise CatBoostError("eval_fraction leaves the learn or the evaluation part empty")
+            eval_pools = [train_pool.slice(np.arange(cut, n_all))]
+            train_pool = train_pool.slice(np.arange(0, cut))
         init = None
         if init_model is not None:
             init = init_model._model if isinstance(init_model, CatBoost) else init_model

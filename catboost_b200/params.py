@@ -57,6 +57,19 @@ CPU_ONLY = {"rsm", "sampling_frequency", "approx_on_full_history", "model_shrink
             "langevin", "diffusion_temperature", "posterior_sampling", "monotone_constraints", "dev_efb_max_buckets",
             "sparse_features_conflict_fraction", "random_score_type"}
 
+# Options that only steer how much memory or which internal block sizes the reference uses: accepted for script
+# compatibility, they have no counterpart here and change no result.
+RESOURCE_HINTS = {"used_ram_limit", "gpu_ram_part", "pinned_memory_size", "device_config", "gpu_cat_features_storage",
+                  "data_partition", "node_type", "dev_score_calc_obj_block_size", "dev_efb_max_buckets",
+                  "observations_to_bootstrap", "fused_levels", "model_size_reg"}
+# Options of the reference whose behaviour is not implemented: a value that differs from the default is refused with an
+# error instead of being silently dropped.
+NOT_IMPLEMENTED = {"counter_calc_method", "ctr_leaf_count_limit", "store_all_simple_ctr", "final_ctr_computation_mode",
+                   "per_feature_ctr", "ctr_description", "ctr_history_unit", "approx_on_full_history", "sampling_frequency",
+                   "sampling_unit", "posterior_sampling", "penalties_coefficient", "first_feature_use_penalties",
+                   "per_object_feature_penalties", "fixed_binary_splits", "sparse_features_conflict_fraction",
+                   "tokenizers", "dictionaries"}
+
 POINTWISE_LOSSES = {"RMSE", "Logloss", "CrossEntropy", "Poisson", "MAE", "Quantile", "LogLinQuantile", "MAPE", "Huber",
                     "Lq", "Expectile", "Tweedie", "LogCosh"}
 MULTI_LOSSES = {"MultiClass", "MultiClassOneVsAll", "MultiLogloss", "MultiCrossEntropy", "MultiRMSE", "RMSEWithUncertainty"}
@@ -189,8 +202,11 @@ def resolve_options(params: Optional[dict], default_loss: str = "RMSE", n_rows: 
         raise CatBoostError(f"task_type must be 'CPU' or 'GPU', got {o.task_type!r}")
     o.task_type = task
     for k in user:
-        if task == "CPU" and k in GPU_ONLY and k not in ("devices",):
-            pass  # GPU-only knobs are ignored on CPU, like TGpuOnlyOption warns and continues
+        if k in NOT_IMPLEMENTED and user[k] is not None and user[k] != DEFAULTS.get(k):
+            raise CatBoostError(f"option {k}={user[k]!r} is not implemented in this framework (only its default "
+                                f"{DEFAULTS.get(k)!r} is accepted)")
+        # GPU-only knobs on CPU and the resource hints are accepted and change nothing (the reference's TGpuOnlyOption
+        # warns and continues)
     # loss
     loss = o.loss_function if o.loss_function is not None else default_loss
     lname, lparams = parse_loss(loss)

@@ -360,6 +360,12 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
     # ---- features --------------------------------------------------------------------------------------
     with prof.span("quantization"):
         plan = plan_features(o, train_pool, ctx, getattr(train_pool, "_quantized", None))
+        if o.output_borders and (ctx is None or ctx.rank == 0):
+            # the border grid that training uses, one "float_feature_index<TAB>border" line each (output_borders option)
+            with open(o.output_borders, "w") as fh:
+                for f, b in enumerate(plan.quant.borders):
+                    for v in b:
+                        fh.write(f"{f}\t{float(v):.9g}\n")
         fweights = None
         if o.feature_weights is not None:
             fw = o.feature_weights

@@ -148,3 +148,27 @@ def test_overfitting_detectors_follow_the_reference_statistics():
     vals = [1.0, 0.5] + [0.5 + 0.01 * k for k in range(1, 15)]
     fired = [od.add(v) for v in vals]
     assert any(fired) and not any(fired[:7])
+
+
+def test_option_handling_eval_fraction_output_borders_and_refusals(tmp_path):
+    import catboost_b200 as cb
+    rng = np.random.default_rng(1)
+    X = rng.standard_normal((1200, 4)).astype(np.float32)
+    y = (X[:, 0] > 0).astype(int)
+    borders = tmp_path / "borders.tsv"
+    m = cb.CatBoostClassifier(iterations=8, depth=3, verbose=False, allow_writing_files=False, eval_fraction=0.25,
+                              output_borders=str(borders), border_count=16)
+    m.fit(X, y)
+    ev = m.get_evals_result()
+    assert "validation" in ev and len(ev["validation"]["Logloss"]) == 8
+    lines = borders.read_text().strip().split("\n")
+    assert len(lines) == 4 * 16 and lines[0].split("\t")[0] == "0"
+    # borders written by one run can be fed to the next one
+    m2 = cb.CatBoostClassifier(iterations=8, depth=3, verbose=False, allow_writing_files=False, eval_fraction=0.25,
+                               input_borders=str(borders), border_count=16).fit(X, y)
+    assert np.allclose(m2.predict(X, prediction_type="RawFormulaVal"), m.predict(X, prediction_type="RawFormulaVal"))
+    # options without an implementation are refused when set to something else than their default, hints are accepted
+    with pytest.raises(cb.CatBoostError, match="not implemented"):
+        cb.CatBoostClassifier(iterations=2, sampling_unit="Group", verbose=False, allow_writing_files=False).fit(X, y)
+    cb.CatBoostClassifier(iterations=2, used_ram_limit="4gb", sampling_unit="Object", verbose=False,
+                          allow_writing_files=False).fit(X, y)

@@ -48,6 +48,11 @@ if mode == "cat":
     params.update(one_hot_max_size=2, max_ctr_complexity=1)
 elif mode == "ordered":
     params["boosting_type"] = "Ordered"
+elif mode.startswith("onefeature"):
+    # fewer features than ranks: some rank owns no histogram column at all
+    X = X[:, :1].copy()
+    y = (X[:, 0] + 0.3 * rng.standard_normal(n, dtype=np.float32) > 0).astype(np.float32)
+    params["histogram_reduce"] = mode.split(":")[1]
 elif mode != "default":
     params["histogram_reduce"] = mode
 m = cb.CatBoostClassifier(**params)
@@ -128,6 +133,24 @@ def test_two_gpus_fused_matches_nccl_baseline():
     assert fused["acc"] > 0.9 and base["acc"] > 0.9
     assert fused["splits"] == base["splits"]
     assert np.allclose(fused["pred"], base["pred"], rtol=1e-3, atol=1e-3)
+    # one feature on two ranks: rank 1 owns no column, scores nothing and still takes part in every exchange
+    f1 = _run(2, "nccl", "onefeature:fused", port=29621)
+    b1 = _run(2, "nccl", "onefeature:nccl", port=29623)
+    assert f1["acc"] > 0.85 and f1["splits"] == b1["splits"]
+    assert np.allclose(f1["pred"], b1["pred"], rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.gpu
+def test_four_gpus_fused_matches_nccl_baseline():
+    import torch
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    fused = _run(4, "nccl", "fused", port=29625)
+    base = _run(4, "nccl", "nccl", port=29627)
+    assert fused["acc"] > 0.9 and fused["splits"] == base["splits"]
+    assert np.allclose(fused["pred"], base["pred"], rtol=1e-3, atol=1e-3)
+    again = _run(4, "nccl", "fused", port=29629)
+    assert again["splits"] == fused["splits"] and np.allclose(again["pred"], fused["pred"], rtol=1e-5, atol=1e-5)
 
 
 FAIL_WORKER = r'''
