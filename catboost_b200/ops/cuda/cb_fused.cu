@@ -23,6 +23,8 @@
 #include "cb_comm.cuh"
 #include <cooperative_groups.h>
 #include <new>
+#include <vector>
+#include <algorithm>
 
 namespace cg = cooperative_groups;
 
@@ -81,8 +83,9 @@ static __device__ void cb_reduce_chunks(const CbFusedArgs& a, int cta, int ncta,
             const float* src = h.priv + ((size_t)slot * S + st) * 4 * B + (size_t)(f & 3) * B + bin
                                + (size_t)(f >> 2) * item_stride;
             const size_t kstride = (size_t)G * item_stride;
+            const int nKg = h.gchunks ? h.gchunks[f >> 2] : nK;       // chunks of this group's bundle
 #pragma unroll 4
-            for (int k = ks; k < nK; k += KS) {
+            for (int k = ks; k < nKg; k += KS) {
                 const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)k * kstride));
                 acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
             }
@@ -215,6 +218,7 @@ __global__ void __launch_bounds__(1024, 1) cb_level_fused_kernel(CbFusedArgs a) 
 }
 
 // ---- host side ---------------------------------------------------------------------------------------
+#define CB_MAX_LEVELS 16
 struct CbFusedPlan {
     CbFusedArgs a;
     int threads;
@@ -225,7 +229,15 @@ struct CbFusedPlan {
     int fuse_leaf_update;   // 1: let the bundled histogram pass apply the previous level's split (default)
     int max_copies;    // most replicas of a histogram cell (2 for dense columns; more when one bin dominates a column,
                        // where most lanes of a warp would otherwise add to the same cell)
+    std::vector<int> group_bins;     // padded bins of the widest feature of every group (empty: all groups take B)
+    // per level: bundle table and work list of the bundled path, on the device (made by cb_fused_geometry)
+    CbBundle* d_btab[CB_MAX_LEVELS];
+    int2* d_items[CB_MAX_LEVELS];
+    int* d_gchunks[CB_MAX_LEVELS];     // document chunks of every feature group (those of its bundle)
+    int n_btab[CB_MAX_LEVELS], n_items[CB_MAX_LEVELS];
+    int single_pass_bundle[CB_MAX_LEVELS];     // 1: one bundle holds every group in one pass (leaf update can be fused)
 };
+
 
 CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigned short* leaf, const float* stats, int S,
                                     int B, float* partial, float* const* local_slots, float* hbuf0, float* hbuf1,
@@ -259,7 +271,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     a.s.learning_rate = lr; a.s.best_key = best_key;
     a.leaf = leaf; a.splits = splits; a.depth = depth; a.mask_out = mask1; a.msg_local = msg_local;
     a.msg_stage = msg_stage; a.msg_stage_stride = msg_stage_stride; a.fuse_leaf = 0;
-    a.h.domw = nullptr;
+    a.h.domw = nullptr; a.h.btab = nullptr; a.h.bitems = nullptr; a.h.nbitems = 0; a.h.gchunks = nullptr;
     a.h.prev_splits = nullptr; a.h.prev_iter = iter_ptr; a.h.prev_depth = depth; a.h.leaf_rw = leaf;
     a.s.ll_epoch = R > 1 ? a.c.epoch + 1 : nullptr; a.s.ll_timeout_ns = a.c.timeout_ns; a.s.ll_status = a.c.status;
     p->threads = threads;
@@ -274,6 +286,7 @@ CB_API CbFusedPlan* cb_fused_create(const CbData* d, const CbComm* comm, unsigne
     cudaDeviceGetAttribute(&p->sm_smem, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
     p->sm_smem -= 2 * (int)fa.sharedSizeBytes;
     p->max_bundle = 0;
+    for (int l = 0; l < CB_MAX_LEVELS; ++l) { p->d_btab[l] = nullptr; p->d_items[l] = nullptr; p->d_gchunks[l] = nullptr; p->n_btab[l] = p->n_items[l] = 0; p->single_pass_bundle[l] = 0; }
     p->max_copies = 2;
     p->fuse_leaf_update = 1;
     if (cudaFuncSetAttribute(cb_level_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, p->max_smem) != cudaSuccess) {
@@ -299,7 +312,21 @@ CB_API void cb_fused_set_features(CbFusedPlan* p, int f_begin, int f_end) {
     p->a.s.f_end = f_end;
 }
 
-CB_API void cb_fused_destroy(CbFusedPlan* p) { delete p; }
+CB_API void cb_fused_destroy(CbFusedPlan* p) {
+    if (!p) return;
+    for (int l = 0; l < CB_MAX_LEVELS; ++l) {
+        if (p->d_btab[l]) cudaFree(p->d_btab[l]);
+        if (p->d_items[l]) cudaFree(p->d_items[l]);
+        if (p->d_gchunks[l]) cudaFree(p->d_gchunks[l]);
+    }
+    delete p;
+}
+
+// Padded number of bins (multiple of 4) of the widest feature of every feature group, host memory.  With it the
+// bundled path sizes the tile of a bundle by its own widest feature instead of the widest feature of the data set.
+CB_API void cb_fused_set_group_bins(CbFusedPlan* p, const int* group_bins, int G) {
+    p->group_bins.assign(group_bins, group_bins + G);
+}
 
 // Launch geometry of one level.  Returns the cooperative grid size (0 on error) and, through the pointers, the
 // slots per pass, dynamic shared memory, block size, document chunks per group and cell replicas.
@@ -314,36 +341,69 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
     const int G = p->a.h.d.G;
     const long long n = p->a.h.d.n;
     int thr = p->threads, spp = nslots, C = 1, gpc = 0, smem = 0;
+    std::vector<CbBundle> bundles;
     if (narrow && p->max_bundle > 0) {
-        // Bundled single-cell path: a block accumulates gpc groups at once.  Tile = slots * gpc * 8 * B * C ints, ring =
-        // warps * 64 * (3 + gpc) words.  Take the widest bundle that fits; then replicate the cells once if there is room.
-        const int cell = 8 * p->a.h.B * 4;                   // bytes per (slot, group)
-        const int gmax = G < p->max_bundle ? G : p->max_bundle;
+        // Bundled single-cell path: a block accumulates the groups of one bundle at once.  Tile of a bundle =
+        // slots * groups * 8 * B * C ints with B the padded bins of its widest feature, ring = warps * 64 * (3 + groups)
+        // words.  Consecutive groups of similar width (within a factor of two) form a run; a run is cut into the fewest
+        // bundles whose tiles hold every slot, evened out (7 groups as 4 + 3 rather than 5 + 2); when not even one group
+        // holds all slots the group takes several passes over the slots.  Then the cells are replicated while room is left.
+        // One 1024-thread block per SM: measured a few percent faster than two 512-thread blocks at every level (one
+        // tile instead of two leaves room for wider bundles and replicas) and it balances better.
         const bool skip = p->a.h.domw != nullptr;       // dominant-bin skipping: 256 bytes of slot totals per slot
-        auto ring_bytes = [](int t, int g) { return (t / 32) * 64 * (3 + g) * 4 + 16; };
-        auto fit = [&](int t, int budget, int slots) {
-            int g = 0;
-            while (g < gmax && slots * (g + 1) * cell + ring_bytes(t, g + 1) + (skip ? slots * 256 : 0) <= budget) ++g;
-            return g;
-        };
-        // one 1024-thread block per SM: measured a few percent faster than two 512-thread blocks at every level (one
-        // tile instead of two leaves room for wider bundles and replicas) and it balances better
-        int budget = p->max_smem;
+        const int budget = p->max_smem;
         thr = 1024;
-        gpc = fit(thr, budget, nslots);
-        if (gpc < 1) {
-            // even one group of all slots does not fit: several passes over the slots
-            gpc = 1;
-            spp = (budget - ring_bytes(thr, 1)) / (cell + (skip ? 256 : 0));
-            if (spp < 1) return 0;
-        }
-        // even out the bundles (7 groups as 4 + 3 rather than 5 + 2 changes nothing in passes but shrinks the tile)
-        const int nb = (G + gpc - 1) / gpc;
-        gpc = (G + nb - 1) / nb;
+        auto gb = [&](int g) { return p->group_bins.empty() ? p->a.h.B : p->group_bins[g]; };
+        auto need = [&](int slots, int gc, int Bb, int Cc) {
+            return slots * gc * 8 * Bb * 4 * Cc + (thr / 32) * 64 * (3 + gc) * 4 + 16 + (skip ? slots * 256 : 0);
+        };
         int max_copies = p->max_copies;
         if (const char* e = getenv("CB200_MAX_COPIES")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4 || v == 8) max_copies = v; }
-        while (C < max_copies && 2 * C * spp * gpc * cell + ring_bytes(thr, gpc) + (skip ? spp * 256 : 0) <= budget) C *= 2;
-        smem = spp * gpc * cell * C + ring_bytes(thr, gpc) + (skip ? spp * 256 : 0);
+        int g = 0;
+        while (g < G) {
+            int lo_b = gb(g), hi_b = gb(g), run = 1;
+            while (g + run < G) {
+                const int b2 = gb(g + run);
+                const int lo2 = b2 < lo_b ? b2 : lo_b, hi2 = b2 > hi_b ? b2 : hi_b;
+                if (hi2 > 2 * lo2) break;
+                lo_b = lo2; hi_b = hi2; ++run;
+            }
+            int fitg = 0;
+            while (fitg < run && fitg < p->max_bundle && need(nslots, fitg + 1, hi_b, 1) <= budget) ++fitg;
+            if (fitg < 1) {
+                for (int q = 0; q < run; ++q) {
+                    const int Bb = gb(g + q);
+                    int s1 = (budget - need(0, 1, Bb, 1)) / (8 * Bb * 4 + (skip ? 256 : 0));
+                    if (s1 < 1) return 0;
+                    const int np = (nslots + s1 - 1) / s1;
+                    s1 = (nslots + np - 1) / np;
+                    bundles.push_back(CbBundle{g + q, 1, Bb, 1, s1, np, 1});
+                }
+            } else {
+                const int nbr = (run + fitg - 1) / fitg;
+                int at = g;
+                for (int q = 0; q < nbr; ++q) {
+                    const int cnt = (run - (at - g) + (nbr - q) - 1) / (nbr - q);
+                    int Bb = 4;
+                    for (int k = 0; k < cnt; ++k) Bb = gb(at + k) > Bb ? gb(at + k) : Bb;
+                    bundles.push_back(CbBundle{at, cnt, Bb, 1, nslots, 1, 1});
+                    at += cnt;
+                }
+            }
+            g += run;
+        }
+        // Replicas: columns of few bins put many lanes of a warp on the same cell whatever the data look like (32 lanes
+        // over 16 bins), so their bundles take up to 8 replicas; measured on 4.5M x 52 columns (13 floats, 39 CTR columns
+        // of 16 bins), depth 8: 7.4 ms per tree against 9.8 ms with 2 replicas.
+        int narrow_copies = 8;
+        if (const char* e = getenv("CB200_NARROW_COPIES")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4 || v == 8) narrow_copies = v; }
+        for (CbBundle& b : bundles) {
+            const int mc = b.B <= 32 ? (narrow_copies > max_copies ? narrow_copies : max_copies) : max_copies;
+            while (b.C < mc && need(b.spp, b.gcnt, b.B, 2 * b.C) <= budget) b.C *= 2;
+            const int nb_ = need(b.spp, b.gcnt, b.B, b.C);
+            if (nb_ > smem) smem = nb_;
+        }
+        spp = bundles[0].spp; C = bundles[0].C; gpc = bundles[0].gcnt;
     } else {
         const int per_slot = p->a.h.S * 4 * p->a.h.B * 4 * ((p->a.h.statmax && !narrow) ? 2 : 1);
         const bool ring = p->a.h.statmax && p->a.h.S == 2;      // per-warp compaction rings (16 bytes x 64 entries)
@@ -376,17 +436,95 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
     const int grid = occ * p->sm_count;
     // document chunks per work unit (group or bundle): at least what the grid offers and what the 2^19-documents-per-
     // tile cap needs; among a few candidates take the one that fills the last round of blocks best
-    const int units = gpc ? (G + gpc - 1) / gpc : G;
-    const int by_grid = grid >= units ? grid / units : 1;
     const int by_docs = (int)((n + (1 << 19) - 1) >> 19);
-    const int lo = by_grid > by_docs ? by_grid : by_docs;
-    int best = lo;
-    double best_eff = 0.0;
-    for (int k = lo; k < lo + 8; ++k) {
-        const long long items = (long long)units * k;
-        const long long rounds = (items + grid - 1) / grid;
-        const double eff = (double)items / (double)(rounds * grid);
-        if (eff > best_eff + 0.02) { best_eff = eff; best = k; }
+    int best = 1;
+    if (bundles.empty()) {
+        const int units = G;
+        const int by_grid = grid >= units ? grid / units : 1;
+        const int lo = by_grid > by_docs ? by_grid : by_docs;
+        best = lo;
+        double best_eff = 0.0;
+        for (int k = lo; k < lo + 8; ++k) {
+            const long long items = (long long)units * k;
+            const long long rounds = (items + grid - 1) / grid;
+            const double eff = (double)items / (double)(rounds * grid);
+            if (eff > best_eff + 0.02) { best_eff = eff; best = k; }
+        }
+    } else {
+        if (level >= CB_MAX_LEVELS) return 0;
+        // Every bundle is cut into its own number of document chunks so that all work items take about the same time
+        // and their number is a whole multiple of the grid.  Cost of an item per document it streams: a fixed part (leaf
+        // index, two statistics, compaction) worth 2.8 groups plus one unit per group of the bundle (measured on 4.5M
+        // x 52 columns, depth 8: a one-group item took 0.49 of the time of a five-group item over the same documents).
+        const int nbun = (int)bundles.size();
+        std::vector<double> cost(nbun);
+        std::vector<int> nk(nbun);
+        double W = 0.0;
+        long long min_items = 0;
+        for (int i = 0; i < nbun; ++i) {
+            cost[i] = 2.8 + bundles[i].gcnt;
+            W += cost[i] * bundles[i].npass;
+            min_items += (long long)bundles[i].npass * by_docs;
+        }
+        // bundles of different shapes: the cost model is rough (bin collisions depend on the data), so the work is cut
+        // into two rounds of items handed out by a counter, which bounds the imbalance by half an item's time (measured
+        // on the same data: 7.2 ms per tree with one round, 7.1 with two, 7.8 with four -- every item zeroes and dumps a tile)
+        bool mixed = false;
+        for (int i = 1; i < nbun; ++i)
+            if (bundles[i].B != bundles[0].B || bundles[i].npass != bundles[0].npass || bundles[i].C != bundles[0].C) mixed = true;
+        int rounds = (mixed && p->a.h.work) ? 2 : 1;
+        if (const char* e = getenv("CB200_ITEM_ROUNDS")) { const int v = atoi(e); if (v >= 1 && v <= 16) rounds = v; }
+        long long T = (long long)grid * rounds;
+        while (T < min_items) T += grid;
+        long long used = 0;
+        for (int i = 0; i < nbun; ++i) {
+            int k = (int)((double)T * cost[i] / W);
+            if (k < by_docs) k = by_docs;
+            if (k < 1) k = 1;
+            nk[i] = k;
+            used += (long long)k * bundles[i].npass;
+        }
+        for (;;) {
+            int pick = -1;
+            double worst = 0.0;
+            for (int i = 0; i < nbun; ++i) {
+                if (used + bundles[i].npass > T) continue;
+                const double t = cost[i] / nk[i];
+                if (t > worst) { worst = t; pick = i; }
+            }
+            if (pick < 0) break;
+            ++nk[pick];
+            used += bundles[pick].npass;
+        }
+        // work list: chunk-major, so that blocks running side by side stream the same documents (their leaf indices and
+        // statistics then come from L2); the wider bundles of a chunk first
+        std::vector<int> order(nbun);
+        for (int i = 0; i < nbun; ++i) order[i] = i;
+        std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return cost[x] / nk[x] > cost[y] / nk[y]; });
+        std::vector<int2> items;
+        std::vector<int> gchunks(G, 1);
+        for (int i = 0; i < nbun; ++i) {
+            bundles[i].nK = nk[i];
+            if (nk[i] > best) best = nk[i];
+            for (int q = 0; q < bundles[i].gcnt; ++q) gchunks[bundles[i].g0 + q] = nk[i];
+        }
+        items.reserve((size_t)used);
+        for (int k = 0; k < best; ++k)
+            for (int bi : order)
+                if (k < nk[bi])
+                    for (int ps = 0; ps < bundles[bi].npass; ++ps) items.push_back(make_int2(bi | (ps << 16), k));
+        if (p->d_btab[level]) { cudaFree(p->d_btab[level]); p->d_btab[level] = nullptr; }
+        if (p->d_items[level]) { cudaFree(p->d_items[level]); p->d_items[level] = nullptr; }
+        if (p->d_gchunks[level]) { cudaFree(p->d_gchunks[level]); p->d_gchunks[level] = nullptr; }
+        if (cudaMalloc(&p->d_btab[level], bundles.size() * sizeof(CbBundle)) != cudaSuccess ||
+            cudaMalloc(&p->d_items[level], items.size() * sizeof(int2)) != cudaSuccess ||
+            cudaMalloc(&p->d_gchunks[level], (size_t)G * sizeof(int)) != cudaSuccess) { cudaGetLastError(); return 0; }
+        cudaMemcpy(p->d_btab[level], bundles.data(), bundles.size() * sizeof(CbBundle), cudaMemcpyHostToDevice);
+        cudaMemcpy(p->d_items[level], items.data(), items.size() * sizeof(int2), cudaMemcpyHostToDevice);
+        cudaMemcpy(p->d_gchunks[level], gchunks.data(), (size_t)G * sizeof(int), cudaMemcpyHostToDevice);
+        p->n_btab[level] = nbun;
+        p->n_items[level] = (int)items.size();
+        p->single_pass_bundle[level] = (nbun == 1 && bundles[0].npass == 1 && bundles[0].gcnt >= G) ? 1 : 0;
     }
     *slots_per_pass = spp;
     *smem_bytes = smem;
@@ -412,7 +550,13 @@ CB_API int cb_fused_launch(CbFusedPlan* p, int level, float* hprev, float* hcur,
     // ... when one bundle holds every feature group: then the split feature's bin word is already in registers and each
     // document is streamed by exactly one block.  With several bundles each of them would have to fetch that word as
     // well, which costs more than the separate pass (measured at 10.5M x 28, level 5, 4 bundles: +86 us against 18 us).
-    a.fuse_leaf = (level > 0 && bundle >= a.h.d.G && a.h.statmax && a.h.S == 2 && a.h.narrow && p->fuse_leaf_update) ? 1 : 0;
+    const bool table = bundle > 0 && level < CB_MAX_LEVELS && p->d_btab[level] != nullptr;
+    a.h.btab = table ? p->d_btab[level] : nullptr;
+    a.h.bitems = table ? p->d_items[level] : nullptr;
+    a.h.nbitems = table ? p->n_items[level] : 0;
+    a.h.gchunks = table ? p->d_gchunks[level] : nullptr;
+    const bool whole = table ? p->single_pass_bundle[level] != 0 : bundle >= a.h.d.G;
+    a.fuse_leaf = (level > 0 && whole && a.h.statmax && a.h.S == 2 && a.h.narrow && p->fuse_leaf_update) ? 1 : 0;
     a.h.prev_splits = a.fuse_leaf ? a.splits : nullptr;
     void* args[] = {&a};
     cudaError_t e = cudaLaunchCooperativeKernel((void*)cb_level_fused_kernel, dim3(grid), dim3(threads), args,

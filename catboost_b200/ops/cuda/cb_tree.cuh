@@ -36,6 +36,15 @@ struct CbData {        // the binned training shard of this rank
     int TB;                         // feat_off[F]
 };
 
+struct CbBundle {
+    int g0, gcnt;      // feature groups g0 .. g0 + gcnt - 1
+    int B;             // bins per feature inside the tile (multiple of 4, >= the widest feature of the bundle)
+    int C;             // replicas of a cell (power of two)
+    int spp;           // slots (leaves) per pass
+    int npass;
+    int nK;            // document chunks of this bundle
+};
+
 struct CbHistArgs {
     CbData d;
     const unsigned short* leaf;
@@ -80,6 +89,15 @@ struct CbHistArgs {
     // is dumped.  On sparse data most (document, feature) pairs hit the dominant bin, so this removes most shared-memory
     // atomics and the hot spot they create.  nullptr = off.
     const unsigned int* domw;
+    // Bundle table of the bundled path (nullptr = uniform bundles of `bundle` groups with B bins and `copies` replicas).
+    // Feature groups differ in their number of bins (128-border float columns next to 16-bin CTR columns or binary
+    // one-hot columns), and the shared-memory tile is what limits how many leaves one pass over the documents can take:
+    // every bundle therefore has its own bin stride, replica count and slots per pass, and the work items
+    // (bundle, document chunk, slot pass) are listed explicitly, heaviest first.
+    const CbBundle* btab;
+    const int2* bitems;         // x = bundle | pass << 16, y = document chunk
+    int nbitems;
+    const int* gchunks;         // [G] document chunks of the bundle every group belongs to
     const CbSplit* prev_splits;
     const int* prev_iter;
     int prev_depth;
@@ -626,10 +644,8 @@ __device__ __forceinline__ void cb_bundle_load(const uint32_t* bg, long long npa
 
 template <int GMAX, bool UPD, bool SKIP>
 static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int gcnt, int chunk, int nK,
-                                      int slot_begin, int slot_count) {
+                                      int slot_begin, int slot_count, int B, int C) {
     constexpr int V = CB_BUNDLE_V(GMAX);
-    const int B = a.B;
-    const int C = a.copies > 0 ? a.copies : 1;
     const int cs = 31 - __clz(C);                // log2(C): shift of a (j, bin) cell index to ints
     const int gstride = 2 * 4 * B * C;
     const int slot_stride = gcnt * gstride;
@@ -790,7 +806,8 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
         }
         __syncthreads();
     }
-    // dump as floats into the private regions [chunk * G + group][slot][s][j][B]
+    // dump as floats into the private regions [chunk * G + group][slot][s][j][a.B]: the region keeps the bin stride of
+    // the widest feature of the data set, the tile only has the B bins this bundle needs
     const int B4 = B >> 2;
     const int cells4 = slot_count * gcnt * 8 * B4;
     const float inv0 = fmaxf(a.statmax[0], 1e-30f) / qmax;
@@ -808,8 +825,8 @@ static __device__ void cb_hist_bundle(const CbHistArgs& a, int* sh, int g0, int 
         for (int q = 0; q < 4; ++q)
             for (int cc = 0; cc < C; ++cc) q4[q] += src[q * C + cc];
         const float inv = (sj & 4) ? inv1 : inv0;
-        float* dst = a.priv + (((size_t)chunk * a.d.G + g0 + gl) * nslots + slot_begin + slot) * (size_t)(8 * B)
-                     + sj * B + b4 * 4;
+        float* dst = a.priv + (((size_t)chunk * a.d.G + g0 + gl) * nslots + slot_begin + slot) * (size_t)(8 * a.B)
+                     + sj * a.B + b4 * 4;
         *reinterpret_cast<float4*>(dst) =
             make_float4((float)q4[0] * inv, (float)q4[1] * inv, (float)q4[2] * inv, (float)q4[3] * inv);
     }
@@ -830,15 +847,16 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
     long long per = (a.d.n + nK - 1) / nK;
     per = (per + 3) & ~3ll;
     const int nslots = cb_hist_nslots(a);
-    const bool one_pass = a.slots_per_pass >= nslots;
     const bool quant2 = a.statmax && a.priv && a.S == 2;      // without private tiles: the stand-alone integer path
     const int gpc = (quant2 && a.narrow && a.bundle > 0) ? a.bundle : 0;      // groups per block, 0 = per-group paths
+    const bool table = gpc && a.btab;                          // explicit work list (bundle, slot pass, chunk)
+    const int spp = table ? nslots : a.slots_per_pass;         // the work list carries the passes of its bundles itself
+    const bool one_pass = spp >= nslots;
     const int nb = gpc ? (G + gpc - 1) / gpc : G;
-    const long long items = (long long)nb * nK;
+    const long long items = table ? (long long)a.nbitems : (long long)nb * nK;
     const bool dyn_items = a.work && quant2 && one_pass && items > ncta;     // whole items from one counter
     __shared__ unsigned int s_item;
-    for (int sb = 0; sb < nslots; sb += a.slots_per_pass) {
-        const int sc = min(a.slots_per_pass, nslots - sb);
+    for (int sb0 = 0; sb0 < nslots; sb0 += spp) {
         for (long long item = cta;; item += ncta) {
             if (dyn_items) {
                 __syncthreads();
@@ -847,20 +865,32 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
                 item = s_item;
             }
             if (item >= items) break;
-            const int g = (int)(item % nb);
-            const long long k = item / nb;
+            int sb = sb0, sc = min(spp, nslots - sb0);
+            int g = (int)(item % nb);
+            long long k = item / nb;
             if (gpc) {
-                const int g0 = g * gpc;
-                const int gcnt = min(gpc, G - g0);
+                int g0 = g * gpc, gcnt = min(gpc, G - g0), Bb = a.B, Cb = a.copies > 0 ? a.copies : 1;
+                bool whole = gpc >= G;
+                int nKb = nK;
+                if (table) {
+                    const int2 it = a.bitems[item];
+                    const CbBundle bd = a.btab[it.x & 0xFFFF];
+                    k = it.y;
+                    nKb = bd.nK;
+                    g0 = bd.g0; gcnt = bd.gcnt; Bb = bd.B; Cb = bd.C;
+                    sb = (it.x >> 16) * bd.spp;
+                    sc = min(bd.spp, nslots - sb);
+                    whole = gcnt >= G && bd.npass == 1;
+                }
                 int* shi = reinterpret_cast<int*>(sh);
-                const bool upd = CB_UPD_ON && a.prev_splits && a.level > 0 && gpc >= G;
+                const bool upd = CB_UPD_ON && a.prev_splits && a.level > 0 && whole;
 #define CB_BUNDLE_CALL(GM) do { \
-                    if (a.domw) { if (upd) cb_hist_bundle<GM, true, true>(a, shi, g0, gcnt, (int)k, nK, sb, sc); \
-                                  else cb_hist_bundle<GM, false, true>(a, shi, g0, gcnt, (int)k, nK, sb, sc); } \
-                    else { if (upd) cb_hist_bundle<GM, true, false>(a, shi, g0, gcnt, (int)k, nK, sb, sc); \
-                           else cb_hist_bundle<GM, false, false>(a, shi, g0, gcnt, (int)k, nK, sb, sc); } } while (0)
-                if (gpc <= 2) CB_BUNDLE_CALL(2);
-                else if (gpc <= 4) CB_BUNDLE_CALL(4);
+                    if (a.domw) { if (upd) cb_hist_bundle<GM, true, true>(a, shi, g0, gcnt, (int)k, nKb, sb, sc, Bb, Cb); \
+                                  else cb_hist_bundle<GM, false, true>(a, shi, g0, gcnt, (int)k, nKb, sb, sc, Bb, Cb); } \
+                    else { if (upd) cb_hist_bundle<GM, true, false>(a, shi, g0, gcnt, (int)k, nKb, sb, sc, Bb, Cb); \
+                           else cb_hist_bundle<GM, false, false>(a, shi, g0, gcnt, (int)k, nKb, sb, sc, Bb, Cb); } } while (0)
+                if (gcnt <= 2) CB_BUNDLE_CALL(2);
+                else if (gcnt <= 4) CB_BUNDLE_CALL(4);
                 else CB_BUNDLE_CALL(8);
 #undef CB_BUNDLE_CALL
                 continue;

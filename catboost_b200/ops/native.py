@@ -224,6 +224,7 @@ _SIGS = {
     "cb_fused_set_max_copies": (None, [c_void_p, c_int]),
     "cb_fused_set_priv": (None, [c_void_p, c_void_p, c_void_p]),
     "cb_fused_destroy": (None, [c_void_p]),
+    "cb_fused_set_group_bins": (None, [c_void_p, c_void_p, c_int]),
     "cb_fused_geometry": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_fused_launch": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_int, c_int, c_int, c_void_p]),

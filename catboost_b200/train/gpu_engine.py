@@ -233,6 +233,13 @@ class GpuObliviousEngine:
         # fixed-point accumulation is on: statmax must be known to the geometry (it doubles the tile size)
         self.lib.cb_fused_set_priv(ctypes.c_void_p(self.plan), None, _p(self.statmax) if self.quantized_hist else None)
         self.lib.cb_fused_set_narrow(ctypes.c_void_p(self.plan), 1 if self.narrow_hist else 0, self.max_bundle)
+        if os.environ.get("CB200_UNIFORM_BINS") != "1":
+            # bins of the widest feature of every group: bundles of narrow columns (CTR, one-hot, binary) get small tiles
+            nbp = np.full(self.store.G * 4, 4, dtype=np.int64)
+            nbp[: self.store.F] = (np.asarray(self.store.feat_nb_host, dtype=np.int64) + 3) // 4 * 4
+            gbins = np.ascontiguousarray(np.maximum(4, nbp.reshape(-1, 4).max(1)).astype(np.int32))
+            self.lib.cb_fused_set_group_bins(ctypes.c_void_p(self.plan), gbins.ctypes.data_as(ctypes.c_void_p), int(len(gbins)))
+            self.group_bins = gbins
         self.lib.cb_fused_set_fuse_leaf(ctypes.c_void_p(self.plan), 1 if self.fuse_leaf_update else 0)
         # columns where one bin holds a large share of the documents (sparse data): most lanes of a warp would add to
         # the same histogram cell, so such data gets up to 8 replicas of every cell instead of 2 (measured on 60 % zeros:
@@ -240,14 +247,18 @@ class GpuObliviousEngine:
         self.dominant_bin_share, self.domw = self._dominant_bins()
         if not (self.narrow_hist and self.S == 2 and self.skip_dominant_bin):
             self.domw = None
-        if self.domw is not None and self.dominant_bin_share > 0.25:
+        gate = float(os.environ.get("CB200_DOMINANT_GATE", "0.25"))
+        if self.domw is not None and self.dominant_bin_share > gate:
             # sparse data: most (document, feature) pairs would hit one hot cell per feature; those are skipped and the
             # cell is restored from per-slot totals
             self.lib.cb_fused_set_dominant(ctypes.c_void_p(self.plan), _p(self.domw))
         else:
             self.domw = None
-            if self.dominant_bin_share > 0.25:
+            if self.dominant_bin_share > gate:
                 self.lib.cb_fused_set_max_copies(ctypes.c_void_p(self.plan), 8)
+        self.work = torch.zeros(self.store.G + 1, dtype=torch.int32, device=self.dev)
+        if self.dynamic_work:
+            self.lib.cb_fused_set_work(ctypes.c_void_p(self.plan), _p(self.work))
         self.level_geo = []
         for level in range(self.depth):
             spp, smem, thr, nk, cp, bd = (ctypes.c_int(0) for _ in range(6))
@@ -263,9 +274,6 @@ class GpuObliviousEngine:
             nslots = 1 if level == 0 else 1 << (level - 1)
             need = max(need, G * geo[4] * nslots * self.S * 4 * self.B)
         self.priv = torch.empty(need, dtype=torch.float32, device=self.dev)
-        self.work = torch.zeros(G + 1, dtype=torch.int32, device=self.dev)
-        if self.dynamic_work:
-            self.lib.cb_fused_set_work(ctypes.c_void_p(self.plan), _p(self.work))
         self.lib.cb_fused_set_priv(ctypes.c_void_p(self.plan), _p(self.priv),
                                    _p(self.statmax) if self.quantized_hist else None)
 

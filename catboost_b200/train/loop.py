@@ -524,6 +524,9 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
             quantized_hist={"narrow": True, "wide": "wide", "float": False}[o.histogram_cells or "narrow"],
             leaf_backtracking=str(o.leaf_estimation_backtracking or "AnyImprovement"), dims=K,
             der_fn=der_fn, zero_mean_leaves=bool(der_fn is not None and getattr(objective, "zero_mean_leaves", False)))
+    phase_timing = os.environ.get("CB200_PHASE_TIMING") == "1" and getattr(eng, "plan", None)
+    if phase_timing:
+        eng.enable_phase_timing()       # developer aid: per-level phase times of the last tree go to stderr
     # resume from a snapshot: same container and state as the general learner writes (trees + metric history), so either
     # trainer can pick up the other's file
     start = 0
@@ -678,6 +681,14 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
                 vals_l = [math.sqrt(v) for v in vals_l]
             hist.data["learn"][name] = vals_l
     launches = eng.launches_per_iter
+    if phase_timing and ctx.rank == 0:
+        import sys
+        print("level geometry (grid, slots/pass, smem, threads, chunks, copies, bundle):", eng.level_geo,
+              "mean share of the most frequent bin:", round(eng.dominant_bin_share, 3), "skipping:", eng.domw is not None,
+              "bins per group:", getattr(eng, "group_bins", None), "feature kinds:",
+              "".join(f.kind[0] for f in store.features), file=sys.stderr)
+        print("phase us per level [leaf update, histogram, grid wait, reduce + push, score, select]:\n",
+              np.round(eng.phase_times_us(), 1), file=sys.stderr)
     train_approx = (eng.approx[:, :n].t().double().cpu().numpy() if K > 1
                     else eng.approx[:n].double().cpu().numpy().reshape(-1, 1))
     eng.close()

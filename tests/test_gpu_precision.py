@@ -404,3 +404,34 @@ def test_dominant_bin_skipping_gives_the_same_trees():
     assert np.array_equal(outs[0][0][:, :, :2], outs[1][0][:, :, :2]), np.argwhere(outs[0][0] != outs[1][0])[:8]
     assert np.allclose(outs[0][2], outs[1][2], rtol=1e-6)
     assert np.allclose(outs[0][1], outs[1][1], rtol=1e-4, atol=1e-5)
+
+
+def test_bundles_sized_by_their_own_bins_give_the_same_model(monkeypatch):
+    """Columns of very different widths (128-border floats next to columns with a handful of values): the level kernel
+    sizes the tile of every bundle by its own widest feature and lists (bundle, slot pass, chunk) work items; the
+    histograms are the same sums as with one bin stride for all bundles, up to the fixed-point scale."""
+    rng = np.random.default_rng(17)
+    n = 120_001
+    wide = rng.standard_normal((n, 9)).astype(np.float32)
+    small = rng.integers(0, 6, size=(n, 27)).astype(np.float32)
+    X = np.concatenate([wide, small], 1)
+    y = (wide[:, 0] + 0.7 * wide[:, 4] + 0.5 * (small[:, 2] > 2) - 0.4 * (small[:, 20] > 3)
+         + 0.3 * rng.standard_normal(n) > 0.2).astype(np.float32)
+    store = _store_of(X, y, 128)
+    assert store.feat_nb_host.max() > 100 and store.feat_nb_host.min() <= 8
+    outs, geos = [], []
+    for uniform in (False, True):
+        if uniform:
+            monkeypatch.setenv("CB200_UNIFORM_BINS", "1")
+        eng = _engine(store, y, "narrow", 8, 6, leaf_iterations=2)
+        geos.append(list(eng.level_geo))
+        eng.step(6)
+        loss = eng.learn_loss_history().copy()
+        sp, vals, wts = eng.finish()
+        outs.append((sp.copy(), vals.copy(), wts.copy(), loss))
+        eng.close()
+    assert np.array_equal(outs[0][0][0, :, :2], outs[1][0][0, :, :2])          # first tree: same statistics
+    assert np.allclose(outs[0][2][0], outs[1][2][0], rtol=1e-6)
+    same = (outs[0][0][:, :, :2] == outs[1][0][:, :, :2]).all(-1).mean()
+    assert same >= 0.9, same
+    assert np.allclose(outs[0][3], outs[1][3], rtol=2e-3)
