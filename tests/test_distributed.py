@@ -141,6 +141,21 @@ def test_two_gpus_fused_matches_nccl_baseline():
 
 
 @pytest.mark.gpu
+def test_two_gpus_categorical_features_sharded_by_hash(monkeypatch):
+    """The CTR engine on two GPUs: categories dealt to the ranks by hash (device sort, scan and bucketing kernels on the
+    owner, two all-to-alls) against every rank computing every table from all-gathered columns."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    res = _run(2, "nccl", mode="cat", port=29625)
+    assert res["acc"] > 0.85, res["acc"]
+    monkeypatch.setenv("CB200_CTR_GATHER", "1")
+    ref = _run(2, "nccl", mode="cat", port=29627)
+    assert res["splits"] == ref["splits"]
+    assert np.allclose(res["pred"], ref["pred"], rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.gpu
 def test_four_gpus_fused_matches_nccl_baseline():
     import torch
     if torch.cuda.device_count() < 4:
@@ -179,11 +194,17 @@ os._exit(0)
 '''
 
 
-def test_gloo_two_ranks_with_categorical_features():
+def test_gloo_two_ranks_with_categorical_features(monkeypatch):
     """CTR statistics are computed from the rows of all ranks: the two-rank model must be as good as a model trained on
-    one rank with all rows (shard-local statistics would lose most of the signal of a 300-value feature)."""
+    one rank with all rows (shard-local statistics would lose most of the signal of a 300-value feature).  The
+    categories are dealt to the ranks by hash; mirroring the categorical columns on every rank instead (the older
+    scheme) must give the same model."""
     res = _run(2, "gloo", mode="cat", port=29619)
     assert res["acc"] > 0.85, res["acc"]
+    monkeypatch.setenv("CB200_CTR_GATHER", "1")
+    ref = _run(2, "gloo", mode="cat", port=29621)
+    assert res["splits"] == ref["splits"]
+    assert np.allclose(res["pred"], ref["pred"], atol=1e-6)
 
 
 def test_lost_rank_is_detected_by_the_survivor():
