@@ -548,6 +548,10 @@ class CatBoost:
             return fstr.interaction(self._model)
         elif t == EFstrType.PredictionDiff:
             return fstr.prediction_diff(self, data)
+        elif t == EFstrType.SageValues:
+            if data is None:
+                raise CatBoostError("SageValues needs a dataset")
+            imp = fstr.sage_values(self, data)
         else:
             raise CatBoostError(f"feature importance type {t!r} is not supported")
         if prettified:

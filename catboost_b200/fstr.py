@@ -6,9 +6,12 @@
   catboost/libs/fstr/shap_values.cpp; output ``[n, n_features + 1]`` (last column = expected value), or
   ``[n, dims, n_features + 1]`` for multi-dimensional models.
 * LossFunctionChange: change of the loss when a feature's SHAP contribution is replaced by its mean.
+* SageValues: Shapley additive global importance by sampling (marginal imputation of features in random order).
 * Interaction: pairwise strength of features that meet in the same tree.
 """
 from __future__ import annotations
+
+import math
 
 import numpy as np
 
@@ -310,3 +313,71 @@ def prediction_diff(estimator, data) -> np.ndarray:
     sv = shap_values(estimator._model, pool)
     d = sv[0, :-1] - sv[1, :-1] if sv.ndim == 2 else (sv[0, :, :-1] - sv[1, :, :-1]).sum(0)
     return np.abs(d)
+
+
+def sage_values(estimator, data, n_samples: int = 128, batch_size: int = 512, detect_convergence: bool = True,
+                seed: int = 228) -> np.ndarray:
+    """SAGE (Shapley additive global importance) of every feature: the mean rise of the model's loss when the feature's
+    column is replaced by draws from its marginal distribution, averaged over random feature orders and random batches
+    (catboost/libs/fstr/sage_values.cpp:334-426: a batch of rows, a random order of the features, the features are
+    imputed one after another and every step's loss change is credited to the feature just imputed; sampling stops
+    early when the widest 95 % confidence interval is below a tenth of the largest value)."""
+    m = estimator._model
+    if m.dims != 1:
+        raise CatBoostError("SageValues: the model must have one dimension")
+    pool = data if isinstance(data, Pool) else Pool(data)
+    if pool.label is None:
+        raise CatBoostError("SageValues needs labels")
+    loss = m.params.get("loss_function", m.loss_name) if isinstance(m.params.get("loss_function", None), str) else m.loss_name
+    metric = make_metric(loss)
+    rng = np.random.default_rng(seed)
+    n = pool.num_row()
+    batch_size = min(int(batch_size), n)
+    columns = [("float", j, c) for j, c in enumerate(pool.float_feature_indices)] + \
+              [("cat", j, c) for j, c in enumerate(pool.cat_feature_indices)] + \
+              [("text", j, c) for j, c in enumerate(getattr(pool, "text_feature_indices", []) or [])] + \
+              [("emb", j, c) for j, c in enumerate(getattr(pool, "embedding_feature_indices", []) or [])]
+    n_ext = max([c for _, _, c in columns] + [m.n_features - 1]) + 1
+    samples = [[0.0] for _ in range(n_ext)]
+    groups = pool.group_offsets() if pool.group_id is not None else None
+
+    def batch_loss(b):
+        raw = estimator._raw(b)
+        kw = {"group_offsets": b.group_offsets()} if b.group_id is not None else {}
+        v = metric.eval(raw, estimator._encode_labels(b.label), b.weight, **kw)
+        return -v if metric.is_max_optimal else v
+
+    for _ in range(int(n_samples)):
+        if groups is None:
+            rows = rng.choice(n, batch_size, replace=False)
+        else:
+            order, rows, got = rng.permutation(len(groups) - 1), [], 0
+            for g in order:
+                rows.append(np.arange(groups[g], groups[g + 1]))
+                got += groups[g + 1] - groups[g]
+                if got >= batch_size:
+                    break
+            rows = np.concatenate(rows)
+        b = pool.slice(rows)
+        prev = batch_loss(b)
+        for k in rng.permutation(len(columns)):
+            kind, j, ext = columns[k]
+            draw = rng.integers(0, n, size=b.num_row())
+            if kind == "float":
+                b.float_data[:, j] = pool.float_data[draw, j]
+            elif kind == "cat":
+                b.cat_hashes[j] = pool.cat_hashes[j, draw]
+                b.__dict__.pop("_cat_hash_tensors", None)
+            elif kind == "text":
+                b.text_data[j] = pool.text_data[j][draw]
+            else:
+                b.embedding_data[j] = pool.embedding_data[j][draw]
+            cur = batch_loss(b)
+            samples[ext].append(cur - prev)
+            prev = cur
+        if detect_convergence:
+            means = np.array([np.mean(s) for s in samples])
+            half = np.array([1.96 * np.std(s) / math.sqrt(len(s)) for s in samples])
+            if half.max() / (np.abs(means).max() + 1e-12) <= 0.1:
+                break
+    return np.array([float(np.mean(s)) for s in samples])

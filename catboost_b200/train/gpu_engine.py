@@ -32,7 +32,7 @@ from ..parallel.runtime import ArenaLayout, DistContext, PeerArena, split_column
 
 SCORE_FN = {"Cosine": (0, 0), "L2": (1, 0), "NewtonCosine": (0, 1), "NewtonL2": (1, 1), "SolarL2": (2, 0),
             "LOOL2": (3, 0), "SatL2": (4, 0)}
-BOOTSTRAP = {"No": 0, "Bayesian": 1, "Bernoulli": 2, "Poisson": 3}
+BOOTSTRAP = {"No": 0, "Bayesian": 1, "Bernoulli": 2, "Poisson": 3, "MVS": 0}      # MVS: its own kernel after the gradients
 
 
 def _p(t):
@@ -57,7 +57,7 @@ class GpuObliviousEngine:
                  ext_der: Optional[torch.Tensor] = None, ext_hess: Optional[torch.Tensor] = None,
                  timeout_s: float = 20.0, quantized_hist: bool = True, dynamic_work: bool = True,
                  der_fn=None, zero_mean_leaves: bool = False, max_bundle: int = 8,
-                 fused_leaf_steps: bool = True, leaf_backtracking: str = "AnyImprovement",
+                 fused_leaf_steps: bool = True, mvs_reg=None, leaf_backtracking: str = "AnyImprovement",
                  fuse_leaf_update: bool = True, dims: int = 1, skip_dominant_bin: bool = True):
         assert store.bins.is_cuda, "GpuObliviousEngine needs a CUDA store"
         if depth > 16:
@@ -73,6 +73,11 @@ class GpuObliviousEngine:
         self.score_fn, self.newton_stats = SCORE_FN[score_function]
         self.random_strength = float(random_strength)
         self.boot_type, self.boot_p = BOOTSTRAP[bootstrap_type], float(bootstrap_param)
+        # minimal-variance sampling: sampling weights from the finished derivatives, block by block (ops/cuda/cb_mvs.cu)
+        self.mvs = bootstrap_type == "MVS" and float(bootstrap_param) < 1.0
+        self.mvs_reg = -1.0 if mvs_reg is None else float(mvs_reg)
+        if self.mvs and dims > 1:
+            raise ValueError("MVS sampling on the device trainer covers one-dimensional losses")
         self.leaf_newton = 1 if leaf_method == "Newton" else 0
         self.leaf_iterations = max(1, int(leaf_iterations))
         self.objective = objective
@@ -320,6 +325,11 @@ class GpuObliviousEngine:
                                        _p(self.scal), _p(self.ext_der), _p(self.ext_hess), _p(self.statmax),
                                        self.grid_stream, self._stream()), "cb_grad_pointwise")
         self.launches_per_iter += 1
+        if self.mvs:
+            chk(self.lib.cb_mvs_sample(_p(self.stats), self.npad, self.n, self.boot_p, self.mvs_reg, self.seed,
+                                       _p(self.iter_ptr), _p(self.statmax) if self.quantized_hist else None, None,
+                                       self._stream()), "cb_mvs_sample")
+            self.launches_per_iter += 1
 
     def _dominant_bins(self, sample: int = 65536):
         """(mean share of the most frequent bin over the features, packed dominant bins per feature group or None).

@@ -89,7 +89,7 @@ def _use_fast_engine(o, objective, store, dims) -> bool:
     return (store.bins.is_cuda and o.grow_policy == "SymmetricTree" and (native or external)
             and o.boosting_type == "Plain" and o.leaf_estimation_method in ("Newton", "Gradient")
             and float(o.rsm) >= 1.0 and int(o.min_data_in_leaf) <= 1
-            and o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson")
+            and (o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson") or (o.bootstrap_type == "MVS" and dims == 1))
             and not o.langevin and not o.monotone_constraints and not o.model_shrink_rate
             and str(o.random_score_type) != "Gumbel")
 
@@ -518,7 +518,8 @@ def _run_fast(o, objective, store, eval_stores, y_train, w_train, base_train, ev
             torch.from_numpy(np.ascontiguousarray(base_train if K > 1 else base_train[0], dtype=np.float32)), objective,
             depth=int(o.depth), iterations=T, learning_rate=float(o.learning_rate), l2_leaf_reg=float(o.l2_leaf_reg),
             score_function=o.score_function, random_strength=float(o.random_strength), bootstrap_type=btype,
-            bootstrap_param=boot_p, leaf_method=o.leaf_estimation_method,
+            bootstrap_param=boot_p, mvs_reg=(None if o.mvs_reg is None else float(o.mvs_reg)),
+            leaf_method=o.leaf_estimation_method,
             leaf_iterations=int(o.leaf_estimation_iterations), seed=int(o.random_seed), ctx=ctx,
             reduce=("fused" if o.histogram_reduce in ("fused", None) else "nccl"), eval_sets=evs,
             quantized_hist={"narrow": True, "wide": "wide", "float": False}[o.histogram_cells or "narrow"],

@@ -1075,3 +1075,19 @@ def test_carry_model_fixes_features():
     Xg[:, 1], Xg[:, 4] = rng.standard_normal(1500), 99.0          # the carried model ignores these columns
     assert np.allclose(carried.predict_raw(Xg), ref)
     assert sum(len(t.splits) for t in carried.trees) < sum(len(t.splits) for t in m._model.trees)
+
+
+def test_sage_values_rank_the_informative_features():
+    """SAGE: the loss rises most when the features the target depends on are replaced by marginal draws; a noise column
+    gets a value near zero (catboost/libs/fstr/sage_values.cpp)."""
+    import catboost_b200 as cb
+    rng = np.random.default_rng(4)
+    n = 3000
+    X = rng.standard_normal((n, 5)).astype(np.float32)
+    y = (2.0 * X[:, 1] + 0.7 * X[:, 3] + 0.2 * rng.standard_normal(n)).astype(np.float32)
+    m = cb.CatBoostRegressor(iterations=60, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False)
+    m.fit(X, y)
+    sage = m.get_feature_importance(cb.Pool(X, y), type="SageValues")
+    assert sage.shape == (5,)
+    assert int(np.argmax(sage)) == 1 and sage[1] > sage[3] > max(sage[0], sage[2], sage[4])
+    assert abs(sage[0]) < 0.1 * sage[1]

@@ -517,3 +517,64 @@ def test_radix_sort_is_stable_and_matches_framework_sort(n):
         ref_k, ref_o = torch.sort(k, stable=True)
         assert torch.equal(sk, ref_k)
         assert torch.equal(order, ref_o)
+
+
+@pytest.mark.parametrize("n,rate,lam", [(8192 * 3 + 517, 0.3, 0.01), (5000, 0.7, -1.0)])
+def test_mvs_sampling_kernel(n, rate, lam):
+    """Minimal-variance sampling: per block of 8192 documents the threshold mu solves sum min(1, c / mu) = rate * m
+    with c = sqrt(der^2 + lambda); a kept document's statistics are scaled by max(1, mu / c), a dropped one's are zero."""
+    import ctypes
+    from catboost_b200.ops import native
+    lib = native.cuda_lib()
+    g = torch.Generator().manual_seed(5)
+    npad = (n + 255) // 256 * 256
+    stats = torch.zeros((2, npad))
+    stats[0, :n] = torch.randn(n, generator=g) * torch.rand(n, generator=g)
+    stats[1, :n] = torch.rand(n, generator=g) + 0.1
+    before = stats.clone()
+    st = stats.cuda()
+    blk = lib.cb_mvs_block_docs()
+    nblk = (n + blk - 1) // blk
+    mu = torch.zeros(nblk, device="cuda")
+    it = torch.zeros(1, dtype=torch.int32, device="cuda")
+    smax = torch.zeros(2, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    native.cuda_check(lib.cb_mvs_sample(p(st), npad, n, rate, lam, 12345, p(it), p(smax), p(mu),
+                                        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "cb_mvs_sample")
+    torch.cuda.synchronize()
+    after, mu = st.cpu(), mu.cpu()
+    kept_total = 0
+    for b in range(nblk):
+        lo, hi = b * blk, min(n, (b + 1) * blk)
+        d = before[0, lo:hi].double()
+        lam_b = lam if lam >= 0 else float(d.abs().mean()) ** 2
+        c = torch.sqrt(d * d + lam_b)
+        m = hi - lo
+        f = torch.clamp(c / float(mu[b]), max=1.0).sum().item()
+        assert abs(f - rate * m) <= 2e-3 * m, (b, f, rate * m)
+        w_full = torch.clamp(float(mu[b]) / c, min=1.0)
+        ratio1 = after[1, lo:hi].double() / before[1, lo:hi].double()
+        kept = ratio1 > 0
+        assert torch.allclose(ratio1[kept], w_full[kept], rtol=1e-4)
+        assert torch.allclose(after[0, lo:hi].double()[kept], (d * w_full)[kept], rtol=1e-4, atol=1e-7)
+        assert (after[0, lo:hi][~kept] == 0).all()
+        assert bool(kept[c >= float(mu[b])].all())               # large gradients are always kept
+        kept_total += int(kept.sum())
+    assert abs(kept_total / n - rate) < 0.03
+    assert float(smax[0]) >= float(after[0].abs().max()) - 1e-6 and float(smax[1]) >= float(after[1].abs().max()) - 1e-6
+
+
+def test_fit_with_mvs_bootstrap_runs_on_the_device_trainer():
+    import catboost_b200 as cb
+    rng = np.random.default_rng(3)
+    n = 60_000
+    X = rng.standard_normal((n, 12)).astype(np.float32)
+    y = (X[:, 0] - 0.8 * X[:, 3] + 0.5 * X[:, 5] * X[:, 6] + 0.4 * rng.standard_normal(n) > 0).astype(np.float32)
+    accs = {}
+    for bt, extra in (("MVS", dict(subsample=0.4)), ("No", {})):
+        m = cb.CatBoostClassifier(iterations=80, depth=6, learning_rate=0.2, task_type="GPU", bootstrap_type=bt,
+                                  verbose=False, allow_writing_files=False, **extra)
+        m.fit(X[:50_000], y[:50_000])
+        assert m._train_info["launches_per_iter"] > 0              # the device engine, not the general learner
+        accs[bt] = float((m.predict(X[50_000:]) == y[50_000:]).mean())
+    assert accs["MVS"] > accs["No"] - 0.02 and accs["MVS"] > 0.85, accs
