@@ -89,8 +89,16 @@ class Dictionary:
     def __init__(self, token_level_type=None, gram_order=None, skip_step=None, start_token_id=None, end_of_word_policy=None,
                  end_of_sentence_policy=None, occurence_lower_bound=None, max_dictionary_size=None, num_bpe_units=None,
                  skip_unknown=None, dictionary_type="FrequencyBased"):
-        if dictionary_type != "FrequencyBased" or num_bpe_units:
-            raise CatBoostError("only frequency-based dictionaries are built here (no BPE)")
+        if dictionary_type not in ("FrequencyBased", "Bpe"):
+            raise CatBoostError("dictionary_type must be 'FrequencyBased' or 'Bpe'")
+        self.dictionary_type = dictionary_type
+        self.num_bpe_units = int(num_bpe_units or 0)
+        if dictionary_type == "Bpe" and self.num_bpe_units <= 0:
+            raise CatBoostError("a Bpe dictionary needs num_bpe_units > 0")
+        if dictionary_type == "Bpe" and int(gram_order or 1) != 1:
+            raise CatBoostError("a Bpe dictionary is built over single tokens (gram_order = 1)")
+        self.skip_unknown = bool(skip_unknown)
+        self._merges: List[tuple] = []              # (left id, right id, count) in the order they were learned
         self.token_level_type = token_level_type or "Word"
         if self.token_level_type not in ("Word", "Letter"):
             raise CatBoostError("token_level_type must be 'Word' or 'Letter'")
@@ -161,7 +169,86 @@ class Dictionary:
         self._counts = [counts[g] for g in keep]
         self._token_to_id = {g: self.start_token_id + i for i, g in enumerate(keep)}
         self._fitted = True
+        if self.dictionary_type == "Bpe":
+            self._fit_bpe(data, tokenizer)
         return self
+
+    # ---- byte-pair encoding ------------------------------------------------------------------------------------------
+    # Behaviour follows library/cpp/text_processing/dictionary/bpe_builder.cpp: the alphabet is the frequency dictionary
+    # of single units; ``num_bpe_units`` times the most frequent pair of neighbouring ids (ties: the smaller pair of
+    # ids) becomes a new unit with the next free id and every non-overlapping occurrence is replaced left to right.
+    # Unknown units break a sentence (no pair spans them) unless ``skip_unknown`` drops them first.
+    def _base_ids(self, toks):
+        ids = []
+        for g in self._units(toks):
+            i = self._token_to_id.get(g)
+            if i is not None:
+                ids.append(i)
+            elif not self.skip_unknown:
+                ids.append(-1)
+        return ids
+
+    @staticmethod
+    def _merge_pair(arr, a, b, new_id):
+        import numpy as np
+        hit = np.nonzero((arr[:-1] == a) & (arr[1:] == b))[0]
+        if a == b and len(hit) > 1:                       # runs "a a a": the pairs must not overlap
+            keep, last = [], -2
+            for i in hit.tolist():
+                if i - last >= 2:
+                    keep.append(i)
+                    last = i
+            hit = np.asarray(keep, dtype=np.int64)
+        if len(hit) == 0:
+            return arr
+        arr = arr.copy()
+        arr[hit] = new_id
+        mask = np.ones(len(arr), dtype=bool)
+        mask[hit + 1] = False
+        return arr[mask]
+
+    def _fit_bpe(self, data, tokenizer):
+        import numpy as np
+        flat: List[int] = []
+        for toks in self._sentences(data, tokenizer):
+            flat.extend(self._base_ids(toks))
+            flat.append(-1)                                # sentence boundary: never part of a pair
+        arr = np.asarray(flat, dtype=np.int64)
+        self._merges = []
+        sep = " " if self.token_level_type == "Word" else ""
+        next_id = self.start_token_id + len(self._tokens)
+        for _ in range(self.num_bpe_units):
+            ok = (arr[:-1] >= 0) & (arr[1:] >= 0)
+            if not ok.any():
+                break
+            key = (arr[:-1][ok] << 32) | arr[1:][ok]
+            uniq, cnt = np.unique(key, return_counts=True)
+            # occurrences of (a, a) overlap in runs; count them as the replacement will see them
+            same = (uniq >> 32) == (uniq & 0xFFFFFFFF)
+            for k in np.nonzero(same & (cnt > 1))[0].tolist():
+                a = int(uniq[k] >> 32)
+                cnt[k] = (len(arr) - len(self._merge_pair(arr, a, a, -2)))
+            best = int(np.argmax(cnt))                     # np.unique sorts the keys: ties go to the smaller pair
+            if cnt[best] < 2:
+                break
+            a, b = int(uniq[best] >> 32), int(uniq[best] & 0xFFFFFFFF)
+            arr = self._merge_pair(arr, a, b, next_id)
+            self._merges.append((a, b, int(cnt[best])))
+            tok = self.get_token(a) + sep + self.get_token(b)
+            self._tokens.append(tok)
+            self._counts.append(int(cnt[best]))
+            self._token_to_id.setdefault(tok, next_id)
+            next_id += 1
+
+    def _apply_bpe(self, toks):
+        import numpy as np
+        arr = np.asarray(self._base_ids(toks) + [-1], dtype=np.int64)
+        first_new = self.start_token_id + len(self._tokens) - len(self._merges)
+        for k, (a, b, _) in enumerate(self._merges):
+            if len(arr) < 3:
+                break
+            arr = self._merge_pair(arr, a, b, first_new + k)
+        return arr[:-1].tolist()
 
     def apply(self, data, tokenizer: Optional[Tokenizer] = None, unknown_token_policy=None):
         """Token ids per document.  Unknown tokens are dropped ('Skip', default) or mapped to ``unknown_token_id``
@@ -174,6 +261,14 @@ class Dictionary:
         out = []
         for toks in self._sentences([data] if isinstance(data, str) else data, tokenizer):
             ids = []
+            if self.dictionary_type == "Bpe":
+                for i in self._apply_bpe(toks):
+                    if i >= 0:
+                        ids.append(i)
+                    elif policy == "Insert":
+                        ids.append(self.unknown_token_id)
+                out.append(ids)
+                continue
             for g in self._grams(toks):
                 i = self._token_to_id.get(g)
                 if i is not None:
@@ -228,6 +323,13 @@ class Dictionary:
             fh.write(json.dumps(opts) + "\n" + str(len(self._tokens)) + "\n")
             for i, (tok, c) in enumerate(zip(self._tokens, self._counts)):
                 fh.write(f"{self.start_token_id + i}\t{c}\t{tok}\n")
+        if self.dictionary_type == "Bpe":
+            if bpe_path is None:
+                raise CatBoostError("a Bpe dictionary is saved to two files: pass bpe_path")
+            first_new = self.start_token_id + len(self._tokens) - len(self._merges)
+            with open(bpe_path, "w", encoding="utf-8") as fh:          # left id, right id, count, text of the new unit
+                for k, (a, b, c) in enumerate(self._merges):
+                    fh.write(f"{a}\t{b}\t{c}\t{self.get_token(first_new + k)}\n")
         return self
 
     def load(self, frequency_dict_path, bpe_path=None):
@@ -246,6 +348,17 @@ class Dictionary:
                 _id, c, tok = fh.readline().rstrip("\n").split("\t", 2)
                 self._tokens.append(tok)
                 self._counts.append(int(c))
-        self._token_to_id = {g: self.start_token_id + i for i, g in enumerate(self._tokens)}
+        self._token_to_id = {}
+        for i, g in enumerate(self._tokens):
+            self._token_to_id.setdefault(g, self.start_token_id + i)
         self._fitted = True
+        self._merges = []
+        if bpe_path is not None:
+            self.dictionary_type = "Bpe"
+            with open(bpe_path, encoding="utf-8") as fh:
+                for line in fh:
+                    a, b, c, _tok = line.rstrip("\n").split("\t", 3)
+                    self._merges.append((int(a), int(b), int(c)))
+            self.num_bpe_units = len(self._merges)
+        return self
         return self

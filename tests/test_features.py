@@ -1091,3 +1091,29 @@ def test_sage_values_rank_the_informative_features():
     assert sage.shape == (5,)
     assert int(np.argmax(sage)) == 1 and sage[1] > sage[3] > max(sage[0], sage[2], sage[4])
     assert abs(sage[0]) < 0.1 * sage[1]
+
+
+def test_bpe_dictionary(tmp_path):
+    """Byte-pair encoding over letters: the most frequent neighbouring pair becomes a unit, repeatedly; applying the
+    dictionary replays the merges in the order they were learned; two files round-trip."""
+    from catboost_b200.text_processing import Dictionary, Tokenizer
+    corpus = ["low low low low low", "lower lower", "newest newest newest newest newest newest", "widest widest widest"]
+    d = Dictionary(token_level_type="Letter", occurence_lower_bound=1, dictionary_type="Bpe", num_bpe_units=6)
+    d.fit(corpus, Tokenizer(lowercasing=True))
+    base = d.size - 6
+    assert base == len(set("".join(corpus).replace(" ", ""))) + 1          # letters + the end-of-word mark
+    new_units = d.get_top_tokens()[base:]
+    assert new_units[0] in ("es", "st", "we", "lo", "ow", "w ")               # a frequent pair first
+    assert any(len(u) >= 3 for u in new_units)                                  # merges build on merges
+    ids = d.apply(["newest lowest"], Tokenizer(lowercasing=True))[0]
+    plain = Dictionary(token_level_type="Letter", occurence_lower_bound=1).fit(corpus, Tokenizer(lowercasing=True))
+    assert len(ids) < len(plain.apply(["newest lowest"], Tokenizer(lowercasing=True))[0])
+    assert "".join(d.get_tokens(ids)) == "newest lowest "
+    f1, f2 = str(tmp_path / "dict.tsv"), str(tmp_path / "bpe.tsv")
+    d.save(f1, f2)
+    d2 = Dictionary().load(f1, f2)
+    assert d2.apply(["newest lowest"], Tokenizer(lowercasing=True))[0] == ids
+    # a run of equal letters: pairs are replaced left to right without overlap
+    r = Dictionary(token_level_type="Letter", occurence_lower_bound=1, dictionary_type="Bpe", num_bpe_units=1,
+                   end_of_word_policy="Skip").fit(["aaaaa aaaa"], Tokenizer())
+    assert [r.get_token(i) for i in r.apply(["aaaaa"], Tokenizer())[0]] == ["aa", "aa", "a"]
