@@ -65,8 +65,8 @@ RESOURCE_HINTS = {"used_ram_limit", "gpu_ram_part", "pinned_memory_size", "devic
 # Options of the reference whose behaviour is not implemented: a value that differs from the default is refused with an
 # error instead of being silently dropped.
 NOT_IMPLEMENTED = {"counter_calc_method", "ctr_leaf_count_limit", "store_all_simple_ctr", "final_ctr_computation_mode",
-                   "per_feature_ctr", "ctr_description", "ctr_history_unit", "approx_on_full_history", "sampling_frequency",
-                   "sampling_unit", "posterior_sampling", "penalties_coefficient", "first_feature_use_penalties",
+                   "ctr_history_unit", "approx_on_full_history", "sampling_frequency",
+                   "penalties_coefficient", "first_feature_use_penalties",
                    "per_object_feature_penalties", "fixed_binary_splits", "sparse_features_conflict_fraction",
                    "tokenizers", "dictionaries"}
 
@@ -277,6 +277,23 @@ def resolve_options(params: Optional[dict], default_loss: str = "RMSE", n_rows: 
             raise CatBoostError("bagging_temperature requires bootstrap_type='Bayesian'")
         if o.subsample is None:
             o.subsample = {"Bernoulli": 0.66, "Poisson": 0.66, "MVS": 0.8, "No": 1.0}[o.bootstrap_type]
+    if o.sampling_unit not in (None, "Object", "Group"):
+        raise CatBoostError(f"unknown sampling_unit {o.sampling_unit!r}")
+    if o.sampling_unit == "Group" and o.bootstrap_type == "MVS":
+        raise CatBoostError("sampling_unit='Group' is not used with the MVS bootstrap")
+    if o.posterior_sampling:
+        # catboost/libs/train_lib/options_helper.cpp:376-392 and catboost_options.cpp:744-751: Langevin boosting whose
+        # diffusion temperature is the number of objects and whose shrink rate is 1 / (2 n)
+        if "langevin" in o["_user_keys"] and not o.langevin:
+            raise CatBoostError("posterior_sampling requires Langevin boosting")
+        if "diffusion_temperature" in o["_user_keys"]:
+            raise CatBoostError("diffusion_temperature is set by posterior_sampling")
+        if o.model_shrink_mode not in (None, "Constant"):
+            raise CatBoostError("posterior_sampling requires the Constant model shrink mode")
+        o.langevin = True
+        if n_rows:
+            o.diffusion_temperature = float(n_rows)
+            o.model_shrink_rate = 1.0 / (2.0 * float(n_rows))
     # learning rate (options_helper.cpp:269 auto-tunes from the dataset size; this is the same functional form)
     if o.learning_rate is None:
         o.learning_rate = auto_learning_rate(lname, int(o.iterations), n_rows, has_eval) if n_rows else 0.03

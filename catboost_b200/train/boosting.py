@@ -359,7 +359,8 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
 
     # ---- features --------------------------------------------------------------------------------------
     with prof.span("quantization"):
-        plan = plan_features(o, train_pool, ctx, getattr(train_pool, "_quantized", None))
+        with prof.span("quantization.borders"):
+            plan = plan_features(o, train_pool, ctx, getattr(train_pool, "_quantized", None))
         if o.output_borders and (ctx is None or ctx.rank == 0):
             # the border grid that training uses, one "float_feature_index<TAB>border" line each (output_borders option)
             with open(o.output_borders, "w") as fh:
@@ -375,8 +376,9 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
         extra_feats, extra_cols, eval_extra_cols = [], None, [None] * len(eval_pools)
         if plan.ctr_plan is not None:
             from .ctr import compute_ctr_features
-            ctr_state = compute_ctr_features(plan.ctr_plan, o, train_pool, y_train, w_train, eval_pools, device, ctx,
-                                             codec)
+            with prof.span("quantization.ctrs"):
+                ctr_state = compute_ctr_features(plan.ctr_plan, o, train_pool, y_train, w_train, eval_pools, device, ctx,
+                                                 codec)
             extra_feats, extra_cols, eval_extra_cols = ctr_state.flat_features, ctr_state.train_bins, ctr_state.eval_bins
         store, h2d_bytes = build_store(plan, train_pool, device, fweights, extra_feats, extra_cols)
         if store.F == 0 or all(f.n_bins <= 1 for f in store.features):

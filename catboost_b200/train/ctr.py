@@ -80,7 +80,7 @@ def _parse_ctr_description(desc: str, default_priors):
 
 def plan_ctrs(o, pool: Pool, ctr_cats: List[int], ctx) -> CtrPlan:
     gpu = o.task_type == "GPU"
-    simple = o.simple_ctr
+    simple = o.simple_ctr if o.simple_ctr is not None else o.ctr_description
     if simple is None:
         simple = ["Borders", "Counter"]          # FeatureFreq is the reference's GPU name for the count-based CTR
     if isinstance(simple, str):
@@ -108,8 +108,17 @@ def plan_ctrs(o, pool: Pool, ctr_cats: List[int], ctx) -> CtrPlan:
                 else:
                     specs.append(CtrSpec(tuple(projection), ctype, num, den, 0, bc or int(o.ctr_border_count)))
 
+    # per_feature_ctr: "<categorical feature (dataset column)>:<CTR description>", several entries per feature allowed
+    per_feature = {}
+    for item in ([o.per_feature_ctr] if isinstance(o.per_feature_ctr, str) else list(o.per_feature_ctr or [])):
+        fid, _, desc = str(item).partition(":")
+        if not desc or not fid.strip().lstrip("-").isdigit():
+            raise CatBoostError(f"per_feature_ctr entry {item!r}: expected '<feature index>:<CTR description>'")
+        if int(fid) not in list(pool.cat_feature_indices):
+            raise CatBoostError(f"per_feature_ctr: feature {int(fid)} is not categorical")
+        per_feature.setdefault(int(fid), []).append(desc)
     for c in ctr_cats:
-        add((c,), simple)
+        add((c,), per_feature.get(int(pool.cat_feature_indices[c]), simple))
     complexity = int(o.max_ctr_complexity)
     if complexity >= 2 and len(ctr_cats) >= 2:
         # Static combinations: pairs (and triples when asked) among the categorical features of lowest cardinality.
@@ -292,6 +301,28 @@ class _KernelGroup:
         return out
 
 
+_STAGE_TIMES = {}          # developer aid (CB200_CTR_TIMING=1): seconds per stage of the CTR computation, rank 0 prints them
+
+
+class _Stage:
+    def __init__(self, name, dev):
+        self.name, self.dev, self.on = name, dev, os.environ.get("CB200_CTR_TIMING") == "1"
+
+    def __enter__(self):
+        if self.on:
+            import time
+            if self.dev.type == "cuda":
+                torch.cuda.synchronize(self.dev)
+            self.t0 = time.perf_counter()
+
+    def __exit__(self, *exc):
+        if self.on:
+            import time
+            if self.dev.type == "cuda":
+                torch.cuda.synchronize(self.dev)
+            _STAGE_TIMES[self.name] = _STAGE_TIMES.get(self.name, 0.0) + time.perf_counter() - self.t0
+
+
 class _ShardedGroup:
     """One projection on several ranks without mirroring the categorical data: every category belongs to the rank its
     hash maps to.  A rank sends (hash, permutation position, target class) of its rows to the owners (one all-to-all),
@@ -306,34 +337,54 @@ class _ShardedGroup:
         self.ctx, self.dist = ctx, dist
         dev = h.device
         R = ctx.world
-        owner = (((h >> 20) ^ h) & 0x7FFFFFFF) % R
-        _, self.perm = torch.sort(owner, stable=True)
-        send = torch.bincount(owner, minlength=R)
-        recv = torch.empty_like(send)
-        dist.all_to_all_single(recv, send, group=ctx.group)
-        self.send_counts, self.recv_counts = [int(v) for v in send.tolist()], [int(v) for v in recv.tolist()]
+        with _Stage("shard: owner sort", dev):
+            owner = (((h >> 20) ^ h) & 0x7FFFFFFF) % R
+            _, self.perm = torch.sort(owner, stable=True)
+            send = torch.bincount(owner, minlength=R)
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send, group=ctx.group)
+            self.send_counts, self.recv_counts = [int(v) for v in send.tolist()], [int(v) for v in recv.tolist()]
         self.n_local = int(h.shape[0])
-        h_r, pos_r, cls_r = self._forward(h[self.perm]), self._forward(pos[self.perm]), self._forward(cls[self.perm])
+        with _Stage("shard: forward exchange", dev):
+            h_r, pos_r, cls_r = self._forward(h[self.perm]), self._forward(pos[self.perm]), self._forward(cls[self.perm])
         self.m = int(h_r.shape[0])
         self.inner = None
         ncols = 1 + len(need_tb)
         if self.m:
-            order_t = torch.argsort(pos_r)
-            self.inner = (_KernelGroup(h_r, order_t, cls_r.to(torch.uint8), need_tb, want_prefix) if dev.type == "cuda"
-                          else _TensorGroup(h_r, order_t, cls_r, need_tb, want_prefix))
-            uniq_l, totals_l = self.inner.uniq_t.cpu().numpy(), self.inner.totals.cpu().numpy()
+            with _Stage("shard: position sort", dev):
+                order_t = torch.argsort(pos_r)
+            with _Stage("shard: group (sort + scan)", dev):
+                self.inner = (_KernelGroup(h_r, order_t, cls_r.to(torch.uint8), need_tb, want_prefix) if dev.type == "cuda"
+                              else _TensorGroup(h_r, order_t, cls_r, need_tb, want_prefix))
+            uniq_l, totals_l = self.inner.uniq_t, self.inner.totals.float()
         else:
-            uniq_l, totals_l = np.zeros(0, np.int64), np.zeros((ncols, 0), np.float32)
-        parts = ctx.all_gather_object((uniq_l, totals_l))
-        uniq = np.concatenate([p_[0] for p_ in parts])
-        totals = np.concatenate([p_[1] for p_ in parts], axis=1)
-        o_ = np.argsort(uniq, kind="stable")
-        self.uniq_t = torch.from_numpy(uniq[o_]).to(dev)
-        self.totals = torch.from_numpy(np.ascontiguousarray(totals[:, o_])).to(dev)
+            uniq_l = torch.zeros(0, dtype=torch.int64, device=dev)
+            totals_l = torch.zeros((ncols, 0), dtype=torch.float32, device=dev)
+        # the model's table = the owners' tables side by side (their hash sets are disjoint), sorted by hash; padded
+        # tensor collectives on the training device, no pickling of arrays that can have one entry per document
+        t_tables = _Stage("shard: table gather", dev)
+        t_tables.__enter__()
+        sizes = [int(v) for v in ctx.all_gather_object(int(uniq_l.shape[0]))]
+        cap = max(max(sizes), 1)
+        ubuf = torch.zeros(cap, dtype=torch.int64, device=dev)
+        ubuf[: uniq_l.shape[0]] = uniq_l
+        tbuf = torch.zeros((ncols, cap), dtype=torch.float32, device=dev)
+        tbuf[:, : uniq_l.shape[0]] = totals_l
+        uall = [torch.empty_like(ubuf) for _ in sizes]
+        tall = [torch.empty_like(tbuf) for _ in sizes]
+        dist.all_gather(uall, ubuf, group=ctx.group)
+        dist.all_gather(tall, tbuf, group=ctx.group)
+        uniq = torch.cat([u[:c] for u, c in zip(uall, sizes)])
+        totals = torch.cat([t[:, :c] for t, c in zip(tall, sizes)], dim=1)
+        del uall, tall, ubuf, tbuf
+        self.uniq_t, o_ = torch.sort(uniq)
+        self.totals = totals[:, o_].contiguous()
+        t_tables.__exit__()
         # items of this owner that belong to the border sample (given as permutation positions)
         self.sample_items = None
         if sample_pos is not None:
-            self.sample_items = torch.nonzero(torch.isin(pos_r, sample_pos)).squeeze(1)
+            with _Stage("shard: sample membership", dev):
+                self.sample_items = torch.nonzero(torch.isin(pos_r, sample_pos)).squeeze(1)
 
     def _exchange(self, t, send_counts, recv_counts, width=1):
         out = torch.empty((sum(recv_counts) * width,), dtype=t.dtype, device=t.device)
@@ -392,6 +443,9 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
     n_local = train_pool.num_row()
     dist_mode = ctx is not None and ctx.is_distributed
     sharded = dist_mode and os.environ.get("CB200_CTR_GATHER") != "1"
+    if os.environ.get("CB200_CTR_SHARDED") == "1" and ctx is not None and not dist_mode:
+        import torch.distributed as dist
+        sharded = dist.is_available() and dist.is_initialized()       # the sharded code on a group of one rank (profiling)
     if dist_mode:
         counts = [int(c) for c in ctx.all_gather_object(n_local)]
         lo_row = sum(counts[: ctx.rank])
@@ -455,18 +509,21 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
         need_tb = sorted({s.target_border_idx for s in specs if s.ctr_type in TARGET_CTRS})
         want_prefix = any(s.ctr_type in TARGET_CTRS for s in specs)
         if sharded:
-            h_train_t = projection_hash_t([_cat_column_t(train_pool, c, dev) for c in proj])
+            with _Stage("hash", dev):
+                h_train_t = projection_hash_t([_cat_column_t(train_pool, c, dev) for c in proj])
             grp = _ShardedGroup(ctx, h_train_t, pos_local, cls_local, need_tb, want_prefix, sample_pos)
         else:
-            h_train_t = projection_hash_t([gathered_cat(c) for c in proj])
-        if sharded:
-            pass
-        elif dev.type == "cuda":
-            grp = _KernelGroup(h_train_t, order_t, cls_u8, need_tb, want_prefix)
-        else:
-            grp = _TensorGroup(h_train_t, order_t, cls_t, need_tb, want_prefix)
+            with _Stage("hash", dev):
+                h_train_t = projection_hash_t([gathered_cat(c) for c in proj])
+            with _Stage("group (sort + scan)", dev):
+                if dev.type == "cuda":
+                    grp = _KernelGroup(h_train_t, order_t, cls_u8, need_tb, want_prefix)
+                else:
+                    grp = _TensorGroup(h_train_t, order_t, cls_t, need_tb, want_prefix)
         uniq_t, totals = grp.uniq_t, grp.totals
         U = int(uniq_t.numel())
+        t_host = _Stage("tables to host", dev)
+        t_host.__enter__()
         # model tables want the hashes in unsigned order: the signed-sorted list is that order rotated
         rot = int((uniq_t < 0).sum().item())
         uniq_s = uniq_t.cpu().numpy().view(np.uint64)
@@ -474,6 +531,7 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
         totals_s = totals.cpu().numpy()
         totals_np = np.concatenate([totals_s[:, rot:], totals_s[:, :rot]], axis=1)
         max_count = float(totals_np[0].max()) if U else 1.0
+        t_host.__exit__()
         eval_keys = []
         for ep in eval_pools:
             he_t = projection_hash_t([_cat_column_t(ep, c, dev) for c in proj])
@@ -494,8 +552,11 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
             else:   # FeatureFreq
                 descs.append((1, 0, float(s.prior_num), float(s.prior_denom), float(n) + s.prior_denom))
         target_pos = [k for k, d in enumerate(descs) if d[0] == 0]
-        ranges = dict(zip(target_pos, grp.value_ranges([descs[k] for k in target_pos]))) if target_pos else {}
+        with _Stage("value ranges", dev):
+            ranges = dict(zip(target_pos, grp.value_ranges([descs[k] for k in target_pos]))) if target_pos else {}
         all_borders = []
+        t_b = _Stage("count-type borders", dev)
+        t_b.__enter__()
         for k, (s, d) in enumerate(zip(specs, descs)):
             if d[0] == 0:
                 # Uniform grid between the smallest and largest learn value (same arithmetic as the host routine:
@@ -511,8 +572,12 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
                 borders, _ = select_borders(sample.cpu().numpy().reshape(-1, 1), s.border_count, "GreedyLogSum")
                 b = np.asarray(borders[0], dtype=np.float32)
             all_borders.append(b)
+        t_b.__exit__()
         keep = [k for k, b in enumerate(all_borders) if len(b)]
-        cols_out = grp.binarize([descs[k] for k in keep], [all_borders[k] for k in keep], lo_row, n_local) if keep else []
+        with _Stage("bucketing", dev):
+            cols_out = grp.binarize([descs[k] for k in keep], [all_borders[k] for k in keep], lo_row, n_local) if keep else []
+        t_m = _Stage("eval columns + model tables", dev)
+        t_m.__enter__()
         for k, col in zip(keep, cols_out):
             s, d, b = specs[k], descs[k], all_borders[k]
             train_cols.append(col)
@@ -537,6 +602,11 @@ def compute_ctr_features(plan: CtrPlan, o, train_pool: Pool, y_train, w_train, e
                                              totals_np[0].astype(np.float64), totals_np[0].astype(np.float64),
                                              max_count if s.ctr_type == "Counter" else float(n)))
             flat.append(FlatFeature("ctr", ctr_index, borders=b, n_bins=len(b) + 1, ctr=s))
+        t_m.__exit__()
+    if _STAGE_TIMES and (ctx is None or ctx.rank == 0):
+        import sys
+        print("CTR stages (s):", {k: round(v, 3) for k, v in _STAGE_TIMES.items()}, "projections:", len(by_proj), file=sys.stderr)
+        _STAGE_TIMES.clear()
     train_bins = torch.stack(train_cols) if train_cols else torch.zeros((0, n_local), dtype=torch.uint8, device=dev)
     eval_bins = [torch.stack(c) if c else torch.zeros((0, ep.num_row()), dtype=torch.uint8, device=dev)
                  for c, ep in zip(eval_cols, eval_pools)]

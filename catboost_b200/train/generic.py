@@ -117,6 +117,7 @@ class GenericLearner:
         self.leaf = torch.zeros(store.npad, dtype=torch.int16, device=self.dev)
         self.use_count = int(opts.min_data_in_leaf) > 1
         self.monotone = None          # float tensor [F] in {-1, 0, +1} per flat feature, set by set_monotone()
+        self.group_of_doc = None      # int64 [n] query number of every document: set for sampling_unit='Group'
         self.n_total = store.n
         if ctx is not None and ctx.is_distributed:
             t = torch.tensor([store.n], dtype=torch.float64, device=self.dev)
@@ -142,6 +143,20 @@ class GenericLearner:
         bt = o.bootstrap_type
         if bt == "No":
             return None
+        if self.group_of_doc is not None and bt in ("Bayesian", "Bernoulli", "Poisson"):
+            # sampling_unit='Group' (catboost/private/libs/algo/bootstrap? fold sampling by query): one draw per
+            # query, shared by its documents
+            ng = int(self.group_of_doc.max().item()) + 1 if n else 0
+            if bt == "Bayesian":
+                t = float(o.bagging_temperature)
+                if t == 0:
+                    return None
+                g = (-torch.log(self._rand(ng).clamp_min(1e-20))) ** t
+            elif bt == "Bernoulli":
+                g = (self._rand(ng) < float(o.subsample)).float()
+            else:
+                g = torch.poisson(torch.full((ng,), float(o.subsample)), generator=self.gen).to(self.dev)
+            return g[self.group_of_doc]
         if bt == "Bayesian":
             t = float(o.bagging_temperature)
             if t == 0:

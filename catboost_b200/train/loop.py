@@ -91,6 +91,7 @@ def _use_fast_engine(o, objective, store, dims) -> bool:
             and float(o.rsm) >= 1.0 and int(o.min_data_in_leaf) <= 1
             and (o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson") or (o.bootstrap_type == "MVS" and dims == 1))
             and not o.langevin and not o.monotone_constraints and not o.model_shrink_rate
+            and str(o.sampling_unit or "Object") == "Object"
             and str(o.random_score_type) != "Gumbel")
 
 
@@ -151,6 +152,11 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
     octx = ObjectiveContext(train_pool, dev)
     eval_approx = [torch.from_numpy(np.ascontiguousarray(b)).to(dev, f32) for b in base_evals]
     learner = GenericLearner(store, o, dims, ctx, seed=int(o.random_seed))
+    if str(o.sampling_unit or "Object") == "Group":
+        if train_pool.group_id is None:
+            raise CatBoostError("sampling_unit='Group' needs group_id")
+        off = train_pool.group_offsets()
+        learner.group_of_doc = torch.from_numpy(np.repeat(np.arange(len(off) - 1), np.diff(off))).to(dev)
     monotone_flat = None
     if o.monotone_constraints:
         mono = _parse_monotone(o.monotone_constraints, train_pool)

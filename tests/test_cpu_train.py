@@ -169,6 +169,46 @@ def test_option_handling_eval_fraction_output_borders_and_refusals(tmp_path):
     assert np.allclose(m2.predict(X, prediction_type="RawFormulaVal"), m.predict(X, prediction_type="RawFormulaVal"))
     # options without an implementation are refused when set to something else than their default, hints are accepted
     with pytest.raises(cb.CatBoostError, match="not implemented"):
-        cb.CatBoostClassifier(iterations=2, sampling_unit="Group", verbose=False, allow_writing_files=False).fit(X, y)
+        cb.CatBoostClassifier(iterations=2, sampling_frequency="PerTreeLevel", verbose=False, allow_writing_files=False).fit(X, y)
     cb.CatBoostClassifier(iterations=2, used_ram_limit="4gb", sampling_unit="Object", verbose=False,
                           allow_writing_files=False).fit(X, y)
+
+
+def test_posterior_sampling_group_sampling_and_per_feature_ctr():
+    import catboost_b200 as cb
+    from catboost_b200.params import resolve_options
+    o = resolve_options(dict(posterior_sampling=True), "RMSE", 500)
+    assert o.langevin and o.diffusion_temperature == 500.0 and abs(o.model_shrink_rate - 1e-3) < 1e-12
+    with pytest.raises(cb.CatBoostError):
+        resolve_options(dict(posterior_sampling=True, diffusion_temperature=5.0), "RMSE", 500)
+    rng = np.random.default_rng(2)
+    n = 1200
+    X = rng.standard_normal((n, 4)).astype(np.float32)
+    y = (X[:, 0] + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    m = cb.CatBoostRegressor(iterations=30, depth=3, posterior_sampling=True, verbose=False, allow_writing_files=False)
+    m.fit(X, y)
+    assert np.corrcoef(m.predict(X), y)[0, 1] > 0.9
+    # one bootstrap draw per query
+    gid = np.repeat(np.arange(n // 10), 10)
+    r = cb.CatBoostRanker(iterations=10, depth=3, loss_function="QueryRMSE", sampling_unit="Group", bootstrap_type="Bernoulli",
+                          subsample=0.5, verbose=False, allow_writing_files=False)
+    r.fit(X, y, group_id=gid)
+    assert np.corrcoef(r.predict(X), y)[0, 1] > 0.5
+    with pytest.raises(cb.CatBoostError):
+        cb.CatBoostRegressor(iterations=2, sampling_unit="Group", verbose=False, allow_writing_files=False).fit(X, y)
+    # per-feature CTR descriptions override simple_ctr for that feature only
+    c = rng.integers(0, 30, n)
+    c2 = rng.integers(0, 25, n)
+    Xo = np.empty((n, 3), dtype=object)
+    Xo[:, 0], Xo[:, 1], Xo[:, 2] = X[:, 0], c, c2
+    yc = (rng.standard_normal(30)[c] + 0.3 * rng.standard_normal(n) > 0).astype(np.float32)
+    m = cb.CatBoostClassifier(iterations=20, depth=3, per_feature_ctr=["1:Counter"], max_ctr_complexity=1, one_hot_max_size=2,
+                              verbose=False, allow_writing_files=False)
+    m.fit(Xo, yc, cat_features=[1, 2])
+    kinds = {}
+    for cf in m._model.ctrs:
+        kinds.setdefault(tuple(cf.cat_features), set()).add(cf.ctr_type)
+    assert kinds[(0,)] == {"Counter"} and "Borders" in kinds[(1,)]
+    with pytest.raises(cb.CatBoostError):
+        cb.CatBoostClassifier(iterations=2, per_feature_ctr=["0:Counter"], verbose=False, allow_writing_files=False).fit(
+            Xo, yc, cat_features=[1, 2])
