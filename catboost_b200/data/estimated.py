@@ -252,15 +252,79 @@ class _EmbeddingCalcers:
 class EstimatedFeatures:
     """All text / embedding columns of a pool -> one float matrix."""
 
-    def __init__(self, text_processing: Optional[dict] = None, seed: int = 0):
-        tp = text_processing or {}
+    def __init__(self, text_processing: Optional[dict] = None, seed: int = 0, tokenizers=None, dictionaries=None,
+                 feature_calcers=None):
+        """``tokenizers`` / ``dictionaries`` / ``feature_calcers`` are the estimator keywords of the same names; the same
+        keys (and ``feature_processing``) may sit inside ``text_processing`` (the reference's JSON layout,
+        catboost/private/libs/options/text_processing_options.cpp).  Every (dictionary, calcer list) pair of the
+        processing description yields its own block of features for every text column."""
+        tp = dict(text_processing or {})
         self.max_dictionary_size = int(tp.get("max_dictionary_size", 50000))
         self.occurrence_lower_bound = int(tp.get("occurrence_lower_bound", 3))
         self.top_tokens = int(tp.get("top_tokens_count", 2000))
-        self.text_calcers = tuple(tp.get("feature_calcers", ("BoW", "NaiveBayes", "BM25")))
+        calc_default = feature_calcers if feature_calcers is not None else tp.get("feature_calcers", ("BoW", "NaiveBayes", "BM25"))
+        self.text_calcers = tuple(self._calcer_names(calc_default))
         self.embedding_calcers = tuple(tp.get("embedding_calcers", ("LDA", "KNN")))
         self.seed = int(seed)
         self.text, self.emb, self.names = [], [], []
+        # tokenizer: the first description (one tokenizer for all dictionaries)
+        toks = tokenizers if tokenizers is not None else tp.get("tokenizers")
+        tk = self._kv(toks[0]) if toks else {}
+        self.lowercasing = str(tk.get("lowercasing", "true")).lower() in ("1", "true", "yes")
+        self.delimiter = tk.get("delimiter") if str(tk.get("separator_type", "BySense")) == "ByDelimiter" else None
+        # dictionaries: (id, max size, occurrence lower bound, gram order)
+        self.dict_specs = []
+        for d in (dictionaries if dictionaries is not None else tp.get("dictionaries") or []):
+            kv = self._kv(d, id_key="dictionary_id")
+            self.dict_specs.append((str(kv.get("dictionary_id", f"dict{len(self.dict_specs)}")),
+                                    int(kv.get("max_dictionary_size", self.max_dictionary_size)),
+                                    int(kv.get("occurrence_lower_bound", kv.get("occurence_lower_bound", self.occurrence_lower_bound))),
+                                    int(kv.get("gram_order", 1))))
+        if not self.dict_specs:
+            self.dict_specs = [("Word", self.max_dictionary_size, self.occurrence_lower_bound, 1)]
+        # processing: which calcers run on which dictionary
+        self.processing = []
+        fp = tp.get("feature_processing")
+        if isinstance(fp, dict) and fp:
+            known = {d[0] for d in self.dict_specs}
+            for item in fp.get("default", next(iter(fp.values()))):
+                for name in item.get("dictionaries_names", [d[0] for d in self.dict_specs]):
+                    if name not in known:
+                        raise ValueError(f"feature_processing names the dictionary {name!r}, which is not described")
+                    self.processing.append((name, tuple(self._calcer_names(item.get("feature_calcers", self.text_calcers)))))
+        else:
+            self.processing = [(d[0], self.text_calcers) for d in self.dict_specs]
+
+    @staticmethod
+    def _kv(desc, id_key=None):
+        """A description given as a dict or as 'Id:key=value,key=value'."""
+        if isinstance(desc, dict):
+            return {str(k): v for k, v in desc.items()}
+        head, _, rest = str(desc).partition(":")
+        out = {id_key: head} if id_key and "=" not in head else {}
+        for part in ([head] if "=" in head else []) + [p for p in rest.split(",") if p]:
+            k, _, v = part.partition("=")
+            out[k.strip()] = v.strip()
+        return out
+
+    def _calcer_names(self, calcers):
+        out = []
+        for c in ([calcers] if isinstance(calcers, str) else list(calcers)):
+            name, _, rest = str(c).partition(":")
+            for part in [p for p in rest.split(",") if p]:
+                k, _, v = part.partition("=")
+                if k.strip() == "top_tokens_count":
+                    self.top_tokens = int(v)
+            if name not in ("BoW", "NaiveBayes", "BM25"):
+                raise ValueError(f"unknown text feature calcer {name!r}")
+            out.append(name)
+        return out
+
+    def _tokens(self, col):
+        if self.delimiter is not None:
+            return [[t for t in ("" if v is None else (str(v).lower() if self.lowercasing else str(v))).split(self.delimiter) if t]
+                    for v in col]
+        return [tokenize(v, self.lowercasing) for v in col]
 
     def fit(self, pool, target: np.ndarray, n_classes: int):
         """target: class index per row for classification (n_classes >= 2), else the numeric target (n_classes = 0)."""
@@ -271,15 +335,22 @@ class EstimatedFeatures:
         mats = []
         self.text_flat = list(pool.text_feature_indices)
         self.emb_flat = list(pool.embedding_feature_indices)
+        specs = {d[0]: d for d in self.dict_specs}
         for j, col in enumerate(pool.text_data):
-            toks = [tokenize(t) for t in col]
-            d = _Dictionary(self.max_dictionary_size, min(self.occurrence_lower_bound, max(1, n // 20)), 1).fit(toks)
-            indptr, indices = d.encode(toks)
-            calc = _TextCalcers(self.top_tokens, self.text_calcers).fit(d, indptr, indices, cls, n_classes)
-            self.text.append((d, calc))
-            inv = {i: g for g, i in d.ids.items()}
-            self.names += calc.names(f"text{self.text_flat[j]}", inv)
-            mats.append(calc.transform_learn(indptr, indices, cls, blocks))
+            toks = self._tokens(col)
+            built = {}
+            for name, calcers in self.processing:
+                _, max_size, lower, gram = specs[name]
+                if name not in built:
+                    d = _Dictionary(max_size, min(lower, max(1, n // 20)), gram).fit(toks)
+                    built[name] = (d,) + d.encode(toks)
+                d, indptr, indices = built[name]
+                calc = _TextCalcers(self.top_tokens, calcers).fit(d, indptr, indices, cls, n_classes)
+                self.text.append((j, d, calc))
+                inv = {i: g for g, i in d.ids.items()}
+                prefix = f"text{self.text_flat[j]}" if len(self.processing) == 1 else f"text{self.text_flat[j]}.{name}"
+                self.names += calc.names(prefix, inv)
+                mats.append(calc.transform_learn(indptr, indices, cls, blocks))
         for j, E in enumerate(pool.embedding_data):
             calc = _EmbeddingCalcers(5, self.embedding_calcers).fit(np.asarray(E, dtype=np.float32), cls if n_classes else target.astype(np.float64), n_classes)
             self.emb.append(calc)
@@ -290,10 +361,14 @@ class EstimatedFeatures:
 
     def transform(self, pool) -> np.ndarray:
         mats = []
-        if len(pool.text_data) != len(self.text) or len(pool.embedding_data) != len(self.emb):
+        n_text = len({t[0] for t in self.text})
+        if len(pool.text_data) != n_text or len(pool.embedding_data) != len(self.emb):
             raise ValueError("the data does not have the text / embedding columns the model was trained with")
-        for (d, calc), col in zip(self.text, pool.text_data):
-            indptr, indices = d.encode([tokenize(t) for t in col])
+        tok_cache = {}
+        for j, d, calc in self.text:
+            if j not in tok_cache:
+                tok_cache[j] = self._tokens(pool.text_data[j])
+            indptr, indices = d.encode(tok_cache[j])
             mats.append(calc.transform(indptr, indices))
         for calc, E in zip(self.emb, pool.embedding_data):
             mats.append(calc.transform(np.asarray(E, dtype=np.float32)))

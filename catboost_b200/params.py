@@ -67,8 +67,7 @@ RESOURCE_HINTS = {"used_ram_limit", "gpu_ram_part", "pinned_memory_size", "devic
 NOT_IMPLEMENTED = {"counter_calc_method", "ctr_leaf_count_limit", "store_all_simple_ctr", "final_ctr_computation_mode",
                    "ctr_history_unit", "approx_on_full_history", "sampling_frequency",
                    "penalties_coefficient", "first_feature_use_penalties",
-                   "per_object_feature_penalties", "fixed_binary_splits", "sparse_features_conflict_fraction",
-                   "tokenizers", "dictionaries"}
+                   "per_object_feature_penalties", "fixed_binary_splits", "sparse_features_conflict_fraction"}
 
 POINTWISE_LOSSES = {"RMSE", "Logloss", "CrossEntropy", "Poisson", "MAE", "Quantile", "LogLinQuantile", "MAPE", "Huber",
                     "Lq", "Expectile", "Tweedie", "LogCosh"}

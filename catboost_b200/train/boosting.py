@@ -351,7 +351,8 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
         from ..data.estimated import EstimatedFeatures
         with prof.span("estimated_features"):
             estimators = EstimatedFeatures(o.text_processing if isinstance(o.text_processing, dict) else None,
-                                           seed=int(o.random_seed))
+                                           seed=int(o.random_seed), tokenizers=o.tokenizers, dictionaries=o.dictionaries,
+                                           feature_calcers=o.feature_calcers)
             n_cls = (codec.n_classes or 2) if objective.is_classification else 0
             learn = estimators.fit(train_pool, np.asarray(y_train), int(n_cls))
             train_pool = train_pool.with_estimated(learn, estimators.names)

@@ -1117,3 +1117,44 @@ def test_bpe_dictionary(tmp_path):
     r = Dictionary(token_level_type="Letter", occurence_lower_bound=1, dictionary_type="Bpe", num_bpe_units=1,
                    end_of_word_policy="Skip").fit(["aaaaa aaaa"], Tokenizer())
     assert [r.get_token(i) for i in r.apply(["aaaaa"], Tokenizer())[0]] == ["aa", "aa", "a"]
+
+
+def test_text_features_with_dictionaries_and_tokenizers(tmp_path):
+    """`dictionaries` (word + bi-gram), `tokenizers` and `feature_calcers`: every dictionary yields its own block of
+    features; a signal that only a word pair carries is found through the bi-gram dictionary; the model file round-trips."""
+    import catboost_b200 as cb
+    rng = np.random.default_rng(8)
+    words = ["red", "green", "blue", "cat", "dog", "bird", "big", "small"]
+    n = 1500
+    docs, y = [], []
+    for _ in range(n):
+        w = list(rng.choice(words, size=6))
+        lab = int(rng.random() < 0.5)
+        if lab:                                  # the label is carried by the ordered pair "big dog" only
+            k = int(rng.integers(0, 5))
+            w[k], w[k + 1] = "big", "dog"
+        else:
+            w = [t for t in w if t != "dog"] + ["dog", "big"]
+        docs.append(" ".join(w))
+        y.append(lab)
+    X = np.empty((n, 2), dtype=object)
+    X[:, 0] = rng.standard_normal(n)
+    X[:, 1] = docs
+    y = np.asarray(y, dtype=np.float32)
+    kw = dict(iterations=40, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False)
+    uni = cb.CatBoostClassifier(dictionaries=["Word:gram_order=1,occurrence_lower_bound=1"], feature_calcers=["BoW"], **kw)
+    uni.fit(X[:1200], y[:1200], text_features=[1])
+    both = cb.CatBoostClassifier(
+        tokenizers=[{"tokenizer_id": "Space", "separator_type": "ByDelimiter", "delimiter": " ", "lowercasing": "true"}],
+        dictionaries=["Word:gram_order=1,occurrence_lower_bound=1", {"dictionary_id": "BiGram", "gram_order": "2",
+                                                                      "occurrence_lower_bound": "1"}],
+        feature_calcers=["BoW:top_tokens_count=200"], **kw)
+    both.fit(X[:1200], y[:1200], text_features=[1])
+    acc_uni = float((uni.predict(X[1200:]) == y[1200:]).mean())
+    acc_both = float((both.predict(X[1200:]) == y[1200:]).mean())
+    assert acc_both > 0.95 and acc_both > acc_uni + 0.1, (acc_uni, acc_both)
+    path = str(tmp_path / "text.cbm")
+    both.save_model(path)
+    again = cb.CatBoostClassifier().load_model(path)
+    assert np.allclose(again.predict(X[1200:], prediction_type="RawFormulaVal"),
+                       both.predict(X[1200:], prediction_type="RawFormulaVal"))
