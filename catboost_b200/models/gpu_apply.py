@@ -41,14 +41,38 @@ class GpuPredictor:
         if self.dims > 8:
             raise ValueError("GPU apply supports up to 8 prediction dimensions")
         self.lib = native.cuda_lib()
+        # Models that use many features are evaluated from the raw values (cb_predict_wide.cu): split = (column, border).
+        # Chosen when the binary searches of the quantising kernel (7 reads per used feature and row) would outnumber
+        # the reads of the tree walk itself (one per split and row), and the row tile fits in shared memory.
+        used, boff = np.asarray(p["used"], dtype=np.int64), np.asarray(p["boff"], dtype=np.int64)
+        sfeat, sbin = np.asarray(p["sfeat"], dtype=np.int64), np.asarray(p["sbin"], dtype=np.int64)
+        self.S = int(len(sfeat))
+        self.F_stage = int(used.max()) + 1 if len(used) else 0
+        self.total_leaf_floats = int(np.asarray(p["vals"]).size)
+        self.wide = None
+        import os
+        mode = os.environ.get("CB200_PREDICT_WIDE", "auto")
+        want = mode == "1" or (mode == "auto" and 7 * self.U > self.S and self.U > 200)
+        if want and self.S > 0 and self.lib.cb_predict_wide_fits(self.F_stage, self.S, self.T, self.dims, self.total_leaf_floats):
+            nanmax_col = np.zeros(self.F_stage, dtype=np.uint8)
+            nanmax_col[used] = np.asarray(p["nanmax"], dtype=np.uint8)
+            self.wide = dict(col=t(used[sfeat], np.int32), border=t(np.asarray(p["borders"], dtype=np.float32)[boff[sfeat] + sbin]),
+                             nanmax=t(nanmax_col) if nanmax_col.any() else None)
 
     def predict_device(self, X: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
         """X: float32 [n, F] on the device (row stride arbitrary).  Returns float32 [dims, n]."""
         n = X.shape[0]
         if out is None:
             out = torch.empty((self.dims, n), dtype=torch.float32, device=self.dev)
-        P = lambda a: ctypes.c_void_p(a.data_ptr())
+        P = lambda a: ctypes.c_void_p(a.data_ptr()) if a is not None else None
         st = ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        if self.wide is not None and X.shape[1] >= self.F_stage and X.stride(1) == 1:
+            w = self.wide
+            native.cuda_check(self.lib.cb_predict_oblivious_wide(
+                P(X), n, X.stride(0), self.F_stage, P(w["nanmax"]), P(self.depth), P(self.soff), P(w["col"]), P(w["border"]),
+                P(self.loff), P(self.vals), self.T, self.S, self.dims, self.total_leaf_floats, self.scale, P(self.bias),
+                P(out), st), "cb_predict_oblivious_wide")
+            return out
         native.cuda_check(self.lib.cb_predict_oblivious(P(X), n, X.stride(0), P(self.used), P(self.borders), P(self.boff),
                                                         P(self.nanmax), self.U, P(self.depth), P(self.soff),
                                                         P(self.sfeat), P(self.sbin), P(self.loff), P(self.vals), self.T,

@@ -779,32 +779,39 @@ struct CbPredictArgs {
     float scale; const float* bias;   // [dims]
     float* out;                  // [dims][n]
     int max_borders;             // largest border count of a used feature
+    int lv_floats;               // shared-memory buffer for the leaf values of a chunk of trees, in floats (0 = none)
 };
 
-// Four rows per thread (1024 rows per block): the split descriptors of a chunk of trees are staged in shared memory
-// as one word (feature << 8 | bin) per split, so a tree level costs one broadcast read + per row one byte read, a
-// compare and an or.
+// Four rows per thread: the split descriptors of a chunk of trees are staged in shared memory as one word
+// (feature << 8 | bin) per split, so a tree level costs one broadcast read + per row one byte read, a compare and an or.
+// The leaf values of the chunk are staged next to them: a row reads one leaf value per tree at a random place, which
+// from global memory is one 32-byte sector per value; from shared memory it is a bank access.  NT threads per block
+// (1024 when the bins of 4096 rows fit beside the leaf buffer, so that the staging is paid once per 4096 rows).
 #define CB_PRED_CHUNK_SPLITS 3072
-template <int CB_PRED_ROWS>
-__global__ void __launch_bounds__(256) cb_predict_kernel(CbPredictArgs a) {
-    // shared memory: bins [U][USTR] (USTR = 256 * rows per thread + 4: the pad keeps the byte writes of 32 features of
-    // one row in 32 different banks), split descriptors [CB_PRED_CHUNK_SPLITS], borders of 32 features [max_borders][32]
+template <int CB_PRED_ROWS, int NT>
+__global__ void __launch_bounds__(NT) cb_predict_kernel(CbPredictArgs a) {
+    // shared memory: bins [U][USTR] (USTR = NT * rows per thread + 4: the pad keeps the byte writes of 32 features of
+    // one row in 32 different banks), split descriptors [CB_PRED_CHUNK_SPLITS], borders of 32 features [max_borders][32],
+    // leaf values of the current chunk of trees [lv_floats]
     extern __shared__ unsigned char sb[];
-    const int RB = 256 * CB_PRED_ROWS;
-    const int USTR = RB + 4;
+    constexpr int RB = NT * CB_PRED_ROWS;
+    constexpr int USTR = RB + 4;
+    constexpr int NW = NT / 32;
     unsigned int* desc = reinterpret_cast<unsigned int*>(sb + (((size_t)a.U * USTR + 15) & ~(size_t)15));
     float* s_bd = reinterpret_cast<float*>(desc + CB_PRED_CHUNK_SPLITS);
+    float* s_lv = s_bd + (size_t)a.max_borders * 32;
     const long long row0 = (long long)blockIdx.x * RB;
     const int nrow = (int)min((long long)RB, a.n - row0);
     // quantise, 32 used features at a time: their borders go to shared memory transposed ([border][feature], so a
     // lane's binary search never meets another lane's bank); then a warp takes one row at a time, lane = feature, so
-    // that the row's values are read as one contiguous piece when the model uses neighbouring columns
+    // that the row's values are read as one contiguous piece when the model uses neighbouring columns.
+    // Row lr of the block belongs to thread lr % NT, slot lr / NT.
     {
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
         const int mb = a.max_borders;
         for (int c0 = 0; c0 < a.U; c0 += 32) {
             __syncthreads();
-            for (int i = threadIdx.x; i < mb * 32; i += blockDim.x) {
+            for (int i = threadIdx.x; i < mb * 32; i += NT) {
                 const int j = i >> 5, u = c0 + (i & 31);
                 float bv = __int_as_float(0x7f800000);                 // +inf: never below a value
                 if (u < a.U) {
@@ -821,16 +828,16 @@ __global__ void __launch_bounds__(256) cb_predict_kernel(CbPredictArgs a) {
                 const bool nmax = a.nan_is_max && a.nan_is_max[u];
                 unsigned char* dst = sb + (size_t)u * USTR;
                 // four rows per step: their loads are issued together, the searches run while later loads land
-                for (int lr0 = warp; lr0 < nrow; lr0 += 32) {
+                for (int lr0 = warp; lr0 < nrow; lr0 += 4 * NW) {
                     float v[4];
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        const int lr = lr0 + 8 * q;
+                        const int lr = lr0 + NW * q;
                         v[q] = lr < nrow ? a.X[(row0 + lr) * a.ldx + col] : 0.0f;
                     }
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        const int lr = lr0 + 8 * q;
+                        const int lr = lr0 + NW * q;
                         if (lr >= nrow) break;
                         int pos = 0;               // borders < v, fixed power-of-two steps
 #pragma unroll
@@ -838,7 +845,7 @@ __global__ void __launch_bounds__(256) cb_predict_kernel(CbPredictArgs a) {
                             const int idx = pos + step;
                             if (idx <= mb && s_bd[((idx - 1) << 5) + lane] < v[q]) pos = idx;
                         }
-                        dst[(lr & 255) * CB_PRED_ROWS + (lr >> 8)] = (unsigned char)((v[q] != v[q]) ? (nmax ? nbd : 0) : pos);
+                        dst[(lr % NT) * CB_PRED_ROWS + (lr / NT)] = (unsigned char)((v[q] != v[q]) ? (nmax ? nbd : 0) : pos);
                     }
                 }
             }
@@ -852,17 +859,31 @@ __global__ void __launch_bounds__(256) cb_predict_kernel(CbPredictArgs a) {
         for (int k = 0; k < 8; ++k) acc[r][k] = 0.0f;
     int t = 0;
     while (t < a.T) {
-        // trees [t, t_end): as many as fit into the descriptor buffer
+        // trees [t, t_end): as many as fit into the descriptor buffer and, when there is one, the leaf-value buffer
         const int s_begin = a.tree_split_off[t];
+        const long long l_begin = a.tree_leaf_off[t];
         int t_end = t, s_end = s_begin;
-        while (t_end < a.T && a.tree_split_off[t_end] + a.tree_depth[t_end] - s_begin <= CB_PRED_CHUNK_SPLITS) {
+        bool staged = a.lv_floats > 0;
+        while (t_end < a.T && a.tree_split_off[t_end] + a.tree_depth[t_end] - s_begin <= CB_PRED_CHUNK_SPLITS &&
+               (!staged || (a.tree_leaf_off[t_end] + (1ll << a.tree_depth[t_end]) - l_begin) * a.dims <= a.lv_floats)) {
             s_end = a.tree_split_off[t_end] + a.tree_depth[t_end];
             ++t_end;
         }
+        if (t_end == t && staged && a.tree_depth[t] <= CB_PRED_CHUNK_SPLITS) {
+            // this tree alone has more leaf values than the buffer holds: it reads them from global memory
+            staged = false;
+            s_end = s_begin + a.tree_depth[t];
+            t_end = t + 1;
+        }
         if (t_end == t) return;                     // a single tree deeper than the buffer cannot happen (depth <= 16)
         __syncthreads();
-        for (int i = threadIdx.x; i < s_end - s_begin; i += blockDim.x)
+        for (int i = threadIdx.x; i < s_end - s_begin; i += NT)
             desc[i] = ((unsigned int)a.split_feat[s_begin + i] << 8) | (unsigned int)a.split_bin[s_begin + i];
+        if (staged) {
+            const long long cnt = (a.tree_leaf_off[t_end - 1] + (1ll << a.tree_depth[t_end - 1]) - l_begin) * a.dims;
+            const float* src = a.leaf_vals + l_begin * a.dims;
+            for (long long i = threadIdx.x; i < cnt; i += NT) s_lv[i] = __ldg(src + i);
+        }
         __syncthreads();
         for (int tt = t; tt < t_end; ++tt) {
             const int depth = a.tree_depth[tt];
@@ -890,18 +911,27 @@ __global__ void __launch_bounds__(256) cb_predict_kernel(CbPredictArgs a) {
                     for (int r = 0; r < CB_PRED_ROWS; ++r) leaf[r] |= ((unsigned int)col[r] > thr) << k;
                 }
             }
-            const float* lv0 = a.leaf_vals + a.tree_leaf_off[tt] * a.dims;
+            if (staged) {
+                const float* lv0 = s_lv + (a.tree_leaf_off[tt] - l_begin) * a.dims;
 #pragma unroll
-            for (int r = 0; r < CB_PRED_ROWS; ++r) {
-                const float* lv = lv0 + (long long)leaf[r] * a.dims;
-                for (int k = 0; k < dims; ++k) acc[r][k] += __ldg(lv + k);
+                for (int r = 0; r < CB_PRED_ROWS; ++r) {
+                    const float* lv = lv0 + leaf[r] * a.dims;
+                    for (int k = 0; k < dims; ++k) acc[r][k] += lv[k];
+                }
+            } else {
+                const float* lv0 = a.leaf_vals + a.tree_leaf_off[tt] * a.dims;
+#pragma unroll
+                for (int r = 0; r < CB_PRED_ROWS; ++r) {
+                    const float* lv = lv0 + (long long)leaf[r] * a.dims;
+                    for (int k = 0; k < dims; ++k) acc[r][k] += __ldg(lv + k);
+                }
             }
         }
         t = t_end;
     }
 #pragma unroll
     for (int r = 0; r < CB_PRED_ROWS; ++r) {
-        const int lr = r * 256 + threadIdx.x;
+        const int lr = r * NT + threadIdx.x;
         if (lr < nrow)
             for (int k = 0; k < dims; ++k)
                 a.out[(long long)k * a.n + row0 + lr] = acc[r][k] * a.scale + (a.bias ? a.bias[k] : 0.0f);
@@ -917,27 +947,51 @@ CB_API int cb_predict_oblivious(const float* X, long long n, long long ldx, cons
     if (n <= 0) return 0;
     if (max_borders < 1) max_borders = 1;
     if (max_borders > 255) return (int)cudaErrorInvalidValue;
-    // four rows per thread when the bins of 1024 rows fit in shared memory, else one row per thread
     const size_t CB_PRED_SMEM_MAX = 224 * 1024;
     const size_t fixed = CB_PRED_CHUNK_SPLITS * 4 + (size_t)max_borders * 32 * sizeof(float);
-    int rows = 4;
-    size_t pred_smem = (((size_t)U * (256 * rows + 4) + 15) & ~(size_t)15) + fixed;
-    if (pred_smem > CB_PRED_SMEM_MAX) {
-        rows = 1;
-        pred_smem = (((size_t)U * (256 + 4) + 15) & ~(size_t)15) + fixed;
+    auto bins_bytes = [&](int nt, int rows) { return (((size_t)U * ((size_t)nt * rows + 4) + 15) & ~(size_t)15); };
+    // geometry: (a) 1024 threads x 4 rows with a 64 KB leaf buffer when the bins of 4096 rows leave room for it (narrow
+    // models: the staging of descriptors and leaf values is paid once per 4096 rows); (b) 256 threads x 4 rows with
+    // what is left of 72 KB for leaf values (three blocks per SM); (c) 256 threads x 1 row for wide models, leaf
+    // values in whatever remains.  CB200_PREDICT_LV=0 keeps the leaf values in global memory.
+    bool lv_on = true;
+    if (const char* e = getenv("CB200_PREDICT_LV")) lv_on = atoi(e) != 0;
+    int nt = 1024, rows = 4;
+    size_t lv_bytes = 0, pred_smem = 0;
+    if (lv_on && bins_bytes(1024, 4) + fixed + 32 * 1024 <= CB_PRED_SMEM_MAX && n >= 4096ll * 148) {
+        lv_bytes = CB_PRED_SMEM_MAX - bins_bytes(1024, 4) - fixed;
+        if (lv_bytes > 64 * 1024) lv_bytes = 64 * 1024;
+        pred_smem = bins_bytes(1024, 4) + fixed + lv_bytes;
+    } else {
+        nt = 256;
+        pred_smem = bins_bytes(256, 4) + fixed;
+        if (pred_smem > CB_PRED_SMEM_MAX) {
+            rows = 1;
+            pred_smem = bins_bytes(256, 1) + fixed;
+        }
+        if (pred_smem > CB_PRED_SMEM_MAX) return (int)cudaErrorInvalidValue;
+        if (lv_on) {
+            const size_t target = rows == 4 ? 72 * 1024 : CB_PRED_SMEM_MAX;       // keep three narrow blocks per SM
+            lv_bytes = pred_smem < target ? target - pred_smem : 0;
+            if (lv_bytes > 64 * 1024) lv_bytes = 64 * 1024;
+            if (lv_bytes < 8 * 1024) lv_bytes = 0;
+            pred_smem += lv_bytes;
+        }
     }
-    if (dims > 8 || pred_smem > CB_PRED_SMEM_MAX) return (int)cudaErrorInvalidValue;
+    if (dims > 8) return (int)cudaErrorInvalidValue;
     CbPredictArgs a{X, n, ldx, used_feat, borders, border_off, nan_is_max, U, tree_depth, tree_split_off, split_feat,
-                    split_bin, tree_leaf_off, leaf_vals, T, dims, scale, bias, out, max_borders};
+                    split_bin, tree_leaf_off, leaf_vals, T, dims, scale, bias, out, max_borders, (int)(lv_bytes / 4)};
     static unsigned long long set = 0ull;
     if (cb_first_on_device(&set)) {
-        cudaError_t e = cudaFuncSetAttribute(cb_predict_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CB_PRED_SMEM_MAX);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_predict_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CB_PRED_SMEM_MAX);
+        cudaError_t e = cudaFuncSetAttribute(cb_predict_kernel<4, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CB_PRED_SMEM_MAX);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_predict_kernel<4, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CB_PRED_SMEM_MAX);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_predict_kernel<1, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CB_PRED_SMEM_MAX);
         if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
     }
-    const unsigned pred_grid = (unsigned)((n + 256 * rows - 1) / (256 * rows));
-    if (rows == 4) cb_predict_kernel<4><<<pred_grid, 256, pred_smem, st>>>(a);
-    else cb_predict_kernel<1><<<pred_grid, 256, pred_smem, st>>>(a);
+    const unsigned pred_grid = (unsigned)((n + (long long)nt * rows - 1) / ((long long)nt * rows));
+    if (nt == 1024) cb_predict_kernel<4, 1024><<<pred_grid, 1024, pred_smem, st>>>(a);
+    else if (rows == 4) cb_predict_kernel<4, 256><<<pred_grid, 256, pred_smem, st>>>(a);
+    else cb_predict_kernel<1, 256><<<pred_grid, 256, pred_smem, st>>>(a);
     CB_LAUNCH_CHECK();
     return 0;
 }

@@ -578,3 +578,57 @@ def test_fit_with_mvs_bootstrap_runs_on_the_device_trainer():
         assert m._train_info["launches_per_iter"] > 0              # the device engine, not the general learner
         accs[bt] = float((m.predict(X[50_000:]) == y[50_000:]).mean())
     assert accs["MVS"] > accs["No"] - 0.02 and accs["MVS"] > 0.85, accs
+
+
+def test_gpu_apply_geometries_match_cpu_apply(monkeypatch):
+    """The batch-apply kernel in its three shapes -- 1024 threads x 4 rows (many rows, narrow model), 256 x 4 and
+    256 x 1 (wide model) -- with the leaf values of a chunk of trees staged in shared memory, and with them left in
+    global memory: all equal to the CPU evaluator."""
+    import catboost_b200 as cb
+    from catboost_b200.models.gpu_apply import GpuPredictor
+    rng = np.random.default_rng(21)
+    # narrow model, enough rows for the 1024-thread shape; depth 9 takes the per-row (not four-rows-per-word) walk
+    X = rng.standard_normal((700_000, 10)).astype(np.float32)
+    X[rng.random(X.shape) < 0.01] = np.nan
+    y = (np.nan_to_num(X[:, 0]) + 0.5 * np.nan_to_num(X[:, 3]) * np.nan_to_num(X[:, 4]) + 0.3 * rng.standard_normal(len(X))).astype(np.float32)
+    for depth, iters in ((6, 70), (9, 12)):
+        m = cb.CatBoostRegressor(iterations=iters, depth=depth, learning_rate=0.2, border_count=64, task_type="GPU",
+                                 verbose=False, allow_writing_files=False).fit(X[:60_000], y[:60_000])
+        want = m.predict(X, prediction_type="RawFormulaVal")
+        xd = torch.from_numpy(X).cuda()
+        for lv in ("1", "0"):
+            monkeypatch.setenv("CB200_PREDICT_LV", lv)
+            got = GpuPredictor(m._model, "cuda:0").predict_device(xd)[0].double().cpu().numpy()
+            assert np.allclose(got, want, rtol=1e-5, atol=1e-5), (depth, lv, float(np.abs(got - want).max()))
+            small = GpuPredictor(m._model, "cuda:0").predict_device(xd[:5001])[0].double().cpu().numpy()
+            assert np.allclose(small, want[:5001], rtol=1e-5, atol=1e-5)
+    # wide model: more used features than four rows per thread allow
+    Xw = rng.standard_normal((30_000, 400)).astype(np.float32)
+    yw = (Xw @ rng.choice([-1.0, 1.0], 400).astype(np.float32) + rng.standard_normal(len(Xw))).astype(np.float32)
+    mw = cb.CatBoostRegressor(iterations=200, depth=6, learning_rate=0.2, border_count=32, task_type="GPU", verbose=False,
+                              allow_writing_files=False).fit(Xw, yw)
+    assert len({s.feature for s in mw._model.splits}) > 210          # beyond what four rows per thread can stage
+    want = mw.predict(Xw, prediction_type="RawFormulaVal")
+    monkeypatch.setenv("CB200_PREDICT_WIDE", "0")
+    for lv in ("1", "0"):
+        monkeypatch.setenv("CB200_PREDICT_LV", lv)
+        got = GpuPredictor(mw._model, "cuda:0").predict_device(torch.from_numpy(Xw).cuda())[0].double().cpu().numpy()
+        assert np.allclose(got, want, rtol=1e-5, atol=1e-4), float(np.abs(got - want).max())
+    # the same models through the kernel that compares raw values with borders (no quantisation): chosen by itself for
+    # the wide model, forced for the narrow one; NaNs take the side their column's NaN mode gives them
+    monkeypatch.setenv("CB200_PREDICT_WIDE", "auto")
+    pw = GpuPredictor(mw._model, "cuda:0")
+    assert pw.wide is not None
+    got = pw.predict_device(torch.from_numpy(Xw).cuda())[0].double().cpu().numpy()
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-4), float(np.abs(got - want).max())
+    monkeypatch.setenv("CB200_PREDICT_WIDE", "1")
+    pn = GpuPredictor(m._model, "cuda:0")
+    assert pn.wide is not None
+    got = pn.predict_device(xd[:100_003])[0].double().cpu().numpy()
+    assert np.allclose(got, m.predict(X[:100_003], prediction_type="RawFormulaVal"), rtol=1e-5, atol=1e-5)
+    mm = cb.CatBoostClassifier(iterations=30, depth=5, learning_rate=0.3, task_type="GPU", verbose=False,
+                               allow_writing_files=False, nan_mode="Max").fit(X[:40_000], (y[:40_000] > 0).astype(int) + (y[:40_000] > 1))
+    pm = GpuPredictor(mm._model, "cuda:0")
+    assert pm.wide is not None and pm.dims == 3
+    got = pm.predict_device(xd[:50_000]).t().double().cpu().numpy()
+    assert np.allclose(got, mm.predict(X[:50_000], prediction_type="RawFormulaVal"), rtol=1e-5, atol=1e-5)
