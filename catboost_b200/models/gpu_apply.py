@@ -19,8 +19,30 @@ import torch
 from ..ops import native
 
 
+_COPY_POOL = None
+
+
+def _parallel_copy(dst: np.ndarray, src: np.ndarray, threads: int = 8):
+    """dst[...] = src with several host threads (numpy releases the interpreter lock while it copies): the copy of
+    pageable rows into a pinned staging buffer is what limits apply from host memory, and one thread moves about a
+    third of what the memory system can."""
+    global _COPY_POOL
+    n = dst.shape[0]
+    if n < 65536 or threads <= 1:
+        np.copyto(dst, src)
+        return
+    if _COPY_POOL is None:
+        from concurrent.futures import ThreadPoolExecutor
+        _COPY_POOL = ThreadPoolExecutor(max_workers=8, thread_name_prefix="cb200-copy")
+    cuts = [n * k // threads for k in range(threads + 1)]
+    futs = [_COPY_POOL.submit(np.copyto, dst[cuts[k]:cuts[k + 1]], src[cuts[k]:cuts[k + 1]]) for k in range(threads)]
+    for f in futs:
+        f.result()
+
+
 class GpuPredictor:
-    """Model arrays resident on one GPU; ``predict`` may be called repeatedly."""
+    """Model arrays resident on one GPU; ``predict`` may be called repeatedly (its staging buffers are kept between
+    calls when they are below 1 GiB of pinned memory)."""
 
     def __init__(self, model, device=None):
         p = model._packed_oblivious()
@@ -76,7 +98,8 @@ class GpuPredictor:
         native.cuda_check(self.lib.cb_predict_oblivious(P(X), n, X.stride(0), P(self.used), P(self.borders), P(self.boff),
                                                         P(self.nanmax), self.U, P(self.depth), P(self.soff),
                                                         P(self.sfeat), P(self.sbin), P(self.loff), P(self.vals), self.T,
-                                                        self.dims, self.scale, P(self.bias), P(out), self.max_borders, st),
+                                                        self.dims, self.scale, P(self.bias), P(out), self.max_borders,
+                                                        self.total_leaf_floats, st),
                           "cb_predict_oblivious")
         return out
 
@@ -94,12 +117,21 @@ class GpuPredictor:
         src_pinned = bool(xt.is_pinned())            # the caller's rows are page-locked: no staging copy needed
         with torch.cuda.device(self.dev):
             nbuf = 2 if n > chunk_rows else 1
-            stage = [None if src_pinned else torch.empty((chunk_rows, F), dtype=torch.float32).pin_memory()
-                     for _ in range(nbuf)]
-            back = [torch.empty((self.dims, chunk_rows), dtype=torch.float32).pin_memory() for _ in range(nbuf)]
-            dbuf = [torch.empty((chunk_rows, F), dtype=torch.float32, device=self.dev) for _ in range(nbuf)]
-            dout = [torch.empty((self.dims, chunk_rows), dtype=torch.float32, device=self.dev) for _ in range(nbuf)]
-            streams = [torch.cuda.Stream(self.dev) for _ in range(nbuf)]
+            key = (chunk_rows, F, src_pinned, nbuf)
+            bufs = self.__dict__.setdefault("_bufs", {}).get(key)
+            if bufs is None:
+                stage = [None if src_pinned else torch.empty((chunk_rows, F), dtype=torch.float32).pin_memory()
+                         for _ in range(nbuf)]
+                back = [torch.empty((self.dims, chunk_rows), dtype=torch.float32).pin_memory() for _ in range(nbuf)]
+                dbuf = [torch.empty((chunk_rows, F), dtype=torch.float32, device=self.dev) for _ in range(nbuf)]
+                dout = [torch.empty((self.dims, chunk_rows), dtype=torch.float32, device=self.dev) for _ in range(nbuf)]
+                streams = [torch.cuda.Stream(self.dev) for _ in range(nbuf)]
+                bufs = (stage, back, dbuf, dout, streams)
+                pinned = nbuf * chunk_rows * (self.dims + (0 if src_pinned else F)) * 4
+                self._bufs.clear()                                # one geometry at a time
+                if pinned <= (1 << 30):
+                    self._bufs[key] = bufs
+            stage, back, dbuf, dout, streams = bufs
             pending = [None] * nbuf                          # (event, r0, r1) of the chunk in flight on every buffer
             cur = torch.cuda.current_stream(self.dev)
             for st in streams:
@@ -118,7 +150,7 @@ class GpuPredictor:
                 m = r1 - r0
                 drain(k)
                 if not src_pinned:
-                    stage[k][:m].copy_(xt[r0:r1])
+                    _parallel_copy(stage[k][:m].numpy(), X[r0:r1])
                 h_src = xt[r0:r1] if src_pinned else stage[k][:m]
                 # a short last chunk uses the front of the buffers as a dense [dims, m] block
                 d_out = dout[k].view(-1)[: self.dims * m].view(self.dims, m)

@@ -185,6 +185,60 @@ def main(argv=None):
         borders = [np.linspace(0.02, 0.98, 15).astype(np.float32) for _ in descs]
         ms = _time(lambda: ops.ctr_binarize(descs, borders, excl, totals, seg_id, rows, 0, n), args.reps, flush)
         report("cb_ctr_binarize_kernel", ms, n * (8 + 4 + 8 + 4 * 1), "four CTRs -> bytes in document order (scattered)")
+    if want("sort"):
+        g = torch.Generator().manual_seed(2)
+        keys = (torch.rand(n, generator=g) ** 3 * 1_000_000).long().to(dev) * 2654435761 - (1 << 40)
+        ms = _time(lambda: ops.sort_pairs(keys), args.reps, flush)
+        # 8 passes, each reads keys + values twice (count, scatter) and writes them once
+        report("cb_sort_pairs_i64 (8 passes x 4 launches)", ms, n * 8 * (8 + 8 + 4 + 8 + 4), "stable radix sort of (int64 key, int32 position)")
+        ms = _time(lambda: torch.sort(keys, stable=True), args.reps, flush)
+        report("torch.sort(stable) for comparison", ms, n * 8 * (8 + 8 + 4 + 8 + 4), "library sort of the same keys")
+    if want("mvs"):
+        stats = eng.stats.clone()
+        smax = torch.zeros(2, device=dev)
+        ms = _time(lambda: lib.cb_mvs_sample(P(stats), store.npad, n, 0.5, -1.0, 7, P(eng.iter_ptr), P(smax), None, st()),
+                   args.reps, flush)
+        report("cb_mvs_kernel", ms, n * (4 + 4) * 2, "derivative + weight rows read and written; 40 bisection steps per block of 8192")
+    if want("leaf_newton"):
+        eng10 = GpuObliviousEngine(store, torch.from_numpy(y), None, torch.zeros(n), obj, depth=args.depth, iterations=4,
+                                   learning_rate=0.1, l2_leaf_reg=3.0, leaf_iterations=10, use_graph=False)
+        eng10.step(1)
+        ms = _time(lambda: eng10._leaves(), args.reps, flush)
+        report("cb_leaf_newton_kernel (10 steps, one launch)", ms, 10 * n * (4 + 4 + 2), "approx, target, leaf per step")
+        eng10.close()
+    if want("multiclass"):
+        K = 5
+        yk = rng.integers(0, K, n).astype(np.float32)
+        engk = GpuObliviousEngine(store, torch.from_numpy(yk), None, torch.zeros((K, n)), make_objective("MultiClass", {}, n_classes=K),
+                                  depth=args.depth, iterations=4, learning_rate=0.1, l2_leaf_reg=3.0, leaf_iterations=1,
+                                  use_graph=False, dims=K, quantized_hist="wide")
+        engk.step(1)
+        ms = _time(lambda: engk._grad(), args.reps, flush)
+        report("cb_mc_grad_kernel (K=5)", ms, n * (K * 4 * 2 + 4 + 2 + (K + 1) * 4), "approx rw, target, leaf, K + 1 statistic rows")
+        ms = _time(lambda: engk._leaves(), args.reps, flush)
+        report("cb_mc_leaf_kernel (K=5: sums + K x K Cholesky per leaf)", ms, n * (K * 4 + 4 + 2), "approx, target, leaf")
+        for level in (0, args.depth - 1):
+            ms = _time(lambda: engk._level_fused(level), args.reps, flush)
+            report(f"cb_level_fused_kernel[K=5, level={level}]", ms, n * (((F + 3) // 4) * 4 + 2 + (K + 1) * 4), "S = 6 statistics, hi/lo cells")
+        engk.close()
+    if want("predict_wide"):
+        Fw, Tw = 700, 200
+        nw = min(n, 1_000_000)
+        Xw = torch.rand((nw, Fw), generator=torch.Generator().manual_seed(3)).to(dev)
+        S = Tw * 6
+        gcol = torch.Generator().manual_seed(4)
+        col = torch.randint(0, Fw, (S,), generator=gcol, dtype=torch.int32).to(dev)
+        bor = torch.rand(S, generator=gcol).to(dev)
+        depth_t = torch.full((Tw,), 6, dtype=torch.int32, device=dev)
+        soff = (torch.arange(Tw, dtype=torch.int32) * 6).to(dev)
+        loff = (torch.arange(Tw, dtype=torch.int64) * 64).to(dev)
+        vals = torch.randn(Tw * 64, generator=gcol).to(dev)
+        bias = torch.zeros(1, device=dev)
+        res = torch.empty((1, nw), device=dev)
+        ms = _time(lambda: lib.cb_predict_oblivious_wide(P(Xw), nw, Fw, Fw, None, P(depth_t), P(soff), P(col), P(bor), P(loff),
+                                                         P(vals), Tw, S, 1, Tw * 64, 1.0, P(bias), P(res), st()), args.reps, flush)
+        report("cb_predict_wide_kernel (1M x 700, 200 trees)", ms, nw * Fw * 4 + nw * 4,
+               f"{nw / (ms * 1e-3):.3g} rows/s; raw values against borders, no quantisation")
     return 0
 
 

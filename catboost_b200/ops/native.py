@@ -206,14 +206,14 @@ _SIGS = {
     "cb_mc_leaf_smem_bytes": (c_int, [c_int, c_int]),
     "cb_mc_leaf_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                c_void_p, c_int, c_void_p]),
+                                c_void_p, c_float, c_int, c_void_p]),
     "cb_mc_metric": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "cb_apply_tree_bins": (c_int, [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                                    c_void_p]),
     "cb_leaf_index": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "cb_predict_oblivious": (c_int, [c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
-                                     c_void_p, c_int, c_void_p]),
+                                     c_void_p, c_int, c_ll, c_void_p]),
     "cb_metric_sum": (c_int, [c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
                              c_int, c_void_p]),
     "cb_device_info": (c_int, [c_void_p, c_void_p]),

@@ -133,9 +133,15 @@ class GpuObliviousEngine:
         self.target = torch.zeros(npad, dtype=f32, device=dev)
         self.target[:n] = target.to(dev, f32)
         self.weight = None
+        self.weight_max = 1.0          # largest document weight over all ranks (scale of the fixed-point leaf cells)
         if weight is not None:
             self.weight = torch.zeros(npad, dtype=f32, device=dev)
             self.weight[:n] = weight.to(dev, f32)
+            wm = self.weight.max().reshape(1).double()
+            if ctx is not None and ctx.is_distributed:
+                import torch.distributed as dist
+                dist.all_reduce(wm, op=dist.ReduceOp.MAX, group=ctx.group)
+            self.weight_max = max(float(wm.item()), 1e-30)
         self.leaf = torch.zeros(npad, dtype=torch.int16, device=dev)
         self.leaf_vmax = torch.zeros(2, dtype=f32, device=dev)
         self.leaf_grid = None
@@ -417,8 +423,8 @@ class GpuObliviousEngine:
                 chk(lib.cb_mc_leaf_step(_p(self.approx), _p(self.target), _p(self.weight), _p(self.leaf), self.n, self.npad,
                                         self.K, self.L, _p(self.delta), _p(self.sums), _p(self.sums_combined), _p(self.leaf_w),
                                         first, last, self.leaf_newton, self.l2, self.lr, _p(self.cur_vals), _p(self.model_vals),
-                                        _p(self.model_wts), self.L, _p(self.iter_ptr), comm, self.sm_count * 4, self._stream()),
-                    "cb_mc_leaf_step")
+                                        _p(self.model_wts), self.L, _p(self.iter_ptr), comm, self.weight_max, self.sm_count * 4,
+                                        self._stream()), "cb_mc_leaf_step")
                 self.launches_per_iter += 2
             return
         if self.R > 1 and comm is None:
