@@ -72,6 +72,7 @@ class GpuPredictor:
         self.F_stage = int(used.max()) + 1 if len(used) else 0
         self.total_leaf_floats = int(np.asarray(p["vals"]).size)
         self.wide = None
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)     # set by a device wait that ran out of time
         import os
         mode = os.environ.get("CB200_PREDICT_WIDE", "auto")
         want = mode == "1" or (mode == "auto" and 7 * self.U > self.S and self.U > 200)
@@ -93,7 +94,7 @@ class GpuPredictor:
             native.cuda_check(self.lib.cb_predict_oblivious_wide(
                 P(X), n, X.stride(0), self.F_stage, P(w["nanmax"]), P(self.depth), P(self.soff), P(w["col"]), P(w["border"]),
                 P(self.loff), P(self.vals), self.T, self.S, self.dims, self.total_leaf_floats, self.scale, P(self.bias),
-                P(out), st), "cb_predict_oblivious_wide")
+                P(out), P(self.status), st), "cb_predict_oblivious_wide")
             return out
         native.cuda_check(self.lib.cb_predict_oblivious(P(X), n, X.stride(0), P(self.used), P(self.borders), P(self.boff),
                                                         P(self.nanmax), self.U, P(self.depth), P(self.soff),
@@ -165,7 +166,15 @@ class GpuPredictor:
             for k in range(nbuf):
                 drain(k)
             cur.wait_stream(streams[0])
+            self.check_status()
         return res
+
+    def check_status(self):
+        """Raise if a bounded device wait of an apply kernel ran out of time (the results of that call are not valid)."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise RuntimeError(f"GPU apply: a device wait timed out (status 0x{code:x})")
 
 
 class MultiGpuPredictor:

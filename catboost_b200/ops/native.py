@@ -195,7 +195,8 @@ _SIGS = {
     "cb_sort_pairs_i64": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_void_p]),
     "cb_predict_wide_fits": (c_int, [c_int, c_int, c_int, c_int, c_ll]),
     "cb_predict_oblivious_wide": (c_int, [c_void_p, c_ll, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                          c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_float, c_void_p, c_void_p, c_void_p]),
+                                          c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_float, c_void_p, c_void_p, c_void_p,
+                                          c_void_p]),
     "cb_mvs_block_docs": (c_int, []),
     "cb_mvs_sample": (c_int, [c_void_p, c_ll, c_ll, c_float, c_float, c_ull, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_mc_max_classes": (c_int, []),

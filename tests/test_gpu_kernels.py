@@ -619,8 +619,14 @@ def test_gpu_apply_geometries_match_cpu_apply(monkeypatch):
     monkeypatch.setenv("CB200_PREDICT_WIDE", "auto")
     pw = GpuPredictor(mw._model, "cuda:0")
     assert pw.wide is not None
-    got = pw.predict_device(torch.from_numpy(Xw).cuda())[0].double().cpu().numpy()
-    assert np.allclose(got, want, rtol=1e-5, atol=1e-4), float(np.abs(got - want).max())
+    for tma in ("0", "1"):                 # rows staged through registers / brought in by bulk copies against mbarriers
+        monkeypatch.setenv("CB200_PREDICT_WIDE_TMA", tma)
+        got = pw.predict_device(torch.from_numpy(Xw).cuda())[0].double().cpu().numpy()
+        assert np.allclose(got, want, rtol=1e-5, atol=1e-4), (tma, float(np.abs(got - want).max()))
+        part = pw.predict_device(torch.from_numpy(Xw).cuda()[:1237])[0].double().cpu().numpy()
+        assert np.allclose(part, want[:1237], rtol=1e-5, atol=1e-4)
+        pw.check_status()
+    monkeypatch.setenv("CB200_PREDICT_WIDE_TMA", "0")
     monkeypatch.setenv("CB200_PREDICT_WIDE", "1")
     pn = GpuPredictor(m._model, "cuda:0")
     assert pn.wide is not None
