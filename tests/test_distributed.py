@@ -141,6 +141,19 @@ def test_two_gpus_fused_matches_nccl_baseline():
 
 
 @pytest.mark.gpu
+def test_two_gpus_training_is_repeatable():
+    """Two runs of the fused two-GPU trainer on the same data: the histograms are integer sums added in rank order, so the
+    splits are the same and the predictions agree to rounding of the first (fp32) leaf step."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    a = _run(2, "nccl", "fused", port=29631)
+    b = _run(2, "nccl", "fused", port=29633)
+    assert a["splits"] == b["splits"]
+    assert np.allclose(a["pred"], b["pred"], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.gpu
 def test_two_gpus_categorical_features_sharded_by_hash(monkeypatch):
     """The CTR engine on two GPUs: categories dealt to the ranks by hash (device sort, scan and bucketing kernels on the
     owner, two all-to-alls) against every rank computing every table from all-gathered columns."""

@@ -1158,3 +1158,27 @@ def test_text_features_with_dictionaries_and_tokenizers(tmp_path):
     again = cb.CatBoostClassifier().load_model(path)
     assert np.allclose(again.predict(X[1200:], prediction_type="RawFormulaVal"),
                        both.predict(X[1200:], prediction_type="RawFormulaVal"))
+
+
+def test_reference_boston_and_mushroom_models():
+    """The reference's own acceptance criteria for two of its model files
+    (catboost/dotnet/CatBoostNetTests/CatBoostModelEvaluatorTest.cs:46-131): the boston model (numerical features)
+    predicts log(target) within 0.4 on all but at most 7 rows; the mushroom model (categorical features only, so every
+    prediction goes through the CTR tables stored in the file: hashes, priors, shifts, scales, target borders) puts
+    every one of the 8124 rows in its class."""
+    bed = os.path.join(REF, "catboost/dotnet/CatBoostNetTests/testbed")
+    if not os.path.exists(bed):
+        pytest.skip("reference model files are not available")
+    rows = [l.split() for l in open(os.path.join(bed, "boston", "housing.data")) if l.strip()]
+    X = np.array([[float(v) for v in r[:-1]] for r in rows], dtype=np.float32)
+    target = np.array([float(r[-1]) for r in rows])
+    m = cb.CatBoostRegressor().load_model(os.path.join(bed, "boston", "boston_housing_model.cbm"))
+    pred = np.asarray(m.predict(X), dtype=float)
+    assert int((np.abs(pred - np.log(target)) >= 0.4).sum()) <= 7
+    rows = [l.strip().split(",") for l in open(os.path.join(bed, "mushrooms", "mushrooms.csv")) if l.strip()]
+    labels = np.array([r[0] for r in rows])
+    data = np.array([r[1:] for r in rows], dtype=object)
+    m = cb.CatBoostClassifier().load_model(os.path.join(bed, "mushrooms", "mushroom_model.cbm"))
+    raw = np.asarray(m.predict(cb.Pool(data, cat_features=list(range(data.shape[1]))), prediction_type="RawFormulaVal"), dtype=float)
+    got = np.where(raw > 0, "p", "e")
+    assert (got == labels).all(), int((got != labels).sum())
