@@ -95,6 +95,42 @@ def sort_pairs(keys: torch.Tensor):
     return ka, va.long()
 
 
+def query_der(kind: str, approx: torch.Tensor, target: torch.Tensor, weight, offsets: torch.Tensor, beta: float = 1.0):
+    """(der, hess) [n] of a query-wise objective on the GPU (ops/cuda/cb_querywise.cu).  ``kind``: 'QueryRMSE',
+    'QuerySoftMax' or 'PairLogit' (all pairs of a query whose labels differ); ``offsets``: int64 [Q + 1] row offsets."""
+    dev = approx.device
+    n = int(approx.shape[0])
+    a, t = approx.contiguous().float(), target.contiguous().float()
+    w = None if weight is None else weight.contiguous().float()
+    off = offsets.contiguous().long()
+    Q = int(off.numel()) - 1
+    der, hess = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    lib = native.cuda_lib()
+    if kind == "QueryRMSE":
+        rc = lib.cb_query_rmse_der(_p(a), _p(t), _p(w), _p(off), Q, _p(der), _p(hess), _stream(dev))
+    elif kind == "QuerySoftMax":
+        rc = lib.cb_query_softmax_der(_p(a), _p(t), _p(w), _p(off), Q, float(beta), _p(der), _p(hess), _stream(dev))
+    elif kind == "PairLogit":
+        rc = lib.cb_pair_logit_labels_der(_p(a), _p(t), _p(off), Q, _p(der), _p(hess), _stream(dev))
+    else:
+        raise ValueError(kind)
+    native.cuda_check(rc, "cb_querywise")
+    return der, hess
+
+
+def pair_logit_der(approx: torch.Tensor, pairs: torch.Tensor, pair_weight):
+    """(der, hess) [n] of PairLogit from explicit (winner, loser) pairs [P, 2] (int64) on the GPU."""
+    dev = approx.device
+    n = int(approx.shape[0])
+    a = approx.contiguous().float()
+    pr = pairs.contiguous().long()
+    pw = None if pair_weight is None else pair_weight.contiguous().float()
+    der, hess = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    native.cuda_check(native.cuda_lib().cb_pair_logit_pairs_der(_p(a), _p(pr), _p(pw), int(pr.shape[0]), _p(der), _p(hess),
+                                                                _stream(dev)), "cb_pair_logit_pairs_der")
+    return der, hess.clamp_min_(1e-16)
+
+
 _SCORE_FN_ID = {"Cosine": 0, "NewtonCosine": 0, "L2": 1, "NewtonL2": 1, "SolarL2": 2, "LOOL2": 3, "SatL2": 4}
 
 

@@ -23,7 +23,7 @@ from pathlib import Path
 _HERE = Path(__file__).resolve().parent
 CUDA_SRC = [_HERE / "cuda" / "cb_kernels.cu", _HERE / "cuda" / "cb_fused.cu", _HERE / "cuda" / "cb_leaf.cu",
             _HERE / "cuda" / "cb_quantize_tma.cu", _HERE / "cuda" / "cb_ranking.cu", _HERE / "cuda" / "cb_ctr.cu",
-            _HERE / "cuda" / "cb_multiclass.cu", _HERE / "cuda" / "cb_search.cu", _HERE / "cuda" / "cb_pairwise.cu", _HERE / "cuda" / "cb_sort.cu", _HERE / "cuda" / "cb_mvs.cu", _HERE / "cuda" / "cb_predict_wide.cu"]
+            _HERE / "cuda" / "cb_multiclass.cu", _HERE / "cuda" / "cb_search.cu", _HERE / "cuda" / "cb_pairwise.cu", _HERE / "cuda" / "cb_sort.cu", _HERE / "cuda" / "cb_mvs.cu", _HERE / "cuda" / "cb_predict_wide.cu", _HERE / "cuda" / "cb_querywise.cu"]
 CUDA_HDR = sorted((_HERE / "cuda").glob("*.cuh")) + sorted((_HERE / "cuda").glob("*.h"))
 CPU_SRC = [_HERE / "cpu" / "cb_cpu.cpp", _HERE / "cpu" / "cb_cityhash.h"]
 MODEL_SRC = [_HERE / "cpu" / "cb_model_capi.cpp", _HERE / "cpu" / "cb_model_capi.h", _HERE / "cpu" / "cb_cityhash.h"]
@@ -197,6 +197,10 @@ _SIGS = {
     "cb_predict_oblivious_wide": (c_int, [c_void_p, c_ll, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_float, c_void_p, c_void_p, c_void_p,
                                           c_void_p]),
+    "cb_query_rmse_der": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p]),
+    "cb_query_softmax_der": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_float, c_void_p, c_void_p, c_void_p]),
+    "cb_pair_logit_pairs_der": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p]),
+    "cb_pair_logit_labels_der": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p]),
     "cb_mvs_block_docs": (c_int, []),
     "cb_mvs_sample": (c_int, [c_void_p, c_ll, c_ll, c_float, c_float, c_ull, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_mc_max_classes": (c_int, []),

@@ -20,6 +20,9 @@ import torch
 from .objectives import Objective, _wsum, _wtot
 
 
+USE_KERNELS = True        # False: the tensor formulations below also on the GPU (they are the oracle of the kernels)
+
+
 class _GroupLayout:
     """Padded view of the query groups: index [Q, Lmax] into the row order, mask of real entries."""
 
@@ -68,6 +71,10 @@ class QueryRMSE(_GroupObjective):
     name = "QueryRMSE"
 
     def der_hess(self, approx, target, weight, ctx=None):
+        if approx.is_cuda and USE_KERNELS:
+            from ..ops import api as ops
+            d, h = ops.query_der("QueryRMSE", approx[0], target, weight, ctx.group_offsets)
+            return d.unsqueeze(0), h.unsqueeze(0)
         lay = _layout(ctx)
         a, n = approx[0], approx.shape[1]
         w = torch.ones_like(a) if weight is None else weight
@@ -88,8 +95,12 @@ class QuerySoftMax(_GroupObjective):
     name = "QuerySoftMax"
 
     def der_hess(self, approx, target, weight, ctx=None):
-        lay = _layout(ctx)
         beta = float(self.params.get("lambda", self.params.get("beta", 1.0)))
+        if approx.is_cuda and USE_KERNELS:
+            from ..ops import api as ops
+            d, h = ops.query_der("QuerySoftMax", approx[0], target, weight, ctx.group_offsets, beta)
+            return d.unsqueeze(0), h.unsqueeze(0)
+        lay = _layout(ctx)
         a, n = approx[0], approx.shape[1]
         w = torch.ones_like(a) if weight is None else weight
         A = lay.gather(a * beta, -1e30)
@@ -121,6 +132,13 @@ class PairLogit(_GroupObjective):
 
     def der_hess(self, approx, target, weight, ctx=None):
         a, n = approx[0], approx.shape[1]
+        if approx.is_cuda and USE_KERNELS:
+            from ..ops import api as ops
+            if ctx is not None and ctx.pairs is not None:
+                d, h = ops.pair_logit_der(a, ctx.pairs, ctx.pairs_weight)
+            else:
+                d, h = ops.query_der("PairLogit", a, target, None, ctx.group_offsets)
+            return d.unsqueeze(0), h.unsqueeze(0)
         der = torch.zeros(n, device=a.device)
         hess = torch.zeros(n, device=a.device)
         if ctx is not None and ctx.pairs is not None:

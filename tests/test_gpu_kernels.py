@@ -638,3 +638,51 @@ def test_gpu_apply_geometries_match_cpu_apply(monkeypatch):
     assert pm.wide is not None and pm.dims == 3
     got = pm.predict_device(xd[:50_000]).t().double().cpu().numpy()
     assert np.allclose(got, mm.predict(X[:50_000], prediction_type="RawFormulaVal"), rtol=1e-5, atol=1e-5)
+
+
+def test_querywise_derivative_kernels_match_the_tensor_formulations():
+    """QueryRMSE / QuerySoftMax / PairLogit (pairs from labels and explicit pairs) on the device against the tensor code
+    of train/ranking.py on the same inputs."""
+    from catboost_b200.train import ranking as R
+    from catboost_b200.train.ranking import make_ranking_objective
+    g = torch.Generator().manual_seed(11)
+    sizes = torch.randint(1, 70, (400,), generator=g)
+    sizes[7] = 300                                        # a query longer than a warp several times over
+    off = torch.cat([torch.zeros(1, dtype=torch.long), torch.cumsum(sizes, 0)])
+    n = int(off[-1])
+    approx = torch.randn(1, n, generator=g).cuda()
+    target = torch.randint(0, 5, (n,), generator=g).float().cuda()
+    weight = (torch.rand(n, generator=g) + 0.5).cuda()
+
+    class Ctx:
+        pass
+    ctx = Ctx()
+    ctx.group_offsets, ctx.pairs, ctx.pairs_weight, ctx.device = off.cuda(), None, None, torch.device("cuda")
+    for loss, w in (("QueryRMSE", weight), ("QueryRMSE", None), ("QuerySoftMax", weight), ("PairLogit", None)):
+        obj = make_ranking_objective(loss, {})
+        R.USE_KERNELS = True
+        d1, h1 = obj.der_hess(approx, target, w, ctx)
+        R.USE_KERNELS = False
+        try:
+            d0, h0 = obj.der_hess(approx, target, w, ctx)
+        finally:
+            R.USE_KERNELS = True
+        assert torch.allclose(d1, d0, rtol=2e-4, atol=2e-5), (loss, float((d1 - d0).abs().max()))
+        assert torch.allclose(h1, h0, rtol=2e-4, atol=2e-5), (loss, float((h1 - h0).abs().max()))
+    # explicit pairs
+    P = 5000
+    q = torch.randint(0, 400, (P,), generator=g)
+    lo, sz = off[q], sizes[q]
+    wi = lo + (torch.rand(P, generator=g) * sz).long().clamp(max=sz - 1)
+    li = lo + (torch.rand(P, generator=g) * sz).long().clamp(max=sz - 1)
+    keep = wi != li
+    ctx.pairs = torch.stack([wi[keep], li[keep]], 1).cuda()
+    ctx.pairs_weight = (torch.rand(int(keep.sum()), generator=g) + 0.5).cuda()
+    obj = make_ranking_objective("PairLogit", {})
+    d1, h1 = obj.der_hess(approx, target, None, ctx)
+    R.USE_KERNELS = False
+    try:
+        d0, h0 = obj.der_hess(approx, target, None, ctx)
+    finally:
+        R.USE_KERNELS = True
+    assert torch.allclose(d1, d0, rtol=1e-4, atol=1e-5) and torch.allclose(h1, h0, rtol=1e-4, atol=1e-5)
