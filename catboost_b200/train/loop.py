@@ -374,10 +374,67 @@ def _best_scores(hist, metrics):
 _Y_CACHE = {}
 
 
-def _device_metric(metric, approx, y, w):
+_GROUP_CACHE = {}
+
+
+def _device_ndcg(metric, approx, y, w, pool):
+    """NDCG / DCG where the approximations live (catboost/cuda/targets/kernel/dcg.cu:17-347 does the same in three
+    steps): one stable sort of the documents by (query, descending approximation) -- the hand-written radix sort of
+    ops/cuda/cb_sort.cu on a 64-bit key, so ties keep the document order like the host metric --, the position of a
+    document inside its query, and a per-query sum of gain / discount; the ideal order is the same with the labels as
+    the sort key.  Parameters: top, type (Base / Exp), denominator (LogPosition / Position)."""
+    p = dict(getattr(metric, "params", None) or {})
+    if set(p) - {"top", "type", "denominator"} or pool is None or pool.group_id is None:
+        return None
+    if not approx.is_cuda or approx.shape[0] != 1 or np.ndim(y) != 1:
+        return None
+    dev = approx.device
+    n = len(y)
+    key = (id(pool), str(dev))
+    if key not in _GROUP_CACHE:
+        if len(_GROUP_CACHE) > 8:
+            _GROUP_CACHE.clear()
+        off = torch.from_numpy(np.asarray(pool.group_offsets(), dtype=np.int64)).to(dev)
+        sizes = off[1:] - off[:-1]
+        gid = torch.repeat_interleave(torch.arange(sizes.numel(), device=dev), sizes, output_size=n)
+        gw = torch.ones(sizes.numel(), dtype=torch.float64, device=dev) if w is None else \
+            torch.from_numpy(np.ascontiguousarray(w, dtype=np.float64)).to(dev)[off[:-1].clamp(max=max(n - 1, 0))]
+        _GROUP_CACHE[key] = (pool, off, gid, gw, torch.from_numpy(np.ascontiguousarray(y, dtype=np.float32)).to(dev))
+    _, off, gid, gw, yt = _GROUP_CACHE[key]
+    Q = off.numel() - 1
+    if Q <= 0:
+        return None
+    top = int(p.get("top", -1))
+    exp_num = str(p.get("type", "Base")) == "Exp"
+    log_den = str(p.get("denominator", "LogPosition")) == "LogPosition"
+
+    def dcg(values):
+        # ascending order of (query, -value): float bits mapped to integers of the same order
+        bits = (0.0 - values.float()).contiguous().view(torch.int32).long()          # 0.0 - x: never a negative zero
+        ordered = torch.where(bits < 0, bits ^ 0x7FFFFFFF, bits) + (1 << 31)          # in [0, 2^32)
+        _, order = ops.sort_pairs((gid << 32) | ordered)
+        rank = torch.arange(n, device=dev) - off[gid[order]]
+        rel = yt[order].double()
+        gain = (torch.pow(2.0, rel) - 1.0) if exp_num else rel
+        disc = torch.log2(rank.double() + 2.0) if log_den else (rank.double() + 1.0)
+        term = gain / disc
+        if top > 0:
+            term = torch.where(rank < top, term, torch.zeros_like(term))
+        return torch.zeros(Q, dtype=torch.float64, device=dev).index_add_(0, gid[order], term)
+
+    got = dcg(approx[0][:n])
+    if getattr(metric, "name", None) == "NDCG":
+        ideal = dcg(yt)
+        got = torch.where(ideal > 0, got / ideal.clamp_min(1e-300), torch.ones_like(got))
+    return float(((got * gw).sum() / gw.sum().clamp_min(1e-300)).item())
+
+
+def _device_metric(metric, approx, y, w, pool=None):
     """The common additive metrics evaluated where the approximations live (a host round trip of a 1M x 5 cursor per
     iteration costs more than growing the tree).  Returns None for metrics without a device formula."""
     name = getattr(metric, "name", None)
+    if name in ("NDCG", "DCG"):
+        return _device_ndcg(metric, approx, y, w, pool)
     if name not in ("Logloss", "RMSE", "MAE", "MultiClass", "Accuracy", "AUC", "Precision", "Recall", "F1", "R2") \
             or getattr(metric, "params", None):
         return None
@@ -446,7 +503,7 @@ def _device_metric(metric, approx, y, w):
 
 def _dist_metric(metric, approx, y, w, pool, ctx, objective):
     """Metric value over all ranks (additive metrics are averaged by weight; rank-local otherwise)."""
-    v = _device_metric(metric, approx, y, w) if isinstance(approx, torch.Tensor) else None
+    v = _device_metric(metric, approx, y, w, pool) if isinstance(approx, torch.Tensor) else None
     if v is None:
         v = _host_metric(metric, approx, y, w, pool, objective.dims)
     if ctx is None or not ctx.is_distributed:

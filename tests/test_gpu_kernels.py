@@ -686,3 +686,25 @@ def test_querywise_derivative_kernels_match_the_tensor_formulations():
     finally:
         R.USE_KERNELS = True
     assert torch.allclose(d1, d0, rtol=1e-4, atol=1e-5) and torch.allclose(h1, h0, rtol=1e-4, atol=1e-5)
+
+
+def test_device_side_ndcg_matches_the_host_metric():
+    """NDCG / DCG (top, Exp gains, position denominator) evaluated on the device with the stable radix sort against the
+    host metric, including queries whose approximations tie."""
+    from catboost_b200.data.pool import Pool
+    from catboost_b200.metrics import make_metric
+    from catboost_b200.train.loop import _device_metric
+    rng = np.random.default_rng(5)
+    sizes = rng.integers(1, 40, 700)
+    gid = np.repeat(np.arange(len(sizes)), sizes)
+    n = len(gid)
+    X = rng.standard_normal((n, 3)).astype(np.float32)
+    y = rng.integers(0, 5, n).astype(np.float32)
+    approx = np.round(rng.standard_normal(n), 1).astype(np.float32)         # one decimal: plenty of ties
+    pool = Pool(X, y, group_id=gid)
+    a_dev = torch.from_numpy(approx).cuda().unsqueeze(0)
+    for desc in ("NDCG", "NDCG:top=5", "NDCG:type=Exp", "NDCG:top=3;type=Exp;denominator=Position", "DCG:top=10"):
+        metric = make_metric(desc)
+        got = _device_metric(metric, a_dev, y, None, pool)
+        want = metric.eval(approx.reshape(-1, 1).astype(np.float64), y, None, group_offsets=pool.group_offsets())
+        assert got is not None and abs(got - want) < 1e-6 * max(1.0, abs(want)), (desc, got, want)
