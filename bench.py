@@ -40,6 +40,8 @@ CONFIGS = {
     # learning to rank: 2M documents x 700 features in groups of about 100, YetiRank, 64 borders; end-to-end fit() only
     "ranking": dict(rows=2_000_000, features=700, depth=6, border_count=64, model="YetiRank symmetric depth6 2Mx700"),
     "criteo": dict(rows=45_000_000, features=39, depth=8, border_count=128, model="Logloss symmetric depth8 13num+26cat CTR"),
+    # the CPU plumbing config: 100K x 50, 200 iterations, task_type CPU; runs without a GPU (wall time of fit())
+    "cpu": dict(rows=100_000, features=50, depth=6, border_count=128, model="Logloss symmetric depth6 100Kx50 on CPU"),
 }
 
 
@@ -198,6 +200,36 @@ def bench_ranking(args, cfg, rank, world, dev):
                                   "fit_breakdown_s": {k: round(float(v), 4) for k, v in tm.items()}},
                           "clocks": clocks, "ndcg_first_last": [float(ndcg[0]), float(ndcg[-1])], "apply": apply,
                           "gpu_launches": int(model._train_info.get("launches_per_iter", 0)) * iters}))
+    return 0
+
+
+def bench_cpu(args):
+    """Config 1: binary Logloss on the CPU trainer, 100K x 50, depth 6, 128 borders, learning rate 0.1, l2 3, 200
+    iterations; the metric is the wall time of the iterations phase of fit() scaled to 1000 iterations."""
+    import catboost_b200 as cb
+    cfg = CONFIGS["cpu"]
+    n, F = (args.rows or cfg["rows"]), cfg["features"]
+    rng = np.random.default_rng(1)
+    X = rng.standard_normal((n, F)).astype(np.float32)
+    w = rng.standard_normal(F) / np.sqrt(F)
+    y = (rng.random(n) < 1.0 / (1.0 + np.exp(-(X @ w + 0.5 * rng.standard_normal(n))))).astype(np.float32)
+    iters = args.e2e_iters if args.e2e_iters > 0 else 200
+    m = cb.CatBoostClassifier(loss_function="Logloss", iterations=iters, depth=6, border_count=128, learning_rate=0.1,
+                              l2_leaf_reg=3.0, task_type="CPU", random_seed=0, allow_writing_files=False, verbose=False)
+    t0 = time.perf_counter()
+    m.fit(X, y)
+    fit_s = time.perf_counter() - t0
+    tm = m._train_info.get("timings", {})
+    it_s = float(tm.get("iterations", fit_s))
+    acc = float((m.predict(X) == y).mean())
+    print(json.dumps({"metric": "sec/1000 iters (wall time of the iterations phase of fit(), CPU trainer)",
+                      "value": it_s / iters * 1000.0, "unit": "s/1000iter", "n_gpus": 0, "steps": iters, "warmup": 0,
+                      "ms_per_step": it_s / iters * 1000.0, "higher_is_better": False, "scaling": "strong",
+                      "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "impl": "ours",
+                      "config": {"model": cfg["model"], "global_batch": n, "seq_len": F, "parallelism": "one process, OpenMP"},
+                      "e2e": {"value": fit_s / iters * 1000.0, "unit": "s/1000iter", "fit_seconds": fit_s,
+                              "fit_breakdown_s": {k: round(float(v), 4) for k, v in tm.items()}},
+                      "learn_accuracy": acc, "gpu_launches": 0}))
     return 0
 
 
@@ -371,6 +403,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.config == "cpu":
+        return bench_cpu(args)
     if args.warmup < 3:
         args.warmup = 3
     if args.gpus > 1 and "RANK" not in os.environ:
