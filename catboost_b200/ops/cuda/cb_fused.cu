@@ -405,7 +405,8 @@ CB_API int cb_fused_geometry(CbFusedPlan* p, int level, int* slots_per_pass, int
         }
         spp = bundles[0].spp; C = bundles[0].C; gpc = bundles[0].gcnt;
     } else {
-        const int per_slot = p->a.h.S * 4 * p->a.h.B * 4 * ((p->a.h.statmax && !narrow) ? 2 : 1);
+        const bool narrow_cells = p->a.h.statmax && p->a.h.narrow;      // one int32 per cell, any number of statistics
+        const int per_slot = p->a.h.S * 4 * p->a.h.B * 4 * ((p->a.h.statmax && !narrow_cells) ? 2 : 1);
         const bool ring = p->a.h.statmax && p->a.h.S == 2;      // per-warp compaction rings (16 bytes x 64 entries)
         int ring_bytes = ring ? (thr / 32) * 64 * 16 + 16 : 0;
         int budget = p->max_smem - ring_bytes;

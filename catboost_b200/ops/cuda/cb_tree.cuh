@@ -289,11 +289,15 @@ static __device__ void cb_hist_item_n(const CbHistArgs& a, int* sh, int g, long 
 }
 
 // Fixed-point variant of cb_hist_item (see CbHistArgs::statmax).  sh layout: int [slot][s][part][j][B], part 0 = high.
+// NARROW: one int32 cell per (statistic, feature, bin) whose scale is (2^31 - 1) / (documents of this item), so that the
+// cell cannot overflow (12-16 bits per addend); else a signed high / unsigned low pair of 12 + 12 bits (exact).
+template <bool NARROW>
 static __device__ void cb_hist_item_q(const CbHistArgs& a, int* sh, int g, long long item, long long d_begin,
                                       long long d_end, int slot_begin, int slot_count) {
     const int B = a.B;
     const int S = a.S;
-    const int total = slot_count * S * 8 * B;
+    const int PS = NARROW ? 4 : 8;                  // rows of B cells per (slot, statistic)
+    const int total = slot_count * S * PS * B;
     for (int i = threadIdx.x; i < total; i += blockDim.x) sh[i] = 0;
     __syncthreads();
 
@@ -301,7 +305,8 @@ static __device__ void cb_hist_item_q(const CbHistArgs& a, int* sh, int g, long 
     const int level = a.level;
     const int nslots = cb_hist_nslots(a);
     const unsigned int pmask = (unsigned int)(nslots - 1);
-    const int slot_stride = S * 8 * B;
+    const int slot_stride = S * PS * B;
+    const float qmax = NARROW ? fminf(8388607.0f, floorf(2147483647.0f / (float)max(d_end - d_begin, 1ll)) - 1.0f) : 8388607.0f;
     for (long long i = d_begin + (long long)threadIdx.x * 4; i < d_end; i += (long long)blockDim.x * 4) {
         const uint4 w = *reinterpret_cast<const uint4*>(bg + i);
         const ushort4 lf = *reinterpret_cast<const ushort4*>(a.leaf + i);
@@ -326,21 +331,26 @@ static __device__ void cb_hist_item_q(const CbHistArgs& a, int* sh, int g, long 
             off[k] = (take && (unsigned)slot < (unsigned)slot_count) ? slot * slot_stride : -1;
         }
         for (int s = 0; s < S; ++s) {
-            const float sc = 8388607.0f / fmaxf(a.statmax[s], 1e-30f);
+            const float sc = qmax / fmaxf(a.statmax[s], 1e-30f);
             const float4 t = *reinterpret_cast<const float4*>(a.stats + (long long)s * a.d.npad + i);
             const float tv[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 if (off[k] >= 0) {
                     const int q = __float2int_rn(tv[k] * sc);
-                    const int hi = q >> 12;
-                    const unsigned int lo = (unsigned int)q & 4095u;
-                    int* base = sh + off[k] + s * 8 * B;
+                    int* base = sh + off[k] + s * PS * B;
+                    if (NARROW) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const unsigned int bin = (wv[k] >> (8 * j)) & 255u;
-                        atomicAdd(base + j * B + bin, hi);
-                        atomicAdd(reinterpret_cast<unsigned int*>(base) + (4 + j) * B + bin, lo);
+                        for (int j = 0; j < 4; ++j) atomicAdd(base + j * B + ((wv[k] >> (8 * j)) & 255u), q);
+                    } else {
+                        const int hi = q >> 12;
+                        const unsigned int lo = (unsigned int)q & 4095u;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const unsigned int bin = (wv[k] >> (8 * j)) & 255u;
+                            atomicAdd(base + j * B + bin, hi);
+                            atomicAdd(reinterpret_cast<unsigned int*>(base) + (4 + j) * B + bin, lo);
+                        }
                     }
                 }
             }
@@ -356,14 +366,19 @@ static __device__ void cb_hist_item_q(const CbHistArgs& a, int* sh, int g, long 
         const int r = c / B4;            // (slot * S + s) * 4 + j
         const int j = r & 3;
         const int ss = r >> 2;           // slot * S + s
-        const float inv = fmaxf(a.statmax[ss % S], 1e-30f) * (1.0f / 8388607.0f);
-        const int4 hi = *reinterpret_cast<const int4*>(sh + (size_t)ss * 8 * B + j * B + b4 * 4);
-        const uint4 lo = *reinterpret_cast<const uint4*>(sh + (size_t)ss * 8 * B + (4 + j) * B + b4 * 4);
+        const float inv = fmaxf(a.statmax[ss % S], 1e-30f) / qmax;
         float4 v;
-        v.x = fmaf((float)hi.x, 4096.0f * inv, (float)lo.x * inv);
-        v.y = fmaf((float)hi.y, 4096.0f * inv, (float)lo.y * inv);
-        v.z = fmaf((float)hi.z, 4096.0f * inv, (float)lo.z * inv);
-        v.w = fmaf((float)hi.w, 4096.0f * inv, (float)lo.w * inv);
+        if (NARROW) {
+            const int4 q4 = *reinterpret_cast<const int4*>(sh + (size_t)ss * 4 * B + j * B + b4 * 4);
+            v = make_float4((float)q4.x * inv, (float)q4.y * inv, (float)q4.z * inv, (float)q4.w * inv);
+        } else {
+            const int4 hi = *reinterpret_cast<const int4*>(sh + (size_t)ss * 8 * B + j * B + b4 * 4);
+            const uint4 lo = *reinterpret_cast<const uint4*>(sh + (size_t)ss * 8 * B + (4 + j) * B + b4 * 4);
+            v.x = fmaf((float)hi.x, 4096.0f * inv, (float)lo.x * inv);
+            v.y = fmaf((float)hi.y, 4096.0f * inv, (float)lo.y * inv);
+            v.z = fmaf((float)hi.z, 4096.0f * inv, (float)lo.z * inv);
+            v.w = fmaf((float)hi.w, 4096.0f * inv, (float)lo.w * inv);
+        }
         dst[c] = v;
     }
     __syncthreads();
@@ -901,7 +916,8 @@ static __device__ void cb_hist_phase(const CbHistArgs& a, float* sh, int cta, in
             if (quant2 && a.narrow) cb_hist_item_q2<true>(a, reinterpret_cast<int*>(sh), g, it2, (int)k, nK, sb, sc);
             else if (quant2) cb_hist_item_q2<false>(a, reinterpret_cast<int*>(sh), g, it2, (int)k, nK, sb, sc);
             else if (a.statmax && !a.priv) { if (b < e) cb_hist_item_n(a, reinterpret_cast<int*>(sh), g, min(b, e), e, sb, sc); }
-            else if (a.statmax) cb_hist_item_q(a, reinterpret_cast<int*>(sh), g, it2, min(b, e), e, sb, sc);
+            else if (a.statmax && a.narrow) cb_hist_item_q<true>(a, reinterpret_cast<int*>(sh), g, it2, min(b, e), e, sb, sc);
+            else if (a.statmax) cb_hist_item_q<false>(a, reinterpret_cast<int*>(sh), g, it2, min(b, e), e, sb, sc);
             else if (b < e || a.priv) cb_hist_item(a, sh, g, it2, min(b, e), e, sb, sc);
         }
     }

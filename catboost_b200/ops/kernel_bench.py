@@ -209,18 +209,22 @@ def main(argv=None):
     if want("multiclass"):
         K = 5
         yk = rng.integers(0, K, n).astype(np.float32)
-        engk = GpuObliviousEngine(store, torch.from_numpy(yk), None, torch.zeros((K, n)), make_objective("MultiClass", {}, n_classes=K),
-                                  depth=args.depth, iterations=4, learning_rate=0.1, l2_leaf_reg=3.0, leaf_iterations=1,
-                                  use_graph=False, dims=K, quantized_hist="wide")
-        engk.step(1)
-        ms = _time(lambda: engk._grad(), args.reps, flush)
-        report("cb_mc_grad_kernel (K=5)", ms, n * (K * 4 * 2 + 4 + 2 + (K + 1) * 4), "approx rw, target, leaf, K + 1 statistic rows")
-        ms = _time(lambda: engk._leaves(), args.reps, flush)
-        report("cb_mc_leaf_kernel (K=5: sums + K x K Cholesky per leaf)", ms, n * (K * 4 + 4 + 2), "approx, target, leaf")
-        for level in (0, args.depth - 1):
-            ms = _time(lambda: engk._level_fused(level), args.reps, flush)
-            report(f"cb_level_fused_kernel[K=5, level={level}]", ms, n * (((F + 3) // 4) * 4 + 2 + (K + 1) * 4), "S = 6 statistics, hi/lo cells")
-        engk.close()
+        for cells, label in ((True, "single int32 cells"), ("wide", "hi/lo cells")):
+            engk = GpuObliviousEngine(store, torch.from_numpy(yk), None, torch.zeros((K, n)),
+                                      make_objective("MultiClass", {}, n_classes=K), depth=args.depth, iterations=4,
+                                      learning_rate=0.1, l2_leaf_reg=3.0, leaf_iterations=1, use_graph=False, dims=K,
+                                      quantized_hist=cells)
+            engk.step(1)
+            if cells is True:
+                ms = _time(lambda: engk._grad(), args.reps, flush)
+                report("cb_mc_grad_kernel (K=5)", ms, n * (K * 4 * 2 + 4 + 2 + (K + 1) * 4), "approx rw, target, leaf, K + 1 statistic rows")
+                ms = _time(lambda: engk._leaves(), args.reps, flush)
+                report("cb_mc_leaf_kernel (K=5: sums + K x K Cholesky per leaf)", ms, n * (K * 4 + 4 + 2), "approx, target, leaf")
+            for level in (0, args.depth - 1):
+                ms = _time(lambda: engk._level_fused(level), args.reps, flush)
+                report(f"cb_level_fused_kernel[K=5, level={level}, {label}]", ms, n * (((F + 3) // 4) * 4 + 2 + (K + 1) * 4),
+                       "S = 6 statistics")
+            engk.close()
     if want("predict_wide"):
         Fw, Tw = 700, 200
         nw = min(n, 1_000_000)

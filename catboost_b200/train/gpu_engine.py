@@ -117,10 +117,8 @@ class GpuObliviousEngine:
                 raise ValueError("too many classes for the device trainer")
             if der_fn is not None or ext_der is not None:
                 raise ValueError("external derivatives are one-dimensional")
-            if self.quantized_hist:
-                self.narrow_hist = False          # single-cell bundles exist for two statistics only: exact hi/lo cells
-            else:
-                self.quantized_hist = True
+            if not self.quantized_hist:
+                self.quantized_hist, self.narrow_hist = True, False       # no fp32-atomic path for K + 1 statistics
         self.S = K + 1
         self.L = 1 << depth
         f32, i32, i64, f64 = torch.float32, torch.int32, torch.int64, torch.float64

@@ -234,13 +234,18 @@ def test_multiclass_device_trainer_matches_the_tensor_learner():
     y = np.argmax(X @ centers.T + 0.5 * rng.standard_normal((n, K)).astype(np.float32), axis=1).astype(np.float32)
     store = _store_of(X, (y > 0).astype(np.float32), 32)
     obj = make_objective("MultiClass", {}, n_classes=K)
-    eng = GpuObliviousEngine(store, torch.from_numpy(y), None, torch.zeros((K, n)), obj, depth=depth, iterations=2,
-                             learning_rate=0.5, l2_leaf_reg=3.0, random_strength=0.0, bootstrap_type="No",
-                             leaf_method="Newton", leaf_iterations=1, seed=0, dims=K)
-    eng.step(1)
-    loss_dev = eng.current_learn_loss()
-    sp, vals, wts = eng.finish()
-    eng.close()
+    outs = {}
+    for cells in (True, "wide"):                 # single int32 cells (the default) and exact hi / lo pairs
+        eng = GpuObliviousEngine(store, torch.from_numpy(y), None, torch.zeros((K, n)), obj, depth=depth, iterations=2,
+                                 learning_rate=0.5, l2_leaf_reg=3.0, random_strength=0.0, bootstrap_type="No",
+                                 leaf_method="Newton", leaf_iterations=1, seed=0, dims=K, quantized_hist=cells)
+        assert eng.narrow_hist == (cells is True)
+        eng.step(1)
+        loss_dev = eng.current_learn_loss()
+        outs[cells] = eng.finish()
+        eng.close()
+    assert np.array_equal(outs[True][0][:, :, :2], outs["wide"][0][:, :, :2])          # same features and bins
+    sp, vals, wts = outs[True]
     o = resolve_options(dict(loss_function="MultiClass", depth=depth, task_type="GPU", bootstrap_type="No",
                              random_strength=0, leaf_estimation_iterations=1, learning_rate=0.5, l2_leaf_reg=3.0,
                              border_count=32), "MultiClass", n)
