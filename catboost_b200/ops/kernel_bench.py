@@ -225,6 +225,20 @@ def main(argv=None):
                 report(f"cb_level_fused_kernel[K=5, level={level}, {label}]", ms, n * (((F + 3) // 4) * 4 + 2 + (K + 1) * 4),
                        "S = 6 statistics")
             engk.close()
+    if want("yetirank"):
+        from ..train.ranking import YetiRank, _GroupLayout
+        g = torch.Generator().manual_seed(6)
+        sizes = torch.randint(5, 201, (max(1, n // 100),), generator=g)
+        off = torch.cat([torch.zeros(1, dtype=torch.long), torch.cumsum(sizes, 0)])
+        off = off[off <= n]
+        nq = int(off[-1])
+        lay = _GroupLayout(off.to(dev))
+        ya = YetiRank({})
+        a_ = torch.randn(nq, generator=g).to(dev)
+        t_ = torch.randint(0, 5, (nq,), generator=g).float().to(dev)
+        ms = _time(lambda: ya._der_hess_device(a_, t_, None, lay), args.reps, flush)
+        report("cb_yetirank_kernel (queries of 5..200 documents, 10 permutations)", ms, nq * (4 + 4 + 8),
+               f"{lay.Q} queries, {nq} documents")
     if want("predict_wide"):
         Fw, Tw = 700, 200
         nw = min(n, 1_000_000)

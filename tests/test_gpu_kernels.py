@@ -227,6 +227,8 @@ def test_yetirank_kernel_matches_tensor_reference():
     from catboost_b200.train.ranking import YetiRank, _GroupLayout
     rng = np.random.default_rng(5)
     sizes = rng.integers(1, 70, 300)
+    # longer queries: 4 and 8 keys per lane in the warp-per-permutation kernel, and two that the block-wide kernel takes
+    sizes[3], sizes[10], sizes[20], sizes[30], sizes[40] = 130, 250, 256, 300, 600
     off = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
     n = int(off[-1])
     dev = torch.device("cuda")
