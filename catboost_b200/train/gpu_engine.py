@@ -146,6 +146,7 @@ class GpuObliviousEngine:
         self.fused_leaf_steps = bool(fused_leaf_steps)
         self.leaf_backtracking = {"No": 0, "AnyImprovement": 1, "Armijo": 2}[str(leaf_backtracking or "AnyImprovement")]
         self.fuse_leaf_update = bool(fuse_leaf_update)
+        self._check_each = os.environ.get("CB200_CHECK") == "1"      # invariants after every iteration (slow, debugging)
         self.skip_dominant_bin = bool(skip_dominant_bin) and os.environ.get("CB200_SKIP_DOMINANT", "1") != "0"
         self.stats = torch.zeros((self.S, npad), dtype=f32, device=dev)
         self.scal = torch.zeros(4, dtype=f64, device=dev)
@@ -560,6 +561,8 @@ class GpuObliviousEngine:
                     self._capture()
                 self.graph.replay()
             self.done += 1
+            if self._check_each:
+                self.check_invariants()
 
     def current_learn_loss(self, pinned: Optional[torch.Tensor] = None) -> float:
         """Mean learn loss including the newest tree (one streaming kernel + a 16-byte device->host read),
@@ -601,6 +604,49 @@ class GpuObliviousEngine:
         return sp, self.model_vals[:T].cpu().numpy(), self.model_wts[:T].cpu().numpy()
 
     # ------------------------------------------------------------------------------------------------------
+    def check_invariants(self):
+        """Checks of the device state after the latest iteration (a debugging aid in the place of a race detector: a lost
+        update, a stale read across ranks or an out-of-range write shows up here long before it shows up in the loss).
+        Synchronises the device.  Raises RuntimeError with the first violated invariant.  ``CB200_CHECK=1`` makes the
+        training loop call it after every iteration."""
+        torch.cuda.synchronize(self.dev)
+        if self.arena is not None:
+            self.arena.check_status()                       # a bounded device wait that ran out of time
+        T, n, F = self.done, self.n, self.store.F
+        if T == 0:
+            return
+        sp = self.splits[(T - 1) * self.depth: T * self.depth]
+        feat, bins = sp[:, 0], sp[:, 1]
+        if bool(((feat < -1) | (feat >= F)).any()):
+            raise RuntimeError(f"invariant: split feature outside [-1, {F}) in tree {T - 1}: {feat.tolist()}")
+        nb = self.store.feat_nb.to(self.dev)
+        ok = feat >= 0
+        if bool(ok.any()) and bool((bins[ok] >= nb[feat[ok].long()]).any() or (bins[ok] < 0).any()):
+            raise RuntimeError(f"invariant: split bin outside its feature's bins in tree {T - 1}")
+        leaf = self.leaf[:n].long() & 0xFFFF
+        if bool((leaf >= self.L).any()):
+            raise RuntimeError("invariant: a document's leaf index is outside the tree")
+        if not bool(torch.isfinite(self.approx).all()):
+            raise RuntimeError("invariant: a non-finite approximation")
+        if not bool(torch.isfinite(self.model_vals[T - 1]).all()):
+            raise RuntimeError("invariant: a non-finite leaf value")
+        # the leaf weights of the newest tree are the document weights, summed over all ranks
+        w_local = float(n) if self.weight is None else float(self.weight[:n].double().sum().item())
+        tot = torch.tensor([w_local], dtype=torch.float64, device=self.dev)
+        if self.ctx is not None and self.ctx.is_distributed:
+            self.ctx.all_reduce_sum_(tot)
+        got = float(self.model_wts[T - 1].double().sum().item())
+        if abs(got - float(tot.item())) > 1e-4 * max(1.0, float(tot.item())):
+            raise RuntimeError(f"invariant: leaf weights of tree {T - 1} sum to {got}, the data weighs {float(tot.item())}")
+        # every rank holds the same tree
+        if self.ctx is not None and self.ctx.is_distributed:
+            mine = sp[:, :2].contiguous().long()
+            ref = mine.clone()
+            import torch.distributed as dist
+            dist.broadcast(ref, src=0, group=self.ctx.group)
+            if not bool(torch.equal(mine, ref)):
+                raise RuntimeError(f"invariant: rank {self.ctx.rank} holds a different tree {T - 1} than rank 0")
+
     def export_trees(self):
         """(splits [T, depth, 4], leaf values [T, L], leaf weights [T, L]) of the finished iterations, on the host.
         Unlike ``finish`` this leaves the engine ready to continue (used for snapshots)."""

@@ -710,3 +710,31 @@ def test_device_side_ndcg_matches_the_host_metric():
         got = _device_metric(metric, a_dev, y, None, pool)
         want = metric.eval(approx.reshape(-1, 1).astype(np.float64), y, None, group_offsets=pool.group_offsets())
         assert got is not None and abs(got - want) < 1e-6 * max(1.0, abs(want)), (desc, got, want)
+
+
+def test_engine_invariant_checks(monkeypatch):
+    """CB200_CHECK=1: the trainer verifies its device state after every iteration (split ranges, leaf indices, finite
+    values, leaf weights against the data); a state that breaks an invariant is reported."""
+    import catboost_b200 as cb
+    rng = np.random.default_rng(9)
+    X = rng.standard_normal((30_000, 8)).astype(np.float32)
+    y = (X[:, 0] + X[:, 1] * X[:, 2] > 0).astype(int)
+    w = (rng.random(30_000) + 0.5).astype(np.float32)
+    monkeypatch.setenv("CB200_CHECK", "1")
+    m = cb.CatBoostClassifier(iterations=12, depth=5, learning_rate=0.3, task_type="GPU", verbose=False,
+                              allow_writing_files=False)
+    m.fit(X, y, sample_weight=w)
+    assert m._train_info["launches_per_iter"] > 0
+    # a corrupted state is caught
+    store = __import__("tests.test_gpu_precision", fromlist=["_store_of"])._store_of(X, y.astype(np.float32), 32)
+    eng = __import__("tests.test_gpu_precision", fromlist=["_engine"])._engine(store, y.astype(np.float32), "narrow", 4, 3)
+    eng.step(2)
+    eng.check_invariants()
+    eng.model_wts[1, 0] += 100.0
+    with pytest.raises(RuntimeError, match="leaf weights"):
+        eng.check_invariants()
+    eng.model_wts[1, 0] -= 100.0
+    eng.approx[5] = float("nan")
+    with pytest.raises(RuntimeError, match="non-finite"):
+        eng.check_invariants()
+    eng.close()
