@@ -113,11 +113,13 @@ class GpuPredictor:
         if n == 0:
             return res
         if chunk_rows <= 0:
-            chunk_rows = max(4096, min(n, (64 << 20) // max(F, 1)))          # about 256 MB of floats per buffer
+            # about 256 MB of floats per buffer; one geometry for every batch above 64K rows, so that the buffers kept
+            # from the previous call fit the next one whatever its length
+            chunk_rows = max(4096, (64 << 20) // max(F, 1)) if n > 65536 else n
         xt = torch.from_numpy(X)
         src_pinned = bool(xt.is_pinned())            # the caller's rows are page-locked: no staging copy needed
         with torch.cuda.device(self.dev):
-            nbuf = 2 if n > chunk_rows else 1
+            nbuf = 2 if n > 65536 or n > chunk_rows else 1
             key = (chunk_rows, F, src_pinned, nbuf)
             bufs = self.__dict__.setdefault("_bufs", {}).get(key)
             if bufs is None:
@@ -129,8 +131,9 @@ class GpuPredictor:
                 streams = [torch.cuda.Stream(self.dev) for _ in range(nbuf)]
                 bufs = (stage, back, dbuf, dout, streams)
                 pinned = nbuf * chunk_rows * (self.dims + (0 if src_pinned else F)) * 4
-                self._bufs.clear()                                # one geometry at a time
                 if pinned <= (1 << 30):
+                    while len(self._bufs) >= 2:                   # at most two geometries are kept (a small and a large one)
+                        self._bufs.pop(next(iter(self._bufs)))
                     self._bufs[key] = bufs
             stage, back, dbuf, dout, streams = bufs
             pending = [None] * nbuf                          # (event, r0, r1) of the chunk in flight on every buffer
