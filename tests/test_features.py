@@ -1182,3 +1182,28 @@ def test_reference_boston_and_mushroom_models():
     raw = np.asarray(m.predict(cb.Pool(data, cat_features=list(range(data.shape[1]))), prediction_type="RawFormulaVal"), dtype=float)
     got = np.where(raw > 0, "p", "e")
     assert (got == labels).all(), int((got != labels).sum())
+
+
+def test_carry_and_uplift():
+    """catboost.carry: a model with float features fixed reads them no more; lists of values give one output dimension
+    each; uplift is the difference between two fixings.  By flat index and by name."""
+    from catboost_b200.carry import carry, uplift
+    rng = np.random.default_rng(0)
+    X = rng.standard_normal((2500, 5)).astype(np.float32)
+    y = (2 * X[:, 1] + X[:, 3] * X[:, 1] + 0.1 * rng.standard_normal(2500)).astype(np.float32)
+    m = cb.CatBoostRegressor(iterations=40, depth=4, learning_rate=0.3, verbose=False, allow_writing_files=False)
+    m.fit(cb.Pool(X, y, feature_names=["a", "b", "c", "d", "e"]))
+    fixed = X.copy()
+    fixed[:, 1] = 0.5
+    assert np.allclose(carry(m, {1: 0.5}).predict(X), m.predict(fixed))
+    assert np.allclose(carry(m, {"b": 0.5}).predict(X), m.predict(fixed))
+    p = carry(m, {1: [0.5, -1.0], 3: [0.0, 2.0]}).predict(X, prediction_type="RawFormulaVal")
+    assert p.shape == (2500, 2)
+    for j, (v1, v3) in enumerate([(0.5, 0.0), (-1.0, 2.0)]):
+        fixed[:, 1], fixed[:, 3] = v1, v3
+        assert np.allclose(p[:, j], m.predict(fixed))
+    lo, hi = X.copy(), X.copy()
+    lo[:, 1], hi[:, 1] = 0.0, 1.0
+    assert np.allclose(uplift(m, {"b": (0.0, 1.0)}).predict(X), m.predict(hi) - m.predict(lo), atol=1e-9)
+    with pytest.raises(cb.CatBoostError):
+        carry(m, {1: [1.0, 2.0], 3: [1.0]})
