@@ -557,8 +557,16 @@ def _exact_leaves(objective, approx, target, weight, idx, n_leaves, n, lr, ctx):
         res = torch.cat([p[0] for p in parts]).to(approx.device)
         w = torch.cat([p[1] for p in parts]).to(approx.device)
         idx = torch.cat([p[2] for p in parts]).to(approx.device)
-    order = torch.argsort(res, stable=True)
-    order = order[torch.argsort(idx[order], stable=True)]
+    if res.is_cuda:
+        # one stable radix sort (ops/cuda/cb_sort.cu) by (leaf, residual): the residual's float32 bits mapped to integers
+        # of the same order sit below the leaf number in a 64-bit key (catboost/cuda/methods/kernel/exact_estimation.cu
+        # sorts per-leaf segments for the same purpose)
+        bits = (res.float() + 0.0).contiguous().view(torch.int32).long()
+        ordered = torch.where(bits < 0, bits ^ 0x7FFFFFFF, bits) + (1 << 31)
+        _, order = ops.sort_pairs((idx.long() << 32) | ordered)
+    else:
+        order = torch.argsort(res, stable=True)
+        order = order[torch.argsort(idx[order], stable=True)]
     li, r, ww = idx[order], res[order], w[order]
     cw = torch.cumsum(ww, 0)
     tot = torch.zeros(n_leaves, dtype=torch.float64, device=approx.device).index_add_(0, li, ww)

@@ -738,3 +738,21 @@ def test_engine_invariant_checks(monkeypatch):
     with pytest.raises(RuntimeError, match="non-finite"):
         eng.check_invariants()
     eng.close()
+
+
+def test_exact_quantile_leaves_on_the_device_match_the_cpu_trainer():
+    """MAE / Quantile with leaf_estimation_method='Exact': the per-leaf weighted quantiles come from one radix sort by
+    (leaf, residual) on the device; the model equals the CPU trainer's on the same borders."""
+    import catboost_b200 as cb
+    rng = np.random.default_rng(14)
+    X = rng.standard_normal((20_000, 6)).astype(np.float32)
+    y = (X[:, 0] + 0.5 * X[:, 1] ** 2 + rng.standard_t(3, 20_000) * 0.3).astype(np.float32)
+    for loss in ("MAE", "Quantile:alpha=0.8"):
+        preds = {}
+        for task in ("GPU", "CPU"):
+            m = cb.CatBoostRegressor(loss_function=loss, iterations=15, depth=4, learning_rate=0.3, task_type=task,
+                                     leaf_estimation_method="Exact", bootstrap_type="No", random_strength=0, border_count=32,
+                                     verbose=False, allow_writing_files=False, boost_from_average=True)
+            m.fit(X, y)
+            preds[task] = m.predict(X)
+        assert np.allclose(preds["GPU"], preds["CPU"], rtol=1e-3, atol=1e-3), (loss, float(np.abs(preds["GPU"] - preds["CPU"]).max()))
