@@ -463,6 +463,9 @@ def enforce_monotone_leaves(vals: np.ndarray, wts: np.ndarray, splits: np.ndarra
     return vals
 
 
+_LANGEVIN_DRAWS = [0]
+
+
 def estimate_leaves(objective, approx, target, weight, leaf, n_leaves, n, opts, ctx=None, obj_ctx=None,
                     total_weight: Optional[float] = None):
     """Leaf values [n_leaves, dims] (already multiplied by the learning rate) and leaf weights [n_leaves]."""
@@ -501,6 +504,18 @@ def estimate_leaves(objective, approx, target, weight, leaf, n_leaves, n, opts, 
         sd, sh, sw = sums[:, :dims], sums[:, dims:2 * dims], sums[:, 2 * dims]
         if leaf_w is None:
             leaf_w = sw.clone()
+        if getattr(opts, "langevin", False) and float(opts.diffusion_temperature or 0.0) > 0.0:
+            # Langevin boosting also perturbs the per-leaf derivative sums (catboost/private/libs/algo_helpers/
+            # langevin_utils.cpp:79-142): rate * sqrt(|sum of second derivatives| + l2) for Newton steps,
+            # rate * sqrt(leaf weight + l2) for gradient steps, rate = sqrt(2 / learning rate / temperature); leaves
+            # without weight are left alone.  Every rank draws the same numbers (seeded by the iteration state).
+            rate = math.sqrt(2.0 / lr / float(opts.diffusion_temperature))
+            gen = torch.Generator(device="cpu")
+            _LANGEVIN_DRAWS[0] += 1                       # the same sequence on every rank: they call in lockstep
+            gen.manual_seed((int(opts.random_seed) * 1000003 + 7919 * _LANGEVIN_DRAWS[0]) & 0x7FFFFFFF)
+            z = torch.randn((n_leaves, dims), generator=gen).to(dev)
+            scale = torch.sqrt((sh.abs() if method == "Newton" else sw.unsqueeze(1).expand_as(sd)) + l2)
+            sd = sd + torch.where(sw.unsqueeze(1) >= 1e-9, rate * scale * z, torch.zeros_like(sd)).to(sd.dtype)
         blocks = getattr(objective, "hess_blocks", None) if (method == "Newton" and dims > 1) else None
         if blocks is not None:
             # the K x K Hessian block of every leaf (catboost/cuda/methods/leaves_estimation/descent_helpers.cpp:91-117):
