@@ -95,6 +95,46 @@ def sort_pairs(keys: torch.Tensor):
     return ka, va.long()
 
 
+_LEAF_NEWTON_STATE = {}
+
+
+def leaf_newton(loss_id: int, p0: float, p1: float, approx: torch.Tensor, target: torch.Tensor, weight, leaf: torch.Tensor,
+                n: int, n_leaves: int, steps: int, newton: bool, l2: float, lr: float, backtracking: str = "No"):
+    """All leaf-estimation steps of one tree in one cooperative launch (ops/cuda/cb_leaf.cu, the kernel of the device
+    trainer) for a tree of any shape: ``leaf`` holds the leaf number of every document.  Returns (leaf values times the
+    learning rate [n_leaves], leaf weights [n_leaves]) on the device, or None when the tree has too many leaves for the
+    kernel's shared-memory cells.  One rank only."""
+    dev = approx.device
+    lib = native.cuda_lib()
+    L = int(n_leaves)
+    grid = int(lib.cb_leaf_newton_max_grid(L))
+    if grid <= 0:
+        return None
+    key = (str(dev), L)
+    st = _LEAF_NEWTON_STATE.get(key)
+    if st is None:
+        if len(_LEAF_NEWTON_STATE) > 16:
+            _LEAF_NEWTON_STATE.clear()
+        st = (torch.zeros(int(lib.cb_leaf_newton_sums_doubles(L)), dtype=torch.float64, device=dev),
+              torch.zeros(1, dtype=torch.int32, device=dev), torch.zeros(2, dtype=torch.float32, device=dev),
+              torch.zeros(1, dtype=torch.int32, device=dev))
+        _LEAF_NEWTON_STATE[key] = st
+    sums, counter, vmax, iter_ptr = st
+    delta = torch.zeros(L, dtype=torch.float32, device=dev)
+    cur = torch.zeros(L, dtype=torch.float32, device=dev)
+    leaf_w = torch.zeros(L, dtype=torch.float32, device=dev)
+    a, t = approx.contiguous().float(), target.contiguous().float()
+    w = None if weight is None else weight.contiguous().float()
+    bt = {"No": 0, "AnyImprovement": 1, "Armijo": 2}[str(backtracking or "No")]
+    rc = lib.cb_leaf_newton(int(loss_id), float(p0), float(p1), _p(a), _p(t), _p(w), _p(leaf), int(n), L, _p(delta), _p(sums),
+                            _p(counter), _p(vmax), int(steps), 1 if newton else 0, float(l2), float(lr), _p(cur), None, None, L,
+                            _p(iter_ptr), _p(leaf_w), None, bt, grid, _stream(dev))
+    if rc == -2:
+        return None
+    native.cuda_check(rc, "cb_leaf_newton")
+    return cur, leaf_w
+
+
 def query_der(kind: str, approx: torch.Tensor, target: torch.Tensor, weight, offsets: torch.Tensor, beta: float = 1.0):
     """(der, hess) [n] of a query-wise objective on the GPU (ops/cuda/cb_querywise.cu).  ``kind``: 'QueryRMSE',
     'QuerySoftMax' or 'PairLogit' (all pairs of a query whose labels differ); ``offsets``: int64 [Q + 1] row offsets."""

@@ -464,6 +464,7 @@ def enforce_monotone_leaves(vals: np.ndarray, wts: np.ndarray, splits: np.ndarra
 
 
 _LANGEVIN_DRAWS = [0]
+USE_LEAF_KERNEL = True        # False: the tensor formulation below also on the GPU (the oracle of the kernel path)
 
 
 def estimate_leaves(objective, approx, target, weight, leaf, n_leaves, n, opts, ctx=None, obj_ctx=None,
@@ -476,6 +477,17 @@ def estimate_leaves(objective, approx, target, weight, leaf, n_leaves, n, opts, 
     idx = leaf[:n].long() & 0xFFFF
     if method == "Exact":
         return _exact_leaves(objective, approx, target, weight, idx, n_leaves, n, lr, ctx)
+    if (USE_LEAF_KERNEL and approx.is_cuda and dims == 1 and method in ("Newton", "Gradient") and objective.native_id is not None
+            and not (ctx is not None and ctx.is_distributed) and not getattr(opts, "langevin", False)
+            and not getattr(objective, "zero_mean_leaves", False) and leaf.dtype == torch.int16 and n_leaves <= 4096):
+        # one-dimensional losses with a device formula: every step of the estimation in one cooperative launch, the same
+        # kernel the symmetric-tree trainer uses (per-leaf sums in shared cells, the step taken on the device)
+        p0, p1 = (float(x) for x in objective.native_params())
+        out = ops.leaf_newton(int(objective.native_id), p0, p1, approx[0], target, None if weight is None else weight[:n],
+                              leaf, n, n_leaves, max(1, iters), method == "Newton", l2, lr,
+                              str(getattr(opts, "leaf_estimation_backtracking", None) or "No"))
+        if out is not None:
+            return out[0].double().unsqueeze(1).cpu().numpy(), out[1].cpu().numpy()
     delta = torch.zeros((n_leaves, dims), dtype=torch.float32, device=dev)
     wcol = torch.ones(n, dtype=torch.float32, device=dev) if weight is None else weight[:n]
     leaf_w = None

@@ -756,3 +756,30 @@ def test_exact_quantile_leaves_on_the_device_match_the_cpu_trainer():
             m.fit(X, y)
             preds[task] = m.predict(X)
         assert np.allclose(preds["GPU"], preds["CPU"], rtol=1e-3, atol=1e-3), (loss, float(np.abs(preds["GPU"] - preds["CPU"]).max()))
+
+
+@pytest.mark.parametrize("policy,loss", [("Depthwise", "Logloss"), ("Lossguide", "RMSE"), ("Depthwise", "Poisson")])
+def test_leaf_kernel_in_the_general_learner_matches_tensor_code(policy, loss):
+    """Depthwise / Lossguide trees estimate their leaves with the device trainer's cooperative kernel (all steps in one
+    launch, backtracking included); the models agree with the tensor formulation of the same steps."""
+    import catboost_b200 as cb
+    from catboost_b200.train import generic as G
+    rng = np.random.default_rng(31)
+    X = rng.standard_normal((40_000, 8)).astype(np.float32)
+    f = X[:, 0] * X[:, 1] + X[:, 2]
+    y = {"Logloss": (f + 0.4 * rng.standard_normal(len(X)) > 0).astype(np.float32),
+         "RMSE": (f + 0.2 * rng.standard_normal(len(X))).astype(np.float32),
+         "Poisson": rng.poisson(np.exp(0.4 * f)).astype(np.float32)}[loss]
+    w = (rng.random(len(X)) + 0.5).astype(np.float32)
+    cls = cb.CatBoostClassifier if loss == "Logloss" else cb.CatBoostRegressor
+    preds = {}
+    for use in (True, False):
+        G.USE_LEAF_KERNEL = use
+        try:
+            m = cls(loss_function=loss, iterations=12, depth=4, learning_rate=0.3, task_type="GPU", grow_policy=policy,
+                    max_leaves=12, bootstrap_type="No", random_strength=0, verbose=False, allow_writing_files=False)
+            m.fit(X, y, sample_weight=w)
+        finally:
+            G.USE_LEAF_KERNEL = True
+        preds[use] = m.predict(X, prediction_type="RawFormulaVal")
+    assert np.allclose(preds[True], preds[False], rtol=2e-3, atol=2e-3), float(np.abs(preds[True] - preds[False]).max())
