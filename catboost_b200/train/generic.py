@@ -116,6 +116,7 @@ class GenericLearner:
         self.gen.manual_seed(int(seed) + 12345)
         self.leaf = torch.zeros(store.npad, dtype=torch.int16, device=self.dev)
         self.use_count = int(opts.min_data_in_leaf) > 1
+        self._onehot_host = store.feat_onehot.cpu().numpy().astype(bool)        # read on the host by the growth loops
         self.monotone = None          # float tensor [F] in {-1, 0, +1} per flat feature, set by set_monotone()
         self.group_of_doc = None      # int64 [n] query number of every document: set for sampling_unit='Group'
         self.n_total = store.n
@@ -311,7 +312,7 @@ class GenericLearner:
             f, b = best // sc.B, best % sc.B
             if not math.isfinite(float(score[f, b].item())):
                 break
-            onehot = bool(self.store.feat_onehot[f].item())
+            onehot = bool(self._onehot_host[f])
             splits[level] = (f, b, 0, 1 if onehot else 0)
             ops.update_leaf(self.store, self.leaf, f, b, onehot, level)
             # which child of every leaf is the lighter one (by the weight column) decides what the next level accumulates
@@ -381,7 +382,7 @@ class GenericLearner:
                 left = len(node_split)
                 node_split.append([-1, 0, 0, -1])
                 node_split.append([-1, 0, 0, -1])
-                node_split[node] = [f, b, 1 if bool(self.store.feat_onehot[f].item()) else 0, left]
+                node_split[node] = [f, b, 1 if bool(self._onehot_host[f]) else 0, left]
                 new_frontier += [left, left + 1]
             if not new_frontier:
                 break
@@ -413,7 +414,7 @@ class GenericLearner:
             left = len(node_split)
             node_split += [[-1, 0, 0, -1], [-1, 0, 0, -1]]
             node_depth += [node_depth[node] + 1] * 2
-            node_split[node] = [f, b, 1 if bool(self.store.feat_onehot[f].item()) else 0, left]
+            node_split[node] = [f, b, 1 if bool(self._onehot_host[f]) else 0, left]
             step = [[-1, 0, 0, -1]] * len(node_split)
             step[node] = node_split[node]
             ops.update_nodes(self.store, self.leaf, torch.tensor(step, dtype=torch.int32, device=self.dev))
