@@ -245,6 +245,16 @@ def update_nodes(store: BinnedStore, leaf: torch.Tensor, node_split: torch.Tenso
                                                         sm * 8, _stream(dev)), "cb_update_nodes")
 
 
+def update_one_node(store: BinnedStore, leaf: torch.Tensor, node: int, feature: int, bin_: int, onehot: bool, left_child: int):
+    """The documents of ``node`` move to ``left_child`` (+1 when the split condition holds); GPU only (the split travels as
+    kernel arguments, nothing is uploaded)."""
+    dev = store.bins.device
+    sm, _ = device_info(dev)
+    native.cuda_check(native.cuda_lib().cb_update_one_node(ctypes.c_void_p(store.handle), _p(leaf), int(node), int(feature),
+                                                           int(bin_), 1 if onehot else 0, int(left_child), sm * 8,
+                                                           _stream(dev)), "cb_update_one_node")
+
+
 def leaf_index(store: BinnedStore, splits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Oblivious leaf index of every document for int32 split records [depth, 4] = (feature, bin, _, flags)."""
     dev = store.bins.device

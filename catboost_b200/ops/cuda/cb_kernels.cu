@@ -297,6 +297,29 @@ CB_API int cb_update_nodes(const CbData* d, unsigned short* leaf, const int* nod
     return 0;
 }
 
+// One node splits (leaf-wise growth): its documents move to left_child (+1 when the condition holds).  The split comes
+// as kernel arguments, so the growth loop uploads nothing per split.
+__global__ void __launch_bounds__(256) cb_update_one_node_kernel(CbData d, unsigned short* leaf, int node, int feature, int bin,
+                                                                 int onehot, int left_child) {
+    const uint32_t* col = d.bins + (long long)(feature >> 2) * d.npad;
+    const int sh = (feature & 3) * 8;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < d.n; i += stride) {
+        if (leaf[i] != (unsigned short)node) continue;
+        const unsigned int b = (col[i] >> sh) & 255u;
+        const bool right = onehot ? (b == (unsigned)bin) : (b > (unsigned)bin);
+        leaf[i] = (unsigned short)(left_child + (right ? 1 : 0));
+    }
+}
+
+CB_API int cb_update_one_node(const CbData* d, unsigned short* leaf, int node, int feature, int bin, int onehot, int left_child,
+                              int grid, cudaStream_t st) {
+    if (feature < 0 || feature >= d->F) return (int)cudaErrorInvalidValue;
+    cb_update_one_node_kernel<<<grid, 256, 0, st>>>(*d, leaf, node, feature, bin, onehot, left_child);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
 // ======================================================================================================
 // K6a  stand-alone histogram kernel (non-fused path, NCCL baseline, CPU-oracle tests)
 __global__ void __launch_bounds__(512) cb_hist_kernel(CbHistArgs a) {

@@ -143,6 +143,7 @@ _SIGS = {
     "cb_comm_destroy": (None, [c_void_p]),
     "cb_update_leaf": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "cb_update_nodes": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "cb_update_one_node": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "cb_hist_smem_bytes": (c_int, [c_int, c_int, c_int]),
     "cb_hist": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                         c_int, c_int, c_void_p]),

@@ -324,7 +324,16 @@ class GenericLearner:
         if self.dev.type == "cuda" and self.monotone is None:
             # device search: one warp per (leaf, feature) + one warp per leaf, 16 bytes per leaf read back
             self._search_calls = getattr(self, "_search_calls", 0) + 1
-            lid = None if node_ids is None else torch.tensor(list(node_ids), dtype=torch.int32, device=self.dev)
+            if node_ids is None:
+                lid = None
+            else:
+                ids = list(node_ids)
+                if len(ids) <= 4 or ids == list(range(ids[0], ids[0] + len(ids))):
+                    # consecutive node numbers (the two children of a split, a whole level): made on the device
+                    lid = torch.arange(ids[0], ids[0] + len(ids), dtype=torch.int32, device=self.dev) \
+                        if ids == list(range(ids[0], ids[0] + len(ids))) else torch.tensor(ids, dtype=torch.int32, device=self.dev)
+                else:
+                    lid = torch.tensor(ids, dtype=torch.int32, device=self.dev)
             score, feat, bins, gain = ops.leaf_search(
                 self.store, h, K, self.scorer.l2, self.o.score_function, noise_std,
                 (int(self.o.random_seed) * 1000003 + self._search_calls * 7919) & 0x7FFFFFFFFFFFFFFF, lid, fmask.float(),
@@ -397,10 +406,15 @@ class GenericLearner:
         node_depth = [0]
         cand = {}        # node -> (gain, feature, bin)
 
+        cuda = self.dev.type == "cuda"
+        # slot table over all nodes the tree can have, kept on the device and edited in place (no upload per split)
+        table_all = torch.full((2 * max_leaves + 1,), -1, dtype=torch.int16, device=self.dev)
+
         def evaluate(nodes):
-            table = torch.full((len(node_split),), -1, dtype=torch.int16, device=self.dev)
-            table[torch.tensor(nodes, device=self.dev)] = torch.arange(len(nodes), dtype=torch.int16, device=self.dev)
-            h = self._hist(stats, table, len(nodes))
+            table_all.fill_(-1)
+            for j, node in enumerate(nodes):
+                table_all[node] = j                       # scalar writes: kernel arguments, not host-to-device copies
+            h = self._hist(stats, table_all[: len(node_split)], len(nodes))
             best, bscore, bgain = self._per_leaf_best(h, K, noise_std, fmask, nodes)
             for j, node in enumerate(nodes):
                 if math.isfinite(float(bscore[j])) and node_depth[node] < max_depth:
@@ -415,9 +429,12 @@ class GenericLearner:
             node_split += [[-1, 0, 0, -1], [-1, 0, 0, -1]]
             node_depth += [node_depth[node] + 1] * 2
             node_split[node] = [f, b, 1 if bool(self._onehot_host[f]) else 0, left]
-            step = [[-1, 0, 0, -1]] * len(node_split)
-            step[node] = node_split[node]
-            ops.update_nodes(self.store, self.leaf, torch.tensor(step, dtype=torch.int32, device=self.dev))
+            if cuda:
+                ops.update_one_node(self.store, self.leaf, node, f, b, bool(self._onehot_host[f]), left)
+            else:
+                step = [[-1, 0, 0, -1]] * len(node_split)
+                step[node] = node_split[node]
+                ops.update_nodes(self.store, self.leaf, torch.tensor(step, dtype=torch.int32, device=self.dev))
             n_leaves += 1
             if n_leaves < max_leaves:
                 evaluate([left, left + 1])
