@@ -158,6 +158,24 @@ def query_der(kind: str, approx: torch.Tensor, target: torch.Tensor, weight, off
     return der, hess
 
 
+def pair_metric(approx: torch.Tensor, target, offsets, pairs=None, pair_weight=None):
+    """(PairLogit loss, PairAccuracy) of the approximations on the GPU: explicit (winner, loser) pairs, or every pair of a
+    query whose labels differ."""
+    dev = approx.device
+    out = torch.zeros(3, dtype=torch.float64, device=dev)
+    a = approx.contiguous().float()
+    if pairs is not None:
+        pr = pairs.contiguous().long()
+        pw = None if pair_weight is None else pair_weight.contiguous().float()
+        rc = native.cuda_lib().cb_pair_metric(_p(a), None, None, 0, _p(pr), _p(pw), int(pr.shape[0]), _p(out), _stream(dev))
+    else:
+        t, off = target.contiguous().float(), offsets.contiguous().long()
+        rc = native.cuda_lib().cb_pair_metric(_p(a), _p(t), _p(off), int(off.numel()) - 1, None, None, 0, _p(out), _stream(dev))
+    native.cuda_check(rc, "cb_pair_metric")
+    l, w, c = (float(v) for v in out.tolist())
+    return (l / w if w > 0 else 0.0), (c / w if w > 0 else 1.0)
+
+
 def pair_logit_der(approx: torch.Tensor, pairs: torch.Tensor, pair_weight):
     """(der, hess) [n] of PairLogit from explicit (winner, loser) pairs [P, 2] (int64) on the GPU."""
     dev = approx.device

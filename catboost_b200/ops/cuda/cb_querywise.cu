@@ -119,6 +119,60 @@ __global__ void __launch_bounds__(256) cb_pair_logit_labels_kernel(const float* 
     }
 }
 
+// ---- PairLogit / PairAccuracy metrics -------------------------------------------------------------------------------
+// out[0] += sum pw log(1 + exp(-(a_winner - a_loser))), out[1] += sum pw, out[2] += sum pw [a_winner > a_loser]
+__device__ __forceinline__ void cb_qw_metric_flush(double l, double w, double c, double* out) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        l += __shfl_xor_sync(0xffffffffu, l, o);
+        w += __shfl_xor_sync(0xffffffffu, w, o);
+        c += __shfl_xor_sync(0xffffffffu, c, o);
+    }
+    if ((threadIdx.x & 31) == 0 && w != 0.0) { atomicAdd(out, l); atomicAdd(out + 1, w); atomicAdd(out + 2, c); }
+}
+
+__device__ __forceinline__ float cb_qw_softplus_neg(float d) {          // log(1 + exp(-d)), stable for both signs
+    return d > 0.0f ? __logf(1.0f + __expf(-d)) : -d + __logf(1.0f + __expf(d));
+}
+
+__global__ void __launch_bounds__(256) cb_pair_metric_pairs_kernel(const float* approx, const long long* pairs, const float* pair_w,
+                                                                   long long P, double* out) {
+    double l = 0.0, w = 0.0, c = 0.0;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x; k < P; k += stride) {
+        const float d = approx[pairs[2 * k]] - approx[pairs[2 * k + 1]];
+        const float pw = pair_w ? pair_w[k] : 1.0f;
+        l += (double)(pw * cb_qw_softplus_neg(d));
+        w += (double)pw;
+        c += d > 0.0f ? (double)pw : 0.0;
+    }
+    cb_qw_metric_flush(l, w, c, out);
+}
+
+__global__ void __launch_bounds__(256) cb_pair_metric_labels_kernel(const float* approx, const float* target, const long long* offsets,
+                                                                    long long Q, double* out) {
+    const int lane = threadIdx.x & 31;
+    const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    double l = 0.0, w = 0.0, c = 0.0;
+    for (long long q = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; q < Q; q += warps) {
+        const long long b = offsets[q], e = offsets[q + 1];
+        for (long long i = b + lane; i < e; i += 32) {
+            const float ai = approx[i], ti = target[i];
+            float fl = 0.0f, fw = 0.0f, fc = 0.0f;
+            for (long long j = b; j < e; ++j) {
+                if (ti > target[j]) {                         // i beats j
+                    const float d = ai - approx[j];
+                    fl += cb_qw_softplus_neg(d);
+                    fw += 1.0f;
+                    fc += d > 0.0f ? 1.0f : 0.0f;
+                }
+            }
+            l += (double)fl; w += (double)fw; c += (double)fc;
+        }
+    }
+    cb_qw_metric_flush(l, w, c, out);
+}
+
 static unsigned int cb_qw_grid(long long items, int per_block) {
     long long g = (items + per_block - 1) / per_block;
     if (g < 1) g = 1;
@@ -155,6 +209,20 @@ CB_API int cb_pair_logit_labels_der(const float* approx, const float* target, co
                                     float* hess, cudaStream_t st) {
     if (Q <= 0) return 0;
     cb_pair_logit_labels_kernel<<<cb_qw_grid(Q, 8), 256, 0, st>>>(approx, target, offsets, Q, der, hess);
+    CB_LAUNCH_CHECK();
+    return 0;
+}
+
+// out: three doubles, zero on entry (loss sum, pair weight sum, weight of correctly ordered pairs).
+CB_API int cb_pair_metric(const float* approx, const float* target, const long long* offsets, long long Q, const long long* pairs,
+                          const float* pair_w, long long P, double* out, cudaStream_t st) {
+    if (pairs) {
+        if (P <= 0) return 0;
+        cb_pair_metric_pairs_kernel<<<cb_qw_grid(P, 256), 256, 0, st>>>(approx, pairs, pair_w, P, out);
+    } else {
+        if (Q <= 0) return 0;
+        cb_pair_metric_labels_kernel<<<cb_qw_grid(Q, 8), 256, 0, st>>>(approx, target, offsets, Q, out);
+    }
     CB_LAUNCH_CHECK();
     return 0;
 }

@@ -202,6 +202,7 @@ _SIGS = {
     "cb_query_softmax_der": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_float, c_void_p, c_void_p, c_void_p]),
     "cb_pair_logit_pairs_der": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p]),
     "cb_pair_logit_labels_der": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p]),
+    "cb_pair_metric": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_void_p, c_void_p]),
     "cb_mvs_block_docs": (c_int, []),
     "cb_mvs_sample": (c_int, [c_void_p, c_ll, c_ll, c_float, c_float, c_ull, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_mc_max_classes": (c_int, []),

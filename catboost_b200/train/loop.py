@@ -92,6 +92,7 @@ def _use_fast_engine(o, objective, store, dims) -> bool:
             and (o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson") or (o.bootstrap_type == "MVS" and dims == 1))
             and not o.langevin and not o.monotone_constraints and not o.model_shrink_rate
             and str(o.sampling_unit or "Object") == "Object"
+            and not getattr(objective, "pairwise_scoring", False)       # pairwise systems live in the general learner
             and str(o.random_score_type) != "Gumbel")
 
 
@@ -384,7 +385,12 @@ def _device_ndcg(metric, approx, y, w, pool):
     document inside its query, and a per-query sum of gain / discount; the ideal order is the same with the labels as
     the sort key.  Parameters: top, type (Base / Exp), denominator (LogPosition / Position)."""
     p = dict(getattr(metric, "params", None) or {})
-    if set(p) - {"top", "type", "denominator"} or pool is None or pool.group_id is None:
+    name = getattr(metric, "name", None)
+    if name in ("YetiRank", "YetiRankPairwise"):
+        name = "PFound"                       # the value these objectives are logged with
+        p = {k: v for k, v in p.items() if k in ("top", "decay")}
+    allowed = {"top", "decay"} if name == "PFound" else {"top", "type", "denominator"}
+    if set(p) - allowed or pool is None or pool.group_id is None:
         return None
     if not approx.is_cuda or approx.shape[0] != 1 or np.ndim(y) != 1:
         return None
@@ -422,8 +428,37 @@ def _device_ndcg(metric, approx, y, w, pool):
             term = torch.where(rank < top, term, torch.zeros_like(term))
         return torch.zeros(Q, dtype=torch.float64, device=dev).index_add_(0, gid[order], term)
 
+    if name == "PFound":
+        # sum over the positions of a query of plook_k * r_k with plook_0 = 1, plook_{k+1} = plook_k (1 - r_k) decay: the
+        # running product inside a query as an exclusive segmented sum of logarithms (magnitude), with the sign and a
+        # "hit zero" flag carried by two more segmented sums
+        decay = float(p.get("decay", 0.85))
+        bits = (0.0 - approx[0][:n].float()).contiguous().view(torch.int32).long()
+        ordered = torch.where(bits < 0, bits ^ 0x7FFFFFFF, bits) + (1 << 31)
+        _, order = ops.sort_pairs((gid << 32) | ordered)
+        g_sorted = gid[order]
+        rank = torch.arange(n, device=dev) - off[g_sorted]
+        rel = yt[order].double()
+        fac = (1.0 - rel) * decay
+        zero, neg = (fac == 0), (fac < 0)
+        lg = torch.where(zero, torch.zeros_like(fac), torch.log(fac.abs().clamp_min(1e-300)))
+
+        def excl_seg(v):
+            c = torch.cumsum(v, 0)
+            first = off[:-1].clamp(max=max(n - 1, 0))
+            base = torch.where(off[:-1] < n, c[first] - v[first], torch.zeros_like(c[first]))
+            return c - v - base[g_sorted]
+
+        plook = torch.exp(excl_seg(lg))
+        plook = torch.where(excl_seg(zero.double()) > 0, torch.zeros_like(plook), plook)
+        plook = torch.where((excl_seg(neg.double()).round().long() & 1) == 1, -plook, plook)
+        term = plook * rel
+        if top > 0:
+            term = torch.where(rank < top, term, torch.zeros_like(term))
+        got = torch.zeros(Q, dtype=torch.float64, device=dev).index_add_(0, g_sorted, term)
+        return float(((got * gw).sum() / gw.sum().clamp_min(1e-300)).item())
     got = dcg(approx[0][:n])
-    if getattr(metric, "name", None) == "NDCG":
+    if name == "NDCG":
         ideal = dcg(yt)
         got = torch.where(ideal > 0, got / ideal.clamp_min(1e-300), torch.ones_like(got))
     return float(((got * gw).sum() / gw.sum().clamp_min(1e-300)).item())
@@ -433,8 +468,25 @@ def _device_metric(metric, approx, y, w, pool=None):
     """The common additive metrics evaluated where the approximations live (a host round trip of a 1M x 5 cursor per
     iteration costs more than growing the tree).  Returns None for metrics without a device formula."""
     name = getattr(metric, "name", None)
-    if name in ("NDCG", "DCG"):
+    if name in ("NDCG", "DCG", "PFound", "YetiRank", "YetiRankPairwise"):
         return _device_ndcg(metric, approx, y, w, pool)
+    if name in ("PairLogit", "PairLogitPairwise", "PairAccuracy"):
+        # all pairs of a query whose labels differ, or the pool's explicit pairs (ops/cuda/cb_querywise.cu)
+        if not approx.is_cuda or approx.shape[0] != 1 or getattr(metric, "params", None) or pool is None or np.ndim(y) != 1:
+            return None
+        dev = approx.device
+        n = len(y)
+        if pool.pairs is not None:
+            pr = torch.from_numpy(np.ascontiguousarray(pool.pairs, dtype=np.int64)).to(dev)
+            pw = None if pool.pairs_weight is None else torch.from_numpy(np.ascontiguousarray(pool.pairs_weight, dtype=np.float32)).to(dev)
+            loss, acc = ops.pair_metric(approx[0][:n], None, None, pr, pw)
+        elif pool.group_id is not None:
+            off = torch.from_numpy(np.asarray(pool.group_offsets(), dtype=np.int64)).to(dev)
+            yt = torch.from_numpy(np.ascontiguousarray(y, dtype=np.float32)).to(dev)
+            loss, acc = ops.pair_metric(approx[0][:n], yt, off)
+        else:
+            return None
+        return acc if name == "PairAccuracy" else loss
     if name not in ("Logloss", "RMSE", "MAE", "MultiClass", "Accuracy", "AUC", "Precision", "Recall", "F1", "R2") \
             or getattr(metric, "params", None):
         return None

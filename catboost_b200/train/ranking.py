@@ -170,9 +170,23 @@ class PairLogit(_GroupObjective):
             wi, li, pw = ctx.pairs[:, 0], ctx.pairs[:, 1], ctx.pairs_weight.float()
         else:
             lay = _layout(ctx)
-            pm = _make_pairs_from_labels(lay, target)                 # [q, i, j]: i beats j
-            q, i, j = pm.nonzero(as_tuple=True)
-            wi, li = lay.index[q, i], lay.index[q, j]
+            cached = getattr(lay, "_label_pairs", None)
+            if cached is None:
+                # the pairs only depend on the labels: enumerated once per data set, query by query in blocks so that
+                # the [queries, L, L] mask never exists for all queries at once
+                ws, ls = [], []
+                step = max(1, (1 << 26) // max(1, lay.Lmax * lay.Lmax))
+                T = lay.gather(target, float("nan"))
+                for q0 in range(0, lay.Q, step):
+                    Tq, mq = T[q0:q0 + step], lay.mask[q0:q0 + step]
+                    pm = (Tq.unsqueeze(2) > Tq.unsqueeze(1)) & mq.unsqueeze(2) & mq.unsqueeze(1)      # [q, i, j]: i beats j
+                    q, i, j = pm.nonzero(as_tuple=True)
+                    ws.append(lay.index[q0 + q, i])
+                    ls.append(lay.index[q0 + q, j])
+                cached = (torch.cat(ws) if ws else torch.zeros(0, dtype=torch.long, device=a.device),
+                          torch.cat(ls) if ls else torch.zeros(0, dtype=torch.long, device=a.device))
+                lay._label_pairs = cached
+            wi, li = cached
             pw = torch.ones(wi.shape[0], device=a.device)
         p = torch.sigmoid(a[li] - a[wi])
         return wi, li, pw * p, pw * p * (1 - p)

@@ -705,6 +705,27 @@ def test_device_side_ndcg_matches_the_host_metric():
     approx = np.round(rng.standard_normal(n), 1).astype(np.float32)         # one decimal: plenty of ties
     pool = Pool(X, y, group_id=gid)
     a_dev = torch.from_numpy(approx).cuda().unsqueeze(0)
+    for desc in ("PairLogit", "PairAccuracy"):          # pairs from labels, then the pool's explicit pairs
+        metric = make_metric(desc)
+        got = _device_metric(metric, a_dev, y, None, pool)
+        want = metric.eval(approx.reshape(-1, 1).astype(np.float64), y, None, group_offsets=pool.group_offsets())
+        assert got is not None and abs(got - want) < 1e-5 * max(1.0, abs(want)), (desc, got, want)
+        offs = pool.group_offsets()
+        qs = rng.integers(0, len(sizes), 3000)
+        pairs = np.stack([offs[qs] + rng.integers(0, 1 << 30, 3000) % sizes[qs], offs[qs] + rng.integers(0, 1 << 30, 3000) % sizes[qs]], 1)
+        pairs = pairs[pairs[:, 0] != pairs[:, 1]]
+        pw = (rng.random(len(pairs)) + 0.5).astype(np.float32)
+        pool_p = Pool(X, y, group_id=gid, pairs=pairs, pairs_weight=pw)
+        got = _device_metric(metric, a_dev, y, None, pool_p)
+        want = metric.eval(approx.reshape(-1, 1).astype(np.float64), y, None, pairs=pairs, pairs_weight=pw)
+        assert got is not None and abs(got - want) < 1e-5 * max(1.0, abs(want)), (desc, got, want)
+    yp = (y / 4.0).astype(np.float32)                                       # PFound takes relevances in [0, 1]
+    for desc in ("PFound", "PFound:top=4;decay=0.7"):
+        metric = make_metric(desc)
+        poolp = Pool(X, yp, group_id=gid)
+        got = _device_metric(metric, a_dev, yp, None, poolp)
+        want = metric.eval(approx.reshape(-1, 1).astype(np.float64), yp, None, group_offsets=poolp.group_offsets())
+        assert got is not None and abs(got - want) < 1e-6 * max(1.0, abs(want)), (desc, got, want)
     for desc in ("NDCG", "NDCG:top=5", "NDCG:type=Exp", "NDCG:top=3;type=Exp;denominator=Position", "DCG:top=10"):
         metric = make_metric(desc)
         got = _device_metric(metric, a_dev, y, None, pool)
