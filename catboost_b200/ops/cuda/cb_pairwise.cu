@@ -33,36 +33,41 @@ struct CbPairHistArgs {
     float* H;                       // [ng * 4][B][L][L][4]
 };
 
-// One thread per (pair, feature group): the two bin words give four features at once; 8 atomics.
-__global__ void __launch_bounds__(256) cb_pair_hist_kernel(CbPairHistArgs a) {
-    const long long total = a.npairs * a.ng;
+// One thread per pair and range of feature groups (blockIdx.y = range): the thread reads its pair once (documents, leaves,
+// weight) and walks the groups of the range; all pairs of a range run before the next range, so the range's bin columns
+// (4 bytes per document and group) and its histograms stay in L2 while the pairs stream past.  (Pair-major over all
+// groups touched every column of the store at once: 2.0 s per tree at 2M documents x 700 features and 20M pairs;
+// group-major with one group per thread re-read the pair for every group.)  The two bin words of a group give four
+// features at once; 8 atomics.
+__global__ void __launch_bounds__(256) cb_pair_hist_kernel(CbPairHistArgs a, int gpr) {
+    const int gl_lo = blockIdx.y * gpr, gl_hi = min(a.ng, gl_lo + gpr);
     const long long stride = (long long)gridDim.x * blockDim.x;
     const size_t fstride = (size_t)a.B * a.L * a.L * 4;
-    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
-        const long long p = idx / a.ng;
-        const int gl = (int)(idx - p * a.ng);
-        const int g = a.g0 + gl;
-        const int i = a.wi[p], j = a.li[p];
+    const size_t bs = (size_t)a.L * a.L * 4;
+    for (long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x; p < a.npairs; p += stride) {
         const float w = a.w[p];
         if (w == 0.0f) continue;
-        const uint32_t wi_ = a.d.bins[(long long)g * a.d.npad + i], wj_ = a.d.bins[(long long)g * a.d.npad + j];
+        const int i = a.wi[p], j = a.li[p];
         const int la = a.leaf[i], lb = a.leaf[j];
         const size_t cell = ((size_t)la * a.L + lb) * 4;
+        for (int gl = gl_lo; gl < gl_hi; ++gl) {
+            const int g = a.g0 + gl;
+            const uint32_t wi_ = a.d.bins[(long long)g * a.d.npad + i], wj_ = a.d.bins[(long long)g * a.d.npad + j];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int f = g * 4 + q;
-            if (f >= a.d.F) break;
-            const int bi = (int)((wi_ >> (8 * q)) & 255u), bj = (int)((wj_ >> (8 * q)) & 255u);
-            float* Hf = a.H + (size_t)(gl * 4 + q) * fstride;
-            const size_t bs = (size_t)a.L * a.L * 4;
-            if (a.d.feat_onehot && a.d.feat_onehot[f]) {
-                if (bi == bj) atomicAdd(Hf + bi * bs + cell, w);
-                else { atomicAdd(Hf + bi * bs + cell + 1, w); atomicAdd(Hf + bj * bs + cell + 2, w); }
-            } else {
-                const bool wsmall = bi < bj;
-                const int lo = wsmall ? bi : bj, hi = wsmall ? bj : bi;
-                atomicAdd(Hf + lo * bs + cell + (wsmall ? 0 : 2), w);
-                atomicAdd(Hf + hi * bs + cell + (wsmall ? 1 : 3), w);
+            for (int q = 0; q < 4; ++q) {
+                const int f = g * 4 + q;
+                if (f >= a.d.F) break;
+                const int bi = (int)((wi_ >> (8 * q)) & 255u), bj = (int)((wj_ >> (8 * q)) & 255u);
+                float* Hf = a.H + (size_t)(gl * 4 + q) * fstride;
+                if (a.d.feat_onehot && a.d.feat_onehot[f]) {
+                    if (bi == bj) atomicAdd(Hf + bi * bs + cell, w);
+                    else { atomicAdd(Hf + bi * bs + cell + 1, w); atomicAdd(Hf + bj * bs + cell + 2, w); }
+                } else {
+                    const bool wsmall = bi < bj;
+                    const int lo = wsmall ? bi : bj, hi = wsmall ? bj : bi;
+                    atomicAdd(Hf + lo * bs + cell + (wsmall ? 0 : 2), w);
+                    atomicAdd(Hf + hi * bs + cell + (wsmall ? 1 : 3), w);
+                }
             }
         }
     }
@@ -74,8 +79,8 @@ __global__ void __launch_bounds__(256) cb_pair_der_hist_kernel(CbData d, const u
     const long long total = d.n * ng;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
-        const long long i = idx / ng;
-        const int gl = (int)(idx - i * ng);
+        const int gl = (int)(idx / d.n);
+        const long long i = idx - (long long)gl * d.n;
         const int g = g0 + gl;
         const float v = der[i];
         const uint32_t wd = d.bins[(long long)g * d.npad + i];
@@ -260,7 +265,16 @@ CB_API int cb_pair_hist(const CbData* d, const unsigned short* leaf, const int* 
                         long long npairs, const float* der, int L, int B, int g0, int ng, float* H, float* D, int grid,
                         cudaStream_t st) {
     CbPairHistArgs a{*d, leaf, wi, li, w, npairs, L, B, g0, ng, H};
-    if (npairs > 0) cb_pair_hist_kernel<<<grid, 256, 0, st>>>(a);
+    if (npairs > 0 && ng > 0) {
+        // groups per range: the range's bin columns and histograms together within about half of the 126 MB L2
+        const double per_group = (double)d->npad * 4.0 + 4.0 * (double)B * L * L * 16.0;
+        int gpr = (int)(60.0e6 / per_group);
+        if (gpr < 1) gpr = 1;
+        if (gpr > 16) gpr = 16;
+        if (gpr > ng) gpr = ng;
+        const int ranges = (ng + gpr - 1) / gpr;
+        cb_pair_hist_kernel<<<dim3((unsigned)grid, (unsigned)ranges), 256, 0, st>>>(a, gpr);
+    }
     cb_pair_der_hist_kernel<<<grid, 256, 0, st>>>(*d, leaf, der, L, B, g0, ng, D);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
