@@ -20,6 +20,7 @@
 //   [0] += w at v = bin_i = bin_j (both right)   [1] += w at v = bin_i != bin_j (winner right)
 //   [2] += w at v = bin_j != bin_i (loser right)  both left = total - [0] - [1] - [2]
 #include "cb_common.cuh"
+#include <cstdlib>
 #include "cb_tree.cuh"
 
 struct CbPairHistArgs {
@@ -70,6 +71,66 @@ __global__ void __launch_bounds__(256) cb_pair_hist_kernel(CbPairHistArgs a, int
                 }
             }
         }
+    }
+}
+
+// Shallow levels (the histogram of a group -- NFEAT = 4 features, or of one feature -- fits in shared memory): a block
+// takes a chunk of CB_PAIR_CHUNK pairs of one group, accumulates in shared int32 cells in fixed point (scale = 2^31 /
+// (chunk x largest pair weight), 17 bits of the largest weight: the cell cannot overflow) and adds its non-zero cells to
+// the global histogram at the end.  Native integer reductions in shared memory replace two global float atomics per
+// (pair, feature); the flush costs one global atomic per non-zero cell and chunk.  blockIdx.x (fastest) walks the
+// chunks of one group, so the group's bin column stays in L2.
+#define CB_PAIR_CHUNK 16384
+
+template <int NFEAT>
+__global__ void __launch_bounds__(256) cb_pair_hist_smem_kernel(CbPairHistArgs a, float qs) {
+    extern __shared__ int cb_ph[];                  // [NFEAT][B][L][L][4]
+    const size_t bs = (size_t)a.L * a.L * 4;
+    const int per_feat = a.B * (int)bs;
+    const int cells = NFEAT * per_feat;
+    for (int c = threadIdx.x; c < cells; c += blockDim.x) cb_ph[c] = 0;
+    __syncthreads();
+    const int gl = NFEAT == 4 ? (int)blockIdx.y : (int)(blockIdx.y >> 2);
+    const int q_lo = NFEAT == 4 ? 0 : (int)(blockIdx.y & 3), q_hi = NFEAT == 4 ? 4 : q_lo + 1;
+    const int g = a.g0 + gl;
+    bool onehot[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) onehot[q] = (g * 4 + q < a.d.F) && a.d.feat_onehot && a.d.feat_onehot[g * 4 + q];
+    const long long begin = (long long)blockIdx.x * CB_PAIR_CHUNK;
+    const long long end = min(a.npairs, begin + CB_PAIR_CHUNK);
+    const uint32_t* col = a.d.bins + (long long)g * a.d.npad;
+    for (long long p = begin + threadIdx.x; p < end; p += blockDim.x) {
+        const float w = a.w[p];
+        if (w == 0.0f) continue;
+        const int i = a.wi[p], j = a.li[p];
+        const int cell = (a.leaf[i] * a.L + a.leaf[j]) * 4;
+        const uint32_t wi_ = col[i], wj_ = col[j];
+        const int qw = __float2int_rn(w * qs);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (q < q_lo || q >= q_hi || g * 4 + q >= a.d.F) continue;
+            const int bi = (int)((wi_ >> (8 * q)) & 255u), bj = (int)((wj_ >> (8 * q)) & 255u);
+            int* Hf = cb_ph + (NFEAT == 4 ? q * per_feat : 0);
+            if (onehot[q]) {
+                if (bi == bj) atomicAdd(Hf + bi * (int)bs + cell, qw);
+                else { atomicAdd(Hf + bi * (int)bs + cell + 1, qw); atomicAdd(Hf + bj * (int)bs + cell + 2, qw); }
+            } else {
+                const bool wsmall = bi < bj;
+                const int lo = wsmall ? bi : bj, hi = wsmall ? bj : bi;
+                atomicAdd(Hf + lo * (int)bs + cell + (wsmall ? 0 : 2), qw);
+                atomicAdd(Hf + hi * (int)bs + cell + (wsmall ? 1 : 3), qw);
+            }
+        }
+    }
+    __syncthreads();
+    const float inv = 1.0f / qs;
+    const size_t fstride = (size_t)a.B * bs;
+    for (int c = threadIdx.x; c < cells; c += blockDim.x) {
+        const int v = cb_ph[c];
+        if (v == 0) continue;
+        const int q = NFEAT == 4 ? c / per_feat : q_lo;
+        const int rem = NFEAT == 4 ? c - q * per_feat : c;
+        atomicAdd(a.H + (size_t)(gl * 4 + q) * fstride + rem, (float)v * inv);
     }
 }
 
@@ -262,10 +323,27 @@ CB_API long long cb_pair_hist_floats(int nfeat, int L, int B) { return (long lon
 
 // Pair histograms + derivative histograms of feature groups [g0, g0 + ng) (H and D zeroed by the caller), scanned.
 CB_API int cb_pair_hist(const CbData* d, const unsigned short* leaf, const int* wi, const int* li, const float* w,
-                        long long npairs, const float* der, int L, int B, int g0, int ng, float* H, float* D, int grid,
-                        cudaStream_t st) {
+                        long long npairs, const float* der, int L, int B, int g0, int ng, float* H, float* D, float wmax,
+                        int grid, cudaStream_t st) {
     CbPairHistArgs a{*d, leaf, wi, li, w, npairs, L, B, g0, ng, H};
-    if (npairs > 0 && ng > 0) {
+    // wmax: the largest pair weight (> 0 selects the shared-memory kernel where the level's histogram fits)
+    const size_t per_feat_bytes = (size_t)B * L * L * 4 * 4;
+    bool smem_ok = wmax > 0.0f && npairs > 0 && ng > 0 && per_feat_bytes <= 96 * 1024;
+    if (const char* e = getenv("CB200_PAIR_SMEM")) smem_ok = smem_ok && atoi(e) != 0;
+    if (smem_ok) {
+        static unsigned long long set = 0ull;
+        if (cb_first_on_device(&set)) {
+            cudaError_t e = cudaFuncSetAttribute(cb_pair_hist_smem_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_pair_hist_smem_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
+        }
+        const float qs = 2147483647.0f / ((float)CB_PAIR_CHUNK * wmax) * 0.999f;
+        const unsigned chunks = (unsigned)((npairs + CB_PAIR_CHUNK - 1) / CB_PAIR_CHUNK);
+        if (4 * per_feat_bytes <= 96 * 1024)
+            cb_pair_hist_smem_kernel<4><<<dim3(chunks, (unsigned)ng), 256, 4 * per_feat_bytes, st>>>(a, qs);
+        else
+            cb_pair_hist_smem_kernel<1><<<dim3(chunks, (unsigned)ng * 4), 256, per_feat_bytes, st>>>(a, qs);
+    } else if (npairs > 0 && ng > 0) {
         // groups per range: the range's bin columns and histograms together within about half of the 126 MB L2
         const double per_group = (double)d->npad * 4.0 + 4.0 * (double)B * L * L * 16.0;
         int gpr = (int)(60.0e6 / per_group);

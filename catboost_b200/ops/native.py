@@ -188,7 +188,7 @@ _SIGS = {
                                c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_pair_hist_floats": (c_ll, [c_int, c_int, c_int]),
     "cb_pair_hist": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int,
-                             c_void_p, c_void_p, c_int, c_void_p]),
+                             c_void_p, c_void_p, c_float, c_int, c_void_p]),
     "cb_pair_scan": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "cb_pair_solve_smem_bytes": (c_int, [c_int]),
     "cb_pair_solve": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p]),

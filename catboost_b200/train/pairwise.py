@@ -224,6 +224,8 @@ class PairwiseKernelLearner(PairwiseLearner):
         grid = 148 * 8
         wi32, li32 = wi.to(torch.int32).contiguous(), li.to(torch.int32).contiguous()
         h32 = h.to(torch.float32).contiguous()
+        # the largest pair weight scales the fixed-point cells of the shared-memory histogram kernel (shallow levels)
+        wmax = float(h32.abs().max().item()) if h32.numel() else 0.0
         if lib.cb_pair_solve_smem_bytes(L) > 227 * 1024:
             raise RuntimeError("too many leaves for the pairwise solve kernel")
         for g0 in range(0, G, ng_max):
@@ -231,7 +233,7 @@ class PairwiseKernelLearner(PairwiseLearner):
             H = torch.zeros(ng * 4 * B * L * L * 4, dtype=torch.float32, device=self.dev)
             D = torch.zeros(ng * 4 * B * L, dtype=torch.float32, device=self.dev)
             native.cuda_check(lib.cb_pair_hist(ctypes.c_void_p(st.handle), p(self.leaf), p(wi32), p(li32), p(h32),
-                                               int(wi32.numel()), p(der_pad), L, B, g0, ng, p(H), p(D), grid, stream),
+                                               int(wi32.numel()), p(der_pad), L, B, g0, ng, p(H), p(D), wmax, grid, stream),
                               "cb_pair_hist")
             self._reduce(H)
             self._reduce(D)
