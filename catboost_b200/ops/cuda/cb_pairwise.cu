@@ -134,6 +134,69 @@ __global__ void __launch_bounds__(256) cb_pair_hist_smem_kernel(CbPairHistArgs a
     }
 }
 
+// Deep levels (L x L leaf pairs no longer fit in shared memory): the caller sorts the pairs by leaf pair and cuts every
+// leaf pair's run into chunks of at most CB_PAIR_CHUNK pairs; a block takes one chunk of one group, so all its pairs share
+// the (leaf of winner, leaf of loser) cell and the shared histogram is just [4 features][B bins][4] int32 cells.  No leaf
+// look-ups in the kernel, native shared-memory integer reductions, one global atomic per non-zero cell at the end.
+// chunks[c] = (first pair, one past the last pair, leaf pair number la * L + lb, unused).
+__global__ void __launch_bounds__(256) cb_pair_hist_sorted_kernel(CbPairHistArgs a, const int4* chunks, float qs) {
+    __shared__ int hist[4 * 256 * 4];
+    const int cells = 4 * a.B * 4;
+    for (int c = threadIdx.x; c < cells; c += blockDim.x) hist[c] = 0;
+    __syncthreads();
+    const int4 ch = chunks[blockIdx.x];
+    const int gl = blockIdx.y, g = a.g0 + gl;
+    bool onehot[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) onehot[q] = (g * 4 + q < a.d.F) && a.d.feat_onehot && a.d.feat_onehot[g * 4 + q];
+    const uint32_t* col = a.d.bins + (long long)g * a.d.npad;
+    for (int p = ch.x + (int)threadIdx.x; p < ch.y; p += blockDim.x) {
+        const float w = a.w[p];
+        if (w == 0.0f) continue;
+        const uint32_t wi_ = col[a.wi[p]], wj_ = col[a.li[p]];
+        const int qw = __float2int_rn(w * qs);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (g * 4 + q >= a.d.F) continue;
+            const int bi = (int)((wi_ >> (8 * q)) & 255u), bj = (int)((wj_ >> (8 * q)) & 255u);
+            int* Hf = hist + q * a.B * 4;
+            if (onehot[q]) {
+                if (bi == bj) atomicAdd(Hf + bi * 4, qw);
+                else { atomicAdd(Hf + bi * 4 + 1, qw); atomicAdd(Hf + bj * 4 + 2, qw); }
+            } else {
+                const bool wsmall = bi < bj;
+                const int lo = wsmall ? bi : bj, hi = wsmall ? bj : bi;
+                atomicAdd(Hf + lo * 4 + (wsmall ? 0 : 2), qw);
+                atomicAdd(Hf + hi * 4 + (wsmall ? 1 : 3), qw);
+            }
+        }
+    }
+    __syncthreads();
+    const float inv = 1.0f / qs;
+    const size_t bs = (size_t)a.L * a.L * 4, fstride = (size_t)a.B * bs;
+    const size_t cell = (size_t)ch.z * 4;
+    for (int c = threadIdx.x; c < cells; c += blockDim.x) {
+        const int v = hist[c];
+        if (v == 0) continue;
+        const int q = c / (a.B * 4), rem = c - q * a.B * 4;
+        atomicAdd(a.H + (size_t)(gl * 4 + q) * fstride + (size_t)(rem >> 2) * bs + cell + (rem & 3), (float)v * inv);
+    }
+}
+
+// Pair histograms from pairs sorted by leaf pair (see the kernel above).  H zeroed by the caller; B <= 256.
+CB_API int cb_pair_hist_sorted(const CbData* d, const int* wi, const int* li, const float* w, long long npairs,
+                               const int* chunks, int nchunks, int L, int B, int g0, int ng, float* H, float wmax,
+                               cudaStream_t st) {
+    if (npairs <= 0 || nchunks <= 0 || ng <= 0) return 0;
+    if (B > 256 || wmax <= 0.0f) return (int)cudaErrorInvalidValue;
+    CbPairHistArgs a{*d, nullptr, wi, li, w, npairs, L, B, g0, ng, H};
+    const float qs = 2147483647.0f / ((float)CB_PAIR_CHUNK * wmax) * 0.999f;
+    cb_pair_hist_sorted_kernel<<<dim3((unsigned)nchunks, (unsigned)ng), 256, 0, st>>>(a, reinterpret_cast<const int4*>(chunks), qs);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+CB_API int cb_pair_chunk_pairs(void) { return CB_PAIR_CHUNK; }
+
 // Per-document derivative sums D[f][bin][leaf] for the same features (one thread per (document, group)).
 __global__ void __launch_bounds__(256) cb_pair_der_hist_kernel(CbData d, const unsigned short* leaf, const float* der, int L,
                                                                int B, int g0, int ng, float* D) {
@@ -328,21 +391,19 @@ CB_API int cb_pair_hist(const CbData* d, const unsigned short* leaf, const int* 
     CbPairHistArgs a{*d, leaf, wi, li, w, npairs, L, B, g0, ng, H};
     // wmax: the largest pair weight (> 0 selects the shared-memory kernel where the level's histogram fits)
     const size_t per_feat_bytes = (size_t)B * L * L * 4 * 4;
-    bool smem_ok = wmax > 0.0f && npairs > 0 && ng > 0 && per_feat_bytes <= 96 * 1024;
+    // (one feature per block also fits up to 8 leaves, but then every block flushes 16K cells for a quarter of the work:
+    // 108 ms per level at 2M x 700 against 22 ms for the sorted-pair kernel, which the caller uses from there on)
+    bool smem_ok = wmax > 0.0f && npairs > 0 && ng > 0 && 4 * per_feat_bytes <= 96 * 1024;
     if (const char* e = getenv("CB200_PAIR_SMEM")) smem_ok = smem_ok && atoi(e) != 0;
     if (smem_ok) {
         static unsigned long long set = 0ull;
         if (cb_first_on_device(&set)) {
             cudaError_t e = cudaFuncSetAttribute(cb_pair_hist_smem_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-            if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_pair_hist_smem_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
             if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
         }
         const float qs = 2147483647.0f / ((float)CB_PAIR_CHUNK * wmax) * 0.999f;
         const unsigned chunks = (unsigned)((npairs + CB_PAIR_CHUNK - 1) / CB_PAIR_CHUNK);
-        if (4 * per_feat_bytes <= 96 * 1024)
-            cb_pair_hist_smem_kernel<4><<<dim3(chunks, (unsigned)ng), 256, 4 * per_feat_bytes, st>>>(a, qs);
-        else
-            cb_pair_hist_smem_kernel<1><<<dim3(chunks, (unsigned)ng * 4), 256, per_feat_bytes, st>>>(a, qs);
+        cb_pair_hist_smem_kernel<4><<<dim3(chunks, (unsigned)ng), 256, 4 * per_feat_bytes, st>>>(a, qs);
     } else if (npairs > 0 && ng > 0) {
         // groups per range: the range's bin columns and histograms together within about half of the 126 MB L2
         const double per_group = (double)d->npad * 4.0 + 4.0 * (double)B * L * L * 16.0;

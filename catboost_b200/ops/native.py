@@ -187,6 +187,9 @@ _SIGS = {
     "cb_leaf_search": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_ull, c_void_p, c_void_p,
                                c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_pair_hist_floats": (c_ll, [c_int, c_int, c_int]),
+    "cb_pair_hist_sorted": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                    c_void_p, c_float, c_void_p]),
+    "cb_pair_chunk_pairs": (c_int, []),
     "cb_pair_hist": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_int,
                              c_void_p, c_void_p, c_float, c_int, c_void_p]),
     "cb_pair_scan": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),

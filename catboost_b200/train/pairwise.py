@@ -192,6 +192,7 @@ class PairwiseKernelLearner(PairwiseLearner):
     one more system over the final leaves, assembled from a pair histogram without a feature dimension."""
 
     H_BUDGET_BYTES = 1 << 30
+    USE_SORTED_PAIRS = True        # False: deep levels through global atomics (the oracle of the sorted-pair kernel)
 
     def __init__(self, store, opts, seed: int = 0, ctx=None):
         self.store, self.o = store, opts
@@ -228,13 +229,35 @@ class PairwiseKernelLearner(PairwiseLearner):
         wmax = float(h32.abs().max().item()) if h32.numel() else 0.0
         if lib.cb_pair_solve_smem_bytes(L) > 227 * 1024:
             raise RuntimeError("too many leaves for the pairwise solve kernel")
+        # Deep levels (the L x L cells of a feature group no longer fit in shared memory): the pairs are sorted by leaf pair once
+        # per level (the hand-written radix sort) and cut into chunks that share one cell, see cb_pair_hist_sorted_kernel
+        sorted_pairs = None
+        if wmax > 0.0 and 4 * B * L * L * 16 > 96 * 1024 and B <= 256 and wi32.numel() > 0 and self.USE_SORTED_PAIRS:
+            from ..ops import api as ops
+            key = self.leaf[wi].long() * L + self.leaf[li].long()
+            _, order = ops.sort_pairs(key)
+            counts = torch.bincount(key, minlength=L * L).cpu().numpy()
+            chunk = int(lib.cb_pair_chunk_pairs())
+            rows, begin = [], 0
+            for cell, c in enumerate(counts.tolist()):
+                for b in range(0, c, chunk):
+                    rows.append((begin + b, begin + min(c, b + chunk), cell, 0))
+                begin += c
+            table = torch.tensor(rows, dtype=torch.int32, device=self.dev).contiguous()
+            sorted_pairs = (wi32[order].contiguous(), li32[order].contiguous(), h32[order].contiguous(), table)
         for g0 in range(0, G, ng_max):
             ng = min(ng_max, G - g0)
             H = torch.zeros(ng * 4 * B * L * L * 4, dtype=torch.float32, device=self.dev)
             D = torch.zeros(ng * 4 * B * L, dtype=torch.float32, device=self.dev)
+            if sorted_pairs is not None:
+                ws, ls, hs, table = sorted_pairs
+                native.cuda_check(lib.cb_pair_hist_sorted(ctypes.c_void_p(st.handle), p(ws), p(ls), p(hs), int(ws.numel()),
+                                                          p(table), int(table.shape[0]), L, B, g0, ng, p(H), wmax, stream),
+                                  "cb_pair_hist_sorted")
+            # (with sorted pairs only the derivative histograms are left for this call)
             native.cuda_check(lib.cb_pair_hist(ctypes.c_void_p(st.handle), p(self.leaf), p(wi32), p(li32), p(h32),
-                                               int(wi32.numel()), p(der_pad), L, B, g0, ng, p(H), p(D), wmax, grid, stream),
-                              "cb_pair_hist")
+                                               0 if sorted_pairs is not None else int(wi32.numel()), p(der_pad), L, B, g0, ng,
+                                               p(H), p(D), wmax, grid, stream), "cb_pair_hist")
             self._reduce(H)
             self._reduce(D)
             native.cuda_check(lib.cb_pair_scan(ctypes.c_void_p(st.handle), g0 * 4, ng * 4, L, B, p(H), p(D), grid, stream),

@@ -283,8 +283,16 @@ class YetiRank(_GroupObjective):
             return empty, empty, torch.zeros(0, device=dev), torch.zeros(0, device=dev)
         decay_pow = self.decay ** torch.arange(L - 1, device=dev, dtype=torch.float32)
         out = []
+        if dev.type == "cuda" and getattr(self, "_gen_dev", None) is None:
+            # the uniforms are drawn where they are used: 4M numbers per permutation from the host generator plus their
+            # upload cost more than the sorting they feed
+            self._gen_dev = torch.Generator(device=dev)
+            self._gen_dev.manual_seed(20240229)
         for _ in range(self.permutations):
-            u = torch.rand((Q, L), generator=self._gen).to(dev).clamp(1e-6, 1 - 1e-6)
+            if dev.type == "cuda":
+                u = torch.rand((Q, L), generator=self._gen_dev, device=dev).clamp(1e-6, 1 - 1e-6)
+            else:
+                u = torch.rand((Q, L), generator=self._gen).clamp(1e-6, 1 - 1e-6)
             noisy = A + torch.log(u / (1.000001 - u))
             noisy = torch.where(lay.mask, noisy, torch.full_like(noisy, -1e30))
             order = torch.argsort(noisy, dim=1, descending=True, stable=True)

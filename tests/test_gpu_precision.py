@@ -363,7 +363,7 @@ def test_pairwise_kernels_match_the_tensor_oracle():
     kern = PairwiseKernelLearner(store, o)
     der_pad = torch.zeros(store.npad, device="cuda")
     der_pad[:n] = der
-    for L in (1, 2, 8):
+    for L in (1, 2, 8, 32):          # 32 leaves: pairs sorted by leaf pair, one cell per chunk (cb_pair_hist_sorted_kernel)
         leaf = torch.from_numpy(rng.integers(0, L, n)).cuda()
         kern.leaf.zero_()
         kern.leaf[:n] = leaf.to(torch.int16)
