@@ -46,58 +46,81 @@ struct CbMcGradArgs {
     float* statmax;                // [K + 1] max |statistic| of this iteration (atomicMax on the bit patterns)
 };
 
-// One document per thread and step; every row of approx / stats is read and written with coalesced 4-byte accesses.
-__global__ void __launch_bounds__(256) cb_mc_grad_kernel(CbMcGradArgs a) {
+// CB_MC_V documents per thread and step (loads of all of them issued before the arithmetic, so twice the bytes are in
+// flight per warp); every row of approx / stats is read and written with coalesced 4-byte accesses.  KM bounds the
+// class count at compile time: the per-class arrays live in registers, and a kernel sized for 16 classes held 87 of
+// them (two blocks per SM) when most models have a handful of classes.
+#define CB_MC_V 2
+template <int KM>
+__global__ void __launch_bounds__(256, KM <= 8 ? 3 : 2) cb_mc_grad_kernel(CbMcGradArgs a) {
     const int K = a.K;
     const int it = *a.iter_ptr;
     double s_loss = 0.0, s_w = 0.0, s_d2 = 0.0, s_n = 0.0;
-    float mx[CB_MC_MAX_K + 1];
+    float mx[KM + 1];
 #pragma unroll
-    for (int k = 0; k <= CB_MC_MAX_K; ++k) mx[k] = 0.0f;
+    for (int k = 0; k <= KM; ++k) mx[k] = 0.0f;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.npad; i += stride) {
-        const bool live = i < a.n;
-        const int lf = a.leaf[i];
-        a.leaf[i] = 0;
-        float ap[CB_MC_MAX_K];
-        float m = -3.0e38f;
+    for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < a.npad; i0 += stride * CB_MC_V) {
+        float ap[CB_MC_V][KM];
+        int lf[CB_MC_V], y[CB_MC_V];
+        float w[CB_MC_V];
+        bool in[CB_MC_V], live[CB_MC_V];
 #pragma unroll
-        for (int k = 0; k < CB_MC_MAX_K; ++k) {
-            if (k < K) {
-                float v = a.approx[(long long)k * a.npad + i];
-                if (a.cur_vals) { v += a.cur_vals[lf * K + k]; a.approx[(long long)k * a.npad + i] = v; }
-                ap[k] = v;
-                m = fmaxf(m, v);
+        for (int v = 0; v < CB_MC_V; ++v) {
+            const long long i = i0 + v * stride;
+            in[v] = i < a.npad;
+            live[v] = i < a.n;
+            lf[v] = in[v] ? (int)a.leaf[i] : 0;
+            y[v] = live[v] ? (int)a.target[i] : 0;
+            w[v] = (a.weight && in[v]) ? a.weight[i] : 1.0f;
+#pragma unroll
+            for (int k = 0; k < KM; ++k)
+                if (k < K) ap[v][k] = in[v] ? a.approx[(long long)k * a.npad + i] : 0.0f;
+        }
+#pragma unroll
+        for (int v = 0; v < CB_MC_V; ++v) {
+            if (!in[v]) continue;
+            const long long i = i0 + v * stride;
+            a.leaf[i] = 0;
+            float m = -3.0e38f;
+#pragma unroll
+            for (int k = 0; k < KM; ++k) {
+                if (k < K) {
+                    float x = ap[v][k];
+                    if (a.cur_vals) { x += a.cur_vals[lf[v] * K + k]; a.approx[(long long)k * a.npad + i] = x; }
+                    ap[v][k] = x;
+                    m = fmaxf(m, x);
+                }
+            }
+            float Z = 0.0f;
+#pragma unroll
+            for (int k = 0; k < KM; ++k)
+                if (k < K) { ap[v][k] = __expf(ap[v][k] - m); Z += ap[v][k]; }
+            const float invZ = 1.0f / Z;
+            const float wb = (a.boot_type && live[v])
+                ? cb_mc_boot(a.boot_type, a.boot_p, cb_mix64(a.seed ^ cb_mix64(((unsigned long long)it << 40) ^ (unsigned long long)i)))
+                : 1.0f;
+            float hs = 0.0f, d2 = 0.0f, py = 1.0f;
+#pragma unroll
+            for (int k = 0; k < KM; ++k) {
+                if (k < K) {
+                    const float p = ap[v][k] * invZ;
+                    if (k == y[v]) py = p;
+                    const float d = w[v] * ((k == y[v] ? 1.0f : 0.0f) - p);
+                    const float st = live[v] ? wb * d : 0.0f;
+                    a.stats[(long long)k * a.npad + i] = st;
+                    mx[k] = fmaxf(mx[k], fabsf(st));
+                    hs += p * (1.0f - p);
+                    d2 += d * d;
+                }
+            }
+            const float wc = live[v] ? wb * w[v] * (a.newton_stats ? hs / (float)K : 1.0f) : 0.0f;
+            a.stats[(long long)K * a.npad + i] = wc;
+            mx[KM] = fmaxf(mx[KM], fabsf(wc));
+            if (live[v]) {
+                s_loss += (double)(-w[v] * __logf(fmaxf(py, 1e-38f))); s_w += (double)w[v]; s_d2 += (double)d2; s_n += 1.0;
             }
         }
-        float Z = 0.0f;
-#pragma unroll
-        for (int k = 0; k < CB_MC_MAX_K; ++k)
-            if (k < K) { ap[k] = __expf(ap[k] - m); Z += ap[k]; }
-        const float invZ = 1.0f / Z;
-        const int y = live ? (int)a.target[i] : 0;
-        const float w = a.weight ? a.weight[i] : 1.0f;
-        const float wb = (a.boot_type && live)
-            ? cb_mc_boot(a.boot_type, a.boot_p, cb_mix64(a.seed ^ cb_mix64(((unsigned long long)it << 40) ^ (unsigned long long)i)))
-            : 1.0f;
-        float hs = 0.0f, d2 = 0.0f, py = 1.0f;
-#pragma unroll
-        for (int k = 0; k < CB_MC_MAX_K; ++k) {
-            if (k < K) {
-                const float p = ap[k] * invZ;
-                if (k == y) py = p;
-                const float d = w * ((k == y ? 1.0f : 0.0f) - p);
-                const float st = live ? wb * d : 0.0f;
-                a.stats[(long long)k * a.npad + i] = st;
-                mx[k] = fmaxf(mx[k], fabsf(st));
-                hs += p * (1.0f - p);
-                d2 += d * d;
-            }
-        }
-        const float wc = live ? wb * w * (a.newton_stats ? hs / (float)K : 1.0f) : 0.0f;
-        a.stats[(long long)K * a.npad + i] = wc;
-        mx[CB_MC_MAX_K] = fmaxf(mx[CB_MC_MAX_K], fabsf(wc));
-        if (live) { s_loss += (double)(-w * __logf(fmaxf(py, 1e-38f))); s_w += (double)w; s_d2 += (double)d2; s_n += 1.0; }
     }
     __shared__ double red[4][8];
     s_loss = cb_warp_sum_d(s_loss); s_w = cb_warp_sum_d(s_w); s_d2 = cb_warp_sum_d(s_d2); s_n = cb_warp_sum_d(s_n);
@@ -111,12 +134,12 @@ __global__ void __launch_bounds__(256) cb_mc_grad_kernel(CbMcGradArgs a) {
     }
     if (a.statmax) {
 #pragma unroll
-        for (int k = 0; k <= CB_MC_MAX_K; ++k) {
-            if (k < K || k == CB_MC_MAX_K) {
+        for (int k = 0; k <= KM; ++k) {
+            if (k < K || k == KM) {
                 float v = mx[k];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-                if (lane == 0) atomicMax(reinterpret_cast<int*>(a.statmax) + (k == CB_MC_MAX_K ? K : k), __float_as_int(v));
+                if (lane == 0) atomicMax(reinterpret_cast<int*>(a.statmax) + (k == KM ? K : k), __float_as_int(v));
             }
         }
     }
@@ -130,7 +153,17 @@ CB_API int cb_mc_grad(float* approx, const float* target, const float* weight, u
     if (K < 2 || K > CB_MC_MAX_K) return (int)cudaErrorInvalidValue;
     CbMcGradArgs a{approx, target, weight, leaf, cur_vals, n, npad, K, stats, newton_stats, boot_type, boot_p, seed, iter_ptr,
                    scal, statmax};
-    cb_mc_grad_kernel<<<grid, 256, 0, st>>>(a);
+    // One wave of resident blocks: `grid` is the caller's SM count times a guess, the occupancy query knows the real
+    // number of blocks per SM for this instantiation.
+    int dev = 0, sms = 0, occ = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    auto kern = K <= 4 ? cb_mc_grad_kernel<4> : K <= 8 ? cb_mc_grad_kernel<8> : cb_mc_grad_kernel<16>;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, 256, 0) == cudaSuccess && occ > 0 && sms > 0) grid = sms * occ;
+    const long long need = (npad + 255) / 256;
+    if (grid > need) grid = (int)need;
+    if (grid < 1) grid = 1;
+    kern<<<grid, 256, 0, st>>>(a);
     return (int)cudaGetLastError();
 }
 
