@@ -183,7 +183,7 @@ class CatBoost:
     def _format(self, raw, prediction_type):
         m = self._model
         pt = prediction_type
-        binclass = m.loss_name in ("Logloss", "CrossEntropy")
+        binclass = m.loss_name in ("Logloss", "CrossEntropy", "Focal")
         multi = m.loss_name in ("MultiClass", "MultiClassOneVsAll")
         if pt == "RawFormulaVal":
             return raw[:, 0] if raw.shape[1] == 1 else raw
@@ -585,9 +585,9 @@ class CatBoost:
     def _encode_labels(self, label):
         names = self._model.class_names
         lab = np.asarray(label)
-        if names is not None and self._model.loss_name in ("Logloss", "MultiClass", "MultiClassOneVsAll"):
+        if names is not None and self._model.loss_name in ("Logloss", "Focal", "MultiClass", "MultiClassOneVsAll"):
             tb = self._model.params.get("target_border")
-            if tb is not None and self._model.loss_name == "Logloss":
+            if tb is not None and self._model.loss_name in ("Logloss", "Focal"):
                 return (lab.astype(np.float64) > float(tb)).astype(np.float32)
             m = {v: i for i, v in enumerate(names)}
             return np.array([m.get(v, -1) for v in lab.tolist()], dtype=np.float32)

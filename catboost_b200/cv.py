@@ -57,7 +57,7 @@ def cv(pool=None, params=None, dtrain=None, iterations=None, num_boost_round=Non
     k = fold_count or nfold or 3
     loss = params.get("loss_function", params.get("objective"))
     if stratified is None:
-        stratified = isinstance(loss, str) and loss.split(":")[0] in ("Logloss", "MultiClass", "MultiClassOneVsAll")
+        stratified = isinstance(loss, str) and loss.split(":")[0] in ("Logloss", "Focal", "MultiClass", "MultiClassOneVsAll")
     seed = partition_random_seed if seed is None else seed
     splits = folds if folds is not None else _fold_indices(pool, k, shuffle, seed, stratified, inverted)
     params.setdefault("verbose", bool(verbose or verbose_eval) if (verbose or verbose_eval) is not None else False)

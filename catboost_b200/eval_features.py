@@ -64,7 +64,7 @@ def eval_features(pool: Pool, params: dict, features_to_eval: Sequence, eval_typ
     user_ignored = list(params.pop("ignored_features", None) or [])
     params.setdefault("verbose", False)
     params.setdefault("allow_writing_files", False)
-    stratified = str(params["loss_function"]).split(":")[0] in ("Logloss", "MultiClass", "MultiClassOneVsAll")
+    stratified = str(params["loss_function"]).split(":")[0] in ("Logloss", "Focal", "MultiClass", "MultiClassOneVsAll")
     folds = _fold_indices(pool, fold_count, True, partition_random_seed, stratified)
     values = {m: {lab: [] for lab, _ in [baseline] + tests} for m in metrics}
     for train_idx, test_idx in folds:

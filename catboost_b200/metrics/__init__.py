@@ -588,7 +588,8 @@ def _multirmse_missing(a, y, w, p, c):
 
 
 def _cox(a, y, w, p, c):
-    # negative partial log-likelihood; |y| = time, y > 0 = event observed, y < 0 = censored (the reference's convention)
+    # partial log-likelihood, larger is better (catboost/libs/metrics/metric.cpp TCoxMetric); |y| = time, y > 0 = event
+    # observed, y < 0 = censored
     yy = np.asarray(y, dtype=np.float64)
     t = np.abs(yy)
     order = np.argsort(-t, kind="stable")
@@ -596,7 +597,7 @@ def _cox(a, y, w, p, c):
     m = f.max() if len(f) else 0.0
     lse = m + np.log(np.cumsum(np.exp(f - m)))            # log sum over the risk set (times >= t_i)
     ev = yy[order] > 0
-    return float(-np.sum((f - lse)[ev]))
+    return float(np.sum((f - lse)[ev]))
 
 
 def _multi_quantile(a, y, w, p, c):
@@ -609,12 +610,39 @@ def _multi_quantile(a, y, w, p, c):
     return float(tot / (w.sum() * max(len(alphas), 1)))
 
 
+def _survival_aft(a, y, w, p, c):
+    # mean distance of exp(approx) from the target interval, 0 inside it (catboost/libs/metrics/metric.cpp
+    # TSurvivalAftMetric); an end of -1 is open
+    yy = np.asarray(y, dtype=np.float64).reshape(len(a), 2)
+    lo = yy[:, 0]
+    up = np.where(yy[:, 1] == -1, np.inf, yy[:, 1])
+    lo = np.where(lo == -1, np.inf, lo)
+    e = np.exp(a[:, 0])
+    out = (e <= lo) | (e >= up)
+    with np.errstate(invalid="ignore"):
+        dist = np.minimum(np.abs(e - lo), np.abs(e - up))
+    return float(np.sum(w * np.where(out, dist, 0.0)) / w.sum())
+
+
+def _group_quantile(a, y, w, p, c):
+    # pinball loss of the residual after the weighted mean residual of the document's group is taken out
+    alpha = float(p.get("alpha", 0.5))
+    off = _groups(c, len(a))
+    g = np.repeat(np.arange(len(off) - 1), np.diff(off))
+    r = np.asarray(y, dtype=np.float64) - a[:, 0]
+    sw = np.bincount(g, weights=w)
+    shift = np.bincount(g, weights=w * r) / np.maximum(sw, 1e-300)
+    d = r - shift[g]
+    return float(np.sum(w * np.where(d >= 0, alpha * d, (alpha - 1) * d)) / w.sum())
+
+
 _METRICS: Dict[str, tuple] = {
+    "SurvivalAft": (_survival_aft, False, ""), "GroupQuantile": (_group_quantile, False, "group"),
     "RMSPE": (_rmspe, False, ""), "Focal": (_focal, False, ""), "F": (_f_beta, True, ""), "WKappa": (_wkappa, True, ""),
     "LogLikelihoodOfPrediction": (_loglik_of_prediction, True, ""), "PRAUC": (_prauc, True, ""),
     "QueryAverage": (_query_average, True, "group"), "FilteredDCG": (_filtered_dcg, True, "group"),
     "ERR": (_err, True, "group"), "MultiRMSEWithMissingValues": (_multirmse_missing, False, ""),
-    "Cox": (_cox, False, ""), "MultiQuantile": (_multi_quantile, False, ""),
+    "Cox": (_cox, True, ""), "MultiQuantile": (_multi_quantile, False, ""),
     # name: (fn, is_max_optimal, needs)
     "RMSE": (_rmse, False, ""), "MAE": (_mae, False, ""), "MAPE": (_mape, False, ""), "SMAPE": (_smape, False, ""),
     "MSLE": (_msle, False, ""), "R2": (_r2, True, ""), "MedianAbsoluteError": (_median_abs, False, ""),
@@ -640,6 +668,7 @@ _METRICS: Dict[str, tuple] = {
     "YetiRank": (_pfound, True, "group"), "YetiRankPairwise": (_pfound, True, "group"),
     "PairLogitPairwise": (_pairlogit, False, "pairs"), "QueryCrossEntropy": (_logloss, False, "group"),
     "LambdaMart": (_ndcg, True, "group"), "StochasticRank": (_ndcg, True, "group"),
+    "StochasticFilter": (_filtered_dcg, True, "group"),
     "RMSEWithUncertainty": (lambda a, y, w, p, c: float(np.sum(w * (a[:, 1] + 0.5 * (y - a[:, 0]) ** 2 * np.exp(-2 * a[:, 1])
                                                                  + 0.5 * math.log(2 * math.pi))) / w.sum()), False, ""),
 }

@@ -104,7 +104,7 @@ def _flatten_trees(m: Model):
 
 def model_to_onnx_bytes(m: Model) -> bytes:
     trees = _flatten_trees(m)
-    classifier = m.class_names is not None and m.loss_name in ("Logloss", "CrossEntropy", "MultiClass", "MultiClassOneVsAll")
+    classifier = m.class_names is not None and m.loss_name in ("Logloss", "CrossEntropy", "Focal", "MultiClass", "MultiClassOneVsAll")
     dims = m.dims
     treeids, nodeids, featids, values, modes, trueids, falseids, missing = [], [], [], [], [], [], [], []
     t_tree, t_node, t_id, t_w = [], [], [], []

@@ -328,7 +328,7 @@ def model_from_cbm_bytes(blob: bytes) -> Model:
                 m.class_names = cp["class_names"]
         except ValueError:
             pass
-    if m.class_names is None and m.loss_name in ("Logloss", "CrossEntropy"):
+    if m.class_names is None and m.loss_name in ("Logloss", "CrossEntropy", "Focal"):
         m.class_names = [0, 1]
     flat = [f.flat_index for f in m.float_features] + [c.flat_index for c in m.cat_features]
     m.n_features = meta.get("n_features") or (max(flat) + 1 if flat else 0)

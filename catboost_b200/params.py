@@ -65,17 +65,18 @@ RESOURCE_HINTS = {"used_ram_limit", "gpu_ram_part", "pinned_memory_size", "devic
 # Options of the reference whose behaviour is not implemented: a value that differs from the default is refused with an
 # error instead of being silently dropped.
 NOT_IMPLEMENTED = {"counter_calc_method", "ctr_leaf_count_limit", "store_all_simple_ctr", "final_ctr_computation_mode",
-                   "ctr_history_unit", "approx_on_full_history", "sampling_frequency",
-                   "penalties_coefficient", "first_feature_use_penalties",
-                   "per_object_feature_penalties", "fixed_binary_splits", "sparse_features_conflict_fraction"}
+                   "ctr_history_unit", "approx_on_full_history", "fixed_binary_splits",
+                   "sparse_features_conflict_fraction"}
 
 POINTWISE_LOSSES = {"RMSE", "Logloss", "CrossEntropy", "Poisson", "MAE", "Quantile", "LogLinQuantile", "MAPE", "Huber",
-                    "Lq", "Expectile", "Tweedie", "LogCosh"}
-MULTI_LOSSES = {"MultiClass", "MultiClassOneVsAll", "MultiLogloss", "MultiCrossEntropy", "MultiRMSE", "RMSEWithUncertainty"}
+                    "Lq", "Expectile", "Tweedie", "LogCosh", "Focal"}
+MULTI_LOSSES = {"MultiClass", "MultiClassOneVsAll", "MultiLogloss", "MultiCrossEntropy", "MultiRMSE", "RMSEWithUncertainty",
+                "MultiQuantile"}
+SURVIVAL_LOSSES = {"Cox", "SurvivalAft"}
 RANKING_LOSSES = {"YetiRank", "YetiRankPairwise", "PairLogit", "PairLogitPairwise", "QueryRMSE", "QuerySoftMax",
-                  "QueryCrossEntropy", "LambdaMart", "StochasticRank", "StochasticFilter"}
+                  "QueryCrossEntropy", "LambdaMart", "StochasticRank", "StochasticFilter", "GroupQuantile"}
 PAIRWISE_HIST_LOSSES = {"YetiRankPairwise", "PairLogitPairwise", "QueryCrossEntropy"}
-ALL_LOSSES = POINTWISE_LOSSES | MULTI_LOSSES | RANKING_LOSSES | {"PythonUserDefinedPerObject"}
+ALL_LOSSES = POINTWISE_LOSSES | MULTI_LOSSES | RANKING_LOSSES | SURVIVAL_LOSSES | {"PythonUserDefinedPerObject"}
 
 # (newton iterations, gradient iterations, method, l2)  -- catboost_options.cpp:31-271
 _LEAF_DEFAULTS = {
@@ -90,7 +91,9 @@ _LEAF_DEFAULTS = {
     "YetiRankPairwise": (1, 1, "Simple", 0.0), "QueryCrossEntropy": (10, 1, "Newton", 1.0),
     "LambdaMart": (1, 1, "Newton", 0.0), "StochasticRank": (1, 1, "Gradient", 3.0),
     "StochasticFilter": (1, 100, "Gradient", 3.0), "Tweedie": (1, 1, "Newton", 3.0), "Lq": (1, 1, "Newton", 3.0),
-    "PythonUserDefinedPerObject": (1, 1, "Gradient", 3.0),
+    "PythonUserDefinedPerObject": (1, 1, "Gradient", 3.0), "MultiQuantile": (1, 1, "Gradient", 3.0),
+    "GroupQuantile": (1, 1, "Gradient", 3.0), "Focal": (1, 1, "Newton", 3.0), "Cox": (1, 1, "Newton", 3.0),
+    "SurvivalAft": (1, 1, "Gradient", 3.0),
 }
 
 
@@ -103,6 +106,11 @@ def parse_loss(desc: str):
     if rest:
         for tok in re.split(r"[;,]", rest):
             if not tok:
+                continue
+            if "=" not in tok and params:
+                # 'alpha=0.2,0.8': a bare token continues the list value of the key before it
+                last = next(reversed(params))
+                params[last] = f"{params[last]:g},{tok.strip()}" if isinstance(params[last], float) else f"{params[last]},{tok.strip()}"
                 continue
             k, _, v = tok.partition("=")
             try:

@@ -56,10 +56,10 @@ class LabelCodec:
         self.loss = o.loss_name
         self.class_names = None
         self.n_classes = None
-        self.is_binclass = self.loss in ("Logloss", "CrossEntropy")
+        self.is_binclass = self.loss in ("Logloss", "CrossEntropy", "Focal")
         self.is_multiclass = self.loss in ("MultiClass", "MultiClassOneVsAll")
         lab = np.asarray(label)
-        if self.loss == "Logloss":
+        if self.loss in ("Logloss", "Focal"):
             if o.target_border is not None:
                 self.border = float(o.target_border)
                 self.class_names = [0, 1]
@@ -69,7 +69,7 @@ class LabelCodec:
                 if o.class_names is not None:
                     uniq = list(o.class_names)
                 if len(uniq) > 2:
-                    raise CatBoostError(f"Logloss needs a binary target; got {len(uniq)} distinct values "
+                    raise CatBoostError(f"{self.loss} needs a binary target; got {len(uniq)} distinct values "
                                         "(set target_border or use MultiClass)")
                 if len(uniq) < 2 and not o.allow_const_label:
                     raise CatBoostError("target contains only one unique value")
@@ -122,7 +122,7 @@ class LabelCodec:
 
     def encode(self, label) -> np.ndarray:
         lab = np.asarray(label)
-        if self.loss == "Logloss":
+        if self.loss in ("Logloss", "Focal"):
             if self.border is not None:
                 return (lab.astype(np.float64) > self.border).astype(np.float32)
             return self._map(lab)
@@ -324,7 +324,7 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
 
     # ---- targets ---------------------------------------------------------------------------------------
     codec = LabelCodec(o, train_pool.label, ctx)
-    multi_target = o.loss_name in ("MultiRMSE", "MultiLogloss", "MultiCrossEntropy")
+    multi_target = o.loss_name in ("MultiRMSE", "MultiLogloss", "MultiCrossEntropy", "SurvivalAft")
     if multi_target:
         y_train = np.asarray(train_pool.label, dtype=np.float32).reshape(train_pool.num_row(), -1)
         n_targets = y_train.shape[1]
@@ -340,6 +340,10 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
         w_train = cw if w_train is None else w_train * cw
     if objective.needs_groups and train_pool.group_id is None:
         raise CatBoostError(f"{o.loss_name} needs group_id")
+    if o.loss_name == "Cox" and ctx.is_distributed:
+        raise CatBoostError("Cox couples all documents through one sorted pass: train it on one rank")
+    if o.loss_name == "SurvivalAft" and n_targets != 2:
+        raise CatBoostError("SurvivalAft needs two label columns: lower and upper bound (-1 = open end)")
 
     # ---- text / embedding columns -> estimated numeric features ----------------------------------------
     estimators = None

@@ -119,11 +119,88 @@ class GenericLearner:
         self._onehot_host = store.feat_onehot.cpu().numpy().astype(bool)        # read on the host by the growth loops
         self.monotone = None          # float tensor [F] in {-1, 0, +1} per flat feature, set by set_monotone()
         self.group_of_doc = None      # int64 [n] query number of every document: set for sampling_unit='Group'
+        # feature penalties (set_penalties): the score of a candidate loses coef * first_use[f] while feature f is in no
+        # tree yet, and coef * per_object[f] * (documents of the leaf that have not met f on their path in any tree)
+        self.pen_first = None         # float tensor [F] or None
+        self.pen_object = None        # float tensor [F] or None
+        self.pen_coef = 1.0
+        self.used_feature = torch.zeros(store.F, dtype=torch.bool, device=self.dev)
+        self.used_by_doc = {}         # flat feature -> bool [n], only for features with a per-object penalty
+        self._resample = None         # set by build_tree when the bootstrap is redrawn at every level
         self.n_total = store.n
         if ctx is not None and ctx.is_distributed:
             t = torch.tensor([store.n], dtype=torch.float64, device=self.dev)
             ctx.all_reduce_sum_(t)
             self.n_total = int(t.item())
+
+
+    # -- feature penalties (catboost/private/libs/algo/feature_penalties_calcer.cpp) ------------------------
+    def set_penalties(self, first_use, per_object, coef: float):
+        """first_use / per_object: float arrays [F] over the flat features of the store (zeros = no penalty)."""
+        to = lambda v: None if v is None or not np.any(v) else torch.from_numpy(np.asarray(v, dtype=np.float32)).to(self.dev)
+        self.pen_first, self.pen_object, self.pen_coef = to(first_use), to(per_object), float(coef)
+        if self.pen_object is not None:
+            for f in torch.nonzero(self.pen_object).flatten().tolist():
+                self.used_by_doc[int(f)] = torch.zeros(self.store.n, dtype=torch.bool, device=self.dev)
+
+    @property
+    def has_penalties(self) -> bool:
+        return self.pen_first is not None or self.pen_object is not None
+
+    def _penalty(self, node_ids=None):
+        """Penalty [L, F] (L = 1 for symmetric trees, where a level splits every leaf) to subtract from the scores."""
+        if not self.has_penalties:
+            return None
+        L = 1 if node_ids is None else len(node_ids)
+        pen = torch.zeros((L, self.store.F), dtype=torch.float32, device=self.dev)
+        if self.pen_first is not None:
+            pen += (self.pen_first * (~self.used_feature).float()).unsqueeze(0)
+        if self.pen_object is not None:
+            n = self.store.n
+            row = None
+            if node_ids is not None:
+                lut = torch.full((max(int(max(node_ids)) + 1, 1),), -1, dtype=torch.long, device=self.dev)
+                lut[torch.tensor(list(node_ids), device=self.dev)] = torch.arange(L, device=self.dev)
+                node = self.leaf[:n].long() & 0xFFFF
+                row = torch.where(node < lut.numel(), lut[node.clamp_max(lut.numel() - 1)], torch.full_like(node, -1))
+            for f, seen in self.used_by_doc.items():
+                fresh = ~seen
+                if row is None:
+                    cnt = fresh.sum().view(1).float()
+                else:
+                    sel = fresh & (row >= 0)
+                    cnt = torch.bincount(row[sel], minlength=L).float()
+                if self.ctx is not None and self.ctx.is_distributed:
+                    cnt = cnt.double()
+                    self.ctx.all_reduce_sum_(cnt)
+                    cnt = cnt.float()
+                pen[:, f] += self.pen_object[f] * cnt
+        return pen * self.pen_coef
+
+    def _mark_used(self, tr: "TreeResult"):
+        """After a tree: the features it splits on count as used; per-object flags follow the path of every document."""
+        if not self.has_penalties:
+            return
+        n = self.store.n
+        if tr.kind == "oblivious":
+            for f in tr.splits[:, 0]:
+                if f >= 0:
+                    self.used_feature[int(f)] = True
+                    if int(f) in self.used_by_doc:
+                        self.used_by_doc[int(f)].fill_(True)
+            return
+        ns = tr.node_split
+        on_path = {0: frozenset()}
+        for node in range(len(ns)):
+            f, left = int(ns[node, 0]), int(ns[node, 3])
+            if f >= 0:
+                self.used_feature[f] = True
+                on_path[left] = on_path[left + 1] = on_path[node] | {f}
+        leaf_doc = self.leaf[:n].long() & 0xFFFF
+        for f, seen in self.used_by_doc.items():
+            leaves = [int(tr.leaf_of_node[node]) for node, fs in on_path.items() if f in fs and tr.leaf_of_node[node] >= 0]
+            if leaves:
+                seen |= torch.isin(leaf_doc, torch.tensor(leaves, device=self.dev))
 
     # -- helpers ---------------------------------------------------------------------------------------
     def _rand(self, shape):
@@ -228,27 +305,39 @@ class GenericLearner:
         """der/hess: [dims, npad] (already multiplied by the sample weights)."""
         o, n, npad = self.o, self.store.n, self.store.npad
         newton = o.score_function.startswith("Newton")
-        bw = self.bootstrap_weights(der)
         K = self.dims
         rows = K + 1 + (1 if self.use_count else 0)
-        stats = torch.zeros((rows, npad), dtype=torch.float32, device=self.dev)
         wcol = hess[:, :n].sum(0) / K if newton else (torch.ones(n, device=self.dev) if weight is None else weight[:n])
-        if bw is not None:
-            stats[:K, :n] = der[:, :n] * bw
-            stats[K, :n] = wcol * bw
-        else:
-            stats[:K, :n] = der[:, :n]
-            stats[K, :n] = wcol
-        if self.use_count:
-            stats[K + 1, :n] = 1.0
+
+        def make_stats():
+            bw = self.bootstrap_weights(der)
+            st = torch.zeros((rows, npad), dtype=torch.float32, device=self.dev)
+            if bw is not None:
+                st[:K, :n] = der[:, :n] * bw
+                st[K, :n] = wcol * bw
+            else:
+                st[:K, :n] = der[:, :n]
+                st[K, :n] = wcol
+            if self.use_count:
+                st[K + 1, :n] = 1.0
+            return st
+
+        stats = make_stats()
+        # sampling_frequency='PerTreeLevel' (catboost/private/libs/algo/greedy_tensor_search.cpp: the bootstrap runs before
+        # every level's candidate scoring): the growers call this for fresh weights at every level after the first
+        self._resample = make_stats if (str(o.sampling_frequency or "PerTree") == "PerTreeLevel"
+                                        and o.bootstrap_type != "No") else None
         self.leaf.zero_()
         noise_std = self._noise_std(der, iteration)
         fmask = self._feature_mask()
         if o.grow_policy == "SymmetricTree":
-            return self._grow_symmetric(stats, K, noise_std, fmask)
-        if o.grow_policy in ("Depthwise", "Region"):
-            return self._grow_depthwise(stats, K, noise_std, fmask)
-        return self._grow_lossguide(stats, K, noise_std, fmask)
+            tr = self._grow_symmetric(stats, K, noise_std, fmask)
+        elif o.grow_policy in ("Depthwise", "Region"):
+            tr = self._grow_depthwise(stats, K, noise_std, fmask)
+        else:
+            tr = self._grow_lossguide(stats, K, noise_std, fmask)
+        self._mark_used(tr)
+        return tr
 
     def set_monotone(self, per_float_feature: dict):
         """``per_float_feature``: {float-feature index: +1 / -1}.  A candidate on a constrained feature is only allowed
@@ -283,6 +372,8 @@ class GenericLearner:
         h_prev, small_right = None, None
         for level in range(depth):
             L = 1 << level
+            if level and self._resample is not None:
+                stats, h_prev = self._resample(), None       # new weights: the parent histograms no longer apply
             if h_prev is None:
                 table = torch.arange(L, dtype=torch.int16, device=self.dev)
                 h = self._hist(stats, table, L)
@@ -302,6 +393,9 @@ class GenericLearner:
             if noise_std > 0:
                 score = score + self._score_noise(score.shape) * noise_std
             score = score * fw.unsqueeze(1)
+            pen = self._penalty()
+            if pen is not None:
+                score = score - pen[0].unsqueeze(1)
             mask = self._cand_mask(fmask, cnt)
             if self.monotone is not None and K == 1:
                 mask = mask & self._monotone_ok(sides_[0], sides_[1], K)
@@ -323,6 +417,9 @@ class GenericLearner:
         return TreeResult("oblivious", splits=splits, n_leaves=1 << depth, leaf=self.leaf)
 
     def _per_leaf_best(self, h, K, noise_std, fmask, node_ids=None):
+        if self.has_penalties:
+            return self._per_leaf_best_tensor(h, K, noise_std, fmask, self._penalty(node_ids if node_ids is not None
+                                                                                  else range(h.shape[0])))
         if self.dev.type == "cuda" and self.monotone is None:
             # device search: one warp per (leaf, feature) + one warp per leaf, 16 bytes per leaf read back
             self._search_calls = getattr(self, "_search_calls", 0) + 1
@@ -344,7 +441,7 @@ class GenericLearner:
             return best, np.where(feat >= 0, score, -np.inf), gain
         return self._per_leaf_best_tensor(h, K, noise_std, fmask)
 
-    def _per_leaf_best_tensor(self, h, K, noise_std, fmask):
+    def _per_leaf_best_tensor(self, h, K, noise_std, fmask, penalty=None):
         """The same search as tensor code (CPU path, monotone constraints, and the oracle of the device kernel)."""
         sc = self.scorer
         cstat = K + 1 if self.use_count else None
@@ -360,6 +457,8 @@ class GenericLearner:
         if noise_std > 0:
             score = score + self._score_noise(score.shape) * noise_std
         score = score * self.store.feat_weight.view(1, -1, 1)
+        if penalty is not None:
+            score = score - penalty.unsqueeze(-1)
         mask = (sc.valid_cand & fmask.unsqueeze(1)).unsqueeze(0).expand_as(score)
         nonempty = (left[:, K] > 0) & (right[:, K] > 0)
         mask = mask & nonempty
@@ -381,6 +480,8 @@ class GenericLearner:
         for level in range(depth):
             if not frontier:
                 break
+            if level and self._resample is not None:
+                stats = self._resample()
             table = torch.full((len(node_split),), -1, dtype=torch.int16, device=self.dev)
             table[torch.tensor(frontier, device=self.dev)] = torch.arange(len(frontier), dtype=torch.int16, device=self.dev)
             h = self._hist(stats, table, len(frontier))
@@ -413,6 +514,9 @@ class GenericLearner:
         table_all = torch.full((2 * max_leaves + 1,), -1, dtype=torch.int16, device=self.dev)
 
         def evaluate(nodes):
+            nonlocal stats
+            if nodes != [0] and self._resample is not None:
+                stats = self._resample()
             table_all.fill_(-1)
             for j, node in enumerate(nodes):
                 table_all[node] = j                       # scalar writes: kernel arguments, not host-to-device copies

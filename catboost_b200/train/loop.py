@@ -73,6 +73,50 @@ def _parse_monotone(spec, pool) -> dict:
     return out
 
 
+def _per_feature_values(spec, pool) -> dict:
+    """{external feature index: value} from a list per feature, a dict by index or name, or the strings "(1,0,2)" /
+    "0:1.5,3:2" / "name:1" (the forms feature_weights and the penalty options take,
+    catboost/private/libs/options/feature_penalties_options.cpp)."""
+    out = {}
+    if spec is None:
+        return out
+    key = lambda k: pool.feature_names.index(k) if isinstance(k, str) and not k.strip().lstrip("-").isdigit() else int(k)
+    if isinstance(spec, str):
+        items = [x.strip() for x in spec.strip().strip("()[]").split(",") if x.strip()]
+        if items and all(":" not in x for x in items):
+            out = {i: float(x) for i, x in enumerate(items)}
+        else:
+            for x in items:
+                k, v = x.split(":")
+                out[key(k.strip())] = float(v)
+    elif isinstance(spec, dict):
+        out = {key(k): float(v) for k, v in spec.items()}
+    else:
+        out = {i: float(v) for i, v in enumerate(spec)}
+    return {k: v for k, v in out.items() if v != 0.0}
+
+
+def _flat_penalties(spec, pool, store) -> Optional[np.ndarray]:
+    """Per-feature option values laid over the flat features of the store: a quantised float feature and a one-hot
+    feature take the value of their source column; features computed from several columns (CTRs) take none."""
+    vals = _per_feature_values(spec, pool)
+    if not vals:
+        return None
+    if any(v < 0 for v in vals.values()):
+        raise CatBoostError("feature penalties must be non-negative")
+    out = np.zeros(store.F, dtype=np.float32)
+    for i, f in enumerate(store.features):
+        if f.kind == "float" and f.source >= 0:
+            out[i] = vals.get(pool.float_feature_indices[f.source], 0.0)
+        elif f.kind == "onehot":
+            out[i] = vals.get(pool.cat_feature_indices[f.source], 0.0)
+    return out
+
+
+def _has_penalties(o) -> bool:
+    return bool(o.first_feature_use_penalties) or bool(o.per_object_feature_penalties)
+
+
 def _use_fast_engine(o, objective, store, dims) -> bool:
     # objectives without a device formula still use the fused level kernels: their derivatives are computed by the
     # objective's tensor code once per tree, which only allows a single leaf-estimation step
@@ -92,6 +136,7 @@ def _use_fast_engine(o, objective, store, dims) -> bool:
             and (o.bootstrap_type in ("No", "Bayesian", "Bernoulli", "Poisson") or (o.bootstrap_type == "MVS" and dims == 1))
             and not o.langevin and not o.monotone_constraints and not o.model_shrink_rate
             and str(o.sampling_unit or "Object") == "Object"
+            and not _has_penalties(o) and str(o.sampling_frequency or "PerTree") == "PerTree"
             and not getattr(objective, "pairwise_scoring", False)       # pairwise systems live in the general learner
             and str(o.random_score_type) != "Gumbel")
 
@@ -158,6 +203,10 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
             raise CatBoostError("sampling_unit='Group' needs group_id")
         off = train_pool.group_offsets()
         learner.group_of_doc = torch.from_numpy(np.repeat(np.arange(len(off) - 1), np.diff(off))).to(dev)
+    if _has_penalties(o):
+        learner.set_penalties(_flat_penalties(o.first_feature_use_penalties, train_pool, store),
+                              _flat_penalties(o.per_object_feature_penalties, train_pool, store),
+                              float(o.penalties_coefficient if o.penalties_coefficient is not None else 1.0))
     monotone_flat = None
     if o.monotone_constraints:
         mono = _parse_monotone(o.monotone_constraints, train_pool)
@@ -187,6 +236,15 @@ def run_boosting(o, objective, store, eval_stores, y_train, w_train, base_train,
             _apply_tree_to(store, t, approx, n, dims, dev)
             for es, ea in zip(eval_stores, eval_approx):
                 _apply_tree_to(es, t, ea, es.n, dims, dev)
+            if learner.has_penalties:
+                # features of the restored trees count as used (for every document: the per-document paths of
+                # non-symmetric trees are not stored)
+                used = t["splits"][:, 0] if t["kind"] == "oblivious" else t["node_split"][:, 0]
+                for f in used:
+                    if f >= 0:
+                        learner.used_feature[int(f)] = True
+                        if int(f) in learner.used_by_doc:
+                            learner.used_by_doc[int(f)].fill_(True)
         if ordered is not None:
             ordered.approx.copy_(approx[:, :n])      # ordered cursors are not stored; resume from the plain cursor
         learner.gen.manual_seed(int(o.random_seed) + 12345 + start_iter)

@@ -362,10 +362,13 @@ class RMSEWithUncertainty(Objective):
 
     def der_hess(self, approx, target, weight, ctx=None):
         mu, ls = approx[0], approx[1]          # mean, log std
+        # the natural gradient of the Gaussian likelihood (gradient times the inverse Fisher information), as in
+        # catboost/private/libs/algo_helpers/error_functions.h TRMSEWithUncertaintyError: the mean's derivative is the
+        # plain residual with unit second derivative
         prec = torch.exp(-2 * ls)
-        d0 = (target - mu) * prec
+        d0 = target - mu
         d1 = (target - mu) ** 2 * prec - 1.0
-        h0 = prec
+        h0 = torch.ones_like(mu)
         h1 = (2 * (target - mu) ** 2 * prec).clamp_min(1e-6)
         der, hess = torch.stack([d0, d1]), torch.stack([h0, h1])
         if weight is not None:
@@ -381,6 +384,203 @@ class RMSEWithUncertainty(Objective):
         m = float(np.average(target, weights=weight))
         var = float(np.average((target - m) ** 2, weights=weight))
         return np.array([m, 0.5 * math.log(max(var, 1e-12))])
+
+
+class Focal(_Pointwise):
+    """Focal loss for binary classification, -a_t (1 - p_t)^gamma log p_t with p_t the probability of the true class
+    (first and second derivatives as in catboost/private/libs/algo_helpers/error_functions.h:1669-1710)."""
+    name = "Focal"
+    is_classification = True
+
+    def _point(self, a, y):
+        alpha = float(self.params.get("focal_alpha", 0.25))
+        gamma = float(self.params.get("focal_gamma", 2.0))
+        pos = y > 0.5
+        p = torch.sigmoid(a).clamp(1e-13, 1.0 - 1e-13)
+        pt = torch.where(pos, p, 1.0 - p)
+        at = torch.where(pos, torch.full_like(p, alpha), torch.full_like(p, 1.0 - alpha))
+        sgn = torch.where(pos, torch.ones_like(p), -torch.ones_like(p))
+        lg = torch.log(pt)
+        u = at * sgn * (1.0 - pt) ** gamma
+        du = -at * sgn * gamma * (1.0 - pt) ** (gamma - 1.0)
+        v = gamma * pt * lg + pt - 1.0
+        dv = gamma * lg + gamma + 1.0
+        der = -(u * v)                                             # ascent direction of -loss
+        hess = ((du * v + u * dv) * sgn * (pt * (1.0 - pt))).clamp_min(1e-16)
+        return der, hess, -at * (1.0 - pt) ** gamma * lg
+
+
+class Cox(Objective):
+    """Cox proportional hazards: |target| is the time, target > 0 an observed event, target < 0 a censored one.  The
+    partial likelihood couples all documents, so the derivatives come from one pass over the documents sorted by time
+    (catboost/private/libs/algo_helpers/error_functions.cpp:153-205): with S_i the sum of exp(approx) over documents at
+    position >= i, r_i = sum over events e <= i of 1 / S_e and s_i the same sum of 1 / S_e^2,
+    der_i = [event_i] - exp(approx_i) r_i and hess_i = exp(approx_i) r_i - exp(approx_i)^2 s_i.  Weights are not used,
+    as in the reference."""
+    name = "Cox"
+    is_pointwise = False
+
+    def _sorted_terms(self, a, target):
+        order = torch.sort(target.abs(), stable=True).indices
+        e = torch.exp((a - a.max()).double())[order]
+        S = torch.flip(torch.cumsum(torch.flip(e, [0]), 0), [0]).clamp_min(1e-300)
+        ev = (target[order] > 0).double()
+        return order, e, S, ev
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        a = approx[0]
+        order, e, S, ev = self._sorted_terms(a, target)
+        r = torch.cumsum(ev / S, 0)
+        s2 = torch.cumsum(ev / (S * S), 0)
+        d_s = ev - e * r
+        h_s = (e * r - e * e * s2).clamp_min(1e-16)
+        der = torch.empty_like(a)
+        hess = torch.empty_like(a)
+        der[order] = d_s.float()
+        hess[order] = h_s.float()
+        return der.unsqueeze(0), hess.unsqueeze(0)
+
+    def value(self, approx, target, weight, ctx=None):
+        """Negative log partial likelihood (the quantity training minimises)."""
+        a = approx[0]
+        order, e, S, ev = self._sorted_terms(a, target)
+        ll = ((a - a.max()).double()[order] - torch.log(S)) * ev
+        return -float(ll.sum().item())
+
+
+class SurvivalAft(Objective):
+    """Accelerated failure time model on interval-censored targets: two label columns [lower, upper], -1 for an open
+    end, equal ends for an observed time.  z = (log t - approx) / scale follows the chosen distribution (Normal,
+    Logistic or Extreme); derivatives of the log-likelihood with the reference's clipping and its limits for vanishing
+    denominators (catboost/private/libs/algo_helpers/error_functions.cpp:360-450, survival_aft_utils.cpp,
+    catboost/libs/helpers/distribution_helpers.cpp)."""
+    name = "SurvivalAft"
+    is_pointwise = False
+    target_columns = 2
+
+    def __init__(self, params=None):
+        super().__init__(params)
+        self.dist = str(self.params.get("dist", "Normal")).capitalize()
+        self.scale = float(self.params.get("scale", 1.0))
+        if self.dist not in ("Normal", "Logistic", "Extreme"):
+            raise CatBoostError(f"SurvivalAft: unknown distribution {self.dist!r}")
+        if not self.scale > 0:
+            raise CatBoostError("SurvivalAft: scale should be positive")
+
+    # pdf, cdf, pdf', pdf'' of the three distributions ------------------------------------------------
+    def _pdf_cdf(self, z):
+        if self.dist == "Normal":
+            pdf = torch.exp(-0.5 * z * z) * 0.3989422804014327
+            cdf = 0.5 + 0.5 * torch.erf(z / math.sqrt(2.0))
+            return pdf, cdf, -z * pdf, (z * z - 1.0) * pdf
+        ez = torch.exp(z)
+        fin = torch.isfinite(ez) & torch.isfinite(ez * ez)
+        zero = torch.zeros_like(z)
+        if self.dist == "Extreme":
+            pdf = torch.where(torch.isfinite(ez), ez * torch.exp(-ez), zero)
+            cdf = 1.0 - torch.exp(-ez)
+            d1 = torch.where(torch.isfinite(ez), (1.0 - ez) * pdf, zero)
+            d2 = torch.where(fin, (ez * ez - 3.0 * ez + 1.0) * pdf, zero)
+            return pdf, cdf, d1, d2
+        pdf = torch.where(fin, ez / (1.0 + ez) ** 2, zero)
+        cdf = torch.where(torch.isfinite(ez), ez / (1.0 + ez), torch.ones_like(z))
+        d1 = torch.where(torch.isfinite(ez), pdf * (1.0 - ez) / (1.0 + ez), zero)
+        d2 = torch.where(fin, pdf * (ez * ez - 4.0 * ez + 1.0) / (1.0 + ez) ** 2, zero)
+        return pdf, cdf, d1, d2
+
+    def _limits(self, order):
+        """(min, max) per censoring kind [uncensored / interval, right, left] for a vanishing denominator."""
+        s = self.scale
+        if order == 1:
+            return {"Normal": ((-15.0, 15.0), (-15.0, 0.0), (0.0, 15.0)),
+                    "Extreme": ((-15.0, 1.0 / s), (-15.0, 0.0), (0.0, 1.0 / s)),
+                    "Logistic": ((-1.0 / s, 1.0 / s), (-1.0 / s, 0.0), (0.0, 1.0 / s))}[self.dist]
+        m = 1e-16
+        return {"Normal": ((1.0 / s ** 2, 1.0 / s ** 2), (1.0 / s ** 2, m), (m, 1.0 / s ** 2)),
+                "Extreme": ((15.0, m), (15.0, m), (m, m)),
+                "Logistic": ((m, m), (m, m), (m, m))}[self.dist]
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        a = approx[0].double()
+        lo, up = target[0].double(), target[1].double()
+        s = self.scale
+        unc = lo == up
+        right = (up == -1) & ~unc
+        left = (lo == -1) & ~unc
+        zl = (torch.log(lo.clamp_min(1e-300)) - a) / s
+        zu = (torch.log(up.clamp_min(1e-300)) - a) / s
+        pl, cl, dl, d2l = self._pdf_cdf(zl)
+        pu, cu, du, _ = self._pdf_cdf(zu)
+        zero, one = torch.zeros_like(a), torch.ones_like(a)
+        pu, cu, du = torch.where(right, zero, pu), torch.where(right, one, cu), torch.where(right, zero, du)
+        pl_i, cl_i, dl_i = torch.where(left, zero, pl), torch.where(left, zero, cl), torch.where(left, zero, dl)
+        n1 = torch.where(unc, dl, pu - pl_i)
+        q1 = torch.where(unc, s * pl, s * (cu - cl_i))
+        n2 = torch.where(unc, -(pl * d2l - dl * dl), -(cu - cl_i) * (du - dl_i) + (pu - pl_i) ** 2)
+        q2 = torch.where(unc, (s * pl) ** 2, (s * (cu - cl_i)) ** 2)
+        sign = torch.where(unc, zl > 0, (torch.where(left, zero, zl) > 0) | (torch.where(right, zero, zu) > 0))
+        kind = torch.where(right, 1, torch.where(left, 2, 0))
+
+        def guarded(num, den, order):
+            r = num / den
+            lim = self._limits(order)
+            mn = torch.tensor([x[0] for x in lim], dtype=a.dtype, device=a.device)[kind]
+            mx = torch.tensor([x[1] for x in lim], dtype=a.dtype, device=a.device)[kind]
+            bad = (den < 1e-12) & ~torch.isfinite(r)
+            return torch.where(bad, torch.where(sign, mn, mx), r)
+
+        d1 = -guarded(n1, q1, 1).clamp(-15.0, 15.0)
+        h = guarded(n2, q2, 2).clamp(1e-16, 15.0)
+        return d1.float().unsqueeze(0), h.float().unsqueeze(0)
+
+    def value(self, approx, target, weight, ctx=None):
+        """Negative log-likelihood per document."""
+        a = approx[0].double()
+        lo, up = target[0].double(), target[1].double()
+        s = self.scale
+        unc = lo == up
+        zl = (torch.log(lo.clamp_min(1e-300)) - a) / s
+        zu = (torch.log(up.clamp_min(1e-300)) - a) / s
+        pl, cl, _, _ = self._pdf_cdf(zl)
+        _, cu, _, _ = self._pdf_cdf(zu)
+        cu = torch.where(up == -1, torch.ones_like(a), cu)
+        cl = torch.where(lo == -1, torch.zeros_like(a), cl)
+        lik = torch.where(unc, pl / (s * lo.clamp_min(1e-300)), cu - cl).clamp_min(1e-12)
+        v = -torch.log(lik).float()
+        return _wsum(v, weight) / max(_wtot(a.numel(), weight), 1e-300)
+
+
+class MultiQuantile(Objective):
+    """One approx dimension per level in ``alpha=a1,a2,...``: the pinball loss of every level
+    (catboost/private/libs/algo_helpers/error_functions.cpp TMultiQuantileError::CalcDersMulti)."""
+    name = "MultiQuantile"
+    is_pointwise = False
+
+    def __init__(self, params=None):
+        super().__init__(params)
+        al = self.params.get("alpha", 0.5)
+        self.alphas = [float(x) for x in str(al).split(",")] if not isinstance(al, (int, float)) else [float(al)]
+        self.delta = float(self.params.get("delta", 1e-6))
+        self.dims = len(self.alphas)
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        al = torch.tensor(self.alphas, dtype=approx.dtype, device=approx.device).unsqueeze(1)
+        r = target.unsqueeze(0) - approx
+        d = torch.where(r > 0, al.expand_as(r), (al - 1.0).expand_as(r))
+        d = torch.where(r.abs() < self.delta, torch.zeros_like(d), d)
+        h = torch.ones_like(d)
+        if weight is not None:
+            d, h = d * weight, h * weight
+        return d, h
+
+    def value(self, approx, target, weight, ctx=None):
+        al = torch.tensor(self.alphas, dtype=approx.dtype, device=approx.device).unsqueeze(1)
+        r = target.unsqueeze(0) - approx
+        v = torch.where(r >= 0, al * r, (al - 1.0) * r).sum(0) / self.dims
+        return _wsum(v, weight) / max(_wtot(target.numel(), weight), 1e-300)
+
+    def start_constant(self, target, weight):
+        return np.array([_weighted_quantile(target, weight, a) for a in self.alphas])
 
 
 class UserObjective(Objective):
@@ -418,7 +618,7 @@ def _weighted_quantile(values, weight, alpha):
 
 
 _POINTWISE = {c.name: c for c in (RMSE, Logloss, CrossEntropy, Poisson, MAE, Quantile, LogLinQuantile, MAPE, Huber,
-                                  Lq, Expectile, Tweedie, LogCosh)}
+                                  Lq, Expectile, Tweedie, LogCosh, Focal)}
 
 
 def make_objective(loss, params: dict, n_classes: Optional[int] = None, n_targets: int = 1) -> Objective:
@@ -438,6 +638,12 @@ def make_objective(loss, params: dict, n_classes: Optional[int] = None, n_target
         return MultiCrossEntropy(params, n_targets)
     if loss == "RMSEWithUncertainty":
         return RMSEWithUncertainty(params)
+    if loss == "Cox":
+        return Cox(params)
+    if loss == "SurvivalAft":
+        return SurvivalAft(params)
+    if loss == "MultiQuantile":
+        return MultiQuantile(params)
     from .ranking import make_ranking_objective
     obj = make_ranking_objective(loss, params)
     if obj is None:

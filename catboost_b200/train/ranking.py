@@ -91,6 +91,34 @@ class QueryRMSE(_GroupObjective):
         return math.sqrt(float(((d[0] / w.clamp_min(1e-30)) ** 2 * w).sum().item()) / max(float(w.sum().item()), 1e-300))
 
 
+class GroupQuantile(_GroupObjective):
+    """Quantile loss of the residual left after the weighted mean residual of the document's group is removed
+    (catboost/private/libs/algo_helpers/error_functions.h:935-1000)."""
+    name = "GroupQuantile"
+
+    def _resid(self, approx, target, weight, ctx):
+        lay = _layout(ctx)
+        a = approx[0]
+        w = torch.ones_like(a) if weight is None else weight
+        res = (target - a) * w
+        gsum = torch.zeros(lay.Q, device=a.device).index_add_(0, lay.group_of_row, res)
+        gw = torch.zeros(lay.Q, device=a.device).index_add_(0, lay.group_of_row, w)
+        return target - a - (gsum / gw.clamp_min(1e-30))[lay.group_of_row], w
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        alpha, delta = float(self.params.get("alpha", 0.5)), float(self.params.get("delta", 1e-6))
+        val, w = self._resid(approx, target, weight, ctx)
+        d = torch.where(val > 0, torch.full_like(val, alpha), torch.full_like(val, alpha - 1.0))
+        d = torch.where(val.abs() < delta, torch.zeros_like(d), d) * w
+        return d.unsqueeze(0), w.unsqueeze(0).clone()
+
+    def value(self, approx, target, weight, ctx=None):
+        alpha = float(self.params.get("alpha", 0.5))
+        val, w = self._resid(approx, target, weight, ctx)
+        v = torch.where(val >= 0, alpha * val, (alpha - 1.0) * val) * w
+        return float(v.sum().item()) / max(float(w.sum().item()), 1e-300)
+
+
 class QuerySoftMax(_GroupObjective):
     name = "QuerySoftMax"
 
@@ -343,6 +371,50 @@ class LambdaMart(_GroupObjective):
         return float("nan")
 
 
+class StochasticFilter(_GroupObjective):
+    """Policy gradient for a document filter: every document is kept with probability sigmoid(sigma * approx), the
+    reward of a sampled filter is sum over kept documents of target / (position among the kept ones), and the
+    derivative is the REINFORCE estimate (kept ? 1 - p : -p) * (reward - baseline) averaged over ``num_estimations``
+    samples, with the reward of the deterministic filter approx >= 0 as baseline
+    (catboost/private/libs/algo_helpers/error_functions.h:1226-1320).  Gradient steps only."""
+    name = "StochasticFilter"
+    stochastic = True
+
+    def __init__(self, params=None):
+        super().__init__(params)
+        self.sigma = float(self.params.get("sigma", 1.0))
+        self.num_est = int(self.params.get("num_estimations", 1))
+        if not self.sigma > 0 or self.num_est < 1:
+            raise CatBoostError("StochasticFilter: sigma must be positive and num_estimations a positive integer")
+        self._draws = 0
+
+    @staticmethod
+    def _reward(keep, T):
+        pos = torch.cumsum(keep, 1) - keep                   # kept documents before this one
+        return (keep * T / (pos + 1.0)).sum(1, keepdim=True)
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        lay = _layout(ctx)
+        a, n = approx[0], approx.shape[1]
+        A = lay.gather(a, -1e30)
+        T = lay.gather(target)
+        m = lay.mask.float()
+        base = self._reward((A >= 0).float() * m, T)
+        P = torch.sigmoid(A * self.sigma)
+        gen = torch.Generator(device="cpu")
+        d = torch.zeros_like(A)
+        for _ in range(self.num_est):
+            self._draws += 1
+            gen.manual_seed((int(self.params.get("seed", 0)) * 1000003 + 7919 * self._draws) & 0x7FFFFFFF)
+            u = torch.rand(A.shape, generator=gen).to(A.device)
+            keep = (P >= u).float() * m
+            d += torch.where(keep > 0, 1.0 - P, -P) * (self._reward(keep, T) - base) / self.num_est
+        return lay.scatter(d * m, n).unsqueeze(0), torch.ones((1, n), dtype=a.dtype, device=a.device)
+
+    def value(self, approx, target, weight, ctx=None):
+        return float("nan")
+
+
 class QueryCrossEntropy(_GroupObjective):
     """Logloss with a per-query shift chosen so that the mean predicted probability matches the query's mean target,
     mixed with plain Logloss by ``alpha`` (catboost/cuda/targets/kernel/query_cross_entropy.cu)."""
@@ -384,7 +456,7 @@ class StochasticRank(LambdaMart):
 def make_ranking_objective(loss, params):
     table = {"QueryRMSE": QueryRMSE, "QuerySoftMax": QuerySoftMax, "PairLogit": PairLogit, "PairLogitPairwise": PairLogit,
              "YetiRank": YetiRank, "YetiRankPairwise": YetiRank, "LambdaMart": LambdaMart,
-             "QueryCrossEntropy": QueryCrossEntropy, "StochasticRank": StochasticRank, "StochasticFilter": None}
+             "QueryCrossEntropy": QueryCrossEntropy, "StochasticRank": StochasticRank, "StochasticFilter": StochasticFilter, "GroupQuantile": GroupQuantile}
     cls = table.get(loss)
     if cls is None:
         return None

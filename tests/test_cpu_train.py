@@ -169,7 +169,7 @@ def test_option_handling_eval_fraction_output_borders_and_refusals(tmp_path):
     assert np.allclose(m2.predict(X, prediction_type="RawFormulaVal"), m.predict(X, prediction_type="RawFormulaVal"))
     # options without an implementation are refused when set to something else than their default, hints are accepted
     with pytest.raises(cb.CatBoostError, match="not implemented"):
-        cb.CatBoostClassifier(iterations=2, sampling_frequency="PerTreeLevel", verbose=False, allow_writing_files=False).fit(X, y)
+        cb.CatBoostClassifier(iterations=2, fixed_binary_splits=[0], verbose=False, allow_writing_files=False).fit(X, y)
     cb.CatBoostClassifier(iterations=2, used_ram_limit="4gb", sampling_unit="Object", verbose=False,
                           allow_writing_files=False).fit(X, y)
 

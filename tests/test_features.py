@@ -1207,3 +1207,188 @@ def test_carry_and_uplift():
     assert np.allclose(uplift(m, {"b": (0.0, 1.0)}).predict(X), m.predict(hi) - m.predict(lo), atol=1e-9)
     with pytest.raises(cb.CatBoostError):
         carry(m, {1: [1.0, 2.0], 3: [1.0]})
+
+
+# ---- survival, focal, multi-quantile and group-quantile objectives -----------------------------------------------
+def _autograd_check(obj, approx, target, neg_loglik, tol=2e-4):
+    """der of the objective = -d(loss)/d(approx), hess = d2(loss)/d(approx)^2 on the diagonal."""
+    import torch
+    a = approx.clone().double().requires_grad_(True)
+    loss = neg_loglik(a)
+    g, = torch.autograd.grad(loss, a, create_graph=True)
+    der, hess = obj.der_hess(approx.float().unsqueeze(0), target, None)
+    assert torch.allclose(der[0].double(), -g.detach(), atol=tol, rtol=1e-3)
+    h = torch.stack([torch.autograd.grad(g[i], a, retain_graph=True)[0][i] for i in range(len(a))])
+    assert torch.allclose(hess[0].double(), h.clamp_min(1e-16), atol=tol, rtol=1e-3)
+
+
+def test_focal_derivatives_match_autograd():
+    import torch
+    from catboost_b200.train.objectives import make_objective
+    torch.manual_seed(0)
+    a = torch.randn(40)
+    y = (torch.rand(40) > 0.5).float()
+    obj = make_objective("Focal", {"focal_alpha": 0.3, "focal_gamma": 1.5})
+
+    def loss(x):
+        p = torch.sigmoid(x)
+        pt = torch.where(y > 0.5, p, 1 - p)
+        at = torch.where(y > 0.5, torch.tensor(0.3, dtype=x.dtype), torch.tensor(0.7, dtype=x.dtype))
+        return (-at * (1 - pt) ** 1.5 * torch.log(pt)).sum()
+
+    x = a.clone().double().requires_grad_(True)
+    gr, = torch.autograd.grad(loss(x), x)
+    der, _ = obj.der_hess(a.unsqueeze(0), y, None)
+    assert torch.allclose(der[0].double(), -gr, atol=1e-5)
+
+
+def test_cox_derivatives_match_autograd():
+    import torch
+    from catboost_b200.train.objectives import make_objective
+    torch.manual_seed(1)
+    n = 30
+    a = torch.randn(n)
+    t = (torch.rand(n) * 10 + 0.1) * torch.where(torch.rand(n) < 0.3, -1.0, 1.0)
+    obj = make_objective("Cox", {})
+
+    def nll(x):
+        order = torch.sort(t.abs(), stable=True).indices
+        xs = x[order]
+        lse = torch.flip(torch.logcumsumexp(torch.flip(xs, [0]), 0), [0])
+        return -((xs - lse) * (t[order] > 0).double()).sum()
+
+    _autograd_check(obj, a, t, nll)
+    # the value reported by the objective is the same negative log-likelihood
+    assert abs(obj.value(a.unsqueeze(0), t, None) - float(nll(a.double()))) < 1e-6
+
+
+@pytest.mark.parametrize("dist", ["Normal", "Logistic", "Extreme"])
+def test_survival_aft_derivatives_match_autograd(dist):
+    import torch
+    from catboost_b200.train.objectives import make_objective
+    torch.manual_seed(2)
+    n = 24
+    a = torch.randn(n) * 0.5
+    lo = torch.rand(n) * 3 + 0.2
+    up = lo + torch.rand(n) * 2 + 0.1
+    up[:8] = lo[:8]                      # observed
+    up[8:12] = -1.0                      # right-censored
+    lo[12:16] = -1.0                     # left-censored
+    target = torch.stack([lo, up])
+    s = 0.8
+    obj = make_objective("SurvivalAft", {"dist": dist, "scale": s})
+
+    def cdf(z):
+        if dist == "Normal":
+            return 0.5 + 0.5 * torch.erf(z / 2 ** 0.5)
+        if dist == "Logistic":
+            return torch.sigmoid(z)
+        return 1 - torch.exp(-torch.exp(z))
+
+    def logpdf(z):
+        if dist == "Normal":
+            return -0.5 * z * z
+        if dist == "Logistic":
+            return z - 2 * torch.log1p(torch.exp(z))
+        return z - torch.exp(z)
+
+    def nll(x):
+        lod, upd = lo.double(), up.double()
+        zl = (torch.log(lod.clamp_min(1e-30)) - x) / s
+        zu = (torch.log(upd.clamp_min(1e-30)) - x) / s
+        cu = torch.where(upd == -1, torch.ones_like(x), cdf(zu))
+        cl = torch.where(lod == -1, torch.zeros_like(x), cdf(zl))
+        ll = torch.where(lod == upd, logpdf(zl), torch.log((cu - cl).clamp_min(1e-300)))
+        return -ll.sum()
+
+    _autograd_check(obj, a, target, nll, tol=5e-4)
+
+
+def test_survival_and_quantile_objectives_learn():
+    rng = np.random.default_rng(5)
+    n = 600
+    X = rng.normal(size=(n, 5)).astype(np.float32)
+    risk = X[:, 0] - 0.5 * X[:, 1]
+    # Cox: larger risk -> earlier event; 25 % censored
+    time = rng.exponential(np.exp(-risk)) + 0.01
+    y = np.where(rng.random(n) < 0.25, -time, time).astype(np.float32)
+    m = cb.CatBoostRegressor(iterations=40, depth=3, learning_rate=0.2, loss_function="Cox", verbose=0).fit(X, y)
+    ll = m.evals_result_["learn"]["Cox"]
+    assert ll[-1] > ll[0]                                  # the partial log-likelihood grows
+    assert np.corrcoef(m.predict(X), risk)[0, 1] > 0.7
+    # SurvivalAft: log time = signal + noise, a third right-censored, a third interval-censored
+    t = np.exp(1.0 + 0.8 * X[:, 0] + 0.2 * rng.normal(size=n))
+    lo, up = t.copy(), t.copy()
+    up[: n // 3] = -1
+    lo[: n // 3] *= 0.7
+    lo[n // 3: 2 * n // 3] *= 0.8
+    up[n // 3: 2 * n // 3] *= 1.2
+    ya = np.stack([lo, up], 1).astype(np.float32)
+    m = cb.CatBoostRegressor(iterations=60, depth=3, learning_rate=0.2, loss_function="SurvivalAft:dist=Normal;scale=0.5",
+                             verbose=0).fit(X, ya)
+    v = list(m.evals_result_["learn"].values())[0]
+    assert v[-1] < 0.5 * v[0]
+    assert np.corrcoef(m.predict(X), np.log(t))[0, 1] > 0.9
+    assert np.allclose(m.predict(X, prediction_type="Exponent"), np.exp(m.predict(X)))
+    # MultiQuantile: one column per level, ordered on average, each close to its own coverage
+    yq = (X[:, 0] + rng.normal(size=n)).astype(np.float32)
+    m = cb.CatBoostRegressor(iterations=80, depth=3, learning_rate=0.2, loss_function="MultiQuantile:alpha=0.1,0.5,0.9",
+                             verbose=0).fit(X, yq)
+    pr = m.predict(X)
+    assert pr.shape == (n, 3)
+    cover = [(yq <= pr[:, k]).mean() for k in range(3)]
+    assert abs(cover[0] - 0.1) < 0.06 and abs(cover[1] - 0.5) < 0.08 and abs(cover[2] - 0.9) < 0.06
+    # Focal and GroupQuantile
+    yb = (risk + 0.3 * rng.normal(size=n) > 0).astype(np.float32)
+    m = cb.CatBoostClassifier(iterations=40, depth=3, loss_function="Focal:focal_alpha=0.5;focal_gamma=2", verbose=0).fit(X, yb)
+    assert (m.predict(X).astype(np.float32) == yb).mean() > 0.85
+    assert m.predict_proba(X).shape == (n, 2)
+    gid = np.repeat(np.arange(n // 10), 10)
+    m = cb.CatBoostRanker(iterations=30, depth=3, loss_function="GroupQuantile:alpha=0.5", verbose=0).fit(X, yq, group_id=gid)
+    v = list(m.evals_result_["learn"].values())[0]
+    assert v[-1] < v[0]
+    # StochasticFilter: relevant documents are worth 1, keeping an irrelevant one costs 0.5
+    rel = (X[:, 0] + 0.3 * rng.normal(size=n) > 0.3)
+    yf = np.where(rel, 1.0, -0.5).astype(np.float32)
+    m = cb.CatBoostRanker(iterations=40, depth=3, learning_rate=0.3, verbose=0,
+                          loss_function="StochasticFilter:sigma=1;num_estimations=5").fit(X, yf, group_id=gid)
+    p = m.predict(X)
+    assert (p[rel] > 0).mean() > 0.7 and (p[~rel] > 0).mean() < 0.2
+
+
+def test_feature_penalties_and_per_level_sampling():
+    rng = np.random.default_rng(11)
+    n = 1500
+    X = rng.normal(size=(n, 5)).astype(np.float32)
+    X[:, 1] = X[:, 0] + 0.05 * rng.normal(size=n).astype(np.float32)         # a near copy of feature 0
+    y = (X[:, 0] + 0.5 * X[:, 2] + 0.1 * rng.normal(size=n)).astype(np.float32)
+
+    def used(model):
+        imp = model.get_feature_importance()
+        return set(int(i) for i in np.nonzero(np.asarray(imp) > 0)[0])
+
+    kw = dict(iterations=15, depth=3, learning_rate=0.3, verbose=0, bootstrap_type="No", random_strength=0)
+    base = cb.CatBoostRegressor(**kw).fit(X, y)
+    assert 0 in used(base)
+    # a large first-use penalty on feature 0 sends the trees to its near copy instead
+    pen = cb.CatBoostRegressor(first_feature_use_penalties={0: 1e9}, **kw).fit(X, y)
+    assert 0 not in used(pen) and 1 in used(pen)
+    # the coefficient scales the penalty: zero switches it off again
+    off = cb.CatBoostRegressor(first_feature_use_penalties="0:1e9", penalties_coefficient=0.0, **kw).fit(X, y)
+    assert np.allclose(off.predict(X), base.predict(X))
+    # per-object penalties, symmetric and non-symmetric trees
+    for gp in ("SymmetricTree", "Depthwise", "Lossguide"):
+        m = cb.CatBoostRegressor(per_object_feature_penalties=[1e6, 0, 0, 0, 0], grow_policy=gp, **kw).fit(X, y)
+        assert 0 not in used(m), gp
+    # a small penalty is paid once: after its first use the feature competes without it
+    small = cb.CatBoostRegressor(first_feature_use_penalties={0: 1e-6}, **kw).fit(X, y)
+    assert 0 in used(small)
+    # bootstrap weights redrawn at every level: a different model than one draw per tree, same quality
+    kw2 = dict(iterations=30, depth=4, learning_rate=0.2, verbose=0, bootstrap_type="Bernoulli", subsample=0.5, random_seed=3)
+    a = cb.CatBoostRegressor(**kw2).fit(X, y)
+    for gp in ("SymmetricTree", "Depthwise", "Lossguide"):
+        b = cb.CatBoostRegressor(sampling_frequency="PerTreeLevel", grow_policy=gp, **kw2).fit(X, y)
+        rm = float(np.sqrt(np.mean((b.predict(X) - y) ** 2)))
+        assert rm < 0.35, (gp, rm)
+    b = cb.CatBoostRegressor(sampling_frequency="PerTreeLevel", **kw2).fit(X, y)
+    assert not np.allclose(a.predict(X), b.predict(X))
