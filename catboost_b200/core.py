@@ -53,6 +53,10 @@ class CatBoost:
     def get_params(self, deep=True):
         return copy.deepcopy(self._init_params)
 
+    def get_init_params(self):
+        """The parameters this object was constructed with (before training filled in defaults)."""
+        return copy.deepcopy(self._init_params)
+
     def set_params(self, **params):
         normalize_params(params)
         self._init_params.update(params)
@@ -577,7 +581,7 @@ class CatBoost:
             kw["group_offsets"] = pool.group_offsets()
         if pool.pairs is not None:
             kw["pairs"], kw["pairs_weight"] = pool.pairs, pool.pairs_weight
-        for raw in self._model.staged_raw(fd, ch, ntree_start, ntree_end, eval_period):
+        for raw in self._model.staged_raw(fd, ch, ntree_start, ntree_end, eval_period, at_iterations=True):
             for m in ms:
                 out[str(m)].append(m.eval(raw, y, pool.weight, **kw))
         return out
@@ -882,7 +886,7 @@ class _BatchMetricCalcer:
             raise CatBoostError("add() needs a Pool with labels")
         m = self.model._model
         fd, ch = m.pool_arrays(pool)
-        staged = list(m.staged_raw(fd, ch, self.range[0], self.range[1], self.range[2]))
+        staged = list(m.staged_raw(fd, ch, self.range[0], self.range[1], self.range[2], at_iterations=True))
         if self.stages is None:
             self.stages = [[s.copy()] for s in staged]
         else:

@@ -262,7 +262,11 @@ class Model:
         oc = self._split_outcomes_block(float_data, cat_hashes, self._ctr_values(cat_hashes))
         return np.stack([self.leaf_indices_of_tree(t, oc) for t in self.trees[ntree_start:ntree_end]], axis=1)
 
-    def staged_raw(self, float_data, cat_hashes=None, ntree_start=0, ntree_end=0, eval_period=1):
+    def staged_raw(self, float_data, cat_hashes=None, ntree_start=0, ntree_end=0, eval_period=1, at_iterations=False):
+        """Raw predictions of growing prefixes of the ensemble.  Staged prediction yields after every ``eval_period``
+        trees (and after the last one); metric evaluation (``at_iterations``) yields at the iterations
+        ntree_start, ntree_start + eval_period, ... and the last one, where iteration i is the model of i + 1 trees
+        (catboost/private/libs/algo/plot.cpp)."""
         T = len(self.trees)
         ntree_end = T if ntree_end in (0, None) or ntree_end > T else ntree_end
         oc = self._split_outcomes_block(float_data, cat_hashes, self._ctr_values(cat_hashes))
@@ -270,7 +274,7 @@ class Model:
         bias = np.broadcast_to(self.bias, (self.dims,))
         for k, t in enumerate(self.trees[ntree_start:ntree_end], start=ntree_start):
             acc += t.leaf_values[self.leaf_indices_of_tree(t, oc)]
-            if (k + 1 - ntree_start) % eval_period == 0 or k + 1 == ntree_end:
+            if (k + (0 if at_iterations else 1) - ntree_start) % eval_period == 0 or k + 1 == ntree_end:
                 yield acc * self.scale + bias
 
     # ------------------------------------------------------------------ pool plumbing

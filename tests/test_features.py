@@ -687,7 +687,7 @@ def test_remaining_public_methods(tmp_path):
     assert fig is None and pp[0].shape == (10, nb)
     m2 = cb.CatBoostRegressor(iterations=T, depth=2, verbose=False, allow_writing_files=False).fit(X[:700], y[:700])
     cmp_ = m.compare(m2, cb.Pool(X[700:], y[700:]), ["RMSE"], eval_period=10)
-    assert len(cmp_["RMSE"][0]) == len(cmp_["RMSE"][1]) == (T + 9) // 10
+    assert len(cmp_["RMSE"][0]) == len(cmp_["RMSE"][1]) == len(sorted(set(list(range(0, T, 10)) + [T - 1])))
     calc = m.create_metric_calcer(["RMSE"], eval_period=20)
     calc.add(cb.Pool(X[:400], y[:400]))
     calc.add(cb.Pool(X[400:], y[400:]))
@@ -761,7 +761,7 @@ def test_metric_objects():
     m = cb.CatBoostClassifier(iterations=10, depth=2, verbose=False, allow_writing_files=False, eval_metric=metrics.AUC(),
                               custom_metric=[metrics.Accuracy()], use_best_model=False).fit(X, t, eval_set=(X, t))
     assert list(m.evals_result_["validation"]) == ["AUC", "Accuracy", "Logloss"]
-    assert len(m.eval_metrics(cb.Pool(X, t), [metrics.F1()], eval_period=5)["F1"]) == 2
+    assert len(m.eval_metrics(cb.Pool(X, t), [metrics.F1()], eval_period=5)["F1"]) == 3        # iterations 0, 5, 9
 
 
 def test_public_tokenizer_and_dictionary(tmp_path):
@@ -1392,3 +1392,64 @@ def test_feature_penalties_and_per_level_sampling():
         assert rm < 0.35, (gp, rm)
     b = cb.CatBoostRegressor(sampling_frequency="PerTreeLevel", **kw2).fit(X, y)
     assert not np.allclose(a.predict(X), b.predict(X))
+
+
+def test_eval_package_and_dataset_cache(tmp_path):
+    from catboost_b200 import datasets
+    from catboost_b200.eval import (CatboostEvaluation, EvalType, ExecutionCase, ScoreType, calc_bootstrap_ci_for_mean,
+                                    calc_wilcoxon_test)
+    rng = np.random.default_rng(0)
+    n = 2400
+    X = rng.normal(size=(n, 5)).astype(np.float32)
+    y = (X[:, 0] + 0.7 * X[:, 1] + 0.3 * rng.normal(size=n) > 0).astype(int)
+    # the same data as a file with a column description
+    path, cd = tmp_path / "data.tsv", tmp_path / "cd.tsv"
+    with open(path, "w") as fh:
+        for i in range(n):
+            fh.write(str(y[i]) + "\t" + "\t".join(f"{v:.6g}" for v in X[i]) + "\n")
+    cd.write_text("0\tLabel\n")
+    ev = CatboostEvaluation(str(path), fold_size=400, fold_count=6, column_description=str(cd))
+    params = {"iterations": 20, "depth": 3, "loss_function": "Logloss", "learning_rate": 0.3}
+    res = ev.eval_features(params, [0, 4], eval_type=EvalType.SeqAddAndAll, eval_metrics=["AUC"], eval_step=5)
+    assert set(res.get_metrics()) == {"AUC", "Logloss"}
+    mr = res.get_metric_results("Logloss")
+    assert len(mr.get_fold_ids()) == 6 and len(mr.get_cases()) == 4
+    table = mr.get_baseline_comparison(ScoreType.Rel)
+    # bringing the informative feature back helps by far more than the noise feature
+    assert table.loc["Features: 0", "Score"] > 20 and abs(table.loc["Features: 4", "Score"]) < 5
+    assert table.loc["Features: 0", "PValue"] < 0.05
+    assert res.get_metric_results("AUC").get_baseline_comparison(ScoreType.Abs).loc["Features: 0", "Score"] > 0.05
+    curve = mr.get_case_result(mr.get_baseline_case()).get_fold_curve(0)
+    assert len(curve) == 5                                            # iterations 0, 5, 10, 15 and the last one
+    # two configurations compared directly
+    short = ExecutionCase(dict(params, iterations=5), label="short")
+    long_ = ExecutionCase(dict(params, iterations=40), label="long")
+    cmp_ = ev.eval_cases(short, [long_], ["Logloss"]).get_metric_results("Logloss").get_baseline_comparison()
+    assert cmp_.loc["long", "Score"] > 0
+    with pytest.raises(cb.CatBoostError):
+        ev.eval_cases(short, [short], ["Logloss"])
+    assert calc_wilcoxon_test([1, 2, 3], [1, 2, 3]) == 1.0
+    lo, hi = calc_bootstrap_ci_for_mean(np.array([1.0, 2.0, 3.0, 4.0]))
+    assert 1.0 <= lo <= hi <= 4.0
+    # datasets: read from a local cache, never downloaded
+    datasets.set_cache_path(tmp_path / "cache")
+    with pytest.raises(cb.CatBoostError, match="does not download"):
+        datasets.higgs()
+    d = tmp_path / "cache" / "higgs"
+    d.mkdir(parents=True)
+    block = datasets.synthetic("higgs", rows=50, seed=1)
+    assert block.shape == (50, 29) and set(np.unique(block[:, 0])) <= {0.0, 1.0}
+    for name, part in (("train.tsv", block[:40]), ("test.tsv", block[40:])):
+        with open(d / name, "w") as fh:
+            for row in part:
+                fh.write("\t".join(f"{v:.9g}" for v in row) + "\n")
+    tr, te = datasets.higgs()
+    assert tr.shape == (40, 29) and te.shape == (10, 29) and np.allclose(tr, block[:40], rtol=1e-6)
+    d = tmp_path / "cache" / "titanic"
+    d.mkdir()
+    (d / "train.csv").write_text("PassengerId,Survived,Sex\n1,0,male\n2,1,female\n")
+    (d / "test.csv").write_text("PassengerId,Sex\n3,male\n")
+    tr, te = datasets.titanic()
+    assert list(tr.columns) == ["PassengerId", "Survived", "Sex"] and len(te) == 1
+    m = cb.CatBoostRegressor(iterations=3, depth=2)
+    assert m.get_init_params() == {"iterations": 3, "depth": 2}
