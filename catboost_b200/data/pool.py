@@ -391,6 +391,15 @@ class Pool:
     def get_cat_feature_indices(self):
         return list(self.cat_feature_indices)
 
+    def get_text_feature_indices(self):
+        return list(getattr(self, "text_feature_indices", None) or [])
+
+    def get_embedding_feature_indices(self):
+        return list(getattr(self, "embedding_feature_indices", None) or [])
+
+    def num_pairs(self) -> int:
+        return 0 if self.pairs is None else int(len(self.pairs))
+
     def get_feature_names(self):
         return list(self.feature_names)
 

@@ -95,6 +95,77 @@ def sort_pairs(keys: torch.Tensor):
     return ka, va.long()
 
 
+KNN_TIMEOUT = 0x61
+
+
+def knn_candidates(Q: torch.Tensor, E: torch.Tensor):
+    """Approximate nearest rows of ``E`` for every row of ``Q`` on the tensor cores (ops/cuda/cb_knn_tc.cu: TMA-fed
+    tcgen05 GEMM with the accumulator in TMEM, top-k selection in the epilogue).  Q [nq, d], E [ne, d] float tensors on
+    one CUDA device, d <= cb_knn_max_dim().  Returns (idx int64 [nq, C], score float32 [nq, C]) with
+    score = |e|^2 - 2 q.e computed from bf16-rounded inputs, ascending; C = cb_knn_candidates(); idx is -1 where the
+    cloud has fewer than C rows.  Returns None when the shape does not qualify."""
+    lib = native.cuda_lib()
+    dev = Q.device
+    nq, d = int(Q.shape[0]), int(Q.shape[1])
+    ne = int(E.shape[0])
+    C = int(lib.cb_knn_candidates())
+    if d > int(lib.cb_knn_max_dim()) or nq == 0 or ne == 0 or nq >= (1 << 31) or ne >= (1 << 31):
+        return None
+    dpad = (d + 63) // 64 * 64
+    qb = torch.zeros((nq, dpad), dtype=torch.bfloat16, device=dev)
+    eb = torch.zeros((ne, dpad), dtype=torch.bfloat16, device=dev)
+    qb[:, :d] = Q
+    eb[:, :d] = E
+    e2 = (eb.float() ** 2).sum(1).contiguous()
+    splits = int(lib.cb_knn_splits(nq, ne))
+    out_idx = torch.empty((nq, splits, C), dtype=torch.int32, device=dev)
+    out_val = torch.empty((nq, splits, C), dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    rc = lib.cb_knn_tc(_p(qb), nq, _p(eb), ne, dpad, _p(e2), splits, _p(out_idx), _p(out_val), _p(status), _stream(dev))
+    if rc == -2:
+        return None
+    native.cuda_check(rc, "cb_knn_tc")
+    if int(status.item()) != 0:
+        raise RuntimeError(f"cb_knn_tc: a wait inside the kernel ran out (status {int(status.item()):#x})")
+    val = out_val.reshape(nq, splits * C)
+    idx = out_idx.reshape(nq, splits * C).long()
+    if splits > 1:
+        val, pos = torch.topk(val, C, dim=1, largest=False, sorted=True)
+        idx = idx.gather(1, pos)
+    return idx, val
+
+
+def knn_search(Q: torch.Tensor, E: torch.Tensor, k: int):
+    """Indices [nq, k] of the k nearest rows of ``E`` (Euclidean) for every row of ``Q``: tensor-core candidates
+    re-ranked by fp32 distances.  Falls back to a chunked fp32 distance matrix (library GEMM) when the shape does not
+    qualify for the tensor-core kernel (more than cb_knn_max_dim() dimensions, k above half the candidate count)."""
+    k = min(int(k), int(E.shape[0]))
+    cand = None
+    if Q.is_cuda and 2 * k <= int(native.cuda_lib().cb_knn_candidates()):
+        cand = knn_candidates(Q, E)
+    if cand is not None:
+        idx, _ = cand
+        Qf, Ef = Q.float(), E.float()
+        out = torch.empty((Q.shape[0], k), dtype=torch.long, device=Q.device)
+        step = max(1, (64 << 20) // max(1, idx.shape[1] * Ef.shape[1] * 4))
+        for s in range(0, Q.shape[0], step):
+            ii = idx[s:s + step]
+            g = Ef[ii.clamp_min(0)]                                    # [b, C, d]
+            d2 = ((g - Qf[s:s + step].unsqueeze(1)) ** 2).sum(2)
+            d2 = torch.where(ii >= 0, d2, torch.full_like(d2, float("inf")))
+            pos = torch.topk(d2, k, dim=1, largest=False, sorted=True).indices
+            out[s:s + step] = ii.gather(1, pos)
+        return out
+    Qf, Ef = Q.float(), E.float()
+    e2 = (Ef * Ef).sum(1)
+    out = torch.empty((Q.shape[0], k), dtype=torch.long, device=Q.device)
+    step = max(1, (256 << 20) // max(1, Ef.shape[0] * 4))
+    for s in range(0, Q.shape[0], step):
+        d2 = e2.unsqueeze(0) - 2.0 * Qf[s:s + step] @ Ef.t()
+        out[s:s + step] = torch.topk(d2, k, dim=1, largest=False, sorted=True).indices
+    return out
+
+
 _LEAF_NEWTON_STATE = {}
 
 

@@ -1,0 +1,313 @@
+// Nearest-neighbour candidates for embedding features: distance GEMM on the 5th-generation tensor cores fused with the
+// top-k selection, so the [queries x cloud] distance matrix never exists in memory.
+//
+// What it computes (the estimator it serves: catboost/private/libs/embedding_features/knn.cpp, class votes of the k
+// nearest learn documents): for every query row q and every cloud row e, s(q, e) = |e|^2 - 2 q.e, which orders the cloud
+// rows exactly like the Euclidean distance does; the CB_KNN_CAND smallest s per query come back with their indices.
+// Inputs are bf16 (fp32 accumulation), so the order is approximate among near ties: the caller re-ranks the candidates
+// with fp32 distances and keeps k <= CB_KNN_CAND / 2 of them.
+//
+// Structure of a CTA (256 threads, one tile of 128 queries, a range of 128-row cloud tiles):
+//   warp 0   producer: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) loads the query tile once -- all K chunks stay
+//            in shared memory -- and streams the cloud tiles through a 4-stage ring of [128 rows x 64 bf16] boxes;
+//   warp 1   one elected lane issues tcgen05.mma (M = N = 128, K = 16, operands from shared memory through matrix
+//            descriptors, accumulator in TMEM), tcgen05.commit releases the ring stage / publishes the accumulator;
+//   warp 2   allocates and frees 256 TMEM columns: two accumulators, so tile i + 1 is multiplied while tile i is read;
+//   warps 4-7 epilogue: thread = query row = TMEM lane; tcgen05.ld brings 32 columns at a time into registers, each
+//            value goes through s = |e|^2 - 2 acc and a sorted insertion into the thread's candidate list.
+// Every mbarrier wait is bounded; when one runs out the CTA records CB_KNN_TIMEOUT in *status, every role leaves its
+// loop, the CTA idles long enough for copies and MMAs in flight to land, frees its TMEM and returns.
+#include "cb_common.cuh"
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#define CB_KNN_CAND 16
+#define CB_KNN_TM 128                 // queries per CTA (MMA M)
+#define CB_KNN_TN 128                 // cloud rows per tile (MMA N)
+#define CB_KNN_KC 64                  // bf16 per K chunk = one 128-byte swizzled row
+#define CB_KNN_STAGES 4
+#define CB_KNN_MAX_KCHUNKS 6          // query tile resident in shared memory: up to 384 dimensions
+#define CB_KNN_TILE_BYTES (CB_KNN_TN * CB_KNN_KC * 2)
+#define CB_KNN_TIMEOUT 0x61
+#define CB_KNN_WAIT_LIMIT (1 << 22)
+
+__device__ __forceinline__ unsigned int cbk_smem_u32(const void* p) { return (unsigned int)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool cbk_wait(unsigned int bar, unsigned int parity) {
+    for (int it = 0; it < CB_KNN_WAIT_LIMIT; ++it) {
+        unsigned int ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the 128-byte swizzle: groups
+// of 8 rows lie 1024 bytes apart (stride byte offset), the leading byte offset is not used by swizzled K-major layouts
+// (1 by convention), descriptor version 1, layout type 2 = SWIZZLE_128B.  Addresses and offsets are in 16-byte units.
+__device__ __forceinline__ unsigned long long cbk_desc(unsigned int smem_addr) {
+    return (unsigned long long)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor: D = fp32 (bits 4-5 = 1), A = B = bf16 (bits 7-9 and 10-12 = 1), both K-major, N / 8 at bit 17,
+// M / 16 at bit 24.
+#define CB_KNN_IDESC ((1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(CB_KNN_TN >> 3) << 17) | ((unsigned)(CB_KNN_TM >> 4) << 24))
+
+struct CbKnnArgs {
+    const float* e2;          // [ne] squared norms of the (bf16-rounded) cloud rows
+    int nq, ne, kchunks;
+    int tiles_per_split;      // cloud tiles handled by one blockIdx.y
+    int* out_idx;             // [nq][splits][CB_KNN_CAND]
+    float* out_val;
+    int* status;
+};
+
+__global__ void __launch_bounds__(256, 1) cb_knn_tc_kernel(const __grid_constant__ CUtensorMap tmq,
+                                                           const __grid_constant__ CUtensorMap tme, CbKnnArgs a) {
+    extern __shared__ unsigned char cbk_raw[];
+    unsigned char* smem = cbk_raw + ((1024u - (cbk_smem_u32(cbk_raw) & 1023u)) & 1023u);
+    // [kchunks] query chunks | [STAGES] cloud chunks | barriers | tmem base
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + CB_KNN_MAX_KCHUNKS * CB_KNN_TILE_BYTES;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sB + CB_KNN_STAGES * CB_KNN_TILE_BYTES);
+    // bars: full[STAGES] | empty[STAGES] | a_full | tmem_full[2] | tmem_empty[2]
+    const unsigned int bar_full = cbk_smem_u32(bars), bar_empty = cbk_smem_u32(bars + CB_KNN_STAGES);
+    const unsigned int bar_a = cbk_smem_u32(bars + 2 * CB_KNN_STAGES);
+    const unsigned int bar_tfull = cbk_smem_u32(bars + 2 * CB_KNN_STAGES + 1);
+    const unsigned int bar_tempty = cbk_smem_u32(bars + 2 * CB_KNN_STAGES + 3);
+    unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(bars + 2 * CB_KNN_STAGES + 5);
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ntiles_all = (a.ne + CB_KNN_TN - 1) / CB_KNN_TN;
+    const int t0 = blockIdx.y * a.tiles_per_split;
+    const int t1 = min(ntiles_all, t0 + a.tiles_per_split);
+    const int ntiles = max(0, t1 - t0);
+    const int kch = a.kchunks;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < CB_KNN_STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_full + 8 * s) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_empty + 8 * s) : "memory");
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a) : "memory");
+        for (int b = 0; b < 2; ++b) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_tfull + 8 * b) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(bar_tempty + 8 * b) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(cbk_smem_u32(tmem_slot)), "r"(256)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned int tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- producer ----------------------------------------------------------------------------------------
+        if (lane == 0 && ntiles > 0) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(kch * CB_KNN_TILE_BYTES) : "memory");
+            for (int kc = 0; kc < kch; ++kc)
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(cbk_smem_u32(sA + kc * CB_KNN_TILE_BYTES)), "l"(&tmq), "r"(kc * CB_KNN_KC),
+                               "r"((int)(blockIdx.x * CB_KNN_TM)), "r"(bar_a) : "memory");
+            int it = 0;
+            bool ok = true;
+            for (int t = 0; t < ntiles && ok; ++t) {
+                for (int kc = 0; kc < kch; ++kc, ++it) {
+                    const int s = it % CB_KNN_STAGES;
+                    const unsigned int ph = (unsigned)(it / CB_KNN_STAGES) & 1u;
+                    if (*(volatile int*)&s_abort || !cbk_wait(bar_empty + 8 * s, ph ^ 1u)) { ok = false; break; }
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_full + 8 * s), "r"(CB_KNN_TILE_BYTES) : "memory");
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                 ::"r"(cbk_smem_u32(sB + s * CB_KNN_TILE_BYTES)), "l"(&tme), "r"(kc * CB_KNN_KC),
+                                   "r"((t0 + t) * CB_KNN_TN), "r"(bar_full + 8 * s) : "memory");
+                }
+            }
+            if (!ok) { atomicExch(a.status, CB_KNN_TIMEOUT); *(volatile int*)&s_abort = 1; }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----------------------------------------------------------------------------------------
+        if (lane == 0 && ntiles > 0) {
+            bool ok = cbk_wait(bar_a, 0u);
+            int it = 0;
+            for (int t = 0; t < ntiles && ok; ++t) {
+                const int buf = t & 1;
+                const unsigned int tph = (unsigned)(t >> 1) & 1u;
+                if (*(volatile int*)&s_abort || !cbk_wait(bar_tempty + 8 * buf, tph ^ 1u)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned int dcol = tmem_base + (unsigned)buf * CB_KNN_TN;
+                for (int kc = 0; kc < kch; ++kc, ++it) {
+                    const int s = it % CB_KNN_STAGES;
+                    const unsigned int ph = (unsigned)(it / CB_KNN_STAGES) & 1u;
+                    if (!cbk_wait(bar_full + 8 * s, ph)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned long long da = cbk_desc(cbk_smem_u32(sA + kc * CB_KNN_TILE_BYTES));
+                    const unsigned long long db = cbk_desc(cbk_smem_u32(sB + s * CB_KNN_TILE_BYTES));
+#pragma unroll
+                    for (int k = 0; k < CB_KNN_KC / 16; ++k) {
+                        const unsigned int acc = (kc | k) ? 1u : 0u;
+                        // 16 bf16 = 32 bytes = 2 descriptor units further along the swizzled row
+                        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                                     ::"r"(dcol), "l"(da + 2ull * k), "l"(db + 2ull * k), "r"(CB_KNN_IDESC), "r"(acc) : "memory");
+                    }
+                    // the stage may be refilled once these MMAs have read it
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_empty + 8 * s) : "memory");
+                }
+                if (ok)
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_tfull + 8 * buf) : "memory");
+            }
+            if (!ok) { atomicExch(a.status, CB_KNN_TIMEOUT); *(volatile int*)&s_abort = 1; }
+        }
+    } else if (warp >= 4) {
+        // ---- epilogue ------------------------------------------------------------------------------------------
+        const int wq = warp & 3;                                  // TMEM lanes 32 wq .. 32 wq + 31 belong to this warp
+        const int row = blockIdx.x * CB_KNN_TM + wq * 32 + lane;
+        float val[CB_KNN_CAND];
+        int idx[CB_KNN_CAND];
+#pragma unroll
+        for (int c = 0; c < CB_KNN_CAND; ++c) { val[c] = 3.0e38f; idx[c] = -1; }
+        bool ok = true;
+        for (int t = 0; t < ntiles && ok; ++t) {
+            const int buf = t & 1;
+            const unsigned int tph = (unsigned)(t >> 1) & 1u;
+            if (*(volatile int*)&s_abort || !cbk_wait(bar_tfull + 8 * buf, tph)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int col0 = (t0 + t) * CB_KNN_TN;
+#pragma unroll 1
+            for (int c = 0; c < CB_KNN_TN / 32; ++c) {
+                unsigned int r[32];
+                const unsigned int taddr = tmem_base + ((unsigned)(wq * 32) << 16) + (unsigned)(buf * CB_KNN_TN + c * 32);
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                               "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                               "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                             : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int cb = col0 + c * 32;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int col = cb + j;
+                    if (col < a.ne) {
+                        const float s = __ldg(a.e2 + col) - 2.0f * __uint_as_float(r[j]);
+                        if (s < val[CB_KNN_CAND - 1]) {
+                            val[CB_KNN_CAND - 1] = s;
+                            idx[CB_KNN_CAND - 1] = col;
+#pragma unroll
+                            for (int q = CB_KNN_CAND - 1; q > 0; --q) {
+                                if (val[q] < val[q - 1]) {
+                                    const float tv = val[q]; val[q] = val[q - 1]; val[q - 1] = tv;
+                                    const int ti = idx[q]; idx[q] = idx[q - 1]; idx[q - 1] = ti;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            // this accumulator may be overwritten by the tile after the next one
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_tempty + 8 * buf) : "memory");
+        }
+        if (!ok) { atomicExch(a.status, CB_KNN_TIMEOUT); *(volatile int*)&s_abort = 1; }
+        if (row < a.nq) {
+            const long long o = ((long long)row * gridDim.y + blockIdx.y) * CB_KNN_CAND;
+#pragma unroll
+            for (int c = 0; c < CB_KNN_CAND; ++c) { a.out_val[o + c] = val[c]; a.out_idx[o + c] = idx[c]; }
+        }
+    }
+    __syncthreads();
+    if (*(volatile int*)&s_abort) {
+        // copies and MMAs that were issued before a wait ran out get time to land before the CTA's memory is given back
+        for (int w = 0; w < 200; ++w) __nanosleep(1000);
+        __syncthreads();
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (warp == 2)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
+}
+
+typedef CUresult (*CbkEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static CbkEncodeTiled cbk_encode_tiled() {
+    static CbkEncodeTiled fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<CbkEncodeTiled>(p);
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+static int cbk_make_map(CUtensorMap* tm, const void* base, long long rows, int dpad) {
+    CbkEncodeTiled enc = cbk_encode_tiled();
+    if (!enc) return -2;
+    const cuuint64_t gdim[2] = {(cuuint64_t)dpad, (cuuint64_t)rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)dpad * 2};
+    const cuuint32_t box[2] = {CB_KNN_KC, CB_KNN_TN};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+CB_API int cb_knn_candidates(void) { return CB_KNN_CAND; }
+CB_API int cb_knn_max_dim(void) { return CB_KNN_MAX_KCHUNKS * CB_KNN_KC; }
+
+// Number of cloud ranges (blockIdx.y) that fills the device about once without making a range shorter than 4 tiles.
+CB_API int cb_knn_splits(int nq, int ne) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    const int qt = (nq + CB_KNN_TM - 1) / CB_KNN_TM, et = (ne + CB_KNN_TN - 1) / CB_KNN_TN;
+    int s = (sms + qt - 1) / (qt > 0 ? qt : 1);
+    if (s > et / 4) s = et / 4;
+    if (s < 1) s = 1;
+    if (s > 64) s = 64;
+    return s;
+}
+
+// Q [nq][dpad] and E [ne][dpad] are bf16, row-major, 16-byte aligned, dpad a multiple of 64 and at most
+// cb_knn_max_dim(); e2 [ne] fp32.  out_idx / out_val are [nq][splits][CB_KNN_CAND]; entries that were never filled hold
+// index -1.  Returns 0 when the kernel was enqueued, -2 when the shape does not qualify, a CUDA error code otherwise.
+// *status (device int, zero on entry) receives CB_KNN_TIMEOUT when a wait inside the kernel ran out.
+CB_API int cb_knn_tc(const void* Q, int nq, const void* E, int ne, int dpad, const float* e2, int splits, int* out_idx,
+                     float* out_val, int* status, cudaStream_t st) {
+    if (nq <= 0 || ne <= 0) return 0;
+    if (dpad <= 0 || dpad % CB_KNN_KC != 0 || dpad > CB_KNN_MAX_KCHUNKS * CB_KNN_KC || splits < 1 || splits > 65535) return -2;
+    if ((reinterpret_cast<unsigned long long>(Q) & 15ull) || (reinterpret_cast<unsigned long long>(E) & 15ull)) return -2;
+    CUtensorMap tmq, tme;
+    if (cbk_make_map(&tmq, Q, nq, dpad) != 0 || cbk_make_map(&tme, E, ne, dpad) != 0) return -2;
+    const int smem = 1024 + (CB_KNN_MAX_KCHUNKS + CB_KNN_STAGES) * CB_KNN_TILE_BYTES + 16 * 8;
+    static unsigned long long set = 0ull;
+    if (cb_first_on_device(&set)) {
+        cudaError_t e = cudaFuncSetAttribute(cb_knn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
+    }
+    const int et = (ne + CB_KNN_TN - 1) / CB_KNN_TN;
+    CbKnnArgs a{e2, nq, ne, dpad / CB_KNN_KC, (et + splits - 1) / splits, out_idx, out_val, status};
+    dim3 grid((unsigned)((nq + CB_KNN_TM - 1) / CB_KNN_TM), (unsigned)splits);
+    cb_knn_tc_kernel<<<grid, 256, smem, st>>>(tmq, tme, a);
+    const cudaError_t le = cudaGetLastError();
+    return le == cudaSuccess ? 0 : (int)le;
+}

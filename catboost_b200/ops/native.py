@@ -23,7 +23,8 @@ from pathlib import Path
 _HERE = Path(__file__).resolve().parent
 CUDA_SRC = [_HERE / "cuda" / "cb_kernels.cu", _HERE / "cuda" / "cb_fused.cu", _HERE / "cuda" / "cb_leaf.cu",
             _HERE / "cuda" / "cb_quantize_tma.cu", _HERE / "cuda" / "cb_ranking.cu", _HERE / "cuda" / "cb_ctr.cu",
-            _HERE / "cuda" / "cb_multiclass.cu", _HERE / "cuda" / "cb_search.cu", _HERE / "cuda" / "cb_pairwise.cu", _HERE / "cuda" / "cb_sort.cu", _HERE / "cuda" / "cb_mvs.cu", _HERE / "cuda" / "cb_predict_wide.cu", _HERE / "cuda" / "cb_querywise.cu"]
+            _HERE / "cuda" / "cb_multiclass.cu", _HERE / "cuda" / "cb_search.cu", _HERE / "cuda" / "cb_pairwise.cu", _HERE / "cuda" / "cb_sort.cu", _HERE / "cuda" / "cb_mvs.cu", _HERE / "cuda" / "cb_predict_wide.cu", _HERE / "cuda" / "cb_querywise.cu",
+            _HERE / "cuda" / "cb_knn_tc.cu"]
 CUDA_HDR = sorted((_HERE / "cuda").glob("*.cuh")) + sorted((_HERE / "cuda").glob("*.h"))
 CPU_SRC = [_HERE / "cpu" / "cb_cpu.cpp", _HERE / "cpu" / "cb_cityhash.h"]
 MODEL_SRC = [_HERE / "cpu" / "cb_model_capi.cpp", _HERE / "cpu" / "cb_model_capi.h", _HERE / "cpu" / "cb_cityhash.h"]
@@ -206,6 +207,10 @@ _SIGS = {
     "cb_pair_logit_pairs_der": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p]),
     "cb_pair_logit_labels_der": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p]),
     "cb_pair_metric": (c_int, [c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_void_p, c_void_p]),
+    "cb_knn_candidates": (c_int, []),
+    "cb_knn_max_dim": (c_int, []),
+    "cb_knn_splits": (c_int, [c_int, c_int]),
+    "cb_knn_tc": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_mvs_block_docs": (c_int, []),
     "cb_mvs_sample": (c_int, [c_void_p, c_ll, c_ll, c_float, c_float, c_ull, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_mc_max_classes": (c_int, []),

@@ -804,3 +804,45 @@ def test_leaf_kernel_in_the_general_learner_matches_tensor_code(policy, loss):
             G.USE_LEAF_KERNEL = True
         preds[use] = m.predict(X, prediction_type="RawFormulaVal")
     assert np.allclose(preds[True], preds[False], rtol=2e-3, atol=2e-3), float(np.abs(preds[True] - preds[False]).max())
+
+
+@pytest.mark.parametrize("nq,ne,d", [(300, 1000, 96), (130, 129, 200), (256, 40000, 64), (1000, 5000, 384)])
+def test_knn_tensor_core_candidates_match_fp32_reference(nq, ne, d):
+    """tcgen05 distance GEMM + top-k epilogue against a plain fp32 computation on the same bf16-rounded inputs."""
+    from catboost_b200.ops import api as ops
+    g = torch.Generator(device="cpu").manual_seed(nq + ne + d)
+    Q = torch.randn((nq, d), generator=g).cuda()
+    E = torch.randn((ne, d), generator=g).cuda()
+    out = ops.knn_candidates(Q, E)
+    assert out is not None
+    idx, val = out
+    C = idx.shape[1]
+    qb, eb = Q.bfloat16().float(), E.bfloat16().float()
+    ref = (eb * eb).sum(1).unsqueeze(0) - 2.0 * qb @ eb.t()
+    rv, ri = torch.topk(ref, min(C, ne), dim=1, largest=False, sorted=True)
+    m = min(C, ne)
+    assert bool((idx[:, :m] >= 0).all()) and (m == C or bool((idx[:, m:] == -1).all()))
+    assert torch.allclose(val[:, :m], rv, atol=2e-3 * d ** 0.5, rtol=1e-4)
+    # the same rows are selected; rows whose scores tie within rounding may swap places
+    same = (idx[:, :m] == ri).float().mean().item()
+    assert same > 0.99, same
+    # the score reported for a candidate is the score of that candidate
+    assert torch.allclose(val[:, :m], ref.gather(1, idx[:, :m]), atol=2e-3 * d ** 0.5, rtol=1e-4)
+    # end to end: candidates re-ranked in fp32 against the exact neighbours
+    k = 5
+    got = ops.knn_search(Q, E, k)
+    d2 = torch.cdist(Q, E)
+    want = torch.topk(d2, k, dim=1, largest=False, sorted=True).indices
+    recall = np.mean([len(set(a.tolist()) & set(b.tolist())) / k for a, b in zip(got.cpu(), want.cpu())])
+    assert recall > 0.995, recall
+
+
+def test_knn_search_falls_back_for_wide_embeddings():
+    from catboost_b200.ops import api as ops
+    g = torch.Generator(device="cpu").manual_seed(3)
+    Q = torch.randn((50, 500), generator=g).cuda()
+    E = torch.randn((400, 500), generator=g).cuda()
+    assert ops.knn_candidates(Q, E) is None                       # more dimensions than the resident query tile holds
+    got = ops.knn_search(Q, E, 3)
+    want = torch.topk(torch.cdist(Q, E), 3, dim=1, largest=False).indices
+    assert (got.sort(1).values == want.sort(1).values).float().mean().item() > 0.99
