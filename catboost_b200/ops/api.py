@@ -118,8 +118,9 @@ def knn_candidates(Q: torch.Tensor, E: torch.Tensor):
     eb[:, :d] = E
     e2 = (eb.float() ** 2).sum(1).contiguous()
     splits = int(lib.cb_knn_splits(nq, ne))
-    out_idx = torch.empty((nq, splits, C), dtype=torch.int32, device=dev)
-    out_val = torch.empty((nq, splits, C), dtype=torch.float32, device=dev)
+    lists = 2 * splits                       # the kernel keeps one list per column half of a cloud tile
+    out_idx = torch.empty((nq, lists, C), dtype=torch.int32, device=dev)
+    out_val = torch.empty((nq, lists, C), dtype=torch.float32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     rc = lib.cb_knn_tc(_p(qb), nq, _p(eb), ne, dpad, _p(e2), splits, _p(out_idx), _p(out_val), _p(status), _stream(dev))
     if rc == -2:
@@ -127,12 +128,10 @@ def knn_candidates(Q: torch.Tensor, E: torch.Tensor):
     native.cuda_check(rc, "cb_knn_tc")
     if int(status.item()) != 0:
         raise RuntimeError(f"cb_knn_tc: a wait inside the kernel ran out (status {int(status.item()):#x})")
-    val = out_val.reshape(nq, splits * C)
-    idx = out_idx.reshape(nq, splits * C).long()
-    if splits > 1:
-        val, pos = torch.topk(val, C, dim=1, largest=False, sorted=True)
-        idx = idx.gather(1, pos)
-    return idx, val
+    val = out_val.reshape(nq, lists * C)
+    idx = out_idx.reshape(nq, lists * C).long()
+    val, pos = torch.topk(val, C, dim=1, largest=False, sorted=True)
+    return idx.gather(1, pos), val
 
 
 def knn_search(Q: torch.Tensor, E: torch.Tensor, k: int):

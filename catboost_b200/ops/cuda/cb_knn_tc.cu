@@ -7,14 +7,16 @@
 // Inputs are bf16 (fp32 accumulation), so the order is approximate among near ties: the caller re-ranks the candidates
 // with fp32 distances and keeps k <= CB_KNN_CAND / 2 of them.
 //
-// Structure of a CTA (256 threads, one tile of 128 queries, a range of 128-row cloud tiles):
+// Structure of a CTA (384 threads, one tile of 128 queries, a range of 128-row cloud tiles):
 //   warp 0   producer: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) loads the query tile once -- all K chunks stay
 //            in shared memory -- and streams the cloud tiles through a 4-stage ring of [128 rows x 64 bf16] boxes;
 //   warp 1   one elected lane issues tcgen05.mma (M = N = 128, K = 16, operands from shared memory through matrix
 //            descriptors, accumulator in TMEM), tcgen05.commit releases the ring stage / publishes the accumulator;
 //   warp 2   allocates and frees 256 TMEM columns: two accumulators, so tile i + 1 is multiplied while tile i is read;
-//   warps 4-7 epilogue: thread = query row = TMEM lane; tcgen05.ld brings 32 columns at a time into registers, each
-//            value goes through s = |e|^2 - 2 acc and a sorted insertion into the thread's candidate list.
+//   warps 4-11 epilogue: thread = query row = TMEM lane, two warps per lane quarter (64 columns of the tile each);
+//            tcgen05.ld brings the 64 columns into registers, the TMEM buffer is handed back at once, then
+//            s = |e|^2 - 2 acc (|e|^2 from shared memory), the minimum of every 32 scores by a tree of minima, and a
+//            sorted insertion into the thread's candidate list only for groups that hold something below its worst entry.
 // Every mbarrier wait is bounded; when one runs out the CTA records CB_KNN_TIMEOUT in *status, every role leaves its
 // loop, the CTA idles long enough for copies and MMAs in flight to land, frees its TMEM and returns.
 #include "cb_common.cuh"
@@ -30,6 +32,7 @@
 #define CB_KNN_TILE_BYTES (CB_KNN_TN * CB_KNN_KC * 2)
 #define CB_KNN_TIMEOUT 0x61
 #define CB_KNN_WAIT_LIMIT (1 << 22)
+#define CB_KNN_THREADS 384             // 4 role warps + 8 epilogue warps
 
 __device__ __forceinline__ unsigned int cbk_smem_u32(const void* p) { return (unsigned int)__cvta_generic_to_shared(p); }
 
@@ -58,12 +61,12 @@ struct CbKnnArgs {
     const float* e2;          // [ne] squared norms of the (bf16-rounded) cloud rows
     int nq, ne, kchunks;
     int tiles_per_split;      // cloud tiles handled by one blockIdx.y
-    int* out_idx;             // [nq][splits][CB_KNN_CAND]
+    int* out_idx;             // [nq][2 * splits][CB_KNN_CAND]
     float* out_val;
     int* status;
 };
 
-__global__ void __launch_bounds__(256, 1) cb_knn_tc_kernel(const __grid_constant__ CUtensorMap tmq,
+__global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __grid_constant__ CUtensorMap tmq,
                                                            const __grid_constant__ CUtensorMap tme, CbKnnArgs a) {
     extern __shared__ unsigned char cbk_raw[];
     unsigned char* smem = cbk_raw + ((1024u - (cbk_smem_u32(cbk_raw) & 1023u)) & 1023u);
@@ -78,6 +81,7 @@ __global__ void __launch_bounds__(256, 1) cb_knn_tc_kernel(const __grid_constant
     const unsigned int bar_tempty = cbk_smem_u32(bars + 2 * CB_KNN_STAGES + 3);
     unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(bars + 2 * CB_KNN_STAGES + 5);
     __shared__ int s_abort;
+    __shared__ __align__(16) float s_e2[8][64];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntiles_all = (a.ne + CB_KNN_TN - 1) / CB_KNN_TN;
@@ -95,7 +99,7 @@ __global__ void __launch_bounds__(256, 1) cb_knn_tc_kernel(const __grid_constant
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a) : "memory");
         for (int b = 0; b < 2; ++b) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_tfull + 8 * b) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(bar_tempty + 8 * b) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;" ::"r"(bar_tempty + 8 * b) : "memory");
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -167,61 +171,106 @@ __global__ void __launch_bounds__(256, 1) cb_knn_tc_kernel(const __grid_constant
             if (!ok) { atomicExch(a.status, CB_KNN_TIMEOUT); *(volatile int*)&s_abort = 1; }
         }
     } else if (warp >= 4) {
-        // ---- epilogue ------------------------------------------------------------------------------------------
-        const int wq = warp & 3;                                  // TMEM lanes 32 wq .. 32 wq + 31 belong to this warp
+        // ---- epilogue: 8 warps, warp quarter = TMEM lanes (a warp may only read lanes 32 (warp % 4) ...), warp half =
+        // columns 0-63 or 64-127 of the tile; a query row therefore has two candidate lists, merged by the caller ------
+        const int ew = warp - 4, wq = ew & 3, half = ew >> 2;
         const int row = blockIdx.x * CB_KNN_TM + wq * 32 + lane;
         float val[CB_KNN_CAND];
         int idx[CB_KNN_CAND];
 #pragma unroll
         for (int c = 0; c < CB_KNN_CAND; ++c) { val[c] = 3.0e38f; idx[c] = -1; }
         bool ok = true;
+        // |e|^2 of the warp's 64 columns goes through the warp's own piece of shared memory (broadcast reads; no barrier
+        // between warps, so a warp that gives up on a wait cannot leave the others stuck).  Columns past the end of the
+        // cloud get a huge norm and never enter a list.  The values of the next tile are fetched while this one is processed.
+        float* my_e2 = s_e2[ew];
+        float e2a = 3.0e38f, e2b = 3.0e38f;
+        if (ntiles > 0) {
+            const int col = t0 * CB_KNN_TN + half * 64 + lane;
+            if (col < a.ne) e2a = __ldg(a.e2 + col);
+            if (col + 32 < a.ne) e2b = __ldg(a.e2 + col + 32);
+        }
         for (int t = 0; t < ntiles && ok; ++t) {
             const int buf = t & 1;
             const unsigned int tph = (unsigned)(t >> 1) & 1u;
-            if (*(volatile int*)&s_abort || !cbk_wait(bar_tfull + 8 * buf, tph)) { ok = false; break; }
+            __syncwarp();                                          // the previous tile's reads are done
+            my_e2[lane] = e2a;
+            my_e2[lane + 32] = e2b;
+            __syncwarp();
+            e2a = 3.0e38f; e2b = 3.0e38f;
+            if (t + 1 < ntiles) {
+                const int col = (t0 + t + 1) * CB_KNN_TN + half * 64 + lane;
+                if (col < a.ne) e2a = __ldg(a.e2 + col);
+                if (col + 32 < a.ne) e2b = __ldg(a.e2 + col + 32);
+            }
+            // the verdict of the wait is taken by the whole warp: the votes further down need all 32 lanes
+            const bool arrived = !(*(volatile int*)&s_abort) && cbk_wait(bar_tfull + 8 * buf, tph);
+            if (!__all_sync(0xffffffffu, arrived)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int col0 = (t0 + t) * CB_KNN_TN;
-#pragma unroll 1
-            for (int c = 0; c < CB_KNN_TN / 32; ++c) {
-                unsigned int r[32];
-                const unsigned int taddr = tmem_base + ((unsigned)(wq * 32) << 16) + (unsigned)(buf * CB_KNN_TN + c * 32);
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                               "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                               "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                             : "r"(taddr) : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int cb = col0 + c * 32;
+            unsigned int r[64];
+            const unsigned int taddr = tmem_base + ((unsigned)(wq * 32) << 16) + (unsigned)(buf * CB_KNN_TN + half * 64);
+#define CBK_LD32(R, ADDR)                                                                                                  \
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                         \
+                         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                         \
+                         "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"          \
+                         : "=r"(R[0]), "=r"(R[1]), "=r"(R[2]), "=r"(R[3]), "=r"(R[4]), "=r"(R[5]), "=r"(R[6]), "=r"(R[7]), \
+                           "=r"(R[8]), "=r"(R[9]), "=r"(R[10]), "=r"(R[11]), "=r"(R[12]), "=r"(R[13]), "=r"(R[14]),        \
+                           "=r"(R[15]), "=r"(R[16]), "=r"(R[17]), "=r"(R[18]), "=r"(R[19]), "=r"(R[20]), "=r"(R[21]),      \
+                           "=r"(R[22]), "=r"(R[23]), "=r"(R[24]), "=r"(R[25]), "=r"(R[26]), "=r"(R[27]), "=r"(R[28]),      \
+                           "=r"(R[29]), "=r"(R[30]), "=r"(R[31])                                                           \
+                         : "r"(ADDR) : "memory")
+            CBK_LD32((r), taddr);
+            CBK_LD32((r + 32), taddr + 32u);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // the accumulator is in registers now: hand the TMEM buffer back before the selection work
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_tempty + 8 * buf) : "memory");
+            const int cbase = (t0 + t) * CB_KNN_TN + half * 64;
+            const float4* e4 = reinterpret_cast<const float4*>(my_e2);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int col = cb + j;
-                    if (col < a.ne) {
-                        const float s = __ldg(a.e2 + col) - 2.0f * __uint_as_float(r[j]);
-                        if (s < val[CB_KNN_CAND - 1]) {
-                            val[CB_KNN_CAND - 1] = s;
-                            idx[CB_KNN_CAND - 1] = col;
+            for (int c = 0; c < 2; ++c) {
+                float sc[32];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 e = e4[c * 8 + j];
+                    sc[4 * j + 0] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 0]), e.x);
+                    sc[4 * j + 1] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 1]), e.y);
+                    sc[4 * j + 2] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 2]), e.z);
+                    sc[4 * j + 3] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 3]), e.w);
+                }
+                // smallest score of the 32 by a tree of minima: most groups hold nothing below the list's worst entry
+                float m[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) m[j] = fminf(sc[2 * j], sc[2 * j + 1]);
+#pragma unroll
+                for (int w = 8; w > 0; w >>= 1)
+#pragma unroll
+                    for (int j = 0; j < w; ++j) m[j] = fminf(m[j], m[j + w]);
+                // Warp-uniform branches (votes) around the insertion: a thread's list changes about 16 ln(columns / 16)
+                // times in a whole scan, so a group of 32 columns holds two or three insertions per warp on average; the
+                // sorted insertion (75 predicated instructions) runs only for the columns where some lane has one.
+                if (__any_sync(0xffffffffu, m[0] < val[CB_KNN_CAND - 1])) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const bool hit = sc[j] < val[CB_KNN_CAND - 1];
+                        if (__any_sync(0xffffffffu, hit)) {
+                            if (hit) { val[CB_KNN_CAND - 1] = sc[j]; idx[CB_KNN_CAND - 1] = cbase + c * 32 + j; }
 #pragma unroll
                             for (int q = CB_KNN_CAND - 1; q > 0; --q) {
-                                if (val[q] < val[q - 1]) {
-                                    const float tv = val[q]; val[q] = val[q - 1]; val[q - 1] = tv;
-                                    const int ti = idx[q]; idx[q] = idx[q - 1]; idx[q - 1] = ti;
-                                }
+                                const bool sw = val[q] < val[q - 1];
+                                const float lo = sw ? val[q] : val[q - 1], hi = sw ? val[q - 1] : val[q];
+                                const int li = sw ? idx[q] : idx[q - 1], hi_i = sw ? idx[q - 1] : idx[q];
+                                val[q - 1] = lo; val[q] = hi; idx[q - 1] = li; idx[q] = hi_i;
                             }
                         }
                     }
                 }
             }
-            // this accumulator may be overwritten by the tile after the next one
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_tempty + 8 * buf) : "memory");
         }
         if (!ok) { atomicExch(a.status, CB_KNN_TIMEOUT); *(volatile int*)&s_abort = 1; }
         if (row < a.nq) {
-            const long long o = ((long long)row * gridDim.y + blockIdx.y) * CB_KNN_CAND;
+            const long long o = ((long long)row * (gridDim.y * 2) + blockIdx.y * 2 + half) * CB_KNN_CAND;
 #pragma unroll
             for (int c = 0; c < CB_KNN_CAND; ++c) { a.out_val[o + c] = val[c]; a.out_idx[o + c] = idx[c]; }
         }
@@ -307,7 +356,7 @@ CB_API int cb_knn_tc(const void* Q, int nq, const void* E, int ne, int dpad, con
     const int et = (ne + CB_KNN_TN - 1) / CB_KNN_TN;
     CbKnnArgs a{e2, nq, ne, dpad / CB_KNN_KC, (et + splits - 1) / splits, out_idx, out_val, status};
     dim3 grid((unsigned)((nq + CB_KNN_TM - 1) / CB_KNN_TM), (unsigned)splits);
-    cb_knn_tc_kernel<<<grid, 256, smem, st>>>(tmq, tme, a);
+    cb_knn_tc_kernel<<<grid, CB_KNN_THREADS, smem, st>>>(tmq, tme, a);
     const cudaError_t le = cudaGetLastError();
     return le == cudaSuccess ? 0 : (int)le;
 }

@@ -43,6 +43,10 @@ def main(argv=None):
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--kernel", default="all")
     ap.add_argument("--peak-gbs", type=float, default=0.0, help="measured copy bandwidth of the GPU in GB/s")
+    ap.add_argument("--peak-tflops", type=float, default=0.0, help="measured bf16 GEMM throughput of the GPU in TFLOP/s")
+    ap.add_argument("--knn-queries", type=int, default=65536)
+    ap.add_argument("--knn-cloud", type=int, default=131072)
+    ap.add_argument("--knn-dim", type=int, default=128)
     args = ap.parse_args(argv)
     from ..data.pool import Pool
     from ..data.quantization import build_quantization, make_store, quantize_floats_into, FlatFeature
@@ -268,6 +272,43 @@ def main(argv=None):
         report("cb_predict_wide_kernel (1M x 700, 200 trees)", ms, nw * Fw * 4 + nw * 4,
                f"{nw / (ms * 1e-3):.3g} rows/s; rows by register-staged loads; largest difference to the bulk-copy variant "
                f"{float((res - ref).abs().max()):.3g}")
+    if want("knn"):
+        # distance GEMM + top-k on the tensor cores against the library route (bf16 matmul, then topk over the matrix)
+        nq, ne, d = args.knn_queries, args.knn_cloud, args.knn_dim
+        tf_peak, tf_src = (args.peak_tflops, "given") if args.peak_tflops > 0 else (1590.0, "default")
+        gk = torch.Generator().manual_seed(5)
+        dpad = (d + 63) // 64 * 64
+        qb = torch.zeros((nq, dpad), dtype=torch.bfloat16, device=dev)
+        eb = torch.zeros((ne, dpad), dtype=torch.bfloat16, device=dev)
+        qb[:, :d] = torch.randn((nq, d), generator=gk).to(dev)
+        eb[:, :d] = torch.randn((ne, d), generator=gk).to(dev)
+        e2 = (eb.float() ** 2).sum(1).contiguous()
+        C = int(lib.cb_knn_candidates())
+        splits = int(lib.cb_knn_splits(nq, ne))
+        oi = torch.empty((nq, 2 * splits, C), dtype=torch.int32, device=dev)
+        ov = torch.empty((nq, 2 * splits, C), dtype=torch.float32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        flops = 2.0 * nq * ne * dpad
+        ms = _time(lambda: lib.cb_knn_tc(P(qb), nq, P(eb), ne, dpad, P(e2), splits, P(oi), P(ov), P(status), st()),
+                   args.reps, flush)
+        tf = flops / (ms * 1e-3) / 1e12
+        rec = {"kernel": f"cb_knn_tc_kernel ({nq} x {ne} x {dpad}, {splits} cloud ranges)", "ms": round(ms, 4),
+               "TFLOPs": round(tf, 1), "frac_of_bf16_peak": round(tf / tf_peak, 3), "peak_source": f"{tf_src} {tf_peak} TFLOP/s",
+               "note": f"tcgen05.mma + top-{C} epilogue, no distance matrix in memory; status {int(status.item())}"}
+        out.append(rec)
+        print(json.dumps(rec))
+
+        def library():
+            step = max(1, (1 << 30) // (ne * 2))
+            for s0 in range(0, nq, step):
+                sc = e2.unsqueeze(0) - 2.0 * (qb[s0:s0 + step] @ eb.t()).float()
+                torch.topk(sc, C, dim=1, largest=False, sorted=True)
+
+        ms2 = _time(library, max(1, args.reps // 2), flush)
+        rec = {"kernel": "library route: bf16 matmul + topk in chunks of 1 GiB of scores", "ms": round(ms2, 4),
+               "TFLOPs": round(flops / (ms2 * 1e-3) / 1e12, 1), "note": f"{ms2 / ms:.1f} x the fused kernel's time"}
+        out.append(rec)
+        print(json.dumps(rec))
     return 0
 
 
