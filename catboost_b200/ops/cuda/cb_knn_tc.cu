@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
                                                            const __grid_constant__ CUtensorMap tme, CbKnnArgs a) {
     extern __shared__ unsigned char cbk_raw[];
     unsigned char* smem = cbk_raw + ((1024u - (cbk_smem_u32(cbk_raw) & 1023u)) & 1023u);
-    // [kchunks] query chunks | [STAGES] cloud chunks | barriers | tmem base
+    // [kchunks] query chunks | [STAGES] cloud chunks | barriers | tmem base | insertion scratch of the epilogue warps
     unsigned char* sA = smem;
     unsigned char* sB = smem + CB_KNN_MAX_KCHUNKS * CB_KNN_TILE_BYTES;
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(sB + CB_KNN_STAGES * CB_KNN_TILE_BYTES);
@@ -80,6 +80,7 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
     const unsigned int bar_tfull = cbk_smem_u32(bars + 2 * CB_KNN_STAGES + 1);
     const unsigned int bar_tempty = cbk_smem_u32(bars + 2 * CB_KNN_STAGES + 3);
     unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(bars + 2 * CB_KNN_STAGES + 5);
+    float* scratch = reinterpret_cast<float*>(bars + 16);         // 8 epilogue warps x 1024 floats
     __shared__ int s_abort;
     __shared__ __align__(16) float s_e2[8][64];
 
@@ -184,6 +185,7 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
         // between warps, so a warp that gives up on a wait cannot leave the others stuck).  Columns past the end of the
         // cloud get a huge norm and never enter a list.  The values of the next tile are fetched while this one is processed.
         float* my_e2 = s_e2[ew];
+        float* my_sc = scratch + ew * 1024;                       // [32 columns][32 lanes] of the group being inserted
         float e2a = 3.0e38f, e2b = 3.0e38f;
         if (ntiles > 0) {
             const int col = t0 * CB_KNN_TN + half * 64 + lane;
@@ -247,22 +249,31 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
                 for (int w = 8; w > 0; w >>= 1)
 #pragma unroll
                     for (int j = 0; j < w; ++j) m[j] = fminf(m[j], m[j + w]);
-                // Warp-uniform branches (votes) around the insertion: a thread's list changes about 16 ln(columns / 16)
-                // times in a whole scan, so a group of 32 columns holds two or three insertions per warp on average; the
-                // sorted insertion (75 predicated instructions) runs only for the columns where some lane has one.
+                // A thread's list changes about 16 ln(columns / 16) times in a whole scan, so a group of 32 columns holds
+                // two or three insertions per warp on average.  The insertion is a compact loop, not 32 unrolled copies
+                // (those ran into instruction-fetch stalls: 12.6 stalled cycles per issue): the group's scores go to the
+                // warp's scratch in shared memory, every lane keeps a bit mask of its columns below the worst entry, and
+                // the warp loops while any lane has a bit left, one sorted insertion (75 predicated instructions) a turn.
                 if (__any_sync(0xffffffffu, m[0] < val[CB_KNN_CAND - 1])) {
+                    unsigned int hm = 0u;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const bool hit = sc[j] < val[CB_KNN_CAND - 1];
-                        if (__any_sync(0xffffffffu, hit)) {
-                            if (hit) { val[CB_KNN_CAND - 1] = sc[j]; idx[CB_KNN_CAND - 1] = cbase + c * 32 + j; }
+                        my_sc[j * 32 + lane] = sc[j];
+                        hm |= (sc[j] < val[CB_KNN_CAND - 1]) ? (1u << j) : 0u;
+                    }
+                    while (__any_sync(0xffffffffu, hm != 0u)) {
+                        if (hm) {
+                            const int j = __ffs(hm) - 1;
+                            hm &= hm - 1u;
+                            const float sv = my_sc[j * 32 + lane];
+                            if (sv < val[CB_KNN_CAND - 1]) { val[CB_KNN_CAND - 1] = sv; idx[CB_KNN_CAND - 1] = cbase + c * 32 + j; }
+                        }
 #pragma unroll
-                            for (int q = CB_KNN_CAND - 1; q > 0; --q) {
-                                const bool sw = val[q] < val[q - 1];
-                                const float lo = sw ? val[q] : val[q - 1], hi = sw ? val[q - 1] : val[q];
-                                const int li = sw ? idx[q] : idx[q - 1], hi_i = sw ? idx[q - 1] : idx[q];
-                                val[q - 1] = lo; val[q] = hi; idx[q - 1] = li; idx[q] = hi_i;
-                            }
+                        for (int q = CB_KNN_CAND - 1; q > 0; --q) {
+                            const bool sw = val[q] < val[q - 1];
+                            const float lo = sw ? val[q] : val[q - 1], hi = sw ? val[q - 1] : val[q];
+                            const int li = sw ? idx[q] : idx[q - 1], hi_i = sw ? idx[q - 1] : idx[q];
+                            val[q - 1] = lo; val[q] = hi; idx[q - 1] = li; idx[q] = hi_i;
                         }
                     }
                 }
@@ -347,7 +358,7 @@ CB_API int cb_knn_tc(const void* Q, int nq, const void* E, int ne, int dpad, con
     if ((reinterpret_cast<unsigned long long>(Q) & 15ull) || (reinterpret_cast<unsigned long long>(E) & 15ull)) return -2;
     CUtensorMap tmq, tme;
     if (cbk_make_map(&tmq, Q, nq, dpad) != 0 || cbk_make_map(&tme, E, ne, dpad) != 0) return -2;
-    const int smem = 1024 + (CB_KNN_MAX_KCHUNKS + CB_KNN_STAGES) * CB_KNN_TILE_BYTES + 16 * 8;
+    const int smem = 1024 + (CB_KNN_MAX_KCHUNKS + CB_KNN_STAGES) * CB_KNN_TILE_BYTES + 16 * 8 + 8 * 1024 * 4;
     static unsigned long long set = 0ull;
     if (cb_first_on_device(&set)) {
         cudaError_t e = cudaFuncSetAttribute(cb_knn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
