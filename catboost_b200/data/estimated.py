@@ -166,8 +166,9 @@ class _TextCalcers:
 class _EmbeddingCalcers:
     """LDA projection (classification) and KNN votes / mean target over one embedding column."""
 
-    def __init__(self, k=5, calcers=("LDA", "KNN")):
+    def __init__(self, k=5, calcers=("LDA", "KNN"), device=None):
         self.k, self.calcers = int(k), tuple(calcers)
+        self.device = device          # a CUDA torch.device sends the neighbour search of large clouds to the GPU
 
     def _lda(self, E, cls, n_classes):
         d = E.shape[1]
@@ -190,10 +191,28 @@ class _EmbeddingCalcers:
         u, _, _ = np.linalg.svd(W, full_matrices=False)
         return u[:, :k]
 
+    # clouds of at least this many rows go to the tensor-core search when the calcers were given a CUDA device
+    DEVICE_MIN_CLOUD = 1024
+
     def _knn(self, Q, E, tgt, n_classes):
         if len(E) == 0:
             return np.zeros((len(Q), n_classes if n_classes else 1), dtype=np.float32)
         out = np.zeros((len(Q), n_classes if n_classes else 1), dtype=np.float32)
+        dev = getattr(self, "device", None)
+        if dev is not None and getattr(dev, "type", "") == "cuda" and len(E) >= self.DEVICE_MIN_CLOUD and len(Q):
+            # neighbours from the device (ops/cuda/cb_knn_tc.cu: tcgen05 distance GEMM with a top-k epilogue, candidates
+            # re-ranked by fp32 distances); the votes are counted on the host from the returned indices
+            import torch
+            from ..ops import api as ops
+            k = min(self.k, len(E))
+            nn = ops.knn_search(torch.from_numpy(np.ascontiguousarray(Q, dtype=np.float32)).to(dev),
+                                torch.from_numpy(np.ascontiguousarray(E, dtype=np.float32)).to(dev), k).cpu().numpy()
+            if n_classes:
+                for c in range(n_classes):
+                    out[:, c] = (tgt[nn] == c).mean(1)
+            else:
+                out[:, 0] = tgt[nn].mean(1)
+            return out
         e2 = (E * E).sum(1)
         for s in range(0, len(Q), 2048):
             q = Q[s:s + 2048]
@@ -252,6 +271,15 @@ class _EmbeddingCalcers:
 class EstimatedFeatures:
     """All text / embedding columns of a pool -> one float matrix."""
 
+    def set_device(self, device):
+        """A CUDA ``torch.device`` sends the neighbour search of the embedding calcers to the GPU; ``None`` (the state a
+        model is stored and loaded in) keeps it on the host."""
+        self.device = device
+        for item in self.emb:
+            for obj in (item if isinstance(item, (list, tuple)) else [item]):
+                if isinstance(obj, _EmbeddingCalcers):
+                    obj.device = device
+
     def __init__(self, text_processing: Optional[dict] = None, seed: int = 0, tokenizers=None, dictionaries=None,
                  feature_calcers=None):
         """``tokenizers`` / ``dictionaries`` / ``feature_calcers`` are the estimator keywords of the same names; the same
@@ -266,6 +294,7 @@ class EstimatedFeatures:
         self.text_calcers = tuple(self._calcer_names(calc_default))
         self.embedding_calcers = tuple(tp.get("embedding_calcers", ("LDA", "KNN")))
         self.seed = int(seed)
+        self.device = None            # set_device(): where the embedding neighbour search runs during training
         self.text, self.emb, self.names = [], [], []
         # tokenizer: the first description (one tokenizer for all dictionaries)
         toks = tokenizers if tokenizers is not None else tp.get("tokenizers")
@@ -352,7 +381,7 @@ class EstimatedFeatures:
                 self.names += calc.names(prefix, inv)
                 mats.append(calc.transform_learn(indptr, indices, cls, blocks))
         for j, E in enumerate(pool.embedding_data):
-            calc = _EmbeddingCalcers(5, self.embedding_calcers).fit(np.asarray(E, dtype=np.float32), cls if n_classes else target.astype(np.float64), n_classes)
+            calc = _EmbeddingCalcers(5, self.embedding_calcers, device=self.device).fit(np.asarray(E, dtype=np.float32), cls if n_classes else target.astype(np.float64), n_classes)
             self.emb.append(calc)
             self.names += calc.names(f"emb{self.emb_flat[j]}")
             mats.append(calc.transform_learn(np.asarray(E, dtype=np.float32), blocks))

@@ -358,9 +358,11 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
                                            seed=int(o.random_seed), tokenizers=o.tokenizers, dictionaries=o.dictionaries,
                                            feature_calcers=o.feature_calcers)
             n_cls = (codec.n_classes or 2) if objective.is_classification else 0
+            estimators.set_device(device if device.type == "cuda" else None)
             learn = estimators.fit(train_pool, np.asarray(y_train), int(n_cls))
             train_pool = train_pool.with_estimated(learn, estimators.names)
             eval_pools = [ep.with_estimated(estimators.transform(ep), estimators.names) for ep in eval_pools]
+            estimators.set_device(None)                   # the stored model searches on the host
 
     # ---- features --------------------------------------------------------------------------------------
     with prof.span("quantization"):

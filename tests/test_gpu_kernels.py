@@ -846,3 +846,33 @@ def test_knn_search_falls_back_for_wide_embeddings():
     got = ops.knn_search(Q, E, 3)
     want = torch.topk(torch.cdist(Q, E), 3, dim=1, largest=False).indices
     assert (got.sort(1).values == want.sort(1).values).float().mean().item() > 0.99
+
+
+def test_embedding_knn_features_from_the_device_match_the_host():
+    """The KNN class votes of an embedding column computed through the tensor-core search against the host search."""
+    import catboost_b200 as cb
+    from catboost_b200.data.estimated import _EmbeddingCalcers
+    rng = np.random.default_rng(4)
+    n, d = 6000, 48
+    cls = rng.integers(0, 3, n)
+    centers = rng.standard_normal((3, d))
+    E = (centers[cls] * 0.5 + rng.standard_normal((n, d))).astype(np.float32)
+    host = _EmbeddingCalcers(5, ("KNN",)).fit(E[:4000], cls[:4000], 3)
+    dev = _EmbeddingCalcers(5, ("KNN",), device=torch.device("cuda", 0)).fit(E[:4000], cls[:4000], 3)
+    a, b = host.transform(E[4000:]), dev.transform(E[4000:])
+    assert a.shape == b.shape == (2000, 3)
+    assert np.mean(np.abs(a - b) < 1e-6) > 0.995                 # votes are multiples of 1/5: equal unless a neighbour differs
+    # the ordered learn features too: every block searched in the documents before it
+    blocks = np.array_split(rng.permutation(4000), 4)
+    la, lb = host.transform_learn(E[:4000], blocks), dev.transform_learn(E[:4000], blocks)
+    assert np.mean(np.abs(la - lb) < 1e-6) > 0.995
+    # end to end on the GPU trainer
+    X = np.empty((n, 2), dtype=object)
+    X[:, 0] = rng.standard_normal(n).astype(np.float32)
+    for i in range(n):
+        X[i, 1] = E[i]
+    m = cb.CatBoostClassifier(iterations=30, depth=4, learning_rate=0.2, verbose=False, allow_writing_files=False,
+                              task_type="GPU", devices="0")
+    m.fit(X[:5000], cls[:5000], embedding_features=[1])
+    acc = float((m.predict(X[5000:]).reshape(-1).astype(int) == cls[5000:]).mean())
+    assert acc > 0.8, acc
