@@ -27,7 +27,9 @@
 #define CB_KNN_TM 128                 // queries per CTA (MMA M)
 #define CB_KNN_TN 128                 // cloud rows per tile (MMA N)
 #define CB_KNN_KC 64                  // bf16 per K chunk = one 128-byte swizzled row
-#define CB_KNN_STAGES 4
+#define CB_KNN_STAGES 4                // ring of cloud chunks when the query tile is resident
+#define CB_KNN_STAGES_STREAM 5         // ring of (query chunk, cloud chunk) pairs when it is not: same 160 KB
+#define CB_KNN_MAX_STAGES 5
 #define CB_KNN_MAX_KCHUNKS 6          // query tile resident in shared memory: up to 384 dimensions
 #define CB_KNN_TILE_BYTES (CB_KNN_TN * CB_KNN_KC * 2)
 #define CB_KNN_TIMEOUT 0x61
@@ -60,6 +62,7 @@ __device__ __forceinline__ unsigned long long cbk_desc(unsigned int smem_addr) {
 struct CbKnnArgs {
     const float* e2;          // [ne] squared norms of the (bf16-rounded) cloud rows
     int nq, ne, kchunks;
+    int stream_a;             // more K chunks than fit resident: the query chunk travels with every cloud chunk
     int tiles_per_split;      // cloud tiles handled by one blockIdx.y
     int* out_idx;             // [nq][2 * splits][CB_KNN_CAND]
     float* out_val;
@@ -71,15 +74,19 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
     extern __shared__ unsigned char cbk_raw[];
     unsigned char* smem = cbk_raw + ((1024u - (cbk_smem_u32(cbk_raw) & 1023u)) & 1023u);
     // [kchunks] query chunks | [STAGES] cloud chunks | barriers | tmem base | insertion scratch of the epilogue warps
-    unsigned char* sA = smem;
-    unsigned char* sB = smem + CB_KNN_MAX_KCHUNKS * CB_KNN_TILE_BYTES;
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sB + CB_KNN_STAGES * CB_KNN_TILE_BYTES);
-    // bars: full[STAGES] | empty[STAGES] | a_full | tmem_full[2] | tmem_empty[2]
-    const unsigned int bar_full = cbk_smem_u32(bars), bar_empty = cbk_smem_u32(bars + CB_KNN_STAGES);
-    const unsigned int bar_a = cbk_smem_u32(bars + 2 * CB_KNN_STAGES);
-    const unsigned int bar_tfull = cbk_smem_u32(bars + 2 * CB_KNN_STAGES + 1);
-    const unsigned int bar_tempty = cbk_smem_u32(bars + 2 * CB_KNN_STAGES + 3);
-    unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(bars + 2 * CB_KNN_STAGES + 5);
+    const bool stream = a.stream_a != 0;
+    const int nst = stream ? CB_KNN_STAGES_STREAM : CB_KNN_STAGES;
+    const int stage_bytes = stream ? 2 * CB_KNN_TILE_BYTES : CB_KNN_TILE_BYTES;
+    unsigned char* sA = smem;                                               // resident query chunks (not when streaming)
+    unsigned char* ring = stream ? smem : smem + CB_KNN_MAX_KCHUNKS * CB_KNN_TILE_BYTES;
+    unsigned char* sB = ring + (stream ? CB_KNN_TILE_BYTES : 0);              // cloud chunk of stage 0
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (CB_KNN_MAX_KCHUNKS + CB_KNN_STAGES) * CB_KNN_TILE_BYTES);
+    // bars: full[MAX_STAGES] | empty[MAX_STAGES] | a_full | tmem_full[2] | tmem_empty[2]
+    const unsigned int bar_full = cbk_smem_u32(bars), bar_empty = cbk_smem_u32(bars + CB_KNN_MAX_STAGES);
+    const unsigned int bar_a = cbk_smem_u32(bars + 2 * CB_KNN_MAX_STAGES);
+    const unsigned int bar_tfull = cbk_smem_u32(bars + 2 * CB_KNN_MAX_STAGES + 1);
+    const unsigned int bar_tempty = cbk_smem_u32(bars + 2 * CB_KNN_MAX_STAGES + 3);
+    unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(bars + 2 * CB_KNN_MAX_STAGES + 5);
     float* scratch = reinterpret_cast<float*>(bars + 16);         // 8 epilogue warps x 1024 floats
     __shared__ int s_abort;
     __shared__ __align__(16) float s_e2[8][64];
@@ -93,7 +100,7 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
 
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < CB_KNN_STAGES; ++s) {
+        for (int s = 0; s < CB_KNN_MAX_STAGES; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_full + 8 * s) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_empty + 8 * s) : "memory");
         }
@@ -117,21 +124,27 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
     if (warp == 0) {
         // ---- producer ----------------------------------------------------------------------------------------
         if (lane == 0 && ntiles > 0) {
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(kch * CB_KNN_TILE_BYTES) : "memory");
-            for (int kc = 0; kc < kch; ++kc)
-                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                             ::"r"(cbk_smem_u32(sA + kc * CB_KNN_TILE_BYTES)), "l"(&tmq), "r"(kc * CB_KNN_KC),
-                               "r"((int)(blockIdx.x * CB_KNN_TM)), "r"(bar_a) : "memory");
+            if (!stream) {
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(kch * CB_KNN_TILE_BYTES) : "memory");
+                for (int kc = 0; kc < kch; ++kc)
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                 ::"r"(cbk_smem_u32(sA + kc * CB_KNN_TILE_BYTES)), "l"(&tmq), "r"(kc * CB_KNN_KC),
+                                   "r"((int)(blockIdx.x * CB_KNN_TM)), "r"(bar_a) : "memory");
+            }
             int it = 0;
             bool ok = true;
             for (int t = 0; t < ntiles && ok; ++t) {
                 for (int kc = 0; kc < kch; ++kc, ++it) {
-                    const int s = it % CB_KNN_STAGES;
-                    const unsigned int ph = (unsigned)(it / CB_KNN_STAGES) & 1u;
+                    const int s = it % nst;
+                    const unsigned int ph = (unsigned)(it / nst) & 1u;
                     if (*(volatile int*)&s_abort || !cbk_wait(bar_empty + 8 * s, ph ^ 1u)) { ok = false; break; }
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_full + 8 * s), "r"(CB_KNN_TILE_BYTES) : "memory");
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_full + 8 * s), "r"(stage_bytes) : "memory");
+                    if (stream)
+                        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                     ::"r"(cbk_smem_u32(ring + s * stage_bytes)), "l"(&tmq), "r"(kc * CB_KNN_KC),
+                                       "r"((int)(blockIdx.x * CB_KNN_TM)), "r"(bar_full + 8 * s) : "memory");
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                                 ::"r"(cbk_smem_u32(sB + s * CB_KNN_TILE_BYTES)), "l"(&tme), "r"(kc * CB_KNN_KC),
+                                 ::"r"(cbk_smem_u32(sB + s * stage_bytes)), "l"(&tme), "r"(kc * CB_KNN_KC),
                                    "r"((t0 + t) * CB_KNN_TN), "r"(bar_full + 8 * s) : "memory");
                 }
             }
@@ -140,7 +153,7 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
     } else if (warp == 1) {
         // ---- MMA issuer ----------------------------------------------------------------------------------------
         if (lane == 0 && ntiles > 0) {
-            bool ok = cbk_wait(bar_a, 0u);
+            bool ok = stream ? true : cbk_wait(bar_a, 0u);
             int it = 0;
             for (int t = 0; t < ntiles && ok; ++t) {
                 const int buf = t & 1;
@@ -149,12 +162,12 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned int dcol = tmem_base + (unsigned)buf * CB_KNN_TN;
                 for (int kc = 0; kc < kch; ++kc, ++it) {
-                    const int s = it % CB_KNN_STAGES;
-                    const unsigned int ph = (unsigned)(it / CB_KNN_STAGES) & 1u;
+                    const int s = it % nst;
+                    const unsigned int ph = (unsigned)(it / nst) & 1u;
                     if (!cbk_wait(bar_full + 8 * s, ph)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned long long da = cbk_desc(cbk_smem_u32(sA + kc * CB_KNN_TILE_BYTES));
-                    const unsigned long long db = cbk_desc(cbk_smem_u32(sB + s * CB_KNN_TILE_BYTES));
+                    const unsigned long long da = cbk_desc(cbk_smem_u32(stream ? ring + s * stage_bytes : sA + kc * CB_KNN_TILE_BYTES));
+                    const unsigned long long db = cbk_desc(cbk_smem_u32(sB + s * stage_bytes));
 #pragma unroll
                     for (int k = 0; k < CB_KNN_KC / 16; ++k) {
                         const unsigned int acc = (kc | k) ? 1u : 0u;
@@ -331,15 +344,20 @@ static int cbk_make_map(CUtensorMap* tm, const void* base, long long rows, int d
 }
 
 CB_API int cb_knn_candidates(void) { return CB_KNN_CAND; }
-CB_API int cb_knn_max_dim(void) { return CB_KNN_MAX_KCHUNKS * CB_KNN_KC; }
+// Largest dimension count (after padding to 64) the kernel takes; up to 384 the query tile stays in shared memory, above
+// that its chunks are streamed with the cloud chunks.
+CB_API int cb_knn_max_dim(void) { return 4096; }
 
-// Number of cloud ranges (blockIdx.y) that fills the device about once without making a range shorter than 4 tiles.
+// Number of cloud ranges (blockIdx.y); a range is never shorter than 4 tiles.
 CB_API int cb_knn_splits(int nq, int ne) {
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
     const int qt = (nq + CB_KNN_TM - 1) / CB_KNN_TM, et = (ne + CB_KNN_TN - 1) / CB_KNN_TN;
+    // Ranges are only there to give every SM a CTA when there are few query tiles: every range keeps candidate lists of
+    // its own, and a list over fewer columns changes more often per column (16 ln(columns / 16) insertions), which is
+    // what the epilogue pays for.  Measured at 65536 x 131072 x 128: 1 range 4.39 ms, 2 ranges (fuller last round) 4.67 ms.
     int s = (sms + qt - 1) / (qt > 0 ? qt : 1);
     if (s > et / 4) s = et / 4;
     if (s < 1) s = 1;
@@ -354,7 +372,7 @@ CB_API int cb_knn_splits(int nq, int ne) {
 CB_API int cb_knn_tc(const void* Q, int nq, const void* E, int ne, int dpad, const float* e2, int splits, int* out_idx,
                      float* out_val, int* status, cudaStream_t st) {
     if (nq <= 0 || ne <= 0) return 0;
-    if (dpad <= 0 || dpad % CB_KNN_KC != 0 || dpad > CB_KNN_MAX_KCHUNKS * CB_KNN_KC || splits < 1 || splits > 65535) return -2;
+    if (dpad <= 0 || dpad % CB_KNN_KC != 0 || dpad > 4096 || splits < 1 || splits > 65535) return -2;
     if ((reinterpret_cast<unsigned long long>(Q) & 15ull) || (reinterpret_cast<unsigned long long>(E) & 15ull)) return -2;
     CUtensorMap tmq, tme;
     if (cbk_make_map(&tmq, Q, nq, dpad) != 0 || cbk_make_map(&tme, E, ne, dpad) != 0) return -2;
@@ -365,7 +383,8 @@ CB_API int cb_knn_tc(const void* Q, int nq, const void* E, int ne, int dpad, con
         if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
     }
     const int et = (ne + CB_KNN_TN - 1) / CB_KNN_TN;
-    CbKnnArgs a{e2, nq, ne, dpad / CB_KNN_KC, (et + splits - 1) / splits, out_idx, out_val, status};
+    CbKnnArgs a{e2, nq, ne, dpad / CB_KNN_KC, dpad / CB_KNN_KC > CB_KNN_MAX_KCHUNKS ? 1 : 0, (et + splits - 1) / splits, out_idx, out_val,
+                status};
     dim3 grid((unsigned)((nq + CB_KNN_TM - 1) / CB_KNN_TM), (unsigned)splits);
     cb_knn_tc_kernel<<<grid, CB_KNN_THREADS, smem, st>>>(tmq, tme, a);
     const cudaError_t le = cudaGetLastError();

@@ -806,7 +806,8 @@ def test_leaf_kernel_in_the_general_learner_matches_tensor_code(policy, loss):
     assert np.allclose(preds[True], preds[False], rtol=2e-3, atol=2e-3), float(np.abs(preds[True] - preds[False]).max())
 
 
-@pytest.mark.parametrize("nq,ne,d", [(300, 1000, 96), (130, 129, 200), (256, 40000, 64), (1000, 5000, 384)])
+@pytest.mark.parametrize("nq,ne,d", [(300, 1000, 96), (130, 129, 200), (256, 40000, 64), (1000, 5000, 384),
+                                      (200, 3000, 500), (150, 2000, 768)])
 def test_knn_tensor_core_candidates_match_fp32_reference(nq, ne, d):
     """tcgen05 distance GEMM + top-k epilogue against a plain fp32 computation on the same bf16-rounded inputs."""
     from catboost_b200.ops import api as ops
@@ -837,14 +838,13 @@ def test_knn_tensor_core_candidates_match_fp32_reference(nq, ne, d):
     assert recall > 0.995, recall
 
 
-def test_knn_search_falls_back_for_wide_embeddings():
+def test_knn_search_falls_back_for_many_neighbours():
     from catboost_b200.ops import api as ops
     g = torch.Generator(device="cpu").manual_seed(3)
-    Q = torch.randn((50, 500), generator=g).cuda()
-    E = torch.randn((400, 500), generator=g).cuda()
-    assert ops.knn_candidates(Q, E) is None                       # more dimensions than the resident query tile holds
-    got = ops.knn_search(Q, E, 3)
-    want = torch.topk(torch.cdist(Q, E), 3, dim=1, largest=False).indices
+    Q = torch.randn((50, 40), generator=g).cuda()
+    E = torch.randn((400, 40), generator=g).cuda()
+    got = ops.knn_search(Q, E, 12)                                # more than half the kernel's candidate list: library GEMM
+    want = torch.topk(torch.cdist(Q, E), 12, dim=1, largest=False).indices
     assert (got.sort(1).values == want.sort(1).values).float().mean().item() > 0.99
 
 
