@@ -98,17 +98,18 @@ def sort_pairs(keys: torch.Tensor):
 KNN_TIMEOUT = 0x61
 
 
-def knn_candidates(Q: torch.Tensor, E: torch.Tensor):
+def knn_candidates(Q: torch.Tensor, E: torch.Tensor, cand: int = 16):
     """Approximate nearest rows of ``E`` for every row of ``Q`` on the tensor cores (ops/cuda/cb_knn_tc.cu: TMA-fed
     tcgen05 GEMM with the accumulator in TMEM, top-k selection in the epilogue).  Q [nq, d], E [ne, d] float tensors on
     one CUDA device, d <= cb_knn_max_dim().  Returns (idx int64 [nq, C], score float32 [nq, C]) with
-    score = |e|^2 - 2 q.e computed from bf16-rounded inputs, ascending; C = cb_knn_candidates(); idx is -1 where the
-    cloud has fewer than C rows.  Returns None when the shape does not qualify."""
+    score = |e|^2 - 2 q.e computed from bf16-rounded inputs, ascending; C = 2 * cand: the kernel keeps a list of ``cand``
+    (8 or 16) per half of a cloud tile and the two halves are merged here; idx is -1 where the cloud has fewer rows.
+    Returns None when the shape does not qualify."""
     lib = native.cuda_lib()
     dev = Q.device
     nq, d = int(Q.shape[0]), int(Q.shape[1])
     ne = int(E.shape[0])
-    C = int(lib.cb_knn_candidates())
+    C = int(cand)
     if d > int(lib.cb_knn_max_dim()) or nq == 0 or ne == 0 or nq >= (1 << 31) or ne >= (1 << 31):
         return None
     dpad = (d + 63) // 64 * 64
@@ -122,7 +123,7 @@ def knn_candidates(Q: torch.Tensor, E: torch.Tensor):
     out_idx = torch.empty((nq, lists, C), dtype=torch.int32, device=dev)
     out_val = torch.empty((nq, lists, C), dtype=torch.float32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    rc = lib.cb_knn_tc(_p(qb), nq, _p(eb), ne, dpad, _p(e2), splits, _p(out_idx), _p(out_val), _p(status), _stream(dev))
+    rc = lib.cb_knn_tc(_p(qb), nq, _p(eb), ne, dpad, _p(e2), splits, C, _p(out_idx), _p(out_val), _p(status), _stream(dev))
     if rc == -2:
         return None
     native.cuda_check(rc, "cb_knn_tc")
@@ -130,18 +131,20 @@ def knn_candidates(Q: torch.Tensor, E: torch.Tensor):
         raise RuntimeError(f"cb_knn_tc: a wait inside the kernel ran out (status {int(status.item()):#x})")
     val = out_val.reshape(nq, lists * C)
     idx = out_idx.reshape(nq, lists * C).long()
-    val, pos = torch.topk(val, C, dim=1, largest=False, sorted=True)
+    val, pos = torch.topk(val, min(2 * C, val.shape[1]), dim=1, largest=False, sorted=True)
     return idx.gather(1, pos), val
 
 
 def knn_search(Q: torch.Tensor, E: torch.Tensor, k: int):
     """Indices [nq, k] of the k nearest rows of ``E`` (Euclidean) for every row of ``Q``: tensor-core candidates
     re-ranked by fp32 distances.  Falls back to a chunked fp32 distance matrix (library GEMM) when the shape does not
-    qualify for the tensor-core kernel (more than cb_knn_max_dim() dimensions, k above half the candidate count)."""
+    qualify for the tensor-core kernel (more than cb_knn_max_dim() dimensions, k above 8)."""
     k = min(int(k), int(E.shape[0]))
     cand = None
-    if Q.is_cuda and 2 * k <= int(native.cuda_lib().cb_knn_candidates()):
-        cand = knn_candidates(Q, E)
+    if Q.is_cuda and k <= 8:
+        # lists of 8 hold the 5 nearest of a tile half with room for the reordering bf16 rounding causes; longer lists
+        # for k up to 8
+        cand = knn_candidates(Q, E, 8 if k <= 5 else 16)
     if cand is not None:
         idx, _ = cand
         Qf, Ef = Q.float(), E.float()

@@ -27,9 +27,10 @@
 #define CB_KNN_TM 128                 // queries per CTA (MMA M)
 #define CB_KNN_TN 128                 // cloud rows per tile (MMA N)
 #define CB_KNN_KC 64                  // bf16 per K chunk = one 128-byte swizzled row
-#define CB_KNN_STAGES 4                // ring of cloud chunks when the query tile is resident
-#define CB_KNN_STAGES_STREAM 5         // ring of (query chunk, cloud chunk) pairs when it is not: same 160 KB
-#define CB_KNN_MAX_STAGES 5
+#define CB_KNN_MAX_STAGES 12           // the ring takes what is left of the 227 KB, up to this many stages
+#define CB_KNN_FIXED_BYTES 35840       // barriers (256) | norms (2048) | abort flag | insertion scratch (32768), 1024-aligned
+#define CB_KNN_SMEM_BYTES 232448       // all the shared memory a CTA may have
+#define CB_KNN_BAD_LAYOUT 0x62
 #define CB_KNN_MAX_KCHUNKS 6          // query tile resident in shared memory: up to 384 dimensions
 #define CB_KNN_TILE_BYTES (CB_KNN_TN * CB_KNN_KC * 2)
 #define CB_KNN_TIMEOUT 0x61
@@ -63,41 +64,50 @@ struct CbKnnArgs {
     const float* e2;          // [ne] squared norms of the (bf16-rounded) cloud rows
     int nq, ne, kchunks;
     int stream_a;             // more K chunks than fit resident: the query chunk travels with every cloud chunk
+    int smem_bytes;           // dynamic shared memory of the launch
     int tiles_per_split;      // cloud tiles handled by one blockIdx.y
-    int* out_idx;             // [nq][2 * splits][CB_KNN_CAND]
+    int* out_idx;             // [nq][2 * splits][candidates per list]
     float* out_val;
     int* status;
 };
 
+template <int CAND>
 __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __grid_constant__ CUtensorMap tmq,
                                                            const __grid_constant__ CUtensorMap tme, CbKnnArgs a) {
     extern __shared__ unsigned char cbk_raw[];
     unsigned char* smem = cbk_raw + ((1024u - (cbk_smem_u32(cbk_raw) & 1023u)) & 1023u);
-    // [kchunks] query chunks | [STAGES] cloud chunks | barriers | tmem base | insertion scratch of the epilogue warps
+    // barriers | norms of the epilogue warps | abort flag | insertion scratch || [kchunks] query chunks | ring.  A copy in
+    // flight is the only thing that hides the L2 latency from the tensor pipe (with 4 stages of 16 KB it was busy a third
+    // of the time), so the ring gets every byte the CTA can have.
     const bool stream = a.stream_a != 0;
-    const int nst = stream ? CB_KNN_STAGES_STREAM : CB_KNN_STAGES;
     const int stage_bytes = stream ? 2 * CB_KNN_TILE_BYTES : CB_KNN_TILE_BYTES;
-    unsigned char* sA = smem;                                               // resident query chunks (not when streaming)
-    unsigned char* ring = stream ? smem : smem + CB_KNN_MAX_KCHUNKS * CB_KNN_TILE_BYTES;
-    unsigned char* sB = ring + (stream ? CB_KNN_TILE_BYTES : 0);              // cloud chunk of stage 0
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (CB_KNN_MAX_KCHUNKS + CB_KNN_STAGES) * CB_KNN_TILE_BYTES);
-    // bars: full[MAX_STAGES] | empty[MAX_STAGES] | a_full | tmem_full[2] | tmem_empty[2]
+    const int kch = a.kchunks;
+    const int pad = (int)(smem - cbk_raw);
+    int nst = (a.smem_bytes - pad - CB_KNN_FIXED_BYTES - (stream ? 0 : kch * CB_KNN_TILE_BYTES)) / stage_bytes;
+    if (nst > CB_KNN_MAX_STAGES) nst = CB_KNN_MAX_STAGES;
+    if (nst < 2) {                                                          // uniform: nobody has touched a barrier yet
+        if (threadIdx.x == 0) atomicExch(a.status, CB_KNN_BAD_LAYOUT);
+        return;
+    }
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem);
+    // bars: full[MAX_STAGES] | empty[MAX_STAGES] | a_full | tmem_full[2] | tmem_empty[2] | tmem base
     const unsigned int bar_full = cbk_smem_u32(bars), bar_empty = cbk_smem_u32(bars + CB_KNN_MAX_STAGES);
     const unsigned int bar_a = cbk_smem_u32(bars + 2 * CB_KNN_MAX_STAGES);
     const unsigned int bar_tfull = cbk_smem_u32(bars + 2 * CB_KNN_MAX_STAGES + 1);
     const unsigned int bar_tempty = cbk_smem_u32(bars + 2 * CB_KNN_MAX_STAGES + 3);
     unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(bars + 2 * CB_KNN_MAX_STAGES + 5);
-    float* scratch = reinterpret_cast<float*>(bars + 16);         // 8 epilogue warps x 1024 floats
-    __shared__ int s_abort;
-    __shared__ __align__(16) float s_e2[8][64];
+    float (*s_e2)[64] = reinterpret_cast<float (*)[64]>(smem + 256);          // [8][64]
+    int& s_abort = *reinterpret_cast<int*>(smem + 256 + 2048);
+    float* scratch = reinterpret_cast<float*>(smem + 3072);                    // 8 epilogue warps x 1024 floats
+    unsigned char* sA = smem + CB_KNN_FIXED_BYTES;                            // resident query chunks (not when streaming)
+    unsigned char* ring = stream ? sA : sA + kch * CB_KNN_TILE_BYTES;
+    unsigned char* sB = ring + (stream ? CB_KNN_TILE_BYTES : 0);              // cloud chunk of stage 0
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntiles_all = (a.ne + CB_KNN_TN - 1) / CB_KNN_TN;
     const int t0 = blockIdx.y * a.tiles_per_split;
     const int t1 = min(ntiles_all, t0 + a.tiles_per_split);
     const int ntiles = max(0, t1 - t0);
-    const int kch = a.kchunks;
-
     if (threadIdx.x == 0) {
         s_abort = 0;
         for (int s = 0; s < CB_KNN_MAX_STAGES; ++s) {
@@ -189,10 +199,10 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
         // columns 0-63 or 64-127 of the tile; a query row therefore has two candidate lists, merged by the caller ------
         const int ew = warp - 4, wq = ew & 3, half = ew >> 2;
         const int row = blockIdx.x * CB_KNN_TM + wq * 32 + lane;
-        float val[CB_KNN_CAND];
-        int idx[CB_KNN_CAND];
+        float val[CAND];
+        int idx[CAND];
 #pragma unroll
-        for (int c = 0; c < CB_KNN_CAND; ++c) { val[c] = 3.0e38f; idx[c] = -1; }
+        for (int c = 0; c < CAND; ++c) { val[c] = 3.0e38f; idx[c] = -1; }
         bool ok = true;
         // |e|^2 of the warp's 64 columns goes through the warp's own piece of shared memory (broadcast reads; no barrier
         // between warps, so a warp that gives up on a wait cannot leave the others stuck).  Columns past the end of the
@@ -267,22 +277,22 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
                 // (those ran into instruction-fetch stalls: 12.6 stalled cycles per issue): the group's scores go to the
                 // warp's scratch in shared memory, every lane keeps a bit mask of its columns below the worst entry, and
                 // the warp loops while any lane has a bit left, one sorted insertion (75 predicated instructions) a turn.
-                if (__any_sync(0xffffffffu, m[0] < val[CB_KNN_CAND - 1])) {
+                if (__any_sync(0xffffffffu, m[0] < val[CAND - 1])) {
                     unsigned int hm = 0u;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         my_sc[j * 32 + lane] = sc[j];
-                        hm |= (sc[j] < val[CB_KNN_CAND - 1]) ? (1u << j) : 0u;
+                        hm |= (sc[j] < val[CAND - 1]) ? (1u << j) : 0u;
                     }
                     while (__any_sync(0xffffffffu, hm != 0u)) {
                         if (hm) {
                             const int j = __ffs(hm) - 1;
                             hm &= hm - 1u;
                             const float sv = my_sc[j * 32 + lane];
-                            if (sv < val[CB_KNN_CAND - 1]) { val[CB_KNN_CAND - 1] = sv; idx[CB_KNN_CAND - 1] = cbase + c * 32 + j; }
+                            if (sv < val[CAND - 1]) { val[CAND - 1] = sv; idx[CAND - 1] = cbase + c * 32 + j; }
                         }
 #pragma unroll
-                        for (int q = CB_KNN_CAND - 1; q > 0; --q) {
+                        for (int q = CAND - 1; q > 0; --q) {
                             const bool sw = val[q] < val[q - 1];
                             const float lo = sw ? val[q] : val[q - 1], hi = sw ? val[q - 1] : val[q];
                             const int li = sw ? idx[q] : idx[q - 1], hi_i = sw ? idx[q - 1] : idx[q];
@@ -294,9 +304,9 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
         }
         if (!ok) { atomicExch(a.status, CB_KNN_TIMEOUT); *(volatile int*)&s_abort = 1; }
         if (row < a.nq) {
-            const long long o = ((long long)row * (gridDim.y * 2) + blockIdx.y * 2 + half) * CB_KNN_CAND;
+            const long long o = ((long long)row * (gridDim.y * 2) + blockIdx.y * 2 + half) * CAND;
 #pragma unroll
-            for (int c = 0; c < CB_KNN_CAND; ++c) { a.out_val[o + c] = val[c]; a.out_idx[o + c] = idx[c]; }
+            for (int c = 0; c < CAND; ++c) { a.out_val[o + c] = val[c]; a.out_idx[o + c] = idx[c]; }
         }
     }
     __syncthreads();
@@ -368,25 +378,29 @@ CB_API int cb_knn_splits(int nq, int ne) {
 // Q [nq][dpad] and E [ne][dpad] are bf16, row-major, 16-byte aligned, dpad a multiple of 64 and at most
 // cb_knn_max_dim(); e2 [ne] fp32.  out_idx / out_val are [nq][splits][CB_KNN_CAND]; entries that were never filled hold
 // index -1.  Returns 0 when the kernel was enqueued, -2 when the shape does not qualify, a CUDA error code otherwise.
-// *status (device int, zero on entry) receives CB_KNN_TIMEOUT when a wait inside the kernel ran out.
-CB_API int cb_knn_tc(const void* Q, int nq, const void* E, int ne, int dpad, const float* e2, int splits, int* out_idx,
+// *status (device int, zero on entry) receives CB_KNN_TIMEOUT when a wait inside the kernel ran out.  cand = 8 or 16 is the
+// length of a candidate list (the last dimension of the outputs): the epilogue's work grows with its square.
+CB_API int cb_knn_tc(const void* Q, int nq, const void* E, int ne, int dpad, const float* e2, int splits, int cand, int* out_idx,
                      float* out_val, int* status, cudaStream_t st) {
+    if (cand != 8 && cand != 16) return -2;
     if (nq <= 0 || ne <= 0) return 0;
     if (dpad <= 0 || dpad % CB_KNN_KC != 0 || dpad > 4096 || splits < 1 || splits > 65535) return -2;
     if ((reinterpret_cast<unsigned long long>(Q) & 15ull) || (reinterpret_cast<unsigned long long>(E) & 15ull)) return -2;
     CUtensorMap tmq, tme;
     if (cbk_make_map(&tmq, Q, nq, dpad) != 0 || cbk_make_map(&tme, E, ne, dpad) != 0) return -2;
-    const int smem = 1024 + (CB_KNN_MAX_KCHUNKS + CB_KNN_STAGES) * CB_KNN_TILE_BYTES + 16 * 8 + 8 * 1024 * 4;
+    const int smem = CB_KNN_SMEM_BYTES;
     static unsigned long long set = 0ull;
     if (cb_first_on_device(&set)) {
-        cudaError_t e = cudaFuncSetAttribute(cb_knn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(cb_knn_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(cb_knn_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) { cudaGetLastError(); set = 0ull; return (int)e; }
     }
     const int et = (ne + CB_KNN_TN - 1) / CB_KNN_TN;
-    CbKnnArgs a{e2, nq, ne, dpad / CB_KNN_KC, dpad / CB_KNN_KC > CB_KNN_MAX_KCHUNKS ? 1 : 0, (et + splits - 1) / splits, out_idx, out_val,
-                status};
+    CbKnnArgs a{e2, nq, ne, dpad / CB_KNN_KC, dpad / CB_KNN_KC > CB_KNN_MAX_KCHUNKS ? 1 : 0, smem, (et + splits - 1) / splits, out_idx,
+                out_val, status};
     dim3 grid((unsigned)((nq + CB_KNN_TM - 1) / CB_KNN_TM), (unsigned)splits);
-    cb_knn_tc_kernel<<<grid, CB_KNN_THREADS, smem, st>>>(tmq, tme, a);
+    if (cand == 8) cb_knn_tc_kernel<8><<<grid, CB_KNN_THREADS, smem, st>>>(tmq, tme, a);
+    else cb_knn_tc_kernel<16><<<grid, CB_KNN_THREADS, smem, st>>>(tmq, tme, a);
     const cudaError_t le = cudaGetLastError();
     return le == cudaSuccess ? 0 : (int)le;
 }

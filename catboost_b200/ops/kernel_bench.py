@@ -47,6 +47,7 @@ def main(argv=None):
     ap.add_argument("--knn-queries", type=int, default=65536)
     ap.add_argument("--knn-cloud", type=int, default=131072)
     ap.add_argument("--knn-dim", type=int, default=128)
+    ap.add_argument("--knn-candidates", type=int, default=8, choices=(8, 16), help="length of a candidate list")
     args = ap.parse_args(argv)
     from ..data.pool import Pool
     from ..data.quantization import build_quantization, make_store, quantize_floats_into, FlatFeature
@@ -283,13 +284,13 @@ def main(argv=None):
         qb[:, :d] = torch.randn((nq, d), generator=gk).to(dev)
         eb[:, :d] = torch.randn((ne, d), generator=gk).to(dev)
         e2 = (eb.float() ** 2).sum(1).contiguous()
-        C = int(lib.cb_knn_candidates())
+        C = args.knn_candidates
         splits = int(lib.cb_knn_splits(nq, ne))
         oi = torch.empty((nq, 2 * splits, C), dtype=torch.int32, device=dev)
         ov = torch.empty((nq, 2 * splits, C), dtype=torch.float32, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         flops = 2.0 * nq * ne * dpad
-        ms = _time(lambda: lib.cb_knn_tc(P(qb), nq, P(eb), ne, dpad, P(e2), splits, P(oi), P(ov), P(status), st()),
+        ms = _time(lambda: lib.cb_knn_tc(P(qb), nq, P(eb), ne, dpad, P(e2), splits, C, P(oi), P(ov), P(status), st()),
                    args.reps, flush)
         tf = flops / (ms * 1e-3) / 1e12
         rec = {"kernel": f"cb_knn_tc_kernel ({nq} x {ne} x {dpad}, {splits} cloud ranges)", "ms": round(ms, 4),

@@ -210,7 +210,7 @@ _SIGS = {
     "cb_knn_candidates": (c_int, []),
     "cb_knn_max_dim": (c_int, []),
     "cb_knn_splits": (c_int, [c_int, c_int]),
-    "cb_knn_tc": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "cb_knn_tc": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_mvs_block_docs": (c_int, []),
     "cb_mvs_sample": (c_int, [c_void_p, c_ll, c_ll, c_float, c_float, c_ull, c_void_p, c_void_p, c_void_p, c_void_p]),
     "cb_mc_max_classes": (c_int, []),
