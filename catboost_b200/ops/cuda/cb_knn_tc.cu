@@ -7,14 +7,15 @@
 // Inputs are bf16 (fp32 accumulation), so the order is approximate among near ties: the caller re-ranks the candidates
 // with fp32 distances and keeps k <= CB_KNN_CAND / 2 of them.
 //
-// Structure of a CTA (384 threads, one tile of 128 queries, a range of 128-row cloud tiles):
+// Structure of a CTA (384 threads, one tile of 128 queries, a range of 256-row cloud tiles):
 //   warp 0   producer: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle) loads the query tile once -- all K chunks stay
-//            in shared memory -- and streams the cloud tiles through a 4-stage ring of [128 rows x 64 bf16] boxes;
-//   warp 1   one elected lane issues tcgen05.mma (M = N = 128, K = 16, operands from shared memory through matrix
+//            in shared memory up to 256 dimensions, above that they travel with the cloud chunks -- and streams the
+//            cloud tiles through a ring of [256 rows x 64 bf16] boxes that takes all the shared memory left;
+//   warp 1   one elected lane issues tcgen05.mma (M = 128, N = 256, K = 16, operands from shared memory through matrix
 //            descriptors, accumulator in TMEM), tcgen05.commit releases the ring stage / publishes the accumulator;
-//   warp 2   allocates and frees 256 TMEM columns: two accumulators, so tile i + 1 is multiplied while tile i is read;
-//   warps 4-11 epilogue: thread = query row = TMEM lane, two warps per lane quarter (64 columns of the tile each);
-//            tcgen05.ld brings the 64 columns into registers, the TMEM buffer is handed back at once, then
+//   warp 2   allocates and frees all 512 TMEM columns: two accumulators, so tile i + 1 is multiplied while tile i is read;
+//   warps 4-11 epilogue: thread = query row = TMEM lane, two warps per lane quarter (128 columns of the tile each);
+//            tcgen05.ld brings 64 columns at a time into registers, the TMEM buffer is handed back after the second read,
 //            s = |e|^2 - 2 acc (|e|^2 from shared memory), the minimum of every 32 scores by a tree of minima, and a
 //            sorted insertion into the thread's candidate list only for groups that hold something below its worst entry.
 // Every mbarrier wait is bounded; when one runs out the CTA records CB_KNN_TIMEOUT in *status, every role leaves its
@@ -25,14 +26,16 @@
 
 #define CB_KNN_CAND 16
 #define CB_KNN_TM 128                 // queries per CTA (MMA M)
-#define CB_KNN_TN 128                 // cloud rows per tile (MMA N)
+#define CB_KNN_TN 256                 // cloud rows per tile (MMA N): at N = 128 an MMA reads 8 KB of operands per 64 clocks,
+                                      // all a SM's shared memory can deliver; at N = 256 it is 12 KB per 128 clocks
 #define CB_KNN_KC 64                  // bf16 per K chunk = one 128-byte swizzled row
 #define CB_KNN_MAX_STAGES 12           // the ring takes what is left of the 227 KB, up to this many stages
-#define CB_KNN_FIXED_BYTES 35840       // barriers (256) | norms (2048) | abort flag | insertion scratch (32768), 1024-aligned
+#define CB_KNN_FIXED_BYTES 37888       // barriers (256) | norms (4096) | abort flag | insertion scratch (32768), 1024-aligned
 #define CB_KNN_SMEM_BYTES 232448       // all the shared memory a CTA may have
 #define CB_KNN_BAD_LAYOUT 0x62
-#define CB_KNN_MAX_KCHUNKS 6          // query tile resident in shared memory: up to 384 dimensions
-#define CB_KNN_TILE_BYTES (CB_KNN_TN * CB_KNN_KC * 2)
+#define CB_KNN_MAX_KCHUNKS 4          // query tile resident in shared memory: up to 256 dimensions
+#define CB_KNN_A_BYTES (CB_KNN_TM * CB_KNN_KC * 2)   // one K chunk of the query tile: 16 KB
+#define CB_KNN_B_BYTES (CB_KNN_TN * CB_KNN_KC * 2)   // one K chunk of a cloud tile: 32 KB
 #define CB_KNN_TIMEOUT 0x61
 #define CB_KNN_WAIT_LIMIT (1 << 22)
 #define CB_KNN_THREADS 384             // 4 role warps + 8 epilogue warps
@@ -80,10 +83,10 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
     // flight is the only thing that hides the L2 latency from the tensor pipe (with 4 stages of 16 KB it was busy a third
     // of the time), so the ring gets every byte the CTA can have.
     const bool stream = a.stream_a != 0;
-    const int stage_bytes = stream ? 2 * CB_KNN_TILE_BYTES : CB_KNN_TILE_BYTES;
+    const int stage_bytes = stream ? CB_KNN_A_BYTES + CB_KNN_B_BYTES : CB_KNN_B_BYTES;
     const int kch = a.kchunks;
     const int pad = (int)(smem - cbk_raw);
-    int nst = (a.smem_bytes - pad - CB_KNN_FIXED_BYTES - (stream ? 0 : kch * CB_KNN_TILE_BYTES)) / stage_bytes;
+    int nst = (a.smem_bytes - pad - CB_KNN_FIXED_BYTES - (stream ? 0 : kch * CB_KNN_A_BYTES)) / stage_bytes;
     if (nst > CB_KNN_MAX_STAGES) nst = CB_KNN_MAX_STAGES;
     if (nst < 2) {                                                          // uniform: nobody has touched a barrier yet
         if (threadIdx.x == 0) atomicExch(a.status, CB_KNN_BAD_LAYOUT);
@@ -96,12 +99,12 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
     const unsigned int bar_tfull = cbk_smem_u32(bars + 2 * CB_KNN_MAX_STAGES + 1);
     const unsigned int bar_tempty = cbk_smem_u32(bars + 2 * CB_KNN_MAX_STAGES + 3);
     unsigned int* tmem_slot = reinterpret_cast<unsigned int*>(bars + 2 * CB_KNN_MAX_STAGES + 5);
-    float (*s_e2)[64] = reinterpret_cast<float (*)[64]>(smem + 256);          // [8][64]
-    int& s_abort = *reinterpret_cast<int*>(smem + 256 + 2048);
-    float* scratch = reinterpret_cast<float*>(smem + 3072);                    // 8 epilogue warps x 1024 floats
+    float (*s_e2)[128] = reinterpret_cast<float (*)[128]>(smem + 256);        // [8][128]
+    int& s_abort = *reinterpret_cast<int*>(smem + 256 + 4096);
+    float* scratch = reinterpret_cast<float*>(smem + 5120);                    // 8 epilogue warps x 1024 floats
     unsigned char* sA = smem + CB_KNN_FIXED_BYTES;                            // resident query chunks (not when streaming)
-    unsigned char* ring = stream ? sA : sA + kch * CB_KNN_TILE_BYTES;
-    unsigned char* sB = ring + (stream ? CB_KNN_TILE_BYTES : 0);              // cloud chunk of stage 0
+    unsigned char* ring = stream ? sA : sA + kch * CB_KNN_A_BYTES;
+    unsigned char* sB = ring + (stream ? CB_KNN_A_BYTES : 0);              // cloud chunk of stage 0
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntiles_all = (a.ne + CB_KNN_TN - 1) / CB_KNN_TN;
@@ -122,7 +125,7 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 2) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(cbk_smem_u32(tmem_slot)), "r"(256)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(cbk_smem_u32(tmem_slot)), "r"(512)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -135,10 +138,10 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
         // ---- producer ----------------------------------------------------------------------------------------
         if (lane == 0 && ntiles > 0) {
             if (!stream) {
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(kch * CB_KNN_TILE_BYTES) : "memory");
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(kch * CB_KNN_A_BYTES) : "memory");
                 for (int kc = 0; kc < kch; ++kc)
                     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                                 ::"r"(cbk_smem_u32(sA + kc * CB_KNN_TILE_BYTES)), "l"(&tmq), "r"(kc * CB_KNN_KC),
+                                 ::"r"(cbk_smem_u32(sA + kc * CB_KNN_A_BYTES)), "l"(&tmq), "r"(kc * CB_KNN_KC),
                                    "r"((int)(blockIdx.x * CB_KNN_TM)), "r"(bar_a) : "memory");
             }
             int it = 0;
@@ -176,7 +179,7 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
                     const unsigned int ph = (unsigned)(it / nst) & 1u;
                     if (!cbk_wait(bar_full + 8 * s, ph)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned long long da = cbk_desc(cbk_smem_u32(stream ? ring + s * stage_bytes : sA + kc * CB_KNN_TILE_BYTES));
+                    const unsigned long long da = cbk_desc(cbk_smem_u32(stream ? ring + s * stage_bytes : sA + kc * CB_KNN_A_BYTES));
                     const unsigned long long db = cbk_desc(cbk_smem_u32(sB + s * stage_bytes));
 #pragma unroll
                     for (int k = 0; k < CB_KNN_KC / 16; ++k) {
@@ -196,7 +199,7 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
         }
     } else if (warp >= 4) {
         // ---- epilogue: 8 warps, warp quarter = TMEM lanes (a warp may only read lanes 32 (warp % 4) ...), warp half =
-        // columns 0-63 or 64-127 of the tile; a query row therefore has two candidate lists, merged by the caller ------
+        // columns 0-127 or 128-255 of the tile; a query row therefore has two candidate lists, merged by the caller ------
         const int ew = warp - 4, wq = ew & 3, half = ew >> 2;
         const int row = blockIdx.x * CB_KNN_TM + wq * 32 + lane;
         float val[CAND];
@@ -204,36 +207,33 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
 #pragma unroll
         for (int c = 0; c < CAND; ++c) { val[c] = 3.0e38f; idx[c] = -1; }
         bool ok = true;
-        // |e|^2 of the warp's 64 columns goes through the warp's own piece of shared memory (broadcast reads; no barrier
+        // |e|^2 of the warp's 128 columns goes through the warp's own piece of shared memory (broadcast reads; no barrier
         // between warps, so a warp that gives up on a wait cannot leave the others stuck).  Columns past the end of the
         // cloud get a huge norm and never enter a list.  The values of the next tile are fetched while this one is processed.
         float* my_e2 = s_e2[ew];
         float* my_sc = scratch + ew * 1024;                       // [32 columns][32 lanes] of the group being inserted
-        float e2a = 3.0e38f, e2b = 3.0e38f;
-        if (ntiles > 0) {
-            const int col = t0 * CB_KNN_TN + half * 64 + lane;
-            if (col < a.ne) e2a = __ldg(a.e2 + col);
-            if (col + 32 < a.ne) e2b = __ldg(a.e2 + col + 32);
+        float e2v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int col = t0 * CB_KNN_TN + half * 128 + u * 32 + lane;
+            e2v[u] = (ntiles > 0 && col < a.ne) ? __ldg(a.e2 + col) : 3.0e38f;
         }
         for (int t = 0; t < ntiles && ok; ++t) {
             const int buf = t & 1;
             const unsigned int tph = (unsigned)(t >> 1) & 1u;
             __syncwarp();                                          // the previous tile's reads are done
-            my_e2[lane] = e2a;
-            my_e2[lane + 32] = e2b;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) my_e2[u * 32 + lane] = e2v[u];
             __syncwarp();
-            e2a = 3.0e38f; e2b = 3.0e38f;
-            if (t + 1 < ntiles) {
-                const int col = (t0 + t + 1) * CB_KNN_TN + half * 64 + lane;
-                if (col < a.ne) e2a = __ldg(a.e2 + col);
-                if (col + 32 < a.ne) e2b = __ldg(a.e2 + col + 32);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int col = (t0 + t + 1) * CB_KNN_TN + half * 128 + u * 32 + lane;
+                e2v[u] = (t + 1 < ntiles && col < a.ne) ? __ldg(a.e2 + col) : 3.0e38f;
             }
             // the verdict of the wait is taken by the whole warp: the votes further down need all 32 lanes
             const bool arrived = !(*(volatile int*)&s_abort) && cbk_wait(bar_tfull + 8 * buf, tph);
             if (!__all_sync(0xffffffffu, arrived)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            unsigned int r[64];
-            const unsigned int taddr = tmem_base + ((unsigned)(wq * 32) << 16) + (unsigned)(buf * CB_KNN_TN + half * 64);
 #define CBK_LD32(R, ADDR)                                                                                                  \
             asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                         \
                          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                         \
@@ -244,59 +244,66 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
                            "=r"(R[22]), "=r"(R[23]), "=r"(R[24]), "=r"(R[25]), "=r"(R[26]), "=r"(R[27]), "=r"(R[28]),      \
                            "=r"(R[29]), "=r"(R[30]), "=r"(R[31])                                                           \
                          : "r"(ADDR) : "memory")
-            CBK_LD32((r), taddr);
-            CBK_LD32((r + 32), taddr + 32u);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            // the accumulator is in registers now: hand the TMEM buffer back before the selection work
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_tempty + 8 * buf) : "memory");
-            const int cbase = (t0 + t) * CB_KNN_TN + half * 64;
-            const float4* e4 = reinterpret_cast<const float4*>(my_e2);
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                float sc[32];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float4 e = e4[c * 8 + j];
-                    sc[4 * j + 0] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 0]), e.x);
-                    sc[4 * j + 1] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 1]), e.y);
-                    sc[4 * j + 2] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 2]), e.z);
-                    sc[4 * j + 3] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 3]), e.w);
+            const unsigned int taddr = tmem_base + ((unsigned)(wq * 32) << 16) + (unsigned)(buf * CB_KNN_TN + half * 128);
+#pragma unroll 1
+            for (int pass = 0; pass < 2; ++pass) {                  // 64 of the warp's 128 columns at a time
+                unsigned int r[64];
+                CBK_LD32((r), taddr + (unsigned)(pass * 64));
+                CBK_LD32((r + 32), taddr + (unsigned)(pass * 64 + 32));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (pass == 1) {
+                    // the whole accumulator has been read: hand the TMEM buffer back before the selection work
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_tempty + 8 * buf) : "memory");
                 }
-                // smallest score of the 32 by a tree of minima: most groups hold nothing below the list's worst entry
-                float m[16];
+                const int cbase = (t0 + t) * CB_KNN_TN + half * 128 + pass * 64;
+                const float4* e4 = reinterpret_cast<const float4*>(my_e2 + pass * 64);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) m[j] = fminf(sc[2 * j], sc[2 * j + 1]);
+                for (int c = 0; c < 2; ++c) {
+                    float sc[32];
 #pragma unroll
-                for (int w = 8; w > 0; w >>= 1)
-#pragma unroll
-                    for (int j = 0; j < w; ++j) m[j] = fminf(m[j], m[j + w]);
-                // A thread's list changes about 16 ln(columns / 16) times in a whole scan, so a group of 32 columns holds
-                // two or three insertions per warp on average.  The insertion is a compact loop, not 32 unrolled copies
-                // (those ran into instruction-fetch stalls: 12.6 stalled cycles per issue): the group's scores go to the
-                // warp's scratch in shared memory, every lane keeps a bit mask of its columns below the worst entry, and
-                // the warp loops while any lane has a bit left, one sorted insertion (75 predicated instructions) a turn.
-                if (__any_sync(0xffffffffu, m[0] < val[CAND - 1])) {
-                    unsigned int hm = 0u;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        my_sc[j * 32 + lane] = sc[j];
-                        hm |= (sc[j] < val[CAND - 1]) ? (1u << j) : 0u;
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 e = e4[c * 8 + j];
+                        sc[4 * j + 0] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 0]), e.x);
+                        sc[4 * j + 1] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 1]), e.y);
+                        sc[4 * j + 2] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 2]), e.z);
+                        sc[4 * j + 3] = fmaf(-2.0f, __uint_as_float(r[c * 32 + 4 * j + 3]), e.w);
                     }
-                    while (__any_sync(0xffffffffu, hm != 0u)) {
-                        if (hm) {
-                            const int j = __ffs(hm) - 1;
-                            hm &= hm - 1u;
-                            const float sv = my_sc[j * 32 + lane];
-                            if (sv < val[CAND - 1]) { val[CAND - 1] = sv; idx[CAND - 1] = cbase + c * 32 + j; }
-                        }
+                    // smallest score of the 32 by a tree of minima: most groups hold nothing below the list's worst entry
+                    float m[16];
 #pragma unroll
-                        for (int q = CAND - 1; q > 0; --q) {
-                            const bool sw = val[q] < val[q - 1];
-                            const float lo = sw ? val[q] : val[q - 1], hi = sw ? val[q - 1] : val[q];
-                            const int li = sw ? idx[q] : idx[q - 1], hi_i = sw ? idx[q - 1] : idx[q];
-                            val[q - 1] = lo; val[q] = hi; idx[q - 1] = li; idx[q] = hi_i;
+                    for (int j = 0; j < 16; ++j) m[j] = fminf(sc[2 * j], sc[2 * j + 1]);
+#pragma unroll
+                    for (int w = 8; w > 0; w >>= 1)
+#pragma unroll
+                        for (int j = 0; j < w; ++j) m[j] = fminf(m[j], m[j + w]);
+                    // A thread's list changes about CAND ln(columns / CAND) times in a whole scan, so a group of 32 columns
+                    // holds a few insertions per warp.  The insertion is a compact loop, not 32 unrolled copies (those ran
+                    // into instruction-fetch stalls: 12.6 stalled cycles per issue): the group's scores go to the warp's
+                    // scratch in shared memory, every lane keeps a bit mask of its columns below the worst entry, and the
+                    // warp loops while any lane has a bit left, one sorted insertion a turn.
+                    if (__any_sync(0xffffffffu, m[0] < val[CAND - 1])) {
+                        unsigned int hm = 0u;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            my_sc[j * 32 + lane] = sc[j];
+                            hm |= (sc[j] < val[CAND - 1]) ? (1u << j) : 0u;
+                        }
+                        while (__any_sync(0xffffffffu, hm != 0u)) {
+                            if (hm) {
+                                const int j = __ffs(hm) - 1;
+                                hm &= hm - 1u;
+                                const float sv = my_sc[j * 32 + lane];
+                                if (sv < val[CAND - 1]) { val[CAND - 1] = sv; idx[CAND - 1] = cbase + c * 32 + j; }
+                            }
+#pragma unroll
+                            for (int q = CAND - 1; q > 0; --q) {
+                                const bool sw = val[q] < val[q - 1];
+                                const float lo = sw ? val[q] : val[q - 1], hi = sw ? val[q - 1] : val[q];
+                                const int li = sw ? idx[q] : idx[q - 1], hi_i = sw ? idx[q - 1] : idx[q];
+                                val[q - 1] = lo; val[q] = hi; idx[q - 1] = li; idx[q] = hi_i;
+                            }
                         }
                     }
                 }
@@ -317,7 +324,7 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (warp == 2)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
 }
 
 typedef CUresult (*CbkEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -340,12 +347,12 @@ static CbkEncodeTiled cbk_encode_tiled() {
     return fn;
 }
 
-static int cbk_make_map(CUtensorMap* tm, const void* base, long long rows, int dpad) {
+static int cbk_make_map(CUtensorMap* tm, const void* base, long long rows, int dpad, int box_rows) {
     CbkEncodeTiled enc = cbk_encode_tiled();
     if (!enc) return -2;
     const cuuint64_t gdim[2] = {(cuuint64_t)dpad, (cuuint64_t)rows};
     const cuuint64_t gstride[1] = {(cuuint64_t)dpad * 2};
-    const cuuint32_t box[2] = {CB_KNN_KC, CB_KNN_TN};
+    const cuuint32_t box[2] = {CB_KNN_KC, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -354,7 +361,7 @@ static int cbk_make_map(CUtensorMap* tm, const void* base, long long rows, int d
 }
 
 CB_API int cb_knn_candidates(void) { return CB_KNN_CAND; }
-// Largest dimension count (after padding to 64) the kernel takes; up to 384 the query tile stays in shared memory, above
+// Largest dimension count (after padding to 64) the kernel takes; up to 256 the query tile stays in shared memory, above
 // that its chunks are streamed with the cloud chunks.
 CB_API int cb_knn_max_dim(void) { return 4096; }
 
@@ -387,7 +394,7 @@ CB_API int cb_knn_tc(const void* Q, int nq, const void* E, int ne, int dpad, con
     if (dpad <= 0 || dpad % CB_KNN_KC != 0 || dpad > 4096 || splits < 1 || splits > 65535) return -2;
     if ((reinterpret_cast<unsigned long long>(Q) & 15ull) || (reinterpret_cast<unsigned long long>(E) & 15ull)) return -2;
     CUtensorMap tmq, tme;
-    if (cbk_make_map(&tmq, Q, nq, dpad) != 0 || cbk_make_map(&tme, E, ne, dpad) != 0) return -2;
+    if (cbk_make_map(&tmq, Q, nq, dpad, CB_KNN_TM) != 0 || cbk_make_map(&tme, E, ne, dpad, CB_KNN_TN) != 0) return -2;
     const int smem = CB_KNN_SMEM_BYTES;
     static unsigned long long set = 0ull;
     if (cb_first_on_device(&set)) {
