@@ -137,6 +137,7 @@ def _use_fast_engine(o, objective, store, dims) -> bool:
             and not o.langevin and not o.monotone_constraints and not o.model_shrink_rate
             and str(o.sampling_unit or "Object") == "Object"
             and not _has_penalties(o) and str(o.sampling_frequency or "PerTree") == "PerTree"
+            and getattr(objective, "target_columns", 1) == 1          # interval labels stay on the general learner
             and not getattr(objective, "pairwise_scoring", False)       # pairwise systems live in the general learner
             and str(o.random_score_type) != "Gumbel")
 

@@ -877,3 +877,32 @@ def test_embedding_knn_features_from_the_device_match_the_host():
     m.fit(X[:5000], cls[:5000], embedding_features=[1])
     acc = float((m.predict(X[5000:]).reshape(-1).astype(int) == cls[5000:]).mean())
     assert acc > 0.8, acc
+
+
+def test_objectives_without_device_formula_train_on_gpu():
+    """Survival, focal, multi-quantile and filter objectives on task_type='GPU' (general learner or external derivatives)."""
+    import catboost_b200 as cb
+    rng = np.random.default_rng(2)
+    n = 3000
+    X = rng.normal(size=(n, 5)).astype(np.float32)
+    t = np.exp(1.0 + 0.8 * X[:, 0] + 0.2 * rng.normal(size=n))
+    lo, up = t.copy(), t.copy()
+    up[: n // 3] = -1
+    lo[: n // 3] *= 0.7
+    kw = dict(iterations=40, depth=3, learning_rate=0.2, verbose=0, task_type="GPU", devices="0", allow_writing_files=False)
+    m = cb.CatBoostRegressor(loss_function="SurvivalAft:dist=Normal;scale=0.5", **kw).fit(X, np.stack([lo, up], 1).astype(np.float32))
+    assert np.corrcoef(m.predict(X), np.log(t))[0, 1] > 0.9
+    risk = X[:, 0] - 0.5 * X[:, 1]
+    time = rng.exponential(np.exp(-risk)) + 0.01
+    yc = np.where(rng.random(n) < 0.25, -time, time).astype(np.float32)
+    m = cb.CatBoostRegressor(loss_function="Cox", **kw).fit(X, yc)
+    assert np.corrcoef(m.predict(X), risk)[0, 1] > 0.7
+    yb = (risk + 0.3 * rng.normal(size=n) > 0).astype(np.float32)
+    m = cb.CatBoostClassifier(loss_function="Focal:focal_alpha=0.5;focal_gamma=2", **kw).fit(X, yb)
+    assert (m.predict(X).astype(np.float32).reshape(-1) == yb).mean() > 0.85
+    yq = (X[:, 0] + rng.normal(size=n)).astype(np.float32)
+    m = cb.CatBoostRegressor(loss_function="MultiQuantile:alpha=0.1,0.9", **kw).fit(X, yq)
+    pr = m.predict(X)
+    assert abs((yq <= pr[:, 0]).mean() - 0.1) < 0.06 and abs((yq <= pr[:, 1]).mean() - 0.9) < 0.06
+    m = cb.CatBoostRegressor(first_feature_use_penalties={0: 1e9}, **kw).fit(X, yq)
+    assert m.get_feature_importance()[0] == 0
