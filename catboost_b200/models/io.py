@@ -490,6 +490,9 @@ def _export_arrays(m: Model):
 
 
 def model_to_python(m: Model) -> str:
+    if not m._float_only_oblivious():
+        from .codegen import model_to_python_general          # categorical features: hash, CTR tables and trees inlined
+        return model_to_python_general(m)
     p = _export_arrays(m)
     lines = ["# Stand-alone apply code generated by catboost_b200", "import bisect", "",
              f"USED_FEATURES = {[int(m.float_features[int(f)].flat_index) for f in p['used']]}",
@@ -511,6 +514,9 @@ def model_to_python(m: Model) -> str:
 
 
 def model_to_cpp(m: Model) -> str:
+    if not m._float_only_oblivious():
+        from .codegen import model_to_cpp_general
+        return model_to_cpp_general(m)
     p = _export_arrays(m)
     def arr(name, ctype, vals):
         return f"static const {ctype} {name}[] = {{{', '.join(str(v) for v in vals)}}};"

@@ -1453,3 +1453,51 @@ def test_eval_package_and_dataset_cache(tmp_path):
     assert list(tr.columns) == ["PassengerId", "Survived", "Sex"] and len(te) == 1
     m = cb.CatBoostRegressor(iterations=3, depth=2)
     assert m.get_init_params() == {"iterations": 3, "depth": 2}
+
+
+def test_code_export_with_categorical_features(tmp_path):
+    """Stand-alone Python and C++ apply code of a model with float, one-hot and CTR splits against predict()."""
+    import pandas as pd
+    from catboost_b200.data.cat_hash import hash_strings
+    rng = np.random.default_rng(0)
+    n = 1500
+    Xn = rng.normal(size=(n, 3)).astype(np.float32)
+    Xn[rng.random((n, 3)) < 0.05] = np.nan
+    cat1 = rng.integers(0, 40, n)
+    cat2 = rng.choice(["red", "green", "blue"], n)
+    y = ((np.nan_to_num(Xn[:, 0]) + (cat1 % 3 == 0) * 1.0 + (cat2 == "red") * 0.7 + 0.3 * rng.normal(size=n)) > 0.5).astype(int)
+    df = pd.DataFrame({"a": Xn[:, 0], "k1": cat1.astype(str), "b": Xn[:, 1], "k2": cat2, "c": Xn[:, 2]})
+    m = cb.CatBoostClassifier(iterations=30, depth=4, verbose=0, allow_writing_files=False, one_hot_max_size=4)
+    m.fit(df, y, cat_features=["k1", "k2"])
+    assert {s.kind for s in m._model.splits} == {"float", "onehot", "ctr"}
+    raw = m.predict(df, prediction_type="RawFormulaVal")
+    py = tmp_path / "model.py"
+    m.save_model(str(py), format="python")
+    ns = {}
+    exec(py.read_text(), ns)
+    # the pure-Python CityHash of the generated code against the native one, over every length class of the algorithm
+    strs = ["", "a", "abcd", "abcdefgh", "x" * 15, "y" * 17, "z" * 33, "w" * 64, "q" * 65, "long " * 50, "ünï"] + [str(i) for i in range(50)]
+    assert [int(h) for h in hash_strings(strs)] == [ns["calc_cat_feature_hash"](s) for s in strs]
+    got = [ns["apply_catboost_model"]([float(r.a), float(r.b), float(r.c)], [r.k1, r.k2]) for r in df.iloc[:150].itertuples()]
+    assert np.max(np.abs(np.array(got) - raw[:150])) < 1e-9
+    import shutil
+    if shutil.which("g++") is None:
+        return
+    m.save_model(str(tmp_path / "model.cpp"), format="cpp")
+    (tmp_path / "main.cpp").write_text(r'''
+#include <cstdio>
+#include <cstdlib>
+#include "model.cpp"
+int main() {
+    char k1[64], k2[64], fa[64], fb[64], fc[64];
+    while (scanf("%63s %63s %63s %63s %63s", fa, k1, fb, k2, fc) == 5) {
+        std::vector<float> f = {(float)atof(fa), (float)atof(fb), (float)atof(fc)};
+        std::vector<std::string> c = {k1, k2};
+        printf("%.12g\n", ApplyCatboostModel(f, c)[0]);
+    }
+}
+''')
+    subprocess.check_call(["g++", "-O1", "-std=c++17", "-o", str(tmp_path / "app"), str(tmp_path / "main.cpp")], cwd=tmp_path)
+    inp = "\n".join(f"{r.a:.9g} {r.k1} {r.b:.9g} {r.k2} {r.c:.9g}" for r in df.iloc[:150].itertuples())
+    out = subprocess.run([str(tmp_path / "app")], input=inp.encode(), capture_output=True, check=True).stdout.decode().split()
+    assert np.max(np.abs(np.array([float(v) for v in out]) - raw[:150])) < 1e-7
