@@ -44,8 +44,40 @@ class GpuPredictor:
     """Model arrays resident on one GPU; ``predict`` may be called repeatedly (its staging buffers are kept between
     calls when they are below 1 GiB of pinned memory)."""
 
-    def __init__(self, model, device=None):
-        p = model._packed_oblivious()
+    # used features one launch of the quantising kernel can hold (one byte per feature and row of a 256-row block plus the
+    # staged borders, within 224 KB of shared memory); models above it are evaluated as a sum of tree ranges
+    MAX_USED = 700
+
+    @staticmethod
+    def _slice_packed(p, t0, t1):
+        """The packed arrays of trees [t0, t1) as a model of their own: only the features those trees use."""
+        depth = np.asarray(p["depth"])[t0:t1]
+        s0 = int(np.asarray(p["soff"])[t0])
+        s1 = s0 + int(depth.sum())
+        sfeat_old = np.asarray(p["sfeat"], dtype=np.int64)[s0:s1]
+        keep = np.unique(sfeat_old)                                   # positions in the full model's used list
+        remap = np.full(len(p["used"]), -1, dtype=np.int64)
+        remap[keep] = np.arange(len(keep))
+        boff = np.asarray(p["boff"], dtype=np.int64)
+        borders = np.asarray(p["borders"], dtype=np.float32)
+        nb = (boff[keep + 1] - boff[keep]) if len(keep) else np.zeros(0, dtype=np.int64)
+        new_boff = np.zeros(len(keep) + 1, dtype=np.int32)
+        new_boff[1:] = np.cumsum(nb)
+        new_borders = np.concatenate([borders[boff[k]:boff[k + 1]] for k in keep]) if len(keep) else np.zeros(1, np.float32)
+        l0 = int(np.asarray(p["loff"])[t0])
+        leaves = (1 << depth.astype(np.int64))
+        loff = np.zeros(len(depth), dtype=np.int64)
+        loff[1:] = np.cumsum(leaves)[:-1]
+        soff = np.zeros(len(depth), dtype=np.int32)
+        soff[1:] = np.cumsum(depth)[:-1]
+        return dict(T=int(t1 - t0), used=np.asarray(p["used"])[keep].astype(np.int32), borders=new_borders, boff=new_boff,
+                    depth=depth.astype(np.int32), soff=soff, sfeat=remap[sfeat_old].astype(np.uint16),
+                    sbin=np.asarray(p["sbin"])[s0:s1], loff=loff,
+                    vals=np.ascontiguousarray(np.asarray(p["vals"])[l0:l0 + int(leaves.sum())]),
+                    nanmax=np.asarray(p["nanmax"])[keep])
+
+    def __init__(self, model, device=None, packed=None, with_bias=True):
+        p = packed if packed is not None else model._packed_oblivious()
         self.dev = torch.device(device if device is not None else "cuda")
         if self.dev.index is None:
             self.dev = torch.device("cuda", torch.cuda.current_device())
@@ -59,7 +91,7 @@ class GpuPredictor:
         boff = np.asarray(p["boff"], dtype=np.int64)
         self.max_borders = int(np.diff(boff).max()) if len(boff) > 1 else 1
         self.scale = float(model.scale)
-        self.bias = t(np.broadcast_to(model.bias, (model.dims,)), np.float32)
+        self.bias = t(np.broadcast_to(model.bias if with_bias else np.zeros(1), (model.dims,)), np.float32)
         if self.dims > 8:
             raise ValueError("GPU apply supports up to 8 prediction dimensions")
         self.lib = native.cuda_lib()
@@ -81,12 +113,33 @@ class GpuPredictor:
             nanmax_col[used] = np.asarray(p["nanmax"], dtype=np.uint8)
             self.wide = dict(col=t(used[sfeat], np.int32), border=t(np.asarray(p["borders"], dtype=np.float32)[boff[sfeat] + sbin]),
                              nanmax=t(nanmax_col) if nanmax_col.any() else None)
+        # Too many used features for one launch of either kernel (2000 columns: the raw-value kernel's row tile does not
+        # fit either): consecutive tree ranges that each use at most MAX_USED features, outputs summed.
+        self.parts = None
+        if self.wide is None and self.U > self.MAX_USED:
+            ranges, t0, seen = [], 0, set()
+            soff_h, depth_h = np.asarray(p["soff"], dtype=np.int64), np.asarray(p["depth"], dtype=np.int64)
+            for tr in range(self.T):
+                feats = set(sfeat[soff_h[tr]:soff_h[tr] + depth_h[tr]].tolist())
+                if len(seen | feats) > self.MAX_USED and tr > t0:
+                    ranges.append((t0, tr))
+                    t0, seen = tr, set()
+                seen |= feats
+            ranges.append((t0, self.T))
+            self.parts = [GpuPredictor(model, self.dev, packed=self._slice_packed(p, a, b), with_bias=(k == 0))
+                          for k, (a, b) in enumerate(ranges)]
 
     def predict_device(self, X: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
         """X: float32 [n, F] on the device (row stride arbitrary).  Returns float32 [dims, n]."""
         n = X.shape[0]
         if out is None:
             out = torch.empty((self.dims, n), dtype=torch.float32, device=self.dev)
+        if self.parts is not None:
+            self.parts[0].predict_device(X, out)
+            tmp = torch.empty_like(out)
+            for part in self.parts[1:]:
+                out += part.predict_device(X, tmp)
+            return out
         P = lambda a: ctypes.c_void_p(a.data_ptr()) if a is not None else None
         st = ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
         if self.wide is not None and X.shape[1] >= self.F_stage and X.stride(1) == 1:

@@ -906,3 +906,23 @@ def test_objectives_without_device_formula_train_on_gpu():
     assert abs((yq <= pr[:, 0]).mean() - 0.1) < 0.06 and abs((yq <= pr[:, 1]).mean() - 0.9) < 0.06
     m = cb.CatBoostRegressor(first_feature_use_penalties={0: 1e9}, **kw).fit(X, yq)
     assert m.get_feature_importance()[0] == 0
+
+
+def test_gpu_apply_of_model_with_more_used_features_than_one_launch_holds():
+    """2000 columns and about a thousand used features: neither apply kernel takes the model in one launch, so it is
+    evaluated as a sum of tree ranges."""
+    import catboost_b200 as cb
+    from catboost_b200.models.gpu_apply import GpuPredictor
+    rng = np.random.default_rng(9)
+    n, F = 3000, 2000
+    X = rng.standard_normal((n, F)).astype(np.float32)
+    y = (X[:, :50].sum(1) + rng.standard_normal(n) * 3 > 0).astype(np.float32)
+    m = cb.CatBoostClassifier(iterations=300, depth=6, learning_rate=0.1, verbose=False, allow_writing_files=False,
+                              task_type="GPU", devices="0", random_strength=5.0)
+    m.fit(X, y)
+    pred = GpuPredictor(m._model, torch.device("cuda", 0))
+    assert pred.U > GpuPredictor.MAX_USED and pred.parts is not None and len(pred.parts) >= 2
+    assert all(p.U <= GpuPredictor.MAX_USED for p in pred.parts)
+    host = m.predict(X, prediction_type="RawFormulaVal")
+    dev = m.predict(X, prediction_type="RawFormulaVal", task_type="GPU")
+    assert np.max(np.abs(host - dev)) < 1e-4
