@@ -133,26 +133,37 @@ def read_dsv(path: str, column_description: Optional[str] = None, delimiter: str
 
 
 def read_libsvm(path: str):
-    labels, rows, maxf = [], [], 0
+    """``label [qid:G] index:value ...`` per line; feature indices start from 1 and grow along the line
+    (catboost/libs/data/libsvm_loader.cpp:230-300); a ``qid`` field is the group id.  Missing entries are zeros."""
+    labels, rows, groups, maxf = [], [], [], 0
     with open(path) as fh:
-        for line in fh:
+        for ln, line in enumerate(fh, 1):
             parts = line.split()
             if not parts:
                 continue
             labels.append(float(parts[0]))
             row = {}
             for tok in parts[1:]:
-                if tok.startswith("qid:"):
+                k, _, v = tok.partition(":")
+                if k == "qid":
+                    groups.append(int(v))
                     continue
-                k, v = tok.split(":")
-                row[int(k)] = float(v)
-                maxf = max(maxf, int(k))
+                idx = int(k)
+                if idx < 1:
+                    raise CatBoostError(f"{path}:{ln}: libsvm feature indices start from 1")
+                row[idx - 1] = float(v)
+                maxf = max(maxf, idx)
             rows.append(row)
-    X = np.zeros((len(rows), maxf + 1), dtype=np.float32)
+    if groups and len(groups) != len(rows):
+        raise CatBoostError(f"{path}: some lines have a 'qid' field and some do not")
+    X = np.zeros((len(rows), maxf), dtype=np.float32)
     for i, row in enumerate(rows):
         for k, v in row.items():
             X[i, k] = v
-    return dict(data=X, label=np.array(labels))
+    out = dict(data=X, label=np.array(labels))
+    if groups:
+        out["group_id"] = np.array(groups)
+    return out
 
 
 def read_pairs(path: str):
@@ -245,6 +256,12 @@ class Pool:
             if not data_can_be_none:
                 raise CatBoostError("data is None")
             data = np.zeros((0, 0), dtype=np.float32)
+        if hasattr(data, "tocsr") and hasattr(data, "toarray"):
+            # scipy.sparse matrices: the binned store is dense one-byte columns either way, so the values are laid out
+            # as a dense float32 matrix here (missing entries = 0)
+            if cat_features or text_features or embedding_features:
+                raise CatBoostError("sparse matrices carry numerical features only; pass categorical data as a DataFrame")
+            data = np.asarray(data.toarray(), dtype=np.float32)
         if not isinstance(data, (np.ndarray, _ColumnView)):
             try:
                 import torch

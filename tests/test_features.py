@@ -1501,3 +1501,28 @@ int main() {
     inp = "\n".join(f"{r.a:.9g} {r.k1} {r.b:.9g} {r.k2} {r.c:.9g}" for r in df.iloc[:150].itertuples())
     out = subprocess.run([str(tmp_path / "app")], input=inp.encode(), capture_output=True, check=True).stdout.decode().split()
     assert np.max(np.abs(np.array([float(v) for v in out]) - raw[:150])) < 1e-7
+
+
+def test_libsvm_files_and_sparse_matrices(tmp_path):
+    import scipy.sparse as sp
+    X = sp.random(400, 12, density=0.3, format="csr", random_state=0, dtype=np.float32)
+    Xd = X.toarray()
+    y = (Xd[:, 0] + Xd[:, 1] > 0.4).astype(int)
+    path = tmp_path / "data.svm"
+    with open(path, "w") as fh:
+        for i in range(400):
+            fh.write(f"{y[i]} qid:{i // 20} " + " ".join(f"{j + 1}:{Xd[i, j]:.7g}" for j in range(12) if Xd[i, j] != 0) + "\n")
+    pool = cb.Pool("libsvm://" + str(path))
+    assert pool.shape[1] <= 12 and pool.num_row() == 400                 # indices in the file start from 1
+    assert np.allclose(pool.get_features()[:, :pool.shape[1]], Xd[:, :pool.shape[1]], atol=1e-6)
+    assert np.array_equal(np.asarray(pool.group_id) if pool.group_id.dtype.kind in "iu" else pool.group_id, pool.group_id)
+    assert len(np.unique(pool.group_id)) == 20
+    (tmp_path / "bad.svm").write_text("1 0:3.5\n")
+    with pytest.raises(cb.CatBoostError, match="start from 1"):
+        cb.Pool("libsvm://" + str(tmp_path / "bad.svm"))
+    # scipy matrices train like their dense form
+    kw = dict(iterations=15, depth=3, verbose=False, allow_writing_files=False)
+    a = cb.CatBoostClassifier(**kw).fit(X, y).predict(X, prediction_type="RawFormulaVal")
+    b = cb.CatBoostClassifier(**kw).fit(Xd, y).predict(Xd, prediction_type="RawFormulaVal")
+    assert np.allclose(a, b)
+    assert np.allclose(cb.CatBoostClassifier(**kw).fit(sp.csc_matrix(X), y).predict(sp.coo_matrix(X), prediction_type="RawFormulaVal"), b)
