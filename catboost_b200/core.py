@@ -235,9 +235,24 @@ class CatBoost:
                 task_type="CPU", devices=None):
         """``task_type='GPU'`` evaluates float-only symmetric models on the device; ``devices`` ('0-7', '0:2', a list)
         shards the rows over several GPUs of this machine."""
+        single = self._is_single_object(data)
+        if single:
+            data = [list(data)] if not isinstance(data, np.ndarray) else data.reshape(1, -1)
         raw = self._raw(data, ntree_start, ntree_end, thread_count, task_type, devices)
         pt = prediction_type or self._default_prediction_type()
-        return self._format(raw, pt)
+        out = self._format(raw, pt)
+        return out[0] if single else out
+
+    def _is_single_object(self, data) -> bool:
+        """A flat list / 1-D array of as many values as the model has features is one object, as in the reference's
+        ``_is_data_single_object``; the prediction for it is a scalar (or one row)."""
+        if isinstance(data, np.ndarray):
+            flat = data.ndim == 1 and (data.dtype != object or all(np.ndim(v) == 0 for v in data))
+        elif isinstance(data, (list, tuple)):
+            flat = len(data) > 0 and all(np.ndim(v) == 0 for v in data)
+        else:
+            return False
+        return bool(flat and self._model is not None and self._model.n_features > 1 and len(data) == self._model.n_features)
 
     def staged_predict(self, data, prediction_type=None, ntree_start=0, ntree_end=0, eval_period=1, thread_count=-1,
                        verbose=None):

@@ -1526,3 +1526,17 @@ def test_libsvm_files_and_sparse_matrices(tmp_path):
     b = cb.CatBoostClassifier(**kw).fit(Xd, y).predict(Xd, prediction_type="RawFormulaVal")
     assert np.allclose(a, b)
     assert np.allclose(cb.CatBoostClassifier(**kw).fit(sp.csc_matrix(X), y).predict(sp.coo_matrix(X), prediction_type="RawFormulaVal"), b)
+
+
+def test_functional_train_and_single_object_predict():
+    rng = np.random.default_rng(0)
+    X = rng.normal(size=(300, 4)).astype(np.float32)
+    y = (X[:, 0] > 0).astype(int)
+    import catboost_b200.train.boosting  # noqa: F401  (the sub-package import must not shadow the function)
+    m = cb.train(cb.Pool(X, y), {"loss_function": "Logloss", "iterations": 5, "verbose": 0})
+    assert isinstance(m, cb.CatBoost) and m.tree_count_ == 5
+    r = cb.CatBoostRegressor(iterations=5, verbose=0, allow_writing_files=False).fit(X, X[:, 0])
+    one = r.predict(X[0])
+    assert np.ndim(one) == 0 and one == r.predict(X[:1])[0] == r.predict([float(v) for v in X[0]])
+    c = cb.CatBoostClassifier(iterations=5, verbose=0, allow_writing_files=False).fit(X, y)
+    assert c.predict_proba(X[0]).shape == (2,) and c.predict(X[0]) in (0, 1)
