@@ -252,21 +252,53 @@ def mode_model_sum(argv):
 
 def mode_normalize_model(argv):
     ap = argparse.ArgumentParser(prog="catboost_b200 normalize-model")
-    ap.add_argument("-m", "--model-file", default="model.bin")
+    ap.add_argument("-m", "--model-file", "--model-path", dest="model_file", default="model.bin")
     ap.add_argument("--set-scale", type=float)
     ap.add_argument("--set-bias", type=float)
     ap.add_argument("-o", "--output-model")
+    ap.add_argument("--output-model-format", default=None)
     ap.add_argument("--print-scale-and-bias", action="store_true")
+    ap.add_argument("-i", "--input-path", action="append", default=[],
+                    help="pool(s): scale and bias are chosen so that the model's values on them span [0, 1]")
+    ap.add_argument("--column-description", "--cd", dest="cd")
+    ap.add_argument("--delimiter", default="\t")
+    ap.add_argument("--has-header", action="store_true")
+    ap.add_argument("-T", "--thread-count", type=int, default=-1)
+    ap.add_argument("--logging-level", default="Info")
     args = ap.parse_args(argv)
     from .core import CatBoost
+    from .data.pool import CatBoostError
     model = CatBoost().load_model(args.model_file)
     scale, bias = model.get_scale_and_bias()
-    if args.set_scale is not None or args.set_bias is not None:
+    before = (scale, bias)
+    if args.print_scale_and_bias:
+        print(f"Input model scale {scale} bias {bias}")
+    if args.input_path:
+        # catboost/app/mode_normalize_model.cpp: minimum and maximum of the unscaled model over all pools
+        if args.set_scale is not None or args.set_bias is not None:
+            raise CatBoostError("Conflicting options: -i and --set-scale/bias")
+        model.set_scale_and_bias(1.0, 0.0)
+        lo, hi = float("inf"), float("-inf")
+        for path in args.input_path:
+            raw = np.asarray(model.predict(_pool(path, args), prediction_type="RawFormulaVal"))
+            if raw.ndim != 1:
+                raise CatBoostError("No sense in normalizing a multiclass/multitarget model")
+            lo, hi = min(lo, float(raw.min())), max(hi, float(raw.max()))
+        if not lo < hi:
+            raise CatBoostError("Model gives same result on all docs")
+        model.set_scale_and_bias(1.0 / (hi - lo), -lo / (hi - lo))
+    else:
         model.set_scale_and_bias(args.set_scale if args.set_scale is not None else scale,
                                  args.set_bias if args.set_bias is not None else bias)
-        model.save_model(args.output_model or args.model_file)
-    if args.print_scale_and_bias:
-        print(model.get_scale_and_bias())
+    after = model.get_scale_and_bias()
+    if after != before or args.output_model:
+        if args.print_scale_and_bias:
+            print(f"Output model scale {after[0]} bias {after[1]}")
+        out = args.output_model or args.model_file
+        if args.output_model_format:
+            model.save_model(out, format=args.output_model_format.lower().replace("catboostbinary", "cbm"))
+        else:
+            model.save_model(out)
     return 0
 
 
@@ -278,6 +310,11 @@ def mode_select_features(argv):
     ap.add_argument("--num-features-to-select", type=int, required=True)
     ap.add_argument("--features-selection-steps", type=int, default=1)
     ap.add_argument("--features-selection-result-path", default="selection_result.json")
+    ap.add_argument("--features-selection-algorithm", default="RecursiveByShapValues")
+    ap.add_argument("--shap-calc-type", default="Regular")
+    ap.add_argument("--train-final-model", action="store_true")
+    ap.add_argument("-m", "--model-file", default=None, help="where the final model goes with --train-final-model")
+    ap.add_argument("--verbose", type=int, default=0)
     ap.add_argument("--use-best-model")
     ap.add_argument("--save-snapshot", action="store_true")
     for flag, typ, dest in _FIT_PARAMS:
@@ -291,9 +328,16 @@ def mode_select_features(argv):
             feats += list(range(int(a), int(b) + 1))
         else:
             feats.append(int(tok))
-    est = CatBoost({**_fit_params(args), "verbose": False})
-    res = est.select_features(_pool(args.learn_set, args), features_for_select=feats,
-                              num_features_to_select=args.num_features_to_select, steps=args.features_selection_steps)
+    fp = _fit_params(args)
+    extra = {} if fp.get("train_dir") else {"allow_writing_files": False}
+    est = CatBoost({**fp, "verbose": bool(args.verbose), **extra})
+    evals = [_pool(t, args) for t in args.test_set]
+    res = est.select_features(_pool(args.learn_set, args), eval_set=evals[0] if evals else None, features_for_select=feats,
+                              num_features_to_select=args.num_features_to_select, steps=args.features_selection_steps,
+                              algorithm=args.features_selection_algorithm, shap_calc_type=args.shap_calc_type,
+                              train_final_model=args.train_final_model, logging_level="Verbose" if args.verbose else "Silent")
+    if args.train_final_model and args.model_file:
+        est.save_model(args.model_file)
     with open(args.features_selection_result_path, "w") as fh:
         json.dump(res, fh)
     return 0
