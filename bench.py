@@ -27,7 +27,8 @@ import time
 
 import numpy as np
 
-BASELINE_S_PER_1000 = {"higgs": 55.601, "epsilon": 44.971, "small": None, "criteo": None, "ranking": None, "sparse": None}
+BASELINE_S_PER_1000 = {"higgs": 55.601, "epsilon": 44.971, "small": None, "criteo": None, "ranking": None, "sparse": None,
+                       "airline": 485.825, "msrank": 11.057, "synthetic": 36.658, "synthetic5k": 28.014}
 CONFIGS = {
     # rows, float features, depth, border_count
     "higgs": dict(rows=10_500_000, features=28, depth=6, border_count=128, model="Logloss symmetric depth6 10.5Mx28"),
@@ -40,6 +41,12 @@ CONFIGS = {
     # learning to rank: 2M documents x 700 features in groups of about 100, YetiRank, 64 borders; end-to-end fit() only
     "ranking": dict(rows=2_000_000, features=700, depth=6, border_count=64, model="YetiRank symmetric depth6 2Mx700"),
     "criteo": dict(rows=45_000_000, features=39, depth=8, border_count=128, model="Logloss symmetric depth8 13num+26cat CTR"),
+    # the other shapes of the reference's training_speed benchmark (catboost/benchmarks/training_speed/README.md:207-228),
+    # as synthetic matrices of those sizes under Logloss
+    "airline": dict(rows=115_000_000, features=13, depth=6, border_count=128, model="Logloss symmetric depth6 115Mx13"),
+    "msrank": dict(rows=1_200_000, features=137, depth=6, border_count=128, model="Logloss symmetric depth6 1.2Mx137"),
+    "synthetic": dict(rows=10_000_000, features=100, depth=6, border_count=128, model="Logloss symmetric depth6 10Mx100"),
+    "synthetic5k": dict(rows=100_000, features=5000, depth=6, border_count=128, model="Logloss symmetric depth6 100Kx5000"),
     # the CPU plumbing config: 100K x 50, 200 iterations, task_type CPU; runs without a GPU (wall time of fit())
     "cpu": dict(rows=100_000, features=50, depth=6, border_count=128, model="Logloss symmetric depth6 100Kx50 on CPU"),
 }
