@@ -350,6 +350,151 @@ CBC_API void cbc_leaf_sums(const uint16_t* leaf, long long n, const float* cols,
     }
 }
 
+// Split scores of one level of a symmetric tree from the level's histograms: hist [L][S][TB] floats (S statistics: K
+// derivative sums, then the weight), out [F][B] floats.  Candidate (f, b): "bin <= b goes left" (one-hot: "bin != b goes
+// left"); every leaf contributes both sides; fn 0 = Cosine: sum s mu / sqrt(sum w mu^2) with mu = s / (w + l2),
+// fn 1 = L2: sum s^2 / (w + l2).  The same formulas as SplitScorer in train/generic.py (its oracle), accumulated in
+// doubles; positions that are no candidates (b >= candidates of f) get -3e38.
+CBC_API void cbc_symmetric_scores(const float* hist, int L, int S, int K, int TB, int F, const int* feat_off, const int* nb,
+                                  const unsigned char* onehot, int fn, double l2, int B, float* out) {
+#pragma omp parallel
+    {
+        std::vector<double> num, den, cum, tot;
+#pragma omp for schedule(dynamic, 1)
+        for (int f = 0; f < F; ++f) {
+            const int n = nb[f], off = feat_off[f];
+            const int ncand = onehot[f] ? n : n - 1;
+            num.assign((size_t)std::max(n, 1), 0.0);
+            den.assign((size_t)std::max(n, 1), 0.0);
+            cum.resize((size_t)(K + 1));
+            tot.resize((size_t)(K + 1));
+            for (int l = 0; l < L; ++l) {
+                const float* hl = hist + (size_t)l * S * TB + off;
+                for (int k = 0; k <= K; ++k) {
+                    double t = 0.0;
+                    const float* row = hl + (size_t)k * TB;
+                    for (int b = 0; b < n; ++b) t += (double)row[b];
+                    tot[k] = t;
+                    cum[k] = 0.0;
+                }
+                for (int b = 0; b < ncand; ++b) {
+                    double lw, rw;
+                    if (onehot[f]) {
+                        rw = (double)hl[(size_t)K * TB + b];
+                        lw = tot[K] - rw;
+                    } else {
+                        cum[K] += (double)hl[(size_t)K * TB + b];
+                        lw = cum[K];
+                        rw = tot[K] - lw;
+                    }
+                    lw = std::max(lw, 0.0);
+                    rw = std::max(rw, 0.0);
+                    for (int k = 0; k < K; ++k) {
+                        double ls, rs;
+                        if (onehot[f]) { rs = (double)hl[(size_t)k * TB + b]; ls = tot[k] - rs; }
+                        else { cum[k] += (double)hl[(size_t)k * TB + b]; ls = cum[k]; rs = tot[k] - ls; }
+                        if (fn == 0) {
+                            const double ml = lw > 0.0 ? ls / (lw + l2) : 0.0, mr = rw > 0.0 ? rs / (rw + l2) : 0.0;
+                            num[b] += ls * ml + rs * mr;
+                            den[b] += lw * ml * ml + rw * mr * mr;
+                        } else {
+                            num[b] += (lw > 1e-20 ? ls * ls / (lw + l2) : 0.0) + (rw > 1e-20 ? rs * rs / (rw + l2) : 0.0);
+                        }
+                    }
+                }
+            }
+            float* o = out + (size_t)f * B;
+            for (int b = 0; b < B; ++b) {
+                if (b >= ncand) { o[b] = -3.0e38f; continue; }
+                o[b] = fn == 0 ? (den[b] > 1e-15 ? (float)(num[b] / std::sqrt(den[b] + 1e-10)) : -3.0e38f) : (float)num[b];
+            }
+        }
+    }
+}
+
+// All Newton / gradient steps of the leaf estimation of one tree for the losses with a closed formula here (0 RMSE,
+// 1 Logloss, 2 CrossEntropy, 3 Poisson): per step one pass over the documents (loss value and derivatives at
+// approx + delta[leaf], per-leaf sums in per-thread doubles), then delta += sum der / (sum hess or sum weight + l2).
+// backtrack = 1 (AnyImprovement) / 2 (Armijo): a point whose loss fails the condition is dropped and the next pass tries
+// half the step from the last accepted point; a rejected try uses up one step (the step-length control of the general
+// learner's tensor formulation, which stays the path of every other loss and is the oracle of this routine).
+// Returns 0, or -1 when the loss has no formula here.  delta [L] (unscaled), leaf_w [L].
+CBC_API int cbc_leaf_newton(int loss, const float* approx, const float* target, const float* weight, const uint16_t* leaf,
+                            long long n, int L, int steps, int newton, double l2, int backtrack, double* delta,
+                            double* leaf_w) {
+    if (loss < 0 || loss > 3) return -1;
+    int nthreads = 1;
+#ifdef _OPENMP
+    nthreads = omp_get_max_threads();
+#endif
+    if (steps < 1) steps = 1;
+    if (steps == 1) backtrack = 0;
+    std::vector<std::vector<double>> priv(nthreads);
+    std::vector<float> dl((size_t)L, 0.0f), base((size_t)L, 0.0f), dir((size_t)L, 0.0f);
+    std::vector<double> sd((size_t)L), sh((size_t)L), sw((size_t)L);
+    for (int l = 0; l < L; ++l) { delta[l] = 0.0; leaf_w[l] = 0.0; }
+    double f_base = 0.0, dirgrad = 0.0, cur_step = 1.0;
+    bool have_w = false;
+    for (int step = 0; step < steps; ++step) {
+#pragma omp parallel
+        {
+            int t = 0;
+#ifdef _OPENMP
+            t = omp_get_thread_num();
+#endif
+            priv[t].assign((size_t)L * 3 + 1, 0.0);
+            double* h = priv[t].data();
+            double vsum = 0.0;
+#pragma omp for schedule(static)
+            for (long long i = 0; i < n; ++i) {
+                const int l = leaf[i];
+                const float a = approx[i] + dl[l], y = target[i], w = weight ? weight[i] : 1.0f;
+                float d, hs, v;
+                if (loss == 0) { d = y - a; hs = 1.0f; v = d * d; }
+                else if (loss == 3) { const float e = std::exp(a); d = y - e; hs = e; v = e - y * a; }
+                else {
+                    const float p = 1.0f / (1.0f + std::exp(-a));
+                    d = y - p; hs = std::max(p * (1.0f - p), 1e-16f);
+                    v = backtrack ? (std::max(a, 0.0f) + std::log1p(std::exp(-std::fabs(a))) - y * a) : 0.0f;
+                }
+                h[(size_t)l * 3] += (double)(d * w);
+                h[(size_t)l * 3 + 1] += (double)(hs * w);
+                h[(size_t)l * 3 + 2] += (double)w;
+                vsum += (double)(v * w);
+            }
+            h[(size_t)L * 3] = vsum;
+        }
+        double v = 0.0;
+        for (int t = 0; t < nthreads; ++t) if (!priv[t].empty()) v += priv[t][(size_t)L * 3];
+        if (backtrack && step > 0 && !(v <= f_base - (backtrack == 2 ? 1e-5 * cur_step * dirgrad : 0.0))) {
+            cur_step *= 0.5;
+            for (int l = 0; l < L; ++l) dl[l] = base[l] + (float)cur_step * dir[l];
+            continue;
+        }
+        for (int l = 0; l < L; ++l) {
+            double a = 0.0, b = 0.0, c = 0.0;
+            for (int t = 0; t < nthreads; ++t)
+                if (!priv[t].empty()) { a += priv[t][(size_t)l * 3]; b += priv[t][(size_t)l * 3 + 1]; c += priv[t][(size_t)l * 3 + 2]; }
+            sd[l] = a; sh[l] = b; sw[l] = c;
+        }
+        if (!have_w) { for (int l = 0; l < L; ++l) leaf_w[l] = sw[l]; have_w = true; }
+        dirgrad = 0.0;
+        for (int l = 0; l < L; ++l) {
+            const double den = (newton ? sh[l] : sw[l]) + l2;
+            // the general learner keeps its running leaf values in float32: so does this
+            const float stepv = den > 0.0 ? (float)(sd[l] / den) : 0.0f;
+            base[l] = dl[l];
+            dir[l] = stepv;
+            dirgrad += sd[l] * (double)stepv;
+            dl[l] += stepv;
+        }
+        f_base = v;
+        cur_step = 1.0;
+    }
+    for (int l = 0; l < L; ++l) delta[l] = (double)dl[l];
+    return 0;
+}
+
 // ------------------------------------------------------------------------------------------------------
 // Batch apply of an oblivious ensemble to raw float rows (CPU evaluator).  Blocks of 128 rows are quantised
 // for the used features, then every tree is walked for the block (libs/model/cpu/evaluator_impl.cpp:13-260

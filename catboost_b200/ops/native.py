@@ -126,6 +126,7 @@ def cpu_lib() -> ctypes.CDLL:
         lib = ctypes.CDLL(str(CPU_LIB))
         lib.cbc_select_borders.restype = c_int
         lib.cbc_num_threads.restype = c_int
+        lib.cbc_leaf_newton.restype = c_int
         _cpu = lib
     return _cpu
 

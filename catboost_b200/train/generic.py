@@ -388,8 +388,14 @@ class GenericLearner:
                 h_small = self._hist(stats, table, half)
                 h_big = h_prev - h_small
                 h = torch.where(is_small.view(L, 1, 1), h_small[parent], h_big[parent])
-            num, den, cnt, sides_ = sc.candidate_terms(h, K, cstat)
-            score = sc.finish(num.sum(0), None if den is None else den.sum(0))          # [F, B]
+            native_scores = (USE_NATIVE_CPU_SCORES and self.dev.type == "cpu" and cstat is None and self.monotone is None
+                             and sc.fn in ("Cosine", "NewtonCosine", "L2", "NewtonL2") and h.dtype == torch.float32)
+            if native_scores:
+                # host: one native pass per feature over the level's histograms (ops/cpu/cb_cpu.cpp cbc_symmetric_scores)
+                score, cnt, sides_ = self._native_symmetric_scores(h, K), None, None
+            else:
+                num, den, cnt, sides_ = sc.candidate_terms(h, K, cstat)
+                score = sc.finish(num.sum(0), None if den is None else den.sum(0))          # [F, B]
             if noise_std > 0:
                 score = score + self._score_noise(score.shape) * noise_std
             score = score * fw.unsqueeze(1)
@@ -412,9 +418,35 @@ class GenericLearner:
             splits[level] = (f, b, 0, 1 if onehot else 0)
             ops.update_leaf(self.store, self.leaf, f, b, onehot, level)
             # which child of every leaf is the lighter one (by the weight column) decides what the next level accumulates
-            small_right = sides_[1][:, K, f, b] < sides_[0][:, K, f, b]
+            if sides_ is not None:
+                small_right = sides_[1][:, K, f, b] < sides_[0][:, K, f, b]
+            else:
+                o0, nbf = int(self.store.feat_off_host[f]), int(self.store.feat_nb_host[f])
+                wrow = h[:, K, o0:o0 + nbf]
+                wl = (wrow.sum(1) - wrow[:, b]) if onehot else wrow[:, :b + 1].sum(1)
+                small_right = (wrow.sum(1) - wl) < wl
             h_prev = h
         return TreeResult("oblivious", splits=splits, n_leaves=1 << depth, leaf=self.leaf)
+
+    def _native_symmetric_scores(self, h, K):
+        import ctypes
+        from ..ops import native
+        st = self.store
+        L, S, TB = int(h.shape[0]), int(h.shape[1]), int(h.shape[2])
+        hc = h.contiguous()
+        out = torch.empty((st.F, self.scorer.B), dtype=torch.float32)
+        cache = self.__dict__.get("_native_score_args")
+        if cache is None:
+            cache = (np.ascontiguousarray(st.feat_off_host[:-1], dtype=np.int32), np.ascontiguousarray(st.feat_nb_host, dtype=np.int32),
+                     np.ascontiguousarray(self._onehot_host, dtype=np.uint8))
+            self.__dict__["_native_score_args"] = cache
+        off, nb, oh = cache
+        P = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+        native.cpu_lib().cbc_symmetric_scores(
+            ctypes.c_void_p(hc.data_ptr()), L, S, int(K), TB, int(st.F), P(off), P(nb), P(oh),
+            0 if self.scorer.fn in ("Cosine", "NewtonCosine") else 1, ctypes.c_double(self.scorer.l2), int(self.scorer.B),
+            ctypes.c_void_p(out.data_ptr()))
+        return out
 
     def _per_leaf_best(self, h, K, noise_std, fmask, node_ids=None):
         if self.has_penalties:
@@ -589,6 +621,8 @@ def enforce_monotone_leaves(vals: np.ndarray, wts: np.ndarray, splits: np.ndarra
 
 _LANGEVIN_DRAWS = [0]
 USE_LEAF_KERNEL = True        # False: the tensor formulation below also on the GPU (the oracle of the kernel path)
+USE_NATIVE_CPU_LEAVES = True  # False: the tensor formulation also on the CPU (the oracle of cbc_leaf_newton)
+USE_NATIVE_CPU_SCORES = True  # False: SplitScorer's tensor code scores symmetric levels on the CPU too (the oracle)
 
 
 def estimate_leaves(objective, approx, target, weight, leaf, n_leaves, n, opts, ctx=None, obj_ctx=None,
@@ -612,6 +646,30 @@ def estimate_leaves(objective, approx, target, weight, leaf, n_leaves, n, opts, 
                               str(getattr(opts, "leaf_estimation_backtracking", None) or "No"))
         if out is not None:
             return out[0].double().unsqueeze(1).cpu().numpy(), out[1].cpu().numpy()
+    if (USE_NATIVE_CPU_LEAVES and not approx.is_cuda and dims == 1 and method in ("Newton", "Gradient")
+            and objective.native_id in (0, 1, 2, 3) and type(objective).__name__ in ("RMSE", "Logloss", "CrossEntropy", "Poisson")
+            and not (ctx is not None and ctx.is_distributed) and not getattr(opts, "langevin", False)
+            and not getattr(objective, "zero_mean_leaves", False) and leaf.dtype == torch.int16
+            and str(getattr(opts, "leaf_estimation_backtracking", None) or "No") in ("No", "AnyImprovement", "Armijo")
+            and approx.dtype == torch.float32 and target.dtype == torch.float32 and target.dim() == 1):
+        # host losses with a closed formula: all steps in one native call (ops/cpu/cb_cpu.cpp cbc_leaf_newton)
+        import ctypes
+        from ..ops import native
+        a0 = approx[0, :n].contiguous()
+        tg = target[:n].contiguous()
+        wt = None if weight is None else weight[:n].contiguous().float()
+        lf = leaf[:n].contiguous()
+        dl = np.zeros(n_leaves, dtype=np.float64)
+        lw = np.zeros(n_leaves, dtype=np.float64)
+        P = lambda t: ctypes.c_void_p(t.data_ptr())
+        rc = native.cpu_lib().cbc_leaf_newton(
+            ctypes.c_int(int(objective.native_id)), P(a0), P(tg), None if wt is None else P(wt), P(lf), ctypes.c_longlong(n),
+            ctypes.c_int(int(n_leaves)), ctypes.c_int(max(1, iters)), ctypes.c_int(1 if method == "Newton" else 0),
+            ctypes.c_double(l2),
+            ctypes.c_int({"No": 0, "AnyImprovement": 1, "Armijo": 2}[str(getattr(opts, "leaf_estimation_backtracking", None) or "No")]),
+            dl.ctypes.data_as(ctypes.c_void_p), lw.ctypes.data_as(ctypes.c_void_p))
+        if rc == 0:
+            return (dl * lr).reshape(-1, 1), lw
     delta = torch.zeros((n_leaves, dims), dtype=torch.float32, device=dev)
     wcol = torch.ones(n, dtype=torch.float32, device=dev) if weight is None else weight[:n]
     leaf_w = None

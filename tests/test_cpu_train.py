@@ -212,3 +212,55 @@ def test_posterior_sampling_group_sampling_and_per_feature_ctr():
     with pytest.raises(cb.CatBoostError):
         cb.CatBoostClassifier(iterations=2, per_feature_ctr=["0:Counter"], verbose=False, allow_writing_files=False).fit(
             Xo, yc, cat_features=[1, 2])
+
+
+def test_native_cpu_leaf_estimation_matches_tensor_path():
+    """cbc_leaf_newton (all steps of a tree's leaf estimation in one native call, with step-length control) against the
+    tensor formulation of the general learner."""
+    import catboost_b200 as cb
+    from catboost_b200.train import generic
+    rng = np.random.default_rng(0)
+    n, F = 20000, 10
+    X = rng.standard_normal((n, F), dtype=np.float32)
+    y = (X[:, 0] + X[:, 1] * X[:, 2] + 0.5 * rng.standard_normal(n) > 0).astype(np.float32)
+    w = rng.random(n).astype(np.float32)
+    out = {}
+    try:
+        for native in (True, False):
+            generic.USE_NATIVE_CPU_LEAVES = native
+            for loss, target, bt in (("Logloss", y, "AnyImprovement"), ("Logloss", y, "Armijo"), ("Logloss", y, "No"),
+                                     ("RMSE", X[:, 0] + 0.1 * y, "AnyImprovement")):
+                kw = dict(loss_function=loss, iterations=15, depth=5, learning_rate=0.5, verbose=False, allow_writing_files=False,
+                          bootstrap_type="No", random_strength=0, leaf_estimation_backtracking=bt, leaf_estimation_iterations=8)
+                m = (cb.CatBoostClassifier if loss == "Logloss" else cb.CatBoostRegressor)(**kw).fit(X, target, sample_weight=w)
+                out[(native, loss, bt)] = m.predict(X[:3000], prediction_type="RawFormulaVal")
+    finally:
+        generic.USE_NATIVE_CPU_LEAVES = True
+    for key in [k[1:] for k in out if k[0]]:
+        assert np.max(np.abs(out[(True,) + key] - out[(False,) + key])) < 2e-5, key
+
+
+def test_native_cpu_level_scores_match_tensor_scorer():
+    """cbc_symmetric_scores against SplitScorer's tensor code: same trees for Cosine and L2, float and one-hot splits."""
+    import catboost_b200 as cb
+    from catboost_b200.train import generic
+    rng = np.random.default_rng(1)
+    n = 15000
+    X = rng.standard_normal((n, 8), dtype=np.float32)
+    y = (X[:, 0] + X[:, 1] * X[:, 2] + 0.5 * rng.standard_normal(n) > 0).astype(np.float32)
+    Xc = np.c_[X[:, :5], rng.integers(0, 4, n)].astype(object)
+    out = {}
+    try:
+        for native in (True, False):
+            generic.USE_NATIVE_CPU_SCORES = native
+            for sf in ("Cosine", "L2", "NewtonL2"):
+                m = cb.CatBoostClassifier(iterations=12, depth=5, verbose=False, allow_writing_files=False, bootstrap_type="No",
+                                          random_strength=0, score_function=sf).fit(X, y)
+                out[(native, sf)] = m.predict(X[:2000], prediction_type="RawFormulaVal")
+            m = cb.CatBoostClassifier(iterations=12, depth=4, verbose=False, allow_writing_files=False, bootstrap_type="No",
+                                      random_strength=0, one_hot_max_size=8).fit(Xc, y, cat_features=[5])
+            out[(native, "onehot")] = m.predict(Xc[:2000], prediction_type="RawFormulaVal")
+    finally:
+        generic.USE_NATIVE_CPU_SCORES = True
+    for key in [k[1] for k in out if k[0]]:
+        assert np.max(np.abs(out[(True, key)] - out[(False, key)])) < 1e-6, key
