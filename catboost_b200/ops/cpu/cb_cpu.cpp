@@ -254,17 +254,31 @@ CBC_API void cbc_hist(const uint32_t* bins, long long npad, long long n, int F, 
 #endif
         std::vector<double>& h = priv[t];
         h.assign(total, 0.0);
-#pragma omp for schedule(static)
-        for (long long i = 0; i < n; ++i) {
-            const int slot = slot_of_leaf[leaf[i]];
-            if (slot < 0) continue;
-            for (int g = 0; g < G; ++g) {
-                const uint32_t w = bins[(size_t)g * npad + i];
-                for (int j = 0; j < 4; ++j) {
-                    const int f = 4 * g + j;
-                    if (f >= F) break;
-                    const int col = feat_off[f] + int((w >> (8 * j)) & 255u);
-                    for (int s = 0; s < S; ++s) h[((size_t)slot * S + s) * TB + col] += stats[(size_t)s * npad + i];
+        // a thread's documents are walked once per feature group: the cells one pass touches (slots x statistics x the
+        // bins of 4 features) stay in the core's cache, where walking all groups per document spread the updates over the
+        // whole private histogram
+        long long i0 = 0, i1 = n;
+#ifdef _OPENMP
+        {
+            const int nt = omp_get_num_threads();
+            i0 = n * t / nt;
+            i1 = n * (t + 1) / nt;
+        }
+#endif
+        for (int g = 0; g < G; ++g) {
+            const uint32_t* row = bins + (size_t)g * npad;
+            const int fcount = std::min(4, F - 4 * g);
+            int off4[4] = {0, 0, 0, 0};
+            for (int j = 0; j < fcount; ++j) off4[j] = feat_off[4 * g + j];
+            for (long long i = i0; i < i1; ++i) {
+                const int slot = slot_of_leaf[leaf[i]];
+                if (slot < 0) continue;
+                const uint32_t w = row[i];
+                double* hs = h.data() + (size_t)slot * S * TB;
+                for (int s = 0; s < S; ++s) {
+                    const double v = (double)stats[(size_t)s * npad + i];
+                    double* hh = hs + (size_t)s * TB;
+                    for (int j = 0; j < fcount; ++j) hh[off4[j] + int((w >> (8 * j)) & 255u)] += v;
                 }
             }
         }

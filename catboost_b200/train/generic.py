@@ -239,7 +239,8 @@ class GenericLearner:
             t = float(o.bagging_temperature)
             if t == 0:
                 return None
-            return (-torch.log(self._rand(n).clamp_min(1e-20))) ** t
+            e = -torch.log(self._rand(n).clamp_min(1e-20))
+            return e if t == 1.0 else e ** t
         if bt == "Bernoulli":
             return (self._rand(n) < float(o.subsample)).float()
         if bt == "Poisson":
