@@ -14,10 +14,12 @@ from .compat import (EFeaturesSelectionAlgorithm, EFeaturesSelectionGrouping, ES
                      MultiRegressionCustomMetric, MultiRegressionCustomObjective, MultiTargetCustomMetric,
                      MultiTargetCustomObjective)
 
+from .widget import MetricVisualizer  # noqa: E402,F401
+
 CatboostError = CatBoostError          # spelling kept by the reference for old code
 __version__ = "0.1.0"
 __all__ = ["CatBoost", "CatBoostClassifier", "CatBoostRegressor", "CatBoostRanker", "Pool", "CatBoostError", "train",
            "cv", "sum_models", "to_classifier", "to_regressor", "to_ranker", "EFstrType", "EShapCalcType",
            "EFeaturesSelectionAlgorithm", "EFeaturesSelectionGrouping", "FeaturesData", "CatboostError",
            "sample_gaussian_process", "eval_features", "MultiRegressionCustomMetric", "MultiRegressionCustomObjective",
-           "MultiTargetCustomMetric", "MultiTargetCustomObjective"]
+           "MultiTargetCustomMetric", "MultiTargetCustomObjective", "MetricVisualizer"]

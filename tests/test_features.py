@@ -1540,3 +1540,23 @@ def test_functional_train_and_single_object_predict():
     assert np.ndim(one) == 0 and one == r.predict(X[:1])[0] == r.predict([float(v) for v in X[0]])
     c = cb.CatBoostClassifier(iterations=5, verbose=0, allow_writing_files=False).fit(X, y)
     assert c.predict_proba(X[0]).shape == (2,) and c.predict(X[0]) in (0, 1)
+
+
+def test_metric_visualizer_reads_training_logs(tmp_path):
+    from catboost_b200.widget import MetricVisualizer, MetricsPlotter
+    rng = np.random.default_rng(0)
+    X = rng.normal(size=(400, 4)).astype(np.float32)
+    y = (X[:, 0] > 0).astype(int)
+    cb.CatBoostClassifier(iterations=12, verbose=0, train_dir=str(tmp_path / "run")).fit(X[:300], y[:300], eval_set=(X[300:], y[300:]))
+    viz = MetricVisualizer(str(tmp_path), subdirs=True)
+    curves = viz.curves()
+    (run, parts), = curves.items()
+    assert set(parts) == {"learn", "test"} and len(parts["learn"]["Logloss"]) == 12 and len(parts["test"]["Logloss"]) == 12
+    assert parts["learn"]["Logloss"][-1] < parts["learn"]["Logloss"][0]
+    assert "learn Logloss" in viz.to_text()
+    p = MetricsPlotter(["loss"])
+    for i in range(5):
+        p.log(i, True, {"loss": 1.0 / (i + 1)})
+    assert p.curves()["run"]["learn"]["loss"] == [1.0, 0.5, 1 / 3, 0.25, 0.2]
+    with pytest.raises(cb.CatBoostError):
+        p.log(0, True, {"other": 1.0})
