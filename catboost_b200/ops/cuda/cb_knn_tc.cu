@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(CB_KNN_THREADS, 1) cb_knn_tc_kernel(const __gr
                 const int col = (t0 + t + 1) * CB_KNN_TN + half * 128 + u * 32 + lane;
                 e2v[u] = (t + 1 < ntiles && col < a.ne) ? __ldg(a.e2 + col) : 3.0e38f;
             }
-            // the verdict of the wait is taken by the whole warp: the votes further down need all 32 lanes
+            // the whole warp decides together whether the wait succeeded: the votes further down need all 32 lanes
             const bool arrived = !(*(volatile int*)&s_abort) && cbk_wait(bar_tfull + 8 * buf, tph);
             if (!__all_sync(0xffffffffu, arrived)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
