@@ -45,7 +45,14 @@ class TrainResult:
 
 # ---------------------------------------------------------------------------------------------------------
 def _unique_labels(lab: np.ndarray) -> np.ndarray:
-    return np.unique(np.asarray(lab))
+    """Distinct label values.  Numeric labels with at most two values (the usual binary target) are recognised by three
+    passes instead of a sort (np.unique takes 26 ms on 10.5M floats)."""
+    lab = np.asarray(lab)
+    if lab.dtype.kind in "fiub" and lab.size:
+        mn, mx = lab.min(), lab.max()
+        if mn == mn and mx == mx and bool(((lab == mn) | (lab == mx)).all()):
+            return np.array([mn] if mn == mx else [mn, mx], dtype=lab.dtype)
+    return np.unique(lab)
 
 
 class LabelCodec:

@@ -108,7 +108,11 @@ class Logloss(_Pointwise):
         return y - p, (p * (1 - p)).clamp_min(1e-16), v
 
     def start_constant(self, target, weight):
-        p = float(np.average(target.astype(np.float64), weights=weight))
+        t = np.asarray(target)
+        if weight is None:
+            p = float(t.sum(dtype=np.float64)) / max(t.size, 1)             # no float64 copy of the target
+        else:
+            p = float(np.dot(t.astype(np.float64, copy=False), np.asarray(weight, dtype=np.float64)) / np.sum(weight, dtype=np.float64))
         p = min(max(p, 1e-9), 1 - 1e-9)
         return np.array([math.log(p / (1 - p))])
 
