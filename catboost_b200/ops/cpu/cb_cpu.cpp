@@ -162,16 +162,22 @@ static void cbc_radix_sort_floats(std::vector<float>& v, std::vector<uint32_t>& 
 // re-read the whole matrix once per column: 25 GB of traffic for 200K x 2000).
 CBC_API void cbc_select_borders_matrix(const float* X, long long n, int F, long long ld, int max_borders, int type,
                                        float* out_borders, int* out_counts, unsigned char* has_nan) {
-    const int CB = 16;
+    const int CBMAX = 16;
+    int nthr = 1;
+#ifdef _OPENMP
+    nthr = omp_get_max_threads();
+#endif
+    // narrow matrices: fewer columns per work item so that every thread has one (28 columns in blocks of 16 kept 2 busy)
+    const int CB = std::max(1, std::min(CBMAX, F / (2 * std::max(nthr, 1))));
     const int nblocks = (F + CB - 1) / CB;
 #pragma omp parallel
     {
-        std::vector<float> col[CB];
+        std::vector<float> col[CBMAX];
         std::vector<uint32_t> ka, kb;
 #pragma omp for schedule(dynamic, 1)
         for (int blk = 0; blk < nblocks; ++blk) {
             const int f0 = blk * CB, w = std::min(CB, F - f0);
-            bool nan[CB] = {false};
+            bool nan[CBMAX] = {false};
             for (int j = 0; j < w; ++j) { col[j].clear(); col[j].reserve((size_t)n); }
             for (long long i = 0; i < n; ++i) {
                 const float* row = X + i * ld + f0;
