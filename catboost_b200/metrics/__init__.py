@@ -33,6 +33,16 @@ class Metric:
     def __init__(self, desc: str):
         self.desc = desc
         self.name, self.params = parse_loss(desc)
+        if self.name == "Combination":
+            # a combination of losses is reported by the metric of its first loss with a non-zero weight
+            # (catboost/private/libs/options/loss_description.cpp GetMetricFromCombination)
+            first = next((str(self.params[f"loss{i}"]) for i in range(len(self.params) // 2)
+                          if f"loss{i}" in self.params and float(self.params.get(f"weight{i}", 0.0)) != 0.0), None)
+            if first is None:
+                raise ValueError("Combination loss must have one or more non-zero weights")
+            inner = Metric(first)
+            self.params, self.fn, self.is_max_optimal, self.needs = inner.params, inner.fn, inner.is_max_optimal, inner.needs
+            return
         if self.name not in _METRICS:
             raise ValueError(f"unknown metric {self.name!r}")
         self.fn, self.is_max_optimal, self.needs = _METRICS[self.name]

@@ -73,10 +73,12 @@ POINTWISE_LOSSES = {"RMSE", "Logloss", "CrossEntropy", "Poisson", "MAE", "Quanti
 MULTI_LOSSES = {"MultiClass", "MultiClassOneVsAll", "MultiLogloss", "MultiCrossEntropy", "MultiRMSE", "RMSEWithUncertainty",
                 "MultiQuantile"}
 SURVIVAL_LOSSES = {"Cox", "SurvivalAft"}
+COMBINED_LOSSES = {"Combination"}
 RANKING_LOSSES = {"YetiRank", "YetiRankPairwise", "PairLogit", "PairLogitPairwise", "QueryRMSE", "QuerySoftMax",
                   "QueryCrossEntropy", "LambdaMart", "StochasticRank", "StochasticFilter", "GroupQuantile"}
 PAIRWISE_HIST_LOSSES = {"YetiRankPairwise", "PairLogitPairwise", "QueryCrossEntropy"}
-ALL_LOSSES = POINTWISE_LOSSES | MULTI_LOSSES | RANKING_LOSSES | SURVIVAL_LOSSES | {"PythonUserDefinedPerObject"}
+ALL_LOSSES = (POINTWISE_LOSSES | MULTI_LOSSES | RANKING_LOSSES | SURVIVAL_LOSSES | COMBINED_LOSSES
+              | {"PythonUserDefinedPerObject"})
 
 # (newton iterations, gradient iterations, method, l2)  -- catboost_options.cpp:31-271
 _LEAF_DEFAULTS = {

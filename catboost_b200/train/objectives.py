@@ -587,6 +587,62 @@ class MultiQuantile(Objective):
         return np.array([_weighted_quantile(target, weight, a) for a in self.alphas])
 
 
+class Combination(Objective):
+    """Weighted sum of one-dimensional losses, ``Combination:loss0=Logloss;weight0=1;loss1=QueryRMSE;weight1=0.5``:
+    derivatives and second derivatives are the weighted sums of the parts'
+    (catboost/cuda/targets/combination_targets_impl.h, catboost/private/libs/options/loss_description.h:176-193);
+    parts with weight 0 are left out, the others need a positive weight."""
+    name = "Combination"
+    is_pointwise = False
+
+    def __init__(self, params=None):
+        super().__init__(params)
+        count = len(self.params) // 2
+        if count < 2:
+            raise CatBoostError("Combination loss must have two or more parameters")
+        self.parts = []
+        for i in range(count):
+            lk, wk = f"loss{i}", f"weight{i}"
+            if lk not in self.params or wk not in self.params:
+                raise CatBoostError(f"Mandatory parameter {lk} or {wk} is missing")
+            try:
+                w = float(self.params[wk])
+            except (TypeError, ValueError):
+                raise CatBoostError(f"Value of {wk} must be floating point number, not {self.params[wk]}")
+            if w == 0.0:
+                continue
+            if w < 0.0:
+                raise CatBoostError(f"Value of {wk} must be positive, not {w}")
+            from ..params import parse_loss
+            nm, sub = parse_loss(str(self.params[lk]))
+            if nm == "Combination":
+                raise CatBoostError("Combination losses do not nest")
+            part = make_objective(nm, sub)
+            if part.dims != 1:
+                raise CatBoostError(f"Combination takes one-dimensional losses; {nm} is not one")
+            self.parts.append((part, w))
+        if not self.parts:
+            raise CatBoostError("Combination loss must have one or more non-zero weights")
+        self.needs_groups = any(p.needs_groups for p, _ in self.parts)
+        self.needs_pairs = any(p.needs_pairs for p, _ in self.parts)
+        self.is_classification = self.parts[0][0].is_classification
+        self.stochastic = any(p.stochastic for p, _ in self.parts)
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        der = hess = None
+        for part, w in self.parts:
+            d, h = part.der_hess(approx, target, weight, ctx)
+            der = d * w if der is None else der + d * w
+            hess = h * w if hess is None else hess + h * w
+        return der, hess
+
+    def value(self, approx, target, weight, ctx=None):
+        return float(sum(w * part.value(approx, target, weight, ctx) for part, w in self.parts))
+
+    def start_constant(self, target, weight):
+        return self.parts[0][0].start_constant(target, weight) if len(self.parts) == 1 else np.zeros(1)
+
+
 class UserObjective(Objective):
     """Python custom objective with ``calc_ders_range(approxes, targets, weights)`` returning (der, der2) pairs in
     the reference's sign convention (der2 <= 0), see catboost/python-package/catboost/_catboost.pyx trampolines."""
@@ -642,6 +698,8 @@ def make_objective(loss, params: dict, n_classes: Optional[int] = None, n_target
         return MultiCrossEntropy(params, n_targets)
     if loss == "RMSEWithUncertainty":
         return RMSEWithUncertainty(params)
+    if loss == "Combination":
+        return Combination(params)
     if loss == "Cox":
         return Cox(params)
     if loss == "SurvivalAft":

@@ -1560,3 +1560,27 @@ def test_metric_visualizer_reads_training_logs(tmp_path):
     assert p.curves()["run"]["learn"]["loss"] == [1.0, 0.5, 1 / 3, 0.25, 0.2]
     with pytest.raises(cb.CatBoostError):
         p.log(0, True, {"other": 1.0})
+
+
+def test_combination_loss():
+    rng = np.random.default_rng(0)
+    n = 2000
+    X = rng.normal(size=(n, 5)).astype(np.float32)
+    y = (X[:, 0] + 0.3 * rng.normal(size=n) > 0).astype(np.float32)
+    pool = cb.Pool(X, y, group_id=np.repeat(np.arange(n // 10), 10))
+    kw = dict(iterations=20, depth=4, learning_rate=0.2, verbose=0, allow_writing_files=False, bootstrap_type="No",
+              random_strength=0, leaf_estimation_iterations=1, boost_from_average=False)
+    only = "Combination:loss0=Logloss;weight0=1.0;loss1=QueryRMSE;weight1=0.0"
+    a = cb.CatBoost(dict(loss_function=only, **kw)).fit(pool)
+    b = cb.CatBoost(dict(loss_function="Logloss", **kw)).fit(pool)
+    assert np.max(np.abs(a.predict(X) - b.predict(X))) < 1e-5            # a part with weight 0 is left out
+    # reported by the metric of the first weighted part
+    assert np.allclose(a.evals_result_["learn"][only], b.evals_result_["learn"]["Logloss"], atol=1e-6)
+    mixed = "Combination:loss0=Logloss;weight0=1.0;loss1=QueryRMSE;weight1=0.5"
+    c = cb.CatBoost(dict(loss_function=mixed, **kw)).fit(pool)
+    curve = c.evals_result_["learn"][mixed]
+    assert curve[-1] < curve[0] and np.max(np.abs(c.predict(X) - b.predict(X))) > 1e-3
+    for bad in ("Combination:loss0=Logloss;weight0=-1;loss1=RMSE;weight1=1", "Combination:loss0=Logloss;weight0=1",
+                "Combination:loss0=MultiClass;weight0=1;loss1=RMSE;weight1=1"):
+        with pytest.raises(cb.CatBoostError):
+            cb.CatBoost(dict(loss_function=bad, **kw)).fit(pool)
