@@ -71,14 +71,14 @@ NOT_IMPLEMENTED = {"counter_calc_method", "ctr_leaf_count_limit", "store_all_sim
 POINTWISE_LOSSES = {"RMSE", "Logloss", "CrossEntropy", "Poisson", "MAE", "Quantile", "LogLinQuantile", "MAPE", "Huber",
                     "Lq", "Expectile", "Tweedie", "LogCosh", "Focal"}
 MULTI_LOSSES = {"MultiClass", "MultiClassOneVsAll", "MultiLogloss", "MultiCrossEntropy", "MultiRMSE", "RMSEWithUncertainty",
-                "MultiQuantile"}
+                "MultiQuantile", "PythonUserDefinedMultiTarget"}
 SURVIVAL_LOSSES = {"Cox", "SurvivalAft"}
 COMBINED_LOSSES = {"Combination"}
 RANKING_LOSSES = {"YetiRank", "YetiRankPairwise", "PairLogit", "PairLogitPairwise", "QueryRMSE", "QuerySoftMax",
                   "QueryCrossEntropy", "LambdaMart", "StochasticRank", "StochasticFilter", "GroupQuantile"}
 PAIRWISE_HIST_LOSSES = {"YetiRankPairwise", "PairLogitPairwise", "QueryCrossEntropy"}
 ALL_LOSSES = (POINTWISE_LOSSES | MULTI_LOSSES | RANKING_LOSSES | SURVIVAL_LOSSES | COMBINED_LOSSES
-              | {"PythonUserDefinedPerObject"})
+              | {"PythonUserDefinedPerObject", "PythonUserDefinedMultiTarget"})
 
 # (newton iterations, gradient iterations, method, l2)  -- catboost_options.cpp:31-271
 _LEAF_DEFAULTS = {
@@ -93,7 +93,8 @@ _LEAF_DEFAULTS = {
     "YetiRankPairwise": (1, 1, "Simple", 0.0), "QueryCrossEntropy": (10, 1, "Newton", 1.0),
     "LambdaMart": (1, 1, "Newton", 0.0), "StochasticRank": (1, 1, "Gradient", 3.0),
     "StochasticFilter": (1, 100, "Gradient", 3.0), "Tweedie": (1, 1, "Newton", 3.0), "Lq": (1, 1, "Newton", 3.0),
-    "PythonUserDefinedPerObject": (1, 1, "Gradient", 3.0), "MultiQuantile": (1, 1, "Gradient", 3.0),
+    "PythonUserDefinedPerObject": (1, 1, "Gradient", 3.0), "PythonUserDefinedMultiTarget": (1, 1, "Newton", 3.0),
+    "MultiQuantile": (1, 1, "Gradient", 3.0),
     "GroupQuantile": (1, 1, "Gradient", 3.0), "Focal": (1, 1, "Newton", 3.0), "Cox": (1, 1, "Newton", 3.0),
     "SurvivalAft": (1, 1, "Gradient", 3.0),
 }
@@ -366,4 +367,4 @@ def default_eval_metric(loss: str) -> str:
     name, _ = parse_loss(loss)
     return {"YetiRank": "PFound", "YetiRankPairwise": "PFound", "PairLogitPairwise": "PairLogit",
             "LambdaMart": "NDCG", "StochasticRank": "NDCG", "StochasticFilter": "FilteredDCG",
-            "PythonUserDefinedPerObject": "RMSE"}.get(name, loss)
+            "PythonUserDefinedPerObject": "RMSE", "PythonUserDefinedMultiTarget": "MultiRMSE"}.get(name, loss)

@@ -268,7 +268,7 @@ def _metric_list(o: Options):
         if extra is None:
             continue
         descs += [extra] if isinstance(extra, str) else list(extra)
-    if isinstance(o.loss_function, str) and o.loss_function not in descs:
+    if isinstance(o.loss_function, str) and o.loss_function not in descs and not o.loss_function.startswith("PythonUserDefined"):
         descs.append(o.loss_function)
     out, seen = [], set()
     from ..metrics import BuiltinMetric
@@ -315,7 +315,8 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
     user_obj = params.get("loss_function") if params and not isinstance(params.get("loss_function"), (str, type(None))) else None
     p = dict(params or {})
     if user_obj is not None:
-        p["loss_function"] = "PythonUserDefinedPerObject"
+        # objects with calc_ders_multi drive a multi-dimensional model (one dimension per target column or per class)
+        p["loss_function"] = "PythonUserDefinedMultiTarget" if hasattr(user_obj, "calc_ders_multi") else "PythonUserDefinedPerObject"
     n_rows = train_pool.num_row()
     if ctx.is_distributed:
         n_rows = int(sum(ctx.all_gather_object(n_rows)))
@@ -332,6 +333,15 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
     # ---- targets ---------------------------------------------------------------------------------------
     codec = LabelCodec(o, train_pool.label, ctx)
     multi_target = o.loss_name in ("MultiRMSE", "MultiLogloss", "MultiCrossEntropy", "SurvivalAft")
+    user_dims = None
+    if o.loss_name == "PythonUserDefinedMultiTarget":
+        lab2 = np.asarray(train_pool.label)
+        multi_target = lab2.ndim == 2 and lab2.shape[1] > 1
+        if not multi_target:
+            # class labels 0 .. K-1: one dimension per class
+            user_dims = int(o.classes_count) if o.classes_count else int(np.asarray(lab2, dtype=np.float64).max()) + 1
+            if o.eval_metric == "MultiRMSE":
+                o.eval_metric = "MultiClass"
     if multi_target:
         y_train = np.asarray(train_pool.label, dtype=np.float32).reshape(train_pool.num_row(), -1)
         n_targets = y_train.shape[1]
@@ -339,7 +349,7 @@ def train_model(params: dict, train_pool: Pool, eval_pools: Optional[List[Pool]]
         y_train = codec.encode(train_pool.label)
         n_targets = 1
     objective = make_objective(user_obj if user_obj is not None else o.loss_name, o.loss_params,
-                               n_classes=codec.n_classes, n_targets=n_targets)
+                               n_classes=codec.n_classes if user_dims is None else user_dims, n_targets=n_targets)
     dims = objective.dims
     w_train = train_pool.weight
     cw = class_weight_vector(o, codec, y_train) if objective.is_classification and not multi_target else None

@@ -667,6 +667,37 @@ class UserObjective(Objective):
         return float("nan")
 
 
+class UserMultiObjective(Objective):
+    """Python custom objective with ``calc_ders_multi(approxes, target, weight)`` per object, returning the first
+    derivatives [dims] and the matrix of second derivatives [dims][dims] in the reference's sign convention
+    (catboost/python-package/catboost/_catboost.pyx trampolines); the diagonal of the matrix is used.  The target of an
+    object is its row of target columns (multi-target labels) or its class index."""
+    name = "PythonUserDefinedMultiTarget"
+    is_pointwise = False
+
+    def __init__(self, obj, dims: int, target_is_vector: bool):
+        super().__init__({})
+        self.obj, self.dims, self.target_is_vector = obj, int(dims), bool(target_is_vector)
+
+    def der_hess(self, approx, target, weight, ctx=None):
+        A = approx.detach().t().cpu().numpy().astype(np.float64)                     # [n, dims]
+        T = target.detach().cpu().numpy().astype(np.float64)
+        T = T.T if self.target_is_vector else T
+        w = None if weight is None else weight.detach().cpu().numpy().astype(np.float64)
+        n = A.shape[0]
+        d = np.empty((n, self.dims), dtype=np.float32)
+        h = np.empty((n, self.dims), dtype=np.float32)
+        for i in range(n):
+            di, hi = self.obj.calc_ders_multi(A[i], T[i], 1.0 if w is None else float(w[i]))
+            d[i] = np.asarray(di, dtype=np.float64)
+            h[i] = -np.diagonal(np.asarray(hi, dtype=np.float64).reshape(self.dims, self.dims))
+        dev = approx.device
+        return torch.from_numpy(d.T.copy()).to(dev), torch.from_numpy(h.T.copy()).to(dev).clamp_min(1e-16)
+
+    def value(self, approx, target, weight, ctx=None):
+        return float("nan")
+
+
 def _weighted_quantile(values, weight, alpha):
     v = np.asarray(values, dtype=np.float64)
     order = np.argsort(v, kind="stable")
@@ -683,6 +714,9 @@ _POINTWISE = {c.name: c for c in (RMSE, Logloss, CrossEntropy, Poisson, MAE, Qua
 
 def make_objective(loss, params: dict, n_classes: Optional[int] = None, n_targets: int = 1) -> Objective:
     if not isinstance(loss, str):
+        if hasattr(loss, "calc_ders_multi"):
+            vector = n_targets > 1
+            return UserMultiObjective(loss, n_targets if vector else int(n_classes or 2), vector)
         return UserObjective(loss)
     if loss in _POINTWISE:
         return _POINTWISE[loss](params)

@@ -1584,3 +1584,33 @@ def test_combination_loss():
                 "Combination:loss0=MultiClass;weight0=1;loss1=RMSE;weight1=1"):
         with pytest.raises(cb.CatBoostError):
             cb.CatBoost(dict(loss_function=bad, **kw)).fit(pool)
+
+
+def test_custom_multi_dimensional_objectives():
+    rng = np.random.default_rng(0)
+    n = 500
+    X = rng.normal(size=(n, 4)).astype(np.float32)
+    Y = np.stack([X[:, 0] * 2 + 0.1 * rng.normal(size=n), X[:, 1] - X[:, 2]], 1).astype(np.float32)
+
+    class SquaredError(cb.MultiTargetCustomObjective):
+        def calc_ders_multi(self, approx, target, weight):
+            return (np.asarray(target) - np.asarray(approx)) * weight, -np.eye(len(approx)) * weight
+
+    kw = dict(iterations=25, depth=3, learning_rate=0.3, verbose=0, allow_writing_files=False)
+    m = cb.CatBoostRegressor(loss_function=SquaredError(), eval_metric="MultiRMSE", **kw).fit(X, Y)
+    ref = cb.CatBoostRegressor(loss_function="MultiRMSE", boost_from_average=False, **kw).fit(X, Y)
+    assert m.predict(X).shape == (n, 2) and np.allclose(m.predict(X), ref.predict(X), atol=1e-5)
+
+    class Softmax:
+        def calc_ders_multi(self, approx, target, weight):
+            e = np.exp(approx - approx.max())
+            p = e / e.sum()
+            d = -p.copy()
+            d[int(target)] += 1
+            return d * weight, -(np.diag(p) - np.outer(p, p)) * weight
+
+    y = np.digitize(X[:, 0], [-0.5, 0.5])
+    mc = cb.CatBoostClassifier(loss_function=Softmax(), classes_count=3, **kw).fit(X, y)
+    raw = mc.predict(X, prediction_type="RawFormulaVal")
+    assert raw.shape == (n, 3) and (raw.argmax(1) == y).mean() > 0.95
+    assert list(mc.evals_result_["learn"]) == ["MultiClass"]
