@@ -191,6 +191,11 @@ class CatBoost:
         multi = m.loss_name in ("MultiClass", "MultiClassOneVsAll")
         if pt == "RawFormulaVal":
             return raw[:, 0] if raw.shape[1] == 1 else raw
+        if pt == "MultiProbability":
+            # per-label probabilities of a multi-label model (catboost/private/libs/options/enums.h EPredictionType)
+            if m.loss_name not in ("MultiLogloss", "MultiCrossEntropy"):
+                raise CatBoostError("prediction_type 'MultiProbability' needs a MultiLogloss / MultiCrossEntropy model")
+            return _sigmoid(raw)
         if pt in ("Probability", "LogProbability"):
             if binclass:
                 p1 = _sigmoid(raw[:, 0])
@@ -624,7 +629,8 @@ class CatBoost:
             m = make_metric("NDCG")
             return m.eval(raw, np.asarray(yy, dtype=np.float64), pool.weight, group_offsets=pool.group_offsets())
         yy = np.asarray(yy, dtype=np.float64)
-        p = raw[:, 0]
+        # R2 of the prediction on the scale of the target: models with a log link predict exp(raw)
+        p = np.exp(raw[:, 0]) if self._default_prediction_type() == "Exponent" else raw[:, 0]
         den = np.sum((yy - yy.mean()) ** 2)
         return float(1 - np.sum((yy - p) ** 2) / den) if den > 0 else 0.0
 
@@ -834,6 +840,16 @@ class CatBoostClassifier(CatBoost):
 class CatBoostRegressor(CatBoost):
     _default_loss = "RMSE"
     _estimator_type = "regressor"
+
+    def _default_prediction_type(self):
+        # catboost/python-package/catboost/core.py CatBoostRegressor._get_default_prediction_type: models with a log link
+        # answer on the scale of the target
+        loss = str(self._model.loss_name if self._model is not None else self._init_params.get("loss_function") or "")
+        if loss.startswith("Poisson") or loss.startswith("Tweedie"):
+            return "Exponent"
+        if loss == "RMSEWithUncertainty":
+            return "RMSEWithUncertainty"
+        return "RawFormulaVal"
 
 
 class CatBoostRanker(CatBoost):

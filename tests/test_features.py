@@ -1614,3 +1614,21 @@ def test_custom_multi_dimensional_objectives():
     raw = mc.predict(X, prediction_type="RawFormulaVal")
     assert raw.shape == (n, 3) and (raw.argmax(1) == y).mean() > 0.95
     assert list(mc.evals_result_["learn"]) == ["MultiClass"]
+
+
+def test_default_prediction_types_follow_the_loss():
+    rng = np.random.default_rng(0)
+    X = rng.normal(size=(400, 4)).astype(np.float32)
+    kw = dict(iterations=20, depth=3, verbose=0, allow_writing_files=False)
+    y = rng.poisson(np.exp(0.5 * X[:, 0])).astype(np.float32)
+    r = cb.CatBoostRegressor(loss_function="Poisson", **kw).fit(X, y)
+    assert np.allclose(r.predict(X), np.exp(r.predict(X, prediction_type="RawFormulaVal")))       # log link: Exponent
+    assert r.score(X, y) > 0.2
+    u = cb.CatBoostRegressor(loss_function="RMSEWithUncertainty", **kw).fit(X, X[:, 0])
+    assert u.predict(X).shape == (400, 2) and (u.predict(X)[:, 1] > 0).all()                       # mean and variance
+    Y = np.stack([X[:, 0] > 0, X[:, 1] > 0], 1).astype(np.float32)
+    m = cb.CatBoostClassifier(loss_function="MultiLogloss", **kw).fit(X, Y)
+    p = m.predict(X, prediction_type="MultiProbability")
+    assert p.shape == (400, 2) and ((p > 0.5) == (Y > 0.5)).mean() > 0.9
+    with pytest.raises(cb.CatBoostError):
+        r.predict(X, prediction_type="MultiProbability")
