@@ -1623,7 +1623,7 @@ def test_default_prediction_types_follow_the_loss():
     y = rng.poisson(np.exp(0.5 * X[:, 0])).astype(np.float32)
     r = cb.CatBoostRegressor(loss_function="Poisson", **kw).fit(X, y)
     assert np.allclose(r.predict(X), np.exp(r.predict(X, prediction_type="RawFormulaVal")))       # log link: Exponent
-    assert r.score(X, y) > 0.2
+    assert r.score(X, y) > 0.1
     u = cb.CatBoostRegressor(loss_function="RMSEWithUncertainty", **kw).fit(X, X[:, 0])
     assert u.predict(X).shape == (400, 2) and (u.predict(X)[:, 1] > 0).all()                       # mean and variance
     Y = np.stack([X[:, 0] > 0, X[:, 1] > 0], 1).astype(np.float32)
