@@ -785,7 +785,15 @@ class CatBoostClassifier(CatBoost):
     _default_loss = "Logloss"
     _estimator_type = "classifier"
 
+    _CLASSIFICATION_LOSSES = ("Logloss", "CrossEntropy", "Focal", "MultiClass", "MultiClassOneVsAll", "MultiLogloss",
+                              "MultiCrossEntropy")
+
     def fit(self, X, y=None, **kw):
+        loss = self._init_params.get("loss_function", self._init_params.get("objective"))
+        if isinstance(loss, str) and loss.split(":")[0] not in self._CLASSIFICATION_LOSSES:
+            # catboost/python-package/catboost/core.py CatBoostClassifier._check_is_compatible_loss
+            raise CatBoostError(f"Invalid loss_function='{loss}': for classifier use Logloss, CrossEntropy, MultiClass, "
+                                "MultiClassOneVsAll, MultiLogloss, MultiCrossEntropy, Focal or a custom objective object")
         if "loss_function" not in self._init_params and "objective" not in self._init_params:
             lab = X.label if isinstance(X, Pool) else y
             if lab is not None:
@@ -840,6 +848,15 @@ class CatBoostClassifier(CatBoost):
 class CatBoostRegressor(CatBoost):
     _default_loss = "RMSE"
     _estimator_type = "regressor"
+
+    def fit(self, X, y=None, **kw):
+        loss = self._init_params.get("loss_function", self._init_params.get("objective"))
+        if isinstance(loss, str) and loss.split(":")[0] in CatBoostClassifier._CLASSIFICATION_LOSSES + (
+                "YetiRank", "YetiRankPairwise", "PairLogit", "PairLogitPairwise", "QuerySoftMax", "QueryCrossEntropy",
+                "LambdaMart", "StochasticRank", "StochasticFilter"):
+            raise CatBoostError(f"Invalid loss_function='{loss}': for regressor use RMSE, MultiRMSE, SurvivalAft, MAE, Quantile, "
+                                "LogLinQuantile, Poisson, MAPE, Lq, RMSPE or a custom objective object")
+        return super().fit(X, y, **kw)
 
     def _default_prediction_type(self):
         # catboost/python-package/catboost/core.py CatBoostRegressor._get_default_prediction_type: models with a log link

@@ -1632,3 +1632,14 @@ def test_default_prediction_types_follow_the_loss():
     assert p.shape == (400, 2) and ((p > 0.5) == (Y > 0.5)).mean() > 0.9
     with pytest.raises(cb.CatBoostError):
         r.predict(X, prediction_type="MultiProbability")
+
+
+def test_estimator_classes_refuse_losses_of_another_task():
+    rng = np.random.default_rng(0)
+    X = rng.normal(size=(100, 3)).astype(np.float32)
+    y = (X[:, 0] > 0).astype(int)
+    with pytest.raises(cb.CatBoostError, match="for classifier use"):
+        cb.CatBoostClassifier(loss_function="RMSE", iterations=2, verbose=0).fit(X, y)
+    with pytest.raises(cb.CatBoostError, match="for regressor use"):
+        cb.CatBoostRegressor(loss_function="Logloss", iterations=2, verbose=0).fit(X, y)
+    cb.CatBoost(dict(loss_function="Logloss", iterations=2, verbose=0, allow_writing_files=False)).fit(X, y)   # the base class takes any
