@@ -152,7 +152,13 @@ def _multirmse(a, y, w, p, c):
 
 # ---- binary classification ----------------------------------------------------------------------------------
 def _logloss(a, y, w, p, c):
-    x = a[:, 0]
+    x = np.ascontiguousarray(a[:, 0], dtype=np.float64)
+    if x.size >= 20000:
+        # large batches: the vectorised, threaded softplus (exact in float64 with the linear branch from 40 on)
+        import torch
+        tx = torch.from_numpy(x)
+        v = torch.nn.functional.softplus(tx, threshold=40.0) - torch.from_numpy(np.ascontiguousarray(y, dtype=np.float64)) * tx
+        return float((v * torch.from_numpy(np.ascontiguousarray(w, dtype=np.float64))).sum()) / float(w.sum())
     return np.sum(w * (np.logaddexp(0, x) - y * x)) / w.sum()
 
 
