@@ -1643,3 +1643,35 @@ def test_estimator_classes_refuse_losses_of_another_task():
     with pytest.raises(cb.CatBoostError, match="for regressor use"):
         cb.CatBoostRegressor(loss_function="Logloss", iterations=2, verbose=0).fit(X, y)
     cb.CatBoost(dict(loss_function="Logloss", iterations=2, verbose=0, allow_writing_files=False)).fit(X, y)   # the base class takes any
+
+
+def test_adult_reader_and_grouped_evaluation_folds(tmp_path):
+    from catboost_b200 import datasets
+    from catboost_b200.eval import CatboostEvaluation, ExecutionCase
+    d = tmp_path / "cache" / "adult"
+    d.mkdir(parents=True)
+    (d / "adult.data").write_text("39, State-gov, 77516, Bachelors, 13, Never-married, Adm-clerical, Not-in-family, White, Male, 2174, 0, 40, United-States, <=50K\n"
+                                  "50, ?, 83311, Bachelors, 13, Married-civ-spouse, Exec-managerial, Husband, White, Male, 0, 0, 13, United-States, >50K\n")
+    (d / "adult.test").write_text("|1x3 Cross validator\n"
+                                  "25, Private, 226802, 11th, 7, Never-married, Machine-op-inspct, Own-child, Black, Male, 0, 0, 40, United-States, <=50K.\n")
+    datasets.set_cache_path(tmp_path / "cache")
+    tr, te = datasets.adult()
+    assert list(tr.columns)[:3] == ["age", "workclass", "fnlwgt"] and tr["age"].dtype == float
+    assert tr["workclass"].isna().sum() == 1 and te["income"].iloc[0] == "<=50K"        # '?' is missing; the dot is cut
+    # folds of a grouped pool keep whole groups together
+    rng = np.random.default_rng(0)
+    n = 1200
+    X = rng.normal(size=(n, 4)).astype(np.float32)
+    y = (X[:, 0] + 0.3 * rng.normal(size=n)).astype(np.float32)
+    gid = np.repeat(np.arange(n // 12), 12)
+    pool = cb.Pool(X, y, group_id=gid)
+    ev = CatboostEvaluation(pool, fold_size=240, fold_count=4)
+    folds = ev._folds(pool)
+    assert len(folds) >= 4 and sum(len(f) for f in folds) == n
+    for f in folds:
+        g = gid[f]
+        assert all((gid == v).sum() == (g == v).sum() for v in np.unique(g))
+    base = ExecutionCase({"loss_function": "QueryRMSE", "iterations": 10, "depth": 3}, label="ten")
+    more = ExecutionCase({"loss_function": "QueryRMSE", "iterations": 30, "depth": 3}, label="thirty")
+    table = ev.eval_cases(base, [more], ["QueryRMSE"]).get_metric_results("QueryRMSE").get_baseline_comparison()
+    assert table.loc["thirty", "Score"] > 0
