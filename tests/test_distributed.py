@@ -286,3 +286,24 @@ def test_launcher_hands_the_pool_over_in_shared_memory():
     ref, ref_splits = _single("CPU")
     got_splits = [(s.feature, s.border) for s in res.model.splits]
     assert got_splits == ref_splits
+
+
+def test_gloo_two_ranks_feature_penalties_match_single_process():
+    """Per-object feature penalties count documents over all ranks: two CPU ranks build the trees of one process."""
+    import catboost_b200 as cb
+    from catboost_b200.parallel.launcher import spawn_training
+    rng = np.random.default_rng(5)
+    n = 3000
+    X = rng.standard_normal((n, 5)).astype(np.float32)
+    X[:, 1] = X[:, 0] + 0.05 * rng.standard_normal(n).astype(np.float32)
+    y = (X[:, 0] + 0.5 * X[:, 2] + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    pool = cb.Pool(X, y)
+    for policy in ("SymmetricTree", "Depthwise"):
+        params = dict(iterations=8, depth=3, learning_rate=0.3, verbose=False, allow_writing_files=False, random_strength=0,
+                      bootstrap_type="No", task_type="CPU", border_count=32, loss_function="RMSE", grow_policy=policy,
+                      per_object_feature_penalties={0: 1e-4}, first_feature_use_penalties={2: 1e-3})
+        res = spawn_training(params, pool, [], [0, 1], default_loss="RMSE", backend="gloo")
+        ref = cb.CatBoostRegressor(**params).fit(pool)
+        got = [(s.feature, round(float(s.border), 5)) for s in res.model.splits]
+        want = [(s.feature, round(float(s.border), 5)) for s in ref._model.splits]
+        assert got == want, policy
