@@ -307,3 +307,26 @@ def test_gloo_two_ranks_feature_penalties_match_single_process():
         got = [(s.feature, round(float(s.border), 5)) for s in res.model.splits]
         want = [(s.feature, round(float(s.border), 5)) for s in ref._model.splits]
         assert got == want, policy
+
+
+def test_gloo_two_ranks_survival_and_multi_quantile_match_single_process():
+    import catboost_b200 as cb
+    from catboost_b200.parallel.launcher import spawn_training
+    rng = np.random.default_rng(6)
+    n = 2400
+    X = rng.standard_normal((n, 4)).astype(np.float32)
+    t = np.exp(1.0 + 0.8 * X[:, 0] + 0.2 * rng.standard_normal(n))
+    lo, up = t.copy(), t.copy()
+    up[::3] = -1
+    lo[::3] *= 0.7
+    cases = [("SurvivalAft:dist=Logistic;scale=0.7", np.stack([lo, up], 1).astype(np.float32)),
+             ("MultiQuantile:alpha=0.2,0.8", (X[:, 0] + rng.standard_normal(n)).astype(np.float32))]
+    for loss, y in cases:
+        pool = cb.Pool(X, y)
+        params = dict(iterations=8, depth=3, learning_rate=0.3, verbose=False, allow_writing_files=False, random_strength=0,
+                      bootstrap_type="No", task_type="CPU", border_count=32, loss_function=loss, boost_from_average=False)
+        res = spawn_training(params, pool, [], [0, 1], default_loss="RMSE", backend="gloo")
+        ref = cb.CatBoostRegressor(**params).fit(pool)
+        got = [(s.feature, round(float(s.border), 5)) for s in res.model.splits]
+        want = [(s.feature, round(float(s.border), 5)) for s in ref._model.splits]
+        assert got == want, loss
