@@ -754,7 +754,74 @@ class CatBoost:
         return out, None
 
     def plot_tree(self, tree_idx=0, pool=None):
-        raise CatBoostError("plot_tree needs graphviz, which is not available in this build")
+        """The tree as a graph: a ``graphviz.Source`` when the graphviz package is importable, otherwise an object whose
+        ``source`` attribute (and ``str()``) is the same DOT text (catboost/python-package/catboost/core.py plot_tree).
+        Leaves show their values; inner nodes the condition whose "yes" branch goes right."""
+        self._check_fitted()
+        m = self._model
+        if not 0 <= int(tree_idx) < len(m.trees):
+            raise CatBoostError(f"tree_idx must be in [0, {len(m.trees)})")
+        t = m.trees[int(tree_idx)]
+        fname = {f.feature_index: (f.name or str(f.flat_index)) for f in m.float_features}
+        cname = {c.feature_index: (c.name or str(c.flat_index)) for c in m.cat_features}
+
+        def cond(si):
+            sp = m.splits[int(si)]
+            if sp.kind == "float":
+                return f"{fname.get(sp.feature, sp.feature)}, value > {float(sp.border):.9g}"
+            if sp.kind == "onehot":
+                text = m.cat_hash_to_string.get(int(sp.value), int(sp.value)) if getattr(m, "cat_hash_to_string", None) else int(sp.value)
+                return f"{cname.get(sp.feature, sp.feature)}, value = {text}"
+            c = m.ctrs[sp.feature]
+            cats = ", ".join(str(cname.get(k, k)) for k in c.cat_features)
+            return f"{c.ctr_type} ctr of {{{cats}}}, value > {float(sp.border):.9g}"
+
+        def leaf_text(v):
+            v = np.asarray(v, dtype=np.float64).reshape(-1)
+            return "val = " + (f"{v[0]:.6g}" if v.size == 1 else "[" + ", ".join(f"{x:.4g}" for x in v) + "]")
+
+        lines = ["digraph {", "  node [shape=rectangle];"]
+        from .models.model import ObliviousTree
+        if isinstance(t, ObliviousTree):
+            depth = len(t.splits)
+            # node ids by (level, prefix of the decisions taken so far); the split of level k decides bit k of the leaf index
+            for level in range(depth):
+                for pre in range(1 << level):
+                    lines.append(f'  n{level}_{pre} [label="{cond(t.splits[level])}"];')
+            for leaf in range(1 << depth):
+                lines.append(f'  leaf{leaf} [shape=ellipse, label="{leaf_text(t.leaf_values[leaf])}"];')
+            for level in range(depth):
+                for pre in range(1 << level):
+                    for bit, lab in ((0, "No"), (1, "Yes")):
+                        nxt = pre | (bit << level)
+                        dst = f"leaf{nxt}" if level + 1 == depth else f"n{level + 1}_{nxt}"
+                        lines.append(f'  n{level}_{pre} -> {dst} [label="{lab}"];')
+            if depth == 0:
+                pass
+        else:
+            for node in range(len(t.split_of_node)):
+                if t.split_of_node[node] >= 0:
+                    lines.append(f'  n{node} [label="{cond(t.split_of_node[node])}"];')
+                    lines.append(f'  n{node} -> n{int(t.left[node])} [label="No"];')
+                    lines.append(f'  n{node} -> n{int(t.right[node])} [label="Yes"];')
+                else:
+                    lines.append(f'  n{node} [shape=ellipse, label="{leaf_text(t.leaf_values[int(t.leaf_of_node[node])])}"];')
+        lines.append("}")
+        dot = "\n".join(lines)
+        try:
+            import graphviz
+            return graphviz.Source(dot)
+        except ImportError:
+            class _DotGraph:
+                def __init__(self, source):
+                    self.source = source
+
+                def __str__(self):
+                    return self.source
+
+                def render(self, *a, **k):
+                    raise CatBoostError("rendering needs the graphviz package; the DOT text is in .source")
+            return _DotGraph(dot)
 
     # ------------------------------------------------------------------ search helpers
     def grid_search(self, param_grid, X, y=None, cv=3, partition_random_seed=0, calc_cv_statistics=True,

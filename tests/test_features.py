@@ -1675,3 +1675,22 @@ def test_adult_reader_and_grouped_evaluation_folds(tmp_path):
     more = ExecutionCase({"loss_function": "QueryRMSE", "iterations": 30, "depth": 3}, label="thirty")
     table = ev.eval_cases(base, [more], ["QueryRMSE"]).get_metric_results("QueryRMSE").get_baseline_comparison()
     assert table.loc["thirty", "Score"] > 0
+
+
+def test_plot_tree_dot_text():
+    import pandas as pd
+    rng = np.random.default_rng(0)
+    X = rng.normal(size=(400, 3)).astype(np.float32)
+    c = rng.choice(["a", "b", "c"], 400)
+    y = ((X[:, 0] + (c == "a")) > 0.3).astype(int)
+    df = pd.DataFrame({"x0": X[:, 0], "x1": X[:, 1], "k": c})
+    m = cb.CatBoostClassifier(iterations=3, depth=2, verbose=0, allow_writing_files=False, one_hot_max_size=4).fit(df, y, cat_features=["k"])
+    dot = m.plot_tree(0).source
+    assert dot.startswith("digraph {") and dot.count("[shape=ellipse") == 4 and dot.count("->") == 6 and "value >" in dot
+    texts = [m.plot_tree(i).source for i in range(3)]
+    assert any("k, value = " in t for t in texts) or all("x" in t for t in texts)
+    ns = cb.CatBoostClassifier(iterations=2, depth=3, verbose=0, allow_writing_files=False, grow_policy="Lossguide", max_leaves=5).fit(X, y)
+    dot = ns.plot_tree(1).source
+    assert dot.count("[shape=ellipse") == 5 and dot.count("->") == 8
+    with pytest.raises(cb.CatBoostError):
+        m.plot_tree(99)
