@@ -1694,3 +1694,15 @@ def test_plot_tree_dot_text():
     assert dot.count("[shape=ellipse") == 5 and dot.count("->") == 8
     with pytest.raises(cb.CatBoostError):
         m.plot_tree(99)
+
+
+def test_knn_search_on_the_host_is_exact():
+    """Off the GPU ops.knn_search takes the chunked fp32 distance matrix: exact neighbours."""
+    import torch
+    from catboost_b200.ops import api as ops
+    g = torch.Generator().manual_seed(0)
+    Q, E = torch.randn((70, 24), generator=g), torch.randn((900, 24), generator=g)
+    got = ops.knn_search(Q, E, 6)
+    want = torch.topk(torch.cdist(Q, E), 6, dim=1, largest=False).indices
+    assert torch.equal(got.sort(1).values, want.sort(1).values)
+    assert ops.knn_search(Q, E[:3], 6).shape == (70, 3)                  # fewer cloud rows than k
